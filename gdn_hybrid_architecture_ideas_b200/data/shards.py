@@ -1,0 +1,66 @@
+"""Packs the documents of a shard set into fixed-length training rows.
+
+Each epoch is one permutation of the documents (seeded by (seed, epoch)); documents are laid end to end and cut
+into rows of seq_len + 1 tokens; a document cut by a row boundary continues in the next row under a new document
+id. Row r of the global stream is a pure function of (seed, r), so `rows(first, count)` serves data-parallel slices
+and a resume needs only the step (reference: ced/train/shards.py:92-342 — same contract, own algorithm).
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..config import DataConfig
+from .synthetic import Batch
+
+
+class ShardPacker:
+    def __init__(self, shards, cfg: DataConfig):
+        self.shards, self.cfg = shards, cfg
+        self.n_docs = len(shards)
+        lens = shards.doc_len(np.arange(self.n_docs))
+        self.tokens_per_epoch = int(lens.sum())
+        self.row_tokens = cfg.seq_len + 1
+        self.rows_per_epoch = self.tokens_per_epoch // self.row_tokens
+        if self.rows_per_epoch < 1:
+            raise ValueError("the shard set holds less than one row of tokens")
+        self._epoch = None
+
+    def _load_epoch(self, epoch: int) -> None:
+        if self._epoch == epoch:
+            return
+        rng = np.random.default_rng([self.cfg.seed, epoch])
+        self._perm = rng.permutation(self.n_docs)
+        self._cum = np.concatenate([[0], np.cumsum(self.shards.doc_len(self._perm))])
+        self._epoch = epoch
+
+    def row(self, index: int):
+        """(tokens (L+1,), doc ids (L+1,)) of global row `index`."""
+        epoch, r = divmod(index, self.rows_per_epoch)
+        self._load_epoch(epoch)
+        lo, hi = r * self.row_tokens, (r + 1) * self.row_tokens
+        d = int(np.searchsorted(self._cum, lo, side="right") - 1)
+        toks, docs, at, k = [], [], lo, 0
+        while at < hi:
+            doc = self.shards.doc(int(self._perm[d]))
+            a = at - int(self._cum[d])
+            take = min(len(doc) - a, hi - at)
+            toks.append(doc[a:a + take])
+            docs.append(np.full(take, k, dtype=np.int64))
+            at, d, k = at + take, d + 1, k + 1
+        return np.concatenate(toks).astype(np.int64), np.concatenate(docs)
+
+    def rows(self, first: int, count: int) -> Batch:
+        rows = [self.row(i) for i in range(first, first + count)]
+        seq = torch.from_numpy(np.stack([r[0] for r in rows]))
+        docs = torch.from_numpy(np.stack([r[1] for r in rows]))
+        return Batch(tokens=seq[:, :-1].contiguous(), targets=seq[:, 1:].contiguous(),
+                     target_valid=(docs[:, 1:] == docs[:, :-1]).contiguous(), doc_ids=docs[:, :-1].contiguous())
+
+    def batch(self, step: int, first: int = 0, count: int | None = None) -> Batch:
+        B = self.cfg.batch_size
+        return self.rows(step * B + first, B - first if count is None else count)
+
+    def fingerprint(self) -> str:
+        return self.shards.fingerprint()

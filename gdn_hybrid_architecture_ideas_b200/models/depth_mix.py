@@ -1,0 +1,39 @@
+"""Depth mixing over finished blocks (block-entry attention residuals).
+
+A reader holds a (d,) pseudo-query w and an RMSNorm gain g, both zeros at init, and mixes a list of sources v_i per
+position with weights softmax_i(w . RMSNorm(v_i)) (reference: ced/model/attn_res.py:406-482). With "block_entry" the
+stack is cut into blocks of `full_attn_interval` layers; b_0 is the embedding output and b_n the sum of what block n's
+sublayers added; block n >= 2 starts from the mix over [b_0 .. b_{n-1}] and the model output is the mix over all of
+them (reference: ced/model/attn_res.py:670-797). On CUDA the mix is one kernel that reads every source once.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .norms import RMSNorm
+
+
+class DepthQuery(nn.Module):
+    def __init__(self, d: int, eps: float):
+        super().__init__()
+        self.query = nn.Parameter(torch.zeros(d))
+        self.key_norm = RMSNorm(d, eps)
+
+    def forward(self, sources: list) -> torch.Tensor:
+        if len(sources) == 1:
+            return sources[0]
+        return ops.depth_mix(sources, self.query, self.key_norm.weight, self.key_norm.eps)
+
+
+class EntryLayer(nn.Module):
+    """What a layer that opens or closes a block holds: `entry` (reader of the block's input; first layer of blocks
+    2..N) and `out` (reader of the model output; last layer of the stack)."""
+
+    def __init__(self, d: int, eps: float, entry: bool, closes: bool, last: bool):
+        super().__init__()
+        self.entry = DepthQuery(d, eps) if entry else None
+        self.closes = closes
+        self.out = DepthQuery(d, eps) if last else None

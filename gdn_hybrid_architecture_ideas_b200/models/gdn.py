@@ -1,0 +1,161 @@
+"""Gated DeltaNet mixer.
+
+in_proj_qkv -> causal document-masked conv (K taps) -> SiLU -> split q,k,v -> L2-normalise q,k (q scaled dk^-0.5);
+beta = sigmoid(in_proj_b x); g = -exp(A_log) softplus(in_proj_a x + dt_bias); gated delta rule; out_proj of the gated
+RMSNorm of the readout with z = in_proj_z x. Value head j reads key head j // (Hv/Hk)
+(reference: ced/model/gdn.py:261-375, 599-849).
+
+The write/query depth mixes ("arms", reference: ced/model/gdn_arms.py:809-928) change which input each row range of
+the projections reads: with x_w = x + lambda (m' - x) and x_q = x + lambda_q (m'_q - x), variant "qmix" projects the
+q rows from x_q and the k, v, decay and beta rows from x_w. `project` below holds that routing for every variant.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from ..config import GDNConfig
+from .linear import Linear
+from .norms import GatedRMSNorm
+from .sequence import SeqContext
+
+READ_MIX_VARIANTS = ("qmix", "kqmix")
+
+
+@dataclass
+class GDNState:
+    conv_input: torch.Tensor   # (B, K-1, C) last pre-conv inputs
+    conv_doc: torch.Tensor     # (B, K-1) their document ids (-1: none)
+    S: torch.Tensor | None     # (B, Hv, dk, dv)
+
+
+class GDNArms(nn.Module):
+    """Parameters of one GDN layer's write mix (and, for qmix/kqmix, query mix): lambda scalars and, from the second
+    block on, a depth query over the finished blocks. All zeros at init, so the layer starts as the plain layer."""
+
+    def __init__(self, d: int, eps: float, has_query: bool, variant: str):
+        super().__init__()
+        from .depth_mix import DepthQuery
+
+        self.write_mix = "layer"
+        self.variant = variant
+        self.write_query = DepthQuery(d, eps) if has_query else None
+        self.write_lambda = nn.Parameter(torch.zeros(1))
+        if variant in READ_MIX_VARIANTS:
+            self.qmix_lambda = nn.Parameter(torch.zeros(1))
+            self.qmix_query = DepthQuery(d, eps) if has_query else None
+
+
+class GatedDeltaNet(nn.Module):
+    def __init__(self, d_model: int, cfg: GDNConfig, norm_eps: float, norm_gain: str = "channel"):
+        super().__init__()
+        if cfg.n_v_heads % cfg.n_k_heads:
+            raise ValueError("gdn.n_v_heads must be a multiple of gdn.n_k_heads")
+        self.cfg = cfg
+        hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        self.conv_channels = 2 * hk * dk + hv * dv
+        self.in_proj_qkv = Linear(d_model, self.conv_channels)
+        self.in_proj_z = Linear(d_model, hv * dv)
+        self.in_proj_b = Linear(d_model, hv)
+        self.in_proj_a = Linear(d_model, hv)
+        self.conv_weight = nn.Parameter(torch.empty(self.conv_channels, cfg.conv_kernel))
+        self.A_log = nn.Parameter(torch.empty(hv))
+        self.dt_bias = nn.Parameter(torch.empty(hv))
+        self.norm = GatedRMSNorm(dv, norm_eps, gate=cfg.output_gate, gain=norm_gain)
+        self.out_proj = Linear(hv * dv, d_model)
+        self.reset_gate_parameters(cfg.init)
+        bound = 1.0 / math.sqrt(cfg.conv_kernel)
+        nn.init.uniform_(self.conv_weight, -bound, bound)
+        self.write_mix = "none"
+
+    @torch.no_grad()
+    def reset_gate_parameters(self, scheme: str) -> None:
+        """"fla": A ~ U(0,16), dt ~ logU(1e-3, 1e-1) clamped at 1e-4, dt_bias = softplus^-1(dt);
+        "hf": A ~ U(0.01, 16), dt_bias = 1 (reference: ced/model/gdn.py:375-399)."""
+        hv = self.cfg.n_v_heads
+        if scheme == "fla":
+            A = torch.empty(hv).uniform_(0, 16)
+            dt = torch.exp(torch.rand(hv) * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3)).clamp(min=1e-4)
+            bias = dt + torch.log(-torch.expm1(-dt))
+        elif scheme == "hf":
+            A = torch.empty(hv).uniform_(0.01, 16)
+            bias = torch.ones(hv)
+        else:
+            raise ValueError(f"unknown GDN init scheme {scheme!r}")
+        self.A_log.copy_(torch.log(A))
+        self.dt_bias.copy_(bias)
+
+    # ------------------------------------------------------------------ projections
+
+    def project(self, x, arms: GDNArms | None, x_write, x_read):
+        """(u_pre, a_lin, b_lin): the pre-conv in-projection and the decay / beta pre-activations, each row range
+        reading the input its variant assigns."""
+        hk, dk = self.cfg.n_k_heads, self.cfg.k_head_dim
+        nq, C = hk * dk, self.conv_channels
+        if arms is None:
+            return self.in_proj_qkv(x), self.in_proj_a(x), self.in_proj_b(x)
+        wd = torch.promote_types(x.dtype, torch.float32)
+        xw = torch.addcmul(x.to(wd), (x_write.to(wd) - x.to(wd)), arms.write_lambda.to(wd))
+        xw = ops_cast(xw, x)
+        W = self.in_proj_qkv
+        v = arms.variant
+        if v in READ_MIX_VARIANTS:
+            xr = torch.addcmul(x.to(wd), (x_read.to(wd) - x.to(wd)), arms.qmix_lambda.to(wd))
+            xr = ops_cast(xr, x)
+        if v == "none":
+            u = torch.cat([W.rows(0, nq)(x), W.rows(nq, C)(xw)], dim=-1)
+        elif v == "qmix":
+            u = torch.cat([W.rows(0, nq)(xr), W.rows(nq, C)(xw)], dim=-1)
+        elif v == "kqmix":
+            u = torch.cat([W.rows(0, 2 * nq)(xr), W.rows(2 * nq, C)(xw)], dim=-1)
+        elif v == "korig":
+            u = torch.cat([W.rows(0, 2 * nq)(x), W.rows(2 * nq, C)(xw)], dim=-1)
+        elif v == "vonly":
+            u = torch.cat([W.rows(0, 2 * nq)(x), W.rows(2 * nq, C)(xw)], dim=-1)
+            return u, self.in_proj_a(x), self.in_proj_b(x)
+        elif v == "qshare":
+            u = W(xw)
+        elif v == "qshare_kv":
+            return W(xw), self.in_proj_a(x), self.in_proj_b(x)
+        elif v == "qshare_bd":
+            u = torch.cat([W.rows(0, nq)(xw), W.rows(nq, C)(x)], dim=-1)
+        else:
+            raise ValueError(f"gdn_write_variant {v!r}")
+        return u, self.in_proj_a(xw), self.in_proj_b(xw)
+
+    # ------------------------------------------------------------------ forward
+
+    def forward(self, x: torch.Tensor, ctx: SeqContext, state: GDNState | None = None, arms: GDNArms | None = None,
+                x_write: torch.Tensor | None = None, x_read: torch.Tensor | None = None, need_state: bool = True):
+        """x (B, L, d) normed layer input. Returns (y, GDNState). state: the cache of earlier chunks (None: the row
+        starts here). need_state False (training) lets the kernel skip the final state."""
+        if (arms is None) != (self.write_mix == "none"):
+            raise ValueError("a GDN layer with write/query mixes is called with its arms (through its encoder layer)")
+        B, L, _ = x.shape
+        cfg = self.cfg
+        hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        u_pre, a_lin, b_lin = self.project(x, arms, x_write, x_read)
+        hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
+        q, k, v, conv_input, conv_doc = ops.gdn_prep(u_pre, ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
+                                                     single_doc=ctx.single_doc)
+        g, beta = ops.gdn_gates(a_lin, b_lin, self.A_log, self.dt_bias, ctx.gdn_scale, ctx.gdn_beta_power)
+        S0 = None if state is None else state.S
+        kernel = "recurrence" if cfg.kernel == "recurrence" else "chunked"
+        o, S = ops.delta_rule(q, k, v, g, beta, ctx.is_doc_start, S0, kernel=kernel, chunk_size=cfg.chunk_size,
+                              need_state=need_state)
+        z = self.in_proj_z(x).view(B, L, hv, dv)
+        y = self.out_proj(self.norm(o, z).flatten(2))
+        return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)
+
+
+def ops_cast(t: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    """t in the dtype projections compute in: autocast's when it is on, else `like`'s own."""
+    dev = t.device.type
+    if torch.is_autocast_enabled(dev):
+        return t.to(torch.get_autocast_dtype(dev))
+    return t.to(like.dtype)

@@ -1,0 +1,113 @@
+"""Op layer: every model op has a pure-PyTorch statement (`ops.reference`) and, for CUDA tensors, a hand-written
+sm_100a kernel behind a `torch.autograd.Function` (`ops.native`).
+
+Dispatch rule: a CUDA input runs the native kernel unless the process set `GHB_KERNELS=reference` (debug switch, used
+to produce oracle values on the GPU). A CUDA input with the extension missing raises: there is no silent fallback.
+CPU inputs always run the reference statement (the gloo/CPU path and the tests' oracle).
+"""
+
+from __future__ import annotations
+
+import os
+
+import torch
+
+from . import reference as ref
+
+_MODE = os.environ.get("GHB_KERNELS", "native")
+
+
+def set_mode(mode: str) -> None:
+    """"native" (default) or "reference": which implementation CUDA tensors use."""
+    global _MODE
+    assert mode in ("native", "reference"), mode
+    _MODE = mode
+
+
+def mode() -> str:
+    return _MODE
+
+
+def use_native(x: torch.Tensor) -> bool:
+    return x.is_cuda and _MODE == "native"
+
+
+def _native():
+    from . import native
+    return native
+
+
+def rmsnorm(x, weight, eps, out_dtype=None):
+    if use_native(x):
+        return _native().rmsnorm(x, weight, eps, out_dtype)
+    return ref.rmsnorm(x, weight, eps, out_dtype)
+
+
+def gated_rmsnorm(x, z, weight, eps, gate, out_dtype=None):
+    if use_native(x):
+        return _native().gated_rmsnorm(x, z, weight, eps, gate, out_dtype)
+    return ref.gated_rmsnorm(x, z, weight, eps, gate, out_dtype)
+
+
+def linear(x, lin):
+    if use_native(x):
+        return _native().linear(x, lin)
+    if getattr(lin, "precision", "bf16") != "bf16" and lin.training:
+        return lin.lowp.emulated_linear(x, lin.weight)
+    return ref.linear(x, lin)
+
+
+def swiglu_mlp(x, w_gate, w_up, w_down):
+    if use_native(x):
+        return _native().swiglu_mlp(x, w_gate, w_up, w_down)
+    return linear(torch.nn.functional.silu(linear(x, w_gate)) * linear(x, w_up), w_down)
+
+
+def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist=None, hist_doc=None, single_doc=False):
+    if use_native(u_pre) and hist is None:
+        return _native().gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc)
+    return ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist, hist_doc)
+
+
+def gdn_gates(a_lin, b_lin, A_log, dt_bias, scale=1, beta_power=False):
+    if use_native(a_lin) and scale == 1:
+        return _native().gdn_gates(a_lin, b_lin, A_log, dt_bias)
+    return ref.gdn_gates(a_lin, b_lin, A_log, dt_bias, scale, beta_power)
+
+
+def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=64, need_state=True):
+    """(o, S_final). q,k (B,L,Hk,dk) with Hv a multiple of Hk: value head j reads key head j // (Hv/Hk)."""
+    if use_native(q) and q.shape[1] > 1:
+        return _native().delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state)
+    rep = v.shape[2] // q.shape[2]
+    if rep > 1:
+        q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
+    if S0 is None:
+        S0 = q.new_zeros(q.shape[0], v.shape[2], q.shape[-1], v.shape[-1])
+    if kernel == "recurrence" or q.shape[1] == 1:
+        return ref.delta_rule_recurrence(q, k, v, g, beta, is_doc_start, S0)
+    return ref.chunked_delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size)
+
+
+def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=None, cap=None, self_aligned=False):
+    """self_aligned: queries and keys are the same positions of the same rows (a training forward without a cache),
+    which is the case the fused training kernel covers."""
+    if use_native(q) and self_aligned:
+        return _native().attention(q, k, v, q_doc, q_far, k_far, cap)
+    return ref.attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok, q_far, k_far, cap)
+
+
+def depth_mix(sources, query, gain, eps):
+    if use_native(sources[0]):
+        return _native().depth_mix(sources, query, gain, eps)
+    return ref.depth_mix(sources, query, gain, eps)
+
+
+def embedding(tokens, weight):
+    return ref.embedding(tokens, weight)
+
+
+def lm_loss_sums(hidden, weight, targets, weights=None, z_loss=0.0, weight_lp=None):
+    if use_native(hidden):
+        return _native().lm_loss_sums(hidden, weight, targets, weights, z_loss, weight_lp)
+    return ref.lm_loss_sums(hidden, weight, targets, weights, z_loss)

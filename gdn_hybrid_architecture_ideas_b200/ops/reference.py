@@ -1,0 +1,260 @@
+"""Pure-PyTorch statement of every op of the model: the numerical oracle of the CUDA kernels and the CPU path.
+
+Each function here defines WHAT the corresponding sm_100a kernel computes; kernels are tested against these in
+float32/float64. Dtype rule throughout: reductions, softmaxes and norms run in at least float32 (float64 inputs stay
+float64) and results return in the input dtype unless `out_dtype` says otherwise.
+"""
+
+from __future__ import annotations
+
+import math
+from functools import reduce
+
+import torch
+import torch.nn.functional as F
+
+
+def work_dtype(x: torch.Tensor) -> torch.dtype:
+    return torch.promote_types(x.dtype, torch.float32)
+
+
+# ------------------------------------------------------------------------------------------------ norms
+
+def rmsnorm(x, weight, eps, out_dtype=None):
+    """y = x rsqrt(mean x^2 + eps) (1 + w) (reference: ced/model/norms.py:70-74)."""
+    dt = work_dtype(x)
+    xf = x.to(dt)
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * (1.0 + weight.to(dt))).to(out_dtype or x.dtype)
+
+
+def gated_rmsnorm(x, z, weight, eps, gate, out_dtype=None):
+    """rmsnorm(x) * act(z), act SiLU or sigmoid, the product formed in the inputs' dtype
+    (reference: ced/model/norms.py:77-94)."""
+    act = F.silu(z) if gate == "silu" else torch.sigmoid(z)
+    y = rmsnorm(x, weight, eps) * act
+    return y.to(out_dtype) if out_dtype is not None else y
+
+
+# ------------------------------------------------------------------------------------------------ GEMMs
+
+def linear(x, lin):
+    return F.linear(x, lin.weight)
+
+
+def swiglu_mlp(x, w_gate, w_up, w_down):
+    return linear(F.silu(linear(x, w_gate)) * linear(x, w_up), w_down)
+
+
+# ------------------------------------------------------------------------------------------------ GDN
+
+def l2_normalize(x, eps: float = 1e-6):
+    return x * torch.rsqrt(x.pow(2).sum(-1, keepdim=True) + eps)
+
+
+def causal_doc_conv(u, doc, weight, hist=None, hist_doc=None):
+    """Depthwise causal conv over [history ; u] that only reads taps of the position's own document.
+
+    u (B, L, C); doc (B, L); weight (C, K) with weight[:, K-1] on the current input; hist (B, K-1, C) and
+    hist_doc (B, K-1) from earlier chunks (None: zeros / id -1). Returns (out, new_hist, new_hist_doc)
+    (reference: ced/model/gdn.py:222-258)."""
+    B, L, C = u.shape
+    K = weight.shape[1]
+    if hist is None:
+        hist = u.new_zeros(B, K - 1, C)
+        hist_doc = torch.full((B, K - 1), -1, dtype=torch.long, device=u.device)
+    full = torch.cat([hist.to(u.dtype), u], dim=1)
+    full_doc = torch.cat([hist_doc, doc], dim=1)
+    out = torch.zeros_like(u)
+    for back in range(K):
+        lo = K - 1 - back
+        same = (full_doc[:, lo:lo + L] == doc).to(u.dtype)
+        out = out + full[:, lo:lo + L] * same[..., None] * weight[:, K - 1 - back].to(u.dtype)
+    return out, full[:, L:], full_doc[:, L:]
+
+
+def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist=None, hist_doc=None):
+    """conv (K taps, document-masked) -> SiLU -> split -> L2-normalise q and k, scale q by dk^-0.5.
+    Returns q (B,L,hk,dk), k (B,L,hk,dk), v (B,L,hv,dv), new conv history and its document ids
+    (reference: ced/model/gdn.py:692-699)."""
+    B, L, _ = u_pre.shape
+    u, h, hd = causal_doc_conv(u_pre, doc, conv_weight, hist, hist_doc)
+    u = F.silu(u)
+    q, k, v = torch.split(u, [hk * dk, hk * dk, hv * dv], dim=-1)
+    q = l2_normalize(q.view(B, L, hk, dk)) * dk ** -0.5
+    k = l2_normalize(k.view(B, L, hk, dk))
+    return q, k, v.view(B, L, hv, dv), h, hd
+
+
+def gdn_gates(a_lin, b_lin, A_log, dt_bias, scale: int = 1, beta_power: bool = False):
+    """g = -exp(A_log) softplus(a + dt_bias) (log decay per step), beta = sigmoid(b); with `scale` s a position
+    stands for s tokens: g *= s and, with beta_power, beta = 1 - (1 - sigmoid(b))^s
+    (reference: ced/model/gdn.py:506-547)."""
+    g = -torch.exp(A_log) * F.softplus(a_lin + dt_bias)
+    if scale != 1:
+        g = g * scale
+    if scale != 1 and beta_power:
+        bf = b_lin.to(work_dtype(b_lin))
+        beta = (-torch.expm1(-scale * F.softplus(bf))).to(b_lin.dtype)
+    else:
+        beta = torch.sigmoid(b_lin)
+    return g, beta
+
+
+def delta_rule_recurrence(q, k, v, g, beta, is_doc_start, S):
+    """Gated delta rule one token at a time (the ground truth): per token reset at a document start,
+    S *= exp(g); S += k (x) beta (v - S^T k); o = S^T q. q,k (B,L,H,dk); v (B,L,H,dv); g,beta (B,L,H);
+    S (B,H,dk,dv) (reference: ced/model/gdn.py:1153-1189)."""
+    outs = []
+    for q_t, k_t, v_t, g_t, b_t, s_t in zip(q.unbind(1), k.unbind(1), v.unbind(1), g.unbind(1), beta.unbind(1),
+                                            is_doc_start.unbind(1)):
+        S = S * (~s_t).to(S.dtype)[:, None, None, None]
+        S = S * torch.exp(g_t)[:, :, None, None]
+        pred = torch.einsum("bhkv,bhk->bhv", S, k_t)
+        S = S + torch.einsum("bhk,bhv->bhkv", k_t, b_t[:, :, None] * (v_t - pred))
+        outs.append(torch.einsum("bhkv,bhk->bhv", S, q_t))
+    return torch.stack(outs, dim=1), S
+
+
+def chunk_local(q, k, v, g, beta, is_doc_start, C):
+    """Everything of the chunked delta rule that does not depend on the carried state, for all chunks at once.
+
+    Inputs as delta_rule_recurrence's, L a multiple of C. Returns a dict of (B,H,n,C,...) tensors:
+      U (.., dv) = (I+A)^-1 beta v;  W (.., dk) = (I+A)^-1 beta gamma k [first segment only];
+      Aqk (.., C) = q_i.k_j exp(c_i-c_j) for j<=i in one document;  q_in = q gamma [first segment];
+      k_out = k exp(c_last - c_j) [last segment];  carry (B,H,n) = gamma_last if the chunk has no document start else 0.
+    These are exactly the operands of the sequential state pass (`chunk_scan`). Documents inside a chunk are handled
+    by segment masks, so shapes never depend on where documents start (reference: ced/model/gdn_chunked.py:71-140)."""
+    B, L, H, dk = q.shape
+    n = L // C
+    wd = reduce(torch.promote_types, (t.dtype for t in (q, k, v, g, beta)), torch.float32)
+
+    def heads(x):
+        x = x.to(wd).transpose(1, 2)
+        return x.reshape(B, H, n, C, *x.shape[3:])
+
+    q, k, v, g, beta = map(heads, (q, k, v, g, beta))
+    seg = is_doc_start.to(torch.long).reshape(B, 1, n, C).cumsum(-1)
+    tril = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+    pair = (seg[..., :, None] == seg[..., None, :]) & tril
+    first = (seg == 0).to(wd)
+    last = (seg == seg[..., -1:]).to(wd)
+    zero = torch.zeros((), dtype=wd, device=q.device)
+    c = g.cumsum(-1)
+    strict = tril.tril(-1)
+    pexp = torch.where(strict, g[..., :, None].expand(*g.shape, C), zero).cumsum(-2)   # c_i - c_j, summed directly
+    decay = torch.where(pair, torch.exp(torch.where(pair, pexp, zero)), zero)
+    gamma = torch.exp(c)
+    to_end = torch.exp(pexp[..., -1, :])
+    kb = k * beta[..., None]
+    A = (kb @ k.transpose(-1, -2)) * torch.where(strict, decay, zero)
+    eye = torch.eye(C, dtype=wd, device=q.device)
+    rhs = torch.cat([v * beta[..., None], kb * (gamma * first)[..., None]], dim=-1)
+    sol = torch.linalg.solve_triangular(eye + A, rhs, upper=False, unitriangular=True)
+    U, W = sol.split([v.shape[-1], dk], dim=-1)
+    return dict(U=U, W=W, Aqk=(q @ k.transpose(-1, -2)) * decay, q_in=q * (gamma * first)[..., None],
+                k_out=k * (to_end * last)[..., None], carry=gamma[..., -1] * (seg[..., -1] == 0).to(wd))
+
+
+def chunk_scan(parts, S):
+    """The sequential pass over chunks: v_new = U - W S; o = q_in S + Aqk v_new; S = carry S + k_out^T v_new.
+    Returns o (B,H,n,C,dv) and the final state (reference: ced/model/gdn_chunked.py:142-160)."""
+    outs = []
+    for U, W, qi, Aqk, ko, cy in zip(*(parts[n].unbind(2) for n in ("U", "W", "q_in", "Aqk", "k_out", "carry"))):
+        vn = U - W @ S
+        outs.append(qi @ S + Aqk @ vn)
+        S = S * cy[..., None, None] + ko.transpose(-1, -2) @ vn
+    return torch.stack(outs, dim=2), S
+
+
+def chunked_delta_rule(q, k, v, g, beta, is_doc_start, S, chunk_size: int = 64):
+    """delta_rule_recurrence computed chunk by chunk (WY / UT-transform form, arXiv 2412.06464 section 3.3)."""
+    B, L, H, dk = q.shape
+    out_dt = reduce(torch.promote_types, (t.dtype for t in (q, k, v, g, beta, S)))
+    C = min(chunk_size, L)
+    pad = (-L) % C
+    if pad:
+        q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+        g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
+        is_doc_start = F.pad(is_doc_start, (0, pad))
+    parts = chunk_local(q, k, v, g, beta, is_doc_start, C)
+    o, S = chunk_scan(parts, S.to(parts["U"].dtype))
+    o = o.reshape(B, H, L + pad, -1)[:, :, :L].transpose(1, 2)
+    return o.to(out_dt), S.to(out_dt)
+
+
+# ------------------------------------------------------------------------------------------------ attention
+
+def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=None, cap=None, return_lse=False):
+    """Causal, document-masked softmax attention with grouped KV heads and an optional rotary distance cap.
+
+    q (B,Lq,Hq,hd) and k,v (B,S,Hkv,hd), Hq a multiple of Hkv (KV head j serves query heads j*g .. (j+1)*g-1).
+    A key is allowed iff k_ok, k_idx <= q_idx and k_doc == q_doc. With a cap C, a pair with q_idx - k_idx > C is
+    scored q_far . k_far (query rotated by C against the unrotated key) instead of q . k. One softmax in >= float32,
+    scale hd^-0.5 (reference: ced/model/attention.py:227-260, 519-553)."""
+    hq, hkv = q.shape[2], k.shape[2]
+    rep = hq // hkv
+    dt = work_dtype(q)
+    scale = q.shape[-1] ** -0.5
+    allow = (k_idx[:, None, :] <= q_idx[:, :, None]) & (k_doc[:, None, :] == q_doc[:, :, None])
+    if k_ok is not None:
+        allow = allow & k_ok[:, None, :]
+    kk = k.repeat_interleave(rep, dim=2).to(dt)
+    vv = v.repeat_interleave(rep, dim=2).to(dt)
+    s = torch.einsum("bqhd,bshd->bhqs", q.to(dt), kk) * scale
+    if cap is not None:
+        far = (q_idx[:, :, None] - k_idx[:, None, :]) > cap
+        sf = torch.einsum("bqhd,bshd->bhqs", q_far.to(dt), k_far.repeat_interleave(rep, dim=2).to(dt)) * scale
+        s = torch.where(far[:, None], sf, s)
+    s = s.masked_fill(~allow[:, None], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    o = torch.einsum("bhqs,bshd->bqhd", p, vv).to(q.dtype)
+    if return_lse:
+        return o, torch.logsumexp(s, dim=-1)
+    return o
+
+
+# ------------------------------------------------------------------------------------------------ depth mix
+
+def depth_mix(sources, query, gain, eps, return_weights=False):
+    """Per position, h = sum_i softmax_i(w . RMSNorm(v_i)) v_i over the sources v_i (B,L,d), with the logit formed
+    without a normalised copy: (v @ (w (1+g))) rsqrt(mean v^2 + eps); >= float32, autocast off
+    (reference: ced/model/attn_res.py:457-482)."""
+    v0 = sources[0]
+    dt = work_dtype(v0)
+    with torch.autocast(v0.device.type, enabled=False):
+        u = query.to(dt) * (1.0 + gain.to(dt))
+        logits = [(v.to(dt) @ u) * torch.rsqrt(v.to(dt).pow(2).mean(-1) + eps) for v in sources]
+        alpha = torch.softmax(torch.stack(logits, dim=-1), dim=-1)
+        h = alpha[..., 0:1] * v0.to(dt)
+        for i in range(1, len(sources)):
+            h = h + alpha[..., i:i + 1] * sources[i].to(dt)
+    h = h.to(v0.dtype)
+    return (h, alpha) if return_weights else h
+
+
+# ------------------------------------------------------------------------------------------------ loss
+
+def lm_loss_sums(hidden, weight, targets, weights=None, z_loss: float = 0.0):
+    """Sum over positions of weight * (CE + z_loss * lse^2) with fp32 logits, and the plain CE sum.
+    hidden (N,d), weight (V,d), targets (N,) (or (N,s) with weights (N,s) for bags); a target < 0 is ignored
+    (reference: ced/train/loss.py:20-58, ced/train/fused_head.py:56-66)."""
+    dt = work_dtype(hidden)
+    logits = F.linear(hidden.to(dt), weight.to(dt))
+    lse = torch.logsumexp(logits, dim=-1)
+    if targets.dim() == 1:
+        targets, weights = targets[:, None], (torch.ones_like(targets, dtype=dt)[:, None] if weights is None else weights[:, None])
+    valid = targets >= 0
+    picked = logits.gather(1, targets.clamp(min=0))
+    w = weights.to(dt) * valid.to(dt)
+    ce = ((lse[:, None] - picked) * w).sum()
+    wsum = w.sum(1)
+    total = ce + z_loss * (lse.pow(2) * wsum).sum()
+    return total, ce
+
+
+def embedding(tokens, weight):
+    """Rows of `weight`; bags (B,L,s) give the mean of their s rows in the table's dtype
+    (reference: ced/model/control.py:436-455)."""
+    e = F.embedding(tokens, weight)
+    return e.mean(dim=2) if tokens.dim() == 3 else e

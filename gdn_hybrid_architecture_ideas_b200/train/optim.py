@@ -1,0 +1,228 @@
+"""Optimizer construction: parameter groups by name, flat parameter / gradient / moment buffers, AdamW over them.
+
+Group rules (reference: ced/train/optim.py:198-470): no weight decay for the token embedding (= the tied head),
+`A_log`, `dt_bias`; with `optim.zero_gate_decay: none` also the zero-initialised mix lambdas; with
+`optim.mix_query_decay` the named depth-mix pseudo-queries. Under `optim.name: muon` 2-D hidden matrices go to Muon
+and everything else (embeddings, norm gains, conv, gates, in_proj_a/b, depth readers) to AdamW.
+
+Layout: every parameter is a view into ONE flat float32 master buffer (64-element aligned), its gradient a view into
+one flat float32 gradient buffer, and — on CUDA — its bfloat16 compute copy a view into one flat bfloat16 buffer that
+the update kernel refreshes in the same pass that applies AdamW. Flat buffers are what the data-parallel collectives
+and the fused reduce-scatter + update kernels operate on; their element ranges are the ZeRO shards.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias")
+ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda")
+MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
+                   "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
+ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight")
+ALIGN = 64
+
+
+def no_decay_suffixes(o) -> tuple:
+    if o.zero_gate_decay not in ("decay", "none"):
+        raise ValueError(f"optim.zero_gate_decay {o.zero_gate_decay!r}: 'decay' or 'none'")
+    if o.mix_query_decay not in MIX_QUERY_DECAY:
+        raise ValueError(f"optim.mix_query_decay {o.mix_query_decay!r}: one of {list(MIX_QUERY_DECAY)}")
+    extra = ZERO_GATE_SUFFIXES if o.zero_gate_decay == "none" else ()
+    return NO_DECAY_SUFFIXES + extra + MIX_QUERY_DECAY[o.mix_query_decay]
+
+
+def is_muon_param(name: str, p: torch.Tensor) -> bool:
+    if p.ndim != 2 or name.endswith(("embed.weight", "conv_weight") + ADAMW_MATRIX_SUFFIXES):
+        return False
+    return ".attn_res." not in name
+
+
+def param_groups(model, o) -> list[dict]:
+    """Groups as dicts {"names", "params", "weight_decay", "lr_scale", "kind"}; kind "adamw" or "muon"."""
+    suffixes = no_decay_suffixes(o)
+    named = list(model.named_parameters())
+    if o.name == "adamw":
+        decay = [(n, p) for n, p in named if not n.endswith(suffixes)]
+        plain = [(n, p) for n, p in named if n.endswith(suffixes)]
+        spec = [("adamw", decay, o.weight_decay, 1.0), ("adamw", plain, 0.0, 1.0)]
+    elif o.name == "muon":
+        mats = [(n, p) for n, p in named if is_muon_param(n, p)]
+        rest = [(n, p) for n, p in named if not is_muon_param(n, p)]
+        decay = [(n, p) for n, p in rest if not n.endswith(suffixes)]
+        plain = [(n, p) for n, p in rest if n.endswith(suffixes)]
+        spec = [("muon", mats, o.weight_decay, 1.0), ("adamw", decay, o.weight_decay, o.adamw_lr_scale),
+                ("adamw", plain, 0.0, o.adamw_lr_scale)]
+    else:
+        raise ValueError(f"optim.name {o.name!r}: 'adamw' or 'muon'")
+    return [{"kind": k, "names": [n for n, _ in items], "params": [p for _, p in items], "weight_decay": wd, "lr_scale": s}
+            for k, items, wd, s in spec if items]
+
+
+@dataclass
+class Segment:
+    name: str
+    offset: int
+    numel: int
+    shape: tuple
+    group: int
+
+
+class FlatBuffers:
+    """The model's parameters re-homed into flat buffers, group by group (each group one contiguous range)."""
+
+    def __init__(self, model, groups: list[dict], device, lp_dtype=None):
+        self.segments: list[Segment] = []
+        self.group_ranges: list[tuple[int, int]] = []
+        at = 0
+        for gi, g in enumerate(groups):
+            lo = at
+            for n, p in zip(g["names"], g["params"]):
+                self.segments.append(Segment(n, at, p.numel(), tuple(p.shape), gi))
+                at += -(-p.numel() // ALIGN) * ALIGN
+            self.group_ranges.append((lo, at))
+        self.size = -(-at // 1024) * 1024
+        self.params = torch.zeros(self.size, dtype=torch.float32, device=device)
+        self.grads = torch.zeros(self.size, dtype=torch.float32, device=device)
+        self.lp = torch.zeros(self.size, dtype=lp_dtype, device=device) if lp_dtype is not None else None
+        by_name = dict(model.named_parameters())
+        self.by_name = {}
+        for s in self.segments:
+            p = by_name[s.name]
+            view = self.params[s.offset:s.offset + s.numel].view(s.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
+            self.by_name[s.name] = s
+        if self.lp is not None:
+            self.refresh_lp()
+            mods = dict(model.named_modules())
+            for s in self.segments:
+                owner, _, leaf = s.name.rpartition(".")
+                m = mods.get(owner)
+                if leaf == "weight" and hasattr(m, "weight_lp"):
+                    m.weight_lp = self.lp[s.offset:s.offset + s.numel].view(s.shape)
+            head = "embed.weight" if model.out_embed is None else "out_embed.weight"
+            s = self.by_name[head]
+            model.head_weight_lp = self.lp[s.offset:s.offset + s.numel].view(s.shape)
+
+    def refresh_lp(self) -> None:
+        if self.lp is not None:
+            self.lp.copy_(self.params)
+
+    def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
+        s = self.by_name[name]
+        return flat[s.offset:s.offset + s.numel].view(s.shape)
+
+    def rebind_grads(self, model) -> None:
+        """Point every parameter's .grad at its flat view again (after something set it to None)."""
+        for n, p in model.named_parameters():
+            p.grad = self.view(self.grads, n)
+
+
+class FlatAdamW:
+    """AdamW on flat buffers with decoupled weight decay, bias correction as torch.optim.AdamW.
+
+    shard (lo, hi): the element range this rank updates (ZeRO); moments exist for that range only. On CUDA the update
+    of a group is one launch of the fused kernel (moments, master weight and bf16 copy in one pass)."""
+
+    def __init__(self, flat: FlatBuffers, groups: list[dict], betas, eps: float, shard: tuple[int, int] | None = None):
+        self.flat, self.groups = flat, groups
+        self.betas, self.eps = tuple(betas), eps
+        self.lo, self.hi = shard or (0, flat.size)
+        n = self.hi - self.lo
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=flat.params.device)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=flat.params.device)
+        self.steps = 0
+        self.param_groups = [{"lr": 0.0, "lr_scale": g["lr_scale"], "weight_decay": g["weight_decay"], "kind": g["kind"]}
+                             for g in groups]
+
+    def owned(self, gi: int) -> tuple[int, int]:
+        glo, ghi = self.flat.group_ranges[gi]
+        return max(glo, self.lo), min(ghi, self.hi)
+
+    @torch.no_grad()
+    def step(self, lr: float, grad_scale: torch.Tensor | float = 1.0, kinds=("adamw",)) -> None:
+        """One update at learning rate lr (times each group's lr_scale). grad_scale multiplies the gradient first
+        (the clip coefficient; a 0-dim device tensor avoids a host sync)."""
+        self.steps += 1
+        b1, b2 = self.betas
+        c1, c2 = 1.0 - b1 ** self.steps, 1.0 - b2 ** self.steps
+        for gi, g in enumerate(self.param_groups):
+            g["lr"] = lr * g["lr_scale"]
+            if g["kind"] not in kinds:
+                continue
+            a, b = self.owned(gi)
+            if b <= a:
+                continue
+            p, gr = self.flat.params[a:b], self.flat.grads[a:b]
+            m, v = self.exp_avg[a - self.lo:b - self.lo], self.exp_avg_sq[a - self.lo:b - self.lo]
+            lp = None if self.flat.lp is None else self.flat.lp[a:b]
+            if p.is_cuda:
+                from ..ops import native
+
+                native.adamw_(p, gr, m, v, lp, g["lr"], b1, b2, self.eps, g["weight_decay"], c1, c2, grad_scale)
+                continue
+            gs = gr * grad_scale
+            p.mul_(1.0 - g["lr"] * g["weight_decay"])
+            m.lerp_(gs, 1.0 - b1)
+            v.mul_(b2).addcmul_(gs, gs, value=1.0 - b2)
+            p.addcdiv_(m, (v / c2).sqrt_().add_(self.eps), value=-g["lr"] / c1)
+            if lp is not None:
+                lp.copy_(p)
+
+    # ---- torch.optim-shaped state for checkpoints (reference: ced/train/trainer.py:3602-3627 saves optimizer.state_dict())
+    def state_dict(self) -> dict:
+        state, index = {}, 0
+        packed_groups = []
+        for gi, g in enumerate(self.param_groups):
+            ids = []
+            for s in (s for s in self.flat.segments if s.group == gi):
+                if g["kind"] == "adamw" and s.offset >= self.lo and s.offset + s.numel <= self.hi:
+                    a = s.offset - self.lo
+                    state[index] = {"step": torch.tensor(float(self.steps)),
+                                    "exp_avg": self.exp_avg[a:a + s.numel].view(s.shape).clone(),
+                                    "exp_avg_sq": self.exp_avg_sq[a:a + s.numel].view(s.shape).clone()}
+                ids.append(index)
+                index += 1
+            packed_groups.append({**g, "betas": self.betas, "eps": self.eps, "params": ids})
+        return {"state": state, "param_groups": packed_groups, "names": [s.name for s in self.flat.segments]}
+
+    def load_state_dict(self, sd: dict) -> None:
+        names = sd.get("names") or [s.name for s in self.flat.segments]
+        for index, name in enumerate(names):
+            st = sd["state"].get(index)
+            s = self.flat.by_name.get(name)
+            if st is None or s is None or s.offset < self.lo or s.offset + s.numel > self.hi:
+                continue
+            a = s.offset - self.lo
+            self.exp_avg[a:a + s.numel].copy_(st["exp_avg"].reshape(-1))
+            self.exp_avg_sq[a:a + s.numel].copy_(st["exp_avg_sq"].reshape(-1))
+            self.steps = int(st["step"])
+
+    def reset_moments(self) -> None:
+        self.exp_avg.zero_()
+        self.exp_avg_sq.zero_()
+        self.steps = 0
+
+
+def grad_norm(flat: FlatBuffers, lo: int = 0, hi: int | None = None) -> torch.Tensor:
+    g = flat.grads[lo:hi if hi is not None else flat.size]
+    if g.is_cuda:
+        from ..ops import native
+
+        return native.sumsq(g).sqrt()
+    return g.double().pow(2).sum().sqrt().float()
+
+
+def build_optimizer(model, cfg_optim, device, lp_dtype=None, shard=None):
+    """(flat buffers, optimizer) for `optim.name` 'adamw' or 'muon' (reference: ced/train/optim.py:927-979)."""
+    groups = param_groups(model, cfg_optim)
+    flat = FlatBuffers(model, groups, device, lp_dtype)
+    if cfg_optim.name == "muon":
+        from .muon import MuonWithAdamW
+
+        return flat, MuonWithAdamW(flat, groups, cfg_optim, shard)
+    return flat, FlatAdamW(flat, groups, cfg_optim.betas, cfg_optim.eps, shard)

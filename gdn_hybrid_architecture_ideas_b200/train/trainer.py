@@ -1,0 +1,403 @@
+"""Trainer: builds the model, the flat-buffer optimizer, the data source and the parallel plan from a TrainConfig and
+runs the training loop with checkpoints, metrics and clean stops.
+
+One step (reference: ced/train/trainer.py:2823-3362): batch for this rank (pure function of the step) -> micro-batch
+loop {pinned H2D, forward to hidden states, fused head + loss, backward into the flat gradient buffer} -> gradient
+synchronisation (NCCL all-reduce, or ZeRO reduce-scatter; on CUDA optionally the fused peer-memory kernel that also
+applies the update) -> global-norm clip -> optimizer update (+ parameter all-gather under ZeRO) -> metrics.
+The loss is sum(valid (ce + z lse^2)) / global valid count, so summing gradients over ranks gives the 1-process step.
+
+Stops: a non-finite loss writes `diverged.json` and raises Diverged (the CLI exits 86; the run directory then refuses
+to train); SIGTERM sets a flag that is OR-reduced over ranks each step so all ranks save and leave together
+(trainer.py:4361-4404, 4678-4695).
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import random
+import signal
+import time
+from pathlib import Path
+
+import torch
+
+from .. import config as C
+from ..data import make_data
+from ..data.batch_check import BatchError, check_batch
+from ..models import build_model
+from . import checkpoint as ckpt
+from .fused_head import chunked_ce, fused_linear_ce
+from .lr import lr_of
+from .optim import build_optimizer, grad_norm
+
+EXIT_DIVERGED = 86
+
+
+class Diverged(RuntimeError):
+    pass
+
+
+def pick_device(name: str) -> torch.device:
+    if name == "auto":
+        return torch.device("cuda" if torch.cuda.is_available() else "cpu")
+    return torch.device(name)
+
+
+class Trainer:
+    def __init__(self, cfg: C.TrainConfig, run_dir: str | Path | None = None, dp=None, device: torch.device | None = None):
+        C.require_supported(cfg)
+        self.cfg, self.dp = cfg, dp
+        self.run_dir = Path(run_dir) if run_dir is not None else None
+        self.device = device or (dp.device if dp is not None else pick_device(cfg.device))
+        self.rank, self.world = (dp.rank, dp.world) if dp is not None else (0, 1)
+        self.lead = self.rank == 0
+        random.seed(cfg.seed)
+        torch.manual_seed(cfg.seed)
+        if cfg.tf32 and self.device.type == "cuda":
+            torch.backends.cuda.matmul.allow_tf32 = True
+        dtype = {"float32": torch.float32, "float64": torch.float64, "bfloat16": torch.bfloat16}[cfg.dtype]
+        self.model = build_model(cfg.model).to(dtype).to(self.device)
+        self.model.encoder.activation_checkpoint = cfg.activation_checkpoint
+        self.autocast = cfg.autocast == "bfloat16"
+        native = self.device.type == "cuda"
+        from .. import ops
+
+        self.native = native and ops.mode() == "native"
+        lp = torch.bfloat16 if (self.native and self.autocast) else None
+        self.sharding = cfg.optimizer_sharding if self.world > 1 else "replicated"
+        if cfg.micro_batch_size is not None and dp is not None:
+            dp.check(cfg.data.batch_size, cfg.micro_batch_size)
+        self.flat, self.optimizer, self.zero = self._build_optimizer(lp)
+        self.data = make_data(cfg.data, cfg.model.vocab_size)
+        self.tst = None
+        if cfg.tst.schedule:
+            from .tst import TSTPlan
+
+            self.tst = TSTPlan(cfg.tst, self.data, cfg.model.vocab_size)
+        self.step = 0
+        self.wandb_run_id = None
+        self.init_info = self.resume_info = None
+        self._stop = False
+        self._saver = ckpt.AsyncSaver() if cfg.ckpt_async else None
+        self._last_ckpt_time = time.time()
+        self._pinned = None
+        self.last_metrics: dict = {}
+        self.h2d_bytes = self.d2h_bytes = 0
+        if self.run_dir is not None and self.lead:
+            self.run_dir.mkdir(parents=True, exist_ok=True)
+        if cfg.init_from:
+            self.init_from_checkpoint(cfg.init_from)
+
+    # ------------------------------------------------------------------ construction
+
+    def _build_optimizer(self, lp):
+        cfg = self.cfg
+        zero = None
+        if self.sharding in ("zero1", "zero2"):
+            from ..parallel.zero import ZeroPlan
+
+            zero = ZeroPlan(self.model, cfg.optim, self.dp, self.sharding)
+            flat, opt = zero.build(self.device, lp)
+        else:
+            flat, opt = build_optimizer(self.model, cfg.optim, self.device, lp)
+        return flat, opt, zero
+
+    # ------------------------------------------------------------------ data
+
+    def batch_at(self, step: int):
+        B = self.cfg.data.batch_size
+        first, count = self.dp.rows(B) if self.dp is not None else (0, B)
+        src_step = step + self.cfg.data_start_step
+        if self.tst is not None:
+            return self.tst.batch_at(src_step, first, count)
+        return self.data.batch(src_step, first, count)
+
+    def _global_counts(self, batch) -> tuple[int, int]:
+        """(valid targets over all ranks, bad-batch flag over all ranks) from one host reduction."""
+        bad = 0
+        try:
+            check_batch(batch, self.cfg.model.vocab_size)
+        except BatchError as e:
+            bad, self._bad = 1, e
+        n = int(batch.target_valid.sum()) if batch.multi_valid is None else int(batch.multi_valid.any(-1).sum())
+        if self.dp is not None:
+            n, bad = self.dp.sum_host([n, bad])
+        return n, bad
+
+    # ------------------------------------------------------------------ one step
+
+    def _micro_loss(self, mb, n_global: int):
+        cfg = self.cfg
+        z = cfg.loss.z_loss
+        s = mb.tokens.shape[2] if mb.tokens.dim() == 3 else 1
+        kw = {}
+        if s > 1 and cfg.tst.gdn_resolution_gates != "none":
+            kw.update(gdn_scale=s, gdn_beta_power=cfg.tst.gdn_resolution_gates == "E")
+        if s > 1 and cfg.tst.token_scale_rope:
+            kw.update(rope_scale=s)
+        ac = torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast and not self.native)
+        with ac:
+            out = self.model(mb.tokens, mb.doc_ids, return_hidden=True, single_doc=mb.single_doc, **kw)
+        hidden = out.hidden_aux
+        if mb.multi_targets is not None:
+            from .tst import bag_weights
+
+            w = bag_weights(s).to(hidden.device)
+            targets = mb.multi_targets
+            a = mb.multi_valid.to(torch.float32) * w / n_global
+            b = mb.multi_valid.any(-1).to(torch.float32) * (z / n_global)
+        else:
+            targets = mb.targets
+            valid = mb.target_valid.to(torch.float32)
+            a, b = valid / n_global, valid * (z / n_global)
+        W = self.model.head_weight()
+        if cfg.head_impl == "fused":
+            loss, ce, _ = fused_linear_ce(hidden, W, targets, a, b, cfg.head_chunk, self.model.head_weight_lp)
+            ce_sum = (ce.detach() if mb.multi_targets is not None else ce.detach()).sum()
+        else:
+            loss, ce_sum = chunked_ce(hidden, W, targets, a, b)
+            ce_sum = ce_sum.detach()
+        return loss, ce_sum
+
+    def train_step(self) -> dict:
+        cfg = self.cfg
+        t0 = time.perf_counter()
+        step = self.step
+        if self.tst is not None and self.tst.schedule.is_switch(step) and not cfg.tst.keep_optimizer_state:
+            self.optimizer.reset_moments()
+        batch = self.batch_at(step)
+        n_global, bad = self._global_counts(batch)
+        if bad:
+            self._halt_bad_batch(step)
+        lr = lr_of(cfg, step)
+        self.flat.grads.zero_()
+        rows = batch.tokens.shape[0]
+        micro = cfg.micro_batch_size or rows
+        if rows % micro:
+            raise ValueError(f"micro_batch_size {micro} does not divide this rank's {rows} rows")
+        if self.device.type == "cuda":
+            batch = batch.pin()
+        loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        ce_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        self.h2d_bytes = 0
+        for lo in range(0, rows, micro):
+            mb = _slice(batch, lo, lo + micro)
+            self.h2d_bytes += mb.h2d_bytes()
+            mb = mb.to(self.device)
+            loss, ce = self._micro_loss(mb, max(n_global, 1))
+            loss.backward()
+            loss_sum += loss.detach().float()
+            ce_sum += ce.float()
+        # ---- gradient synchronisation, clip, update
+        stats = torch.stack([loss_sum, ce_sum]).double()
+        if self.zero is not None:
+            gnorm = self.zero.sync_and_step(self.optimizer, lr, cfg.optim.grad_clip, stats)
+        else:
+            if self.dp is not None:
+                self.dp.all_reduce_(self.flat.grads)
+                self.dp.all_reduce_(stats)
+            gnorm = grad_norm(self.flat)
+            scale = _clip_coef(gnorm, cfg.optim.grad_clip)
+            self.optimizer.step(lr, scale)
+        host = torch.stack([stats[0].float(), stats[1].float(), gnorm.float()]).cpu()   # the step's one device->host read
+        self.d2h_bytes = host.numel() * host.element_size()
+        loss_v, ce_v, gn_v = (float(x) for x in host)
+        seconds = time.perf_counter() - t0
+        s = batch.tokens.shape[2] if batch.tokens.dim() == 3 else 1
+        n_tokens = cfg.data.batch_size * cfg.data.seq_len * s
+        m = {"step": step, "loss": loss_v, "ce_dec": ce_v * 1.0, "lr": lr, "grad_norm": gn_v, "n_targets": n_global,
+             "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
+        if self.device.type == "cuda":
+            m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        self.step += 1
+        self.last_metrics = m
+        if not math.isfinite(loss_v):
+            self._halt_diverged(m)
+        if self.dp is not None and self.dp.check_every and self.step % self.dp.check_every == 0:
+            self.dp.check_replicas(list(self.model.named_parameters()))
+        return m
+
+    # ------------------------------------------------------------------ loop
+
+    def fit(self, until_step: int | None = None) -> None:
+        cfg = self.cfg
+        if self.run_dir is not None and (self.run_dir / "diverged.json").exists():
+            raise Diverged(f"{self.run_dir} is marked diverged: start a new run directory")
+        end = cfg.steps if until_step is None else min(cfg.steps, until_step)
+        old = None
+        try:
+            old = signal.signal(signal.SIGTERM, self._request_stop)
+        except ValueError:  # not the main thread
+            pass
+        self._jsonl({"event": "start", "step": self.step, "world": self.world, "device": str(self.device),
+                     "params": sum(p.numel() for p in self.model.parameters())})
+        try:
+            while self.step < end:
+                m = self.train_step()
+                if self.lead:
+                    self._jsonl(m)
+                    if cfg.log_every and (m["step"] % cfg.log_every == 0 or self.step == end):
+                        print(f"step {m['step']:6d} loss {m['loss']:.4f} lr {m['lr']:.2e} gnorm {m['grad_norm']:.3f} "
+                              f"{m['tokens_per_s']:.0f} tok/s", flush=True)
+                due = self._ckpt_due(end)
+                stop = self._stop
+                if self.dp is not None:
+                    stop, due = self.dp.agree(stop, due)
+                if self._saver is not None:
+                    self._saver.commit()
+                if due or stop:
+                    self.save_checkpoint(sync=stop or self.step == end)
+                if stop:
+                    break
+        finally:
+            if self._saver is not None:
+                self._saver.commit(block=True)
+            if old is not None:
+                signal.signal(signal.SIGTERM, old)
+
+    def _request_stop(self, *_):
+        self._stop = True
+
+    def _ckpt_due(self, end: int) -> bool:
+        cfg = self.cfg
+        if self.run_dir is None:
+            return False
+        if self.step == end or self.step in cfg.checkpoint_steps:
+            return True
+        if cfg.ckpt_every_steps and self.step % cfg.ckpt_every_steps == 0:
+            return True
+        if cfg.ckpt_every_minutes and time.time() - self._last_ckpt_time > 60.0 * cfg.ckpt_every_minutes:
+            return True
+        return False
+
+    # ------------------------------------------------------------------ failure paths
+
+    def _halt_diverged(self, m: dict):
+        if self.run_dir is not None and self.lead:
+            (self.run_dir / "diverged.json").write_text(json.dumps({"step": m["step"], "loss": str(m["loss"])}))
+            self._jsonl({"event": "diverged", **{k: (str(v) if isinstance(v, float) and not math.isfinite(v) else v) for k, v in m.items()}})
+        raise Diverged(f"non-finite loss at step {m['step']}")
+
+    def _halt_bad_batch(self, step: int):
+        info = {"rank": self.rank, "error": str(getattr(self, "_bad", "")), "rows": getattr(getattr(self, "_bad", None), "rows", [])}
+        infos = self.dp.gather_host(info) if self.dp is not None else [info]
+        if self.run_dir is not None and self.lead:
+            self._jsonl({"event": "bad_batch", "step": step, "ranks": [i for i in infos if i["error"]]})
+        raise BatchError(f"bad batch at step {step}: {[i for i in infos if i['error']]}")
+
+    def _jsonl(self, record: dict) -> None:
+        if self.run_dir is None or not self.lead or not self.cfg.metrics_jsonl:
+            return
+        with open(self.run_dir / "metrics.jsonl", "a") as f:
+            f.write(json.dumps(record) + "\n")
+
+    # ------------------------------------------------------------------ checkpoints
+
+    def data_state(self) -> dict:
+        d = self.cfg.data
+        state = {"kind": d.kind, "seed": d.seed, "seq_len": d.seq_len, "batch_size": d.batch_size}
+        if d.kind == "shards":
+            state["fingerprint"] = self.data.fingerprint()
+        if self.cfg.data_start_step:
+            state["data_start_step"] = self.cfg.data_start_step
+        if self.tst is not None:
+            state.update(self.tst.data_state())
+        return state
+
+    def state_dict(self) -> dict:
+        if self.zero is not None:
+            self.zero.gather_master()
+        state = {
+            "step": self.step, "config": C.to_dict(self.cfg),
+            "model": {k: v.detach().clone() for k, v in self.model.state_dict().items()},
+            "optimizer": self.optimizer.state_dict() if self.zero is None else self.zero.optimizer_state(self.optimizer),
+            "torch_rng": torch.get_rng_state(),
+            "cuda_rng": torch.cuda.get_rng_state_all() if self.device.type == "cuda" and self.dp is None else None,
+            "python_rng": random.getstate(), "wandb_run_id": self.wandb_run_id, "data_state": self.data_state(),
+            "init_from": self.init_info, "resumed_from": self.resume_info,
+        }
+        if self.dp is not None:
+            state["data_parallel"] = {"world_size": self.world, "sharding": self.sharding}
+        return state
+
+    def save_checkpoint(self, sync: bool = True) -> Path | None:
+        if self.run_dir is None:
+            return None
+        path = ckpt.step_path(self.run_dir, self.step)
+        state = self.state_dict()   # collective under ZeRO: every rank takes part
+        if self.lead:
+            if self._saver is not None and not sync:
+                self._saver.start(state, path, self.cfg.ckpt_keep, self.cfg.checkpoint_steps)
+            else:
+                if self._saver is not None:
+                    self._saver.commit(block=True)
+                ckpt.write_atomic(state, path)
+                ckpt.point_latest(path, self.cfg.ckpt_keep, self.cfg.checkpoint_steps)
+        if self.dp is not None:
+            self.dp.barrier()
+        self._last_ckpt_time = time.time()
+        return path
+
+    def load_state_dict(self, state: dict, check_config: bool = True, weights_only: bool = False) -> None:
+        if check_config:
+            saved = C.checkpoint_config(state["config"])
+            diff = C.config_differences(C.to_dict(C.from_dict(C.TrainConfig, saved)), C.to_dict(self.cfg))
+            if diff:
+                raise ValueError(f"the checkpoint was written by a run with a different config: {diff}")
+        with torch.no_grad():
+            own = self.model.state_dict()
+            missing = [k for k in own if k not in state["model"]]
+            if missing and not weights_only:
+                raise KeyError(f"checkpoint lacks parameters {missing[:6]}")
+            for k, v in state["model"].items():
+                if k in own:
+                    own[k].copy_(v)
+        self.flat.refresh_lp()
+        if weights_only:
+            return
+        if self.zero is not None:
+            self.zero.load_optimizer_state(self.optimizer, state["optimizer"])
+        else:
+            self.optimizer.load_state_dict(state["optimizer"])
+        self.step = int(state["step"])
+        torch.set_rng_state(state["torch_rng"])
+        random.setstate(state["python_rng"])
+        if state.get("cuda_rng") is not None and self.device.type == "cuda" and self.dp is None:
+            torch.cuda.set_rng_state_all(state["cuda_rng"])
+        self.wandb_run_id = state.get("wandb_run_id")
+        if state.get("data_state") and state["data_state"] != self.data_state():
+            raise ValueError(f"the checkpoint's data stream {state['data_state']} is not this run's {self.data_state()}")
+
+    def resume_from_checkpoint(self, path: str | Path | None = None) -> bool:
+        """Resume from `path`, or from the run directory's latest checkpoint; False when there is none."""
+        p = Path(path) if path is not None else (ckpt.latest_path(self.run_dir) if self.run_dir is not None else None)
+        if p is None:
+            return False
+        self.load_state_dict(ckpt.load(p))
+        self.resume_info = {"path": str(p), "step": self.step}
+        return True
+
+    def init_from_checkpoint(self, path: str | Path) -> None:
+        """Weights only, from another run; parameters the file lacks keep their initial values."""
+        state = ckpt.load(Path(path))
+        self.load_state_dict(state, check_config=False, weights_only=True)
+        self.init_info = {"path": str(path), "step": int(state.get("step", 0))}
+
+
+def _slice(batch, lo: int, hi: int):
+    from ..data.synthetic import Batch
+
+    def cut(t):
+        return t[lo:hi] if isinstance(t, torch.Tensor) else t
+    return Batch(tokens=cut(batch.tokens), targets=cut(batch.targets), target_valid=cut(batch.target_valid),
+                 doc_ids=cut(batch.doc_ids), dec_mask=cut(batch.dec_mask), multi_targets=cut(batch.multi_targets),
+                 multi_valid=cut(batch.multi_valid), loss_mask=cut(batch.loss_mask), single_doc=batch.single_doc)
+
+
+def _clip_coef(norm: torch.Tensor, max_norm: float):
+    """min(1, max_norm / (norm + 1e-6)) as a 0-dim tensor (no host sync); 1.0 when clipping is off."""
+    if not max_norm or max_norm <= 0:
+        return 1.0
+    return torch.clamp(max_norm / (norm + 1e-6), max=1.0)

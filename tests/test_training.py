@@ -1,0 +1,154 @@
+"""Trainer behaviour on CPU: resume is bit-exact, micro-batching matches, data-parallel gloo ranks equal one process
+(replicated, ZeRO-1, ZeRO-2), SIGTERM saves and leaves, a non-finite loss marks the run, a changed config is refused."""
+
+import copy
+import json
+import os
+import signal
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import pytest
+import torch
+import yaml
+
+from gdn_hybrid_architecture_ideas_b200 import config as C
+from gdn_hybrid_architecture_ideas_b200.train import checkpoint as ckpt
+from gdn_hybrid_architecture_ideas_b200.train.trainer import Diverged, Trainer
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def tiny_train_config(**kw) -> C.TrainConfig:
+    cfg = C.TrainConfig(model=C.tiny_full_config(), data=C.tiny_data_config(seq_len=48, batch_size=4), steps=6, seed=3)
+    cfg.optim.warmup_steps, cfg.ckpt_every_steps, cfg.metrics_jsonl, cfg.head_impl, cfg.log_every = 2, 3, True, "fused", 0
+    for k, v in kw.items():
+        C.apply_override(cfg, f"{k}={v}")
+    return cfg
+
+
+def weights(t: Trainer):
+    return {k: v.clone() for k, v in t.model.state_dict().items()}
+
+
+def test_resume_is_bit_exact(tmp_path):
+    cfg = tiny_train_config()
+    a = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    a.fit()
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(3)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 3
+    c.fit()
+    wa, wc = weights(a), weights(c)
+    assert all(torch.equal(wa[k], wc[k]) for k in wa)
+    assert (tmp_path / "b" / "checkpoints" / "latest").read_text() == "step_00000006.pt"
+    lines = [json.loads(x) for x in (tmp_path / "a" / "metrics.jsonl").read_text().splitlines()]
+    assert lines[0]["event"] == "start" and lines[-1]["step"] == 5
+
+
+def test_fused_head_equals_chunked_head():
+    g = {}
+    for impl in ("fused", "chunked"):
+        t = Trainer(tiny_train_config(head_impl=impl), None)
+        t.train_step()
+        g[impl] = t.flat.grads.clone()
+    assert torch.allclose(g["fused"], g["chunked"], atol=1e-6, rtol=1e-4)
+
+
+def test_microbatch_gradients_match():
+    full = Trainer(tiny_train_config(), None)
+    half = Trainer(tiny_train_config(micro_batch_size=2), None)
+    full.train_step(), half.train_step()
+    assert torch.allclose(full.flat.grads, half.flat.grads, atol=2e-6, rtol=1e-4)
+
+
+def test_changed_config_is_refused(tmp_path):
+    a = Trainer(tiny_train_config(), tmp_path)
+    a.fit(3)
+    other = tiny_train_config()
+    other.model.ffn_hidden = 128
+    b = Trainer(other, tmp_path)
+    with pytest.raises(ValueError, match="different config"):
+        b.load_state_dict(ckpt.load(ckpt.latest_path(tmp_path)))
+
+
+def test_non_finite_loss_marks_the_run(tmp_path):
+    t = Trainer(tiny_train_config(), tmp_path)
+    with torch.no_grad():
+        t.model.final_norm.weight.fill_(float("nan"))
+    with pytest.raises(Diverged):
+        t.fit()
+    assert (tmp_path / "diverged.json").exists()
+    with pytest.raises(Diverged):
+        Trainer(tiny_train_config(), tmp_path).fit()
+
+
+def test_async_checkpoint_equals_sync(tmp_path):
+    a = Trainer(tiny_train_config(), tmp_path / "s")
+    a.fit()
+    b = Trainer(tiny_train_config(ckpt_async=True), tmp_path / "a")
+    b.fit()
+    sa = ckpt.load(ckpt.latest_path(tmp_path / "s"))
+    sb = ckpt.load(ckpt.latest_path(tmp_path / "a"))
+    assert all(torch.equal(sa["model"][k], sb["model"][k]) for k in sa["model"])
+    assert sa["step"] == sb["step"] == 6
+
+
+def _write_config(path: Path, cfg: C.TrainConfig) -> Path:
+    C.save_yaml(cfg, path)
+    return path
+
+
+def _run_cli(args, nproc=1, port=29541, env=None, **popen):
+    cmd = [sys.executable]
+    if nproc > 1:
+        cmd += ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+                "--master-port", str(port)]
+    cmd += [str(ROOT / "scripts" / "train.py")] + args
+    e = {**os.environ, "GHB_DP_BACKEND": "gloo", "OMP_NUM_THREADS": "2", **(env or {})}
+    return subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600, **popen)
+
+
+@pytest.mark.parametrize("sharding,optim", [("replicated", "adamw"), ("zero1", "adamw"), ("zero2", "adamw"), ("zero1", "muon")])
+def test_two_gloo_ranks_equal_one_process(tmp_path, sharding, optim):
+    cfg = tiny_train_config(micro_batch_size=2, steps=4)
+    cfg.optim.name = optim
+    cfg.device = "cpu"
+    path = _write_config(tmp_path / "c.yaml", cfg)
+    one = _run_cli(["--config", str(path), "--run-dir", str(tmp_path / "one")])
+    assert one.returncode == 0, one.stderr[-2000:]
+    two = _run_cli(["--config", str(path), "--run-dir", str(tmp_path / "two"), "--set", f"optimizer_sharding={sharding}"],
+                   nproc=2, port=29541 + hash((sharding, optim)) % 200)
+    assert two.returncode == 0, two.stderr[-2000:]
+    a = ckpt.load(ckpt.latest_path(tmp_path / "one"))
+    b = ckpt.load(ckpt.latest_path(tmp_path / "two"))
+    worst = max((a["model"][k] - b["model"][k]).abs().max().item() for k in a["model"])
+    assert worst < (1e-6 if optim == "adamw" else 2e-3), worst
+    if sharding != "replicated":   # the sharded run's optimizer state loads into one process (world size change)
+        t = Trainer(copy.deepcopy(cfg), None)
+        t.load_state_dict(b, check_config=False)
+        assert t.step == 4
+
+
+def test_sigterm_saves_and_resumes(tmp_path):
+    cfg = tiny_train_config(steps=4000)
+    cfg.ckpt_every_steps, cfg.device = 0, "cpu"
+    cfg.ckpt_every_minutes = 0.0
+    path = _write_config(tmp_path / "c.yaml", cfg)
+    cmd = [sys.executable, str(ROOT / "scripts" / "train.py"), "--config", str(path), "--run-dir", str(tmp_path / "r")]
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE)
+    deadline = time.time() + 120
+    while time.time() < deadline and not (tmp_path / "r" / "metrics.jsonl").exists():
+        time.sleep(0.2)
+    time.sleep(1.0)
+    p.send_signal(signal.SIGTERM)
+    p.wait(timeout=120)
+    latest = ckpt.latest_path(tmp_path / "r")
+    assert latest is not None, p.stderr.read().decode()[-2000:]
+    step = ckpt.load(latest)["step"]
+    assert 0 < step < 4000
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
+    assert t.resume_from_checkpoint() and t.step == step
