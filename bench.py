@@ -1,0 +1,286 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of the 200M full hybrid (bf16, AdamW, seq 4096, 16 rows per GPU, synthetic
+uniform token ids, random-init weights) on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 is launched by torchrun (one rank per GPU, NCCL); this file reads RANK / LOCAL_RANK / WORLD_SIZE. Rank 0 prints
+ONE JSON line. `value` is device-timed (CUDA events around K steps whose inputs are already on the device, max over
+ranks); `e2e.value` times K calls of the public `Trainer.train_step()` — batch construction, the pinned host->device
+copy of the step's inputs and the device->host read of the step's loss included. `--impl reference` runs the
+unmodified reference package installed under baseline/_ref through its own Trainer on the same configuration.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL = "200m-full-hybrid"
+SEQ_LEN = 4096
+ROWS_PER_GPU = 16
+VOCAB = 32768
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", default="200m", help="model size preset (the headline is 200m)")
+    ap.add_argument("--seq-len", type=int, default=SEQ_LEN)
+    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU per step")
+    ap.add_argument("--sharding", default="auto", help="replicated | zero1 | zero2 | auto (zero2 when N > 1)")
+    ap.add_argument("--comm", default="auto", help="fused | nccl | auto")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi samples of SM clocks and throttle reasons while the timed region runs (rank 0 only)."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, enabled: bool):
+        self.proc, self.path = None, None
+        if not enabled:
+            return
+        self.path = tempfile.NamedTemporaryFile(prefix="clocks_", suffix=".csv", delete=False).name
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self, n_gpus: int) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        self.proc.wait()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[0].isdigit() or int(f[0]) >= n_gpus:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def max_over_ranks(value: float, dp) -> float:
+    return value if dp is None else dp.max_over_ranks(value)
+
+
+def baseline_number():
+    try:
+        pub = json.loads((ROOT / "BASELINE.json").read_text()).get("published") or {}
+        return pub.get("train_tokens_per_s")
+    except Exception:
+        return None
+
+
+# ---------------------------------------------------------------------------------------------------------- ours
+
+def run_ours(args) -> dict:
+    import torch
+
+    from gdn_hybrid_architecture_ideas_b200 import config as C
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.parallel import data_parallel
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    dp = data_parallel.from_environment()
+    world = 1 if dp is None else dp.world
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
+    cfg = C.TrainConfig(model=C.hybrid_model_config(args.size, full=True))
+    cfg.data = C.DataConfig(kind="uniform", seq_len=args.seq_len, batch_size=args.rows * world, seed=1)
+    cfg.micro_batch_size = args.rows
+    cfg.steps, cfg.seed, cfg.dtype, cfg.autocast, cfg.head_impl = 10 ** 6, 1, "float32", "bfloat16", "fused"
+    cfg.optim.name, cfg.optim.warmup_steps = "adamw", 100
+    cfg.metrics_jsonl, cfg.log_every, cfg.ckpt_every_steps, cfg.ckpt_every_minutes = False, 0, 0, 0.0
+    cfg.optimizer_sharding = ("zero2" if world > 1 else "replicated") if args.sharding == "auto" else args.sharding
+    if args.comm != "auto":
+        os.environ["GHB_COMM"] = args.comm
+    trainer = Trainer(cfg, None, dp)
+    dev = trainer.device
+    for _ in range(args.warmup):
+        trainer.train_step()
+    # ---- device-timed region: inputs resident on the device, no host read inside
+    batches = [trainer.batch_at(trainer.step + i).pin().to(dev) for i in range(args.steps)]
+    counts = [trainer._global_counts(trainer.batch_at(trainer.step + i))[0] for i in range(args.steps)]
+    torch.cuda.synchronize()
+    if dp is not None:
+        dp.barrier()
+    sampler = ClockSampler(dp is None or dp.lead)
+    ops.reset_launch_count()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for b, n in zip(batches, counts):
+        trainer.device_step(b, n)
+    end.record()
+    torch.cuda.synchronize()
+    launches = ops.launch_count()
+    if dp is not None:
+        dp.barrier()
+    dev_ms = max_over_ranks(start.elapsed_time(end), dp) / args.steps
+    # ---- end-to-end region: the public train_step (batch build, pinned H2D, D2H loss read) every step
+    torch.cuda.synchronize()
+    if dp is not None:
+        dp.barrier()
+    start.record()
+    for _ in range(args.steps):
+        m = trainer.train_step()
+    end.record()
+    torch.cuda.synchronize()
+    if dp is not None:
+        dp.barrier()
+    e2e_ms = max_over_ranks(start.elapsed_time(end), dp) / args.steps
+    clocks = sampler.stop(world)
+    tokens = args.rows * world * args.seq_len
+    base = baseline_number()
+    value = tokens / (dev_ms / 1e3)
+    out = {
+        "metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / base) if base else None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": MODEL if args.size == "200m" else args.size, "global_batch": args.rows * world,
+                   "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("" if world == 1 else f"-{cfg.optimizer_sharding}"),
+                   "optimizer": "adamw", "vocab": VOCAB, "l2": "per-step working set (GBs of activations) >> 126 MB L2",
+                   "comm": os.environ.get("GHB_COMM", "auto"), "loss": m["loss"]},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": trainer.h2d_bytes, "d2h_bytes_per_step": trainer.d2h_bytes},
+        "gpu_launches": launches, "impl": "ours",
+    }
+    if dp is not None:
+        dp.close()
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------- reference
+
+def reference_config(args, world: int, micro: int) -> dict:
+    """The same model and step as `run_ours`, in the reference's own config keys; implementation switches are the
+    ones its shipped 200M base config uses (compiled layers, flex attention, fused head, TF32), except the GDN kernel:
+    its Triton kernel refuses value dim 256, so the layer runs its own chunked PyTorch path."""
+    attn = dict(n_q_heads=16, n_kv_heads=4, head_dim=64, gate="elementwise", qk_norm=True, rope_fraction=0.25,
+                rope_theta=1e7, rope_max_distance=2048, backend=os.environ.get("GHB_REF_ATTENTION", "flex"))
+    gdn = dict(n_k_heads=8, n_v_heads=8, k_head_dim=128, v_head_dim=256, conv_kernel=4, init="fla", kernel="chunked",
+               chunk_size=64, output_gate="sigmoid", input_dtype="bfloat16")
+    enc = dict(n_layers=16, full_attn_interval=4, attention=attn, gdn=gdn, nope_global_layers=[3], attn_res="block_entry",
+               gdn_write_mix="layer", gdn_write_variant="qmix")
+    model = dict(arch="control", vocab_size=VOCAB, tie_embeddings=True, d_model=1024, ffn_hidden=2816, init_std=0.02,
+                 encoder=enc)
+    data = dict(kind="synthetic", seq_len=args.seq_len, batch_size=args.rows * world, doc_len_min=args.seq_len + 1,
+                doc_len_max=args.seq_len + 1, seed=1)
+    optim = dict(name="adamw", warmup_steps=100)
+    return dict(model=model, data=data, optim=optim, steps=10 ** 6, seed=1, dtype="float32", autocast="bfloat16",
+                micro_batch_size=micro, tf32=True, deterministic=False, metrics_jsonl=False, log_every=10 ** 9,
+                ckpt_every_steps=10 ** 9, ckpt_every_minutes=10 ** 9, compile=os.environ.get("GHB_REF_COMPILE", "all"),
+                head_select=True, head_impl="fused", device="auto")
+
+
+def run_reference(args) -> dict:
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "ced").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref /root/reference/code)"}
+    sys.path.insert(0, str(ref))
+    try:
+        import torch
+        import ced.config as RC
+        from ced.train import data_parallel as rdp
+        from ced.train.trainer import Trainer as RefTrainer
+    except Exception as e:  # the package does not import here
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(e).__name__}: {str(e)[:160]}"}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    dp = rdp.from_environment() if int(os.environ.get("WORLD_SIZE", "1")) > 1 else None
+    world = 1 if dp is None else dp.world
+    micro, err = args.rows, None
+    while micro >= 1:
+        try:
+            cfg = RC.from_dict(RC.TrainConfig, reference_config(args, world, micro))
+            run_dir = tempfile.mkdtemp(prefix="refrun_")
+            trainer = RefTrainer(cfg, run_dir, dp=dp)
+            for _ in range(args.warmup):
+                trainer.train_step()
+            break
+        except torch.cuda.OutOfMemoryError as e:
+            err, trainer = e, None
+            torch.cuda.empty_cache()
+            micro //= 2
+    else:
+        return {"impl": "reference", "unavailable": f"reference ran out of memory at every micro-batch size: {str(err)[:120]}"}
+    torch.cuda.synchronize()
+    if dp is not None:
+        dp.barrier()
+    sampler = ClockSampler(dp is None or dp.lead)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        m = trainer.train_step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end)
+    if dp is not None:
+        t = torch.tensor([ms], device="cuda")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+    ms /= args.steps
+    clocks = sampler.stop(world)
+    tokens = args.rows * world * args.seq_len
+    value = tokens / (ms / 1e3)
+    loss = m.get("loss") if isinstance(m, dict) else None
+    out = {"metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"model": MODEL, "global_batch": args.rows * world, "seq_len": args.seq_len,
+                      "parallelism": f"dp{world}", "optimizer": "adamw", "micro_batch": micro,
+                      "compile": os.environ.get("GHB_REF_COMPILE", "all"),
+                      "attention": os.environ.get("GHB_REF_ATTENTION", "flex"), "gdn": "chunked (torch)", "loss": loss},
+           "clocks": clocks, "e2e": {"value": value, "unit": "tokens/s", "note": "the reference's train_step is end to end"},
+           "impl": "reference"}
+    if dp is not None:
+        dp.close()
+    return out
+
+
+def main():
+    args = parse()
+    t0 = time.time()
+    try:
+        out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    except Exception as e:
+        if args.impl != "reference":
+            raise
+        out = {"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+    if int(os.environ.get("RANK", "0")) == 0:
+        out["wall_s"] = round(time.time() - t0, 1)
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

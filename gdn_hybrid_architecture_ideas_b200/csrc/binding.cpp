@@ -1,0 +1,164 @@
+// Python bindings of the sm_100a kernels: tensors in, raw pointers + the current CUDA stream out.
+// Shape and dtype checks live here so that no kernel ever receives a pointer it was not written for.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+int sm_count() { return at::cuda::getCurrentDeviceProperties()->multiProcessorCount; }
+void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, ": launch refused (code ", rc, ")"); }
+bool is_bf16(const Tensor& t) { return t.scalar_type() == torch::kBFloat16; }
+bool is_f32(const Tensor& t) { return t.scalar_type() == torch::kFloat32; }
+const float* fptr(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr<float>() : nullptr; }
+
+// D = A B^T (+ D). a: [M,K] (or [K,M] when a_mn), b: [N,K] (or [K,N] when b_mn), 2-D with unit inner stride.
+void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, bool accumulate, Tensor& err) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && out.is_cuda() && is_bf16(a) && is_bf16(b), "gemm: bf16 CUDA operands");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 && out.stride(1) == 1, "gemm: 2-D, unit inner stride");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb && out.size(0) == M && out.size(1) == N, "gemm: shape mismatch");
+  int mode;
+  if (is_bf16(out)) { TORCH_CHECK(!accumulate, "gemm: accumulation needs an fp32 output"); mode = 0; }
+  else { TORCH_CHECK(is_f32(out), "gemm: output bf16 or fp32"); mode = accumulate ? 2 : 1; }
+  check(ghb::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), a_mn, b_mn, mode,
+                       err.data_ptr<int>(), sm_count(), stream()), "gemm_bf16");
+}
+
+void rmsnorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& z, int64_t gate, const c10::optional<Tensor>& resid,
+                 Tensor& y, const c10::optional<Tensor>& rstd, double eps, double scale) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && is_f32(w), "rmsnorm_fwd: contiguous inputs, fp32 gain");
+  const int d = x.size(-1);
+  const long rows = x.numel() / d;
+  TORCH_CHECK(w.numel() == d || w.numel() == 1, "rmsnorm_fwd: gain of size d or 1");
+  if (gate) TORCH_CHECK(z.has_value() && is_bf16(*z) && z->is_contiguous() && z->numel() == x.numel(), "rmsnorm_fwd: bf16 gate input");
+  if (resid.has_value()) TORCH_CHECK(is_f32(*resid) && is_f32(y) && resid->is_contiguous() && resid->numel() == x.numel(), "rmsnorm_fwd: fp32 residual");
+  check(ghb::rmsnorm_fwd(x.data_ptr(), is_bf16(x), w.data_ptr<float>(), w.numel() == 1, gate ? z->data_ptr() : nullptr, gate, fptr(resid),
+                         y.data_ptr(), is_bf16(y), rstd.has_value() ? rstd->data_ptr<float>() : nullptr, rows, d, eps, scale, stream()),
+        "rmsnorm_fwd");
+}
+
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& w, const c10::optional<Tensor>& z, int64_t gate, const Tensor& rstd,
+                 const c10::optional<Tensor>& dres, Tensor& dx, const c10::optional<Tensor>& dz, Tensor& dw, double scale) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous() && is_f32(dw) && dx.scalar_type() == x.scalar_type(), "rmsnorm_bwd: layout");
+  const int d = x.size(-1);
+  const long rows = x.numel() / d;
+  if (gate) TORCH_CHECK(z.has_value() && dz.has_value() && is_bf16(*dz), "rmsnorm_bwd: gate tensors");
+  check(ghb::rmsnorm_bwd(dy.data_ptr(), is_bf16(dy), x.data_ptr(), is_bf16(x), w.data_ptr<float>(), w.numel() == 1, gate ? z->data_ptr() : nullptr,
+                         gate, rstd.data_ptr<float>(), fptr(dres), dx.data_ptr(), gate ? dz->data_ptr() : nullptr, dw.data_ptr<float>(), rows, d,
+                         scale, sm_count(), stream()), "rmsnorm_bwd");
+}
+
+void silu_mul_fwd(const Tensor& gu, Tensor& h) {
+  const c10::cuda::CUDAGuard guard(gu.device());
+  const int f = h.size(-1);
+  TORCH_CHECK(is_bf16(gu) && is_bf16(h) && gu.size(-1) == 2 * f && gu.is_contiguous() && h.is_contiguous(), "silu_mul_fwd: gu [rows, 2f] bf16");
+  const long rows = h.numel() / f;
+  auto* p = static_cast<const __nv_bfloat16*>(gu.data_ptr());
+  check(ghb::silu_mul_fwd(p, p + f, 2L * f, h.data_ptr(), rows, f, sm_count(), stream()), "silu_mul_fwd");
+}
+void silu_mul_bwd(const Tensor& dh, const Tensor& gu, Tensor& dgu) {
+  const c10::cuda::CUDAGuard guard(gu.device());
+  const int f = dh.size(-1);
+  TORCH_CHECK(is_bf16(gu) && is_bf16(dh) && is_bf16(dgu) && gu.is_contiguous() && dh.is_contiguous() && dgu.is_contiguous(), "silu_mul_bwd: bf16 contiguous");
+  const long rows = dh.numel() / f;
+  auto* p = static_cast<const __nv_bfloat16*>(gu.data_ptr());
+  auto* q = static_cast<__nv_bfloat16*>(dgu.data_ptr());
+  check(ghb::silu_mul_bwd(dh.data_ptr(), p, p + f, 2L * f, q, q + f, rows, f, sm_count(), stream()), "silu_mul_bwd");
+}
+
+void adamw(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const c10::optional<Tensor>& lp, double lr, double b1, double b2, double eps,
+           double wd, double c1, double c2, const c10::optional<Tensor>& grad_scale, double scale_host) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(is_f32(p) && is_f32(g) && is_f32(m) && is_f32(v) && p.is_contiguous() && g.is_contiguous(), "adamw: fp32 flat buffers");
+  check(ghb::adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), lp.has_value() ? lp->data_ptr() : nullptr,
+                   p.numel(), lr, b1, b2, eps, wd, c1, c2, fptr(grad_scale), scale_host, sm_count(), stream()), "adamw");
+}
+Tensor sumsq(const Tensor& x) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(is_f32(x) && x.is_contiguous(), "sumsq: fp32 contiguous");
+  const int blocks = 1024;
+  Tensor part = torch::empty({blocks}, x.options());
+  check(ghb::sumsq_partials(x.data_ptr<float>(), x.numel(), part.data_ptr<float>(), blocks, stream()), "sumsq");
+  return part.sum();
+}
+void cast_bf16(const Tensor& x, Tensor& y) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(is_f32(x) && is_bf16(y) && x.numel() == y.numel(), "cast_bf16");
+  check(ghb::cast_bf16(x.data_ptr<float>(), y.data_ptr(), x.numel(), sm_count(), stream()), "cast_bf16");
+}
+
+void gdn_prep_fwd(const Tensor& u, const c10::optional<Tensor>& doc, const Tensor& w, Tensor& out, int64_t L, int64_t nq, double qscale) {
+  const c10::cuda::CUDAGuard guard(u.device());
+  const int C = u.size(-1);
+  TORCH_CHECK(is_bf16(u) && is_bf16(out) && u.is_contiguous() && out.is_contiguous() && is_f32(w) && w.is_contiguous() && w.size(0) == C && w.size(1) == 4,
+              "gdn_prep_fwd: bf16 [rows, C], conv weight fp32 [C, 4]");
+  if (doc.has_value()) TORCH_CHECK(doc->scalar_type() == torch::kInt32 && doc->is_contiguous() && doc->numel() * C == u.numel(), "gdn_prep_fwd: int32 doc ids");
+  check(ghb::gdn_prep_fwd(u.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, w.data_ptr<float>(), out.data_ptr(), u.numel() / C, L, C, nq,
+                          qscale, stream()), "gdn_prep_fwd");
+}
+void gdn_prep_bwd(const Tensor& u, const c10::optional<Tensor>& doc, const Tensor& w, const Tensor& dout, Tensor& dconv, Tensor& du, Tensor& dw,
+                  int64_t L, int64_t nq, double qscale) {
+  const c10::cuda::CUDAGuard guard(u.device());
+  const int C = u.size(-1);
+  TORCH_CHECK(is_bf16(dout) && dout.is_contiguous() && is_bf16(dconv) && is_bf16(du) && is_f32(dw) && dw.is_contiguous(), "gdn_prep_bwd: layout");
+  check(ghb::gdn_prep_bwd(u.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, w.data_ptr<float>(), dout.data_ptr(), dconv.data_ptr(),
+                          du.data_ptr(), dw.data_ptr<float>(), u.numel() / C, L, C, nq, qscale, stream()), "gdn_prep_bwd");
+}
+
+void depth_mix_fwd(const std::vector<Tensor>& src, const Tensor& ueff, Tensor& out, Tensor& alpha, Tensor& rnorm, double eps) {
+  const c10::cuda::CUDAGuard guard(out.device());
+  const int d = out.size(-1);
+  std::vector<const float*> p;
+  for (auto& s : src) { TORCH_CHECK(is_f32(s) && s.is_contiguous() && s.numel() == out.numel(), "depth_mix_fwd: fp32 contiguous sources"); p.push_back(s.data_ptr<float>()); }
+  check(ghb::depth_mix_fwd(p.data(), p.size(), ueff.data_ptr<float>(), out.data_ptr<float>(), alpha.data_ptr<float>(), rnorm.data_ptr<float>(),
+                           out.numel() / d, d, eps, stream()), "depth_mix_fwd");
+}
+void depth_mix_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& dsrc, const Tensor& ueff, const Tensor& dh, const Tensor& alpha,
+                   const Tensor& rnorm, Tensor& du) {
+  const c10::cuda::CUDAGuard guard(dh.device());
+  const int d = dh.size(-1);
+  TORCH_CHECK(is_f32(dh) && dh.is_contiguous() && is_f32(du), "depth_mix_bwd: fp32");
+  std::vector<const float*> p; std::vector<float*> q;
+  for (auto& s : src) p.push_back(s.data_ptr<float>());
+  for (auto& s : dsrc) { TORCH_CHECK(is_f32(s) && s.is_contiguous(), "depth_mix_bwd: fp32 outputs"); q.push_back(s.data_ptr<float>()); }
+  check(ghb::depth_mix_bwd(p.data(), q.data(), p.size(), ueff.data_ptr<float>(), dh.data_ptr<float>(), alpha.data_ptr<float>(), rnorm.data_ptr<float>(),
+                           du.data_ptr<float>(), dh.numel() / d, d, sm_count(), stream()), "depth_mix_bwd");
+}
+
+void ce_grad(const Tensor& logits, const Tensor& targets, const Tensor& a, const Tensor& b, Tensor& grad, Tensor& ce, Tensor& lse) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(is_f32(logits) && logits.is_contiguous() && is_bf16(grad) && grad.is_contiguous() && targets.scalar_type() == torch::kInt64 &&
+              targets.is_contiguous() && is_f32(a) && a.is_contiguous() && is_f32(b) && b.is_contiguous(), "ce_grad: layout");
+  const long rows = logits.size(0);
+  const int V = logits.size(1), s = targets.numel() / rows;
+  check(ghb::ce_grad(logits.data_ptr<float>(), reinterpret_cast<const long*>(targets.data_ptr<int64_t>()), a.data_ptr<float>(), b.data_ptr<float>(),
+                     grad.data_ptr(), ce.data_ptr<float>(), lse.data_ptr<float>(), rows, V, s, stream()), "ce_grad");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("silu_mul_fwd", &silu_mul_fwd);
+  m.def("silu_mul_bwd", &silu_mul_bwd);
+  m.def("adamw", &adamw);
+  m.def("sumsq", &sumsq);
+  m.def("cast_bf16", &cast_bf16);
+  m.def("gdn_prep_fwd", &gdn_prep_fwd);
+  m.def("gdn_prep_bwd", &gdn_prep_bwd);
+  m.def("depth_mix_fwd", &depth_mix_fwd);
+  m.def("depth_mix_bwd", &depth_mix_bwd);
+  m.def("ce_grad", &ce_grad);
+}

@@ -1,0 +1,381 @@
+// Fused model-specific kernels: GDN input preparation (causal document-masked conv + SiLU + L2 norm), the depth-mix
+// softmax combine over finished blocks, and the cross-entropy gradient of one chunk of logits.
+//
+// Reference behaviour: ced/model/gdn.py:218-258, 692-699 (conv taps of another document contribute nothing; q, k
+// L2-normalised with eps 1e-6, q scaled by dk^-0.5); ced/model/attn_res.py:457-482 (logit = (v . w(1+g)) rsqrt(mean
+// v^2 + eps), softmax over sources, weighted sum, >= fp32); ced/train/fused_head.py:56-110 (online LSE over the
+// vocabulary; logits overwritten by softmax * (a + 2 b lse) - a onehot).
+#include "kernels.h"
+#include <cuda_bf16.h>
+
+namespace ghb {
+
+__device__ __forceinline__ float wsum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float wmax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float sigm(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
+  uint2 t = *reinterpret_cast<const uint2*>(p);
+  float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&t.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&t.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t; t.x = *reinterpret_cast<uint32_t*>(&a); t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+// ================================================================================================ GDN input prep
+// Work unit: one token x one group of 128 channels (a q head, a k head, or a 128-wide slice of v); one warp per unit,
+// 4 channels per lane. K = 4 taps. doc == nullptr means every row is a single document (only t - j >= 0 is checked).
+// Channels [0, nq) are q (norm + scale), [nq, 2nq) are k (norm), the rest v (no norm). dk must be 128.
+constexpr int PREP_K = 4;
+
+__device__ __forceinline__ void conv_taps(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, long row, int t, int C,
+                                          int c, const float* __restrict__ w, float (&out)[4]) {
+  float wt[4][PREP_K];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c + e) * PREP_K); wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w; }
+  out[0] = out[1] = out[2] = out[3] = 0.f;
+  const int my_doc = doc ? doc[row] : 0;
+#pragma unroll
+  for (int j = 0; j < PREP_K; ++j) {   // tap j looks j steps back and uses weight column K-1-j
+    if (t - j < 0) break;
+    if (doc && doc[row - j] != my_doc) break;   // document ids increase along a row: once different, always different
+    float x[4]; ld4(u + (row - j) * C + c, x);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) out[e] += x[e] * wt[e][PREP_K - 1 - j];
+  }
+}
+
+__global__ void gdn_prep_fwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                    __nv_bfloat16* __restrict__ out, long rows, int L, int C, int nq, float qscale) {
+  const int lane = threadIdx.x & 31;
+  const int groups = C / 128;
+  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * groups) return;
+  const long row = unit / groups; const int grp = static_cast<int>(unit % groups);
+  const int t = static_cast<int>(row % L), c = grp * 128 + lane * 4;
+  float a[4];
+  conv_taps(u, doc, row, t, C, c, w, a);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) a[e] = a[e] * sigm(a[e]);
+  if (c < 2 * nq) {
+    float ss = wsum(a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3]);
+    const float r = rsqrtf(ss + 1e-6f) * (c < nq ? qscale : 1.f);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[e] *= r;
+  }
+  st4(out + row * C + c, a);
+}
+
+// Backward part 1: gradient w.r.t. the conv output (pre-SiLU), dconv (rows, C) bf16, recomputing the forward values.
+__global__ void gdn_prep_bwd_conv_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                         const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dconv, long rows, int L,
+                                         int C, int nq, float qscale) {
+  const int lane = threadIdx.x & 31;
+  const int groups = C / 128;
+  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * groups) return;
+  const long row = unit / groups; const int grp = static_cast<int>(unit % groups);
+  const int t = static_cast<int>(row % L), c = grp * 128 + lane * 4;
+  float pre[4], a[4], dy[4], da[4];
+  conv_taps(u, doc, row, t, C, c, w, pre);
+  ld4(dout + row * C + c, dy);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) a[e] = pre[e] * sigm(pre[e]);
+  if (c < 2 * nq) {
+    const float ss = wsum(a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3]);
+    const float r = rsqrtf(ss + 1e-6f), s = c < nq ? qscale : 1.f;
+    const float ady = wsum(a[0] * dy[0] + a[1] * dy[1] + a[2] * dy[2] + a[3] * dy[3]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) da[e] = s * r * (dy[e] - a[e] * r * r * ady);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) da[e] = dy[e];
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float sg = sigm(pre[e]); da[e] *= sg * (1.f + pre[e] * (1.f - sg)); }
+  st4(dconv + row * C + c, da);
+}
+
+// Backward part 2: du[t] = sum_j dconv[t + j] w[K-1-j] over later tokens of the same document, and the conv-weight
+// gradient dw[c][K-1-j] += sum_t dconv[t] u[t - j]. One warp walks TOK consecutive tokens of one 128-channel group.
+__global__ void gdn_prep_bwd_input_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                          const __nv_bfloat16* __restrict__ dconv, __nv_bfloat16* __restrict__ du, float* __restrict__ dw,
+                                          long rows, int L, int C, int tok_per_warp) {
+  const int lane = threadIdx.x & 31;
+  const int groups = C / 128;
+  const long chunks = (rows + tok_per_warp - 1) / tok_per_warp;
+  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= chunks * groups) return;
+  const long chunk = unit / groups; const int grp = static_cast<int>(unit % groups);
+  const int c = grp * 128 + lane * 4;
+  float wt[4][PREP_K], acc[4][PREP_K];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c + e) * PREP_K);
+    wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w;
+#pragma unroll
+    for (int j = 0; j < PREP_K; ++j) acc[e][j] = 0.f;
+  }
+  const long r0 = chunk * tok_per_warp, r1 = min(rows, r0 + tok_per_warp);
+  for (long row = r0; row < r1; ++row) {
+    const int t = static_cast<int>(row % L);
+    const int my_doc = doc ? doc[row] : 0;
+    float x[4], g[4] = {0.f, 0.f, 0.f, 0.f};
+    ld4(u + row * C + c, x);
+#pragma unroll
+    for (int j = 0; j < PREP_K; ++j) {   // token row + j reads this token through tap j
+      if (t + j >= L) break;
+      if (doc && doc[row + j] != my_doc) break;
+      float d[4]; ld4(dconv + (row + j) * C + c, d);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { g[e] += d[e] * wt[e][PREP_K - 1 - j]; acc[e][PREP_K - 1 - j] += d[e] * x[e]; }
+    }
+    st4(du + row * C + c, g);
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e)
+#pragma unroll
+    for (int j = 0; j < PREP_K; ++j) atomicAdd(dw + static_cast<long>(c + e) * PREP_K + j, acc[e][j]);
+}
+
+int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long rows, int L, int C, int nq, float qscale, cudaStream_t st) {
+  if (C % 128 || nq % 128) return 1;
+  const long units = rows * (C / 128);
+  gdn_prep_fwd_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<__nv_bfloat16*>(out), rows, L, C, nq, qscale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* dconv, void* du, float* dw, long rows, int L, int C,
+                 int nq, float qscale, cudaStream_t st) {
+  if (C % 128 || nq % 128) return 1;
+  const long units = rows * (C / 128);
+  gdn_prep_bwd_conv_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dout),
+                                                                                  static_cast<__nv_bfloat16*>(dconv), rows, L, C, nq, qscale);
+  const int tok = 64;
+  const long units2 = ((rows + tok - 1) / tok) * (C / 128);
+  gdn_prep_bwd_input_kernel<<<static_cast<unsigned>((units2 + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dconv),
+                                                                                    static_cast<__nv_bfloat16*>(du), dw, rows, L, C, tok);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// ================================================================================================ depth mix
+// One CTA of 128 threads per row; thread holds VPT float4 of every source (d = 512 * VPT). Sources fp32.
+constexpr int MIX_MAX = 8;
+struct MixPtrs { const float* src[MIX_MAX]; float* dsrc[MIX_MAX]; };
+
+__device__ __forceinline__ float block_sum_128(float v, float* sh) {
+  v = wsum(v);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = sh[0] + sh[1] + sh[2] + sh[3];
+  __syncthreads();
+  return t;
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(128) depth_mix_fwd_kernel(MixPtrs p, int n, const float* __restrict__ ueff, float* __restrict__ out,
+                                                            float* __restrict__ alpha, float* __restrict__ rnorm, int d, float eps) {
+  __shared__ float sh[4];
+  const long row = blockIdx.x;
+  float4 v[MIX_MAX][VPT];
+  float logit[MIX_MAX];
+  float4 uq[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) uq[k] = reinterpret_cast<const float4*>(ueff)[k * 128 + threadIdx.x];
+#pragma unroll
+  for (int i = 0; i < MIX_MAX; ++i) {
+    if (i < n) {
+      float dot = 0.f, ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        v[i][k] = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
+        dot += v[i][k].x * uq[k].x + v[i][k].y * uq[k].y + v[i][k].z * uq[k].z + v[i][k].w * uq[k].w;
+        ss += v[i][k].x * v[i][k].x + v[i][k].y * v[i][k].y + v[i][k].z * v[i][k].z + v[i][k].w * v[i][k].w;
+      }
+      dot = block_sum_128(dot, sh);
+      ss = block_sum_128(ss, sh);
+      const float r = rsqrtf(ss / d + eps);
+      logit[i] = dot * r;
+      if (threadIdx.x == 0) rnorm[row * n + i] = r;
+    } else logit[i] = -INFINITY;
+  }
+  float mx = -INFINITY, den = 0.f;
+#pragma unroll
+  for (int i = 0; i < MIX_MAX; ++i) mx = fmaxf(mx, logit[i]);
+#pragma unroll
+  for (int i = 0; i < MIX_MAX; ++i) { logit[i] = i < n ? __expf(logit[i] - mx) : 0.f; den += logit[i]; }
+  float4 acc[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < MIX_MAX; ++i) {
+    if (i < n) {
+      const float a = logit[i] / den;
+      if (threadIdx.x == 0) alpha[row * n + i] = a;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) { acc[k].x += a * v[i][k].x; acc[k].y += a * v[i][k].y; acc[k].z += a * v[i][k].z; acc[k].w += a * v[i][k].w; }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) reinterpret_cast<float4*>(out + row * d)[k * 128 + threadIdx.x] = acc[k];
+}
+
+// dv_i = alpha_i dh + dl_i (u r_i - (v_i . u) r_i^3 v_i / d), dl_i = alpha_i (dh . v_i - sum_j alpha_j dh . v_j);
+// du += sum_i dl_i r_i v_i (accumulated per CTA over a grid-stride of rows, then atomics).
+template <int VPT>
+__global__ void __launch_bounds__(128) depth_mix_bwd_kernel(MixPtrs p, int n, const float* __restrict__ ueff, const float* __restrict__ dh,
+                                                            const float* __restrict__ alpha, const float* __restrict__ rnorm,
+                                                            float* __restrict__ du, long rows, int d) {
+  __shared__ float sh[4];
+  float4 uq[VPT], dacc[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) { uq[k] = reinterpret_cast<const float4*>(ueff)[k * 128 + threadIdx.x]; dacc[k] = make_float4(0.f, 0.f, 0.f, 0.f); }
+  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+    float4 g[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) g[k] = reinterpret_cast<const float4*>(dh + row * d)[k * 128 + threadIdx.x];
+    float da[MIX_MAX], vu[MIX_MAX];
+    float mean = 0.f;
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i) {
+      da[i] = 0.f; vu[i] = 0.f;
+      if (i < n) {
+        float a = 0.f, b = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const float4 v = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
+          a += g[k].x * v.x + g[k].y * v.y + g[k].z * v.z + g[k].w * v.w;
+          b += uq[k].x * v.x + uq[k].y * v.y + uq[k].z * v.z + uq[k].w * v.w;
+        }
+        da[i] = block_sum_128(a, sh);
+        vu[i] = block_sum_128(b, sh);
+        mean += alpha[row * n + i] * da[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i) {
+      if (i < n) {
+        const float al = alpha[row * n + i], r = rnorm[row * n + i];
+        const float dl = al * (da[i] - mean);
+        const float c1 = dl * r, c2 = dl * vu[i] * r * r * r / d;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+          const float4 v = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
+          float4 o;
+          o.x = al * g[k].x + c1 * uq[k].x - c2 * v.x; o.y = al * g[k].y + c1 * uq[k].y - c2 * v.y;
+          o.z = al * g[k].z + c1 * uq[k].z - c2 * v.z; o.w = al * g[k].w + c1 * uq[k].w - c2 * v.w;
+          reinterpret_cast<float4*>(p.dsrc[i] + row * d)[k * 128 + threadIdx.x] = o;
+          dacc[k].x += c1 * v.x; dacc[k].y += c1 * v.y; dacc[k].z += c1 * v.z; dacc[k].w += c1 * v.w;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    float* o = du + (k * 128 + threadIdx.x) * 4;
+    atomicAdd(o, dacc[k].x); atomicAdd(o + 1, dacc[k].y); atomicAdd(o + 2, dacc[k].z); atomicAdd(o + 3, dacc[k].w);
+  }
+}
+
+int depth_mix_fwd(const float* const* src, int n, const float* ueff, float* out, float* alpha, float* rnorm, long rows, int d, float eps,
+                  cudaStream_t st) {
+  if (n < 1 || n > MIX_MAX || d % 512 || d > 2048) return 1;
+  MixPtrs p{};
+  for (int i = 0; i < n; ++i) p.src[i] = src[i];
+  switch (d / 512) {
+    case 1: depth_mix_fwd_kernel<1><<<static_cast<unsigned>(rows), 128, 0, st>>>(p, n, ueff, out, alpha, rnorm, d, eps); break;
+    case 2: depth_mix_fwd_kernel<2><<<static_cast<unsigned>(rows), 128, 0, st>>>(p, n, ueff, out, alpha, rnorm, d, eps); break;
+    case 4: depth_mix_fwd_kernel<4><<<static_cast<unsigned>(rows), 128, 0, st>>>(p, n, ueff, out, alpha, rnorm, d, eps); break;
+    default: return 1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const float* ueff, const float* dh, const float* alpha,
+                  const float* rnorm, float* du, long rows, int d, int sms, cudaStream_t st) {
+  if (n < 1 || n > MIX_MAX || d % 512 || d > 2048) return 1;
+  MixPtrs p{};
+  for (int i = 0; i < n; ++i) { p.src[i] = src[i]; p.dsrc[i] = dsrc[i]; }
+  const unsigned grid = static_cast<unsigned>(rows < sms * 16L ? rows : sms * 16L);
+  switch (d / 512) {
+    case 1: depth_mix_bwd_kernel<1><<<grid, 128, 0, st>>>(p, n, ueff, dh, alpha, rnorm, du, rows, d); break;
+    case 2: depth_mix_bwd_kernel<2><<<grid, 128, 0, st>>>(p, n, ueff, dh, alpha, rnorm, du, rows, d); break;
+    case 4: depth_mix_bwd_kernel<4><<<grid, 128, 0, st>>>(p, n, ueff, dh, alpha, rnorm, du, rows, d); break;
+    default: return 1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// ================================================================================================ CE gradient
+// One CTA per row of fp32 logits (n, V). Pass 1: online max / sum over the row (kept in shared memory when it fits),
+// pass 2: grad = softmax * (asum + 2 b lse) written as bf16 in a separate (n, V) buffer, then the s targets subtract
+// their weights. ce[row] = sum_k a_k (lse - logit[t_k]); lse[row] saved.
+__global__ void __launch_bounds__(512) ce_grad_kernel(const float* __restrict__ logits, const long* __restrict__ targets, const float* __restrict__ a,
+                                                      const float* __restrict__ b, __nv_bfloat16* __restrict__ grad, float* __restrict__ ce,
+                                                      float* __restrict__ lse_out, int V, int s, int cache_row) {
+  extern __shared__ float rowbuf[];
+  __shared__ float redm[16], reds[16];
+  const long row = blockIdx.x;
+  const float* lr = logits + row * V;
+  float m = -INFINITY, sum = 0.f;
+  for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
+    float4 t = *reinterpret_cast<const float4*>(lr + i);
+    if (cache_row) *reinterpret_cast<float4*>(rowbuf + i) = t;
+    const float mm = fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w));
+    if (mm > m) { sum *= __expf(m - mm); m = mm; }
+    sum += __expf(t.x - m) + __expf(t.y - m) + __expf(t.z - m) + __expf(t.w - m);
+  }
+  const float wm = wmax(m);
+  sum *= __expf(m - wm);
+  sum = wsum(sum);
+  if ((threadIdx.x & 31) == 0) { redm[threadIdx.x >> 5] = wm; reds[threadIdx.x >> 5] = sum; }
+  __syncthreads();
+  float gm = -INFINITY, gs = 0.f;
+  const int nw = blockDim.x >> 5;
+  for (int i = 0; i < nw; ++i) gm = fmaxf(gm, redm[i]);
+  for (int i = 0; i < nw; ++i) gs += reds[i] * __expf(redm[i] - gm);
+  const float lse = gm + __logf(gs);
+  float asum = 0.f;
+  for (int k = 0; k < s; ++k) asum += a[row * s + k];
+  const float coef = asum + 2.f * b[row] * lse;
+  __nv_bfloat16* gr = grad + row * V;
+  for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
+    float4 t = cache_row ? *reinterpret_cast<const float4*>(rowbuf + i) : *reinterpret_cast<const float4*>(lr + i);
+    float o[4] = {coef * __expf(t.x - lse), coef * __expf(t.y - lse), coef * __expf(t.z - lse), coef * __expf(t.w - lse)};
+    st4(gr + i, o);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float c = 0.f;
+    for (int k = 0; k < s; ++k) {
+      const float ak = a[row * s + k];
+      const long t = targets[row * s + k];
+      if (ak != 0.f && t >= 0 && t < V) {
+        c += ak * (lse - lr[t]);
+        gr[t] = __float2bfloat16(__bfloat162float(gr[t]) - ak);
+      }
+    }
+    ce[row] = c;
+    lse_out[row] = lse;
+  }
+}
+int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,
+            int s, cudaStream_t st) {
+  if (V % 4) return 1;
+  const size_t bytes = static_cast<size_t>(V) * 4;
+  const int cache = bytes <= 200 * 1024;
+  static bool attr = false;
+  if (!attr) { cudaFuncSetAttribute(ce_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+  ce_grad_kernel<<<static_cast<unsigned>(rows), 512, cache ? bytes : 0, st>>>(logits, targets, a, b, static_cast<__nv_bfloat16*>(grad), ce, lse, V, s, cache);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+}  // namespace ghb

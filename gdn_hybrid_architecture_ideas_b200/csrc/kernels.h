@@ -1,0 +1,39 @@
+// Host-callable launchers of the sm_100a kernels (raw pointers + stream; no framework types), and the TMA descriptor
+// helper shared by the kernels that use tensor maps.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ghb {
+
+// Encodes a 2-D tiled tensor map through the driver entry point resolved at run time (no link dependency on libcuda).
+// dims/box: innermost first; strides: bytes of dimension 1. Returns false if the driver refuses the descriptor.
+bool encode_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes, const uint64_t dims[2], const uint64_t strides[1],
+                          const uint32_t box[2], bool swizzle128);
+
+int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn,
+              int out, int* err, int sms, cudaStream_t stream);
+
+int rmsnorm_fwd(const void* x, int in_bf16, const float* w, int w_scalar, const void* z, int gate, const float* resid, void* y,
+                int out_bf16, float* rstd, long rows, int d, float eps, float scale, cudaStream_t st);
+int rmsnorm_bwd(const void* dy, int dy_bf16, const void* x, int x_bf16, const float* w, int w_scalar, const void* z, int gate,
+                const float* rstd, const float* dres, void* dx, void* dz, float* dw, long rows, int d, float scale, int sms, cudaStream_t st);
+int silu_mul_fwd(const void* g, const void* u, long ld, void* h, long rows, int f, int sms, cudaStream_t st);
+int silu_mul_bwd(const void* dh, const void* g, const void* u, long ld, void* dg, void* du, long rows, int f, int sms, cudaStream_t st);
+int adamw(float* p, const float* g, float* m, float* v, void* lp, long n, float lr, float b1, float b2, float eps, float wd, float c1,
+          float c2, const float* grad_scale, float scale_host, int sms, cudaStream_t st);
+int sumsq_partials(const float* x, long n, float* partial, int blocks, cudaStream_t st);
+int cast_bf16(const float* x, void* y, long n, int sms, cudaStream_t st);
+
+int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long rows, int L, int C, int nq, float qscale, cudaStream_t st);
+int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* dconv, void* du, float* dw, long rows, int L, int C,
+                 int nq, float qscale, cudaStream_t st);
+int depth_mix_fwd(const float* const* src, int n, const float* ueff, float* out, float* alpha, float* rnorm, long rows, int d, float eps,
+                  cudaStream_t st);
+int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const float* ueff, const float* dh, const float* alpha,
+                  const float* rnorm, float* du, long rows, int d, int sms, cudaStream_t st);
+int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,
+            int s, cudaStream_t st);
+
+}  // namespace ghb

@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 import torch.utils.checkpoint as ckpt
 
+from .. import ops
 from ..config import ModelConfig
 from .attention import GatedAttention
 from .depth_mix import EntryLayer
@@ -68,10 +69,10 @@ class EncoderLayer(nn.Module):
             mixed, new_cache = self.mixer(h, ctx, cache, need_state=need_state)
         else:
             mixed, new_cache = self.mixer(h, ctx, cache)
-        y = x + self.residual_scale * self.mixer_out_norm(mixed)
+        y = ops.norm_add(x, mixed, self.mixer_out_norm.weight, self.mixer_out_norm.eps, self.residual_scale)
         if self.stream_bf16:
             y = round_stream(y)
-        y = y + self.residual_scale * self.mlp_out_norm(self.mlp(self.mlp_in_norm(y)))
+        y = ops.norm_add(y, self.mlp(self.mlp_in_norm(y)), self.mlp_out_norm.weight, self.mlp_out_norm.eps, self.residual_scale)
         if self.stream_bf16:
             y = round_stream(y)
         return y, new_cache

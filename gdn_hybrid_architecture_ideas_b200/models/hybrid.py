@@ -63,7 +63,8 @@ class HybridLM(nn.Module):
     lm_head_weight = head_weight
 
     def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
-        return self.embed_norm(ops.embedding(tokens, self.embed.weight))
+        e = ops.embedding(tokens, self.embed.weight)
+        return self.embed_norm(e, out_dtype=e.dtype) if self.cfg.embed_norm else e   # the residual stream keeps the table's dtype
 
     def forward(self, tokens: torch.Tensor, doc_ids: torch.Tensor, dec_mask=None, T=None, capacity=None,
                 cache: ControlCache | None = None, return_cache: bool = False, return_hidden: bool = False,

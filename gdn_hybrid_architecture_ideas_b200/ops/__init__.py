@@ -97,6 +97,24 @@ def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=
     return ref.attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok, q_far, k_far, cap)
 
 
+def norm_add(resid, branch, weight, eps, scale):
+    """resid + scale * rmsnorm(branch): the Peri-LN residual update."""
+    if use_native(branch):
+        return _native().norm_add(resid, branch, weight, eps, scale)
+    return resid + scale * ref.rmsnorm(branch, weight, eps)
+
+
+def launch_count() -> int:
+    """Kernels of this framework launched since the last reset (bench.py reports it)."""
+    from . import native
+    return native.launch_count()
+
+
+def reset_launch_count() -> None:
+    from . import native
+    native.reset_launch_count()
+
+
 def depth_mix(sources, query, gain, eps):
     if use_native(sources[0]):
         return _native().depth_mix(sources, query, gain, eps)

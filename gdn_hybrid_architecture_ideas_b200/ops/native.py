@@ -1,0 +1,410 @@
+"""CUDA path of the op layer: `torch.autograd.Function`s over the in-tree sm_100a extension `_native.so`.
+
+Precision policy (the reference's "float32 master weights + bfloat16 autocast", ced/train/trainer.py:1241-1886, made
+explicit): GEMM operands are bfloat16 with fp32 accumulation; the residual stream, norm statistics, softmaxes, the
+loss and the optimizer are fp32. A Linear reads its bfloat16 shadow weight (`weight_lp`, refreshed by the fused
+AdamW kernel) when one exists, else casts the master weight.
+
+Importing this module on a machine with a GPU but without the built extension raises: there is no silent fallback.
+"""
+
+from __future__ import annotations
+
+import importlib.util
+from pathlib import Path
+
+import torch
+
+from . import reference as ref
+
+_SO = Path(__file__).resolve().parent.parent / "_native.so"
+_ext = None
+_launches = 0
+_err = {}
+
+
+def ext():
+    global _ext
+    if _ext is None:
+        if not _SO.exists():
+            raise RuntimeError(f"native extension {_SO} is not built: run `python -m gdn_hybrid_architecture_ideas_b200.build`")
+        spec = importlib.util.spec_from_file_location("_native", _SO)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _ext = mod
+    return _ext
+
+
+def _count(n: int = 1) -> None:
+    global _launches
+    _launches += n
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
+def err_flag(device) -> torch.Tensor:
+    """Per-device int32 status word the tensor-core kernels write when a bounded wait gives up (0 = clean)."""
+    key = torch.device(device).index or 0
+    if key not in _err:
+        _err[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _err[key]
+
+
+def check_status(device=None) -> None:
+    """Raises if any kernel reported a protocol timeout since the last check (one host read)."""
+    for key, flag in _err.items():
+        code = int(flag.item())
+        if code:
+            flag.zero_()
+            raise RuntimeError(f"sm_100a kernel reported status {code} on cuda:{key} (a bounded wait gave up)")
+
+
+BF16 = torch.bfloat16
+
+
+def _bf16(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == BF16 else t.to(BF16)
+
+
+# ------------------------------------------------------------------------------------------------------------ GEMM
+
+def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=BF16):
+    """out = a b^T (+ out): a [M,K] (or [K,M] with a_mn), b [N,K] (or [K,N] with b_mn), bf16 operands."""
+    M = a.shape[1] if a_mn else a.shape[0]
+    N = b.shape[1] if b_mn else b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    ext().gemm(a, b, out, a_mn, b_mn, accumulate, err_flag(a.device))
+    _count()
+    return out
+
+
+def _w_lp(lin) -> torch.Tensor:
+    lp = getattr(lin, "weight_lp", None)
+    return lp if lp is not None else lin.weight.detach().to(BF16)
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, w_lp):
+        x2 = _bf16(x).reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        y = gemm(x2, w_lp)
+        ctx.save_for_backward(x2, w_lp)
+        ctx.xshape, ctx.xdtype = x.shape, x.dtype
+        return y.view(*x.shape[:-1], w_lp.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_lp = ctx.saved_tensors
+        dy2 = _bf16(dy).reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w_lp, b_mn=True).view(ctx.xshape)           # dy [M,N] . W [N,K]
+            if ctx.xdtype != BF16:
+                dx = dx.to(ctx.xdtype)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)   # dy^T [N,M] . x [M,K]
+        return dx, dw, None
+
+
+def linear(x, lin):
+    if getattr(lin, "precision", "bf16") != "bf16" and lin.training:
+        from . import lowp
+
+        return lowp.native_linear(x, lin)
+    return _Linear.apply(x, lin.weight, _w_lp(lin))
+
+
+# ------------------------------------------------------------------------------------------------------------ norms
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps, out_dtype, z, gate, resid, scale):
+        xc = x.contiguous()
+        y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        rstd = torch.empty(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device)
+        zc = None if z is None else _bf16(z).contiguous()
+        ext().rmsnorm_fwd(xc, weight, zc, gate, None if resid is None else resid.contiguous(), y, rstd, eps, scale)
+        _count()
+        ctx.save_for_backward(xc, weight, rstd, zc)
+        ctx.gate, ctx.scale, ctx.has_resid = gate, scale, resid is not None
+        ctx.zdtype = None if z is None else z.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, weight, rstd, zc = ctx.saved_tensors
+        dy = dy.contiguous()
+        if dy.dtype not in (BF16, torch.float32):
+            dy = dy.float()
+        dx = torch.empty_like(xc)
+        dz = torch.empty_like(zc) if zc is not None else None
+        dw = torch.zeros_like(weight)
+        ext().rmsnorm_bwd(dy, xc, weight, zc, ctx.gate, rstd, None, dx, dz, dw, ctx.scale)
+        _count()
+        if dz is not None and ctx.zdtype != BF16:
+            dz = dz.to(ctx.zdtype)
+        return dx, dw, None, None, dz, None, (dy if ctx.has_resid else None), None
+
+
+def _norm_ok(x, weight) -> bool:
+    return x.dtype in (BF16, torch.float32) and weight.dtype == torch.float32 and x.shape[-1] % 4 == 0 and x.shape[-1] <= 2048
+
+
+def rmsnorm(x, weight, eps, out_dtype=None):
+    if not _norm_ok(x, weight):
+        return ref.rmsnorm(x, weight, eps, out_dtype)
+    return _RMSNorm.apply(x, weight, eps, out_dtype or BF16, None, 0, None, 1.0)
+
+
+def gated_rmsnorm(x, z, weight, eps, gate, out_dtype=None):
+    if not _norm_ok(x, weight):
+        return ref.gated_rmsnorm(x, z, weight, eps, gate, out_dtype)
+    return _RMSNorm.apply(x, weight, eps, out_dtype or BF16, z, 1 if gate == "silu" else 2, None, 1.0)
+
+
+def norm_add(resid, branch, weight, eps, scale):
+    """resid + scale * rmsnorm(branch) in fp32, one pass."""
+    if not _norm_ok(branch, weight) or resid.dtype != torch.float32:
+        return resid + scale * ref.rmsnorm(branch, weight, eps)
+    return _RMSNorm.apply(branch, weight, eps, torch.float32, None, 0, resid, float(scale))
+
+
+# ------------------------------------------------------------------------------------------------------------ MLP
+
+class _SiluMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        f = gu.shape[-1] // 2
+        h = torch.empty(*gu.shape[:-1], f, dtype=BF16, device=gu.device)
+        ext().silu_mul_fwd(gu, h)
+        _count()
+        ctx.save_for_backward(gu)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        (gu,) = ctx.saved_tensors
+        dgu = torch.empty_like(gu)
+        ext().silu_mul_bwd(_bf16(dh).contiguous(), gu, dgu)
+        _count()
+        return dgu
+
+
+class _CatLinear(torch.autograd.Function):
+    """y = x [W1; W2]^T as one GEMM when the two shadow weights are adjacent in the flat buffer (else two GEMMs into
+    one output), returning the concatenated [.., n1 + n2] activations; gradients go to each weight separately."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2, lp1, lp2):
+        x2 = _bf16(x).reshape(-1, x.shape[-1]).contiguous()
+        n1, n2 = lp1.shape[0], lp2.shape[0]
+        out = torch.empty(x2.shape[0], n1 + n2, dtype=BF16, device=x.device)
+        adjacent = (lp1.data_ptr() + lp1.numel() * 2 == lp2.data_ptr()) and lp1.is_contiguous() and lp2.is_contiguous()
+        if adjacent:
+            wcat = torch.as_strided(lp1, (n1 + n2, lp1.shape[1]), (lp1.shape[1], 1))
+            gemm(x2, wcat, out=out)
+        else:
+            wcat = None
+            gemm(x2, lp1, out=out[:, :n1])
+            gemm(x2, lp2, out=out[:, n1:])
+        ctx.save_for_backward(x2, lp1, lp2)
+        ctx.adjacent, ctx.xshape, ctx.xdtype = adjacent, x.shape, x.dtype
+        return out.view(*x.shape[:-1], n1 + n2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, lp1, lp2 = ctx.saved_tensors
+        n1, n2 = lp1.shape[0], lp2.shape[0]
+        dy2 = _bf16(dy).reshape(-1, n1 + n2).contiguous()
+        if ctx.adjacent:
+            wcat = torch.as_strided(lp1, (n1 + n2, lp1.shape[1]), (lp1.shape[1], 1))
+            dx = gemm(dy2, wcat, b_mn=True)
+        else:
+            dx = gemm(dy2[:, :n1], lp1, b_mn=True, out_dtype=torch.float32)
+            gemm(dy2[:, n1:], lp2, b_mn=True, out=dx, accumulate=True)
+            dx = dx.to(BF16)
+        dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dx = dx.view(ctx.xshape)
+        return (dx if ctx.xdtype == BF16 else dx.to(ctx.xdtype)), dw[:n1], dw[n1:], None, None
+
+
+def swiglu_mlp(x, w_gate, w_up, w_down):
+    if any(getattr(m, "precision", "bf16") != "bf16" and m.training for m in (w_gate, w_up, w_down)):
+        return linear(torch.nn.functional.silu(linear(x, w_gate)) * linear(x, w_up), w_down)
+    gu = _CatLinear.apply(x, w_gate.weight, w_up.weight, _w_lp(w_gate), _w_lp(w_up))
+    return linear(_SiluMul.apply(gu), w_down)
+
+
+# ------------------------------------------------------------------------------------------------------------ GDN prep / gates
+
+class _GdnPrep(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, u_pre, doc32, conv_weight, L, nq, qscale):
+        u = _bf16(u_pre).contiguous()
+        out = torch.empty_like(u)
+        ext().gdn_prep_fwd(u, doc32, conv_weight, out, L, nq, qscale)
+        _count()
+        ctx.save_for_backward(u, doc32, conv_weight)
+        ctx.meta = (L, nq, qscale, u_pre.dtype)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        u, doc32, w = ctx.saved_tensors
+        L, nq, qscale, dt = ctx.meta
+        dconv, du = torch.empty_like(u), torch.empty_like(u)
+        dw = torch.zeros_like(w)
+        ext().gdn_prep_bwd(u, doc32, w, _bf16(dout).contiguous(), dconv, du, dw, L, nq, qscale)
+        _count(2)
+        return (du if dt == BF16 else du.to(dt)), None, dw, None, None, None
+
+
+def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc=False):
+    B, L, C = u_pre.shape
+    ok = dk == 128 and (hv * dv) % 128 == 0 and conv_weight.shape[1] == 4 and conv_weight.dtype == torch.float32
+    if not ok:
+        return ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv)
+    doc32 = None if single_doc else doc.to(torch.int32).contiguous()
+    out = _GdnPrep.apply(u_pre, doc32, conv_weight, L, hk * dk, dk ** -0.5)
+    nq = hk * dk
+    q = out[..., :nq].view(B, L, hk, dk)
+    k = out[..., nq:2 * nq].view(B, L, hk, dk)
+    v = out[..., 2 * nq:].view(B, L, hv, dv)
+    K = conv_weight.shape[1]
+    return q, k, v, u_pre[:, L - (K - 1):], doc[:, L - (K - 1):]
+
+
+def gdn_gates(a_lin, b_lin, A_log, dt_bias):
+    """Tiny (B, L, Hv) elementwise maths in fp32; left to the framework's elementwise kernels."""
+    g = -torch.exp(A_log) * torch.nn.functional.softplus(a_lin.float() + dt_bias)
+    return g, torch.sigmoid(b_lin.float())
+
+
+# ------------------------------------------------------------------------------------------------------------ depth mix
+
+class _DepthMix(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, query, gain, eps, *sources):
+        srcs = [s.contiguous() for s in sources]
+        ueff = (query * (1.0 + gain)).contiguous()
+        out = torch.empty_like(srcs[0])
+        rows = out.numel() // out.shape[-1]
+        alpha = torch.empty(rows, len(srcs), dtype=torch.float32, device=out.device)
+        rnorm = torch.empty_like(alpha)
+        ext().depth_mix_fwd(srcs, ueff, out, alpha, rnorm, eps)
+        _count()
+        ctx.save_for_backward(query, gain, ueff, alpha, rnorm, *srcs)
+        return out
+
+    @staticmethod
+    def backward(ctx, dh):
+        query, gain, ueff, alpha, rnorm, *srcs = ctx.saved_tensors
+        dsrc = [torch.empty_like(s) for s in srcs]
+        du = torch.zeros_like(ueff)
+        ext().depth_mix_bwd(srcs, dsrc, ueff, dh.contiguous().float(), alpha, rnorm, du)
+        _count()
+        return (du * (1.0 + gain), du * query, None, *dsrc)
+
+
+def depth_mix(sources, query, gain, eps):
+    d = sources[0].shape[-1]
+    if len(sources) > 8 or d % 512 or d > 2048 or any(s.dtype != torch.float32 for s in sources):
+        return ref.depth_mix(sources, query, gain, eps)
+    return _DepthMix.apply(query, gain, eps, *sources)
+
+
+# ------------------------------------------------------------------------------------------------------------ fused head + CE
+
+class _FusedLinearCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, a, b, chunk, w_lp):
+        d = hidden.shape[-1]
+        h = _bf16(hidden).reshape(-1, d).contiguous()
+        n, V = h.shape[0], w_lp.shape[0]
+        t = targets.reshape(n, -1).contiguous()
+        a2 = a.reshape(n, -1).float().contiguous()
+        b1 = b.reshape(-1).float().contiguous()
+        ce = torch.empty(n, dtype=torch.float32, device=h.device)
+        lse = torch.empty_like(ce)
+        dh = torch.empty(n, d, dtype=BF16, device=h.device)
+        dW = torch.zeros(V, d, dtype=torch.float32, device=h.device)
+        logits = torch.empty(min(chunk, n), V, dtype=torch.float32, device=h.device)
+        grad = torch.empty(min(chunk, n), V, dtype=BF16, device=h.device)
+        for lo in range(0, n, chunk):
+            hi = min(n, lo + chunk)
+            m = hi - lo
+            gemm(h[lo:hi], w_lp, out=logits[:m])
+            ext().ce_grad(logits[:m], t[lo:hi], a2[lo:hi], b1[lo:hi], grad[:m], ce[lo:hi], lse[lo:hi])
+            _count()
+            gemm(grad[:m], w_lp, out=dh[lo:hi], b_mn=True)
+            gemm(grad[:m], h[lo:hi], out=dW, a_mn=True, b_mn=True, accumulate=True)
+        loss = ce.sum() + (b1 * lse * lse).sum()
+        ctx.save_for_backward(dh, dW)
+        ctx.meta = (hidden.dtype, hidden.shape, weight.dtype)
+        ctx.mark_non_differentiable(ce, lse)
+        return loss, ce, lse
+
+    @staticmethod
+    def backward(ctx, g_loss, g_ce, g_lse):
+        dh, dW = ctx.saved_tensors
+        hd, hs, wd = ctx.meta
+        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None, None
+
+
+def fused_linear_ce(hidden, weight, targets, a, b, chunk, weight_lp=None):
+    w_lp = weight_lp if weight_lp is not None else weight.detach().to(BF16)
+    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk, w_lp)
+
+
+def lm_loss_sums(hidden, weight, targets, weights=None, z_loss=0.0, weight_lp=None):
+    n = hidden.reshape(-1, hidden.shape[-1]).shape[0]
+    t = targets.reshape(n, -1)
+    a = torch.ones_like(t, dtype=torch.float32) if weights is None else weights.reshape(n, -1).float()
+    a = a * (t >= 0)
+    b = a.sum(1) * z_loss
+    loss, ce, _ = fused_linear_ce(hidden, weight, t, a, b, 2048, weight_lp)
+    return loss, ce.sum()
+
+
+# ------------------------------------------------------------------------------------------------------------ optimizer
+
+def adamw_(p, g, m, v, lp, lr, b1, b2, eps, wd, c1, c2, grad_scale):
+    gs_t, gs_h = (grad_scale.reshape(1).float(), 1.0) if isinstance(grad_scale, torch.Tensor) else (None, float(grad_scale))
+    ext().adamw(p, g, m, v, lp, lr, b1, b2, eps, wd, c1, c2, gs_t, gs_h)
+    _count()
+
+
+def sumsq(x):
+    _count()
+    return ext().sumsq(x)
+
+
+def cast_bf16_(x, y):
+    ext().cast_bf16(x, y)
+    _count()
+
+
+# ------------------------------------------------------------------------------------------------------------ sequence mixers
+
+def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
+    from . import gdn_native
+
+    return gdn_native.delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state)
+
+
+def attention(q, k, v, doc, q_far, k_far, cap):
+    from . import attention_native
+
+    return attention_native.attention(q, k, v, doc, q_far, k_far, cap)

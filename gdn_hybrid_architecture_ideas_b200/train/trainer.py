@@ -161,7 +161,40 @@ class Trainer:
             ce_sum = ce_sum.detach()
         return loss, ce_sum
 
+    def device_step(self, batch, n_global: int, lr: float | None = None) -> torch.Tensor:
+        """The device part of a step on a batch already on the device: zero gradients, micro-batch loop (forward,
+        fused head + loss, backward), gradient synchronisation, clip, update. Returns a device tensor
+        (loss, ce sum, gradient norm); nothing is read back to the host here."""
+        cfg = self.cfg
+        lr = lr_of(cfg, self.step) if lr is None else lr
+        self.flat.grads.zero_()
+        rows = batch.tokens.shape[0]
+        micro = cfg.micro_batch_size or rows
+        if rows % micro:
+            raise ValueError(f"micro_batch_size {micro} does not divide this rank's {rows} rows")
+        loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        ce_sum = torch.zeros((), dtype=torch.float32, device=self.device)
+        for lo in range(0, rows, micro):
+            mb = batch if micro == rows else _slice(batch, lo, lo + micro)
+            loss, ce = self._micro_loss(mb, max(n_global, 1))
+            loss.backward()
+            loss_sum += loss.detach().float()
+            ce_sum += ce.float()
+        stats = torch.stack([loss_sum, ce_sum]).double()
+        if self.zero is not None:
+            gnorm = self.zero.sync_and_step(self.optimizer, lr, cfg.optim.grad_clip, stats)
+        else:
+            if self.dp is not None:
+                self.dp.all_reduce_(self.flat.grads)
+                self.dp.all_reduce_(stats)
+            gnorm = grad_norm(self.flat)
+            self.optimizer.step(lr, _clip_coef(gnorm, cfg.optim.grad_clip))
+        self.step += 1
+        return torch.stack([stats[0].float(), stats[1].float(), gnorm.float()])
+
     def train_step(self) -> dict:
+        """One full training step through the public path: build this rank's batch (a pure function of the step),
+        copy it from pinned host memory to the device, run `device_step`, read (loss, ce, grad norm) back."""
         cfg = self.cfg
         t0 = time.perf_counter()
         step = self.step
@@ -172,46 +205,20 @@ class Trainer:
         if bad:
             self._halt_bad_batch(step)
         lr = lr_of(cfg, step)
-        self.flat.grads.zero_()
-        rows = batch.tokens.shape[0]
-        micro = cfg.micro_batch_size or rows
-        if rows % micro:
-            raise ValueError(f"micro_batch_size {micro} does not divide this rank's {rows} rows")
         if self.device.type == "cuda":
             batch = batch.pin()
-        loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
-        ce_sum = torch.zeros((), dtype=torch.float32, device=self.device)
-        self.h2d_bytes = 0
-        for lo in range(0, rows, micro):
-            mb = _slice(batch, lo, lo + micro)
-            self.h2d_bytes += mb.h2d_bytes()
-            mb = mb.to(self.device)
-            loss, ce = self._micro_loss(mb, max(n_global, 1))
-            loss.backward()
-            loss_sum += loss.detach().float()
-            ce_sum += ce.float()
-        # ---- gradient synchronisation, clip, update
-        stats = torch.stack([loss_sum, ce_sum]).double()
-        if self.zero is not None:
-            gnorm = self.zero.sync_and_step(self.optimizer, lr, cfg.optim.grad_clip, stats)
-        else:
-            if self.dp is not None:
-                self.dp.all_reduce_(self.flat.grads)
-                self.dp.all_reduce_(stats)
-            gnorm = grad_norm(self.flat)
-            scale = _clip_coef(gnorm, cfg.optim.grad_clip)
-            self.optimizer.step(lr, scale)
-        host = torch.stack([stats[0].float(), stats[1].float(), gnorm.float()]).cpu()   # the step's one device->host read
+        self.h2d_bytes = batch.h2d_bytes()
+        dev_batch = batch.to(self.device)
+        host = self.device_step(dev_batch, n_global, lr).cpu()      # the step's one device->host read
         self.d2h_bytes = host.numel() * host.element_size()
         loss_v, ce_v, gn_v = (float(x) for x in host)
         seconds = time.perf_counter() - t0
         s = batch.tokens.shape[2] if batch.tokens.dim() == 3 else 1
         n_tokens = cfg.data.batch_size * cfg.data.seq_len * s
-        m = {"step": step, "loss": loss_v, "ce_dec": ce_v * 1.0, "lr": lr, "grad_norm": gn_v, "n_targets": n_global,
+        m = {"step": step, "loss": loss_v, "ce_dec": ce_v, "lr": lr, "grad_norm": gn_v, "n_targets": n_global,
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
-        self.step += 1
         self.last_metrics = m
         if not math.isfinite(loss_v):
             self._halt_diverged(m)

@@ -1,0 +1,213 @@
+"""Each sm_100a kernel against the plain PyTorch fp32 statement of the same op, forward and backward."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _close(a, b, atol, rtol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    assert bool((err <= bound).all()), f"{what}: max err {err.max().item():.3e} (bound {bound.max().item():.3e}), worst ratio {(err / bound).max().item():.2f}"
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 1024, 1024), (300, 200, 264), (128, 16, 1024), (1024, 4112, 1024), (4096, 2816, 1024)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_gemm_layouts(M, N, K, layout):
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    g = torch.Generator(device="cpu").manual_seed(M * 7 + N * 3 + K)
+    a = torch.randn(M, K, generator=g).to(_dev(), torch.bfloat16)
+    b = torch.randn(N, K, generator=g).to(_dev(), torch.bfloat16)
+    want = a.float() @ b.float().T
+    if layout == "nt":
+        got = native.gemm(a, b, out_dtype=torch.float32)
+    elif layout == "nn":      # b stored [K, N]
+        got = native.gemm(a, b.T.contiguous(), b_mn=True, out_dtype=torch.float32)
+    else:                     # both stored with the reduction dimension outermost
+        got = native.gemm(a.T.contiguous(), b.T.contiguous(), a_mn=True, b_mn=True, out_dtype=torch.float32)
+    native.check_status()
+    _close(got, want, 2e-3 * K ** 0.5, 1e-3, f"gemm {layout} {M}x{N}x{K}")
+    got16 = native.gemm(a, b)
+    _close(got16, want, 2e-2 * K ** 0.5, 1e-2, "bf16 out")
+    acc = torch.ones(M, N, device=_dev())
+    native.gemm(a, b, out=acc, accumulate=True)
+    _close(acc, want + 1, 2e-3 * K ** 0.5, 1e-3, "accumulate")
+    native.check_status()
+
+
+def test_linear_autograd():
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.models.linear import Linear
+
+    lin = Linear(512, 384).to(_dev())
+    x = torch.randn(4, 96, 512, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = ops.linear(x, lin)
+    w = lin.weight.detach().to(torch.bfloat16).float()
+    _close(y, x.detach().float() @ w.T, 2e-2, 1e-2)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    _close(x.grad, gy.float() @ w, 3e-2, 2e-2)
+    _close(lin.weight.grad, gy.float().reshape(-1, 384).T @ x.detach().float().reshape(-1, 512), 5e-2, 2e-2)
+
+
+@pytest.mark.parametrize("d,in_dt,gate", [(1024, torch.float32, None), (64, torch.bfloat16, None), (256, torch.bfloat16, "sigmoid"),
+                                         (256, torch.float32, "silu"), (512, torch.float32, None), (2048, torch.float32, None)])
+def test_rmsnorm_family(d, in_dt, gate):
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    rows = 333
+    x = torch.randn(rows, d, device=_dev()).to(in_dt).requires_grad_()
+    w = (torch.randn(d, device=_dev()) * 0.1).requires_grad_()
+    z = torch.randn(rows, d, device=_dev()).to(torch.bfloat16).requires_grad_() if gate else None
+    xr, wr = x.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    zr = z.detach().float().requires_grad_() if gate else None
+    if gate:
+        y = native.gated_rmsnorm(x, z, w, 1e-6, gate, out_dtype=torch.float32)
+        yr = ref.gated_rmsnorm(xr, zr, wr, 1e-6, gate)
+    else:
+        y = native.rmsnorm(x, w, 1e-6, out_dtype=torch.float32)
+        yr = ref.rmsnorm(xr, wr, 1e-6)
+    tol = 2e-2 if in_dt == torch.bfloat16 else 1e-5
+    _close(y, yr, tol, tol, "fwd")
+    gy = torch.randn_like(yr)
+    y.backward(gy), yr.backward(gy)
+    _close(x.grad, xr.grad, 3e-2 if in_dt == torch.bfloat16 else 1e-4, 2e-2 if in_dt == torch.bfloat16 else 1e-4, "dx")
+    _close(w.grad, wr.grad, 2e-3 * rows ** 0.5, 1e-3, "dw")
+    if gate:
+        _close(z.grad, zr.grad, 3e-2, 2e-2, "dz")
+
+
+def test_norm_add():
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    rows, d = 257, 1024
+    resid = torch.randn(rows, d, device=_dev(), requires_grad=True)
+    br = torch.randn(rows, d, device=_dev()).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(d, device=_dev()) * 0.1).requires_grad_()
+    y = native.norm_add(resid, br, w, 1e-6, 0.5)
+    r2, b2, w2 = resid.detach().clone().requires_grad_(), br.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = r2 + 0.5 * ref.rmsnorm(b2, w2, 1e-6)
+    _close(y, yr, 1e-5, 1e-5)
+    gy = torch.randn_like(yr)
+    y.backward(gy), yr.backward(gy)
+    _close(resid.grad, r2.grad, 0, 0)
+    _close(br.grad, b2.grad, 2e-2, 2e-2)
+    _close(w.grad, w2.grad, 5e-2, 1e-3)
+
+
+def test_swiglu_mlp():
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.models.mlp import SwiGLU
+
+    m = SwiGLU(256, 704).to(_dev())
+    x = torch.randn(3, 100, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    y = m(x)
+    ops.set_mode("reference")
+    try:
+        xr = x.detach().float().requires_grad_()
+        mr = SwiGLU(256, 704).to(_dev())
+        mr.load_state_dict(m.state_dict())
+        yr = mr(xr)
+    finally:
+        ops.set_mode("native")
+    _close(y, yr, 3e-2, 3e-2)
+    gy = torch.randn_like(yr)
+    y.backward(gy.to(y.dtype)), yr.backward(gy)
+    _close(x.grad, xr.grad, 5e-2, 5e-2)
+    for a, b in zip(m.parameters(), mr.parameters()):
+        _close(a.grad, b.grad, 1e-1, 5e-2)
+
+
+@pytest.mark.parametrize("single", [True, False])
+def test_gdn_prep(single):
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    B, L, hk, hv, dk, dv = 2, 200, 2, 2, 128, 256
+    C = 2 * hk * dk + hv * dv
+    u = torch.randn(B, L, C, device=_dev()).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(C, 4, device=_dev()) * 0.5).requires_grad_()
+    doc = torch.zeros(B, L, dtype=torch.long, device=_dev())
+    if not single:
+        doc[0, 50:] = 1
+        doc[0, 51:] = 2
+        doc[1, 199:] = 3
+    q, k, v, hist, _ = native.gdn_prep(u, doc, w, hk, hv, dk, dv, single_doc=single)
+    ur, wr = u.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
+    qr, kr, vr, histr, _ = ref.gdn_prep(ur, doc, wr, hk, hv, dk, dv)
+    for a, b, n in ((q, qr, "q"), (k, kr, "k"), (v, vr, "v")):
+        _close(a, b, 1e-2, 2e-2, n)
+    gq, gk, gv = torch.randn_like(qr), torch.randn_like(kr), torch.randn_like(vr)
+    torch.autograd.backward([q, k, v], [gq.to(q.dtype), gk.to(k.dtype), gv.to(v.dtype)])
+    torch.autograd.backward([qr, kr, vr], [gq, gk, gv])
+    _close(u.grad, ur.grad, 5e-2, 5e-2, "du")
+    _close(w.grad, wr.grad, 0.5, 3e-2, "dw")
+
+
+@pytest.mark.parametrize("n,d", [(2, 1024), (5, 1024), (4, 512), (3, 2048)])
+def test_depth_mix(n, d):
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    rows = 97
+    src = [torch.randn(2, rows, d, device=_dev()).requires_grad_() for _ in range(n)]
+    qy = (torch.randn(d, device=_dev()) * 0.2).requires_grad_()
+    gn = (torch.randn(d, device=_dev()) * 0.1).requires_grad_()
+    y = native.depth_mix(src, qy, gn, 1e-6)
+    src2 = [s.detach().clone().requires_grad_() for s in src]
+    q2, g2 = qy.detach().clone().requires_grad_(), gn.detach().clone().requires_grad_()
+    yr = ref.depth_mix(src2, q2, g2, 1e-6)
+    _close(y, yr, 1e-4, 1e-4)
+    gy = torch.randn_like(yr)
+    y.backward(gy), yr.backward(gy)
+    for a, b in zip(src, src2):
+        _close(a.grad, b.grad, 1e-4, 1e-3, "dsrc")
+    _close(qy.grad, q2.grad, 1e-3, 1e-3, "dq")
+    _close(gn.grad, g2.grad, 1e-3, 1e-3, "dgain")
+
+
+@pytest.mark.parametrize("s", [1, 4])
+def test_fused_linear_ce(s):
+    from gdn_hybrid_architecture_ideas_b200.train.fused_head import _FusedLinearCE, fused_linear_ce
+
+    n, d, V = 700, 256, 4096
+    h = torch.randn(n, d, device=_dev()).to(torch.bfloat16).requires_grad_()
+    W = (torch.randn(V, d, device=_dev()) * 0.05).requires_grad_()
+    t = torch.randint(0, V, (n, s), device=_dev())
+    a = torch.rand(n, s, device=_dev()) / n
+    a[5] = 0
+    b = a.sum(1) * 1e-2
+    loss, ce, lse = fused_linear_ce(h, W, t, a, b, 256)
+    loss.backward()
+    hr = h.detach().float().requires_grad_()
+    Wr = W.detach().to(torch.bfloat16).float().requires_grad_()
+    lossr, cer, lser = _FusedLinearCE.apply(hr, Wr, t, a, b, 256)
+    lossr.backward()
+    _close(loss, lossr, 1e-3, 1e-3, "loss")
+    _close(lse, lser, 2e-3, 1e-3, "lse")
+    _close(h.grad, hr.grad, 2e-5, 5e-2, "dh")
+    _close(W.grad, Wr.grad, 2e-5, 5e-2, "dW")
+
+
+def test_adamw_and_sumsq():
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    n = 1 << 20
+    p = torch.randn(n, device=_dev())
+    g = torch.randn(n, device=_dev())
+    m, v = torch.zeros(n, device=_dev()), torch.zeros(n, device=_dev())
+    lp = torch.empty(n, device=_dev(), dtype=torch.bfloat16)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 4):
+        ref_p.grad = g * 0.5
+        opt.step()
+        native.adamw_(p, g, m, v, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, 1 - 0.9 ** step, 1 - 0.95 ** step, torch.tensor(0.5, device=_dev()))
+    _close(p, ref_p.detach(), 1e-6, 1e-5)
+    _close(lp, p, 1e-2, 1e-2)
+    _close(native.sumsq(g), g.double().pow(2).sum(), 1.0, 1e-5)
