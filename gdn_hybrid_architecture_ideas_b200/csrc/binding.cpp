@@ -28,8 +28,11 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, b
   int mode;
   if (is_bf16(out)) { TORCH_CHECK(!accumulate, "gemm: accumulation needs an fp32 output"); mode = 0; }
   else { TORCH_CHECK(is_f32(out), "gemm: output bf16 or fp32"); mode = accumulate ? 2 : 1; }
-  check(ghb::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), a_mn, b_mn, mode,
-                       err.data_ptr<int>(), sm_count(), stream()), "gemm_bf16");
+  const int rc = ghb::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), a_mn, b_mn, mode,
+                                err.data_ptr<int>(), sm_count(), stream());
+  TORCH_CHECK(rc == 0, "gemm_bf16 refused (code ", rc, "): M=", M, " N=", N, " K=", K, " lda=", a.stride(0), " ldb=", b.stride(0), " ldc=",
+              out.stride(0), " a_mn=", a_mn, " b_mn=", b_mn, " ptrs%16=", reinterpret_cast<uintptr_t>(a.data_ptr()) % 16, ",",
+              reinterpret_cast<uintptr_t>(b.data_ptr()) % 16, ",", reinterpret_cast<uintptr_t>(out.data_ptr()) % 16);
 }
 
 void rmsnorm_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& z, int64_t gate, const c10::optional<Tensor>& resid,
@@ -145,6 +148,36 @@ void ce_grad(const Tensor& logits, const Tensor& targets, const Tensor& a, const
                      grad.data_ptr(), ce.data_ptr<float>(), lse.data_ptr<float>(), rows, V, s, stream()), "ce_grad");
 }
 
+const void* optr(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+void check_heads(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.is_contiguous() && t.dim() == 4 && t.size(3) == 64, name, ": bf16 contiguous [B, L, H, 64]");
+}
+
+void attention_fwd(const Tensor& q, const c10::optional<Tensor>& qf, const Tensor& k, const c10::optional<Tensor>& kf, const Tensor& v, Tensor& o,
+                   Tensor& lse, const c10::optional<Tensor>& doc, const c10::optional<Tensor>& pos, int64_t cap, double scale, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  check_heads(q, "q"); check_heads(k, "k"); check_heads(v, "v"); check_heads(o, "o");
+  if (cap >= 0) { TORCH_CHECK(qf.has_value() && kf.has_value(), "attention_fwd: the cap needs q_far and k_far"); check_heads(*qf, "q_far"); check_heads(*kf, "k_far"); }
+  if (doc.has_value()) TORCH_CHECK(pos.has_value() && doc->scalar_type() == torch::kInt32 && pos->scalar_type() == torch::kInt32 && doc->is_contiguous() && pos->is_contiguous(), "attention_fwd: int32 doc / pos");
+  TORCH_CHECK(is_f32(lse) && lse.is_contiguous(), "attention_fwd: fp32 lse");
+  check(ghb::attention_fwd(q.data_ptr(), optr(qf), k.data_ptr(), optr(kf), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                           doc.has_value() ? doc->data_ptr<int>() : nullptr, pos.has_value() ? pos->data_ptr<int>() : nullptr, q.size(0), q.size(1),
+                           q.size(2), k.size(2), cap, scale, err.data_ptr<int>(), stream()), "attention_fwd");
+}
+
+void attention_bwd(const Tensor& q, const c10::optional<Tensor>& qf, const Tensor& k, const c10::optional<Tensor>& kf, const Tensor& v, const Tensor& o,
+                   const Tensor& dO, const Tensor& lse, Tensor& dsum, Tensor& dq, const c10::optional<Tensor>& dqf, Tensor& dk,
+                   const c10::optional<Tensor>& dkf, Tensor& dv, const c10::optional<Tensor>& doc, int64_t cap, double scale, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  check_heads(q, "q"); check_heads(k, "k"); check_heads(v, "v"); check_heads(o, "o"); check_heads(dO, "dO"); check_heads(dk, "dk"); check_heads(dv, "dv");
+  TORCH_CHECK(is_f32(dq) && dq.is_contiguous() && is_f32(dsum) && is_f32(lse), "attention_bwd: fp32 dq / dsum / lse");
+  if (cap >= 0) TORCH_CHECK(qf.has_value() && kf.has_value() && dqf.has_value() && dkf.has_value() && is_f32(*dqf), "attention_bwd: far tensors");
+  check(ghb::attention_bwd(q.data_ptr(), optr(qf), k.data_ptr(), optr(kf), v.data_ptr(), o.data_ptr(), dO.data_ptr(), lse.data_ptr<float>(),
+                           dsum.data_ptr<float>(), dq.data_ptr<float>(), dqf.has_value() ? dqf->data_ptr<float>() : nullptr, dk.data_ptr(),
+                           dkf.has_value() ? dkf->data_ptr() : nullptr, dv.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, q.size(0),
+                           q.size(1), q.size(2), k.size(2), cap, scale, err.data_ptr<int>(), stream()), "attention_bwd");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -161,4 +194,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("attention_fwd", &attention_fwd);
+  m.def("attention_bwd", &attention_bwd);
 }

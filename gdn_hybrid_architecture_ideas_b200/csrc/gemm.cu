@@ -222,8 +222,12 @@ static int launch_major(bool a_mn, bool b_mn, const void* A, const void* B, void
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn,
               int out, int* err, int sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((lda % 8) || (ldb % 8) || (ldc % (out == 0 ? 8 : 4))) return 1;
-  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15) return 1;
+  if (lda % 8) return 11;                       // TMA: row strides are multiples of 16 bytes
+  if (ldb % 8) return 12;
+  if (ldc % (out == 0 ? 8 : 4)) return 13;      // vectorised epilogue stores
+  if (reinterpret_cast<uintptr_t>(A) & 15) return 14;
+  if (reinterpret_cast<uintptr_t>(B) & 15) return 15;
+  if (reinterpret_cast<uintptr_t>(C) & 15) return 16;
   const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
 #define GHB_DISPATCH(BN)                                                                                              \
   switch (out) {                                                                                                      \

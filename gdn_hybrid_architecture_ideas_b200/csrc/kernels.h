@@ -12,6 +12,9 @@ namespace ghb {
 bool encode_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes, const uint64_t dims[2], const uint64_t strides[1],
                           const uint32_t box[2], bool swizzle128);
 
+bool encode_tensor_map_3d(CUtensorMap* map, const void* ptr, int elem_bytes, const uint64_t dims[3], const uint64_t strides[2],
+                          const uint32_t box[3], bool swizzle128);
+
 int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn,
               int out, int* err, int sms, cudaStream_t stream);
 
@@ -35,5 +38,11 @@ int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const floa
                   const float* rnorm, float* du, long rows, int d, int sms, cudaStream_t st);
 int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,
             int s, cudaStream_t st);
+
+int attention_fwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, void* o, float* lse, const int* doc,
+                  const int* pos, int B, int L, int Hq, int Hkv, int cap, float scale, int* err, cudaStream_t st);
+int attention_bwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, const void* o, const void* dO,
+                  const float* lse, float* dsum, float* dq, float* dqf, void* dk, void* dkf, void* dv, const int* doc, int B, int L, int Hq,
+                  int Hkv, int cap, float scale, int* err, cudaStream_t st);
 
 }  // namespace ghb

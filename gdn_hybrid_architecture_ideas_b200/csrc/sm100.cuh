@@ -1,7 +1,7 @@
 // Thin inline-PTX layer for Blackwell (sm_100a): mbarriers with bounded waits, TMA tile copies (never cluster
 // multicast), tensor memory allocation, tcgen05 MMA issue / commit / TMEM loads, and UMMA descriptors.
 //
-// Every wait in this file is bounded: after WAIT_LIMIT polls it gives up and returns false; callers record an error
+// Every wait in this file is bounded in wall time: past the limit it gives up and returns false; callers record an error
 // code in global memory and leave their loops, so a protocol bug ends as a host-visible status, never a hung GPU.
 #pragma once
 #include <cuda.h>
@@ -11,7 +11,7 @@
 
 namespace sm100 {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;   // polls; each poll may suspend up to ~1 us in hardware
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;   // a wait that lasts 2 s is a protocol failure, not a slow tile
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -38,11 +38,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-// Bounded wait: false after WAIT_LIMIT unsuccessful polls.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false once WAIT_LIMIT_NS of wall time has passed without the phase completing.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > WAIT_LIMIT_NS) return false;
+  }
 }
 
 // ---------------------------------------------------------------------------------------------- fences

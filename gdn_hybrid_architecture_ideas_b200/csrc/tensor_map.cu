@@ -28,4 +28,18 @@ bool encode_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes, con
   return r == CUDA_SUCCESS;
 }
 
+bool encode_tensor_map_3d(CUtensorMap* map, const void* ptr, int elem_bytes, const uint64_t dims[3], const uint64_t strides[2],
+                          const uint32_t box[3], bool swizzle128) {
+  auto fn = encode_fn();
+  if (!fn) return false;
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                           : (elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
+  CUresult r = fn(map, dt, 3, const_cast<void*>(ptr), reinterpret_cast<const cuuint64_t*>(dims),
+                  reinterpret_cast<const cuuint64_t*>(strides), reinterpret_cast<const cuuint32_t*>(box), estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace ghb

@@ -233,5 +233,6 @@ class GatedAttention(nn.Module):
             keys = KeySet.cat(cache, new)
             k, k_far, v = keys.k, keys.k_far, keys.v
         o = ops.attention(q, k, v, ctx.idx, ctx.doc, keys.idx, keys.doc, None if cache is None else keys.ok,
-                          q_far=q_far, k_far=k_far, cap=cap, self_aligned=cache is None)
+                          q_far=q_far, k_far=k_far, cap=cap, self_aligned=cache is None, q_pos=ctx.pos,
+                          single_doc=ctx.single_doc)
         return self.output(o, gate), keys

@@ -89,11 +89,12 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=
     return ref.chunked_delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size)
 
 
-def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=None, cap=None, self_aligned=False):
+def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=None, cap=None, self_aligned=False, q_pos=None,
+              single_doc=False):
     """self_aligned: queries and keys are the same positions of the same rows (a training forward without a cache),
     which is the case the fused training kernel covers."""
     if use_native(q) and self_aligned:
-        return _native().attention(q, k, v, q_doc, q_far, k_far, cap)
+        return _native().attention(q, k, v, q_doc, q_far, k_far, cap, q_pos, single_doc)
     return ref.attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok, q_far, k_far, cap)
 
 

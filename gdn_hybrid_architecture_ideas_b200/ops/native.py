@@ -91,21 +91,38 @@ def _w_lp(lin) -> torch.Tensor:
     return lp if lp is not None else lin.weight.detach().to(BF16)
 
 
+def _pad_rows(w: torch.Tensor, mult: int = 8) -> torch.Tensor:
+    """Weight [N, K] zero-padded to a multiple of `mult` rows (projections with a handful of outputs, such as the
+    per-head decay and beta gates, get 16-byte-aligned output rows this way)."""
+    n = w.shape[0]
+    if n % mult == 0:
+        return w
+    out = torch.zeros(-(-n // mult) * mult, w.shape[1], dtype=w.dtype, device=w.device)
+    out[:n] = w
+    return out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, w_lp):
         x2 = _bf16(x).reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
+        n = w_lp.shape[0]
+        w_lp = _pad_rows(w_lp)
         y = gemm(x2, w_lp)
         ctx.save_for_backward(x2, w_lp)
-        ctx.xshape, ctx.xdtype = x.shape, x.dtype
-        return y.view(*x.shape[:-1], w_lp.shape[0])
+        ctx.xshape, ctx.xdtype, ctx.n = x.shape, x.dtype, n
+        if n != w_lp.shape[0]:
+            y = y[:, :n]
+        return y.reshape(*x.shape[:-1], n)
 
     @staticmethod
     def backward(ctx, dy):
         x2, w_lp = ctx.saved_tensors
         dy2 = _bf16(dy).reshape(-1, dy.shape[-1])
+        if ctx.n != w_lp.shape[0]:
+            dy2 = torch.nn.functional.pad(dy2, (0, w_lp.shape[0] - ctx.n))
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = None
@@ -114,7 +131,7 @@ class _Linear(torch.autograd.Function):
             if ctx.xdtype != BF16:
                 dx = dx.to(ctx.xdtype)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)   # dy^T [N,M] . x [M,K]
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)[:ctx.n]   # dy^T [N,M] . x [M,K]
         return dx, dw, None
 
 
@@ -404,7 +421,7 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
     return gdn_native.delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state)
 
 
-def attention(q, k, v, doc, q_far, k_far, cap):
+def attention(q, k, v, doc, q_far, k_far, cap, pos=None, single_doc=False):
     from . import attention_native
 
-    return attention_native.attention(q, k, v, doc, q_far, k_far, cap)
+    return attention_native.attention(q, k, v, doc, q_far, k_far, cap, pos, single_doc)

@@ -17,7 +17,7 @@ def _close(a, b, atol, rtol, what=""):
     assert bool((err <= bound).all()), f"{what}: max err {err.max().item():.3e} (bound {bound.max().item():.3e}), worst ratio {(err / bound).max().item():.2f}"
 
 
-@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 1024, 1024), (300, 200, 264), (128, 16, 1024), (1024, 4112, 1024), (4096, 2816, 1024)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 128), (512, 1024, 1024), (304, 200, 264), (128, 16, 1024), (1024, 4112, 1024), (4096, 2816, 1024)])
 @pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
 def test_gemm_layouts(M, N, K, layout):
     from gdn_hybrid_architecture_ideas_b200.ops import native
@@ -211,3 +211,38 @@ def test_adamw_and_sumsq():
     _close(p, ref_p.detach(), 1e-6, 1e-5)
     _close(lp, p, 1e-2, 1e-2)
     _close(native.sumsq(g), g.double().pow(2).sum(), 1.0, 1e-5)
+
+
+@pytest.mark.parametrize("L,cap,docs,Hq,Hkv", [(256, None, False, 4, 2), (384, 100, False, 4, 1), (300, 64, True, 2, 2), (512, 200, True, 8, 2),
+                                               (1024, None, True, 2, 1)])
+def test_attention_kernels(L, cap, docs, Hq, Hkv):
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    B, hd = 2, 64
+    g = torch.Generator().manual_seed(L + Hq)
+    def mk(h):
+        return (torch.randn(B, L, h, hd, generator=g) * 0.7).to(_dev(), torch.bfloat16)
+    q, qf, k, kf, v = mk(Hq), mk(Hq), mk(Hkv), mk(Hkv), mk(Hkv)
+    doc = torch.zeros(B, L, dtype=torch.long, device=_dev())
+    if docs:
+        doc[0, L // 3:] = 1
+        doc[0, L // 3 + 5:] = 2
+        doc[1, L - 7:] = 4
+    idx = torch.arange(L, device=_dev())[None].expand(B, L)
+    start = torch.where(torch.cat([torch.ones(B, 1, dtype=torch.bool, device=_dev()), doc[:, 1:] != doc[:, :-1]], 1), idx, torch.zeros_like(idx)).cummax(1).values
+    pos = idx - start
+    leaves = [t.clone().requires_grad_() for t in (q, k, v, qf, kf)]
+    o = native.attention(leaves[0], leaves[1], leaves[2], doc, leaves[3] if cap else None, leaves[4] if cap else None, cap, pos, single_doc=not docs)
+    native.check_status()
+    refs = [t.float().requires_grad_() for t in (q, k, v, qf, kf)]
+    orf = ref.attention(refs[0], refs[1], refs[2], idx, doc, idx, doc, None, refs[3] if cap else None, refs[4] if cap else None, cap)
+    _close(o, orf, 2e-2, 2e-2, "o")
+    go = torch.randn_like(orf)
+    o.backward(go.to(o.dtype))
+    orf.backward(go)
+    native.check_status()
+    names = ["dq", "dk", "dv", "dq_far", "dk_far"]
+    for n, a, b in zip(names, leaves, refs):
+        if b.grad is None:
+            continue
+        _close(a.grad, b.grad, 4e-2, 4e-2, n)
