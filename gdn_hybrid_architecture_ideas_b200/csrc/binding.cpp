@@ -178,6 +178,38 @@ void attention_bwd(const Tensor& q, const c10::optional<Tensor>& qf, const Tenso
                            q.size(1), q.size(2), k.size(2), cap, scale, err.data_ptr<int>(), stream()), "attention_bwd");
 }
 
+void check_rows(const Tensor& t, int64_t cols, const char* name) {
+  TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.is_contiguous() && t.size(-1) == cols, name, ": bf16 contiguous [..., ", cols, "]");
+}
+float* fmut(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr<float>() : nullptr; }
+void* vmut(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+// All operands laid out [B, H, L, *] with L a multiple of 64 (chunks never straddle rows).
+void gdn_scan_fwd(const Tensor& W, const Tensor& Qin, const Tensor& Kout, const Tensor& Aqk, const Tensor& U, const Tensor& carry,
+                  const c10::optional<Tensor>& S0, Tensor& O, const c10::optional<Tensor>& Sfinal, const c10::optional<Tensor>& Hsave,
+                  const c10::optional<Tensor>& Vnew, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(W.device());
+  const int B = U.size(0), H = U.size(1), L = U.size(2), dv = U.size(3);
+  check_rows(W, 128, "W"); check_rows(Qin, 128, "q_in"); check_rows(Kout, 128, "k_out"); check_rows(Aqk, 64, "Aqk"); check_rows(U, dv, "U"); check_rows(O, dv, "O");
+  TORCH_CHECK(is_f32(carry) && carry.is_contiguous() && carry.numel() == static_cast<int64_t>(B) * H * (L / 64), "gdn_scan_fwd: carry [B, H, L/64] fp32");
+  if (S0.has_value()) TORCH_CHECK(is_f32(*S0) && S0->is_contiguous(), "gdn_scan_fwd: S0 fp32");
+  check(ghb::gdn_scan_fwd(W.data_ptr(), Qin.data_ptr(), Kout.data_ptr(), Aqk.data_ptr(), U.data_ptr(), carry.data_ptr<float>(), fptr(S0), O.data_ptr(),
+                          fmut(Sfinal), vmut(Hsave), vmut(Vnew), B, H, L, dv, err.data_ptr<int>(), stream()), "gdn_scan_fwd");
+}
+
+void gdn_scan_bwd(const Tensor& W, const Tensor& Qin, const Tensor& Kout, const Tensor& Aqk, const Tensor& Hsave, const Tensor& Vnew, const Tensor& dO,
+                  const Tensor& carry, const c10::optional<Tensor>& dSfinal, Tensor& dU, Tensor& dWp, Tensor& dQp, Tensor& dKp, Tensor& dcarry,
+                  const c10::optional<Tensor>& dS0, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(W.device());
+  const int B = Vnew.size(0), H = Vnew.size(1), L = Vnew.size(2), dv = Vnew.size(3);
+  check_rows(W, 128, "W"); check_rows(Qin, 128, "q_in"); check_rows(Kout, 128, "k_out"); check_rows(Aqk, 64, "Aqk"); check_rows(Vnew, dv, "v_new");
+  check_rows(dO, dv, "dO"); check_rows(dU, dv, "dU"); check_rows(Hsave, 128, "h_save");
+  TORCH_CHECK(is_f32(dWp) && is_f32(dQp) && is_f32(dKp) && is_f32(dcarry) && dWp.is_contiguous() && dQp.is_contiguous() && dKp.is_contiguous(), "gdn_scan_bwd: fp32 partials");
+  check(ghb::gdn_scan_bwd(W.data_ptr(), Qin.data_ptr(), Kout.data_ptr(), Aqk.data_ptr(), Hsave.data_ptr(), Vnew.data_ptr(), dO.data_ptr(),
+                          carry.data_ptr<float>(), fptr(dSfinal), dU.data_ptr(), dWp.data_ptr<float>(), dQp.data_ptr<float>(), dKp.data_ptr<float>(),
+                          dcarry.data_ptr<float>(), fmut(dS0), B, H, L, dv, err.data_ptr<int>(), stream()), "gdn_scan_bwd");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -194,6 +226,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("gdn_scan_fwd", &gdn_scan_fwd);
+  m.def("gdn_scan_bwd", &gdn_scan_bwd);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
 }

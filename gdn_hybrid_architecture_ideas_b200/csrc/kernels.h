@@ -45,4 +45,10 @@ int attention_bwd(const void* q, const void* qf, const void* k, const void* kf, 
                   const float* lse, float* dsum, float* dq, float* dqf, void* dk, void* dkf, void* dv, const int* doc, int B, int L, int Hq,
                   int Hkv, int cap, float scale, int* err, cudaStream_t st);
 
+int gdn_scan_fwd(const void* W, const void* Qin, const void* Kout, const void* Aqk, const void* U, const float* carry, const float* S0,
+                 void* O, float* Sfinal, void* Hsave, void* Vnew, int B, int H, int L, int dv, int* err, cudaStream_t st);
+int gdn_scan_bwd(const void* W, const void* Qin, const void* Kout, const void* Aqk, const void* Hsave, const void* Vnew, const void* dO,
+                 const float* carry, const float* dSfinal, void* dU, float* dWp, float* dQp, float* dKp, float* dcarry, float* dS0, int B, int H,
+                 int L, int dv, int* err, cudaStream_t st);
+
 }  // namespace ghb

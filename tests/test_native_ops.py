@@ -246,3 +246,45 @@ def test_attention_kernels(L, cap, docs, Hq, Hkv):
         if b.grad is None:
             continue
         _close(a.grad, b.grad, 4e-2, 4e-2, n)
+
+
+@pytest.mark.parametrize("L,dv,H,docs,with_state", [(128, 128, 2, False, False), (256, 256, 2, True, True), (200, 256, 1, True, False)])
+def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state):
+    from gdn_hybrid_architecture_ideas_b200.ops import gdn_native, native, reference as ref
+
+    B, dk = 2, 128
+    g_ = torch.Generator().manual_seed(L + dv)
+    q = torch.nn.functional.normalize(torch.randn(B, L, H, dk, generator=g_), dim=-1) * dk ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(B, L, H, dk, generator=g_), dim=-1)
+    v = torch.randn(B, L, H, dv, generator=g_)
+    g = -torch.rand(B, L, H, generator=g_) * 0.5
+    beta = torch.rand(B, L, H, generator=g_)
+    S0 = torch.randn(B, H, dk, dv, generator=g_) * 0.1 if with_state else None
+    start = torch.zeros(B, L, dtype=torch.bool)
+    if docs:
+        start[0, 70] = True
+        start[1, 3] = True
+        start[1, L - 2] = True
+    dev = _dev()
+    leaves = [t.to(dev).to(torch.bfloat16 if i < 3 else torch.float32).requires_grad_() for i, t in enumerate((q, k, v, g, beta))]
+    S0d = S0.to(dev).requires_grad_() if with_state else None
+    o, S = gdn_native.delta_rule(*leaves, start.to(dev), S0d, 64, need_state=with_state)
+    native.check_status()
+    refs = [t.detach().float().requires_grad_() for t in leaves]
+    S0r = S0.to(dev).requires_grad_() if with_state else torch.zeros(B, H, dk, dv, device=dev)
+    orf, Sr = ref.chunked_delta_rule(*refs, start.to(dev), S0r, 64)
+    _close(o, orf, 2e-2, 3e-2, "o")
+    go = torch.randn_like(orf)
+    if with_state:
+        _close(S, Sr, 2e-2, 3e-2, "S")
+        gS = torch.randn_like(Sr) * 0.1
+        torch.autograd.backward([o, S], [go.to(o.dtype), gS])
+        torch.autograd.backward([orf, Sr], [go, gS])
+        _close(S0d.grad, S0r.grad, 3e-2, 5e-2, "dS0")
+    else:
+        o.backward(go.to(o.dtype))
+        orf.backward(go)
+    native.check_status()
+    for n, a, b in zip(("dq", "dk", "dv", "dg", "dbeta"), leaves, refs):
+        scale = b.grad.abs().max().item()
+        _close(a.grad, b.grad, 3e-2 * scale, 5e-2, n)
