@@ -31,7 +31,7 @@ void gemm(const Tensor& a, const Tensor& b, Tensor& out, bool a_mn, bool b_mn, b
   const int rc = ghb::gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0), a_mn, b_mn, mode,
                                 err.data_ptr<int>(), sm_count(), stream());
   TORCH_CHECK(rc == 0, "gemm_bf16 refused (code ", rc, "): M=", M, " N=", N, " K=", K, " lda=", a.stride(0), " ldb=", b.stride(0), " ldc=",
-              out.stride(0), " a_mn=", a_mn, " b_mn=", b_mn, " ptrs%16=", reinterpret_cast<uintptr_t>(a.data_ptr()) % 16, ",",
+              out.stride(0), " a_mn=", a_mn, " b_mn=", b_mn, " cuerr=", ghb::last_encode_error(), " ptrs%16=", reinterpret_cast<uintptr_t>(a.data_ptr()) % 16, ",",
               reinterpret_cast<uintptr_t>(b.data_ptr()) % 16, ",", reinterpret_cast<uintptr_t>(out.data_ptr()) % 16);
 }
 
@@ -210,6 +210,38 @@ void gdn_scan_bwd(const Tensor& W, const Tensor& Qin, const Tensor& Kout, const 
                           dcarry.data_ptr<float>(), fmut(dS0), B, H, L, dv, err.data_ptr<int>(), stream()), "gdn_scan_bwd");
 }
 
+void check_tok_major(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && is_bf16(t) && t.dim() == 4 && t.stride(3) == 1 && t.stride(2) == t.size(3) && t.stride(0) == t.stride(1) * t.size(1),
+              name, ": bf16 [B, L, H, d] with contiguous heads and a constant token stride");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0 && t.stride(1) % 8 == 0, name, ": 16-byte aligned rows");
+}
+
+// q, k: [B, L, Hk, 128]; v: [B, L, Hv, dv]; g, beta: [B, L, Hv] fp32; start: [B, L] uint8. Outputs are [B, Hv, L, *].
+void gdn_local_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const Tensor& start, Tensor& U, Tensor& W,
+                   Tensor& Aqk, Tensor& Qin, Tensor& Kout, Tensor& carry) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  check_tok_major(q, "q"); check_tok_major(k, "k"); check_tok_major(v, "v");
+  TORCH_CHECK(is_f32(g) && g.is_contiguous() && is_f32(beta) && beta.is_contiguous() && start.scalar_type() == torch::kUInt8 && start.is_contiguous(), "gdn_local_fwd: gates fp32, starts uint8");
+  const int B = v.size(0), L = v.size(1), Hv = v.size(2), dv = v.size(3), Hk = q.size(2);
+  TORCH_CHECK(q.size(3) == 128 && k.size(3) == 128, "gdn_local_fwd: key dimension 128");
+  check(ghb::gdn_local_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), k.stride(1), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(),
+                           start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, U.data_ptr(), W.data_ptr(), Aqk.data_ptr(), Qin.data_ptr(), Kout.data_ptr(),
+                           carry.data_ptr<float>(), stream()), "gdn_local_fwd");
+}
+void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const Tensor& start, const Tensor& dU,
+                   const Tensor& dW, const Tensor& dQin, const Tensor& dKout, const Tensor& dAqk, const Tensor& dcarry, Tensor& dq, Tensor& dk, Tensor& dv_,
+                   Tensor& dg, Tensor& dbeta) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  check_tok_major(q, "q"); check_tok_major(k, "k"); check_tok_major(v, "v");
+  const int B = v.size(0), L = v.size(1), Hv = v.size(2), dv = v.size(3), Hk = q.size(2);
+  for (const Tensor* t : {&dU, &dW, &dQin, &dKout, &dAqk}) TORCH_CHECK(is_bf16(*t) && t->is_contiguous(), "gdn_local_bwd: bf16 contiguous gradients");
+  TORCH_CHECK(is_f32(dq) && is_f32(dk) && is_bf16(dv_) && is_f32(dg) && is_f32(dbeta) && is_f32(dcarry) && dq.is_contiguous() && dk.is_contiguous() && dv_.is_contiguous(), "gdn_local_bwd: outputs");
+  check(ghb::gdn_local_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), k.stride(1), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(),
+                           start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, dU.data_ptr(), dW.data_ptr(), dQin.data_ptr(), dKout.data_ptr(), dAqk.data_ptr(),
+                           dcarry.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv_.data_ptr(), dg.data_ptr<float>(), dbeta.data_ptr<float>(),
+                           stream()), "gdn_local_bwd");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -226,6 +258,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("gdn_local_fwd", &gdn_local_fwd);
+  m.def("gdn_local_bwd", &gdn_local_bwd);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);
   m.def("gdn_scan_bwd", &gdn_scan_bwd);
   m.def("attention_fwd", &attention_fwd);

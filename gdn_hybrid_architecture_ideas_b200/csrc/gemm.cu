@@ -195,7 +195,8 @@ template <int BN, bool A_MN, bool B_MN, int OUT>
 static int launch_cfg(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, int* err,
                       int sms, cudaStream_t stream) {
   CUtensorMap ta, tb;
-  if (!encode_operand(&ta, A, M, K, lda, A_MN, BM) || !encode_operand(&tb, B, N, K, ldb, B_MN, BN)) return 2;
+  if (!encode_operand(&ta, A, M, K, lda, A_MN, BM)) return 21;
+  if (!encode_operand(&tb, B, N, K, ldb, B_MN, BN)) return 22;
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN, OUT>;
   static bool attr_done = false;

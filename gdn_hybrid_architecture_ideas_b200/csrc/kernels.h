@@ -12,6 +12,7 @@ namespace ghb {
 bool encode_tensor_map_2d(CUtensorMap* map, const void* ptr, int elem_bytes, const uint64_t dims[2], const uint64_t strides[1],
                           const uint32_t box[2], bool swizzle128);
 
+int last_encode_error();
 bool encode_tensor_map_3d(CUtensorMap* map, const void* ptr, int elem_bytes, const uint64_t dims[3], const uint64_t strides[2],
                           const uint32_t box[3], bool swizzle128);
 
@@ -50,5 +51,23 @@ int gdn_scan_fwd(const void* W, const void* Qin, const void* Kout, const void* A
 int gdn_scan_bwd(const void* W, const void* Qin, const void* Kout, const void* Aqk, const void* Hsave, const void* Vnew, const void* dO,
                  const float* carry, const float* dSfinal, void* dU, float* dWp, float* dQp, float* dKp, float* dcarry, float* dS0, int B, int H,
                  int L, int dv, int* err, cudaStream_t st);
+
+int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
+                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, void* U, void* W, void* Aqk, void* Qin, void* Kout,
+                  float* carry, cudaStream_t st);
+int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
+                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* dU, const void* dW, const void* dQin,
+                  const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv, float* dg, float* dbeta,
+                  cudaStream_t st);
+
+// Fused data-parallel step over peer memory (csrc/comm.cu). `peers` points at a host copy of the CommPeers table
+// (comm_peers_bytes() bytes: 5 arrays of 8 device pointers, then 3 multicast pointers).
+size_t comm_peers_bytes();
+int comm_reduce(const void* peers, int rank, int world, long lo, long n, float* shard, unsigned int seq, float* block_acc,
+                unsigned int* done_counter, int* err, int sms, cudaStream_t st);
+int comm_update(const void* peers, int rank, int world, long lo, long n, const float* shard, float* m, float* v, int n_groups,
+                const long* group_start, const float* group_wd, const float* group_lr, float b1, float b2, float eps, float c1, float c2,
+                float max_norm, unsigned int seq, float* norm_out, unsigned int* done_counter, int* err, int sms, cudaStream_t st);
+int comm_wait_probe(const unsigned int* flag, unsigned int seq, unsigned long long limit_ns, int* err, cudaStream_t st);
 
 }  // namespace ghb

@@ -61,19 +61,64 @@ class _Scan(torch.autograd.Function):
         return dU, dW, dQ, dA, dK, dcarry, dS0, None
 
 
+class _Local(torch.autograd.Function):
+    """Chunk-local stage on the device kernels of csrc/gdn_local.cu: (q, k, v, g, beta, starts) -> (U, W, q_in, Aqk, k_out,
+    carry), inputs token-major [B, L, H, *] (strided views are fine), outputs [B, Hv, L, *]."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, start_u8):
+        B, L, Hv, dv = v.shape
+        dev = v.device
+
+        def out(d, dtype=BF16):
+            return torch.empty(B, Hv, L, d, dtype=dtype, device=dev)
+
+        U, W, Aqk, Qin, Kout = out(dv), out(128), out(CHUNK), out(128), out(128)
+        carry = torch.empty(B, Hv, L // CHUNK, dtype=torch.float32, device=dev)
+        native.ext().gdn_local_fwd(q, k, v, g, beta, start_u8, U, W, Aqk, Qin, Kout, carry)
+        native._count()
+        ctx.save_for_backward(q, k, v, g, beta, start_u8)
+        return U, W, Qin, Aqk, Kout, carry
+
+    @staticmethod
+    def backward(ctx, dU, dW, dQin, dAqk, dKout, dcarry):
+        q, k, v, g, beta, start_u8 = ctx.saved_tensors
+        B, L, Hv, dv = v.shape
+        Hk = q.shape[2]
+        dev = v.device
+        dq = torch.empty(B, L, Hv, 128, dtype=torch.float32, device=dev)
+        dk = torch.empty_like(dq)
+        dv_ = torch.empty(B, L, Hv, dv, dtype=BF16, device=dev)
+        dg = torch.empty(B, L, Hv, dtype=torch.float32, device=dev)
+        dbeta = torch.empty_like(dg)
+        c = lambda t: native._bf16(t).contiguous()
+        native.ext().gdn_local_bwd(q, k, v, g, beta, start_u8, c(dU), c(dW), c(dQin), c(dKout), c(dAqk), dcarry.float().contiguous(), dq, dk, dv_, dg, dbeta)
+        native._count()
+        if Hv != Hk:
+            dq = dq.view(B, L, Hk, Hv // Hk, 128).sum(3)
+            dk = dk.view(B, L, Hk, Hv // Hk, 128).sum(3)
+        return dq.to(q.dtype), dk.to(k.dtype), dv_.to(v.dtype), dg, dbeta, None
+
+
+def _tok_major_ok(t) -> bool:
+    return (t.dtype == BF16 and t.stride(3) == 1 and t.stride(2) == t.shape[3] and t.stride(0) == t.stride(1) * t.shape[1]
+            and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0)
+
+
 def supported(q, v) -> bool:
     return q.shape[-1] == 128 and v.shape[-1] % 128 == 0
 
 
 def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
-    rep = v.shape[2] // q.shape[2]
-    if rep > 1:
-        q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
-    B, L, H, dk = q.shape
-    dv = v.shape[-1]
-    if not supported(q, v) or chunk_size != CHUNK:
+    """q, k: [B, L, Hk, dk]; v: [B, L, Hv, dv]; g, beta: [B, L, Hv]. Returns (o [B, L, Hv, dv], final state or None)."""
+    B, L, Hk, dk = q.shape
+    Hv, dv = v.shape[2], v.shape[3]
+    if not (dk == 128 and dv in (128, 256) and chunk_size == CHUNK):
+        rep = Hv // Hk
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
         if S0 is None:
-            S0 = torch.zeros(B, H, dk, dv, dtype=torch.float32, device=q.device)
+            S0 = torch.zeros(B, Hv, dk, dv, dtype=torch.float32, device=q.device)
         o, S = ref.chunked_delta_rule(q.float(), k.float(), v.float(), g.float(), beta.float(), is_doc_start, S0.float(), chunk_size)
         return o.to(v.dtype), S
     pad = (-L) % CHUNK
@@ -81,13 +126,9 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
         q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
         g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
         is_doc_start = F.pad(is_doc_start, (0, pad))
-    parts = ref.chunk_local(q.float(), k.float(), v.float(), g.float(), beta.float(), is_doc_start, CHUNK)
-    Lp = L + pad
-
-    def rows(x):    # [B, H, n, C, *] fp32 -> [B, H, L, *] bf16
-        return x.reshape(B, H, Lp, x.shape[-1]).to(BF16).contiguous()
-
-    O, S = _Scan.apply(rows(parts["U"]), rows(parts["W"]), rows(parts["q_in"]), rows(parts["Aqk"]), rows(parts["k_out"]),
-                       parts["carry"].contiguous(), None if S0 is None else S0.float().contiguous(), need_state)
+    q, k, v = (t if _tok_major_ok(t) else native._bf16(t).contiguous() for t in (q, k, v))
+    U, W, Qin, Aqk, Kout, carry = _Local.apply(q, k, v, g.float().contiguous(), beta.float().contiguous(),
+                                               is_doc_start.to(torch.uint8).contiguous())
+    O, S = _Scan.apply(U, W, Qin, Aqk, Kout, carry, None if S0 is None else S0.float().contiguous(), need_state)
     o = O[:, :, :L].transpose(1, 2)
     return o, (S if need_state else None)

@@ -248,14 +248,15 @@ def test_attention_kernels(L, cap, docs, Hq, Hkv):
         _close(a.grad, b.grad, 4e-2, 4e-2, n)
 
 
-@pytest.mark.parametrize("L,dv,H,docs,with_state", [(128, 128, 2, False, False), (256, 256, 2, True, True), (200, 256, 1, True, False)])
-def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state):
+@pytest.mark.parametrize("L,dv,H,docs,with_state,rep", [(128, 128, 2, False, False, 1), (256, 256, 2, True, True, 1), (200, 256, 1, True, False, 1),
+                                                         (192, 128, 4, True, False, 2)])
+def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state, rep):
     from gdn_hybrid_architecture_ideas_b200.ops import gdn_native, native, reference as ref
 
     B, dk = 2, 128
     g_ = torch.Generator().manual_seed(L + dv)
-    q = torch.nn.functional.normalize(torch.randn(B, L, H, dk, generator=g_), dim=-1) * dk ** -0.5
-    k = torch.nn.functional.normalize(torch.randn(B, L, H, dk, generator=g_), dim=-1)
+    q = torch.nn.functional.normalize(torch.randn(B, L, H // rep, dk, generator=g_), dim=-1) * dk ** -0.5
+    k = torch.nn.functional.normalize(torch.randn(B, L, H // rep, dk, generator=g_), dim=-1)
     v = torch.randn(B, L, H, dv, generator=g_)
     g = -torch.rand(B, L, H, generator=g_) * 0.5
     beta = torch.rand(B, L, H, generator=g_)
@@ -272,7 +273,7 @@ def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state):
     native.check_status()
     refs = [t.detach().float().requires_grad_() for t in leaves]
     S0r = S0.to(dev).requires_grad_() if with_state else torch.zeros(B, H, dk, dv, device=dev)
-    orf, Sr = ref.chunked_delta_rule(*refs, start.to(dev), S0r, 64)
+    orf, Sr = ref.chunked_delta_rule(refs[0].repeat_interleave(rep, dim=2), refs[1].repeat_interleave(rep, dim=2), *refs[2:], start.to(dev), S0r, 64)
     _close(o, orf, 2e-2, 3e-2, "o")
     go = torch.randn_like(orf)
     if with_state:
