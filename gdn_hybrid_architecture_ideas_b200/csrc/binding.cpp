@@ -242,6 +242,33 @@ void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
                            stream()), "gdn_local_bwd");
 }
 
+// ---- fused data-parallel step over peer memory. `peers` is a CPU uint8 tensor holding the pointer table.
+void comm_reduce(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, Tensor& shard, int64_t seq, Tensor& acc, Tensor& counter,
+                 Tensor& err) {
+  const c10::cuda::CUDAGuard guard(shard.device());
+  TORCH_CHECK(!peers.is_cuda() && peers.numel() == static_cast<int64_t>(ghb::comm_peers_bytes()), "comm_reduce: peer table of ", ghb::comm_peers_bytes(), " bytes");
+  TORCH_CHECK(is_f32(shard) && shard.numel() >= n, "comm_reduce: fp32 shard");
+  check(ghb::comm_reduce(peers.data_ptr(), rank, world, lo, n, shard.data_ptr<float>(), static_cast<unsigned int>(seq), acc.data_ptr<float>(),
+                         reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), err.data_ptr<int>(), sm_count(), stream()), "comm_reduce");
+}
+void comm_update(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, const Tensor& shard, Tensor& m, Tensor& v,
+                 const std::vector<int64_t>& group_start, const std::vector<double>& group_wd, const std::vector<double>& group_lr, double b1, double b2,
+                 double eps, double c1, double c2, double max_norm, int64_t seq, Tensor& norm_out, Tensor& counter, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(shard.device());
+  TORCH_CHECK(!peers.is_cuda() && peers.numel() == static_cast<int64_t>(ghb::comm_peers_bytes()), "comm_update: peer table");
+  std::vector<long> gs(group_start.begin(), group_start.end());
+  std::vector<float> wd(group_wd.begin(), group_wd.end()), lr(group_lr.begin(), group_lr.end());
+  check(ghb::comm_update(peers.data_ptr(), rank, world, lo, n, shard.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), gs.size(), gs.data(),
+                         wd.data(), lr.data(), b1, b2, eps, c1, c2, max_norm, static_cast<unsigned int>(seq), norm_out.data_ptr<float>(),
+                         reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), err.data_ptr<int>(), sm_count(), stream()), "comm_update");
+}
+void comm_wait_probe(const Tensor& flag, int64_t seq, int64_t limit_ns, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(flag.device());
+  check(ghb::comm_wait_probe(reinterpret_cast<const unsigned int*>(flag.data_ptr<int>()), static_cast<unsigned int>(seq), limit_ns, err.data_ptr<int>(), stream()),
+        "comm_wait_probe");
+}
+int64_t comm_peers_bytes() { return ghb::comm_peers_bytes(); }
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -258,6 +285,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("comm_reduce", &comm_reduce);
+  m.def("comm_update", &comm_update);
+  m.def("comm_wait_probe", &comm_wait_probe);
+  m.def("comm_peers_bytes", &comm_peers_bytes);
   m.def("gdn_local_fwd", &gdn_local_fwd);
   m.def("gdn_local_bwd", &gdn_local_bwd);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);

@@ -28,7 +28,7 @@ struct LocalIn {
   int L, Hv, rep;                                                           // rep = Hv / Hk
 };
 
-struct ChunkScalars {
+struct alignas(16) ChunkScalars {     // 16-byte multiple: the buffers laid out after it are read as 16-byte vectors
   float c[LC], beta[LC], gamma[LC], to_end[LC];
   int seg[LC];
   float carry;
@@ -97,7 +97,7 @@ template <int DV>
 __global__ void __launch_bounds__(256)
 gdn_local_fwd_kernel(LocalIn in, __nv_bfloat16* __restrict__ U, __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ Aqk,
                      __nv_bfloat16* __restrict__ Qin, __nv_bfloat16* __restrict__ Kout, float* __restrict__ carry) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* sK = sm;                       // [64][KS]
   float* sQ = sK + LC * KS;             // [64][KS]
   float* sA = sQ + LC * KS;             // [64][AS]
@@ -175,6 +175,7 @@ gdn_local_fwd_kernel(LocalIn in, __nv_bfloat16* __restrict__ U, __nv_bfloat16* _
   }
 }
 
+static_assert(sizeof(ChunkScalars) % 16 == 0 && (LC * KS * 4) % 16 == 0 && (LC * AS * 4) % 16 == 0, "16-byte aligned shared-memory carve-up");
 constexpr size_t LOCAL_FWD_SMEM = (2 * LC * KS + LC * AS) * sizeof(float) + sizeof(ChunkScalars) + LC * LC * 2 + 64;
 
 int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
@@ -236,7 +237,7 @@ __device__ __forceinline__ void tile_dot_acc(const float* X, const float* Y, int
 template <int DV>
 __global__ void __launch_bounds__(256, 1)
 gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   float* sK = sm;
   float* sQ = sK + LC * KS;
   float* sDR = sQ + LC * KS;            // staged dR columns [64][KS]

@@ -34,6 +34,7 @@ class ZeroPlan:
     def __init__(self, model, o, dp, stage: str):
         self.model, self.o, self.dp, self.stage = model, o, dp, stage
         self.world, self.rank = dp.world, dp.rank
+        self.fused = None
 
     def build(self, device, lp_dtype):
         groups = param_groups(self.model, self.o)
@@ -58,26 +59,34 @@ class ZeroPlan:
 
     def _regrow(self, size: int, device, lp_dtype) -> None:
         f = self.flat
+        new = {}
         for name in ("params", "grads", "lp"):
             old = getattr(f, name)
             if old is None:
+                new[name] = None
                 continue
-            new = torch.zeros(size, dtype=old.dtype, device=device)
-            new[:old.numel()].copy_(old)
-            setattr(f, name, new)
-        f.size = size
-        named = dict(self.model.named_parameters())
-        mods = dict(self.model.named_modules())
-        for s in f.segments:
-            p = named[s.name]
-            p.data = f.params[s.offset:s.offset + s.numel].view(s.shape)
-            p.grad = f.grads[s.offset:s.offset + s.numel].view(s.shape)
-            owner, _, leaf = s.name.rpartition(".")
-            if f.lp is not None and leaf == "weight" and hasattr(mods.get(owner), "weight_lp"):
-                mods[owner].weight_lp = f.lp[s.offset:s.offset + s.numel].view(s.shape)
-        if f.lp is not None:
-            head = "embed.weight" if self.model.out_embed is None else "out_embed.weight"
-            self.model.head_weight_lp = f.view(f.lp, head)
+            new[name] = torch.zeros(size, dtype=old.dtype, device=device)
+            new[name][:old.numel()].copy_(old)
+        f.rebind(self.model, new["params"], new["grads"], new["lp"])
+
+    def enable_fused(self) -> bool:
+        """Switch the step to the peer-memory kernels when symmetric memory is available (CUDA, AdamW, world <= 8)."""
+        import os
+
+        from . import fused_comm
+
+        want = os.environ.get("GHB_COMM", "auto")
+        if want == "nccl" or self.o.name != "adamw" or not fused_comm.available(self.dp):
+            return False
+        try:
+            self.fused = fused_comm.FusedComm(self.dp, self.flat, self.model, lambda p, g, lp: self.flat.rebind(self.model, p, g, lp))
+        except Exception as e:   # no symmetric memory on this system: the NCCL path stays
+            if want == "fused":
+                raise
+            if self.dp.lead:
+                print(f"[zero] fused peer-memory step unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+            self.fused = None
+        return self.fused is not None
 
     # ------------------------------------------------------------------ the step
 
@@ -86,6 +95,9 @@ class ZeroPlan:
         """Reduce-scatter gradients, clip by the global norm, update the owned range, all-gather the weights.
         stats: small float64 vector summed over ranks on the way. Returns the global gradient norm."""
         f, dp = self.flat, self.dp
+        if getattr(self, "fused", None) is not None:
+            dp.all_reduce_(stats)
+            return self.fused.step(opt, lr, max_norm)
         shard = f.grads[self.lo:self.hi]
         if self.o.name == "muon":
             dp.all_reduce_(f.grads)      # whole matrices are needed by their owners

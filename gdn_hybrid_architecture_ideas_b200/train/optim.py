@@ -108,9 +108,32 @@ class FlatBuffers:
             s = self.by_name[head]
             model.head_weight_lp = self.lp[s.offset:s.offset + s.numel].view(s.shape)
 
+    def rebind(self, model, params, grads, lp) -> None:
+        """Move the model onto other flat buffers of at least this size (symmetric memory, grown ZeRO buffers): the
+        contents must already be there; parameters, gradients and bf16 copies become views of the new buffers."""
+        self.params, self.grads, self.lp = params, grads, lp
+        self.size = params.numel()
+        named = dict(model.named_parameters())
+        mods = dict(model.named_modules())
+        for s in self.segments:
+            p = named[s.name]
+            p.data = params[s.offset:s.offset + s.numel].view(s.shape)
+            p.grad = grads[s.offset:s.offset + s.numel].view(s.shape)
+            owner, _, leaf = s.name.rpartition(".")
+            if lp is not None and leaf == "weight" and hasattr(mods.get(owner), "weight_lp"):
+                mods[owner].weight_lp = lp[s.offset:s.offset + s.numel].view(s.shape)
+        if lp is not None:
+            head = "embed.weight" if model.out_embed is None else "out_embed.weight"
+            model.head_weight_lp = self.view(lp, head)
+
     def refresh_lp(self) -> None:
         if self.lp is not None:
-            self.lp.copy_(self.params)
+            if self.params.is_cuda:
+                from ..ops import native
+
+                native.cast_bf16_(self.params, self.lp)
+            else:
+                self.lp.copy_(self.params)
 
     def view(self, flat: torch.Tensor, name: str) -> torch.Tensor:
         s = self.by_name[name]

@@ -100,6 +100,8 @@ class Trainer:
 
             zero = ZeroPlan(self.model, cfg.optim, self.dp, self.sharding)
             flat, opt = zero.build(self.device, lp)
+            if self.device.type == "cuda":
+                zero.enable_fused()
         else:
             flat, opt = build_optimizer(self.model, cfg.optim, self.device, lp)
         return flat, opt, zero
