@@ -228,17 +228,18 @@ void gdn_local_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
                            start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, U.data_ptr(), W.data_ptr(), Aqk.data_ptr(), Qin.data_ptr(), Kout.data_ptr(),
                            carry.data_ptr<float>(), stream()), "gdn_local_fwd");
 }
-void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const Tensor& start, const Tensor& dU,
+void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const Tensor& start, const Tensor& U,
+                   const Tensor& W, const Tensor& dU,
                    const Tensor& dW, const Tensor& dQin, const Tensor& dKout, const Tensor& dAqk, const Tensor& dcarry, Tensor& dq, Tensor& dk, Tensor& dv_,
                    Tensor& dg, Tensor& dbeta) {
   const c10::cuda::CUDAGuard guard(q.device());
   check_tok_major(q, "q"); check_tok_major(k, "k"); check_tok_major(v, "v");
   const int B = v.size(0), L = v.size(1), Hv = v.size(2), dv = v.size(3), Hk = q.size(2);
-  for (const Tensor* t : {&dU, &dW, &dQin, &dKout, &dAqk}) TORCH_CHECK(is_bf16(*t) && t->is_contiguous(), "gdn_local_bwd: bf16 contiguous gradients");
+  for (const Tensor* t : {&U, &W, &dU, &dW, &dQin, &dKout, &dAqk}) TORCH_CHECK(is_bf16(*t) && t->is_contiguous(), "gdn_local_bwd: bf16 contiguous gradients");
   TORCH_CHECK(is_f32(dq) && is_f32(dk) && is_bf16(dv_) && is_f32(dg) && is_f32(dbeta) && is_f32(dcarry) && dq.is_contiguous() && dk.is_contiguous() && dv_.is_contiguous(), "gdn_local_bwd: outputs");
   check(ghb::gdn_local_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), k.stride(1), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(),
-                           start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, dU.data_ptr(), dW.data_ptr(), dQin.data_ptr(), dKout.data_ptr(), dAqk.data_ptr(),
-                           dcarry.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv_.data_ptr(), dg.data_ptr<float>(), dbeta.data_ptr<float>(),
+                           start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, U.data_ptr(), W.data_ptr(), dU.data_ptr(), dW.data_ptr(), dQin.data_ptr(), dKout.data_ptr(),
+                           dAqk.data_ptr(), dcarry.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv_.data_ptr(), dg.data_ptr<float>(), dbeta.data_ptr<float>(),
                            stream()), "gdn_local_bwd");
 }
 

@@ -211,6 +211,7 @@ int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long 
 namespace ghb {
 
 struct LocalGrads {
+  const __nv_bfloat16* U; const __nv_bfloat16* W;       // the forward's outputs (X = [U | W])
   const __nv_bfloat16* dU; const __nv_bfloat16* dW; const __nv_bfloat16* dQin; const __nv_bfloat16* dKout; const __nv_bfloat16* dAqk;
   const float* dcarry;
   float* dq; float* dk;            // [B, L, Hv, 128] fp32 (per value head; heads sharing a key head are summed by the caller)
@@ -244,8 +245,8 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
   float* sX = sDR + LC * KS;            // staged X columns  [64][KS]
   float* sG = sX + LC * KS;             // G, later dKK      [64][AS]
   float* sAq = sG + LC * AS;            // Aqk, later dQK    [64][AS]
-  float* sAm = sAq + LC * AS;           // A = beta G        [64][AS]
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sAm + LC * AS);
+  float* sT = sAq + LC * AS;            // T = (I + A)^-1    [64][AS]
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sT + LC * AS);
   float* sdc = reinterpret_cast<float*>(sc + 1);   // [64] decay gradient
   float* sdb = sdc + LC;                            // [64] beta gradient
 
@@ -273,72 +274,88 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
         const int i = ty + 16 * ii, j = tx + 16 * jj;
         const float e = (j <= i && sc->seg[i] == sc->seg[j]) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
         sG[i * AS + j] = (j < i) ? kk[ii][jj] * e : 0.f;
-        sAm[i * AS + j] = (j < i) ? sc->beta[i] * kk[ii][jj] * e : 0.f;
         sAq[i * AS + j] = qk[ii][jj] * e;
       }
   }
   __syncthreads();
 
-  // ---- solve and its adjoint, a column per thread; dA accumulated over staged column blocks
+  // ---- T = (I + A)^-1, one column per thread (threads 0..63): x_c = 1, x_i = -sum_{m < i} A_im x_m
+  if (t < LC) {
+    float x[LC];
+#pragma unroll
+    for (int i = 0; i < LC; ++i) x[i] = (i == t) ? 1.f : 0.f;
+#pragma unroll
+    for (int i = 1; i < LC; ++i) {
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int m = 0; m + 1 < i; m += 2) { a0 += sG[i * AS + m] * x[m]; a1 += sG[i * AS + m + 1] * x[m + 1]; }
+      if (i & 1) a0 += sG[i * AS + i - 1] * x[i - 1];
+      x[i] -= sc->beta[i] * (a0 + a1);
+    }
+#pragma unroll
+    for (int i = 0; i < LC; ++i) sT[i * AS + t] = x[i];
+  }
+  __syncthreads();
+
+  // ---- per block of 128 columns of [U | W]: X from the forward's outputs, dR = T^T dX, dA -= dR X^T
   float dA[4][4];
 #pragma unroll
   for (int ii = 0; ii < 4; ++ii)
 #pragma unroll
     for (int jj = 0; jj < 4; ++jj) dA[ii][jj] = 0.f;
   constexpr int COLS = DV + LK;
+  float* sDX = sQ;      // the q tile is not needed again until the outputs; it is reloaded there
 #pragma unroll 1
-  for (int blk = 0; blk < COLS / 128; ++blk) {      // 128 columns at a time; the W columns form the last block
-    if (t < 128) {
-      const int col = blk * 128 + t;
-      float x[LC], dr[LC];
-      if (col < DV) {
-        const __nv_bfloat16* vp = in.v + tok0 * in.v_tok + static_cast<long>(hv) * DV + col;
+  for (int blk = 0; blk < COLS / 128; ++blk) {
+    const bool is_u = blk * 128 < DV;
+    const int c0 = is_u ? blk * 128 : 0;
+    const __nv_bfloat16* gx = is_u ? gr.dU + row0 * DV + c0 : gr.dW + row0 * LK;
+    const __nv_bfloat16* xx = is_u ? gr.U + row0 * DV + c0 : gr.W + row0 * LK;
+    const int ld = is_u ? DV : LK;
+    for (int idx = t; idx < LC * 16; idx += 256) {          // 64 rows x 16 vectors of 8
+      const int row = idx >> 4, c8 = (idx & 15) * 8;
+      const uint4 a = *reinterpret_cast<const uint4*>(gx + static_cast<long>(row) * ld + c8);
+      const uint4 bq = *reinterpret_cast<const uint4*>(xx + static_cast<long>(row) * ld + c8);
+      const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
-        for (int i = 0; i < LC; ++i) x[i] = sc->beta[i] * __bfloat162float(vp[i * in.v_tok]);
-      } else {
-#pragma unroll
-        for (int i = 0; i < LC; ++i) {
-          x[i] = sc->seg[i] == 0 ? sc->beta[i] * sc->gamma[i] * sK[i * KS + (col - DV)] : 0.f;
-        }
+      for (int e = 0; e < 4; ++e) {
+        const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wa[e]));
+        const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wb[e]));
+        sDX[row * KS + c8 + 2 * e] = fa.x; sDX[row * KS + c8 + 2 * e + 1] = fa.y;
+        sX[row * KS + c8 + 2 * e] = fb.x; sX[row * KS + c8 + 2 * e + 1] = fb.y;
       }
+    }
+    __syncthreads();
+    {
+      const int col = t & 127, i0 = (t >> 7) * 32;          // 32 rows of one column per thread
+      float acc[32];
 #pragma unroll
-      for (int i = 1; i < LC; ++i) {
-        float acc = 0.f;
+      for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+      for (int j = i0; j < LC; ++j) {                          // dR_i = sum_{j >= i} T_ji dX_j
+        const float d = sDX[j * KS + col];
 #pragma unroll
-        for (int j = 0; j < i; ++j) acc += sAm[i * AS + j] * x[j];
-        x[i] -= acc;
+        for (int e = 0; e < 32; ++e) acc[e] += sT[j * AS + i0 + e] * d;
       }
+      if (is_u) {      // dv = beta dR_u ; dbeta += dR_u . v
+        const __nv_bfloat16* vp = in.v + tok0 * in.v_tok + static_cast<long>(hv) * DV + c0 + col;
 #pragma unroll
-      for (int i = 0; i < LC; ++i) sX[i * KS + t] = x[i];
-      __syncwarp();                     // x is dead from here: keeps the two substitutions from being interleaved
-      asm volatile("" ::: "memory");
-#pragma unroll
-      for (int i = 0; i < LC; ++i) dr[i] = col < DV ? __bfloat162float(gr.dU[(row0 + i) * DV + col]) : __bfloat162float(gr.dW[(row0 + i) * LK + (col - DV)]);
-#pragma unroll
-      for (int i = LC - 2; i >= 0; --i) {
-        float acc = 0.f;
-#pragma unroll
-        for (int j = i + 1; j < LC; ++j) acc += sAm[j * AS + i] * dr[j];
-        dr[i] -= acc;
-      }
-#pragma unroll
-      for (int i = 0; i < LC; ++i) sDR[i * KS + t] = dr[i];
-      if (col < DV) {      // dv = beta dR_u ; dbeta += dR_u . v
-        const __nv_bfloat16* vp = in.v + tok0 * in.v_tok + static_cast<long>(hv) * DV + col;
-#pragma unroll
-        for (int i = 0; i < LC; ++i) {
-          gr.dv[(tok0 + i) * in.Hv * DV + static_cast<long>(hv) * DV + col] = __float2bfloat16(sc->beta[i] * dr[i]);
-          float p = dr[i] * __bfloat162float(vp[i * in.v_tok]);
+        for (int e = 0; e < 32; ++e) {
+          const int i = i0 + e;
+          gr.dv[(tok0 + i) * in.Hv * DV + static_cast<long>(hv) * DV + c0 + col] = __float2bfloat16(sc->beta[i] * acc[e]);
+          float p = acc[e] * __bfloat162float(vp[i * in.v_tok]);
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
           if (lane == 0) atomicAdd(&sdb[i], p);
         }
       }
+#pragma unroll
+      for (int e = 0; e < 32; ++e) sDR[(i0 + e) * KS + col] = acc[e];
     }
     __syncthreads();
     tile_dot_acc(sDR, sX, ty, tx, dA);
-    if (blk + 1 < COLS / 128) __syncthreads();
+    __syncthreads();
   }
+  load_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
   __syncthreads();   // sDR / sX now hold the W columns: dR_w [i][kk] and W [i][kk]
 
   // ---- score matrices: beta / decay gradients, then overwrite sG <- dKK, sAq <- dQK
@@ -447,13 +464,13 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
 constexpr size_t LOCAL_BWD_SMEM = (4 * LC * KS + 3 * LC * AS + 2 * LC) * sizeof(float) + sizeof(ChunkScalars) + 64;
 
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
-                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* dU, const void* dW, const void* dQin,
+                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU, const void* dW, const void* dQin,
                   const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv, float* dg, float* dbeta,
                   cudaStream_t st) {
   if (L % LC || (dv != 128 && dv != 256) || Hv % Hk) return 1;
   LocalIn in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), q_tok, k_tok, v_tok,
              g, beta, start, L, Hv, Hv / Hk};
-  LocalGrads gr{static_cast<const __nv_bfloat16*>(dU), static_cast<const __nv_bfloat16*>(dW), static_cast<const __nv_bfloat16*>(dQin),
+  LocalGrads gr{static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(dU), static_cast<const __nv_bfloat16*>(dW), static_cast<const __nv_bfloat16*>(dQin),
                 static_cast<const __nv_bfloat16*>(dKout), static_cast<const __nv_bfloat16*>(dAqk), dcarry, dq, dk,
                 static_cast<__nv_bfloat16*>(dvv), dg, dbeta};
   dim3 grid(L / LC, Hv, B);

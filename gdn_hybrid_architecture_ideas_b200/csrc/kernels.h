@@ -56,9 +56,9 @@ int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long 
                   const unsigned char* start, int B, int L, int Hv, int Hk, int dv, void* U, void* W, void* Aqk, void* Qin, void* Kout,
                   float* carry, cudaStream_t st);
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
-                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* dU, const void* dW, const void* dQin,
-                  const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv, float* dg, float* dbeta,
-                  cudaStream_t st);
+                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU,
+                  const void* dW, const void* dQin, const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv,
+                  float* dg, float* dbeta, cudaStream_t st);
 
 // Fused data-parallel step over peer memory (csrc/comm.cu). `peers` points at a host copy of the CommPeers table
 // (comm_peers_bytes() bytes: 5 arrays of 8 device pointers, then 3 multicast pointers).

@@ -77,12 +77,12 @@ class _Local(torch.autograd.Function):
         carry = torch.empty(B, Hv, L // CHUNK, dtype=torch.float32, device=dev)
         native.ext().gdn_local_fwd(q, k, v, g, beta, start_u8, U, W, Aqk, Qin, Kout, carry)
         native._count()
-        ctx.save_for_backward(q, k, v, g, beta, start_u8)
+        ctx.save_for_backward(q, k, v, g, beta, start_u8, U, W)
         return U, W, Qin, Aqk, Kout, carry
 
     @staticmethod
     def backward(ctx, dU, dW, dQin, dAqk, dKout, dcarry):
-        q, k, v, g, beta, start_u8 = ctx.saved_tensors
+        q, k, v, g, beta, start_u8, U, W = ctx.saved_tensors
         B, L, Hv, dv = v.shape
         Hk = q.shape[2]
         dev = v.device
@@ -92,7 +92,7 @@ class _Local(torch.autograd.Function):
         dg = torch.empty(B, L, Hv, dtype=torch.float32, device=dev)
         dbeta = torch.empty_like(dg)
         c = lambda t: native._bf16(t).contiguous()
-        native.ext().gdn_local_bwd(q, k, v, g, beta, start_u8, c(dU), c(dW), c(dQin), c(dKout), c(dAqk), dcarry.float().contiguous(), dq, dk, dv_, dg, dbeta)
+        native.ext().gdn_local_bwd(q, k, v, g, beta, start_u8, U, W, c(dU), c(dW), c(dQin), c(dKout), c(dAqk), dcarry.float().contiguous(), dq, dk, dv_, dg, dbeta)
         native._count()
         if Hv != Hk:
             dq = dq.view(B, L, Hk, Hv // Hk, 128).sum(3)

@@ -1,0 +1,52 @@
+"""Multi-GPU tests (one process per GPU under torchrun): the fused peer-memory data-parallel step equals the NCCL
+reduce-scatter / AdamW / all-gather path, with and without NVSwitch multimem; and the bounded device-side wait reports
+a status instead of hanging when its flag is never set."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _run(out: Path, mode: str, nproc: int, port: int, env=None):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "dp_worker.py"), str(out), mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env={**os.environ, **(env or {})})
+    assert r.returncode == 0, r.stderr[-3000:]
+    return torch.load(out, weights_only=False)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_fused_step_equals_nccl(tmp_path, multimem):
+    n = min(torch.cuda.device_count(), 4)
+    ref = _run(tmp_path / "nccl.pt", "nccl", n, 29631)
+    got = _run(tmp_path / "fused.pt", "fused", n, 29633, {"GHB_COMM_MULTIMEM": multimem})
+    assert got["fused"] and not ref["fused"]
+    assert max(abs(a - b) for a, b in zip(ref["losses"], got["losses"])) < 2e-2, (ref["losses"], got["losses"])
+    diff = (ref["params"] - got["params"]).abs().max().item()
+    assert diff < 5e-3, diff
+
+
+@pytest.mark.gpu
+def test_bounded_wait_reports_status():
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    dev = torch.device("cuda", 0)
+    flag = torch.zeros(1, dtype=torch.int32, device=dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    native.ext().comm_wait_probe(flag, 1, 50_000_000, err)     # nothing ever sets the flag: gives up after 50 ms
+    torch.cuda.synchronize()
+    assert int(err.item()) == 404
+    flag.fill_(1)
+    err.zero_()
+    native.ext().comm_wait_probe(flag, 1, 50_000_000, err)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 0
+    assert torch.ones(4, device=dev).sum().item() == 4.0      # the context is still usable
