@@ -243,6 +243,20 @@ void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
                            stream()), "gdn_local_bwd");
 }
 
+void decode_attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lens, const c10::optional<Tensor>& doc_start, const Tensor& cos_t,
+                      const Tensor& sin_t, Tensor& out, Tensor& part_o, Tensor& part_ml, int64_t rot, int64_t cap, int64_t splits, double scale) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(is_f32(q) && q.is_contiguous() && q.dim() == 3 && q.size(2) == 64, "decode_attention: q fp32 [B, Hq, 64]");
+  check_heads(k, "k cache"); check_heads(v, "v cache");
+  TORCH_CHECK(lens.scalar_type() == torch::kInt32 && is_bf16(out) && out.is_contiguous() && is_f32(part_o) && is_f32(part_ml) && is_f32(cos_t) && is_f32(sin_t),
+              "decode_attention: dtypes");
+  const int B = q.size(0), Hq = q.size(1), T = k.size(1), Hkv = k.size(2);
+  TORCH_CHECK(part_o.numel() >= static_cast<int64_t>(B) * Hq * splits * 64 && part_ml.numel() >= static_cast<int64_t>(B) * Hq * splits * 2, "decode_attention: scratch too small");
+  check(ghb::decode_attention(q.data_ptr<float>(), k.data_ptr(), v.data_ptr(), lens.data_ptr<int>(), doc_start.has_value() ? doc_start->data_ptr<int>() : nullptr,
+                              cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), out.data_ptr(), part_o.data_ptr<float>(), part_ml.data_ptr<float>(), B, T, Hq,
+                              Hkv, rot, cap, rot ? cos_t.size(0) : 1, splits, scale, stream()), "decode_attention");
+}
+
 // ---- fused data-parallel step over peer memory. `peers` is a CPU uint8 tensor holding the pointer table.
 void comm_reduce(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, Tensor& shard, int64_t seq, Tensor& acc, Tensor& counter,
                  Tensor& err) {
@@ -286,6 +300,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("decode_attention", &decode_attention);
   m.def("comm_reduce", &comm_reduce);
   m.def("comm_update", &comm_update);
   m.def("comm_wait_probe", &comm_wait_probe);

@@ -1,0 +1,173 @@
+// Single-token decode attention over a static KV cache (flash-decoding: split the cached positions over CTAs, merge
+// the partial softmax statistics), with the rotary distance cap applied through the relative-rotation identity
+//   R(p_q) q . R(p_k) k = q . R(-(p_q - p_k)) k     and, beyond the cap C,   R(C) q . k = q . R(-C) k,
+// so the cache holds ONE copy of the keys (normed, unrotated) and the kernel rotates by min(distance, C) while it
+// scores; the reference keeps a rotated and an unrotated copy and scores near and far keys in two partial attentions
+// merged by log-sum-exp (ced/infer/engine.py:391-457). Batched (the reference engine is batch 1), any query/KV head
+// grouping; memory-bound by design: every cached key and value byte is read once per step.
+#include "kernels.h"
+#include <cuda_bf16.h>
+
+namespace ghb {
+
+constexpr int DH = 64;          // head dimension
+constexpr int DTILE = 32;       // positions per warp tile
+constexpr int DWARPS = 4;
+constexpr int MAXG = 16;        // query heads per KV head
+
+struct DecodeArgs {
+  const float* q;               // [B, Hq, 64] normed, temperature-scaled, unrotated queries
+  const __nv_bfloat16* k;       // [B, T, Hkv, 64] normed, unrotated keys
+  const __nv_bfloat16* v;       // [B, T, Hkv, 64]
+  const int* lens;              // [B] cached positions including the current token
+  const int* doc_start;         // [B] first position of the current document (earlier positions are masked), or null
+  const float* cos_t; const float* sin_t;   // [n_angles, r/2] rotation tables indexed by min(distance, cap)
+  float* part_o; float* part_ml;             // [B, Hq, splits, 64], [B, Hq, splits, 2]
+  int T, Hq, Hkv, rot, cap, n_angles, splits;
+  float scale;
+};
+
+template <int G>
+__global__ void __launch_bounds__(DWARPS * 32)
+decode_attn_partial_kernel(DecodeArgs a) {
+  __shared__ float sq[MAXG][DH];
+  __shared__ float sp[DWARPS][DTILE][MAXG];
+  __shared__ float s_m[DWARPS][MAXG], s_l[DWARPS][MAXG], s_o[DWARPS][MAXG][DH];
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < G * DH; i += blockDim.x) sq[i / DH][i % DH] = a.q[(static_cast<long>(b) * a.Hq + hk * G + i / DH) * DH + i % DH] * a.scale;
+  __syncthreads();
+  const int len = a.lens[b];
+  const int first = a.doc_start ? a.doc_start[b] : 0;
+  const int per = (len - first + a.splits - 1) / a.splits;
+  const int lo = first + split * per, hi = min(len, lo + per);
+  const int qpos = len - 1;
+  const int half = a.rot / 2;
+  float m[G], l[G], o[G][2];
+#pragma unroll
+  for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; o[g][0] = o[g][1] = 0.f; }
+  for (int t0 = lo + warp * DTILE; t0 < hi; t0 += DWARPS * DTILE) {
+    const int t = t0 + lane;
+    float logit[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) logit[g] = -INFINITY;
+    if (t < hi) {
+      const __nv_bfloat16* kp = a.k + ((static_cast<long>(b) * a.T + t) * a.Hkv + hk) * DH;
+      float kf[DH];
+#pragma unroll
+      for (int c = 0; c < DH / 8; ++c) {
+        const uint4 pk = reinterpret_cast<const uint4*>(kp)[c];
+        const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); kf[c * 8 + 2 * e] = f.x; kf[c * 8 + 2 * e + 1] = f.y; }
+      }
+      if (half > 0) {       // rotate the key by -(min(distance, cap)): k'_i = k_i cos + k_{i+half} sin ; k'_{i+half} = k_{i+half} cos - k_i sin
+        int d = qpos - t;
+        if (a.cap >= 0 && d > a.cap) d = a.cap;
+        d = min(d, a.n_angles - 1);
+        // half is one of 8 / 16 / 32 in practice; static indices keep the key row in registers
+#define GHB_ROT(HALF)                                                                   \
+        _Pragma("unroll") for (int i = 0; i < HALF; ++i) {                              \
+          const float c = a.cos_t[d * HALF + i], s = a.sin_t[d * HALF + i];              \
+          const float x1 = kf[i], x2 = kf[i + HALF];                                     \
+          kf[i] = x1 * c + x2 * s;                                                       \
+          kf[i + HALF] = x2 * c - x1 * s;                                                \
+        }
+        if (half == 8) { GHB_ROT(8) } else if (half == 16) { GHB_ROT(16) } else if (half == 32) { GHB_ROT(32) } else if (half == 4) { GHB_ROT(4) }
+#undef GHB_ROT
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float acc = 0.f;
+#pragma unroll
+        for (int dd = 0; dd < DH; ++dd) acc += sq[g][dd] * kf[dd];
+        logit[g] = acc;
+      }
+    }
+    // tile softmax statistics per head, then P V with lanes over dimensions
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float mx = logit[g];
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+      const float m_new = fmaxf(m[g], mx);
+      const float p = (logit[g] == -INFINITY) ? 0.f : __expf(logit[g] - m_new);
+      float ps = p;
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, s);
+      const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
+      l[g] = l[g] * alpha + ps;
+      o[g][0] *= alpha; o[g][1] *= alpha;
+      m[g] = m_new;
+      sp[warp][lane][g] = p;
+    }
+    __syncwarp();
+    const int n = min(DTILE, hi - t0);
+    for (int j = 0; j < n; ++j) {
+      const __nv_bfloat162 vv = reinterpret_cast<const __nv_bfloat162*>(a.v + ((static_cast<long>(b) * a.T + t0 + j) * a.Hkv + hk) * DH)[lane];
+      const float v0 = __bfloat162float(vv.x), v1 = __bfloat162float(vv.y);
+#pragma unroll
+      for (int g = 0; g < G; ++g) { const float p = sp[warp][j][g]; o[g][0] += p * v0; o[g][1] += p * v1; }
+    }
+    __syncwarp();
+  }
+  // merge the warps of this CTA, write the split's partial result
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+    s_o[warp][g][2 * lane] = o[g][0]; s_o[warp][g][2 * lane + 1] = o[g][1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * DH; idx += blockDim.x) {
+    const int g = idx / DH, d = idx % DH;
+    float mm = -INFINITY;
+    for (int w = 0; w < DWARPS; ++w) mm = fmaxf(mm, s_m[w][g]);
+    float ll = 0.f, oo = 0.f;
+    for (int w = 0; w < DWARPS; ++w) {
+      const float sc = (s_m[w][g] == -INFINITY) ? 0.f : __expf(s_m[w][g] - mm);
+      ll += s_l[w][g] * sc; oo += s_o[w][g][d] * sc;
+    }
+    const long base = (static_cast<long>(b) * a.Hq + hk * G + g) * a.splits + split;
+    a.part_o[base * DH + d] = oo;
+    if (d == 0) { a.part_ml[base * 2] = mm; a.part_ml[base * 2 + 1] = ll; }
+  }
+}
+
+__global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                                         int splits) {
+  const long bh = blockIdx.x;           // (b, query head)
+  const int d = threadIdx.x;            // 64 threads
+  float mm = -INFINITY;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(bh * splits + s) * 2]);
+  float ll = 0.f, oo = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[(bh * splits + s) * 2];
+    const float sc = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+    ll += part_ml[(bh * splits + s) * 2 + 1] * sc;
+    oo += part_o[(bh * splits + s) * DH + d] * sc;
+  }
+  out[bh * DH + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+}
+
+// q: [B, Hq, 64] fp32; k, v: [B, T, Hkv, 64] bf16; out: [B, Hq, 64] bf16; part_o / part_ml: scratch of
+// B*Hq*splits*64 and B*Hq*splits*2 floats. cap < 0: no distance cap. rot: rotary dimensions (0: position-free).
+int decode_attention(const float* q, const void* k, const void* v, const int* lens, const int* doc_start, const float* cos_t, const float* sin_t,
+                     void* out, float* part_o, float* part_ml, int B, int T, int Hq, int Hkv, int rot, int cap, int n_angles, int splits,
+                     float scale, cudaStream_t st) {
+  if (Hq % Hkv || Hq / Hkv > MAXG || (rot != 0 && rot != 8 && rot != 16 && rot != 32 && rot != 64) || splits < 1) return 1;
+  DecodeArgs a{q, static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), lens, doc_start, cos_t, sin_t, part_o, part_ml,
+               T, Hq, Hkv, rot, cap, n_angles, splits, scale};
+  const dim3 grid(splits, Hkv, B);
+  switch (Hq / Hkv) {
+    case 1: decode_attn_partial_kernel<1><<<grid, DWARPS * 32, 0, st>>>(a); break;
+    case 2: decode_attn_partial_kernel<2><<<grid, DWARPS * 32, 0, st>>>(a); break;
+    case 4: decode_attn_partial_kernel<4><<<grid, DWARPS * 32, 0, st>>>(a); break;
+    case 8: decode_attn_partial_kernel<8><<<grid, DWARPS * 32, 0, st>>>(a); break;
+    case 16: decode_attn_partial_kernel<16><<<grid, DWARPS * 32, 0, st>>>(a); break;
+    default: return 1;
+  }
+  decode_attn_merge_kernel<<<B * Hq, DH, 0, st>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+}  // namespace ghb

@@ -60,6 +60,10 @@ int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long 
                   const void* dW, const void* dQin, const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv,
                   float* dg, float* dbeta, cudaStream_t st);
 
+int decode_attention(const float* q, const void* k, const void* v, const int* lens, const int* doc_start, const float* cos_t, const float* sin_t,
+                     void* out, float* part_o, float* part_ml, int B, int T, int Hq, int Hkv, int rot, int cap, int n_angles, int splits,
+                     float scale, cudaStream_t st);
+
 // Fused data-parallel step over peer memory (csrc/comm.cu). `peers` points at a host copy of the CommPeers table
 // (comm_peers_bytes() bytes: 5 arrays of 8 device pointers, then 3 multicast pointers).
 size_t comm_peers_bytes();

@@ -22,7 +22,7 @@ def main():
     model.encoder.n_layers, model.encoder.nope_global_layers, model.vocab_size = 4, (0,), 4096
     cfg = C.TrainConfig(model=model, data=C.DataConfig(kind="uniform", seq_len=256, batch_size=2 * dp.world, seed=5), steps=100, seed=7)
     cfg.autocast, cfg.head_impl, cfg.metrics_jsonl, cfg.log_every, cfg.optimizer_sharding = "bfloat16", "fused", False, 0, "zero2"
-    cfg.optim.warmup_steps = 1
+    cfg.optim.warmup_steps, cfg.optim.lr = 1, 1e-4     # small steps: Adam's sign-like first updates would amplify rounding noise
     t = Trainer(cfg, None, dp)
     losses = [t.train_step()["loss"] for _ in range(3)]
     native.check_status()

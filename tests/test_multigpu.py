@@ -30,8 +30,8 @@ def test_fused_step_equals_nccl(tmp_path, multimem):
     got = _run(tmp_path / "fused.pt", "fused", n, 29633, {"GHB_COMM_MULTIMEM": multimem})
     assert got["fused"] and not ref["fused"]
     assert max(abs(a - b) for a, b in zip(ref["losses"], got["losses"])) < 2e-2, (ref["losses"], got["losses"])
-    diff = (ref["params"] - got["params"]).abs().max().item()
-    assert diff < 5e-3, diff
+    diff = (ref["params"] - got["params"]).abs()
+    assert diff.max().item() < 1e-3 and diff.mean().item() < 2e-5, (diff.max().item(), diff.mean().item())
 
 
 @pytest.mark.gpu
