@@ -207,7 +207,7 @@ def run_decode(args) -> dict:
     model = build_model(cfg).to(dev)
     flat, _ = build_optimizer(model, C.OptimConfig(), dev, torch.bfloat16)      # bf16 weight copies for the GEMMs
     B, P = args.batch, args.prompt
-    eng = DecodeEngine(model, B, P + args.steps + args.warmup + 8)
+    eng = DecodeEngine(model, B, P + 2 * args.steps + args.warmup + 8)      # device-timed and end-to-end loops both generate `steps` tokens
     g = torch.Generator().manual_seed(1 + (0 if dp is None else dp.rank))
     prompts = torch.randint(0, VOCAB, (B, P), generator=g).pin_memory().to(dev, non_blocking=True)
     t0 = time.time()

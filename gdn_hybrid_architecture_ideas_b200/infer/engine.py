@@ -70,6 +70,7 @@ class DecodeEngine:
         self.part_o = torch.zeros(B * hq * self.splits * 64, dtype=torch.float32, device=dev)
         self.part_ml = torch.zeros(B * hq * self.splits * 2, dtype=torch.float32, device=dev)
         self.graph = None
+        self._host_len = 0          # host-side mirror of the (equal) row lengths: guards the static capacity before each launch
 
     # ------------------------------------------------------------------ sizes
 
@@ -119,6 +120,7 @@ class DecodeEngine:
             self.doc_start[lo:hi] = start.to(torch.int32)
             self.doc_id[lo:hi] = d[:, -1]
         self.lens.fill_(P)
+        self._host_len = P
         nxt = torch.cat(first)
         self.tokens.copy_(nxt)
         return nxt
@@ -218,6 +220,9 @@ class DecodeEngine:
     @torch.no_grad()
     def step(self) -> torch.Tensor:
         """Consume `self.tokens`, append it to the caches, return the next token of every row (B,) (a static buffer)."""
+        if self._host_len + 1 > self.T:
+            raise RuntimeError(f"decode cache is full: {self._host_len} positions cached, capacity {self.T}")
+        self._host_len += 1
         if not self.use_graph:
             self._step_impl()
             return self.next_tokens
@@ -229,6 +234,8 @@ class DecodeEngine:
     def _capture(self) -> None:
         """Warm up on a side stream, then capture one step. State touched by the warm-up steps is restored before the
         capture, and the captured step itself is not run by capture."""
+        if self._host_len + 2 > self.T:
+            raise RuntimeError("the capture's two warm-up steps need two free cache positions")
         snap = self._snapshot()
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))

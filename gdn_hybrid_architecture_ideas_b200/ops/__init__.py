@@ -82,8 +82,17 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=
     rep = v.shape[2] // q.shape[2]
     if rep > 1:
         q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
+    out_dtype = v.dtype
+    if q.is_cuda:      # a cached step on the device: the recurrence runs in fp32 on the fp32 state
+        q, k, v, g, beta = (t.float() for t in (q, k, v, g, beta))
     if S0 is None:
         S0 = q.new_zeros(q.shape[0], v.shape[2], q.shape[-1], v.shape[-1])
+    elif q.is_cuda:
+        S0 = S0.float()
+    if q.is_cuda:
+        o, S = (ref.delta_rule_recurrence if (kernel == "recurrence" or q.shape[1] == 1) else ref.chunked_delta_rule)(
+            q, k, v, g, beta, is_doc_start, S0, *(() if (kernel == "recurrence" or q.shape[1] == 1) else (chunk_size,)))
+        return o.to(out_dtype), S
     if kernel == "recurrence" or q.shape[1] == 1:
         return ref.delta_rule_recurrence(q, k, v, g, beta, is_doc_start, S0)
     return ref.chunked_delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size)

@@ -228,7 +228,8 @@ class _CatLinear(torch.autograd.Function):
         x2 = _bf16(x).reshape(-1, x.shape[-1]).contiguous()
         n1, n2 = lp1.shape[0], lp2.shape[0]
         out = torch.empty(x2.shape[0], n1 + n2, dtype=BF16, device=x.device)
-        adjacent = (lp1.data_ptr() + lp1.numel() * 2 == lp2.data_ptr()) and lp1.is_contiguous() and lp2.is_contiguous()
+        adjacent = (lp1.data_ptr() + lp1.numel() * 2 == lp2.data_ptr() and lp1.is_contiguous() and lp2.is_contiguous()
+                    and lp1.untyped_storage().data_ptr() == lp2.untyped_storage().data_ptr())     # views of one flat buffer
         if adjacent:
             wcat = torch.as_strided(lp1, (n1 + n2, lp1.shape[1]), (lp1.shape[1], 1))
             gemm(x2, wcat, out=out)

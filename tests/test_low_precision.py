@@ -1,0 +1,92 @@
+"""Block-scaled formats: bytes and values equal the reference's emulations; quantised linears train (finite, close to
+bf16) and are inactive in evaluation mode."""
+
+import pytest
+import torch
+
+from gdn_hybrid_architecture_ideas_b200 import config as C
+from gdn_hybrid_architecture_ideas_b200.models import build_model
+from gdn_hybrid_architecture_ideas_b200.ops import lowp
+from tests.helpers import random_rows
+
+
+def _samples():
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(48, 100, generator=g) * torch.logspace(-6, 4, 48)[:, None]
+    x[0, :32] = 0
+    x[1, 5] = float("inf")
+    x[2, 7] = float("nan")
+    x[3] *= 1e30
+    return x
+
+
+def test_mxfp8_bytes_equal_reference(reference):
+    import ced.model.mxfp8 as rmx
+
+    x = _samples()
+    for dim in (-1, 0):
+        q, b = lowp.mx_quantize(x, dim)
+        rq, rb = rmx.quantize(x, dim)
+        assert torch.equal(q.view(torch.uint8), rq.view(torch.uint8)) and torch.equal(b, rb)
+        d, rd = lowp.mx_dequantize(q, b, dim), rmx.dequantize(rq, rb, dim)
+        assert torch.equal(torch.nan_to_num(d, nan=7.0), torch.nan_to_num(rd, nan=7.0))
+
+
+def test_nvfp4_values_equal_reference(reference):
+    import ced.model.nvfp4 as rnv
+
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(40, 70, generator=g) * 3
+    assert torch.equal(lowp.nvfp4_fake(x), rnv.fake_quantize(x))
+    assert torch.equal(lowp.nvfp4_fake(x, block_2d=True), rnv.fake_quantize(x, block_2d=True))
+    assert torch.equal(lowp.rht_matrix(), rnv.rht_matrix())
+    assert torch.equal(lowp.rht_tokens(x, lowp.rht_matrix()), rnv.rht_tokens(x, rnv.rht_matrix()))
+    torch.manual_seed(9)
+    a = lowp.nvfp4_fake(x, stochastic=True)
+    torch.manual_seed(9)
+    b = rnv.fake_quantize(x, stochastic=True)
+    assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("scaling", ["mxfp8", "rowwise", "tensorwise"])
+def test_fp8_linear_matches_reference(reference, scaling):
+    import ced.model.fp8 as rfp8
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(3, 20, 64, generator=g, requires_grad=True)
+    w = (torch.randn(96, 64, generator=g) * 0.1).requires_grad_()
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    kind = "mxfp8" if scaling == "mxfp8" else "fp8_" + scaling
+    y = lowp.Recipe(kind).emulated_linear(x, w)
+    yr = rfp8.FP8LinearFunction.apply(x2, w2, scaling, torch.float32)
+    assert torch.allclose(y, yr, atol=1e-5, rtol=1e-5)
+    gy = torch.randn(3, 20, 96, generator=g)
+    y.backward(gy), yr.backward(gy)
+    assert torch.allclose(x.grad, x2.grad, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(w.grad, w2.grad, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("which", ["mxfp8", "nvfp4"])
+def test_quantised_model_trains_and_evaluates_in_high_precision(which):
+    cfg = C.tiny_control_config()
+    cfg.d_model, cfg.ffn_hidden = 64, 192
+    if which == "mxfp8":
+        cfg.fp8.mode, cfg.fp8.scaling = "linears", "mxfp8"
+    else:
+        cfg.nvfp4.mode = "all_linears"
+    torch.manual_seed(0)
+    m = build_model(cfg)
+    plain = C.tiny_control_config()
+    torch.manual_seed(0)
+    base = build_model(plain)
+    quantised = [n for n, mod in m.named_modules() if getattr(mod, "precision", "bf16") != "bf16"]
+    assert quantised and not any(n.endswith(("in_proj_a", "in_proj_b")) for n in quantised)
+    tok, doc = random_rows(2, 32)
+    m.eval(), base.eval()
+    assert torch.equal(m(tok, doc).logits, base(tok, doc).logits)          # evaluation runs in high precision
+    m.train(), base.train()
+    a, b = m(tok, doc).logits, base(tok, doc).logits
+    rel = ((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt()).item()
+    assert torch.isfinite(a).all() and rel < (0.6 if which == "mxfp8" else 1.5), rel
+    a.logsumexp(-1).sum().backward()
+    assert all(torch.isfinite(p.grad).all() for p in m.parameters() if p.grad is not None)
