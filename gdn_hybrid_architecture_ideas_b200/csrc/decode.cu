@@ -171,3 +171,62 @@ int decode_attention(const float* q, const void* k, const void* v, const int* le
 }
 
 }  // namespace ghb
+
+// ================================================================================================ allocation-free entry
+// See noalloc.h for who needs this and the contract. The scratch is a file-scope device array: in host code its name
+// is only a handle for the runtime, so the device address is resolved once per device with cudaGetSymbolAddress.
+#include "noalloc.h"
+#include <mutex>
+#include <stdio.h>
+
+namespace {
+constexpr size_t NOALLOC_FLOATS = GHB_NOALLOC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_noalloc_scratch[NOALLOC_FLOATS];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_scratch_addr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_scratch_mutex;
+
+int fail(int code, char* buf, int len, const char* msg) {
+  if (buf && len > 0) snprintf(buf, static_cast<size_t>(len), "%s", msg);
+  return code;
+}
+}  // namespace
+
+extern "C" int ghb_decode_attention_noalloc(const float* q, const void* k, const void* v, const int* lens, const int* doc_start,
+                                            const float* cos_t, const float* sin_t, void* out, int B, int T, int Hq, int Hkv, int rot,
+                                            int cap, int n_angles, int splits, float scale, void* stream, char* errbuf, int errlen) {
+  if (B < 1 || T < 1 || Hq < 1 || Hkv < 1 || splits < 1)
+    return fail(1, errbuf, errlen, "ghb_decode_attention_noalloc: B, T, Hq, Hkv and splits must be positive");
+  const size_t need = static_cast<size_t>(B) * Hq * splits * 66;
+  if (need > NOALLOC_FLOATS) {
+    char msg[200];
+    snprintf(msg, sizeof msg, "ghb_decode_attention_noalloc: B*Hq*splits*66 = %zu floats exceeds the built-in scratch of %zu floats; use fewer splits or the regular entry",
+             need, static_cast<size_t>(NOALLOC_FLOATS));
+    return fail(1, errbuf, errlen, msg);
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+    return fail(2, errbuf, errlen, "ghb_decode_attention_noalloc: no current device (or more than 64 devices)");
+  float* scratch;
+  {
+    std::lock_guard<std::mutex> hold(g_scratch_mutex);
+    if (!g_scratch_addr[dev]) {     // first call on this device: resolve the array's device address (before any stream capture)
+      void* p = nullptr;
+      const cudaError_t rc = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (rc != cudaSuccess || !p) {
+        char msg[200];
+        snprintf(msg, sizeof msg, "ghb_decode_attention_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(rc));
+        return fail(2, errbuf, errlen, msg);
+      }
+      g_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    scratch = g_scratch_addr[dev];
+  }
+  float* part_o = scratch;
+  float* part_ml = scratch + static_cast<size_t>(B) * Hq * splits * 64;
+  const int rc = ghb::decode_attention(q, k, v, lens, doc_start, cos_t, sin_t, out, part_o, part_ml, B, T, Hq, Hkv, rot, cap, n_angles, splits,
+                                       scale, static_cast<cudaStream_t>(stream));
+  if (rc == 1) return fail(1, errbuf, errlen, "ghb_decode_attention_noalloc: unsupported head grouping (Hq/Hkv in 1,2,4,8,16) or rotary width (0,8,16,32,64)");
+  if (rc != 0) return fail(4, errbuf, errlen, "ghb_decode_attention_noalloc: kernel launch refused by the runtime");
+  return 0;
+}
