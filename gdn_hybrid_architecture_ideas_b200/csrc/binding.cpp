@@ -191,6 +191,7 @@ void gdn_scan_fwd(const Tensor& W, const Tensor& Qin, const Tensor& Kout, const 
   const c10::cuda::CUDAGuard guard(W.device());
   const int B = U.size(0), H = U.size(1), L = U.size(2), dv = U.size(3);
   check_rows(W, 128, "W"); check_rows(Qin, 128, "q_in"); check_rows(Kout, 128, "k_out"); check_rows(Aqk, 64, "Aqk"); check_rows(U, dv, "U"); check_rows(O, dv, "O");
+  TORCH_CHECK(O.dim() == 4 && O.size(1) == L && O.size(2) == H, "gdn_scan_fwd: O is token-major [B, L, H, dv]");
   TORCH_CHECK(is_f32(carry) && carry.is_contiguous() && carry.numel() == static_cast<int64_t>(B) * H * (L / 64), "gdn_scan_fwd: carry [B, H, L/64] fp32");
   if (S0.has_value()) TORCH_CHECK(is_f32(*S0) && S0->is_contiguous(), "gdn_scan_fwd: S0 fp32");
   check(ghb::gdn_scan_fwd(W.data_ptr(), Qin.data_ptr(), Kout.data_ptr(), Aqk.data_ptr(), U.data_ptr(), carry.data_ptr<float>(), fptr(S0), O.data_ptr(),
@@ -204,6 +205,7 @@ void gdn_scan_bwd(const Tensor& W, const Tensor& Qin, const Tensor& Kout, const 
   const int B = Vnew.size(0), H = Vnew.size(1), L = Vnew.size(2), dv = Vnew.size(3);
   check_rows(W, 128, "W"); check_rows(Qin, 128, "q_in"); check_rows(Kout, 128, "k_out"); check_rows(Aqk, 64, "Aqk"); check_rows(Vnew, dv, "v_new");
   check_rows(dO, dv, "dO"); check_rows(dU, dv, "dU"); check_rows(Hsave, 128, "h_save");
+  TORCH_CHECK(dO.dim() == 4 && dO.size(1) == L && dO.size(2) == H, "gdn_scan_bwd: dO is token-major [B, L, H, dv]");
   TORCH_CHECK(is_f32(dWp) && is_f32(dQp) && is_f32(dKp) && is_f32(dcarry) && dWp.is_contiguous() && dQp.is_contiguous() && dKp.is_contiguous(), "gdn_scan_bwd: fp32 partials");
   check(ghb::gdn_scan_bwd(W.data_ptr(), Qin.data_ptr(), Kout.data_ptr(), Aqk.data_ptr(), Hsave.data_ptr(), Vnew.data_ptr(), dO.data_ptr(),
                           carry.data_ptr<float>(), fptr(dSfinal), dU.data_ptr(), dWp.data_ptr<float>(), dQp.data_ptr<float>(), dKp.data_ptr<float>(),
@@ -229,18 +231,23 @@ void gdn_local_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
                            carry.data_ptr<float>(), stream()), "gdn_local_fwd");
 }
 void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const Tensor& start, const Tensor& U,
-                   const Tensor& W, const Tensor& dU,
-                   const Tensor& dW, const Tensor& dQin, const Tensor& dKout, const Tensor& dAqk, const Tensor& dcarry, Tensor& dq, Tensor& dk, Tensor& dv_,
-                   Tensor& dg, Tensor& dbeta) {
+                   const Tensor& W, const Tensor& dU, const Tensor& parts, const Tensor& dO, const Tensor& Vnew, const Tensor& dcarry, Tensor& dq,
+                   Tensor& dk, Tensor& dv_, Tensor& dg, Tensor& dbeta) {
+  // parts: [3, n_part, B, H, L, 128] fp32 = per value-slice partial sums of (dW, dq_in, dk_out) from the state pass
   const c10::cuda::CUDAGuard guard(q.device());
   check_tok_major(q, "q"); check_tok_major(k, "k"); check_tok_major(v, "v");
   const int B = v.size(0), L = v.size(1), Hv = v.size(2), dv = v.size(3), Hk = q.size(2);
-  for (const Tensor* t : {&U, &W, &dU, &dW, &dQin, &dKout, &dAqk}) TORCH_CHECK(is_bf16(*t) && t->is_contiguous(), "gdn_local_bwd: bf16 contiguous gradients");
+  for (const Tensor* t : {&U, &W, &dU, &dO, &Vnew}) TORCH_CHECK(is_bf16(*t) && t->is_contiguous(), "gdn_local_bwd: bf16 contiguous operands");
+  TORCH_CHECK(is_f32(parts) && parts.is_contiguous() && parts.dim() == 6 && parts.size(0) == 3, "gdn_local_bwd: parts [3, n, B, H, L, 128] fp32");
+  TORCH_CHECK(dO.dim() == 4 && dO.size(1) == L && dO.size(2) == Hv, "gdn_local_bwd: dO token-major [B, L, H, dv]");
   TORCH_CHECK(is_f32(dq) && is_f32(dk) && is_bf16(dv_) && is_f32(dg) && is_f32(dbeta) && is_f32(dcarry) && dq.is_contiguous() && dk.is_contiguous() && dv_.is_contiguous(), "gdn_local_bwd: outputs");
+  const int n_part = parts.size(1);
+  const long each = parts.stride(0);
+  const float* p = parts.data_ptr<float>();
   check(ghb::gdn_local_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), k.stride(1), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(),
-                           start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, U.data_ptr(), W.data_ptr(), dU.data_ptr(), dW.data_ptr(), dQin.data_ptr(), dKout.data_ptr(),
-                           dAqk.data_ptr(), dcarry.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv_.data_ptr(), dg.data_ptr<float>(), dbeta.data_ptr<float>(),
-                           stream()), "gdn_local_bwd");
+                           start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, U.data_ptr(), W.data_ptr(), dU.data_ptr(), p, p + each, p + 2 * each, n_part,
+                           dO.data_ptr(), Vnew.data_ptr(), dcarry.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv_.data_ptr(),
+                           dg.data_ptr<float>(), dbeta.data_ptr<float>(), stream()), "gdn_local_bwd");
 }
 
 void decode_attention(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lens, const c10::optional<Tensor>& doc_start, const Tensor& cos_t,

@@ -201,85 +201,141 @@ int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long 
 }  // namespace ghb
 
 // ================================================================================================ backward
-// Gradients of the chunk-local stage, one CTA per (batch row, value head, chunk). Inputs: the forward inputs and the
-// gradients of U, W, q_in, k_out, Aqk, carry handed back by the state pass. The forward quantities are recomputed.
-//   solve:   X = (I + A)^-1 R (as forward), dR = (I + A)^-T dX by back substitution (column per thread, registers);
-//            dA_ij = -sum_col dR_i X_j, accumulated by a tiled product over staged column blocks;
-//   scores:  A_ij = beta_i G_ij, G_ij = (k_i.k_j) E_ij  ->  dbeta, dc (decay), dKK = dG E;  Aqk likewise -> dQK, dc;
-//   outputs: dk = (dKK + dKK^T) K + dQK^T Q + diagonal terms, dq = dQK K + diagonal term, dv = beta dR_u,
-//            dg = reverse cumulative sum of dc, dbeta.
+// Gradients of the chunk-local stage, one CTA per (batch row, value head, chunk). Inputs: the forward inputs, the
+// forward's outputs X = [U | W], and the gradients of U, W, q_in, k_out, Aqk, carry handed back by the state pass.
+//   T = (I + A)^-1 explicitly (one column per thread), then every product is a warp-level tensor-core GEMM
+//   (mma.sync m16n8k8, tf32 operands, fp32 accumulation) on fp32 tiles in shared memory:
+//   dR = T^T dX per block of 128 columns;  dA = -dR X^T;  A_ij = beta_i G_ij, G = (K K^T) E  ->  dbeta, dc, dKK = dG E;
+//   Aqk = (Q K^T) E -> dQK, dc;  dk = (dKK + dKK^T) K + dQK^T Q + diagonal terms, dq = dQK K + diagonal term,
+//   dv = beta dR_u, dg = reverse cumulative sum of dc.
 namespace ghb {
+
+constexpr int BS = 68;          // padded row stride of the 64 x 64 matrices of the backward kernel
 
 struct LocalGrads {
   const __nv_bfloat16* U; const __nv_bfloat16* W;       // the forward's outputs (X = [U | W])
-  const __nv_bfloat16* dU; const __nv_bfloat16* dW; const __nv_bfloat16* dQin; const __nv_bfloat16* dKout; const __nv_bfloat16* dAqk;
+  const __nv_bfloat16* dU;                               // [B, H, L, DV]
+  const float* dWp; const float* dQp; const float* dKp;  // per value-slice partial sums [n_part, B, H, L, 128] of dW, dq_in, dk_out
+  long part_stride; int n_part;
+  const __nv_bfloat16* dO; const __nv_bfloat16* Vnew;     // dO token-major [B, L, H, DV]; v_new [B, H, L, DV]: dAqk = dO v_new^T is formed here
   const float* dcarry;
   float* dq; float* dk;            // [B, L, Hv, 128] fp32 (per value head; heads sharing a key head are summed by the caller)
   __nv_bfloat16* dv;               // [B, L, Hv, DV]
   float* dg; float* dbeta;         // [B, L, Hv]
 };
 
-__device__ __forceinline__ void tile_dot_acc(const float* X, const float* Y, int ty, int tx, float (&acc)[4][4]) {
-#pragma unroll 4
-  for (int kk = 0; kk < LK; kk += 4) {
-    float4 a[4], bq[4];
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// One warp accumulates a 16 x (8 NT) tile: acc[nt] += A(16 x K) B(K x 8 nt). A points at the tile's first row, B at its first
+// column. A_T: A(m, k) is stored at A[k * lda + m] (else A[m * lda + k]). B_K: B(k, n) is stored at B[k * ldb + n] (else B[n * ldb + k]).
+// Fragment layout of mma.m16n8k8: g = lane / 4, t = lane % 4; a0 (g, t) a1 (g+8, t) a2 (g, t+4) a3 (g+8, t+4); b0 (t, g) b1 (t+4, g);
+// c0 (g, 2t) c1 (g, 2t+1) c2 (g+8, 2t) c3 (g+8, 2t+1).
+template <int NT, bool A_T, bool B_K>
+__device__ __forceinline__ void warp_gemm(const float* A, int lda, const float* B, int ldb, int K, float (&acc)[NT][4], int lane) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll 2
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    uint32_t a[4];
+    if (A_T) {
+      a[0] = to_tf32(A[(k0 + t) * lda + g]); a[1] = to_tf32(A[(k0 + t) * lda + g + 8]);
+      a[2] = to_tf32(A[(k0 + t + 4) * lda + g]); a[3] = to_tf32(A[(k0 + t + 4) * lda + g + 8]);
+    } else {
+      a[0] = to_tf32(A[g * lda + k0 + t]); a[1] = to_tf32(A[(g + 8) * lda + k0 + t]);
+      a[2] = to_tf32(A[g * lda + k0 + t + 4]); a[3] = to_tf32(A[(g + 8) * lda + k0 + t + 4]);
+    }
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii) a[ii] = *reinterpret_cast<const float4*>(X + (ty + 16 * ii) * KS + kk);
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) bq[jj] = *reinterpret_cast<const float4*>(Y + (tx + 16 * jj) * KS + kk);
-#pragma unroll
-    for (int ii = 0; ii < 4; ++ii)
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj)
-        acc[ii][jj] += a[ii].x * bq[jj].x + a[ii].y * bq[jj].y + a[ii].z * bq[jj].z + a[ii].w * bq[jj].w;
+    for (int nt = 0; nt < NT; ++nt) {
+      uint32_t b0, b1;
+      if (B_K) { b0 = to_tf32(B[(k0 + t) * ldb + nt * 8 + g]); b1 = to_tf32(B[(k0 + t + 4) * ldb + nt * 8 + g]); }
+      else { b0 = to_tf32(B[(nt * 8 + g) * ldb + k0 + t]); b1 = to_tf32(B[(nt * 8 + g) * ldb + k0 + t + 4]); }
+      mma_tf32(acc[nt], a, b0, b1);
+    }
   }
+}
+template <int NT>
+__device__ __forceinline__ void zero_acc(float (&acc)[NT][4]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
+}
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); f[2 * e] = v.x; f[2 * e + 1] = v.y; }
+}
+template <int NP>
+__device__ __forceinline__ void sum8(const float* p, long stride, float (&f)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] = 0.f;
+#pragma unroll
+  for (int s = 0; s < NP; ++s) {
+    const float4 a = *reinterpret_cast<const float4*>(p + s * stride), c = *reinterpret_cast<const float4*>(p + s * stride + 4);
+    f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w; f[4] += c.x; f[5] += c.y; f[6] += c.z; f[7] += c.w;
+  }
+}
+template <int NP>
+__device__ __forceinline__ float2 sum2(const float* p, long stride) {
+  float2 r = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int s = 0; s < NP; ++s) { const float2 a = *reinterpret_cast<const float2*>(p + s * stride); r.x += a.x; r.y += a.y; }
+  return r;
 }
 
 template <int DV>
 __global__ void __launch_bounds__(256, 1)
 gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
   extern __shared__ __align__(16) float sm[];
-  float* sK = sm;
-  float* sQ = sK + LC * KS;
-  float* sDR = sQ + LC * KS;            // staged dR columns [64][KS]
-  float* sX = sDR + LC * KS;            // staged X columns  [64][KS]
-  float* sG = sX + LC * KS;             // G, later dKK      [64][AS]
-  float* sAq = sG + LC * AS;            // Aqk, later dQK    [64][AS]
-  float* sT = sAq + LC * AS;            // T = (I + A)^-1    [64][AS]
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sT + LC * AS);
+  float* sK = sm;                       // [64][KS]
+  float* sQ = sK + LC * KS;             // [64][KS] (also the staging of dX blocks)
+  float* sDR = sQ + LC * KS;            // dR block [64][KS]
+  float* sX = sDR + LC * KS;            // X block  [64][KS]
+  float* sG = sX + LC * KS;             // G, later S = dKK + dKK^T   [64][BS]
+  float* sAq = sG + LC * BS;            // Aqk, later dQK             [64][BS]
+  float* sT = sAq + LC * BS;            // T = (I + A)^-1, later dA   [64][BS]
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sT + LC * BS);
   float* sdc = reinterpret_cast<float*>(sc + 1);   // [64] decay gradient
   float* sdb = sdc + LC;                            // [64] beta gradient
 
   const int chunk = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int hk = hv / in.rep;
-  const int NT = in.L / LC;
+  const int NT_ = in.L / LC;
   const long tok0 = static_cast<long>(b) * in.L + chunk * LC;
   const long row0 = (static_cast<long>(b) * in.Hv + hv) * in.L + chunk * LC;     // rows of the [B, H, L, *] operands
-  const int t = threadIdx.x, lane = t & 31;
-  const int ty = t >> 4, tx = t & 15;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int g = lane >> 2, tq = lane & 3;
+  const int m0 = (warp & 3) * 16;                  // this warp's 16 output rows in every product
 
   load_scalars(in, b, hv, chunk, sc);
   load_tile(in.k + tok0 * in.k_tok + hk * LK, in.k_tok, sK);
   load_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
   if (t < LC) { sdc[t] = 0.f; sdb[t] = 0.f; }
   __syncthreads();
-  {
+  {   // G = (K K^T) E (strictly lower), Aqk = (Q K^T) E (lower): warp tile 16 x 32
+    const int n0 = (warp >> 2) * 32;
     float kk[4][4], qk[4][4];
-    tile_dot(sK, sK, ty, tx, kk);
-    tile_dot(sQ, sK, ty, tx, qk);
+    zero_acc(kk); zero_acc(qk);
+    warp_gemm<4, false, false>(sK + m0 * KS, KS, sK + n0 * KS, KS, LK, kk, lane);
+    warp_gemm<4, false, false>(sQ + m0 * KS, KS, sK + n0 * KS, KS, LK, qk, lane);
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii)
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int i = ty + 16 * ii, j = tx + 16 * jj;
-        const float e = (j <= i && sc->seg[i] == sc->seg[j]) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
-        sG[i * AS + j] = (j < i) ? kk[ii][jj] * e : 0.f;
-        sAq[i * AS + j] = qk[ii][jj] * e;
+      for (int e = 0; e < 4; ++e) {
+        const int i = m0 + g + (e >> 1) * 8, j = n0 + nt * 8 + 2 * tq + (e & 1);
+        const float ex = (j <= i && sc->seg[i] == sc->seg[j]) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
+        sG[i * BS + j] = (j < i) ? kk[nt][e] * ex : 0.f;
+        sAq[i * BS + j] = qk[nt][e] * ex;
       }
   }
   __syncthreads();
-
-  // ---- T = (I + A)^-1, one column per thread (threads 0..63): x_c = 1, x_i = -sum_{m < i} A_im x_m
+  // ---- T = (I + A)^-1, one column per thread (threads 0..63): x_c = 1, x_i = -beta_i sum_{m < i} G_im x_m
   if (t < LC) {
     float x[LC];
 #pragma unroll
@@ -288,169 +344,193 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
     for (int i = 1; i < LC; ++i) {
       float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-      for (int m = 0; m + 1 < i; m += 2) { a0 += sG[i * AS + m] * x[m]; a1 += sG[i * AS + m + 1] * x[m + 1]; }
-      if (i & 1) a0 += sG[i * AS + i - 1] * x[i - 1];
+      for (int m = 0; m + 1 < i; m += 2) { a0 += sG[i * BS + m] * x[m]; a1 += sG[i * BS + m + 1] * x[m + 1]; }
+      if (i & 1) a0 += sG[i * BS + i - 1] * x[i - 1];
       x[i] -= sc->beta[i] * (a0 + a1);
     }
 #pragma unroll
-    for (int i = 0; i < LC; ++i) sT[i * AS + t] = x[i];
+    for (int i = 0; i < LC; ++i) sT[i * BS + t] = x[i];
   }
   __syncthreads();
 
-  // ---- per block of 128 columns of [U | W]: X from the forward's outputs, dR = T^T dX, dA -= dR X^T
-  float dA[4][4];
-#pragma unroll
-  for (int ii = 0; ii < 4; ++ii)
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) dA[ii][jj] = 0.f;
   constexpr int COLS = DV + LK;
+  constexpr int NP = DV / 128;      // one partial sum per 128-wide value slice of the state pass
   float* sDX = sQ;      // the q tile is not needed again until the outputs; it is reloaded there
+  // ---- dAqk = dO v_new^T over the value dimension, 128 columns at a time (warp tile 16 x 32), kept in registers
+  float dAq[4][4];
+  zero_acc(dAq);
+#pragma unroll 1
+  for (int vb = 0; vb < DV / 128; ++vb) {
+    for (int idx = t; idx < LC * 16; idx += 256) {
+      const int row = idx >> 4, c8 = (idx & 15) * 8;
+      float fa[8], fb[8];
+      load8(gr.dO + ((tok0 + row) * in.Hv + hv) * DV + vb * 128 + c8, fa);
+      load8(gr.Vnew + (row0 + row) * DV + vb * 128 + c8, fb);
+      *reinterpret_cast<float4*>(sDR + row * KS + c8) = make_float4(fa[0], fa[1], fa[2], fa[3]);
+      *reinterpret_cast<float4*>(sDR + row * KS + c8 + 4) = make_float4(fa[4], fa[5], fa[6], fa[7]);
+      *reinterpret_cast<float4*>(sX + row * KS + c8) = make_float4(fb[0], fb[1], fb[2], fb[3]);
+      *reinterpret_cast<float4*>(sX + row * KS + c8 + 4) = make_float4(fb[4], fb[5], fb[6], fb[7]);
+    }
+    __syncthreads();
+    warp_gemm<4, false, false>(sDR + m0 * KS, KS, sX + (warp >> 2) * 32 * KS, KS, 128, dAq, lane);
+    __syncthreads();
+  }
+  // ---- per block of 128 columns of [U | W]: dR = T^T dX (warp tile 16 x 64), dA += dR X^T (warp tile 16 x 32)
+  float dA[4][4];
+  zero_acc(dA);
 #pragma unroll 1
   for (int blk = 0; blk < COLS / 128; ++blk) {
     const bool is_u = blk * 128 < DV;
     const int c0 = is_u ? blk * 128 : 0;
-    const __nv_bfloat16* gx = is_u ? gr.dU + row0 * DV + c0 : gr.dW + row0 * LK;
     const __nv_bfloat16* xx = is_u ? gr.U + row0 * DV + c0 : gr.W + row0 * LK;
     const int ld = is_u ? DV : LK;
     for (int idx = t; idx < LC * 16; idx += 256) {          // 64 rows x 16 vectors of 8
       const int row = idx >> 4, c8 = (idx & 15) * 8;
-      const uint4 a = *reinterpret_cast<const uint4*>(gx + static_cast<long>(row) * ld + c8);
-      const uint4 bq = *reinterpret_cast<const uint4*>(xx + static_cast<long>(row) * ld + c8);
-      const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {bq.x, bq.y, bq.z, bq.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float2 fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wa[e]));
-        const float2 fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wb[e]));
-        sDX[row * KS + c8 + 2 * e] = fa.x; sDX[row * KS + c8 + 2 * e + 1] = fa.y;
-        sX[row * KS + c8 + 2 * e] = fb.x; sX[row * KS + c8 + 2 * e + 1] = fb.y;
-      }
+      float fa[8], fb[8];
+      load8(xx + static_cast<long>(row) * ld + c8, fb);
+      if (is_u) load8(gr.dU + (row0 + row) * DV + c0 + c8, fa);
+      else sum8<NP>(gr.dWp + (row0 + row) * LK + c8, gr.part_stride, fa);
+      *reinterpret_cast<float4*>(sDX + row * KS + c8) = make_float4(fa[0], fa[1], fa[2], fa[3]);
+      *reinterpret_cast<float4*>(sDX + row * KS + c8 + 4) = make_float4(fa[4], fa[5], fa[6], fa[7]);
+      *reinterpret_cast<float4*>(sX + row * KS + c8) = make_float4(fb[0], fb[1], fb[2], fb[3]);
+      *reinterpret_cast<float4*>(sX + row * KS + c8 + 4) = make_float4(fb[4], fb[5], fb[6], fb[7]);
     }
     __syncthreads();
     {
-      const int col = t & 127, i0 = (t >> 7) * 32;          // 32 rows of one column per thread
-      float acc[32];
+      const int n0 = (warp >> 2) * 64;
+      float dr[8][4];
+      zero_acc(dr);
+      warp_gemm<8, true, true>(sT + m0, BS, sDX + n0, KS, LC, dr, lane);      // A(i, j) = T[j][i], B(j, col) = dX[j][col]
+      // dv = beta dR_u ; dbeta += dR_u . v ; stage dR
+      float pb0 = 0.f, pb1 = 0.f;
 #pragma unroll
-      for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-      for (int j = i0; j < LC; ++j) {                          // dR_i = sum_{j >= i} T_ji dX_j
-        const float d = sDX[j * KS + col];
+      for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-        for (int e = 0; e < 32; ++e) acc[e] += sT[j * AS + i0 + e] * d;
-      }
-      if (is_u) {      // dv = beta dR_u ; dbeta += dR_u . v
-        const __nv_bfloat16* vp = in.v + tok0 * in.v_tok + static_cast<long>(hv) * DV + c0 + col;
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int i = i0 + e;
-          gr.dv[(tok0 + i) * in.Hv * DV + static_cast<long>(hv) * DV + c0 + col] = __float2bfloat16(sc->beta[i] * acc[e]);
-          float p = acc[e] * __bfloat162float(vp[i * in.v_tok]);
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-          if (lane == 0) atomicAdd(&sdb[i], p);
+        for (int e = 0; e < 4; ++e) {
+          const int i = m0 + g + (e >> 1) * 8, col = n0 + nt * 8 + 2 * tq + (e & 1);
+          const float v = dr[nt][e];
+          sDR[i * KS + col] = v;
+          if (is_u) {
+            const long vidx = (tok0 + i) * in.v_tok + static_cast<long>(hv) * DV + c0 + col;
+            const float pv = v * __bfloat162float(in.v[vidx]);
+            if (e >> 1) pb1 += pv; else pb0 += pv;
+            gr.dv[(tok0 + i) * in.Hv * DV + static_cast<long>(hv) * DV + c0 + col] = __float2bfloat16(sc->beta[i] * v);
+          }
         }
+      if (is_u) {      // reduce over the 4 lanes that share a row, then one shared atomic per row per warp
+        pb0 += __shfl_xor_sync(0xffffffffu, pb0, 1); pb0 += __shfl_xor_sync(0xffffffffu, pb0, 2);
+        pb1 += __shfl_xor_sync(0xffffffffu, pb1, 1); pb1 += __shfl_xor_sync(0xffffffffu, pb1, 2);
+        if (tq == 0) { atomicAdd(&sdb[m0 + g], pb0); atomicAdd(&sdb[m0 + g + 8], pb1); }
       }
-#pragma unroll
-      for (int e = 0; e < 32; ++e) sDR[(i0 + e) * KS + col] = acc[e];
     }
     __syncthreads();
-    tile_dot_acc(sDR, sX, ty, tx, dA);
+    warp_gemm<4, false, false>(sDR + m0 * KS, KS, sX + (warp >> 2) * 32 * KS, KS, 128, dA, lane);   // dR X^T
     __syncthreads();
   }
+  // sDR / sX now hold the W columns: dR_w [i][kk] and W [i][kk]. Reload q (its buffer staged dX).
   load_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
-  __syncthreads();   // sDR / sX now hold the W columns: dR_w [i][kk] and W [i][kk]
 
-  // ---- score matrices: beta / decay gradients, then overwrite sG <- dKK, sAq <- dQK
+  // ---- score matrices: beta / decay gradients; then sT <- dKK (lower), sAq <- dQK
   {
-    float dGs[4][4], dQs[4][4];
+    const int n0 = (warp >> 2) * 32;
+    float dKKv[4][4], dQKv[4][4];
+    float rb[2] = {0.f, 0.f}, rc[2] = {0.f, 0.f};
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii) {
-      const int i = ty + 16 * ii;
-      float rb = 0.f, rc = 0.f;
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int j = tx + 16 * jj;
+      for (int e = 0; e < 4; ++e) {
+        const int i = m0 + g + (e >> 1) * 8, j = n0 + nt * 8 + 2 * tq + (e & 1);
         const bool same = sc->seg[i] == sc->seg[j];
-        const float e = (j <= i && same) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
-        const float G = sG[i * AS + j];
-        const float da = (j < i && same) ? -dA[ii][jj] : 0.f;
-        rb += da * G;
+        const float ex = (j <= i && same) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
+        const float G = sG[i * BS + j];
+        const float da = (j < i && same) ? -dA[nt][e] : 0.f;
         const float dG = da * sc->beta[i];
         const float t1 = dG * G;
-        const float dq_ij = (j <= i && same) ? __bfloat162float(gr.dAqk[(row0 + i) * LC + j]) : 0.f;
-        const float t2 = dq_ij * sAq[i * AS + j];
-        rc += t1 + t2;
+        const float dq_ij = (j <= i && same) ? dAq[nt][e] : 0.f;
+        const float t2 = dq_ij * sAq[i * BS + j];
+        rb[e >> 1] += da * G;
+        rc[e >> 1] += t1 + t2;
         atomicAdd(&sdc[j], -(t1 + t2));
-        dGs[ii][jj] = dG * e;
-        dQs[ii][jj] = dq_ij * e;
+        dKKv[nt][e] = dG * ex;
+        dQKv[nt][e] = dq_ij * ex;
       }
 #pragma unroll
-      for (int o = 8; o > 0; o >>= 1) { rb += __shfl_xor_sync(0xffffffffu, rb, o); rc += __shfl_xor_sync(0xffffffffu, rc, o); }
-      if (tx == 0) { atomicAdd(&sdb[i], rb); atomicAdd(&sdc[i], rc); }
+    for (int h = 0; h < 2; ++h) {
+      rb[h] += __shfl_xor_sync(0xffffffffu, rb[h], 1); rb[h] += __shfl_xor_sync(0xffffffffu, rb[h], 2);
+      rc[h] += __shfl_xor_sync(0xffffffffu, rc[h], 1); rc[h] += __shfl_xor_sync(0xffffffffu, rc[h], 2);
+      if (tq == 0) { atomicAdd(&sdb[m0 + g + 8 * h], rb[h]); atomicAdd(&sdc[m0 + g + 8 * h], rc[h]); }
     }
-    __syncthreads();
+    __syncthreads();     // every reader of sG / sAq / sT (old contents) is done
 #pragma unroll
-    for (int ii = 0; ii < 4; ++ii)
+    for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int i = ty + 16 * ii, j = tx + 16 * jj;
-        sG[i * AS + j] = dGs[ii][jj];
-        sAq[i * AS + j] = dQs[ii][jj];
+      for (int e = 0; e < 4; ++e) {
+        const int i = m0 + g + (e >> 1) * 8, j = n0 + nt * 8 + 2 * tq + (e & 1);
+        sT[i * BS + j] = dKKv[nt][e];
+        sAq[i * BS + j] = dQKv[nt][e];
       }
   }
   __syncthreads();
+  for (int idx = t; idx < LC * LC; idx += 256) {      // S = dKK + dKK^T (dKK is strictly lower)
+    const int i = idx >> 6, j = idx & 63;
+    sG[i * BS + j] = sT[i * BS + j] + sT[j * BS + i];
+  }
+  __syncthreads();
 
-  // ---- outputs: thread owns row r and 32 consecutive key channels
+  // ---- outputs: dk = S K + dQK^T Q + diagonal terms ; dq = dQK K + diagonal term (warp tile 16 x 64)
   {
-    const int r = t >> 2, k0 = (t & 3) * 32;
-    float dk[32], dq[32];
+    const int n0 = (warp >> 2) * 64;
+    float dk[8][4], dq[8][4];
+    zero_acc(dk); zero_acc(dq);
+    float2 pq[2][8], pk[2][8];          // the state pass's dq_in / dk_out, fetched ahead of the products that hide their latency
 #pragma unroll
-    for (int e = 0; e < 32; ++e) { dk[e] = 0.f; dq[e] = 0.f; }
-    for (int i = 0; i < LC; ++i) {
-      const float s_ri = i < r ? sG[r * AS + i] : (i > r ? sG[i * AS + r] : 0.f);      // (dKK + dKK^T)[r][i]
-      const float qk_ir = i >= r ? sAq[i * AS + r] : 0.f;                                // dQK[i][r]
-      const float qk_ri = i <= r ? sAq[r * AS + i] : 0.f;                                // dQK[r][i]
+    for (int h = 0; h < 2; ++h)
 #pragma unroll
-      for (int e = 0; e < 32; e += 4) {
-        const float4 kv = *reinterpret_cast<const float4*>(sK + i * KS + k0 + e);
-        const float4 qv = *reinterpret_cast<const float4*>(sQ + i * KS + k0 + e);
-        dk[e] += s_ri * kv.x + qk_ir * qv.x; dk[e + 1] += s_ri * kv.y + qk_ir * qv.y;
-        dk[e + 2] += s_ri * kv.z + qk_ir * qv.z; dk[e + 3] += s_ri * kv.w + qk_ir * qv.w;
-        dq[e] += qk_ri * kv.x; dq[e + 1] += qk_ri * kv.y; dq[e + 2] += qk_ri * kv.z; dq[e + 3] += qk_ri * kv.w;
+      for (int nt = 0; nt < 8; ++nt) {
+        const long at = (row0 + m0 + g + 8 * h) * LK + n0 + nt * 8 + 2 * tq;
+        pq[h][nt] = sum2<NP>(gr.dQp + at, gr.part_stride);
+        pk[h][nt] = sum2<NP>(gr.dKp + at, gr.part_stride);
       }
-    }
-    const float fq = sc->seg[r] == 0 ? sc->gamma[r] : 0.f;                       // q_in = q fq ; W rhs = beta fq k
-    const float fk = sc->seg[r] == sc->last_seg ? sc->to_end[r] : 0.f;           // k_out = k fk
-    const float br = sc->beta[r];
-    float dot_w = 0.f, dot_q = 0.f, dot_k = 0.f;
+    warp_gemm<8, false, true>(sG + m0 * BS, BS, sK + n0, KS, LC, dk, lane);       // S K
+    warp_gemm<8, true, true>(sAq + m0, BS, sQ + n0, KS, LC, dk, lane);           // dQK^T Q : A(r, i) = dQK[i][r]
+    warp_gemm<8, false, true>(sAq + m0 * BS, BS, sK + n0, KS, LC, dq, lane);      // dQK K
+    float dots[2][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}};
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const float kre = sK[r * KS + k0 + e], qre = sQ[r * KS + k0 + e];
-      const float drw = sDR[r * KS + k0 + e];
-      const float dqi = __bfloat162float(gr.dQin[(row0 + r) * LK + k0 + e]);
-      const float dko = __bfloat162float(gr.dKout[(row0 + r) * LK + k0 + e]);
-      dk[e] += br * fq * drw + fk * dko;
-      dq[e] += fq * dqi;
-      dot_w += drw * kre; dot_q += dqi * qre; dot_k += dko * kre;
-    }
+    for (int h = 0; h < 2; ++h) {
+      const int r = m0 + g + 8 * h;
+      const float fq = sc->seg[r] == 0 ? sc->gamma[r] : 0.f;                       // q_in = q fq ; W rhs = beta fq k
+      const float fk = sc->seg[r] == sc->last_seg ? sc->to_end[r] : 0.f;           // k_out = k fk
+      const float br = sc->beta[r];
+      float* dqo = gr.dq + ((tok0 + r) * in.Hv + hv) * LK;
+      float* dko = gr.dk + ((tok0 + r) * in.Hv + hv) * LK;
 #pragma unroll
-    for (int o = 2; o > 0; o >>= 1) {
-      dot_w += __shfl_xor_sync(0xffffffffu, dot_w, o); dot_q += __shfl_xor_sync(0xffffffffu, dot_q, o); dot_k += __shfl_xor_sync(0xffffffffu, dot_k, o);
-    }
-    if ((t & 3) == 0) {
-      atomicAdd(&sdb[r], fq * dot_w);
-      atomicAdd(&sdc[r], br * fq * dot_w + fq * dot_q - fk * dot_k);
-      atomicAdd(&sdc[LC - 1], fk * dot_k);
-    }
-    float* dqo = gr.dq + ((tok0 + r) * in.Hv + hv) * LK + k0;
-    float* dko_ = gr.dk + ((tok0 + r) * in.Hv + hv) * LK + k0;
+      for (int nt = 0; nt < 8; ++nt) {
+        const int kk = n0 + nt * 8 + 2 * tq;
+        const float2 drw = *reinterpret_cast<const float2*>(sDR + r * KS + kk);
+        const float2 kre = *reinterpret_cast<const float2*>(sK + r * KS + kk);
+        const float2 qre = *reinterpret_cast<const float2*>(sQ + r * KS + kk);
+        const float2 dqi = pq[h][nt], dkv = pk[h][nt];
+        float2 ok, oq;
+        ok.x = dk[nt][2 * h] + br * fq * drw.x + fk * dkv.x; ok.y = dk[nt][2 * h + 1] + br * fq * drw.y + fk * dkv.y;
+        oq.x = dq[nt][2 * h] + fq * dqi.x; oq.y = dq[nt][2 * h + 1] + fq * dqi.y;
+        *reinterpret_cast<float2*>(dko + kk) = ok;
+        *reinterpret_cast<float2*>(dqo + kk) = oq;
+        dots[h][0] += drw.x * kre.x + drw.y * kre.y;
+        dots[h][1] += dqi.x * qre.x + dqi.y * qre.y;
+        dots[h][2] += dkv.x * kre.x + dkv.y * kre.y;
+      }
 #pragma unroll
-    for (int e = 0; e < 32; e += 4) {
-      *reinterpret_cast<float4*>(dqo + e) = make_float4(dq[e], dq[e + 1], dq[e + 2], dq[e + 3]);
-      *reinterpret_cast<float4*>(dko_ + e) = make_float4(dk[e], dk[e + 1], dk[e + 2], dk[e + 3]);
+      for (int w = 0; w < 3; ++w) { dots[h][w] += __shfl_xor_sync(0xffffffffu, dots[h][w], 1); dots[h][w] += __shfl_xor_sync(0xffffffffu, dots[h][w], 2); }
+      if (tq == 0) {
+        atomicAdd(&sdb[r], fq * dots[h][0]);
+        atomicAdd(&sdc[r], br * fq * dots[h][0] + fq * dots[h][1] - fk * dots[h][2]);
+        atomicAdd(&sdc[LC - 1], fk * dots[h][2]);
+      }
     }
   }
   __syncthreads();
   if (t == 0) {
-    sdc[LC - 1] += sc->carry * gr.dcarry[(static_cast<long>(b) * in.Hv + hv) * NT + chunk];
+    sdc[LC - 1] += sc->carry * gr.dcarry[(static_cast<long>(b) * in.Hv + hv) * NT_ + chunk];
     float acc = 0.f;
     for (int i = LC - 1; i >= 0; --i) { acc += sdc[i]; sdc[i] = acc; }      // dg_m = sum_{i >= m} dc_i
   }
@@ -461,18 +541,18 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
   }
 }
 
-constexpr size_t LOCAL_BWD_SMEM = (4 * LC * KS + 3 * LC * AS + 2 * LC) * sizeof(float) + sizeof(ChunkScalars) + 64;
+constexpr size_t LOCAL_BWD_SMEM = (4 * LC * KS + 3 * LC * BS + 2 * LC) * sizeof(float) + sizeof(ChunkScalars) + 64;
 
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
-                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU, const void* dW, const void* dQin,
-                  const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv, float* dg, float* dbeta,
-                  cudaStream_t st) {
-  if (L % LC || (dv != 128 && dv != 256) || Hv % Hk) return 1;
+                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU,
+                  const float* dWp, const float* dQp, const float* dKp, int n_part, const void* dO, const void* Vnew, const float* dcarry,
+                  float* dq, float* dk, void* dvv, float* dg, float* dbeta, cudaStream_t st) {
+  if (L % LC || (dv != 128 && dv != 256) || Hv % Hk || n_part != dv / 128) return 1;
   LocalIn in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), q_tok, k_tok, v_tok,
              g, beta, start, L, Hv, Hv / Hk};
-  LocalGrads gr{static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(dU), static_cast<const __nv_bfloat16*>(dW), static_cast<const __nv_bfloat16*>(dQin),
-                static_cast<const __nv_bfloat16*>(dKout), static_cast<const __nv_bfloat16*>(dAqk), dcarry, dq, dk,
-                static_cast<__nv_bfloat16*>(dvv), dg, dbeta};
+  LocalGrads gr{static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(dU), dWp, dQp, dKp,
+                static_cast<long>(B) * Hv * L * LK, n_part, static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(Vnew), dcarry,
+                dq, dk, static_cast<__nv_bfloat16*>(dvv), dg, dbeta};
   dim3 grid(L / LC, Hv, B);
   static bool attr = false;
   if (!attr) {

@@ -205,7 +205,8 @@ gdn_scan_fwd_kernel(const __grid_constant__ ScanMaps maps, const float* __restri
         tmem_ld_x32(tO + lane_off + half * 32, ov);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) O[(tok0 + half * 32 + e) * dv + vcol] = __float2bfloat16(__uint_as_float(ov[e]));
+        for (int e = 0; e < 32; ++e)      // token-major output [B, L, H, dv]: what the gated norm and the out-projection read
+          O[((static_cast<long>(b) * L + c * GC + half * 32 + e) * H + h) * dv + vcol] = __float2bfloat16(__uint_as_float(ov[e]));
       }
       const float cy = carry[bh * NT + c];
 #pragma unroll
@@ -281,7 +282,7 @@ gdn_scan_bwd_kernel(const __grid_constant__ ScanMaps maps, const float* __restri
         const int row = static_cast<int>(bh * L + static_cast<long>(c) * GC);
         mbar_expect_tx(bar_full, BS_STAGE);
         for (int kb = 0; kb < 2; ++kb) {
-          tma_load_2d(st + BS_DO + kb * B8K, &maps.dO, bar_full, vs * GV + kb * 64, row);
+          tma_load_2d(st + BS_DO + kb * B8K, &maps.dO, bar_full, h * dv + vs * GV + kb * 64, static_cast<int>(static_cast<long>(b) * L + c * GC));
           tma_load_2d(st + BS_K + kb * B8K, &maps.k, bar_full, kb * 64, row);
           tma_load_2d(st + BS_Q + kb * B8K, &maps.q, bar_full, kb * 64, row);
           tma_load_2d(st + BS_W + kb * B8K, &maps.w, bar_full, kb * 64, row);
@@ -430,7 +431,7 @@ static bool map2d(CUtensorMap* m, const void* p, long rows, int cols, int box_co
 }
 
 // W, Qin, Kout: [B*H*L, 128]; Aqk: [B*H*L, 64]; U: [B*H*L, dv] (bf16, chunks of 64 rows); carry: [B*H*NT] fp32;
-// S0 / Sfinal: [B, H, 128, dv] fp32 or null; O: [B*H*L, dv] bf16; Hsave: [B*H*NT*dv, 128] bf16 or null; Vnew like U or null.
+// S0 / Sfinal: [B, H, 128, dv] fp32 or null; O: [B, L, H, dv] bf16 (token-major); Hsave: [B*H*NT*dv, 128] bf16 or null; Vnew like U or null.
 int gdn_scan_fwd(const void* W, const void* Qin, const void* Kout, const void* Aqk, const void* U, const float* carry, const float* S0,
                  void* O, float* Sfinal, void* Hsave, void* Vnew, int B, int H, int L, int dv, int* err, cudaStream_t st) {
   if (L % GC || dv % GV) return 1;
@@ -457,7 +458,7 @@ int gdn_scan_bwd(const void* W, const void* Qin, const void* Kout, const void* A
   const long hrows = static_cast<long>(B) * H * (L / GC) * dv;
   if (!map2d(&m.w, W, rows, GK, 64, 64, true) || !map2d(&m.q, Qin, rows, GK, 64, 64, true) || !map2d(&m.k, Kout, rows, GK, 64, 64, true) ||
       !map2d(&m.a, Aqk, rows, GC, 64, 64, true) || !map2d(&m.h, Hsave, hrows, GK, 64, 128, true) || !map2d(&m.vn, Vnew, rows, dv, 64, 64, true) ||
-      !map2d(&m.dO, dO, rows, dv, 64, 64, true)) return 2;
+      !map2d(&m.dO, dO, static_cast<long>(B) * L, H * dv, 64, 64, true)) return 2;     // dO is token-major [B, L, H, dv]
   m.u = m.vn;
   static bool attr = false;
   if (!attr) { if (cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BS_SMEM) != cudaSuccess) return 3; attr = true; }

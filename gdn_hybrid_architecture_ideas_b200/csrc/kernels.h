@@ -57,8 +57,8 @@ int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long 
                   float* carry, cudaStream_t st);
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
                   const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU,
-                  const void* dW, const void* dQin, const void* dKout, const void* dAqk, const float* dcarry, float* dq, float* dk, void* dvv,
-                  float* dg, float* dbeta, cudaStream_t st);
+                  const float* dWp, const float* dQp, const float* dKp, int n_part, const void* dO, const void* Vnew, const float* dcarry,
+                  float* dq, float* dk, void* dvv, float* dg, float* dbeta, cudaStream_t st);
 
 int decode_attention(const float* q, const void* k, const void* v, const int* lens, const int* doc_start, const float* cos_t, const float* sin_t,
                      void* out, float* part_o, float* part_ml, int B, int T, int Hq, int Hkv, int rot, int cap, int n_angles, int splits,

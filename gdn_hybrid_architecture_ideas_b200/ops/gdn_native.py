@@ -2,9 +2,8 @@
 
 Two stages. The chunk-local stage (cumulative decays, the (I + A)^-1 solve giving U and W, the intra-chunk score
 matrix, document masks) is independent across chunks; the sequential stage carries the state across chunks. The
-sequential stage is the hand-written tcgen05 kernel pair of csrc/gdn_scan.cu behind `_Scan` (key dimension 128, value
-dimension a multiple of 128, chunk 64). The chunk-local stage currently runs as batched fp32 device ops with autograd
-(`reference.chunk_local`); its operands are handed to the scan in bfloat16.
+sequential stage is the hand-written tcgen05 kernel pair of csrc/gdn_scan.cu (key dimension 128, value dimension 128 or
+256, chunk 64); the chunk-local stage is the kernel pair of csrc/gdn_local.cu. `_DeltaRule` chains the four launches.
 """
 
 from __future__ import annotations
@@ -19,21 +18,34 @@ BF16 = torch.bfloat16
 CHUNK = 64
 
 
-class _Scan(torch.autograd.Function):
-    """(U, W, q_in, Aqk, k_out, carry, S0) -> (o, S_final); tensors [B, H, L, *] bf16, carry [B, H, L/64] fp32."""
+class _DeltaRule(torch.autograd.Function):
+    """(q, k, v, g, beta, starts, S0) -> (o [B, L, Hv, dv], S_final). Inputs token-major [B, L, H, *] (strided views are
+    fine). Forward: the chunk-local kernel writes U, W, q_in, Aqk, k_out [B, Hv, L, *] and the per-chunk carry, the state
+    scan consumes them and writes the output token-major. Backward: the state scan's backward leaves dU and fp32 partial
+    sums (one per 128-wide value slice) of dW, dq_in, dk_out; the chunk-local backward reads those directly, forms
+    dAqk = dO v_new^T itself and writes dq, dk, dv, dg, dbeta token-major."""
 
     @staticmethod
-    def forward(ctx, U, W, Qin, Aqk, Kout, carry, S0, need_state):
-        B, H, L, dv = U.shape
-        dev = U.device
+    def forward(ctx, q, k, v, g, beta, start_u8, S0, need_state):
+        B, L, Hv, dv = v.shape
+        dev = v.device
+        ex = native.ext()
         needs_grad = any(ctx.needs_input_grad[:7])
-        O = torch.empty_like(U)
-        Sfinal = torch.empty(B, H, 128, dv, dtype=torch.float32, device=dev) if need_state else None
-        Hsave = torch.empty(B, H, L // CHUNK, dv, 128, dtype=BF16, device=dev) if needs_grad else None
+
+        def buf(d, dtype=BF16):
+            return torch.empty(B, Hv, L, d, dtype=dtype, device=dev)
+
+        U, W, Aqk, Qin, Kout = buf(dv), buf(128), buf(CHUNK), buf(128), buf(128)
+        carry = torch.empty(B, Hv, L // CHUNK, dtype=torch.float32, device=dev)
+        ex.gdn_local_fwd(q, k, v, g, beta, start_u8, U, W, Aqk, Qin, Kout, carry)
+        O = torch.empty(B, L, Hv, dv, dtype=BF16, device=dev)
+        Sfinal = torch.empty(B, Hv, 128, dv, dtype=torch.float32, device=dev) if need_state else None
+        Hsave = torch.empty(B, Hv, L // CHUNK, dv, 128, dtype=BF16, device=dev) if needs_grad else None
         Vnew = torch.empty_like(U) if needs_grad else None
-        native.ext().gdn_scan_fwd(W, Qin, Kout, Aqk, U, carry, S0, O, Sfinal, Hsave, Vnew, native.err_flag(dev))
-        native._count()
-        ctx.save_for_backward(W, Qin, Kout, Aqk, carry, Hsave, Vnew)
+        ex.gdn_scan_fwd(W, Qin, Kout, Aqk, U, carry, S0, O, Sfinal, Hsave, Vnew, native.err_flag(dev))
+        native._count(2)
+        if needs_grad:
+            ctx.save_for_backward(q, k, v, g, beta, start_u8, U, W, Qin, Kout, Aqk, carry, Hsave, Vnew)
         ctx.has_s0 = S0 is not None
         if Sfinal is None:
             Sfinal = torch.zeros(0, device=dev)
@@ -42,62 +54,31 @@ class _Scan(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dO, dSfinal):
-        W, Qin, Kout, Aqk, carry, Hsave, Vnew = ctx.saved_tensors
-        B, H, L, dv = Vnew.shape
-        dev = W.device
-        nvs = dv // 128
-        dO = native._bf16(dO).contiguous()
-        dU = torch.empty_like(Vnew)
-        parts = torch.empty(3, nvs, B, H, L, 128, dtype=torch.float32, device=dev)
-        dcarry = torch.zeros_like(carry)
-        dS0 = torch.empty(B, H, 128, dv, dtype=torch.float32, device=dev) if ctx.has_s0 else None
-        dSf = dSfinal.float().contiguous() if (dSfinal is not None and dSfinal.numel()) else None
-        native.ext().gdn_scan_bwd(W, Qin, Kout, Aqk, Hsave.view(-1, 128), Vnew, dO, carry, dSf, dU, parts[0], parts[1], parts[2], dcarry, dS0,
-                                  native.err_flag(dev))
-        native._count()
-        dW, dQ, dK = (parts[i].sum(0).to(BF16) if nvs > 1 else parts[i, 0].to(BF16) for i in range(3))
-        n = L // CHUNK
-        dA = torch.matmul(dO.view(B, H, n, CHUNK, dv), Vnew.view(B, H, n, CHUNK, dv).transpose(-1, -2)).view(B, H, L, CHUNK)
-        return dU, dW, dQ, dA, dK, dcarry, dS0, None
-
-
-class _Local(torch.autograd.Function):
-    """Chunk-local stage on the device kernels of csrc/gdn_local.cu: (q, k, v, g, beta, starts) -> (U, W, q_in, Aqk, k_out,
-    carry), inputs token-major [B, L, H, *] (strided views are fine), outputs [B, Hv, L, *]."""
-
-    @staticmethod
-    def forward(ctx, q, k, v, g, beta, start_u8):
-        B, L, Hv, dv = v.shape
-        dev = v.device
-
-        def out(d, dtype=BF16):
-            return torch.empty(B, Hv, L, d, dtype=dtype, device=dev)
-
-        U, W, Aqk, Qin, Kout = out(dv), out(128), out(CHUNK), out(128), out(128)
-        carry = torch.empty(B, Hv, L // CHUNK, dtype=torch.float32, device=dev)
-        native.ext().gdn_local_fwd(q, k, v, g, beta, start_u8, U, W, Aqk, Qin, Kout, carry)
-        native._count()
-        ctx.save_for_backward(q, k, v, g, beta, start_u8, U, W)
-        return U, W, Qin, Aqk, Kout, carry
-
-    @staticmethod
-    def backward(ctx, dU, dW, dQin, dAqk, dKout, dcarry):
-        q, k, v, g, beta, start_u8, U, W = ctx.saved_tensors
+        q, k, v, g, beta, start_u8, U, W, Qin, Kout, Aqk, carry, Hsave, Vnew = ctx.saved_tensors
         B, L, Hv, dv = v.shape
         Hk = q.shape[2]
         dev = v.device
+        ex = native.ext()
+        nvs = dv // 128
+        dO = native._bf16(dO).contiguous()
+        dU = torch.empty_like(Vnew)
+        parts = torch.empty(3, nvs, B, Hv, L, 128, dtype=torch.float32, device=dev)
+        dcarry = torch.zeros_like(carry)
+        dS0 = torch.empty(B, Hv, 128, dv, dtype=torch.float32, device=dev) if ctx.has_s0 else None
+        dSf = dSfinal.float().contiguous() if (dSfinal is not None and dSfinal.numel()) else None
+        ex.gdn_scan_bwd(W, Qin, Kout, Aqk, Hsave.view(-1, 128), Vnew, dO, carry, dSf, dU, parts[0], parts[1], parts[2], dcarry, dS0,
+                        native.err_flag(dev))
         dq = torch.empty(B, L, Hv, 128, dtype=torch.float32, device=dev)
         dk = torch.empty_like(dq)
         dv_ = torch.empty(B, L, Hv, dv, dtype=BF16, device=dev)
         dg = torch.empty(B, L, Hv, dtype=torch.float32, device=dev)
         dbeta = torch.empty_like(dg)
-        c = lambda t: native._bf16(t).contiguous()
-        native.ext().gdn_local_bwd(q, k, v, g, beta, start_u8, U, W, c(dU), c(dW), c(dQin), c(dKout), c(dAqk), dcarry.float().contiguous(), dq, dk, dv_, dg, dbeta)
-        native._count()
+        ex.gdn_local_bwd(q, k, v, g, beta, start_u8, U, W, dU, parts, dO, Vnew, dcarry, dq, dk, dv_, dg, dbeta)
+        native._count(2)
         if Hv != Hk:
             dq = dq.view(B, L, Hk, Hv // Hk, 128).sum(3)
             dk = dk.view(B, L, Hk, Hv // Hk, 128).sum(3)
-        return dq.to(q.dtype), dk.to(k.dtype), dv_.to(v.dtype), dg, dbeta, None
+        return dq.to(q.dtype), dk.to(k.dtype), dv_.to(v.dtype), dg, dbeta, None, dS0, None
 
 
 def _tok_major_ok(t) -> bool:
@@ -127,8 +108,6 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
         g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
         is_doc_start = F.pad(is_doc_start, (0, pad))
     q, k, v = (t if _tok_major_ok(t) else native._bf16(t).contiguous() for t in (q, k, v))
-    U, W, Qin, Aqk, Kout, carry = _Local.apply(q, k, v, g.float().contiguous(), beta.float().contiguous(),
-                                               is_doc_start.to(torch.uint8).contiguous())
-    O, S = _Scan.apply(U, W, Qin, Aqk, Kout, carry, None if S0 is None else S0.float().contiguous(), need_state)
-    o = O[:, :, :L].transpose(1, 2)
-    return o, (S if need_state else None)
+    O, S = _DeltaRule.apply(q, k, v, g.float().contiguous(), beta.float().contiguous(), is_doc_start.to(torch.uint8).contiguous(),
+                            None if S0 is None else S0.float().contiguous(), need_state)
+    return (O[:, :L] if pad else O), (S if need_state else None)
