@@ -167,14 +167,15 @@ void attention_fwd(const Tensor& q, const c10::optional<Tensor>& qf, const Tenso
 
 void attention_bwd(const Tensor& q, const c10::optional<Tensor>& qf, const Tensor& k, const c10::optional<Tensor>& kf, const Tensor& v, const Tensor& o,
                    const Tensor& dO, const Tensor& lse, Tensor& dsum, Tensor& dq, const c10::optional<Tensor>& dqf, Tensor& dk,
-                   const c10::optional<Tensor>& dkf, Tensor& dv, const c10::optional<Tensor>& doc, int64_t cap, double scale, Tensor& err) {
+                   const c10::optional<Tensor>& dkf, Tensor& dv, const c10::optional<Tensor>& pos, int64_t cap, double scale, Tensor& err) {
   const c10::cuda::CUDAGuard guard(q.device());
   check_heads(q, "q"); check_heads(k, "k"); check_heads(v, "v"); check_heads(o, "o"); check_heads(dO, "dO"); check_heads(dk, "dk"); check_heads(dv, "dv");
   TORCH_CHECK(is_f32(dq) && dq.is_contiguous() && is_f32(dsum) && is_f32(lse), "attention_bwd: fp32 dq / dsum / lse");
   if (cap >= 0) TORCH_CHECK(qf.has_value() && kf.has_value() && dqf.has_value() && dkf.has_value() && is_f32(*dqf), "attention_bwd: far tensors");
+  if (pos.has_value()) TORCH_CHECK(pos->scalar_type() == torch::kInt32 && pos->is_contiguous(), "attention_bwd: int32 pos");
   check(ghb::attention_bwd(q.data_ptr(), optr(qf), k.data_ptr(), optr(kf), v.data_ptr(), o.data_ptr(), dO.data_ptr(), lse.data_ptr<float>(),
                            dsum.data_ptr<float>(), dq.data_ptr<float>(), dqf.has_value() ? dqf->data_ptr<float>() : nullptr, dk.data_ptr(),
-                           dkf.has_value() ? dkf->data_ptr() : nullptr, dv.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, q.size(0),
+                           dkf.has_value() ? dkf->data_ptr() : nullptr, dv.data_ptr(), pos.has_value() ? pos->data_ptr<int>() : nullptr, q.size(0),
                            q.size(1), q.size(2), k.size(2), cap, scale, err.data_ptr<int>(), stream()), "attention_bwd");
 }
 

@@ -43,7 +43,7 @@ int ce_grad(const float* logits, const long* targets, const float* a, const floa
 int attention_fwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, void* o, float* lse, const int* doc,
                   const int* pos, int B, int L, int Hq, int Hkv, int cap, float scale, int* err, cudaStream_t st);
 int attention_bwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, const void* o, const void* dO,
-                  const float* lse, float* dsum, float* dq, float* dqf, void* dk, void* dkf, void* dv, const int* doc, int B, int L, int Hq,
+                  const float* lse, float* dsum, float* dq, float* dqf, void* dk, void* dkf, void* dv, const int* pos, int B, int L, int Hq,
                   int Hkv, int cap, float scale, int* err, cudaStream_t st);
 
 int gdn_scan_fwd(const void* W, const void* Qin, const void* Kout, const void* Aqk, const void* U, const float* carry, const float* S0,

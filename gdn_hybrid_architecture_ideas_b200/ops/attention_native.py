@@ -27,13 +27,13 @@ class _Attention(torch.autograd.Function):
         lse = torch.empty(B, Hq, L, dtype=torch.float32, device=q.device)
         native.ext().attention_fwd(qc, qf, kc, kf, vc, o, lse, doc32, pos32, cap if capped else -1, hd ** -0.5, native.err_flag(q.device))
         native._count()
-        ctx.save_for_backward(qc, kc, vc, qf, kf, o, lse, doc32)
+        ctx.save_for_backward(qc, kc, vc, qf, kf, o, lse, pos32)
         ctx.cap, ctx.dtypes = cap, (q.dtype, k.dtype, v.dtype)
         return o
 
     @staticmethod
     def backward(ctx, dO):
-        qc, kc, vc, qf, kf, o, lse, doc32 = ctx.saved_tensors
+        qc, kc, vc, qf, kf, o, lse, pos32 = ctx.saved_tensors
         capped = ctx.cap is not None
         B, L, Hq, hd = qc.shape
         dq = torch.zeros(qc.shape, dtype=torch.float32, device=qc.device)
@@ -41,7 +41,7 @@ class _Attention(torch.autograd.Function):
         dk, dv = torch.empty_like(kc), torch.empty_like(vc)
         dkf = torch.empty_like(kc) if capped else None
         dsum = torch.empty_like(lse)
-        native.ext().attention_bwd(qc, qf, kc, kf, vc, o, native._bf16(dO).contiguous(), lse, dsum, dq, dqf, dk, dkf, dv, doc32,
+        native.ext().attention_bwd(qc, qf, kc, kf, vc, o, native._bf16(dO).contiguous(), lse, dsum, dq, dqf, dk, dkf, dv, pos32,
                                    ctx.cap if capped else -1, hd ** -0.5, native.err_flag(qc.device))
         native._count(2)
         qd, kd, vd = ctx.dtypes

@@ -1,0 +1,157 @@
+"""Time one hot op of the package in isolation (forward and backward), CUDA events after warm-up.
+
+    python scripts/op_bench.py attention --B 2 --L 4096 --cap 1024
+    python scripts/op_bench.py gdn --B 2 --L 4096
+    python scripts/op_bench.py gemm --M 65536 --N 1024 --K 1024
+    python scripts/op_bench.py rmsnorm --rows 65536 --d 1024
+
+Prints one JSON line per op with milliseconds per call and the achieved rate against the op's algorithmic FLOPs or
+bytes. `--iters 1 --warmup 0` gives a run short enough to capture under a profiler. Inputs are larger than the L2
+cache at the default sizes; an L2 flush (a 256 MB write) runs between timed calls.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from gdn_hybrid_architecture_ideas_b200.ops import attention_native, gdn_native, native  # noqa: E402
+
+BF16 = torch.bfloat16
+
+
+def timed(fn, iters, warmup):
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    native.check_status()
+    return total / max(iters, 1)
+
+
+def bench_attention(a):
+    B, L, Hq, Hkv, hd = a.B, a.L, a.Hq, a.Hkv, 64
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda h: torch.randn(B, L, h, hd, device="cuda", generator=g).to(BF16).requires_grad_()
+    q, k, v = mk(Hq), mk(Hkv), mk(Hkv)
+    capped = a.cap >= 0
+    qf, kf = (mk(Hq), mk(Hkv)) if capped else (None, None)
+    doc = pos = None
+    if a.doc_len:
+        idx = torch.arange(L, device="cuda")
+        doc = (idx // a.doc_len).to(torch.int32)[None].expand(B, L).contiguous()
+        pos = (idx % a.doc_len).to(torch.int32)[None].expand(B, L).contiguous()
+    out = {}
+
+    def fwd():
+        out["o"] = attention_native._Attention.apply(q, k, v, qf, kf, doc, pos, a.cap if capped else None)
+
+    ms_f = timed(fwd, a.iters, a.warmup)
+    do = torch.randn_like(out["o"])
+
+    def bwd():
+        out["o"].backward(do, retain_graph=True)
+
+    ms_b = timed(bwd, a.iters, a.warmup)
+    span = min(a.doc_len, L) if a.doc_len else L
+    pairs = B * Hq * (L // span) * span * (span + 1) / 2          # visible (query, key) pairs
+    f_fwd, f_bwd = 4 * pairs * hd, 10 * pairs * hd
+    return {"op": "attention", "B": B, "L": L, "Hq": Hq, "Hkv": Hkv, "cap": a.cap, "doc_len": a.doc_len, "fwd_ms": ms_f, "bwd_ms": ms_b,
+            "fwd_tflops": f_fwd / ms_f / 1e9, "bwd_tflops": f_bwd / ms_b / 1e9}
+
+
+def bench_gdn(a):
+    B, L, H, dk, dv = a.B, a.L, a.H, 128, a.dv
+    g_ = torch.Generator(device="cuda").manual_seed(0)
+    rn = lambda *s: torch.randn(*s, device="cuda", generator=g_)
+    q = (torch.nn.functional.normalize(rn(B, L, H, dk), dim=-1) * dk ** -0.5).to(BF16).requires_grad_()
+    k = torch.nn.functional.normalize(rn(B, L, H, dk), dim=-1).to(BF16).requires_grad_()
+    v = rn(B, L, H, dv).to(BF16).requires_grad_()
+    g = (-torch.rand(B, L, H, device="cuda", generator=g_) * 0.5).requires_grad_()
+    beta = torch.rand(B, L, H, device="cuda", generator=g_).requires_grad_()
+    start = torch.zeros(B, L, dtype=torch.bool, device="cuda")
+    out = {}
+
+    def fwd():
+        out["o"], _ = gdn_native.delta_rule(q, k, v, g, beta, start, None, 64, False)
+
+    ms_f = timed(fwd, a.iters, a.warmup)
+    do = torch.randn_like(out["o"])
+
+    def bwd():
+        out["o"].backward(do, retain_graph=True)
+
+    ms_b = timed(bwd, a.iters, a.warmup)
+    return {"op": "gdn", "B": B, "L": L, "H": H, "dv": dv, "fwd_ms": ms_f, "bwd_ms": ms_b}
+
+
+def bench_gemm(a):
+    M, N, K = a.M, a.N, a.K
+    x = torch.randn(M, K, device="cuda").to(BF16)
+    w = torch.randn(N, K, device="cuda").to(BF16)
+    ms = timed(lambda: native.gemm(x, w), a.iters, a.warmup)
+    ms_lib = timed(lambda: torch.matmul(x, w.t()), a.iters, a.warmup)
+    fl = 2.0 * M * N * K
+    return {"op": "gemm", "M": M, "N": N, "K": K, "ms": ms, "tflops": fl / ms / 1e9, "cublas_ms": ms_lib, "cublas_tflops": fl / ms_lib / 1e9}
+
+
+def bench_rmsnorm(a):
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    x = torch.randn(a.rows, a.d, device="cuda", requires_grad=True)
+    w = torch.zeros(a.d, device="cuda", requires_grad=True)
+    out = {}
+
+    def fwd():
+        out["y"] = ops.rmsnorm(x, w, 1e-6, out_dtype=BF16)
+
+    ms_f = timed(fwd, a.iters, a.warmup)
+    dy = torch.randn_like(out["y"])
+
+    def bwd():
+        out["y"].backward(dy, retain_graph=True)
+
+    ms_b = timed(bwd, a.iters, a.warmup)
+    n = a.rows * a.d
+    return {"op": "rmsnorm", "rows": a.rows, "d": a.d, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_gbs": n * 6 / ms_f / 1e6, "bwd_gbs": n * 10 / ms_b / 1e6}
+
+
+def main():
+    p = argparse.ArgumentParser()
+    p.add_argument("op", choices=["attention", "gdn", "gemm", "rmsnorm"])
+    p.add_argument("--iters", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--B", type=int, default=2)
+    p.add_argument("--L", type=int, default=4096)
+    p.add_argument("--Hq", type=int, default=16)
+    p.add_argument("--Hkv", type=int, default=16)
+    p.add_argument("--H", type=int, default=8)
+    p.add_argument("--dv", type=int, default=256)
+    p.add_argument("--cap", type=int, default=-1)
+    p.add_argument("--doc-len", type=int, default=0)
+    p.add_argument("--M", type=int, default=65536)
+    p.add_argument("--N", type=int, default=1024)
+    p.add_argument("--K", type=int, default=1024)
+    p.add_argument("--rows", type=int, default=65536)
+    p.add_argument("--d", type=int, default=1024)
+    a = p.parse_args()
+    res = {"attention": bench_attention, "gdn": bench_gdn, "gemm": bench_gemm, "rmsnorm": bench_rmsnorm}[a.op](a)
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()

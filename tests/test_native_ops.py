@@ -213,9 +213,10 @@ def test_adamw_and_sumsq():
     _close(native.sumsq(g), g.double().pow(2).sum(), 1.0, 1e-5)
 
 
-@pytest.mark.parametrize("L,cap,docs,Hq,Hkv", [(256, None, False, 4, 2), (384, 100, False, 4, 1), (300, 64, True, 2, 2), (512, 200, True, 8, 2),
-                                               (1024, None, True, 2, 1)])
-def test_attention_kernels(L, cap, docs, Hq, Hkv):
+@pytest.mark.parametrize("L,cap,docs,Hq,Hkv,ramp", [(256, None, False, 4, 2, False), (384, 100, False, 4, 1, False), (300, 64, True, 2, 2, False),
+                                                    (512, 200, True, 8, 2, False), (1024, None, True, 2, 1, False), (1024, 300, False, 2, 1, True),
+                                                    (640, None, False, 2, 2, True)])
+def test_attention_kernels(L, cap, docs, Hq, Hkv, ramp):
     from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
 
     B, hd = 2, 64
@@ -223,6 +224,9 @@ def test_attention_kernels(L, cap, docs, Hq, Hkv):
     def mk(h):
         return (torch.randn(B, L, h, hd, generator=g) * 0.7).to(_dev(), torch.bfloat16)
     q, qf, k, kf, v = mk(Hq), mk(Hq), mk(Hkv), mk(Hkv), mk(Hkv)
+    if ramp:      # key norms grow along the row, so later key tiles raise the row maxima by many powers of two
+        grow = torch.linspace(0.2, 9.0, L, device=_dev())[None, :, None, None]
+        k, kf = (k.float() * grow).to(torch.bfloat16), (kf.float() * grow).to(torch.bfloat16)
     doc = torch.zeros(B, L, dtype=torch.long, device=_dev())
     if docs:
         doc[0, L // 3:] = 1
