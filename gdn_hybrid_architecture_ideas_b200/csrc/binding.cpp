@@ -185,6 +185,25 @@ void check_rows(const Tensor& t, int64_t cols, const char* name) {
 float* fmut(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr<float>() : nullptr; }
 void* vmut(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }
 
+void dual_lerp_fwd(const Tensor& x, const Tensor& ya, const c10::optional<Tensor>& yb, const Tensor& la, const c10::optional<Tensor>& lb, Tensor& oa,
+                   const c10::optional<Tensor>& ob) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(is_bf16(x) && is_bf16(ya) && is_bf16(oa) && x.is_contiguous() && ya.is_contiguous() && oa.is_contiguous() && is_f32(la) && ya.numel() == x.numel(),
+              "dual_lerp_fwd: bf16 contiguous tensors, fp32 scalar weights");
+  if (yb.has_value()) TORCH_CHECK(is_bf16(*yb) && yb->is_contiguous() && yb->numel() == x.numel() && lb.has_value() && is_f32(*lb) && ob.has_value() && is_bf16(*ob) && ob->is_contiguous(), "dual_lerp_fwd: second mix");
+  check(ghb::dual_lerp_fwd(x.data_ptr(), ya.data_ptr(), optr(yb), la.data_ptr<float>(), fptr(lb), oa.data_ptr(), vmut(ob), x.numel(), sm_count(), stream()),
+        "dual_lerp_fwd");
+}
+void dual_lerp_bwd(const Tensor& ga, const c10::optional<Tensor>& gb, const Tensor& x, const Tensor& ya, const c10::optional<Tensor>& yb, const Tensor& la,
+                   const c10::optional<Tensor>& lb, Tensor& dx, Tensor& dya, const c10::optional<Tensor>& dyb, Tensor& dl) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(is_bf16(ga) && ga.is_contiguous() && is_bf16(dx) && dx.is_contiguous() && is_bf16(dya) && dya.is_contiguous() && is_f32(dl) && dl.numel() >= 2,
+              "dual_lerp_bwd: layout");
+  if (yb.has_value()) TORCH_CHECK(gb.has_value() && is_bf16(*gb) && gb->is_contiguous() && dyb.has_value() && is_bf16(*dyb) && dyb->is_contiguous(), "dual_lerp_bwd: second mix");
+  check(ghb::dual_lerp_bwd(ga.data_ptr(), optr(gb), x.data_ptr(), ya.data_ptr(), optr(yb), la.data_ptr<float>(), fptr(lb), dx.data_ptr(), dya.data_ptr(),
+                           vmut(dyb), dl.data_ptr<float>(), x.numel(), sm_count(), stream()), "dual_lerp_bwd");
+}
+
 // All operands laid out [B, H, L, *] with L a multiple of 64 (chunks never straddle rows).
 void gdn_scan_fwd(const Tensor& W, const Tensor& Qin, const Tensor& Kout, const Tensor& Aqk, const Tensor& U, const Tensor& carry,
                   const c10::optional<Tensor>& S0, Tensor& O, const c10::optional<Tensor>& Sfinal, const c10::optional<Tensor>& Hsave,
@@ -234,20 +253,26 @@ void gdn_local_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tens
 void gdn_local_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const Tensor& start, const Tensor& U,
                    const Tensor& W, const Tensor& dU, const Tensor& parts, const Tensor& dO, const Tensor& Vnew, const Tensor& dcarry, Tensor& dq,
                    Tensor& dk, Tensor& dv_, Tensor& dg, Tensor& dbeta) {
-  // parts: [3, n_part, B, H, L, 128] fp32 = per value-slice partial sums of (dW, dq_in, dk_out) from the state pass
+  // parts: [3, n_part, B, H, L, 128] fp32 = per value-slice partial sums of (dW, dq_in, dk_out) from the state pass.
+  // dq, dk: fp32 [B, L, Hv, 128] (per value head), or bf16 token-major views [B, L, Hk, 128] (Hv == Hk) written in place;
+  // dv: bf16 token-major view [B, L, Hv, dv]. The views may be column ranges of one packed gradient buffer.
   const c10::cuda::CUDAGuard guard(q.device());
-  check_tok_major(q, "q"); check_tok_major(k, "k"); check_tok_major(v, "v");
+  check_tok_major(q, "q"); check_tok_major(k, "k"); check_tok_major(v, "v"); check_tok_major(dv_, "dv");
   const int B = v.size(0), L = v.size(1), Hv = v.size(2), dv = v.size(3), Hk = q.size(2);
   for (const Tensor* t : {&U, &W, &dU, &dO, &Vnew}) TORCH_CHECK(is_bf16(*t) && t->is_contiguous(), "gdn_local_bwd: bf16 contiguous operands");
   TORCH_CHECK(is_f32(parts) && parts.is_contiguous() && parts.dim() == 6 && parts.size(0) == 3, "gdn_local_bwd: parts [3, n, B, H, L, 128] fp32");
   TORCH_CHECK(dO.dim() == 4 && dO.size(1) == L && dO.size(2) == Hv, "gdn_local_bwd: dO token-major [B, L, H, dv]");
-  TORCH_CHECK(is_f32(dq) && is_f32(dk) && is_bf16(dv_) && is_f32(dg) && is_f32(dbeta) && is_f32(dcarry) && dq.is_contiguous() && dk.is_contiguous() && dv_.is_contiguous(), "gdn_local_bwd: outputs");
+  TORCH_CHECK(is_f32(dg) && is_f32(dbeta) && is_f32(dcarry), "gdn_local_bwd: fp32 gate gradients");
+  const bool half = is_bf16(dq);
+  if (half) { check_tok_major(dq, "dq"); check_tok_major(dk, "dk"); TORCH_CHECK(dq.stride(1) == dk.stride(1) && Hv == Hk, "gdn_local_bwd: bf16 dq / dk need Hv == Hk"); }
+  else TORCH_CHECK(is_f32(dq) && is_f32(dk) && dq.is_contiguous() && dk.is_contiguous(), "gdn_local_bwd: fp32 dq / dk contiguous");
   const int n_part = parts.size(1);
   const long each = parts.stride(0);
   const float* p = parts.data_ptr<float>();
   check(ghb::gdn_local_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(1), k.stride(1), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(),
                            start.data_ptr<uint8_t>(), B, L, Hv, Hk, dv, U.data_ptr(), W.data_ptr(), dU.data_ptr(), p, p + each, p + 2 * each, n_part,
-                           dO.data_ptr(), Vnew.data_ptr(), dcarry.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv_.data_ptr(),
+                           dO.data_ptr(), Vnew.data_ptr(), dcarry.data_ptr<float>(), half ? nullptr : dq.data_ptr<float>(), half ? nullptr : dk.data_ptr<float>(),
+                           half ? dq.data_ptr() : nullptr, half ? dk.data_ptr() : nullptr, half ? dq.stride(1) : 0, dv_.data_ptr(), dv_.stride(1),
                            dg.data_ptr<float>(), dbeta.data_ptr<float>(), stream()), "gdn_local_bwd");
 }
 
@@ -305,6 +330,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_bf16", &cast_bf16);
   m.def("gdn_prep_fwd", &gdn_prep_fwd);
   m.def("gdn_prep_bwd", &gdn_prep_bwd);
+  m.def("dual_lerp_fwd", &dual_lerp_fwd);
+  m.def("dual_lerp_bwd", &dual_lerp_bwd);
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
   m.def("ce_grad", &ce_grad);

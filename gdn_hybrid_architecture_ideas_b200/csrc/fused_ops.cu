@@ -378,4 +378,79 @@ int ce_grad(const float* logits, const long* targets, const float* a, const floa
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// ================================================================================================ input mixes of a GDN layer
+// out_a = x + la (ya - x), out_b = x + lb (yb - x) in fp32, rounded to bf16 (the write and query inputs of a GDN layer
+// with mixes: ced/model/gdn.py:599-640 forms them as addcmul in fp32 and casts). yb == nullptr: only the first.
+// Backward: dx = (1 - la) ga + (1 - lb) gb, dya = la ga, dyb = lb gb, dla = sum ga (ya - x), dlb = sum gb (yb - x).
+__global__ void dual_lerp_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ ya, const __nv_bfloat16* __restrict__ yb,
+                                     const float* __restrict__ la, const float* __restrict__ lb, __nv_bfloat16* __restrict__ oa,
+                                     __nv_bfloat16* __restrict__ ob, long n4) {
+  const float a = *la, b = yb ? *lb : 0.f;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float xv[4], yv[4], o[4];
+    ld4(x + i * 4, xv);
+    ld4(ya + i * 4, yv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = fmaf(a, yv[e] - xv[e], xv[e]);
+    st4(oa + i * 4, o);
+    if (yb) {
+      ld4(yb + i * 4, yv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = fmaf(b, yv[e] - xv[e], xv[e]);
+      st4(ob + i * 4, o);
+    }
+  }
+}
+__global__ void dual_lerp_bwd_kernel(const __nv_bfloat16* __restrict__ ga, const __nv_bfloat16* __restrict__ gb, const __nv_bfloat16* __restrict__ x,
+                                     const __nv_bfloat16* __restrict__ ya, const __nv_bfloat16* __restrict__ yb, const float* __restrict__ la,
+                                     const float* __restrict__ lb, __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dya,
+                                     __nv_bfloat16* __restrict__ dyb, float* __restrict__ dl, long n4) {
+  const float a = *la, b = yb ? *lb : 0.f;
+  float sa = 0.f, sb = 0.f;
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    float xv[4], yv[4], g[4], d[4], o[4];
+    ld4(x + i * 4, xv);
+    ld4(ya + i * 4, yv);
+    ld4(ga + i * 4, g);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { d[e] = (1.f - a) * g[e]; o[e] = a * g[e]; sa += g[e] * (yv[e] - xv[e]); }
+    st4(dya + i * 4, o);
+    if (yb) {
+      ld4(yb + i * 4, yv);
+      ld4(gb + i * 4, g);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { d[e] += (1.f - b) * g[e]; o[e] = b * g[e]; sb += g[e] * (yv[e] - xv[e]); }
+      st4(dyb + i * 4, o);
+    }
+    st4(dx + i * 4, d);
+  }
+  __shared__ float red[2][32];
+  sa = wsum(sa); sb = wsum(sb);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { red[0][warp] = sa; red[1][warp] = sb; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    sa = wsum(lane < nw ? red[0][lane] : 0.f);
+    sb = wsum(lane < nw ? red[1][lane] : 0.f);
+    if (lane == 0) { atomicAdd(dl, sa); if (yb) atomicAdd(dl + 1, sb); }
+  }
+}
+int dual_lerp_fwd(const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* oa, void* ob, long n, int sms, cudaStream_t st) {
+  if (n % 4) return 1;
+  using T = __nv_bfloat16;
+  dual_lerp_fwd_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const T*>(x), static_cast<const T*>(ya), static_cast<const T*>(yb), la, lb, static_cast<T*>(oa),
+                                                static_cast<T*>(ob), n / 4);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+// dl: [2] fp32, zeroed by the caller.
+int dual_lerp_bwd(const void* ga, const void* gb, const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* dx, void* dya,
+                  void* dyb, float* dl, long n, int sms, cudaStream_t st) {
+  if (n % 4) return 1;
+  using T = __nv_bfloat16;
+  dual_lerp_bwd_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const T*>(ga), static_cast<const T*>(gb), static_cast<const T*>(x), static_cast<const T*>(ya),
+                                                static_cast<const T*>(yb), la, lb, static_cast<T*>(dx), static_cast<T*>(dya), static_cast<T*>(dyb), dl, n / 4);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 }  // namespace ghb

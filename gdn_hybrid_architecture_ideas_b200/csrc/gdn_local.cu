@@ -219,8 +219,9 @@ struct LocalGrads {
   long part_stride; int n_part;
   const __nv_bfloat16* dO; const __nv_bfloat16* Vnew;     // dO token-major [B, L, H, DV]; v_new [B, H, L, DV]: dAqk = dO v_new^T is formed here
   const float* dcarry;
-  float* dq; float* dk;            // [B, L, Hv, 128] fp32 (per value head; heads sharing a key head are summed by the caller)
-  __nv_bfloat16* dv;               // [B, L, Hv, DV]
+  float* dq; float* dk;            // [B, L, Hv, 128] fp32 (per value head; heads sharing a key head are summed by the caller), or null:
+  __nv_bfloat16* dq16; __nv_bfloat16* dk16; long qk_tok;   // bf16 rows [token][head][128] with token stride qk_tok (one value head per key head only)
+  __nv_bfloat16* dv; long dv_tok;  // [token][Hv][DV] with token stride dv_tok
   float* dg; float* dbeta;         // [B, L, Hv]
 };
 
@@ -414,7 +415,7 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
             const long vidx = (tok0 + i) * in.v_tok + static_cast<long>(hv) * DV + c0 + col;
             const float pv = v * __bfloat162float(in.v[vidx]);
             if (e >> 1) pb1 += pv; else pb0 += pv;
-            gr.dv[(tok0 + i) * in.Hv * DV + static_cast<long>(hv) * DV + c0 + col] = __float2bfloat16(sc->beta[i] * v);
+            gr.dv[(tok0 + i) * gr.dv_tok + static_cast<long>(hv) * DV + c0 + col] = __float2bfloat16(sc->beta[i] * v);
           }
         }
       if (is_u) {      // reduce over the 4 lanes that share a row, then one shared atomic per row per warp
@@ -501,8 +502,10 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
       const float fq = sc->seg[r] == 0 ? sc->gamma[r] : 0.f;                       // q_in = q fq ; W rhs = beta fq k
       const float fk = sc->seg[r] == sc->last_seg ? sc->to_end[r] : 0.f;           // k_out = k fk
       const float br = sc->beta[r];
-      float* dqo = gr.dq + ((tok0 + r) * in.Hv + hv) * LK;
-      float* dko = gr.dk + ((tok0 + r) * in.Hv + hv) * LK;
+      float* dqo = gr.dq16 ? nullptr : gr.dq + ((tok0 + r) * in.Hv + hv) * LK;
+      float* dko = gr.dq16 ? nullptr : gr.dk + ((tok0 + r) * in.Hv + hv) * LK;
+      __nv_bfloat16* dqh = gr.dq16 ? gr.dq16 + (tok0 + r) * gr.qk_tok + static_cast<long>(hv) * LK : nullptr;
+      __nv_bfloat16* dkh = gr.dq16 ? gr.dk16 + (tok0 + r) * gr.qk_tok + static_cast<long>(hv) * LK : nullptr;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int kk = n0 + nt * 8 + 2 * tq;
@@ -513,8 +516,13 @@ gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
         float2 ok, oq;
         ok.x = dk[nt][2 * h] + br * fq * drw.x + fk * dkv.x; ok.y = dk[nt][2 * h + 1] + br * fq * drw.y + fk * dkv.y;
         oq.x = dq[nt][2 * h] + fq * dqi.x; oq.y = dq[nt][2 * h + 1] + fq * dqi.y;
-        *reinterpret_cast<float2*>(dko + kk) = ok;
-        *reinterpret_cast<float2*>(dqo + kk) = oq;
+        if (dqh) {
+          *reinterpret_cast<__nv_bfloat162*>(dkh + kk) = __floats2bfloat162_rn(ok.x, ok.y);
+          *reinterpret_cast<__nv_bfloat162*>(dqh + kk) = __floats2bfloat162_rn(oq.x, oq.y);
+        } else {
+          *reinterpret_cast<float2*>(dko + kk) = ok;
+          *reinterpret_cast<float2*>(dqo + kk) = oq;
+        }
         dots[h][0] += drw.x * kre.x + drw.y * kre.y;
         dots[h][1] += dqi.x * qre.x + dqi.y * qre.y;
         dots[h][2] += dkv.x * kre.x + dkv.y * kre.y;
@@ -546,13 +554,14 @@ constexpr size_t LOCAL_BWD_SMEM = (4 * LC * KS + 3 * LC * BS + 2 * LC) * sizeof(
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
                   const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU,
                   const float* dWp, const float* dQp, const float* dKp, int n_part, const void* dO, const void* Vnew, const float* dcarry,
-                  float* dq, float* dk, void* dvv, float* dg, float* dbeta, cudaStream_t st) {
+                  float* dq, float* dk, void* dq16, void* dk16, long qk_tok, void* dvv, long dv_tok, float* dg, float* dbeta, cudaStream_t st) {
   if (L % LC || (dv != 128 && dv != 256) || Hv % Hk || n_part != dv / 128) return 1;
+  if (dq16 ? (Hv != Hk || !dk16 || qk_tok % 2) : (!dq || !dk)) return 1;
   LocalIn in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), q_tok, k_tok, v_tok,
              g, beta, start, L, Hv, Hv / Hk};
   LocalGrads gr{static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(dU), dWp, dQp, dKp,
                 static_cast<long>(B) * Hv * L * LK, n_part, static_cast<const __nv_bfloat16*>(dO), static_cast<const __nv_bfloat16*>(Vnew), dcarry,
-                dq, dk, static_cast<__nv_bfloat16*>(dvv), dg, dbeta};
+                dq, dk, static_cast<__nv_bfloat16*>(dq16), static_cast<__nv_bfloat16*>(dk16), qk_tok, static_cast<__nv_bfloat16*>(dvv), dv_tok, dg, dbeta};
   dim3 grid(L / LC, Hv, B);
   static bool attr = false;
   if (!attr) {

@@ -5,8 +5,9 @@
 // accumulator from tensor memory (tcgen05.ld) and store the tile. Two accumulators alternate so the epilogue of tile
 // i overlaps the main loop of tile i+1. Each operand may be K-major (reduction dimension contiguous: forward
 // y = x W^T) or MN-major (dgrad dx = dy W, wgrad dW = dy^T x), selected in the UMMA instruction descriptor; the
-// shared-memory tiles are 128-byte swizzled in both cases. Output: bf16, fp32, or fp32 accumulated in place
-// (main-gradient accumulation). No cluster multicast is used anywhere.
+// shared-memory tiles are 128-byte swizzled in both cases. Output: bf16, fp32, fp32 accumulated in place
+// (main-gradient accumulation), or fp32 reduced into the output by several slices of the reduction dimension (split-K
+// for weight gradients, whose few output tiles would otherwise leave most SMs idle). No cluster multicast is used.
 //
 // Replaces the cuBLAS calls behind every nn.Linear of the reference (ced/model/gdn.py:599-849,
 // ced/model/attention.py:836-900, ced/model/mlp.py:20-36) and its fp32 wgrad accumulation
@@ -40,7 +41,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int BN, bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, void* __restrict__ Cout,
-            long ldc, int M, int N, int K, int* __restrict__ err) {
+            long ldc, int M, int N, int K, int splits, int* __restrict__ err) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -56,6 +57,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  const int kbs = (num_kb + splits - 1) / splits;      // k-blocks per split; the host guarantees every split is non-empty
+  const int units = tiles * splits;                    // work unit = (output tile, slice of the reduction)
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
@@ -73,10 +76,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   if (warp == 0) {
     if (lane == 0) {
       int s = 0; uint32_t ph = 0; bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        int tm, tn; tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        int tm, tn; tile_coords(unit % tiles, tiles_m, tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (unit / tiles) * kbs, kb1 = min(num_kb, kb0 + kbs);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 101); ok = false; break; }
           mbar_expect_tx(&full[s], Cfg::A_BYTES + Cfg::B_BYTES);
           uint8_t* a = sA + s * Cfg::A_BYTES; uint8_t* b = sB + s * Cfg::B_BYTES;
@@ -93,12 +97,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
       int s = 0; uint32_t ph = 0; int it = 0; bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++it) {
         const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
         if (!mbar_wait(&tempty[acc], aph ^ 1)) { atomicExch(err, 102); ok = false; break; }
         tc_fence_after();
         const uint32_t d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (unit / tiles) * kbs, kb1 = min(num_kb, kb0 + kbs);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[s], ph)) { atomicExch(err, 103); ok = false; break; }
           tc_fence_after();
           const uint32_t a = smem_u32(sA + s * Cfg::A_BYTES), b = smem_u32(sB + s * Cfg::B_BYTES);
@@ -106,7 +111,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           for (int k = 0; k < BK / UK; ++k) {
             const uint64_t da = A_MN ? umma_desc_sw128(a + k * UK * 128, BK * 128, 1024) : umma_desc_sw128(a + k * UK * 2, 16, 1024);
             const uint64_t db = B_MN ? umma_desc_sw128(b + k * UK * 128, BK * 128, 1024) : umma_desc_sw128(b + k * UK * 2, 16, 1024);
-            umma_bf16(d, da, db, idesc, (kb | k) != 0);
+            umma_bf16(d, da, db, idesc, kb != kb0 || k != 0);
           }
           umma_commit(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -117,9 +122,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   } else {
     const int quad = warp & 3;   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     int it = 0; bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++it) {
       const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
-      int tm, tn; tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      int tm, tn; tile_coords(unit % tiles, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait(&tfull[acc], aph)) { if (lane == 0) atomicExch(err, 104); ok = false; break; }
       tc_fence_after();
       const long row = static_cast<long>(tm) * BM + quad * 32 + lane;
@@ -152,7 +157,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             }
           } else {
             float* out = reinterpret_cast<float*>(Cout) + row * ldc + col;
-            if (col + 32 <= N) {
+            if (OUT == 3) {          // slices of one tile's reduction meet in the output through fp32 reductions in L2
+              if (col + 32 <= N) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + e), "f"(__uint_as_float(r[e])), "f"(__uint_as_float(r[e + 1])),
+                               "f"(__uint_as_float(r[e + 2])), "f"(__uint_as_float(r[e + 3])) : "memory");
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) if (col + e < N) atomicAdd(out + e, __uint_as_float(r[e]));
+              }
+            } else if (col + 32 <= N) {
               float4* o4 = reinterpret_cast<float4*>(out);
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
@@ -192,7 +207,7 @@ static bool encode_operand(CUtensorMap* map, const void* ptr, long rows, long co
 }
 
 template <int BN, bool A_MN, bool B_MN, int OUT>
-static int launch_cfg(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, int* err,
+static int launch_cfg(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, int splits, int* err,
                       int sms, cudaStream_t stream) {
   CUtensorMap ta, tb;
   if (!encode_operand(&ta, A, M, K, lda, A_MN, BM)) return 21;
@@ -205,17 +220,17 @@ static int launch_cfg(const void* A, const void* B, void* C, int M, int N, int K
     attr_done = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  kern<<<min(tiles, sms), GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, C, ldc, M, N, K, err);
+  kern<<<min(tiles * splits, sms), GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, C, ldc, M, N, K, splits, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
 template <int BN, int OUT>
 static int launch_major(bool a_mn, bool b_mn, const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb,
-                        long ldc, int* err, int sms, cudaStream_t st) {
-  if (!a_mn && !b_mn) return launch_cfg<BN, false, false, OUT>(A, B, C, M, N, K, lda, ldb, ldc, err, sms, st);
-  if (!a_mn && b_mn) return launch_cfg<BN, false, true, OUT>(A, B, C, M, N, K, lda, ldb, ldc, err, sms, st);
-  if (a_mn && !b_mn) return launch_cfg<BN, true, false, OUT>(A, B, C, M, N, K, lda, ldb, ldc, err, sms, st);
-  return launch_cfg<BN, true, true, OUT>(A, B, C, M, N, K, lda, ldb, ldc, err, sms, st);
+                        long ldc, int splits, int* err, int sms, cudaStream_t st) {
+  if (!a_mn && !b_mn) return launch_cfg<BN, false, false, OUT>(A, B, C, M, N, K, lda, ldb, ldc, splits, err, sms, st);
+  if (!a_mn && b_mn) return launch_cfg<BN, false, true, OUT>(A, B, C, M, N, K, lda, ldb, ldc, splits, err, sms, st);
+  if (a_mn && !b_mn) return launch_cfg<BN, true, false, OUT>(A, B, C, M, N, K, lda, ldb, ldc, splits, err, sms, st);
+  return launch_cfg<BN, true, true, OUT>(A, B, C, M, N, K, lda, ldb, ldc, splits, err, sms, st);
 }
 
 // D = A B^T. a_mn / b_mn: the operand is stored with its M (N) dimension contiguous, i.e. as [K][M] ([K][N]) with row
@@ -230,11 +245,25 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long l
   if (reinterpret_cast<uintptr_t>(B) & 15) return 15;
   if (reinterpret_cast<uintptr_t>(C) & 15) return 16;
   const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  // A long reduction into few output tiles (weight gradients: K = tokens) leaves most SMs idle; slice the reduction so
+  // that the units fill the machine. Only the fp32 outputs can be reduced into: out 1 is zeroed first, out 2 already
+  // holds the running sum. Slices meet through floating-point reductions, so the summation order is not fixed.
+  int splits = 1;
+  if (out != 0) {
+    const int tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn), num_kb = (K + BK - 1) / BK;
+    splits = max(1, min(min(sms / tiles, num_kb / 16), 16));
+    while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;     // no empty slice
+    if (splits > 1) {
+      if (out == 1 && cudaMemset2DAsync(C, ldc * 4, 0, static_cast<size_t>(N) * 4, M, stream) != cudaSuccess) return 5;
+      out = 3;
+    }
+  }
 #define GHB_DISPATCH(BN)                                                                                              \
   switch (out) {                                                                                                      \
-    case 0: return launch_major<BN, 0>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, err, sms, stream);                 \
-    case 1: return launch_major<BN, 1>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, err, sms, stream);                 \
-    default: return launch_major<BN, 2>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, err, sms, stream);                \
+    case 0: return launch_major<BN, 0>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, 1, err, sms, stream);              \
+    case 1: return launch_major<BN, 1>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, 1, err, sms, stream);              \
+    case 2: return launch_major<BN, 2>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, 1, err, sms, stream);              \
+    default: return launch_major<BN, 3>(a_mn, b_mn, A, B, C, M, N, K, lda, ldb, ldc, splits, err, sms, stream);        \
   }
   if (bn == 256) { GHB_DISPATCH(256) }
   if (bn == 128) { GHB_DISPATCH(128) }

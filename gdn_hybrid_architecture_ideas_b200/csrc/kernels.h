@@ -40,6 +40,10 @@ int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const floa
 int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,
             int s, cudaStream_t st);
 
+int dual_lerp_fwd(const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* oa, void* ob, long n, int sms, cudaStream_t st);
+int dual_lerp_bwd(const void* ga, const void* gb, const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* dx, void* dya,
+                  void* dyb, float* dl, long n, int sms, cudaStream_t st);
+
 int attention_fwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, void* o, float* lse, const int* doc,
                   const int* pos, int B, int L, int Hq, int Hkv, int cap, float scale, int* err, cudaStream_t st);
 int attention_bwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, const void* o, const void* dO,
@@ -58,7 +62,7 @@ int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long 
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
                   const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU,
                   const float* dWp, const float* dQp, const float* dKp, int n_part, const void* dO, const void* Vnew, const float* dcarry,
-                  float* dq, float* dk, void* dvv, float* dg, float* dbeta, cudaStream_t st);
+                  float* dq, float* dk, void* dq16, void* dk16, long qk_tok, void* dvv, long dv_tok, float* dg, float* dbeta, cudaStream_t st);
 
 int decode_attention(const float* q, const void* k, const void* v, const int* lens, const int* doc_start, const float* cos_t, const float* sin_t,
                      void* out, float* part_o, float* part_ml, int B, int T, int Hq, int Hkv, int rot, int cap, int n_angles, int splits,

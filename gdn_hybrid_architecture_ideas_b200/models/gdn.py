@@ -99,31 +99,27 @@ class GatedDeltaNet(nn.Module):
         nq, C = hk * dk, self.conv_channels
         if arms is None:
             return self.in_proj_qkv(x), self.in_proj_a(x), self.in_proj_b(x)
-        wd = torch.promote_types(x.dtype, torch.float32)
-        xw = torch.addcmul(x.to(wd), (x_write.to(wd) - x.to(wd)), arms.write_lambda.to(wd))
-        xw = ops_cast(xw, x)
-        W = self.in_proj_qkv
         v = arms.variant
-        if v in READ_MIX_VARIANTS:
-            xr = torch.addcmul(x.to(wd), (x_read.to(wd) - x.to(wd)), arms.qmix_lambda.to(wd))
-            xr = ops_cast(xr, x)
+        W = self.in_proj_qkv
+        reads = v in READ_MIX_VARIANTS
+        xw, xr = ops.input_mixes(x, x_write, arms.write_lambda, x_read if reads else None, arms.qmix_lambda if reads else None)
+        # (rows [0, split) read `first`, rows [split, C) read `second`)
         if v == "none":
-            u = torch.cat([W.rows(0, nq)(x), W.rows(nq, C)(xw)], dim=-1)
+            u = ops.split_linear(x, xw, W, nq)
         elif v == "qmix":
-            u = torch.cat([W.rows(0, nq)(xr), W.rows(nq, C)(xw)], dim=-1)
+            u = ops.split_linear(xr, xw, W, nq)
         elif v == "kqmix":
-            u = torch.cat([W.rows(0, 2 * nq)(xr), W.rows(2 * nq, C)(xw)], dim=-1)
+            u = ops.split_linear(xr, xw, W, 2 * nq)
         elif v == "korig":
-            u = torch.cat([W.rows(0, 2 * nq)(x), W.rows(2 * nq, C)(xw)], dim=-1)
+            u = ops.split_linear(x, xw, W, 2 * nq)
         elif v == "vonly":
-            u = torch.cat([W.rows(0, 2 * nq)(x), W.rows(2 * nq, C)(xw)], dim=-1)
-            return u, self.in_proj_a(x), self.in_proj_b(x)
+            return ops.split_linear(x, xw, W, 2 * nq), self.in_proj_a(x), self.in_proj_b(x)
         elif v == "qshare":
             u = W(xw)
         elif v == "qshare_kv":
             return W(xw), self.in_proj_a(x), self.in_proj_b(x)
         elif v == "qshare_bd":
-            u = torch.cat([W.rows(0, nq)(xw), W.rows(nq, C)(x)], dim=-1)
+            u = ops.split_linear(xw, x, W, nq)
         else:
             raise ValueError(f"gdn_write_variant {v!r}")
         return u, self.in_proj_a(xw), self.in_proj_b(xw)
@@ -141,21 +137,13 @@ class GatedDeltaNet(nn.Module):
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
         u_pre, a_lin, b_lin = self.project(x, arms, x_write, x_read)
         hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
-        q, k, v, conv_input, conv_doc = ops.gdn_prep(u_pre, ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
-                                                     single_doc=ctx.single_doc)
+        qkv, conv_input, conv_doc = ops.gdn_prep(u_pre, ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
+                                                 single_doc=ctx.single_doc, packed=True)
         g, beta = ops.gdn_gates(a_lin, b_lin, self.A_log, self.dt_bias, ctx.gdn_scale, ctx.gdn_beta_power)
         S0 = None if state is None else state.S
         kernel = "recurrence" if cfg.kernel == "recurrence" else "chunked"
-        o, S = ops.delta_rule(q, k, v, g, beta, ctx.is_doc_start, S0, kernel=kernel, chunk_size=cfg.chunk_size,
-                              need_state=need_state)
+        o, S = ops.delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, ctx.is_doc_start, S0, kernel=kernel,
+                                     chunk_size=cfg.chunk_size, need_state=need_state)
         z = self.in_proj_z(x).view(B, L, hv, dv)
         y = self.out_proj(self.norm(o, z).flatten(2))
         return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)
-
-
-def ops_cast(t: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
-    """t in the dtype projections compute in: autocast's when it is on, else `like`'s own."""
-    dev = t.device.type
-    if torch.is_autocast_enabled(dev):
-        return t.to(torch.get_autocast_dtype(dev))
-    return t.to(like.dtype)

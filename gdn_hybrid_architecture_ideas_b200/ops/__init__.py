@@ -57,16 +57,35 @@ def linear(x, lin):
     return ref.linear(x, lin)
 
 
+def split_linear(xa, xb, lin, n):
+    """[lin.rows(0, n)(xa) | lin.rows(n, N)(xb)]: two row ranges of one projection reading two inputs."""
+    if use_native(xa):
+        return _native().split_linear(xa, xb, lin, n)
+    return torch.cat([linear(xa, lin.rows(0, n)), linear(xb, lin.rows(n, lin.weight.shape[0]))], dim=-1)
+
+
+def input_mixes(x, y_write, lam_write, y_read=None, lam_read=None):
+    """The write (and query) input of a GDN layer with mixes: x + lam (y - x) per mix."""
+    if use_native(x) and x.dtype == torch.bfloat16:
+        return _native().input_mixes(x, y_write, lam_write, y_read, lam_read)
+    return ref.input_mixes(x, y_write, lam_write, y_read, lam_read)
+
+
 def swiglu_mlp(x, w_gate, w_up, w_down):
     if use_native(x):
         return _native().swiglu_mlp(x, w_gate, w_up, w_down)
     return linear(torch.nn.functional.silu(linear(x, w_gate)) * linear(x, w_up), w_down)
 
 
-def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist=None, hist_doc=None, single_doc=False):
+def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist=None, hist_doc=None, single_doc=False, packed=False):
+    """(q, k, v, conv history, its document ids); packed: (qkv, history, ids) with qkv = [q | k | v] per token, the
+    layout `delta_rule_packed` reads."""
     if use_native(u_pre) and hist is None:
-        return _native().gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc)
-    return ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist, hist_doc)
+        return _native().gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc, packed)
+    q, k, v, h, hd = ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist, hist_doc)
+    if packed:
+        return torch.cat([q.flatten(2), k.flatten(2), v.flatten(2)], dim=-1), h, hd
+    return q, k, v, h, hd
 
 
 def gdn_gates(a_lin, b_lin, A_log, dt_bias, scale=1, beta_power=False):
@@ -96,6 +115,19 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=
     if kernel == "recurrence" or q.shape[1] == 1:
         return ref.delta_rule_recurrence(q, k, v, g, beta, is_doc_start, S0)
     return ref.chunked_delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size)
+
+
+def delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=64, need_state=True):
+    """`delta_rule` on the packed [q | k | v] tensor of `gdn_prep(packed=True)`: on the CUDA kernels the whole rule is
+    one autograd node whose gradient returns packed the same way."""
+    B, L, _ = qkv.shape
+    if use_native(qkv) and L > 1 and kernel != "recurrence":
+        from . import gdn_native
+        if gdn_native.packed_ok(qkv, hk, hv, dk, dv, chunk_size):
+            return _native().delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, need_state)
+    nq = hk * dk
+    q, k, v = qkv[..., :nq].view(B, L, hk, dk), qkv[..., nq:2 * nq].view(B, L, hk, dk), qkv[..., 2 * nq:].view(B, L, hv, dv)
+    return delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel=kernel, chunk_size=chunk_size, need_state=need_state)
 
 
 def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=None, cap=None, self_aligned=False, q_pos=None,

@@ -18,19 +18,28 @@ BF16 = torch.bfloat16
 CHUNK = 64
 
 
+def _unpack(qkv, hk, hv, dk, dv):
+    """Token-major views (q, k, v) of a packed [B, L, hk dk | hk dk | hv dv] tensor."""
+    B, L, _ = qkv.shape
+    nq = hk * dk
+    return (qkv[..., :nq].view(B, L, hk, dk), qkv[..., nq:2 * nq].view(B, L, hk, dk), qkv[..., 2 * nq:].view(B, L, hv, dv))
+
+
 class _DeltaRule(torch.autograd.Function):
-    """(q, k, v, g, beta, starts, S0) -> (o [B, L, Hv, dv], S_final). Inputs token-major [B, L, H, *] (strided views are
-    fine). Forward: the chunk-local kernel writes U, W, q_in, Aqk, k_out [B, Hv, L, *] and the per-chunk carry, the state
-    scan consumes them and writes the output token-major. Backward: the state scan's backward leaves dU and fp32 partial
+    """(qkv, g, beta, starts, S0) -> (o [B, L, Hv, dv], S_final); qkv packs q | k | v per token ([B, L, C] bf16).
+    Forward: the chunk-local kernel writes U, W, q_in, Aqk, k_out [B, Hv, L, *] and the per-chunk carry, the state scan
+    consumes them and writes the output token-major. Backward: the state scan's backward leaves dU and fp32 partial
     sums (one per 128-wide value slice) of dW, dq_in, dk_out; the chunk-local backward reads those directly, forms
-    dAqk = dO v_new^T itself and writes dq, dk, dv, dg, dbeta token-major."""
+    dAqk = dO v_new^T itself and writes dq | dk | dv into one packed gradient (fp32 dq, dk and a head-group sum when
+    several value heads share a key head)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, g, beta, start_u8, S0, need_state):
-        B, L, Hv, dv = v.shape
+    def forward(ctx, qkv, g, beta, start_u8, S0, need_state, hk, hv, dk, dv):
+        q, k, v = _unpack(qkv, hk, hv, dk, dv)
+        B, L, Hv, _ = v.shape
         dev = v.device
         ex = native.ext()
-        needs_grad = any(ctx.needs_input_grad[:7])
+        needs_grad = any(ctx.needs_input_grad[:5])
 
         def buf(d, dtype=BF16):
             return torch.empty(B, Hv, L, d, dtype=dtype, device=dev)
@@ -45,8 +54,8 @@ class _DeltaRule(torch.autograd.Function):
         ex.gdn_scan_fwd(W, Qin, Kout, Aqk, U, carry, S0, O, Sfinal, Hsave, Vnew, native.err_flag(dev))
         native._count(2)
         if needs_grad:
-            ctx.save_for_backward(q, k, v, g, beta, start_u8, U, W, Qin, Kout, Aqk, carry, Hsave, Vnew)
-        ctx.has_s0 = S0 is not None
+            ctx.save_for_backward(qkv, g, beta, start_u8, U, W, Qin, Kout, Aqk, carry, Hsave, Vnew)
+        ctx.has_s0, ctx.dims = S0 is not None, (hk, hv, dk, dv)
         if Sfinal is None:
             Sfinal = torch.zeros(0, device=dev)
             ctx.mark_non_differentiable(Sfinal)
@@ -54,9 +63,10 @@ class _DeltaRule(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dO, dSfinal):
-        q, k, v, g, beta, start_u8, U, W, Qin, Kout, Aqk, carry, Hsave, Vnew = ctx.saved_tensors
-        B, L, Hv, dv = v.shape
-        Hk = q.shape[2]
+        qkv, g, beta, start_u8, U, W, Qin, Kout, Aqk, carry, Hsave, Vnew = ctx.saved_tensors
+        hk, hv, dk_, dv = ctx.dims
+        q, k, v = _unpack(qkv, hk, hv, dk_, dv)
+        B, L, Hv, _ = v.shape
         dev = v.device
         ex = native.ext()
         nvs = dv // 128
@@ -68,17 +78,20 @@ class _DeltaRule(torch.autograd.Function):
         dSf = dSfinal.float().contiguous() if (dSfinal is not None and dSfinal.numel()) else None
         ex.gdn_scan_bwd(W, Qin, Kout, Aqk, Hsave.view(-1, 128), Vnew, dO, carry, dSf, dU, parts[0], parts[1], parts[2], dcarry, dS0,
                         native.err_flag(dev))
-        dq = torch.empty(B, L, Hv, 128, dtype=torch.float32, device=dev)
-        dk = torch.empty_like(dq)
-        dv_ = torch.empty(B, L, Hv, dv, dtype=BF16, device=dev)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv_ = _unpack(dqkv, hk, hv, dk_, dv)
         dg = torch.empty(B, L, Hv, dtype=torch.float32, device=dev)
         dbeta = torch.empty_like(dg)
-        ex.gdn_local_bwd(q, k, v, g, beta, start_u8, U, W, dU, parts, dO, Vnew, dcarry, dq, dk, dv_, dg, dbeta)
+        if hv == hk:
+            ex.gdn_local_bwd(q, k, v, g, beta, start_u8, U, W, dU, parts, dO, Vnew, dcarry, dq, dk, dv_, dg, dbeta)
+        else:
+            dq32 = torch.empty(B, L, Hv, 128, dtype=torch.float32, device=dev)
+            dk32 = torch.empty_like(dq32)
+            ex.gdn_local_bwd(q, k, v, g, beta, start_u8, U, W, dU, parts, dO, Vnew, dcarry, dq32, dk32, dv_, dg, dbeta)
+            dq.copy_(dq32.view(B, L, hk, hv // hk, 128).sum(3))
+            dk.copy_(dk32.view(B, L, hk, hv // hk, 128).sum(3))
         native._count(2)
-        if Hv != Hk:
-            dq = dq.view(B, L, Hk, Hv // Hk, 128).sum(3)
-            dk = dk.view(B, L, Hk, Hv // Hk, 128).sum(3)
-        return dq.to(q.dtype), dk.to(k.dtype), dv_.to(v.dtype), dg, dbeta, None, dS0, None
+        return dqkv, dg, dbeta, None, dS0, None, None, None, None, None
 
 
 def _tok_major_ok(t) -> bool:
@@ -88,6 +101,19 @@ def _tok_major_ok(t) -> bool:
 
 def supported(q, v) -> bool:
     return q.shape[-1] == 128 and v.shape[-1] % 128 == 0
+
+
+def packed_ok(qkv, hk, hv, dk, dv, chunk_size) -> bool:
+    return (dk == 128 and dv in (128, 256) and chunk_size == CHUNK and qkv.dtype == BF16 and qkv.is_contiguous() and qkv.shape[1] % CHUNK == 0
+            and qkv.shape[-1] % 8 == 0)
+
+
+def delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, need_state):
+    """qkv: [B, L, hk dk | hk dk | hv dv] bf16 (the conv/norm stage's output); g, beta: [B, L, Hv]. Returns
+    (o [B, L, Hv, dv], final state or None). One autograd node: its gradient comes back packed the same way."""
+    O, S = _DeltaRule.apply(qkv, g.float().contiguous(), beta.float().contiguous(), is_doc_start.to(torch.uint8).contiguous(),
+                            None if S0 is None else S0.float().contiguous(), need_state, hk, hv, dk, dv)
+    return O, (S if need_state else None)
 
 
 def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
@@ -107,7 +133,6 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
         q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
         g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
         is_doc_start = F.pad(is_doc_start, (0, pad))
-    q, k, v = (t if _tok_major_ok(t) else native._bf16(t).contiguous() for t in (q, k, v))
-    O, S = _DeltaRule.apply(q, k, v, g.float().contiguous(), beta.float().contiguous(), is_doc_start.to(torch.uint8).contiguous(),
-                            None if S0 is None else S0.float().contiguous(), need_state)
-    return (O[:, :L] if pad else O), (S if need_state else None)
+    qkv = torch.cat([native._bf16(t).flatten(2) for t in (q, k, v)], dim=-1)
+    O, S = delta_rule_packed(qkv, Hk, Hv, dk, dv, g, beta, is_doc_start, S0, need_state)
+    return (O[:, :L] if pad else O), S

@@ -143,6 +143,89 @@ def linear(x, lin):
     return _Linear.apply(x, lin.weight, _w_lp(lin))
 
 
+class _SplitLinear(torch.autograd.Function):
+    """u = [xa W[:n]^T | xb W[n:]^T]: two row ranges of one weight project two inputs into one output buffer (the q/k/v
+    projection of a GDN layer whose query and write inputs differ). The GEMMs write into and read from column ranges of
+    the [rows, N] buffers directly (row stride N), so neither direction copies a slice."""
+
+    @staticmethod
+    def forward(ctx, xa, xb, weight, w_lp, n):
+        a2 = _bf16(xa).reshape(-1, xa.shape[-1]).contiguous()
+        b2 = _bf16(xb).reshape(-1, xb.shape[-1]).contiguous()
+        N = w_lp.shape[0]
+        out = torch.empty(a2.shape[0], N, dtype=BF16, device=xa.device)
+        gemm(a2, w_lp[:n], out=out[:, :n])
+        gemm(b2, w_lp[n:], out=out[:, n:])
+        ctx.save_for_backward(a2, b2, w_lp)
+        ctx.n, ctx.shapes, ctx.dtypes = n, (xa.shape, xb.shape), (xa.dtype, xb.dtype)
+        return out.view(*xa.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        a2, b2, w_lp = ctx.saved_tensors
+        n = ctx.n
+        dy2 = _bf16(dy).reshape(-1, dy.shape[-1]).contiguous()
+        dxa = gemm(dy2[:, :n], w_lp[:n], b_mn=True).view(ctx.shapes[0])
+        dxb = gemm(dy2[:, n:], w_lp[n:], b_mn=True).view(ctx.shapes[1])
+        dw = torch.empty(w_lp.shape, dtype=torch.float32, device=dy.device)
+        gemm(dy2[:, :n], a2, out=dw[:n], a_mn=True, b_mn=True)
+        gemm(dy2[:, n:], b2, out=dw[n:], a_mn=True, b_mn=True)
+        da, db = ctx.dtypes
+        return (dxa if da == BF16 else dxa.to(da)), (dxb if db == BF16 else dxb.to(db)), dw, None, None
+
+
+def split_linear(xa, xb, lin, n):
+    if getattr(lin, "precision", "bf16") != "bf16" and lin.training or lin.weight.shape[0] % 8 or n % 8:
+        from ..models.linear import RowView
+        N = lin.weight.shape[0]
+        return torch.cat([linear(xa, RowView(lin, 0, n)), linear(xb, RowView(lin, n, N))], dim=-1)
+    return _SplitLinear.apply(xa, xb, lin.weight, _w_lp(lin), n)
+
+
+class _DualLerp(torch.autograd.Function):
+    """(x + la (ya - x), x + lb (yb - x)) in fp32, rounded to bf16; la, lb one-element fp32 parameters. yb None: the
+    first only."""
+
+    @staticmethod
+    def forward(ctx, x, ya, la, yb, lb):
+        xc, yac = _bf16(x).contiguous(), _bf16(ya).contiguous()
+        ybc = None if yb is None else _bf16(yb).contiguous()
+        laf = la.detach().float().reshape(1)
+        lbf = None if yb is None else lb.detach().float().reshape(1)
+        oa = torch.empty_like(xc)
+        ob = None if yb is None else torch.empty_like(xc)
+        ext().dual_lerp_fwd(xc, yac, ybc, laf, lbf, oa, ob)
+        _count()
+        ctx.save_for_backward(xc, yac, ybc, laf, lbf)
+        ctx.meta = (x.dtype, ya.dtype, None if yb is None else yb.dtype, la.dtype, la.shape, None if yb is None else lb.dtype)
+        if yb is None:
+            ob = oa.new_zeros(0)
+            ctx.mark_non_differentiable(ob)
+        return oa, ob
+
+    @staticmethod
+    def backward(ctx, ga, gb):
+        xc, yac, ybc, laf, lbf = ctx.saved_tensors
+        xd, yad, ybd, lad, lshape, lbd = ctx.meta
+        dual = ybc is not None
+        gac = _bf16(ga).contiguous()
+        gbc = _bf16(gb).contiguous() if dual else None
+        dx, dya = torch.empty_like(xc), torch.empty_like(xc)
+        dyb = torch.empty_like(xc) if dual else None
+        dl = torch.zeros(2, dtype=torch.float32, device=xc.device)
+        ext().dual_lerp_bwd(gac, gbc, xc, yac, ybc, laf, lbf, dx, dya, dyb, dl)
+        _count()
+        return (dx.to(xd), dya.to(yad), dl[0].reshape(lshape).to(lad), dyb.to(ybd) if dual else None,
+                dl[1].reshape(lshape).to(lbd) if dual else None)
+
+
+def input_mixes(x, y_write, lam_write, y_read=None, lam_read=None):
+    if lam_write.numel() != 1 or x.numel() % 4 or (y_read is not None and lam_read.numel() != 1):
+        return ref.input_mixes(x, y_write, lam_write, y_read, lam_read)
+    oa, ob = _DualLerp.apply(x, y_write, lam_write, y_read, lam_read)
+    return oa, (ob if y_read is not None else None)
+
+
 # ------------------------------------------------------------------------------------------------------------ norms
 
 class _RMSNorm(torch.autograd.Function):
@@ -289,14 +372,18 @@ class _GdnPrep(torch.autograd.Function):
         return (du if dt == BF16 else du.to(dt)), None, dw, None, None, None
 
 
-def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc=False):
+def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc=False, packed=False):
     B, L, C = u_pre.shape
     ok = dk == 128 and (hv * dv) % 128 == 0 and conv_weight.shape[1] == 4 and conv_weight.dtype == torch.float32
     if not ok:
-        return ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv)
+        q, k, v, h, hd = ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv)
+        return (torch.cat([q.flatten(2), k.flatten(2), v.flatten(2)], dim=-1), h, hd) if packed else (q, k, v, h, hd)
     doc32 = None if single_doc else doc.to(torch.int32).contiguous()
     out = _GdnPrep.apply(u_pre, doc32, conv_weight, L, hk * dk, dk ** -0.5)
     nq = hk * dk
+    if packed:
+        K = conv_weight.shape[1]
+        return out, u_pre[:, L - (K - 1):], doc[:, L - (K - 1):]
     q = out[..., :nq].view(B, L, hk, dk)
     k = out[..., nq:2 * nq].view(B, L, hk, dk)
     v = out[..., 2 * nq:].view(B, L, hv, dv)
@@ -415,6 +502,11 @@ def cast_bf16_(x, y):
 
 
 # ------------------------------------------------------------------------------------------------------------ sequence mixers
+
+def delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, need_state):
+    from . import gdn_native
+    return gdn_native.delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, need_state)
+
 
 def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
     from . import gdn_native

@@ -258,3 +258,16 @@ def embedding(tokens, weight):
     (reference: ced/model/control.py:436-455)."""
     e = F.embedding(tokens, weight)
     return e.mean(dim=2) if tokens.dim() == 3 else e
+
+
+def input_mixes(x, y_write, lam_write, y_read=None, lam_read=None):
+    """(x + lam_w (y_write - x), x + lam_r (y_read - x) or None): the write and query inputs of a GDN layer with mixes,
+    formed in >= fp32 and returned in the dtype projections compute in (reference: ced/model/gdn.py:599-640)."""
+    wd = torch.promote_types(x.dtype, torch.float32)
+    dev = x.device.type
+    out_dtype = torch.get_autocast_dtype(dev) if torch.is_autocast_enabled(dev) else x.dtype
+
+    def mix(y, lam):
+        return torch.addcmul(x.to(wd), y.to(wd) - x.to(wd), lam.to(wd)).to(out_dtype)
+
+    return mix(y_write, lam_write), (None if y_read is None else mix(y_read, lam_read))

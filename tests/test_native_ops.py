@@ -42,6 +42,78 @@ def test_gemm_layouts(M, N, K, layout):
     native.check_status()
 
 
+def test_gemm_split_k():
+    """Few output tiles and a long reduction: the reduction is sliced across CTAs and meets in the fp32 output."""
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    M, N, K = 256, 384, 16384
+    g = torch.Generator(device="cpu").manual_seed(5)
+    a = torch.randn(K, M, generator=g).to(_dev(), torch.bfloat16)      # stored [K, M]: the weight-gradient layout
+    b = torch.randn(K, N, generator=g).to(_dev(), torch.bfloat16)
+    want = a.float().T @ b.float()
+    got = native.gemm(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    _close(got, want, 2e-3 * K ** 0.5, 1e-3, "split-k store")
+    acc = torch.full((M, N), 2.0, device=_dev())
+    native.gemm(a, b, out=acc, a_mn=True, b_mn=True, accumulate=True)
+    _close(acc, want + 2, 2e-3 * K ** 0.5, 1e-3, "split-k accumulate")
+    wide = torch.zeros(M, N + 8, device=_dev())                        # a strided output (row stride > N) stays intact outside N
+    native.gemm(a, b, out=wide[:, :N], a_mn=True, b_mn=True)
+    _close(wide[:, :N], want, 2e-3 * K ** 0.5, 1e-3, "split-k strided")
+    assert float(wide[:, N:].abs().max()) == 0.0
+    native.check_status()
+
+
+@pytest.mark.parametrize("dual", [True, False])
+def test_input_mixes_kernel(dual):
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    g = torch.Generator().manual_seed(3)
+    mk = lambda: torch.randn(3, 50, 256, generator=g).to(_dev(), torch.bfloat16)
+    x, ya, yb = mk(), mk(), mk()
+    la, lb = torch.tensor([0.3], device=_dev()), torch.tensor([-0.7], device=_dev())
+    leaves = [t.clone().requires_grad_() for t in (x, ya, la, yb, lb)]
+    refs = [t.clone().float().requires_grad_() for t in (x, ya, la, yb, lb)]
+    oa, ob = native.input_mixes(leaves[0], leaves[1], leaves[2], leaves[3] if dual else None, leaves[4] if dual else None)
+    ra, rb = ref.input_mixes(refs[0], refs[1], refs[2], refs[3] if dual else None, refs[4] if dual else None)
+    _close(oa, ra, 2e-2, 1e-2, "write mix")
+    ga, gb = torch.randn_like(ra), torch.randn_like(ra)
+    if dual:
+        _close(ob, rb, 2e-2, 1e-2, "query mix")
+        (oa.float() * ga + ob.float() * gb).sum().backward()
+        (ra * ga + rb * gb).sum().backward()
+    else:
+        assert ob is None
+        (oa.float() * ga).sum().backward()
+        (ra * ga).sum().backward()
+    for name, a, b in zip(("dx", "dya", "dla", "dyb", "dlb"), leaves, refs):
+        if b.grad is None:
+            assert a.grad is None
+            continue
+        scale = float(b.grad.abs().max())
+        _close(a.grad, b.grad, 2e-2 * max(scale, 1.0), 2e-2, name)
+    native.check_status()
+
+
+def test_split_linear_kernel():
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.models.linear import Linear
+
+    lin = Linear(256, 640).to(_dev())
+    g = torch.Generator().manual_seed(4)
+    xa = torch.randn(2, 70, 256, generator=g).to(_dev(), torch.bfloat16).requires_grad_()
+    xb = torch.randn(2, 70, 256, generator=g).to(_dev(), torch.bfloat16).requires_grad_()
+    y = ops.split_linear(xa, xb, lin, 128)
+    want = torch.cat([xa.float() @ lin.weight[:128].T, xb.float() @ lin.weight[128:].T], dim=-1)
+    _close(y, want, 3e-2, 2e-2, "split linear")
+    go = torch.randn_like(want).to(torch.bfloat16).float()
+    y.backward(go.to(y.dtype))
+    got = (xa.grad.clone(), xb.grad.clone(), lin.weight.grad.clone())
+    xa.grad = xb.grad = lin.weight.grad = None
+    want.backward(go)
+    for name, a, b in zip(("dxa", "dxb", "dw"), got, (xa.grad, xb.grad, lin.weight.grad)):
+        _close(a, b, 1e-1, 3e-2, name)
+
+
 def test_linear_autograd():
     from gdn_hybrid_architecture_ideas_b200 import ops
     from gdn_hybrid_architecture_ideas_b200.models.linear import Linear
