@@ -109,12 +109,12 @@ void gdn_prep_fwd(const Tensor& u, const c10::optional<Tensor>& doc, const Tenso
   check(ghb::gdn_prep_fwd(u.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, w.data_ptr<float>(), out.data_ptr(), u.numel() / C, L, C, nq,
                           qscale, stream()), "gdn_prep_fwd");
 }
-void gdn_prep_bwd(const Tensor& u, const c10::optional<Tensor>& doc, const Tensor& w, const Tensor& dout, Tensor& dconv, Tensor& du, Tensor& dw,
+void gdn_prep_bwd(const Tensor& u, const c10::optional<Tensor>& doc, const Tensor& w, const Tensor& dout, Tensor& du, Tensor& dw,
                   int64_t L, int64_t nq, double qscale) {
   const c10::cuda::CUDAGuard guard(u.device());
   const int C = u.size(-1);
-  TORCH_CHECK(is_bf16(dout) && dout.is_contiguous() && is_bf16(dconv) && is_bf16(du) && is_f32(dw) && dw.is_contiguous(), "gdn_prep_bwd: layout");
-  check(ghb::gdn_prep_bwd(u.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, w.data_ptr<float>(), dout.data_ptr(), dconv.data_ptr(),
+  TORCH_CHECK(is_bf16(dout) && dout.is_contiguous() && is_bf16(du) && du.is_contiguous() && is_f32(dw) && dw.is_contiguous(), "gdn_prep_bwd: layout");
+  check(ghb::gdn_prep_bwd(u.data_ptr(), doc.has_value() ? doc->data_ptr<int>() : nullptr, w.data_ptr<float>(), dout.data_ptr(),
                           du.data_ptr(), dw.data_ptr<float>(), u.numel() / C, L, C, nq, qscale, stream()), "gdn_prep_bwd");
 }
 

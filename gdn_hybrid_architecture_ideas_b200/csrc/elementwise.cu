@@ -78,39 +78,47 @@ __global__ void rmsnorm_fwd_kernel(const TI* __restrict__ x, const float* __rest
 
 // ------------------------------------------------------------------------------------------------ RMSNorm backward
 // g = scale * dy * [act(z)] * (1 + w); dx = rstd * (g - xhat * mean(g * xhat)) [+ dres]; dw += scale * dy * [act] * xhat;
-// dz = dy * scale * xhat * (1 + w) * act'(z). Each warp walks rows with a grid stride and keeps its dw partial in
-// registers; partials are reduced through shared memory and one atomicAdd per channel per block.
-template <typename TI, typename TG, int ITERS, int GATE>
-__global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TI* __restrict__ x, const float* __restrict__ w, int w_scalar,
-                                   const __nv_bfloat16* __restrict__ z, const float* __restrict__ rstd, const float* __restrict__ dres,
-                                   TI* __restrict__ dx, __nv_bfloat16* __restrict__ dz, float* __restrict__ dw, long rows, int d, float scale) {
-  extern __shared__ float red[];   // d floats
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+// dz = dy * scale * xhat * (1 + w) * act'(z). WPR warps share a row (each lane covers 4 * ITERS of its warp's
+// d / WPR channels), so a wide row costs few registers per thread and many warps stay resident; the row's dot
+// product crosses warps through shared memory. Blocks walk rows with a grid stride (the same trip count for every
+// warp of a block) and keep their dw partial in registers; partials meet in shared memory, then one atomicAdd per
+// channel per block.
+constexpr int NORM_BWD_WARPS = 8;
+
+template <typename TI, typename TG, int ITERS, int WPR, int GATE>
+__global__ void __launch_bounds__(NORM_BWD_WARPS * 32)
+rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TI* __restrict__ x, const float* __restrict__ w, int w_scalar,
+                   const __nv_bfloat16* __restrict__ z, const float* __restrict__ rstd, const float* __restrict__ dres,
+                   TI* __restrict__ dx, __nv_bfloat16* __restrict__ dz, float* __restrict__ dw, long rows, int d, float scale) {
+  extern __shared__ float red[];   // d floats, then 2 x NORM_BWD_WARPS exchange slots
+  float* xch = red + d;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int RPB = NORM_BWD_WARPS / WPR;            // rows per block per trip
+  const int rsub = warp / WPR, wsub = warp % WPR;
   for (int c = threadIdx.x; c < d; c += blockDim.x) red[c] = 0.f;
   __syncthreads();
   float acc[ITERS][4];
-  float g1[ITERS][4];
 #pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int c = (i * 32 + lane) * 4;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) { acc[i][e] = 0.f; g1[i][e] = 1.f; }
-    if (c < d) {
-      if (w_scalar) { g1[i][0] = g1[i][1] = g1[i][2] = g1[i][3] = 1.f + w[0]; }
-      else { float4 t = *reinterpret_cast<const float4*>(w + c); g1[i][0] = 1.f + t.x; g1[i][1] = 1.f + t.y; g1[i][2] = 1.f + t.z; g1[i][3] = 1.f + t.w; }
-    }
-  }
-  for (long row = static_cast<long>(blockIdx.x) * nwarp + warp; row < rows; row += static_cast<long>(gridDim.x) * nwarp) {
-    const float r = rstd[row];
+  for (int i = 0; i < ITERS; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const float g_scalar = w_scalar ? 1.f + w[0] : 0.f;
+  int par = 0;
+  for (long base = static_cast<long>(blockIdx.x) * RPB; base < rows; base += static_cast<long>(gridDim.x) * RPB) {
+    const long row = base + rsub;
+    const bool live = row < rows;
+    const float r = live ? rstd[row] : 0.f;
     float xh[ITERS][4], gg[ITERS][4];
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
-      const int c = (i * 32 + lane) * 4;
-      if (c < d) {
-        float xv[4], dv[4];
+      const int c = ((wsub * ITERS + i) * 32 + lane) * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { xh[i][e] = 0.f; gg[i][e] = 0.f; }
+      if (live && c < d) {
+        float xv[4], dv[4], g1[4];
         Vec4<TI>::load(x + row * d + c, xv);
         Vec4<TG>::load(dy + row * d + c, dv);
+        if (w_scalar) { g1[0] = g1[1] = g1[2] = g1[3] = g_scalar; }
+        else { const float4 t = __ldg(reinterpret_cast<const float4*>(w + c)); g1[0] = 1.f + t.x; g1[1] = 1.f + t.y; g1[2] = 1.f + t.z; g1[3] = 1.f + t.w; }
         float zz[4] = {0.f, 0.f, 0.f, 0.f};
         if (GATE) Vec4<__nv_bfloat16>::load(z + row * d + c, zz);
         float dzv[4];
@@ -122,21 +130,30 @@ __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TI* __restri
             const float s = sigmoidf_(zz[e]);
             const float act = GATE == 1 ? zz[e] * s : s;
             const float dact = GATE == 1 ? s * (1.f + zz[e] * (1.f - s)) : s * (1.f - s);
-            dzv[e] = dn * xh[i][e] * g1[i][e] * dact;
+            dzv[e] = dn * xh[i][e] * g1[e] * dact;
             dn *= act;
           }
           acc[i][e] += dn * xh[i][e];
-          gg[i][e] = dn * g1[i][e];
+          gg[i][e] = dn * g1[e];
           dot += gg[i][e] * xh[i][e];
         }
         if (GATE) Vec4<__nv_bfloat16>::store(dz + row * d + c, dzv);
       }
     }
-    dot = warp_sum(dot) / d;
+    dot = warp_sum(dot);
+    if (WPR > 1) {                     // two alternating slot sets: a warp may run one trip ahead of its row partners
+      if (lane == 0) xch[par * NORM_BWD_WARPS + warp] = dot;
+      __syncthreads();
+      dot = 0.f;
+#pragma unroll
+      for (int k = 0; k < WPR; ++k) dot += xch[par * NORM_BWD_WARPS + rsub * WPR + k];
+      par ^= 1;
+    }
+    dot /= d;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
-      const int c = (i * 32 + lane) * 4;
-      if (c < d) {
+      const int c = ((wsub * ITERS + i) * 32 + lane) * 4;
+      if (live && c < d) {
         float o[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = r * (gg[i][e] - xh[i][e] * dot);
@@ -149,7 +166,7 @@ __global__ void rmsnorm_bwd_kernel(const TG* __restrict__ dy, const TI* __restri
   }
 #pragma unroll
   for (int i = 0; i < ITERS; ++i) {
-    const int c = (i * 32 + lane) * 4;
+    const int c = ((wsub * ITERS + i) * 32 + lane) * 4;
     if (c < d) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) atomicAdd(&red[c + e], acc[i][e]);
@@ -193,18 +210,33 @@ int rmsnorm_fwd(const void* x, int in_bf16, const float* w, int w_scalar, const 
 #undef GHB_G
 }
 
+template <typename TI, typename TG, int ITERS, int WPR, int GATE>
+static int norm_bwd_launch(const void* dy, const void* x, const float* w, int ws, const void* z, const float* rstd, const float* dres, void* dx,
+                           void* dz, float* dw, long rows, int d, float scale, int sms, cudaStream_t st) {
+  auto kern = rmsnorm_bwd_kernel<TI, TG, ITERS, WPR, GATE>;
+  const size_t sh = (d + 2 * NORM_BWD_WARPS) * sizeof(float);
+  int resident = 0;                  // blocks that fit one SM: the grid is one full wave, so no tail wave runs part-empty
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, kern, NORM_BWD_WARPS * 32, sh) != cudaSuccess || resident < 1) resident = 1;
+  constexpr int RPB = NORM_BWD_WARPS / WPR;
+  const long want = (rows + RPB - 1) / RPB;
+  const long cap = static_cast<long>(sms) * resident;
+  kern<<<static_cast<unsigned>(want < cap ? want : cap), NORM_BWD_WARPS * 32, sh, st>>>(
+      static_cast<const TG*>(dy), static_cast<const TI*>(x), w, ws, static_cast<const __nv_bfloat16*>(z), rstd, dres, static_cast<TI*>(dx),
+      static_cast<__nv_bfloat16*>(dz), dw, rows, d, scale);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 template <typename TI, typename TG, int GATE>
 static int norm_bwd_t(const void* dy, const void* x, const float* w, int ws, const void* z, const float* rstd, const float* dres, void* dx,
                       void* dz, float* dw, long rows, int d, float scale, int sms, cudaStream_t st) {
-  const int warps = 8;
-  long want = (rows + warps - 1) / warps;
-  dim3 grid(static_cast<unsigned>(want < sms * 4 ? want : sms * 4)), block(warps * 32);
-  const size_t sh = d * sizeof(float);
-#define GHB_LAUNCH(IT) rmsnorm_bwd_kernel<TI, TG, IT, GATE><<<grid, block, sh, st>>>(static_cast<const TG*>(dy), static_cast<const TI*>(x), w, ws, static_cast<const __nv_bfloat16*>(z), rstd, dres, static_cast<TI*>(dx), static_cast<__nv_bfloat16*>(dz), dw, rows, d, scale)
-  if (d <= 128) GHB_LAUNCH(1); else if (d <= 256) GHB_LAUNCH(2); else if (d <= 512) GHB_LAUNCH(4); else if (d <= 1024) GHB_LAUNCH(8);
-  else if (d <= 2048) GHB_LAUNCH(16); else return 1;
+#define GHB_LAUNCH(IT, WPR) return norm_bwd_launch<TI, TG, IT, WPR, GATE>(dy, x, w, ws, z, rstd, dres, dx, dz, dw, rows, d, scale, sms, st)
+  if (d <= 128) GHB_LAUNCH(1, 1);
+  if (d <= 256) GHB_LAUNCH(2, 1);
+  if (d <= 512) GHB_LAUNCH(4, 1);
+  if (d <= 1024) GHB_LAUNCH(4, 2);
+  if (d <= 2048) GHB_LAUNCH(4, 4);
 #undef GHB_LAUNCH
-  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+  return 1;
 }
 
 // x_bf16: dtype of x and dx; dy_bf16: dtype of dy. dw must be zeroed (or hold a running sum) by the caller.

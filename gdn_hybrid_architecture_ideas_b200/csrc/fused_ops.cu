@@ -76,41 +76,15 @@ __global__ void gdn_prep_fwd_kernel(const __nv_bfloat16* __restrict__ u, const i
   st4(out + row * C + c, a);
 }
 
-// Backward part 1: gradient w.r.t. the conv output (pre-SiLU), dconv (rows, C) bf16, recomputing the forward values.
-__global__ void gdn_prep_bwd_conv_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
-                                         const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dconv, long rows, int L,
-                                         int C, int nq, float qscale) {
-  const int lane = threadIdx.x & 31;
-  const int groups = C / 128;
-  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= rows * groups) return;
-  const long row = unit / groups; const int grp = static_cast<int>(unit % groups);
-  const int t = static_cast<int>(row % L), c = grp * 128 + lane * 4;
-  float pre[4], a[4], dy[4], da[4];
-  conv_taps(u, doc, row, t, C, c, w, pre);
-  ld4(dout + row * C + c, dy);
-#pragma unroll
-  for (int e = 0; e < 4; ++e) a[e] = pre[e] * sigm(pre[e]);
-  if (c < 2 * nq) {
-    const float ss = wsum(a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3]);
-    const float r = rsqrtf(ss + 1e-6f), s = c < nq ? qscale : 1.f;
-    const float ady = wsum(a[0] * dy[0] + a[1] * dy[1] + a[2] * dy[2] + a[3] * dy[3]);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) da[e] = s * r * (dy[e] - a[e] * r * r * ady);
-  } else {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) da[e] = dy[e];
-  }
-#pragma unroll
-  for (int e = 0; e < 4; ++e) { const float sg = sigm(pre[e]); da[e] *= sg * (1.f + pre[e] * (1.f - sg)); }
-  st4(dconv + row * C + c, da);
-}
-
-// Backward part 2: du[t] = sum_j dconv[t + j] w[K-1-j] over later tokens of the same document, and the conv-weight
-// gradient dw[c][K-1-j] += sum_t dconv[t] u[t - j]. One warp walks TOK consecutive tokens of one 128-channel group.
-__global__ void gdn_prep_bwd_input_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
-                                          const __nv_bfloat16* __restrict__ dconv, __nv_bfloat16* __restrict__ du, float* __restrict__ dw,
-                                          long rows, int L, int C, int tok_per_warp) {
+// Backward, one pass: a warp walks TOK consecutive tokens of one 128-channel group (4 channels per lane). At token s it
+// recomputes the conv output from a register window of the last K inputs, forms dconv[s] (through the L2 norm and
+// SiLU) and adds dconv[s] u[s - j] into its conv-weight partial; K - 1 tokens later du[s - (K-1)] =
+// sum_j dconv[s - (K-1) + j] w[K-1-j] leaves from a register window of the last K dconv rows. The K - 1 tokens after
+// the warp's range are recomputed (they belong to the next warp) so no dconv tensor ever reaches memory. Loads run
+// one token ahead of the arithmetic.
+__global__ void gdn_prep_bwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                    const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ du, float* __restrict__ dw,
+                                    long rows, int L, int C, int nq, float qscale, int tok_per_warp) {
   const int lane = threadIdx.x & 31;
   const int groups = C / 128;
   const long chunks = (rows + tok_per_warp - 1) / tok_per_warp;
@@ -127,20 +101,83 @@ __global__ void gdn_prep_bwd_input_kernel(const __nv_bfloat16* __restrict__ u, c
     for (int j = 0; j < PREP_K; ++j) acc[e][j] = 0.f;
   }
   const long r0 = chunk * tok_per_warp, r1 = min(rows, r0 + tok_per_warp);
-  for (long row = r0; row < r1; ++row) {
-    const int t = static_cast<int>(row % L);
-    const int my_doc = doc ? doc[row] : 0;
-    float x[4], g[4] = {0.f, 0.f, 0.f, 0.f};
-    ld4(u + row * C + c, x);
+  float uw[PREP_K][4], dc[PREP_K][4];     // uw[j] = u[s - j], dc[j] = dconv[s - j] at step s
+  int dd[PREP_K];                          // document ids of tokens s - j
 #pragma unroll
-    for (int j = 0; j < PREP_K; ++j) {   // token row + j reads this token through tap j
-      if (t + j >= L) break;
-      if (doc && doc[row + j] != my_doc) break;
-      float d[4]; ld4(dconv + (row + j) * C + c, d);
+  for (int j = 0; j < PREP_K; ++j) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { g[e] += d[e] * wt[e][PREP_K - 1 - j]; acc[e][PREP_K - 1 - j] += d[e] * x[e]; }
+    for (int e = 0; e < 4; ++e) { uw[j][e] = 0.f; dc[j][e] = 0.f; }
+    dd[j] = -1;
+  }
+#pragma unroll
+  for (int j = 1; j < PREP_K; ++j) {       // the window before the first token (entries of another row are never used)
+    if (r0 - (j - 1) - 1 >= 0) { ld4(u + (r0 - j) * C + c, uw[j - 1]); dd[j - 1] = doc ? doc[r0 - j] : 0; }
+  }
+  float nu[4] = {0.f, 0.f, 0.f, 0.f}, ndy[4] = {0.f, 0.f, 0.f, 0.f};
+  int ndoc = 0;
+  if (r0 < rows) { ld4(u + r0 * C + c, nu); ld4(dout + r0 * C + c, ndy); ndoc = doc ? doc[r0] : 0; }
+  const float s_norm = c < nq ? qscale : 1.f;
+  const bool normed = c < 2 * nq;
+  for (long s = r0; s < r1 + (PREP_K - 1); ++s) {
+#pragma unroll
+    for (int j = PREP_K - 1; j > 0; --j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { uw[j][e] = uw[j - 1][e]; dc[j][e] = dc[j - 1][e]; }
+      dd[j] = dd[j - 1];
     }
-    st4(du + row * C + c, g);
+    float dy[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { uw[0][e] = nu[e]; dy[e] = ndy[e]; dc[0][e] = 0.f; }
+    dd[0] = ndoc;
+    const bool in = s < rows;
+    if (s + 1 < rows && s + 1 < r1 + (PREP_K - 1)) { ld4(u + (s + 1) * C + c, nu); ld4(dout + (s + 1) * C + c, ndy); ndoc = doc ? doc[s + 1] : 0; }
+    if (in) {
+      const int t = static_cast<int>(s % L);
+      float pre[4] = {0.f, 0.f, 0.f, 0.f}, a[4], da[4];
+      int taps = 0;                         // valid taps of token s: the same count gates the weight-gradient terms
+#pragma unroll
+      for (int j = 0; j < PREP_K; ++j) {
+        if (t - j < 0 || (doc && dd[j] != dd[0])) break;
+        ++taps;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) pre[e] += uw[j][e] * wt[e][PREP_K - 1 - j];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] = pre[e] * sigm(pre[e]);
+      if (normed) {
+        const float ss = wsum(a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3]);
+        const float r = rsqrtf(ss + 1e-6f);
+        const float ady = wsum(a[0] * dy[0] + a[1] * dy[1] + a[2] * dy[2] + a[3] * dy[3]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) da[e] = s_norm * r * (dy[e] - a[e] * r * r * ady);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) da[e] = dy[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float sg = sigm(pre[e]); dc[0][e] = da[e] * sg * (1.f + pre[e] * (1.f - sg)); }
+      if (s < r1) {
+#pragma unroll
+        for (int j = 0; j < PREP_K; ++j) {
+          if (j < taps) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e][PREP_K - 1 - j] += dc[0][e] * uw[j][e];
+          }
+        }
+      }
+    }
+    const long tr = s - (PREP_K - 1);       // the token whose last reader (tap K-1) was just formed
+    if (tr >= r0 && tr < r1) {
+      const int tt = static_cast<int>(tr % L);
+      float g[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < PREP_K; ++j) {     // token tr + j reads tr through tap j
+        if (tt + j >= L || tr + j >= rows || (doc && dd[PREP_K - 1 - j] != dd[PREP_K - 1])) break;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) g[e] += dc[PREP_K - 1 - j][e] * wt[e][PREP_K - 1 - j];
+      }
+      st4(du + tr * C + c, g);
+    }
   }
 #pragma unroll
   for (int e = 0; e < 4; ++e)
@@ -154,16 +191,13 @@ int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long 
   gdn_prep_fwd_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<__nv_bfloat16*>(out), rows, L, C, nq, qscale);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
-int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* dconv, void* du, float* dw, long rows, int L, int C,
+int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* du, float* dw, long rows, int L, int C,
                  int nq, float qscale, cudaStream_t st) {
   if (C % 128 || nq % 128) return 1;
-  const long units = rows * (C / 128);
-  gdn_prep_bwd_conv_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dout),
-                                                                                  static_cast<__nv_bfloat16*>(dconv), rows, L, C, nq, qscale);
   const int tok = 64;
-  const long units2 = ((rows + tok - 1) / tok) * (C / 128);
-  gdn_prep_bwd_input_kernel<<<static_cast<unsigned>((units2 + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dconv),
-                                                                                    static_cast<__nv_bfloat16*>(du), dw, rows, L, C, tok);
+  const long units = ((rows + tok - 1) / tok) * (C / 128);
+  gdn_prep_bwd_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dout),
+                                                                            static_cast<__nv_bfloat16*>(du), dw, rows, L, C, nq, qscale, tok);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

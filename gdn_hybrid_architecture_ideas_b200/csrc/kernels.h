@@ -31,7 +31,7 @@ int sumsq_partials(const float* x, long n, float* partial, int blocks, cudaStrea
 int cast_bf16(const float* x, void* y, long n, int sms, cudaStream_t st);
 
 int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long rows, int L, int C, int nq, float qscale, cudaStream_t st);
-int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* dconv, void* du, float* dw, long rows, int L, int C,
+int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* du, float* dw, long rows, int L, int C,
                  int nq, float qscale, cudaStream_t st);
 int depth_mix_fwd(const float* const* src, int n, const float* ueff, float* out, float* alpha, float* rnorm, long rows, int d, float eps,
                   cudaStream_t st);

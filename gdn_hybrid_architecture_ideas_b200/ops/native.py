@@ -365,10 +365,10 @@ class _GdnPrep(torch.autograd.Function):
     def backward(ctx, dout):
         u, doc32, w = ctx.saved_tensors
         L, nq, qscale, dt = ctx.meta
-        dconv, du = torch.empty_like(u), torch.empty_like(u)
+        du = torch.empty_like(u)
         dw = torch.zeros_like(w)
-        ext().gdn_prep_bwd(u, doc32, w, _bf16(dout).contiguous(), dconv, du, dw, L, nq, qscale)
-        _count(2)
+        ext().gdn_prep_bwd(u, doc32, w, _bf16(dout).contiguous(), du, dw, L, nq, qscale)
+        _count()
         return (du if dt == BF16 else du.to(dt)), None, dw, None, None, None
 
 
