@@ -35,6 +35,9 @@ from .optim import build_optimizer, grad_norm
 EXIT_DIVERGED = 86
 
 
+from . import periodic_eval
+
+
 class Diverged(RuntimeError):
     pass
 
@@ -250,6 +253,10 @@ class Trainer:
                     if cfg.log_every and (m["step"] % cfg.log_every == 0 or self.step == end):
                         print(f"step {m['step']:6d} loss {m['loss']:.4f} lr {m['lr']:.2e} gnorm {m['grad_norm']:.3f} "
                               f"{m['tokens_per_s']:.0f} tok/s", flush=True)
+                if periodic_eval.due(cfg, self.step):
+                    scores = periodic_eval.run_eval_sets(self)
+                    if self.lead:
+                        self._jsonl({"event": "eval", "step": self.step, **{f"eval/{k}/bpb": v["bpb"] for k, v in scores.items()}})
                 due = self._ckpt_due(end)
                 stop = self._stop
                 if self.dp is not None:

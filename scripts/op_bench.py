@@ -2,7 +2,8 @@
 
     python scripts/op_bench.py attention --B 2 --L 4096 --cap 1024
     python scripts/op_bench.py gdn --B 2 --L 4096
-    python scripts/op_bench.py gemm --M 65536 --N 1024 --K 1024
+    python scripts/op_bench.py gdn_prep --B 2 --L 4096
+    python scripts/op_bench.py gemm --M 65536 --N 1024 --K 1024 --layout nt
     python scripts/op_bench.py rmsnorm --rows 65536 --d 1024
 
 Prints one JSON line per op with milliseconds per call and the achieved rate against the op's algorithmic FLOPs or
@@ -101,13 +102,49 @@ def bench_gdn(a):
 
 
 def bench_gemm(a):
+    """--layout nt: y = x W^T (forward); nn: dx = dy W (W stored [K, N]); tn: dW = dy^T x (both stored [K, *], fp32 out)."""
     M, N, K = a.M, a.N, a.K
-    x = torch.randn(M, K, device="cuda").to(BF16)
-    w = torch.randn(N, K, device="cuda").to(BF16)
-    ms = timed(lambda: native.gemm(x, w), a.iters, a.warmup)
-    ms_lib = timed(lambda: torch.matmul(x, w.t()), a.iters, a.warmup)
+    if a.layout == "nt":
+        x = torch.randn(M, K, device="cuda").to(BF16)
+        w = torch.randn(N, K, device="cuda").to(BF16)
+        ours, lib = (lambda: native.gemm(x, w)), (lambda: torch.matmul(x, w.t()))
+    elif a.layout == "nn":
+        x = torch.randn(M, K, device="cuda").to(BF16)
+        w = torch.randn(K, N, device="cuda").to(BF16)
+        ours, lib = (lambda: native.gemm(x, w, b_mn=True)), (lambda: torch.matmul(x, w))
+    else:
+        x = torch.randn(K, M, device="cuda").to(BF16)
+        w = torch.randn(K, N, device="cuda").to(BF16)
+        out = torch.empty(M, N, device="cuda")
+        ours, lib = (lambda: native.gemm(x, w, out=out, a_mn=True, b_mn=True)), (lambda: torch.matmul(x.t(), w))
+    ms = timed(ours, a.iters, a.warmup)
+    ms_lib = timed(lib, a.iters, a.warmup)
     fl = 2.0 * M * N * K
-    return {"op": "gemm", "M": M, "N": N, "K": K, "ms": ms, "tflops": fl / ms / 1e9, "cublas_ms": ms_lib, "cublas_tflops": fl / ms_lib / 1e9}
+    return {"op": "gemm", "layout": a.layout, "M": M, "N": N, "K": K, "ms": ms, "tflops": fl / ms / 1e9, "cublas_ms": ms_lib,
+            "cublas_tflops": fl / ms_lib / 1e9}
+
+
+def bench_gdn_prep(a):
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    B, L, hk, hv, dk, dv = a.B, a.L, a.H, a.H, 128, a.dv
+    C = 2 * hk * dk + hv * dv
+    u = torch.randn(B, L, C, device="cuda").to(BF16).requires_grad_()
+    w = (torch.rand(C, 4, device="cuda") - 0.5).requires_grad_()
+    doc = torch.zeros(B, L, dtype=torch.long, device="cuda")
+    out = {}
+
+    def fwd():
+        out["y"] = ops.gdn_prep(u, doc, w, hk, hv, dk, dv, single_doc=True, packed=True)[0]
+
+    ms_f = timed(fwd, a.iters, a.warmup)
+    dy = torch.randn_like(out["y"])
+
+    def bwd():
+        out["y"].backward(dy, retain_graph=True)
+
+    ms_b = timed(bwd, a.iters, a.warmup)
+    n = B * L * C
+    return {"op": "gdn_prep", "B": B, "L": L, "C": C, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_gbs": n * 4 / ms_f / 1e6, "bwd_gbs": n * 6 / ms_b / 1e6}
 
 
 def bench_rmsnorm(a):
@@ -132,7 +169,8 @@ def bench_rmsnorm(a):
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("op", choices=["attention", "gdn", "gemm", "rmsnorm"])
+    p.add_argument("op", choices=["attention", "gdn", "gdn_prep", "gemm", "rmsnorm"])
+    p.add_argument("--layout", choices=["nt", "nn", "tn"], default="nt")
     p.add_argument("--iters", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--B", type=int, default=2)
@@ -149,7 +187,7 @@ def main():
     p.add_argument("--rows", type=int, default=65536)
     p.add_argument("--d", type=int, default=1024)
     a = p.parse_args()
-    res = {"attention": bench_attention, "gdn": bench_gdn, "gemm": bench_gemm, "rmsnorm": bench_rmsnorm}[a.op](a)
+    res = {"attention": bench_attention, "gdn": bench_gdn, "gdn_prep": bench_gdn_prep, "gemm": bench_gemm, "rmsnorm": bench_rmsnorm}[a.op](a)
     print(json.dumps(res))
 
 

@@ -1,0 +1,238 @@
+"""CPU tests of the evaluation package, the accounting helpers and the small training-runtime modules."""
+
+import json
+import math
+
+import pytest
+import torch
+
+from gdn_hybrid_architecture_ideas_b200 import config as C
+from gdn_hybrid_architecture_ideas_b200.models import build_model
+
+
+def _tiny():
+    torch.manual_seed(0)
+    return build_model(C.tiny_full_config()).eval()
+
+
+def test_criterion_rule():
+    from gdn_hybrid_architecture_ideas_b200.utils.criterion import Rule, Tally, nan_max
+
+    r = Rule(4.0, 1e-6)
+    assert r.passes(3e-3, 1e-3) and not r.passes(5e-3, 1e-3)
+    assert r.read("x", 5e-7, 0.0).only_floor and r.read("x", 0.0, 0.0).by_ratio
+    assert not r.passes(float("nan"), 1.0) and not r.passes(1.0, float("nan"))
+    assert Rule(2.0, 1e-6, form="max").bound(1e-9) == 1e-6
+    assert math.isnan(nan_max([1.0, float("nan"), 0.5]))
+    t = Tally()
+    t.add(r.read("a", 1e-3, 1e-3)); t.add(r.read("b", 1.0, 1e-3))
+    assert (t.passed, t.failed, t.ok) == (1, 1, False)
+
+
+def test_params_and_flops():
+    from gdn_hybrid_architecture_ideas_b200.utils import params
+
+    cfg = C.tiny_full_config()
+    meta = params.build_on_meta(cfg)
+    real = build_model(cfg)
+    groups = params.parameter_breakdown(meta)
+    assert groups["total"] == sum(p.numel() for p in real.parameters())
+    assert groups["embeddings"] + groups["non-embedding"] == groups["total"]
+    f = params.flops_per_token(cfg, 128)
+    assert f["training"] > 3 * f["prefill_context"] > 0 and f["decode_generated"] > f["prefill_context"]
+
+
+def test_shape_schedule_matches_walk():
+    from gdn_hybrid_architecture_ideas_b200.train.shape_schedule import ShapeSchedule, reference_walk
+
+    phases = [(0.25, 4, 64), (0.5, 8, 128)]
+    sch = ShapeSchedule(phases, steps=8, batch_rows=16, seq_len=128, micro_rows=4)
+    walk = reference_walk(phases, 8, 16, 128)
+    assert sch.total_steps == len(walk)
+    for k, (rows, length, first_token) in enumerate(walk):
+        s = sch.at(k)
+        assert (s.rows, s.seq_len) == (rows, length) and s.first_row * length == first_token
+        assert abs(s.clock * 16 * 128 - first_token) < 1e-6
+    assert sch.at(sch.total_steps - 1).rows == 16
+    rows_mode = ShapeSchedule(phases, 8, 16, 128, lr_mode="rows")
+    assert rows_mode.at(0).lr_scale == 1.0 / rows_mode.phases[0].per_ref
+    with pytest.raises(ValueError):
+        ShapeSchedule([(0.5, 3, 100)], 8, 16, 128)
+
+
+def test_loss_forms_agree():
+    from gdn_hybrid_architecture_ideas_b200.train.chunked_loss import head_positions, token_ce
+    from gdn_hybrid_architecture_ideas_b200.train.loss import lm_loss
+
+    torch.manual_seed(1)
+    h = torch.randn(2, 50, 16, requires_grad=True)
+    w = torch.randn(40, 16, requires_grad=True)
+    t = torch.randint(0, 40, (2, 50))
+    valid = torch.rand(2, 50) > 0.3
+    loss, ce, z, n = lm_loss(h @ w.t(), t, valid, z_loss=1e-3)
+    ce2, z2, n2 = token_ce(h, w, t, valid, 1e-3, chunk=32)
+    assert torch.allclose(ce, ce2, rtol=1e-5) and torch.allclose(z, z2, rtol=1e-5) and n == n2
+    idx, wt = head_positions(valid, 32)
+    assert idx.numel() % 32 == 0 and int(wt.sum()) == int(valid.sum())
+    g1 = torch.autograd.grad(ce, h, retain_graph=True)[0]
+    g2 = torch.autograd.grad(ce2, h)[0]
+    assert torch.allclose(g1, g2, atol=1e-5)
+
+
+def test_freeze_trunk_and_zero_wgrad():
+    from gdn_hybrid_architecture_ideas_b200.train.freeze_trunk import TrunkGuard
+    from gdn_hybrid_architecture_ideas_b200.train.zero_wgrad import ZeroWgradMonitor
+
+    m = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.Linear(4, 2))
+    guard = TrunkGuard(m, ("1.",))
+    mon = ZeroWgradMonitor(m)
+    m(torch.randn(3, 4)).sum().backward()
+    guard.check_grads(); guard.check_values()
+    guard.check_optimizer(torch.optim.SGD([p for p in m.parameters() if p.requires_grad], lr=0.1))
+    assert set(mon.counts()) == {"1.weight"}
+    with torch.no_grad():
+        m[0].weight.add_(1.0)
+    with pytest.raises(RuntimeError):
+        guard.check_values()
+
+
+def test_position_masks_are_pure_and_causal():
+    from gdn_hybrid_architecture_ideas_b200.train.positions import AnswerSpanRule, PositionSampler, answer_span_mask
+
+    doc = torch.tensor([[0] * 300 + [1] * 212])
+    valid = torch.ones(1, 512, dtype=torch.bool)
+    rule = AnswerSpanRule(min_context=16, gap_mean=20.0, span_min=4, span_max=12)
+    a = answer_span_mask(doc, valid, rule, 3, 7)
+    assert torch.equal(a, answer_span_mask(doc, valid, rule, 3, 7)) and a.any()
+    assert not a[0, :16].any() and not a[0, 300:316].any()
+    # prefix stability: what the row holds after position 200 does not change the mask before it
+    doc2 = torch.tensor([[0] * 200 + [5] * 312])
+    assert torch.equal(a[0, :200], answer_span_mask(doc2, valid, rule, 3, 7)[0, :200])
+    s = PositionSampler("random", seed=1, capacity=40)
+    m = s.mask(doc, valid, 2)
+    assert int(m.sum()) == 40 and torch.equal(m, s.mask(doc, valid, 2)) and not torch.equal(m, s.mask(doc, valid, 3))
+
+
+def test_span_bpb_pack_join_and_se():
+    from gdn_hybrid_architecture_ideas_b200.eval import span_bpb as sb
+
+    model = _tiny()
+    V = model.cfg.vocab_size
+    g = torch.Generator().manual_seed(0)
+    docs = [sb.TokenizedDoc(torch.randint(1, V, (n,), generator=g).tolist(), [2] * n) for n in (9, 30, 17, 40, 5, 200)]
+    rows = sb.build_eval_rows(docs, 64)
+    assert rows.skipped == [5] and rows.tokens.shape[1] == 64
+    full = sb.evaluate(model, rows, batch_size=2)
+    half = [sb.evaluate(model, rows, 2, row_indices=[r for r in range(rows.tokens.shape[0]) if r % 2 == k]) for k in (0, 1)]
+    joined = sb.join_batches(half)
+    assert torch.allclose(full.row_nats, joined.row_nats, rtol=1e-6) and abs(full.bpb - joined.bpb) < 1e-9
+    # a document scores the same alone as packed beside others (document isolation)
+    alone = sb.evaluate(model, sb.build_eval_rows([docs[1]], 64))
+    assert abs(float(alone.doc_nats[0]) - float(full.doc_nats[1])) < 1e-3 * float(alone.doc_nats[0])
+    assert sb.bpb_se(full) > 0
+    assert abs(sb.paired_difference(full, full).diff_bpb) < 1e-12
+
+
+def test_batched_generation_matches_uncached_argmax():
+    from gdn_hybrid_architecture_ideas_b200.eval.generate import full_forward_argmax, generate_greedy, generate_greedy_batched
+
+    model = _tiny()
+    V = model.cfg.vocab_size
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(1, V, (n,), generator=g).tolist() for n in (12, 5, 9)]
+    outs = generate_greedy_batched(model, prompts, 6, prefill_chunk=4, check_every=2)
+    for p, o in zip(prompts, outs):
+        assert len(o) == 6
+        seq = p + o
+        want = full_forward_argmax(model, seq, [len(p) - 1 + i for i in range(6)])
+        assert want == o
+    assert generate_greedy(model, prompts[1], 6) == outs[1]
+    stop = generate_greedy_batched(model, prompts, 6, eos_id=outs[0][2], check_every=1)
+    assert len(stop[0]) <= 3
+
+
+def test_gqa_fold_matches_expanded_read():
+    from gdn_hybrid_architecture_ideas_b200.eval.gqa_fold import attend_capped_folded, attend_folded
+    from gdn_hybrid_architecture_ideas_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    B, L, Hq, Hkv, hd = 2, 10, 4, 2, 8
+    q, qf = torch.randn(B, L, Hq, hd), torch.randn(B, L, Hq, hd)
+    k, kf, v = (torch.randn(B, L, Hkv, hd) for _ in range(3))
+    idx = torch.arange(L)[None].expand(B, L)
+    doc = torch.zeros(B, L, dtype=torch.long)
+    allow = idx[:, :, None] >= idx[:, None, :]
+    want = ref.attention(q, k, v, idx, doc, idx, doc)
+    assert torch.allclose(attend_folded(q, k, v, allow), want, atol=1e-5)
+    cap = 3
+    far = (idx[:, :, None] - idx[:, None, :]) > cap
+    want_c = ref.attention(q, k, v, idx, doc, idx, doc, None, qf, kf, cap)
+    assert torch.allclose(attend_capped_folded(q, qf, k, kf, v, allow, far), want_c, atol=1e-5)
+
+
+def test_long_context_buckets_and_probes_and_choice():
+    from gdn_hybrid_architecture_ideas_b200.eval import long_context as lc, multiple_choice as mc, probes
+
+    model = _tiny()
+    V = model.cfg.vocab_size
+    assert lc.bucket_names((4, 8)) == ["0-4", "4-8", ">8"]
+    pos = torch.arange(12)
+    sums = lc.bucket_sums(torch.ones(12), pos, (4, 8))
+    assert sums.tolist() == [4.0, 4.0, 4.0]
+    ids = torch.randint(1, V, (40,), generator=torch.Generator().manual_seed(1))
+    whole = lc.position_ce(model, ids, chunk=64)
+    parts = lc.position_ce(model, ids, chunk=7)
+    assert torch.allclose(whole, parts, atol=2e-4)
+    res = lc.score_position_bpb(model, [{"ids": ids, "byte_lens": torch.ones(40, dtype=torch.long)}] * 2, edges=(16, 32), chunk=16)
+    assert len(res["table"]) == 3 and res["table"][0]["docs"] == 2
+    ps = [probes.build_probe(kind, V, 48, seed=0, index=i) for i, kind in enumerate(probes.PROBE_KINDS)]
+    for p in ps:
+        assert p.answer_start + p.answer_len == len(p.ids) and min(p.ids) >= 1
+    assert probes.build_probe("needle", V, 48, 0, 0).ids == ps[0].ids
+    out = probes.score_probes(model, ps, batch_size=3)
+    assert out["n"] == 4 and 0.0 <= out["exact"] <= 1.0 and out["ce"] > 0
+    items = [mc.Item([3, 4, 5], [[6, 7], [8], [9, 10, 11]], 1)]
+    assert mc.score_items(model, items, seq_len=32)["n"] == 1
+
+
+def test_gdn_diag_and_units(tmp_path):
+    from gdn_hybrid_architecture_ideas_b200.eval import gdn_diag, units
+
+    model = _tiny()
+    tok = torch.randint(1, model.cfg.vocab_size, (1, 24), generator=torch.Generator().manual_seed(2))
+    recs = gdn_diag.encoder_gdn_diag(model, tok, torch.zeros_like(tok), block=8)
+    assert [r["position"] for r in recs] == [8, 16, 24]
+    layers = recs[-1]["layers"]
+    assert layers and all(v["stable_rank"] >= 1.0 - 1e-4 and "rel_change" in v for v in layers.values())
+    store = units.UnitStore(tmp_path / "u", {"model": "a"})
+    calls = []
+    assert store.run({"set": "x", "rows": [0, 1]}, lambda: calls.append(1) or {"v": 3}) == {"v": 3}
+    assert store.run({"set": "x", "rows": [0, 1]}, lambda: calls.append(1) or {"v": 4}) == {"v": 3} and len(calls) == 1
+    assert units.UnitStore(tmp_path / "u", {"model": "b"}).get({"set": "x", "rows": [0, 1]}) is None
+
+
+def test_periodic_eval_leaves_training_untouched(tmp_path):
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    def run(with_eval):
+        cfg = C.TrainConfig(model=C.tiny_full_config(), data=C.tiny_data_config())
+        cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device = 4, 0, False, "cpu"
+        if with_eval:
+            cfg.eval.sets, cfg.eval.every_steps = {"held": "synthetic:3"}, 2
+        t = Trainer(cfg, tmp_path / ("e" if with_eval else "p"))
+        t.fit()
+        return t
+
+    a, b = run(True), run(False)
+    for (n, p), (_, q) in zip(a.model.named_parameters(), b.model.named_parameters()):
+        assert torch.equal(p, q), n
+    rec = json.loads((tmp_path / "e" / "eval" / "step_2.json").read_text())
+    assert rec["sets"]["held"]["bpb"] > 0 and (tmp_path / "e" / "eval" / "step_4.json").exists()
+
+
+def test_sharded_eval_blocks_cover_rows():
+    from gdn_hybrid_architecture_ideas_b200.train.sharded_eval import batch_block
+
+    for n, bs, w in ((10, 3, 4), (7, 2, 2), (5, 8, 3)):
+        got = sorted(sum((batch_block(n, bs, r, w) for r in range(w)), []))
+        assert got == list(range(n))
