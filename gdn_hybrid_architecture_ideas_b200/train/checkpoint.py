@@ -60,6 +60,27 @@ def load(path: Path, map_location="cpu") -> dict:
     return torch.load(path, map_location=map_location, weights_only=False)
 
 
+def load_model(path, device="cpu", dtype=None):
+    """(model, train config, step) from a checkpoint file or a run directory (its latest checkpoint): the model is built
+    from the checkpoint's own config and takes its weights (evaluation scripts start here)."""
+    from .. import config as C
+    from ..models import build_model
+
+    p = Path(path)
+    if p.is_dir():
+        p = latest_path(p)
+        if p is None:
+            raise FileNotFoundError(f"no checkpoint under {path}")
+    state = load(p)
+    cfg = C.from_dict(C.TrainConfig, C.checkpoint_config(state["config"]))
+    model = build_model(cfg.model)
+    model.load_state_dict(state["model"])
+    model = model.to(device)
+    if dtype is not None:
+        model = model.to(dtype)
+    return model.eval(), cfg, int(state["step"])
+
+
 def _tensors(obj, out: list, prefix=()):
     if isinstance(obj, torch.Tensor):
         out.append((prefix, obj))

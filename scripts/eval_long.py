@@ -1,0 +1,55 @@
+#!/usr/bin/env python
+"""Long-context bits per byte by position bucket, and GDN state diagnostics along the row
+(reference: scripts/eval_long.py).
+
+    python scripts/eval_long.py --checkpoint RUN --docs long.pt --max-len 65536 [--gdn-diag] [--out long.json]
+
+`long.pt` holds {"docs": [{"ids": LongTensor, "byte_lens": LongTensor}, ...]}.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from gdn_hybrid_architecture_ideas_b200.eval import gdn_diag, long_context  # noqa: E402
+from gdn_hybrid_architecture_ideas_b200.train import checkpoint as ckpt  # noqa: E402
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--checkpoint", required=True)
+    ap.add_argument("--docs", required=True)
+    ap.add_argument("--max-len", type=int, default=0)
+    ap.add_argument("--base", type=int, default=long_context.BASE_LEN)
+    ap.add_argument("--chunk", type=int, default=8192)
+    ap.add_argument("--gdn-diag", action="store_true")
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--out")
+    a = ap.parse_args(argv)
+    model, cfg, step = ckpt.load_model(a.checkpoint, a.device)
+    ac = torch.bfloat16 if a.device.startswith("cuda") else None
+    docs = torch.load(a.docs, map_location="cpu", weights_only=False)["docs"]
+    docs = [{"ids": torch.as_tensor(d["ids"]), "byte_lens": torch.as_tensor(d["byte_lens"])} for d in docs]
+    res = long_context.score_position_bpb(model, docs, base=a.base, max_len=a.max_len or None, chunk=a.chunk, autocast_dtype=ac)
+    for line in res["table"]:
+        if line["bpb"] is not None:
+            print(f"{line['bucket']:>12s}: bpb {line['bpb']:.4f} ({line['docs']} documents)")
+    out = {"step": step, "edges": res["edges"], "table": res["table"]}
+    if a.gdn_diag:
+        ids = docs[0]["ids"][: a.max_len or None][None]
+        out["gdn_diag"] = gdn_diag.encoder_gdn_diag(model, ids, torch.zeros_like(ids), block=a.chunk, autocast_dtype=ac)
+    if a.out:
+        with open(a.out, "w") as f:
+            json.dump(out, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,49 @@
+#!/usr/bin/env python
+"""Synthetic recall probes (needle, multikey, copy, two-hop) on a checkpoint, teacher-forced
+(reference: scripts/eval_probes.py).
+
+    python scripts/eval_probes.py --checkpoint RUN --lengths 512,2048,8192 --per-kind 32 [--out probes.json]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from gdn_hybrid_architecture_ideas_b200.eval import probes  # noqa: E402
+from gdn_hybrid_architecture_ideas_b200.train import checkpoint as ckpt  # noqa: E402
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--checkpoint", required=True)
+    ap.add_argument("--lengths", default="512,2048")
+    ap.add_argument("--per-kind", type=int, default=16)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--batch-size", type=int, default=4)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--out")
+    a = ap.parse_args(argv)
+    model, cfg, step = ckpt.load_model(a.checkpoint, a.device)
+    ac = torch.bfloat16 if a.device.startswith("cuda") else None
+    table = {}
+    for length in (int(x) for x in a.lengths.split(",")):
+        for kind in probes.PROBE_KINDS:
+            ps = [probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
+            r = probes.score_probes(model, ps, a.batch_size, ac)
+            table[f"{kind}@{length}"] = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
+            print(f"{kind:9s} length {length:6d}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
+    if a.out:
+        with open(a.out, "w") as f:
+            json.dump({"step": step, "probes": table}, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

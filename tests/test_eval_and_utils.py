@@ -236,3 +236,54 @@ def test_sharded_eval_blocks_cover_rows():
     for n, bs, w in ((10, 3, 4), (7, 2, 2), (5, 8, 3)):
         got = sorted(sum((batch_block(n, bs, r, w) for r in range(w)), []))
         assert got == list(range(n))
+
+
+def test_shipped_configs_and_run_entries_load():
+    """Every shipped config builds (refuse-by-name passes) and every run entry's overrides apply to its base config."""
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root / "scripts"))
+    import run_entry
+
+    configs = sorted((root / "configs").rglob("*.yaml"))
+    assert len(configs) >= 7
+    for p in configs:
+        C.require_supported(C.load_yaml(p))
+    for runs_file in sorted((root / "runs").glob("*.yaml")):
+        runs = run_entry.load_runs(runs_file, "/data", "/tmp/runs")
+        for entry in runs["runs"]:
+            cfg = C.load_yaml(root / entry["config"])
+            for item in entry.get("set", []):
+                C.apply_override(cfg, item)
+            C.require_supported(cfg)
+            assert run_entry.build_command(runs, entry, "/tmp/runs", nproc=2)[1:3] == ["-m", "torch.distributed.run"]
+
+
+def test_eval_scripts_run_on_a_checkpoint(tmp_path):
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    root = Path(__file__).resolve().parent.parent
+    cfg = C.TrainConfig(model=C.tiny_full_config(), data=C.tiny_data_config())
+    cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device = 1, 0, False, "cpu"
+    Trainer(cfg, tmp_path / "run").fit()
+    V = cfg.model.vocab_size
+    g = torch.Generator().manual_seed(0)
+    docs = [{"ids": torch.randint(1, V, (n,), generator=g).tolist(), "byte_lens": [1] * n} for n in (20, 33)]
+    torch.save({"docs": docs}, tmp_path / "set.pt")
+    torch.save({"docs": [{"ids": torch.randint(1, V, (48,), generator=g), "byte_lens": torch.ones(48, dtype=torch.long)}]}, tmp_path / "long.pt")
+    run = lambda *a: subprocess.run([sys.executable, *a], check=True, capture_output=True, text=True, timeout=600)
+    run(str(root / "scripts/rescore.py"), "--checkpoint", str(tmp_path / "run"), "--set", f"x={tmp_path / 'set.pt'}", "--seq-len", "64",
+        "--device", "cpu", "--out", str(tmp_path / "s.json"))
+    assert json.loads((tmp_path / "s.json").read_text())["scores"]["x"]["bpb"] > 0
+    run(str(root / "scripts/eval_probes.py"), "--checkpoint", str(tmp_path / "run"), "--lengths", "40", "--per-kind", "2", "--device", "cpu",
+        "--out", str(tmp_path / "p.json"))
+    assert len(json.loads((tmp_path / "p.json").read_text())["probes"]) == 4
+    run(str(root / "scripts/eval_long.py"), "--checkpoint", str(tmp_path / "run"), "--docs", str(tmp_path / "long.pt"), "--base", "16",
+        "--chunk", "16", "--gdn-diag", "--device", "cpu", "--out", str(tmp_path / "l.json"))
+    assert json.loads((tmp_path / "l.json").read_text())["gdn_diag"]
