@@ -319,6 +319,37 @@ int64_t comm_peers_bytes() { return ghb::comm_peers_bytes(); }
 
 }  // namespace
 
+// ---- tensor-parallel fused GEMMs. args: CPU uint8 tensor holding the kernel's argument table.
+void gemm_tp(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& out, bool a_mn, bool b_mn, bool accumulate, const Tensor& args, Tensor& err) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && is_bf16(a) && is_bf16(b) && a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_tp: bf16 2-D operands");
+  TORCH_CHECK(!args.is_cuda() && args.numel() == static_cast<int64_t>(ghb::tp_args_bytes()), "gemm_tp: argument table size");
+  const c10::cuda::CUDAGuard guard(a.device());
+  const int M = a_mn ? a.size(1) : a.size(0), K = a_mn ? a.size(0) : a.size(1);
+  const int N = b_mn ? b.size(1) : b.size(0), Kb = b_mn ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm_tp: reduction sizes differ");
+  int mode = 0; long ldc = 8; void* c = nullptr;
+  if (out.has_value()) {
+    TORCH_CHECK(out->dim() == 2 && out->size(0) == M && out->size(1) == N && out->stride(1) == 1, "gemm_tp: output shape");
+    mode = is_bf16(*out) ? 0 : (accumulate ? 2 : 1);
+    TORCH_CHECK(mode == 0 || is_f32(*out), "gemm_tp: output bf16 or fp32");
+    ldc = out->stride(0); c = out->data_ptr();
+  }
+  const int rc = ghb::gemm_tp(a.data_ptr(), b.data_ptr(), c, M, N, K, a.stride(0), b.stride(0), ldc, a_mn, b_mn, mode, args.data_ptr(),
+                              err.data_ptr<int>(), sm_count(), stream());
+  TORCH_CHECK(rc == 0, "gemm_tp refused (code ", rc, "): M=", M, " N=", N, " K=", K, " cuerr=", ghb::last_encode_error());
+}
+void tp_rs_reduce(const Tensor& stage, Tensor& out, const Tensor& args, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(stage.device());
+  TORCH_CHECK(is_bf16(stage) && stage.is_contiguous() && out.is_contiguous() && (is_bf16(out) || is_f32(out)), "tp_rs_reduce: layout");
+  check(ghb::tp_rs_reduce(stage.data_ptr(), out.data_ptr(), is_f32(out), out.numel(), args.data_ptr(), err.data_ptr<int>(), sm_count(), stream()), "tp_rs_reduce");
+}
+void tp_signal(const Tensor& args, int64_t word, const Tensor& like) {
+  const c10::cuda::CUDAGuard guard(like.device());
+  check(ghb::tp_signal(args.data_ptr(), word, stream()), "tp_signal");
+}
+int64_t tp_args_bytes() { return ghb::tp_args_bytes(); }
+int64_t tp_pad_words() { return ghb::tp_pad_words(); }
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
@@ -344,6 +375,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gdn_local_bwd", &gdn_local_bwd);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);
   m.def("gdn_scan_bwd", &gdn_scan_bwd);
+  m.def("gemm_tp", &gemm_tp);
+  m.def("tp_rs_reduce", &tp_rs_reduce);
+  m.def("tp_signal", &tp_signal);
+  m.def("tp_args_bytes", &tp_args_bytes);
+  m.def("tp_pad_words", &tp_pad_words);
   m.def("attention_fwd", &attention_fwd);
   m.def("attention_bwd", &attention_bwd);
 }

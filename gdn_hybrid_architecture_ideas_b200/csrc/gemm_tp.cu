@@ -1,0 +1,440 @@
+// Tensor-parallel GEMMs fused with their sequence-parallel collectives over NVLink peer memory.
+//
+//   AG (all-gather -> GEMM): one operand is the concatenation over ranks of token shards ("gathered" buffer, rows
+//     [r Ts, (r+1) Ts) owned by rank r). A few CTAs of the launch push this rank's shard into every peer's gathered
+//     buffer with plain 16-byte peer stores, 128 rows at a time, and raise one flag per 128-row chunk on the
+//     destination; the GEMM CTAs of the same launch walk their tiles starting at the local shard and, before the TMA
+//     loads of a tile whose chunk came from a peer, wait (bounded) for that chunk's flag. The transfer of shard r + 2
+//     thus overlaps the math on shard r + 1. The gathered operand can be the row operand (forward, dgrad: chunks
+//     index the M tiles) or lie along the reduction (wgrad: chunks index the k-blocks).
+//   RS (GEMM -> reduce-scatter): the product is a partial sum over ranks whose rows are owned rank by rank. The
+//     epilogue stores each tile (bf16) straight into the owner's staging buffer, slot = this rank, starting with the
+//     next rank's rows so that at any time the ranks write to different owners; the last CTA to finish raises this
+//     rank's "landed" flag on every peer. `tp_rs_reduce` on the owner waits (bounded) for all ranks' flags and sums
+//     the slots in fp32: a deterministic reduction with bf16 on the wire.
+//
+// Buffers are reused in rings; a writer never overwrites a slot before its readers are done: readers publish
+// "released up to call n" counters (`tp_signal`, the tail of `tp_rs_reduce`) and writers wait (bounded) for them.
+// All flags are call sequence numbers written with system-scope release stores and read with acquire loads; a wait
+// that runs out writes a status code and the kernel drains and returns. No TMA load here uses cluster multicast.
+// The reference has no tensor parallelism; its sequence of NCCL calls for the same math would be all_gather_into_tensor
+// + matmul and matmul + reduce_scatter_tensor.
+#include "kernels.h"
+#include "sm100.cuh"
+#include <cstring>
+
+namespace ghb {
+using namespace sm100;
+
+namespace tp {
+constexpr int BM = 128, BK = 64, UK = 16, BN = 256;
+constexpr int THREADS = 192;
+constexpr int STAGES = 4;
+constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
+constexpr uint32_t TMEM_COLS = 2 * BN;
+constexpr int MAXR = 8;
+constexpr unsigned long long WAIT_NS = 2000000000ull;
+constexpr int CHUNK = 128;           // rows per gather chunk = BM
+
+// Pad layout (uint32 words) of each rank's symmetric signal pad.
+constexpr int PAD_AG_DONE = 0;       // [MAXR]  AG_DONE[j]: rank j has released every gather slot use <= value
+constexpr int PAD_RS_READY = 8;      // [MAXR]  RS_READY[j]: rank j's partial tiles of call <= value have landed here
+constexpr int PAD_RS_DONE = 16;      // [MAXR]  RS_DONE[j]: rank j has reduced every staging slot use <= value
+constexpr int PAD_WORDS = 32;
+
+struct Args {
+  // --- gather
+  __nv_bfloat16* xg[MAXR];           // every rank's gathered buffer for this call's slot
+  unsigned int* chunk[MAXR];         // every rank's chunk flags for this slot: [rows / CHUNK]
+  unsigned int* pad[MAXR];           // every rank's signal pad
+  int rank, world;
+  int mode;                          // 0: AG, 1: RS, 2: plain
+  int push;                          // AG: this launch pushes the local shard (first consumer of the gather)
+  int axis;                          // AG: 0 = gathered rows are A's rows (M tiles); 1 = gathered rows lie along K
+  long shard_rows;                   // Ts
+  long row_elems;                    // elements per gathered row
+  long ld;                           // row stride (elements) of the gathered buffers
+  unsigned int seq;                  // sequence number of the gather (AG) or of the scatter (RS)
+  unsigned int need;                 // peers must have released uses <= need of the slot before it is overwritten
+  int n_push;                        // CTAs [0, n_push) push, the rest multiply
+  // --- scatter
+  __nv_bfloat16* stage[MAXR];        // every rank's staging buffer for this call's slot: [world][Ts][N]
+  unsigned int* done_counter;        // local, zero between launches
+};
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int seq) {
+  if (static_cast<int>(ld_acquire_sys(p) - seq) >= 0) return true;
+  const unsigned long long t0 = now_ns();
+  while (static_cast<int>(ld_acquire_sys(p) - seq) < 0) {
+    if (now_ns() - t0 > WAIT_NS) return false;
+    __nanosleep(100);
+  }
+  return true;
+}
+}  // namespace tp
+
+// out: 0 bf16, 1 fp32, 2 fp32 accumulate (modes AG and plain); RS writes bf16 staging tiles.
+template <bool A_MN, bool B_MN, int OUT>
+__global__ void __launch_bounds__(tp::THREADS, 1)
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, void* __restrict__ Cout,
+               long ldc, int M, int N, int K, const __grid_constant__ tp::Args a, int* __restrict__ err) {
+  using namespace tp;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
+
+  // ------------------------------------------------------------------ push CTAs (AG): local shard -> every peer
+  if (a.mode == 0 && static_cast<int>(blockIdx.x) < a.n_push) {
+    if (!a.push) return;
+    __shared__ int go;
+    const long chunks_per_shard = a.shard_rows / CHUNK;
+    const long vec_per_row = a.row_elems / 8;                 // 16-byte vectors
+    const __nv_bfloat16* src = a.xg[a.rank] + a.rank * a.shard_rows * a.ld;
+    for (int q = 1; q < a.world; ++q) {
+      const int d = (a.rank - q + a.world) % a.world;         // destination d reads shard d + q as its q-th shard
+      if (threadIdx.x == 0) {
+        go = wait_flag(a.pad[a.rank] + PAD_AG_DONE + d, a.need) ? 1 : 0;
+        if (!go) atomicExch(err, 501);
+      }
+      __syncthreads();
+      if (!go) return;
+      __nv_bfloat16* dst = a.xg[d] + a.rank * a.shard_rows * a.ld;
+      for (long c = blockIdx.x; c < chunks_per_shard; c += a.n_push) {
+        const long total = CHUNK * vec_per_row;
+        for (long i = threadIdx.x; i < total; i += blockDim.x) {
+          const long r = c * CHUNK + i / vec_per_row, v = i % vec_per_row;
+          reinterpret_cast<uint4*>(dst + r * a.ld)[v] = reinterpret_cast<const uint4*>(src + r * a.ld)[v];
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          st_release_sys(a.chunk[d] + a.rank * chunks_per_shard + c, a.seq);
+        }
+      }
+      __syncthreads();
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ GEMM CTAs
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+
+  const int first = a.mode == 0 ? a.n_push : 0;
+  const int cta = static_cast<int>(blockIdx.x) - first, n_cta = static_cast<int>(gridDim.x) - first;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN, tiles = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  // ring order: AG starts at the local shard, RS at the next rank's rows (its own rows last)
+  const int tiles_per_shard = a.mode == 2 ? 0 : static_cast<int>(a.shard_rows / BM);
+  const int m_rot = a.mode == 0 ? (a.axis == 0 ? a.rank * tiles_per_shard : 0) : (a.mode == 1 ? ((a.rank + 1) % a.world) * tiles_per_shard : 0);
+  const int kb_rot = (a.mode == 0 && a.axis == 1) ? static_cast<int>(a.rank * (a.shard_rows / BK)) : 0;
+  auto tile_of = [&](int t, int& tm, int& tn) {           // column tiles of one row tile are consecutive: they share its chunk
+    tm = (t / tiles_n + m_rot) % tiles_m;
+    tn = t % tiles_n;
+  };
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0; bool ok = true;
+      const long chunks_per_shard = a.mode == 0 ? a.shard_rows / CHUNK : 1;
+      auto chunk_ready = [&](long chunk) -> bool {        // chunks of the local shard never wait
+        if (chunk / chunks_per_shard == a.rank) return true;
+        if (!wait_flag(a.chunk[a.rank] + chunk, a.seq)) { atomicExch(err, 502); return false; }
+        asm volatile("fence.proxy.async.global;" ::: "memory");   // peer stores (generic proxy) before TMA reads (async proxy)
+        return true;
+      };
+      for (int t = cta; t < tiles && ok; t += n_cta) {
+        int tm, tn; tile_of(t, tm, tn);
+        const int m0 = tm * BM, n0 = tn * BN;
+        if (a.mode == 0 && a.axis == 0 && !chunk_ready(tm)) { ok = false; break; }
+        for (int kk = 0; kk < num_kb; ++kk) {
+          const int kb = (kk + kb_rot) % num_kb;
+          if (a.mode == 0 && a.axis == 1 && (kb & 1) == 0 && !chunk_ready(kb / 2)) { ok = false; break; }
+          if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 503); ok = false; break; }
+          mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+          uint8_t* pa = sA + s * A_BYTES; uint8_t* pb = sB + s * B_BYTES;
+          if (!A_MN) tma_load_2d(pa, &tma_a, &full[s], kb * BK, m0);
+          else for (int j = 0; j < BM / 64; ++j) tma_load_2d(pa + j * (BK * 128), &tma_a, &full[s], m0 + j * 64, kb * BK);
+          if (!B_MN) tma_load_2d(pb, &tma_b, &full[s], kb * BK, n0);
+          else for (int j = 0; j < BN / 64; ++j) tma_load_2d(pb + j * (BK * 128), &tma_b, &full[s], n0 + j * 64, kb * BK);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+      if (!ok) __nanosleep(100000);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int s = 0; uint32_t ph = 0; int it = 0; bool ok = true;
+      for (int t = cta; t < tiles && ok; t += n_cta, ++it) {
+        const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], aph ^ 1)) { atomicExch(err, 504); ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + acc * BN;
+        for (int kk = 0; kk < num_kb; ++kk) {
+          if (!mbar_wait(&full[s], ph)) { atomicExch(err, 505); ok = false; break; }
+          tc_fence_after();
+          const uint32_t pa = smem_u32(sA + s * A_BYTES), pb = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UK; ++k) {
+            const uint64_t da = A_MN ? umma_desc_sw128(pa + k * UK * 128, BK * 128, 1024) : umma_desc_sw128(pa + k * UK * 2, 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(pb + k * UK * 128, BK * 128, 1024) : umma_desc_sw128(pb + k * UK * 2, 16, 1024);
+            umma_bf16(d, da, db, idesc, kk != 0 || k != 0);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    int it = 0; bool ok = true;
+    unsigned int dest_ok = 0;                 // RS: destinations whose staging slot is known to be free
+    for (int t = cta; t < tiles && ok; t += n_cta, ++it) {
+      const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
+      int tm, tn; tile_of(t, tm, tn);
+      if (!mbar_wait(&tfull[acc], aph)) { if (lane == 0) atomicExch(err, 506); ok = false; break; }
+      tc_fence_after();
+      const long row = static_cast<long>(tm) * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      __nv_bfloat16* rs_row = nullptr;
+      if (a.mode == 1) {
+        const int d = static_cast<int>((static_cast<long>(tm) * BM) / a.shard_rows);
+        if (!((dest_ok >> d) & 1u)) {
+          int good = 1;
+          if (lane == 0 && d != a.rank) good = wait_flag(a.pad[a.rank] + PAD_RS_DONE + d, a.need) ? 1 : 0;
+          good = __shfl_sync(0xffffffffu, good, 0);
+          if (!good) { if (lane == 0) atomicExch(err, 507); ok = false; }
+          dest_ok |= 1u << d;
+        }
+        rs_row = a.stage[d] + ((static_cast<long>(a.rank) * a.shard_rows + (row - d * a.shard_rows)) * N);
+      }
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col = n0 + c * 32;
+        if (ok && row < M && col < N) {
+          if (a.mode == 1 || OUT == 0) {
+            __nv_bfloat16* out = a.mode == 1 ? rs_row + col : reinterpret_cast<__nv_bfloat16*>(Cout) + row * ldc + col;
+            if (col + 32 <= N) {
+              uint4* o4 = reinterpret_cast<uint4*>(out);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint32_t p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
+                  p[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                o4[v] = make_uint4(p[0], p[1], p[2], p[3]);
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (col + e < N) out[e] = __float2bfloat16(__uint_as_float(r[e]));
+            }
+          } else {
+            float* out = reinterpret_cast<float*>(Cout) + row * ldc + col;
+            if (col + 32 <= N) {
+              float4* o4 = reinterpret_cast<float4*>(out);
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 x = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (OUT == 2) { float4 y = o4[v]; x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w; }
+                o4[v] = x;
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) if (col + e < N) out[e] = (OUT == 2 ? out[e] : 0.f) + __uint_as_float(r[e]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (a.mode == 1 && threadIdx.x == 0) {      // RS: the last CTA to finish tells every rank that this rank's tiles have landed
+    __threadfence_system();
+    const unsigned int ticket = atomicAdd(a.done_counter, 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence_system();
+      for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_READY + a.rank, a.seq);
+      *a.done_counter = 0u;
+    }
+  }
+}
+
+// out[r][c] = sum_j stage[j][r][c] over the world's slots, after every rank's tiles of call `seq` have landed; then this
+// rank's "reduced" counter is published so writers may reuse the slot. out_f32: fp32 output (else bf16).
+__global__ void tp_rs_reduce_kernel(const __nv_bfloat16* __restrict__ stage, void* __restrict__ out, int out_f32, long n, tp::Args a,
+                                    int* __restrict__ err) {
+  using namespace tp;
+  __shared__ int go;
+  if (threadIdx.x == 0) {
+    go = 1;
+    for (int j = 0; j < a.world && go; ++j) go = wait_flag(a.pad[a.rank] + PAD_RS_READY + j, a.seq) ? 1 : 0;
+    if (!go) atomicExch(err, 508);
+  }
+  __syncthreads();
+  if (go) {
+    const long n8 = n / 8;
+    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
+      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < a.world; ++j) {
+        const uint4 v = reinterpret_cast<const uint4*>(stage + j * n)[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); s[2 * e] += f.x; s[2 * e + 1] += f.y; }
+      }
+      if (out_f32) {
+        float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + i * 8);
+        o[0] = make_float4(s[0], s[1], s[2], s[3]); o[1] = make_float4(s[4], s[5], s[6], s[7]);
+      } else {
+        uint32_t p[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { __nv_bfloat162 h = __floats2bfloat162_rn(s[2 * e], s[2 * e + 1]); p[e] = *reinterpret_cast<uint32_t*>(&h); }
+        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + i * 8)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int ticket = atomicAdd(a.done_counter, 1u);
+    if (ticket == gridDim.x - 1) {
+      if (go) for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_DONE + a.rank, a.seq);
+      *a.done_counter = 0u;
+    }
+  }
+}
+
+// Publishes "this rank has released gather-slot uses <= seq" to every rank (stream-ordered after the slot's readers).
+__global__ void tp_signal_kernel(tp::Args a, int word) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int p = 0; p < a.world; ++p) tp::st_release_sys(a.pad[p] + word + a.rank, a.seq);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static bool tp_encode(CUtensorMap* map, const void* ptr, long rows, long cols, long ld, bool mn_major, int block_mn) {
+  uint64_t dims[2], strides[1];
+  uint32_t box[2];
+  if (!mn_major) { dims[0] = cols; dims[1] = rows; box[0] = tp::BK; box[1] = block_mn; }
+  else { dims[0] = rows; dims[1] = cols; box[0] = 64; box[1] = tp::BK; }
+  strides[0] = static_cast<uint64_t>(ld) * 2;
+  return encode_tensor_map_2d(map, ptr, 2, dims, strides, box, true);
+}
+
+size_t tp_args_bytes() { return sizeof(tp::Args); }
+int tp_pad_words() { return tp::PAD_WORDS; }
+
+template <bool A_MN, bool B_MN, int OUT>
+static int tp_launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long ldc, int M, int N, int K, const tp::Args& a, int* err, int sms,
+                     cudaStream_t st) {
+  auto kern = gemm_tp_kernel<A_MN, B_MN, OUT>;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, tp::SMEM) != cudaSuccess) return 3;
+    attr = true;
+  }
+  const int tiles = ((M + tp::BM - 1) / tp::BM) * ((N + tp::BN - 1) / tp::BN);
+  const int first = a.mode == 0 ? a.n_push : 0;
+  const int grid = first + (tiles < sms - first ? tiles : sms - first);       // every CTA co-resident: one per SM
+  kern<<<grid, tp::THREADS, tp::SMEM, st>>>(ta, tb, C, ldc, M, N, K, a, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// D = A B^T on this rank's operands; `args` is a host copy of tp::Args (tp_args_bytes() bytes). mode AG: the gathered
+// operand is whichever of A (axis 0: its rows; axis 1 with a_gathered) or B (axis 1) lives in args.xg[rank].
+// out: 0 bf16, 1 fp32, 2 fp32 accumulate (ignored in mode RS, whose tiles go to the staging buffers as bf16).
+int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn, int out,
+            const void* args, int* err, int sms, cudaStream_t st) {
+  tp::Args a;
+  memcpy(&a, args, sizeof(a));       // the table arrives in a byte buffer of unknown alignment
+  if (M <= 0 || N <= 0 || K <= 0) return 1;
+  if (lda % 8 || ldb % 8) return 11;
+  if (a.mode != 1 && (ldc % (out == 0 ? 8 : 4))) return 13;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return 14;
+  if (a.world > tp::MAXR || a.world < 1) return 1;
+  if (a.mode != 2) {
+    if (a.shard_rows % tp::CHUNK) return 17;
+    if (a.mode == 0 && (a.row_elems % 8 || a.ld % 8 || a.n_push < 1 || a.n_push >= sms)) return 18;
+    if (a.mode == 0 && a.axis == 0 && static_cast<long>(M) != a.shard_rows * a.world) return 19;
+    if (a.mode == 0 && a.axis == 1 && static_cast<long>(K) != a.shard_rows * a.world) return 19;
+    if (a.mode == 1 && (static_cast<long>(M) != a.shard_rows * a.world || N % 8)) return 19;
+  }
+  CUtensorMap ta, tb;
+  if (!tp_encode(&ta, A, M, K, lda, a_mn, tp::BM)) return 21;
+  if (!tp_encode(&tb, B, N, K, ldb, b_mn, tp::BN)) return 22;
+#define GHB_TP(AM, BMN)                                                                              \
+  switch (a.mode == 1 ? 0 : out) {                                                                   \
+    case 0: return tp_launch<AM, BMN, 0>(ta, tb, C, ldc, M, N, K, a, err, sms, st);                  \
+    case 1: return tp_launch<AM, BMN, 1>(ta, tb, C, ldc, M, N, K, a, err, sms, st);                  \
+    default: return tp_launch<AM, BMN, 2>(ta, tb, C, ldc, M, N, K, a, err, sms, st);                 \
+  }
+  if (!a_mn && !b_mn) { GHB_TP(false, false) }
+  if (!a_mn && b_mn) { GHB_TP(false, true) }
+  if (a_mn && !b_mn) { GHB_TP(true, false) }
+  GHB_TP(true, true)
+#undef GHB_TP
+}
+
+int tp_rs_reduce(const void* stage, void* out, int out_f32, long n, const void* args, int* err, int sms, cudaStream_t st) {
+  if (n % 8) return 1;
+  tp::Args a;
+  memcpy(&a, args, sizeof(a));
+  tp_rs_reduce_kernel<<<sms * 4, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(stage), out, out_f32, n, a, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int tp_signal(const void* args, int word, cudaStream_t st) {
+  tp::Args a;
+  memcpy(&a, args, sizeof(a));
+  tp_signal_kernel<<<1, 32, 0, st>>>(a, word);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+}  // namespace ghb

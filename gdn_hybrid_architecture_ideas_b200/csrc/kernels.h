@@ -78,4 +78,13 @@ int comm_update(const void* peers, int rank, int world, long lo, long n, const f
                 float max_norm, unsigned int seq, float* norm_out, unsigned int* done_counter, int* err, int sms, cudaStream_t st);
 int comm_wait_probe(const unsigned int* flag, unsigned int seq, unsigned long long limit_ns, int* err, cudaStream_t st);
 
+// Tensor-parallel GEMMs fused with the sequence-parallel all-gather / reduce-scatter (csrc/gemm_tp.cu). `args` points at a
+// host copy of the kernel's argument table (tp_args_bytes() bytes; layout in parallel/tensor_parallel.py).
+size_t tp_args_bytes();
+int tp_pad_words();
+int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn, int out,
+            const void* args, int* err, int sms, cudaStream_t st);
+int tp_rs_reduce(const void* stage, void* out, int out_f32, long n, const void* args, int* err, int sms, cudaStream_t st);
+int tp_signal(const void* args, int word, cudaStream_t st);
+
 }  // namespace ghb

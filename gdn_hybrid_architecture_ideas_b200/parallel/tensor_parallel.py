@@ -1,0 +1,284 @@
+"""Tensor parallelism with sequence-parallel norm regions (Megatron-style), for the hybrid stack.
+
+Between the residual stream and a mixer / MLP the tokens are sharded over the ranks ([T / W, d] per rank: norms,
+depth mixes and residual adds cost 1 / W); inside, the heads (GDN heads, attention heads, SwiGLU hidden units) are
+sharded and every rank sees all tokens. The two boundaries are the collectives:
+
+  column-parallel projection   y = all_gather(x) W_r^T          `ag_gemm`: gather fused into the GEMM's main loop
+  row-parallel projection      out = reduce_scatter(h W_r^T)     `gemm_rs`: scatter fused into the GEMM's epilogue
+
+Backward mirrors them (dx = reduce_scatter(dy W_r), dW_r = dy^T all_gather(x); dh = all_gather(dout) W_r,
+dW_r = all_gather(dout)^T h); activations are re-gathered in the backward rather than kept.
+
+Two implementations of the same functions: "fused" (csrc/gemm_tp.cu over symmetric memory: peer stores, flags,
+bounded waits) and "collective" (`torch.distributed` all_gather_into_tensor / reduce_scatter_tensor around a plain
+GEMM: the baseline and the CPU / gloo path). The reference has no tensor parallelism.
+"""
+
+from __future__ import annotations
+
+import os
+import struct
+
+import torch
+import torch.distributed as dist
+
+BF16 = torch.bfloat16
+MAXR = 8
+CHUNK = 128
+N_GATHER_SLOTS = 4
+N_STAGE_SLOTS = 2
+PAD_AG_DONE, PAD_RS_READY, PAD_RS_DONE = 0, 8, 16
+_ARGS_FMT = "<8Q8Q8Q5i4x3q2Ii4x8QQ"
+
+
+class Gathered:
+    """A token-sharded activation placed in a gather slot: `full` is the [T, width] view of this rank's gathered buffer
+    (complete once a consuming GEMM has run); `pushed` turns true when the first consumer has sent the local shard."""
+
+    def __init__(self, slot, seq, need, full, shard_rows, width):
+        self.slot, self.seq, self.need, self.full, self.shard_rows, self.width = slot, seq, need, full, shard_rows, width
+        self.pushed = False
+
+
+class TensorParallel:
+    def __init__(self, dp, max_tokens: int, max_width: int, impl: str | None = None):
+        """dp: the process-group wrapper (rank, world, device, tensor_group). max_tokens: tokens of a micro-batch over
+        all ranks (a multiple of 128 x world); max_width: widest gathered or scattered row (elements)."""
+        self.dp = dp
+        self.rank, self.world, self.device = dp.rank, dp.world, dp.device
+        self.group = dp.tensor_group
+        impl = impl or os.environ.get("GHB_TP_IMPL", "fused" if self.device.type == "cuda" else "collective")
+        self.impl = impl
+        self.max_tokens, self.max_width = max_tokens, max_width
+        self.ag_seq = self.rs_seq = 0
+        self._cache = {}
+        if impl != "fused":
+            return
+        import torch.distributed._symmetric_memory as symm
+
+        from ..ops import native
+
+        if self.world > MAXR or max_tokens % (CHUNK * self.world):
+            raise ValueError(f"tensor parallel: {max_tokens} tokens over {self.world} ranks must be a multiple of {CHUNK} per rank")
+        name = self.group.group_name
+        try:
+            symm.enable_symm_mem_for_group(name)
+        except Exception:
+            pass
+
+        def alloc(count, dtype):
+            t = symm.empty(count, dtype=dtype, device=self.device)
+            t.zero_()
+            return t, symm.rendezvous(t, name)
+
+        n_chunks = max_tokens // CHUNK
+        self.gather_buf, hg = alloc(N_GATHER_SLOTS * max_tokens * max_width, BF16)
+        self.chunk_flags, hc = alloc(N_GATHER_SLOTS * n_chunks, torch.int32)
+        self.stage_buf, hs = alloc(N_STAGE_SLOTS * max_tokens * max_width, BF16)
+        self.pad, hp = alloc(native.ext().tp_pad_words(), torch.int32)
+        self._handles = (hg, hc, hs, hp)
+        self._ptrs = {k: [int(p) for p in h.buffer_ptrs] for k, h in zip("gcsp", self._handles)}
+        self.n_chunks = n_chunks
+        self.slot_seq = [0] * N_GATHER_SLOTS
+        self.next_slot = 0
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", "16"))
+        torch.cuda.synchronize(self.device)
+        dp.barrier()
+
+    # ------------------------------------------------------------------ argument table
+
+    def _args(self, mode, slot=0, seq=0, need=0, push=0, axis=0, shard_rows=0, row_elems=0, ld=8, stage_slot=0):
+        def peers(key, offset_bytes):
+            got = [p + offset_bytes for p in self._ptrs[key]]
+            return got + [0] * (MAXR - len(got))
+
+        g_off = slot * self.max_tokens * self.max_width * 2
+        c_off = slot * self.n_chunks * 4
+        s_off = stage_slot * self.max_tokens * self.max_width * 2
+        raw = struct.pack(_ARGS_FMT, *peers("g", g_off), *peers("c", c_off), *peers("p", 0), self.rank, self.world, mode, push, axis,
+                          shard_rows, row_elems, ld, seq, need, self.n_push, *peers("s", s_off), self.done_counter.data_ptr())
+        return torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+
+    # ------------------------------------------------------------------ gather handles
+
+    def gather(self, x_shard: torch.Tensor) -> Gathered:
+        """x_shard [Ts, width] (bf16 on the fused path). Several GEMMs may consume the same handle; the first one moves
+        the data."""
+        key = (x_shard.data_ptr(), x_shard._version, tuple(x_shard.shape))
+        hit = self._cache.get(key)
+        if hit is not None:
+            return hit
+        Ts, width = x_shard.shape
+        T = Ts * self.world
+        if self.impl != "fused":
+            full = torch.empty(T, width, dtype=x_shard.dtype, device=x_shard.device)
+            dist.all_gather_into_tensor(full, x_shard.contiguous(), group=self.group)
+            g = Gathered(-1, 0, 0, full, Ts, width)
+            g.pushed = True
+        else:
+            from ..ops import native
+
+            if T > self.max_tokens or width > self.max_width or Ts % CHUNK or width % 8:
+                raise ValueError(f"tensor parallel gather of [{Ts}, {width}] exceeds the workspace ({self.max_tokens} x {self.max_width})")
+            slot = self.next_slot
+            self.next_slot = (slot + 1) % N_GATHER_SLOTS
+            prev = self.slot_seq[slot]
+            if prev:       # everything launched so far has read the slot's previous contents: tell the peers it is free
+                native.ext().tp_signal(self._args(2, seq=prev), PAD_AG_DONE, self.pad)
+                self._cache = {k: v for k, v in self._cache.items() if v.slot != slot}
+            self.ag_seq += 1
+            self.slot_seq[slot] = self.ag_seq
+            base = slot * self.max_tokens * self.max_width
+            full = self.gather_buf[base:base + T * width].view(T, width)
+            full[self.rank * Ts:(self.rank + 1) * Ts].copy_(x_shard)
+            g = Gathered(slot, self.ag_seq, prev, full, Ts, width)
+        g.src = x_shard          # keeps the shard's memory alive while the handle is cached: its address cannot be recycled
+        if len(self._cache) > 8:
+            self._cache.clear()
+        self._cache[key] = g
+        return g
+
+    def _ag_args(self, g: Gathered, axis: int):
+        push = 0 if g.pushed else 1
+        g.pushed = True
+        return self._args(0, slot=g.slot, seq=g.seq, need=g.need, push=push, axis=axis, shard_rows=g.shard_rows, row_elems=g.width, ld=g.width)
+
+    # ------------------------------------------------------------------ the four products
+
+    def ag_gemm(self, g: Gathered, w: torch.Tensor, b_mn: bool = False, out_dtype=BF16) -> torch.Tensor:
+        """all_gather(x) w^T ([T, N]); w [N, K], or [K, N] with b_mn."""
+        if self.impl != "fused":
+            return (g.full.float() @ (w.float() if b_mn else w.float().t())).to(out_dtype)
+        from ..ops import native
+
+        N = w.shape[1] if b_mn else w.shape[0]
+        out = torch.empty(g.full.shape[0], N, dtype=out_dtype, device=self.device)
+        native.ext().gemm_tp(g.full, w, out, False, b_mn, False, self._ag_args(g, 0), native.err_flag(self.device))
+        native._count()
+        return out
+
+    def gemm_gathered_k(self, a: torch.Tensor, b: torch.Tensor, g: Gathered, out: torch.Tensor | None = None) -> torch.Tensor:
+        """a^T b over all tokens ([cols(a), cols(b)], fp32), a and b stored [T, *]; one of them is `g.full` (a weight gradient
+        whose token dimension is gathered)."""
+        if self.impl != "fused":
+            res = a.float().t() @ b.float()
+            return res if out is None else out.copy_(res)
+        from ..ops import native
+
+        if out is None:
+            out = torch.empty(a.shape[1], b.shape[1], dtype=torch.float32, device=self.device)
+        native.ext().gemm_tp(a, b, out, True, True, False, self._ag_args(g, 1), native.err_flag(self.device))
+        native._count()
+        return out
+
+    def gemm_rs(self, h: torch.Tensor, w: torch.Tensor, b_mn: bool = False, out_dtype=BF16) -> torch.Tensor:
+        """reduce_scatter(h w^T) over token shards ([T / W, N]); h [T, K_r]; w [N, K_r], or [K_r, N] with b_mn."""
+        T = h.shape[0]
+        N = w.shape[1] if b_mn else w.shape[0]
+        Ts = T // self.world
+        if self.impl != "fused":
+            part = (h.float() @ (w.float() if b_mn else w.float().t()))
+            if h.dtype == BF16:
+                part = part.to(BF16).float()       # the wire format of the fused path
+            out = torch.empty(Ts, N, dtype=torch.float32, device=h.device)
+            dist.reduce_scatter_tensor(out, part.contiguous(), group=self.group)
+            return out.to(out_dtype)
+        from ..ops import native
+
+        if T > self.max_tokens or N > self.max_width or Ts % CHUNK or N % 8:
+            raise ValueError(f"tensor parallel scatter of [{T}, {N}] exceeds the workspace ({self.max_tokens} x {self.max_width})")
+        self.rs_seq += 1
+        seq, slot = self.rs_seq, self.rs_seq % N_STAGE_SLOTS
+        args = self._args(1, seq=seq, need=max(seq - N_STAGE_SLOTS, 0), shard_rows=Ts, stage_slot=slot)
+        err = native.err_flag(self.device)
+        native.ext().gemm_tp(h, w, None, False, b_mn, False, args, err)
+        base = slot * self.max_tokens * self.max_width
+        stage = self.stage_buf[base:base + self.world * Ts * N]
+        out = torch.empty(Ts, N, dtype=out_dtype, device=self.device)
+        native.ext().tp_rs_reduce(stage, out, args, err)
+        native._count(2)
+        return out
+
+    # ------------------------------------------------------------------ replicated parameters
+
+    def all_reduce_grads(self, params) -> None:
+        """Sum over ranks of the gradients of replicated parameters (each rank saw its own token shard)."""
+        grads = [p.grad for p in params if p.grad is not None]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in grads])
+        dist.all_reduce(flat, group=self.group)
+        at = 0
+        for g in grads:
+            g.copy_(flat[at:at + g.numel()].view_as(g))
+            at += g.numel()
+
+
+# ---------------------------------------------------------------------------------------------------- autograd
+
+
+class _ColumnParallel(torch.autograd.Function):
+    """y [T, N_r] = all_gather(x) W_r^T for a token shard x [Ts, K]."""
+
+    @staticmethod
+    def forward(ctx, x, weight, w_lp, tp):
+        x2 = x.reshape(-1, x.shape[-1])
+        n = w_lp.shape[0]
+        if tp.impl == "fused":
+            from ..ops.native import _pad_rows
+            x2, w_lp = x2.to(BF16), _pad_rows(w_lp)       # output rows stay 16-byte aligned for projections with a few outputs
+        y = tp.ag_gemm(tp.gather(x2), w_lp, out_dtype=x2.dtype)
+        ctx.save_for_backward(x2, w_lp)
+        ctx.tp, ctx.xshape, ctx.xdtype, ctx.n = tp, x.shape, x.dtype, n
+        return y[:, :n] if n != w_lp.shape[0] else y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_lp = ctx.saved_tensors
+        tp = ctx.tp
+        dy2 = dy.reshape(-1, dy.shape[-1]).to(x2.dtype)
+        if ctx.n != w_lp.shape[0]:
+            dy2 = torch.nn.functional.pad(dy2, (0, w_lp.shape[0] - ctx.n))
+        dy2 = dy2.contiguous()
+        dx = tp.gemm_rs(dy2, w_lp, b_mn=True, out_dtype=x2.dtype)
+        g = tp.gather(x2)
+        dw = tp.gemm_gathered_k(dy2, g.full, g)[:ctx.n]
+        return dx.view(ctx.xshape).to(ctx.xdtype), dw, None, None
+
+
+class _RowParallel(torch.autograd.Function):
+    """out [Ts, N] = reduce_scatter(h W_r^T) for h [T, K_r] (all tokens, this rank's hidden slice)."""
+
+    @staticmethod
+    def forward(ctx, h, weight, w_lp, tp):
+        h2 = h.reshape(-1, h.shape[-1])
+        if tp.impl == "fused":
+            h2 = h2.to(BF16)
+        h2 = h2.contiguous()
+        out = tp.gemm_rs(h2, w_lp, out_dtype=h2.dtype)
+        ctx.save_for_backward(h2, w_lp)
+        ctx.tp, ctx.hshape, ctx.hdtype = tp, h.shape, h.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        h2, w_lp = ctx.saved_tensors
+        tp = ctx.tp
+        g = tp.gather(dout.reshape(-1, dout.shape[-1]).to(h2.dtype).contiguous())
+        dh = tp.ag_gemm(g, w_lp, b_mn=True, out_dtype=h2.dtype)
+        dw = tp.gemm_gathered_k(g.full, h2, g)
+        return dh.view(ctx.hshape).to(ctx.hdtype), dw, None, None
+
+
+def column_parallel(x, lin, tp):
+    from ..ops.native import _w_lp
+    w_lp = _w_lp(lin) if tp.impl == "fused" else lin.weight.detach()
+    return _ColumnParallel.apply(x, lin.weight, w_lp, tp)
+
+
+def row_parallel(h, lin, tp):
+    from ..ops.native import _w_lp
+    w_lp = _w_lp(lin) if tp.impl == "fused" else lin.weight.detach()
+    return _RowParallel.apply(h, lin.weight, w_lp, tp)

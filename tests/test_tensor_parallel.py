@@ -1,0 +1,40 @@
+"""Tensor / sequence parallel products: the collective implementation equals dense single-process math (gloo ranks on
+the CPU); the fused kernels over symmetric memory equal the collective implementation (GPUs)."""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+NAMES = ("y", "y_small", "dx", "dw", "dw_small", "out", "dh", "dw_row")
+
+
+def _run(out: Path, mode: str, nproc: int, port: int, env=None):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "tp_worker.py"), str(out), mode]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env={**os.environ, **(env or {})})
+    assert r.returncode == 0, r.stderr[-3000:]
+    return [torch.load(f"{out}.{k}", weights_only=False) for k in range(nproc)]
+
+
+def test_collective_products_equal_dense_math(tmp_path):
+    res = _run(tmp_path / "tp", "collective", 2, 29671, {"GHB_DP_BACKEND": "gloo", "OMP_NUM_THREADS": "2", "CUDA_VISIBLE_DEVICES": ""})
+    for rank in res:
+        for name, got, want in zip(NAMES, rank["collective"], rank["dense"]):
+            assert torch.allclose(got, want, atol=1e-4, rtol=1e-4), name
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fused_products_equal_collective(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    res = _run(tmp_path / "tp", "fused", n, 29673)
+    for rank in res:
+        for name, got, want in zip(NAMES, rank["fused"], rank["collective"]):
+            scale = float(want.abs().max()) + 1e-6
+            err = float((got - want).abs().max()) / scale
+            assert err < 3e-2, (name, err)
