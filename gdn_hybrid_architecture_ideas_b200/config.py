@@ -537,6 +537,7 @@ class TrainConfig(_Section):
     cuda_graphs_docs_per_row: int = 64
     wgrad_accum: str = 'autograd'
     optimizer_sharding: str = 'replicated'
+    tensor_parallel: int = 1
     tst: TSTConfig = field(default_factory=TSTConfig)
     stage_shape: str = 'source'
 

@@ -368,14 +368,14 @@ __global__ void __launch_bounds__(512) ce_grad_kernel(const float* __restrict__ 
     sum += __expf(t.x - m) + __expf(t.y - m) + __expf(t.z - m) + __expf(t.w - m);
   }
   const float wm = wmax(m);
-  sum *= __expf(m - wm);
+  sum = (m == -INFINITY) ? 0.f : sum * __expf(m - wm);      // lanes past the row's end (V < 4 x threads) hold no terms
   sum = wsum(sum);
   if ((threadIdx.x & 31) == 0) { redm[threadIdx.x >> 5] = wm; reds[threadIdx.x >> 5] = sum; }
   __syncthreads();
   float gm = -INFINITY, gs = 0.f;
   const int nw = blockDim.x >> 5;
   for (int i = 0; i < nw; ++i) gm = fmaxf(gm, redm[i]);
-  for (int i = 0; i < nw; ++i) gs += reds[i] * __expf(redm[i] - gm);
+  for (int i = 0; i < nw; ++i) if (redm[i] > -INFINITY) gs += reds[i] * __expf(redm[i] - gm);
   const float lse = gm + __logf(gs);
   float asum = 0.f;
   for (int k = 0; k < s; ++k) asum += a[row * s + k];

@@ -173,7 +173,7 @@ class GatedAttention(nn.Module):
     def queries(self, x: torch.Tensor, rot_pos: torch.Tensor, pos: torch.Tensor):
         """(q, q_far or None, gate): normed query rotated at its position, and under the cap also by the cap itself;
         the temperature multiplies both."""
-        B, L, _ = x.shape
+        B, L = pos.shape           # the input may be a token shard (tensor parallel); projections return all tokens
         hq, hd = self.cfg.n_q_heads, self.cfg.head_dim
         gate = None
         if self.cfg.gate == "elementwise":
@@ -208,7 +208,7 @@ class GatedAttention(nn.Module):
 
     def forward(self, x: torch.Tensor, ctx: SeqContext, cache: KeySet | None = None):
         """Causal self-attention over this chunk plus the cached entries. Returns (y, KeySet incl. this chunk)."""
-        B, L, _ = x.shape
+        B, L = ctx.doc.shape
         cfg = self.cfg
         hkv, hd = cfg.n_kv_heads, cfg.head_dim
         scaled = ctx.rope_scale != 1 and self.cap is not None   # token-scale rotary acts on the capped layers only

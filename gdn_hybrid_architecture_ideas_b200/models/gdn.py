@@ -132,7 +132,7 @@ class GatedDeltaNet(nn.Module):
         starts here). need_state False (training) lets the kernel skip the final state."""
         if (arms is None) != (self.write_mix == "none"):
             raise ValueError("a GDN layer with write/query mixes is called with its arms (through its encoder layer)")
-        B, L, _ = x.shape
+        B, L = ctx.doc.shape       # the input may be a token shard (tensor parallel); projections return all tokens
         cfg = self.cfg
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
         u_pre, a_lin, b_lin = self.project(x, arms, x_write, x_read)

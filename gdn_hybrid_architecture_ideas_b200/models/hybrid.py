@@ -53,6 +53,7 @@ class HybridLM(nn.Module):
         self.final_norm = RMSNorm(cfg.d_model, cfg.norm_eps)
         self.out_embed = None if cfg.tie_embeddings else nn.Embedding(cfg.vocab_size, cfg.d_model)
         self.head_weight_lp: torch.Tensor | None = None  # bf16 shadow of the head matrix (set by the engine)
+        self.tp = None      # tensor-parallel context (parallel.tp_model.apply): the stream is then this rank's token shard
         for m in self.modules():
             if isinstance(m, (nn.Linear, nn.Embedding)):
                 nn.init.normal_(m.weight, mean=0.0, std=cfg.init_std)
@@ -84,6 +85,13 @@ class HybridLM(nn.Module):
             ctx.rope_scale, ctx.gdn_scale, ctx.gdn_beta_power = int(rope_scale), int(gdn_scale), bool(gdn_beta_power)
         B, L = tokens.shape[:2]
         need_state = return_cache or cache is not None
+        if self.tp is not None:
+            if need_state:
+                raise ValueError("tensor parallel runs training forwards only (no cache)")
+            tp = self.tp
+            tp.batch_shape = (B, L)
+            per = B * L // tp.world
+            tokens = tokens.reshape(B * L, *tokens.shape[2:])[tp.rank * per:(tp.rank + 1) * per][None]     # this rank's token shard
         h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state)
         hidden = self.final_norm(h)
         logits = None if return_hidden else lm_head(hidden, self.head_weight())

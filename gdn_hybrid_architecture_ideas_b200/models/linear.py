@@ -22,6 +22,8 @@ class Linear(nn.Linear):
         self.weight_lp: torch.Tensor | None = None
         self.precision: str = "bf16"
         self.lowp = None  # recipe state (ops.lowp.Recipe) when precision != "bf16"
+        self.tp = None           # parallel.tensor_parallel.TensorParallel when this projection is sharded over ranks
+        self.tp_mode = None      # "column" (output features sharded, token-sharded input) or "row" (input features sharded)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return ops.linear(x, self)
@@ -49,6 +51,14 @@ class RowView:
     @property
     def precision(self):
         return self.base.precision
+
+    @property
+    def tp(self):
+        return self.base.tp
+
+    @property
+    def tp_mode(self):
+        return self.base.tp_mode
 
     @property
     def lowp(self):

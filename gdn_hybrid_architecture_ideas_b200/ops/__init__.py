@@ -49,7 +49,17 @@ def gated_rmsnorm(x, z, weight, eps, gate, out_dtype=None):
     return ref.gated_rmsnorm(x, z, weight, eps, gate, out_dtype)
 
 
+def _tp_linear(x, lin):
+    from ..parallel import tensor_parallel as tpm
+    tp = lin.tp
+    if lin.tp_mode == "column":
+        return tpm.column_parallel(x, lin, tp).view(*tp.batch_shape, -1)
+    return tpm.row_parallel(x, lin, tp).unsqueeze(0)
+
+
 def linear(x, lin):
+    if getattr(lin, "tp_mode", None) is not None:
+        return _tp_linear(x, lin)
     if use_native(x):
         return _native().linear(x, lin)
     if getattr(lin, "precision", "bf16") != "bf16" and lin.training:
@@ -59,6 +69,8 @@ def linear(x, lin):
 
 def split_linear(xa, xb, lin, n):
     """[lin.rows(0, n)(xa) | lin.rows(n, N)(xb)]: two row ranges of one projection reading two inputs."""
+    if getattr(lin, "tp_mode", None) is not None:
+        return torch.cat([linear(xa, lin.rows(0, n)), linear(xb, lin.rows(n, lin.weight.shape[0]))], dim=-1)
     if use_native(xa):
         return _native().split_linear(xa, xb, lin, n)
     return torch.cat([linear(xa, lin.rows(0, n)), linear(xb, lin.rows(n, lin.weight.shape[0]))], dim=-1)
@@ -72,6 +84,8 @@ def input_mixes(x, y_write, lam_write, y_read=None, lam_read=None):
 
 
 def swiglu_mlp(x, w_gate, w_up, w_down):
+    if getattr(w_gate, "tp_mode", None) is not None:
+        return linear(torch.nn.functional.silu(linear(x, w_gate)) * linear(x, w_up), w_down)
     if use_native(x):
         return _native().swiglu_mlp(x, w_gate, w_up, w_down)
     return linear(torch.nn.functional.silu(linear(x, w_gate)) * linear(x, w_up), w_down)

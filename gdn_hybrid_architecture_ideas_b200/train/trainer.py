@@ -61,7 +61,24 @@ class Trainer:
         if cfg.tf32 and self.device.type == "cuda":
             torch.backends.cuda.matmul.allow_tf32 = True
         dtype = {"float32": torch.float32, "float64": torch.float64, "bfloat16": torch.bfloat16}[cfg.dtype]
-        self.model = build_model(cfg.model).to(dtype).to(self.device)
+        self.tp = None
+        model_cfg = cfg.model
+        if cfg.tensor_parallel > 1:
+            from ..parallel import tp_model
+
+            if dp is None or cfg.tensor_parallel != dp.world:
+                raise ValueError("tensor_parallel must equal the number of ranks (one tensor-parallel group per job)")
+            if cfg.optimizer_sharding != "replicated" or cfg.tst.schedule:
+                raise ValueError("tensor_parallel runs with optimizer_sharding=replicated and without token superposition")
+            model_cfg = tp_model.local_model_config(cfg.model, dp.world)
+        self.model = build_model(model_cfg).to(dtype).to(self.device)
+        if cfg.tensor_parallel > 1:
+            from ..parallel.tensor_parallel import TensorParallel
+
+            tokens = (cfg.micro_batch_size or cfg.data.batch_size) * cfg.data.seq_len
+            width = max(cfg.model.d_model, cfg.model.ffn_hidden // dp.world)
+            self.tp = TensorParallel(dp, tokens, width)
+            tp_model.apply(self.model, self.tp)
         self.model.encoder.activation_checkpoint = cfg.activation_checkpoint
         self.autocast = cfg.autocast == "bfloat16"
         native = self.device.type == "cuda"
@@ -70,7 +87,7 @@ class Trainer:
         self.native = native and ops.mode() == "native"
         lp = torch.bfloat16 if (self.native and self.autocast) else None
         self.sharding = cfg.optimizer_sharding if self.world > 1 else "replicated"
-        if cfg.micro_batch_size is not None and dp is not None:
+        if cfg.micro_batch_size is not None and dp is not None and self.tp is None:
             dp.check(cfg.data.batch_size, cfg.micro_batch_size)
         self.flat, self.optimizer, self.zero = self._build_optimizer(lp)
         self.data = make_data(cfg.data, cfg.model.vocab_size)
@@ -113,7 +130,7 @@ class Trainer:
 
     def batch_at(self, step: int):
         B = self.cfg.data.batch_size
-        first, count = self.dp.rows(B) if self.dp is not None else (0, B)
+        first, count = self.dp.rows(B) if (self.dp is not None and self.tp is None) else (0, B)   # tensor-parallel ranks share the rows
         src_step = step + self.cfg.data_start_step
         if self.tst is not None:
             return self.tst.batch_at(src_step, first, count)
@@ -127,7 +144,7 @@ class Trainer:
         except BatchError as e:
             bad, self._bad = 1, e
         n = int(batch.target_valid.sum()) if batch.multi_valid is None else int(batch.multi_valid.any(-1).sum())
-        if self.dp is not None:
+        if self.dp is not None and self.tp is None:
             n, bad = self.dp.sum_host([n, bad])
         return n, bad
 
@@ -156,6 +173,10 @@ class Trainer:
         else:
             targets = mb.targets
             valid = mb.target_valid.to(torch.float32)
+            if self.tp is not None:        # the hidden states are this rank's token shard: score the same tokens
+                per = targets.numel() // self.tp.world
+                cut = slice(self.tp.rank * per, (self.tp.rank + 1) * per)
+                targets, valid = targets.reshape(-1)[cut][None], valid.reshape(-1)[cut][None]
             a, b = valid / n_global, valid * (z / n_global)
         W = self.model.head_weight()
         if cfg.head_impl == "fused":
@@ -188,6 +209,17 @@ class Trainer:
         stats = torch.stack([loss_sum, ce_sum]).double()
         if self.zero is not None:
             gnorm = self.zero.sync_and_step(self.optimizer, lr, cfg.optim.grad_clip, stats)
+        elif self.tp is not None:
+            from ..parallel import tp_model
+
+            self.tp.all_reduce_grads(tp_model.replicated_parameters(self.model))
+            self.dp.all_reduce_(stats)
+            sq = torch.stack([sum((p.grad.float() ** 2).sum() for p in self.model.parameters() if p.grad is not None and getattr(p, "tp_sharded", False)),
+                              sum((p.grad.float() ** 2).sum() for p in self.model.parameters() if p.grad is not None and not getattr(p, "tp_sharded", False))])
+            part = sq[0:1].clone()
+            self.dp.all_reduce_(part)
+            gnorm = (part[0] + sq[1]).sqrt()
+            self.optimizer.step(lr, _clip_coef(gnorm, cfg.optim.grad_clip))
         else:
             if self.dp is not None:
                 self.dp.all_reduce_(self.flat.grads)
