@@ -43,6 +43,9 @@ def parse():
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU per step")
     ap.add_argument("--sharding", default="auto", help="replicated | zero1 | zero2 | auto (zero2 when N > 1)")
     ap.add_argument("--comm", default="auto", help="fused | nccl | auto")
+    ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
+                    help="tp: tensor parallel over all ranks with a sequence-parallel stream (--rows is then the whole job's rows per step)")
+    ap.add_argument("--tp-impl", default="fused", choices=["fused", "collective"], help="tp: fused peer-memory GEMMs or NCCL collectives around plain GEMMs")
     ap.add_argument("--mode", default="train", choices=["train", "decode"], help="decode: static-cache greedy decode tokens/s")
     ap.add_argument("--kv", default="gqa", choices=["gqa", "grid"], help="decode: KV sharing of the attention layers")
     ap.add_argument("--prompt", type=int, default=32768, help="decode: prompt length")
@@ -119,12 +122,17 @@ def run_ours(args) -> dict:
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
     cfg = C.TrainConfig(model=C.hybrid_model_config(args.size, full=True))
-    cfg.data = C.DataConfig(kind="uniform", seq_len=args.seq_len, batch_size=args.rows * world, seed=1)
+    tp = args.parallelism == "tp" and world > 1
+    job_rows = args.rows if tp else args.rows * world
+    cfg.data = C.DataConfig(kind="uniform", seq_len=args.seq_len, batch_size=job_rows, seed=1)
     cfg.micro_batch_size = args.rows
+    if tp:
+        cfg.tensor_parallel = world
+        os.environ["GHB_TP_IMPL"] = args.tp_impl
     cfg.steps, cfg.seed, cfg.dtype, cfg.autocast, cfg.head_impl = 10 ** 6, 1, "float32", "bfloat16", "fused"
     cfg.optim.name, cfg.optim.warmup_steps = "adamw", 100
     cfg.metrics_jsonl, cfg.log_every, cfg.ckpt_every_steps, cfg.ckpt_every_minutes = False, 0, 0, 0.0
-    cfg.optimizer_sharding = ("zero2" if world > 1 else "replicated") if args.sharding == "auto" else args.sharding
+    cfg.optimizer_sharding = ("zero2" if world > 1 and not tp else "replicated") if args.sharding == "auto" else args.sharding
     if args.comm != "auto":
         os.environ["GHB_COMM"] = args.comm
     trainer = Trainer(cfg, None, dp)
@@ -163,15 +171,16 @@ def run_ours(args) -> dict:
         dp.barrier()
     e2e_ms = max_over_ranks(start.elapsed_time(end), dp) / args.steps
     clocks = sampler.stop(world)
-    tokens = args.rows * world * args.seq_len
+    tokens = job_rows * args.seq_len
     base = baseline_number()
     value = tokens / (dev_ms / 1e3)
     out = {
         "metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": (value / base) if base else None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": MODEL if args.size == "200m" else args.size, "global_batch": args.rows * world,
-                   "seq_len": args.seq_len, "parallelism": f"dp{world}" + ("" if world == 1 else f"-{cfg.optimizer_sharding}"),
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong" if tp else "weak",
+        "vs_baseline": (value / base) if base and not tp else None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": MODEL if args.size == "200m" else args.size, "global_batch": job_rows,
+                   "seq_len": args.seq_len,
+                   "parallelism": (f"tp{world}-sp-{args.tp_impl}" if tp else f"dp{world}" + ("" if world == 1 else f"-{cfg.optimizer_sharding}")),
                    "optimizer": "adamw", "vocab": VOCAB, "l2": "per-step working set (GBs of activations) >> 126 MB L2",
                    "comm": os.environ.get("GHB_COMM", "auto"), "loss": m["loss"]},
         "clocks": clocks,
@@ -325,7 +334,7 @@ def run_reference(args) -> dict:
         ms = float(t[0])
     ms /= args.steps
     clocks = sampler.stop(world)
-    tokens = args.rows * world * args.seq_len
+    tokens = job_rows * args.seq_len
     value = tokens / (ms / 1e3)
     loss = m.get("loss") if isinstance(m, dict) else None
     out = {"metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,

@@ -150,7 +150,7 @@ class TensorParallel:
     def ag_gemm(self, g: Gathered, w: torch.Tensor, b_mn: bool = False, out_dtype=BF16) -> torch.Tensor:
         """all_gather(x) w^T ([T, N]); w [N, K], or [K, N] with b_mn."""
         if self.impl != "fused":
-            return (g.full.float() @ (w.float() if b_mn else w.float().t())).to(out_dtype)
+            return self._plain(g.full, w, False, b_mn, out_dtype)
         from ..ops import native
 
         N = w.shape[1] if b_mn else w.shape[0]
@@ -163,7 +163,7 @@ class TensorParallel:
         """a^T b over all tokens ([cols(a), cols(b)], fp32), a and b stored [T, *]; one of them is `g.full` (a weight gradient
         whose token dimension is gathered)."""
         if self.impl != "fused":
-            res = a.float().t() @ b.float()
+            res = self._plain(a, b, True, True, torch.float32)
             return res if out is None else out.copy_(res)
         from ..ops import native
 
@@ -179,10 +179,12 @@ class TensorParallel:
         N = w.shape[1] if b_mn else w.shape[0]
         Ts = T // self.world
         if self.impl != "fused":
-            part = (h.float() @ (w.float() if b_mn else w.float().t()))
-            if h.dtype == BF16:
-                part = part.to(BF16).float()       # the wire format of the fused path
-            out = torch.empty(Ts, N, dtype=torch.float32, device=h.device)
+            if h.is_cuda and h.dtype == BF16:      # the baseline on GPUs: the same bf16 GEMM, then NCCL's reduce-scatter in bf16
+                part = self._plain(h, w, False, b_mn, BF16)
+                out = torch.empty(Ts, N, dtype=BF16, device=h.device)
+            else:
+                part = self._plain(h, w, False, b_mn, torch.float32)
+                out = torch.empty(Ts, N, dtype=torch.float32, device=h.device)
             dist.reduce_scatter_tensor(out, part.contiguous(), group=self.group)
             return out.to(out_dtype)
         from ..ops import native
@@ -200,6 +202,17 @@ class TensorParallel:
         native.ext().tp_rs_reduce(stage, out, args, err)
         native._count(2)
         return out
+
+    @staticmethod
+    def _plain(a, b, a_mn, b_mn, out_dtype):
+        """a b^T without communication: the framework's GEMM on CUDA bf16 operands, float math elsewhere."""
+        if a.is_cuda and a.dtype == BF16 and b.dtype == BF16:
+            from ..ops import native
+
+            return native.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=out_dtype)
+        af = a.float().t() if a_mn else a.float()
+        bf = b.float() if b_mn else b.float().t()
+        return (af @ bf).to(out_dtype)
 
     # ------------------------------------------------------------------ replicated parameters
 
@@ -226,7 +239,7 @@ class _ColumnParallel(torch.autograd.Function):
     def forward(ctx, x, weight, w_lp, tp):
         x2 = x.reshape(-1, x.shape[-1])
         n = w_lp.shape[0]
-        if tp.impl == "fused":
+        if x.is_cuda:
             from ..ops.native import _pad_rows
             x2, w_lp = x2.to(BF16), _pad_rows(w_lp)       # output rows stay 16-byte aligned for projections with a few outputs
         y = tp.ag_gemm(tp.gather(x2), w_lp, out_dtype=x2.dtype)
@@ -254,7 +267,7 @@ class _RowParallel(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, weight, w_lp, tp):
         h2 = h.reshape(-1, h.shape[-1])
-        if tp.impl == "fused":
+        if h.is_cuda:
             h2 = h2.to(BF16)
         h2 = h2.contiguous()
         out = tp.gemm_rs(h2, w_lp, out_dtype=h2.dtype)
@@ -274,11 +287,11 @@ class _RowParallel(torch.autograd.Function):
 
 def column_parallel(x, lin, tp):
     from ..ops.native import _w_lp
-    w_lp = _w_lp(lin) if tp.impl == "fused" else lin.weight.detach()
+    w_lp = _w_lp(lin) if x.is_cuda else lin.weight.detach()
     return _ColumnParallel.apply(x, lin.weight, w_lp, tp)
 
 
 def row_parallel(h, lin, tp):
     from ..ops.native import _w_lp
-    w_lp = _w_lp(lin) if tp.impl == "fused" else lin.weight.detach()
+    w_lp = _w_lp(lin) if h.is_cuda else lin.weight.detach()
     return _RowParallel.apply(h, lin.weight, w_lp, tp)
