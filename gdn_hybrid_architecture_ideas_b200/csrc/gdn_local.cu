@@ -1,15 +1,22 @@
 // Chunk-local stage of the gated delta rule: everything that does not depend on the state carried between chunks.
+// One CTA per (batch row, value head, chunk of 64 tokens); two CTAs share an SM (107 KB of shared memory, <= 128 registers).
 //
-// Forward, one CTA per (batch row, value head, chunk of 64 tokens), fp32 maths:
 //   c_i = cumulative log decay inside the chunk, seg_i = number of document starts at or before i (0 = the document
 //   that continues from the previous chunk), E_ij = exp(c_i - c_j) for j <= i in the same segment;
-//   A_ij = beta_i (k_i . k_j) E_ij (j < i);  X = (I + A)^-1 [beta v | beta gamma first k] by forward substitution, one
-//   column per thread held in registers (columns are independent, so the solve needs no synchronisation);
-//   outputs U, W (the two column blocks of X), Aqk_ij = (q_i . k_j) E_ij (j <= i), q_in = q gamma first,
-//   k_out = k exp(c_last - c) last, carry = gamma_last if the chunk has no document start else 0.
-// These are the operands of the sequential state pass (gdn_scan.cu). Same function as the PyTorch statement
-// `reference.chunk_local`; the reference computes it with batched matmuls and solve_triangular
-// (ced/model/gdn_chunked.py:100-140) or its Triton kernels for value dimension 128 (ced/kernels/gdn_triton.py:96-374).
+//   G = (K K^T) E (strictly lower), A = diag(beta) G, T = (I + A)^-1 by a blocked inverse: the four 16 x 16 diagonal
+//   blocks by substitution (one column per thread), then two merge levels [[P, 0], [C, Q]]^-1 = [[P^-1, 0],
+//   [-Q^-1 C P^-1, Q^-1]] as small tf32 products (the form ced/kernels/gdn_triton.py:133-325 uses).
+// Forward: U = (T diag(beta)) V, W = (T diag(beta gamma first)) K, Aqk = (Q K^T) E (lower), q_in = q gamma first,
+//   k_out = k exp(c_last - c) last, carry = gamma_last if the chunk has no document start else 0: the operands of the
+//   sequential state pass (gdn_scan.cu). Same function as the PyTorch statement `reference.chunk_local`; the reference
+//   computes it with batched matmuls and solve_triangular (ced/model/gdn_chunked.py:100-140) or its Triton kernels.
+// Backward: gradients of the above given the state pass's dU, partial sums of dW / dq_in / dk_out, dO and v_new (it
+//   forms dAqk = dO v_new^T itself):  dR = T^T dX per block of 128 columns of X = [U | W];  dA = -dR X^T;  dbeta, dc,
+//   dKK = dG E from A_ij = beta_i G_ij;  dQK, dc from Aqk;  dk = (dKK + dKK^T) K + dQK^T Q + diagonal terms,
+//   dq = dQK K + diagonal term, dv = beta dR_u, dg = reverse cumulative sum of dc.
+// Tiles that are bf16 in memory (K, Q, V, U, W, dU, dO, v_new) are copied to shared memory as they are and fed to
+// mma.sync m16n8k16 through ldmatrix, plain or transposed, so no tile is stored twice; fp32 matrices that become MMA
+// operands (T, its scaled forms) enter as a bf16 pair (value + residual).
 #include "kernels.h"
 #include <cuda_bf16.h>
 #include <cstdlib>
@@ -18,8 +25,10 @@ namespace ghb {
 
 constexpr int LC = 64;          // chunk length
 constexpr int LK = 128;         // key head dimension
-constexpr int KS = 132;         // padded row stride of the fp32 q / k tiles in shared memory
-constexpr int AS = 65;          // padded row stride of the 64 x 64 matrices
+constexpr int BS = 68;          // row stride (elements) of the fp32 64 x 64 matrices
+constexpr int TS = 136;         // row stride (elements) of the 64 x 128 bf16 tiles: 272 bytes, conflict-free for ldmatrix
+constexpr int MS = 72;          // row stride (elements) of the 64 x 64 bf16 matrices
+
 
 struct LocalIn {
   const __nv_bfloat16* q; const __nv_bfloat16* k; const __nv_bfloat16* v;   // token-major with per-token strides
@@ -59,160 +68,6 @@ __device__ __forceinline__ void load_scalars(const LocalIn& in, int b, int hv, i
   __syncthreads();
 }
 
-// fp32 tile [64][KS] of one head's rows of q or k for this chunk
-__device__ __forceinline__ void load_tile(const __nv_bfloat16* base, long tok_stride, float* tile) {
-  for (int idx = threadIdx.x; idx < LC * (LK / 8); idx += blockDim.x) {
-    const int row = idx / (LK / 8), c8 = (idx % (LK / 8)) * 8;
-    const uint4 pk = *reinterpret_cast<const uint4*>(base + row * tok_stride + c8);
-    const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
-      tile[row * KS + c8 + 2 * e] = f.x; tile[row * KS + c8 + 2 * e + 1] = f.y;
-    }
-  }
-}
-
-// acc[ii][jj] = sum_kk X[i][kk] * Y[j][kk] for i = ty + 16 ii, j = tx + 16 jj (interleaved rows: conflict-free float4 loads)
-__device__ __forceinline__ void tile_dot(const float* X, const float* Y, int ty, int tx, float (&acc)[4][4]) {
-#pragma unroll
-  for (int ii = 0; ii < 4; ++ii)
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) acc[ii][jj] = 0.f;
-#pragma unroll 4
-  for (int kk = 0; kk < LK; kk += 4) {
-    float4 a[4], bq[4];
-#pragma unroll
-    for (int ii = 0; ii < 4; ++ii) a[ii] = *reinterpret_cast<const float4*>(X + (ty + 16 * ii) * KS + kk);
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj) bq[jj] = *reinterpret_cast<const float4*>(Y + (tx + 16 * jj) * KS + kk);
-#pragma unroll
-    for (int ii = 0; ii < 4; ++ii)
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj)
-        acc[ii][jj] += a[ii].x * bq[jj].x + a[ii].y * bq[jj].y + a[ii].z * bq[jj].z + a[ii].w * bq[jj].w;
-  }
-}
-
-template <int DV>
-__global__ void __launch_bounds__(256)
-gdn_local_fwd_kernel(LocalIn in, __nv_bfloat16* __restrict__ U, __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ Aqk,
-                     __nv_bfloat16* __restrict__ Qin, __nv_bfloat16* __restrict__ Kout, float* __restrict__ carry) {
-  extern __shared__ __align__(16) float sm[];
-  float* sK = sm;                       // [64][KS]
-  float* sQ = sK + LC * KS;             // [64][KS]
-  float* sA = sQ + LC * KS;             // [64][AS]
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sA + LC * AS);
-  __nv_bfloat16* sAq = reinterpret_cast<__nv_bfloat16*>(sc + 1);   // [64][64] staging of Aqk
-
-  const int chunk = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
-  const int hk = hv / in.rep;
-  const int NT = in.L / LC;
-  const long tok0 = static_cast<long>(b) * in.L + chunk * LC;
-  const long out_row0 = (static_cast<long>(b) * in.Hv + hv) * in.L + chunk * LC;
-
-  load_scalars(in, b, hv, chunk, sc);
-  load_tile(in.k + tok0 * in.k_tok + hk * LK, in.k_tok, sK);
-  load_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
-  __syncthreads();
-  if (threadIdx.x == 0) carry[(static_cast<long>(b) * in.Hv + hv) * NT + chunk] = sc->carry;
-
-  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
-  {
-    float kk[4][4], qk[4][4];
-    tile_dot(sK, sK, ty, tx, kk);
-    tile_dot(sQ, sK, ty, tx, qk);
-#pragma unroll
-    for (int ii = 0; ii < 4; ++ii)
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        const int i = ty + 16 * ii, j = tx + 16 * jj;
-        const bool same = sc->seg[i] == sc->seg[j];
-        const float e = (j <= i && same) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
-        sA[i * AS + j] = (j < i) ? sc->beta[i] * kk[ii][jj] * e : 0.f;
-        sAq[i * LC + j] = __float2bfloat16(qk[ii][jj] * e);
-      }
-  }
-  __syncthreads();
-  // Aqk, q_in, k_out (coalesced bf16 rows)
-  for (int idx = threadIdx.x; idx < LC * LC / 8; idx += blockDim.x)
-    reinterpret_cast<uint4*>(Aqk + out_row0 * LC)[idx] = reinterpret_cast<const uint4*>(sAq)[idx];
-  for (int idx = threadIdx.x; idx < LC * LK / 2; idx += blockDim.x) {
-    const int row = idx / (LK / 2), c2 = (idx % (LK / 2)) * 2;
-    const float fq = sc->seg[row] == 0 ? sc->gamma[row] : 0.f;
-    const float fk = sc->seg[row] == sc->last_seg ? sc->to_end[row] : 0.f;
-    reinterpret_cast<__nv_bfloat162*>(Qin + (out_row0 + row) * LK)[c2 / 2] = __floats2bfloat162_rn(sQ[row * KS + c2] * fq, sQ[row * KS + c2 + 1] * fq);
-    reinterpret_cast<__nv_bfloat162*>(Kout + (out_row0 + row) * LK)[c2 / 2] = __floats2bfloat162_rn(sK[row * KS + c2] * fk, sK[row * KS + c2 + 1] * fk);
-  }
-  // forward substitution, one column of [U | W] per thread (a second column for the first DV + 128 - 256 threads)
-  constexpr int COLS = DV + LK;
-#pragma unroll 1
-  for (int rep = 0; rep < (COLS + 255) / 256; ++rep) {
-    const int col = rep * 256 + threadIdx.x;
-    if (col >= COLS) break;
-    float x[LC];
-    if (col < DV) {
-      const __nv_bfloat16* vp = in.v + tok0 * in.v_tok + static_cast<long>(hv) * DV + col;
-#pragma unroll
-      for (int i = 0; i < LC; ++i) x[i] = sc->beta[i] * __bfloat162float(vp[i * in.v_tok]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < LC; ++i) x[i] = sc->seg[i] == 0 ? sc->beta[i] * sc->gamma[i] * sK[i * KS + (col - DV)] : 0.f;
-    }
-#pragma unroll
-    for (int i = 1; i < LC; ++i) {
-      float acc = x[i];
-#pragma unroll
-      for (int j = 0; j < i; ++j) acc -= sA[i * AS + j] * x[j];
-      x[i] = acc;
-    }
-    if (col < DV) {
-#pragma unroll
-      for (int i = 0; i < LC; ++i) U[(out_row0 + i) * DV + col] = __float2bfloat16(x[i]);
-    } else {
-#pragma unroll
-      for (int i = 0; i < LC; ++i) W[(out_row0 + i) * LK + (col - DV)] = __float2bfloat16(x[i]);
-    }
-  }
-}
-
-static_assert(sizeof(ChunkScalars) % 16 == 0 && (LC * KS * 4) % 16 == 0 && (LC * AS * 4) % 16 == 0, "16-byte aligned shared-memory carve-up");
-constexpr size_t LOCAL_FWD_SMEM = (2 * LC * KS + LC * AS) * sizeof(float) + sizeof(ChunkScalars) + LC * LC * 2 + 64;
-
-int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
-                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, void* U, void* W, void* Aqk, void* Qin, void* Kout,
-                  float* carry, cudaStream_t st) {
-  if (L % LC || (dv != 128 && dv != 256) || Hv % Hk) return 1;
-  LocalIn in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), q_tok, k_tok, v_tok,
-             g, beta, start, L, Hv, Hv / Hk};
-  dim3 grid(L / LC, Hv, B);
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(gdn_local_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(LOCAL_FWD_SMEM));
-    cudaFuncSetAttribute(gdn_local_fwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(LOCAL_FWD_SMEM));
-    attr = true;
-  }
-  auto* u = static_cast<__nv_bfloat16*>(U); auto* w = static_cast<__nv_bfloat16*>(W); auto* a = static_cast<__nv_bfloat16*>(Aqk);
-  auto* qi = static_cast<__nv_bfloat16*>(Qin); auto* ko = static_cast<__nv_bfloat16*>(Kout);
-  if (dv == 128) gdn_local_fwd_kernel<128><<<grid, 256, LOCAL_FWD_SMEM, st>>>(in, u, w, a, qi, ko, carry);
-  else gdn_local_fwd_kernel<256><<<grid, 256, LOCAL_FWD_SMEM, st>>>(in, u, w, a, qi, ko, carry);
-  return cudaGetLastError() == cudaSuccess ? 0 : 4;
-}
-
-}  // namespace ghb
-
-// ================================================================================================ backward
-// Gradients of the chunk-local stage, one CTA per (batch row, value head, chunk). Inputs: the forward inputs, the
-// forward's outputs X = [U | W], and the gradients of U, W, q_in, k_out, Aqk, carry handed back by the state pass.
-//   T = (I + A)^-1 explicitly (one column per thread), then every product is a warp-level tensor-core GEMM
-//   (mma.sync m16n8k8, tf32 operands, fp32 accumulation) on fp32 tiles in shared memory:
-//   dR = T^T dX per block of 128 columns;  dA = -dR X^T;  A_ij = beta_i G_ij, G = (K K^T) E  ->  dbeta, dc, dKK = dG E;
-//   Aqk = (Q K^T) E -> dQK, dc;  dk = (dKK + dKK^T) K + dQK^T Q + diagonal terms, dq = dQK K + diagonal term,
-//   dv = beta dR_u, dg = reverse cumulative sum of dc.
-namespace ghb {
-
-constexpr int BS = 68;          // padded row stride of the 64 x 64 matrices of the backward kernel
-
 struct LocalGrads {
   const __nv_bfloat16* U; const __nv_bfloat16* W;       // the forward's outputs (X = [U | W])
   const __nv_bfloat16* dU;                               // [B, H, L, DV]
@@ -235,44 +90,14 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
   asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// One warp accumulates a 16 x (8 NT) tile: acc[nt] += A(16 x K) B(K x 8 nt). A points at the tile's first row, B at its first
-// column. A_T: A(m, k) is stored at A[k * lda + m] (else A[m * lda + k]). B_K: B(k, n) is stored at B[k * ldb + n] (else B[n * ldb + k]).
-// Fragment layout of mma.m16n8k8: g = lane / 4, t = lane % 4; a0 (g, t) a1 (g+8, t) a2 (g, t+4) a3 (g+8, t+4); b0 (t, g) b1 (t+4, g);
-// c0 (g, 2t) c1 (g, 2t+1) c2 (g+8, 2t) c3 (g+8, 2t+1).
-template <int NT, bool A_T, bool B_K>
-__device__ __forceinline__ void warp_gemm(const float* A, int lda, const float* B, int ldb, int K, float (&acc)[NT][4], int lane) {
-  const int g = lane >> 2, t = lane & 3;
-#pragma unroll 2
-  for (int k0 = 0; k0 < K; k0 += 8) {
-    uint32_t a[4];
-    if (A_T) {
-      a[0] = to_tf32(A[(k0 + t) * lda + g]); a[1] = to_tf32(A[(k0 + t) * lda + g + 8]);
-      a[2] = to_tf32(A[(k0 + t + 4) * lda + g]); a[3] = to_tf32(A[(k0 + t + 4) * lda + g + 8]);
-    } else {
-      a[0] = to_tf32(A[g * lda + k0 + t]); a[1] = to_tf32(A[(g + 8) * lda + k0 + t]);
-      a[2] = to_tf32(A[g * lda + k0 + t + 4]); a[3] = to_tf32(A[(g + 8) * lda + k0 + t + 4]);
-    }
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      uint32_t b0, b1;
-      if (B_K) { b0 = to_tf32(B[(k0 + t) * ldb + nt * 8 + g]); b1 = to_tf32(B[(k0 + t + 4) * ldb + nt * 8 + g]); }
-      else { b0 = to_tf32(B[(nt * 8 + g) * ldb + k0 + t]); b1 = to_tf32(B[(nt * 8 + g) * ldb + k0 + t + 4]); }
-      mma_tf32(acc[nt], a, b0, b1);
-    }
-  }
-}
+// Accumulator fragments (both MMA shapes used here): g = lane / 4, t = lane % 4; c0 (g, 2t) c1 (g, 2t+1) c2 (g+8, 2t)
+// c3 (g+8, 2t+1). tf32 m16n8k8 operands: a0 (g, t) a1 (g+8, t) a2 (g, t+4) a3 (g+8, t+4); b0 (t, g) b1 (t+4, g).
 template <int NT>
 __device__ __forceinline__ void zero_acc(float (&acc)[NT][4]) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
 }
 
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
-  const uint4 a = *reinterpret_cast<const uint4*>(p);
-  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-  for (int e = 0; e < 4; ++e) { const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); f[2 * e] = v.x; f[2 * e + 1] = v.y; }
-}
 template <int NP>
 __device__ __forceinline__ void sum8(const float* p, long stride, float (&f)[8]) {
 #pragma unroll
@@ -290,274 +115,6 @@ __device__ __forceinline__ float2 sum2(const float* p, long stride) {
   for (int s = 0; s < NP; ++s) { const float2 a = *reinterpret_cast<const float2*>(p + s * stride); r.x += a.x; r.y += a.y; }
   return r;
 }
-
-template <int DV>
-__global__ void __launch_bounds__(256, 1)
-gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
-  extern __shared__ __align__(16) float sm[];
-  float* sK = sm;                       // [64][KS]
-  float* sQ = sK + LC * KS;             // [64][KS] (also the staging of dX blocks)
-  float* sDR = sQ + LC * KS;            // dR block [64][KS]
-  float* sX = sDR + LC * KS;            // X block  [64][KS]
-  float* sG = sX + LC * KS;             // G, later S = dKK + dKK^T   [64][BS]
-  float* sAq = sG + LC * BS;            // Aqk, later dQK             [64][BS]
-  float* sT = sAq + LC * BS;            // T = (I + A)^-1, later dA   [64][BS]
-  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(sT + LC * BS);
-  float* sdc = reinterpret_cast<float*>(sc + 1);   // [64] decay gradient
-  float* sdb = sdc + LC;                            // [64] beta gradient
-
-  const int chunk = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
-  const int hk = hv / in.rep;
-  const int NT_ = in.L / LC;
-  const long tok0 = static_cast<long>(b) * in.L + chunk * LC;
-  const long row0 = (static_cast<long>(b) * in.Hv + hv) * in.L + chunk * LC;     // rows of the [B, H, L, *] operands
-  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-  const int g = lane >> 2, tq = lane & 3;
-  const int m0 = (warp & 3) * 16;                  // this warp's 16 output rows in every product
-
-  load_scalars(in, b, hv, chunk, sc);
-  load_tile(in.k + tok0 * in.k_tok + hk * LK, in.k_tok, sK);
-  load_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
-  if (t < LC) { sdc[t] = 0.f; sdb[t] = 0.f; }
-  __syncthreads();
-  {   // G = (K K^T) E (strictly lower), Aqk = (Q K^T) E (lower): warp tile 16 x 32
-    const int n0 = (warp >> 2) * 32;
-    float kk[4][4], qk[4][4];
-    zero_acc(kk); zero_acc(qk);
-    warp_gemm<4, false, false>(sK + m0 * KS, KS, sK + n0 * KS, KS, LK, kk, lane);
-    warp_gemm<4, false, false>(sQ + m0 * KS, KS, sK + n0 * KS, KS, LK, qk, lane);
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = m0 + g + (e >> 1) * 8, j = n0 + nt * 8 + 2 * tq + (e & 1);
-        const float ex = (j <= i && sc->seg[i] == sc->seg[j]) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
-        sG[i * BS + j] = (j < i) ? kk[nt][e] * ex : 0.f;
-        sAq[i * BS + j] = qk[nt][e] * ex;
-      }
-  }
-  __syncthreads();
-  // ---- T = (I + A)^-1, one column per thread (threads 0..63): x_c = 1, x_i = -beta_i sum_{m < i} G_im x_m
-  if (t < LC) {
-    float x[LC];
-#pragma unroll
-    for (int i = 0; i < LC; ++i) x[i] = (i == t) ? 1.f : 0.f;
-#pragma unroll
-    for (int i = 1; i < LC; ++i) {
-      float a0 = 0.f, a1 = 0.f;
-#pragma unroll
-      for (int m = 0; m + 1 < i; m += 2) { a0 += sG[i * BS + m] * x[m]; a1 += sG[i * BS + m + 1] * x[m + 1]; }
-      if (i & 1) a0 += sG[i * BS + i - 1] * x[i - 1];
-      x[i] -= sc->beta[i] * (a0 + a1);
-    }
-#pragma unroll
-    for (int i = 0; i < LC; ++i) sT[i * BS + t] = x[i];
-  }
-  __syncthreads();
-
-  constexpr int COLS = DV + LK;
-  constexpr int NP = DV / 128;      // one partial sum per 128-wide value slice of the state pass
-  float* sDX = sQ;      // the q tile is not needed again until the outputs; it is reloaded there
-  // ---- dAqk = dO v_new^T over the value dimension, 128 columns at a time (warp tile 16 x 32), kept in registers
-  float dAq[4][4];
-  zero_acc(dAq);
-#pragma unroll 1
-  for (int vb = 0; vb < DV / 128; ++vb) {
-    for (int idx = t; idx < LC * 16; idx += 256) {
-      const int row = idx >> 4, c8 = (idx & 15) * 8;
-      float fa[8], fb[8];
-      load8(gr.dO + ((tok0 + row) * in.Hv + hv) * DV + vb * 128 + c8, fa);
-      load8(gr.Vnew + (row0 + row) * DV + vb * 128 + c8, fb);
-      *reinterpret_cast<float4*>(sDR + row * KS + c8) = make_float4(fa[0], fa[1], fa[2], fa[3]);
-      *reinterpret_cast<float4*>(sDR + row * KS + c8 + 4) = make_float4(fa[4], fa[5], fa[6], fa[7]);
-      *reinterpret_cast<float4*>(sX + row * KS + c8) = make_float4(fb[0], fb[1], fb[2], fb[3]);
-      *reinterpret_cast<float4*>(sX + row * KS + c8 + 4) = make_float4(fb[4], fb[5], fb[6], fb[7]);
-    }
-    __syncthreads();
-    warp_gemm<4, false, false>(sDR + m0 * KS, KS, sX + (warp >> 2) * 32 * KS, KS, 128, dAq, lane);
-    __syncthreads();
-  }
-  // ---- per block of 128 columns of [U | W]: dR = T^T dX (warp tile 16 x 64), dA += dR X^T (warp tile 16 x 32)
-  float dA[4][4];
-  zero_acc(dA);
-#pragma unroll 1
-  for (int blk = 0; blk < COLS / 128; ++blk) {
-    const bool is_u = blk * 128 < DV;
-    const int c0 = is_u ? blk * 128 : 0;
-    const __nv_bfloat16* xx = is_u ? gr.U + row0 * DV + c0 : gr.W + row0 * LK;
-    const int ld = is_u ? DV : LK;
-    for (int idx = t; idx < LC * 16; idx += 256) {          // 64 rows x 16 vectors of 8
-      const int row = idx >> 4, c8 = (idx & 15) * 8;
-      float fa[8], fb[8];
-      load8(xx + static_cast<long>(row) * ld + c8, fb);
-      if (is_u) load8(gr.dU + (row0 + row) * DV + c0 + c8, fa);
-      else sum8<NP>(gr.dWp + (row0 + row) * LK + c8, gr.part_stride, fa);
-      *reinterpret_cast<float4*>(sDX + row * KS + c8) = make_float4(fa[0], fa[1], fa[2], fa[3]);
-      *reinterpret_cast<float4*>(sDX + row * KS + c8 + 4) = make_float4(fa[4], fa[5], fa[6], fa[7]);
-      *reinterpret_cast<float4*>(sX + row * KS + c8) = make_float4(fb[0], fb[1], fb[2], fb[3]);
-      *reinterpret_cast<float4*>(sX + row * KS + c8 + 4) = make_float4(fb[4], fb[5], fb[6], fb[7]);
-    }
-    __syncthreads();
-    {
-      const int n0 = (warp >> 2) * 64;
-      float dr[8][4];
-      zero_acc(dr);
-      warp_gemm<8, true, true>(sT + m0, BS, sDX + n0, KS, LC, dr, lane);      // A(i, j) = T[j][i], B(j, col) = dX[j][col]
-      // dv = beta dR_u ; dbeta += dR_u . v ; stage dR
-      float pb0 = 0.f, pb1 = 0.f;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = m0 + g + (e >> 1) * 8, col = n0 + nt * 8 + 2 * tq + (e & 1);
-          const float v = dr[nt][e];
-          sDR[i * KS + col] = v;
-          if (is_u) {
-            const long vidx = (tok0 + i) * in.v_tok + static_cast<long>(hv) * DV + c0 + col;
-            const float pv = v * __bfloat162float(in.v[vidx]);
-            if (e >> 1) pb1 += pv; else pb0 += pv;
-            gr.dv[(tok0 + i) * gr.dv_tok + static_cast<long>(hv) * DV + c0 + col] = __float2bfloat16(sc->beta[i] * v);
-          }
-        }
-      if (is_u) {      // reduce over the 4 lanes that share a row, then one shared atomic per row per warp
-        pb0 += __shfl_xor_sync(0xffffffffu, pb0, 1); pb0 += __shfl_xor_sync(0xffffffffu, pb0, 2);
-        pb1 += __shfl_xor_sync(0xffffffffu, pb1, 1); pb1 += __shfl_xor_sync(0xffffffffu, pb1, 2);
-        if (tq == 0) { atomicAdd(&sdb[m0 + g], pb0); atomicAdd(&sdb[m0 + g + 8], pb1); }
-      }
-    }
-    __syncthreads();
-    warp_gemm<4, false, false>(sDR + m0 * KS, KS, sX + (warp >> 2) * 32 * KS, KS, 128, dA, lane);   // dR X^T
-    __syncthreads();
-  }
-  // sDR / sX now hold the W columns: dR_w [i][kk] and W [i][kk]. Reload q (its buffer staged dX).
-  load_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
-
-  // ---- score matrices: beta / decay gradients; then sT <- dKK (lower), sAq <- dQK
-  {
-    const int n0 = (warp >> 2) * 32;
-    float dKKv[4][4], dQKv[4][4];
-    float rb[2] = {0.f, 0.f}, rc[2] = {0.f, 0.f};
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = m0 + g + (e >> 1) * 8, j = n0 + nt * 8 + 2 * tq + (e & 1);
-        const bool same = sc->seg[i] == sc->seg[j];
-        const float ex = (j <= i && same) ? __expf(sc->c[i] - sc->c[j]) : 0.f;
-        const float G = sG[i * BS + j];
-        const float da = (j < i && same) ? -dA[nt][e] : 0.f;
-        const float dG = da * sc->beta[i];
-        const float t1 = dG * G;
-        const float dq_ij = (j <= i && same) ? dAq[nt][e] : 0.f;
-        const float t2 = dq_ij * sAq[i * BS + j];
-        rb[e >> 1] += da * G;
-        rc[e >> 1] += t1 + t2;
-        atomicAdd(&sdc[j], -(t1 + t2));
-        dKKv[nt][e] = dG * ex;
-        dQKv[nt][e] = dq_ij * ex;
-      }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      rb[h] += __shfl_xor_sync(0xffffffffu, rb[h], 1); rb[h] += __shfl_xor_sync(0xffffffffu, rb[h], 2);
-      rc[h] += __shfl_xor_sync(0xffffffffu, rc[h], 1); rc[h] += __shfl_xor_sync(0xffffffffu, rc[h], 2);
-      if (tq == 0) { atomicAdd(&sdb[m0 + g + 8 * h], rb[h]); atomicAdd(&sdc[m0 + g + 8 * h], rc[h]); }
-    }
-    __syncthreads();     // every reader of sG / sAq / sT (old contents) is done
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = m0 + g + (e >> 1) * 8, j = n0 + nt * 8 + 2 * tq + (e & 1);
-        sT[i * BS + j] = dKKv[nt][e];
-        sAq[i * BS + j] = dQKv[nt][e];
-      }
-  }
-  __syncthreads();
-  for (int idx = t; idx < LC * LC; idx += 256) {      // S = dKK + dKK^T (dKK is strictly lower)
-    const int i = idx >> 6, j = idx & 63;
-    sG[i * BS + j] = sT[i * BS + j] + sT[j * BS + i];
-  }
-  __syncthreads();
-
-  // ---- outputs: dk = S K + dQK^T Q + diagonal terms ; dq = dQK K + diagonal term (warp tile 16 x 64)
-  {
-    const int n0 = (warp >> 2) * 64;
-    float dk[8][4], dq[8][4];
-    zero_acc(dk); zero_acc(dq);
-    float2 pq[2][8], pk[2][8];          // the state pass's dq_in / dk_out, fetched ahead of the products that hide their latency
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const long at = (row0 + m0 + g + 8 * h) * LK + n0 + nt * 8 + 2 * tq;
-        pq[h][nt] = sum2<NP>(gr.dQp + at, gr.part_stride);
-        pk[h][nt] = sum2<NP>(gr.dKp + at, gr.part_stride);
-      }
-    warp_gemm<8, false, true>(sG + m0 * BS, BS, sK + n0, KS, LC, dk, lane);       // S K
-    warp_gemm<8, true, true>(sAq + m0, BS, sQ + n0, KS, LC, dk, lane);           // dQK^T Q : A(r, i) = dQK[i][r]
-    warp_gemm<8, false, true>(sAq + m0 * BS, BS, sK + n0, KS, LC, dq, lane);      // dQK K
-    float dots[2][3] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}};
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = m0 + g + 8 * h;
-      const float fq = sc->seg[r] == 0 ? sc->gamma[r] : 0.f;                       // q_in = q fq ; W rhs = beta fq k
-      const float fk = sc->seg[r] == sc->last_seg ? sc->to_end[r] : 0.f;           // k_out = k fk
-      const float br = sc->beta[r];
-      float* dqo = gr.dq16 ? nullptr : gr.dq + ((tok0 + r) * in.Hv + hv) * LK;
-      float* dko = gr.dq16 ? nullptr : gr.dk + ((tok0 + r) * in.Hv + hv) * LK;
-      __nv_bfloat16* dqh = gr.dq16 ? gr.dq16 + (tok0 + r) * gr.qk_tok + static_cast<long>(hv) * LK : nullptr;
-      __nv_bfloat16* dkh = gr.dq16 ? gr.dk16 + (tok0 + r) * gr.qk_tok + static_cast<long>(hv) * LK : nullptr;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int kk = n0 + nt * 8 + 2 * tq;
-        const float2 drw = *reinterpret_cast<const float2*>(sDR + r * KS + kk);
-        const float2 kre = *reinterpret_cast<const float2*>(sK + r * KS + kk);
-        const float2 qre = *reinterpret_cast<const float2*>(sQ + r * KS + kk);
-        const float2 dqi = pq[h][nt], dkv = pk[h][nt];
-        float2 ok, oq;
-        ok.x = dk[nt][2 * h] + br * fq * drw.x + fk * dkv.x; ok.y = dk[nt][2 * h + 1] + br * fq * drw.y + fk * dkv.y;
-        oq.x = dq[nt][2 * h] + fq * dqi.x; oq.y = dq[nt][2 * h + 1] + fq * dqi.y;
-        if (dqh) {
-          *reinterpret_cast<__nv_bfloat162*>(dkh + kk) = __floats2bfloat162_rn(ok.x, ok.y);
-          *reinterpret_cast<__nv_bfloat162*>(dqh + kk) = __floats2bfloat162_rn(oq.x, oq.y);
-        } else {
-          *reinterpret_cast<float2*>(dko + kk) = ok;
-          *reinterpret_cast<float2*>(dqo + kk) = oq;
-        }
-        dots[h][0] += drw.x * kre.x + drw.y * kre.y;
-        dots[h][1] += dqi.x * qre.x + dqi.y * qre.y;
-        dots[h][2] += dkv.x * kre.x + dkv.y * kre.y;
-      }
-#pragma unroll
-      for (int w = 0; w < 3; ++w) { dots[h][w] += __shfl_xor_sync(0xffffffffu, dots[h][w], 1); dots[h][w] += __shfl_xor_sync(0xffffffffu, dots[h][w], 2); }
-      if (tq == 0) {
-        atomicAdd(&sdb[r], fq * dots[h][0]);
-        atomicAdd(&sdc[r], br * fq * dots[h][0] + fq * dots[h][1] - fk * dots[h][2]);
-        atomicAdd(&sdc[LC - 1], fk * dots[h][2]);
-      }
-    }
-  }
-  __syncthreads();
-  if (t == 0) {
-    sdc[LC - 1] += sc->carry * gr.dcarry[(static_cast<long>(b) * in.Hv + hv) * NT_ + chunk];
-    float acc = 0.f;
-    for (int i = LC - 1; i >= 0; --i) { acc += sdc[i]; sdc[i] = acc; }      // dg_m = sum_{i >= m} dc_i
-  }
-  __syncthreads();
-  if (t < LC) {
-    gr.dg[(tok0 + t) * in.Hv + hv] = sdc[t];
-    gr.dbeta[(tok0 + t) * in.Hv + hv] = sdb[t];
-  }
-}
-
-// ================================================================================================ backward, bf16 tiles
-// Same function as gdn_local_bwd_kernel on bf16 shared-memory tiles: operands that are bf16 in memory (K, Q, U, W, dU,
-// dO, v_new) are copied as they are and fed to mma.sync m16n8k16 through ldmatrix (plain or transposed, so no tile is
-// ever stored twice); T = (I + A)^-1 comes from a blocked inverse (16 x 16 diagonal blocks by substitution, then two
-// merge levels of small tf32 products, the form ced/kernels/gdn_triton.py:133-325 uses) and enters its products as a
-// bf16 pair (value + residual). Shared memory 107 KB and at most 128 registers: two CTAs per SM.
-constexpr int TS = 136;         // row stride (elements) of the 64 x 128 bf16 tiles: 272 bytes, conflict-free for ldmatrix
-constexpr int MS = 72;          // row stride (elements) of the 64 x 64 bf16 matrices
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
   const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -679,7 +236,7 @@ __device__ __forceinline__ void blocked_inverse(const float* sG, float* sT, cons
   __syncthreads();
 }
 
-struct Bwd2Smem {
+struct BwdSmem {
   static constexpr size_t TILE = LC * TS * 2;             // 17408
   static constexpr size_t MAT32 = LC * BS * 4;            // 17408
   static constexpr size_t MAT16 = LC * MS * 2;            // 9216
@@ -695,9 +252,9 @@ struct Bwd2Smem {
 
 template <int DV>
 __global__ void __launch_bounds__(256, 2)
-gdn_local_bwd2_kernel(LocalIn in, LocalGrads gr) {
+gdn_local_bwd_kernel(LocalIn in, LocalGrads gr) {
   extern __shared__ __align__(16) unsigned char smb[];
-  using S = Bwd2Smem;
+  using S = BwdSmem;
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smb + S::OFF_R1);
   __nv_bfloat16* sQ = sK + LC * TS;
   __nv_bfloat16* sX = sK;                 // the K / Q region holds the X and dX blocks between the score products
@@ -927,7 +484,119 @@ gdn_local_bwd2_kernel(LocalIn in, LocalGrads gr) {
   }
 }
 
-constexpr size_t LOCAL_BWD_SMEM = (4 * LC * KS + 3 * LC * BS + 2 * LC) * sizeof(float) + sizeof(ChunkScalars) + 64;
+// ================================================================================================ forward
+// U = (T diag(beta)) V and W = (T diag(beta gamma first)) K: the scaled inverses enter as bf16 pairs, so V and K are
+// multiplied exactly as stored (no rounding of beta v).
+struct FwdSmem {
+  static constexpr size_t TILE = LC * TS * 2, MAT32 = LC * BS * 4, MAT16 = LC * MS * 2;
+  static constexpr size_t OFF_K = 0, OFF_Q = TILE, OFF_G = 2 * TILE, OFF_T = OFF_G + MAT32, OFF_M = OFF_T + MAT32;    // Q tile later holds V blocks
+  static constexpr size_t OFF_SC = OFF_M + 4 * MAT16;
+  static constexpr size_t TOTAL = OFF_SC + sizeof(ChunkScalars);
+};
+
+template <int DV>
+__global__ void __launch_bounds__(256, 2)
+gdn_local_fwd_kernel(LocalIn in, __nv_bfloat16* __restrict__ U, __nv_bfloat16* __restrict__ W, __nv_bfloat16* __restrict__ Aqk,
+                      __nv_bfloat16* __restrict__ Qin, __nv_bfloat16* __restrict__ Kout, float* __restrict__ carry) {
+  extern __shared__ __align__(16) unsigned char smb[];
+  using S = FwdSmem;
+  __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smb + S::OFF_K);
+  __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smb + S::OFF_Q);
+  __nv_bfloat16* sV = sQ;
+  float* sG = reinterpret_cast<float*>(smb + S::OFF_G);
+  float* sT = reinterpret_cast<float*>(smb + S::OFF_T);
+  __nv_bfloat16* sUh = reinterpret_cast<__nv_bfloat16*>(smb + S::OFF_M);      // T diag(beta): value and residual
+  __nv_bfloat16* sUl = sUh + LC * MS;
+  __nv_bfloat16* sWh = sUl + LC * MS;                                          // T diag(beta gamma first)
+  __nv_bfloat16* sWl = sWh + LC * MS;
+  ChunkScalars* sc = reinterpret_cast<ChunkScalars*>(smb + S::OFF_SC);
+
+  const int chunk = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+  const int hk = hv / in.rep;
+  const int NT_ = in.L / LC;
+  const long tok0 = static_cast<long>(b) * in.L + chunk * LC;
+  const long row0 = (static_cast<long>(b) * in.Hv + hv) * in.L + chunk * LC;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int g = lane >> 2, tq = lane & 3;
+  const int m0 = (warp & 3) * 16;
+
+  load_scalars(in, b, hv, chunk, sc);
+  copy_tile(in.k + tok0 * in.k_tok + hk * LK, in.k_tok, sK);
+  copy_tile(in.q + tok0 * in.q_tok + hk * LK, in.q_tok, sQ);
+  __syncthreads();
+  if (t == 0) carry[(static_cast<long>(b) * in.Hv + hv) * NT_ + chunk] = sc->carry;
+  {
+    const int n0 = (warp >> 2) * 32;
+    float kk[4][4], qk[4][4];
+    zero_acc(kk); zero_acc(qk);
+    wgemm<4, false, false>(sK + m0 * TS, TS, sK + n0 * TS, TS, LK, kk, lane);
+    wgemm<4, false, false>(sQ + m0 * TS, TS, sK + n0 * TS, TS, LK, qk, lane);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = m0 + g + h * 8, j = n0 + nt * 8 + 2 * tq;
+        float a[2];
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+          const int jj = j + e2;
+          const float ex = (jj <= i && sc->seg[i] == sc->seg[jj]) ? __expf(sc->c[i] - sc->c[jj]) : 0.f;
+          sG[i * BS + jj] = (jj < i) ? kk[nt][2 * h + e2] * ex : 0.f;
+          a[e2] = qk[nt][2 * h + e2] * ex;
+        }
+        *reinterpret_cast<__nv_bfloat162*>(Aqk + (row0 + i) * LC + j) = __floats2bfloat162_rn(a[0], a[1]);
+      }
+  }
+  // q_in = q gamma (rows of the continuing document), k_out = k exp(c_last - c) (rows of the last document)
+  for (int idx = t; idx < LC * LK / 2; idx += 256) {
+    const int row = idx / (LK / 2), c2 = (idx % (LK / 2)) * 2;
+    const float fq = sc->seg[row] == 0 ? sc->gamma[row] : 0.f;
+    const float fk = sc->seg[row] == sc->last_seg ? sc->to_end[row] : 0.f;
+    const float2 qv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sQ + row * TS + c2));
+    const float2 kv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(sK + row * TS + c2));
+    reinterpret_cast<__nv_bfloat162*>(Qin + (row0 + row) * LK)[c2 / 2] = __floats2bfloat162_rn(qv.x * fq, qv.y * fq);
+    reinterpret_cast<__nv_bfloat162*>(Kout + (row0 + row) * LK)[c2 / 2] = __floats2bfloat162_rn(kv.x * fk, kv.y * fk);
+  }
+  __syncthreads();
+  blocked_inverse(sG, sT, sc);
+  for (int idx = t; idx < LC * LC; idx += 256) {
+    const int i = idx >> 6, j = idx & 63;
+    const float bj = sc->beta[j];
+    const float u = sT[i * BS + j] * bj;
+    const float w = sc->seg[j] == 0 ? u * sc->gamma[j] : 0.f;
+    const __nv_bfloat16 uh = __float2bfloat16(u), wh = __float2bfloat16(w);
+    sUh[i * MS + j] = uh; sUl[i * MS + j] = __float2bfloat16(u - __bfloat162float(uh));
+    sWh[i * MS + j] = wh; sWl[i * MS + j] = __float2bfloat16(w - __bfloat162float(wh));
+  }
+  __syncthreads();
+  const int n0 = (warp >> 2) * 64;
+  {   // W = (T diag(beta gamma first)) K
+    float acc[8][4];
+    zero_acc(acc);
+    wgemm<8, false, true>(sWh + m0 * MS, MS, sK + n0, TS, LC, acc, lane);
+    wgemm<8, false, true>(sWl + m0 * MS, MS, sK + n0, TS, LC, acc, lane);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        *reinterpret_cast<__nv_bfloat162*>(W + (row0 + m0 + g + h * 8) * LK + n0 + nt * 8 + 2 * tq) = __floats2bfloat162_rn(acc[nt][2 * h], acc[nt][2 * h + 1]);
+  }
+#pragma unroll 1
+  for (int vb = 0; vb < DV / 128; ++vb) {   // U = (T diag(beta)) V, 128 value columns at a time (the Q tile's buffer holds them)
+    __syncthreads();
+    copy_tile(in.v + tok0 * in.v_tok + static_cast<long>(hv) * DV + vb * 128, in.v_tok, sV);
+    __syncthreads();
+    float acc[8][4];
+    zero_acc(acc);
+    wgemm<8, false, true>(sUh + m0 * MS, MS, sV + n0, TS, LC, acc, lane);
+    wgemm<8, false, true>(sUl + m0 * MS, MS, sV + n0, TS, LC, acc, lane);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+        *reinterpret_cast<__nv_bfloat162*>(U + (row0 + m0 + g + h * 8) * DV + vb * 128 + n0 + nt * 8 + 2 * tq) = __floats2bfloat162_rn(acc[nt][2 * h], acc[nt][2 * h + 1]);
+  }
+}
 
 int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
                   const unsigned char* start, int B, int L, int Hv, int Hk, int dv, const void* U, const void* W, const void* dU,
@@ -935,6 +604,7 @@ int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long 
                   float* dq, float* dk, void* dq16, void* dk16, long qk_tok, void* dvv, long dv_tok, float* dg, float* dbeta, cudaStream_t st) {
   if (L % LC || (dv != 128 && dv != 256) || Hv % Hk || n_part != dv / 128) return 1;
   if (dq16 ? (Hv != Hk || !dk16 || qk_tok % 2) : (!dq || !dk)) return 1;
+  if (dv_tok % 2) return 1;
   LocalIn in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), q_tok, k_tok, v_tok,
              g, beta, start, L, Hv, Hv / Hk};
   LocalGrads gr{static_cast<const __nv_bfloat16*>(U), static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(dU), dWp, dQp, dKp,
@@ -943,27 +613,36 @@ int gdn_local_bwd(const void* q, const void* k, const void* v, long q_tok, long 
   dim3 grid(L / LC, Hv, B);
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(gdn_local_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(LOCAL_BWD_SMEM));
-    cudaFuncSetAttribute(gdn_local_bwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(LOCAL_BWD_SMEM));
+    cudaFuncSetAttribute(gdn_local_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(BwdSmem::TOTAL));
+    cudaFuncSetAttribute(gdn_local_bwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(BwdSmem::TOTAL));
+    cudaFuncSetAttribute(gdn_local_bwd_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(gdn_local_bwd_kernel<256>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr = true;
   }
-  static int version = 0;
-  if (!version) { const char* e = getenv("GHB_GDN_LOCAL"); version = (e && e[0] == '1') ? 1 : 2; }
-  if (version == 2) {
-    static bool attr2 = false;
-    if (!attr2) {
-      cudaFuncSetAttribute(gdn_local_bwd2_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Bwd2Smem::TOTAL));
-      cudaFuncSetAttribute(gdn_local_bwd2_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Bwd2Smem::TOTAL));
-      cudaFuncSetAttribute(gdn_local_bwd2_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-      cudaFuncSetAttribute(gdn_local_bwd2_kernel<256>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-      attr2 = true;
-    }
-    if (dv == 128) gdn_local_bwd2_kernel<128><<<grid, 256, Bwd2Smem::TOTAL, st>>>(in, gr);
-    else gdn_local_bwd2_kernel<256><<<grid, 256, Bwd2Smem::TOTAL, st>>>(in, gr);
-    return cudaGetLastError() == cudaSuccess ? 0 : 4;
+  if (dv == 128) gdn_local_bwd_kernel<128><<<grid, 256, BwdSmem::TOTAL, st>>>(in, gr);
+  else gdn_local_bwd_kernel<256><<<grid, 256, BwdSmem::TOTAL, st>>>(in, gr);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+int gdn_local_fwd(const void* q, const void* k, const void* v, long q_tok, long k_tok, long v_tok, const float* g, const float* beta,
+                  const unsigned char* start, int B, int L, int Hv, int Hk, int dv, void* U, void* W, void* Aqk, void* Qin, void* Kout,
+                  float* carry, cudaStream_t st) {
+  if (L % LC || (dv != 128 && dv != 256) || Hv % Hk) return 1;
+  LocalIn in{static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), q_tok, k_tok, v_tok,
+             g, beta, start, L, Hv, Hv / Hk};
+  dim3 grid(L / LC, Hv, B);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(gdn_local_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FwdSmem::TOTAL));
+    cudaFuncSetAttribute(gdn_local_fwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(FwdSmem::TOTAL));
+    cudaFuncSetAttribute(gdn_local_fwd_kernel<128>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(gdn_local_fwd_kernel<256>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    attr = true;
   }
-  if (dv == 128) gdn_local_bwd_kernel<128><<<grid, 256, LOCAL_BWD_SMEM, st>>>(in, gr);
-  else gdn_local_bwd_kernel<256><<<grid, 256, LOCAL_BWD_SMEM, st>>>(in, gr);
+  auto* u = static_cast<__nv_bfloat16*>(U); auto* w = static_cast<__nv_bfloat16*>(W); auto* a = static_cast<__nv_bfloat16*>(Aqk);
+  auto* qi = static_cast<__nv_bfloat16*>(Qin); auto* ko = static_cast<__nv_bfloat16*>(Kout);
+  if (dv == 128) gdn_local_fwd_kernel<128><<<grid, 256, FwdSmem::TOTAL, st>>>(in, u, w, a, qi, ko, carry);
+  else gdn_local_fwd_kernel<256><<<grid, 256, FwdSmem::TOTAL, st>>>(in, u, w, a, qi, ko, carry);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
