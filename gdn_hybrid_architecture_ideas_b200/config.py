@@ -676,7 +676,7 @@ _TRAIN_BUILT = {
     "loss.normalization": ("global_token_mean",),
     "loss.ce_form": ("standard",),
     "head_impl": ("fused", "chunked"),
-    "activation_checkpoint": ("none", "layer", "block"),
+    "activation_checkpoint": ("none", "layer", "block", "host", "host_overlap"),
     "freeze_trunk": (False,),
     "precision_switch": (False,),
     "cuda_graphs": ("none", "microbatch", "step"),

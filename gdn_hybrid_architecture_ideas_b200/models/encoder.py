@@ -13,10 +13,10 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-import torch.utils.checkpoint as ckpt
 
 from .. import ops
 from ..config import ModelConfig
+from . import act_checkpoint
 from .attention import GatedAttention
 from .depth_mix import EntryLayer
 from .gdn import READ_MIX_VARIANTS, GatedDeltaNet, GDNArms
@@ -91,6 +91,7 @@ class Encoder(nn.Module):
         self.block = enc.full_attn_interval
         self.block_entry = enc.attn_res == "block_entry"
         self.activation_checkpoint = "none"
+        self.host_pool = None
         d, eps, S, n = cfg.d_model, cfg.norm_eps, self.block, enc.n_layers
         if self.block_entry:
             if S <= 0 or n % S:
@@ -110,13 +111,31 @@ class Encoder(nn.Module):
             raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none' or 'layer'")
 
     def _run(self, layer, x, ctx, cache, sources, need_state):
-        """One layer call, wrapped in activation checkpointing when that is on for a gradient-tracking forward."""
-        if self.activation_checkpoint == "layer" and cache is None and torch.is_grad_enabled() and x.requires_grad:
+        """One layer call under the stack's activation memory mode (models/act_checkpoint.py)."""
+        mode = self.activation_checkpoint
+        training = cache is None and torch.is_grad_enabled() and x.requires_grad
+        if mode == "layer" and training:
             def call(x_, *src):
                 return layer(x_, ctx, None, list(src) if src else None, False)[0]
-            y = ckpt.checkpoint(call, x, *(sources or ()), use_reentrant=False)
-            return y, None
+            return act_checkpoint.run_checkpointed(call, x, *(sources or ())), None
+        if mode in ("host", "host_overlap") and training:
+            if self.host_pool is None or self.host_pool.device != x.device:
+                self.host_pool = act_checkpoint.HostPool(x.device, overlap=mode == "host_overlap")
+            with self.host_pool.offload():
+                return layer(x, ctx, cache, sources, need_state)
         return layer(x, ctx, cache, sources, need_state)
+
+    def _run_block(self, b, x, ctx, sources):
+        """The layers of block b as one recomputed unit ("block" mode)."""
+        S = self.block
+        layers = [self.layers[i] for i in range(b * S, (b + 1) * S)]
+
+        def call(x_, *src):
+            for layer in layers:
+                use = list(src) if getattr(layer, "gdn_arms", None) is not None else None
+                x_ = layer(x_, ctx, None, use, False)[0]
+            return x_
+        return act_checkpoint.run_checkpointed(call, x, *sources)
 
     def forward(self, x: torch.Tensor, ctx: SeqContext, caches: list | None = None, need_state: bool = True):
         """x: embedding-stage output (B, L, d). Returns (stream entering final_norm, per-layer caches)."""
@@ -135,6 +154,11 @@ class Encoder(nn.Module):
             if b > 0 and first.stream_bf16:
                 start = round_stream(start)
             x = start
+            if self.activation_checkpoint == "block" and caches is None and torch.is_grad_enabled() and x.requires_grad:
+                x = self._run_block(b, x, ctx, sources)
+                new_caches.extend([None] * S)
+                sources = sources + [x - start]
+                continue
             for i in range(b * S, (b + 1) * S):
                 layer = self.layers[i]
                 src = sources if getattr(layer, "gdn_arms", None) is not None else None

@@ -152,3 +152,32 @@ def test_sigterm_saves_and_resumes(tmp_path):
     assert 0 < step < 4000
     t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
     assert t.resume_from_checkpoint() and t.step == step
+
+
+@pytest.mark.parametrize("mode", ["layer", "block", "host"])
+def test_activation_memory_modes_give_the_same_gradients(mode):
+    """Recomputing layers or blocks, or parking saved activations in the host pool, changes no gradient."""
+    from gdn_hybrid_architecture_ideas_b200.models import act_checkpoint, build_model
+
+    cfg = C.tiny_full_config()
+    torch.manual_seed(0)
+    tok = torch.randint(1, cfg.vocab_size, (2, 24))
+    doc = torch.zeros_like(tok)
+    grads = {}
+    for m in ("none", mode):
+        torch.manual_seed(1)
+        model = build_model(cfg)
+        model.encoder.activation_checkpoint = m
+        if m == "host":
+            model.encoder.host_pool = act_checkpoint.HostPool(torch.device("cpu"), min_bytes=0)
+        model(tok, doc).logits.float().square().mean().backward()
+        grads[m] = {k: p.grad.clone() for k, p in model.named_parameters() if p.grad is not None}
+        if m == "host":
+            st = model.encoder.host_pool.stats
+            assert st["packed"] > 0 and 0 < st["unpacked"] <= st["packed"] and st["allocated"] <= st["packed"]
+            del model
+            import gc
+            gc.collect()
+    assert grads["none"].keys() == grads[mode].keys()
+    for k in grads["none"]:
+        assert torch.allclose(grads["none"][k], grads[mode][k], atol=1e-6, rtol=1e-5), k
