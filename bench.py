@@ -43,6 +43,7 @@ def parse():
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU, help="rows per GPU per step")
     ap.add_argument("--sharding", default="auto", help="replicated | zero1 | zero2 | auto (zero2 when N > 1)")
     ap.add_argument("--comm", default="auto", help="fused | nccl | auto")
+    ap.add_argument("--graphs", action="store_true", help="replay the micro-batch as a CUDA graph after warm-up")
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="tp: tensor parallel over all ranks with a sequence-parallel stream (--rows is then the whole job's rows per step)")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "collective"], help="tp: fused peer-memory GEMMs or NCCL collectives around plain GEMMs")
@@ -135,6 +136,8 @@ def run_ours(args) -> dict:
     cfg.optimizer_sharding = ("zero2" if world > 1 and not tp else "replicated") if args.sharding == "auto" else args.sharding
     if args.comm != "auto":
         os.environ["GHB_COMM"] = args.comm
+    if args.graphs:
+        cfg.cuda_graphs = "microbatch"
     trainer = Trainer(cfg, None, dp)
     dev = trainer.device
     for _ in range(args.warmup):
@@ -182,7 +185,7 @@ def run_ours(args) -> dict:
                    "seq_len": args.seq_len,
                    "parallelism": (f"tp{world}-sp-{args.tp_impl}" if tp else f"dp{world}" + ("" if world == 1 else f"-{cfg.optimizer_sharding}")),
                    "optimizer": "adamw", "vocab": VOCAB, "l2": "per-step working set (GBs of activations) >> 126 MB L2",
-                   "comm": os.environ.get("GHB_COMM", "auto"), "loss": m["loss"]},
+                   "comm": os.environ.get("GHB_COMM", "auto"), "cuda_graphs": cfg.cuda_graphs, "loss": m["loss"]},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": trainer.h2d_bytes, "d2h_bytes_per_step": trainer.d2h_bytes},

@@ -43,6 +43,19 @@ class Batch:
             moved[name] = t.to(device, non_blocking=non_blocking) if isinstance(t, torch.Tensor) else t
         return Batch(single_doc=self.single_doc, **moved)
 
+    _TENSORS = ("tokens", "targets", "target_valid", "doc_ids", "dec_mask", "multi_targets", "multi_valid", "loss_mask")
+
+    def clone_static(self) -> "Batch":
+        """A copy on fixed buffers (CUDA-graph replay reads its inputs from them)."""
+        got = {n: (getattr(self, n).clone() if isinstance(getattr(self, n), torch.Tensor) else getattr(self, n)) for n in self._TENSORS}
+        return Batch(single_doc=self.single_doc, **got)
+
+    def copy_from(self, other: "Batch") -> None:
+        for n in self._TENSORS:
+            mine, theirs = getattr(self, n), getattr(other, n)
+            if isinstance(mine, torch.Tensor):
+                mine.copy_(theirs, non_blocking=True)
+
     def h2d_bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in (self.tokens, self.targets, self.target_valid, self.doc_ids)
                    if isinstance(t, torch.Tensor))

@@ -109,6 +109,11 @@ class Trainer:
             self.run_dir.mkdir(parents=True, exist_ok=True)
         if cfg.init_from:
             self.init_from_checkpoint(cfg.init_from)
+        self.graphs = None
+        if cfg.cuda_graphs != "none":
+            from .cuda_graphs import GraphRunner
+
+            self.graphs = GraphRunner(self)
 
     # ------------------------------------------------------------------ construction
 
@@ -150,8 +155,11 @@ class Trainer:
 
     # ------------------------------------------------------------------ one step
 
-    def _micro_loss(self, mb, n_global: int):
+    def _micro_loss(self, mb, n_global):
+        """n_global: the number of valid targets over all ranks (int), or a 0-dim device tensor holding its inverse
+        (CUDA-graph replay: the normaliser must not be baked into the graph)."""
         cfg = self.cfg
+        inv = n_global if isinstance(n_global, torch.Tensor) else 1.0 / n_global
         z = cfg.loss.z_loss
         s = mb.tokens.shape[2] if mb.tokens.dim() == 3 else 1
         kw = {}
@@ -168,8 +176,8 @@ class Trainer:
 
             w = bag_weights(s).to(hidden.device)
             targets = mb.multi_targets
-            a = mb.multi_valid.to(torch.float32) * w / n_global
-            b = mb.multi_valid.any(-1).to(torch.float32) * (z / n_global)
+            a = mb.multi_valid.to(torch.float32) * w * inv
+            b = mb.multi_valid.any(-1).to(torch.float32) * (z * inv)
         else:
             targets = mb.targets
             valid = mb.target_valid.to(torch.float32)
@@ -177,7 +185,7 @@ class Trainer:
                 per = targets.numel() // self.tp.world
                 cut = slice(self.tp.rank * per, (self.tp.rank + 1) * per)
                 targets, valid = targets.reshape(-1)[cut][None], valid.reshape(-1)[cut][None]
-            a, b = valid / n_global, valid * (z / n_global)
+            a, b = valid * inv, valid * (z * inv)
         W = self.model.head_weight()
         if cfg.head_impl == "fused":
             loss, ce, _ = fused_linear_ce(hidden, W, targets, a, b, cfg.head_chunk, self.model.head_weight_lp)
@@ -202,9 +210,13 @@ class Trainer:
         ce_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         for lo in range(0, rows, micro):
             mb = batch if micro == rows else _slice(batch, lo, lo + micro)
-            loss, ce = self._micro_loss(mb, max(n_global, 1))
-            loss.backward()
-            loss_sum += loss.detach().float()
+            if self.graphs is not None:
+                loss, ce = self.graphs.micro(mb, n_global)
+                loss_sum += loss
+            else:
+                loss, ce = self._micro_loss(mb, max(n_global, 1))
+                loss.backward()
+                loss_sum += loss.detach().float()
             ce_sum += ce.float()
         stats = torch.stack([loss_sum, ce_sum]).double()
         if self.zero is not None:
