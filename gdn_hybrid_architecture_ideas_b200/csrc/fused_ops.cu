@@ -33,47 +33,101 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
 }
 
 // ================================================================================================ GDN input prep
-// Work unit: one token x one group of 128 channels (a q head, a k head, or a 128-wide slice of v); one warp per unit,
-// 4 channels per lane. K = 4 taps. doc == nullptr means every row is a single document (only t - j >= 0 is checked).
-// Channels [0, nq) are q (norm + scale), [nq, 2nq) are k (norm), the rest v (no norm). dk must be 128.
+// Channels come in groups of 128 (a q head, a k head, or a 128-wide slice of v). K = 4 taps. doc == nullptr means every
+// row is a single document (only t - j >= 0 is checked). Channels [0, nq) are q (norm + scale), [nq, 2nq) are k (norm),
+// the rest v (no norm). dk must be 128.
 constexpr int PREP_K = 4;
 
-__device__ __forceinline__ void conv_taps(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, long row, int t, int C,
-                                          int c, const float* __restrict__ w, float (&out)[4]) {
-  float wt[4][PREP_K];
+// Forward: half a warp walks TOK consecutive tokens of one 128-channel group, 8 channels per lane (16-byte loads and
+// stores), keeping the last K inputs in registers so every input row is read once; the next token's row is fetched
+// while the current one is computed. The L2 norm of a q or k head is a reduction over the 16 lanes of the half-warp.
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
-  for (int e = 0; e < 4; ++e) { float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c + e) * PREP_K); wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w; }
-  out[0] = out[1] = out[2] = out[3] = 0.f;
-  const int my_doc = doc ? doc[row] : 0;
+  for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float (&v)[8]) {
+  uint32_t w[4];
 #pragma unroll
-  for (int j = 0; j < PREP_K; ++j) {   // tap j looks j steps back and uses weight column K-1-j
-    if (t - j < 0) break;
-    if (doc && doc[row - j] != my_doc) break;   // document ids increase along a row: once different, always different
-    float x[4]; ld4(u + (row - j) * C + c, x);
+  for (int e = 0; e < 4; ++e) { __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]); w[e] = *reinterpret_cast<uint32_t*>(&h); }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ float hsum16(float v) {       // sum over the 16 lanes of a half-warp
 #pragma unroll
-    for (int e = 0; e < 4; ++e) out[e] += x[e] * wt[e][PREP_K - 1 - j];
-  }
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
 }
 
-__global__ void gdn_prep_fwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
-                                    __nv_bfloat16* __restrict__ out, long rows, int L, int C, int nq, float qscale) {
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(256) gdn_prep_fwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ out, long rows, int L, int C, int nq, float qscale, int tok_per_unit) {
+  const int lane16 = threadIdx.x & 15;
   const int groups = C / 128;
-  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= rows * groups) return;
-  const long row = unit / groups; const int grp = static_cast<int>(unit % groups);
-  const int t = static_cast<int>(row % L), c = grp * 128 + lane * 4;
-  float a[4];
-  conv_taps(u, doc, row, t, C, c, w, a);
+  const long chunks = (rows + tok_per_unit - 1) / tok_per_unit;
+  const long unit = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;      // one half-warp per unit
+  const bool live = unit < chunks * groups;                                                // dead half-warps still join the shuffles
+  const long chunk = live ? unit / groups : 0; const int grp = live ? static_cast<int>(unit % groups) : 0;
+  const int c = grp * 128 + lane16 * 8;
+  float wt[8][PREP_K];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) a[e] = a[e] * sigm(a[e]);
-  if (c < 2 * nq) {
-    float ss = wsum(a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3]);
-    const float r = rsqrtf(ss + 1e-6f) * (c < nq ? qscale : 1.f);
+  for (int e = 0; e < 8; ++e) { const float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c + e) * PREP_K); wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w; }
+  const long r0 = chunk * tok_per_unit, r1 = live ? min(rows, r0 + tok_per_unit) : r0;
+  float win[PREP_K][8];            // win[j] = u[s - j]
+  int dd[PREP_K];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) a[e] *= r;
+  for (int j = 0; j < PREP_K; ++j) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) win[j][e] = 0.f;
+    dd[j] = -1;
   }
-  st4(out + row * C + c, a);
+#pragma unroll
+  for (int j = 1; j < PREP_K; ++j)
+    if (live && r0 - j >= 0) { ld8(u + (r0 - j) * C + c, win[j - 1]); dd[j - 1] = doc ? doc[r0 - j] : 0; }
+  float nu[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int ndoc = 0;
+  if (r0 < r1) { ld8(u + r0 * C + c, nu); ndoc = doc ? doc[r0] : 0; }
+  const bool normed = c < 2 * nq;
+  const float s_norm = c < nq ? qscale : 1.f;
+  const long mine = r1 - r0, other = __shfl_xor_sync(0xffffffffu, mine, 16);
+  const long steps = mine > other ? mine : other;
+  for (long k = 0; k < steps; ++k) {          // both halves of the warp run the same number of steps (the shuffles need every lane)
+    const long s = r0 + k;
+    const bool on = s < r1;
+#pragma unroll
+    for (int j = PREP_K - 1; j > 0; --j) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[j][e] = win[j - 1][e];
+      dd[j] = dd[j - 1];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) win[0][e] = nu[e];
+    dd[0] = ndoc;
+    if (s + 1 < r1) { ld8(u + (s + 1) * C + c, nu); ndoc = doc ? doc[s + 1] : 0; }
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (on) {
+      const int t = static_cast<int>(s % L);
+#pragma unroll
+      for (int j = 0; j < PREP_K; ++j) {
+        if (t - j < 0 || (doc && dd[j] != dd[0])) break;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += win[j][e] * wt[e][PREP_K - 1 - j];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] = a[e] * sigm(a[e]);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += a[e] * a[e];
+    ss = hsum16(ss);
+    if (on) {
+      if (normed) {
+        const float r = rsqrtf(ss + 1e-6f) * s_norm;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] *= r;
+      }
+      st8(out + s * C + c, a);
+    }
+  }
 }
 
 // Backward, one pass: a warp walks TOK consecutive tokens of one 128-channel group (4 channels per lane). At token s it
@@ -187,8 +241,9 @@ __global__ void gdn_prep_bwd_kernel(const __nv_bfloat16* __restrict__ u, const i
 
 int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long rows, int L, int C, int nq, float qscale, cudaStream_t st) {
   if (C % 128 || nq % 128) return 1;
-  const long units = rows * (C / 128);
-  gdn_prep_fwd_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<__nv_bfloat16*>(out), rows, L, C, nq, qscale);
+  const int tok = 64;
+  const long units = ((rows + tok - 1) / tok) * (C / 128);          // half-warps
+  gdn_prep_fwd_kernel<<<static_cast<unsigned>((units + 15) / 16), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<__nv_bfloat16*>(out), rows, L, C, nq, qscale, tok);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* du, float* dw, long rows, int L, int C,

@@ -31,7 +31,9 @@ constexpr int BM = 128, BK = 64, UK = 16, BN = 256;
 constexpr int THREADS = 192;
 constexpr int STAGES = 4;
 constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
+constexpr uint32_t STG_ROW = 144;      // bytes per staged row: 64 bf16 + 16 bytes of padding (conflict-free 16-byte accesses)
+constexpr uint32_t STG_BYTES = 4 * 32 * STG_ROW;   // RS epilogue staging: 4 warps x 32 rows
+constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + 256 + STG_BYTES + 1024;
 constexpr uint32_t TMEM_COLS = 2 * BN;
 constexpr int MAXR = 8;
 constexpr unsigned long long WAIT_NS = 2000000000ull;
@@ -117,9 +119,19 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       __nv_bfloat16* dst = a.xg[d] + a.rank * a.shard_rows * a.ld;
       for (long c = blockIdx.x; c < chunks_per_shard; c += a.n_push) {
         const long total = CHUNK * vec_per_row;
-        for (long i = threadIdx.x; i < total; i += blockDim.x) {
-          const long r = c * CHUNK + i / vec_per_row, v = i % vec_per_row;
-          reinterpret_cast<uint4*>(dst + r * a.ld)[v] = reinterpret_cast<const uint4*>(src + r * a.ld)[v];
+        constexpr int UNROLL = 8;                              // loads in flight per thread: the copy is latency-bound otherwise
+        for (long i0 = threadIdx.x; i0 < total; i0 += static_cast<long>(blockDim.x) * UNROLL) {
+          uint4 v[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long i = i0 + static_cast<long>(u) * blockDim.x;
+            if (i < total) v[u] = reinterpret_cast<const uint4*>(src + (c * CHUNK + i / vec_per_row) * a.ld)[i % vec_per_row];
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long i = i0 + static_cast<long>(u) * blockDim.x;
+            if (i < total) reinterpret_cast<uint4*>(dst + (c * CHUNK + i / vec_per_row) * a.ld)[i % vec_per_row] = v[u];
+          }
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -140,6 +152,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint8_t* stg = smem + STAGES * (A_BYTES + B_BYTES) + 256;
 
   const int first = a.mode == 0 ? a.n_push : 0;
   const int cta = static_cast<int>(blockIdx.x) - first, n_cta = static_cast<int>(gridDim.x) - first;
@@ -233,7 +246,6 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const long row = static_cast<long>(tm) * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      __nv_bfloat16* rs_row = nullptr;
       if (a.mode == 1) {
         const int d = static_cast<int>((static_cast<long>(tm) * BM) / a.shard_rows);
         if (!((dest_ok >> d) & 1u)) {
@@ -243,8 +255,40 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           if (!good) { if (lane == 0) atomicExch(err, 507); ok = false; }
           dest_ok |= 1u << d;
         }
-        rs_row = a.stage[d] + ((static_cast<long>(a.rank) * a.shard_rows + (row - d * a.shard_rows)) * N);
       }
+      if (a.mode == 1) {
+        // RS: 64 columns at a time through shared memory, so that every peer store instruction covers 4 rows x 128
+        // contiguous bytes (a thread's own row segments would go out as isolated 16-byte writes over NVLink)
+        uint8_t* ws = stg + quad * 32 * STG_ROW;
+        const int d = static_cast<int>((static_cast<long>(tm) * BM) / a.shard_rows);
+        __nv_bfloat16* tile0 = a.stage[d] + (static_cast<long>(a.rank) * a.shard_rows + (static_cast<long>(tm) * BM + quad * 32 - d * a.shard_rows)) * N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t r[64];
+          tmem_ld_x32(taddr + c * 64, r);
+          tmem_ld_x32(taddr + c * 64 + 32, r + 32);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            uint32_t p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
+              p[e] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(ws + lane * STG_ROW + v * 16) = make_uint4(p[0], p[1], p[2], p[3]);
+          }
+          __syncwarp();
+          const int col0 = n0 + c * 64 + (lane & 7) * 8;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4*>(ws + rr * STG_ROW + (lane & 7) * 16);
+            if (ok && col0 < N) *reinterpret_cast<uint4*>(tile0 + static_cast<long>(rr) * N + col0) = v;
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -252,8 +296,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         tmem_ld_wait();
         const int col = n0 + c * 32;
         if (ok && row < M && col < N) {
-          if (a.mode == 1 || OUT == 0) {
-            __nv_bfloat16* out = a.mode == 1 ? rs_row + col : reinterpret_cast<__nv_bfloat16*>(Cout) + row * ldc + col;
+          if (OUT == 0) {
+            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Cout) + row * ldc + col;
             if (col + 32 <= N) {
               uint4* o4 = reinterpret_cast<uint4*>(out);
 #pragma unroll
@@ -286,6 +330,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             }
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
@@ -401,7 +446,7 @@ int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda
   if (a.world > tp::MAXR || a.world < 1) return 1;
   if (a.mode != 2) {
     if (a.shard_rows % tp::CHUNK) return 17;
-    if (a.mode == 0 && (a.row_elems % 8 || a.ld % 8 || a.n_push < 1 || a.n_push >= sms)) return 18;
+    if (a.mode == 0 && (a.row_elems % 8 || a.ld % 8 || a.n_push < (a.push ? 1 : 0) || a.n_push >= sms)) return 18;
     if (a.mode == 0 && a.axis == 0 && static_cast<long>(M) != a.shard_rows * a.world) return 19;
     if (a.mode == 0 && a.axis == 1 && static_cast<long>(K) != a.shard_rows * a.world) return 19;
     if (a.mode == 1 && (static_cast<long>(M) != a.shard_rows * a.world || N % 8)) return 19;

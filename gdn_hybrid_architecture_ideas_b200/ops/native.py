@@ -102,6 +102,20 @@ def _pad_rows(w: torch.Tensor, mult: int = 8) -> torch.Tensor:
     return out
 
 
+# `wgrad_accum: fp32`: weight-gradient GEMMs add straight into the parameter's fp32 main gradient (the epilogue's
+# accumulate mode) and autograd receives no weight gradient, instead of producing a tensor that autograd then adds
+# (reference: ced/train/wgrad_accum.py:87-369).
+WGRAD_INTO_MAIN = False
+
+
+def _wgrad(dy2, x2, weight, n):
+    main = getattr(weight, "main_grad", None) if WGRAD_INTO_MAIN else None
+    if main is not None and main.dtype == torch.float32 and main.shape[0] == n and dy2.shape[1] == n:
+        gemm(dy2, x2, out=main, a_mn=True, b_mn=True, accumulate=True)
+        return None
+    return gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)[:n]
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, w_lp):
@@ -112,7 +126,7 @@ class _Linear(torch.autograd.Function):
         w_lp = _pad_rows(w_lp)
         y = gemm(x2, w_lp)
         ctx.save_for_backward(x2, w_lp)
-        ctx.xshape, ctx.xdtype, ctx.n = x.shape, x.dtype, n
+        ctx.xshape, ctx.xdtype, ctx.n, ctx.weight = x.shape, x.dtype, n, weight
         if n != w_lp.shape[0]:
             y = y[:, :n]
         return y.reshape(*x.shape[:-1], n)
@@ -131,7 +145,7 @@ class _Linear(torch.autograd.Function):
             if ctx.xdtype != BF16:
                 dx = dx.to(ctx.xdtype)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=torch.float32)[:ctx.n]   # dy^T [N,M] . x [M,K]
+            dw = _wgrad(dy2, x2, ctx.weight, ctx.n)          # dy^T [N,M] . x [M,K]
         return dx, dw, None
 
 

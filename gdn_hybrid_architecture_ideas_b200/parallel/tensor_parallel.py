@@ -83,13 +83,14 @@ class TensorParallel:
         self.slot_seq = [0] * N_GATHER_SLOTS
         self.next_slot = 0
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", "16"))
+        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", "32"))
         torch.cuda.synchronize(self.device)
         dp.barrier()
 
     # ------------------------------------------------------------------ argument table
 
     def _args(self, mode, slot=0, seq=0, need=0, push=0, axis=0, shard_rows=0, row_elems=0, ld=8, stage_slot=0):
+        n_push = self.n_push if push else 0        # a later consumer of a gather multiplies on every SM
         def peers(key, offset_bytes):
             got = [p + offset_bytes for p in self._ptrs[key]]
             return got + [0] * (MAXR - len(got))
@@ -98,7 +99,7 @@ class TensorParallel:
         c_off = slot * self.n_chunks * 4
         s_off = stage_slot * self.max_tokens * self.max_width * 2
         raw = struct.pack(_ARGS_FMT, *peers("g", g_off), *peers("c", c_off), *peers("p", 0), self.rank, self.world, mode, push, axis,
-                          shard_rows, row_elems, ld, seq, need, self.n_push, *peers("s", s_off), self.done_counter.data_ptr())
+                          shard_rows, row_elems, ld, seq, need, n_push, *peers("s", s_off), self.done_counter.data_ptr())
         return torch.frombuffer(bytearray(raw), dtype=torch.uint8)
 
     # ------------------------------------------------------------------ gather handles

@@ -95,6 +95,7 @@ class FlatBuffers:
             view.copy_(p.data)
             p.data = view
             p.grad = self.grads[s.offset:s.offset + s.numel].view(s.shape)
+            p.main_grad = p.grad        # where weight-gradient GEMMs may accumulate directly (`wgrad_accum: fp32`)
             self.by_name[s.name] = s
         if self.lp is not None:
             self.refresh_lp()
@@ -119,6 +120,7 @@ class FlatBuffers:
             p = named[s.name]
             p.data = params[s.offset:s.offset + s.numel].view(s.shape)
             p.grad = grads[s.offset:s.offset + s.numel].view(s.shape)
+            p.main_grad = p.grad
             owner, _, leaf = s.name.rpartition(".")
             if lp is not None and leaf == "weight" and hasattr(mods.get(owner), "weight_lp"):
                 mods[owner].weight_lp = lp[s.offset:s.offset + s.numel].view(s.shape)
@@ -143,6 +145,7 @@ class FlatBuffers:
         """Point every parameter's .grad at its flat view again (after something set it to None)."""
         for n, p in model.named_parameters():
             p.grad = self.view(self.grads, n)
+            p.main_grad = p.grad
 
 
 class FlatAdamW:

@@ -109,6 +109,15 @@ class Trainer:
             self.run_dir.mkdir(parents=True, exist_ok=True)
         if cfg.init_from:
             self.init_from_checkpoint(cfg.init_from)
+        if self.native:
+            from ..ops import native as _native_ops
+
+            _native_ops.WGRAD_INTO_MAIN = cfg.wgrad_accum == "fp32"
+        self.zero_wgrad = None
+        if cfg.log_zero_wgrad_every:
+            from .zero_wgrad import ZeroWgradMonitor
+
+            self.zero_wgrad = ZeroWgradMonitor(self.model)
         self.graphs = None
         if cfg.cuda_graphs != "none":
             from .cuda_graphs import GraphRunner
@@ -268,6 +277,8 @@ class Trainer:
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        if self.zero_wgrad is not None and self.step % cfg.log_zero_wgrad_every == 0:
+            m.update(self.zero_wgrad.summary())
         self.last_metrics = m
         if not math.isfinite(loss_v):
             self._halt_diverged(m)

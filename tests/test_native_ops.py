@@ -390,3 +390,26 @@ def test_cuda_graph_training_matches_eager():
     assert max(abs(a - b) for a, b in zip(l0, l1)) < 2e-2, (l0, l1)
     diff = (p0 - p1).abs()
     assert diff.max().item() < 1e-3 and diff.mean().item() < 2e-5, (diff.max().item(), diff.mean().item())
+
+
+def test_wgrad_accumulates_into_main_grad():
+    """`wgrad_accum: fp32`: the weight-gradient GEMM adds into the parameter's fp32 main gradient; autograd gets none."""
+    from gdn_hybrid_architecture_ideas_b200.models.linear import Linear
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    lin = Linear(256, 384).to(_dev())
+    x = torch.randn(200, 256, device=_dev(), dtype=torch.bfloat16, requires_grad=True)
+    go = torch.randn(200, 384, device=_dev(), dtype=torch.bfloat16)
+    lin(x).backward(go)
+    want = lin.weight.grad.clone()
+    lin.weight.grad = None
+    lin.weight.main_grad = torch.full_like(want, 0.5)
+    native.WGRAD_INTO_MAIN = True
+    try:
+        for _ in range(2):
+            lin(x).backward(go)
+    finally:
+        native.WGRAD_INTO_MAIN = False
+    assert lin.weight.grad is None
+    _close(lin.weight.main_grad, 2 * want + 0.5, 2e-2 * float(want.abs().max()), 1e-2, "main grad")
+    native.check_status()
