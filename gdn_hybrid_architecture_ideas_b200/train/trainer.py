@@ -118,6 +118,11 @@ class Trainer:
             from .zero_wgrad import ZeroWgradMonitor
 
             self.zero_wgrad = ZeroWgradMonitor(self.model)
+        self.prefetch = None
+        if cfg.data_prefetch:
+            from ..data.prefetch import BatchPrefetcher
+
+            self.prefetch = BatchPrefetcher(self.batch_at)
         self.graphs = None
         if cfg.cuda_graphs != "none":
             from .cuda_graphs import GraphRunner
@@ -258,7 +263,11 @@ class Trainer:
         step = self.step
         if self.tst is not None and self.tst.schedule.is_switch(step) and not cfg.tst.keep_optimizer_state:
             self.optimizer.reset_moments()
-        batch = self.batch_at(step)
+        if self.prefetch is not None:          # the batch was built by the background thread while the last step ran
+            batch = self.prefetch.get(step).batch
+            self.prefetch.start(step + 1)
+        else:
+            batch = self.batch_at(step)
         n_global, bad = self._global_counts(batch)
         if bad:
             self._halt_bad_batch(step)

@@ -167,9 +167,94 @@ def bench_rmsnorm(a):
     return {"op": "rmsnorm", "rows": a.rows, "d": a.d, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_gbs": n * 6 / ms_f / 1e6, "bwd_gbs": n * 10 / ms_b / 1e6}
 
 
+def bench_depth_mix(a):
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    rows, d, n = a.rows, a.d, a.sources
+    srcs = [torch.randn(1, rows, d, device="cuda", requires_grad=True) for _ in range(n)]
+    q = (torch.randn(d, device="cuda") * 0.1).requires_grad_()
+    gain = torch.zeros(d, device="cuda", requires_grad=True)
+    out = {}
+
+    def fwd():
+        out["y"] = ops.depth_mix(srcs, q, gain, 1e-6)
+
+    ms_f = timed(fwd, a.iters, a.warmup)
+    dy = torch.randn_like(out["y"])
+
+    def bwd():
+        out["y"].backward(dy, retain_graph=True)
+
+    ms_b = timed(bwd, a.iters, a.warmup)
+    nb = rows * d * 4
+    return {"op": "depth_mix", "rows": rows, "d": d, "sources": n, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_gbs": nb * (n + 1) / ms_f / 1e6,
+            "bwd_gbs": nb * (2 * n + 1) / ms_b / 1e6}
+
+
+def bench_swiglu(a):
+    rows, f = a.rows, a.ffn
+    gu = torch.randn(rows, 2 * f, device="cuda").to(BF16).requires_grad_()
+    out = {}
+
+    def fwd():
+        out["y"] = native._SiluMul.apply(gu)
+
+    ms_f = timed(fwd, a.iters, a.warmup)
+    dy = torch.randn_like(out["y"])
+
+    def bwd():
+        out["y"].backward(dy, retain_graph=True)
+
+    ms_b = timed(bwd, a.iters, a.warmup)
+    nb = rows * f * 2
+    return {"op": "swiglu", "rows": rows, "ffn": f, "fwd_ms": ms_f, "bwd_ms": ms_b, "fwd_gbs": nb * 3 / ms_f / 1e6, "bwd_gbs": nb * 5 / ms_b / 1e6}
+
+
+def bench_lm_head(a):
+    rows, d, V = a.rows, a.d, a.vocab
+    h = torch.randn(rows, d, device="cuda").to(BF16).requires_grad_()
+    W = (torch.randn(V, d, device="cuda") * 0.02).requires_grad_()
+    t = torch.randint(0, V, (rows, 1), device="cuda")
+    w = torch.full((rows, 1), 1.0 / rows, device="cuda")
+    b = torch.zeros(rows, device="cuda")
+    ms = timed(lambda: native.fused_linear_ce(h, W, t, w, b, 2048)[0].backward(), a.iters, a.warmup)
+    return {"op": "lm_head", "rows": rows, "d": d, "vocab": V, "fwd_bwd_ms": ms, "tflops": 6.0 * rows * d * V / ms / 1e9}
+
+
+def bench_adamw(a):
+    n = a.numel
+    p, g = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    lp = torch.empty(n, device="cuda", dtype=BF16)
+    ms = timed(lambda: native.adamw_(p, g, m, v, lp, 1e-3, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0), a.iters, a.warmup)
+    return {"op": "adamw", "numel": n, "ms": ms, "gbs": n * 30 / ms / 1e6}
+
+
+def bench_decode_attention(a):
+    from gdn_hybrid_architecture_ideas_b200.ops import native as nat
+    B, T, Hq, Hkv, hd = a.B, a.L, a.Hq, a.Hkv, 64
+    q = torch.randn(B, Hq, hd, device="cuda")
+    k = torch.randn(B, T, Hkv, hd, device="cuda").to(BF16)
+    v = torch.randn(B, T, Hkv, hd, device="cuda").to(BF16)
+    lens = torch.full((B,), T, dtype=torch.int32, device="cuda")
+    rot = 16
+    ang = torch.arange(max(a.cap, 1) + 1, device="cuda")[:, None] * (1e7 ** (-torch.arange(rot // 2, device="cuda") / (rot // 2)))[None]
+    cos_t, sin_t = ang.cos().float().contiguous(), ang.sin().float().contiguous()
+    out = torch.empty(B, Hq, hd, device="cuda", dtype=BF16)
+    splits = 16
+    po = torch.empty(B, Hq, splits, hd, device="cuda")
+    pml = torch.empty(B, Hq, splits, 2, device="cuda")
+    ms = timed(lambda: nat.ext().decode_attention(q, k, v, lens, None, cos_t, sin_t, out, po, pml, rot, a.cap, splits, hd ** -0.5), a.iters, a.warmup)
+    nb = 2 * B * T * Hkv * hd * 2
+    return {"op": "decode_attention", "B": B, "T": T, "Hq": Hq, "Hkv": Hkv, "ms": ms, "gbs": nb / ms / 1e6}
+
+
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("op", choices=["attention", "gdn", "gdn_prep", "gemm", "rmsnorm"])
+    p.add_argument("op", choices=["attention", "gdn", "gdn_prep", "gemm", "rmsnorm", "depth_mix", "swiglu", "lm_head", "adamw", "decode_attention"])
+    p.add_argument("--sources", type=int, default=4)
+    p.add_argument("--ffn", type=int, default=2816)
+    p.add_argument("--vocab", type=int, default=32768)
+    p.add_argument("--numel", type=int, default=1 << 28)
     p.add_argument("--layout", choices=["nt", "nn", "tn"], default="nt")
     p.add_argument("--iters", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
@@ -187,7 +272,9 @@ def main():
     p.add_argument("--rows", type=int, default=65536)
     p.add_argument("--d", type=int, default=1024)
     a = p.parse_args()
-    res = {"attention": bench_attention, "gdn": bench_gdn, "gdn_prep": bench_gdn_prep, "gemm": bench_gemm, "rmsnorm": bench_rmsnorm}[a.op](a)
+    res = {"attention": bench_attention, "gdn": bench_gdn, "gdn_prep": bench_gdn_prep, "gemm": bench_gemm, "rmsnorm": bench_rmsnorm,
+           "depth_mix": bench_depth_mix, "swiglu": bench_swiglu, "lm_head": bench_lm_head, "adamw": bench_adamw,
+           "decode_attention": bench_decode_attention}[a.op](a)
     print(json.dumps(res))
 
 

@@ -181,3 +181,14 @@ def test_activation_memory_modes_give_the_same_gradients(mode):
     assert grads["none"].keys() == grads[mode].keys()
     for k in grads["none"]:
         assert torch.allclose(grads["none"][k], grads[mode][k], atol=1e-6, rtol=1e-5), k
+
+
+def test_data_prefetch_trains_on_the_same_batches(tmp_path):
+    """Building step N + 1's batch on a background thread changes nothing about the run."""
+    def run(prefetch):
+        cfg = C.TrainConfig(model=C.tiny_full_config(), data=C.tiny_data_config())
+        cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device, cfg.data_prefetch = 3, 0, False, "cpu", prefetch
+        t = Trainer(cfg, None)
+        return [t.train_step()["loss"] for _ in range(3)]
+
+    assert run(False) == run(True)
