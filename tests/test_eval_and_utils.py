@@ -287,3 +287,20 @@ def test_eval_scripts_run_on_a_checkpoint(tmp_path):
     run(str(root / "scripts/eval_long.py"), "--checkpoint", str(tmp_path / "run"), "--docs", str(tmp_path / "long.pt"), "--base", "16",
         "--chunk", "16", "--gdn-diag", "--device", "cpu", "--out", str(tmp_path / "l.json"))
     assert json.loads((tmp_path / "l.json").read_text())["gdn_diag"]
+
+
+def test_build_eval_set_script(tmp_path):
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    (tmp_path / "docs.jsonl").write_text('{"text": "hello world"}\nplain line of text\n')
+    (tmp_path / "chat.jsonl").write_text(json.dumps({"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"}]}) + "\n")
+    run = lambda *a: subprocess.run([sys.executable, str(root / "scripts/build_eval_set.py"), *a], check=True, capture_output=True, timeout=300)
+    run("--input", str(tmp_path / "docs.jsonl"), "--out", str(tmp_path / "a.pt"))
+    run("--input", str(tmp_path / "chat.jsonl"), "--out", str(tmp_path / "b.pt"), "--chat")
+    a = torch.load(tmp_path / "a.pt", weights_only=False)["docs"]
+    b = torch.load(tmp_path / "b.pt", weights_only=False)["docs"]
+    assert [len(d["ids"]) for d in a] == [11, 18] and a[0]["ids"][:5] == list(b"hello")
+    assert sum(b[0]["scored"]) == 3 and len(b[0]["scored"]) == len(b[0]["ids"])
