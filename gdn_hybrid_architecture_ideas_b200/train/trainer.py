@@ -35,7 +35,7 @@ from .optim import build_optimizer, grad_norm
 EXIT_DIVERGED = 86
 
 
-from . import periodic_eval
+from . import bpb_readout, periodic_eval
 
 
 class Diverged(RuntimeError):
@@ -118,6 +118,7 @@ class Trainer:
             from .zero_wgrad import ZeroWgradMonitor
 
             self.zero_wgrad = ZeroWgradMonitor(self.model)
+        self._readout = None
         self.prefetch = None
         if cfg.data_prefetch:
             from ..data.prefetch import BatchPrefetcher
@@ -317,6 +318,12 @@ class Trainer:
                     if cfg.log_every and (m["step"] % cfg.log_every == 0 or self.step == end):
                         print(f"step {m['step']:6d} loss {m['loss']:.4f} lr {m['lr']:.2e} gnorm {m['grad_norm']:.3f} "
                               f"{m['tokens_per_s']:.0f} tok/s", flush=True)
+                if bpb_readout.due(cfg, self.step):
+                    if self._readout is None:
+                        self._readout = bpb_readout.BpbReadout(self)
+                    scores = self._readout.run()
+                    if self.lead and scores:
+                        self._jsonl({"event": "readout", "step": self.step, **scores})
                 if periodic_eval.due(cfg, self.step):
                     scores = periodic_eval.run_eval_sets(self)
                     if self.lead:

@@ -304,3 +304,20 @@ def test_build_eval_set_script(tmp_path):
     b = torch.load(tmp_path / "b.pt", weights_only=False)["docs"]
     assert [len(d["ids"]) for d in a] == [11, 18] and a[0]["ids"][:5] == list(b"hello")
     assert sum(b[0]["scored"]) == 3 and len(b[0]["scored"]) == len(b[0]["ids"])
+
+
+def test_bpb_readout_uses_fixed_rows(tmp_path):
+    from gdn_hybrid_architecture_ideas_b200.train.bpb_readout import BpbReadout, due
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    cfg = C.TrainConfig(model=C.tiny_full_config(), data=C.tiny_data_config())
+    cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device = 2, 0, True, "cpu"
+    cfg.eval.bpb_readout_sets, cfg.eval.bpb_readout_every, cfg.eval.bpb_readout_rows = {"held": "synthetic:6"}, 1, 3
+    assert due(cfg, 1) and not due(cfg, 0) or cfg.eval.bpb_readout_from == 0
+    t = Trainer(cfg, tmp_path / "r")
+    r = BpbReadout(t)
+    a, b = r.run(), r.run()
+    assert a == b and a["readout/held/bpb"] > 0 and len(r.sets["held"].chosen) == 3
+    t.fit()
+    lines = [json.loads(x) for x in (tmp_path / "r" / "metrics.jsonl").read_text().splitlines()]
+    assert sum(1 for x in lines if x.get("event") == "readout") == 2
