@@ -319,6 +319,47 @@ int64_t comm_peers_bytes() { return ghb::comm_peers_bytes(); }
 
 }  // namespace
 
+// ---- attention q / k preparation. q: [B, L, Hq, 64] view of the query projection (head stride 64 or 128 with the gate
+// interleaved), k: [B, L, Hkv, 64]; cos / sin: [B * L, R2] fp32 (R2 may be 0); cos_c / sin_c: [R2] or none.
+void attn_prep_fwd(const Tensor& q, const Tensor& k, const Tensor& wq, const Tensor& wk, const Tensor& cos, const Tensor& sin,
+                   const c10::optional<Tensor>& cos_c, const c10::optional<Tensor>& sin_c, double eps, Tensor& qr, const c10::optional<Tensor>& qf,
+                   Tensor& kr, const c10::optional<Tensor>& kf) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(is_bf16(q) && is_bf16(k) && q.dim() == 4 && k.dim() == 4 && q.size(3) == 64 && k.size(3) == 64 && q.stride(3) == 1 && k.stride(3) == 1 &&
+              k.stride(2) == 64 && q.stride(0) == q.stride(1) * q.size(1) && k.stride(0) == k.stride(1) * k.size(1), "attn_prep_fwd: q / k layout");
+  TORCH_CHECK(is_f32(wq) && is_f32(wk) && is_f32(cos) && is_f32(sin) && cos.is_contiguous() && sin.is_contiguous(), "attn_prep_fwd: fp32 gains and tables");
+  const long tokens = q.size(0) * q.size(1);
+  const int R2 = cos.numel() / std::max<long>(tokens, 1);
+  check(ghb::attn_prep_fwd(q.data_ptr(), q.stride(1), q.stride(2), k.data_ptr(), k.stride(1), wq.data_ptr<float>(), wk.data_ptr<float>(), cos.data_ptr<float>(),
+                           sin.data_ptr<float>(), fptr(cos_c), fptr(sin_c), q.size(2), k.size(2), R2, eps, tokens, qr.data_ptr(), vmut(qf), kr.data_ptr(), vmut(kf),
+                           sm_count(), stream()), "attn_prep_fwd");
+}
+void attn_prep_bwd(const Tensor& q, const Tensor& k, const Tensor& wq, const Tensor& wk, const Tensor& cos, const Tensor& sin,
+                   const c10::optional<Tensor>& cos_c, const c10::optional<Tensor>& sin_c, double eps, const Tensor& dqr, const c10::optional<Tensor>& dqf,
+                   const Tensor& dkr, const c10::optional<Tensor>& dkf, Tensor& dqraw, Tensor& dkraw, Tensor& dw) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(is_bf16(dqr) && dqr.is_contiguous() && is_bf16(dkr) && dkr.is_contiguous() && is_bf16(dqraw) && is_bf16(dkraw) && is_f32(dw) && dw.numel() == 128,
+              "attn_prep_bwd: layout");
+  TORCH_CHECK(dqraw.strides() == q.strides() && dkraw.strides() == k.strides(), "attn_prep_bwd: gradients laid out like the raw q / k");
+  const long tokens = q.size(0) * q.size(1);
+  const int R2 = cos.numel() / std::max<long>(tokens, 1);
+  check(ghb::attn_prep_bwd(q.data_ptr(), q.stride(1), q.stride(2), k.data_ptr(), k.stride(1), wq.data_ptr<float>(), wk.data_ptr<float>(), cos.data_ptr<float>(),
+                           sin.data_ptr<float>(), fptr(cos_c), fptr(sin_c), q.size(2), k.size(2), R2, eps, tokens, dqr.data_ptr(), optr(dqf), dkr.data_ptr(), optr(dkf),
+                           dqraw.data_ptr(), dkraw.data_ptr(), dw.data_ptr<float>(), sm_count(), stream()), "attn_prep_bwd");
+}
+
+// o, y: [B, L, Hq, 64] contiguous; qg: [B, L, Hq * 128] contiguous (per head [q | gate]).
+void gate_out_fwd(const Tensor& o, const Tensor& qg, Tensor& y) {
+  const c10::cuda::CUDAGuard guard(o.device());
+  TORCH_CHECK(is_bf16(o) && is_bf16(qg) && is_bf16(y) && o.is_contiguous() && qg.is_contiguous() && y.is_contiguous() && qg.numel() == 2 * o.numel(), "gate_out_fwd: layout");
+  check(ghb::gate_out_fwd(o.data_ptr(), qg.data_ptr(), y.data_ptr(), o.numel() / 64, sm_count(), stream()), "gate_out_fwd");
+}
+void gate_out_bwd(const Tensor& dy, const Tensor& o, const Tensor& qg, Tensor& dO, Tensor& dqg) {
+  const c10::cuda::CUDAGuard guard(o.device());
+  TORCH_CHECK(is_bf16(dy) && dy.is_contiguous() && is_bf16(dO) && dO.is_contiguous() && is_bf16(dqg) && dqg.is_contiguous() && dqg.numel() == qg.numel(), "gate_out_bwd: layout");
+  check(ghb::gate_out_bwd(dy.data_ptr(), o.data_ptr(), qg.data_ptr(), dO.data_ptr(), dqg.data_ptr(), o.numel() / 64, sm_count(), stream()), "gate_out_bwd");
+}
+
 // ---- tensor-parallel fused GEMMs. args: CPU uint8 tensor holding the kernel's argument table.
 void gemm_tp(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& out, bool a_mn, bool b_mn, bool accumulate, const Tensor& args, Tensor& err) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && is_bf16(a) && is_bf16(b) && a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm_tp: bf16 2-D operands");
@@ -375,6 +416,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gdn_local_bwd", &gdn_local_bwd);
   m.def("gdn_scan_fwd", &gdn_scan_fwd);
   m.def("gdn_scan_bwd", &gdn_scan_bwd);
+  m.def("gate_out_fwd", &gate_out_fwd);
+  m.def("gate_out_bwd", &gate_out_bwd);
+  m.def("attn_prep_fwd", &attn_prep_fwd);
+  m.def("attn_prep_bwd", &attn_prep_bwd);
   m.def("gemm_tp", &gemm_tp);
   m.def("tp_rs_reduce", &tp_rs_reduce);
   m.def("tp_signal", &tp_signal);

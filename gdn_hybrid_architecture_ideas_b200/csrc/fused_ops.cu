@@ -542,4 +542,176 @@ int dual_lerp_bwd(const void* ga, const void* gb, const void* x, const void* ya,
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// ================================================================================================ attention q / k preparation
+// Per token and head (head dim 64, two channels per lane, one warp per token walking its heads): zero-centred RMSNorm,
+// then the partial NeoX rotation at the token's position, and under the distance cap a second copy of the query
+// rotated by the cap itself and the unrotated normed key (ced/model/attention.py:836-935, ced/model/rope.py:14-58 do
+// this as separate norm, table and rotate ops). cos / sin: [tokens, R2] fp32 tables (R2 = rotary pairs, a power of two
+// <= 32, or 0 for a position-free layer); cos_c / sin_c: [R2] tables of the cap rotation or null.
+struct PrepQK {
+  const __nv_bfloat16* q; long q_ts; int q_hs;      // raw queries: token stride, head stride (the gate may be interleaved)
+  const __nv_bfloat16* k; long k_ts;                // raw keys [tokens, Hkv, 64]
+  const float* wq; const float* wk;                 // norm gains [64]
+  const float* cos; const float* sin; const float* cos_c; const float* sin_c;
+  int Hq, Hkv, R2; float eps; long tokens;
+};
+
+__device__ __forceinline__ void rot_pair(float& v0, float& v1, int lane, int R2, const float* c, const float* s, bool inverse) {
+  // lanes [0, R2 / 2) hold the first halves of the rotary pairs (channels 2 lane, 2 lane + 1), lanes [R2 / 2, R2) the second
+  const int half = R2 >> 1;
+  const float p0 = __shfl_xor_sync(0xffffffffu, v0, half), p1 = __shfl_xor_sync(0xffffffffu, v1, half);
+  if (lane < R2) {
+    const bool first = lane < half;
+    const int i = (first ? lane : lane - half) * 2;
+    const float c0 = c[i], c1 = c[i + 1], s0 = inverse ? -s[i] : s[i], s1 = inverse ? -s[i + 1] : s[i + 1];
+    v0 = first ? v0 * c0 - p0 * s0 : v0 * c0 + p0 * s0;
+    v1 = first ? v1 * c1 - p1 * s1 : v1 * c1 + p1 * s1;
+  }
+}
+
+__global__ void __launch_bounds__(256) attn_prep_fwd_kernel(PrepQK a, __nv_bfloat16* __restrict__ qr, __nv_bfloat16* __restrict__ qf,
+                                                            __nv_bfloat16* __restrict__ kr, __nv_bfloat16* __restrict__ kf) {
+  const int lane = threadIdx.x & 31;
+  const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const float gq0 = 1.f + a.wq[2 * lane], gq1 = 1.f + a.wq[2 * lane + 1], gk0 = 1.f + a.wk[2 * lane], gk1 = 1.f + a.wk[2 * lane + 1];
+  for (long t = warp; t < a.tokens; t += nwarp) {
+    const float* ct = a.cos + t * a.R2; const float* st = a.sin + t * a.R2;
+    for (int h = 0; h < a.Hq + a.Hkv; ++h) {
+      const bool is_q = h < a.Hq;
+      const int hh = is_q ? h : h - a.Hq;
+      const __nv_bfloat16* src = is_q ? a.q + t * a.q_ts + static_cast<long>(hh) * a.q_hs : a.k + t * a.k_ts + static_cast<long>(hh) * 64;
+      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[lane]);
+      const float r = rsqrtf(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + a.eps);
+      const float n0 = x.x * r * (is_q ? gq0 : gk0), n1 = x.y * r * (is_q ? gq1 : gk1);
+      float v0 = n0, v1 = n1;
+      if (a.R2) rot_pair(v0, v1, lane, a.R2, ct, st, false);
+      const long o = (t * (is_q ? a.Hq : a.Hkv) + hh) * 64;
+      reinterpret_cast<__nv_bfloat162*>((is_q ? qr : kr) + o)[lane] = __floats2bfloat162_rn(v0, v1);
+      if (a.cos_c) {
+        if (is_q) {
+          float f0 = n0, f1 = n1;
+          rot_pair(f0, f1, lane, a.R2, a.cos_c, a.sin_c, false);
+          reinterpret_cast<__nv_bfloat162*>(qf + o)[lane] = __floats2bfloat162_rn(f0, f1);
+        } else {
+          reinterpret_cast<__nv_bfloat162*>(kf + o)[lane] = __floats2bfloat162_rn(n0, n1);
+        }
+      }
+    }
+  }
+}
+
+// Gradients w.r.t. the raw q / k and the two gains. dqraw is written with the raw queries' strides (the interleaved gate
+// half is left untouched); dw: [2][64] fp32, zeroed by the caller.
+__global__ void __launch_bounds__(256) attn_prep_bwd_kernel(PrepQK a, const __nv_bfloat16* __restrict__ dqr, const __nv_bfloat16* __restrict__ dqf,
+                                                            const __nv_bfloat16* __restrict__ dkr, const __nv_bfloat16* __restrict__ dkf,
+                                                            __nv_bfloat16* __restrict__ dqraw, __nv_bfloat16* __restrict__ dkraw, float* __restrict__ dw) {
+  __shared__ float red[8][4][32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const float gq0 = 1.f + a.wq[2 * lane], gq1 = 1.f + a.wq[2 * lane + 1], gk0 = 1.f + a.wk[2 * lane], gk1 = 1.f + a.wk[2 * lane + 1];
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};      // dwq (2 channels), dwk (2 channels)
+  for (long t = warp; t < a.tokens; t += nwarp) {
+    const float* ct = a.cos + t * a.R2; const float* st = a.sin + t * a.R2;
+    for (int h = 0; h < a.Hq + a.Hkv; ++h) {
+      const bool is_q = h < a.Hq;
+      const int hh = is_q ? h : h - a.Hq;
+      const long o = (t * (is_q ? a.Hq : a.Hkv) + hh) * 64;
+      const __nv_bfloat16* src = is_q ? a.q + t * a.q_ts + static_cast<long>(hh) * a.q_hs : a.k + t * a.k_ts + static_cast<long>(hh) * 64;
+      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[lane]);
+      const float r = rsqrtf(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + a.eps);
+      const float h0 = x.x * r, h1 = x.y * r;
+      const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>((is_q ? dqr : dkr) + o)[lane]);
+      float d0 = g.x, d1 = g.y;
+      if (a.R2) rot_pair(d0, d1, lane, a.R2, ct, st, true);
+      if (a.cos_c) {
+        const float2 gf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>((is_q ? dqf : dkf) + o)[lane]);
+        float f0 = gf.x, f1 = gf.y;
+        if (is_q) rot_pair(f0, f1, lane, a.R2, a.cos_c, a.sin_c, true);
+        d0 += f0; d1 += f1;
+      }
+      acc[is_q ? 0 : 2] += d0 * h0; acc[is_q ? 1 : 3] += d1 * h1;
+      const float e0 = d0 * (is_q ? gq0 : gk0), e1 = d1 * (is_q ? gq1 : gk1);
+      const float dot = wsum(e0 * h0 + e1 * h1) * (1.f / 64.f);
+      __nv_bfloat16* dst = is_q ? dqraw + t * a.q_ts + static_cast<long>(hh) * a.q_hs : dkraw + t * a.k_ts + static_cast<long>(hh) * 64;
+      reinterpret_cast<__nv_bfloat162*>(dst)[lane] = __floats2bfloat162_rn(r * (e0 - h0 * dot), r * (e1 - h1 * dot));
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) red[wib][e][lane] = acc[e];
+  __syncthreads();
+  if (wib == 0) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float s = 0.f;
+      for (int w = 0; w < 8; ++w) s += red[w][e][lane];
+      atomicAdd(dw + (e >> 1) * 64 + 2 * lane + (e & 1), s);
+    }
+  }
+}
+
+static int prep_check(const PrepQK& a) {
+  if (a.R2 < 0 || a.R2 > 32 || (a.R2 & (a.R2 - 1)) || a.R2 == 1 || a.q_hs % 2 || a.q_ts % 2 || a.k_ts % 2) return 1;
+  if (a.cos_c && !a.R2) return 1;
+  return 0;
+}
+int attn_prep_fwd(const void* q, long q_ts, int q_hs, const void* k, long k_ts, const float* wq, const float* wk, const float* cos, const float* sin,
+                  const float* cos_c, const float* sin_c, int Hq, int Hkv, int R2, float eps, long tokens, void* qr, void* qf, void* kr, void* kf,
+                  int sms, cudaStream_t st) {
+  PrepQK a{static_cast<const __nv_bfloat16*>(q), q_ts, q_hs, static_cast<const __nv_bfloat16*>(k), k_ts, wq, wk, cos, sin, cos_c, sin_c, Hq, Hkv, R2, eps, tokens};
+  if (prep_check(a)) return 1;
+  attn_prep_fwd_kernel<<<sms * 8, 256, 0, st>>>(a, static_cast<__nv_bfloat16*>(qr), static_cast<__nv_bfloat16*>(qf), static_cast<__nv_bfloat16*>(kr),
+                                                static_cast<__nv_bfloat16*>(kf));
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+int attn_prep_bwd(const void* q, long q_ts, int q_hs, const void* k, long k_ts, const float* wq, const float* wk, const float* cos, const float* sin,
+                  const float* cos_c, const float* sin_c, int Hq, int Hkv, int R2, float eps, long tokens, const void* dqr, const void* dqf,
+                  const void* dkr, const void* dkf, void* dqraw, void* dkraw, float* dw, int sms, cudaStream_t st) {
+  PrepQK a{static_cast<const __nv_bfloat16*>(q), q_ts, q_hs, static_cast<const __nv_bfloat16*>(k), k_ts, wq, wk, cos, sin, cos_c, sin_c, Hq, Hkv, R2, eps, tokens};
+  if (prep_check(a)) return 1;
+  attn_prep_bwd_kernel<<<sms * 4, 256, 0, st>>>(a, static_cast<const __nv_bfloat16*>(dqr), static_cast<const __nv_bfloat16*>(dqf),
+                                                static_cast<const __nv_bfloat16*>(dkr), static_cast<const __nv_bfloat16*>(dkf),
+                                                static_cast<__nv_bfloat16*>(dqraw), static_cast<__nv_bfloat16*>(dkraw), dw);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// ================================================================================================ attention output gate
+// y = o * sigmoid(gate) with the gate interleaved in the query projection's output: per token and head the 128
+// channels are [q (64) | gate (64)]. Backward writes do and the gate half of the projection's gradient buffer.
+__global__ void gate_out_fwd_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ y, long n4) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long unit = i >> 4; const int c = static_cast<int>(i & 15) * 4;      // (token, head), channel
+    float ov[4], gv[4], out[4];
+    ld4(o + unit * 64 + c, ov);
+    ld4(qg + unit * 128 + 64 + c, gv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) out[e] = ov[e] * sigm(gv[e]);
+    st4(y + unit * 64 + c, out);
+  }
+}
+__global__ void gate_out_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ qg,
+                                    __nv_bfloat16* __restrict__ dO, __nv_bfloat16* __restrict__ dqg, long n4) {
+  for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4; i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long unit = i >> 4; const int c = static_cast<int>(i & 15) * 4;
+    float dv[4], ov[4], gv[4], a[4], b[4];
+    ld4(dy + unit * 64 + c, dv);
+    ld4(o + unit * 64 + c, ov);
+    ld4(qg + unit * 128 + 64 + c, gv);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { const float s = sigm(gv[e]); a[e] = dv[e] * s; b[e] = dv[e] * ov[e] * s * (1.f - s); }
+    st4(dO + unit * 64 + c, a);
+    st4(dqg + unit * 128 + 64 + c, b);
+  }
+}
+int gate_out_fwd(const void* o, const void* qg, void* y, long units, int sms, cudaStream_t st) {
+  using T = __nv_bfloat16;
+  gate_out_fwd_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const T*>(o), static_cast<const T*>(qg), static_cast<T*>(y), units * 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+int gate_out_bwd(const void* dy, const void* o, const void* qg, void* dO, void* dqg, long units, int sms, cudaStream_t st) {
+  using T = __nv_bfloat16;
+  gate_out_bwd_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const T*>(dy), static_cast<const T*>(o), static_cast<const T*>(qg), static_cast<T*>(dO),
+                                               static_cast<T*>(dqg), units * 16);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 }  // namespace ghb

@@ -244,7 +244,13 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long l
   if (reinterpret_cast<uintptr_t>(A) & 15) return 14;
   if (reinterpret_cast<uintptr_t>(B) & 15) return 15;
   if (reinterpret_cast<uintptr_t>(C) & 15) return 16;
-  const int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  int bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+  if (bn == 256 && out == 0) {     // few 128 x 256 tiles and no split-K (bf16 output): narrower tiles fill more SMs
+    const long t256 = static_cast<long>((M + BM - 1) / BM) * ((N + 255) / 256), t128 = static_cast<long>((M + BM - 1) / BM) * ((N + 127) / 128);
+    auto waves = [&](long t) { return (t + sms - 1) / sms; };
+    // time ~ waves x tile width: take 128-wide tiles when they finish sooner
+    if (waves(t128) * 128 < waves(t256) * 256) bn = 128;
+  }
   // A long reduction into few output tiles (weight gradients: K = tokens) leaves most SMs idle; slice the reduction so
   // that the units fill the machine. Only the fp32 outputs can be reduced into: out 1 is zeroed first, out 2 already
   // holds the running sum. Slices meet through floating-point reductions, so the summation order is not fixed.

@@ -44,6 +44,16 @@ int dual_lerp_fwd(const void* x, const void* ya, const void* yb, const float* la
 int dual_lerp_bwd(const void* ga, const void* gb, const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* dx, void* dya,
                   void* dyb, float* dl, long n, int sms, cudaStream_t st);
 
+int attn_prep_fwd(const void* q, long q_ts, int q_hs, const void* k, long k_ts, const float* wq, const float* wk, const float* cos, const float* sin,
+                  const float* cos_c, const float* sin_c, int Hq, int Hkv, int R2, float eps, long tokens, void* qr, void* qf, void* kr, void* kf,
+                  int sms, cudaStream_t st);
+int attn_prep_bwd(const void* q, long q_ts, int q_hs, const void* k, long k_ts, const float* wq, const float* wk, const float* cos, const float* sin,
+                  const float* cos_c, const float* sin_c, int Hq, int Hkv, int R2, float eps, long tokens, const void* dqr, const void* dqf,
+                  const void* dkr, const void* dkf, void* dqraw, void* dkraw, float* dw, int sms, cudaStream_t st);
+
+int gate_out_fwd(const void* o, const void* qg, void* y, long units, int sms, cudaStream_t st);
+int gate_out_bwd(const void* dy, const void* o, const void* qg, void* dO, void* dqg, long units, int sms, cudaStream_t st);
+
 int attention_fwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, void* o, float* lse, const int* doc,
                   const int* pos, int B, int L, int Hq, int Hkv, int cap, float scale, int* err, cudaStream_t st);
 int attention_bwd(const void* q, const void* qf, const void* k, const void* kf, const void* v, const void* o, const void* dO,

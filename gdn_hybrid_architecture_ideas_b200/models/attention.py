@@ -204,6 +204,47 @@ class GatedAttention(nn.Module):
             o = o * torch.sigmoid(gate)
         return self.o_proj(o.flatten(2))
 
+    def fused_prep_ok(self, x: torch.Tensor) -> bool:
+        """One kernel does QK-norm, both rotations and the far copies when the layer has the common shape: head
+        dimension 64, QK-norm on, fixed temperature, grouped (not grid) keys, 0 or a power of two (<= 32) rotary pairs."""
+        cfg = self.cfg
+        r2 = rotary_dims(cfg.head_dim, cfg.rope_fraction) // 2
+        return (ops.use_native(x) and x.dtype == torch.bfloat16 and self.grid is None and cfg.qk_norm and cfg.temperature == "fixed"
+                and cfg.head_dim == 64 and cfg.gate in ("elementwise", "none") and r2 in (0, 2, 4, 8, 16, 32))
+
+    def _forward_fused(self, x, ctx, cache, rot_pos, cap):
+        from ..ops import attention_native as an
+        B, L = ctx.doc.shape
+        cfg = self.cfg
+        hq, hkv, hd = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim
+        r = rotary_dims(hd, cfg.rope_fraction)
+        key = ("attn_rot", r, cfg.rope_theta, cap, ctx.rope_scale if self.cap is not None else 1)
+        tables = ctx.memo.get(key) if hasattr(ctx, "memo") else None
+        if tables is None:
+            if r:
+                tables = an.rotary_tables(rot_pos, r, cfg.rope_theta, cap)
+            else:
+                z = torch.zeros(1, dtype=torch.float32, device=x.device)
+                tables = (z, z, None, None)
+            if hasattr(ctx, "memo"):
+                ctx.memo[key] = tables
+        interleaved = cfg.gate == "elementwise"
+        slot = an.GradSlot() if interleaved and torch.is_grad_enabled() else None
+        qg = self.q_proj(x)
+        q, q_far, k_new, kf_new = an._AttnPrep.apply(qg, self.k_proj(x), self.q_norm.weight, self.k_norm.weight, *tables,
+                                                     self.q_norm.eps, hq, hkv, interleaved, slot)
+        if cap is None:
+            q_far = kf_new = None
+        ok = torch.ones_like(ctx.doc, dtype=torch.bool)
+        new = KeySet(k=k_new, v=self.v_proj(x).view(B, L, hkv, hd), idx=ctx.idx, doc=ctx.doc, ok=ok, k_far=kf_new)
+        keys = KeySet.cat(cache, new)
+        o = ops.attention(q, keys.k, keys.v, ctx.idx, ctx.doc, keys.idx, keys.doc, None if cache is None else keys.ok,
+                          q_far=q_far, k_far=keys.k_far, cap=cap, self_aligned=cache is None, q_pos=ctx.pos,
+                          single_doc=ctx.single_doc)
+        if interleaved:
+            o = an._GateOut.apply(o, qg, slot)
+        return self.o_proj(o.flatten(2)), keys
+
     # ------------------------------------------------------------------ forward
 
     def forward(self, x: torch.Tensor, ctx: SeqContext, cache: KeySet | None = None):
@@ -218,6 +259,8 @@ class GatedAttention(nn.Module):
             cap = cap // ctx.rope_scale
             if cap < 1:
                 raise ValueError("rope_max_distance under token-scale rotary leaves no near key")
+        if self.fused_prep_ok(x):
+            return self._forward_fused(x, ctx, cache, rot_pos, cap)
         q, q_far, gate = self.queries(x, rot_pos, ctx.pos)
         ok = torch.ones_like(ctx.doc, dtype=torch.bool)
         if self.grid is not None:

@@ -69,3 +69,102 @@ def attention(q, k, v, doc, q_far, k_far, cap, pos=None, single_doc=False):
         else:
             outs.append(_row(*args, cap))
     return torch.cat(outs, dim=0)
+
+
+# ---------------------------------------------------------------------------------------------------- q / k preparation
+
+
+class GradSlot:
+    """Hands the gate half of the query projection's gradient (written by the output gate's backward, which runs first)
+    to the q / k preparation's backward, which fills the query half of the same buffer: the projection gets one dense
+    gradient and no slice is ever re-assembled."""
+
+    def __init__(self):
+        self.buf = None
+
+
+class _AttnPrep(torch.autograd.Function):
+    """(qg [B, L, Hq * hq_width], k_raw [B, L, Hkv * 64], gains, rotary tables) -> (q, q_far, k, k_far): RMSNorm per head,
+    rotation at the token's position, and under the cap the query rotated by the cap and the unrotated normed key."""
+
+    @staticmethod
+    def forward(ctx, qg, k_raw, wq, wk, cos, sin, cos_c, sin_c, eps, hq, hkv, interleaved, slot):
+        B, L = qg.shape[:2]
+        qv = native._bf16(qg).contiguous().view(B, L, hq, 128 if interleaved else 64)[..., :64]
+        kv = native._bf16(k_raw).contiguous().view(B, L, hkv, 64)
+        dev = qg.device
+        capped = cos_c is not None
+        qr = torch.empty(B, L, hq, 64, dtype=BF16, device=dev)
+        kr = torch.empty(B, L, hkv, 64, dtype=BF16, device=dev)
+        qf = torch.empty_like(qr) if capped else None
+        kf = torch.empty_like(kr) if capped else None
+        wdt = (wq.dtype, wk.dtype)
+        wq, wk = wq.detach().float().contiguous(), wk.detach().float().contiguous()
+        native.ext().attn_prep_fwd(qv, kv, wq, wk, cos, sin, cos_c, sin_c, eps, qr, qf, kr, kf)
+        native._count()
+        ctx.save_for_backward(qv, kv, wq, wk, cos, sin, cos_c, sin_c)
+        ctx.meta = (eps, interleaved, slot, qg.dtype, k_raw.dtype, qg.shape, k_raw.shape, wdt)
+        if not capped:
+            qf, kf = qr.new_zeros(0), kr.new_zeros(0)
+            ctx.mark_non_differentiable(qf, kf)
+        return qr, qf, kr, kf
+
+    @staticmethod
+    def backward(ctx, dqr, dqf, dkr, dkf):
+        qv, kv, wq, wk, cos, sin, cos_c, sin_c = ctx.saved_tensors
+        eps, interleaved, slot, qdt, kdt, qshape, kshape, wdt = ctx.meta
+        capped = cos_c is not None
+        B, L, hq, _ = qv.shape
+        full = slot.buf if (slot is not None and slot.buf is not None) else None
+        if full is None:
+            full = torch.zeros(B, L, hq * (128 if interleaved else 64), dtype=BF16, device=qv.device) if interleaved else \
+                torch.empty(B, L, hq * 64, dtype=BF16, device=qv.device)
+        if slot is not None:
+            slot.buf = None
+        dq_view = full.view(B, L, hq, 128 if interleaved else 64)[..., :64]
+        dk = torch.empty(kv.shape, dtype=BF16, device=kv.device)
+        dw = torch.zeros(2, 64, dtype=torch.float32, device=qv.device)
+        c = lambda t: native._bf16(t).contiguous()
+        native.ext().attn_prep_bwd(qv, kv, wq, wk, cos, sin, cos_c, sin_c, eps, c(dqr), c(dqf) if capped else None, c(dkr), c(dkf) if capped else None,
+                                   dq_view, dk, dw)
+        native._count()
+        return (full.view(qshape).to(qdt), dk.view(kshape).to(kdt), dw[0].to(wdt[0]), dw[1].to(wdt[1]), None, None, None, None, None, None, None, None,
+                None)
+
+
+class _GateOut(torch.autograd.Function):
+    """y = o * sigmoid(gate), the gate being the second 64 channels of every head of the query projection's output."""
+
+    @staticmethod
+    def forward(ctx, o, qg, slot):
+        oc, qc = native._bf16(o).contiguous(), native._bf16(qg).contiguous()
+        y = torch.empty_like(oc)
+        native.ext().gate_out_fwd(oc, qc, y)
+        native._count()
+        ctx.save_for_backward(oc, qc)
+        ctx.slot, ctx.odt, ctx.qdt = slot, o.dtype, qg.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        oc, qc = ctx.saved_tensors
+        do = torch.empty_like(oc)
+        dqg = torch.empty_like(qc)        # the query half is written by the preparation's backward
+        native.ext().gate_out_bwd(native._bf16(dy).contiguous(), oc, qc, do, dqg)
+        native._count()
+        if ctx.slot is not None:
+            ctx.slot.buf = dqg
+            return do.to(ctx.odt), None, None
+        dqg.view(*qc.shape[:2], -1, 128)[..., :64].zero_()
+        return do.to(ctx.odt), dqg.to(ctx.qdt), None
+
+
+def rotary_tables(pos, r: int, theta: float, cap):
+    """cos / sin [tokens, r / 2] fp32 at positions `pos` (angles in float64), and the tables of the cap rotation."""
+    inv = theta ** (-torch.arange(0, r, 2, dtype=torch.float64, device=pos.device) / r)
+    ang = pos.reshape(-1, 1).to(torch.float64) * inv
+    cap_t = (None, None)
+    if cap is not None:
+        a = float(cap) * inv
+        cap_t = (a.cos().float().contiguous(), a.sin().float().contiguous())
+    return ang.cos().float().contiguous(), ang.sin().float().contiguous(), cap_t[0], cap_t[1]

@@ -413,3 +413,58 @@ def test_wgrad_accumulates_into_main_grad():
     assert lin.weight.grad is None
     _close(lin.weight.main_grad, 2 * want + 0.5, 2e-2 * float(want.abs().max()), 1e-2, "main grad")
     native.check_status()
+
+
+@pytest.mark.parametrize("gate,cap,frac,docs", [("elementwise", 64, 0.25, True), ("none", None, 0.5, False), ("elementwise", None, 0.0, False)])
+def test_attention_layer_fused_prep(gate, cap, frac, docs):
+    """The layer with the fused q / k preparation (norm + rotations + far copies, output gate) against the same layer
+    run in float32 through the PyTorch statements."""
+    import copy
+
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.config import AttentionConfig
+    from gdn_hybrid_architecture_ideas_b200.models.attention import GatedAttention
+    from gdn_hybrid_architecture_ideas_b200.models.sequence import sequence_context
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    torch.manual_seed(11)
+    B, L, d = 2, 320, 256
+    cfg = AttentionConfig(n_q_heads=4, n_kv_heads=2, head_dim=64, gate=gate, rope_fraction=frac, rope_max_distance=cap, rope_theta=10000.0)
+    layer = GatedAttention(d, cfg, 1e-6).to(_dev())
+    with torch.no_grad():
+        layer.q_norm.weight.normal_(0, 0.2)
+        layer.k_norm.weight.normal_(0, 0.2)
+    oracle = copy.deepcopy(layer).float()
+    layer = layer.to(torch.bfloat16)
+    for p, q in zip(layer.parameters(), oracle.parameters()):
+        q.data.copy_(p.data.float())
+    doc = torch.zeros(B, L, dtype=torch.long, device=_dev())
+    if docs:
+        doc[0, 100:] = 1
+        doc[1, 37:] = 1
+        doc[1, 250:] = 2
+    x = torch.randn(B, L, d, device=_dev()).to(torch.bfloat16)
+    go = torch.randn(B, L, d, device=_dev()).to(torch.bfloat16)
+    xa = x.clone().requires_grad_(True)
+    xb = x.float().requires_grad_(True)
+    ctx, _ = sequence_context(doc)
+    assert layer.fused_prep_ok(xa)
+    y, keys = layer(xa, ctx)
+    y.backward(go)
+    native.check_status()
+    ops.set_mode("reference")
+    try:
+        ctx2, _ = sequence_context(doc)
+        y2, keys2 = oracle(xb, ctx2)
+        y2.backward(go.float())
+    finally:
+        ops.set_mode("native")
+    _close(keys.k, keys2.k, 3e-2, 2e-2, "k")
+    if cap is not None:
+        _close(keys.k_far, keys2.k_far, 3e-2, 2e-2, "k_far")
+    scale = y2.abs().max().item()
+    _close(y, y2, 3e-2 * scale, 3e-2, "y")
+    _close(xa.grad, xb.grad, 4e-2 * xb.grad.abs().max().item(), 3e-2, "dx")
+    for (n, p), q in zip(layer.named_parameters(), oracle.parameters()):
+        assert p.grad is not None, n
+        _close(p.grad, q.grad, 4e-2 * q.grad.abs().max().item() + 1e-3, 3e-2, f"d{n}")
