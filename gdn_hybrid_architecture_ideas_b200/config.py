@@ -640,11 +640,10 @@ _BUILT = {
     "model.encoder.gdn.decay_cumsum": ("plain",),
     "model.encoder.gdn.kda.decay": ("scalar",),
     "model.encoder.gdn.erase.mode": ("none",),
-    "model.encoder.gdn.negeig.beta_max": (1,),
+    "model.encoder.gdn.negeig.beta_max": (1, 2),
     "model.encoder.gdn.dprod.n_h": (1,),
     "model.encoder.loops": (1,),
-    "model.encoder.layer_scalars": ("none",),
-    "model.encoder.canon_kernel": (0,),
+    "model.encoder.layer_scalars": ("none", "skip_x0", "skip_x0_span", "x0", "skip"),
     "model.encoder.attn_res": ("none", "block_entry"),
     "model.encoder.attn_res_heads": (1,),
     "model.encoder.attn_res_query": ("static",),

@@ -22,6 +22,7 @@ import torch
 
 from .. import ops
 from ..models.attention import assemble_grid
+from ..models.encoder import apply_layer_scalars
 from ..models.gdn import READ_MIX_VARIANTS, GDNState
 from ..models.rope import apply_rope, rotary_dims
 from ..models.sequence import SeqContext
@@ -43,6 +44,9 @@ class DecodeEngine:
         self.next_tokens = torch.zeros(B, dtype=torch.long, device=dev)     # static output of the step
         self.logits = torch.zeros(B, self.cfg.vocab_size, dtype=torch.float32, device=dev)
         self.layers = []
+        if self.cfg.encoder.canon_kernel:
+            raise ValueError("the decode engine does not keep a Canon layer's input history (model.encoder.canon_kernel): "
+                             "generate through the model's cached forward (eval.generate)")
         kv_dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
         for layer in model.encoder.layers:
             m = layer.mixer
@@ -178,10 +182,12 @@ class DecodeEngine:
         S = enc.block
         sources = [x]
         n = len(enc.layers)
+        scalars = enc.layer_scalar_args(x)
         for i, (layer, st) in enumerate(zip(enc.layers, self.layers)):
             if enc.block_entry and i % S == 0:
                 start = x if i == 0 else layer.attn_res.entry(sources)
                 x = start
+            x_in = x
             h = layer.mixer_in_norm(x)
             if layer.kind == "gdn":
                 arms = getattr(layer, "gdn_arms", None)
@@ -201,6 +207,8 @@ class DecodeEngine:
                 mixed = self._attention_step(layer, st, h, pos)
             x = ops.norm_add(x, mixed, layer.mixer_out_norm.weight, layer.mixer_out_norm.eps, layer.residual_scale)
             x = ops.norm_add(x, layer.mlp(layer.mlp_in_norm(x)), layer.mlp_out_norm.weight, layer.mlp_out_norm.eps, layer.residual_scale)
+            if scalars is not None:
+                x = apply_layer_scalars(x, x_in, *scalars[i])
             if enc.block_entry and i % S == S - 1:
                 sources = sources + [x - start]
         if enc.block_entry:

@@ -40,6 +40,8 @@ class KeySet:
     ok: torch.Tensor
     k_far: torch.Tensor | None = None
     pos: torch.Tensor | None = None
+    canon_input: torch.Tensor | None = None    # last K - 1 inputs of the layer's Canon convolution and their documents:
+    canon_doc: torch.Tensor | None = None      # set by the encoder layer, not joined by `cat`
 
     @staticmethod
     def cat(*sets: "KeySet | None") -> "KeySet":

@@ -11,6 +11,9 @@ same sources (reference: ced/model/attn_res.py:700-797, ced/model/gdn_arms.py:76
 
 from __future__ import annotations
 
+import hashlib
+import math
+
 import torch
 import torch.nn as nn
 
@@ -35,6 +38,77 @@ def residual_scale(cfg: ModelConfig) -> float:
     raise ValueError(f"unknown residual scale mode {rs.mode!r}")
 
 
+LAYER_SCALARS = ("none", "skip_x0", "skip_x0_span", "x0", "skip")
+SPAN_CLAMP = 3.0
+
+
+def layer_scalar_parameters(mode: str) -> tuple[str, ...]:
+    """Names of the (n_layers,) tensors a residual-scalar form stores on the encoder, in state-dict order."""
+    if mode not in LAYER_SCALARS:
+        raise ValueError(f"model.encoder.layer_scalars {mode!r}: one of {LAYER_SCALARS}")
+    return {"none": (), "x0": ("x0_gain",), "skip": ("skip_gain",)}.get(mode, ("skip_gain", "x0_gain"))
+
+
+def layer_scalar_terms(mode: str, skip_gain, x0_gain, span: float = 4.0):
+    """(a - 1, b) of every layer, each (n_layers,) or None, for x <- a x + b x0 + f(x).
+
+    "skip_x0": the stored tensors. "skip": a - 1 stored, b = 0 (None). "x0": a = 1 (None), b stored with b_0 = 0.
+    "skip_x0_span": the stored u gives S_k = (ln(span) / 2) tanh(clamp(u_k, +-3)) (gradient passed straight through the
+    clamp), a_i = exp(S_{i+1} - S_i) with S_0 = 0, so every product of consecutive a stays inside (1 / span, span);
+    b as in "x0" (reference: ced/model/encoder.py:60-100)."""
+    if mode == "skip_x0":
+        return skip_gain, x0_gain
+    if mode == "skip":
+        return skip_gain, None
+    b = torch.cat([x0_gain.new_zeros(1), x0_gain[1:]])
+    if mode == "x0":
+        return None, b
+    u = skip_gain.detach().clamp(-SPAN_CLAMP, SPAN_CLAMP) + (skip_gain - skip_gain.detach())
+    cum = (0.5 * math.log(span)) * torch.tanh(u)
+    return torch.expm1(cum - torch.cat([cum.new_zeros(1), cum[:-1]])), b
+
+
+def apply_layer_scalars(out, x, x0, a_minus_1, b):
+    """out + (a - 1) x + b x0 in at least float32, returned in out's dtype (reference: ced/model/encoder.py:103-140)."""
+    dtype = torch.promote_types(out.dtype, torch.float32)
+    extra = None
+    if a_minus_1 is not None:
+        extra = x.to(dtype) * a_minus_1.to(dtype)
+    if b is not None:
+        inj = x0.to(dtype) * b.to(dtype)
+        extra = inj if extra is None else extra + inj
+    return out if extra is None else (out.to(dtype) + extra).to(out.dtype)
+
+
+class CanonLayer(nn.Module):
+    """h' = h + causal depthwise convolution (kernel K) of h inside each document, on the normed input of a global
+    attention layer; taps zeros as built, so the layer starts as the identity. conv_weight (d, K), [:, K-1] on the current
+    input, the layout of the GDN short convolution (reference: ced/model/canon.py:118-152)."""
+
+    def __init__(self, d_model: int, kernel: int):
+        super().__init__()
+        self.kernel = kernel
+        self.conv_weight = nn.Parameter(torch.zeros(d_model, kernel))
+
+    @torch.no_grad()
+    def init_uniform(self, generator: torch.Generator) -> None:
+        bound = 1.0 / math.sqrt(self.kernel)
+        drawn = torch.empty(tuple(self.conv_weight.shape), dtype=torch.float32).uniform_(-bound, bound, generator=generator)
+        if not self.conv_weight.is_meta:
+            self.conv_weight.copy_(drawn)
+
+    def forward(self, h, doc, hist=None, hist_doc=None):
+        out, hist, hist_doc = ops.ref.causal_doc_conv(h, doc, self.conv_weight, hist, hist_doc)
+        return (h + out).to(h.dtype), hist, hist_doc
+
+
+def canon_generator(seed: int, layer: int) -> torch.Generator:
+    """CPU generator of one Canon layer's uniform start, a function of (run seed, layer index) only
+    (reference: ced/model/canon.py:92-98)."""
+    digest = hashlib.blake2b(f"canon-taps:{seed}:{layer}".encode(), digest_size=8).digest()
+    return torch.Generator(device="cpu").manual_seed(int.from_bytes(digest, "little") & (2 ** 63 - 1))
+
+
 class EncoderLayer(nn.Module):
     def __init__(self, kind: str, cfg: ModelConfig, scale: float, attention=None):
         super().__init__()
@@ -53,9 +127,17 @@ class EncoderLayer(nn.Module):
         else:
             raise ValueError(kind)
         self.mlp = dense_ffn(d, cfg.ffn_hidden, cfg.ffn_activation)
+        self.canon = CanonLayer(d, cfg.encoder.canon_kernel) if kind == "attention" and cfg.encoder.canon_kernel else None
 
-    def forward(self, x: torch.Tensor, ctx: SeqContext, cache=None, sources: list | None = None, need_state: bool = True):
+    def forward(self, x: torch.Tensor, ctx: SeqContext, cache=None, sources: list | None = None, need_state: bool = True,
+                scalars: tuple | None = None):
+        """scalars: (x0, a - 1, b) of this layer's residual scalars, applied as the last term of the layer's own sum."""
         h = self.mixer_in_norm(x)
+        if self.canon is not None:
+            if cache is not None and cache.canon_input is None:
+                raise ValueError("this cache was written without a Canon layer: it cannot be continued with one")
+            h, canon_input, canon_doc = self.canon(h, ctx.doc, None if cache is None else cache.canon_input,
+                                                   None if cache is None else cache.canon_doc)
         arms: GDNArms | None = getattr(self, "gdn_arms", None)
         if arms is not None:
             if sources is None:
@@ -75,6 +157,10 @@ class EncoderLayer(nn.Module):
         y = ops.norm_add(y, self.mlp(self.mlp_in_norm(y)), self.mlp_out_norm.weight, self.mlp_out_norm.eps, self.residual_scale)
         if self.stream_bf16:
             y = round_stream(y)
+        if scalars is not None:
+            y = apply_layer_scalars(y, x, *scalars)
+        if self.canon is not None:
+            new_cache.canon_input, new_cache.canon_doc = canon_input, canon_doc
         return y, new_cache
 
 
@@ -109,11 +195,56 @@ class Encoder(nn.Module):
                     layer.mixer.write_mix = "layer"
         elif enc.gdn_write_mix != "none":
             raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none' or 'layer'")
+        # Canon layers: zeros as built; "uniform" draws each layer's taps from its own seeded CPU generator, so no other
+        # parameter's start changes (reference: ced/model/canon.py:101-115, ced/model/control.py:1195-1243).
+        K = enc.canon_kernel
+        if isinstance(K, bool) or not isinstance(K, int) or K < 0 or K == 1:
+            raise ValueError(f"model.encoder.canon_kernel {K!r}: 0 (no Canon layer) or an integer >= 2")
+        if enc.canon_init not in ("zeros", "uniform") or (not K and enc.canon_init != "zeros"):
+            raise ValueError(f"model.encoder.canon_init {enc.canon_init!r} with canon_kernel {K}: 'zeros' or (with a kernel) 'uniform'")
+        if K and (self.block <= 0 or enc.layer_scalars != "none" or cfg.nvfp4.mode != "none"):
+            raise ValueError("model.encoder.canon_kernel needs a global attention layer and is not built together with "
+                             "layer_scalars or nvfp4")
+        if K and enc.canon_init == "uniform":
+            seed = torch.initial_seed()
+            for i, layer in enumerate(self.layers):
+                if layer.canon is not None:
+                    layer.canon.init_uniform(canon_generator(seed, i))
+        # Per-layer residual scalars x <- a x + b x0 + f(x): (n_layers,) zeros after the layers' own tensors.
+        self.scalar_form = enc.layer_scalars
+        self.scalar_span = float(enc.layer_scalars_span)
+        names = layer_scalar_parameters(self.scalar_form)
+        if not (math.isfinite(self.scalar_span) and self.scalar_span > 1.0):
+            raise ValueError(f"model.encoder.layer_scalars_span {enc.layer_scalars_span!r}: a finite width above 1")
+        if names and cfg.nvfp4.mode != "none":
+            raise ValueError("model.encoder.layer_scalars is not built together with model.nvfp4")
+        if names and self.block_entry:
+            raise ValueError("model.encoder.layer_scalars is not built together with model.encoder.attn_res: both replace "
+                             "the layers' residual add (reference: ced/model/attn_res.py:166-168)")
+        for name in names:
+            setattr(self, name, nn.Parameter(torch.zeros(n)))
 
-    def _run(self, layer, x, ctx, cache, sources, need_state):
+    def layer_scalar_args(self, x0):
+        """Per layer (x0, a - 1, b) as 0-dim tensors, or None without the scalars."""
+        if self.scalar_form == "none":
+            return None
+        a, b = layer_scalar_terms(self.scalar_form, getattr(self, "skip_gain", None), getattr(self, "x0_gain", None), self.scalar_span)
+        return [(x0 if b is not None else None, None if a is None else a[i], None if b is None else b[i]) for i in range(len(self.layers))]
+
+    @torch.no_grad()
+    def project_layer_scalars(self) -> None:
+        """After an optimizer step: the span form's stored u back into [-3, 3] (reference: ced/train/trainer.py:3135)."""
+        if self.scalar_form == "skip_x0_span":
+            self.skip_gain.clamp_(-SPAN_CLAMP, SPAN_CLAMP)
+
+    def _run(self, layer, x, ctx, cache, sources, need_state, scalars=None):
         """One layer call under the stack's activation memory mode (models/act_checkpoint.py)."""
         mode = self.activation_checkpoint
         training = cache is None and torch.is_grad_enabled() and x.requires_grad
+        if scalars is not None:
+            if mode != "none" and training:
+                raise ValueError("model.encoder.layer_scalars runs with activation_checkpoint 'none'")
+            return layer(x, ctx, cache, sources, need_state, scalars)
         if mode == "layer" and training:
             def call(x_, *src):
                 return layer(x_, ctx, None, list(src) if src else None, False)[0]
@@ -141,9 +272,11 @@ class Encoder(nn.Module):
         """x: embedding-stage output (B, L, d). Returns (stream entering final_norm, per-layer caches)."""
         new_caches = []
         get = (lambda i: None) if caches is None else (lambda i: caches[i])
+        sc = self.layer_scalar_args(x)
+        scal = (lambda i: None) if sc is None else (lambda i: sc[i])
         if not self.block_entry:
             for i, layer in enumerate(self.layers):
-                x, c = self._run(layer, x, ctx, get(i), None, need_state)
+                x, c = self._run(layer, x, ctx, get(i), None, need_state, scal(i))
                 new_caches.append(c)
             return x, new_caches
         sources = [x]
@@ -154,7 +287,7 @@ class Encoder(nn.Module):
             if b > 0 and first.stream_bf16:
                 start = round_stream(start)
             x = start
-            if self.activation_checkpoint == "block" and caches is None and torch.is_grad_enabled() and x.requires_grad:
+            if self.activation_checkpoint == "block" and sc is None and caches is None and torch.is_grad_enabled() and x.requires_grad:
                 x = self._run_block(b, x, ctx, sources)
                 new_caches.extend([None] * S)
                 sources = sources + [x - start]
@@ -162,7 +295,7 @@ class Encoder(nn.Module):
             for i in range(b * S, (b + 1) * S):
                 layer = self.layers[i]
                 src = sources if getattr(layer, "gdn_arms", None) is not None else None
-                x, c = self._run(layer, x, ctx, get(i), src, need_state)
+                x, c = self._run(layer, x, ctx, get(i), src, need_state, scal(i))
                 new_caches.append(c)
             sources = sources + [x - start]
         return self.layers[-1].attn_res.out(sources), new_caches

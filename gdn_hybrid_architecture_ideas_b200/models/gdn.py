@@ -56,6 +56,13 @@ class GatedDeltaNet(nn.Module):
         super().__init__()
         if cfg.n_v_heads % cfg.n_k_heads:
             raise ValueError("gdn.n_v_heads must be a multiple of gdn.n_k_heads")
+        # Write strength range: beta = beta_max * sigmoid(b). With 2 the transition's eigenvalue along k spans
+        # (-alpha, alpha) (negative eigenvalues; reference: ced/model/gdn_negeig.py:37-61). The kernels use beta as a
+        # multiplier only, so nothing else changes.
+        m = cfg.negeig.beta_max
+        if isinstance(m, bool) or m not in (1, 2):
+            raise ValueError(f"gdn.negeig.beta_max {m!r}: 1 (beta = sigmoid(b)) or 2 (beta = 2 sigmoid(b))")
+        self.beta_max = m
         self.cfg = cfg
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
         self.conv_channels = 2 * hk * dk + hv * dv
@@ -140,6 +147,11 @@ class GatedDeltaNet(nn.Module):
         qkv, conv_input, conv_doc = ops.gdn_prep(u_pre, ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
                                                  single_doc=ctx.single_doc, packed=True)
         g, beta = ops.gdn_gates(a_lin, b_lin, self.A_log, self.dt_bias, ctx.gdn_scale, ctx.gdn_beta_power)
+        if self.beta_max != 1:
+            if ctx.gdn_scale != 1 and ctx.gdn_beta_power:
+                raise ValueError("gdn.negeig.beta_max 2 with the bag write-strength power (tst.gdn_resolution_gates 'decay_beta'): "
+                                 "1 - (1 - beta)^s is written for beta in (0, 1)")
+            beta = beta * self.beta_max
         S0 = None if state is None else state.S
         kernel = "recurrence" if cfg.kernel == "recurrence" else "chunked"
         o, S = ops.delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, ctx.is_doc_start, S0, kernel=kernel,

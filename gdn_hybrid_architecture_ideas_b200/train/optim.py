@@ -17,7 +17,7 @@ from dataclasses import dataclass
 
 import torch
 
-NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias")
+NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gain", ".x0_gain")
 ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}

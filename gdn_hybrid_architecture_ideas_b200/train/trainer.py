@@ -253,6 +253,8 @@ class Trainer:
                 self.dp.all_reduce_(stats)
             gnorm = grad_norm(self.flat)
             self.optimizer.step(lr, _clip_coef(gnorm, cfg.optim.grad_clip))
+        if not cfg.freeze_trunk:
+            self.model.encoder.project_layer_scalars()      # the span-bounded residual scalars back into their range
         self.step += 1
         return torch.stack([stats[0].float(), stats[1].float(), gnorm.float()])
 

@@ -26,12 +26,23 @@ def _cfg(kind):
     if kind == "grid":
         a = cfg.encoder.attention
         a.kv_sharing, a.n_kv_heads, a.grid_rows, a.grid_cols, a.row_dim, a.col_dim = "grid", 1, 2, 2, 8, 8
-    if kind == "plain":
+    if kind in ("plain", "scalars", "negeig"):
         cfg = C.tiny_control_config()
+    if kind == "scalars":
+        cfg.encoder.layer_scalars = "skip_x0_span"
+    if kind == "negeig":
+        cfg.encoder.gdn.negeig.beta_max = 2
     return cfg
 
 
-@pytest.mark.parametrize("kind", ["full", "grid", "plain"])
+def test_engine_refuses_canon():
+    cfg = C.tiny_control_config()
+    cfg.encoder.canon_kernel = 4
+    with pytest.raises(ValueError, match="Canon"):
+        DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
+
+
+@pytest.mark.parametrize("kind", ["full", "grid", "plain", "scalars", "negeig"])
 def test_engine_matches_prefill_extend_cpu(kind):
     model = make_model(_cfg(kind), dtype=torch.float32).eval()
     B, P, steps = 3, 40, 6

@@ -324,9 +324,10 @@ def test_attention_kernels(L, cap, docs, Hq, Hkv, ramp):
         _close(a.grad, b.grad, 4e-2, 4e-2, n)
 
 
-@pytest.mark.parametrize("L,dv,H,docs,with_state,rep", [(128, 128, 2, False, False, 1), (256, 256, 2, True, True, 1), (200, 256, 1, True, False, 1),
-                                                         (192, 128, 4, True, False, 2)])
-def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state, rep):
+@pytest.mark.parametrize("L,dv,H,docs,with_state,rep,beta_max", [(128, 128, 2, False, False, 1, 1), (256, 256, 2, True, True, 1, 1),
+                                                                  (200, 256, 1, True, False, 1, 1), (192, 128, 4, True, False, 2, 1),
+                                                                  (256, 256, 2, True, True, 1, 2)])
+def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state, rep, beta_max):
     from gdn_hybrid_architecture_ideas_b200.ops import gdn_native, native, reference as ref
 
     B, dk = 2, 128
@@ -335,7 +336,7 @@ def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state, rep):
     k = torch.nn.functional.normalize(torch.randn(B, L, H // rep, dk, generator=g_), dim=-1)
     v = torch.randn(B, L, H, dv, generator=g_)
     g = -torch.rand(B, L, H, generator=g_) * 0.5
-    beta = torch.rand(B, L, H, generator=g_)
+    beta = torch.rand(B, L, H, generator=g_) * beta_max      # 2: write strengths past 1 (negative eigenvalues)
     S0 = torch.randn(B, H, dk, dv, generator=g_) * 0.1 if with_state else None
     start = torch.zeros(B, L, dtype=torch.bool)
     if docs:
@@ -350,21 +351,22 @@ def test_gdn_delta_rule_kernels(L, dv, H, docs, with_state, rep):
     refs = [t.detach().float().requires_grad_() for t in leaves]
     S0r = S0.to(dev).requires_grad_() if with_state else torch.zeros(B, H, dk, dv, device=dev)
     orf, Sr = ref.chunked_delta_rule(refs[0].repeat_interleave(rep, dim=2), refs[1].repeat_interleave(rep, dim=2), *refs[2:], start.to(dev), S0r, 64)
-    _close(o, orf, 2e-2, 3e-2, "o")
+    slack = beta_max                # the inverse's entries reach about beta_max: bf16 rounds them at that absolute error
+    _close(o, orf, 2e-2 * slack, 3e-2, "o")
     go = torch.randn_like(orf)
     if with_state:
-        _close(S, Sr, 2e-2, 3e-2, "S")
+        _close(S, Sr, 2e-2 * slack, 3e-2, "S")
         gS = torch.randn_like(Sr) * 0.1
         torch.autograd.backward([o, S], [go.to(o.dtype), gS])
         torch.autograd.backward([orf, Sr], [go, gS])
-        _close(S0d.grad, S0r.grad, 3e-2, 5e-2, "dS0")
+        _close(S0d.grad, S0r.grad, 3e-2 * slack, 5e-2, "dS0")
     else:
         o.backward(go.to(o.dtype))
         orf.backward(go)
     native.check_status()
     for n, a, b in zip(("dq", "dk", "dv", "dg", "dbeta"), leaves, refs):
         scale = b.grad.abs().max().item()
-        _close(a.grad, b.grad, 3e-2 * scale, 5e-2, n)
+        _close(a.grad, b.grad, 3e-2 * scale * slack, 5e-2, n)
 
 
 def test_cuda_graph_training_matches_eager():

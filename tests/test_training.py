@@ -192,3 +192,34 @@ def test_data_prefetch_trains_on_the_same_batches(tmp_path):
         return [t.train_step()["loss"] for _ in range(3)]
 
     assert run(False) == run(True)
+
+
+def test_experimental_arms_train(tmp_path):
+    """Residual scalars (span form: stored values projected back into [-3, 3] after each step, no weight decay), Canon
+    layers and the doubled write-strength range train through the public trainer."""
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    cfg = tiny_train_config()
+    cfg.model = C.tiny_control_config()
+    cfg.model.encoder.layer_scalars = "skip_x0_span"
+    cfg.model.encoder.gdn.negeig.beta_max = 2
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "s")
+    groups = optim.param_groups(t.model, cfg.optim)
+    plain = [g for g in groups if g["weight_decay"] == 0.0][0]["names"]
+    assert "encoder.skip_gain" in plain and "encoder.x0_gain" in plain
+    with torch.no_grad():
+        t.model.encoder.skip_gain.fill_(7.0)
+    t.train_step()
+    assert float(t.model.encoder.skip_gain.abs().max()) <= 3.0
+    assert t.model.encoder.x0_gain[0] == 0 and t.model.encoder.x0_gain[1:].abs().sum() > 0     # b_0 is never read
+    cfg2 = tiny_train_config()
+    cfg2.model = C.tiny_control_config()
+    cfg2.model.encoder.canon_kernel, cfg2.model.encoder.canon_init = 4, "uniform"
+    t2 = Trainer(copy.deepcopy(cfg2), tmp_path / "c")
+    before = {n: p.detach().clone() for n, p in t2.model.named_parameters() if n.endswith("canon.conv_weight")}
+    assert before and all(v.abs().max() > 0 for v in before.values())
+    l0 = t2.train_step()["loss"]
+    for _ in range(3):
+        l1 = t2.train_step()["loss"]
+    assert l1 < l0
+    assert all(not torch.equal(before[n], p) for n, p in t2.model.named_parameters() if n in before)
