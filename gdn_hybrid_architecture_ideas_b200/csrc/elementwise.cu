@@ -13,7 +13,15 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+// ex2.approx.ftz and rcp.approx.ftz: one issue slot each, relative error of a few ulp (the default forms add denormal
+// scaling, a full-precision division an order of magnitude more; the elementwise kernels are issue-bound). Saturates
+// correctly: ex2 of a large argument is inf and rcp(inf) = 0.
+__device__ __forceinline__ float sigmoidf_(float x) {
+  float e, y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(1.f + e));
+  return y;
+}
 
 template <typename T> struct Vec4;
 template <> struct Vec4<float> {

@@ -20,7 +20,13 @@ __device__ __forceinline__ float wmax(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
-__device__ __forceinline__ float sigm(float x) { return 1.f / (1.f + __expf(-x)); }
+// Special-function instructions in their flush-to-zero forms: one issue slot each (the default forms add denormal
+// scaling around them, and a full-precision division costs an order of magnitude more; the elementwise kernels here are
+// issue-bound). Relative error of a few ulp; ex2 of a large argument gives inf and rcp(inf) = 0, so sigm saturates.
+__device__ __forceinline__ float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float fast_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float fast_rsqrt(float x) { float y; asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float sigm(float x) { return fast_rcp(1.f + fast_ex2(-1.4426950408889634f * x)); }
 __device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&v)[4]) {
   uint2 t = *reinterpret_cast<const uint2*>(p);
   float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&t.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&t.y));
@@ -38,9 +44,9 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&v)[4]) {
 // the rest v (no norm). dk must be 128.
 constexpr int PREP_K = 4;
 
-// Forward: half a warp walks TOK consecutive tokens of one 128-channel group, 8 channels per lane (16-byte loads and
-// stores), keeping the last K inputs in registers so every input row is read once; the next token's row is fetched
-// while the current one is computed. The L2 norm of a q or k head is a reduction over the 16 lanes of the half-warp.
+// Both kernels work on tiles of PREP_TOK tokens x 128 channels: the CTA first issues every load of the tile (inputs with
+// the K - 1 rows before it, 16 bytes per thread and load, all in flight together) into shared memory, then half-warps
+// take tokens (8 channels per lane, 16-byte stores); the L2 norm of a q or k head is a reduction over the 16 lanes.
 __device__ __forceinline__ void ld8(const __nv_bfloat16* p, float (&v)[8]) {
   const uint4 t = *reinterpret_cast<const uint4*>(p);
   const uint32_t w[4] = {t.x, t.y, t.z, t.w};
@@ -59,200 +65,249 @@ __device__ __forceinline__ float hsum16(float v) {       // sum over the 16 lane
   return v;
 }
 
-__global__ void __launch_bounds__(256) gdn_prep_fwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
-                                                           __nv_bfloat16* __restrict__ out, long rows, int L, int C, int nq, float qscale, int tok_per_unit) {
-  const int lane16 = threadIdx.x & 15;
-  const int groups = C / 128;
-  const long chunks = (rows + tok_per_unit - 1) / tok_per_unit;
-  const long unit = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 4;      // one half-warp per unit
-  const bool live = unit < chunks * groups;                                                // dead half-warps still join the shuffles
-  const long chunk = live ? unit / groups : 0; const int grp = live ? static_cast<int>(unit % groups) : 0;
-  const int c = grp * 128 + lane16 * 8;
-  float wt[8][PREP_K];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) { const float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c + e) * PREP_K); wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w; }
-  const long r0 = chunk * tok_per_unit, r1 = live ? min(rows, r0 + tok_per_unit) : r0;
-  float win[PREP_K][8];            // win[j] = u[s - j]
-  int dd[PREP_K];
-#pragma unroll
-  for (int j = 0; j < PREP_K; ++j) {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) win[j][e] = 0.f;
-    dd[j] = -1;
+constexpr int PREP_TOK = 64;
+
+struct PrepTile {        // the tile's place: 128-channel group, first row, and rows of the tensor
+  int grp; long r0, r1;
+};
+
+// Rows [r_lo, r_lo + n) of one 128-channel group into shared memory (row-major, 128 bf16 per row); rows outside
+// [0, rows) are zero-filled.
+__device__ __forceinline__ void prep_load_rows(const __nv_bfloat16* __restrict__ g, __nv_bfloat16* sm, long r_lo, int n, long rows, int C, int c0) {
+  for (int i = threadIdx.x; i < n * 16; i += blockDim.x) {
+    const long r = r_lo + (i >> 4);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r >= 0 && r < rows) v = *reinterpret_cast<const uint4*>(g + r * C + c0 + (i & 15) * 8);
+    reinterpret_cast<uint4*>(sm)[i] = v;
   }
-#pragma unroll
-  for (int j = 1; j < PREP_K; ++j)
-    if (live && r0 - j >= 0) { ld8(u + (r0 - j) * C + c, win[j - 1]); dd[j - 1] = doc ? doc[r0 - j] : 0; }
-  float nu[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  int ndoc = 0;
-  if (r0 < r1) { ld8(u + r0 * C + c, nu); ndoc = doc ? doc[r0] : 0; }
-  const bool normed = c < 2 * nq;
-  const float s_norm = c < nq ? qscale : 1.f;
-  const long mine = r1 - r0, other = __shfl_xor_sync(0xffffffffu, mine, 16);
-  const long steps = mine > other ? mine : other;
-  for (long k = 0; k < steps; ++k) {          // both halves of the warp run the same number of steps (the shuffles need every lane)
-    const long s = r0 + k;
-    const bool on = s < r1;
-#pragma unroll
-    for (int j = PREP_K - 1; j > 0; --j) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) win[j][e] = win[j - 1][e];
-      dd[j] = dd[j - 1];
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) win[0][e] = nu[e];
-    dd[0] = ndoc;
-    if (s + 1 < r1) { ld8(u + (s + 1) * C + c, nu); ndoc = doc ? doc[s + 1] : 0; }
-    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (on) {
+}
+__device__ __forceinline__ void lds8(const __nv_bfloat16* p, float (&v)[8]) { ld8(p, v); }
+
+// Valid taps of every token of a tile, formed once per CTA (the lanes then compare one small integer per tap):
+// back[i]: how many of u[s], u[s-1], ... token s = r0 + i reads (same row, same document); fwd[i]: how many of the tokens
+// s, s+1, ... read u[s]. sdoc: document ids of rows r_lo .. r_lo + n - 1 (zeros without ids), r_lo = r0 - (K - 1).
+__device__ __forceinline__ void prep_tap_counts(const int* sdoc, bool has_doc, long r0, int n_tok, long rows, int L, unsigned char* back, unsigned char* fwd) {
+  for (int i = threadIdx.x; i < n_tok; i += blockDim.x) {
+    const long s = r0 + i;
+    int nb = 0, nf = 0;
+    if (s < rows) {
       const int t = static_cast<int>(s % L);
-#pragma unroll
+      const int d = sdoc[i + PREP_K - 1];
       for (int j = 0; j < PREP_K; ++j) {
-        if (t - j < 0 || (doc && dd[j] != dd[0])) break;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] += win[j][e] * wt[e][PREP_K - 1 - j];
+        if (t - j < 0 || (has_doc && sdoc[i + PREP_K - 1 - j] != d)) break;
+        ++nb;
       }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) a[e] = a[e] * sigm(a[e]);
-    }
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ss += a[e] * a[e];
-    ss = hsum16(ss);
-    if (on) {
-      if (normed) {
-        const float r = rsqrtf(ss + 1e-6f) * s_norm;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) a[e] *= r;
+      if (fwd && i < PREP_TOK) {               // only the tile's own tokens are written; later rows' documents are not staged
+        for (int j = 0; j < PREP_K; ++j) {
+          if (t + j >= L || s + j >= rows || (has_doc && sdoc[i + PREP_K - 1 + j] != d)) break;
+          ++nf;
+        }
       }
-      st8(out + s * C + c, a);
     }
+    back[i] = static_cast<unsigned char>(nb);
+    if (fwd) fwd[i] = static_cast<unsigned char>(nf);
   }
 }
 
-// Backward, one pass: a warp walks TOK consecutive tokens of one 128-channel group (4 channels per lane). At token s it
-// recomputes the conv output from a register window of the last K inputs, forms dconv[s] (through the L2 norm and
-// SiLU) and adds dconv[s] u[s - j] into its conv-weight partial; K - 1 tokens later du[s - (K-1)] =
-// sum_j dconv[s - (K-1) + j] w[K-1-j] leaves from a register window of the last K dconv rows. The K - 1 tokens after
-// the warp's range are recomputed (they belong to the next warp) so no dconv tensor ever reaches memory. Loads run
-// one token ahead of the arithmetic.
-__global__ void gdn_prep_bwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
-                                    const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ du, float* __restrict__ dw,
-                                    long rows, int L, int C, int nq, float qscale, int tok_per_warp) {
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(256) gdn_prep_fwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                                           __nv_bfloat16* __restrict__ out, long rows, int L, int C, int nq, float qscale) {
+  __shared__ __align__(16) __nv_bfloat16 su[(PREP_TOK + PREP_K - 1) * 128];
+  __shared__ int sdoc[PREP_TOK + PREP_K - 1];
+  __shared__ unsigned char sback[PREP_TOK];
   const int groups = C / 128;
-  const long chunks = (rows + tok_per_warp - 1) / tok_per_warp;
-  const long unit = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= chunks * groups) return;
-  const long chunk = unit / groups; const int grp = static_cast<int>(unit % groups);
-  const int c = grp * 128 + lane * 4;
-  float wt[4][PREP_K], acc[4][PREP_K];
+  const int grp = blockIdx.x % groups;
+  const long r0 = static_cast<long>(blockIdx.x / groups) * PREP_TOK, r1 = min(rows, r0 + PREP_TOK);
+  const int c0 = grp * 128, l = threadIdx.x & 15, hw = threadIdx.x >> 4;
+  prep_load_rows(u, su, r0 - (PREP_K - 1), PREP_TOK + PREP_K - 1, rows, C, c0);
+  if (threadIdx.x < PREP_TOK + PREP_K - 1) {
+    const long r = r0 - (PREP_K - 1) + threadIdx.x;
+    sdoc[threadIdx.x] = (doc && r >= 0 && r < rows) ? doc[r] : 0;
+  }
+  float wt[8][PREP_K];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c + e) * PREP_K);
+  for (int e = 0; e < 8; ++e) { const float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c0 + l * 8 + e) * PREP_K); wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w; }
+  const bool normed = c0 < 2 * nq;
+  const float s_norm = c0 < nq ? qscale : 1.f;
+  __syncthreads();
+  prep_tap_counts(sdoc, doc != nullptr, r0, PREP_TOK, rows, L, sback, nullptr);
+  __syncthreads();
+#pragma unroll 1
+  for (int i = hw; i < PREP_TOK; i += 16) {      // every half-warp runs the same trip count: the shuffles need all lanes
+    const long s = r0 + i;
+    const bool on = s < r1;
+    const int taps = sback[i];
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < PREP_K; ++j) {
+      if (j < taps) {
+        float x[8];
+        lds8(su + (i + PREP_K - 1 - j) * 128 + l * 8, x);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] += x[e] * wt[e][PREP_K - 1 - j];
+      }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { a[e] = a[e] * sigm(a[e]); ss += a[e] * a[e]; }
+    if (normed) {
+      ss = hsum16(ss);
+      const float r = fast_rsqrt(ss + 1e-6f) * s_norm;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a[e] *= r;
+    }
+    if (on) st8(out + s * C + c0 + l * 8, a);
+  }
+}
+
+// Backward, one pass per tile: dconv of the tile's tokens and of the K - 1 tokens after it (their taps reach back into
+// the tile; they are recomputed, not read) is formed from the staged inputs and output gradients and kept in shared
+// memory in fp32; then du[s] = sum_j dconv[s + j] w[K-1-j]. The conv-weight gradient is summed per thread over the
+// CTA's tiles (a thread keeps its 8 channels), across the CTA's half-warps in shared memory, then one atomic per entry.
+constexpr int PREP_BROWS = PREP_TOK + 2 * (PREP_K - 1);      // input rows a backward tile reads
+constexpr int PREP_DROWS = PREP_TOK + PREP_K - 1;            // rows of dout read / of dconv formed
+constexpr int PREP_BWD_SMEM = PREP_BROWS * 256 + PREP_DROWS * 256 + PREP_DROWS * 512 + PREP_BROWS * 4 + 2 * PREP_DROWS + 2;
+
+__global__ void __launch_bounds__(256, 2) gdn_prep_bwd_kernel(const __nv_bfloat16* __restrict__ u, const int* __restrict__ doc, const float* __restrict__ w,
+                                                              const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ du, float* __restrict__ dw,
+                                                              long rows, int L, int C, int nq, float qscale, int tiles_per_cta) {
+  extern __shared__ __align__(16) unsigned char prep_smem[];
+  __nv_bfloat16* su = reinterpret_cast<__nv_bfloat16*>(prep_smem);                       // [PREP_BROWS][128], row 0 = r0 - (K-1)
+  __nv_bfloat16* sdy = su + PREP_BROWS * 128;                                             // [PREP_DROWS][128], row 0 = r0
+  float* sdc = reinterpret_cast<float*>(sdy + PREP_DROWS * 128);                          // [PREP_DROWS][128]: lane l's channels at l*4 and 64 + l*4
+  int* sdoc = reinterpret_cast<int*>(sdc + PREP_DROWS * 128);                             // [PREP_BROWS]
+  unsigned char* sback = reinterpret_cast<unsigned char*>(sdoc + PREP_BROWS);             // [PREP_DROWS]
+  unsigned char* sfwd = sback + PREP_DROWS;                                               // [PREP_DROWS]
+  const int groups = C / 128;
+  const int grp = blockIdx.x % groups;
+  const long tile0 = static_cast<long>(blockIdx.x / groups) * tiles_per_cta;
+  const int c0 = grp * 128, l = threadIdx.x & 15, hw = threadIdx.x >> 4;
+  float wt[8][PREP_K], acc[8][PREP_K];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float4 q = *reinterpret_cast<const float4*>(w + static_cast<long>(c0 + l * 8 + e) * PREP_K);
     wt[e][0] = q.x; wt[e][1] = q.y; wt[e][2] = q.z; wt[e][3] = q.w;
 #pragma unroll
     for (int j = 0; j < PREP_K; ++j) acc[e][j] = 0.f;
   }
-  const long r0 = chunk * tok_per_warp, r1 = min(rows, r0 + tok_per_warp);
-  float uw[PREP_K][4], dc[PREP_K][4];     // uw[j] = u[s - j], dc[j] = dconv[s - j] at step s
-  int dd[PREP_K];                          // document ids of tokens s - j
-#pragma unroll
-  for (int j = 0; j < PREP_K; ++j) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) { uw[j][e] = 0.f; dc[j][e] = 0.f; }
-    dd[j] = -1;
-  }
-#pragma unroll
-  for (int j = 1; j < PREP_K; ++j) {       // the window before the first token (entries of another row are never used)
-    if (r0 - (j - 1) - 1 >= 0) { ld4(u + (r0 - j) * C + c, uw[j - 1]); dd[j - 1] = doc ? doc[r0 - j] : 0; }
-  }
-  float nu[4] = {0.f, 0.f, 0.f, 0.f}, ndy[4] = {0.f, 0.f, 0.f, 0.f};
-  int ndoc = 0;
-  if (r0 < rows) { ld4(u + r0 * C + c, nu); ld4(dout + r0 * C + c, ndy); ndoc = doc ? doc[r0] : 0; }
-  const float s_norm = c < nq ? qscale : 1.f;
-  const bool normed = c < 2 * nq;
-  for (long s = r0; s < r1 + (PREP_K - 1); ++s) {
-#pragma unroll
-    for (int j = PREP_K - 1; j > 0; --j) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { uw[j][e] = uw[j - 1][e]; dc[j][e] = dc[j - 1][e]; }
-      dd[j] = dd[j - 1];
+  const bool normed = c0 < 2 * nq;
+  const float s_norm = c0 < nq ? qscale : 1.f;
+  for (int tile = 0; tile < tiles_per_cta; ++tile) {
+    const long r0 = (tile0 + tile) * PREP_TOK;
+    if (r0 >= rows) break;                      // uniform over the CTA
+    const long r1 = min(rows, r0 + PREP_TOK);
+    __syncthreads();                            // the previous tile's readers are done
+    prep_load_rows(u, su, r0 - (PREP_K - 1), PREP_BROWS, rows, C, c0);
+    prep_load_rows(dout, sdy, r0, PREP_DROWS, rows, C, c0);
+    if (threadIdx.x < PREP_BROWS) {
+      const long r = r0 - (PREP_K - 1) + threadIdx.x;
+      sdoc[threadIdx.x] = (doc && r >= 0 && r < rows) ? doc[r] : 0;
     }
-    float dy[4];
+    __syncthreads();
+    prep_tap_counts(sdoc, doc != nullptr, r0, PREP_DROWS, rows, L, sback, sfwd);
+    __syncthreads();
+    // ---- dconv of tokens r0 .. r0 + PREP_DROWS - 1 (token index i: input row i + K - 1 of su)
+#pragma unroll 1
+    for (int round = 0; round < (PREP_DROWS + 15) / 16; ++round) {      // the same trip count for every half-warp (shuffles below)
+      const int i = hw + 16 * round;
+      const bool on = i < PREP_DROWS && r0 + i < rows;
+      const int taps = on ? sback[i] : 0;
+      float pre[8], a[8], dy[8];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) { uw[0][e] = nu[e]; dy[e] = ndy[e]; dc[0][e] = 0.f; }
-    dd[0] = ndoc;
-    const bool in = s < rows;
-    if (s + 1 < rows && s + 1 < r1 + (PREP_K - 1)) { ld4(u + (s + 1) * C + c, nu); ld4(dout + (s + 1) * C + c, ndy); ndoc = doc ? doc[s + 1] : 0; }
-    if (in) {
-      const int t = static_cast<int>(s % L);
-      float pre[4] = {0.f, 0.f, 0.f, 0.f}, a[4], da[4];
-      int taps = 0;                         // valid taps of token s: the same count gates the weight-gradient terms
+      for (int e = 0; e < 8; ++e) { pre[e] = 0.f; dy[e] = 0.f; }
+      if (on) lds8(sdy + i * 128 + l * 8, dy);
 #pragma unroll
       for (int j = 0; j < PREP_K; ++j) {
-        if (t - j < 0 || (doc && dd[j] != dd[0])) break;
-        ++taps;
+        if (j < taps) {
+          float x[8];
+          lds8(su + (i + PREP_K - 1 - j) * 128 + l * 8, x);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) pre[e] += uw[j][e] * wt[e][PREP_K - 1 - j];
+          for (int e = 0; e < 8; ++e) pre[e] += x[e] * wt[e][PREP_K - 1 - j];
+        }
       }
+      float sg[8], ss = 0.f, ady = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) a[e] = pre[e] * sigm(pre[e]);
-      if (normed) {
-        const float ss = wsum(a[0] * a[0] + a[1] * a[1] + a[2] * a[2] + a[3] * a[3]);
-        const float r = rsqrtf(ss + 1e-6f);
-        const float ady = wsum(a[0] * dy[0] + a[1] * dy[1] + a[2] * dy[2] + a[3] * dy[3]);
+      for (int e = 0; e < 8; ++e) { sg[e] = sigm(pre[e]); a[e] = pre[e] * sg[e]; ss += a[e] * a[e]; ady += a[e] * dy[e]; }
+      if (normed) { ss = hsum16(ss); ady = hsum16(ady); }
+      if (on) {
+        float dc[8];
+        const float r = fast_rsqrt(ss + 1e-6f);
+        const float k1 = s_norm * r, k2 = r * r * ady;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) da[e] = s_norm * r * (dy[e] - a[e] * r * r * ady);
-      } else {
+        for (int e = 0; e < 8; ++e) {
+          const float da = normed ? k1 * (dy[e] - a[e] * k2) : dy[e];
+          dc[e] = da * (sg[e] + a[e] * (1.f - sg[e]));          // d silu = sg (1 + pre (1 - sg))
+        }
+        *reinterpret_cast<float4*>(sdc + i * 128 + l * 4) = make_float4(dc[0], dc[1], dc[2], dc[3]);
+        *reinterpret_cast<float4*>(sdc + i * 128 + 64 + l * 4) = make_float4(dc[4], dc[5], dc[6], dc[7]);
+        if (i < PREP_TOK) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) da[e] = dy[e];
-      }
+          for (int j = 0; j < PREP_K; ++j) {
+            if (j < taps) {
+              float x[8];
+              lds8(su + (i + PREP_K - 1 - j) * 128 + l * 8, x);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { const float sg = sigm(pre[e]); dc[0][e] = da[e] * sg * (1.f + pre[e] * (1.f - sg)); }
-      if (s < r1) {
-#pragma unroll
-        for (int j = 0; j < PREP_K; ++j) {
-          if (j < taps) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[e][PREP_K - 1 - j] += dc[0][e] * uw[j][e];
+              for (int e = 0; e < 8; ++e) acc[e][PREP_K - 1 - j] += dc[e] * x[e];
+            }
           }
         }
       }
     }
-    const long tr = s - (PREP_K - 1);       // the token whose last reader (tap K-1) was just formed
-    if (tr >= r0 && tr < r1) {
-      const int tt = static_cast<int>(tr % L);
-      float g[4] = {0.f, 0.f, 0.f, 0.f};
+    __syncthreads();
+    // ---- du of the tile's tokens
+#pragma unroll 1
+    for (int i = hw; i < PREP_TOK; i += 16) {
+      const long tr = r0 + i;
+      if (tr >= r1) break;
+      const int nf = sfwd[i];
+      float g[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < PREP_K; ++j) {     // token tr + j reads tr through tap j
-        if (tt + j >= L || tr + j >= rows || (doc && dd[PREP_K - 1 - j] != dd[PREP_K - 1])) break;
+      for (int j = 0; j < PREP_K; ++j) {       // token tr + j reads tr through tap j
+        if (j < nf) {
+          const float4 d0 = *reinterpret_cast<const float4*>(sdc + (i + j) * 128 + l * 4), d1 = *reinterpret_cast<const float4*>(sdc + (i + j) * 128 + 64 + l * 4);
+          const float dcv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) g[e] += dc[PREP_K - 1 - j][e] * wt[e][PREP_K - 1 - j];
+          for (int e = 0; e < 8; ++e) g[e] += dcv[e] * wt[e][PREP_K - 1 - j];
+        }
       }
-      st4(du + tr * C + c, g);
+      st8(du + tr * C + c0 + l * 8, g);
     }
   }
+  // ---- conv-weight gradient: sum the 16 half-warps in shared memory (the dconv buffer is free now), one atomic per entry
+  __syncthreads();
 #pragma unroll
-  for (int e = 0; e < 4; ++e)
+  for (int e = 0; e < 8; ++e)
 #pragma unroll
-    for (int j = 0; j < PREP_K; ++j) atomicAdd(dw + static_cast<long>(c + e) * PREP_K + j, acc[e][j]);
+    for (int j = 0; j < PREP_K; ++j) sdc[hw * 512 + (l * 8 + e) * PREP_K + j] = acc[e][j];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+    float t = 0.f;
+#pragma unroll
+    for (int h = 0; h < 16; ++h) t += sdc[h * 512 + i];
+    atomicAdd(dw + static_cast<long>(c0) * PREP_K + i, t);
+  }
 }
 
 int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long rows, int L, int C, int nq, float qscale, cudaStream_t st) {
   if (C % 128 || nq % 128) return 1;
-  const int tok = 64;
-  const long units = ((rows + tok - 1) / tok) * (C / 128);          // half-warps
-  gdn_prep_fwd_kernel<<<static_cast<unsigned>((units + 15) / 16), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<__nv_bfloat16*>(out), rows, L, C, nq, qscale, tok);
+  const long tiles = (rows + PREP_TOK - 1) / PREP_TOK;
+  gdn_prep_fwd_kernel<<<static_cast<unsigned>(tiles * (C / 128)), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<__nv_bfloat16*>(out), rows, L, C, nq, qscale);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* du, float* dw, long rows, int L, int C,
                  int nq, float qscale, cudaStream_t st) {
   if (C % 128 || nq % 128) return 1;
-  const int tok = 64;
-  const long units = ((rows + tok - 1) / tok) * (C / 128);
-  gdn_prep_bwd_kernel<<<static_cast<unsigned>((units + 7) / 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dout),
-                                                                            static_cast<__nv_bfloat16*>(du), dw, rows, L, C, nq, qscale, tok);
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(gdn_prep_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PREP_BWD_SMEM) != cudaSuccess) return 4;
+    cudaFuncSetAttribute(gdn_prep_bwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaFuncSetAttribute(gdn_prep_fwd_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    attr = true;
+  }
+  const long tiles = (rows + PREP_TOK - 1) / PREP_TOK;
+  const int per = tiles >= 64 ? 4 : 1;          // several tiles per CTA: fewer conv-weight atomics
+  const long ctas = (tiles + per - 1) / per;
+  gdn_prep_bwd_kernel<<<static_cast<unsigned>(ctas * (C / 128)), 256, PREP_BWD_SMEM, st>>>(
+      static_cast<const __nv_bfloat16*>(u), doc, w, static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(du), dw, rows, L, C, nq, qscale, per);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

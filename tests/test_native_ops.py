@@ -197,11 +197,11 @@ def test_swiglu_mlp():
         _close(a.grad, b.grad, 1e-1, 5e-2)
 
 
-@pytest.mark.parametrize("single", [True, False])
-def test_gdn_prep(single):
+@pytest.mark.parametrize("single,L", [(True, 200), (False, 200), (False, 2100)])
+def test_gdn_prep(single, L):
     from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
 
-    B, L, hk, hv, dk, dv = 2, 200, 2, 2, 128, 256
+    B, hk, hv, dk, dv = 2, 2, 2, 128, 256
     C = 2 * hk * dk + hv * dv
     u = torch.randn(B, L, C, device=_dev()).to(torch.bfloat16).requires_grad_()
     w = (torch.randn(C, 4, device=_dev()) * 0.5).requires_grad_()
@@ -210,6 +210,7 @@ def test_gdn_prep(single):
         doc[0, 50:] = 1
         doc[0, 51:] = 2
         doc[1, 199:] = 3
+        doc[1, L - 1:] = 4
     q, k, v, hist, _ = native.gdn_prep(u, doc, w, hk, hv, dk, dv, single_doc=single)
     ur, wr = u.detach().float().requires_grad_(), w.detach().clone().requires_grad_()
     qr, kr, vr, histr, _ = ref.gdn_prep(ur, doc, wr, hk, hv, dk, dv)
