@@ -658,7 +658,7 @@ _BUILT = {
     "model.loop.recur_layers": ((),),
     "model.loop.segment_passes": (None,),
     "model.loop.unscored_passes": (None,),
-    "model.mtp.enabled": (False,),
+    "model.mtp.enabled": (False, True),
     "model.cp_head.enabled": (False,),
     "model.fp8.mode": ("none", "linears"),
     "model.fp8.scaling": ("rowwise", "tensorwise", "mxfp8"),

@@ -114,7 +114,12 @@ def build_model(cfg: ModelConfig) -> HybridLM:
     """Validated model with initial weights: every Linear/Embedding N(0, init_std); norm gains, depth queries and mix
     lambdas zero; GDN gates by `gdn.init`; low-precision recipes applied last (reference: ced/model/control.py:1246-1346)."""
     require_supported(cfg)
+    from .mtp import attach_mtp, check_mtp
+
+    check_mtp(cfg)
     model = HybridLM(cfg)
+    if cfg.mtp.enabled:
+        attach_mtp(model)       # drawn after every trunk tensor: the trunk starts as the model without the key
     from .lowp import apply_low_precision
 
     apply_low_precision(model, cfg)

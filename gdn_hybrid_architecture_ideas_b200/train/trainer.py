@@ -51,6 +51,9 @@ def pick_device(name: str) -> torch.device:
 class Trainer:
     def __init__(self, cfg: C.TrainConfig, run_dir: str | Path | None = None, dp=None, device: torch.device | None = None):
         C.require_supported(cfg)
+        if cfg.model.mtp.enabled:
+            raise ValueError("model.mtp.enabled: the trainer trains the trunk; the drafter head is trained on a frozen trunk "
+                             "by models.mtp.train_step (scripts/train_mtp.py)")
         self.cfg, self.dp = cfg, dp
         self.run_dir = Path(run_dir) if run_dir is not None else None
         self.device = device or (dp.device if dp is not None else pick_device(cfg.device))

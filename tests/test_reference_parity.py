@@ -94,3 +94,49 @@ def test_every_reference_run_file_parses(reference):
             C.unsupported_options(cfg)   # parses and classifies; experimental arms are reported, not crashed on
             seen += 1
     assert seen > 20
+
+
+def test_mtp_head_matches_reference(reference):
+    """The drafter head on a frozen trunk: same state-dict keys and start under the same seed, same head output and
+    gradients, the trunk untouched by the key."""
+    import ced.config as RC
+    from ced.model import mtp as rmtp
+    from ced.model.sequence import sequence_context as ref_context
+
+    from gdn_hybrid_architecture_ideas_b200.models import mtp
+    from gdn_hybrid_architecture_ideas_b200.models.sequence import sequence_context
+
+    cfg = C.tiny_control_config()
+    plain, _ = _pair(reference, cfg)
+    cfg.mtp.enabled = True
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and any(k.startswith("mtp.") for k in sd)
+    assert all(torch.equal(sd[k], rsd[k]) for k in sd)
+    assert all(torch.equal(v, sd[k]) for k, v in plain.state_dict().items()), "the key changed the trunk's start"
+    tok, doc = random_rows(2, 40)
+    targets = torch.cat([tok[:, 1:], tok[:, :1]], 1)
+    valid = torch.cat([doc[:, 1:] == doc[:, :-1], torch.zeros(2, 1, dtype=torch.bool)], 1)
+    head = mtp.freeze_trunk(mine)
+    rmtp.freeze_trunk(theirs)
+    assert len(head) == len(rmtp.mtp_parameter_names(theirs))
+    ha, hb = mtp.trunk_hidden(mine, tok, doc), rmtp.trunk_hidden(theirs, tok, doc)
+    assert (ha - hb).abs().max() < 1e-10
+    ya, _ = mine.mtp(ha, targets, mine.embed, sequence_context(doc)[0])
+    yb, _ = theirs.mtp(hb, targets, theirs.embed, ref_context(doc, None)[0])
+    assert (ya - yb).abs().max() < 1e-10
+    t2a, v2a = mtp.mtp_targets(targets, valid)
+    t2b, v2b = rmtp.mtp_targets(targets, valid)
+    assert torch.equal(t2a, t2b) and torch.equal(v2a, v2b)
+    ga = torch.autograd.grad(mine.mtp.out_norm(ya).pow(3).sum(), head)
+    gb = torch.autograd.grad(theirs.mtp.out_norm(yb).pow(3).sum(), [p for n, p in theirs.named_parameters() if n.startswith("mtp.")])
+    assert max((x - y).abs().max() for x, y in zip(ga, gb)) < 1e-9
+    mtp.assert_trunk_frozen(mine)
+    opt = torch.optim.AdamW(head, lr=3e-3)
+    first = mtp.train_step(mine, opt, tok, doc, targets, valid)
+    for _ in range(30):
+        last = mtp.train_step(mine, opt, tok, doc, targets, valid)
+    assert last["loss"] < first["loss"] and last["positions"] == int(v2a.sum())
+    ctx = sequence_context(doc[:, :1])[0]
+    drafts, _ = mtp.draft(mine, ha[:, :1], targets[:, :1], ctx, depth=3)
+    assert drafts.shape == (2, 3)

@@ -223,3 +223,24 @@ def test_experimental_arms_train(tmp_path):
         l1 = t2.train_step()["loss"]
     assert l1 < l0
     assert all(not torch.equal(before[n], p) for n, p in t2.model.named_parameters() if n in before)
+
+
+def test_train_mtp_script(tmp_path):
+    """The drafter-head script: loads a trained trunk, freezes it, trains the head, saves the head's tensors only."""
+    cfg = tiny_train_config()
+    cfg.model = C.tiny_control_config()
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "run")
+    t.fit()
+    trunk = weights(t)
+    out = tmp_path / "head.pt"
+    r = subprocess.run([sys.executable, str(ROOT / "scripts" / "train_mtp.py"), "--checkpoint", str(tmp_path / "run"), "--steps", "12", "--lr", "3e-3",
+                        "--device", "cpu", "--log-every", "11", "--out", str(out)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert lines[-1]["loss"] < lines[0]["loss"]
+    saved = torch.load(out, weights_only=False)
+    assert saved["trunk_step"] == 6 and all(k.startswith("mtp.") for k in saved["head"]) and "mtp.eh_proj.weight" in saved["head"]
+    with pytest.raises(ValueError, match="mtp"):
+        bad = copy.deepcopy(cfg)
+        bad.model.mtp.enabled = True
+        Trainer(bad, tmp_path / "bad")
