@@ -321,3 +321,28 @@ def test_bpb_readout_uses_fixed_rows(tmp_path):
     t.fit()
     lines = [json.loads(x) for x in (tmp_path / "r" / "metrics.jsonl").read_text().splitlines()]
     assert sum(1 for x in lines if x.get("event") == "readout") == 2
+
+
+def test_routed_swiglu_dispatch_equals_dense():
+    """Token dispatch (each expert on its routed tokens only) equals the every-expert-on-every-token statement, values and
+    gradients; the balance statistic is 1 for uniform routing probabilities."""
+    import torch
+
+    from gdn_hybrid_architecture_ideas_b200.models.mlp import RoutedSwiGLU
+
+    torch.manual_seed(0)
+    m = RoutedSwiGLU(32, 4, 2, 48).double()
+    x = torch.randn(3, 17, 32, dtype=torch.float64, requires_grad=True)
+    valid = torch.rand(3, 17) > 0.2
+    a = m(x, valid)
+    ga = torch.autograd.grad(a.square().sum(), [x, *m.parameters()])
+    b = m.forward_dense(x, valid)
+    gb = torch.autograd.grad(b.square().sum(), [x, *m.parameters()])
+    assert (a - b).abs().max() < 1e-12
+    assert max((p - q).abs().max() for p, q in zip(ga, gb)) < 1e-10
+    assert float(m.z_loss()) > 0
+    m.reset_stats()
+    with torch.no_grad():
+        m.router.weight.zero_()
+    m(x)
+    assert abs(float(m.balance_loss()) - 1.0) < 1e-9
