@@ -671,7 +671,7 @@ _BUILT = {
 _TRAIN_BUILT = {
     "optim.name": ("adamw", "muon"),
     "optim.hyperball": (False,),
-    "optim.gdn_mup": (False,),
+    "optim.gdn_mup": (False, True),
     "loss.normalization": ("global_token_mean",),
     "loss.ce_form": ("standard",),
     "head_impl": ("fused", "chunked"),

@@ -40,6 +40,50 @@ def is_muon_param(name: str, p: torch.Tensor) -> bool:
     return ".attn_res." not in name
 
 
+GDN_MUP_BASE_WIDTH = 512
+
+
+def gdn_mup_names(model) -> tuple[list[str], list[str]]:
+    """(gate projection weights, gate scalars) of every GatedDeltaNet, by parameter name, in the model's order."""
+    from ..models.gdn import GatedDeltaNet
+
+    gates, scalars = set(), set()
+    for prefix, m in model.named_modules():
+        if isinstance(m, GatedDeltaNet):
+            gates.update(f"{prefix}.{n}.weight" for n in ("in_proj_a", "in_proj_b"))
+            scalars.update(f"{prefix}.{n}" for n in ("A_log", "dt_bias"))
+    names = [n for n, _ in model.named_parameters()]
+    return [n for n in names if n in gates], [n for n in names if n in scalars]
+
+
+def _gdn_mup_spec(spec, model, o, base_scale: float):
+    """muP grouping of the GDN gates under AdamW: the gate projections leave their groups for one group per fan-in with
+    the learning rate scaled by base_width / fan_in (and the run's weight decay); A_log and dt_bias for one group at the
+    plain scale without decay. Every other tensor keeps its group and place (reference: ced/train/optim.py:654-712)."""
+    if type(o.gdn_mup_base_width) is not int or o.gdn_mup_base_width < 1:
+        raise ValueError(f"optim.gdn_mup_base_width {o.gdn_mup_base_width!r}: a positive integer")
+    gates, scalars = gdn_mup_names(model)
+    if not gates:
+        raise ValueError("optim.gdn_mup groups a model's GDN gates and scalars: this model has no GatedDeltaNet layer")
+    moved = set(gates) | set(scalars)
+    named = dict(model.named_parameters())
+    out = [(k, [(n, p) for n, p in items if n not in moved], wd, s) for k, items, wd, s in spec]
+    for fan_in in sorted({named[n].shape[1] for n in gates}):
+        out.append(("adamw", [(n, named[n]) for n in gates if named[n].shape[1] == fan_in], o.weight_decay,
+                    base_scale * o.gdn_mup_base_width / fan_in))
+    out.append(("adamw", [(n, named[n]) for n in scalars], 0.0, base_scale))
+    return out
+
+
+@torch.no_grad()
+def gdn_mup_init_(model, base_width: int = GDN_MUP_BASE_WIDTH) -> None:
+    """The gate projections as drawn times sqrt(base_width / fan_in): variance proportional to 1 / fan_in, today's at the
+    base width. No random number is drawn (reference: ced/train/optim.py:715-727)."""
+    named = dict(model.named_parameters())
+    for n in gdn_mup_names(model)[0]:
+        named[n].mul_((base_width / named[n].shape[1]) ** 0.5)
+
+
 def param_groups(model, o) -> list[dict]:
     """Groups as dicts {"names", "params", "weight_decay", "lr_scale", "kind"}; kind "adamw" or "muon"."""
     suffixes = no_decay_suffixes(o)
@@ -57,6 +101,10 @@ def param_groups(model, o) -> list[dict]:
                 ("adamw", plain, 0.0, o.adamw_lr_scale)]
     else:
         raise ValueError(f"optim.name {o.name!r}: 'adamw' or 'muon'")
+    if o.gdn_mup_base_width != GDN_MUP_BASE_WIDTH and not o.gdn_mup:
+        raise ValueError(f"optim.gdn_mup_base_width {o.gdn_mup_base_width!r} is read with optim.gdn_mup true: leave it {GDN_MUP_BASE_WIDTH}")
+    if o.gdn_mup:
+        spec = _gdn_mup_spec(spec, model, o, 1.0 if o.name == "adamw" else o.adamw_lr_scale)
     return [{"kind": k, "names": [n for n, _ in items], "params": [p for _, p in items], "weight_decay": wd, "lr_scale": s}
             for k, items, wd, s in spec if items]
 

@@ -75,6 +75,10 @@ class Trainer:
                 raise ValueError("tensor_parallel runs with optimizer_sharding=replicated and without token superposition")
             model_cfg = tp_model.local_model_config(cfg.model, dp.world)
         self.model = build_model(model_cfg).to(dtype).to(self.device)
+        if cfg.optim.gdn_mup:      # the gates' start with their learning rate (a resume then loads the trained values over it)
+            from .optim import gdn_mup_init_
+
+            gdn_mup_init_(self.model, cfg.optim.gdn_mup_base_width)
         if cfg.tensor_parallel > 1:
             from ..parallel.tensor_parallel import TensorParallel
 

@@ -244,3 +244,31 @@ def test_train_mtp_script(tmp_path):
         bad = copy.deepcopy(cfg)
         bad.model.mtp.enabled = True
         Trainer(bad, tmp_path / "bad")
+
+
+def test_gdn_mup_groups_and_init(tmp_path):
+    """optim.gdn_mup: the GDN gate projections get base_width / fan_in times the learning rate in a group of their own,
+    A_log / dt_bias a group without decay, nothing else moves; the gates start scaled by sqrt(base_width / fan_in)."""
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    cfg = tiny_train_config()
+    plain = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    cfg.optim.gdn_mup, cfg.optim.gdn_mup_base_width = True, 16
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    d = cfg.model.d_model
+    groups = optim.param_groups(t.model, cfg.optim)
+    base = optim.param_groups(plain.model, copy.deepcopy(plain.cfg.optim))
+    gate = [g for g in groups if any(n.endswith("in_proj_a.weight") for n in g["names"])]
+    assert len(gate) == 1 and gate[0]["lr_scale"] == 16 / d and gate[0]["weight_decay"] == cfg.optim.weight_decay
+    assert all(n.endswith(("in_proj_a.weight", "in_proj_b.weight")) for n in gate[0]["names"])
+    scal = [g for g in groups if any(n.endswith(".A_log") for n in g["names"])]
+    assert len(scal) == 1 and scal[0]["weight_decay"] == 0.0 and all(n.endswith((".A_log", ".dt_bias")) for n in scal[0]["names"])
+    assert sorted(n for g in groups for n in g["names"]) == sorted(n for g in base for n in g["names"])
+    pa, pb = dict(plain.model.named_parameters()), dict(t.model.named_parameters())
+    for n in pa:
+        want = pa[n] * (16 / d) ** 0.5 if n.endswith(("in_proj_a.weight", "in_proj_b.weight")) else pa[n]
+        assert torch.allclose(pb[n], want), n
+    l0 = t.train_step()["loss"]
+    for _ in range(4):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0
