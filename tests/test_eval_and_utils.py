@@ -346,3 +346,52 @@ def test_routed_swiglu_dispatch_equals_dense():
         m.router.weight.zero_()
     m(x)
     assert abs(float(m.balance_loss()) - 1.0) < 1e-9
+
+
+def test_recall_ruler_items_and_scoring(tmp_path):
+    """RULER subset: items are deterministic, fitted to the asked length under the token counter, hold their needles and
+    references; string-match recall and the values file; the scorer script runs a tiny byte-level model end to end."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import torch
+
+    from gdn_hybrid_architecture_ideas_b200 import config as C
+    from gdn_hybrid_architecture_ideas_b200.data.tokenizers import ByteTokenizer
+    from gdn_hybrid_architecture_ideas_b200.eval import recall_ruler as RR
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    tok = ByteTokenizer()
+    count = lambda t: len(tok.encode(t))
+    pool = [("The river bends twice before the mill. Nobody fishes there in winter. " * 40) + f"Document {i} ends here." for i in range(6)]
+    for task in RR.TASKS:
+        a = RR.make_item(task, 4096, 3, count, pool)
+        b = RR.make_item(task, 4096, 3, count, pool)
+        assert a.prompt == b.prompt and a.refs == b.refs and a.id == f"{task}/len=4096/0003"
+        assert 0.95 * (4096 - a.gen_tokens) <= count(a.prompt) <= 4096 - a.gen_tokens, (task, count(a.prompt))
+        n_refs = {"niah_multivalue": 4, "niah_multiquery": 4, "vt": 5}.get(task, 1)
+        assert len(a.refs) == n_refs and len(set(a.refs)) == n_refs
+        assert all(r in a.prompt for r in a.refs)
+        assert RR.make_item(task, 4096, 4, count, pool).prompt != a.prompt
+    single = RR.make_item("niah_multikey_2", 2048, 0, count)
+    assert "A special magic number is hidden" in single.prompt and single.prompt.endswith("mentioned in the provided text is")
+    assert RR.recall(" 12 and ABC\x00def", ["abc", "77"]) == 0.5 and RR.all_found("x1 y2", ["X1", "y2"]) == 1.0
+    vals = RR.values_file("r", [{"task": "vt", "length": 2048, "id": "a", "recall": 0.4, "all_found": 0.0},
+                                {"task": "vt", "length": 2048, "id": "b", "recall": 1.0, "all_found": 1.0},
+                                {"task": "niah_multikey_2", "length": 2048, "id": "c", "recall": 1.0, "all_found": 1.0}], excluded=["b"])
+    assert vals["cells"]["ruler|vt|2048|recall"] == 0.4 and vals["cells"]["ruler|mean|2048|recall"] == 0.7 and vals["n_items"] == 2
+
+    root = Path(__file__).resolve().parent.parent
+    cfg = C.TrainConfig(model=C.tiny_control_config(), data=C.tiny_data_config(seq_len=48, batch_size=2), steps=1, seed=1)
+    cfg.model.vocab_size = 256
+    cfg.ckpt_every_steps, cfg.metrics_jsonl, cfg.log_every = 1, False, 0
+    Trainer(cfg, tmp_path / "run").fit()
+    r = subprocess.run([sys.executable, str(root / "scripts" / "recall_ruler_score.py"), "--checkpoint", str(tmp_path / "run"), "--tokenizer", "bytes",
+                        "--out", str(tmp_path / "o"), "--run", "t", "--tasks", "vt", "--lengths", "1024", "--n-per-cell", "2", "--batch", "2", "--device", "cpu"],
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    values = json.loads((tmp_path / "o" / "t.values.json").read_text())
+    assert values["n_items"] == 2 and "ruler|vt|1024|recall" in values["cells"]
+    assert len((tmp_path / "o" / "t.items.jsonl").read_text().splitlines()) == 2
