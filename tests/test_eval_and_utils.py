@@ -395,3 +395,44 @@ def test_recall_ruler_items_and_scoring(tmp_path):
     values = json.loads((tmp_path / "o" / "t.values.json").read_text())
     assert values["n_items"] == 2 and "ruler|vt|1024|recall" in values["cells"]
     assert len((tmp_path / "o" / "t.items.jsonl").read_text().splitlines()) == 2
+
+
+def test_recall_based_protocol(tmp_path):
+    """Based suite: item files round-trip with their checksums, left truncation keeps the end, the generation is cut at the
+    first newline and before the end-of-document token, "contains" is a case-insensitive search; the scorer script runs."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from gdn_hybrid_architecture_ideas_b200 import config as C
+    from gdn_hybrid_architecture_ideas_b200.eval import recall_based as RB
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    items = {"swde": [RB.Item("swde", f"{i}", f"<page {i}> title: Film {i}\nyear: 19{i:02d}\nyear:", f"19{i:02d}") for i in range(5)],
+             "fda": [RB.Item("fda", "a", "Device name: Pump (X)\nDevice name:", "Pump (X)")]}
+    RB.write_set(tmp_path / "items", items)
+    assert RB.load_set(tmp_path / "items", "swde") == items["swde"]
+    (tmp_path / "items" / RB.MANIFEST_NAME).write_text(json.dumps({"swde": {"n": 5, "set_sha256": "0"}}))
+    try:
+        RB.load_set(tmp_path / "items", "swde")
+        raise AssertionError("a wrong checksum must be refused")
+    except ValueError:
+        pass
+    RB.write_set(tmp_path / "items", items)
+    assert RB.left_truncate(list(range(100)), 80) == (list(range(68, 100)), True) and RB.left_truncate([1, 2], 80) == ([1, 2], False)
+    assert RB.cut_at_stop(" 1999\nyear: 2000") == " 1999" and RB.cut_at_eos([5, 6, 0, 7], 0) == ([5, 6], 2) and RB.cut_at_eos([5], None) == ([5], -1)
+    assert RB.contains_score("the pump (x) model", "Pump (X)") == 1 and RB.contains_score("pump x", "Pump (X)") == 0
+    v = RB.values_json("r", {"swde": [{"id": "0", "hit": 1}, {"id": "1", "hit": 0}]}, exclude=["swde:1"])
+    assert v["cells"] == {"based|swde|all|acc": 1.0} and v["n_items"]["based|swde|all|acc"] == 1
+
+    root = Path(__file__).resolve().parent.parent
+    cfg = C.TrainConfig(model=C.tiny_control_config(), data=C.tiny_data_config(seq_len=64, batch_size=2), steps=1, seed=1)
+    cfg.model.vocab_size = 256
+    cfg.ckpt_every_steps, cfg.metrics_jsonl, cfg.log_every = 1, False, 0
+    Trainer(cfg, tmp_path / "run").fit()
+    r = subprocess.run([sys.executable, str(root / "scripts" / "recall_based_score.py"), "--checkpoint", str(tmp_path / "run"), "--items", str(tmp_path / "items"),
+                        "--tokenizer", "bytes", "--out", str(tmp_path / "o"), "--run", "t", "--batch", "3", "--device", "cpu"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    vals = json.loads((tmp_path / "o" / "t.values.json").read_text())
+    assert set(vals["cells"]) == {"based|swde|all|acc", "based|fda|all|acc"} and vals["n_items"]["based|swde|all|acc"] == 5
