@@ -436,3 +436,47 @@ def test_recall_based_protocol(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     vals = json.loads((tmp_path / "o" / "t.values.json").read_text())
     assert set(vals["cells"]) == {"based|swde|all|acc", "based|fda|all|acc"} and vals["n_items"]["based|swde|all|acc"] == 5
+
+
+def test_tst_diagnostics():
+    import math
+
+    import numpy as np
+    import torch
+
+    from gdn_hybrid_architecture_ideas_b200.eval import tst_diag as TD
+    from gdn_hybrid_architecture_ideas_b200.eval.tokenized import byte_tokenize
+
+    counts = np.array([30, 30, 0, 20, 10, 5, 3, 1, 1, 0])
+    classes, info = TD.frequency_classes(counts)
+    assert classes.tolist() == [0, 0, 3, 1, 2, 2, 3, 3, 3, 3]        # mass before: 0, .3 | .6 | .8, .9 | .95, .98, .99, 1, 1
+    assert info["classes"]["frequent"]["mass"] == 0.6 and info["zero_count_ids"] == 2 and TD.class_name_three(3) == "rare"
+    doc = torch.tensor([[4, 4, 4, 7, 7, 9], [1, 1, 1, 1, 1, 1]])
+    assert TD.context_in_document(doc).tolist() == [[0, 1, 2, 0, 1, 0], [0, 1, 2, 3, 4, 5]]
+    assert TD.bucket_of(torch.tensor([0, 127, 128, 511, 512, 5000]), TD.ROW_EDGES).tolist() == [0, 0, 1, 1, 2, 3]
+    tokens = torch.tensor([[0, 1, 3, 4, 6, 2], [1, 1, 0, 3, 5, 7]])
+    targets = torch.cat([tokens[:, 1:], tokens[:, :1]], 1)
+    scored = torch.tensor([[1, 1, 0, 1, 1, 0], [1, 1, 1, 1, 1, 0]], dtype=torch.bool)
+    ce = torch.rand(2, 6, dtype=torch.float64) + 0.5
+    agg = TD.aggregate_ce(ce, tokens, targets, doc, scored, torch.full((2, 6), 2), classes)
+    want = float((ce * scored).sum()) / (math.log(2) * 2 * int(scored.sum()))
+    for split in agg.values():
+        c = TD.contributions(split)
+        assert abs(c["contribution"].sum() - want) < 1e-12 and abs(c["set_bpb"] - want) < 1e-12 and c["tokens"].sum() == scored.sum()
+    a = {"embed.weight": torch.zeros(4, 2), "out_embed.weight": torch.zeros(4, 2), "embed_norm.weight": torch.zeros(2), "final_norm.weight": torch.zeros(2), "x": torch.ones(1)}
+    b = {k: v + 1 for k, v in a.items()}
+    g = TD.graft_state(a, b)
+    assert g["embed.weight"].eq(1).all() and g["embed_norm.weight"].eq(0).all() and g["x"] is a["x"]
+    assert TD.graft_state(a, b, norms=True)["final_norm.weight"].eq(1).all()
+    try:
+        TD.graft_state({"embed.weight": a["embed.weight"]}, b)
+        raise AssertionError("a tied head cannot be grafted")
+    except ValueError:
+        pass
+    w = torch.tensor([[0.0, 0.0, 0.0, 2.0], [1.0, 0.0, 0.0, 0.0], [1.0, 1.0, 1.0, 1.0]])
+    st = TD.conv_span_stats(w, {"q": (0, 1), "rest": (1, 3)})
+    assert st["q"]["pass_through"] == 1.0 and st["q"]["span90"] == 1.0 and st["q"]["centroid_lag"] == 0.0
+    assert st["rest"]["centroid_lag"] == (3 + 1.5) / 2 and st["rest"]["span90"] == 4.0 and st["all"]["channels"] == 3
+    assert abs(TD.bag_norm_eps_change(np.array([1.0]), 4, 1e-6)[0] - (math.sqrt((1 + 1e-6) / (1 + 0.25e-6)) - 1)) < 1e-15
+    d = byte_tokenize("aé")
+    assert d.ids == [97, 195, 169] and d.byte_lens == [1, 1, 1]
