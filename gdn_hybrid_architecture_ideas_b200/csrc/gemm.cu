@@ -14,6 +14,7 @@
 // (ced/train/wgrad_accum.py:100-145).
 #include "kernels.h"
 #include "sm100.cuh"
+#include <cstdlib>
 
 namespace ghb {
 using namespace sm100;
@@ -248,9 +249,12 @@ int gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long l
   if (bn == 256 && out == 0) {     // few 128 x 256 tiles and no split-K (bf16 output): narrower tiles fill more SMs
     const long t256 = static_cast<long>((M + BM - 1) / BM) * ((N + 255) / 256), t128 = static_cast<long>((M + BM - 1) / BM) * ((N + 127) / 128);
     auto waves = [&](long t) { return (t + sms - 1) / sms; };
-    // time ~ waves x tile width: take 128-wide tiles when they finish sooner
-    if (waves(t128) * 128 < waves(t256) * 256) bn = 128;
+    // time ~ waves x tile width, and a 128-wide tile runs at about 0.8 of the 256-wide tile's rate (measured: 970 against
+    // 1220 TFLOP/s at 65536 x 2816 x 1024): take the narrow tiles only when they save more than that in waves
+    if (waves(t128) * 128 * 10 < waves(t256) * 256 * 7) bn = 128;
   }
+  static const int forced_bn = [] { const char* e = getenv("GHB_GEMM_BN"); return e ? atoi(e) : 0; }();     // measurement knob
+  if (N > 128 && (forced_bn == 128 || forced_bn == 256)) bn = forced_bn;
   // A long reduction into few output tiles (weight gradients: K = tokens) leaves most SMs idle; slice the reduction so
   // that the units fill the machine. Only the fp32 outputs can be reduced into: out 1 is zeroed first, out 2 already
   // holds the running sum. Slices meet through floating-point reductions, so the summation order is not fixed.
