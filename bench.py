@@ -131,6 +131,7 @@ def run_ours(args) -> dict:
         cfg.tensor_parallel = world
         os.environ["GHB_TP_IMPL"] = args.tp_impl
     cfg.steps, cfg.seed, cfg.dtype, cfg.autocast, cfg.head_impl = 10 ** 6, 1, "float32", "bfloat16", "fused"
+    cfg.head_chunk = 4096      # positions per chunk of logits: fills the SMs in the head's input-gradient GEMM (2048: 64 tiles)
     cfg.optim.name, cfg.optim.warmup_steps = "adamw", 100
     cfg.metrics_jsonl, cfg.log_every, cfg.ckpt_every_steps, cfg.ckpt_every_minutes = False, 0, 0, 0.0
     cfg.optimizer_sharding = ("zero2" if world > 1 and not tp else "replicated") if args.sharding == "auto" else args.sharding

@@ -470,12 +470,28 @@ __global__ void __launch_bounds__(512) ce_grad_kernel(const float* __restrict__ 
   const long row = blockIdx.x;
   const float* lr = logits + row * V;
   float m = -INFINITY, sum = 0.f;
-  for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
-    float4 t = *reinterpret_cast<const float4*>(lr + i);
-    if (cache_row) *reinterpret_cast<float4*>(rowbuf + i) = t;
-    const float mm = fmaxf(fmaxf(t.x, t.y), fmaxf(t.z, t.w));
-    if (mm > m) { sum *= __expf(m - mm); m = mm; }
-    sum += __expf(t.x - m) + __expf(t.y - m) + __expf(t.z - m) + __expf(t.w - m);
+  // Batches of CE_UNROLL float4 per thread: every load of a batch is issued before any of it is used (the row is read
+  // once, so the pass is bound by loads in flight), then one max and one sum of exponentials over the registers.
+  constexpr int CE_UNROLL = 8;
+  for (int i0 = threadIdx.x * 4; i0 < V; i0 += blockDim.x * 4 * CE_UNROLL) {
+    float4 t[CE_UNROLL];
+#pragma unroll
+    for (int u = 0; u < CE_UNROLL; ++u) {
+      const int i = i0 + u * blockDim.x * 4;
+      t[u] = i < V ? *reinterpret_cast<const float4*>(lr + i) : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+    }
+    float mm = m;
+#pragma unroll
+    for (int u = 0; u < CE_UNROLL; ++u) {
+      const int i = i0 + u * blockDim.x * 4;
+      if (cache_row && i < V) *reinterpret_cast<float4*>(rowbuf + i) = t[u];
+      mm = fmaxf(mm, fmaxf(fmaxf(t[u].x, t[u].y), fmaxf(t[u].z, t[u].w)));
+    }
+    if (mm > m) { sum *= __expf(m - mm); m = mm; }       // m == -inf: sum is 0 and exp(-inf) = 0
+    if (m > -INFINITY) {
+#pragma unroll
+      for (int u = 0; u < CE_UNROLL; ++u) sum += __expf(t[u].x - m) + __expf(t[u].y - m) + __expf(t[u].z - m) + __expf(t[u].w - m);
+    }
   }
   const float wm = wmax(m);
   sum = (m == -INFINITY) ? 0.f : sum * __expf(m - wm);      // lanes past the row's end (V < 4 x threads) hold no terms

@@ -216,8 +216,8 @@ def bench_lm_head(a):
     t = torch.randint(0, V, (rows, 1), device="cuda")
     w = torch.full((rows, 1), 1.0 / rows, device="cuda")
     b = torch.zeros(rows, device="cuda")
-    ms = timed(lambda: native.fused_linear_ce(h, W, t, w, b, 2048)[0].backward(), a.iters, a.warmup)
-    return {"op": "lm_head", "rows": rows, "d": d, "vocab": V, "fwd_bwd_ms": ms, "tflops": 6.0 * rows * d * V / ms / 1e9}
+    ms = timed(lambda: native.fused_linear_ce(h, W, t, w, b, a.chunk)[0].backward(), a.iters, a.warmup)
+    return {"op": "lm_head", "rows": rows, "d": d, "vocab": V, "chunk": a.chunk, "fwd_bwd_ms": ms, "tflops": 6.0 * rows * d * V / ms / 1e9}
 
 
 def bench_adamw(a):
@@ -254,6 +254,7 @@ def main():
     p.add_argument("--sources", type=int, default=4)
     p.add_argument("--ffn", type=int, default=2816)
     p.add_argument("--vocab", type=int, default=32768)
+    p.add_argument("--chunk", type=int, default=2048, help="lm_head: positions per chunk of logits")
     p.add_argument("--numel", type=int, default=1 << 28)
     p.add_argument("--layout", choices=["nt", "nn", "tn"], default="nt")
     p.add_argument("--iters", type=int, default=5)
