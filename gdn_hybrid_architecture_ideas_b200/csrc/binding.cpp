@@ -138,6 +138,33 @@ void depth_mix_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& dsrc, co
                            du.data_ptr<float>(), dh.numel() / d, d, sm_count(), stream()), "depth_mix_bwd");
 }
 
+// Q readers over the same n sources: ueff [Q, d]; outs: Q tensors like a source; alpha, vu [rows, Q, n]; rnorm [rows, n].
+void depth_mix_multi_fwd(const std::vector<Tensor>& src, const Tensor& ueff, std::vector<Tensor>& outs, Tensor& alpha, Tensor& rnorm, Tensor& vu, double eps) {
+  const c10::cuda::CUDAGuard guard(ueff.device());
+  const int d = ueff.size(-1);
+  std::vector<const float*> p; std::vector<float*> o;
+  for (auto& s : src) { TORCH_CHECK(is_f32(s) && s.is_contiguous() && s.numel() == src[0].numel(), "depth_mix_multi_fwd: fp32 contiguous sources"); p.push_back(s.data_ptr<float>()); }
+  for (auto& t : outs) { TORCH_CHECK(is_f32(t) && t.is_contiguous() && t.numel() == src[0].numel(), "depth_mix_multi_fwd: fp32 outputs"); o.push_back(t.data_ptr<float>()); }
+  TORCH_CHECK(is_f32(ueff) && ueff.is_contiguous() && ueff.size(0) == static_cast<long>(outs.size()) && is_f32(alpha) && is_f32(rnorm) && is_f32(vu), "depth_mix_multi_fwd: layout");
+  check(ghb::depth_mix_multi_fwd(p.data(), p.size(), o.data(), o.size(), ueff.data_ptr<float>(), alpha.data_ptr<float>(), rnorm.data_ptr<float>(),
+                                 vu.data_ptr<float>(), src[0].numel() / d, d, eps, stream()), "depth_mix_multi_fwd");
+}
+void depth_mix_multi_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& dsrc, const Tensor& ueff, const std::vector<c10::optional<Tensor>>& dhs,
+                         const Tensor& alpha, const Tensor& rnorm, const Tensor& vu, Tensor& du) {
+  const c10::cuda::CUDAGuard guard(ueff.device());
+  const int d = ueff.size(-1);
+  std::vector<const float*> p, g; std::vector<float*> q;
+  for (auto& s : src) p.push_back(s.data_ptr<float>());
+  for (auto& s : dsrc) { TORCH_CHECK(is_f32(s) && s.is_contiguous() && s.numel() == src[0].numel(), "depth_mix_multi_bwd: fp32 outputs"); q.push_back(s.data_ptr<float>()); }
+  for (auto& t : dhs) {
+    if (t.has_value()) { TORCH_CHECK(is_f32(*t) && t->is_contiguous() && t->numel() == src[0].numel(), "depth_mix_multi_bwd: fp32 gradients"); g.push_back(t->data_ptr<float>()); }
+    else g.push_back(nullptr);
+  }
+  TORCH_CHECK(ueff.size(0) == static_cast<long>(g.size()) && is_f32(du) && du.is_contiguous() && du.numel() == ueff.numel() && p.size() == q.size(), "depth_mix_multi_bwd: layout");
+  check(ghb::depth_mix_multi_bwd(p.data(), q.data(), p.size(), g.data(), g.size(), ueff.data_ptr<float>(), alpha.data_ptr<float>(), rnorm.data_ptr<float>(),
+                                 vu.data_ptr<float>(), du.data_ptr<float>(), src[0].numel() / d, d, sm_count(), stream()), "depth_mix_multi_bwd");
+}
+
 void ce_grad(const Tensor& logits, const Tensor& targets, const Tensor& a, const Tensor& b, Tensor& grad, Tensor& ce, Tensor& lse) {
   const c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(is_f32(logits) && logits.is_contiguous() && is_bf16(grad) && grad.is_contiguous() && targets.scalar_type() == torch::kInt64 &&
@@ -406,6 +433,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("dual_lerp_bwd", &dual_lerp_bwd);
   m.def("depth_mix_fwd", &depth_mix_fwd);
   m.def("depth_mix_bwd", &depth_mix_bwd);
+  m.def("depth_mix_multi_fwd", &depth_mix_multi_fwd);
+  m.def("depth_mix_multi_bwd", &depth_mix_multi_bwd);
   m.def("ce_grad", &ce_grad);
   m.def("decode_attention", &decode_attention);
   m.def("comm_reduce", &comm_reduce);

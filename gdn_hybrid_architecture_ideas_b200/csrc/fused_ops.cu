@@ -458,6 +458,224 @@ int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const floa
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// ---- several readers over the same sources in one pass. The block-entry mix and the write / query mixes of a block's GDN
+// layers all read the same finished blocks with different pseudo-queries: the sources are read once for all Q readers,
+// and in the backward the Q gradients meet in one write of every source's gradient (instead of Q kernels and Q - 1
+// accumulation passes over (rows, d) tensors). Same arithmetic per reader as the single-reader kernels above.
+constexpr int MIXQ_MAX = 8;
+struct MultiPtrs { const float* src[MIX_MAX]; float* dsrc[MIX_MAX]; float* out[MIXQ_MAX]; const float* dh[MIXQ_MAX]; };
+
+template <int VPT>
+__global__ void __launch_bounds__(128) depth_mix_multi_fwd_kernel(MultiPtrs p, int n, int Q, const float* __restrict__ ueff, float* __restrict__ alpha,
+                                                                  float* __restrict__ rnorm, float* __restrict__ vu, int d, float eps) {
+  __shared__ float part[4][MIX_MAX * (MIXQ_MAX + 1)];
+  __shared__ float sal[MIXQ_MAX][MIX_MAX];
+  const long row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float4 v[MIX_MAX][VPT];
+#pragma unroll
+  for (int i = 0; i < MIX_MAX; ++i) {
+    if (i < n) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        v[i][k] = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
+        ss += v[i][k].x * v[i][k].x + v[i][k].y * v[i][k].y + v[i][k].z * v[i][k].z + v[i][k].w * v[i][k].w;
+      }
+      ss = wsum(ss);
+      if (lane == 0) part[warp][i] = ss;
+    }
+  }
+  for (int q = 0; q < Q; ++q) {
+    float4 uq[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) uq[k] = reinterpret_cast<const float4*>(ueff + static_cast<long>(q) * d)[k * 128 + threadIdx.x];
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i) {
+      if (i < n) {
+        float dot = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) dot += v[i][k].x * uq[k].x + v[i][k].y * uq[k].y + v[i][k].z * uq[k].z + v[i][k].w * uq[k].w;
+        dot = wsum(dot);
+        if (lane == 0) part[warp][n + q * n + i] = dot;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < Q * n) {
+    const int q = threadIdx.x / n, i = threadIdx.x % n;
+    const float ss = part[0][i] + part[1][i] + part[2][i] + part[3][i];
+    const int c = n + threadIdx.x;
+    const float dot = part[0][c] + part[1][c] + part[2][c] + part[3][c];
+    const float r = rsqrtf(ss / d + eps);
+    sal[q][i] = dot * r;
+    vu[(row * Q + q) * n + i] = dot;
+    if (q == 0) rnorm[row * n + i] = r;
+  }
+  __syncthreads();
+  if (threadIdx.x < Q) {
+    const int q = threadIdx.x;
+    float mx = -INFINITY, den = 0.f;
+    for (int i = 0; i < n; ++i) mx = fmaxf(mx, sal[q][i]);
+    for (int i = 0; i < n; ++i) { const float e = __expf(sal[q][i] - mx); sal[q][i] = e; den += e; }
+    for (int i = 0; i < n; ++i) { const float a = sal[q][i] / den; sal[q][i] = a; alpha[(row * Q + q) * n + i] = a; }
+  }
+  __syncthreads();
+  for (int q = 0; q < Q; ++q) {
+    float4 acc[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i) {
+      if (i < n) {
+        const float a = sal[q][i];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) { acc[k].x += a * v[i][k].x; acc[k].y += a * v[i][k].y; acc[k].z += a * v[i][k].z; acc[k].w += a * v[i][k].w; }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) reinterpret_cast<float4*>(p.out[q] + row * d)[k * 128 + threadIdx.x] = acc[k];
+  }
+}
+
+// Rows in a grid-stride loop. Per row: the Q products dh_q . v_i (one pass over the readers' gradients), then every
+// source's gradient summed over the readers (a second pass over the gradients, which the first left in cache). The
+// pseudo-query gradients accumulate per CTA in shared memory (a thread owns its columns), then one atomic per entry.
+template <int VPT>
+__global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, int n, int Q, const float* __restrict__ ueff, const float* __restrict__ alpha,
+                                                                  const float* __restrict__ rnorm, const float* __restrict__ vu, float* __restrict__ du,
+                                                                  long rows, int d) {
+  extern __shared__ float sdu[];                       // [Q][d]
+  __shared__ float part[4][MIX_MAX * MIXQ_MAX];
+  __shared__ float sda[MIXQ_MAX][MIX_MAX], sal[MIXQ_MAX][MIX_MAX], sc1[MIXQ_MAX][MIX_MAX], sc2[MIXQ_MAX][MIX_MAX];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < Q * d; i += 128) sdu[i] = 0.f;
+  __syncthreads();
+  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+    float4 v[MIX_MAX][VPT];
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i)
+      if (i < n) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) v[i][k] = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
+      }
+    for (int q = 0; q < Q; ++q) {
+      if (p.dh[q] == nullptr) continue;
+      float4 g[VPT];
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * 128 + threadIdx.x];
+#pragma unroll
+      for (int i = 0; i < MIX_MAX; ++i) {
+        if (i < n) {
+          float a = 0.f;
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) a += g[k].x * v[i][k].x + g[k].y * v[i][k].y + g[k].z * v[i][k].z + g[k].w * v[i][k].w;
+          a = wsum(a);
+          if (lane == 0) part[warp][q * n + i] = a;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < Q * n) {
+      const int q = threadIdx.x / n, i = threadIdx.x % n, c = threadIdx.x;
+      sda[q][i] = p.dh[q] ? part[0][c] + part[1][c] + part[2][c] + part[3][c] : 0.f;
+      sal[q][i] = alpha[(row * Q + q) * n + i];
+    }
+    __syncthreads();
+    if (threadIdx.x < Q * n) {
+      const int q = threadIdx.x / n, i = threadIdx.x % n;
+      float mean = 0.f;
+      for (int j = 0; j < n; ++j) mean += sal[q][j] * sda[q][j];
+      const float r = rnorm[row * n + i];
+      const float dl = sal[q][i] * (sda[q][i] - mean);
+      sc1[q][i] = dl * r;
+      sc2[q][i] = dl * vu[(row * Q + q) * n + i] * r * r * r / d;
+    }
+    __syncthreads();
+    float4 acc[MIX_MAX][VPT];
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i)
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) acc[i][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int q = 0; q < Q; ++q) {
+      if (p.dh[q] == nullptr) continue;
+      float4 g[VPT], uq[VPT], dq[VPT];
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * 128 + threadIdx.x];
+        uq[k] = reinterpret_cast<const float4*>(ueff + static_cast<long>(q) * d)[k * 128 + threadIdx.x];
+        dq[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < MIX_MAX; ++i) {
+        if (i < n) {
+          const float al = sal[q][i], c1 = sc1[q][i], c2 = sc2[q][i];
+#pragma unroll
+          for (int k = 0; k < VPT; ++k) {
+            acc[i][k].x += al * g[k].x + c1 * uq[k].x - c2 * v[i][k].x; acc[i][k].y += al * g[k].y + c1 * uq[k].y - c2 * v[i][k].y;
+            acc[i][k].z += al * g[k].z + c1 * uq[k].z - c2 * v[i][k].z; acc[i][k].w += al * g[k].w + c1 * uq[k].w - c2 * v[i][k].w;
+            dq[k].x += c1 * v[i][k].x; dq[k].y += c1 * v[i][k].y; dq[k].z += c1 * v[i][k].z; dq[k].w += c1 * v[i][k].w;
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < VPT; ++k) {
+        float4* slot = reinterpret_cast<float4*>(sdu + static_cast<long>(q) * d) + k * 128 + threadIdx.x;
+        float4 t = *slot;
+        t.x += dq[k].x; t.y += dq[k].y; t.z += dq[k].z; t.w += dq[k].w;
+        *slot = t;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < MIX_MAX; ++i)
+      if (i < n) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) reinterpret_cast<float4*>(p.dsrc[i] + row * d)[k * 128 + threadIdx.x] = acc[i][k];
+      }
+    __syncthreads();          // the shared per-row scalars are rewritten by the next row
+  }
+  for (int i = threadIdx.x; i < Q * d; i += 128) atomicAdd(du + i, sdu[i]);
+}
+
+int depth_mix_multi_fwd(const float* const* src, int n, float* const* out, int Q, const float* ueff, float* alpha, float* rnorm, float* vu, long rows,
+                        int d, float eps, cudaStream_t st) {
+  if (n < 1 || n > MIX_MAX || Q < 1 || Q > MIXQ_MAX || d % 512 || d > 2048) return 1;
+  MultiPtrs p{};
+  for (int i = 0; i < n; ++i) p.src[i] = src[i];
+  for (int q = 0; q < Q; ++q) p.out[q] = out[q];
+  const unsigned grid = static_cast<unsigned>(rows);
+  switch (d / 512) {
+    case 1: depth_mix_multi_fwd_kernel<1><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps); break;
+    case 2: depth_mix_multi_fwd_kernel<2><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps); break;
+    case 4: depth_mix_multi_fwd_kernel<4><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps); break;
+    default: return 1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, const float* const* dh, int Q, const float* ueff, const float* alpha,
+                        const float* rnorm, const float* vu, float* du, long rows, int d, int sms, cudaStream_t st) {
+  if (n < 1 || n > MIX_MAX || Q < 1 || Q > MIXQ_MAX || d % 512 || d > 2048) return 1;
+  MultiPtrs p{};
+  for (int i = 0; i < n; ++i) { p.src[i] = src[i]; p.dsrc[i] = dsrc[i]; }
+  for (int q = 0; q < Q; ++q) p.dh[q] = dh[q];
+  const size_t smem = static_cast<size_t>(Q) * d * 4;
+  const unsigned grid = static_cast<unsigned>(rows < sms * 4L ? rows : sms * 4L);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 512 * 4);
+    cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 1024 * 4);
+    cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 2048 * 4);
+    attr = true;
+  }
+  switch (d / 512) {
+    case 1: depth_mix_multi_bwd_kernel<1><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d); break;
+    case 2: depth_mix_multi_bwd_kernel<2><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d); break;
+    case 4: depth_mix_multi_bwd_kernel<4><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d); break;
+    default: return 1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 // ================================================================================================ CE gradient
 // One CTA per row of fp32 logits (n, V). Pass 1: online max / sum over the row (kept in shared memory when it fits),
 // pass 2: grad = softmax * (asum + 2 b lse) written as bf16 in a separate (n, V) buffer, then the s targets subtract

@@ -33,6 +33,10 @@ int cast_bf16(const float* x, void* y, long n, int sms, cudaStream_t st);
 int gdn_prep_fwd(const void* u, const int* doc, const float* w, void* out, long rows, int L, int C, int nq, float qscale, cudaStream_t st);
 int gdn_prep_bwd(const void* u, const int* doc, const float* w, const void* dout, void* du, float* dw, long rows, int L, int C,
                  int nq, float qscale, cudaStream_t st);
+int depth_mix_multi_fwd(const float* const* src, int n, float* const* out, int Q, const float* ueff, float* alpha, float* rnorm, float* vu, long rows,
+                        int d, float eps, cudaStream_t st);
+int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, const float* const* dh, int Q, const float* ueff, const float* alpha,
+                        const float* rnorm, const float* vu, float* du, long rows, int d, int sms, cudaStream_t st);
 int depth_mix_fwd(const float* const* src, int n, const float* ueff, float* out, float* alpha, float* rnorm, long rows, int d, float eps,
                   cudaStream_t st);
 int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const float* ueff, const float* dh, const float* alpha,

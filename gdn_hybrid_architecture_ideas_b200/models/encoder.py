@@ -130,8 +130,10 @@ class EncoderLayer(nn.Module):
         self.canon = CanonLayer(d, cfg.encoder.canon_kernel) if kind == "attention" and cfg.encoder.canon_kernel else None
 
     def forward(self, x: torch.Tensor, ctx: SeqContext, cache=None, sources: list | None = None, need_state: bool = True,
-                scalars: tuple | None = None):
-        """scalars: (x0, a - 1, b) of this layer's residual scalars, applied as the last term of the layer's own sum."""
+                scalars: tuple | None = None, premixed: tuple | None = None):
+        """scalars: (x0, a - 1, b) of this layer's residual scalars, applied as the last term of the layer's own sum.
+        premixed: (write mix, query mix) of this layer over `sources`, already formed by the stack (one kernel for all the
+        readers of a block); an entry that is None is formed here."""
         h = self.mixer_in_norm(x)
         if self.canon is not None:
             if cache is not None and cache.canon_input is None:
@@ -142,10 +144,13 @@ class EncoderLayer(nn.Module):
         if arms is not None:
             if sources is None:
                 raise ValueError("a GDN layer with write/query mixes is called with the finished blocks (sources)")
-            x_write = self.mixer_in_norm(arms.write_query(sources) if arms.write_query is not None else sources[0])
+            pre_w, pre_q = premixed if premixed is not None else (None, None)
+            if pre_w is None:
+                pre_w = arms.write_query(sources) if arms.write_query is not None else sources[0]
+            x_write = self.mixer_in_norm(pre_w)
             x_read = None
             if arms.variant in READ_MIX_VARIANTS:
-                x_read = x_write if arms.qmix_query is None else self.mixer_in_norm(arms.qmix_query(sources))
+                x_read = x_write if arms.qmix_query is None else self.mixer_in_norm(pre_q if pre_q is not None else arms.qmix_query(sources))
             mixed, new_cache = self.mixer(h, ctx, cache, arms=arms, x_write=x_write, x_read=x_read, need_state=need_state)
         elif self.kind == "gdn":
             mixed, new_cache = self.mixer(h, ctx, cache, need_state=need_state)
@@ -237,7 +242,7 @@ class Encoder(nn.Module):
         if self.scalar_form == "skip_x0_span":
             self.skip_gain.clamp_(-SPAN_CLAMP, SPAN_CLAMP)
 
-    def _run(self, layer, x, ctx, cache, sources, need_state, scalars=None):
+    def _run(self, layer, x, ctx, cache, sources, need_state, scalars=None, premixed=None):
         """One layer call under the stack's activation memory mode (models/act_checkpoint.py)."""
         mode = self.activation_checkpoint
         training = cache is None and torch.is_grad_enabled() and x.requires_grad
@@ -245,6 +250,13 @@ class Encoder(nn.Module):
             if mode != "none" and training:
                 raise ValueError("model.encoder.layer_scalars runs with activation_checkpoint 'none'")
             return layer(x, ctx, cache, sources, need_state, scalars)
+        if premixed is not None:
+            if mode in ("host", "host_overlap") and training:
+                if self.host_pool is None or self.host_pool.device != x.device:
+                    self.host_pool = act_checkpoint.HostPool(x.device, overlap=mode == "host_overlap")
+                with self.host_pool.offload():
+                    return layer(x, ctx, cache, sources, need_state, None, premixed)
+            return layer(x, ctx, cache, sources, need_state, None, premixed)
         if mode == "layer" and training:
             def call(x_, *src):
                 return layer(x_, ctx, None, list(src) if src else None, False)[0]
@@ -268,6 +280,33 @@ class Encoder(nn.Module):
             return x_
         return act_checkpoint.run_checkpointed(call, x, *sources)
 
+    def _block_mixes(self, b: int, sources: list) -> dict:
+        """Every depth mix block b takes over the finished blocks, formed together: the block's entry ("entry") and each GDN
+        layer's write ((i, "w")) and query ((i, "q")) mix. They read the same sources with different pseudo-queries, so on
+        CUDA one kernel reads each source once for all of them and one backward kernel writes each source's gradient once
+        (ops.depth_mix_multi). Empty when there is nothing to share."""
+        if len(sources) < 2 or not ops.use_native(sources[0]):
+            return {}
+        S = self.block
+        keys, readers = [], []
+        if b > 0:
+            keys.append("entry")
+            readers.append(self.layers[b * S].attn_res.entry)
+        for i in range(b * S, (b + 1) * S):
+            arms = getattr(self.layers[i], "gdn_arms", None)
+            if arms is None:
+                continue
+            if arms.write_query is not None:
+                keys.append((i, "w"))
+                readers.append(arms.write_query)
+            if arms.variant in READ_MIX_VARIANTS and arms.qmix_query is not None:
+                keys.append((i, "q"))
+                readers.append(arms.qmix_query)
+        if len(readers) < 2 or len(readers) > 8:
+            return {}
+        outs = ops.depth_mix_multi(sources, [(r.query, r.key_norm.weight) for r in readers], readers[0].key_norm.eps)
+        return dict(zip(keys, outs))
+
     def forward(self, x: torch.Tensor, ctx: SeqContext, caches: list | None = None, need_state: bool = True):
         """x: embedding-stage output (B, L, d). Returns (stream entering final_norm, per-layer caches)."""
         new_caches = []
@@ -281,9 +320,11 @@ class Encoder(nn.Module):
             return x, new_caches
         sources = [x]
         S = self.block
+        recompute = self.activation_checkpoint in ("layer", "block") and caches is None and torch.is_grad_enabled() and x.requires_grad
         for b in range(len(self.layers) // S):
             first = self.layers[b * S]
-            start = x if b == 0 else first.attn_res.entry(sources)
+            mixes = {} if recompute else self._block_mixes(b, sources)
+            start = x if b == 0 else (mixes["entry"] if "entry" in mixes else first.attn_res.entry(sources))
             if b > 0 and first.stream_bf16:
                 start = round_stream(start)
             x = start
@@ -295,7 +336,8 @@ class Encoder(nn.Module):
             for i in range(b * S, (b + 1) * S):
                 layer = self.layers[i]
                 src = sources if getattr(layer, "gdn_arms", None) is not None else None
-                x, c = self._run(layer, x, ctx, get(i), src, need_state, scal(i))
+                pre = (mixes.get((i, "w")), mixes.get((i, "q"))) if (src is not None and mixes) else None
+                x, c = self._run(layer, x, ctx, get(i), src, need_state, scal(i), pre)
                 new_caches.append(c)
             sources = sources + [x - start]
         return self.layers[-1].attn_res.out(sources), new_caches

@@ -177,6 +177,13 @@ def depth_mix(sources, query, gain, eps):
     return ref.depth_mix(sources, query, gain, eps)
 
 
+def depth_mix_multi(sources, readers, eps):
+    """Several depth-mix readers [(query, key-norm gain)] over the same sources: a list of mixes, one per reader."""
+    if use_native(sources[0]) and len(sources) > 1:
+        return _native().depth_mix_multi(sources, readers, eps)
+    return [depth_mix(sources, q, g, eps) for q, g in readers]
+
+
 def embedding(tokens, weight):
     return ref.embedding(tokens, weight)
 

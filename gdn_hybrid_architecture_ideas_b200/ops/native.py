@@ -444,6 +444,49 @@ def depth_mix(sources, query, gain, eps):
     return _DepthMix.apply(query, gain, eps, *sources)
 
 
+class _DepthMixMulti(torch.autograd.Function):
+    """Q readers over the same n sources in one pass: args = n sources, Q queries, Q key-norm gains; returns Q mixes."""
+
+    @staticmethod
+    def forward(ctx, eps, n, *args):
+        Q = (len(args) - n) // 2
+        srcs = [s.contiguous() for s in args[:n]]
+        queries, gains = args[n:n + Q], args[n + Q:]
+        ueff = torch.stack([q.float() * (1.0 + g.float()) for q, g in zip(queries, gains)]).contiguous()
+        outs = [torch.empty_like(srcs[0]) for _ in range(Q)]
+        rows = srcs[0].numel() // srcs[0].shape[-1]
+        alpha = torch.empty(rows, Q, n, dtype=torch.float32, device=ueff.device)
+        vu = torch.empty_like(alpha)
+        rnorm = torch.empty(rows, n, dtype=torch.float32, device=ueff.device)
+        ext().depth_mix_multi_fwd(srcs, ueff, outs, alpha, rnorm, vu, eps)
+        _count()
+        ctx.save_for_backward(ueff, alpha, rnorm, vu, *srcs, *queries, *gains)
+        ctx.n, ctx.Q = n, Q
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *dhs):
+        n, Q = ctx.n, ctx.Q
+        ueff, alpha, rnorm, vu, *rest = ctx.saved_tensors
+        srcs, queries, gains = rest[:n], rest[n:n + Q], rest[n + Q:]
+        dsrc = [torch.empty_like(s) for s in srcs]
+        du = torch.zeros_like(ueff)
+        ext().depth_mix_multi_bwd(list(srcs), dsrc, ueff, [None if g is None else g.contiguous().float() for g in dhs], alpha, rnorm, vu, du)
+        _count()
+        dq = [(du[i] * (1.0 + gains[i].float())).to(queries[i].dtype) for i in range(Q)]
+        dg = [(du[i] * queries[i].float()).to(gains[i].dtype) if gains[i].numel() == du[i].numel() else (du[i] * queries[i].float()).sum().reshape(gains[i].shape).to(gains[i].dtype)
+              for i in range(Q)]
+        return (None, None, *dsrc, *dq, *dg)
+
+
+def depth_mix_multi(sources, readers, eps):
+    """readers: [(query, gain)]. One kernel for all of them when the shapes fit, else one mix per reader."""
+    d = sources[0].shape[-1]
+    if len(sources) > 8 or len(readers) > 8 or d % 512 or d > 2048 or any(s.dtype != torch.float32 for s in sources):
+        return [depth_mix(sources, q, g, eps) for q, g in readers]
+    return list(_DepthMixMulti.apply(eps, len(sources), *sources, *[q for q, _ in readers], *[g for _, g in readers]))
+
+
 # ------------------------------------------------------------------------------------------------------------ fused head + CE
 
 class _FusedLinearCE(torch.autograd.Function):

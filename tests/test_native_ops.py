@@ -471,3 +471,35 @@ def test_attention_layer_fused_prep(gate, cap, frac, docs):
     for (n, p), q in zip(layer.named_parameters(), oracle.parameters()):
         assert p.grad is not None, n
         _close(p.grad, q.grad, 4e-2 * q.grad.abs().max().item() + 1e-3, 3e-2, f"d{n}")
+
+
+@pytest.mark.parametrize("n,Q,d", [(2, 7, 1024), (4, 3, 1024), (3, 2, 512), (5, 8, 2048)])
+def test_depth_mix_multi(n, Q, d):
+    """Q readers over the same sources in one kernel against the PyTorch statement of each reader; one output is left
+    without a gradient (a reader whose mix is not used downstream)."""
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    torch.manual_seed(n * 10 + Q)
+    rows = (3, 70)
+    srcs = [(torch.randn(*rows, d, device=_dev()) * (1 + i)).requires_grad_() for i in range(n)]
+    qs = [(torch.randn(d, device=_dev()) * 0.1).requires_grad_() for _ in range(Q)]
+    gs = [(torch.randn(d, device=_dev()) * 0.1).requires_grad_() for _ in range(Q)]
+    outs = native.depth_mix_multi(srcs, list(zip(qs, gs)), 1e-6)
+    native.check_status()
+    rs = [s.detach().clone().requires_grad_() for s in srcs]
+    rq = [q.detach().clone().requires_grad_() for q in qs]
+    rg = [g.detach().clone().requires_grad_() for g in gs]
+    want = [ref.depth_mix(rs, q, g, 1e-6) for q, g in zip(rq, rg)]
+    for a, b in zip(outs, want):
+        _close(a, b, 1e-4, 1e-4, "mix")
+    go = [torch.randn_like(o) for o in outs]
+    used = range(Q - 1)           # the last reader's output gets no gradient
+    torch.autograd.backward([outs[i] for i in used], [go[i] for i in used])
+    torch.autograd.backward([want[i] for i in used], [go[i] for i in used])
+    native.check_status()
+    for a, b in zip(srcs, rs):
+        _close(a.grad, b.grad, 2e-4 * b.grad.abs().max().item(), 1e-3, "dsrc")
+    for i in used:
+        _close(qs[i].grad, rq[i].grad, 2e-3 * rq[i].grad.abs().max().item(), 2e-3, "dquery")
+        _close(gs[i].grad, rg[i].grad, 2e-3 * rg[i].grad.abs().max().item() + 1e-6, 2e-3, "dgain")
+    assert qs[Q - 1].grad is None or float(qs[Q - 1].grad.abs().max()) == 0.0
