@@ -134,7 +134,8 @@ class EncoderLayer(nn.Module):
         """scalars: (x0, a - 1, b) of this layer's residual scalars, applied as the last term of the layer's own sum.
         premixed: (write mix, query mix) of this layer over `sources`, already formed by the stack (one kernel for all the
         readers of a block); an entry that is None is formed here."""
-        h = self.mixer_in_norm(x)
+        x_in = x
+        h, x = ops.prenorm(x, self.mixer_in_norm.weight, self.mixer_in_norm.eps)      # x: the stream, now read by the residual add only
         if self.canon is not None:
             if cache is not None and cache.canon_input is None:
                 raise ValueError("this cache was written without a Canon layer: it cannot be continued with one")
@@ -159,11 +160,12 @@ class EncoderLayer(nn.Module):
         y = ops.norm_add(x, mixed, self.mixer_out_norm.weight, self.mixer_out_norm.eps, self.residual_scale)
         if self.stream_bf16:
             y = round_stream(y)
-        y = ops.norm_add(y, self.mlp(self.mlp_in_norm(y)), self.mlp_out_norm.weight, self.mlp_out_norm.eps, self.residual_scale)
+        h2, y = ops.prenorm(y, self.mlp_in_norm.weight, self.mlp_in_norm.eps)
+        y = ops.norm_add(y, self.mlp(h2), self.mlp_out_norm.weight, self.mlp_out_norm.eps, self.residual_scale)
         if self.stream_bf16:
             y = round_stream(y)
         if scalars is not None:
-            y = apply_layer_scalars(y, x, *scalars)
+            y = apply_layer_scalars(y, x_in, *scalars)
         if self.canon is not None:
             new_cache.canon_input, new_cache.canon_doc = canon_input, canon_doc
         return y, new_cache

@@ -43,6 +43,15 @@ def rmsnorm(x, weight, eps, out_dtype=None):
     return ref.rmsnorm(x, weight, eps, out_dtype)
 
 
+def prenorm(x, weight, eps):
+    """(RMSNorm(x), x): the branch input and the stream for the residual add. On CUDA one autograd node, so the stream's
+    two gradients are summed inside the norm's backward kernel."""
+    if use_native(x) and x.dtype == torch.float32 and weight.dtype == torch.float32 and x.shape[-1] % 4 == 0 and x.shape[-1] <= 2048 \
+            and torch.is_grad_enabled() and x.requires_grad:
+        return _native().prenorm(x, weight, eps)
+    return rmsnorm(x, weight, eps), x
+
+
 def gated_rmsnorm(x, z, weight, eps, gate, out_dtype=None):
     if use_native(x):
         return _native().gated_rmsnorm(x, z, weight, eps, gate, out_dtype)

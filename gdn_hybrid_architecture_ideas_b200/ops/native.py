@@ -272,6 +272,41 @@ class _RMSNorm(torch.autograd.Function):
         return dx, dw, None, None, dz, None, (dy if ctx.has_resid else None), None
 
 
+class _PreNorm(torch.autograd.Function):
+    """(RMSNorm(x), x): the normed branch input and the stream passed through. The stream has two readers in a Peri-LN
+    layer (the branch's norm and the residual add); as one node their two gradients meet inside the norm's backward kernel
+    (dx = norm backward + the pass-through gradient) instead of in a separate accumulation pass over the stream."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps, out_dtype):
+        xc = x.contiguous()
+        y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        rstd = torch.empty(x.numel() // x.shape[-1], dtype=torch.float32, device=x.device)
+        ext().rmsnorm_fwd(xc, weight, None, 0, None, y, rstd, eps, 1.0)
+        _count()
+        ctx.save_for_backward(xc, weight, rstd)
+        return y, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dpass):
+        xc, weight, rstd = ctx.saved_tensors
+        if dy is None:
+            return dpass, None, None, None
+        dy = dy.contiguous()
+        if dy.dtype not in (BF16, torch.float32):
+            dy = dy.float()
+        dx = torch.empty_like(xc)
+        dw = torch.zeros_like(weight)
+        ext().rmsnorm_bwd(dy, xc, weight, None, 0, rstd, None if dpass is None else dpass.contiguous().float(), dx, None, dw, 1.0)
+        _count()
+        return dx, dw, None, None
+
+
+def prenorm(x, weight, eps):
+    """(RMSNorm(x) in bf16, x passed through) as one autograd node; x float32."""
+    return _PreNorm.apply(x, weight, eps, BF16)
+
+
 def _norm_ok(x, weight) -> bool:
     return x.dtype in (BF16, torch.float32) and weight.dtype == torch.float32 and x.shape[-1] % 4 == 0 and x.shape[-1] <= 2048
 

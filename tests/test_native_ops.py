@@ -503,3 +503,28 @@ def test_depth_mix_multi(n, Q, d):
         _close(qs[i].grad, rq[i].grad, 2e-3 * rq[i].grad.abs().max().item(), 2e-3, "dquery")
         _close(gs[i].grad, rg[i].grad, 2e-3 * rg[i].grad.abs().max().item() + 1e-6, 2e-3, "dgain")
     assert qs[Q - 1].grad is None or float(qs[Q - 1].grad.abs().max()) == 0.0
+
+
+def test_prenorm_passthrough():
+    """(RMSNorm(x), x) as one node: the two gradients of x are summed inside the norm's backward kernel."""
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    torch.manual_seed(5)
+    x = torch.randn(4, 300, 1024, device=_dev()).requires_grad_()
+    w = (torch.randn(1024, device=_dev()) * 0.1).requires_grad_()
+    y, xp = ops.prenorm(x, w, 1e-6)
+    assert y.dtype == torch.bfloat16 and xp.data_ptr() == x.data_ptr()
+    gy, gx = torch.randn_like(y), torch.randn_like(x)
+    torch.autograd.backward([y, xp], [gy, gx])
+    native.check_status()
+    xr, wr = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    yr = ref.rmsnorm(xr, wr, 1e-6)
+    torch.autograd.backward([yr, xr * 1.0], [gy.float(), gx])
+    _close(y, yr, 2e-2, 1e-2, "y")
+    _close(x.grad, xr.grad, 2e-2, 1e-2, "dx")
+    _close(w.grad, wr.grad, 5e-2 * wr.grad.abs().max().item(), 2e-2, "dw")
+    x2 = x.detach().clone().requires_grad_()
+    y2, xp2 = ops.prenorm(x2, w, 1e-6)
+    xp2.backward(gx)                       # only the pass-through is used
+    assert torch.equal(x2.grad, gx)
