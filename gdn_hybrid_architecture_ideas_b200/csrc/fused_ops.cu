@@ -462,19 +462,19 @@ int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const floa
 // layers all read the same finished blocks with different pseudo-queries: the sources are read once for all Q readers,
 // and in the backward the Q gradients meet in one write of every source's gradient (instead of Q kernels and Q - 1
 // accumulation passes over (rows, d) tensors). Same arithmetic per reader as the single-reader kernels above.
-constexpr int MIXQ_MAX = 8;
+constexpr int MIXQ_MAX = 8;       // readers per launch; NS below: register slots for sources (2, 4 or 8), so few sources cost few registers
 struct MultiPtrs { const float* src[MIX_MAX]; float* dsrc[MIX_MAX]; float* out[MIXQ_MAX]; const float* dh[MIXQ_MAX]; };
 
-template <int VPT>
+template <int VPT, int NS>
 __global__ void __launch_bounds__(128) depth_mix_multi_fwd_kernel(MultiPtrs p, int n, int Q, const float* __restrict__ ueff, float* __restrict__ alpha,
                                                                   float* __restrict__ rnorm, float* __restrict__ vu, int d, float eps) {
   __shared__ float part[4][MIX_MAX * (MIXQ_MAX + 1)];
   __shared__ float sal[MIXQ_MAX][MIX_MAX];
   const long row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float4 v[MIX_MAX][VPT];
+  float4 v[NS][VPT];
 #pragma unroll
-  for (int i = 0; i < MIX_MAX; ++i) {
+  for (int i = 0; i < NS; ++i) {
     if (i < n) {
       float ss = 0.f;
 #pragma unroll
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_fwd_kernel(MultiPtrs p, i
 #pragma unroll
     for (int k = 0; k < VPT; ++k) uq[k] = reinterpret_cast<const float4*>(ueff + static_cast<long>(q) * d)[k * 128 + threadIdx.x];
 #pragma unroll
-    for (int i = 0; i < MIX_MAX; ++i) {
+    for (int i = 0; i < NS; ++i) {
       if (i < n) {
         float dot = 0.f;
 #pragma unroll
@@ -526,7 +526,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_fwd_kernel(MultiPtrs p, i
 #pragma unroll
     for (int k = 0; k < VPT; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int i = 0; i < MIX_MAX; ++i) {
+    for (int i = 0; i < NS; ++i) {
       if (i < n) {
         const float a = sal[q][i];
 #pragma unroll
@@ -541,7 +541,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_fwd_kernel(MultiPtrs p, i
 // Rows in a grid-stride loop. Per row: the Q products dh_q . v_i (one pass over the readers' gradients), then every
 // source's gradient summed over the readers (a second pass over the gradients, which the first left in cache). The
 // pseudo-query gradients accumulate per CTA in shared memory (a thread owns its columns), then one atomic per entry.
-template <int VPT>
+template <int VPT, int NS>
 __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, int n, int Q, const float* __restrict__ ueff, const float* __restrict__ alpha,
                                                                   const float* __restrict__ rnorm, const float* __restrict__ vu, float* __restrict__ du,
                                                                   long rows, int d) {
@@ -552,9 +552,9 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
   for (int i = threadIdx.x; i < Q * d; i += 128) sdu[i] = 0.f;
   __syncthreads();
   for (long row = blockIdx.x; row < rows; row += gridDim.x) {
-    float4 v[MIX_MAX][VPT];
+    float4 v[NS][VPT];
 #pragma unroll
-    for (int i = 0; i < MIX_MAX; ++i)
+    for (int i = 0; i < NS; ++i)
       if (i < n) {
 #pragma unroll
         for (int k = 0; k < VPT; ++k) v[i][k] = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
@@ -565,7 +565,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
 #pragma unroll
       for (int k = 0; k < VPT; ++k) g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * 128 + threadIdx.x];
 #pragma unroll
-      for (int i = 0; i < MIX_MAX; ++i) {
+      for (int i = 0; i < NS; ++i) {
         if (i < n) {
           float a = 0.f;
 #pragma unroll
@@ -592,9 +592,9 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
       sc2[q][i] = dl * vu[(row * Q + q) * n + i] * r * r * r / d;
     }
     __syncthreads();
-    float4 acc[MIX_MAX][VPT];
+    float4 acc[NS][VPT];
 #pragma unroll
-    for (int i = 0; i < MIX_MAX; ++i)
+    for (int i = 0; i < NS; ++i)
 #pragma unroll
       for (int k = 0; k < VPT; ++k) acc[i][k] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int q = 0; q < Q; ++q) {
@@ -607,7 +607,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
         dq[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
-      for (int i = 0; i < MIX_MAX; ++i) {
+      for (int i = 0; i < NS; ++i) {
         if (i < n) {
           const float al = sal[q][i], c1 = sc1[q][i], c2 = sc2[q][i];
 #pragma unroll
@@ -627,7 +627,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
       }
     }
 #pragma unroll
-    for (int i = 0; i < MIX_MAX; ++i)
+    for (int i = 0; i < NS; ++i)
       if (i < n) {
 #pragma unroll
         for (int k = 0; k < VPT; ++k) reinterpret_cast<float4*>(p.dsrc[i] + row * d)[k * 128 + threadIdx.x] = acc[i][k];
@@ -644,12 +644,17 @@ int depth_mix_multi_fwd(const float* const* src, int n, float* const* out, int Q
   for (int i = 0; i < n; ++i) p.src[i] = src[i];
   for (int q = 0; q < Q; ++q) p.out[q] = out[q];
   const unsigned grid = static_cast<unsigned>(rows);
+  const int ns = n <= 2 ? 2 : (n <= 4 ? 4 : 8);
+#define GHB_MIXF(V, S) depth_mix_multi_fwd_kernel<V, S><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps)
+#define GHB_MIXF_NS(V) (ns == 2 ? GHB_MIXF(V, 2) : (ns == 4 ? GHB_MIXF(V, 4) : GHB_MIXF(V, 8)))
   switch (d / 512) {
-    case 1: depth_mix_multi_fwd_kernel<1><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps); break;
-    case 2: depth_mix_multi_fwd_kernel<2><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps); break;
-    case 4: depth_mix_multi_fwd_kernel<4><<<grid, 128, 0, st>>>(p, n, Q, ueff, alpha, rnorm, vu, d, eps); break;
+    case 1: GHB_MIXF_NS(1); break;
+    case 2: GHB_MIXF_NS(2); break;
+    case 4: GHB_MIXF_NS(4); break;
     default: return 1;
   }
+#undef GHB_MIXF_NS
+#undef GHB_MIXF
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, const float* const* dh, int Q, const float* ueff, const float* alpha,
@@ -659,20 +664,23 @@ int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, cons
   for (int i = 0; i < n; ++i) { p.src[i] = src[i]; p.dsrc[i] = dsrc[i]; }
   for (int q = 0; q < Q; ++q) p.dh[q] = dh[q];
   const size_t smem = static_cast<size_t>(Q) * d * 4;
-  const unsigned grid = static_cast<unsigned>(rows < sms * 4L ? rows : sms * 4L);
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 512 * 4);
-    cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 1024 * 4);
-    cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 2048 * 4);
-    attr = true;
-  }
+  const unsigned grid = static_cast<unsigned>(rows < sms * 6L ? rows : sms * 6L);
+  const int ns = n <= 2 ? 2 : (n <= 4 ? 4 : 8);
+#define GHB_MIXB(V, S)                                                                                                            \
+  do {                                                                                                                            \
+    static bool attr = false;                                                                                                     \
+    if (!attr) { cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<V, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * V * 512 * 4); attr = true; } \
+    depth_mix_multi_bwd_kernel<V, S><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d);                       \
+  } while (0)
+#define GHB_MIXB_NS(V) do { if (ns == 2) GHB_MIXB(V, 2); else if (ns == 4) GHB_MIXB(V, 4); else GHB_MIXB(V, 8); } while (0)
   switch (d / 512) {
-    case 1: depth_mix_multi_bwd_kernel<1><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d); break;
-    case 2: depth_mix_multi_bwd_kernel<2><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d); break;
-    case 4: depth_mix_multi_bwd_kernel<4><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d); break;
+    case 1: GHB_MIXB_NS(1); break;
+    case 2: GHB_MIXB_NS(2); break;
+    case 4: GHB_MIXB_NS(4); break;
     default: return 1;
   }
+#undef GHB_MIXB_NS
+#undef GHB_MIXB
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -680,11 +688,11 @@ int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, cons
 // One CTA per row of fp32 logits (n, V). Pass 1: online max / sum over the row (kept in shared memory when it fits),
 // pass 2: grad = softmax * (asum + 2 b lse) written as bf16 in a separate (n, V) buffer, then the s targets subtract
 // their weights. ce[row] = sum_k a_k (lse - logit[t_k]); lse[row] saved.
-__global__ void __launch_bounds__(512) ce_grad_kernel(const float* __restrict__ logits, const long* __restrict__ targets, const float* __restrict__ a,
+__global__ void __launch_bounds__(1024) ce_grad_kernel(const float* __restrict__ logits, const long* __restrict__ targets, const float* __restrict__ a,
                                                       const float* __restrict__ b, __nv_bfloat16* __restrict__ grad, float* __restrict__ ce,
                                                       float* __restrict__ lse_out, int V, int s, int cache_row) {
   extern __shared__ float rowbuf[];
-  __shared__ float redm[16], reds[16];
+  __shared__ float redm[32], reds[32];
   const long row = blockIdx.x;
   const float* lr = logits + row * V;
   float m = -INFINITY, sum = 0.f;
@@ -752,7 +760,7 @@ int ce_grad(const float* logits, const long* targets, const float* a, const floa
   const int cache = bytes <= 200 * 1024;
   static bool attr = false;
   if (!attr) { cudaFuncSetAttribute(ce_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
-  ce_grad_kernel<<<static_cast<unsigned>(rows), 512, cache ? bytes : 0, st>>>(logits, targets, a, b, static_cast<__nv_bfloat16*>(grad), ce, lse, V, s, cache);
+  ce_grad_kernel<<<static_cast<unsigned>(rows), V >= 16384 ? 1024 : 512, cache ? bytes : 0, st>>>(logits, targets, a, b, static_cast<__nv_bfloat16*>(grad), ce, lse, V, s, cache);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
