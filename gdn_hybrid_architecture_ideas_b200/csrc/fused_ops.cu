@@ -853,16 +853,28 @@ struct PrepQK {
   int Hq, Hkv, R2; float eps; long tokens;
 };
 
-__device__ __forceinline__ void rot_pair(float& v0, float& v1, int lane, int R2, const float* c, const float* s, bool inverse) {
-  // lanes [0, R2 / 2) hold the first halves of the rotary pairs (channels 2 lane, 2 lane + 1), lanes [R2 / 2, R2) the second
-  const int half = R2 >> 1;
-  const float p0 = __shfl_xor_sync(0xffffffffu, v0, half), p1 = __shfl_xor_sync(0xffffffffu, v1, half);
+// Rotation coefficients of one lane: lanes [0, R2 / 2) hold the first halves of the rotary pairs (channels 2 lane,
+// 2 lane + 1), lanes [R2 / 2, R2) the second halves; the partner's values come through a shuffle.
+struct RotCoef { float c0, c1, s0, s1; bool on; };      // s already signed for this lane's half; on: the lane holds rotary channels
+
+__device__ __forceinline__ RotCoef rot_coef(int lane, int R2, const float* c, const float* s) {
+  RotCoef r{1.f, 1.f, 0.f, 0.f, false};
   if (lane < R2) {
+    r.on = true;
+    const int half = R2 >> 1;
     const bool first = lane < half;
     const int i = (first ? lane : lane - half) * 2;
-    const float c0 = c[i], c1 = c[i + 1], s0 = inverse ? -s[i] : s[i], s1 = inverse ? -s[i + 1] : s[i + 1];
-    v0 = first ? v0 * c0 - p0 * s0 : v0 * c0 + p0 * s0;
-    v1 = first ? v1 * c1 - p1 * s1 : v1 * c1 + p1 * s1;
+    r.c0 = c[i]; r.c1 = c[i + 1];
+    r.s0 = first ? -s[i] : s[i]; r.s1 = first ? -s[i + 1] : s[i + 1];
+  }
+  return r;
+}
+// v' = v c + partner s (forward); the inverse rotation flips the sign of s. Lanes outside the rotary range keep v.
+__device__ __forceinline__ void rotate(float& v0, float& v1, int half, const RotCoef& r, bool inverse) {
+  const float p0 = __shfl_xor_sync(0xffffffffu, v0, half), p1 = __shfl_xor_sync(0xffffffffu, v1, half);
+  if (r.on) {
+    v0 = v0 * r.c0 + p0 * (inverse ? -r.s0 : r.s0);
+    v1 = v1 * r.c1 + p1 * (inverse ? -r.s1 : r.s1);
   }
 }
 
@@ -871,34 +883,51 @@ __global__ void __launch_bounds__(256) attn_prep_fwd_kernel(PrepQK a, __nv_bfloa
   const int lane = threadIdx.x & 31;
   const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
   const float gq0 = 1.f + a.wq[2 * lane], gq1 = 1.f + a.wq[2 * lane + 1], gk0 = 1.f + a.wk[2 * lane], gk1 = 1.f + a.wk[2 * lane + 1];
+  const int half = a.R2 >> 1;
+  const RotCoef cap = a.cos_c ? rot_coef(lane, a.R2, a.cos_c, a.sin_c) : RotCoef{1.f, 1.f, 0.f, 0.f, false};
   for (long t = warp; t < a.tokens; t += nwarp) {
-    const float* ct = a.cos + t * a.R2; const float* st = a.sin + t * a.R2;
-    for (int h = 0; h < a.Hq + a.Hkv; ++h) {
-      const bool is_q = h < a.Hq;
-      const int hh = is_q ? h : h - a.Hq;
-      const __nv_bfloat16* src = is_q ? a.q + t * a.q_ts + static_cast<long>(hh) * a.q_hs : a.k + t * a.k_ts + static_cast<long>(hh) * 64;
-      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[lane]);
-      const float r = rsqrtf(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + a.eps);
-      const float n0 = x.x * r * (is_q ? gq0 : gk0), n1 = x.y * r * (is_q ? gq1 : gk1);
+    const RotCoef rc = a.R2 ? rot_coef(lane, a.R2, a.cos + t * a.R2, a.sin + t * a.R2) : RotCoef{1.f, 1.f, 0.f, 0.f, false};
+    const __nv_bfloat16* qs = a.q + t * a.q_ts;
+#pragma unroll 2
+    for (int h = 0; h < a.Hq; ++h) {
+      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(qs + static_cast<long>(h) * a.q_hs)[lane]);
+      const float r = fast_rsqrt(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + a.eps);
+      const float n0 = x.x * r * gq0, n1 = x.y * r * gq1;
       float v0 = n0, v1 = n1;
-      if (a.R2) rot_pair(v0, v1, lane, a.R2, ct, st, false);
-      const long o = (t * (is_q ? a.Hq : a.Hkv) + hh) * 64;
-      reinterpret_cast<__nv_bfloat162*>((is_q ? qr : kr) + o)[lane] = __floats2bfloat162_rn(v0, v1);
+      if (a.R2) rotate(v0, v1, half, rc, false);
+      const long o = (t * a.Hq + h) * 64;
+      reinterpret_cast<__nv_bfloat162*>(qr + o)[lane] = __floats2bfloat162_rn(v0, v1);
       if (a.cos_c) {
-        if (is_q) {
-          float f0 = n0, f1 = n1;
-          rot_pair(f0, f1, lane, a.R2, a.cos_c, a.sin_c, false);
-          reinterpret_cast<__nv_bfloat162*>(qf + o)[lane] = __floats2bfloat162_rn(f0, f1);
-        } else {
-          reinterpret_cast<__nv_bfloat162*>(kf + o)[lane] = __floats2bfloat162_rn(n0, n1);
-        }
+        float f0 = n0, f1 = n1;
+        rotate(f0, f1, half, cap, false);
+        reinterpret_cast<__nv_bfloat162*>(qf + o)[lane] = __floats2bfloat162_rn(f0, f1);
       }
+    }
+    const __nv_bfloat16* ks = a.k + t * a.k_ts;
+    for (int h = 0; h < a.Hkv; ++h) {
+      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(ks + static_cast<long>(h) * 64)[lane]);
+      const float r = fast_rsqrt(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + a.eps);
+      const float n0 = x.x * r * gk0, n1 = x.y * r * gk1;
+      float v0 = n0, v1 = n1;
+      if (a.R2) rotate(v0, v1, half, rc, false);
+      const long o = (t * a.Hkv + h) * 64;
+      reinterpret_cast<__nv_bfloat162*>(kr + o)[lane] = __floats2bfloat162_rn(v0, v1);
+      if (a.cos_c) reinterpret_cast<__nv_bfloat162*>(kf + o)[lane] = __floats2bfloat162_rn(n0, n1);
     }
   }
 }
 
 // Gradients w.r.t. the raw q / k and the two gains. dqraw is written with the raw queries' strides (the interleaved gate
 // half is left untouched); dw: [2][64] fp32, zeroed by the caller.
+__device__ __forceinline__ void prep_bwd_head(float2 x, float d0, float d1, float g0, float g1, float eps, float& acc0, float& acc1, __nv_bfloat16* dst, int lane) {
+  const float r = fast_rsqrt(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + eps);
+  const float h0 = x.x * r, h1 = x.y * r;
+  acc0 += d0 * h0; acc1 += d1 * h1;
+  const float e0 = d0 * g0, e1 = d1 * g1;
+  const float dot = wsum(e0 * h0 + e1 * h1) * (1.f / 64.f);
+  reinterpret_cast<__nv_bfloat162*>(dst)[lane] = __floats2bfloat162_rn(r * (e0 - h0 * dot), r * (e1 - h1 * dot));
+}
+
 __global__ void __launch_bounds__(256) attn_prep_bwd_kernel(PrepQK a, const __nv_bfloat16* __restrict__ dqr, const __nv_bfloat16* __restrict__ dqf,
                                                             const __nv_bfloat16* __restrict__ dkr, const __nv_bfloat16* __restrict__ dkf,
                                                             __nv_bfloat16* __restrict__ dqraw, __nv_bfloat16* __restrict__ dkraw, float* __restrict__ dw) {
@@ -906,31 +935,37 @@ __global__ void __launch_bounds__(256) attn_prep_bwd_kernel(PrepQK a, const __nv
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
   const float gq0 = 1.f + a.wq[2 * lane], gq1 = 1.f + a.wq[2 * lane + 1], gk0 = 1.f + a.wk[2 * lane], gk1 = 1.f + a.wk[2 * lane + 1];
+  const int half = a.R2 >> 1;
+  const RotCoef cap = a.cos_c ? rot_coef(lane, a.R2, a.cos_c, a.sin_c) : RotCoef{1.f, 1.f, 0.f, 0.f, false};
   float acc[4] = {0.f, 0.f, 0.f, 0.f};      // dwq (2 channels), dwk (2 channels)
   for (long t = warp; t < a.tokens; t += nwarp) {
-    const float* ct = a.cos + t * a.R2; const float* st = a.sin + t * a.R2;
-    for (int h = 0; h < a.Hq + a.Hkv; ++h) {
-      const bool is_q = h < a.Hq;
-      const int hh = is_q ? h : h - a.Hq;
-      const long o = (t * (is_q ? a.Hq : a.Hkv) + hh) * 64;
-      const __nv_bfloat16* src = is_q ? a.q + t * a.q_ts + static_cast<long>(hh) * a.q_hs : a.k + t * a.k_ts + static_cast<long>(hh) * 64;
-      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[lane]);
-      const float r = rsqrtf(wsum(x.x * x.x + x.y * x.y) * (1.f / 64.f) + a.eps);
-      const float h0 = x.x * r, h1 = x.y * r;
-      const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>((is_q ? dqr : dkr) + o)[lane]);
+    const RotCoef rc = a.R2 ? rot_coef(lane, a.R2, a.cos + t * a.R2, a.sin + t * a.R2) : RotCoef{1.f, 1.f, 0.f, 0.f, false};
+#pragma unroll 2
+    for (int h = 0; h < a.Hq; ++h) {
+      const long o = (t * a.Hq + h) * 64, so = t * a.q_ts + static_cast<long>(h) * a.q_hs;
+      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(a.q + so)[lane]);
+      const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dqr + o)[lane]);
       float d0 = g.x, d1 = g.y;
-      if (a.R2) rot_pair(d0, d1, lane, a.R2, ct, st, true);
+      if (a.R2) rotate(d0, d1, half, rc, true);
       if (a.cos_c) {
-        const float2 gf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>((is_q ? dqf : dkf) + o)[lane]);
+        const float2 gf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dqf + o)[lane]);
         float f0 = gf.x, f1 = gf.y;
-        if (is_q) rot_pair(f0, f1, lane, a.R2, a.cos_c, a.sin_c, true);
+        rotate(f0, f1, half, cap, true);
         d0 += f0; d1 += f1;
       }
-      acc[is_q ? 0 : 2] += d0 * h0; acc[is_q ? 1 : 3] += d1 * h1;
-      const float e0 = d0 * (is_q ? gq0 : gk0), e1 = d1 * (is_q ? gq1 : gk1);
-      const float dot = wsum(e0 * h0 + e1 * h1) * (1.f / 64.f);
-      __nv_bfloat16* dst = is_q ? dqraw + t * a.q_ts + static_cast<long>(hh) * a.q_hs : dkraw + t * a.k_ts + static_cast<long>(hh) * 64;
-      reinterpret_cast<__nv_bfloat162*>(dst)[lane] = __floats2bfloat162_rn(r * (e0 - h0 * dot), r * (e1 - h1 * dot));
+      prep_bwd_head(x, d0, d1, gq0, gq1, a.eps, acc[0], acc[1], dqraw + so, lane);
+    }
+    for (int h = 0; h < a.Hkv; ++h) {
+      const long o = (t * a.Hkv + h) * 64, so = t * a.k_ts + static_cast<long>(h) * 64;
+      const float2 x = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(a.k + so)[lane]);
+      const float2 g = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dkr + o)[lane]);
+      float d0 = g.x, d1 = g.y;
+      if (a.R2) rotate(d0, d1, half, rc, true);
+      if (a.cos_c) {
+        const float2 gf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(dkf + o)[lane]);
+        d0 += gf.x; d1 += gf.y;
+      }
+      prep_bwd_head(x, d0, d1, gk0, gk1, a.eps, acc[2], acc[3], dkraw + so, lane);
     }
   }
 #pragma unroll
