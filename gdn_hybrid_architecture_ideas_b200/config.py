@@ -673,7 +673,7 @@ _TRAIN_BUILT = {
     "optim.hyperball": (False,),
     "optim.gdn_mup": (False, True),
     "loss.normalization": ("global_token_mean",),
-    "loss.ce_form": ("standard",),
+    "loss.ce_form": ("standard", "fixed"),
     "head_impl": ("fused", "chunked"),
     "activation_checkpoint": ("none", "layer", "block", "host", "host_overlap"),
     "freeze_trunk": (False,),

@@ -165,14 +165,14 @@ void depth_mix_multi_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& ds
                                  vu.data_ptr<float>(), du.data_ptr<float>(), src[0].numel() / d, d, sm_count(), stream()), "depth_mix_multi_bwd");
 }
 
-void ce_grad(const Tensor& logits, const Tensor& targets, const Tensor& a, const Tensor& b, Tensor& grad, Tensor& ce, Tensor& lse) {
+void ce_grad(const Tensor& logits, const Tensor& targets, const Tensor& a, const Tensor& b, Tensor& grad, Tensor& ce, Tensor& lse, bool fixed) {
   const c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(is_f32(logits) && logits.is_contiguous() && is_bf16(grad) && grad.is_contiguous() && targets.scalar_type() == torch::kInt64 &&
               targets.is_contiguous() && is_f32(a) && a.is_contiguous() && is_f32(b) && b.is_contiguous(), "ce_grad: layout");
   const long rows = logits.size(0);
   const int V = logits.size(1), s = targets.numel() / rows;
   check(ghb::ce_grad(logits.data_ptr<float>(), reinterpret_cast<const long*>(targets.data_ptr<int64_t>()), a.data_ptr<float>(), b.data_ptr<float>(),
-                     grad.data_ptr(), ce.data_ptr<float>(), lse.data_ptr<float>(), rows, V, s, stream()), "ce_grad");
+                     grad.data_ptr(), ce.data_ptr<float>(), lse.data_ptr<float>(), rows, V, s, fixed, stream()), "ce_grad");
 }
 
 const void* optr(const c10::optional<Tensor>& t) { return t.has_value() ? t->data_ptr() : nullptr; }

@@ -688,6 +688,11 @@ int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, cons
 // One CTA per row of fp32 logits (n, V). Pass 1: online max / sum over the row (kept in shared memory when it fits),
 // pass 2: grad = softmax * (asum + 2 b lse) written as bf16 in a separate (n, V) buffer, then the s targets subtract
 // their weights. ce[row] = sum_k a_k (lse - logit[t_k]); lse[row] saved.
+// FIXED: the hard-target cross-entropy without the cancellation of softmax_t - 1 (ced/train/ce_fix.py:1-60): a term's loss is
+// softplus(L'), L' = LSE_{j != t}(z_j) - z_t, and its target gradient -sigmoid(L'). Only the row's argmax can have a
+// softmax within rounding of 1, so only that column needs the sum of exponentials without it (two more passes over the
+// cached row); for any other target L' = (lse - z_t) + log1p(-p_t) has no cancellation (ced/train/ce_fix.py:151-170).
+template <bool FIXED>
 __global__ void __launch_bounds__(1024) ce_grad_kernel(const float* __restrict__ logits, const long* __restrict__ targets, const float* __restrict__ a,
                                                       const float* __restrict__ b, __nv_bfloat16* __restrict__ grad, float* __restrict__ ce,
                                                       float* __restrict__ lse_out, int V, int s, int cache_row) {
@@ -728,7 +733,37 @@ __global__ void __launch_bounds__(1024) ce_grad_kernel(const float* __restrict__
   const int nw = blockDim.x >> 5;
   for (int i = 0; i < nw; ++i) gm = fmaxf(gm, redm[i]);
   for (int i = 0; i < nw; ++i) if (redm[i] > -INFINITY) gs += reds[i] * __expf(redm[i] - gm);
-  const float lse = gm + __logf(gs);
+  float lse = gm + __logf(gs);
+  float s_excl = 0.f;
+  int gidx = -1;
+  if (FIXED) {
+    __shared__ int s_idx;
+    __shared__ float red2[32];
+    if (threadIdx.x == 0) s_idx = V;
+    __syncthreads();
+    int mine = V;
+    for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
+      const float4 t = cache_row ? *reinterpret_cast<const float4*>(rowbuf + i) : *reinterpret_cast<const float4*>(lr + i);
+      const float v[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int e = 3; e >= 0; --e) if (v[e] == gm) mine = min(mine, i + e);
+    }
+    if (mine < V) atomicMin(&s_idx, mine);
+    __syncthreads();
+    gidx = s_idx;
+    float se = 0.f;
+    for (int i = threadIdx.x * 4; i < V; i += blockDim.x * 4) {
+      const float4 t = cache_row ? *reinterpret_cast<const float4*>(rowbuf + i) : *reinterpret_cast<const float4*>(lr + i);
+      const float v[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) if (i + e != gidx) se += __expf(v[e] - gm);
+    }
+    se = wsum(se);
+    if ((threadIdx.x & 31) == 0) red2[threadIdx.x >> 5] = se;
+    __syncthreads();
+    for (int i = 0; i < nw; ++i) s_excl += red2[i];
+    lse = gm + log1pf(s_excl);
+  }
   float asum = 0.f;
   for (int k = 0; k < s; ++k) asum += a[row * s + k];
   const float coef = asum + 2.f * b[row] * lse;
@@ -745,8 +780,21 @@ __global__ void __launch_bounds__(1024) ce_grad_kernel(const float* __restrict__
       const float ak = a[row * s + k];
       const long t = targets[row * s + k];
       if (ak != 0.f && t >= 0 && t < V) {
-        c += ak * (lse - lr[t]);
-        gr[t] = __float2bfloat16(__bfloat162float(gr[t]) - ak);
+        if (FIXED) {
+          const float zt = lr[t], pt = expf(zt - lse);
+          const float lp = t == gidx ? logf(s_excl) : (lse - zt) + log1pf(-pt);
+          c += ak * (lp > 0.f ? lp + log1pf(expf(-lp)) : log1pf(expf(lp)));
+          float aj = 0.f;                          // weight of every term whose target is this column
+          for (int k2 = 0; k2 < s; ++k2) if (targets[row * s + k2] == t) aj += a[row * s + k2];
+          const float e = expf(-fabsf(lp));
+          const float sg = (lp < 0.f ? e : 1.f) / (1.f + e);
+          gr[t] = __float2bfloat16((asum - aj + 2.f * b[row] * lse) * pt - aj * sg);
+        } else {
+          c += ak * (lse - lr[t]);
+          float aj = 0.f;
+          for (int k2 = 0; k2 < s; ++k2) if (targets[row * s + k2] == t) aj += a[row * s + k2];
+          gr[t] = __float2bfloat16(coef * expf(lr[t] - lse) - aj);       // formed in fp32 and rounded once (every term of the column writes the same value)
+        }
       }
     }
     ce[row] = c;
@@ -754,13 +802,19 @@ __global__ void __launch_bounds__(1024) ce_grad_kernel(const float* __restrict__
   }
 }
 int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,
-            int s, cudaStream_t st) {
+            int s, bool fixed, cudaStream_t st) {
   if (V % 4) return 1;
   const size_t bytes = static_cast<size_t>(V) * 4;
   const int cache = bytes <= 200 * 1024;
   static bool attr = false;
-  if (!attr) { cudaFuncSetAttribute(ce_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
-  ce_grad_kernel<<<static_cast<unsigned>(rows), V >= 16384 ? 1024 : 512, cache ? bytes : 0, st>>>(logits, targets, a, b, static_cast<__nv_bfloat16*>(grad), ce, lse, V, s, cache);
+  if (!attr) {
+    cudaFuncSetAttribute(ce_grad_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(ce_grad_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    attr = true;
+  }
+  const unsigned threads = V >= 16384 ? 1024 : 512;
+  if (fixed) ce_grad_kernel<true><<<static_cast<unsigned>(rows), threads, cache ? bytes : 0, st>>>(logits, targets, a, b, static_cast<__nv_bfloat16*>(grad), ce, lse, V, s, cache);
+  else ce_grad_kernel<false><<<static_cast<unsigned>(rows), threads, cache ? bytes : 0, st>>>(logits, targets, a, b, static_cast<__nv_bfloat16*>(grad), ce, lse, V, s, cache);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

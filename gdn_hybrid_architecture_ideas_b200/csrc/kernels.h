@@ -42,7 +42,7 @@ int depth_mix_fwd(const float* const* src, int n, const float* ueff, float* out,
 int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const float* ueff, const float* dh, const float* alpha,
                   const float* rnorm, float* du, long rows, int d, int sms, cudaStream_t st);
 int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,
-            int s, cudaStream_t st);
+            int s, bool fixed, cudaStream_t st);
 
 int dual_lerp_fwd(const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* oa, void* ob, long n, int sms, cudaStream_t st);
 int dual_lerp_bwd(const void* ga, const void* gb, const void* x, const void* ya, const void* yb, const float* la, const float* lb, void* dx, void* dya,

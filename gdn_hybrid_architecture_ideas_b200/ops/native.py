@@ -526,7 +526,7 @@ def depth_mix_multi(sources, readers, eps):
 
 class _FusedLinearCE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, targets, a, b, chunk, w_lp):
+    def forward(ctx, hidden, weight, targets, a, b, chunk, w_lp, fixed=False):
         d = hidden.shape[-1]
         h = _bf16(hidden).reshape(-1, d).contiguous()
         n, V = h.shape[0], w_lp.shape[0]
@@ -543,7 +543,7 @@ class _FusedLinearCE(torch.autograd.Function):
             hi = min(n, lo + chunk)
             m = hi - lo
             gemm(h[lo:hi], w_lp, out=logits[:m])
-            ext().ce_grad(logits[:m], t[lo:hi], a2[lo:hi], b1[lo:hi], grad[:m], ce[lo:hi], lse[lo:hi])
+            ext().ce_grad(logits[:m], t[lo:hi], a2[lo:hi], b1[lo:hi], grad[:m], ce[lo:hi], lse[lo:hi], fixed)
             _count()
             gemm(grad[:m], w_lp, out=dh[lo:hi], b_mn=True)
             gemm(grad[:m], h[lo:hi], out=dW, a_mn=True, b_mn=True, accumulate=True)
@@ -557,12 +557,12 @@ class _FusedLinearCE(torch.autograd.Function):
     def backward(ctx, g_loss, g_ce, g_lse):
         dh, dW = ctx.saved_tensors
         hd, hs, wd = ctx.meta
-        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None, None
+        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None, None, None
 
 
-def fused_linear_ce(hidden, weight, targets, a, b, chunk, weight_lp=None):
+def fused_linear_ce(hidden, weight, targets, a, b, chunk, weight_lp=None, fixed=False):
     w_lp = weight_lp if weight_lp is not None else weight.detach().to(BF16)
-    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk, w_lp)
+    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk, w_lp, fixed)
 
 
 def lm_loss_sums(hidden, weight, targets, weights=None, z_loss=0.0, weight_lp=None):

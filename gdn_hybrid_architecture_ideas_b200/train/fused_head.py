@@ -14,11 +14,53 @@ import torch
 import torch.nn.functional as F
 
 CHUNK = 2048
+CE_FORMS = ("standard", "fixed")
 
 
-def _ce_grad_chunk(logits, targets, a, b):
+def check_ce_form(form: str) -> bool:
+    """True for "fixed" (reference: ced/train/ce_fix.py:55-90)."""
+    if form not in CE_FORMS:
+        raise ValueError(f"loss.ce_form {form!r}: one of {CE_FORMS} ('fixed': softplus(LSE_(j != t) z_j - z_t), whose target gradient "
+                         "-sigmoid keeps its accuracy where softmax_t - 1 rounds to 0)")
+    return form == "fixed"
+
+
+def sigmoid_stable(x: torch.Tensor) -> torch.Tensor:
+    e = torch.exp(-x.abs())
+    return torch.where(x < 0, e, torch.ones_like(e)) / (1.0 + e)
+
+
+def fixed_terms(logits: torch.Tensor, targets: torch.Tensor):
+    """(z_t (n, K), L' (n, K), lse (n,)) of the fixed cross-entropy, L'_k = LSE_(j != t_k)(z_j) - z_(t_k). Only the row's
+    argmax can have a softmax within rounding of 1, so only its column needs the log-sum-exp without it; every other
+    target has p <= 1/2 and L' = (lse - z_t) + log1p(-p) without cancellation (reference: ced/train/ce_fix.py:151-170)."""
+    xt = logits.gather(1, targets)
+    am = logits.argmax(dim=-1, keepdim=True)
+    zam = logits.gather(1, am).squeeze(1)
+    lse_am = torch.logsumexp(logits.scatter(1, am, float("-inf")), dim=-1)
+    lse = torch.logaddexp(lse_am, zam)
+    lp_other = (lse[:, None] - xt) + torch.log1p(-torch.exp(xt - lse[:, None]).clamp(max=0.75))
+    return xt, torch.where(targets == am, (lse_am - zam)[:, None], lp_other), lse
+
+
+def _ce_grad_chunk(logits, targets, a, b, fixed: bool = False):
     """(ce (n,), lse (n,), dlogits) for one chunk; targets (n, s), a (n, s) per-target weights (0 = ignored),
-    b (n,) z-loss weights. dlogits = softmax * (sum_k a_k + 2 b lse) - sum_k a_k onehot(t_k)."""
+    b (n,) z-loss weights. dlogits = softmax * (sum_k a_k + 2 b lse) - sum_k a_k onehot(t_k); with the fixed form a term's
+    loss is softplus(L'_k) and column j of the targets gets (A - A_j + 2 b lse) softmax_j - A_j sigmoid(L'_j), A_j the
+    weight of the terms whose target is j (reference: ced/train/ce_fix.py:130-150, 176-190)."""
+    if fixed:
+        t = targets.clamp(min=0)
+        xt, lp, lse = fixed_terms(logits, t)
+        ce = (torch.logaddexp(lp, torch.zeros_like(lp)) * a).sum(1)
+        asum = a.sum(1)
+        g = torch.exp(logits - lse[:, None]) * (asum + 2.0 * b * lse)[:, None]
+        a_j = (a[:, None, :] * (t[:, :, None] == t[:, None, :])).sum(-1)
+        val = (asum[:, None] - a_j + (2.0 * b * lse)[:, None]) * torch.exp(xt - lse[:, None]) - a_j * sigmoid_stable(lp)
+        live = a != 0
+        for k in range(t.shape[1]):
+            col = t[:, k:k + 1]
+            g.scatter_(1, col, torch.where(live[:, k:k + 1], val[:, k:k + 1], g.gather(1, col)))
+        return ce, lse, g
     lse = torch.logsumexp(logits, dim=-1)
     picked = logits.gather(1, targets.clamp(min=0))
     ce = ((lse[:, None] - picked) * a).sum(1)
@@ -30,7 +72,7 @@ def _ce_grad_chunk(logits, targets, a, b):
 
 class _FusedLinearCE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, targets, a, b, chunk):
+    def forward(ctx, hidden, weight, targets, a, b, chunk, fixed=False):
         dt = torch.promote_types(hidden.dtype, torch.float32)
         d = hidden.shape[-1]
         with torch.autocast(hidden.device.type, enabled=False):
@@ -46,7 +88,7 @@ class _FusedLinearCE(torch.autograd.Function):
             dW = torch.zeros_like(W)
             for lo in range(0, n, chunk):
                 hi = min(n, lo + chunk)
-                c, l, g = _ce_grad_chunk(h[lo:hi] @ W.T, t[lo:hi], a2[lo:hi], b1[lo:hi])
+                c, l, g = _ce_grad_chunk(h[lo:hi] @ W.T, t[lo:hi], a2[lo:hi], b1[lo:hi], fixed)
                 ce[lo:hi], lse[lo:hi] = c, l
                 dh[lo:hi] = g @ W
                 dW.addmm_(g.T, h[lo:hi])
@@ -60,25 +102,30 @@ class _FusedLinearCE(torch.autograd.Function):
     def backward(ctx, g_loss, g_ce, g_lse):
         dh, dW = ctx.saved_tensors
         hd, hs, wd = ctx.meta
-        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None
+        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None, None
 
 
-def fused_linear_ce(hidden, weight, targets, a, b, chunk: int | None = None, weight_lp=None):
+def fused_linear_ce(hidden, weight, targets, a, b, chunk: int | None = None, weight_lp=None, ce_form: str = "standard"):
     """hidden (..., d), weight (V, d), targets (...,) or (..., s), a like targets, b (...,) -> (loss, ce, lse) with
     ce, lse per position and without gradient."""
+    fixed = check_ce_form(ce_form)
     if hidden.is_cuda:
         from .. import ops
 
         if ops.use_native(hidden):
             from ..ops import native
 
-            return native.fused_linear_ce(hidden, weight, targets, a, b, chunk or CHUNK, weight_lp)
-    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk or CHUNK)
+            return native.fused_linear_ce(hidden, weight, targets, a, b, chunk or CHUNK, weight_lp, fixed)
+    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk or CHUNK, fixed)
 
 
-def chunked_ce(hidden, weight, targets, a, b, chunk: int = 1024):
-    """Unfused head: checkpointed chunks of fp32 logits through autograd (reference: ced/train/chunked_loss.py:33-140)."""
+def chunked_ce(hidden, weight, targets, a, b, chunk: int = 1024, ce_form: str = "standard"):
+    """Unfused head: checkpointed chunks of fp32 logits through autograd (reference: ced/train/chunked_loss.py:33-140).
+    With the fixed form each term masks its own target column out of the log-sum-exp, so autograd's target gradient is
+    -sigmoid(L') exactly (reference: ced/train/ce_fix.py:94-120)."""
     import torch.utils.checkpoint as ckpt
+
+    fixed = check_ce_form(ce_form)
 
     d = hidden.shape[-1]
     h = hidden.reshape(-1, d)
@@ -88,6 +135,18 @@ def chunked_ce(hidden, weight, targets, a, b, chunk: int = 1024):
     def piece(hc, W, tc, ac, bc):
         dt = torch.promote_types(hc.dtype, torch.float32)
         logits = F.linear(hc.to(dt), W.to(dt))
+        if fixed:
+            tcl = tc.clamp(min=0)
+            ces, lse = [], None
+            for k in range(tcl.shape[1]):
+                col = tcl[:, k:k + 1]
+                zt = logits.gather(1, col).squeeze(1)
+                lse_nt = torch.logsumexp(logits.scatter(1, col, float("-inf")), dim=-1)
+                ces.append(torch.logaddexp(lse_nt - zt, torch.zeros_like(zt)))
+                if lse is None:
+                    lse = torch.logaddexp(lse_nt, zt)
+            ce = (torch.stack(ces, 1) * ac.to(dt)).sum(1)
+            return torch.stack([ce.sum() + (bc.to(dt) * lse * lse).sum(), ce.sum()])
         lse = torch.logsumexp(logits, dim=-1)
         ce = ((lse[:, None] - logits.gather(1, tc.clamp(min=0))) * ac.to(dt)).sum(1)
         return torch.stack([ce.sum() + (bc.to(dt) * lse * lse).sum(), ce.sum()])

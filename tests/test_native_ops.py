@@ -528,3 +528,42 @@ def test_prenorm_passthrough():
     y2, xp2 = ops.prenorm(x2, w, 1e-6)
     xp2.backward(gx)                       # only the pass-through is used
     assert torch.equal(x2.grad, gx)
+
+
+@pytest.mark.parametrize("s,V", [(1, 4096), (3, 32768)])
+def test_ce_grad_fixed_form(s, V):
+    """The fixed cross-entropy in the CE kernel against the PyTorch statement, with rows collapsed onto their target (the
+    argmax column) and onto another column."""
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+    from gdn_hybrid_architecture_ideas_b200.train import fused_head as FH
+
+    torch.manual_seed(V + s)
+    n = 64
+    logits = (torch.randn(n, V, device=_dev()) * 2).contiguous()
+    t = torch.randint(0, V, (n, s), device=_dev())
+    logits[0, t[0, 0]] += 40.0
+    logits[1, (t[1, 0] + 1) % V] += 40.0
+    if s > 1:
+        t[2, 1] = t[2, 0]
+    a = torch.rand(n, s, device=_dev())
+    a[3, 0] = 0.0
+    b = torch.rand(n, device=_dev()) * 0.01
+    grad = torch.empty(n, V, dtype=torch.bfloat16, device=_dev())
+    ce = torch.empty(n, device=_dev())
+    lse = torch.empty(n, device=_dev())
+    native.ext().ce_grad(logits, t, a, b, grad, ce, lse, True)
+    native.check_status()
+    wce, wlse, wg = FH._ce_grad_chunk(logits.double(), t, a.double(), b.double(), fixed=True)
+    _close(lse, wlse, 1e-4, 1e-5, "lse")
+    _close(ce, wce, 1e-4, 1e-4, "ce")
+    _close(grad, wg, 1e-5, 1e-2, "grad")
+    b0 = torch.zeros_like(b)
+    native.ext().ce_grad(logits, t, a, b0, grad, ce, lse, True)
+    tiny = grad[0, t[0, 0]].float().item()
+    want0 = FH._ce_grad_chunk(logits.double(), t, a.double(), b0.double(), fixed=True)[2][0, t[0, 0]].item()
+    assert abs(tiny - want0) <= 2e-2 * abs(want0), (tiny, want0)
+    if s == 1:
+        assert want0 < 0 and abs(want0) < 1e-8, want0          # -a sigmoid(L'): tiny, not zero
+    native.ext().ce_grad(logits, t, a, b0, grad, ce, lse, False)
+    if s == 1:
+        assert abs(grad[0, t[0, 0]].float().item()) < 1e-6      # the standard form's softmax_t - 1 has rounded away (to a few fp32 ulps of a)

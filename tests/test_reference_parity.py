@@ -140,3 +140,52 @@ def test_mtp_head_matches_reference(reference):
     ctx = sequence_context(doc[:, :1])[0]
     drafts, _ = mtp.draft(mine, ha[:, :1], targets[:, :1], ctx, depth=3)
     assert drafts.shape == (2, 3)
+
+
+def test_fixed_cross_entropy_matches_reference(reference):
+    """loss.ce_form "fixed": the chunk gradient (one target and bags) equals the reference's in-place forms and autograd of
+    its per-term definition; at a margin where softmax_t - 1 rounds to zero the target gradient keeps its value."""
+    from ced.train import ce_fix as R
+
+    from gdn_hybrid_architecture_ideas_b200.train import fused_head as FH
+
+    g = torch.Generator().manual_seed(0)
+    n, V, K = 12, 50, 3
+    logits = torch.randn(n, V, generator=g, dtype=torch.float64) * 3
+    logits[0, 7] += 60.0           # a collapsed row: its target is the argmax by a wide margin
+    logits[1, 3] += 60.0           # a collapsed row whose target is NOT the argmax
+    t1 = torch.randint(0, V, (n, 1), generator=g)
+    t1[0, 0], t1[1, 0] = 7, 9
+    a1 = torch.rand(n, 1, generator=g, dtype=torch.float64)
+    b = torch.rand(n, generator=g, dtype=torch.float64) * 0.01
+    ce, lse, grad = FH._ce_grad_chunk(logits.clone(), t1, a1, b, fixed=True)
+    want = logits.clone()
+    rce, rlse = torch.empty(n, dtype=torch.float64), torch.empty(n, dtype=torch.float64)
+    R.ce_grad_fixed_torch(want, t1[:, 0], a1[:, 0], b, rce, rlse)
+    assert (grad - want).abs().max() < 1e-12 and (ce - a1[:, 0] * rce).abs().max() < 1e-12 and (lse - rlse).abs().max() < 1e-12
+    assert abs(float(grad[0].sum() - 2 * b[0] * lse[0])) < 1e-12                 # the row sums to the z-loss part
+    g_fix = FH._ce_grad_chunk(logits.clone(), t1, a1, torch.zeros_like(b), fixed=True)[2]
+    g_std = FH._ce_grad_chunk(logits.clone(), t1, a1, torch.zeros_like(b))[2]
+    assert g_std[0, 7] == 0 and -1e-15 < g_fix[0, 7] < 0 and abs(float(g_fix[0].sum())) < 1e-30      # tiny, not zero, and the row sums to zero
+    z = logits.clone().requires_grad_()
+    rc, rl = R.fixed_ce_lse(z, t1[:, 0])
+    ((a1[:, 0] * rc).sum() + (b * rl * rl).sum()).backward()
+    assert (grad - z.grad).abs().max() < 1e-12
+    tk = torch.randint(0, V, (n, K), generator=g)
+    tk[2, 1] = tk[2, 0]            # a token twice in a bag
+    tk[0, 0] = 7
+    ak = torch.rand(n, K, generator=g, dtype=torch.float64)
+    ce, lse, grad = FH._ce_grad_chunk(logits.clone(), tk, ak, b, fixed=True)
+    z = logits.clone().requires_grad_()
+    rc, rl = R.fixed_multi_ce_lse(z, tk)
+    ((ak * rc).sum() + (b * rl * rl).sum()).backward()
+    assert (grad - z.grad).abs().max() < 1e-11 and (ce - (ak * rc).sum(1)).abs().max() < 1e-11
+    h = torch.randn(n, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    W = torch.randn(V, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    la, _, _ = FH.fused_linear_ce(h, W, tk, ak, b, 5, ce_form="fixed")
+    ga = torch.autograd.grad(la, [h, W])
+    lb, _ = FH.chunked_ce(h, W, tk, ak, b, chunk=5, ce_form="fixed")
+    gb = torch.autograd.grad(lb, [h, W])
+    assert abs(float(la - lb)) < 1e-10 and max((x - y).abs().max() for x, y in zip(ga, gb)) < 1e-10
+    with pytest.raises(ValueError):
+        FH.fused_linear_ce(h, W, tk, ak, b, 5, ce_form="other")

@@ -272,3 +272,19 @@ def test_gdn_mup_groups_and_init(tmp_path):
     for _ in range(4):
         l1 = t.train_step()["loss"]
     assert l1 < l0
+
+
+@pytest.mark.parametrize("head", ["fused", "chunked"])
+def test_fixed_cross_entropy_trains(tmp_path, head):
+    """loss.ce_form "fixed" through the trainer: the first loss equals the standard form's (the two differ only where a row
+    has collapsed), training proceeds."""
+    cfg = tiny_train_config()
+    cfg.head_impl = head
+    a = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    cfg.loss.ce_form = "fixed"
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    la, lb = a.train_step()["loss"], b.train_step()["loss"]
+    assert abs(la - lb) < 1e-5 * abs(la)
+    for _ in range(4):
+        l1 = b.train_step()["loss"]
+    assert l1 < lb
