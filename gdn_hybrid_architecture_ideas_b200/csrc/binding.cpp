@@ -165,6 +165,22 @@ void depth_mix_multi_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& ds
                                  vu.data_ptr<float>(), du.data_ptr<float>(), src[0].numel() / d, d, sm_count(), stream()), "depth_mix_multi_bwd");
 }
 
+// ids: int64 [n, s] contiguous (all inside the table); table / grad: fp32 [V, d]; rows: fp32 [n, d].
+void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
+  const c10::cuda::CUDAGuard guard(table.device());
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.dim() == 2 && is_f32(table) && table.is_contiguous() && is_f32(out) && out.is_contiguous() &&
+              out.numel() == ids.size(0) * table.size(1), "embedding_fwd: layout");
+  check(ghb::embedding_fwd(reinterpret_cast<const long*>(ids.data_ptr<int64_t>()), table.data_ptr<float>(), out.data_ptr<float>(), ids.size(0), ids.size(1),
+                           table.size(1), sm_count(), stream()), "embedding_fwd");
+}
+void embedding_bwd(const Tensor& ids, const Tensor& g, Tensor& table_grad) {
+  const c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.dim() == 2 && is_f32(g) && g.is_contiguous() && is_f32(table_grad) &&
+              table_grad.is_contiguous() && g.numel() == ids.size(0) * table_grad.size(1), "embedding_bwd: layout");
+  check(ghb::embedding_bwd(reinterpret_cast<const long*>(ids.data_ptr<int64_t>()), g.data_ptr<float>(), table_grad.data_ptr<float>(), ids.size(0), ids.size(1),
+                           table_grad.size(1), sm_count(), stream()), "embedding_bwd");
+}
+
 void ce_grad(const Tensor& logits, const Tensor& targets, const Tensor& a, const Tensor& b, Tensor& grad, Tensor& ce, Tensor& lse, bool fixed) {
   const c10::cuda::CUDAGuard guard(logits.device());
   TORCH_CHECK(is_f32(logits) && logits.is_contiguous() && is_bf16(grad) && grad.is_contiguous() && targets.scalar_type() == torch::kInt64 &&
@@ -436,6 +452,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_multi_fwd", &depth_mix_multi_fwd);
   m.def("depth_mix_multi_bwd", &depth_mix_multi_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_bwd", &embedding_bwd);
   m.def("decode_attention", &decode_attention);
   m.def("comm_reduce", &comm_reduce);
   m.def("comm_update", &comm_update);

@@ -375,4 +375,51 @@ int cast_bf16(const float* x, void* y, long n, int sms, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// ================================================================================================ embedding
+// out[n] = mean over the s ids of row n of table[id] (s = 1: a plain gather; s > 1: token-superposition bags;
+// ced/model/control.py:436-455). Backward: table_grad[id] += g[n] / s for every id of the row, through vector
+// reductions in L2 (`red.global.add.v4.f32`): no sort and no (N, s, d) intermediate; the summation order is not fixed.
+// One warp per row, fp32 table and rows, d a multiple of 4.
+__global__ void embedding_fwd_kernel(const long* __restrict__ ids, const float* __restrict__ table, float* __restrict__ out, long n, int s, int d) {
+  const int lane = threadIdx.x & 31;
+  const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const float inv = 1.f / s;
+  for (long r = warp; r < n; r += nwarp) {
+    for (int c = lane * 4; c < d; c += 128) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int k = 0; k < s; ++k) {
+        const float4 v = *reinterpret_cast<const float4*>(table + ids[r * s + k] * d + c);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      if (s > 1) { acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv; }
+      *reinterpret_cast<float4*>(out + r * d + c) = acc;
+    }
+  }
+}
+__global__ void embedding_bwd_kernel(const long* __restrict__ ids, const float* __restrict__ g, float* __restrict__ table_grad, long n, int s, int d) {
+  const int lane = threadIdx.x & 31;
+  const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  const float inv = 1.f / s;
+  for (long r = warp; r < n; r += nwarp) {
+    for (int c = lane * 4; c < d; c += 128) {
+      float4 v = *reinterpret_cast<const float4*>(g + r * d + c);
+      if (s > 1) { v.x *= inv; v.y *= inv; v.z *= inv; v.w *= inv; }
+      for (int k = 0; k < s; ++k) {
+        float* dst = table_grad + ids[r * s + k] * d + c;
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+      }
+    }
+  }
+}
+int embedding_fwd(const long* ids, const float* table, float* out, long n, int s, int d, int sms, cudaStream_t st) {
+  if (d % 4 || s < 1) return 1;
+  embedding_fwd_kernel<<<sms * 8, 256, 0, st>>>(ids, table, out, n, s, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+int embedding_bwd(const long* ids, const float* g, float* table_grad, long n, int s, int d, int sms, cudaStream_t st) {
+  if (d % 4 || s < 1) return 1;
+  embedding_bwd_kernel<<<sms * 8, 256, 0, st>>>(ids, g, table_grad, n, s, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 }  // namespace ghb

@@ -194,6 +194,8 @@ def depth_mix_multi(sources, readers, eps):
 
 
 def embedding(tokens, weight):
+    if use_native(weight):
+        return _native().embedding(tokens, weight)
     return ref.embedding(tokens, weight)
 
 

@@ -446,6 +446,41 @@ def gdn_gates(a_lin, b_lin, A_log, dt_bias):
     return g, torch.sigmoid(b_lin.float())
 
 
+class _Embedding(torch.autograd.Function):
+    """Rows of the table (bags: the mean of their rows). The backward adds the row gradients into a zeroed table gradient
+    with vector reductions (or straight into the parameter's accumulation buffer when weight gradients accumulate there)."""
+
+    @staticmethod
+    def forward(ctx, tokens, weight):
+        ids = tokens.reshape(-1, tokens.shape[2] if tokens.dim() == 3 else 1).contiguous()
+        out = torch.empty(*tokens.shape[:2], weight.shape[1], dtype=torch.float32, device=weight.device)
+        ext().embedding_fwd(ids, weight.detach().contiguous(), out)
+        _count()
+        ctx.save_for_backward(ids)
+        ctx.weight = weight
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (ids,) = ctx.saved_tensors
+        w = ctx.weight
+        main = getattr(w, "main_grad", None) if WGRAD_INTO_MAIN else None
+        if main is not None and main.dtype == torch.float32 and main.shape == w.shape and main.is_contiguous():
+            ext().embedding_bwd(ids, g.contiguous().float(), main)
+            _count()
+            return None, None
+        dw = torch.zeros_like(w, dtype=torch.float32)
+        ext().embedding_bwd(ids, g.contiguous().float(), dw)
+        _count()
+        return None, dw.to(w.dtype)
+
+
+def embedding(tokens, weight):
+    if weight.dtype != torch.float32 or weight.shape[1] % 4 or tokens.dim() not in (2, 3) or torch.are_deterministic_algorithms_enabled():
+        return ref.embedding(tokens, weight)
+    return _Embedding.apply(tokens, weight)
+
+
 # ------------------------------------------------------------------------------------------------------------ depth mix
 
 class _DepthMix(torch.autograd.Function):

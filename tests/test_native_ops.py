@@ -567,3 +567,24 @@ def test_ce_grad_fixed_form(s, V):
     native.ext().ce_grad(logits, t, a, b0, grad, ce, lse, False)
     if s == 1:
         assert abs(grad[0, t[0, 0]].float().item()) < 1e-6      # the standard form's softmax_t - 1 has rounded away (to a few fp32 ulps of a)
+
+
+@pytest.mark.parametrize("s", [1, 4])
+def test_embedding_kernels(s):
+    """Gather (bags: mean of the rows) and the scatter-add backward against torch."""
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    torch.manual_seed(s)
+    V, d, B, L = 1000, 1024, 3, 257
+    w = torch.randn(V, d, device=_dev(), requires_grad=True)
+    tok = torch.randint(0, V, (B, L) if s == 1 else (B, L, s), device=_dev())
+    tok[0, :5] = 7                       # repeated ids: their gradients add up
+    out = native.embedding(tok, w)
+    wr = w.detach().clone().requires_grad_()
+    want = ref.embedding(tok, wr)
+    _close(out, want, 1e-6, 1e-6, "rows")
+    g = torch.randn_like(want)
+    out.backward(g)
+    want.backward(g)
+    native.check_status()
+    _close(w.grad, wr.grad, 1e-5, 1e-5, "table gradient")
