@@ -2,7 +2,10 @@
 """Long-context bits per byte by position bucket, and GDN state diagnostics along the row
 (reference: scripts/eval_long.py).
 
-    python scripts/eval_long.py --checkpoint RUN --docs long.pt --max-len 65536 [--gdn-diag] [--out long.json]
+    python scripts/eval_long.py --checkpoint RUN --docs long.pt --max-len 65536 [--gdn-diag] [--window 8192] [--out long.json] [--summary long.md]
+
+--window W adds, per position bucket beyond W, the bpb of the bucket's targets with the full context minus the same targets
+scored with only the last W tokens of context, and the degradation rule over it (eval/long_report.py).
 
 `long.pt` holds {"docs": [{"ids": LongTensor, "byte_lens": LongTensor}, ...]}.
 """
@@ -18,7 +21,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from gdn_hybrid_architecture_ideas_b200.eval import gdn_diag, long_context  # noqa: E402
+from gdn_hybrid_architecture_ideas_b200.eval import gdn_diag, long_context, long_report  # noqa: E402
 from gdn_hybrid_architecture_ideas_b200.train import checkpoint as ckpt  # noqa: E402
 
 
@@ -30,6 +33,9 @@ def main(argv=None) -> int:
     ap.add_argument("--base", type=int, default=long_context.BASE_LEN)
     ap.add_argument("--chunk", type=int, default=8192)
     ap.add_argument("--gdn-diag", action="store_true")
+    ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--train-len", type=int, default=0, help="degradations are listed beyond this length (default: the run's seq_len)")
+    ap.add_argument("--summary")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--out")
     a = ap.parse_args(argv)
@@ -45,6 +51,17 @@ def main(argv=None) -> int:
     if a.gdn_diag:
         ids = docs[0]["ids"][: a.max_len or None][None]
         out["gdn_diag"] = gdn_diag.encoder_gdn_diag(model, ids, torch.zeros_like(ids), block=a.chunk, autocast_dtype=ac)
+    if a.window:
+        rows = long_report.context_gain(model, docs if not a.max_len else [{k: v[:a.max_len] for k, v in d.items()} for d in docs], res["edges"], a.window,
+                                        a.chunk, ac, full_records=res["records"])
+        summary = {"bpb": {"docs": rows}}
+        entries = long_report.degradations(summary, train_len=a.train_len or cfg.data.seq_len)
+        out["context_gain"], out["degradations"], out["breaks_first"] = rows, entries, long_report.breaks_first(entries)
+        text = long_report.render(summary, entries)
+        print(text)
+        if a.summary:
+            with open(a.summary, "w") as f:
+                f.write(text)
     if a.out:
         with open(a.out, "w") as f:
             json.dump(out, f, indent=1)

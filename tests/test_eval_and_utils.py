@@ -285,8 +285,10 @@ def test_eval_scripts_run_on_a_checkpoint(tmp_path):
         "--out", str(tmp_path / "p.json"))
     assert len(json.loads((tmp_path / "p.json").read_text())["probes"]) == 4
     run(str(root / "scripts/eval_long.py"), "--checkpoint", str(tmp_path / "run"), "--docs", str(tmp_path / "long.pt"), "--base", "16",
-        "--chunk", "16", "--gdn-diag", "--device", "cpu", "--out", str(tmp_path / "l.json"))
-    assert json.loads((tmp_path / "l.json").read_text())["gdn_diag"]
+        "--chunk", "16", "--gdn-diag", "--window", "16", "--train-len", "16", "--summary", str(tmp_path / "l.md"), "--device", "cpu",
+        "--out", str(tmp_path / "l.json"))
+    long = json.loads((tmp_path / "l.json").read_text())
+    assert long["gdn_diag"] and long["context_gain"] and "breaks_first" in long and "difference" in (tmp_path / "l.md").read_text()
 
 
 def test_build_eval_set_script(tmp_path):
@@ -480,3 +482,36 @@ def test_tst_diagnostics():
     assert abs(TD.bag_norm_eps_change(np.array([1.0]), 4, 1e-6)[0] - (math.sqrt((1 + 1e-6) / (1 + 0.25e-6)) - 1)) < 1e-15
     d = byte_tokenize("aé")
     assert d.ids == [97, 195, 169] and d.byte_lens == [1, 1, 1]
+
+
+def test_long_report_context_gain_and_rule():
+    """Context gain: the same targets with the full context and with a short one (a model that ignores everything beyond
+    the window scores them equally); the degradation rule and what breaks first."""
+    import torch
+
+    from gdn_hybrid_architecture_ideas_b200 import config as C
+    from gdn_hybrid_architecture_ideas_b200.eval import long_context as LC, long_report as LR
+    from tests.helpers import make_model
+
+    model = make_model(C.tiny_control_config(), dtype=torch.float32).eval()
+    g = torch.Generator().manual_seed(0)
+    docs = [{"ids": torch.randint(0, 256, (n,), generator=g), "byte_lens": torch.randint(1, 4, (n,), generator=g)} for n in (96, 130, 70)]
+    edges = (0, 32, 64, 128, 256)
+    res = LC.score_position_bpb(model, docs, edges=edges, chunk=64)
+    rows = LR.context_gain(model, docs, edges, window=32, chunk=64, full_records=res["records"])
+    assert [r["bucket"] for r in rows] == LC.bucket_names(edges)[2:5] and [r["docs"] for r in rows] == [3, 3, 1]
+    again = LR.context_gain(model, docs, edges, window=32, chunk=64)
+    assert all(abs(a["full"] - b["full"]) < 1e-5 for a, b in zip(rows, again))
+    assert all(abs(r["full"] - r["short"] - r["diff"]) < 1e-9 for r in rows)
+    summary = {"bpb": {"web": [{"bucket": "16k", "length": 16384, "full": 0.70, "short": 0.71, "diff": -0.01, "se": 0.002, "docs": 9},
+                               {"bucket": "32k", "length": 32768, "full": 0.74, "short": 0.71, "diff": 0.03, "se": 0.004, "docs": 9},
+                               {"bucket": "64k", "length": 65536, "full": 0.73, "short": 0.71, "diff": 0.02, "se": 0.02, "docs": 2}]},
+               "gdn": LR.gdn_factors({"edges": [0, 8192, 16384, 32768], "layers": [{"norm": [1.0, 1.2, 2.0], "erank": [4.0, 4.0, 3.0], "rel_delta": [0.1, 0.1, 0.1]},
+                                                                                {"norm": [2.0, 2.0, 2.2], "erank": [4.0, 5.0, 4.0], "rel_delta": None}]})}
+    entries = LR.degradations(summary, train_len=8192)
+    by = {(e["metric"], e["length"]): e for e in entries}
+    assert not by[("bpb.web", 16384)]["degraded"] and by[("bpb.web", 32768)]["clear"] and by[("bpb.web", 65536)]["degraded"] and not by[("bpb.web", 65536)]["clear"]
+    assert by[("gdn.norm", 32768)]["value"] == 2.0 and by[("gdn.norm", 32768)]["clear"] and not by[("gdn.erank", 16384)]["degraded"]
+    assert LR.breaks_first(entries) == {"length": 32768, "metrics": ["bpb.web", "gdn.norm"]}
+    text = LR.render(summary, entries)
+    assert "Breaks first at 32768" in text and "| 32k | 0.7400 | 0.7100 | +0.0300 +- 0.0040 | 9 |" in text
