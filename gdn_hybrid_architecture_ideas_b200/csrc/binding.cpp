@@ -165,6 +165,13 @@ void depth_mix_multi_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& ds
                                  vu.data_ptr<float>(), du.data_ptr<float>(), src[0].numel() / d, d, sm_count(), stream()), "depth_mix_multi_bwd");
 }
 
+// x: [rows, n] fp32 or bf16 contiguous; out: bf16 like x; blocks of 32 along the last dimension, or along rows.
+void mx_fake(const Tensor& x, Tensor& out, bool along_rows) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && (is_f32(x) || is_bf16(x)) && is_bf16(out) && out.is_contiguous() && out.sizes() == x.sizes(), "mx_fake: layout");
+  check(ghb::mx_fake(x.data_ptr(), is_bf16(x), out.data_ptr(), x.size(0), x.size(1), along_rows, sm_count(), stream()), "mx_fake");
+}
+
 // ids: int64 [n, s] contiguous (all inside the table); table / grad: fp32 [V, d]; rows: fp32 [n, d].
 void embedding_fwd(const Tensor& ids, const Tensor& table, Tensor& out) {
   const c10::cuda::CUDAGuard guard(table.device());
@@ -452,6 +459,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_multi_fwd", &depth_mix_multi_fwd);
   m.def("depth_mix_multi_bwd", &depth_mix_multi_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("mx_fake", &mx_fake);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("decode_attention", &decode_attention);

@@ -5,6 +5,7 @@
 // ced/train/muon.py:112-128 (AdamW branch). The reference leaves these to Inductor-fused elementwise graphs.
 #include "kernels.h"
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 namespace ghb {
 
@@ -419,6 +420,78 @@ int embedding_fwd(const long* ids, const float* table, float* out, long n, int s
 int embedding_bwd(const long* ids, const float* g, float* table_grad, long n, int s, int d, int sms, cudaStream_t st) {
   if (d % 4 || s < 1) return 1;
   embedding_bwd_kernel<<<sms * 8, 256, 0, st>>>(ids, g, table_grad, n, s, d);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// ================================================================================================ MXFP8 fake quantisation
+// Blocks of 32 along one dimension of a [rows, n] matrix: E8M0 exponent of amax / 448 rounded up to a power of two, elements
+// scaled, clamped to +-448 and rounded to E4M3 (nearest even), then multiplied back: the values a block-scaled GEMM
+// would see, written as bf16 (exact: 3 mantissa bits times a power of two). A block with a non-finite element becomes NaN
+// with exponent code 255; a NaN does not count toward amax (ced/model/mxfp8.py:86-188). One read of the input.
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float wmax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ int mx_exponent(float amax) {
+  const int bits = __float_as_int(amax * (1.0f / 448.0f));
+  const int e = (bits >> 23) & 0xFF, m = bits & 0x7FFFFF;
+  if (e == 255) return m == 0 ? 254 : 255;
+  const bool bump = m > 0 && e != 254 && (e != 0 || m > 0x400000);
+  return e + (bump ? 1 : 0);
+}
+__device__ __forceinline__ float mx_round_trip(float x, int b, bool bad) {
+  if (bad) return __int_as_float(0x7FFFFFFF);
+  const float inv = __int_as_float(b == 254 ? 0x00400000 : (254 - b) << 23);
+  const float scale = __int_as_float(b == 0 ? 0x00400000 : b << 23);
+  const float y = fminf(fmaxf(x * inv, -448.f), 448.f);
+  const __nv_fp8_storage_t q = __nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3);
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(q, __NV_E4M3))) * scale;
+}
+template <typename T>
+__global__ void mx_fake_last_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out, long rows, long n) {
+  const int lane = threadIdx.x & 31;
+  const long per_row = (n + 31) / 32, blocks = rows * per_row;
+  const long warp = (static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5, nwarp = (static_cast<long>(gridDim.x) * blockDim.x) >> 5;
+  for (long blk = warp; blk < blocks; blk += nwarp) {
+    const long r = blk / per_row, c = (blk % per_row) * 32 + lane;
+    const bool in = c < n;
+    const float v = in ? to_float(x[r * n + c]) : 0.f;
+    const bool fin = isfinite(v);
+    const float amax = wmax(isnan(v) ? 0.f : fabsf(v));
+    const bool bad = __any_sync(0xffffffffu, !fin);
+    const int b = mx_exponent(amax);
+    if (in) out[r * n + c] = __float2bfloat16(mx_round_trip(v, b, bad));
+  }
+}
+// Blocks of 32 consecutive rows of one column; a thread owns a column of a row block, threads run along the columns.
+template <typename T>
+__global__ void mx_fake_first_kernel(const T* __restrict__ x, __nv_bfloat16* __restrict__ out, long rows, long n) {
+  const long row_blocks = (rows + 31) / 32, units = row_blocks * n;
+  for (long u = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; u < units; u += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long rb = u / n, c = u % n;
+    const long r0 = rb * 32, r1 = min(rows, r0 + 32);
+    float amax = 0.f; bool bad = false;
+    for (long r = r0; r < r1; ++r) {
+      const float v = to_float(x[r * n + c]);
+      bad |= !isfinite(v);
+      amax = fmaxf(amax, isnan(v) ? 0.f : fabsf(v));
+    }
+    const int b = mx_exponent(amax);
+    for (long r = r0; r < r1; ++r) out[r * n + c] = __float2bfloat16(mx_round_trip(to_float(x[r * n + c]), b, bad));
+  }
+}
+int mx_fake(const void* x, bool x_bf16, void* out, long rows, long n, bool along_rows, int sms, cudaStream_t st) {
+  auto* o = static_cast<__nv_bfloat16*>(out);
+  if (along_rows) {
+    if (x_bf16) mx_fake_first_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), o, rows, n);
+    else mx_fake_first_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const float*>(x), o, rows, n);
+  } else {
+    if (x_bf16) mx_fake_last_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), o, rows, n);
+    else mx_fake_last_kernel<<<sms * 8, 256, 0, st>>>(static_cast<const float*>(x), o, rows, n);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -83,6 +83,18 @@ def mx_dequantize(q: torch.Tensor, b: torch.Tensor, dim: int = -1, dtype=torch.f
 
 
 def mx_fake(t: torch.Tensor, dim: int = -1, dtype=torch.float32) -> torch.Tensor:
+    """Quantise to MXFP8 along `dim` and multiply back. A 2-D CUDA tensor goes through one kernel that reads the input once
+    and writes the values as bfloat16 (exact for E4M3 times a power of two); everything else through the tensor ops."""
+    if t.is_cuda and t.dim() == 2 and t.dtype in (torch.float32, torch.bfloat16) and t.is_contiguous() and dim in (-1, 0, 1):
+        from . import use_native
+
+        if use_native(t):
+            from . import native
+
+            out = torch.empty(t.shape, dtype=torch.bfloat16, device=t.device)
+            native.ext().mx_fake(t.detach(), out, dim == 0)
+            native._count()
+            return out
     q, b = mx_quantize(t, dim)
     return mx_dequantize(q, b, dim, dtype)
 

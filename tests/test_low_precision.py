@@ -90,3 +90,32 @@ def test_quantised_model_trains_and_evaluates_in_high_precision(which):
     assert torch.isfinite(a).all() and rel < (0.6 if which == "mxfp8" else 1.5), rel
     a.logsumexp(-1).sum().backward()
     assert all(torch.isfinite(p.grad).all() for p in m.parameters() if p.grad is not None)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim", [-1, 0])
+def test_mxfp8_kernel_equals_emulation(dtype, dim):
+    """The MXFP8 round-trip kernel gives, value for value, what the tensor-op emulation gives (which equals the reference byte
+    for byte): ragged block counts, zero blocks, tiny and huge magnitudes, blocks holding inf or NaN."""
+    from gdn_hybrid_architecture_ideas_b200 import ops
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(203, 150, generator=g) * torch.exp(torch.randn(203, 150, generator=g) * 4)
+    x[5, :40] = 0.0
+    x[:40, 7] = 0.0
+    x[9, 3] = 3e38
+    x[10, 100] = 1e-41
+    x[11, 64] = float("inf")
+    x[100, 11] = float("nan")
+    x = x.to("cuda").to(dtype).contiguous()
+    got = lowp.mx_fake(x, dim)
+    ops.set_mode("reference")
+    try:
+        want = lowp.mx_fake(x, dim)
+    finally:
+        ops.set_mode("native")
+    assert got.dtype == torch.bfloat16 and want.dtype == torch.float32
+    same = (got.float() == want) | (torch.isnan(got.float()) & torch.isnan(want))
+    assert bool(same.all()), f"{int((~same).sum())} values differ; first at {torch.nonzero(~same)[0].tolist()}"
+    assert bool(torch.isnan(want).any()) and bool((want == 0).any())
