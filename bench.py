@@ -293,7 +293,7 @@ def reference_config(args, world: int, micro: int) -> dict:
 def run_reference(args) -> dict:
     ref = ROOT / "baseline" / "_ref"
     if not (ref / "ced").is_dir():
-        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --target baseline/_ref /root/reference/code)"}
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref <reference checkout>/code)"}
     sys.path.insert(0, str(ref))
     try:
         import torch
