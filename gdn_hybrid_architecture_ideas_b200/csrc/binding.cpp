@@ -165,6 +165,19 @@ void depth_mix_multi_bwd(const std::vector<Tensor>& src, std::vector<Tensor>& ds
                                  vu.data_ptr<float>(), du.data_ptr<float>(), src[0].numel() / d, d, sm_count(), stream()), "depth_mix_multi_bwd");
 }
 
+// One decode token of the gated delta rule, in place on S [B, Hv, 128, dv] fp32. q, k [B, Hk, 128]; v, o [B, Hv, dv]; g, beta [B, Hv]
+// (all fp32, contiguous); start: optional bool [B] (document start: the state is dropped first).
+void gdn_step(Tensor& S, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, const c10::optional<Tensor>& start, Tensor& o) {
+  const c10::cuda::CUDAGuard guard(S.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&S, &q, &k, &v, &g, &beta, &o}) TORCH_CHECK(is_f32(*t) && t->is_contiguous(), "gdn_step: fp32 contiguous tensors");
+  TORCH_CHECK(S.dim() == 4 && q.dim() == 3 && v.dim() == 3 && q.sizes() == k.sizes() && o.sizes() == v.sizes() && S.size(0) == q.size(0) && S.size(1) == v.size(1) &&
+              S.size(2) == q.size(2) && S.size(3) == v.size(2) && g.numel() == S.size(0) * S.size(1) && beta.numel() == g.numel(), "gdn_step: shapes");
+  const unsigned char* sp = nullptr;
+  if (start.has_value()) { TORCH_CHECK(start->scalar_type() == at::kBool && start->is_contiguous() && start->numel() == S.size(0), "gdn_step: start"); sp = reinterpret_cast<const unsigned char*>(start->data_ptr<bool>()); }
+  check(ghb::gdn_step(S.data_ptr<float>(), q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(), beta.data_ptr<float>(), sp,
+                      o.data_ptr<float>(), S.size(0), q.size(1), S.size(1), S.size(2), S.size(3), stream()), "gdn_step");
+}
+
 // x: [rows, n] fp32 or bf16 contiguous; out: bf16 like x; blocks of 32 along the last dimension, or along rows.
 void mx_fake(const Tensor& x, Tensor& out, bool along_rows) {
   const c10::cuda::CUDAGuard guard(x.device());
@@ -459,6 +472,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depth_mix_multi_fwd", &depth_mix_multi_fwd);
   m.def("depth_mix_multi_bwd", &depth_mix_multi_bwd);
   m.def("ce_grad", &ce_grad);
+  m.def("gdn_step", &gdn_step);
   m.def("mx_fake", &mx_fake);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);

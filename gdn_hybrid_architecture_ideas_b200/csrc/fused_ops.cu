@@ -1100,4 +1100,55 @@ int gate_out_bwd(const void* dy, const void* o, const void* qg, void* dO, void* 
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// ================================================================================================ GDN decode step
+// One token of the gated delta rule per (row, value head), in place on the fp32 state S [B, Hv, 128, dv]:
+//   S <- 0 at a document start;  S <- S e^g;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// (ced/model/gdn.py:1153-1189 per token). A thread owns one column of S in registers, so the state is read once and
+// written once (the tensor-op form makes five passes over it). q, k: [B, Hk, 128] fp32; v, o: [B, Hv, dv] fp32; g, beta:
+// [B, Hv]; value head j reads key head j / (Hv / Hk). Grid (dv / 128, Hv, B), 256 threads (two per column).
+__global__ void __launch_bounds__(256) gdn_step_kernel(float* __restrict__ S, const float* __restrict__ q, const float* __restrict__ k,
+                                                       const float* __restrict__ v, const float* __restrict__ g, const float* __restrict__ beta,
+                                                       const unsigned char* __restrict__ start, float* __restrict__ o, int Hk, int Hv, int dv) {
+  constexpr int DK = 128, HALF = 64;          // threads 0-127 hold rows 0-63 of their column, threads 128-255 rows 64-127
+  __shared__ float sq[DK], sk[DK], part[2][128];
+  const int b = blockIdx.z, hv = blockIdx.y, c = threadIdx.x & 127, half = threadIdx.x >> 7, col = blockIdx.x * 128 + c;
+  const int hk = hv / (Hv / Hk);
+  if (threadIdx.x < DK) sq[threadIdx.x] = q[(static_cast<long>(b) * Hk + hk) * DK + threadIdx.x];
+  else sk[threadIdx.x - DK] = k[(static_cast<long>(b) * Hk + hk) * DK + threadIdx.x - DK];
+  __syncthreads();
+  const long bh = static_cast<long>(b) * Hv + hv;
+  float* Sp = S + bh * DK * dv + static_cast<long>(half) * HALF * dv + col;
+  const float* kk = sk + half * HALF;
+  const float* qq = sq + half * HALF;
+  const bool fresh = start != nullptr && start[b] != 0;
+  const float decay = __expf(g[bh]);
+  float s[HALF];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) {
+    s[i] = fresh ? 0.f : Sp[static_cast<long>(i) * dv] * decay;
+    dot += s[i] * kk[i];
+  }
+  part[half][c] = dot;
+  __syncthreads();
+  const float u = beta[bh] * (v[bh * dv + col] - (part[0][c] + part[1][c]));
+  float out = 0.f;
+#pragma unroll
+  for (int i = 0; i < HALF; ++i) {
+    s[i] += kk[i] * u;
+    out += s[i] * qq[i];
+    Sp[static_cast<long>(i) * dv] = s[i];
+  }
+  __syncthreads();
+  part[half][c] = out;
+  __syncthreads();
+  if (half == 0) o[bh * dv + col] = part[0][c] + part[1][c];
+}
+int gdn_step(float* S, const float* q, const float* k, const float* v, const float* g, const float* beta, const unsigned char* start, float* o,
+             int B, int Hk, int Hv, int dk, int dv, cudaStream_t st) {
+  if (dk != 128 || dv % 128 || Hv % Hk) return 1;
+  gdn_step_kernel<<<dim3(dv / 128, Hv, B), 256, 0, st>>>(S, q, k, v, g, beta, start, o, Hk, Hv, dv);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 }  // namespace ghb

@@ -41,6 +41,8 @@ int depth_mix_fwd(const float* const* src, int n, const float* ueff, float* out,
                   cudaStream_t st);
 int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const float* ueff, const float* dh, const float* alpha,
                   const float* rnorm, float* du, long rows, int d, int sms, cudaStream_t st);
+int gdn_step(float* S, const float* q, const float* k, const float* v, const float* g, const float* beta, const unsigned char* start, float* o,
+             int B, int Hk, int Hv, int dk, int dv, cudaStream_t st);
 int mx_fake(const void* x, bool x_bf16, void* out, long rows, long n, bool along_rows, int sms, cudaStream_t st);
 int embedding_fwd(const long* ids, const float* table, float* out, long n, int s, int d, int sms, cudaStream_t st);
 int embedding_bwd(const long* ids, const float* g, float* table_grad, long n, int s, int d, int sms, cudaStream_t st);

@@ -178,6 +178,7 @@ class DecodeEngine:
         pos = (self.lens - self.doc_start).long()
         idx = self.lens.long()[:, None]
         ctx = SeqContext(idx=idx, doc=self.doc_id[:, None], pos=pos[:, None], is_doc_start=torch.zeros(B, 1, dtype=torch.bool, device=self.device))
+        ctx.memo["inplace_state"] = True       # the GDN step kernel updates this engine's static state buffers in place
         x = model.embed_tokens(self.tokens[:, None])
         S = enc.block
         sources = [x]
@@ -200,7 +201,8 @@ class DecodeEngine:
                     kw = dict(arms=arms, x_write=xw, x_read=xr)
                 state = GDNState(conv_input=st["conv"], conv_doc=st["conv_doc"], S=st["S"])
                 mixed, new = layer.mixer(h, ctx, state, **kw)
-                st["S"].copy_(new.S)
+                if new.S is not st["S"]:          # the step kernel updated the buffer in place
+                    st["S"].copy_(new.S)
                 st["conv"].copy_(new.conv_input.to(st["conv"].dtype))
                 st["conv_doc"].copy_(new.conv_doc)
             else:

@@ -155,7 +155,7 @@ class GatedDeltaNet(nn.Module):
         S0 = None if state is None else state.S
         kernel = "recurrence" if cfg.kernel == "recurrence" else "chunked"
         o, S = ops.delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, ctx.is_doc_start, S0, kernel=kernel,
-                                     chunk_size=cfg.chunk_size, need_state=need_state)
+                                     chunk_size=cfg.chunk_size, need_state=need_state, inplace_state=bool(ctx.memo.get("inplace_state")))
         z = self.in_proj_z(x).view(B, L, hv, dv)
         y = self.out_proj(self.norm(o, z).flatten(2))
         return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)

@@ -117,10 +117,15 @@ def gdn_gates(a_lin, b_lin, A_log, dt_bias, scale=1, beta_power=False):
     return ref.gdn_gates(a_lin, b_lin, A_log, dt_bias, scale, beta_power)
 
 
-def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=64, need_state=True):
-    """(o, S_final). q,k (B,L,Hk,dk) with Hv a multiple of Hk: value head j reads key head j // (Hv/Hk)."""
+def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=64, need_state=True, inplace_state=False):
+    """(o, S_final). q,k (B,L,Hk,dk) with Hv a multiple of Hk: value head j reads key head j // (Hv/Hk).
+    inplace_state: a single cached token may update S0 in place and return it (the decode engine's static buffers)."""
     if use_native(q) and q.shape[1] > 1:
         return _native().delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state)
+    if use_native(q):
+        from . import gdn_native
+        if gdn_native.step_ok(q, v, S0):
+            return gdn_native.delta_rule_step(q, k, v, g, beta, is_doc_start, S0, inplace_state)
     rep = v.shape[2] // q.shape[2]
     if rep > 1:
         q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
@@ -140,7 +145,7 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=
     return ref.chunked_delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size)
 
 
-def delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=64, need_state=True):
+def delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, kernel="chunked", chunk_size=64, need_state=True, inplace_state=False):
     """`delta_rule` on the packed [q | k | v] tensor of `gdn_prep(packed=True)`: on the CUDA kernels the whole rule is
     one autograd node whose gradient returns packed the same way."""
     B, L, _ = qkv.shape
@@ -150,7 +155,7 @@ def delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, kernel="ch
             return _native().delta_rule_packed(qkv, hk, hv, dk, dv, g, beta, is_doc_start, S0, need_state)
     nq = hk * dk
     q, k, v = qkv[..., :nq].view(B, L, hk, dk), qkv[..., nq:2 * nq].view(B, L, hk, dk), qkv[..., 2 * nq:].view(B, L, hv, dv)
-    return delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel=kernel, chunk_size=chunk_size, need_state=need_state)
+    return delta_rule(q, k, v, g, beta, is_doc_start, S0, kernel=kernel, chunk_size=chunk_size, need_state=need_state, inplace_state=inplace_state)
 
 
 def attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, q_far=None, k_far=None, cap=None, self_aligned=False, q_pos=None,

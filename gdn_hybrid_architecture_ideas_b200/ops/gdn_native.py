@@ -136,3 +136,22 @@ def delta_rule(q, k, v, g, beta, is_doc_start, S0, chunk_size, need_state):
     qkv = torch.cat([native._bf16(t).flatten(2) for t in (q, k, v)], dim=-1)
     O, S = delta_rule_packed(qkv, Hk, Hv, dk, dv, g, beta, is_doc_start, S0, need_state)
     return (O[:, :L] if pad else O), S
+
+
+def step_ok(q, v, S0) -> bool:
+    """One cached token on the fused step kernel: key dim 128, value dim a multiple of 128, an fp32 state, no autograd."""
+    return (q.shape[1] == 1 and S0 is not None and S0.dtype == torch.float32 and q.shape[-1] == 128 and v.shape[-1] % 128 == 0
+            and not (torch.is_grad_enabled() and any(t.requires_grad for t in (q, v, S0))))
+
+
+def delta_rule_step(q, k, v, g, beta, is_doc_start, S0, inplace: bool = False):
+    """(o [B, 1, Hv, dv], S): one token of the rule per row through `gdn_step_kernel`, which reads and writes the state
+    once. inplace: S0 itself is updated and returned (the decode engine's static state buffer); otherwise a copy is."""
+    B = q.shape[0]
+    f = lambda t: t.reshape(B, *t.shape[2:]).float().contiguous()
+    S = S0 if (inplace and S0.is_contiguous()) else S0.clone(memory_format=torch.contiguous_format)
+    o = torch.empty(B, v.shape[2], v.shape[3], dtype=torch.float32, device=v.device)
+    start = None if is_doc_start is None else is_doc_start.reshape(B).to(torch.bool).contiguous()
+    native.ext().gdn_step(S, f(q), f(k), f(v), f(g), f(beta), start, o)
+    native._count()
+    return o.view(B, 1, *o.shape[1:]).to(v.dtype), S

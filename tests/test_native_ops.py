@@ -588,3 +588,37 @@ def test_embedding_kernels(s):
     want.backward(g)
     native.check_status()
     _close(w.grad, wr.grad, 1e-5, 1e-5, "table gradient")
+
+
+@pytest.mark.parametrize("Hk,Hv,dv", [(2, 2, 128), (2, 4, 256)])
+def test_gdn_decode_step_kernel(Hk, Hv, dv):
+    """One cached token of the gated delta rule on the in-place step kernel against the per-token recurrence, over a few
+    steps, with a row that starts a new document."""
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    torch.manual_seed(Hv)
+    B, dk = 5, 128
+    S = torch.randn(B, Hv, dk, dv, device=_dev()) * 0.1
+    Sr = S.clone()
+    buf = S
+    for step in range(3):
+        q = torch.nn.functional.normalize(torch.randn(B, 1, Hk, dk, device=_dev()), dim=-1) * dk ** -0.5
+        k = torch.nn.functional.normalize(torch.randn(B, 1, Hk, dk, device=_dev()), dim=-1)
+        v = torch.randn(B, 1, Hv, dv, device=_dev())
+        g = -torch.rand(B, 1, Hv, device=_dev())
+        beta = torch.rand(B, 1, Hv, device=_dev()) * 2
+        start = torch.zeros(B, 1, dtype=torch.bool, device=_dev())
+        start[1, 0] = step == 1
+        with torch.no_grad():
+            o, S = ops.delta_rule(q.bfloat16(), k.bfloat16(), v.bfloat16(), g, beta, start, S, inplace_state=True)
+            rep = Hv // Hk
+            qr, kr = (t.bfloat16().float().repeat_interleave(rep, dim=2) for t in (q, k))
+            orf, Sr = ref.delta_rule_recurrence(qr, kr, v.bfloat16().float(), g, beta, start, Sr)
+        native.check_status()
+        assert S is buf                      # updated in place
+        _close(o, orf, 2e-2, 2e-2, f"o at step {step}")
+        _close(S, Sr, 1e-5, 1e-5, f"S at step {step}")
+    with torch.no_grad():
+        o2, S2 = ops.delta_rule(q.bfloat16(), k.bfloat16(), v.bfloat16(), g, beta, start, S)
+    assert S2 is not S
