@@ -105,6 +105,8 @@ def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist=None, hist_doc=None, 
     layout `delta_rule_packed` reads."""
     if use_native(u_pre) and hist is None:
         return _native().gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc, packed)
+    if use_native(u_pre) and u_pre.dtype == torch.bfloat16:
+        return _native().gdn_prep_cached(u_pre, doc, conv_weight, hk, hv, dk, dv, hist, hist_doc, packed)
     q, k, v, h, hd = ref.gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, hist, hist_doc)
     if packed:
         return torch.cat([q.flatten(2), k.flatten(2), v.flatten(2)], dim=-1), h, hd

@@ -440,6 +440,18 @@ def gdn_prep(u_pre, doc, conv_weight, hk, hv, dk, dv, single_doc=False, packed=F
     return q, k, v, u_pre[:, L - (K - 1):], doc[:, L - (K - 1):]
 
 
+def gdn_prep_cached(u_pre, doc, conv_weight, hk, hv, dk, dv, hist, hist_doc, packed=False):
+    """`gdn_prep` of a chunk that continues cached rows: the K - 1 cached inputs (and their document ids; -1 where there is
+    none) are placed in front of the chunk, the same kernel runs over the longer rows and the first K - 1 outputs are
+    dropped. The document mask keeps taps of other documents (and of the empty history) out."""
+    K = conv_weight.shape[1]
+    full = torch.cat([hist.to(u_pre.dtype), u_pre], dim=1)
+    full_doc = torch.cat([hist_doc, doc], dim=1)
+    out = gdn_prep(full, full_doc, conv_weight, hk, hv, dk, dv, False, packed)
+    head, (h, hd) = out[:-2], out[-2:]
+    return (*(t[:, K - 1:] for t in head), h, hd)
+
+
 def gdn_gates(a_lin, b_lin, A_log, dt_bias):
     """Tiny (B, L, Hv) elementwise maths in fp32; left to the framework's elementwise kernels."""
     g = -torch.exp(A_log) * torch.nn.functional.softplus(a_lin.float() + dt_bias)

@@ -622,3 +622,31 @@ def test_gdn_decode_step_kernel(Hk, Hv, dv):
     with torch.no_grad():
         o2, S2 = ops.delta_rule(q.bfloat16(), k.bfloat16(), v.bfloat16(), g, beta, start, S)
     assert S2 is not S
+
+
+@pytest.mark.parametrize("L", [1, 2, 70])
+def test_gdn_prep_with_history(L):
+    """A chunk that continues cached rows (K - 1 cached inputs with their document ids, -1 where none) on the prep kernel
+    against the PyTorch statement."""
+    from gdn_hybrid_architecture_ideas_b200 import ops
+    from gdn_hybrid_architecture_ideas_b200.ops import native, reference as ref
+
+    torch.manual_seed(L)
+    B, hk, hv, dk, dv = 3, 2, 2, 128, 256
+    C = 2 * hk * dk + hv * dv
+    u = torch.randn(B, L, C, device=_dev()).to(torch.bfloat16)
+    w = torch.randn(C, 4, device=_dev()) * 0.5
+    hist = torch.randn(B, 3, C, device=_dev()).to(torch.bfloat16)
+    hist_doc = torch.tensor([[5, 5, 5], [-1, -1, 4], [2, 3, 3]], device=_dev())
+    doc = torch.tensor([[5], [4], [4]], device=_dev()).expand(B, L).contiguous()
+    if L > 2:
+        doc = doc.clone()
+        doc[0, L // 2:] = 6
+    with torch.no_grad():
+        qkv, h, hd = ops.gdn_prep(u, doc, w, hk, hv, dk, dv, hist, hist_doc, packed=True)
+        q, k, v, hr, hdr = ref.gdn_prep(u.float(), doc, w, hk, hv, dk, dv, hist.float(), hist_doc)
+    native.check_status()
+    want = torch.cat([q.flatten(2), k.flatten(2), v.flatten(2)], dim=-1)
+    assert qkv.shape == want.shape
+    _close(qkv, want, 1e-2, 2e-2, "qkv")
+    assert torch.equal(hd, hdr) and torch.equal(h.float(), hr)
