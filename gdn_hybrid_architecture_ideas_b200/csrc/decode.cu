@@ -43,9 +43,16 @@ decode_attn_partial_kernel(DecodeArgs a) {
   const int lo = first + split * per, hi = min(len, lo + per);
   const int qpos = len - 1;
   const int half = a.rot / 2;
-  float m[G], l[G], o[G][2];
+  // P V: a lane holds 8 output dimensions (vc .. vc + 7) and every fourth key of a tile (vr, vr + 4, ...), so a tile's values
+  // arrive as 8 independent 16-byte loads per lane (4 key rows per warp instruction); the four lane groups meet at the end.
+  const int vr = lane >> 3, vc = (lane & 7) * 8;
+  float m[G], l[G], o[G][8];
 #pragma unroll
-  for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; o[g][0] = o[g][1] = 0.f; }
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[g][e] = 0.f;
+  }
   for (int t0 = lo + warp * DTILE; t0 < hi; t0 += DWARPS * DTILE) {
     const int t = t0 + lane;
     float logit[G];
@@ -97,25 +104,49 @@ decode_attn_partial_kernel(DecodeArgs a) {
       for (int s = 16; s > 0; s >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, s);
       const float alpha = (m[g] == -INFINITY) ? 0.f : __expf(m[g] - m_new);
       l[g] = l[g] * alpha + ps;
-      o[g][0] *= alpha; o[g][1] *= alpha;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[g][e] *= alpha;
       m[g] = m_new;
-      sp[warp][lane][g] = p;
+      sp[warp][lane][g] = p;          // 0 for the lanes past the end of the split
     }
     __syncwarp();
-    const int n = min(DTILE, hi - t0);
-    for (int j = 0; j < n; ++j) {
-      const __nv_bfloat162 vv = reinterpret_cast<const __nv_bfloat162*>(a.v + ((static_cast<long>(b) * a.T + t0 + j) * a.Hkv + hk) * DH)[lane];
-      const float v0 = __bfloat162float(vv.x), v1 = __bfloat162float(vv.y);
+    uint4 vv[DTILE / 4];
 #pragma unroll
-      for (int g = 0; g < G; ++g) { const float p = sp[warp][j][g]; o[g][0] += p * v0; o[g][1] += p * v1; }
+    for (int i = 0; i < DTILE / 4; ++i) {
+      const int j = 4 * i + vr;
+      vv[i] = (t0 + j < hi) ? *reinterpret_cast<const uint4*>(a.v + ((static_cast<long>(b) * a.T + t0 + j) * a.Hkv + hk) * DH + vc) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int i = 0; i < DTILE / 4; ++i) {
+      const int j = 4 * i + vr;
+      const uint32_t w[4] = {vv[i].x, vv[i].y, vv[i].z, vv[i].w};
+      float vf[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); vf[2 * e] = f.x; vf[2 * e + 1] = f.y; }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float p = sp[warp][j][g];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[g][e] += p * vf[e];
+      }
     }
     __syncwarp();
   }
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      o[g][e] += __shfl_xor_sync(0xffffffffu, o[g][e], 8);
+      o[g][e] += __shfl_xor_sync(0xffffffffu, o[g][e], 16);
+    }
   // merge the warps of this CTA, write the split's partial result
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
-    s_o[warp][g][2 * lane] = o[g][0]; s_o[warp][g][2 * lane + 1] = o[g][1];
+    if (vr == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s_o[warp][g][vc + e] = o[g][e];
+    }
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < G * DH; idx += blockDim.x) {
