@@ -28,7 +28,7 @@ struct DecodeArgs {
 };
 
 template <int G>
-__global__ void __launch_bounds__(DWARPS * 32)
+__global__ void __launch_bounds__(DWARPS * 32, G <= 4 ? 4 : 1)
 decode_attn_partial_kernel(DecodeArgs a) {
   __shared__ float sq[MAXG][DH];
   __shared__ float sp[DWARPS][DTILE][MAXG];
