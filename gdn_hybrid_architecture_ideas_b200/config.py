@@ -150,6 +150,33 @@ class _EncoderLayout:
                              f"global attention layers (0 .. {n - 1})")
         return idx
 
+    def gdn_shapes(self) -> list["GDNConfig"]:
+        """GDNConfig of every GDN layer, bottom first. `gdn_shape_by_layer` {GDN ordinal: [n_k_heads, n_v_heads, head_dim]}
+        gives a layer a copy of `gdn` with its own head counts and head size (key and value alike); without the table every
+        entry is `gdn` itself (reference: ced/config.py:741-770)."""
+        n = len(self.gdn_layers())
+        table = self.gdn_shape_by_layer
+        if not table:
+            return [self.gdn] * n
+        if not isinstance(table, dict):
+            raise ValueError(f"model.encoder.gdn_shape_by_layer {table!r}: a mapping {{GDN ordinal: [n_k_heads, n_v_heads, head_dim]}}")
+        bad = [k for k in table if type(k) is not int or not 0 <= k < n]
+        if bad:
+            raise ValueError(f"model.encoder.gdn_shape_by_layer keys {bad!r}: GDN ordinals among the encoder's {n} GDN layers (0 .. {n - 1})")
+        out = []
+        for i in range(n):
+            if i not in table:
+                out.append(self.gdn)
+                continue
+            shape = table[i]
+            if not (isinstance(shape, (list, tuple)) and len(shape) == 3 and all(type(v) is int and v >= 1 for v in shape)):
+                raise ValueError(f"model.encoder.gdn_shape_by_layer[{i}] {shape!r}: [n_k_heads, n_v_heads, head_dim], three integers >= 1")
+            hk, hv, hd = shape
+            if hv % hk:
+                raise ValueError(f"model.encoder.gdn_shape_by_layer[{i}] {list(shape)!r}: n_v_heads must be a multiple of n_k_heads")
+            out.append(dataclasses.replace(self.gdn, n_k_heads=hk, n_v_heads=hv, k_head_dim=hd, v_head_dim=hd))
+        return out
+
     def global_attention(self) -> list["AttentionConfig"]:
         """Attention config of each global layer, bottom first; a layer listed in nope_global_layers gets a copy with
         rope_fraction 0 and no distance cap (position-free attention)."""
@@ -653,7 +680,6 @@ _BUILT = {
     "model.encoder.gdn_qmix_select_step": (0,),
     "model.encoder.residual_dtype": ("float32", "bf16"),
     "model.encoder.gdn_ccr_spacing": (0,),
-    "model.encoder.gdn_shape_by_layer": ({},),
     "model.loop.pass2_gate": ("none",),
     "model.loop.recur_layers": ((),),
     "model.loop.segment_passes": (None,),

@@ -110,7 +110,7 @@ def canon_generator(seed: int, layer: int) -> torch.Generator:
 
 
 class EncoderLayer(nn.Module):
-    def __init__(self, kind: str, cfg: ModelConfig, scale: float, attention=None):
+    def __init__(self, kind: str, cfg: ModelConfig, scale: float, attention=None, gdn=None):
         super().__init__()
         d, eps, gain = cfg.d_model, cfg.norm_eps, cfg.encoder.block_norm_gain
         self.kind = kind
@@ -121,7 +121,7 @@ class EncoderLayer(nn.Module):
         self.mlp_in_norm = RMSNorm(d, eps, gain=gain)
         self.mlp_out_norm = RMSNorm(d, eps, gain=gain)
         if kind == "gdn":
-            self.mixer = GatedDeltaNet(d, cfg.encoder.gdn, eps, norm_gain=gain)
+            self.mixer = GatedDeltaNet(d, gdn or cfg.encoder.gdn, eps, norm_gain=gain)
         elif kind == "attention":
             self.mixer = GatedAttention(d, attention or cfg.encoder.attention, eps)
         else:
@@ -177,9 +177,13 @@ class Encoder(nn.Module):
         enc = cfg.encoder
         self.cfg = cfg
         scale = residual_scale(cfg)
-        per_global = iter(enc.global_attention())
+        if enc.gdn_shape_by_layer and enc.gdn_write_mix != "none":
+            raise ValueError("model.encoder.gdn_shape_by_layer is not built with model.encoder.gdn_write_mix "
+                             "(reference: ced/model/gdn_dprod_place.py:185-203)")
+        per_global, per_gdn = iter(enc.global_attention()), iter(enc.gdn_shapes())
         self.layers = nn.ModuleList(
-            EncoderLayer(kind, cfg, scale, attention=next(per_global) if kind == "attention" else None)
+            EncoderLayer(kind, cfg, scale, attention=next(per_global) if kind == "attention" else None,
+                         gdn=next(per_gdn) if kind == "gdn" else None)
             for kind in enc.layer_kinds())
         self.block = enc.full_attn_interval
         self.block_entry = enc.attn_res == "block_entry"

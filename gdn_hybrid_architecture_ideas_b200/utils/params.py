@@ -73,7 +73,7 @@ def flops_per_token(cfg: ModelConfig, seq_len: int, attn_context: float | None =
     kinds = cfg.encoder.layer_kinds()
     a = cfg.encoder.attention
     per_key = 4 * a.n_q_heads * a.head_dim * kinds.count("attention")
-    recur = len(cfg.encoder.gdn_layers()) * gdn_recurrence_flops(cfg.encoder.gdn)
+    recur = sum(gdn_recurrence_flops(g) for g in cfg.encoder.gdn_shapes())
     k_train = seq_len / 2 if attn_context is None else attn_context
     return {
         "matrix_params": float(enc), "head_params": float(head),

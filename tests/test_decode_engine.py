@@ -26,10 +26,12 @@ def _cfg(kind):
     if kind == "grid":
         a = cfg.encoder.attention
         a.kv_sharing, a.n_kv_heads, a.grid_rows, a.grid_cols, a.row_dim, a.col_dim = "grid", 1, 2, 2, 8, 8
-    if kind in ("plain", "scalars", "negeig"):
+    if kind in ("plain", "scalars", "negeig", "shapes"):
         cfg = C.tiny_control_config()
     if kind == "scalars":
         cfg.encoder.layer_scalars = "skip_x0_span"
+    if kind == "shapes":
+        cfg.encoder.gdn_shape_by_layer = {0: (1, 2, 8), 2: (2, 2, 16)}
     if kind == "negeig":
         cfg.encoder.gdn.negeig.beta_max = 2
     return cfg
@@ -42,7 +44,7 @@ def test_engine_refuses_canon():
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
 
 
-@pytest.mark.parametrize("kind", ["full", "grid", "plain", "scalars", "negeig"])
+@pytest.mark.parametrize("kind", ["full", "grid", "plain", "scalars", "negeig", "shapes"])
 def test_engine_matches_prefill_extend_cpu(kind):
     model = make_model(_cfg(kind), dtype=torch.float32).eval()
     B, P, steps = 3, 40, 6

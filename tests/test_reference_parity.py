@@ -20,10 +20,10 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
-    cfg = C.tiny_control_config() if preset == "control" or scalars or preset.startswith("canon") else C.tiny_full_config()
+    cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith("canon") else C.tiny_full_config()
     if preset == "grid":
         a = cfg.encoder.attention
         a.kv_sharing, a.n_kv_heads, a.grid_rows, a.grid_cols, a.row_dim, a.col_dim = "grid", 1, 2, 2, 8, 8
@@ -31,6 +31,8 @@ def test_state_dict_forward_backward(reference, preset):
         cfg.encoder.gdn.negeig.beta_max = 2
     if scalars:
         cfg.encoder.layer_scalars = preset
+    if preset == "gdn_shapes":
+        cfg.encoder.gdn_shape_by_layer = {1: (1, 2, 8), 4: (2, 2, 16)}
     if preset.startswith("canon"):
         cfg.encoder.canon_kernel = 4
         cfg.encoder.canon_init = "uniform" if preset == "canon_uniform" else "zeros"
