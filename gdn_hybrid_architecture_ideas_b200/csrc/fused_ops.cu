@@ -541,15 +541,16 @@ __global__ void __launch_bounds__(128) depth_mix_multi_fwd_kernel(MultiPtrs p, i
 // Rows in a grid-stride loop. Per row: the Q products dh_q . v_i (one pass over the readers' gradients), then every
 // source's gradient summed over the readers (a second pass over the gradients, which the first left in cache). The
 // pseudo-query gradients accumulate per CTA in shared memory (a thread owns its columns), then one atomic per entry.
-template <int VPT, int NS>
-__global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, int n, int Q, const float* __restrict__ ueff, const float* __restrict__ alpha,
+// TH threads per row (128 or 256): a thread holds VPT float4 of every source, d = 4 VPT TH.
+template <int VPT, int NS, int TH>
+__global__ void __launch_bounds__(TH) depth_mix_multi_bwd_kernel(MultiPtrs p, int n, int Q, const float* __restrict__ ueff, const float* __restrict__ alpha,
                                                                   const float* __restrict__ rnorm, const float* __restrict__ vu, float* __restrict__ du,
                                                                   long rows, int d) {
   extern __shared__ float sdu[];                       // [Q][d]
-  __shared__ float part[4][MIX_MAX * MIXQ_MAX];
+  __shared__ float part[TH / 32][MIX_MAX * MIXQ_MAX];
   __shared__ float sda[MIXQ_MAX][MIX_MAX], sal[MIXQ_MAX][MIX_MAX], sc1[MIXQ_MAX][MIX_MAX], sc2[MIXQ_MAX][MIX_MAX];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < Q * d; i += 128) sdu[i] = 0.f;
+  for (int i = threadIdx.x; i < Q * d; i += TH) sdu[i] = 0.f;
   __syncthreads();
   for (long row = blockIdx.x; row < rows; row += gridDim.x) {
     float4 v[NS][VPT];
@@ -557,13 +558,13 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
     for (int i = 0; i < NS; ++i)
       if (i < n) {
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) v[i][k] = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * 128 + threadIdx.x];
+        for (int k = 0; k < VPT; ++k) v[i][k] = reinterpret_cast<const float4*>(p.src[i] + row * d)[k * TH + threadIdx.x];
       }
     for (int q = 0; q < Q; ++q) {
       if (p.dh[q] == nullptr) continue;
       float4 g[VPT];
 #pragma unroll
-      for (int k = 0; k < VPT; ++k) g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * 128 + threadIdx.x];
+      for (int k = 0; k < VPT; ++k) g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * TH + threadIdx.x];
 #pragma unroll
       for (int i = 0; i < NS; ++i) {
         if (i < n) {
@@ -578,7 +579,10 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
     __syncthreads();
     if (threadIdx.x < Q * n) {
       const int q = threadIdx.x / n, i = threadIdx.x % n, c = threadIdx.x;
-      sda[q][i] = p.dh[q] ? part[0][c] + part[1][c] + part[2][c] + part[3][c] : 0.f;
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < TH / 32; ++w) tot += part[w][c];
+      sda[q][i] = p.dh[q] ? tot : 0.f;
       sal[q][i] = alpha[(row * Q + q) * n + i];
     }
     __syncthreads();
@@ -602,8 +606,8 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
       float4 g[VPT], uq[VPT], dq[VPT];
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * 128 + threadIdx.x];
-        uq[k] = reinterpret_cast<const float4*>(ueff + static_cast<long>(q) * d)[k * 128 + threadIdx.x];
+        g[k] = reinterpret_cast<const float4*>(p.dh[q] + row * d)[k * TH + threadIdx.x];
+        uq[k] = reinterpret_cast<const float4*>(ueff + static_cast<long>(q) * d)[k * TH + threadIdx.x];
         dq[k] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
@@ -620,7 +624,7 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
       }
 #pragma unroll
       for (int k = 0; k < VPT; ++k) {
-        float4* slot = reinterpret_cast<float4*>(sdu + static_cast<long>(q) * d) + k * 128 + threadIdx.x;
+        float4* slot = reinterpret_cast<float4*>(sdu + static_cast<long>(q) * d) + k * TH + threadIdx.x;
         float4 t = *slot;
         t.x += dq[k].x; t.y += dq[k].y; t.z += dq[k].z; t.w += dq[k].w;
         *slot = t;
@@ -630,11 +634,11 @@ __global__ void __launch_bounds__(128) depth_mix_multi_bwd_kernel(MultiPtrs p, i
     for (int i = 0; i < NS; ++i)
       if (i < n) {
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) reinterpret_cast<float4*>(p.dsrc[i] + row * d)[k * 128 + threadIdx.x] = acc[i][k];
+        for (int k = 0; k < VPT; ++k) reinterpret_cast<float4*>(p.dsrc[i] + row * d)[k * TH + threadIdx.x] = acc[i][k];
       }
     __syncthreads();          // the shared per-row scalars are rewritten by the next row
   }
-  for (int i = threadIdx.x; i < Q * d; i += 128) atomicAdd(du + i, sdu[i]);
+  for (int i = threadIdx.x; i < Q * d; i += TH) atomicAdd(du + i, sdu[i]);
 }
 
 int depth_mix_multi_fwd(const float* const* src, int n, float* const* out, int Q, const float* ueff, float* alpha, float* rnorm, float* vu, long rows,
@@ -664,19 +668,20 @@ int depth_mix_multi_bwd(const float* const* src, float* const* dsrc, int n, cons
   for (int i = 0; i < n; ++i) { p.src[i] = src[i]; p.dsrc[i] = dsrc[i]; }
   for (int q = 0; q < Q; ++q) p.dh[q] = dh[q];
   const size_t smem = static_cast<size_t>(Q) * d * 4;
-  const unsigned grid = static_cast<unsigned>(rows < sms * 6L ? rows : sms * 6L);
+  const unsigned grid = static_cast<unsigned>(rows < sms * 8L ? rows : sms * 8L);
   const int ns = n <= 2 ? 2 : (n <= 4 ? 4 : 8);
-#define GHB_MIXB(V, S)                                                                                                            \
+  // 256 threads per row where d allows (d a multiple of 1024): half the registers per thread, more rows in flight per SM
+#define GHB_MIXB(V, S, TH)                                                                                                        \
   do {                                                                                                                            \
     static bool attr = false;                                                                                                     \
-    if (!attr) { cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<V, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * V * 512 * 4); attr = true; } \
-    depth_mix_multi_bwd_kernel<V, S><<<grid, 128, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d);                       \
+    if (!attr) { cudaFuncSetAttribute(depth_mix_multi_bwd_kernel<V, S, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, MIXQ_MAX * 2048 * 4); attr = true; } \
+    depth_mix_multi_bwd_kernel<V, S, TH><<<grid, TH, smem, st>>>(p, n, Q, ueff, alpha, rnorm, vu, du, rows, d);                    \
   } while (0)
-#define GHB_MIXB_NS(V) do { if (ns == 2) GHB_MIXB(V, 2); else if (ns == 4) GHB_MIXB(V, 4); else GHB_MIXB(V, 8); } while (0)
+#define GHB_MIXB_NS(V, TH) do { if (ns == 2) GHB_MIXB(V, 2, TH); else if (ns == 4) GHB_MIXB(V, 4, TH); else GHB_MIXB(V, 8, TH); } while (0)
   switch (d / 512) {
-    case 1: GHB_MIXB_NS(1); break;
-    case 2: GHB_MIXB_NS(2); break;
-    case 4: GHB_MIXB_NS(4); break;
+    case 1: GHB_MIXB_NS(1, 128); break;
+    case 2: GHB_MIXB_NS(1, 256); break;
+    case 4: GHB_MIXB_NS(2, 256); break;
     default: return 1;
   }
 #undef GHB_MIXB_NS
