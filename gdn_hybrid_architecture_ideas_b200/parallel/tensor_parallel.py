@@ -83,7 +83,9 @@ class TensorParallel:
         self.slot_seq = [0] * N_GATHER_SLOTS
         self.next_slot = 0
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", "32"))
+        # CTAs of a launch that push the local shard to the peers. Measured at 2 GPUs (200M, 16 rows): 8 -> 339 ms per step,
+        # 32 -> 258, 64 -> 235, 96 -> 244, 128 -> 311 (the GEMM CTAs lose their SMs); 32 was the setting of the 8-GPU runs.
+        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", "64" if self.world <= 2 else "32"))
         torch.cuda.synchronize(self.device)
         dp.barrier()
 
