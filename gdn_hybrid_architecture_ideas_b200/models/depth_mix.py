@@ -17,14 +17,22 @@ from .norms import RMSNorm
 
 
 class DepthQuery(nn.Module):
-    def __init__(self, d: int, eps: float):
+    """heads: the number of softmaxes over the sources, one per contiguous slice of d / heads channels
+    (`attn_res_heads`; a plain attribute, never in the state dict). 1 is the one-kernel read."""
+
+    def __init__(self, d: int, eps: float, heads: int = 1):
         super().__init__()
+        if heads < 1 or d % heads:
+            raise ValueError(f"model.encoder.attn_res_heads {heads}: a divisor of d_model {d}")
         self.query = nn.Parameter(torch.zeros(d))
         self.key_norm = RMSNorm(d, eps)
+        self.heads = heads
 
     def forward(self, sources: list) -> torch.Tensor:
         if len(sources) == 1:
             return sources[0]
+        if self.heads > 1:
+            return ops.ref.depth_mix_heads(sources, self.query, self.key_norm.weight, self.key_norm.eps, self.heads)
         return ops.depth_mix(sources, self.query, self.key_norm.weight, self.key_norm.eps)
 
 
@@ -32,8 +40,8 @@ class EntryLayer(nn.Module):
     """What a layer that opens or closes a block holds: `entry` (reader of the block's input; first layer of blocks
     2..N) and `out` (reader of the model output; last layer of the stack)."""
 
-    def __init__(self, d: int, eps: float, entry: bool, closes: bool, last: bool):
+    def __init__(self, d: int, eps: float, entry: bool, closes: bool, last: bool, heads: int = 1):
         super().__init__()
-        self.entry = DepthQuery(d, eps) if entry else None
+        self.entry = DepthQuery(d, eps, heads) if entry else None
         self.closes = closes
-        self.out = DepthQuery(d, eps) if last else None
+        self.out = DepthQuery(d, eps, heads) if last else None

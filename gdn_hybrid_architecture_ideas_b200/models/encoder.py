@@ -190,13 +190,19 @@ class Encoder(nn.Module):
         self.activation_checkpoint = "none"
         self.host_pool = None
         d, eps, S, n = cfg.d_model, cfg.norm_eps, self.block, enc.n_layers
+        H = enc.attn_res_heads
+        if type(H) is not int or H < 1 or d % H:
+            raise ValueError(f"model.encoder.attn_res_heads {H!r}: a whole number of heads that divides d_model {d}")
+        if H != 1 and (not self.block_entry or enc.gdn_write_mix != "none"):
+            raise ValueError(f"model.encoder.attn_res_heads {H} is built for model.encoder.attn_res 'block_entry' (its readers) "
+                             "without the GDN write / query mixes")
         if self.block_entry:
             if S <= 0 or n % S:
                 raise ValueError("model.encoder.attn_res 'block_entry' needs n_layers to be a multiple of full_attn_interval")
             for i, layer in enumerate(self.layers):
                 opens, closes = i > 0 and i % S == 0, i % S == S - 1
                 if opens or closes:
-                    layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1)
+                    layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1, heads=enc.attn_res_heads)
         if enc.gdn_write_mix == "layer":
             if not self.block_entry:
                 raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry'")
@@ -308,7 +314,7 @@ class Encoder(nn.Module):
             if arms.variant in READ_MIX_VARIANTS and arms.qmix_query is not None:
                 keys.append((i, "q"))
                 readers.append(arms.qmix_query)
-        if len(readers) < 2 or len(readers) > 8:
+        if len(readers) < 2 or len(readers) > 8 or any(r.heads > 1 for r in readers):
             return {}
         outs = ops.depth_mix_multi(sources, [(r.query, r.key_norm.weight) for r in readers], readers[0].key_norm.eps)
         return dict(zip(keys, outs))

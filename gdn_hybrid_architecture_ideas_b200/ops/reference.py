@@ -233,6 +233,26 @@ def depth_mix(sources, query, gain, eps, return_weights=False):
     return (h, alpha) if return_weights else h
 
 
+def depth_mix_heads(sources, query, gain, eps, heads: int):
+    """`depth_mix` with `heads` softmaxes over the sources, one per contiguous slice of d / heads channels: the logit of
+    slice h is sum over the slice of u_c v_c times rsqrt(mean over ALL d of v^2 + eps) (the key norm over the full row,
+    then sliced); each slice of the output is its own weighted sum (reference: ced/model/attn_res.py:553-577)."""
+    v0 = sources[0]
+    dt = work_dtype(v0)
+    with torch.autocast(v0.device.type, enabled=False):
+        u = query.to(dt) * (1.0 + gain.to(dt))
+        logits = []
+        for v in sources:
+            vf = v.to(dt)
+            r = torch.rsqrt(vf.pow(2).mean(-1) + eps)
+            logits.append((vf * u).unflatten(-1, (heads, -1)).sum(-1) * r[..., None])
+        alpha = torch.softmax(torch.stack(logits, dim=-1), dim=-1)                # (B, L, H, n)
+        h = alpha[..., 0:1] * v0.to(dt).unflatten(-1, (heads, -1))
+        for i in range(1, len(sources)):
+            h = h + alpha[..., i:i + 1] * sources[i].to(dt).unflatten(-1, (heads, -1))
+    return h.flatten(-2).to(v0.dtype)
+
+
 # ------------------------------------------------------------------------------------------------ loss
 
 def lm_loss_sums(hidden, weight, targets, weights=None, z_loss: float = 0.0):
