@@ -44,6 +44,9 @@ class DecodeEngine:
         self.next_tokens = torch.zeros(B, dtype=torch.long, device=dev)     # static output of the step
         self.logits = torch.zeros(B, self.cfg.vocab_size, dtype=torch.float32, device=dev)
         self.layers = []
+        if self.cfg.encoder.attn_res == "block":
+            raise ValueError("the decode engine walks the plain and the block-entry stacks; model.encoder.attn_res 'block' "
+                             "generates through the model's cached forward (eval.generate)")
         if self.cfg.encoder.canon_kernel:
             raise ValueError("the decode engine does not keep a Canon layer's input history (model.encoder.canon_kernel): "
                              "generate through the model's cached forward (eval.generate)")

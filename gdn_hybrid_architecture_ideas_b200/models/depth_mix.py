@@ -45,3 +45,17 @@ class EntryLayer(nn.Module):
         self.entry = DepthQuery(d, eps, heads) if entry else None
         self.closes = closes
         self.out = DepthQuery(d, eps, heads) if last else None
+
+
+class LayerQueries(nn.Module):
+    """Depth attention of both sublayers of one encoder layer ("block": every sublayer reads the finished blocks and the
+    current block's partial sum): `pre_mixer` (None in layer 0, whose mixer reads the embedding alone) and `pre_mlp`;
+    `first`: the layer opens a block; `out`: only in the last layer, the read of the model output
+    (reference: ced/model/attn_res.py:439-452)."""
+
+    def __init__(self, d: int, eps: float, first: bool, has_mixer_query: bool, last: bool):
+        super().__init__()
+        self.first = first
+        self.pre_mixer = DepthQuery(d, eps) if has_mixer_query else None
+        self.pre_mlp = DepthQuery(d, eps)
+        self.out = DepthQuery(d, eps) if last else None

@@ -21,7 +21,7 @@ from .. import ops
 from ..config import ModelConfig
 from . import act_checkpoint
 from .attention import GatedAttention
-from .depth_mix import EntryLayer
+from .depth_mix import EntryLayer, LayerQueries
 from .gdn import READ_MIX_VARIANTS, GatedDeltaNet, GDNArms
 from .mlp import dense_ffn
 from .norms import RMSNorm, round_stream
@@ -187,6 +187,7 @@ class Encoder(nn.Module):
             for kind in enc.layer_kinds())
         self.block = enc.full_attn_interval
         self.block_entry = enc.attn_res == "block_entry"
+        self.block_every = enc.attn_res == "block"        # every sublayer reads the blocks
         self.activation_checkpoint = "none"
         self.host_pool = None
         d, eps, S, n = cfg.d_model, cfg.norm_eps, self.block, enc.n_layers
@@ -196,6 +197,13 @@ class Encoder(nn.Module):
         if H != 1 and (not self.block_entry or enc.gdn_write_mix != "none"):
             raise ValueError(f"model.encoder.attn_res_heads {H} is built for model.encoder.attn_res 'block_entry' (its readers) "
                              "without the GDN write / query mixes")
+        if self.block_every:
+            if S <= 0 or n % S:
+                raise ValueError("model.encoder.attn_res 'block' needs n_layers to be a multiple of full_attn_interval")
+            if enc.gdn_write_mix != "none":
+                raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry', not 'block'")
+            for i, layer in enumerate(self.layers):
+                layer.attn_res = LayerQueries(d, eps, first=i % S == 0, has_mixer_query=i > 0, last=i == n - 1)
         if self.block_entry:
             if S <= 0 or n % S:
                 raise ValueError("model.encoder.attn_res 'block_entry' needs n_layers to be a multiple of full_attn_interval")
@@ -235,7 +243,7 @@ class Encoder(nn.Module):
             raise ValueError(f"model.encoder.layer_scalars_span {enc.layer_scalars_span!r}: a finite width above 1")
         if names and cfg.nvfp4.mode != "none":
             raise ValueError("model.encoder.layer_scalars is not built together with model.nvfp4")
-        if names and self.block_entry:
+        if names and (self.block_entry or self.block_every):
             raise ValueError("model.encoder.layer_scalars is not built together with model.encoder.attn_res: both replace "
                              "the layers' residual add (reference: ced/model/attn_res.py:166-168)")
         for name in names:
@@ -319,12 +327,43 @@ class Encoder(nn.Module):
         outs = ops.depth_mix_multi(sources, [(r.query, r.key_norm.weight) for r in readers], readers[0].key_norm.eps)
         return dict(zip(keys, outs))
 
+    def _forward_block_every(self, x, ctx, get, need_state):
+        """attn_res "block": each sublayer's input is a depth mix over the finished blocks and the current block's partial
+        sum, and a block's sum starts with its first sublayer's output (reference: ced/model/attn_res.py:580-625, 645-660)."""
+        if self.activation_checkpoint != "none" and torch.is_grad_enabled() and x.requires_grad:
+            raise ValueError("model.encoder.attn_res 'block' runs with activation_checkpoint 'none'")
+        done, new_caches = [], []
+        for i, layer in enumerate(self.layers):
+            res, scale = layer.attn_res, layer.residual_scale
+            sources = [*done, x]
+            h = x if res.pre_mixer is None else res.pre_mixer(sources)
+            if layer.kind == "gdn":
+                mixed, c = layer.mixer(layer.mixer_in_norm(h), ctx, get(i), need_state=need_state)
+            else:
+                mixed, c = layer.mixer(layer.mixer_in_norm(h), ctx, get(i))
+            f = scale * layer.mixer_out_norm(mixed, out_dtype=x.dtype)
+            if res.first:
+                seen, partial = sources, f.to(x.dtype)
+            else:
+                seen, partial = done, x + f
+            h = res.pre_mlp([*seen, partial])
+            partial = partial + scale * layer.mlp_out_norm(layer.mlp(layer.mlp_in_norm(h)), out_dtype=x.dtype)
+            new_caches.append(c)
+            if res.out is not None:
+                return res.out([*seen, partial]), new_caches
+            if res.first:
+                done = done + [x]
+            x = partial
+        return x, new_caches
+
     def forward(self, x: torch.Tensor, ctx: SeqContext, caches: list | None = None, need_state: bool = True):
         """x: embedding-stage output (B, L, d). Returns (stream entering final_norm, per-layer caches)."""
         new_caches = []
         get = (lambda i: None) if caches is None else (lambda i: caches[i])
         sc = self.layer_scalar_args(x)
         scal = (lambda i: None) if sc is None else (lambda i: sc[i])
+        if self.block_every:
+            return self._forward_block_every(x, ctx, get, need_state)
         if not self.block_entry:
             for i, layer in enumerate(self.layers):
                 x, c = self._run(layer, x, ctx, get(i), None, need_state, scal(i))

@@ -42,6 +42,10 @@ def test_engine_refuses_canon():
     cfg.encoder.canon_kernel = 4
     with pytest.raises(ValueError, match="Canon"):
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
+    cfg = C.tiny_control_config()
+    cfg.encoder.attn_res = "block"
+    with pytest.raises(ValueError, match="attn_res"):
+        DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
 
 
 @pytest.mark.parametrize("kind", ["full", "grid", "plain", "scalars", "negeig", "shapes"])

@@ -288,3 +288,16 @@ def test_fixed_cross_entropy_trains(tmp_path, head):
     for _ in range(4):
         l1 = b.train_step()["loss"]
     assert l1 < lb
+
+
+def test_block_attn_res_trains(tmp_path):
+    """attn_res "block" (a depth read before every sublayer) through the trainer."""
+    cfg = tiny_train_config()
+    cfg.model = C.tiny_control_config()
+    cfg.model.encoder.attn_res = "block"
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
+    l0 = t.train_step()["loss"]
+    for _ in range(4):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0
+    assert any(n.endswith("attn_res.pre_mlp.query") for n, _ in t.model.named_parameters())
