@@ -293,8 +293,8 @@ def test_fixed_cross_entropy_trains(tmp_path, head):
 def test_block_attn_res_trains(tmp_path):
     """attn_res "block" (a depth read before every sublayer) through the trainer."""
     cfg = tiny_train_config()
-    cfg.model = C.tiny_control_config()
     cfg.model.encoder.attn_res = "block"
+    cfg.model.encoder.gdn_write_mix, cfg.model.encoder.gdn_write_variant = "none", "none"
     t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
     l0 = t.train_step()["loss"]
     for _ in range(4):
