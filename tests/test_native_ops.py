@@ -650,3 +650,57 @@ def test_gdn_prep_with_history(L):
     assert qkv.shape == want.shape
     _close(qkv, want, 1e-2, 2e-2, "qkv")
     assert torch.equal(hd, hdr) and torch.equal(h.float(), hr)
+
+
+@pytest.mark.parametrize("arm", ["block", "heads", "scalars", "canon", "negeig", "shapes"])
+def test_experimental_arms_on_the_device(arm):
+    """Each experimental arm, forward and backward on the CUDA kernels under bf16 autocast, against the same model on the
+    PyTorch statements: loss and gradient norm agree within bf16 noise."""
+    from gdn_hybrid_architecture_ideas_b200 import config as C, ops
+    from gdn_hybrid_architecture_ideas_b200.models import build_model
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+
+    torch.manual_seed(3)
+    cfg = C.hybrid_model_config("60m", full=arm in ("heads",))
+    cfg.encoder.n_layers, cfg.encoder.nope_global_layers, cfg.vocab_size = 8, (1,), 2048
+    cfg.encoder.attention.rope_max_distance = 96
+    e = cfg.encoder
+    if arm == "block":
+        e.attn_res = "block"
+    if arm == "heads":
+        e.attn_res_heads, e.gdn_write_mix, e.gdn_write_variant = 4, "none", "none"
+    if arm == "scalars":
+        e.layer_scalars = "skip_x0_span"
+    if arm == "canon":
+        e.canon_kernel, e.canon_init = 4, "uniform"
+    if arm == "negeig":
+        e.gdn.negeig.beta_max = 2
+    if arm == "shapes":
+        e.gdn_shape_by_layer = {0: (2, 4, 128), 3: (4, 4, 128)}
+    model = build_model(cfg).cuda()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(torch.randn_like(p) * 0.02)
+    B, L = 2, 384
+    tok = torch.randint(0, 2048, (B, L), device="cuda")
+    doc = torch.zeros(B, L, dtype=torch.long, device="cuda")
+    doc[1, 200:] = 1
+
+    def run():
+        model.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = model(tok, doc)
+        loss = torch.nn.functional.cross_entropy(out.logits[:, :-1].flatten(0, 1).float(), tok[:, 1:].flatten())
+        loss.backward()
+        gn = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in model.parameters() if p.grad is not None))
+        return loss.item(), gn.item()
+
+    la, ga = run()
+    native.check_status()
+    ops.set_mode("reference")
+    try:
+        lb, gb = run()
+    finally:
+        ops.set_mode("native")
+    assert abs(la - lb) < 2e-2 * abs(lb), (la, lb)
+    assert abs(ga - gb) < 8e-2 * gb, (ga, gb)
