@@ -36,15 +36,84 @@ class DepthQuery(nn.Module):
         return ops.depth_mix(sources, self.query, self.key_norm.weight, self.key_norm.eps)
 
 
+OWN_SEED_OFFSET = 0x1D3_2610_18809
+
+
+class OwnLinear(nn.Linear):
+    """A Linear (with bias) the model's N(0, init_std) pass leaves alone: zeros at construction (no draw from the global
+    generator), then started by `init_own_parameters` from a generator of its own, so every other tensor starts as in
+    the model without it (reference: ced/model/ldm.py:88-101)."""
+
+    own_init = True
+
+    def reset_parameters(self) -> None:
+        with torch.no_grad():
+            self.weight.zero_()
+            if self.bias is not None:
+                self.bias.zero_()
+
+
+class AddressNet(nn.Module):
+    """RMSNorm -> Linear(d, hidden) -> SiLU -> Linear(hidden, out); the head starts at zero weights and bias
+    (reference: ced/model/ldm.py:103-137, the form of a token-dependent query)."""
+
+    def __init__(self, d: int, hidden: int, out: int, eps: float):
+        super().__init__()
+        self.norm = RMSNorm(d, eps)
+        self.inp = OwnLinear(d, hidden)
+        self.head = OwnLinear(hidden, out)
+
+    @torch.no_grad()
+    def reset_own(self, g: torch.Generator, std: float) -> None:
+        self.inp.weight.copy_(torch.randn(self.inp.weight.shape, generator=g, dtype=torch.float32, device="cpu") * std)
+        self.inp.bias.zero_()
+        self.head.weight.zero_()
+        self.head.bias.zero_()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        hid = torch.nn.functional.silu(torch.nn.functional.linear(self.norm(x, out_dtype=x.dtype), self.inp.weight.to(x.dtype), self.inp.bias.to(x.dtype)))
+        return torch.nn.functional.linear(hid, self.head.weight.to(x.dtype), self.head.bias.to(x.dtype))
+
+
+def init_own_parameters(model: nn.Module, std: float) -> int:
+    """Start every address network, in module order, from a CPU generator seeded with torch.initial_seed() + a fixed
+    offset; the global generator is not drawn (reference: ced/model/ldm.py:423-438)."""
+    nets = [m for m in model.modules() if isinstance(m, AddressNet)]
+    if nets:
+        g = torch.Generator().manual_seed((torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63))
+        for m in nets:
+            m.reset_own(g, std)
+    return len(nets)
+
+
+class TokenQuery(nn.Module):
+    """A block-entry reader whose query is a function of the stream at the read (`attn_res_query: token`): the key norm
+    of a DepthQuery, and in place of the (d,) pseudo-query an address network whose head starts at zero, so the read
+    starts uniform as the static reader does (reference: ced/model/attn_res.py:422-437)."""
+
+    def __init__(self, d: int, eps: float, hidden: int, heads: int = 1):
+        super().__init__()
+        self.key_norm = RMSNorm(d, eps)
+        self.net = AddressNet(d, hidden, d, eps)
+        self.heads = heads
+
+    def forward(self, sources: list, src: torch.Tensor) -> torch.Tensor:
+        if len(sources) == 1:
+            return sources[0]
+        return ops.ref.depth_mix_heads(sources, self.net(src), self.key_norm.weight, self.key_norm.eps, self.heads)
+
+
 class EntryLayer(nn.Module):
     """What a layer that opens or closes a block holds: `entry` (reader of the block's input; first layer of blocks
     2..N) and `out` (reader of the model output; last layer of the stack)."""
 
-    def __init__(self, d: int, eps: float, entry: bool, closes: bool, last: bool, heads: int = 1):
+    def __init__(self, d: int, eps: float, entry: bool, closes: bool, last: bool, heads: int = 1, query_hidden: int = 0):
         super().__init__()
-        self.entry = DepthQuery(d, eps, heads) if entry else None
+        reader = (lambda: TokenQuery(d, eps, query_hidden, heads)) if query_hidden else (lambda: DepthQuery(d, eps, heads))
+        self.entry = reader() if entry else None
         self.closes = closes
-        self.out = DepthQuery(d, eps, heads) if last else None
+        self.out = reader() if last else None
+        self.token = bool(query_hidden)      # the readers take the stream at the read
 
 
 class LayerQueries(nn.Module):

@@ -194,6 +194,15 @@ class Encoder(nn.Module):
         H = enc.attn_res_heads
         if type(H) is not int or H < 1 or d % H:
             raise ValueError(f"model.encoder.attn_res_heads {H!r}: a whole number of heads that divides d_model {d}")
+        if enc.attn_res_query not in ("static", "token"):
+            raise ValueError(f"model.encoder.attn_res_query {enc.attn_res_query!r}: 'static' or 'token'")
+        self.token_query = enc.attn_res_query == "token"
+        if self.token_query and (not self.block_entry or enc.gdn_write_mix != "none"):
+            raise ValueError("model.encoder.attn_res_query 'token' is built for model.encoder.attn_res 'block_entry' (its readers) "
+                             "without the GDN write / query mixes")
+        if enc.attn_res_query_hidden and not self.token_query:
+            raise ValueError("model.encoder.attn_res_query_hidden is read with model.encoder.attn_res_query 'token' only: leave it 0")
+        query_hidden = (enc.attn_res_query_hidden or max(1, d // 32)) if self.token_query else 0
         if H != 1 and (not self.block_entry or enc.gdn_write_mix != "none"):
             raise ValueError(f"model.encoder.attn_res_heads {H} is built for model.encoder.attn_res 'block_entry' (its readers) "
                              "without the GDN write / query mixes")
@@ -210,7 +219,8 @@ class Encoder(nn.Module):
             for i, layer in enumerate(self.layers):
                 opens, closes = i > 0 and i % S == 0, i % S == S - 1
                 if opens or closes:
-                    layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1, heads=enc.attn_res_heads)
+                    layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1, heads=enc.attn_res_heads,
+                                                query_hidden=query_hidden)
         if enc.gdn_write_mix == "layer":
             if not self.block_entry:
                 raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry'")
@@ -305,7 +315,7 @@ class Encoder(nn.Module):
         layer's write ((i, "w")) and query ((i, "q")) mix. They read the same sources with different pseudo-queries, so on
         CUDA one kernel reads each source once for all of them and one backward kernel writes each source's gradient once
         (ops.depth_mix_multi). Empty when there is nothing to share."""
-        if len(sources) < 2 or not ops.use_native(sources[0]):
+        if len(sources) < 2 or not ops.use_native(sources[0]) or self.token_query:
             return {}
         S = self.block
         keys, readers = [], []
@@ -375,7 +385,12 @@ class Encoder(nn.Module):
         for b in range(len(self.layers) // S):
             first = self.layers[b * S]
             mixes = {} if recompute else self._block_mixes(b, sources)
-            start = x if b == 0 else (mixes["entry"] if "entry" in mixes else first.attn_res.entry(sources))
+            if b == 0:
+                start = x
+            elif "entry" in mixes:
+                start = mixes["entry"]
+            else:       # a token-dependent query is formed from the stream where the block before ended
+                start = first.attn_res.entry(sources, x) if self.token_query else first.attn_res.entry(sources)
             if b > 0 and first.stream_bf16:
                 start = round_stream(start)
             x = start
@@ -391,4 +406,5 @@ class Encoder(nn.Module):
                 x, c = self._run(layer, x, ctx, get(i), src, need_state, scal(i), pre)
                 new_caches.append(c)
             sources = sources + [x - start]
-        return self.layers[-1].attn_res.out(sources), new_caches
+        last = self.layers[-1].attn_res
+        return (last.out(sources, x) if self.token_query else last.out(sources)), new_caches

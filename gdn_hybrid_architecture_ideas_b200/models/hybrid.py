@@ -55,8 +55,12 @@ class HybridLM(nn.Module):
         self.head_weight_lp: torch.Tensor | None = None  # bf16 shadow of the head matrix (set by the engine)
         self.tp = None      # tensor-parallel context (parallel.tp_model.apply): the stream is then this rank's token shard
         for m in self.modules():
-            if isinstance(m, (nn.Linear, nn.Embedding)):
+            if isinstance(m, (nn.Linear, nn.Embedding)) and not getattr(m, "own_init", False):
                 nn.init.normal_(m.weight, mean=0.0, std=cfg.init_std)
+        if cfg.encoder.attn_res_query == "token":       # address networks: from a generator of their own, after every other tensor
+            from .depth_mix import init_own_parameters
+
+            init_own_parameters(self, cfg.init_std)
 
     def head_weight(self) -> torch.Tensor:
         return self.embed.weight if self.out_embed is None else self.out_embed.weight

@@ -46,6 +46,10 @@ def test_engine_refuses_canon():
     cfg.encoder.attn_res, cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "block", "none", "none"
     with pytest.raises(ValueError, match="attn_res"):
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
+    cfg = C.tiny_full_config()
+    cfg.encoder.attn_res_query, cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "token", "none", "none"
+    with pytest.raises(ValueError, match="attn_res_query"):
+        DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
 
 
 @pytest.mark.parametrize("kind", ["full", "grid", "plain", "scalars", "negeig", "shapes"])

@@ -20,7 +20,7 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith("canon") else C.tiny_full_config()
@@ -33,6 +33,9 @@ def test_state_dict_forward_backward(reference, preset):
         cfg.encoder.layer_scalars = preset
     if preset == "block_every":
         cfg.encoder.attn_res = "block"
+        cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
+    if preset == "token_query":
+        cfg.encoder.attn_res_query, cfg.encoder.attn_res_heads = "token", 2
         cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
     if preset == "heads":
         cfg.encoder.attn_res_heads = 4

@@ -290,14 +290,19 @@ def test_fixed_cross_entropy_trains(tmp_path, head):
     assert l1 < lb
 
 
-def test_block_attn_res_trains(tmp_path):
-    """attn_res "block" (a depth read before every sublayer) through the trainer."""
+@pytest.mark.parametrize("arm", ["block", "token"])
+def test_block_attn_res_trains(tmp_path, arm):
+    """attn_res "block" (a depth read before every sublayer) and token-dependent block-entry queries through the trainer."""
     cfg = tiny_train_config()
-    cfg.model.encoder.attn_res = "block"
+    if arm == "block":
+        cfg.model.encoder.attn_res = "block"
+    else:
+        cfg.model.encoder.attn_res_query, cfg.model.encoder.attn_res_heads = "token", 2
     cfg.model.encoder.gdn_write_mix, cfg.model.encoder.gdn_write_variant = "none", "none"
     t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
     l0 = t.train_step()["loss"]
     for _ in range(4):
         l1 = t.train_step()["loss"]
     assert l1 < l0
-    assert any(n.endswith("attn_res.pre_mlp.query") for n, _ in t.model.named_parameters())
+    want = "attn_res.pre_mlp.query" if arm == "block" else "attn_res.entry.net.head.weight"
+    assert any(n.endswith(want) for n, _ in t.model.named_parameters())
