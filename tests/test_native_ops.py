@@ -652,7 +652,7 @@ def test_gdn_prep_with_history(L):
     assert torch.equal(hd, hdr) and torch.equal(h.float(), hr)
 
 
-@pytest.mark.parametrize("arm", ["block", "heads", "scalars", "canon", "negeig", "shapes"])
+@pytest.mark.parametrize("arm", ["block", "heads", "token", "scalars", "canon", "negeig", "shapes"])
 def test_experimental_arms_on_the_device(arm):
     """Each experimental arm, forward and backward on the CUDA kernels under bf16 autocast, against the same model on the
     PyTorch statements: loss and gradient norm agree within bf16 noise."""
@@ -661,7 +661,7 @@ def test_experimental_arms_on_the_device(arm):
     from gdn_hybrid_architecture_ideas_b200.ops import native
 
     torch.manual_seed(3)
-    cfg = C.hybrid_model_config("60m", full=arm in ("heads",))
+    cfg = C.hybrid_model_config("60m", full=arm in ("heads", "token"))
     cfg.encoder.n_layers, cfg.encoder.nope_global_layers, cfg.vocab_size = 8, (1,), 2048
     cfg.encoder.attention.rope_max_distance = 96
     e = cfg.encoder
@@ -669,6 +669,8 @@ def test_experimental_arms_on_the_device(arm):
         e.attn_res = "block"
     if arm == "heads":
         e.attn_res_heads, e.gdn_write_mix, e.gdn_write_variant = 4, "none", "none"
+    if arm == "token":
+        e.attn_res_query, e.gdn_write_mix, e.gdn_write_variant = "token", "none", "none"
     if arm == "scalars":
         e.layer_scalars = "skip_x0_span"
     if arm == "canon":
