@@ -659,7 +659,7 @@ _BUILT = {
     "model.ffn_activation": ("swiglu", "relu2"),
     "model.encoder.attention.gate": ("elementwise", "headwise", "none"),
     "model.encoder.attention.temperature": ("fixed", "learned", "ssmax"),
-    "model.encoder.attention.normalizer": ("softmax",),
+    "model.encoder.attention.normalizer": ("softmax", "asentmax"),
     "model.encoder.attention.kv_sharing": ("gqa", "grid"),
     "model.encoder.attention.row_term": ("stored_o",),
     "model.encoder.gdn.init": ("fla", "hf"),
@@ -752,7 +752,7 @@ def require_supported(cfg) -> None:
 # run, so a resume accepts the difference (reference: ced/train/trainer.py:592).
 IMPLEMENTATION_FIELDS = (
     "model.encoder.attention.backend", "model.encoder.attention.flex_tiles", "model.encoder.attention.fa3_docs_per_row",
-    "model.encoder.attention.fa4_deterministic", "model.encoder.gdn.kernel", "model.encoder.gdn.edges",
+    "model.encoder.attention.fa4_deterministic", "model.encoder.attention.asentmax_chunk", "model.encoder.gdn.kernel", "model.encoder.gdn.edges",
     "model.encoder.gdn.chunk_backend", "model.encoder.attn_res_fused", "model.encoder.mix_fold",
     "model.decoder.attention.backend", "model.decoder.gdn.kernel", "model.fused_projections",
     "compile", "cuda_graphs", "cuda_graphs_docs_per_row", "head_impl", "head_chunk", "data_prefetch", "ckpt_async",

@@ -156,6 +156,45 @@ class GatedAttention(nn.Module):
         self.k_norm = RMSNorm(hd, norm_eps) if cfg.qk_norm else nn.Identity()
         self.temp_w = nn.Parameter(torch.zeros(hq)) if cfg.temperature != "fixed" else None
         self.cap = rope_cap(cfg)
+        if cfg.normalizer not in ("softmax", "asentmax"):
+            raise ValueError(f"attention.normalizer {cfg.normalizer!r}: 'softmax' or 'asentmax'")
+        self.entmax = cfg.normalizer == "asentmax"
+        if self.entmax:
+            # alpha = 1.5 entmax with a learned scale on q: c = 1 + softplus(x w_b + b_b) ln(pos + 2)^(2 tanh(x w_g + b_g)), x the
+            # layer's normed input. The two heads are built without touching the global generator and started by the model
+            # from a generator of their own, so every other tensor starts as in the softmax model
+            # (reference: ced/model/attention.py:32-43, 693-709).
+            if cfg.asentmax_chunk < 0:
+                raise ValueError(f"attention.asentmax_chunk {cfg.asentmax_chunk}: query rows per chunk, 0 for auto")
+            if cfg.temperature != "fixed" or self.cap is not None or self.grid is not None:
+                raise ValueError("attention.normalizer 'asentmax' has its own scale on q: temperature 'fixed', no rotary distance "
+                                 "cap and kv_sharing 'gqa'")
+            with torch.random.fork_rng(devices=[]):
+                self.beta_proj = nn.Linear(d_model, hq, bias=True)
+                self.gamma_proj = nn.Linear(d_model, hq, bias=True)
+            for lin in (self.beta_proj, self.gamma_proj):
+                lin.own_init = True
+            self.reset_asentmax_parameters()
+
+    @torch.no_grad()
+    def reset_asentmax_parameters(self, generator: torch.Generator | None = None) -> None:
+        for lin in (self.beta_proj, self.gamma_proj):
+            if generator is None or lin.weight.is_meta:
+                with torch.random.fork_rng(devices=[]):
+                    nn.init.normal_(lin.weight, mean=0.0, std=0.02)
+            else:
+                lin.weight.copy_(torch.empty(lin.weight.shape, dtype=torch.float32).normal_(0.0, 0.02, generator=generator))
+            lin.bias.zero_()
+
+    def asentmax_scale(self, x: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """c (B, L, Hq) in >= float32."""
+        dt = torch.promote_types(x.dtype, torch.float32)
+        F = torch.nn.functional
+        with torch.autocast(x.device.type, enabled=False):
+            xf = x.to(dt)
+            beta = F.softplus(F.linear(xf, self.beta_proj.weight.to(dt), self.beta_proj.bias.to(dt)))
+            gamma = 2.0 * torch.tanh(F.linear(xf, self.gamma_proj.weight.to(dt), self.gamma_proj.bias.to(dt)))
+            return 1.0 + beta * torch.pow(torch.log((pos + 2).to(dt))[:, :, None], gamma)
 
     # ------------------------------------------------------------------ pieces
 
@@ -188,6 +227,8 @@ class GatedAttention(nn.Module):
         q = self._rot(qn, rot_pos)
         q_far = self._rot(qn, rot_pos.new_full((1, 1), self.cap)) if self.cap is not None else None
         f = self.query_factor(pos, torch.promote_types(q.dtype, torch.float32))
+        if self.entmax:
+            f = self.asentmax_scale(x, pos)[..., None]
         if f is not None:
             q = (q.to(f.dtype) * f).to(q.dtype)
             if q_far is not None:
@@ -211,7 +252,7 @@ class GatedAttention(nn.Module):
         dimension 64, QK-norm on, fixed temperature, grouped (not grid) keys, 0 or a power of two (<= 32) rotary pairs."""
         cfg = self.cfg
         r2 = rotary_dims(cfg.head_dim, cfg.rope_fraction) // 2
-        return (ops.use_native(x) and x.dtype == torch.bfloat16 and self.grid is None and cfg.qk_norm and cfg.temperature == "fixed"
+        return (ops.use_native(x) and not self.entmax and x.dtype == torch.bfloat16 and self.grid is None and cfg.qk_norm and cfg.temperature == "fixed"
                 and cfg.head_dim == 64 and cfg.gate in ("elementwise", "none") and r2 in (0, 2, 4, 8, 16, 32))
 
     def _forward_fused(self, x, ctx, cache, rot_pos, cap):
@@ -277,6 +318,10 @@ class GatedAttention(nn.Module):
             new = KeySet(k=k_new, v=self.v_proj(x).view(B, L, hkv, hd), idx=ctx.idx, doc=ctx.doc, ok=ok, k_far=kf_new)
             keys = KeySet.cat(cache, new)
             k, k_far, v = keys.k, keys.k_far, keys.v
+        if self.entmax:      # the exact tensor-op statement on every path
+            o = ops.ref.entmax_attention(q, k, v, ctx.idx, ctx.doc, keys.idx, keys.doc, None if cache is None else keys.ok,
+                                         chunk=self.cfg.asentmax_chunk)
+            return self.output(o, gate), keys
         o = ops.attention(q, k, v, ctx.idx, ctx.doc, keys.idx, keys.doc, None if cache is None else keys.ok,
                           q_far=q_far, k_far=k_far, cap=cap, self_aligned=cache is None, q_pos=ctx.pos,
                           single_doc=ctx.single_doc)

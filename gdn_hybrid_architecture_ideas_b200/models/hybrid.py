@@ -57,6 +57,11 @@ class HybridLM(nn.Module):
         for m in self.modules():
             if isinstance(m, (nn.Linear, nn.Embedding)) and not getattr(m, "own_init", False):
                 nn.init.normal_(m.weight, mean=0.0, std=cfg.init_std)
+        entmax_layers = [m for m in self.modules() if getattr(m, "entmax", False)]
+        if entmax_layers:           # the scale heads: one CPU generator of their own, in model order (reference: ced/model/looped_ced.py:145-155)
+            g = torch.Generator().manual_seed((torch.initial_seed() + 0xA5E_2506_16640) % (1 << 63))
+            for m in entmax_layers:
+                m.reset_asentmax_parameters(g)
         if cfg.encoder.attn_res_query == "token":       # address networks: from a generator of their own, after every other tensor
             from .depth_mix import init_own_parameters
 

@@ -253,6 +253,70 @@ def depth_mix_heads(sources, query, gain, eps, heads: int):
     return h.flatten(-2).to(v0.dtype)
 
 
+def entmax15(x: torch.Tensor, allow: torch.Tensor) -> torch.Tensor:
+    """alpha = 1.5 entmax over the last dimension of x (already halved scores: p = [x - tau]_+^2 summing to 1) among the
+    allowed entries, by the sort-based closed form: a support of the k largest entries gives tau_k = mean_k -
+    sqrt((1 - k var_k) / k), the support size is the largest k with tau_k <= x_(k). Every support entry lies within 1 of
+    the row maximum, so entries below max - 2 (and the masked ones) are placed at max - 2, where they never enter the
+    support. tau is recomputed from the support with two-pass sums (reference: ced/model/entmax.py:14-45)."""
+    any_ok = allow.any(-1, keepdim=True)
+    xm = torch.where(allow, x, torch.full_like(x, float("-inf"))).amax(-1, keepdim=True)
+    xs = torch.where(allow, (x - torch.where(any_ok, xm, torch.zeros_like(xm))).clamp(min=-2.0), torch.full_like(x, -2.0))
+    srt = xs.sort(dim=-1, descending=True).values
+    k = torch.arange(1, x.shape[-1] + 1, device=x.device, dtype=x.dtype)
+    mean = srt.cumsum(-1) / k
+    meansq = srt.square().cumsum(-1) / k
+    delta = (1.0 - k * (meansq - mean.square())) / k
+    tau_k = mean - delta.clamp(min=0.0).sqrt()
+    kstar = (tau_k <= srt).sum(-1, keepdim=True).clamp(min=1)
+    in_top = torch.arange(x.shape[-1], device=x.device) < kstar
+    kf = kstar.to(x.dtype)
+    m = (srt * in_top).sum(-1, keepdim=True) / kf
+    ssd = ((srt - m).square() * in_top).sum(-1, keepdim=True)
+    tau = m - ((1.0 - ssd).clamp(min=0.0) / kf).sqrt()
+    p = (xs - tau).clamp(min=0.0).square()
+    return torch.where(any_ok, p, torch.zeros_like(p))
+
+
+ENTMAX_AUTO_ELEMENTS = 1 << 25     # score elements of one query chunk when the chunk size is 0 (auto): 128 MiB in float32
+
+
+def entmax_attention(q, k, v, q_idx, q_doc, k_idx, k_doc, k_ok=None, chunk: int = 0):
+    """Causal, document-masked attention with the alpha = 1.5 entmax in place of the softmax: z = q . k hd^-0.5 over the
+    allowed keys, p = entmax15(z / 2), out = p v; grouped KV heads as `attention`; >= float32, autocast off. Queries go
+    in chunks of `chunk` rows (0: as many as keep one chunk's (B, Hq, rows, S) scores at ENTMAX_AUTO_ELEMENTS); with a
+    gradient each chunk is recomputed in the backward, so only one chunk's scores are alive at a time
+    (reference: ced/model/entmax.py:1-13, 372-377)."""
+    B, Lq, hq, _ = q.shape
+    S, rep = k.shape[1], hq // k.shape[2]
+    dt = work_dtype(q)
+    scale = q.shape[-1] ** -0.5
+
+    def rows_out(qc, kk, vv, qi, qd):
+        allow = (k_idx[:, None, :] <= qi[:, :, None]) & (k_doc[:, None, :] == qd[:, :, None])
+        if k_ok is not None:
+            allow = allow & k_ok[:, None, :]
+        with torch.autocast(qc.device.type, enabled=False):
+            z = torch.einsum("bqhd,bshd->bhqs", qc.to(dt), kk.repeat_interleave(rep, dim=2).to(dt)) * scale
+            p = entmax15(z * 0.5, allow[:, None].expand_as(z))
+            return torch.einsum("bhqs,bshd->bqhd", p, vv.repeat_interleave(rep, dim=2).to(dt))
+
+    rows = chunk if chunk > 0 else ENTMAX_AUTO_ELEMENTS // max(1, B * hq * S)
+    rows = max(1, min(rows, Lq))
+    if rows >= Lq:
+        return rows_out(q, k, v, q_idx, q_doc).to(q.dtype)
+    grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v))
+    outs = []
+    for a in range(0, Lq, rows):
+        args = (q[:, a:a + rows], k, v, q_idx[:, a:a + rows], q_doc[:, a:a + rows])
+        if grad:
+            from torch.utils.checkpoint import checkpoint
+            outs.append(checkpoint(rows_out, *args, use_reentrant=False))
+        else:
+            outs.append(rows_out(*args))
+    return torch.cat(outs, dim=1).to(q.dtype)
+
+
 # ------------------------------------------------------------------------------------------------ loss
 
 def lm_loss_sums(hidden, weight, targets, weights=None, z_loss: float = 0.0):

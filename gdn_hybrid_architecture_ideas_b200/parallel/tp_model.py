@@ -28,6 +28,8 @@ def local_model_config(cfg: ModelConfig, world: int) -> ModelConfig:
     if enc.gdn_shape_by_layer:
         raise ValueError("tensor parallel shards one GDN shape for the whole stack: model.encoder.gdn_shape_by_layer is not built with it")
     a, g = enc.attention, enc.gdn
+    if a.normalizer != "softmax":
+        raise ValueError("tensor parallel shards the softmax attention: attention.normalizer 'asentmax' is not built with it")
     sizes = {"gdn.n_k_heads": g.n_k_heads, "gdn.n_v_heads": g.n_v_heads, "attention.n_q_heads": a.n_q_heads,
              "attention.n_kv_heads": a.n_kv_heads, "ffn_hidden": cfg.ffn_hidden}
     bad = [k for k, v in sizes.items() if v % world]

@@ -17,11 +17,12 @@ from dataclasses import dataclass
 
 import torch
 
-NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gain", ".x0_gain")
+NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gain", ".x0_gain", ".beta_proj.weight", ".beta_proj.bias",
+                     ".gamma_proj.weight", ".gamma_proj.bias")
 ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
-ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight")
+ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight", "beta_proj.weight", "gamma_proj.weight")
 ALIGN = 64
 
 

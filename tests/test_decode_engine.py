@@ -42,6 +42,11 @@ def test_engine_refuses_canon():
     cfg.encoder.canon_kernel = 4
     with pytest.raises(ValueError, match="Canon"):
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
+    cfg = C.tiny_control_config()
+    a = cfg.encoder.attention
+    a.normalizer, a.temperature, a.rope_max_distance = "asentmax", "fixed", None
+    with pytest.raises(ValueError, match="asentmax"):
+        DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
     cfg = C.tiny_full_config()
     cfg.encoder.attn_res, cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "block", "none", "none"
     with pytest.raises(ValueError, match="attn_res"):

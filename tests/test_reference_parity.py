@@ -20,7 +20,7 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith("canon") else C.tiny_full_config()
@@ -34,6 +34,10 @@ def test_state_dict_forward_backward(reference, preset):
     if preset == "block_every":
         cfg.encoder.attn_res = "block"
         cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
+    if preset == "asentmax":
+        a = cfg.encoder.attention
+        a.normalizer, a.temperature, a.rope_max_distance = "asentmax", "fixed", None
+        cfg.encoder.nope_global_layers = ()
     if preset == "token_query":
         cfg.encoder.attn_res_query, cfg.encoder.attn_res_heads = "token", 2
         cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
@@ -200,3 +204,51 @@ def test_fixed_cross_entropy_matches_reference(reference):
     assert abs(float(la - lb)) < 1e-10 and max((x - y).abs().max() for x, y in zip(ga, gb)) < 1e-10
     with pytest.raises(ValueError):
         FH.fused_linear_ce(h, W, tk, ak, b, 5, ce_form="other")
+
+
+def test_entmax15_is_the_simplex_projection():
+    """p = [x - tau]_+^2 sums to one over the allowed entries; tau agrees with a bisection solve; a row without an
+    allowed entry is zero; the masked entries get exactly zero and no gradient."""
+    from gdn_hybrid_architecture_ideas_b200.ops.reference import entmax15
+
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(5, 7, 33, generator=g, dtype=torch.float64) * 2).requires_grad_()
+    allow = torch.rand(5, 7, 33, generator=g) < 0.7
+    allow[0, 0] = False
+    allow[1, 1] = False
+    allow[1, 1, 4] = True
+    p = entmax15(x, allow)
+    s = p.sum(-1)
+    assert torch.equal(s[0, 0], torch.zeros((), dtype=torch.float64)) and (p[~allow] == 0).all()
+    rows = allow.any(-1)
+    assert (s[rows] - 1).abs().max() < 1e-12
+    assert p[1, 1, 4] == 1
+    xm = torch.where(allow, x.detach(), torch.full_like(x, -1e9))
+    lo, hi = xm.amax(-1, keepdim=True) - 1.0, xm.amax(-1, keepdim=True)
+    for _ in range(80):
+        mid = (lo + hi) / 2
+        big = (xm - mid).clamp(min=0).square().sum(-1, keepdim=True) > 1
+        lo, hi = torch.where(big, mid, lo), torch.where(big, hi, mid)
+    want = (xm - lo).clamp(min=0).square()
+    assert (p.detach() - want)[rows].abs().max() < 1e-9
+    (p * torch.randn(p.shape, generator=g, dtype=torch.float64)).sum().backward()
+    assert (x.grad[~allow] == 0).all() and torch.isfinite(x.grad).all()
+
+
+def test_entmax_attention_chunks_equal_one_pass():
+    from gdn_hybrid_architecture_ideas_b200.ops.reference import entmax_attention
+
+    g = torch.Generator().manual_seed(5)
+    B, L, H, Hk, D = 2, 37, 4, 2, 8
+    q, k, v = (torch.randn(B, L, h, D, generator=g, dtype=torch.float64, requires_grad=True) for h in (H, Hk, Hk))
+    idx = torch.arange(L)[None].expand(B, L)
+    doc = torch.zeros(B, L, dtype=torch.long)
+    doc[1, 20:] = 1
+    w = torch.randn(B, L, H, D, generator=g, dtype=torch.float64)
+    outs = []
+    for chunk in (64, 8):
+        o = entmax_attention(q, k, v, idx, doc, idx, doc, chunk=chunk)
+        grads = torch.autograd.grad((o * w).sum(), (q, k, v))
+        outs.append((o.detach(), *grads))
+    for a, b in zip(*outs):
+        assert (a - b).abs().max() < 1e-12

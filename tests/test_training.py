@@ -225,6 +225,36 @@ def test_experimental_arms_train(tmp_path):
     assert all(not torch.equal(before[n], p) for n, p in t2.model.named_parameters() if n in before)
 
 
+def test_asentmax_attention_trains(tmp_path):
+    """alpha = 1.5 entmax attention with its learned query scale: the two heads sit in the undecayed AdamW group (Muon
+    never takes them), start from their own generator and train."""
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    cfg = tiny_train_config()
+    cfg.model = C.tiny_control_config()
+    a = cfg.model.encoder.attention
+    a.normalizer, a.temperature, a.rope_max_distance = "asentmax", "fixed", None
+    cfg.optim.name = "muon"
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "e")
+    heads = [n for n, _ in t.model.named_parameters() if ".beta_proj." in n or ".gamma_proj." in n]
+    assert heads
+    for g in optim.param_groups(t.model, cfg.optim):
+        if set(heads) & set(g["names"]):
+            assert g["weight_decay"] == 0.0 and g.get("kind", "adamw") == "adamw", g
+    before = {n: p.detach().clone() for n, p in t.model.named_parameters() if n in heads}
+    l0 = t.train_step()["loss"]
+    for _ in range(3):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0
+    assert all(not torch.equal(before[n], p) for n, p in t.model.named_parameters() if n in before)
+    bad = tiny_train_config()
+    bad.model = C.tiny_control_config()
+    bad.model.encoder.attention.normalizer = "asentmax"
+    bad.model.encoder.attention.temperature = "learned"
+    with pytest.raises(ValueError, match="asentmax"):
+        Trainer(bad, tmp_path / "b")
+
+
 def test_train_mtp_script(tmp_path):
     """The drafter-head script: loads a trained trunk, freezes it, trains the head, saves the head's tensors only."""
     cfg = tiny_train_config()
