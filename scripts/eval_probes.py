@@ -1,5 +1,6 @@
 #!/usr/bin/env python
-"""Synthetic recall probes (needle, multikey, copy, two-hop) on a checkpoint, teacher-forced
+"""Synthetic recall probes (needle, multikey, copy, two-hop, path copy, multi-fact chain / concat, transcode) on a
+checkpoint, teacher-forced
 (reference: scripts/eval_probes.py).
 
     python scripts/eval_probes.py --checkpoint RUN --lengths 512,2048,8192 --per-kind 32 [--out probes.json]
@@ -37,7 +38,18 @@ def main(argv=None) -> int:
         for kind in probes.PROBE_KINDS:
             ps = [probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
             r = probes.score_probes(model, ps, a.batch_size, ac)
-            table[f"{kind}@{length}"] = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
+            cell = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
+            groups = sorted({it["group"] for it in r["items"] if "group" in it})
+            for gname in groups:        # multi-fact layouts, transcode directions
+                own = [it for it in r["items"] if it.get("group") == gname]
+                cell[gname] = {"exact": sum(it["exact"] for it in own) / len(own), "n": len(own)}
+            if kind.startswith("mf_"):
+                for key in ("fact_acc", "first_ok", "nats", "exact_all"):
+                    cell[key] = sum(float(it[key]) for it in r["items"]) / len(r["items"])
+            if kind == "transcode":
+                floors = [probes.copy_floor(q) for q in ps]
+                cell["copy_floor"] = {k: sum(float(f[k]) for f in floors) / len(floors) for k in ("token_acc", "lcs_share")}
+            table[f"{kind}@{length}"] = cell
             print(f"{kind:9s} length {length:6d}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
     if a.out:
         with open(a.out, "w") as f:

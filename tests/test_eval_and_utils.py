@@ -190,9 +190,62 @@ def test_long_context_buckets_and_probes_and_choice():
         assert p.answer_start + p.answer_len == len(p.ids) and min(p.ids) >= 1
     assert probes.build_probe("needle", V, 48, 0, 0).ids == ps[0].ids
     out = probes.score_probes(model, ps, batch_size=3)
-    assert out["n"] == 4 and 0.0 <= out["exact"] <= 1.0 and out["ce"] > 0
+    assert out["n"] == len(probes.PROBE_KINDS) and 0.0 <= out["exact"] <= 1.0 and out["ce"] > 0
     items = [mc.Item([3, 4, 5], [[6, 7], [8], [9, 10, 11]], 1)]
     assert mc.score_items(model, items, seq_len=32)["n"] == 1
+
+
+def test_multifact_and_transcode_probes():
+    """Multi-fact items: the answer's pieces tile it, facts sit where the layout says, the metrics read the fact tokens
+    only. Transcode: the two directions of one base share the content, the escape round-trips, the untranscoded source
+    never equals the answer."""
+    from gdn_hybrid_architecture_ideas_b200.eval import probes
+
+    V = 256
+    for kind in ("mf_chain", "mf_concat"):
+        for i in range(6):
+            p = probes.build_probe(kind, V, 400, seed=1, index=i, n_keys=4)
+            assert p.group == probes.LAYOUTS[i % 3] and sum(n for n, _ in p.pieces) == p.answer_len
+            assert [f for _, f in p.pieces] == [True, False] * 3 + [True] and len(p.ids) == 400
+            where = [j / 400 for j, t in enumerate(p.ids[:p.ids.index(3)]) if t == 1]
+            assert len(where) == 4
+            if p.group == "front":
+                assert max(where) < 0.45
+            if p.group == "back":
+                assert min(where) > 0.5          # depths count haystack tokens, the facts themselves come on top
+    p = probes.build_probe("mf_chain", V, 200, 0, 0, n_keys=3)
+    ans = p.ids[p.answer_start:]
+    facts = {}
+    ctx = p.ids[:p.answer_start]
+    for j, t in enumerate(ctx):
+        if t == 1 and ctx[j + 5] == 2:
+            facts[tuple(ctx[j + 1:j + 5])] = ctx[j + 6:j + 10]
+    q = ctx[ctx.index(3) + 1:ctx.index(3) + 5]
+    chain = []
+    for _ in range(3):
+        q = facts[tuple(q)]
+        chain.append(q)
+    at, got = 0, []
+    for n, is_fact in p.pieces:
+        if is_fact:
+            got.append(ans[at:at + n])
+        at += n
+    assert got == chain
+    ok = [True] * p.answer_len
+    ok[4] = False                                   # a scaffold token wrong: every fact still right
+    m = probes.multifact_metrics(p, ok, [0.5] * p.answer_len)
+    assert m["exact"] and not m["exact_all"] and m["fact_acc"] == 1.0 and m["hop_ok"] == [1.0, 1.0, 1.0]
+    ok = [True] * p.answer_len
+    ok[0] = False
+    m = probes.multifact_metrics(p, ok, [0.5] * p.answer_len)
+    assert not m["exact"] and abs(m["fact_acc"] - 2 / 3) < 1e-9 and abs(m["first_ok"] - 2 / 3) < 1e-9
+    a, b = probes.build_probe("transcode", V, 120, 0, 4), probes.build_probe("transcode", V, 120, 0, 5)
+    assert (a.group, b.group) == ("esc2raw", "raw2esc")
+    raw, esc = a.ids[a.answer_start:], b.ids[b.answer_start:]
+    assert probes.escape_ids(raw) == esc and len(esc) > len(raw) and probes.ESC not in raw
+    for p in (a, b):
+        f = probes.copy_floor(p)
+        assert not f["exact"] and 0 < f["lcs_share"] < 1
 
 
 def test_gdn_diag_and_units(tmp_path):
@@ -283,7 +336,8 @@ def test_eval_scripts_run_on_a_checkpoint(tmp_path):
     assert json.loads((tmp_path / "s.json").read_text())["scores"]["x"]["bpb"] > 0
     run(str(root / "scripts/eval_probes.py"), "--checkpoint", str(tmp_path / "run"), "--lengths", "40", "--per-kind", "2", "--device", "cpu",
         "--out", str(tmp_path / "p.json"))
-    assert len(json.loads((tmp_path / "p.json").read_text())["probes"]) == 4
+    table = json.loads((tmp_path / "p.json").read_text())["probes"]
+    assert len(table) == 8 and "fact_acc" in table["mf_chain@40"] and "copy_floor" in table["transcode@40"]
     run(str(root / "scripts/eval_long.py"), "--checkpoint", str(tmp_path / "run"), "--docs", str(tmp_path / "long.pt"), "--base", "16",
         "--chunk", "16", "--gdn-diag", "--window", "16", "--train-len", "16", "--summary", str(tmp_path / "l.md"), "--device", "cpu",
         "--out", str(tmp_path / "l.json"))
