@@ -7,7 +7,10 @@ and `scripts/eval_long.py` from plain text or JSON-lines (reference: tools/build
 
 Without --tokenizer the bytes of the text are the tokens (ids 0..255, one byte each): enough for smoke evaluations on any
 vocabulary of at least 256 entries. With --chat each JSON line holds {"messages": [{"role", "content"}, ...]}; the
-document is the turns joined as "<role>\\n<content>\\n" and only assistant content is scored.
+document is the turns joined as "<role>\\n<content>\\n" and only assistant content is scored. With --agent each JSON
+line holds a conversation {"tools", "messages" (with "reasoning" and "tool_calls")} and the document is its ChatML-like
+rendering with control tokens at ids 256 upward over byte tokens (`data/chat_format.py`); the set then carries the
+vocabulary's byte table, which is what `scripts/token_type_losses.py` labels the generated tokens from.
 """
 
 from __future__ import annotations
@@ -79,9 +82,24 @@ def main(argv=None) -> int:
     ap.add_argument("--tokenizer")
     ap.add_argument("--field", default="text")
     ap.add_argument("--chat", action="store_true")
+    ap.add_argument("--agent", action="store_true")
     ap.add_argument("--max-docs", type=int)
     ap.add_argument("--min-tokens", type=int, default=2)
     a = ap.parse_args(argv)
+    if a.agent:
+        from gdn_hybrid_architecture_ideas_b200.data.chat_format import ChatTokenizer
+
+        if a.tokenizer:
+            ap.error("--agent renders over byte tokens: no --tokenizer")
+        chat = ChatTokenizer()
+        docs = []
+        with open(a.input) as f:
+            for n, line in enumerate(f):
+                if line.strip() and (not a.max_docs or len(docs) < a.max_docs):
+                    docs.append({**chat.encode_conversation(json.loads(line)), "name": f"doc{n}"})
+        torch.save({"docs": docs, "tokenizer": "bytes+chat", "token_bytes": chat.table, "control": chat.control}, a.out)
+        print(f"{len(docs)} conversations, {sum(len(d['ids']) for d in docs)} tokens -> {a.out}")
+        return 0
     tok = SentencePieceTokenizer(a.tokenizer) if a.tokenizer else ByteTokenizer()
     with open(a.input) as f:
         docs = build(f, tok, a.field, a.chat, a.min_tokens, a.max_docs)

@@ -569,3 +569,115 @@ def test_long_report_context_gain_and_rule():
     assert LR.breaks_first(entries) == {"length": 32768, "metrics": ["bpb.web", "gdn.norm"]}
     text = LR.render(summary, entries)
     assert "Breaks first at 32768" in text and "| 32k | 0.7400 | 0.7100 | +0.0300 +- 0.0040 | 9 |" in text
+
+
+def _agent_conversation():
+    file_text = "def main():\n    print(\"hello world\")\n    return 0\n"
+    return {"tools": [{"name": "editor"}], "messages": [
+        {"role": "system", "content": "You are an agent."},
+        {"role": "user", "content": "Fix the file. <tool_call> is plain text here."},
+        {"role": "assistant", "reasoning": "I should look first.", "content": "Opening the file.",
+         "tool_calls": [{"name": "bash", "arguments": {"command": "cat a.py", "timeout": 5}}]},
+        {"role": "tool", "content": file_text},
+        {"role": "assistant", "content": "", "tool_calls": [{"name": "str_replace_editor", "arguments": {
+            "command": "str_replace", "filePath": "/tmp/a.py", "old_str": file_text, "new_str": "pass", "thought": "swap it"}}]},
+        {"role": "tool", "content": "ok"},
+        {"role": "assistant", "content": "Done:\n```python\nx = 1\n```\nbye",
+         "tool_calls": [{"name": "finish", "arguments": {"message": "All fixed."}}]},
+    ]}
+
+
+def test_chat_format_and_token_types():
+    """The chat rendering keeps control tokens apart from text, and the labeller types every generated token from the
+    ids alone: narration before an acting call, final text before a finish call, path / name heads, a copied editor
+    argument (escapes undone), fenced code; labels of a prefix do not move when the document goes on."""
+    import numpy as np
+
+    from gdn_hybrid_architecture_ideas_b200.data import chat_format as cf
+    from gdn_hybrid_architecture_ideas_b200.eval import token_types as tt
+
+    conv = _agent_conversation()
+    tk = cf.ChatTokenizer()
+    ids, gen = tk.encode_pieces(cf.pieces(conv))
+    assert b"".join(tk.table[t] for t in ids).decode() == cf.render(conv)
+    assert ids.count(tk.control[cf.TOOL_CALL]) == 3            # the user's literal "<tool_call>" stays bytes
+    doc = tk.encode_conversation(conv)
+    assert doc["scored"] == gen and len(doc["byte_lens"]) == len(ids)
+    stats = {}
+    lab = tt.label_document(ids, gen, tk.table, tk.control, stats=stats)
+    assert ((lab >= 0) == np.asarray(gen)).all() and stats["unparsed_calls"] == 0
+
+    def text_of(kind):
+        return b"|".join(b"".join(tk.table[ids[j]] for j in run) for run in _runs(lab, tt.F[kind])).decode()
+
+    assert text_of("reasoning_think") == "I should look first."
+    assert text_of("narration") == "Opening the file."
+    assert text_of("head_name") == "bash|str_replace_editor|str_replace|finish"
+    assert text_of("head_path") == "/tmp/a.py"
+    assert text_of("reasoning_call") == "swap it"
+    assert text_of("code_arg") == "cat a.py|pass"
+    assert text_of("arg") == "5"
+    assert text_of("copied_arg") == 'def main():\\n    print(\\"hello world\\")\\n    return 0\\n'
+    assert text_of("code_content") == "x = 1\n"
+    assert text_of("final_answer") == "Done:\n```python\n|```\nbye|All fixed."
+    assert (lab == tt.F["call_open"]).sum() == 3 and (lab == tt.F["turn_end"]).sum() == 3
+    # a document cut after the second assistant message: the labels before the cut do not move
+    cut = [j for j, t in enumerate(ids) if t == tk.control[cf.IM_END] and gen[j]][1] + 1
+    assert (tt.label_document(ids[:cut], gen[:cut], tk.table, tk.control) == lab[:cut]).all()
+    # the copy window: the same argument with nothing before it to copy from is code
+    solo = {"messages": [conv["messages"][4]]}
+    ids2, gen2 = tk.encode_pieces(cf.pieces(solo))
+    lab2 = tt.label_document(ids2, gen2, tk.table, tk.control)
+    assert (lab2 == tt.F["copied_arg"]).sum() == 0 and (lab2 == tt.F["code_arg"]).sum() > 50
+    # a call that is not JSON counts as an argument, and is counted
+    bad = {"messages": [{"role": "assistant", "content": "x", "tool_calls": [{"name": "t", "arguments": {}}]}]}
+    ids3, gen3 = tk.encode_pieces([(p[0].replace('{"name"', "name="), p[1], p[2]) for p in cf.pieces(bad)])
+    st3 = {}
+    lab3 = tt.label_document(ids3, gen3, tk.table, tk.control, stats=st3)
+    assert st3["unparsed_calls"] == 1 and (lab3 == tt.F["arg"]).sum() > 0
+    seg = tt.segment_positions(ids, gen, tk.table, tk.control)
+    names = [tt.SEGMENTS[s] for s in seg]
+    first_call = ids.index(tk.control[cf.TOOL_CALL])
+    assert names[first_call] == "call_head" and names[ids.index(tk.control[cf.TOOL_CALL_END])] == "call_body"
+    assert names[ids.index(tk.control[cf.THINK])] == "reasoning" and names[0] == "unplaced"
+    assert (tt.segment_positions(ids[:cut], gen[:cut], tk.table, tk.control) == seg[:cut]).all()
+    summ = tt.summarize([lab], [np.asarray(doc["byte_lens"])])
+    assert abs(sum(v["token_share"] for v in summ["types"].values()) - 1) < 1e-9 and summ["types"]["copied"]["tokens"] == 55
+    by = tt.loss_by_type([lab], [np.ones(len(lab))])
+    assert by["head"]["loss"] == 1.0 and by["args"]["tokens"] == 1
+    assert tt.is_path_key("repoDir") and tt.is_path_key("FILE_PATH") and not tt.is_path_key("profile") and not tt.is_path_key("xpath")
+
+
+def _runs(lab, kind):
+    runs, cur = [], []
+    for j, v in enumerate(lab):
+        if v == kind:
+            cur.append(j)
+        elif cur:
+            runs.append(cur)
+            cur = []
+    if cur:
+        runs.append(cur)
+    return runs
+
+
+def test_token_type_losses_script(tmp_path):
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    root = Path(__file__).resolve().parent.parent
+    cfg = C.TrainConfig(model=C.tiny_control_config(), data=C.tiny_data_config())
+    cfg.model.vocab_size = cfg.data.vocab_size = 320
+    cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device = 1, 0, False, "cpu"
+    Trainer(cfg, tmp_path / "run").fit()
+    (tmp_path / "agent.jsonl").write_text(json.dumps(_agent_conversation()) + "\n" + json.dumps(_agent_conversation()) + "\n")
+    run = lambda *a: subprocess.run([sys.executable, *a], check=True, capture_output=True, text=True, timeout=600)
+    run(str(root / "scripts/build_eval_set.py"), "--input", str(tmp_path / "agent.jsonl"), "--out", str(tmp_path / "agent.pt"), "--agent")
+    run(str(root / "scripts/token_type_losses.py"), "--checkpoint", str(tmp_path / "run"), "--set", str(tmp_path / "agent.pt"),
+        "--chunk", "128", "--device", "cpu", "--out", str(tmp_path / "t.json"))
+    out = json.loads((tmp_path / "t.json").read_text())
+    assert out["loss"]["copied"]["tokens"] == 110 and out["loss"]["head"]["loss"] > 0 and out["unparsed_calls"] == 0
+    assert abs(sum(v["token_share"] for v in out["shares"]["types"].values()) - 1) < 1e-9
