@@ -681,3 +681,56 @@ def test_token_type_losses_script(tmp_path):
     out = json.loads((tmp_path / "t.json").read_text())
     assert out["loss"]["copied"]["tokens"] == 110 and out["loss"]["head"]["loss"] > 0 and out["unparsed_calls"] == 0
     assert abs(sum(v["token_share"] for v in out["shares"]["types"].values()) - 1) < 1e-9
+
+
+def test_qa_probe_scores_pairs(tmp_path):
+    """Grounded-QA probe: a left-padded row scores like the item alone, greedy exact match agrees with the
+    teacher-forced argmax, the context gain is the paired gold - swap difference, two evaluations compare on the same
+    tokens only."""
+    from gdn_hybrid_architecture_ideas_b200.eval import qa_probe as qa
+    from tests.helpers import make_model
+
+    model = make_model(C.tiny_control_config(), dtype=torch.float32).eval()
+    rows = []
+    for i in range(6):
+        for cond in ("gold", "swap"):
+            ctx = f"the code of box {i} is {i * 7 + 3}. " * (1 + i % 3) if cond == "gold" else "nothing here. " * (1 + i % 3)
+            rows.append({"kind": "kv", "context": ctx, "question": f"code of box {i}? ", "answer": str(i * 7 + 3),
+                         "meta": {"id": f"kv{i}-{cond}", "pair_id": f"kv{i}", "condition": cond, "bin": "short" if i < 3 else "long",
+                                  "source": "synthetic", "depth_target": i % 2}})
+    (tmp_path / "kv.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    items = qa.load_items(tmp_path)
+    assert len(items) == 12 and len(qa.load_items(tmp_path, max_pairs_per_bin=1)) == 4
+    enc = [qa.encode_item(i) for i in items]
+    scores = qa.score_items(model, enc, batch_size=5)
+    solo = qa.score_items(model, enc[:1], batch_size=1)[0]
+    assert abs(solo.answer_nats - scores[0].answer_nats) < 1e-4 and solo.fingerprint == scores[0].fingerprint
+    for s in scores:
+        assert (s.exact_match is None) == (s.condition == "swap")
+        if s.exact_match is not None:
+            assert s.exact_match == s.tf_greedy
+    summ = qa.summarize(scores)
+    assert set(summ) >= {"kv/all", "kv/short", "kv/long", "kv/short/source=synthetic", "kv/long/depth_target=1"}
+    g = summ["kv/all"]
+    assert g["n"] == 6 and g["n_pairs"] == 6 and g["em_tf_disagreements"] == 0
+    want = sum(scores[2 * i].bpb - scores[2 * i + 1].bpb for i in range(6)) / 6
+    assert abs(g["context_gain"] - want) < 1e-9 and g["context_gain_se"] > 0
+    back = qa.scores_from_json(json.loads(json.dumps(qa.scores_to_json(scores))))
+    diff = qa.paired_difference(scores, back)
+    assert diff["kv/all"]["answer_bpb_diff"] == 0 and diff["kv/all"]["context_gain_diff"] == 0
+    back[0].fingerprint = "x"
+    with pytest.raises(ValueError, match="different tokens"):
+        qa.paired_difference(scores, back)
+    assert qa.batches_by_length([5, 50, 6, 49], 8, max_batch_tokens=100) == [[0, 2], [3, 1]]
+    # the command line: score a checkpoint twice and compare the two files
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    cfg = C.TrainConfig(model=C.tiny_control_config(), data=C.tiny_data_config())
+    cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device = 1, 0, False, "cpu"
+    Trainer(cfg, tmp_path / "run").fit()
+    common = ["--checkpoint", str(tmp_path / "run"), "--probe", str(tmp_path), "--device", "cpu", "--exact-match", "teacher_forced"]
+    a = qa.main(common + ["--out", str(tmp_path / "a.json")])
+    qa.main(common + ["--max-pairs-per-bin", "2", "--out", str(tmp_path / "b.json")])
+    assert a["summary"]["kv/all"]["n"] == 6
+    cmp = qa.main(["--compare", str(tmp_path / "a.json"), str(tmp_path / "b.json")])
+    assert cmp["paired_difference"]["kv/all"]["n"] == 4 and cmp["paired_difference"]["kv/all"]["answer_bpb_diff"] == 0
