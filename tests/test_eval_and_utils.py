@@ -341,6 +341,11 @@ def test_eval_scripts_run_on_a_checkpoint(tmp_path):
     run(str(root / "scripts/eval_long.py"), "--checkpoint", str(tmp_path / "run"), "--docs", str(tmp_path / "long.pt"), "--base", "16",
         "--chunk", "16", "--gdn-diag", "--window", "16", "--train-len", "16", "--summary", str(tmp_path / "l.md"), "--device", "cpu",
         "--out", str(tmp_path / "l.json"))
+    run(str(root / "scripts/report_pcr.py"), "--checkpoint", str(tmp_path / "run"), "--set", f"x={tmp_path / 'set.pt'}", "--set",
+        f"y={tmp_path / 'set.pt'}", "--seq-len", "64", "--edges", "0,8,32", "--copy-lengths", "8,16", "--copy-items", "2", "--device", "cpu",
+        "--out", str(tmp_path / "r.json"))
+    rep = json.loads((tmp_path / "r.json").read_text())
+    assert rep["buckets"] == ["0-7", "8-31", "32-end"] and "all_sets" in rep and set(rep["copy_gain"]) == {"8", "16"}
     long = json.loads((tmp_path / "l.json").read_text())
     assert long["gdn_diag"] and long["context_gain"] and "breaks_first" in long and "difference" in (tmp_path / "l.md").read_text()
 
@@ -734,3 +739,50 @@ def test_qa_probe_scores_pairs(tmp_path):
     assert a["summary"]["kv/all"]["n"] == 6
     cmp = qa.main(["--compare", str(tmp_path / "a.json"), str(tmp_path / "b.json")])
     assert cmp["paired_difference"]["kv/all"]["n"] == 4 and cmp["paired_difference"]["kv/all"]["answer_bpb_diff"] == 0
+
+
+def test_position_and_copy_report():
+    """Loss by position: the scored buckets add up to the evaluation's own row sums for both position measures and the
+    shares add up to the set's bpb. Copy items: copy2 and fresh share their first half, the table buckets by position
+    inside each copy."""
+    import numpy as np
+
+    from gdn_hybrid_architecture_ideas_b200.eval import report_pcr as rp, span_bpb
+    from tests.helpers import make_model
+
+    model = make_model(C.tiny_control_config(), dtype=torch.float32).eval()
+    g = torch.Generator().manual_seed(0)
+    docs = []
+    for n in (50, 90, 20, 127, 64):
+        scored = (torch.rand(n, generator=g) < 0.4).tolist()
+        docs.append(span_bpb.TokenizedDoc(torch.randint(1, 256, (n,), generator=g).tolist(), torch.randint(1, 4, (n,), generator=g).tolist(), scored))
+    rows = span_bpb.build_eval_rows(docs, 128)
+    ev = span_bpb.evaluate(model, rows, 2)
+    ce = rp.position_ce(model, rows, 3)
+    edges = (0, 8, 32, 64)
+    sums = rp.bucket_sums(ce, rows, edges)
+    rp.check_sums(sums, ev.row_nats, ev.row_bytes, ev.row_tokens)
+    rec = rp.set_record(sums)
+    for kind in rp.POS_KINDS:
+        r = rec[kind]["scored"]
+        assert abs(r["bpb_total"] - ev.bpb) < 1e-6 and abs(sum(r["share"]) - ev.bpb) < 1e-6
+        assert rec[kind]["valid"]["tokens_total"] > r["tokens_total"]
+    # a document's first 8 targets sit in the first document bucket wherever the document lies in its row
+    assert rec["doc"]["valid"]["tokens"][0] == 8 * len(docs) and rec["row"]["valid"]["tokens"][0] == 8 * rows.tokens.shape[0]
+    both = rp.all_sets({"a": rec, "b": rec})
+    assert abs(both["doc"]["scored"]["bpb_total"] - ev.bpb) < 1e-6 and both["doc"]["scored"]["sets"] == ["a", "b"]
+    assert len(rp.row_clustered_se(sums)) == 4 and rp.bucket_names(edges) == ["0-7", "8-31", "32-63", "64-end"]
+    allowed = rp.allowed_ids(256, (0, 1))
+    c2, f2 = rp.copy_item(allowed, "pcr_copy2", 16, 3), rp.copy_item(allowed, "pcr_fresh", 16, 3)
+    c3 = rp.copy_item(allowed, "pcr_copy3", 16, 3)
+    assert (c2[0][:16] == c2[0][16:]).all() and (f2[0][:16] == c2[0][:16]).all() and not (f2[0][16:] == c2[0][:16]).all()
+    assert len(c3[0]) == 48 and c3[1] == 16 and c2[0].min() >= 2
+    res = rp.score_copy_items(model, 256, lengths=(16, 40), per_length=3, special_ids=(0, 1), batch_size=2)
+    assert len(res) == 3 * 2 * 3 and len(res[0]["nats"]) == 16 and res[0]["id"] == "pcr_copy2/n=16/0000"
+    table = rp.copy_table(res)
+    assert len(table["pcr_copy3"][16]["copies"]) == 2 and len(table["pcr_copy2"][40]["copies"]) == 1
+    t = table["pcr_copy2"][40]["copies"][0]
+    assert t["tokens"][:5] == [3.0, 9.0, 36.0, 72.0, 0.0] and np.isnan(t["nats"][4])
+    one = [r for r in res if r["variant"] == "pcr_copy2" and r["n"] == 40]
+    assert abs(t["nats"][0] - np.mean([r["nats"][0] for r in one])) < 1e-9
+    assert set(rp.copy_gain(table)) == {16, 40}
