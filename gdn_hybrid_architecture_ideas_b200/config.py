@@ -665,7 +665,7 @@ _BUILT = {
     "model.encoder.gdn.init": ("fla", "hf"),
     "model.encoder.gdn.output_gate": ("silu", "sigmoid"),
     "model.encoder.gdn.decay_cumsum": ("plain",),
-    "model.encoder.gdn.kda.decay": ("scalar",),
+    "model.encoder.gdn.kda.decay": ("scalar", "channel"),
     "model.encoder.gdn.erase.mode": ("none",),
     "model.encoder.gdn.negeig.beta_max": (1, 2),
     "model.encoder.gdn.dprod.n_h": (1,),

@@ -20,6 +20,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..config import GDNConfig
+from . import gdn_kda
 from .linear import Linear
 from .norms import GatedRMSNorm
 from .sequence import SeqContext
@@ -69,10 +70,16 @@ class GatedDeltaNet(nn.Module):
         self.in_proj_qkv = Linear(d_model, self.conv_channels)
         self.in_proj_z = Linear(d_model, hv * dv)
         self.in_proj_b = Linear(d_model, hv)
-        self.in_proj_a = Linear(d_model, hv)
+        # Per-channel decay (gdn.kda.decay 'channel'): the gate's tensors stand where in_proj_a and the per-head dt_bias
+        # were; None for the scalar decay, and then nothing is built and no random number drawn.
+        gdn_kda.check_config(cfg)
+        self.kda = gdn_kda.KDAGate(d_model, cfg) if gdn_kda.is_on(cfg) else None
+        if self.kda is None:
+            self.in_proj_a = Linear(d_model, hv)
         self.conv_weight = nn.Parameter(torch.empty(self.conv_channels, cfg.conv_kernel))
         self.A_log = nn.Parameter(torch.empty(hv))
-        self.dt_bias = nn.Parameter(torch.empty(hv))
+        if self.kda is None:
+            self.dt_bias = nn.Parameter(torch.empty(hv))
         self.norm = GatedRMSNorm(dv, norm_eps, gate=cfg.output_gate, gain=norm_gain)
         self.out_proj = Linear(hv * dv, d_model)
         self.reset_gate_parameters(cfg.init)
@@ -95,7 +102,10 @@ class GatedDeltaNet(nn.Module):
         else:
             raise ValueError(f"unknown GDN init scheme {scheme!r}")
         self.A_log.copy_(torch.log(A))
-        self.dt_bias.copy_(bias)
+        if self.kda is None:
+            self.dt_bias.copy_(bias)
+        else:
+            self.kda.reset_dt_bias(scheme)
 
     # ------------------------------------------------------------------ projections
 
@@ -139,6 +149,8 @@ class GatedDeltaNet(nn.Module):
         starts here). need_state False (training) lets the kernel skip the final state."""
         if (arms is None) != (self.write_mix == "none"):
             raise ValueError("a GDN layer with write/query mixes is called with its arms (through its encoder layer)")
+        if self.kda is not None:
+            return self.forward_kda(x, ctx, state, arms)
         B, L = ctx.doc.shape       # the input may be a token shard (tensor parallel); projections return all tokens
         cfg = self.cfg
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
@@ -158,4 +170,27 @@ class GatedDeltaNet(nn.Module):
                                      chunk_size=cfg.chunk_size, need_state=need_state, inplace_state=bool(ctx.memo.get("inplace_state")))
         z = self.in_proj_z(x).view(B, L, hv, dv)
         y = self.out_proj(self.norm(o, z).flatten(2))
+        return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)
+
+    def forward_kda(self, x, ctx: SeqContext, state: GDNState | None, arms):
+        """The layer with one decay per key channel: the scalar layer's input preparation and output norm around the
+        tensor-op KDA rule (reference: ced/model/gdn_kda.py:481-549)."""
+        if arms is not None or ctx.gdn_scale != 1:
+            raise ValueError("gdn.kda.decay 'channel' is not built with the GDN write / query mixes (model.encoder.gdn_write_mix) nor "
+                             "with TST's resolution-explicit gates (a bag phase)")
+        cfg = self.cfg
+        B, L = ctx.doc.shape
+        hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
+        q, k, v, conv_input, conv_doc = ops.gdn_prep(self.in_proj_qkv(x), ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
+                                                     single_doc=ctx.single_doc)
+        g, beta = gdn_kda.gates(self, x)
+        q, k = q.repeat_interleave(hv // hk, dim=2), k.repeat_interleave(hv // hk, dim=2)
+        S0 = x.new_zeros(B, hv, dk, dv, dtype=g.dtype) if state is None else state.S
+        if cfg.kernel != "recurrence" and L > 1:
+            o, S = ops.ref.kda_chunked(q, k, v, g, beta, ctx.is_doc_start, S0, cfg.chunk_size)
+        else:
+            o, S = ops.ref.kda_recurrence(q, k, v, g, beta, ctx.is_doc_start, S0)
+        z = self.in_proj_z(x).view(B, L, hv, dv)
+        y = self.out_proj(self.norm(o.to(x.dtype), z).flatten(2))
         return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)

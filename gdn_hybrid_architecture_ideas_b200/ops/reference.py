@@ -253,6 +253,61 @@ def depth_mix_heads(sources, query, gain, eps, heads: int):
     return h.flatten(-2).to(v0.dtype)
 
 
+def kda_recurrence(q, k, v, g, beta, is_doc_start, S):
+    """The delta rule with one decay per key channel (KDA), a token at a time: at a document start S = 0; then
+    S <- Diag(exp(g_t)) S (row i of S by its own decay), S += k (beta (v - S^T k))^T, o = S^T q. q, k (B, L, H, dk)
+    already repeated to the value heads, v (B, L, H, dv), g (B, L, H, dk) <= 0, beta (B, L, H), S (B, H, dk, dv). With g the
+    same in every channel this is the scalar rule (reference: ced/model/gdn_kda.py:285-300)."""
+    dt = work_dtype(q)
+    q, k, v, g, beta, S = (t.to(dt) for t in (q, k, v, g, beta, S))
+    outs = []
+    for t in range(q.shape[1]):
+        S = S * (~is_doc_start[:, t]).to(dt)[:, None, None, None]
+        S = S * torch.exp(g[:, t])[..., None]
+        delta = beta[:, t, :, None] * (v[:, t] - torch.einsum("bhkv,bhk->bhv", S, k[:, t]))
+        S = S + torch.einsum("bhk,bhv->bhkv", k[:, t], delta)
+        outs.append(torch.einsum("bhkv,bhk->bhv", S, q[:, t]))
+    return torch.stack(outs, dim=1), S
+
+
+def kda_chunked(q, k, v, g, beta, is_doc_start, S, chunk_size: int = 64):
+    """The same function in chunks of C tokens. With c_t the running sum of g inside the chunk (per channel) and
+    D[t, j] = exp(c_t - c_j) for j <= t in the same document segment (taken per channel inside the products, so nothing
+    overflows), the writes u solve the unit lower-triangular system
+
+        (I + diag(beta) M) U = diag(beta) (V - [t before the chunk's first document start] (exp(c_t) k_t)^T S_0),
+        M[t, j] = sum_c k_t[c] k_j[c] D[t, j, c]  (j < t),
+
+    the reads are o_t = [..] S_0^T (exp(c_t) q_t) + sum_{j <= t} (sum_c q_t[c] k_j[c] D[t, j, c]) u_j, and the state
+    after the chunk is [no start in the chunk] Diag(exp(c_C)) S_0 + sum_{j in the last segment} (exp(c_C - c_j) k_j) u_j^T
+    (reference: ced/model/gdn_kda.py:303-382 states the same WY form)."""
+    dt = work_dtype(q)
+    q, k, v, g, beta, S = (t.to(dt) for t in (q, k, v, g, beta, S))
+    B, L, H, dk = k.shape
+    outs = []
+    for a in range(0, L, chunk_size):
+        sl = slice(a, min(a + chunk_size, L))
+        qc, kc, vc, gc, bc = (t[:, sl].transpose(1, 2) for t in (q, k, v, g, beta))     # (B, H, C, .)
+        C = qc.shape[2]
+        seg = is_doc_start[:, sl].long().cumsum(1)                                        # (B, C)
+        c = gc.cumsum(2)                                                                  # (B, H, C, dk)
+        same = (seg[:, :, None] == seg[:, None, :]) & torch.tril(torch.ones(C, C, dtype=torch.bool, device=q.device))
+        D = torch.exp((c[:, :, :, None, :] - c[:, :, None, :, :]).clamp(max=0.0)) * same[:, None, :, :, None].to(dt)
+        M = torch.einsum("bhtc,bhjc,bhtjc->bhtj", kc, kc, D)
+        P = torch.einsum("bhtc,bhjc,bhtjc->bhtj", qc, kc, D)
+        first = (seg == 0).to(dt)[:, None, :, None]                                       # still the incoming document
+        ec = torch.exp(c)
+        rhs = bc[..., None] * (vc - first * torch.einsum("bhtc,bhcv->bhtv", ec * kc, S))
+        lower = torch.eye(C, dtype=dt, device=q.device) + bc[..., None] * M.tril(-1)
+        U = torch.linalg.solve_triangular(lower, rhs, upper=False, unitriangular=True)
+        o = first * torch.einsum("bhtc,bhcv->bhtv", ec * qc, S) + torch.einsum("bhtj,bhjv->bhtv", P, U)
+        outs.append(o.transpose(1, 2))
+        last = (seg == seg[:, -1:]).to(dt)[:, None, :, None]
+        tail = torch.exp(c[:, :, -1:, :] - c) * kc * last                                 # exp(c_C - c_j) k_j: <= |k_j|
+        S = (seg[:, -1] == 0).to(dt)[:, None, None, None] * ec[:, :, -1, :, None] * S + torch.einsum("bhjc,bhjv->bhcv", tail, U)
+    return torch.cat(outs, dim=1), S
+
+
 def entmax15(x: torch.Tensor, allow: torch.Tensor) -> torch.Tensor:
     """alpha = 1.5 entmax over the last dimension of x (already halved scores: p = [x - tau]_+^2 summing to 1) among the
     allowed entries, by the sort-based closed form: a support of the k largest entries gives tau_k = mean_k -

@@ -22,7 +22,8 @@ NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gai
 ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
-ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight", "beta_proj.weight", "gamma_proj.weight")
+ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight", "beta_proj.weight", "gamma_proj.weight", ".kda.f_down.weight",
+                         ".kda.f_up.weight")
 ALIGN = 64
 
 
@@ -51,6 +52,9 @@ def gdn_mup_names(model) -> tuple[list[str], list[str]]:
     gates, scalars = set(), set()
     for prefix, m in model.named_modules():
         if isinstance(m, GatedDeltaNet):
+            if m.kda is not None:
+                raise ValueError("optim.gdn_mup scales in_proj_a / in_proj_b and the per-head gate scalars: not built with "
+                                 "gdn.kda.decay 'channel'")
             gates.update(f"{prefix}.{n}.weight" for n in ("in_proj_a", "in_proj_b"))
             scalars.update(f"{prefix}.{n}" for n in ("A_log", "dt_bias"))
     names = [n for n, _ in model.named_parameters()]

@@ -47,6 +47,10 @@ def test_engine_refuses_canon():
     a.normalizer, a.temperature, a.rope_max_distance = "asentmax", "fixed", None
     with pytest.raises(ValueError, match="asentmax"):
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
+    cfg = C.tiny_control_config()
+    cfg.encoder.gdn.kda.decay = "channel"
+    with pytest.raises(ValueError, match="kda"):
+        DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
     cfg = C.tiny_full_config()
     cfg.encoder.attn_res, cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "block", "none", "none"
     with pytest.raises(ValueError, match="attn_res"):

@@ -255,6 +255,75 @@ def test_asentmax_attention_trains(tmp_path):
         Trainer(bad, tmp_path / "b")
 
 
+def test_kda_channel_decay(tmp_path):
+    """Per-channel decay: the chunked form equals the token loop (float64, documents and a carried state), a uniform decay
+    is the scalar rule, the cached path equals the full forward, the floored channels' decay never falls below
+    1 - 1/H, the gate's matrices train in AdamW's decayed group and its dt_bias in the undecayed one."""
+    from gdn_hybrid_architecture_ideas_b200.models import gdn_kda
+    from gdn_hybrid_architecture_ideas_b200.ops import reference as R
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+    from tests.helpers import make_model
+
+    g = torch.Generator().manual_seed(0)
+    B, L, H, dk, dv = 2, 70, 2, 8, 4
+    rn = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    q, k, v = rn(B, L, H, dk), torch.nn.functional.normalize(rn(B, L, H, dk), dim=-1), rn(B, L, H, dv)
+    gl, beta = -torch.rand(B, L, H, dk, generator=g, dtype=torch.float64) * 4, torch.rand(B, L, H, generator=g, dtype=torch.float64)
+    starts = torch.zeros(B, L, dtype=torch.bool)
+    starts[0, 33], starts[1, 16], starts[1, 17] = True, True, True
+    S0 = rn(B, H, dk, dv)
+    o1, S1 = R.kda_recurrence(q, k, v, gl, beta, starts, S0)
+    o2, S2 = R.kda_chunked(q, k, v, gl, beta, starts, S0, 16)
+    assert (o1 - o2).abs().max() < 1e-11 and (S1 - S2).abs().max() < 1e-11
+    same = gl[..., :1].expand_as(gl)
+    o3, S3 = R.delta_rule_recurrence(q, k, v, same[..., 0], beta, starts, S0)
+    o4, S4 = R.kda_recurrence(q, k, v, same, beta, starts, S0)
+    assert torch.equal(o3, o4) or (o3 - o4).abs().max() < 1e-13
+    cfg = C.tiny_control_config()
+    kk = cfg.encoder.gdn.kda
+    kk.decay, kk.floor_channels, kk.floor_min, kk.floor_max = "channel", 4, 8.0, 64.0
+    model = make_model(cfg, dtype=torch.float64).eval()
+    tok, doc = torch.randint(0, 256, (2, 40), generator=g), torch.zeros(2, 40, dtype=torch.long)
+    doc[1, 13:] = 1
+    full = model(tok, doc).logits
+    cfg2 = copy.deepcopy(cfg)
+    cfg2.encoder.gdn.kernel, cfg2.encoder.gdn.chunk_size = "chunked", 16
+    chunked = make_model(cfg2, dtype=torch.float64).eval()
+    chunked.load_state_dict(model.state_dict())
+    assert (chunked(tok, doc).logits - full).abs().max() < 1e-9
+    out = chunked.prefill(tok[:, :30], doc[:, :30])
+    cache, parts = out.cache, [out.logits]
+    for i in range(30, 40):
+        out = chunked.extend(tok[:, i:i + 1], doc[:, i:i + 1], None, cache)
+        cache = out.cache
+        parts.append(out.logits)
+    assert (torch.cat(parts, 1) - full).abs().max() < 1e-9
+    layer = next(m for m in model.modules() if getattr(m, "kda", None) is not None)
+    assert not hasattr(layer, "in_proj_a") and "floor_log" not in layer.kda.state_dict()
+    gg, _ = gdn_kda.gates(layer, torch.randn(3, 5, cfg.d_model, generator=g, dtype=torch.float64) * 50)
+    bound = 1 - 1 / torch.tensor(layer.kda.horizons, dtype=torch.float64)
+    assert (torch.exp(gg[..., :4]) >= bound - 1e-12).all() and (gg <= 0).all()
+    tc = tiny_train_config()
+    tc.model = cfg
+    tc.optim.name = "muon"
+    t = Trainer(copy.deepcopy(tc), tmp_path / "k")
+    for grp in optim.param_groups(t.model, tc.optim):
+        names = grp["names"]
+        if any(n.endswith(".kda.f_up.weight") for n in names):
+            assert grp.get("kind", "adamw") == "adamw" and grp["weight_decay"] > 0
+        if any(n.endswith(".kda.dt_bias") for n in names):
+            assert grp["weight_decay"] == 0.0
+    l0 = t.train_step()["loss"]
+    for _ in range(3):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0
+    bad = C.tiny_full_config()
+    bad.encoder.gdn.kda.decay = "channel"
+    m = make_model(bad, dtype=torch.float32)
+    with pytest.raises(ValueError, match="write / query mixes"):
+        m(tok, doc)
+
+
 def test_train_mtp_script(tmp_path):
     """The drafter-head script: loads a trained trunk, freezes it, trains the head, saves the head's tensors only."""
     cfg = tiny_train_config()
