@@ -666,7 +666,7 @@ _BUILT = {
     "model.encoder.gdn.output_gate": ("silu", "sigmoid"),
     "model.encoder.gdn.decay_cumsum": ("plain",),
     "model.encoder.gdn.kda.decay": ("scalar", "channel"),
-    "model.encoder.gdn.erase.mode": ("none",),
+    "model.encoder.gdn.erase.mode": ("none", "eda"),
     "model.encoder.gdn.negeig.beta_max": (1, 2),
     "model.encoder.gdn.dprod.n_h": (1,),
     "model.encoder.loops": (1,),

@@ -20,7 +20,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..config import GDNConfig
-from . import gdn_kda
+from . import gdn_erase, gdn_kda
 from .linear import Linear
 from .norms import GatedRMSNorm
 from .sequence import SeqContext
@@ -86,6 +86,9 @@ class GatedDeltaNet(nn.Module):
         bound = 1.0 / math.sqrt(cfg.conv_kernel)
         nn.init.uniform_(self.conv_weight, -bound, bound)
         self.write_mix = "none"
+        # The erase direction (gdn.erase.mode 'eda'): its tensors come last and draw nothing from the global stream.
+        gdn_erase.check_config(cfg)
+        self.erase = gdn_erase.EraseGate(d_model, cfg) if gdn_erase.is_on(cfg) else None
 
     @torch.no_grad()
     def reset_gate_parameters(self, scheme: str) -> None:
@@ -149,7 +152,7 @@ class GatedDeltaNet(nn.Module):
         starts here). need_state False (training) lets the kernel skip the final state."""
         if (arms is None) != (self.write_mix == "none"):
             raise ValueError("a GDN layer with write/query mixes is called with its arms (through its encoder layer)")
-        if self.kda is not None:
+        if self.kda is not None or self.erase is not None:
             return self.forward_kda(x, ctx, state, arms)
         B, L = ctx.doc.shape       # the input may be a token shard (tensor parallel); projections return all tokens
         cfg = self.cfg
@@ -173,21 +176,29 @@ class GatedDeltaNet(nn.Module):
         return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)
 
     def forward_kda(self, x, ctx: SeqContext, state: GDNState | None, arms):
-        """The layer with one decay per key channel: the scalar layer's input preparation and output norm around the
-        tensor-op KDA rule (reference: ced/model/gdn_kda.py:481-549)."""
+        """The layer with one decay per key channel and / or the erase direction: the scalar layer's input preparation
+        and output norm around the tensor-op rules (reference: ced/model/gdn_kda.py:481-549,
+        ced/model/gdn_erase.py:428-506)."""
         if arms is not None or ctx.gdn_scale != 1:
-            raise ValueError("gdn.kda.decay 'channel' is not built with the GDN write / query mixes (model.encoder.gdn_write_mix) nor "
-                             "with TST's resolution-explicit gates (a bag phase)")
+            raise ValueError("gdn.kda.decay 'channel' / gdn.erase.mode 'eda' are not built with the GDN write / query mixes "
+                             "(model.encoder.gdn_write_mix) nor with TST's resolution-explicit gates (a bag phase)")
         cfg = self.cfg
         B, L = ctx.doc.shape
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
         hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
         q, k, v, conv_input, conv_doc = ops.gdn_prep(self.in_proj_qkv(x), ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
                                                      single_doc=ctx.single_doc)
-        g, beta = gdn_kda.gates(self, x)
-        q, k = q.repeat_interleave(hv // hk, dim=2), k.repeat_interleave(hv // hk, dim=2)
+        if self.kda is not None:
+            g, beta = gdn_kda.gates(self, x)
+        else:
+            g, beta = ops.ref.gdn_gates(self.in_proj_a(x), self.in_proj_b(x), self.A_log, self.dt_bias)
+        rep = hv // hk
+        q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
         S0 = x.new_zeros(B, hv, dk, dv, dtype=g.dtype) if state is None else state.S
-        if cfg.kernel != "recurrence" and L > 1:
+        if self.erase is not None:
+            e = self.erase.direction(x).repeat_interleave(rep, dim=2)
+            o, S = gdn_erase.rule(q, k, v, g, beta, e, self.erase.strength(x), ctx.is_doc_start, S0, cfg.kernel, cfg.chunk_size)
+        elif cfg.kernel != "recurrence" and L > 1:
             o, S = ops.ref.kda_chunked(q, k, v, g, beta, ctx.is_doc_start, S0, cfg.chunk_size)
         else:
             o, S = ops.ref.kda_recurrence(q, k, v, g, beta, ctx.is_doc_start, S0)

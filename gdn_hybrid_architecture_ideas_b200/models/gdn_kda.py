@@ -55,8 +55,8 @@ def check_config(cfg) -> None:
         raise ValueError(f"gdn.kda.floor_channels {k.floor_channels!r}: an integer in [0, k_head_dim = {cfg.k_head_dim})")
     if not (_number(k.floor_min) and _number(k.floor_max) and 1.0 < float(k.floor_min) <= float(k.floor_max)):
         raise ValueError(f"gdn.kda.floor_min / floor_max {k.floor_min!r} / {k.floor_max!r}: horizons in tokens, 1 < floor_min <= floor_max")
-    if cfg.negeig.beta_max != 1 or cfg.erase.mode != "none" or cfg.dprod.n_h != 1:
-        raise ValueError("gdn.kda.decay 'channel' is built on its own: negeig.beta_max 1, erase.mode 'none', dprod.n_h 1")
+    if cfg.negeig.beta_max != 1 or cfg.dprod.n_h != 1:
+        raise ValueError("gdn.kda.decay 'channel' is built with negeig.beta_max 1 and dprod.n_h 1 (and with or without the erase)")
 
 
 def rank_of(cfg) -> int:

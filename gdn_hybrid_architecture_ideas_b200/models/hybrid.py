@@ -62,6 +62,11 @@ class HybridLM(nn.Module):
             g = torch.Generator().manual_seed((torch.initial_seed() + 0xA5E_2506_16640) % (1 << 63))
             for m in entmax_layers:
                 m.reset_asentmax_parameters(g)
+        if cfg.encoder.gdn.erase.mode != "none":        # the erase's tensors: a generator of their own as well
+            from .gdn_erase import check_model, init_own_parameters as init_erase
+
+            check_model(cfg)
+            init_erase(self, cfg.init_std)
         if cfg.encoder.attn_res_query == "token":       # address networks: from a generator of their own, after every other tensor
             from .depth_mix import init_own_parameters
 

@@ -19,11 +19,11 @@ import torch
 
 NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gain", ".x0_gain", ".beta_proj.weight", ".beta_proj.bias",
                      ".gamma_proj.weight", ".gamma_proj.bias")
-ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda")
+ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
 ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight", "beta_proj.weight", "gamma_proj.weight", ".kda.f_down.weight",
-                         ".kda.f_up.weight")
+                         ".kda.f_up.weight", ".erase.e_down.weight", ".erase.e_up.weight", ".erase.in_proj_gamma.weight")
 ALIGN = 64
 
 
@@ -52,9 +52,9 @@ def gdn_mup_names(model) -> tuple[list[str], list[str]]:
     gates, scalars = set(), set()
     for prefix, m in model.named_modules():
         if isinstance(m, GatedDeltaNet):
-            if m.kda is not None:
+            if m.kda is not None or m.erase is not None:
                 raise ValueError("optim.gdn_mup scales in_proj_a / in_proj_b and the per-head gate scalars: not built with "
-                                 "gdn.kda.decay 'channel'")
+                                 "gdn.kda.decay 'channel' or gdn.erase.mode 'eda'")
             gates.update(f"{prefix}.{n}.weight" for n in ("in_proj_a", "in_proj_b"))
             scalars.update(f"{prefix}.{n}" for n in ("A_log", "dt_bias"))
     names = [n for n, _ in model.named_parameters()]

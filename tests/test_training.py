@@ -324,6 +324,66 @@ def test_kda_channel_decay(tmp_path):
         m(tok, doc)
 
 
+def test_erase_direction(tmp_path):
+    """The erase direction: the 2T interleave into the chunked rule equals the token loop on both decays, gamma = 0 is
+    the base rule, the inward clamp passes only gradients that move the scale back toward [0, 1], the scale leaves weight
+    decay under zero_gate_decay none, and the layer trains."""
+    from gdn_hybrid_architecture_ideas_b200.models import gdn_erase
+    from gdn_hybrid_architecture_ideas_b200.ops import reference as R
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+    from tests.helpers import make_model
+
+    g = torch.Generator().manual_seed(0)
+    B, L, H, dk, dv = 2, 45, 2, 8, 4
+    rn = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    unit = lambda t: torch.nn.functional.normalize(t, dim=-1)
+    q, k, e, v = rn(B, L, H, dk), unit(rn(B, L, H, dk)), unit(rn(B, L, H, dk)), rn(B, L, H, dv)
+    beta, gamma = (torch.rand(B, L, H, generator=g, dtype=torch.float64) for _ in range(2))
+    starts = torch.zeros(B, L, dtype=torch.bool)
+    starts[0, 20], starts[1, 7], starts[1, 8] = True, True, True
+    S0 = rn(B, H, dk, dv)
+    for gl in (-torch.rand(B, L, H, generator=g, dtype=torch.float64), -torch.rand(B, L, H, dk, generator=g, dtype=torch.float64) * 3):
+        o1, S1 = gdn_erase.rule(q, k, v, gl, beta, e, gamma, starts, S0, "recurrence", 16)
+        o2, S2 = gdn_erase.rule(q, k, v, gl, beta, e, gamma, starts, S0, "chunked", 16)
+        assert (o1 - o2).abs().max() < 1e-10 and (S1 - S2).abs().max() < 1e-10
+        base = R.kda_recurrence if gl.dim() == 4 else R.delta_rule_recurrence
+        o3, _ = base(q, k, v, gl, beta, starts, S0)
+        o4, _ = gdn_erase.rule(q, k, v, gl, beta, e, torch.zeros_like(gamma), starts, S0, "chunked", 16)
+        assert (o3 - o4).abs().max() < 1e-10 and (o3 - o1).abs().max() > 1e-3
+    s = torch.tensor([-0.5, -0.5, 0.0, 0.5, 1.0, 1.5, 1.5], requires_grad=True)
+    up = torch.tensor([1.0, -1.0, 1.0, 1.0, -1.0, 1.0, -1.0])
+    (gdn_erase.inward_clamp(s) * up).sum().backward()
+    assert s.grad.tolist() == [0.0, -1.0, 1.0, 1.0, -1.0, 1.0, 0.0]
+    assert gdn_erase.inward_clamp(s).tolist() == [0.0, 0.0, 0.0, 0.5, 1.0, 1.0, 1.0]
+    tc = tiny_train_config()
+    tc.model = C.tiny_control_config()
+    tc.model.encoder.gdn.erase.mode, tc.model.encoder.gdn.erase.rank = "eda", 4
+    tc.model.encoder.gdn.kernel, tc.model.encoder.gdn.chunk_size = "chunked", 16
+    tc.optim.zero_gate_decay = "none"
+    t = Trainer(copy.deepcopy(tc), tmp_path / "e")
+    scales = [n for n, _ in t.model.named_parameters() if n.endswith(".erase.scale")]
+    assert scales and all(float(p.abs().max()) == 0 for n, p in t.model.named_parameters() if n in scales)
+    for grp in optim.param_groups(t.model, tc.optim):
+        if set(scales) & set(grp["names"]):
+            assert grp["weight_decay"] == 0.0
+        if any(n.endswith(".erase.e_up.weight") for n in grp["names"]):
+            assert grp.get("kind", "adamw") == "adamw" and grp["weight_decay"] > 0
+    l0 = t.train_step()["loss"]
+    for _ in range(3):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0 and any(float(p.abs().max()) > 0 for n, p in t.model.named_parameters() if n in scales)
+    plain = C.tiny_control_config()
+    torch.manual_seed(5)
+    a = make_model(plain, dtype=torch.float32, seed=5, perturbed=False)
+    b = make_model(tc.model, dtype=torch.float32, seed=5, perturbed=False)
+    sa, sb = a.state_dict(), b.state_dict()
+    assert all(torch.equal(sa[n], sb[n]) for n in sa)          # the base tensors start as in the base model of the same seed
+    bad = C.tiny_full_config()
+    bad.encoder.gdn.erase.mode = "eda"
+    with pytest.raises(ValueError, match="gdn_write_mix"):
+        make_model(bad, dtype=torch.float32)
+
+
 def test_train_mtp_script(tmp_path):
     """The drafter-head script: loads a trained trunk, freezes it, trains the head, saves the head's tensors only."""
     cfg = tiny_train_config()
