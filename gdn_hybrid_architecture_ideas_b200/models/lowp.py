@@ -6,7 +6,7 @@ from __future__ import annotations
 
 from .linear import Linear
 
-KEPT_SUFFIXES = ("in_proj_a", "in_proj_b", "f_down", "f_up", "e_down", "e_up", "in_proj_gamma")
+KEPT_SUFFIXES = ("in_proj_a", "in_proj_b", ".kda.f_down", ".kda.f_up", ".erase.e_down", ".erase.e_up", ".erase.in_proj_gamma")
 
 
 def quantised_linears(model, mode: str, align: int):
