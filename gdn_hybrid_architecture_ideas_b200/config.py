@@ -668,7 +668,7 @@ _BUILT = {
     "model.encoder.gdn.kda.decay": ("scalar", "channel"),
     "model.encoder.gdn.erase.mode": ("none", "eda"),
     "model.encoder.gdn.negeig.beta_max": (1, 2),
-    "model.encoder.gdn.dprod.n_h": (1,),
+    "model.encoder.gdn.dprod.n_h": (1, 2, 3, 4),
     "model.encoder.loops": (1,),
     "model.encoder.layer_scalars": ("none", "skip_x0", "skip_x0_span", "x0", "skip"),
     "model.encoder.attn_res": ("none", "block_entry", "block"),

@@ -50,9 +50,9 @@ class DecodeEngine:
         if self.cfg.encoder.attn_res_query != "static":
             raise ValueError("the decode engine's block-entry reads are the static ones; model.encoder.attn_res_query 'token' "
                              "generates through the model's cached forward (eval.generate)")
-        if self.cfg.encoder.gdn.kda.decay != "scalar" or self.cfg.encoder.gdn.erase.mode != "none":
+        if self.cfg.encoder.gdn.kda.decay != "scalar" or self.cfg.encoder.gdn.erase.mode != "none" or self.cfg.encoder.gdn.dprod.n_h != 1:
             raise ValueError("the decode engine's GDN step kernel reads one decay a value head and one write a token: gdn.kda.decay "
-                             "'channel' and gdn.erase.mode 'eda' generate "
+                             "'channel', gdn.erase.mode 'eda' and gdn.dprod.n_h >= 2 generate "
                              "through the model's cached forward (eval.generate)")
         if self.cfg.encoder.attention.normalizer != "softmax":
             raise ValueError("the decode engine's attention kernel is the softmax one; attention.normalizer 'asentmax' generates "

@@ -20,7 +20,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..config import GDNConfig
-from . import gdn_erase, gdn_kda
+from . import gdn_dprod, gdn_erase, gdn_kda
 from .linear import Linear
 from .norms import GatedRMSNorm
 from .sequence import SeqContext
@@ -89,6 +89,9 @@ class GatedDeltaNet(nn.Module):
         # The erase direction (gdn.erase.mode 'eda'): its tensors come last and draw nothing from the global stream.
         gdn_erase.check_config(cfg)
         self.erase = gdn_erase.EraseGate(d_model, cfg) if gdn_erase.is_on(cfg) else None
+        # Gated DeltaProduct (gdn.dprod.n_h >= 2): the extra steps' tensors, from a stream of their own as well.
+        gdn_dprod.check_config(cfg)
+        self.dprod = gdn_dprod.DeltaProductSteps(d_model, cfg) if gdn_dprod.is_on(cfg) else None
 
     @torch.no_grad()
     def reset_gate_parameters(self, scheme: str) -> None:
@@ -152,7 +155,7 @@ class GatedDeltaNet(nn.Module):
         starts here). need_state False (training) lets the kernel skip the final state."""
         if (arms is None) != (self.write_mix == "none"):
             raise ValueError("a GDN layer with write/query mixes is called with its arms (through its encoder layer)")
-        if self.kda is not None or self.erase is not None:
+        if self.kda is not None or self.erase is not None or self.dprod is not None:
             return self.forward_kda(x, ctx, state, arms)
         B, L = ctx.doc.shape       # the input may be a token shard (tensor parallel); projections return all tokens
         cfg = self.cfg
@@ -180,11 +183,16 @@ class GatedDeltaNet(nn.Module):
         and output norm around the tensor-op rules (reference: ced/model/gdn_kda.py:481-549,
         ced/model/gdn_erase.py:428-506)."""
         if arms is not None or ctx.gdn_scale != 1:
-            raise ValueError("gdn.kda.decay 'channel' / gdn.erase.mode 'eda' are not built with the GDN write / query mixes "
+            raise ValueError("gdn.kda.decay 'channel' / gdn.erase.mode 'eda' / gdn.dprod.n_h >= 2 are not built with the GDN write / query mixes "
                              "(model.encoder.gdn_write_mix) nor with TST's resolution-explicit gates (a bag phase)")
         cfg = self.cfg
         B, L = ctx.doc.shape
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        if self.dprod is not None:
+            o, conv_input, conv_doc, S = gdn_dprod.forward(self, x, ctx, state)
+            z = self.in_proj_z(x).view(B, L, hv, dv)
+            y = self.out_proj(self.norm(o.to(x.dtype), z).flatten(2))
+            return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)
         hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
         q, k, v, conv_input, conv_doc = ops.gdn_prep(self.in_proj_qkv(x), ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc,
                                                      single_doc=ctx.single_doc)

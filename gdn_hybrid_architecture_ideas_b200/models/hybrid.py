@@ -67,6 +67,11 @@ class HybridLM(nn.Module):
 
             check_model(cfg)
             init_erase(self, cfg.init_std)
+        if cfg.encoder.gdn.dprod.n_h != 1:               # Gated DeltaProduct's extra steps: their own generator
+            from . import gdn_dprod
+
+            gdn_dprod.check_model(cfg)
+            gdn_dprod.init_own_parameters(self, cfg.init_std)
         if cfg.encoder.attn_res_query == "token":       # address networks: from a generator of their own, after every other tensor
             from .depth_mix import init_own_parameters
 

@@ -28,9 +28,9 @@ def local_model_config(cfg: ModelConfig, world: int) -> ModelConfig:
     if enc.gdn_shape_by_layer:
         raise ValueError("tensor parallel shards one GDN shape for the whole stack: model.encoder.gdn_shape_by_layer is not built with it")
     a, g = enc.attention, enc.gdn
-    if g.kda.decay != "scalar" or g.erase.mode != "none":
-        raise ValueError("tensor parallel shards the scalar-decay GDN layer: gdn.kda.decay 'channel' and gdn.erase.mode 'eda' are not "
-                         "built with it")
+    if g.kda.decay != "scalar" or g.erase.mode != "none" or g.dprod.n_h != 1:
+        raise ValueError("tensor parallel shards the scalar-decay GDN layer: gdn.kda.decay 'channel', gdn.erase.mode 'eda' and "
+                         "gdn.dprod.n_h >= 2 are not built with it")
     if a.normalizer != "softmax":
         raise ValueError("tensor parallel shards the softmax attention: attention.normalizer 'asentmax' is not built with it")
     sizes = {"gdn.n_k_heads": g.n_k_heads, "gdn.n_v_heads": g.n_v_heads, "attention.n_q_heads": a.n_q_heads,

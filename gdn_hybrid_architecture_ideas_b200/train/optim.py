@@ -52,7 +52,7 @@ def gdn_mup_names(model) -> tuple[list[str], list[str]]:
     gates, scalars = set(), set()
     for prefix, m in model.named_modules():
         if isinstance(m, GatedDeltaNet):
-            if m.kda is not None or m.erase is not None:
+            if m.kda is not None or m.erase is not None or m.dprod is not None:
                 raise ValueError("optim.gdn_mup scales in_proj_a / in_proj_b and the per-head gate scalars: not built with "
                                  "gdn.kda.decay 'channel' or gdn.erase.mode 'eda'")
             gates.update(f"{prefix}.{n}.weight" for n in ("in_proj_a", "in_proj_b"))

@@ -20,10 +20,10 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
-    cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase")) else C.tiny_full_config()
+    cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase", "dprod")) else C.tiny_full_config()
     if preset == "grid":
         a = cfg.encoder.attention
         a.kv_sharing, a.n_kv_heads, a.grid_rows, a.grid_cols, a.row_dim, a.col_dim = "grid", 1, 2, 2, 8, 8
@@ -34,6 +34,10 @@ def test_state_dict_forward_backward(reference, preset):
     if preset == "block_every":
         cfg.encoder.attn_res = "block"
         cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
+    if preset.startswith("dprod"):
+        cfg.encoder.gdn.dprod.n_h = 2 if preset == "dprod" else 3
+        if preset == "dprod_b1":
+            cfg.encoder.gdn.dprod.beta_max, cfg.encoder.gdn.dprod.beta_init = 1, 0.95
     if preset.endswith("erase"):
         cfg.encoder.gdn.erase.mode, cfg.encoder.gdn.erase.rank = "eda", 4
     if preset.startswith("kda"):

@@ -384,6 +384,64 @@ def test_erase_direction(tmp_path):
         make_model(bad, dtype=torch.float32)
 
 
+def test_gated_deltaproduct(tmp_path):
+    """n_h steps a token: the n_h T interleave into the chunked rule equals the token-and-step loop, one step is the
+    plain rule, the extra key / value projection goes to Muon and the extra beta projection and conv to AdamW, the
+    base tensors start as in the base model, and the layer trains on the chunked path."""
+    from gdn_hybrid_architecture_ideas_b200.models import gdn_dprod
+    from gdn_hybrid_architecture_ideas_b200.ops import reference as R
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+    from tests.helpers import make_model
+
+    g = torch.Generator().manual_seed(0)
+    B, L, H, dk, dv, n_h = 2, 37, 2, 8, 4, 3
+    rn = lambda *s: torch.randn(*s, generator=g, dtype=torch.float64)
+    q, k, v = rn(B, L, H, dk), torch.nn.functional.normalize(rn(B, L, n_h, H, dk), dim=-1), rn(B, L, n_h, H, dv)
+    gl, beta = -torch.rand(B, L, H, generator=g, dtype=torch.float64), 2 * torch.rand(B, L, n_h, H, generator=g, dtype=torch.float64)
+    starts = torch.zeros(B, L, dtype=torch.bool)
+    starts[0, 20], starts[1, 7], starts[1, 8] = True, True, True
+    S0 = rn(B, H, dk, dv)
+    o1, S1 = gdn_dprod.dprod_recurrence(q, k, v, gl, beta, starts, S0)
+    qi, ki, vi, gi, bi, si = gdn_dprod.interleave(q, k, v, gl, beta, starts)
+    oi, S2 = R.chunked_delta_rule(qi, ki, vi, gi, bi, si, S0, 16)
+    assert (gdn_dprod.last_substep(oi, n_h) - o1).abs().max() < 1e-10 and (S1 - S2).abs().max() < 1e-10
+    o3, S3 = gdn_dprod.dprod_recurrence(q, k[:, :, :1], v[:, :, :1], gl, beta[:, :, :1], starts, S0)
+    o4, S4 = R.delta_rule_recurrence(q, k[:, :, 0], v[:, :, 0], gl, beta[:, :, 0], starts, S0)
+    assert (o3 - o4).abs().max() < 1e-13
+    tc = tiny_train_config()
+    tc.model = C.tiny_control_config()
+    tc.model.encoder.gdn.dprod.n_h = 2
+    tc.model.encoder.gdn.kernel, tc.model.encoder.gdn.chunk_size = "chunked", 16
+    tc.optim.name = "muon"
+    t = Trainer(copy.deepcopy(tc), tmp_path / "d")
+    for grp in optim.param_groups(t.model, tc.optim):
+        kind = grp.get("kind", "adamw")
+        for n in grp["names"]:
+            if n.endswith(".dprod.in_proj_kv.weight"):
+                assert kind == "muon"
+            if n.endswith((".dprod.in_proj_b.weight", ".dprod.conv_weight")):
+                assert kind == "adamw"
+    l0 = t.train_step()["loss"]
+    for _ in range(3):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0
+    a = make_model(C.tiny_control_config(), dtype=torch.float32, seed=5, perturbed=False).state_dict()
+    b = make_model(tc.model, dtype=torch.float32, seed=5, perturbed=False).state_dict()
+    assert all(torch.equal(a[n], b[n]) for n in a) and len(b) > len(a)
+    layer = next(m for m in t.model.modules() if getattr(m, "dprod", None) is not None)
+    assert sum(p.numel() for p in layer.dprod.parameters()) == gdn_dprod.params_per_layer(tc.model.d_model, tc.model.encoder.gdn)
+    for key, value in (("key", "lowrank"), ("heads", 1), ("route", "one-readout")):
+        bad = C.tiny_control_config()
+        bad.encoder.gdn.dprod.n_h = 2
+        setattr(bad.encoder.gdn.dprod, key, value)
+        with pytest.raises(ValueError, match=key):
+            make_model(bad, dtype=torch.float32)
+    bad = C.tiny_control_config()
+    bad.encoder.gdn.dprod.n_h, bad.encoder.gdn.negeig.beta_max = 2, 2
+    with pytest.raises(ValueError, match="negeig"):
+        make_model(bad, dtype=torch.float32)
+
+
 def test_train_mtp_script(tmp_path):
     """The drafter-head script: loads a trained trunk, freezes it, trains the head, saves the head's tensors only."""
     cfg = tiny_train_config()
