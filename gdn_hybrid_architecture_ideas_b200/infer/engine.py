@@ -44,8 +44,8 @@ class DecodeEngine:
         self.next_tokens = torch.zeros(B, dtype=torch.long, device=dev)     # static output of the step
         self.logits = torch.zeros(B, self.cfg.vocab_size, dtype=torch.float32, device=dev)
         self.layers = []
-        if self.cfg.encoder.attn_res == "block":
-            raise ValueError("the decode engine walks the plain and the block-entry stacks; model.encoder.attn_res 'block' "
+        if self.cfg.encoder.attn_res in ("block", "ldm"):
+            raise ValueError(f"the decode engine walks the plain and the block-entry stacks; model.encoder.attn_res {self.cfg.encoder.attn_res!r} "
                              "generates through the model's cached forward (eval.generate)")
         if self.cfg.encoder.attn_res_query != "static":
             raise ValueError("the decode engine's block-entry reads are the static ones; model.encoder.attn_res_query 'token' "

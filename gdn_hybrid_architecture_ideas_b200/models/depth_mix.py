@@ -54,25 +54,44 @@ class OwnLinear(nn.Linear):
 
 
 class AddressNet(nn.Module):
-    """RMSNorm -> Linear(d, hidden) -> SiLU -> Linear(hidden, out); the head starts at zero weights and bias
-    (reference: ced/model/ldm.py:103-137, the form of a token-dependent query)."""
+    """RMSNorm -> Linear(d, hidden) -> SiLU -> an address head Linear(hidden, out) and, with `gates`, a gate head
+    Linear(hidden, gates). zero_head (a token-dependent query, which must start as the zero pseudo-query): the head
+    starts at zero; otherwise it is drawn as the backbone's linears are. The gate head starts at zero
+    (reference: ced/model/ldm.py:103-137)."""
 
-    def __init__(self, d: int, hidden: int, out: int, eps: float):
+    def __init__(self, d: int, hidden: int, out: int, eps: float, gates: int = 0, zero_head: bool = True):
         super().__init__()
         self.norm = RMSNorm(d, eps)
         self.inp = OwnLinear(d, hidden)
         self.head = OwnLinear(hidden, out)
+        self.gate = OwnLinear(hidden, gates) if gates else None
+        self.zero_head = zero_head
 
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float) -> None:
-        self.inp.weight.copy_(torch.randn(self.inp.weight.shape, generator=g, dtype=torch.float32, device="cpu") * std)
+        draw = lambda t: t.copy_(torch.randn(t.shape, generator=g, dtype=torch.float32, device="cpu") * std)
+        draw(self.inp.weight)
         self.inp.bias.zero_()
-        self.head.weight.zero_()
+        if self.zero_head:
+            self.head.weight.zero_()
+        else:
+            draw(self.head.weight)
         self.head.bias.zero_()
+        if self.gate is not None:
+            self.gate.weight.zero_()
+            self.gate.bias.zero_()
+
+    def hidden(self, x: torch.Tensor) -> torch.Tensor:
+        lin = torch.nn.functional.linear
+        return torch.nn.functional.silu(lin(self.norm(x, out_dtype=x.dtype), self.inp.weight.to(x.dtype), self.inp.bias.to(x.dtype)))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        hid = torch.nn.functional.silu(torch.nn.functional.linear(self.norm(x, out_dtype=x.dtype), self.inp.weight.to(x.dtype), self.inp.bias.to(x.dtype)))
-        return torch.nn.functional.linear(hid, self.head.weight.to(x.dtype), self.head.bias.to(x.dtype))
+        return torch.nn.functional.linear(self.hidden(x), self.head.weight.to(x.dtype), self.head.bias.to(x.dtype))
+
+    def both(self, x: torch.Tensor):
+        """(address, gate logits)."""
+        hid, lin = self.hidden(x), torch.nn.functional.linear
+        return lin(hid, self.head.weight.to(x.dtype), self.head.bias.to(x.dtype)), lin(hid, self.gate.weight.to(x.dtype), self.gate.bias.to(x.dtype))
 
 
 def init_own_parameters(model: nn.Module, std: float) -> int:

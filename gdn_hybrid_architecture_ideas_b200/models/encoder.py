@@ -188,6 +188,7 @@ class Encoder(nn.Module):
         self.block = enc.full_attn_interval
         self.block_entry = enc.attn_res == "block_entry"
         self.block_every = enc.attn_res == "block"        # every sublayer reads the blocks
+        self.ldm = enc.attn_res == "ldm"                  # linear depth memory: a per-position memory beside the stream
         self.activation_checkpoint = "none"
         self.host_pool = None
         d, eps, S, n = cfg.d_model, cfg.norm_eps, self.block, enc.n_layers
@@ -213,6 +214,13 @@ class Encoder(nn.Module):
                 raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry', not 'block'")
             for i, layer in enumerate(self.layers):
                 layer.attn_res = LayerQueries(d, eps, first=i % S == 0, has_mixer_query=i > 0, last=i == n - 1)
+        if self.ldm:
+            from . import ldm
+
+            if enc.gdn_write_mix != "none" or self.token_query or H != 1 or enc.canon_kernel:
+                raise ValueError("model.encoder.attn_res 'ldm' is built on the plain stack: no GDN write / query mixes, token queries, "
+                                 "reader heads or Canon layers")
+            ldm.build(cfg, self.layers)
         if self.block_entry:
             if S <= 0 or n % S:
                 raise ValueError("model.encoder.attn_res 'block_entry' needs n_layers to be a multiple of full_attn_interval")
@@ -374,6 +382,16 @@ class Encoder(nn.Module):
         scal = (lambda i: None) if sc is None else (lambda i: sc[i])
         if self.block_every:
             return self._forward_block_every(x, ctx, get, need_state)
+        if self.ldm:
+            from .ldm import layer_forward
+
+            if self.activation_checkpoint != "none" and torch.is_grad_enabled() and x.requires_grad:
+                raise ValueError("model.encoder.attn_res 'ldm' runs with activation_checkpoint 'none'")
+            M = None
+            for i, layer in enumerate(self.layers):
+                x, M, c = layer_forward(layer, x, M, ctx, get(i), need_state)
+                new_caches.append(c)
+            return x, new_caches
         if not self.block_entry:
             for i, layer in enumerate(self.layers):
                 x, c = self._run(layer, x, ctx, get(i), None, need_state, scal(i))

@@ -72,7 +72,7 @@ class HybridLM(nn.Module):
 
             gdn_dprod.check_model(cfg)
             gdn_dprod.init_own_parameters(self, cfg.init_std)
-        if cfg.encoder.attn_res_query == "token":       # address networks: from a generator of their own, after every other tensor
+        if cfg.encoder.attn_res_query == "token" or cfg.encoder.attn_res == "ldm":       # address networks: from a generator of their own, after every other tensor
             from .depth_mix import init_own_parameters
 
             init_own_parameters(self, cfg.init_std)

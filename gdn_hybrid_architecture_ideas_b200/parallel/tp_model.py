@@ -28,6 +28,8 @@ def local_model_config(cfg: ModelConfig, world: int) -> ModelConfig:
     if enc.gdn_shape_by_layer:
         raise ValueError("tensor parallel shards one GDN shape for the whole stack: model.encoder.gdn_shape_by_layer is not built with it")
     a, g = enc.attention, enc.gdn
+    if enc.attn_res == "ldm":
+        raise ValueError("tensor parallel is not built with model.encoder.attn_res 'ldm' (the depth memory walks the full stream)")
     if g.kda.decay != "scalar" or g.erase.mode != "none" or g.dprod.n_h != 1:
         raise ValueError("tensor parallel shards the scalar-decay GDN layer: gdn.kda.decay 'channel', gdn.erase.mode 'eda' and "
                          "gdn.dprod.n_h >= 2 are not built with it")

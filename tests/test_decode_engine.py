@@ -48,6 +48,10 @@ def test_engine_refuses_canon():
     with pytest.raises(ValueError, match="asentmax"):
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
     cfg = C.tiny_control_config()
+    cfg.encoder.attn_res, cfg.encoder.ldm_groups, cfg.encoder.ldm_key_dim = "ldm", 4, 4
+    with pytest.raises(ValueError, match="ldm"):
+        DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)
+    cfg = C.tiny_control_config()
     cfg.encoder.gdn.dprod.n_h = 2
     with pytest.raises(ValueError, match="dprod"):
         DecodeEngine(make_model(cfg, dtype=torch.float32), 1, 16, device="cpu", use_graph=False)

@@ -20,7 +20,7 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "ldm"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase", "dprod")) else C.tiny_full_config()
@@ -34,6 +34,9 @@ def test_state_dict_forward_backward(reference, preset):
     if preset == "block_every":
         cfg.encoder.attn_res = "block"
         cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
+    if preset == "ldm":
+        cfg.encoder.attn_res, cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "ldm", "none", "none"
+        cfg.encoder.ldm_groups, cfg.encoder.ldm_key_dim, cfg.encoder.ldm_hidden = 4, 4, 6
     if preset.startswith("dprod"):
         cfg.encoder.gdn.dprod.n_h = 2 if preset == "dprod" else 3
         if preset == "dprod_b1":

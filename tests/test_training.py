@@ -442,6 +442,52 @@ def test_gated_deltaproduct(tmp_path):
         make_model(bad, dtype=torch.float32)
 
 
+def test_linear_depth_memory(tmp_path):
+    """attn_res "ldm": the write is lam (I - w k k^T) M + w k v^T, the added tensors count as the shapes say and start
+    without moving any base tensor, every gate starts at 1, the address networks train in AdamW, and the model trains."""
+    from gdn_hybrid_architecture_ideas_b200.models import ldm
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+    from tests.helpers import make_model
+
+    base = C.tiny_control_config()
+    cfg = C.tiny_control_config()
+    cfg.encoder.attn_res, cfg.encoder.ldm_groups, cfg.encoder.ldm_key_dim, cfg.encoder.ldm_hidden = "ldm", 4, 4, 6
+    a = make_model(base, dtype=torch.float64, seed=3, perturbed=False)
+    b = make_model(cfg, dtype=torch.float64, seed=3, perturbed=False)
+    sa, sb = a.state_dict(), b.state_dict()
+    assert all(torch.equal(sa[n], sb[n]) for n in sa)
+    added = sum(p.numel() for n, p in b.named_parameters() if ".attn_res." in n)
+    assert added == ldm.parameter_count(cfg.d_model, cfg.encoder.n_layers, 4, 4, 6)
+    w = b.encoder.layers[1].attn_res.mixer_write
+    with torch.no_grad():
+        w.net.gate.bias.fill_(0.3)
+    g = torch.Generator().manual_seed(0)
+    x, v = torch.randn(2, 5, cfg.d_model, generator=g, dtype=torch.float64), torch.randn(2, 5, cfg.d_model, generator=g, dtype=torch.float64)
+    M = torch.randn(2, 5, 4, 4, cfg.d_model // 4, generator=g, dtype=torch.float64)
+    kw, vw, lam = w.observation(x, v)
+    wgt = (kw * kw).sum(-1)                                    # w, since k is a unit vector
+    k = kw / wgt.sqrt()[..., None]
+    want = lam[:, None, None] * (M - wgt[..., None, None] * k[..., None] * (M * k[..., None]).sum(-2, keepdim=True)) \
+        + wgt[..., None, None] * k[..., None] * v.unflatten(-1, (4, -1))[..., None, :]
+    assert (w.write(M, x, v) - want).abs().max() < 1e-12
+    assert abs(float(lam[0]) - 0.99) < 1e-6 and torch.allclose(wgt, torch.full_like(wgt, 2 * torch.sigmoid(torch.tensor(0.3, dtype=torch.float64))))
+    tc = tiny_train_config()
+    tc.model = cfg
+    tc.optim.name = "muon"
+    t = Trainer(copy.deepcopy(tc), tmp_path / "l")
+    for grp in optim.param_groups(t.model, tc.optim):
+        if any(".attn_res." in n for n in grp["names"]):
+            assert grp.get("kind", "adamw") == "adamw"
+    l0 = t.train_step()["loss"]
+    for _ in range(3):
+        l1 = t.train_step()["loss"]
+    assert l1 < l0
+    bad = C.tiny_full_config()
+    bad.encoder.attn_res = "ldm"
+    with pytest.raises(ValueError):
+        make_model(bad, dtype=torch.float32)
+
+
 def test_train_mtp_script(tmp_path):
     """The drafter-head script: loads a trained trunk, freezes it, trains the head, saves the head's tensors only."""
     cfg = tiny_train_config()
