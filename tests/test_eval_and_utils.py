@@ -786,3 +786,36 @@ def test_position_and_copy_report():
     one = [r for r in res if r["variant"] == "pcr_copy2" and r["n"] == 40]
     assert abs(t["nats"][0] - np.mean([r["nats"][0] for r in one])) < 1e-9
     assert set(rp.copy_gain(table)) == {16, 40}
+
+
+def test_recall_items_plan(tmp_path):
+    """The rerun plan: every item in exactly one group, groups under the budget, deterministic, the old items kept as
+    the first block; the values file averages the plan's items and refuses a missing one."""
+    from gdn_hybrid_architecture_ideas_b200.eval import recall_items as ri
+
+    cells = ri.cells_of(lengths=(8192, 65536, 131072))
+    cell_n = {c.key: 1000 for c in cells}
+    plan = ri.make_plan(cell_n, n_old={cells[0].key: 300}, budget_s=600.0)
+    ri.validate_plan(plan)
+    assert plan == ri.make_plan(cell_n, n_old={cells[0].key: 300}, budget_s=600.0)
+    assert len(plan["groups"]) > 1 and all(g["modelled_s"] <= 600.0 for g in plan["groups"])
+    assert sum(g["items"] for g in plan["groups"]) == 6000
+    first = plan["groups"][0]["parts"][0]
+    assert first["cell"].endswith("|131072") and first["start"] == 0 and first["stop"] % ri.SPLIT_STEP == 0
+    (tmp_path / "plan.json").write_text(json.dumps(plan))
+    assert ri.load_plan(tmp_path / "plan.json")["total"]["groups"] == len(plan["groups"])
+    with pytest.raises(ValueError, match="fewer"):
+        ri.make_plan({cells[0].key: 100}, n_old={cells[0].key: 300})
+    broken = json.loads(json.dumps(plan))
+    broken["groups"][0]["parts"][0]["stop"] -= 1
+    with pytest.raises(ValueError, match="in no group"):
+        ri.validate_plan(broken)
+    cell, idx = ri.parse_item_id("multikey/len=8192/n=4/0012")
+    assert (cell, idx) == (ri.Cell("multikey", 4, 8192), 12) and ri.item_id(cell, idx) == "multikey/len=8192/n=4/0012"
+    small = ri.make_plan({cell.key: 4})
+    res = [{"id": ri.item_id(cell, i), "exact": i != 1} for i in range(4)]
+    vals = ri.values_for_run("r", small, res, exclude={ri.item_id(cell, 3)})
+    assert vals["cells"]["items|multikey_n4|8192|exact"] == 2 / 3 and vals["n_items"]["items|multikey_n4|8192|exact"] == 3
+    with pytest.raises(ValueError, match="not scored"):
+        ri.values_for_run("r", small, res[:2])
+    assert abs(ri.binomial_se(0.5, 100) - 0.05) < 1e-12 and ri.items_for_se(0.5, 0.025) == 400
