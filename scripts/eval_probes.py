@@ -29,28 +29,39 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--batch-size", type=int, default=4)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--set", help="a stored probe set (scripts/build_probes.py) in place of probes built on the fly")
     ap.add_argument("--out")
     a = ap.parse_args(argv)
     model, cfg, step = ckpt.load_model(a.checkpoint, a.device)
     ac = torch.bfloat16 if a.device.startswith("cuda") else None
     table = {}
-    for length in (int(x) for x in a.lengths.split(",")):
-        for kind in probes.PROBE_KINDS:
-            ps = [probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
-            r = probes.score_probes(model, ps, a.batch_size, ac)
-            cell = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
-            groups = sorted({it["group"] for it in r["items"] if "group" in it})
-            for gname in groups:        # multi-fact layouts, transcode directions
-                own = [it for it in r["items"] if it.get("group") == gname]
-                cell[gname] = {"exact": sum(it["exact"] for it in own) / len(own), "n": len(own)}
-            if kind.startswith("mf_"):
-                for key in ("fact_acc", "first_ok", "nats", "exact_all"):
-                    cell[key] = sum(float(it[key]) for it in r["items"]) / len(r["items"])
-            if kind == "transcode":
-                floors = [probes.copy_floor(q) for q in ps]
-                cell["copy_floor"] = {k: sum(float(f[k]) for f in floors) / len(floors) for k in ("token_acc", "lcs_share")}
-            table[f"{kind}@{length}"] = cell
-            print(f"{kind:9s} length {length:6d}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
+    stored = None
+    if a.set:
+        blob = torch.load(a.set, map_location="cpu", weights_only=False)
+        if blob["vocab"] > cfg.model.vocab_size:
+            ap.error(f"the set was built for a vocabulary of {blob['vocab']}, the model has {cfg.model.vocab_size}")
+        stored = {}
+        for p in blob["probes"]:
+            stored.setdefault((p["length"], p["kind"]), []).append(
+                probes.Probe(p["kind"], p["ids"], p["answer_start"], p["answer_len"], tuple(map(tuple, p["pieces"])), p["group"]))
+    cells = sorted(stored) if stored is not None else [(int(x), k) for x in a.lengths.split(",") for k in probes.PROBE_KINDS]
+    for length, kind in cells:
+        ps = stored[(length, kind)] if stored is not None else [
+            probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
+        r = probes.score_probes(model, ps, a.batch_size, ac)
+        cell = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
+        groups = sorted({it["group"] for it in r["items"] if "group" in it})
+        for gname in groups:        # multi-fact layouts, transcode directions
+            own = [it for it in r["items"] if it.get("group") == gname]
+            cell[gname] = {"exact": sum(it["exact"] for it in own) / len(own), "n": len(own)}
+        if kind.startswith("mf_"):
+            for key in ("fact_acc", "first_ok", "nats", "exact_all"):
+                cell[key] = sum(float(it[key]) for it in r["items"]) / len(r["items"])
+        if kind == "transcode":
+            floors = [probes.copy_floor(q) for q in ps]
+            cell["copy_floor"] = {k: sum(float(f[k]) for f in floors) / len(floors) for k in ("token_acc", "lcs_share")}
+        table[f"{kind}@{length}"] = cell
+        print(f"{kind:9s} length {length:6d}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
     if a.out:
         with open(a.out, "w") as f:
             json.dump({"step": step, "probes": table}, f, indent=1)

@@ -341,6 +341,14 @@ def test_eval_scripts_run_on_a_checkpoint(tmp_path):
     run(str(root / "scripts/eval_long.py"), "--checkpoint", str(tmp_path / "run"), "--docs", str(tmp_path / "long.pt"), "--base", "16",
         "--chunk", "16", "--gdn-diag", "--window", "16", "--train-len", "16", "--summary", str(tmp_path / "l.md"), "--device", "cpu",
         "--out", str(tmp_path / "l.json"))
+    run(str(root / "scripts/build_probes.py"), "--vocab", str(V), "--lengths", "40", "--per-kind", "2", "--kinds", "needle,mf_concat",
+        "--out", str(tmp_path / "probes.pt"))
+    run(str(root / "scripts/build_probes.py"), "--vocab", str(V), "--lengths", "40,64", "--per-kind", "3", "--kinds", "needle,mf_concat",
+        "--extend", str(tmp_path / "probes.pt"), "--out", str(tmp_path / "probes2.pt"))
+    run(str(root / "scripts/eval_probes.py"), "--checkpoint", str(tmp_path / "run"), "--set", str(tmp_path / "probes2.pt"), "--device", "cpu",
+        "--out", str(tmp_path / "p2.json"))
+    t2 = json.loads((tmp_path / "p2.json").read_text())["probes"]
+    assert set(t2) == {"needle@40", "mf_concat@40", "needle@64", "mf_concat@64"} and t2["needle@64"]["n"] == 3
     run(str(root / "scripts/report_pcr.py"), "--checkpoint", str(tmp_path / "run"), "--set", f"x={tmp_path / 'set.pt'}", "--set",
         f"y={tmp_path / 'set.pt'}", "--seq-len", "64", "--edges", "0,8,32", "--copy-lengths", "8,16", "--copy-items", "2", "--device", "cpu",
         "--out", str(tmp_path / "r.json"))
