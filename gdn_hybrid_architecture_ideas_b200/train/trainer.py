@@ -135,6 +135,15 @@ class Trainer:
         if cfg.cuda_graphs != "none":
             from .cuda_graphs import GraphRunner
 
+            e = cfg.model.encoder
+            tensor_op_arms = [name for on, name in (
+                (e.attention.normalizer != "softmax", "attention.normalizer 'asentmax'"), (e.gdn.kda.decay != "scalar", "gdn.kda.decay 'channel'"),
+                (e.gdn.erase.mode != "none", "gdn.erase.mode 'eda'"), (e.gdn.dprod.n_h != 1, "gdn.dprod.n_h >= 2"),
+                (e.attn_res == "ldm", "attn_res 'ldm'")) if on]
+            if tensor_op_arms:      # their rules run as eager tensor ops (recompute inside, chunk loops): not captured
+                raise ValueError(f"cuda_graphs {cfg.cuda_graphs!r} is not built with {', '.join(tensor_op_arms)}: these arms run as "
+                                 "tensor ops outside the captured step; train them with cuda_graphs 'none'")
+
             self.graphs = GraphRunner(self)
 
     # ------------------------------------------------------------------ construction

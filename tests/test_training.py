@@ -486,6 +486,10 @@ def test_linear_depth_memory(tmp_path):
     bad.encoder.attn_res = "ldm"
     with pytest.raises(ValueError):
         make_model(bad, dtype=torch.float32)
+    graphs = copy.deepcopy(tc)
+    graphs.cuda_graphs = "step"
+    with pytest.raises(ValueError, match="tensor ops"):
+        Trainer(graphs, tmp_path / "g")
 
 
 def test_train_mtp_script(tmp_path):
