@@ -573,3 +573,24 @@ def test_block_attn_res_trains(tmp_path, arm):
     assert l1 < l0
     want = "attn_res.pre_mlp.query" if arm == "block" else "attn_res.entry.net.head.weight"
     assert any(n.endswith(want) for n, _ in t.model.named_parameters())
+
+
+def test_every_run_entry_builds():
+    """Every entry of the shipped run files loads its config, applies its overrides and builds (meta device)."""
+    import yaml
+    from pathlib import Path
+
+    from gdn_hybrid_architecture_ideas_b200.models import build_model
+
+    root = Path(__file__).resolve().parent.parent
+    seen = 0
+    for path in sorted((root / "runs").glob("*.yaml")):
+        for entry in yaml.safe_load(path.read_text())["runs"]:
+            cfg = C.load_yaml(root / entry["config"])
+            for s in entry.get("set", []):
+                C.apply_override(cfg, s)
+            with torch.device("meta"):
+                model = build_model(cfg.model)
+            assert sum(p.numel() for p in model.parameters()) > 0, entry["name"]
+            seen += 1
+    assert seen >= 10
