@@ -185,8 +185,9 @@ def multifact_metrics(p: Probe, ok: list[bool], nats: list[float]) -> dict:
 
 
 @torch.no_grad()
-def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype=None) -> dict:
-    """Teacher-forced: exact = every answer token is the argmax given the true prefix."""
+def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype=None, keep_tokens: bool = False) -> dict:
+    """Teacher-forced: exact = every answer token is the argmax given the true prefix. keep_tokens: every item also
+    carries its per-token record ("ok", "nats") and its index, what `eval/probe_analysis.py` reads."""
     dev = next(model.parameters()).device
     exact, ce_sum, n_tok, per = 0, 0.0, 0, []
     for s in range(0, len(probes), batch_size):
@@ -213,6 +214,8 @@ def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype
                 item["group"] = p.group
             if p.pieces:         # the headline of a multi-fact item counts the fact tokens only
                 item.update(multifact_metrics(p, (top[b, sl] == tgt[b, sl]).tolist(), ce[b, sl].tolist()), exact_all=hit)
+            if keep_tokens:
+                item.update(index=s + b, ok=(top[b, sl] == tgt[b, sl]).tolist(), nats=ce[b, sl].tolist())
             exact += int(item["exact"])
             per.append(item)
     return {"exact": exact / max(len(probes), 1), "ce": ce_sum / max(n_tok, 1), "n": len(probes), "items": per}

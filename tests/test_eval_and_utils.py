@@ -827,3 +827,32 @@ def test_recall_items_plan(tmp_path):
     with pytest.raises(ValueError, match="not scored"):
         ri.values_for_run("r", small, res[:2])
     assert abs(ri.binomial_se(0.5, 100) - 0.05) < 1e-12 and ri.items_for_se(0.5, 0.025) == 400
+
+
+def test_probe_analysis():
+    """Item metrics from the per-token record, pooled and clustered values, paired differences, first-error histogram."""
+    from gdn_hybrid_architecture_ideas_b200.eval import probe_analysis as pa, probes
+    from tests.helpers import make_model
+
+    m = pa.item_metrics([True, True, False, True], [0.1, 0.2, 2.0, 0.3])
+    assert m["exact"] == 0 and m["token_acc"] == 0.75 and m["first_err_frac"] == 0.5 and m["first_acc"] == 1
+    assert abs(m["nats_per_token_rest"] - 2.5 / 3) < 1e-12 and abs(m["exp_exact_t1"] - math.exp(-2.6)) < 1e-12
+    assert "exact_rest" not in pa.item_metrics([True], [0.5]) and pa.item_metrics([True], [0.5])["first_err_frac"] == 1.0
+    model = make_model(C.tiny_control_config(), dtype=torch.float32).eval()
+    ps = [probes.build_probe("transcode", 256, 60, 0, i) for i in range(8)]
+    res = probes.score_probes(model, ps, batch_size=3, keep_tokens=True)
+    items = pa.with_metrics(res["items"])
+    assert [it["index"] for it in items] == list(range(8)) and len(items[0]["ok"]) == ps[0].answer_len
+    assert abs(sum(it["nats_per_token"] * it["tokens"] for it in items) / sum(it["tokens"] for it in items) - res["ce"]) < 1e-5
+    base = lambda it: it["index"] // 2
+    pc = pa.pooled_clustered(items, base)
+    assert pc["clusters"] == 4 and pa.pooled(items)["n"] == 8
+    d = pa.paired_difference(items, base, lambda it: it["group"], "esc2raw", "raw2esc")
+    want = sum(items[2 * i]["nats_per_token"] - items[2 * i + 1]["nats_per_token"] for i in range(4)) / 4
+    assert d["pairs"] == 4 and abs(d["diff"] - want) < 1e-12
+    table = pa.marginal_table(items, ("kind", "group"))
+    assert set(table) == {"transcode|esc2raw", "transcode|raw2esc"} and table["transcode|esc2raw"]["exact"]["n"] == 4
+    h = pa.first_error_hist(items)
+    assert sum(h["counts"]) + round(h["no_error"] * h["n"]) == 8
+    same = pa.paired_between_runs(items, items, ident=lambda it: it["index"])
+    assert same["diff"] == 0 and same["n"] == 8
