@@ -175,8 +175,10 @@ def run_ours(args) -> dict:
         dp.barrier()
     e2e_ms = max_over_ranks(start.elapsed_time(end), dp) / args.steps
     clocks = sampler.stop(world)
+    ops.check_status()          # a bounded wait that gave up inside a kernel voids the run
     tokens = job_rows * args.seq_len
     base = baseline_number()
+    zero = trainer.zero
     value = tokens / (dev_ms / 1e3)
     out = {
         "metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -186,7 +188,9 @@ def run_ours(args) -> dict:
                    "seq_len": args.seq_len,
                    "parallelism": (f"tp{world}-sp-{args.tp_impl}" if tp else f"dp{world}" + ("" if world == 1 else f"-{cfg.optimizer_sharding}")),
                    "optimizer": "adamw", "vocab": VOCAB, "l2": "per-step working set (GBs of activations) >> 126 MB L2",
-                   "comm": os.environ.get("GHB_COMM", "auto"), "cuda_graphs": cfg.cuda_graphs, "loss": m["loss"]},
+                   "comm": os.environ.get("GHB_COMM", "auto"), "fused": bool(zero is not None and zero.fused is not None),
+                   "multimem": bool(zero is not None and zero.fused is not None and zero.fused.multimem),
+                   "cuda_graphs": cfg.cuda_graphs, "loss": m["loss"]},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": trainer.h2d_bytes, "d2h_bytes_per_step": trainer.d2h_bytes},
@@ -338,7 +342,7 @@ def run_reference(args) -> dict:
         ms = float(t[0])
     ms /= args.steps
     clocks = sampler.stop(world)
-    tokens = job_rows * args.seq_len
+    tokens = args.rows * world * args.seq_len
     value = tokens / (ms / 1e3)
     loss = m.get("loss") if isinstance(m, dict) else None
     out = {"metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,

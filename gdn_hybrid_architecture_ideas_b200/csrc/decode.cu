@@ -228,6 +228,10 @@ extern "C" int ghb_decode_attention_noalloc(const float* q, const void* k, const
                                             int cap, int n_angles, int splits, float scale, void* stream, char* errbuf, int errlen) {
   if (B < 1 || T < 1 || Hq < 1 || Hkv < 1 || splits < 1)
     return fail(1, errbuf, errlen, "ghb_decode_attention_noalloc: B, T, Hq, Hkv and splits must be positive");
+  if (!q || !k || !v || !lens || !out)
+    return fail(1, errbuf, errlen, "ghb_decode_attention_noalloc: q, k, v, lens and out must be device pointers");
+  if (rot < 0 || (rot > 0 && (n_angles < 1 || !cos_t || !sin_t)))
+    return fail(1, errbuf, errlen, "ghb_decode_attention_noalloc: a rotary width above 0 needs cos/sin tables with at least one angle row");
   const size_t need = static_cast<size_t>(B) * Hq * splits * 66;
   if (need > NOALLOC_FLOATS) {
     char msg[200];

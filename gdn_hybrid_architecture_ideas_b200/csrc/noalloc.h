@@ -23,7 +23,8 @@ extern "C" {
 // out [B, Hq, 64] (bf16). Same arithmetic as the regular decode attention entry. `stream` is a cudaStream_t.
 //
 // Returns 0 on success. On failure returns a nonzero code and, when errbuf is not null, writes a message of at most
-// errlen bytes: 1 = a size beyond the limits above (or an unsupported head grouping / rotary width), 2 = the device
+// errlen bytes: 1 = a size beyond the limits above, a null input / output pointer, a rotary width above 0 without angle
+// tables (n_angles < 1 or a null table), or an unsupported head grouping / rotary width; 2 = the device
 // address of the scratch array could not be obtained, 4 = the launch was refused by the runtime.
 //
 // The first call on each device resolves the device address of the scratch array (cudaGetSymbolAddress) with that

@@ -176,6 +176,31 @@ def norm_add(resid, branch, weight, eps, scale):
     return resid + scale * ref.rmsnorm(branch, weight, eps)
 
 
+_cpu_status = torch.zeros(1, dtype=torch.int32)
+
+
+def status_word(device) -> torch.Tensor:
+    """The per-device int32 word that kernels write when a bounded wait gives up (0 = clean). On the CPU a process-wide
+    word with the same contract (nothing writes it but tests and host-side fault injection)."""
+    if torch.device(device).type == "cuda":
+        return _native().err_flag(device)
+    return _cpu_status
+
+
+def clear_status(device) -> None:
+    status_word(device).zero_()
+
+
+def check_status() -> None:
+    """Raises if any device's status word is non-zero (one host read per device), and clears it."""
+    code = int(_cpu_status.item())
+    if code:
+        _cpu_status.zero_()
+        raise RuntimeError(f"status {code} reported on the CPU status word")
+    if torch.cuda.is_available():
+        _native().check_status()
+
+
 def launch_count() -> int:
     """Kernels of this framework launched since the last reset (bench.py reports it)."""
     from . import native

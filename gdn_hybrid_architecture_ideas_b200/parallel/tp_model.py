@@ -73,45 +73,111 @@ def replicated_parameters(model) -> list:
     return [p for p in model.parameters() if not getattr(p, "tp_sharded", False)]
 
 
-def _head_rows(n_heads: int, dim: int, rank: int, world: int, base: int = 0):
-    per = n_heads // world
-    return slice(base + rank * per * dim, base + (rank + 1) * per * dim)
+def _split_plan(name: str, cfg: ModelConfig):
+    """How one named tensor of the full model is cut over ranks: (dim, [(units, unit width), ...]) — along `dim` the
+    tensor is a concatenation of sections, each `units` equal pieces of `width` entries, and rank r owns pieces
+    r*units/W .. (r+1)*units/W - 1 of every section — or None for a replicated tensor."""
+    enc = cfg.encoder
+    a, g = enc.attention, enc.gdn
+    if ".layers." not in name:
+        return None
+    leaf = name.rsplit(".", 1)[-1]
+    owner = name.rsplit(".", 2)[-2] if name.count(".") else ""
+    if owner == "in_proj_qkv" or leaf == "conv_weight":
+        return 0, [(g.n_k_heads, g.k_head_dim), (g.n_k_heads, g.k_head_dim), (g.n_v_heads, g.v_head_dim)]
+    if owner == "in_proj_z":
+        return 0, [(g.n_v_heads, g.v_head_dim)]
+    if owner in ("in_proj_a", "in_proj_b") or leaf in ("A_log", "dt_bias"):
+        return 0, [(g.n_v_heads, 1)]
+    if owner == "out_proj":
+        return 1, [(g.n_v_heads, g.v_head_dim)]
+    if owner == "q_proj":
+        return 0, [(a.n_q_heads, a.head_dim * (2 if a.gate == "elementwise" else 1))]
+    if owner == "g_proj" or leaf == "temp_w":
+        return 0, [(a.n_q_heads, 1)]
+    if owner in ("k_proj", "v_proj"):
+        return 0, [(a.n_kv_heads, a.head_dim)]
+    if owner == "o_proj":
+        return 1, [(a.n_q_heads, a.head_dim)]
+    if owner in ("w_gate", "w_up"):
+        return 0, [(cfg.ffn_hidden, 1)]
+    if owner == "w_down":
+        return 1, [(cfg.ffn_hidden, 1)]
+    return None
+
+
+def shard_tensor(name: str, t: torch.Tensor, cfg: ModelConfig, rank: int, world: int) -> torch.Tensor:
+    plan = _split_plan(name, cfg)
+    if plan is None:
+        return t.clone()
+    dim, sections = plan
+    parts, base = [], 0
+    for units, width in sections:
+        per = units // world * width
+        parts.append(t.narrow(dim, base + rank * per, per))
+        base += units * width
+    return torch.cat(parts, dim).clone()
+
+
+def merge_tensor(name: str, shards: list, cfg: ModelConfig) -> torch.Tensor:
+    """Inverse of `shard_tensor`: the full tensor from every rank's slice (replicated tensors: rank 0's)."""
+    plan = _split_plan(name, cfg)
+    if plan is None:
+        return shards[0].clone()
+    dim, sections = plan
+    world = len(shards)
+    out, base = [], 0
+    for units, width in sections:
+        per = units // world * width
+        out.extend(s.narrow(dim, base, per) for s in shards)
+        base += per
+    return torch.cat(out, dim).clone()
 
 
 def shard_state_dict(full: dict, cfg: ModelConfig, rank: int, world: int) -> dict:
-    """One rank's slice of a full model's state dict."""
-    enc = cfg.encoder
-    a, g = enc.attention, enc.gdn
-    nq, nv = g.n_k_heads * g.k_head_dim, g.n_v_heads * g.v_head_dim
-    out = {}
-    for name, t in full.items():
-        leaf = name.rsplit(".", 1)[-1]
-        owner = name.rsplit(".", 2)[-2] if name.count(".") else ""
-        if ".layers." not in name:
-            out[name] = t.clone()
-            continue
-        if owner == "in_proj_qkv" or leaf == "conv_weight":
-            parts = [t[_head_rows(g.n_k_heads, g.k_head_dim, rank, world)], t[_head_rows(g.n_k_heads, g.k_head_dim, rank, world, nq)],
-                     t[_head_rows(g.n_v_heads, g.v_head_dim, rank, world, 2 * nq)]]
-            out[name] = torch.cat(parts, 0).clone()
-        elif owner == "in_proj_z":
-            out[name] = t[_head_rows(g.n_v_heads, g.v_head_dim, rank, world)].clone()
-        elif owner in ("in_proj_a", "in_proj_b") or leaf in ("A_log", "dt_bias"):
-            out[name] = t[_head_rows(g.n_v_heads, 1, rank, world)].clone()
-        elif owner == "out_proj":
-            out[name] = t[:, _head_rows(g.n_v_heads, g.v_head_dim, rank, world)].clone()
-        elif owner == "q_proj":
-            out[name] = t[_head_rows(a.n_q_heads, a.head_dim * (2 if a.gate == "elementwise" else 1), rank, world)].clone()
-        elif owner == "g_proj" or leaf == "temp_w":
-            out[name] = t[_head_rows(a.n_q_heads, 1, rank, world)].clone()
-        elif owner in ("k_proj", "v_proj"):
-            out[name] = t[_head_rows(a.n_kv_heads, a.head_dim, rank, world)].clone()
-        elif owner == "o_proj":
-            out[name] = t[:, _head_rows(a.n_q_heads, a.head_dim, rank, world)].clone()
-        elif owner in ("w_gate", "w_up"):
-            out[name] = t[_head_rows(cfg.ffn_hidden, 1, rank, world)].clone()
-        elif owner == "w_down":
-            out[name] = t[:, _head_rows(cfg.ffn_hidden, 1, rank, world)].clone()
-        else:
-            out[name] = t.clone()
+    """One rank's slice of a full model's state dict (or of any by-name dict of tensors shaped like the parameters:
+    gradients, optimizer moments)."""
+    return {name: shard_tensor(name, t, cfg, rank, world) for name, t in full.items()}
+
+
+def merge_state_dicts(shards: list[dict], cfg: ModelConfig) -> dict:
+    """The full model's by-name dict from the ranks' dicts, rank order."""
+    return {name: merge_tensor(name, [s[name] for s in shards], cfg) for name in shards[0]}
+
+
+def init_full_then_shard(cfg: ModelConfig, local_cfg: ModelConfig, rank: int, world: int, seed: int, prepare=None):
+    """This rank's model holding ITS slice of the full model's seeded start: every rank draws the full model from the
+    same seed and keeps its cut, so the sharded run starts where the unsharded run with that seed does (ranks that
+    each seeded a local model would all hold the same slice-shaped draw). `prepare(full_model)` runs on the full
+    model before the cut (start-time rescalings)."""
+    from ..models import build_model
+
+    torch.manual_seed(seed)
+    full = build_model(cfg)
+    if prepare is not None:
+        prepare(full)
+    local = build_model(local_cfg)
+    local.load_state_dict(shard_state_dict(full.state_dict(), cfg, rank, world))
+    return local
+
+
+def shard_optimizer_state(sd: dict, cfg: ModelConfig, rank: int, world: int) -> dict:
+    """A full-model optimizer state (FlatAdamW.state_dict form: by-index state plus `names`) cut to one rank."""
+    out = {**sd, "state": {}}
+    for index, name in enumerate(sd["names"]):
+        st = sd["state"].get(index)
+        if st is not None:
+            out["state"][index] = {"step": st["step"], "exp_avg": shard_tensor(name, st["exp_avg"], cfg, rank, world),
+                                   "exp_avg_sq": shard_tensor(name, st["exp_avg_sq"], cfg, rank, world)}
+    return out
+
+
+def merge_optimizer_states(sds: list[dict], cfg: ModelConfig) -> dict:
+    """The full-model optimizer state from the ranks' states, rank order."""
+    out = {**sds[0], "state": {}}
+    for index, name in enumerate(sds[0]["names"]):
+        sts = [sd["state"].get(index) for sd in sds]
+        if sts[0] is not None:
+            out["state"][index] = {"step": sts[0]["step"], "exp_avg": merge_tensor(name, [s["exp_avg"] for s in sts], cfg),
+                                   "exp_avg_sq": merge_tensor(name, [s["exp_avg_sq"] for s in sts], cfg)}
     return out

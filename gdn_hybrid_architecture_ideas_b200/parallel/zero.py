@@ -80,12 +80,11 @@ class ZeroPlan:
             return False
         try:
             self.fused = fused_comm.FusedComm(self.dp, self.flat, self.model, lambda p, g, lp: self.flat.rebind(self.model, p, g, lp))
-        except Exception as e:   # no symmetric memory on this system: the NCCL path stays
-            if want == "fused":
-                raise
-            if self.dp.lead:
-                print(f"[zero] fused peer-memory step unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
-            self.fused = None
+        except Exception as e:   # no symmetric memory on this system
+            # GHB_COMM=nccl is the way to ask for the collective path; falling back silently would let a benchmark
+            # report the NCCL step under the fused step's name
+            raise RuntimeError(f"the fused peer-memory data-parallel step could not be set up ({type(e).__name__}: {e}); "
+                               "set GHB_COMM=nccl to run the NCCL reduce-scatter / all-gather path instead") from e
         return self.fused is not None
 
     # ------------------------------------------------------------------ the step

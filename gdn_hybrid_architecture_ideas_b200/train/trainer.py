@@ -42,6 +42,10 @@ class Diverged(RuntimeError):
     pass
 
 
+class KernelStatus(RuntimeError):
+    """A kernel's bounded wait gave up during the step (the status word was non-zero on some rank)."""
+
+
 def pick_device(name: str) -> torch.device:
     if name == "auto":
         return torch.device("cuda" if torch.cuda.is_available() else "cpu")
@@ -74,11 +78,18 @@ class Trainer:
             if cfg.optimizer_sharding != "replicated" or cfg.tst.schedule:
                 raise ValueError("tensor_parallel runs with optimizer_sharding=replicated and without token superposition")
             model_cfg = tp_model.local_model_config(cfg.model, dp.world)
-        self.model = build_model(model_cfg).to(dtype).to(self.device)
+        mup = None
         if cfg.optim.gdn_mup:      # the gates' start with their learning rate (a resume then loads the trained values over it)
             from .optim import gdn_mup_init_
 
-            gdn_mup_init_(self.model, cfg.optim.gdn_mup_base_width)
+            def mup(m):
+                gdn_mup_init_(m, cfg.optim.gdn_mup_base_width)
+        if cfg.tensor_parallel > 1:     # the full model's seeded start, cut to this rank (ranks seeding local models would all hold the same draw)
+            self.model = tp_model.init_full_then_shard(cfg.model, model_cfg, dp.rank, dp.world, cfg.seed, mup).to(dtype).to(self.device)
+        else:
+            self.model = build_model(model_cfg).to(dtype).to(self.device)
+            if mup is not None:
+                mup(self.model)
         if cfg.tensor_parallel > 1:
             from ..parallel.tensor_parallel import TensorParallel
 
@@ -229,7 +240,7 @@ class Trainer:
     def device_step(self, batch, n_global: int, lr: float | None = None) -> torch.Tensor:
         """The device part of a step on a batch already on the device: zero gradients, micro-batch loop (forward,
         fused head + loss, backward), gradient synchronisation, clip, update. Returns a device tensor
-        (loss, ce sum, gradient norm); nothing is read back to the host here."""
+        (loss, ce sum, gradient norm, kernel status word); nothing is read back to the host here."""
         cfg = self.cfg
         lr = lr_of(cfg, self.step) if lr is None else lr
         self.flat.grads.zero_()
@@ -272,7 +283,10 @@ class Trainer:
         if not cfg.freeze_trunk:
             self.model.encoder.project_layer_scalars()      # the span-bounded residual scalars back into their range
         self.step += 1
-        return torch.stack([stats[0].float(), stats[1].float(), gnorm.float()])
+        from .. import ops
+
+        status = ops.status_word(self.device).to(torch.float32).reshape(())      # kernels' bounded waits report here (0 = clean)
+        return torch.stack([stats[0].float(), stats[1].float(), gnorm.float(), status])
 
     def train_step(self) -> dict:
         """One full training step through the public path: build this rank's batch (a pure function of the step),
@@ -297,7 +311,8 @@ class Trainer:
         dev_batch = batch.to(self.device)
         host = self.device_step(dev_batch, n_global, lr).cpu()      # the step's one device->host read
         self.d2h_bytes = host.numel() * host.element_size()
-        loss_v, ce_v, gn_v = (float(x) for x in host)
+        loss_v, ce_v, gn_v, status = (float(x) for x in host)
+        self._check_kernel_status(int(status), step)
         seconds = time.perf_counter() - t0
         s = batch.tokens.shape[2] if batch.tokens.dim() == 3 else 1
         n_tokens = cfg.data.batch_size * cfg.data.seq_len * s
@@ -385,6 +400,21 @@ class Trainer:
             self._jsonl({"event": "diverged", **{k: (str(v) if isinstance(v, float) and not math.isfinite(v) else v) for k, v in m.items()}})
         raise Diverged(f"non-finite loss at step {m['step']}")
 
+    def _check_kernel_status(self, code: int, step: int) -> None:
+        """A kernel whose bounded wait gave up (a late or lost rank, a protocol error) returns early and leaves partial
+        output behind, so the step that read it is void: every rank learns of any rank's code (MAX over the host group)
+        and all raise together, before metrics, checkpoints or another step."""
+        if self.dp is not None:
+            code = int(self.dp.max_host([code])[0])
+        if code:
+            from .. import ops
+
+            ops.clear_status(self.device)
+            if self.run_dir is not None and self.lead:
+                self._jsonl({"event": "kernel_status", "step": step, "code": code})
+            raise KernelStatus(f"step {step}: a kernel reported status {code} (a bounded wait gave up); the step's update is not trustworthy "
+                               "and no checkpoint is written")
+
     def _halt_bad_batch(self, step: int):
         info = {"rank": self.rank, "error": str(getattr(self, "_bad", "")), "rows": getattr(getattr(self, "_bad", None), "rows", [])}
         infos = self.dp.gather_host(info) if self.dp is not None else [info]
@@ -412,12 +442,21 @@ class Trainer:
         return state
 
     def state_dict(self) -> dict:
-        if self.zero is not None:
-            self.zero.gather_master()
+        model_state = {k: v.detach().clone() for k, v in self.model.state_dict().items()}
+        optim_state = self.optimizer.state_dict() if self.zero is None else self.zero.optimizer_state(self.optimizer)
+        if self.tp is not None:     # the checkpoint holds the FULL model and its moments: every rank's slices meet on the lead
+            from ..parallel import tp_model
+
+            cpu = lambda d: {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
+            opt_cpu = {**optim_state, "state": {i: cpu(st) for i, st in optim_state["state"].items()}}
+            parts = self.dp.gather_to_lead((cpu(model_state), opt_cpu))
+            if self.lead:
+                model_state = tp_model.merge_state_dicts([m for m, _ in parts], self.cfg.model)
+                optim_state = tp_model.merge_optimizer_states([o for _, o in parts], self.cfg.model)
         state = {
             "step": self.step, "config": C.to_dict(self.cfg),
-            "model": {k: v.detach().clone() for k, v in self.model.state_dict().items()},
-            "optimizer": self.optimizer.state_dict() if self.zero is None else self.zero.optimizer_state(self.optimizer),
+            "model": model_state,
+            "optimizer": optim_state,
             "torch_rng": torch.get_rng_state(),
             "cuda_rng": torch.cuda.get_rng_state_all() if self.device.type == "cuda" and self.dp is None else None,
             "python_rng": random.getstate(), "wandb_run_id": self.wandb_run_id, "data_state": self.data_state(),
@@ -451,6 +490,12 @@ class Trainer:
             diff = C.config_differences(C.to_dict(C.from_dict(C.TrainConfig, saved)), C.to_dict(self.cfg))
             if diff:
                 raise ValueError(f"the checkpoint was written by a run with a different config: {diff}")
+        if self.tp is not None:     # checkpoints hold the full model: keep this rank's slices
+            from ..parallel import tp_model
+
+            state = {**state, "model": tp_model.shard_state_dict(state["model"], self.cfg.model, self.rank, self.world)}
+            if not weights_only:
+                state["optimizer"] = tp_model.shard_optimizer_state(state["optimizer"], self.cfg.model, self.rank, self.world)
         with torch.no_grad():
             own = self.model.state_dict()
             missing = [k for k in own if k not in state["model"]]

@@ -7,7 +7,8 @@ import torch
 
 ROOT = Path(__file__).resolve().parent.parent
 sys.path.insert(0, str(ROOT))
-REFERENCE = Path("/root/reference/code")
+# the reference checkout used as an oracle: $GHB_REFERENCE_PATH, else a `reference` folder beside this repository
+REFERENCE = Path(os.environ.get("GHB_REFERENCE_PATH") or ROOT.parent / "reference") / "code"
 
 
 def pytest_configure(config):

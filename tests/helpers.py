@@ -3,6 +3,7 @@ not make a test vacuous), tiny models in float64."""
 
 from __future__ import annotations
 
+import os
 from pathlib import Path
 
 import torch
@@ -11,7 +12,7 @@ from gdn_hybrid_architecture_ideas_b200 import config as C
 from gdn_hybrid_architecture_ideas_b200.models import build_model
 
 
-REFERENCE = Path("/root/reference/code")
+REFERENCE = Path(os.environ.get("GHB_REFERENCE_PATH") or Path(__file__).resolve().parent.parent.parent / "reference") / "code"
 
 
 def perturb(model, scale: float = 0.05, seed: int = 1):

@@ -56,9 +56,14 @@ def test_no_alloc_entry_matches_regular_entry_twice():
                 B, T, Hq, Hkv, rot, cap, cap + 1, splits, 0.125, stream, err, 256)
         assert rc == 0, err.value
         torch.cuda.synchronize()
-        assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), (got.float() - want.float()).abs().max()
+        assert torch.equal(got, want), (got.float() - want.float()).abs().max()      # the same kernels on the same inputs: bit for bit
     # a request larger than the built-in scratch is refused with a message and launches nothing
     err = ctypes.create_string_buffer(256)
     rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), lens.data_ptr(), None, cos_t.data_ptr(), sin_t.data_ptr(), got.data_ptr(),
             B, T, Hq, Hkv, rot, cap, cap + 1, 1 << 20, 0.125, stream, err, 256)
     assert rc == 1 and b"exceeds the built-in scratch" in err.value
+    # a rotary width without angle tables is refused before anything is launched
+    err = ctypes.create_string_buffer(256)
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), lens.data_ptr(), None, None, None, got.data_ptr(),
+            B, T, Hq, Hkv, rot, cap, 0, splits, 0.125, stream, err, 256)
+    assert rc == 1 and b"cos/sin tables" in err.value
