@@ -354,24 +354,29 @@ void decode_attention(const Tensor& q, const Tensor& k, const Tensor& v, const T
 }
 
 // ---- fused data-parallel step over peer memory. `peers` is a CPU uint8 tensor holding the pointer table.
-void comm_reduce(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, Tensor& shard, int64_t seq, Tensor& acc, Tensor& counter,
-                 Tensor& err) {
+void comm_reduce(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, Tensor& shard, int64_t ticket, int64_t publish_seq,
+                 Tensor& acc, Tensor& counter, Tensor& err, int64_t ctas) {
   const c10::cuda::CUDAGuard guard(shard.device());
   TORCH_CHECK(!peers.is_cuda() && peers.numel() == static_cast<int64_t>(ghb::comm_peers_bytes()), "comm_reduce: peer table of ", ghb::comm_peers_bytes(), " bytes");
   TORCH_CHECK(is_f32(shard) && shard.numel() >= n, "comm_reduce: fp32 shard");
-  check(ghb::comm_reduce(peers.data_ptr(), rank, world, lo, n, shard.data_ptr<float>(), static_cast<unsigned int>(seq), acc.data_ptr<float>(),
-                         reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), err.data_ptr<int>(), sm_count(), stream()), "comm_reduce");
+  check(ghb::comm_reduce(peers.data_ptr(), rank, world, lo, n, shard.data_ptr<float>(), static_cast<unsigned int>(ticket),
+                         static_cast<unsigned int>(publish_seq), acc.data_ptr<float>(), reinterpret_cast<unsigned int*>(counter.data_ptr<int>()),
+                         err.data_ptr<int>(), ctas > 0 ? static_cast<int>(ctas) : 2 * sm_count(), stream()), "comm_reduce");
 }
 void comm_update(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, const Tensor& shard, Tensor& m, Tensor& v,
                  const std::vector<int64_t>& group_start, const std::vector<double>& group_wd, const std::vector<double>& group_lr, double b1, double b2,
-                 double eps, double c1, double c2, double max_norm, int64_t seq, Tensor& norm_out, Tensor& counter, Tensor& err) {
+                 double eps, double c1, double c2, double max_norm, int64_t seq, bool first, Tensor& coef_buf, const c10::optional<Tensor>& fp32_map,
+                 int64_t ticket, Tensor& counter, Tensor& err, int64_t ctas) {
   const c10::cuda::CUDAGuard guard(shard.device());
   TORCH_CHECK(!peers.is_cuda() && peers.numel() == static_cast<int64_t>(ghb::comm_peers_bytes()), "comm_update: peer table");
+  TORCH_CHECK(is_f32(shard) && shard.numel() >= n && m.numel() >= n && v.numel() >= n && coef_buf.numel() >= 2, "comm_update: shard / moment sizes");
   std::vector<long> gs(group_start.begin(), group_start.end());
   std::vector<float> wd(group_wd.begin(), group_wd.end()), lr(group_lr.begin(), group_lr.end());
   check(ghb::comm_update(peers.data_ptr(), rank, world, lo, n, shard.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), gs.size(), gs.data(),
-                         wd.data(), lr.data(), b1, b2, eps, c1, c2, max_norm, static_cast<unsigned int>(seq), norm_out.data_ptr<float>(),
-                         reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), err.data_ptr<int>(), sm_count(), stream()), "comm_update");
+                         wd.data(), lr.data(), b1, b2, eps, c1, c2, max_norm, static_cast<unsigned int>(seq), first ? 1 : 0, coef_buf.data_ptr<float>(),
+                         fp32_map.has_value() ? reinterpret_cast<const unsigned int*>(fp32_map->data_ptr<int>()) : nullptr,
+                         static_cast<unsigned int>(ticket), reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), err.data_ptr<int>(),
+                         ctas > 0 ? static_cast<int>(ctas) : 2 * sm_count(), stream()), "comm_update");
 }
 void comm_wait_probe(const Tensor& flag, int64_t seq, int64_t limit_ns, Tensor& err) {
   const c10::cuda::CUDAGuard guard(flag.device());

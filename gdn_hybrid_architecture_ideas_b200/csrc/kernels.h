@@ -90,11 +90,13 @@ int decode_attention(const float* q, const void* k, const void* v, const int* le
 // Fused data-parallel step over peer memory (csrc/comm.cu). `peers` points at a host copy of the CommPeers table
 // (comm_peers_bytes() bytes: 5 arrays of 8 device pointers, then 3 multicast pointers).
 size_t comm_peers_bytes();
-int comm_reduce(const void* peers, int rank, int world, long lo, long n, float* shard, unsigned int seq, float* block_acc,
-                unsigned int* done_counter, int* err, int sms, cudaStream_t st);
+// `ctas`: grid size (a few CTAs for a launch that overlaps the backward, every SM for one that is exposed).
+int comm_reduce(const void* peers, int rank, int world, long lo, long n, float* shard, unsigned int ticket, unsigned int publish_seq,
+                float* block_acc, unsigned int* done_counter, int* err, int ctas, cudaStream_t st);
 int comm_update(const void* peers, int rank, int world, long lo, long n, const float* shard, float* m, float* v, int n_groups,
                 const long* group_start, const float* group_wd, const float* group_lr, float b1, float b2, float eps, float c1, float c2,
-                float max_norm, unsigned int seq, float* norm_out, unsigned int* done_counter, int* err, int sms, cudaStream_t st);
+                float max_norm, unsigned int seq, int first, float* coef_buf, const unsigned int* fp32_map, unsigned int ticket,
+                unsigned int* done_counter, int* err, int ctas, cudaStream_t st);
 int comm_wait_probe(const unsigned int* flag, unsigned int seq, unsigned long long limit_ns, int* err, cudaStream_t st);
 
 // Tensor-parallel GEMMs fused with the sequence-parallel all-gather / reduce-scatter (csrc/gemm_tp.cu). `args` points at a

@@ -191,6 +191,9 @@ class Encoder(nn.Module):
         self.ldm = enc.attn_res == "ldm"                  # linear depth memory: a per-position memory beside the stream
         self.activation_checkpoint = "none"
         self.host_pool = None
+        # bucketed data parallelism (parallel/zero.py): an object with forward_enter(block) / backward_done(block), told when
+        # the forward is about to read a block's matrices and when the gradient of a block's input is complete
+        self.stage_hooks = None
         d, eps, S, n = cfg.d_model, cfg.norm_eps, self.block, enc.n_layers
         H = enc.attn_res_heads
         if type(H) is not int or H < 1 or d % H:
@@ -279,6 +282,16 @@ class Encoder(nn.Module):
         """After an optimizer step: the span form's stored u back into [-3, 3] (reference: ced/train/trainer.py:3135)."""
         if self.scalar_form == "skip_x0_span":
             self.skip_gain.clamp_(-SPAN_CLAMP, SPAN_CLAMP)
+
+    def _stage(self, b: int, x: torch.Tensor) -> None:
+        """Block b starts at stream x: tell the data-parallel plan (if one listens) now, and again when x's gradient is
+        complete — by then every backward node of the block's layers has run, so their matrices' gradients are final."""
+        h = self.stage_hooks
+        if h is None:
+            return
+        h.forward_enter(b)
+        if torch.is_grad_enabled() and x.requires_grad:
+            x.register_hook(lambda g, b=b: h.backward_done(b))
 
     def _run(self, layer, x, ctx, cache, sources, need_state, scalars=None, premixed=None):
         """One layer call under the stack's activation memory mode (models/act_checkpoint.py)."""
@@ -394,6 +407,8 @@ class Encoder(nn.Module):
             return x, new_caches
         if not self.block_entry:
             for i, layer in enumerate(self.layers):
+                if self.block > 0 and i % self.block == 0 and len(self.layers) % self.block == 0:
+                    self._stage(i // self.block, x)
                 x, c = self._run(layer, x, ctx, get(i), None, need_state, scal(i))
                 new_caches.append(c)
             return x, new_caches
@@ -412,6 +427,7 @@ class Encoder(nn.Module):
             if b > 0 and first.stream_bf16:
                 start = round_stream(start)
             x = start
+            self._stage(b, x)
             if self.activation_checkpoint == "block" and sc is None and caches is None and torch.is_grad_enabled() and x.requires_grad:
                 x = self._run_block(b, x, ctx, sources)
                 new_caches.extend([None] * S)

@@ -126,13 +126,18 @@ class Segment:
 class FlatBuffers:
     """The model's parameters re-homed into flat buffers, group by group (each group one contiguous range)."""
 
-    def __init__(self, model, groups: list[dict], device, lp_dtype=None):
+    def __init__(self, model, groups: list[dict], device, lp_dtype=None, order=None):
+        """order: optional key function over parameter names; a group's tensors are laid out sorted by it (stable), so
+        tensors whose gradients finish together can be made neighbours (bucketed gradient reduction)."""
         self.segments: list[Segment] = []
         self.group_ranges: list[tuple[int, int]] = []
         at = 0
         for gi, g in enumerate(groups):
             lo = at
-            for n, p in zip(g["names"], g["params"]):
+            members = list(zip(g["names"], g["params"]))
+            if order is not None:
+                members.sort(key=lambda np_: order(np_[0]))
+            for n, p in members:
                 self.segments.append(Segment(n, at, p.numel(), tuple(p.shape), gi))
                 at += -(-p.numel() // ALIGN) * ALIGN
             self.group_ranges.append((lo, at))
@@ -207,20 +212,32 @@ class FlatAdamW:
     shard (lo, hi): the element range this rank updates (ZeRO); moments exist for that range only. On CUDA the update
     of a group is one launch of the fused kernel (moments, master weight and bf16 copy in one pass)."""
 
-    def __init__(self, flat: FlatBuffers, groups: list[dict], betas, eps: float, shard: tuple[int, int] | None = None):
+    def __init__(self, flat: FlatBuffers, groups: list[dict], betas, eps: float, shard=None):
+        """shard: None (everything), one (lo, hi) element range, or a list of disjoint ascending ranges (a rank's slices
+        of several buckets); the moments are stored range after range."""
         self.flat, self.groups = flat, groups
         self.betas, self.eps = tuple(betas), eps
-        self.lo, self.hi = shard or (0, flat.size)
-        n = self.hi - self.lo
+        ranges = [(0, flat.size)] if shard is None else ([tuple(shard)] if isinstance(shard[0], int) else [tuple(r) for r in shard])
+        self.ranges, n = [], 0          # (lo, hi, offset of the range in the moment buffers)
+        for lo, hi in ranges:
+            self.ranges.append((lo, hi, n))
+            n += hi - lo
+        self.lo, self.hi = ranges[0][0], ranges[-1][1]
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=flat.params.device)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=flat.params.device)
         self.steps = 0
         self.param_groups = [{"lr": 0.0, "lr_scale": g["lr_scale"], "weight_decay": g["weight_decay"], "kind": g["kind"]}
                              for g in groups]
 
-    def owned(self, gi: int) -> tuple[int, int]:
+    def owned(self, gi: int) -> list[tuple[int, int, int]]:
+        """(first element, end, offset in the moment buffers) of every owned piece of group gi."""
         glo, ghi = self.flat.group_ranges[gi]
-        return max(glo, self.lo), min(ghi, self.hi)
+        return [(max(glo, lo), min(ghi, hi), off + max(glo, lo) - lo) for lo, hi, off in self.ranges if min(ghi, hi) > max(glo, lo)]
+
+    def pieces(self, s: Segment) -> list[tuple[int, int, int]]:
+        """(first element, end, offset in the moment buffers) of the owned pieces of one tensor."""
+        return [(max(s.offset, lo), min(s.offset + s.numel, hi), off + max(s.offset, lo) - lo) for lo, hi, off in self.ranges
+                if min(s.offset + s.numel, hi) > max(s.offset, lo)]
 
     @torch.no_grad()
     def step(self, lr: float, grad_scale: torch.Tensor | float = 1.0, kinds=("adamw",)) -> None:
@@ -233,24 +250,22 @@ class FlatAdamW:
             g["lr"] = lr * g["lr_scale"]
             if g["kind"] not in kinds:
                 continue
-            a, b = self.owned(gi)
-            if b <= a:
-                continue
-            p, gr = self.flat.params[a:b], self.flat.grads[a:b]
-            m, v = self.exp_avg[a - self.lo:b - self.lo], self.exp_avg_sq[a - self.lo:b - self.lo]
-            lp = None if self.flat.lp is None else self.flat.lp[a:b]
-            if p.is_cuda:
-                from ..ops import native
+            for a, b, off in self.owned(gi):
+                p, gr = self.flat.params[a:b], self.flat.grads[a:b]
+                m, v = self.exp_avg[off:off + b - a], self.exp_avg_sq[off:off + b - a]
+                lp = None if self.flat.lp is None else self.flat.lp[a:b]
+                if p.is_cuda:
+                    from ..ops import native
 
-                native.adamw_(p, gr, m, v, lp, g["lr"], b1, b2, self.eps, g["weight_decay"], c1, c2, grad_scale)
-                continue
-            gs = gr * grad_scale
-            p.mul_(1.0 - g["lr"] * g["weight_decay"])
-            m.lerp_(gs, 1.0 - b1)
-            v.mul_(b2).addcmul_(gs, gs, value=1.0 - b2)
-            p.addcdiv_(m, (v / c2).sqrt_().add_(self.eps), value=-g["lr"] / c1)
-            if lp is not None:
-                lp.copy_(p)
+                    native.adamw_(p, gr, m, v, lp, g["lr"], b1, b2, self.eps, g["weight_decay"], c1, c2, grad_scale)
+                    continue
+                gs = gr * grad_scale
+                p.mul_(1.0 - g["lr"] * g["weight_decay"])
+                m.lerp_(gs, 1.0 - b1)
+                v.mul_(b2).addcmul_(gs, gs, value=1.0 - b2)
+                p.addcdiv_(m, (v / c2).sqrt_().add_(self.eps), value=-g["lr"] / c1)
+                if lp is not None:
+                    lp.copy_(p)
 
     # ---- torch.optim-shaped state for checkpoints (reference: ced/train/trainer.py:3602-3627 saves optimizer.state_dict())
     def state_dict(self) -> dict:
@@ -259,8 +274,9 @@ class FlatAdamW:
         for gi, g in enumerate(self.param_groups):
             ids = []
             for s in (s for s in self.flat.segments if s.group == gi):
-                if g["kind"] == "adamw" and s.offset >= self.lo and s.offset + s.numel <= self.hi:
-                    a = s.offset - self.lo
+                own = self.pieces(s)
+                if g["kind"] == "adamw" and len(own) == 1 and own[0][1] - own[0][0] == s.numel:      # wholly this rank's
+                    a = own[0][2]
                     state[index] = {"step": torch.tensor(float(self.steps)),
                                     "exp_avg": self.exp_avg[a:a + s.numel].view(s.shape).clone(),
                                     "exp_avg_sq": self.exp_avg_sq[a:a + s.numel].view(s.shape).clone()}
@@ -274,11 +290,11 @@ class FlatAdamW:
         for index, name in enumerate(names):
             st = sd["state"].get(index)
             s = self.flat.by_name.get(name)
-            if st is None or s is None or s.offset < self.lo or s.offset + s.numel > self.hi:
+            if st is None or s is None:
                 continue
-            a = s.offset - self.lo
-            self.exp_avg[a:a + s.numel].copy_(st["exp_avg"].reshape(-1))
-            self.exp_avg_sq[a:a + s.numel].copy_(st["exp_avg_sq"].reshape(-1))
+            for a, b, off in self.pieces(s):      # by name, so a state written at another world size or layout loads
+                self.exp_avg[off:off + b - a].copy_(st["exp_avg"].reshape(-1)[a - s.offset:b - s.offset])
+                self.exp_avg_sq[off:off + b - a].copy_(st["exp_avg_sq"].reshape(-1)[a - s.offset:b - s.offset])
             self.steps = int(st["step"])
 
     def reset_moments(self) -> None:

@@ -156,6 +156,8 @@ class Trainer:
                                  "tensor ops outside the captured step; train them with cuda_graphs 'none'")
 
             self.graphs = GraphRunner(self)
+            if self.zero is not None:      # a captured micro-batch cannot launch per-bucket reductions from its hooks
+                self.model.encoder.stage_hooks = None
 
     # ------------------------------------------------------------------ construction
 
@@ -243,6 +245,8 @@ class Trainer:
         (loss, ce sum, gradient norm, kernel status word); nothing is read back to the host here."""
         cfg = self.cfg
         lr = lr_of(cfg, self.step) if lr is None else lr
+        if self.zero is not None:
+            self.zero.before_step()     # the last step's first-read parameters have landed; peers are done with its gradients
         self.flat.grads.zero_()
         rows = batch.tokens.shape[0]
         micro = cfg.micro_batch_size or rows
@@ -257,6 +261,8 @@ class Trainer:
                 loss_sum += loss
             else:
                 loss, ce = self._micro_loss(mb, max(n_global, 1))
+                if self.zero is not None:       # gradients are final after the last micro-batch: its finished buckets may leave
+                    self.zero.armed = lo + micro >= rows
                 loss.backward()
                 loss_sum += loss.detach().float()
             ce_sum += ce.float()
@@ -280,7 +286,9 @@ class Trainer:
                 self.dp.all_reduce_(stats)
             gnorm = grad_norm(self.flat)
             self.optimizer.step(lr, _clip_coef(gnorm, cfg.optim.grad_clip))
-        if not cfg.freeze_trunk:
+        if not cfg.freeze_trunk and self.model.encoder.scalar_form != "none":
+            if self.zero is not None:
+                self.zero.settle()
             self.model.encoder.project_layer_scalars()      # the span-bounded residual scalars back into their range
         self.step += 1
         from .. import ops
@@ -326,6 +334,8 @@ class Trainer:
         if not math.isfinite(loss_v):
             self._halt_diverged(m)
         if self.dp is not None and self.dp.check_every and self.step % self.dp.check_every == 0:
+            if self.zero is not None:
+                self.zero.gather_master()
             self.dp.check_replicas(list(self.model.named_parameters()))
         return m
 
@@ -442,6 +452,8 @@ class Trainer:
         return state
 
     def state_dict(self) -> dict:
+        if self.zero is not None:
+            self.zero.gather_master()      # fp32 masters that live on their owners only, to every rank (collective)
         model_state = {k: v.detach().clone() for k, v in self.model.state_dict().items()}
         optim_state = self.optimizer.state_dict() if self.zero is None else self.zero.optimizer_state(self.optimizer)
         if self.tp is not None:     # the checkpoint holds the FULL model and its moments: every rank's slices meet on the lead

@@ -27,9 +27,14 @@ def main():
     losses = [t.train_step()["loss"] for _ in range(3)]
     native.check_status()
     fused = t.zero is not None and t.zero.fused is not None
+    lp_before = t.flat.lp.detach().float().cpu().clone()      # the bf16 compute weights are complete on every rank after a step
+    t.zero.gather_master()                                    # fp32 masters of the matrices live on their owners until gathered
+    torch.cuda.synchronize()
+    by_name = {n: t.flat.view(t.flat.params, n).detach().cpu().clone() for n in t.flat.by_name}       # by name: the two runs may lay the buffer out differently
+    lp_by_name = {n: lp_before[t.flat.by_name[n].offset:t.flat.by_name[n].offset + t.flat.by_name[n].numel].clone() for n in t.flat.by_name}
     if dp.lead:
-        torch.save({"losses": losses, "fused": fused, "multimem": bool(fused and t.zero.fused.multimem),
-                    "params": t.flat.params.detach().cpu().clone()}, sys.argv[1])
+        torch.save({"losses": losses, "fused": fused, "multimem": bool(fused and t.zero.fused.multimem), "early": t.zero.early,
+                    "params": by_name, "lp": lp_by_name}, sys.argv[1])
     dp.barrier()
     dp.close()
 

@@ -109,6 +109,10 @@ if mode == "status":
         print("NO RAISE", flush=True)
     except KernelStatus as e:
         print(f"rank {{dp.rank}} raised: {{e}}", flush=True)
+elif mode == "zero2":
+    for _ in range(2):
+        t.train_step()
+    print(f"rank {{dp.rank}} early {{t.zero.early}} buckets {{len(t.zero.buckets)}}", flush=True)
 else:
     # shards drawn from the full model's seed differ across ranks
     w = dict(t.model.named_parameters())
@@ -136,6 +140,13 @@ def _run_worker(tmp_path, cfg, mode, port):
 def test_one_ranks_status_stops_every_rank(tmp_path):
     out = _run_worker(tmp_path, _tiny(), "status", 29811)
     assert "rank 0 raised" in out and "rank 1 raised" in out and "NO RAISE" not in out, out
+
+
+def test_zero2_buckets_leave_during_the_backward(tmp_path):
+    """Stage 2 reduces each block's matrices from a hook inside the backward (only the last micro-batch's): 3 blocks,
+    2 steps -> 6 early reductions per rank; the equality with one process is tests/test_training.py's."""
+    out = _run_worker(tmp_path, _tiny(optimizer_sharding="zero2", micro_batch_size=1), "zero2", 29815)
+    assert "rank 0 early 6 buckets 4" in out and "rank 1 early 6 buckets 4" in out, out
 
 
 def _tp_config():
