@@ -179,6 +179,38 @@ void gdn_step(Tensor& S, const Tensor& q, const Tensor& k, const Tensor& v, cons
 }
 
 // x: [rows, n] fp32 or bf16 contiguous; out: bf16 like x; blocks of 32 along the last dimension, or along rows.
+// x [R, C] -> (q_row [R, C], sf_row) and / or (q_col [C, R], sf_col): uint8 tensors; a pair is skipped when its q is undefined.
+void mx_quantize(const Tensor& x, const c10::optional<Tensor>& q_row, const c10::optional<Tensor>& sf_row, const c10::optional<Tensor>& q_col,
+                 const c10::optional<Tensor>& sf_col) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && (is_f32(x) || is_bf16(x)), "mx_quantize: 2-D fp32 / bf16 input with unit inner stride");
+  const long R = x.size(0), C = x.size(1);
+  auto ok = [&](const c10::optional<Tensor>& q, const c10::optional<Tensor>& sf, long rows, long k) {
+    if (!q.has_value()) return true;
+    return sf.has_value() && q->is_contiguous() && q->numel() == rows * k && q->element_size() == 1 && sf->is_contiguous() &&
+           sf->element_size() == 1 && sf->numel() >= ghb::mx_scale_bytes(rows, k);
+  };
+  TORCH_CHECK(ok(q_row, sf_row, R, C) && ok(q_col, sf_col, C, R), "mx_quantize: output sizes");
+  check(ghb::mx_quantize(x.data_ptr(), is_bf16(x), R, C, x.stride(0), q_row.has_value() ? q_row->data_ptr() : nullptr,
+                         sf_row.has_value() ? sf_row->data_ptr() : nullptr, q_col.has_value() ? q_col->data_ptr() : nullptr,
+                         sf_col.has_value() ? sf_col->data_ptr() : nullptr, sm_count(), stream()), "mx_quantize");
+}
+int64_t mx_scale_bytes(int64_t rows, int64_t k) { return ghb::mx_scale_bytes(rows, k); }
+// out [M, N] (+)= a [M, K] b [N, K]^T over E4M3 bytes with scale cells.
+void gemm_mx(const Tensor& a, const Tensor& sfa, const Tensor& b, const Tensor& sfb, Tensor& out, bool accumulate, Tensor& err) {
+  const c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && out.dim() == 2 && a.is_contiguous() && b.is_contiguous() && out.stride(1) == 1 &&
+              a.element_size() == 1 && b.element_size() == 1, "gemm_mx: contiguous 1-byte operands");
+  const int M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(b.size(1) == K && out.size(0) == M && out.size(1) == N, "gemm_mx: shape mismatch");
+  TORCH_CHECK(sfa.numel() >= ghb::mx_scale_bytes(M, K) && sfb.numel() >= ghb::mx_scale_bytes(N, K), "gemm_mx: scale cells too small");
+  int mode;
+  if (is_bf16(out)) { TORCH_CHECK(!accumulate, "gemm_mx: accumulation needs an fp32 output"); mode = 0; }
+  else { TORCH_CHECK(is_f32(out), "gemm_mx: output bf16 or fp32"); mode = accumulate ? 2 : 1; }
+  const int rc = ghb::gemm_mxfp8(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), out.data_ptr(), M, N, K, out.stride(0), mode,
+                                 err.data_ptr<int>(), sm_count(), stream());
+  TORCH_CHECK(rc == 0, "gemm_mxfp8 refused (code ", rc, "): M=", M, " N=", N, " K=", K, " ldc=", out.stride(0), " cuerr=", ghb::last_encode_error());
+}
 void mx_fake(const Tensor& x, Tensor& out, bool along_rows) {
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && (is_f32(x) || is_bf16(x)) && is_bf16(out) && out.is_contiguous() && out.sizes() == x.sizes(), "mx_fake: layout");
@@ -479,6 +511,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_grad", &ce_grad);
   m.def("gdn_step", &gdn_step);
   m.def("mx_fake", &mx_fake);
+  m.def("mx_quantize", &mx_quantize);
+  m.def("mx_scale_bytes", &mx_scale_bytes);
+  m.def("gemm_mx", &gemm_mx);
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("decode_attention", &decode_attention);

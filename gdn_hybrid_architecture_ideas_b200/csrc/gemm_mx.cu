@@ -27,9 +27,6 @@ using namespace sm100;
 // ================================================================================================ quantiser
 namespace {
 
-__device__ __forceinline__ float mxq_to_float(float v) { return v; }
-__device__ __forceinline__ float mxq_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
-
 __device__ __forceinline__ int mxq_exponent(float amax) {
   const int bits = __float_as_int(amax * (1.0f / 448.0f));
   const int e = (bits >> 23) & 0xFF, m = bits & 0x7FFFFF;

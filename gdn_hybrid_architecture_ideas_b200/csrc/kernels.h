@@ -44,6 +44,13 @@ int depth_mix_bwd(const float* const* src, float* const* dsrc, int n, const floa
 int gdn_step(float* S, const float* q, const float* k, const float* v, const float* g, const float* beta, const unsigned char* start, float* o,
              int B, int Hk, int Hv, int dk, int dv, cudaStream_t st);
 int mx_fake(const void* x, bool x_bf16, void* out, long rows, long n, bool along_rows, int sms, cudaStream_t st);
+// MXFP8 on the tensor cores (csrc/gemm_mx.cu): quantiser to E4M3 + E8M0 scale cells (either or both block orientations
+// in one read) and the block-scaled GEMM D = A B^T over K-major E4M3 operands. out: 0 bf16, 1 fp32, 2 fp32 accumulate.
+long mx_scale_bytes(long rows, long k);
+int mx_quantize(const void* x, bool x_bf16, long R, long C, long ld, void* q_row, void* sf_row, void* q_col, void* sf_col, int sms,
+                cudaStream_t st);
+int gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, void* C, int M, int N, int K, long ldc, int out, int* err,
+               int sms, cudaStream_t stream);
 int embedding_fwd(const long* ids, const float* table, float* out, long n, int s, int d, int sms, cudaStream_t st);
 int embedding_bwd(const long* ids, const float* g, float* table_grad, long n, int s, int d, int sms, cudaStream_t st);
 int ce_grad(const float* logits, const long* targets, const float* a, const float* b, void* grad, float* ce, float* lse, long rows, int V,

@@ -11,10 +11,12 @@ ced/model/nvfp4.py:169-250, ced/model/fp8.py:159-344):
 * FP8 rowwise / tensorwise: E4M3 (E5M2 for tensorwise gradients) with a power-of-two scale per row / per tensor.
 
 A quantised linear keeps its master weight in high precision and quantises both operands of each of its three GEMMs
-from the high-precision tensors, along that GEMM's reduction dimension. The GEMMs run on the bf16 tcgen05 kernel over
-the dequantised operands: every E4M3 / E2M1 value times its power-of-two (or E4M3) scale is exact in bfloat16, so the
-products equal the block-scaled tensor-core products and only the accumulation order differs. Quantised paths are
-active in training mode only; evaluation is bf16.
+from the high-precision tensors, along that GEMM's reduction dimension. MXFP8 linears run on the block-scaled
+tensor-core kernel (`tcgen05.mma.kind::mxf8f6f4.block_scale`, csrc/gemm_mx.cu) over E4M3 bytes and E8M0 scale cells
+written by one quantise kernel per tensor; the other recipes (and shapes the kernel does not take) run on the bf16
+tcgen05 kernel over the dequantised operands: every E4M3 / E2M1 value times its power-of-two (or E4M3) scale is exact
+in bfloat16, so the products equal the block-scaled products and only the accumulation order differs. Quantised paths
+are active in training mode only; evaluation is bf16.
 """
 
 from __future__ import annotations
@@ -286,6 +288,73 @@ class _LowpLinear(torch.autograd.Function):
         return dx, dw, None, None
 
 
+def mx_cells_to_rows(sf: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """Scale cells in the tensor core's layout -> exponents [rows, k / 32] (the inverse of the quantise kernel's placement:
+    cell [row tile][k tile] of 512 bytes, byte (row % 32) * 16 + (row % 128 // 32) * 4 + block % 4)."""
+    rt, kt = -(-rows // 128), -(-k // 128)
+    cells = sf[:rt * kt * 512].view(rt, kt, 32, 4, 4)          # [row tile][k tile][row % 32][row // 32 % 4][block % 4]
+    return cells.permute(0, 3, 2, 1, 4).reshape(rt * 128, kt * 4)[:rows, :k // 32]
+
+
+class _MxLinear(torch.autograd.Function):
+    """A linear whose three GEMMs run on the block-scaled MXFP8 tensor-core kernel. Each activation is quantised once, in
+    both block orientations from one read (x: along features for the forward, along tokens for the weight gradient; dy
+    likewise), the weight once per orientation; the forward keeps x's token-blocked transpose for the backward instead
+    of x itself. Same quantisation points as the emulation (reference: ced/model/fp8.py:223-291)."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        from . import native
+
+        k = x.shape[-1]
+        x2 = x.reshape(-1, k)
+        if x2.dtype not in (torch.float32, torch.bfloat16):
+            x2 = x2.float()
+        need_w = ctx.needs_input_grad[1]
+        xq, xs, xtq, xts = native.mx_quantize(x2, True, need_w)
+        wq, ws, wtq, wts = native.mx_quantize(weight.detach(), True, ctx.needs_input_grad[0])
+        y = native.gemm_mx(xq, xs, wq, ws)
+        ctx.save_for_backward(xtq, xts, wtq, wts)
+        ctx.xshape, ctx.xdtype, ctx.weight = x.shape, x.dtype, weight
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import native
+
+        xtq, xts, wtq, wts = ctx.saved_tensors
+        n = ctx.weight.shape[0]
+        dy2 = dy.reshape(-1, n)
+        if dy2.dtype not in (torch.float32, torch.bfloat16):
+            dy2 = dy2.float()
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        gq, gs, gtq, gts = native.mx_quantize(dy2, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = native.gemm_mx(gq, gs, wtq, wts).view(ctx.xshape)
+            if ctx.xdtype != torch.bfloat16:
+                dx = dx.to(ctx.xdtype)
+        if ctx.needs_input_grad[1]:
+            main = getattr(ctx.weight, "main_grad", None) if native.WGRAD_INTO_MAIN else None
+            if main is not None and main.dtype == torch.float32:
+                native.gemm_mx(gtq, gts, xtq, xts, out=main, accumulate=True)
+            else:
+                dw = native.gemm_mx(gtq, gts, xtq, xts, out_dtype=torch.float32).to(ctx.weight.dtype)
+        return dx, dw
+
+
+def mx_native_ok(x, weight) -> bool:
+    """Shapes the block-scaled kernel takes: every reduction dimension (features in, features out, tokens) a multiple of 128."""
+    tokens = x.numel() // x.shape[-1]
+    return weight.shape[0] % 128 == 0 and weight.shape[1] % 128 == 0 and tokens % 128 == 0 and weight.dtype in (torch.float32, torch.bfloat16)
+
+
 def native_linear(x, lin):
-    """Device path of a quantised linear in training mode."""
+    """Device path of a quantised linear in training mode: MXFP8 on the block-scaled tensor-core kernel where the shapes
+    allow, every other recipe (and odd shapes) on the bf16 kernel over the dequantised operands."""
+    import os
+
+    if lin.lowp.kind == "mxfp8" and mx_native_ok(x, lin.weight) and os.environ.get("GHB_MX_GEMM", "native") == "native":
+        return _MxLinear.apply(x, lin.weight)
     return _LowpLinear.apply(x, lin.weight, lin.lowp, True)

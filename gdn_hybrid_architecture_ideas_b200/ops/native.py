@@ -86,6 +86,35 @@ def gemm(a, b, out=None, a_mn=False, b_mn=False, accumulate=False, out_dtype=BF1
     return out
 
 
+def mx_quantize(x2: torch.Tensor, rowwise: bool = True, colwise: bool = False):
+    """MXFP8 operands of x2 [R, C] (fp32 or bf16; R, C multiples of 32) from one read: (q_row [R, C] E4M3 bytes with blocks
+    along C, its scale cells) and / or (q_col [C, R], the transpose with blocks along R, its scale cells), each None when
+    not asked for. Scale cells are in the tensor core's layout (csrc/gemm_mx.cu); rows padded to 128 are zero."""
+    R, C = x2.shape
+    e = ext()
+    dev = x2.device
+
+    def pair(rows, k):
+        q = torch.empty(rows, k, dtype=torch.uint8, device=dev)
+        n = e.mx_scale_bytes(rows, k)
+        sf = torch.zeros(n, dtype=torch.uint8, device=dev) if rows % 128 or k % 128 else torch.empty(n, dtype=torch.uint8, device=dev)
+        return q, sf
+    qr, sr = pair(R, C) if rowwise else (None, None)
+    qc, sc = pair(C, R) if colwise else (None, None)
+    e.mx_quantize(x2, qr, sr, qc, sc)
+    _count()
+    return qr, sr, qc, sc
+
+
+def gemm_mx(a, sfa, b, sfb, out=None, accumulate=False, out_dtype=BF16):
+    """out = a b^T (+ out) on the block-scaled tensor-core path: a [M, K], b [N, K] E4M3 bytes with their scale cells."""
+    if out is None:
+        out = torch.empty(a.shape[0], b.shape[0], dtype=out_dtype, device=a.device)
+    ext().gemm_mx(a, sfa, b, sfb, out, accumulate, err_flag(a.device))
+    _count()
+    return out
+
+
 def _w_lp(lin) -> torch.Tensor:
     lp = getattr(lin, "weight_lp", None)
     return lp if lp is not None else lin.weight.detach().to(BF16)
