@@ -47,6 +47,8 @@ def parse():
     ap.add_argument("--parallelism", default="dp", choices=["dp", "tp"],
                     help="tp: tensor parallel over all ranks with a sequence-parallel stream (--rows is then the whole job's rows per step)")
     ap.add_argument("--tp-impl", default="fused", choices=["fused", "collective"], help="tp: fused peer-memory GEMMs or NCCL collectives around plain GEMMs")
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "mxfp8", "nvfp4"],
+                    help="GEMM precision of the layers' projections: bf16 (the headline), block-scaled MXFP8 on the tensor cores, or the NVFP4 recipe")
     ap.add_argument("--mode", default="train", choices=["train", "decode"], help="decode: static-cache greedy decode tokens/s")
     ap.add_argument("--kv", default="gqa", choices=["gqa", "grid"], help="decode: KV sharing of the attention layers")
     ap.add_argument("--prompt", type=int, default=32768, help="decode: prompt length")
@@ -123,6 +125,10 @@ def run_ours(args) -> dict:
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torchrun --nproc-per-node {args.gpus}")
     cfg = C.TrainConfig(model=C.hybrid_model_config(args.size, full=True))
+    if args.precision == "mxfp8":
+        cfg.model.fp8.mode, cfg.model.fp8.scaling = "linears", "mxfp8"
+    elif args.precision == "nvfp4":
+        cfg.model.nvfp4.mode = "all_linears"
     tp = args.parallelism == "tp" and world > 1
     job_rows = args.rows if tp else args.rows * world
     cfg.data = C.DataConfig(kind="uniform", seq_len=args.seq_len, batch_size=job_rows, seed=1)
@@ -183,7 +189,7 @@ def run_ours(args) -> dict:
     out = {
         "metric": "train tokens/s/box, 200M hybrid", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "strong" if tp else "weak",
-        "vs_baseline": (value / base) if base and not tp else None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": (value / base) if base and not tp else None, "dtype": args.precision, "data": "synthetic",
         "config": {"model": MODEL if args.size == "200m" else args.size, "global_batch": job_rows,
                    "seq_len": args.seq_len,
                    "parallelism": (f"tp{world}-sp-{args.tp_impl}" if tp else f"dp{world}" + ("" if world == 1 else f"-{cfg.optimizer_sharding}")),

@@ -2,8 +2,9 @@
 //
 // One persistent CTA per SM walks output tiles of 128 x BN. Warp roles: warp 0 issues TMA tile loads into a ring of
 // shared-memory stages, warp 1 (one thread) issues tcgen05.mma and commits stage releases, warps 2-5 drain the
-// accumulator from tensor memory (tcgen05.ld) and store the tile. Two accumulators alternate so the epilogue of tile
-// i overlaps the main loop of tile i+1. Each operand may be K-major (reduction dimension contiguous: forward
+// accumulator from tensor memory (tcgen05.ld) and store the tile (bf16 tiles through swizzled shared-memory slabs and TMA
+// tile stores, csrc/gemm_epilogue.cuh; fp32 tiles straight from registers). Two accumulators alternate so the epilogue
+// of tile i overlaps the main loop of tile i+1. Each operand may be K-major (reduction dimension contiguous: forward
 // y = x W^T) or MN-major (dgrad dx = dy W, wgrad dW = dy^T x), selected in the UMMA instruction descriptor; the
 // shared-memory tiles are 128-byte swizzled in both cases. Output: bf16, fp32, fp32 accumulated in place
 // (main-gradient accumulation), or fp32 reduced into the output by several slices of the reduction dimension (split-K
@@ -14,6 +15,7 @@
 // (ced/train/wgrad_accum.py:100-145).
 #include "kernels.h"
 #include "sm100.cuh"
+#include "gemm_epilogue.cuh"
 #include <cstdlib>
 
 namespace ghb {
@@ -25,7 +27,7 @@ constexpr int GEMM_THREADS = 192;
 template <int BN> struct GemmCfg {
   static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
   static constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-  static constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + 256 + 1024;
+  static constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + EPI_SMEM_BYTES + 256 + 1024;
   static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
 };
 
@@ -41,15 +43,16 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 
 template <int BN, bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, void* __restrict__ Cout,
-            long ldc, int M, int N, int K, int splits, int* __restrict__ err) {
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_c,
+            void* __restrict__ Cout, long ldc, int M, int N, int K, int splits, int* __restrict__ err) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * Cfg::A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (Cfg::A_BYTES + Cfg::B_BYTES));
+  uint8_t* slabs = smem + STAGES * (Cfg::A_BYTES + Cfg::B_BYTES);      // bf16 output staging (1024-byte aligned)
+  uint64_t* full = reinterpret_cast<uint64_t*>(slabs + EPI_SMEM_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -64,6 +67,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (OUT == 0) tma_prefetch_desc(&tma_c);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
     mbar_fence_init();
@@ -123,6 +127,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   } else {
     const int quad = warp & 3;   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     int it = 0; bool ok = true;
+    uint32_t slab_count = 0;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++it) {
       const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
       int tm, tn; tile_coords(unit % tiles, tiles_m, tiles_n, tm, tn);
@@ -131,6 +136,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const long row = static_cast<long>(tm) * BM + quad * 32 + lane;
       const int n0 = tn * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      if (OUT == 0) {      // bf16: through the swizzled staging slabs and TMA tile stores
+        epilogue_store_bf16<BN>(taddr, slabs, &tma_c, tm * BM, n0, N, quad, lane, slab_count, &tempty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -138,25 +147,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         tmem_ld_wait();
         const int col = n0 + c * 32;
         if (row < M && col < N) {
-          if (OUT == 0) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Cout) + row * ldc + col;
-            if (col + 32 <= N) {
-              uint4* o4 = reinterpret_cast<uint4*>(out);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint32_t p[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
-                  p[e] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                o4[v] = make_uint4(p[0], p[1], p[2], p[3]);
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 32; ++e) if (col + e < N) out[e] = __float2bfloat16(__uint_as_float(r[e]));
-            }
-          } else {
+          {
             float* out = reinterpret_cast<float*>(Cout) + row * ldc + col;
             if (OUT == 3) {          // slices of one tile's reduction meet in the output through fp32 reductions in L2
               if (col + 32 <= N) {
@@ -188,6 +179,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+    if (OUT == 0) epilogue_store_drain(quad, lane);
   }
   tc_fence_before();
   __syncthreads();
@@ -210,9 +202,16 @@ static bool encode_operand(CUtensorMap* map, const void* ptr, long rows, long co
 template <int BN, bool A_MN, bool B_MN, int OUT>
 static int launch_cfg(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, int splits, int* err,
                       int sms, cudaStream_t stream) {
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   if (!encode_operand(&ta, A, M, K, lda, A_MN, BM)) return 21;
   if (!encode_operand(&tb, B, N, K, ldb, B_MN, BN)) return 22;
+  if (OUT == 0) {      // bf16 output tiles leave through TMA stores of 64-column slabs
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)}, strides[1] = {static_cast<uint64_t>(ldc) * 2};
+    const uint32_t box[2] = {64, BM};
+    if (!encode_tensor_map_2d(&tc, C, 2, dims, strides, box, true)) return 23;
+  } else {
+    tc = ta;
+  }
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN, OUT>;
   static bool attr_done = false;
@@ -221,7 +220,7 @@ static int launch_cfg(const void* A, const void* B, void* C, int M, int N, int K
     attr_done = true;
   }
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  kern<<<min(tiles * splits, sms), GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, C, ldc, M, N, K, splits, err);
+  kern<<<min(tiles * splits, sms), GEMM_THREADS, Cfg::SMEM, stream>>>(ta, tb, tc, C, ldc, M, N, K, splits, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 

@@ -15,10 +15,11 @@
 // shared-memory stages (two TMA tile loads, 128-byte swizzle, and two 512-byte bulk copies of scale cells per stage),
 // one thread of warp 1 copies the stage's scale cells into tensor memory (`tcgen05.cp`, each stage its own columns)
 // and issues four K = 32 MMAs whose instruction descriptors select the block's scale byte, warps 2-5 drain one of two
-// accumulators while the other is being filled. All three GEMMs of a linear (ced/model/fp8.py:223-291) take this form:
+// accumulators while the other is being filled (bf16 tiles leave through swizzled slabs and TMA tile stores). All three GEMMs of a linear (ced/model/fp8.py:223-291) take this form:
 // forward x_q W_q^T, input gradient dy_q (W^T)_q^T, weight gradient (dy^T)_q (x^T)_q^T.
 #include "kernels.h"
 #include "sm100.cuh"
+#include "gemm_epilogue.cuh"
 #include <cuda_fp8.h>
 
 namespace ghb {
@@ -163,10 +164,10 @@ namespace {
 
 constexpr int MBM = 128, MBN = 128, MBK = 128, MUK = 32;      // K in elements = bytes
 constexpr int MX_THREADS = 192;
-constexpr int MX_STAGES = 6;
+constexpr int MX_STAGES = 5;
 constexpr uint32_t MX_A_BYTES = MBM * MBK, MX_B_BYTES = MBN * MBK, MX_SF_BYTES = 512;
 constexpr uint32_t MX_STAGE_BYTES = MX_A_BYTES + MX_B_BYTES + 2 * MX_SF_BYTES;
-constexpr uint32_t MX_SMEM = MX_STAGES * MX_STAGE_BYTES + 256 + 1024;
+constexpr uint32_t MX_SMEM = MX_STAGES * MX_STAGE_BYTES + EPI_SMEM_BYTES + 256 + 1024;
 constexpr uint32_t MX_TMEM_COLS = 512;        // two 128-column accumulators, then 8 scale columns per stage from column 256
 constexpr uint32_t MX_SF_COL0 = 2 * MBN;
 
@@ -209,13 +210,15 @@ __device__ __forceinline__ void mx_tile_coords(int tile, int tiles_m, int tiles_
 // OUT: 0 bf16, 1 fp32, 2 fp32 accumulated in place, 3 fp32 reduced into the output by `splits` slices of K.
 template <int OUT>
 __global__ void __launch_bounds__(MX_THREADS, 1)
-gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const uint8_t* __restrict__ sfa,
+gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_c,
+               const uint8_t* __restrict__ sfa,
                const uint8_t* __restrict__ sfb, void* __restrict__ Cout, long ldc, int M, int N, int K, int splits, int* __restrict__ err) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = sA + MX_STAGES * MX_A_BYTES;
-  uint8_t* sSA = sB + MX_STAGES * MX_B_BYTES;
+  uint8_t* slabs = sB + MX_STAGES * MX_B_BYTES;          // bf16 output staging (1024-byte aligned)
+  uint8_t* sSA = slabs + EPI_SMEM_BYTES;
   uint8_t* sSB = sSA + MX_STAGES * MX_SF_BYTES;
   uint64_t* full = reinterpret_cast<uint64_t*>(sSB + MX_STAGES * MX_SF_BYTES);
   uint64_t* empty = full + MX_STAGES;
@@ -291,6 +294,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else {
     const int quad = warp & 3;   // TMEM lanes 32*quad .. 32*quad+31 belong to this warp
     int it = 0; bool ok = true;
+    uint32_t slab_count = 0;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++it) {
       const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
       int tm, tn; mx_tile_coords(unit % tiles, tiles_m, tiles_n, tm, tn);
@@ -299,6 +303,10 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       const long row = static_cast<long>(tm) * MBM + quad * 32 + lane;
       const int n0 = tn * MBN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * MBN;
+      if (OUT == 0) {      // bf16: through the swizzled staging slabs and TMA tile stores
+        epilogue_store_bf16<MBN>(taddr, slabs, &tma_c, tm * MBM, n0, N, quad, lane, slab_count, &tempty[acc]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < MBN / 32; ++c) {
         uint32_t r[32];
@@ -306,25 +314,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         tmem_ld_wait();
         const int col = n0 + c * 32;
         if (row < M && col < N) {
-          if (OUT == 0) {
-            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(Cout) + row * ldc + col;
-            if (col + 32 <= N) {
-              uint4* o4 = reinterpret_cast<uint4*>(out);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint32_t p[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
-                  p[e] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                o4[v] = make_uint4(p[0], p[1], p[2], p[3]);
-              }
-            } else {
-#pragma unroll
-              for (int e = 0; e < 32; ++e) if (col + e < N) out[e] = __float2bfloat16(__uint_as_float(r[e]));
-            }
-          } else {
+          {
             float* out = reinterpret_cast<float*>(Cout) + row * ldc + col;
             if (OUT == 3) {
               if (col + 32 <= N) {
@@ -356,6 +346,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
     }
+    if (OUT == 0) epilogue_store_drain(quad, lane);
   }
   tc_fence_before();
   __syncthreads();
@@ -363,7 +354,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 }
 
 template <int OUT>
-int launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const void* sfa, const void* sfb, void* C, long ldc, int M, int N, int K, int splits,
+int launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const void* sfa, const void* sfb, void* C, long ldc, int M, int N, int K, int splits,
               int* err, int sms, cudaStream_t st) {
   auto kern = gemm_mx_kernel<OUT>;
   static bool attr_done = false;
@@ -372,7 +363,7 @@ int launch_mx(const CUtensorMap& ta, const CUtensorMap& tb, const void* sfa, con
     attr_done = true;
   }
   const int tiles = ((M + MBM - 1) / MBM) * ((N + MBN - 1) / MBN);
-  kern<<<min(tiles * splits, sms), MX_THREADS, MX_SMEM, st>>>(ta, tb, static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), C, ldc, M, N, K,
+  kern<<<min(tiles * splits, sms), MX_THREADS, MX_SMEM, st>>>(ta, tb, tc, static_cast<const uint8_t*>(sfa), static_cast<const uint8_t*>(sfb), C, ldc, M, N, K,
                                                               splits, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
@@ -394,6 +385,12 @@ int gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, v
   const uint32_t box_a[2] = {MBK, MBM}, box_b[2] = {MBK, MBN};
   if (!encode_tensor_map_2d(&ta, A, 1, da, strides, box_a, true)) return 21;
   if (!encode_tensor_map_2d(&tb, B, 1, db, strides, box_b, true)) return 22;
+  CUtensorMap tc = ta;
+  if (out == 0) {      // bf16 output tiles leave through TMA stores of 64-column slabs
+    const uint64_t dc[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)}, sc[1] = {static_cast<uint64_t>(ldc) * 2};
+    const uint32_t box_c[2] = {64, MBM};
+    if (!encode_tensor_map_2d(&tc, C, 2, dc, sc, box_c, true)) return 23;
+  }
   int splits = 1;
   if (out != 0) {       // a long reduction into few tiles (weight gradients): slice it over the idle SMs, as the bf16 kernel does
     const int tiles = ((M + MBM - 1) / MBM) * ((N + MBN - 1) / MBN), num_kb = K / MBK;
@@ -405,10 +402,10 @@ int gemm_mxfp8(const void* A, const void* sfa, const void* B, const void* sfb, v
     }
   }
   switch (out) {
-    case 0: return launch_mx<0>(ta, tb, sfa, sfb, C, ldc, M, N, K, 1, err, sms, stream);
-    case 1: return launch_mx<1>(ta, tb, sfa, sfb, C, ldc, M, N, K, 1, err, sms, stream);
-    case 2: return launch_mx<2>(ta, tb, sfa, sfb, C, ldc, M, N, K, 1, err, sms, stream);
-    default: return launch_mx<3>(ta, tb, sfa, sfb, C, ldc, M, N, K, splits, err, sms, stream);
+    case 0: return launch_mx<0>(ta, tb, tc, sfa, sfb, C, ldc, M, N, K, 1, err, sms, stream);
+    case 1: return launch_mx<1>(ta, tb, tc, sfa, sfb, C, ldc, M, N, K, 1, err, sms, stream);
+    case 2: return launch_mx<2>(ta, tb, tc, sfa, sfb, C, ldc, M, N, K, 1, err, sms, stream);
+    default: return launch_mx<3>(ta, tb, tc, sfa, sfb, C, ldc, M, N, K, splits, err, sms, stream);
   }
 }
 

@@ -155,7 +155,9 @@ class ZeroPlan:
         mods = dict(self.model.named_modules())
         for s in f.segments:
             owner, _, leaf = s.name.rpartition(".")
-            if leaf == "weight" and isinstance(mods.get(owner), Linear) and _LAYER.search(s.name) and getattr(mods[owner], "weight_lp", None) is not None:
+            # a low-precision linear quantises its operands from the fp32 master on every rank: it stays complete everywhere
+            if leaf == "weight" and isinstance(mods.get(owner), Linear) and _LAYER.search(s.name) and getattr(mods[owner], "weight_lp", None) is not None \
+                    and getattr(mods[owner], "precision", "bf16") == "bf16":
                 cells[s.offset // 64:(s.offset + s.numel + 63) // 64] = False
         return cells
 

@@ -124,6 +124,25 @@ def bench_gemm(a):
             "cublas_tflops": fl / ms_lib / 1e9}
 
 
+def bench_gemm_mx(a):
+    """MXFP8: the quantise kernel on an [M, K] bf16 activation (both block orientations from one read) and the block-scaled
+    product y = x_q W_q^T, against the bf16 kernel on the same shape."""
+    M, N, K = a.M, a.N, a.K
+    x = torch.randn(M, K, device="cuda").to(BF16)
+    w = torch.randn(N, K, device="cuda") * 0.02
+    xq, xs, _, _ = native.mx_quantize(x, True, False)
+    wq, ws, _, _ = native.mx_quantize(w, True, False)
+    wl = w.to(BF16)
+    ms = timed(lambda: native.gemm_mx(xq, xs, wq, ws), a.iters, a.warmup)
+    ms_bf16 = timed(lambda: native.gemm(x, wl), a.iters, a.warmup)
+    ms_q1 = timed(lambda: native.mx_quantize(x, True, False), a.iters, a.warmup)
+    ms_q2 = timed(lambda: native.mx_quantize(x, True, True), a.iters, a.warmup)
+    fl = 2.0 * M * N * K
+    return {"op": "gemm_mx", "M": M, "N": N, "K": K, "ms": ms, "tflops": fl / ms / 1e9, "bf16_kernel_ms": ms_bf16, "bf16_kernel_tflops": fl / ms_bf16 / 1e9,
+            "quantise_rowwise_ms": ms_q1, "quantise_rowwise_gbs": M * K * 3 / ms_q1 / 1e6, "quantise_both_ms": ms_q2,
+            "quantise_both_gbs": M * K * 4 / ms_q2 / 1e6}
+
+
 def bench_gdn_prep(a):
     from gdn_hybrid_architecture_ideas_b200 import ops
     B, L, hk, hv, dk, dv = a.B, a.L, a.H, a.H, 128, a.dv
@@ -250,7 +269,7 @@ def bench_decode_attention(a):
 
 def main():
     p = argparse.ArgumentParser()
-    p.add_argument("op", choices=["attention", "gdn", "gdn_prep", "gemm", "rmsnorm", "depth_mix", "swiglu", "lm_head", "adamw", "decode_attention"])
+    p.add_argument("op", choices=["attention", "gdn", "gdn_prep", "gemm", "gemm_mx", "rmsnorm", "depth_mix", "swiglu", "lm_head", "adamw", "decode_attention"])
     p.add_argument("--sources", type=int, default=4)
     p.add_argument("--ffn", type=int, default=2816)
     p.add_argument("--vocab", type=int, default=32768)
@@ -273,7 +292,7 @@ def main():
     p.add_argument("--rows", type=int, default=65536)
     p.add_argument("--d", type=int, default=1024)
     a = p.parse_args()
-    res = {"attention": bench_attention, "gdn": bench_gdn, "gdn_prep": bench_gdn_prep, "gemm": bench_gemm, "rmsnorm": bench_rmsnorm,
+    res = {"attention": bench_attention, "gdn": bench_gdn, "gdn_prep": bench_gdn_prep, "gemm": bench_gemm, "gemm_mx": bench_gemm_mx, "rmsnorm": bench_rmsnorm,
            "depth_mix": bench_depth_mix, "swiglu": bench_swiglu, "lm_head": bench_lm_head, "adamw": bench_adamw,
            "decode_attention": bench_decode_attention}[a.op](a)
     print(json.dumps(res))
