@@ -385,6 +385,25 @@ void decode_attention(const Tensor& q, const Tensor& k, const Tensor& v, const T
                               Hkv, rot, cap, rot ? cos_t.size(0) : 1, splits, scale, stream()), "decode_attention");
 }
 
+// q [B, 16, 64] fp32; k, v [B, T, 256] bf16 raw grid components; gain: the key norm's [64] fp32 gain, or none.
+void decode_attention_grid(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& lens, const c10::optional<Tensor>& doc_start,
+                           const Tensor& cos_t, const Tensor& sin_t, const c10::optional<Tensor>& gain, Tensor& out, Tensor& part_o, Tensor& part_ml,
+                           int64_t rot, int64_t cap, int64_t splits, double scale, double eps) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(is_f32(q) && q.is_contiguous() && q.dim() == 3 && q.size(1) == 16 && q.size(2) == 64, "decode_attention_grid: q fp32 [B, 16, 64]");
+  TORCH_CHECK(is_bf16(k) && is_bf16(v) && k.is_contiguous() && v.is_contiguous() && k.dim() == 3 && k.size(2) == 256 && v.sizes() == k.sizes(),
+              "decode_attention_grid: k, v bf16 [B, T, 256]");
+  TORCH_CHECK(lens.scalar_type() == torch::kInt32 && is_bf16(out) && out.is_contiguous() && is_f32(part_o) && is_f32(part_ml) && is_f32(cos_t) && is_f32(sin_t),
+              "decode_attention_grid: dtypes");
+  TORCH_CHECK(!gain.has_value() || (is_f32(*gain) && gain->numel() == 64), "decode_attention_grid: gain fp32 [64]");
+  const int B = q.size(0), T = k.size(1);
+  TORCH_CHECK(part_o.numel() >= static_cast<int64_t>(B) * 16 * splits * 64 && part_ml.numel() >= static_cast<int64_t>(B) * 16 * splits * 2,
+              "decode_attention_grid: scratch too small");
+  check(ghb::decode_attention_grid(q.data_ptr<float>(), k.data_ptr(), v.data_ptr(), lens.data_ptr<int>(), doc_start.has_value() ? doc_start->data_ptr<int>() : nullptr,
+                                   cos_t.data_ptr<float>(), sin_t.data_ptr<float>(), fptr(gain), out.data_ptr(), part_o.data_ptr<float>(),
+                                   part_ml.data_ptr<float>(), B, T, rot, cap, rot ? cos_t.size(0) : 1, splits, scale, eps, stream()), "decode_attention_grid");
+}
+
 // ---- fused data-parallel step over peer memory. `peers` is a CPU uint8 tensor holding the pointer table.
 void comm_reduce(const Tensor& peers, int64_t rank, int64_t world, int64_t lo, int64_t n, Tensor& shard, int64_t ticket, int64_t publish_seq,
                  Tensor& acc, Tensor& counter, Tensor& err, int64_t ctas) {
@@ -517,6 +536,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("embedding_fwd", &embedding_fwd);
   m.def("embedding_bwd", &embedding_bwd);
   m.def("decode_attention", &decode_attention);
+  m.def("decode_attention_grid", &decode_attention_grid);
   m.def("comm_reduce", &comm_reduce);
   m.def("comm_update", &comm_update);
   m.def("comm_wait_probe", &comm_wait_probe);

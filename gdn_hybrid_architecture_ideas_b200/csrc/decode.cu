@@ -201,6 +201,208 @@ int decode_attention(const float* q, const void* k, const void* v, const int* le
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
+// ================================================================================================ grid KV sharing
+// Grid-shared keys and values (4 row components and 4 column components of 32 channels; head (i, j) reads
+// [row_i ; col_j]) scored straight from the RAW cached components, so the cache holds 256 channels per token like
+// grouped attention with 4 KV heads instead of the 16 assembled heads (reference cache: ced/model/attention.py:943-1030).
+// The key norm runs over the assembled 64-channel head, so it cannot be cached per component; it factors as
+//   k_(i,j) = [g_r * row_i ; g_c * col_j] * rsqrt((|row_i|^2 + |col_j|^2) / 64 + eps)
+// and the kernel forms the two sums of squares from the cached values, applies the gain, rotates the row part by
+// min(distance, cap) (the rotary channels are the head's first ones) and scales each head's score by its factor.
+// One CTA per (split of the cached positions, batch row): a tile of 32 positions is staged in shared memory once
+// (512 bytes of keys and of values per position), warp i scores and accumulates the four heads of grid row i.
+constexpr int GR = 4, GCO = 4, GD = 32;            // grid rows, columns, channels per component
+constexpr int GW = (GR + GCO) * GD;                // 256 cached channels per token
+constexpr int GROW = GW * 2 + 16;                  // shared-memory bytes per cached token (16 bytes of padding: conflict-free 16-byte reads)
+
+struct GridDecodeArgs {
+  const float* q;               // [B, 16, 64] normed, temperature-scaled, unrotated queries
+  const __nv_bfloat16* k;       // [B, T, 256] raw key components
+  const __nv_bfloat16* v;       // [B, T, 256] raw value components
+  const int* lens; const int* doc_start;
+  const float* cos_t; const float* sin_t;
+  const float* gain;            // [64] key-norm gain, or null (no key norm)
+  float* part_o; float* part_ml;
+  int T, rot, cap, n_angles, splits;
+  float scale, eps;
+};
+
+__device__ __forceinline__ void unpack8(const uint4 pk, float* f) {
+  const uint32_t w[4] = {pk.x, pk.y, pk.z, pk.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); f[2 * e] = t.x; f[2 * e + 1] = t.y; }
+}
+
+__global__ void __launch_bounds__(GR * 32, 4)
+decode_attn_grid_kernel(GridDecodeArgs a) {
+  __shared__ float sq[GR * GCO][DH];
+  __shared__ float sg[DH];
+  __shared__ __align__(16) uint8_t sk[DTILE * GROW];
+  __shared__ __align__(16) uint8_t sv[DTILE * GROW];
+  __shared__ float sp[GR][DTILE][GCO];
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;      // warp = grid row
+  for (int i = threadIdx.x; i < GR * GCO * DH; i += blockDim.x) sq[i / DH][i % DH] = a.q[static_cast<long>(b) * GR * GCO * DH + i] * a.scale;
+  if (threadIdx.x < DH) sg[threadIdx.x] = a.gain ? a.gain[threadIdx.x] : 1.f;
+  __syncthreads();
+  const int len = a.lens[b];
+  const int first = a.doc_start ? a.doc_start[b] : 0;
+  const int per = (len - first + a.splits - 1) / a.splits;
+  const int lo = first + split * per, hi = min(len, lo + per);
+  const int qpos = len - 1;
+  const int half = a.rot / 2;
+  const int vr = lane >> 3, vc8 = lane & 7;
+  float m[GCO], l[GCO], o[GCO][8];
+#pragma unroll
+  for (int j = 0; j < GCO; ++j) {
+    m[j] = -INFINITY; l[j] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[j][e] = 0.f;
+  }
+  for (int t0 = lo; t0 < hi; t0 += DTILE) {
+    __syncthreads();      // the tile before is consumed
+    // ---- stage 32 positions x 512 bytes of keys and of values (16 bytes per thread and pass, coalesced)
+    {
+      uint4 kk[8], vv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + threadIdx.x;          // 16-byte piece of the tile
+        const int tok = idx >> 5, piece = idx & 31;
+        const bool in = t0 + tok < hi;
+        const long off = (static_cast<long>(b) * a.T + t0 + tok) * GW + piece * 8;
+        kk[i] = in ? *reinterpret_cast<const uint4*>(a.k + off) : make_uint4(0u, 0u, 0u, 0u);
+        vv[i] = in ? *reinterpret_cast<const uint4*>(a.v + off) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + threadIdx.x;
+        const int tok = idx >> 5, piece = idx & 31;
+        *reinterpret_cast<uint4*>(sk + tok * GROW + piece * 16) = kk[i];
+        *reinterpret_cast<uint4*>(sv + tok * GROW + piece * 16) = vv[i];
+      }
+    }
+    __syncthreads();
+    // ---- scores of heads (warp, 0..3) for position t0 + lane
+    const int t = t0 + lane;
+    float logit[GCO];
+#pragma unroll
+    for (int j = 0; j < GCO; ++j) logit[j] = -INFINITY;
+    if (t < hi) {
+      float x[GD];
+      const uint8_t* base = sk + lane * GROW;
+#pragma unroll
+      for (int c = 0; c < GD / 8; ++c) unpack8(*reinterpret_cast<const uint4*>(base + warp * (GD * 2) + c * 16), x + c * 8);
+      float ss_r = 0.f;
+#pragma unroll
+      for (int i = 0; i < GD; ++i) { ss_r += x[i] * x[i]; x[i] *= sg[i]; }
+      if (half > 0) {
+        int d = qpos - t;
+        if (a.cap >= 0 && d > a.cap) d = a.cap;
+        d = min(d, a.n_angles - 1);
+#define GHB_GROT(HALF)                                                                  \
+        _Pragma("unroll") for (int i = 0; i < HALF; ++i) {                              \
+          const float c = a.cos_t[d * HALF + i], s = a.sin_t[d * HALF + i];              \
+          const float x1 = x[i], x2 = x[i + HALF];                                       \
+          x[i] = x1 * c + x2 * s;                                                        \
+          x[i + HALF] = x2 * c - x1 * s;                                                 \
+        }
+        if (half == 8) { GHB_GROT(8) } else if (half == 16) { GHB_GROT(16) } else if (half == 4) { GHB_GROT(4) }
+#undef GHB_GROT
+      }
+      float acc[GCO];
+#pragma unroll
+      for (int j = 0; j < GCO; ++j) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < GD; ++i) s += sq[warp * GCO + j][i] * x[i];
+        acc[j] = s;
+      }
+#pragma unroll
+      for (int j = 0; j < GCO; ++j) {
+#pragma unroll
+        for (int c = 0; c < GD / 8; ++c) unpack8(*reinterpret_cast<const uint4*>(base + (GR + j) * (GD * 2) + c * 16), x + c * 8);
+        float ss_c = 0.f, s = 0.f;
+#pragma unroll
+        for (int i = 0; i < GD; ++i) { ss_c += x[i] * x[i]; s += sq[warp * GCO + j][GD + i] * (x[i] * sg[GD + i]); }
+        const float factor = a.gain ? rsqrtf((ss_r + ss_c) * (1.f / DH) + a.eps) : 1.f;
+        logit[j] = (acc[j] + s) * factor;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < GCO; ++j) {
+      float mx = logit[j];
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+      const float m_new = fmaxf(m[j], mx);
+      const float p = (logit[j] == -INFINITY) ? 0.f : __expf(logit[j] - m_new);
+      float ps = p;
+#pragma unroll
+      for (int s = 16; s > 0; s >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, s);
+      const float alpha = (m[j] == -INFINITY) ? 0.f : __expf(m[j] - m_new);
+      l[j] = l[j] * alpha + ps;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[j][e] *= alpha;
+      m[j] = m_new;
+      sp[warp][lane][j] = p;
+    }
+    __syncwarp();
+    // ---- P V: a lane holds 8 channels of the head's output and every fourth position; channels 0..31 come from value
+    // row component `warp` (shared by the four heads), channels 32..63 from column component j
+#pragma unroll
+    for (int i = 0; i < DTILE / 4; ++i) {
+      const int jt = 4 * i + vr;
+      const uint8_t* base = sv + jt * GROW;
+      float vf[8];
+      if (vc8 < 4) {
+        unpack8(*reinterpret_cast<const uint4*>(base + warp * (GD * 2) + vc8 * 16), vf);
+#pragma unroll
+        for (int j = 0; j < GCO; ++j) {
+          const float p = sp[warp][jt][j];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[j][e] += p * vf[e];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < GCO; ++j) {
+          unpack8(*reinterpret_cast<const uint4*>(base + (GR + j) * (GD * 2) + (vc8 - 4) * 16), vf);
+          const float p = sp[warp][jt][j];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[j][e] += p * vf[e];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < GCO; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      o[j][e] += __shfl_xor_sync(0xffffffffu, o[j][e], 8);
+      o[j][e] += __shfl_xor_sync(0xffffffffu, o[j][e], 16);
+    }
+  // every warp owns its four heads: the split's partial result leaves without a merge across warps
+#pragma unroll
+  for (int j = 0; j < GCO; ++j) {
+    const long base = (static_cast<long>(b) * GR * GCO + warp * GCO + j) * a.splits + split;
+    if (vr == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) a.part_o[base * DH + vc8 * 8 + e] = o[j][e];
+    }
+    if (lane == 0) { a.part_ml[base * 2] = m[j]; a.part_ml[base * 2 + 1] = l[j]; }
+  }
+}
+
+// q [B, 16, 64] fp32; k, v [B, T, 256] bf16 raw components of a 4 x 4 grid with 32-channel components; gain [64] or null.
+int decode_attention_grid(const float* q, const void* k, const void* v, const int* lens, const int* doc_start, const float* cos_t,
+                          const float* sin_t, const float* gain, void* out, float* part_o, float* part_ml, int B, int T, int rot, int cap,
+                          int n_angles, int splits, float scale, float eps, cudaStream_t st) {
+  if ((rot != 0 && rot != 8 && rot != 16 && rot != 32) || rot > GD || splits < 1) return 1;
+  GridDecodeArgs a{q, static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), lens, doc_start, cos_t, sin_t, gain, part_o, part_ml,
+                   T, rot, cap, n_angles, splits, scale, eps};
+  decode_attn_grid_kernel<<<dim3(splits, 1, B), GR * 32, 0, st>>>(a);
+  decode_attn_merge_kernel<<<B * GR * GCO, DH, 0, st>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), splits);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
 }  // namespace ghb
 
 // ================================================================================================ allocation-free entry

@@ -94,6 +94,11 @@ int decode_attention(const float* q, const void* k, const void* v, const int* le
                      void* out, float* part_o, float* part_ml, int B, int T, int Hq, int Hkv, int rot, int cap, int n_angles, int splits,
                      float scale, cudaStream_t st);
 
+// The same over the raw components of a 4 x 4 grid-shared cache (k, v [B, T, 256]; 16 query heads); gain: key-norm gain or null.
+int decode_attention_grid(const float* q, const void* k, const void* v, const int* lens, const int* doc_start, const float* cos_t,
+                          const float* sin_t, const float* gain, void* out, float* part_o, float* part_ml, int B, int T, int rot, int cap,
+                          int n_angles, int splits, float scale, float eps, cudaStream_t st);
+
 // Fused data-parallel step over peer memory (csrc/comm.cu). `peers` points at a host copy of the CommPeers table
 // (comm_peers_bytes() bytes: 5 arrays of 8 device pointers, then 3 multicast pointers).
 size_t comm_peers_bytes();

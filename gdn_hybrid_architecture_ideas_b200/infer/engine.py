@@ -7,7 +7,10 @@ batch size with fixed-shape state:
 
 * attention layers: key/value caches [B, max_len, Hkv, hd] allocated once. Keys are stored normed and UNROTATED; the
   decode kernel applies the rotation by min(distance, cap) while scoring (csrc/decode.cu), so the distance cap needs
-  no second key copy. Grid KV layers cache the assembled per-head keys/values.
+  no second key copy. Grid KV layers cache the RAW row / column components [B, max_len, 1, width] (the reference's
+  cache, ced/model/attention.py:943-1030: a 4 x 4 grid of 32-channel components holds 256 channels per token, the
+  same bytes as 4 grouped KV heads); the key norm over the assembled head and the rotation are applied while scoring,
+  on the GPU inside the grid decode kernel.
 * GDN layers: the recurrent state S [B, Hv, dk, dv] (fp32) and the K-1 conv inputs, updated in place.
 * one decode step (embedding -> all layers -> final norm -> head -> argmax) is captured in a CUDA graph on static
   input/output buffers; per-row lengths live on the device and advance inside the graph.
@@ -65,11 +68,11 @@ class DecodeEngine:
             m = layer.mixer
             if layer.kind == "attention":
                 c = m.cfg
-                heads = c.n_q_heads if m.grid is not None else c.n_kv_heads
+                heads, width = (1, m.grid.width) if m.grid is not None else (c.n_kv_heads, c.head_dim)
                 rot = rotary_dims(c.head_dim, c.rope_fraction)
                 n_ang = (m.cap + 1) if m.cap is not None else max_len
-                st = {"k": torch.zeros(B, T, heads, c.head_dim, dtype=kv_dtype, device=dev),
-                      "v": torch.zeros(B, T, heads, c.head_dim, dtype=kv_dtype, device=dev), "rot": rot, "heads": heads}
+                st = {"k": torch.zeros(B, T, heads, width, dtype=kv_dtype, device=dev),
+                      "v": torch.zeros(B, T, heads, width, dtype=kv_dtype, device=dev), "rot": rot, "heads": heads}
                 if rot:
                     inv = c.rope_theta ** (-torch.arange(0, rot, 2, dtype=torch.float64, device=dev) / rot)
                     ang = torch.arange(n_ang, dtype=torch.float64, device=dev)[:, None] * inv
@@ -84,8 +87,11 @@ class DecodeEngine:
                                     "conv_doc": torch.full((B, g.conv_kernel - 1), -1, dtype=torch.long, device=dev)})
         hq = max((l.mixer.cfg.n_q_heads for l in model.encoder.layers if l.kind == "attention"), default=1)
         self.splits = splits or max(1, min(64, (148 * 2) // max(1, B)))
-        self.part_o = torch.zeros(B * hq * self.splits * 64, dtype=torch.float32, device=dev)
-        self.part_ml = torch.zeros(B * hq * self.splits * 2, dtype=torch.float32, device=dev)
+        grid_layers = any(l.kind == "attention" and l.mixer.grid is not None for l in model.encoder.layers)
+        scratch_splits = self.splits * (4 if grid_layers else 1)
+        self.part_o = torch.zeros(B * hq * scratch_splits * 64, dtype=torch.float32, device=dev)
+        self.part_ml = torch.zeros(B * hq * scratch_splits * 2, dtype=torch.float32, device=dev)
+        self.native_grid = True     # False: score grid layers through the assembled-heads statement (oracle of the grid kernel)
         self.graph = None
         self._host_len = 0          # host-side mirror of the (equal) row lengths: guards the static capacity before each launch
 
@@ -117,9 +123,8 @@ class DecodeEngine:
             for st, layer, cache in zip(self.layers, self.model.encoder.layers, out.cache.encoder):
                 if layer.kind == "attention":
                     m = layer.mixer
-                    if m.grid is not None:
-                        kn = m.k_norm(assemble_grid(cache.k, m.grid))
-                        v = assemble_grid(cache.v, m.grid)
+                    if m.grid is not None:      # raw components, as the model's own cache holds them
+                        kn, v = cache.k, cache.v
                     else:
                         v = cache.v
                         if cache.k_far is not None or st["rot"] == 0:
@@ -161,8 +166,7 @@ class DecodeEngine:
             qn = qn * f
         if m.grid is not None:
             kw = m.grid.width
-            k_new = m.k_norm(assemble_grid(m.k_proj(h).view(B, 1, 1, kw), m.grid))
-            v_new = assemble_grid(m.v_proj(h).view(B, 1, 1, kw), m.grid)
+            k_new, v_new = m.k_proj(h).view(B, 1, 1, kw), m.v_proj(h).view(B, 1, 1, kw)
         else:
             k_new = m.k_norm(m.k_proj(h).view(B, 1, c.n_kv_heads, hd)) if hasattr(m.k_norm, "weight") else m.k_proj(h).view(B, 1, c.n_kv_heads, hd)
             v_new = m.v_proj(h).view(B, 1, c.n_kv_heads, hd)
@@ -171,6 +175,25 @@ class DecodeEngine:
         st["k"][rows, at] = k_new[:, 0].to(st["k"].dtype)
         st["v"][rows, at] = v_new[:, 0].to(st["v"].dtype)
         cap = m.cap if m.cap is not None else -1
+        if m.grid is not None:
+            g = m.grid
+            normed = hasattr(m.k_norm, "weight")
+            if self.native and self.native_grid and (g.rows, g.cols, g.row_dim, g.col_dim, g.heads_per_cell, g.depth) == (4, 4, 32, 32, 1, 0) and st["rot"] <= 32:
+                from ..ops import native
+
+                o = torch.empty(B, hq, hd, dtype=torch.bfloat16, device=h.device)
+                splits = self.splits * 4          # one CTA serves all 16 heads of a split: four times the splits fill the same grid
+                # (the norm's gain is stored zero-centred: the kernel takes 1 + w)
+                native.ext().decode_attention_grid(qn.view(B, hq, hd).contiguous(), st["k"].view(B, self.T, kw), st["v"].view(B, self.T, kw),
+                                                   (self.lens + 1).contiguous(), self.doc_start, st["cos"], st["sin"],
+                                                   (1.0 + m.k_norm.weight.float()) if normed else None, o, self.part_o, self.part_ml, st["rot"], cap, splits,
+                                                   hd ** -0.5, m.k_norm.eps if normed else 0.0)
+                native._count(2)
+                return m.output(o.view(B, 1, hq, hd).to(h.dtype) if gate is None else o.view(B, 1, hq, hd).to(gate.dtype), gate)
+            # other grid shapes and the CPU: assemble the heads from the cached components, then the plain statement
+            kk = m.k_norm(assemble_grid(st["k"], g).float())
+            o = _decode_attention_reference(qn.view(B, hq, hd), kk, assemble_grid(st["v"], g), self.lens + 1, self.doc_start, st["cos"], st["sin"], st["rot"], cap)
+            return m.output(o.view(B, 1, hq, hd).to(h.dtype) if gate is None else o.view(B, 1, hq, hd).to(gate.dtype), gate)
         if self.native and hd == 64:
             from ..ops import native
 
