@@ -365,14 +365,67 @@ def run_reference(args) -> dict:
     return out
 
 
+def run_reference_decode(args) -> dict:
+    """The reference's own batched greedy generation (ced/eval/recall_ruler_gen.py `generate_greedy_batched`: chunked
+    prefill through its cached forward, caches that grow by concatenation, one `extend` per token) on the same model,
+    batch, prompt length and number of generated tokens. Its decode engine proper is batch 1 and refuses depth mixing,
+    the GDN mixes and grid KV, so this is the path its evaluations use at batch > 1. The rate is its own
+    `decode_steps` / `decode_s` (a host clock between device synchronisations, as the function reports it)."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "ced").is_dir():
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (pip install --no-deps --target baseline/_ref <reference checkout>/code)"}
+    sys.path.insert(0, str(ref))
+    import torch
+    import ced.config as RC
+    from ced.eval.recall_ruler_gen import generate_greedy_batched
+    from ced.model.control import build_model as ref_build
+
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    args_t = argparse.Namespace(**{**vars(args), "rows": 1})
+    mcfg = reference_config(args_t, 1, 1)["model"]
+    mcfg["encoder"]["attention"]["backend"] = os.environ.get("GHB_REF_DECODE_ATTENTION", "reference")     # the cached forward's own attention
+    if args.kv == "grid":
+        mcfg["encoder"]["attention"].update(kv_sharing="grid", n_kv_heads=1, grid_rows=4, grid_cols=4, row_dim=32, col_dim=32)
+    torch.manual_seed(1)
+    model = ref_build(RC.from_dict(RC.ModelConfig, mcfg)).to(dev).eval()
+    g = torch.Generator().manual_seed(1 + rank)
+    B, P = args.batch, args.prompt
+    prompts = torch.randint(0, VOCAB, (B, P), generator=g).tolist()
+    sampler = ClockSampler(rank == 0)
+    n_new = args.steps + args.warmup + 1
+    _, stats = generate_greedy_batched(model, prompts, n_new, prefill_rows=int(os.environ.get("GHB_REF_PREFILL_ROWS", "2")), autocast_dtype=torch.bfloat16)
+    clocks = sampler.stop(world)
+    ms = 1e3 * stats["decode_s"] / max(1, stats["decode_steps"])
+    if world > 1:
+        import torch.distributed as dist
+
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=dev)
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        dist.destroy_process_group()
+    value = B * world / (ms / 1e3)
+    return {"metric": "decode tokens/s at 32k context", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": stats["decode_steps"], "warmup": 0,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": MODEL + ("-grid4x4" if args.kv == "grid" else "-gqa4"), "batch_per_gpu": B, "prompt": P, "parallelism": f"dp{world}",
+                       "prefill_s": stats["prefill_s"], "path": "generate_greedy_batched (prefill / extend, concatenated caches)",
+                       "timing": "the function's own decode_s / decode_steps (host clock between synchronisations)"},
+            "clocks": clocks, "e2e": {"value": value, "unit": "tokens/s", "note": "the reference's loop reads every token back to the host"},
+            "impl": "reference"}
+
+
 def main():
     args = parse()
     t0 = time.time()
     try:
         if args.mode == "decode":
-            out = ({"impl": "reference", "unavailable": "the reference has no batched static-cache decode: its engine is batch 1 and refuses "
-                    "depth mixing / GDN mixes / grid KV; its prefill/extend path materialises dense 32k x 32k attention masks"}
-                   if args.impl == "reference" else run_decode(args))
+            out = run_reference_decode(args) if args.impl == "reference" else run_decode(args)
         else:
             out = run_reference(args) if args.impl == "reference" else run_ours(args)
     except Exception as e:

@@ -101,8 +101,13 @@ class SyntheticPackedData:
         return tokens, docs
 
     def batch(self, step: int, first: int = 0, count: int | None = None) -> Batch:
-        last = self.cfg.batch_size if count is None else first + count
-        rows = [self._row(counter_generator(self.cfg.seed, step, 1000 + b)) for b in range(first, last)]
+        B = self.cfg.batch_size
+        return self.rows(step * B + first, B - first if count is None else count)
+
+    def rows(self, first: int, count: int) -> Batch:
+        """Base rows first .. first + count - 1 of the run's row sequence (row g is row g % B of step g // B)."""
+        B = self.cfg.batch_size
+        rows = [self._row(counter_generator(self.cfg.seed, g // B, 1000 + g % B)) for g in range(first, first + count)]
         seq = torch.stack([r[0] for r in rows])
         docs = torch.stack([r[1] for r in rows])
         return Batch(tokens=seq[:, :-1].contiguous(), targets=seq[:, 1:].contiguous(),
@@ -118,10 +123,14 @@ class UniformTokens:
         self.cfg, self.vocab_size = cfg, vocab_size
 
     def batch(self, step: int, first: int = 0, count: int | None = None) -> Batch:
-        last = self.cfg.batch_size if count is None else first + count
-        L = self.cfg.seq_len
-        seq = torch.stack([torch.randint(0, self.vocab_size, (L + 1,), generator=counter_generator(self.cfg.seed, step, 1000 + b))
-                           for b in range(first, last)])
+        B = self.cfg.batch_size
+        return self.rows(step * B + first, B - first if count is None else count)
+
+    def rows(self, first: int, count: int) -> Batch:
+        """Base rows first .. first + count - 1 of the run's row sequence (row g is row g % B of step g // B)."""
+        B, L = self.cfg.batch_size, self.cfg.seq_len
+        seq = torch.stack([torch.randint(0, self.vocab_size, (L + 1,), generator=counter_generator(self.cfg.seed, g // B, 1000 + g % B))
+                           for g in range(first, first + count)])
         B = seq.shape[0]
         return Batch(tokens=seq[:, :-1].contiguous(), targets=seq[:, 1:].contiguous(),
                      target_valid=torch.ones(B, L, dtype=torch.bool), doc_ids=torch.zeros(B, L, dtype=torch.long),

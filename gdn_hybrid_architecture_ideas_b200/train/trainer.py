@@ -113,7 +113,7 @@ class Trainer:
         if cfg.tst.schedule:
             from .tst import TSTPlan
 
-            self.tst = TSTPlan(cfg.tst, self.data, cfg.model.vocab_size)
+            self.tst = TSTPlan(cfg.tst, self.data, cfg.model.vocab_size, cfg.data.batch_size, cfg.seed)
         self.step = 0
         self.wandb_run_id = None
         self.init_info = self.resume_info = None
@@ -302,8 +302,7 @@ class Trainer:
         cfg = self.cfg
         t0 = time.perf_counter()
         step = self.step
-        if self.tst is not None and self.tst.schedule.is_switch(step) and not cfg.tst.keep_optimizer_state:
-            self.optimizer.reset_moments()
+        tst_event = self.tst.switch(self, step) if self.tst is not None else None     # a later phase's first step starts with the switch
         if self.prefetch is not None:          # the batch was built by the background thread while the last step ran
             batch = self.prefetch.get(step).batch
             self.prefetch.start(step + 1)
@@ -313,6 +312,10 @@ class Trainer:
         if bad:
             self._halt_bad_batch(step)
         lr = lr_of(cfg, step)
+        if self.tst is not None:
+            factor = self.tst.lr_factor(step)
+            if factor is not None:
+                lr = lr * factor
         if self.device.type == "cuda":
             batch = batch.pin()
         self.h2d_bytes = batch.h2d_bytes()
@@ -328,6 +331,8 @@ class Trainer:
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        if tst_event is not None:
+            m["tst_switch"] = tst_event
         if self.zero_wgrad is not None and self.step % cfg.log_zero_wgrad_every == 0:
             m.update(self.zero_wgrad.summary())
         self.last_metrics = m
@@ -357,6 +362,8 @@ class Trainer:
             while self.step < end:
                 m = self.train_step()
                 if self.lead:
+                    if "tst_switch" in m:
+                        self._jsonl({"event": "tst_switch", **m["tst_switch"]})
                     self._jsonl(m)
                     if cfg.log_every and (m["step"] % cfg.log_every == 0 or self.step == end):
                         print(f"step {m['step']:6d} loss {m['loss']:.4f} lr {m['lr']:.2e} gnorm {m['grad_norm']:.3f} "
