@@ -61,6 +61,30 @@ class Batch:
                    if isinstance(t, torch.Tensor))
 
 
+def short_rows(data, first: int, count: int, length: int, full_length: int) -> Batch:
+    """Rows first .. first + count - 1 of the run's rows cut to `length` tokens (batch-shape schedules): base row g of
+    full_length tokens is cut into full_length / length consecutive pieces, piece j holding its tokens [j length, j length +
+    length] (inputs and the last one's target), so short row i is piece i % n of base row i // n. A piece that starts
+    inside a document keeps the document (its ids are re-based to start at 0 for the row)."""
+    if length == full_length:
+        return data.rows(first, count)
+    n = full_length // length
+    g0, g1 = first // n, (first + count - 1) // n
+    base = data.rows(g0, g1 - g0 + 1)
+    seq = torch.cat([base.tokens, base.targets[:, -1:]], dim=1)
+    last_doc = torch.where(base.target_valid[:, -1], base.doc_ids[:, -1], base.doc_ids[:, -1] + 1)
+    docs = torch.cat([base.doc_ids, last_doc[:, None]], dim=1)
+    toks, dcs = [], []
+    for i in range(first, first + count):
+        r, j = i // n - g0, i % n
+        toks.append(seq[r, j * length: j * length + length + 1])
+        d = docs[r, j * length: j * length + length + 1]
+        dcs.append(d - d[0])
+    t, d = torch.stack(toks), torch.stack(dcs)
+    return Batch(tokens=t[:, :-1].contiguous(), targets=t[:, 1:].contiguous(), target_valid=(d[:, 1:] == d[:, :-1]).contiguous(),
+                 doc_ids=d[:, :-1].contiguous(), single_doc=base.single_doc)
+
+
 def counter_generator(seed: int, step: int, stream: int) -> torch.Generator:
     """Generator seeded from blake2b("seed:step:stream"): counter-based randomness, distinct triples never alias."""
     digest = hashlib.blake2b(f"{seed}:{step}:{stream}".encode(), digest_size=8).digest()

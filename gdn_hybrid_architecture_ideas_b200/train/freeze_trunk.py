@@ -1,6 +1,7 @@
 """Guard for training a small part of a model on a frozen trunk: the frozen parameters take no gradient, own no
 optimizer state, and their bytes are checked against a digest taken at start
-(reference: ced/train/freeze_trunk.py:57-219)."""
+(reference: ced/train/freeze_trunk.py:57-219, where the part that trains is the copy-paste head; here it guards the
+drafter head's training on a finished trunk, scripts/train_mtp.py)."""
 
 from __future__ import annotations
 

@@ -35,7 +35,7 @@ from .optim import build_optimizer, grad_norm
 EXIT_DIVERGED = 86
 
 
-from . import bpb_readout, periodic_eval
+from . import bpb_readout, monitor, periodic_eval
 
 
 class Diverged(RuntimeError):
@@ -114,6 +114,22 @@ class Trainer:
             from .tst import TSTPlan
 
             self.tst = TSTPlan(cfg.tst, self.data, cfg.model.vocab_size, cfg.data.batch_size, cfg.seed)
+        self.shape = None
+        if cfg.shape_schedule:       # rows per step and row length by phases of the run's tokens
+            from .shape_schedule import ShapeSchedule
+
+            if cfg.tst.schedule or cfg.tensor_parallel > 1 or cfg.cuda_graphs != "none" or cfg.data_prefetch:
+                raise ValueError("shape_schedule changes the batch shape between phases: not built together with tst.schedule, "
+                                 "tensor_parallel, cuda_graphs or data_prefetch")
+            self.shape = ShapeSchedule(cfg.shape_schedule, cfg.steps, cfg.data.batch_size, cfg.data.seq_len, cfg.micro_batch_size, cfg.shape_lr)
+            bad = [p.rows for p in self.shape.phases if p.rows % self.world]
+            if bad:
+                raise ValueError(f"shape_schedule: rows per step {bad} must divide over the {self.world} data-parallel ranks")
+        import os
+
+        self._nvtx = os.environ.get("GHB_NVTX", "0") == "1"      # named ranges around the step's phases for a profiler timeline
+        self._wandb = None
+        self.total_steps = cfg.steps if self.shape is None else self.shape.total_steps      # optimizer steps of the run
         self.step = 0
         self.wandb_run_id = None
         self.init_info = self.resume_info = None
@@ -178,12 +194,29 @@ class Trainer:
     # ------------------------------------------------------------------ data
 
     def batch_at(self, step: int):
+        if self.shape is not None:
+            from ..data.synthetic import short_rows
+
+            sh = self.shape.at(step)
+            per = sh.rows // self.world
+            return short_rows(self.data, sh.first_row + self.rank * per, per, sh.seq_len, self.cfg.data.seq_len)
         B = self.cfg.data.batch_size
         first, count = self.dp.rows(B) if (self.dp is not None and self.tp is None) else (0, B)   # tensor-parallel ranks share the rows
         src_step = step + self.cfg.data_start_step
         if self.tst is not None:
             return self.tst.batch_at(src_step, first, count)
         return self.data.batch(src_step, first, count)
+
+    def lr_at(self, step: int) -> float:
+        """The schedule's LR of optimizer step `step`: under a batch-shape schedule read at the step's token clock (and
+        divided by the phase's steps per reference step in "rows" mode), so warm-up and decay sit where they are in tokens."""
+        if self.shape is None:
+            return lr_of(self.cfg, step)
+        from .lr import lr_schedule
+
+        sh = self.shape.at(min(step, self.shape.total_steps - 1))
+        total = self.cfg.steps if self.cfg.optim.schedule_steps is None else self.cfg.optim.schedule_steps
+        return lr_schedule(self.cfg.optim, total, sh.clock) * sh.lr_scale
 
     def _global_counts(self, batch) -> tuple[int, int]:
         """(valid targets over all ranks, bad-batch flag over all ranks) from one host reduction."""
@@ -244,12 +277,18 @@ class Trainer:
         fused head + loss, backward), gradient synchronisation, clip, update. Returns a device tensor
         (loss, ce sum, gradient norm, kernel status word); nothing is read back to the host here."""
         cfg = self.cfg
-        lr = lr_of(cfg, self.step) if lr is None else lr
+        lr = self.lr_at(self.step) if lr is None else lr
         if self.zero is not None:
             self.zero.before_step()     # the last step's first-read parameters have landed; peers are done with its gradients
         self.flat.grads.zero_()
         rows = batch.tokens.shape[0]
         micro = cfg.micro_batch_size or rows
+        if self.shape is not None:      # the config's TOKENS per forward/backward, whatever the phase's row length
+            sh = self.shape.at(self.step)
+            per_rank = cfg.micro_batch_size or max(1, cfg.data.batch_size // self.world)
+            micro = max(1, min(rows, per_rank * cfg.data.seq_len // sh.seq_len))
+            while rows % micro:
+                micro -= 1
         if rows % micro:
             raise ValueError(f"micro_batch_size {micro} does not divide this rank's {rows} rows")
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
@@ -260,13 +299,17 @@ class Trainer:
                 loss, ce = self.graphs.micro(mb, n_global)
                 loss_sum += loss
             else:
-                loss, ce = self._micro_loss(mb, max(n_global, 1))
+                with monitor.nvtx_range("forward", self._nvtx):
+                    loss, ce = self._micro_loss(mb, max(n_global, 1))
                 if self.zero is not None:       # gradients are final after the last micro-batch: its finished buckets may leave
                     self.zero.armed = lo + micro >= rows
-                loss.backward()
+                with monitor.nvtx_range("backward", self._nvtx):
+                    loss.backward()
                 loss_sum += loss.detach().float()
             ce_sum += ce.float()
         stats = torch.stack([loss_sum, ce_sum]).double()
+        nvtx_sync = monitor.nvtx_range("grad_sync+optimizer", self._nvtx)
+        nvtx_sync.__enter__()
         if self.zero is not None:
             gnorm = self.zero.sync_and_step(self.optimizer, lr, cfg.optim.grad_clip, stats)
         elif self.tp is not None:
@@ -284,17 +327,22 @@ class Trainer:
             if self.dp is not None:
                 self.dp.all_reduce_(self.flat.grads)
                 self.dp.all_reduce_(stats)
+            if cfg.log_every and self.step % cfg.log_every == 0:      # per-family gradient norms before clipping (whole gradients are here)
+                self._family_norms = monitor.family_grad_norms(self.flat)
             gnorm = grad_norm(self.flat)
             self.optimizer.step(lr, _clip_coef(gnorm, cfg.optim.grad_clip))
         if not cfg.freeze_trunk and self.model.encoder.scalar_form != "none":
             if self.zero is not None:
                 self.zero.settle()
             self.model.encoder.project_layer_scalars()      # the span-bounded residual scalars back into their range
+        nvtx_sync.__exit__(None, None, None)
         self.step += 1
         from .. import ops
 
         status = ops.status_word(self.device).to(torch.float32).reshape(())      # kernels' bounded waits report here (0 = clean)
-        return torch.stack([stats[0].float(), stats[1].float(), gnorm.float(), status])
+        out = torch.stack([stats[0].float(), stats[1].float(), gnorm.float(), status])
+        fam, self._family_norms = getattr(self, "_family_norms", None), None
+        return out if fam is None else torch.cat([out, fam.float()])
 
     def train_step(self) -> dict:
         """One full training step through the public path: build this rank's batch (a pure function of the step),
@@ -311,7 +359,7 @@ class Trainer:
         n_global, bad = self._global_counts(batch)
         if bad:
             self._halt_bad_batch(step)
-        lr = lr_of(cfg, step)
+        lr = self.lr_at(step)
         if self.tst is not None:
             factor = self.tst.lr_factor(step)
             if factor is not None:
@@ -322,17 +370,29 @@ class Trainer:
         dev_batch = batch.to(self.device)
         host = self.device_step(dev_batch, n_global, lr).cpu()      # the step's one device->host read
         self.d2h_bytes = host.numel() * host.element_size()
-        loss_v, ce_v, gn_v, status = (float(x) for x in host)
+        loss_v, ce_v, gn_v, status = (float(x) for x in host[:4])
         self._check_kernel_status(int(status), step)
         seconds = time.perf_counter() - t0
         s = batch.tokens.shape[2] if batch.tokens.dim() == 3 else 1
         n_tokens = cfg.data.batch_size * cfg.data.seq_len * s
+        if self.shape is not None:
+            n_tokens = self.shape.at(step).rows * self.shape.at(step).seq_len
         m = {"step": step, "loss": loss_v, "ce_dec": ce_v, "lr": lr, "grad_norm": gn_v, "n_targets": n_global,
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
         if tst_event is not None:
             m["tst_switch"] = tst_event
+        if host.numel() > 4:        # a logging step: gradient norm per parameter family, the depth-mix readers' state
+            m.update({f"grad_norm/{n}": float(v) for n, v in zip(monitor.family_names(), host[4:])})
+            readers = monitor.depth_reader_summary(self.model)
+            if readers:
+                m["depth_readers"] = readers
+        if cfg.log_stream_rms_every and self.step % cfg.log_stream_rms_every == 0:
+            with torch.no_grad(), monitor.StreamRMS(self.model) as rms:
+                probe = _slice(dev_batch, 0, 1)
+                self.model(probe.tokens, probe.doc_ids, return_hidden=True, single_doc=probe.single_doc)
+            m["stream_rms"] = rms.values()
         if self.zero_wgrad is not None and self.step % cfg.log_zero_wgrad_every == 0:
             m.update(self.zero_wgrad.summary())
         self.last_metrics = m
@@ -350,7 +410,7 @@ class Trainer:
         cfg = self.cfg
         if self.run_dir is not None and (self.run_dir / "diverged.json").exists():
             raise Diverged(f"{self.run_dir} is marked diverged: start a new run directory")
-        end = cfg.steps if until_step is None else min(cfg.steps, until_step)
+        end = self.total_steps if until_step is None else min(self.total_steps, until_step)
         old = None
         try:
             old = signal.signal(signal.SIGTERM, self._request_stop)
@@ -358,6 +418,9 @@ class Trainer:
             pass
         self._jsonl({"event": "start", "step": self.step, "world": self.world, "device": str(self.device),
                      "params": sum(p.numel() for p in self.model.parameters())})
+        if self.lead and cfg.wandb.mode != "disabled":
+            self._wandb = monitor.WandbLogger(cfg.wandb, self.wandb_run_id, C.to_dict(cfg), directory=self.run_dir)
+            self.wandb_run_id = self._wandb.run_id
         try:
             while self.step < end:
                 m = self.train_step()
@@ -386,9 +449,14 @@ class Trainer:
                     self._saver.commit()
                 if due or stop:
                     self.save_checkpoint(sync=stop or self.step == end)
+                if self._wandb is not None:      # after the save: logging can never hold up a checkpoint
+                    self._wandb.log(m, self.step)
                 if stop:
                     break
         finally:
+            if self._wandb is not None:
+                self._wandb.finish()
+                self._wandb = None
             if self._saver is not None:
                 self._saver.commit(block=True)
             if old is not None:

@@ -43,9 +43,14 @@ def main(argv=None) -> int:
         mtp.attach_mtp(model)
         model.mtp.to(a.device)
     head = mtp.freeze_trunk(model)
+    # the frozen trunk is guarded: no gradient, no optimizer state, and its bytes are checked against the digest taken here
+    from gdn_hybrid_architecture_ideas_b200.train.freeze_trunk import TrunkGuard
+
+    guard = TrunkGuard(model, (mtp.PREFIX,))
     model.eval()
     model.mtp.train()
     opt = torch.optim.AdamW(head, lr=a.lr, weight_decay=a.weight_decay)
+    guard.check_optimizer(opt)
     data = make_data(cfg.data, cfg.model.vocab_size)
     rows = a.rows or cfg.data.batch_size
     ac = torch.autocast("cuda", dtype=torch.bfloat16) if a.device.startswith("cuda") else torch.autocast("cpu", enabled=False)
@@ -55,8 +60,11 @@ def main(argv=None) -> int:
         dev = lambda t: t.to(a.device, non_blocking=True)
         with ac:
             last = mtp.train_step(model, opt, dev(b.tokens), dev(b.doc_ids), dev(b.targets), dev(b.target_valid))
+        guard.check_grads()
         if a.log_every and (i % a.log_every == 0 or i == a.steps - 1):
+            guard.check_values()
             print(json.dumps({"step": i, **last}))
+    guard.check_values()
     if a.out:
         torch.save({"trunk_step": step, "head": {k: v.cpu() for k, v in model.state_dict().items() if k.startswith(mtp.PREFIX)}}, a.out)
     return 0

@@ -60,9 +60,10 @@ def test_reference_arm_assembles_its_line(monkeypatch, tmp_path):
     monkeypatch.setattr(bench, "ClockSampler", lambda enabled: types.SimpleNamespace(stop=lambda n: {"sm_mhz": 1.0, "sm_max_mhz": 1.0, "reasons": []}))
     monkeypatch.delenv("WORLD_SIZE", raising=False)
     args = types.SimpleNamespace(rows=16, seq_len=4096, steps=4, warmup=1, gpus=1)
+    monkeypatch.setattr(sys, "path", list(sys.path))          # the arm puts its package directory in front: undone with the test
     out = bench.run_reference(args)
     for name in [m for m in sys.modules if m == "ced" or m.startswith("ced.")]:
-        monkeypatch.delitem(sys.modules, name)
+        del sys.modules[name]          # the stub package must not outlive the test (a monkeypatched deletion would be undone)
     assert out.get("impl") == "reference" and "unavailable" not in out, out
     assert out["config"]["global_batch"] == 16 and out["ms_per_step"] == 20.0
     assert out["value"] == pytest.approx(16 * 4096 / 0.020) and out["e2e"]["value"] == out["value"]
@@ -184,3 +185,29 @@ def test_tensor_parallel_trainer_from_seed_checkpoints_the_full_model(tmp_path):
     lines = [json.loads(x) for x in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines()]
     got = next(x for x in lines if x.get("step") == 0 and "loss" in x)["loss"]
     assert abs(got - first) < 1e-4 * max(1.0, abs(first)), (got, first)
+
+
+def test_monitors_and_best_effort_wandb(tmp_path, capsys):
+    """A logging step carries the gradient norm per parameter family (their squares add up to the clipped norm's), the
+    depth-mix readers' state and, when asked, the stream RMS per layer; an unusable W&B sink warns and the run goes on."""
+    import json
+
+    cfg = _tiny(steps=2, log_every=1, log_stream_rms_every=1)
+    cfg.wandb.mode = "offline"
+    cfg.ckpt_every_steps = 0
+    t = Trainer(cfg, tmp_path / "r")
+    t.fit()
+    lines = [json.loads(x) for x in (tmp_path / "r" / "metrics.jsonl").read_text().splitlines()]
+    step0 = next(x for x in lines if x.get("step") == 0 and "loss" in x)
+    fam = {k: v for k, v in step0.items() if k.startswith("grad_norm/")}
+    assert set(fam) >= {"grad_norm/embed", "grad_norm/gdn", "grad_norm/attention", "grad_norm/mlp", "grad_norm/depth_mix"}
+    assert sum(v * v for v in fam.values()) ** 0.5 == pytest.approx(step0["grad_norm"], rel=1e-4)
+    assert len(step0["stream_rms"]) == len(t.model.encoder.layers) and len(step0["depth_readers"]["readers"]) > 0
+    assert t.step == 2          # the run finished whether or not the W&B package exists here
+
+
+def test_cuda_graphs_step_is_refused_by_name():
+    cfg = _tiny()
+    cfg.cuda_graphs = "step"
+    with pytest.raises(ValueError, match="cuda_graphs"):
+        Trainer(cfg, None)
