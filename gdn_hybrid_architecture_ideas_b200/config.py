@@ -575,8 +575,18 @@ class TrainConfig(_Section):
 # ----------------------------------------------------------------------------------------------------------------
 
 
+# Keys this framework adds to the reference's config tree. They are left out of a written dict while at their defaults, so
+# a config or checkpoint of a run that does not use them loads, strictly, into the reference's dataclasses too.
+EXTENSION_DEFAULTS = {"tensor_parallel": 1}
+
+
 def to_dict(cfg) -> dict:
-    return dataclasses.asdict(cfg)
+    out = dataclasses.asdict(cfg)
+    if isinstance(cfg, TrainConfig):
+        for key, default in EXTENSION_DEFAULTS.items():
+            if out.get(key) == default:
+                del out[key]
+    return out
 
 
 def from_dict(cls, data: dict | None):

@@ -312,7 +312,7 @@ class ZeroPlan:
         whole.flat, whole.groups, whole.betas, whole.eps = f, opt.groups, opt.betas, opt.eps
         whole.ranges, whole.lo, whole.hi = [(0, f.size, 0)], 0, f.size
         whole.exp_avg, whole.exp_avg_sq, whole.steps = self._gather_moments(opt.exp_avg), self._gather_moments(opt.exp_avg_sq), opt.steps
-        whole.param_groups = opt.param_groups
+        whole.param_groups, whole.torch_order = opt.param_groups, opt.torch_order
         sd = FlatAdamW.state_dict(whole)
         if hasattr(opt, "buf"):
             gathered = self.dp.gather_host({n: b.cpu() for n, b in opt.buf.items()})

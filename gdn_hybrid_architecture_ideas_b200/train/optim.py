@@ -228,6 +228,9 @@ class FlatAdamW:
         self.steps = 0
         self.param_groups = [{"lr": 0.0, "lr_scale": g["lr_scale"], "weight_decay": g["weight_decay"], "kind": g["kind"]}
                              for g in groups]
+        # the order torch.optim numbers parameters in: group after group, each in the model's parameter order (the flat
+        # layout may order a group's tensors differently; checkpoints are written and read in this order)
+        self.torch_order = [[n for n in g["names"]] for g in groups]
 
     def owned(self, gi: int) -> list[tuple[int, int, int]]:
         """(first element, end, offset in the moment buffers) of every owned piece of group gi."""
@@ -268,25 +271,33 @@ class FlatAdamW:
                     lp.copy_(p)
 
     # ---- torch.optim-shaped state for checkpoints (reference: ced/train/trainer.py:3602-3627 saves optimizer.state_dict())
+    # Parameters are numbered as torch.optim.AdamW built over the same groups numbers them, and each group carries
+    # torch's own keys, so the file loads into a torch.optim.AdamW (the reference's optimizer) and the other way round.
+    TORCH_GROUP_KEYS = {"amsgrad": False, "maximize": False, "foreach": None, "capturable": False, "differentiable": False, "fused": None,
+                        "decoupled_weight_decay": True}
+
     def state_dict(self) -> dict:
-        state, index = {}, 0
+        state, index, names = {}, 0, []
         packed_groups = []
         for gi, g in enumerate(self.param_groups):
             ids = []
-            for s in (s for s in self.flat.segments if s.group == gi):
+            for name in self.torch_order[gi]:
+                s = self.flat.by_name[name]
                 own = self.pieces(s)
-                if g["kind"] == "adamw" and len(own) == 1 and own[0][1] - own[0][0] == s.numel:      # wholly this rank's
+                if g["kind"] == "adamw" and self.steps > 0 and len(own) == 1 and own[0][1] - own[0][0] == s.numel:      # wholly this rank's
                     a = own[0][2]
                     state[index] = {"step": torch.tensor(float(self.steps)),
                                     "exp_avg": self.exp_avg[a:a + s.numel].view(s.shape).clone(),
                                     "exp_avg_sq": self.exp_avg_sq[a:a + s.numel].view(s.shape).clone()}
                 ids.append(index)
+                names.append(name)
                 index += 1
-            packed_groups.append({**g, "betas": self.betas, "eps": self.eps, "params": ids})
-        return {"state": state, "param_groups": packed_groups, "names": [s.name for s in self.flat.segments]}
+            packed_groups.append({**self.TORCH_GROUP_KEYS, **g, "betas": self.betas, "eps": self.eps, "params": ids})
+        return {"state": state, "param_groups": packed_groups, "names": names}
 
     def load_state_dict(self, sd: dict) -> None:
-        names = sd.get("names") or [s.name for s in self.flat.segments]
+        names = sd.get("names") or [n for group in self.torch_order for n in group]       # a torch.optim file: numbered in torch's order
+        self.reset_moments()
         for index, name in enumerate(names):
             st = sd["state"].get(index)
             s = self.flat.by_name.get(name)

@@ -266,3 +266,64 @@ def test_entmax_attention_chunks_equal_one_pass():
         outs.append((o.detach(), *grads))
     for a, b in zip(*outs):
         assert (a - b).abs().max() < 1e-12
+
+
+def _tiny_train_cfg():
+    cfg = C.TrainConfig(model=C.tiny_full_config(), data=C.tiny_data_config(seq_len=48, batch_size=4), steps=6, seed=3)
+    cfg.optim.warmup_steps, cfg.ckpt_every_steps, cfg.metrics_jsonl, cfg.head_impl, cfg.log_every, cfg.device = 2, 0, False, "chunked", 1000, "cpu"
+    return cfg
+
+
+def test_checkpoints_cross_between_the_trainers(reference, tmp_path):
+    """The checkpoint format is shared: a file written by the reference's Trainer loads into this Trainer (weights and
+    AdamW moments, so the next update is the reference's next update on the same batch), and a file written here loads
+    into the reference's Trainer."""
+    import ced.config as RC
+    from ced.train.trainer import Trainer as RefTrainer
+
+    from gdn_hybrid_architecture_ideas_b200.train import checkpoint as ckpt
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    cfg = _tiny_train_cfg()
+    ref_cfg = RC.from_dict(RC.TrainConfig, C.to_dict(cfg))
+    theirs = RefTrainer(ref_cfg, str(tmp_path / "ref"))
+    for _ in range(2):
+        theirs.train_step()
+    ref_path = theirs.save_checkpoint()
+    state = ckpt.load(ref_path)
+    mine = Trainer(cfg, tmp_path / "mine")
+    mine.load_state_dict(state, check_config=False)
+    assert mine.step == 2
+    sd, rsd = mine.model.state_dict(), theirs.model.state_dict()
+    assert all(torch.equal(sd[k], rsd[k]) for k in rsd)
+    # the moments came along: one more update of each trainer on ONE batch (given to both) lands on the same weights
+    batch = mine.batch_at(2)
+    n = int(batch.target_valid.sum())
+    mine.device_step(batch, n, lr=1e-3)
+    ref_opt = theirs.optimizer
+    for g in ref_opt.param_groups:
+        g["lr"] = 1e-3 * g.get("lr_scale", 1.0)
+    theirs.model.zero_grad(set_to_none=True)
+    out = theirs.model(batch.tokens, batch.doc_ids, None, return_hidden=True)
+    from ced.model.looped_ced import lm_head as ref_head
+
+    logits = ref_head(out.hidden_aux, theirs.model.head_weight()).float()
+    lse = logits.logsumexp(-1)
+    ce = lse - logits.gather(-1, batch.targets[..., None])[..., 0]
+    valid = batch.target_valid.float()
+    ((valid * (ce + cfg.loss.z_loss * lse ** 2)).sum() / n).backward()
+    torch.nn.utils.clip_grad_norm_(theirs.model.parameters(), cfg.optim.grad_clip)
+    ref_opt.step()
+    sd, rsd = mine.model.state_dict(), theirs.model.state_dict()
+    worst = max((sd[k] - rsd[k]).abs().max().item() for k in rsd)
+    assert worst < 2e-6, worst
+    # and back: this trainer's file into the reference's trainer
+    path = mine.save_checkpoint()
+    back = RefTrainer(ref_cfg, str(tmp_path / "ref2"))
+    back.load_state_dict(torch.load(path, weights_only=False), check_data=False)
+    assert back.step == mine.step
+    bsd = back.model.state_dict()
+    assert all(torch.equal(bsd[k], sd[k]) for k in sd)
+    st = back.optimizer.state_dict()["state"]
+    assert len(st) > 0 and all(float(v["step"]) == 3.0 for v in st.values())
+    back.train_step()          # the loaded optimizer steps (every key torch's AdamW reads is in the file's groups)

@@ -487,7 +487,7 @@ def test_linear_depth_memory(tmp_path):
     with pytest.raises(ValueError):
         make_model(bad, dtype=torch.float32)
     graphs = copy.deepcopy(tc)
-    graphs.cuda_graphs = "step"
+    graphs.cuda_graphs = "microbatch"
     with pytest.raises(ValueError, match="tensor ops"):
         Trainer(graphs, tmp_path / "g")
 
