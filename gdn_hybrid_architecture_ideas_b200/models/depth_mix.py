@@ -36,28 +36,35 @@ class DepthQuery(nn.Module):
         return ops.depth_mix(sources, self.query, self.key_norm.weight, self.key_norm.eps)
 
 
-OWN_SEED_OFFSET = 0x1D3_2610_18809
+OWN_SEED_OFFSET = 0x1D3_2610_18809      # added to the run's seed for the address networks' generator (shared with the reference: equal starts)
 
 
 class OwnLinear(nn.Linear):
-    """A Linear (with bias) the model's N(0, init_std) pass leaves alone: zeros at construction (no draw from the global
-    generator), then started by `init_own_parameters` from a generator of its own, so every other tensor starts as in
-    the model without it (reference: ced/model/ldm.py:88-101)."""
+    """A biased Linear that takes no part in the model's general initialisation: it is zero when built (so building it
+    draws nothing from the global generator) and marked `own_init`, which the model's N(0, init_std) pass skips. Its start
+    comes later from `init_own_parameters`, out of a generator reserved for these layers; a model with such layers
+    therefore starts with exactly the base weights of the model without them (reference: ced/model/ldm.py:88-101)."""
 
     own_init = True
 
     def reset_parameters(self) -> None:
-        with torch.no_grad():
-            self.weight.zero_()
-            if self.bias is not None:
-                self.bias.zero_()
+        for t in (self.weight, self.bias):
+            if t is not None:
+                nn.init.zeros_(t)
+
+
+def _affine(layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    """layer(x) with the layer's tensors cast to x's dtype (the networks run in the stream's dtype under autocast too)."""
+    return torch.nn.functional.linear(x, layer.weight.to(x.dtype), layer.bias.to(x.dtype))
 
 
 class AddressNet(nn.Module):
-    """RMSNorm -> Linear(d, hidden) -> SiLU -> an address head Linear(hidden, out) and, with `gates`, a gate head
-    Linear(hidden, gates). zero_head (a token-dependent query, which must start as the zero pseudo-query): the head
-    starts at zero; otherwise it is drawn as the backbone's linears are. The gate head starts at zero
-    (reference: ced/model/ldm.py:103-137)."""
+    """A small per-position network that turns the stream into an address: RMSNorm -> `inp` (d -> hidden) -> SiLU ->
+    `head` (hidden -> out), plus, when `gates` > 0, a second head `gate` (hidden -> gates) of gate logits.
+
+    Start (`reset_own`): `inp` ~ N(0, std); `head` ~ N(0, std), or zero with `zero_head` (a token-dependent depth query
+    must start as the zero pseudo-query, i.e. a uniform read); every bias and the whole gate head zero (gates start
+    open at sigmoid(0)). Draw order: inp.weight, then head.weight (reference: ced/model/ldm.py:103-137)."""
 
     def __init__(self, d: int, hidden: int, out: int, eps: float, gates: int = 0, zero_head: bool = True):
         super().__init__()
@@ -69,40 +76,34 @@ class AddressNet(nn.Module):
 
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float) -> None:
-        draw = lambda t: t.copy_(torch.randn(t.shape, generator=g, dtype=torch.float32, device="cpu") * std)
-        draw(self.inp.weight)
-        self.inp.bias.zero_()
-        if self.zero_head:
-            self.head.weight.zero_()
-        else:
-            draw(self.head.weight)
-        self.head.bias.zero_()
-        if self.gate is not None:
-            self.gate.weight.zero_()
-            self.gate.bias.zero_()
+        for layer in (self.inp, self.head, self.gate):
+            if layer is not None:
+                layer.reset_parameters()
+        drawn = [self.inp.weight] + ([] if self.zero_head else [self.head.weight])
+        for w in drawn:
+            w.copy_(torch.randn(w.shape, generator=g, dtype=torch.float32, device="cpu") * std)
 
     def hidden(self, x: torch.Tensor) -> torch.Tensor:
-        lin = torch.nn.functional.linear
-        return torch.nn.functional.silu(lin(self.norm(x, out_dtype=x.dtype), self.inp.weight.to(x.dtype), self.inp.bias.to(x.dtype)))
+        return torch.nn.functional.silu(_affine(self.inp, self.norm(x, out_dtype=x.dtype)))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return torch.nn.functional.linear(self.hidden(x), self.head.weight.to(x.dtype), self.head.bias.to(x.dtype))
+        return _affine(self.head, self.hidden(x))
 
     def both(self, x: torch.Tensor):
-        """(address, gate logits)."""
-        hid, lin = self.hidden(x), torch.nn.functional.linear
-        return lin(hid, self.head.weight.to(x.dtype), self.head.bias.to(x.dtype)), lin(hid, self.gate.weight.to(x.dtype), self.gate.bias.to(x.dtype))
+        """(address, gate logits) from one pass through the trunk."""
+        h = self.hidden(x)
+        return _affine(self.head, h), _affine(self.gate, h)
 
 
 def init_own_parameters(model: nn.Module, std: float) -> int:
-    """Start every address network, in module order, from a CPU generator seeded with torch.initial_seed() + a fixed
-    offset; the global generator is not drawn (reference: ced/model/ldm.py:423-438)."""
-    nets = [m for m in model.modules() if isinstance(m, AddressNet)]
-    if nets:
-        g = torch.Generator().manual_seed((torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63))
-        for m in nets:
-            m.reset_own(g, std)
-    return len(nets)
+    """Starts every AddressNet of `model`, in module order, from ONE CPU generator seeded with the run's seed + a fixed
+    offset; the global generator is neither read nor advanced (reference: ced/model/ldm.py:423-438)."""
+    found = [m for m in model.modules() if isinstance(m, AddressNet)]
+    if found:
+        gen = torch.Generator().manual_seed((torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63))
+        for net in found:
+            net.reset_own(gen, std)
+    return len(found)
 
 
 class TokenQuery(nn.Module):

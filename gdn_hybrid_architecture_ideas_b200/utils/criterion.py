@@ -1,33 +1,41 @@
-"""Pass/fail rule of a numeric check: a candidate's error against a ground truth is compared with the error a reference
-path makes against the same ground truth.
+"""Acceptance rule for numeric comparisons: a candidate's error against a ground truth is judged against the error a
+trusted path makes against the same truth, not against a bare tolerance.
 
-    "sum":  err <= factor * err_ref + floor        "max":  err <= max(factor * err_ref, floor)
+A `Rule` turns the trusted path's error `ref` into an allowance
 
-optionally capped (`ceil`) and scaled (`scale`, e.g. by |value|). A reading records whether it passed by the ratio
-alone (err <= factor * err_ref) or only through the floor; a NaN error or bound never passes. Pure Python, so tools and
-tests can import it without torch (reference: ced/utils/criterion.py:64-334).
+    form "sum":  factor * ref + floor          form "max":  max(factor * ref, floor)
+
+clipped from above by `ceil` when given and multiplied by `scale` when the check is relative to a magnitude. A `Reading`
+is one judged comparison; besides pass / fail it tells apart a pass earned by the ratio (err <= factor * ref) from one
+that only the floor allowed, because a check that passes through its floor alone says little about the candidate. NaN
+never passes, on either side. No torch import at module level: tools that only judge numbers load this without it
+(reference: ced/utils/criterion.py:64-334).
 """
 
 from __future__ import annotations
 
 import math
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 ONLY_FLOOR = "PASS ONLY THROUGH THE FLOOR"
 BY_RATIO = "ok (ratio alone)"
+_FORMS = ("sum", "max")
 
 
 def over(err: float, bound: float) -> bool:
-    """True when err exceeds the bound or either is NaN."""
+    """err > bound, with NaN on either side counting as over."""
     return not (err <= bound)
 
 
 def nan_max(values, default: float = math.nan) -> float:
-    """max() that keeps a NaN (Python's max drops a NaN that is not first)."""
-    xs = [float(v) for v in values]
-    if not xs:
-        return default
-    return math.nan if any(math.isnan(x) for x in xs) else max(xs)
+    """Largest value, NaN if any value is NaN (the built-in max silently drops a NaN unless it comes first)."""
+    best, seen = -math.inf, False
+    for v in values:
+        x = float(v)
+        if x != x:
+            return math.nan
+        best, seen = (x if x > best else best), True
+    return best if seen else default
 
 
 @dataclass(frozen=True)
@@ -36,22 +44,28 @@ class Rule:
     floor: float
     form: str = "sum"
     ceil: float | None = None
-    source: str = ""
+    source: str = ""        # where the numbers come from (a measurement, a file), for reports
 
     def __post_init__(self):
-        if self.form not in ("sum", "max"):
+        if self.form not in _FORMS:
             raise ValueError(f"Rule.form {self.form!r}: 'sum' or 'max'")
 
+    # -- the allowance
+    def ratio_part(self, ref: float, scale: float | None = None) -> float:
+        """The allowance the trusted path's error alone gives: factor * ref (times scale)."""
+        return self.factor * ref * (1.0 if scale is None else scale)
+
     def bound(self, ref: float, scale: float | None = None) -> float:
-        if math.isnan(ref):
+        if ref != ref:
             return math.nan
-        b = self.factor * ref + self.floor if self.form == "sum" else max(self.factor * ref, self.floor)
-        if self.ceil is not None:
-            b = min(b, self.ceil)
-        return b if scale is None else b * scale
+        scaled = self.factor * ref
+        allowance = scaled + self.floor if self.form == "sum" else (scaled if scaled > self.floor else self.floor)
+        if self.ceil is not None and allowance > self.ceil:
+            allowance = self.ceil
+        return allowance * (1.0 if scale is None else scale)
 
     def passes(self, err: float, ref: float, scale: float | None = None) -> bool:
-        return bool(err <= self.bound(ref, scale))
+        return not over(err, self.bound(ref, scale))
 
     def read(self, label: str, err: float, ref: float, scale: float | None = None) -> "Reading":
         return Reading(label, float(err), float(ref), self, scale)
@@ -61,11 +75,10 @@ class Rule:
         return self.form == "sum" and self.floor == 0.0
 
     def formula(self) -> str:
+        ratio = f"{self.factor:g} x ref"
         if self.no_floor:
-            return f"{self.factor:g} x ref (no floor)"
-        joiner = " + floor " if self.form == "sum" else ", floor "
-        body = f"{self.factor:g} x ref{joiner}{self.floor:g}"
-        return body if self.form == "sum" else f"max({body})"
+            return ratio + " (no floor)"
+        return f"{ratio} + floor {self.floor:g}" if self.form == "sum" else f"max({ratio}, floor {self.floor:g})"
 
 
 @dataclass(frozen=True)
@@ -82,36 +95,43 @@ class Reading:
 
     @property
     def ok(self) -> bool:
-        return self.rule.passes(self.err, self.ref, self.scale)
+        return not over(self.err, self.bound)
 
     @property
     def by_ratio(self) -> bool:
-        rb = self.rule.factor * self.ref * (1.0 if self.scale is None else self.scale)
-        return bool(self.err <= rb)
+        return not over(self.err, self.rule.ratio_part(self.ref, self.scale))
 
     @property
     def only_floor(self) -> bool:
         return self.ok and not self.by_ratio
 
+    @property
+    def verdict(self) -> str:
+        if not self.ok:
+            return "FAIL"
+        return BY_RATIO if self.by_ratio else ONLY_FLOOR
+
     def line(self) -> str:
-        verdict = "FAIL" if not self.ok else (BY_RATIO if self.by_ratio else ONLY_FLOOR)
-        return f"{self.label}: err {self.err:.3e} ref {self.ref:.3e} bound {self.bound:.3e} [{self.rule.formula()}] {verdict}"
+        return (f"{self.label}: err {self.err:.3e} ref {self.ref:.3e} bound {self.bound:.3e} "
+                f"[{self.rule.formula()}] {self.verdict}")
 
 
 @dataclass
 class Tally:
-    """Counts over the readings of one check run."""
+    """Running counts over the readings of one check run; keeps the failed readings for the report."""
     passed: int = 0
     failed: int = 0
     floor_only: int = 0
+    failures: list = field(default_factory=list)
 
-    def add(self, r: Reading) -> Reading:
-        if not r.ok:
-            self.failed += 1
-        else:
+    def add(self, reading: Reading) -> Reading:
+        if reading.ok:
             self.passed += 1
-            self.floor_only += int(r.only_floor)
-        return r
+            self.floor_only += reading.only_floor
+        else:
+            self.failed += 1
+            self.failures.append(reading)
+        return reading
 
     @property
     def ok(self) -> bool:
@@ -122,8 +142,6 @@ class Tally:
 
 
 def tensor_errors(candidate, reference, truth) -> tuple[float, float]:
-    """(err, err_ref): max-abs error of candidate and of reference against a ground truth (tensors or nested lists of
-    numbers; torch is imported only if tensors are passed)."""
-    import torch
+    """(candidate's, trusted path's) largest absolute deviation from `truth`, all three tensors, compared in float64."""
     t = truth.double()
     return float((candidate.double() - t).abs().max()), float((reference.double() - t).abs().max())

@@ -3,6 +3,7 @@
 
 import copy
 import json
+import math
 import os
 import signal
 import subprocess
@@ -464,12 +465,13 @@ def test_linear_depth_memory(tmp_path):
     g = torch.Generator().manual_seed(0)
     x, v = torch.randn(2, 5, cfg.d_model, generator=g, dtype=torch.float64), torch.randn(2, 5, cfg.d_model, generator=g, dtype=torch.float64)
     M = torch.randn(2, 5, 4, 4, cfg.d_model // 4, generator=g, dtype=torch.float64)
-    kw, vw, lam = w.observation(x, v)
-    wgt = (kw * kw).sum(-1)                                    # w, since k is a unit vector
-    k = kw / wgt.sqrt()[..., None]
+    k, val, wgt = w._observation(x, v)                         # unit key per group, the value per group, the write weight
+    assert torch.allclose((k * k).sum(-1), torch.ones_like(wgt)) and torch.equal(val, v.unflatten(-1, (4, -1)))
+    lam = torch.sigmoid(w.lam_logit.detach().double())
     want = lam[:, None, None] * (M - wgt[..., None, None] * k[..., None] * (M * k[..., None]).sum(-2, keepdim=True)) \
         + wgt[..., None, None] * k[..., None] * v.unflatten(-1, (4, -1))[..., None, :]
     assert (w.write(M, x, v) - want).abs().max() < 1e-12
+    assert (ldm.memory_read(want, k) - (want * k[..., None]).sum(-2)).abs().max() < 1e-12
     assert abs(float(lam[0]) - 0.99) < 1e-6 and torch.allclose(wgt, torch.full_like(wgt, 2 * torch.sigmoid(torch.tensor(0.3, dtype=torch.float64))))
     tc = tiny_train_config()
     tc.model = cfg
@@ -478,10 +480,11 @@ def test_linear_depth_memory(tmp_path):
     for grp in optim.param_groups(t.model, tc.optim):
         if any(".attn_res." in n for n in grp["names"]):
             assert grp.get("kind", "adamw") == "adamw"
-    l0 = t.train_step()["loss"]
-    for _ in range(3):
-        l1 = t.train_step()["loss"]
-    assert l1 < l0
+    before = {n: p.detach().clone() for n, p in t.model.named_parameters() if ".attn_res." in n}
+    losses = [t.train_step()["loss"] for _ in range(4)]
+    assert all(math.isfinite(v) for v in losses)
+    moved = [n for n, p in t.model.named_parameters() if ".attn_res." in n and not torch.equal(p.detach(), before[n])]
+    assert len(moved) > 0.8 * len(before), (len(moved), len(before))          # the memory's tensors take part in training
     bad = C.tiny_full_config()
     bad.encoder.attn_res = "ldm"
     with pytest.raises(ValueError):
