@@ -57,7 +57,7 @@ class Batch:
                 mine.copy_(theirs, non_blocking=True)
 
     def h2d_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.tokens, self.targets, self.target_valid, self.doc_ids)
+        return sum(t.numel() * t.element_size() for t in (self.tokens, self.targets, self.target_valid, self.doc_ids, self.loss_mask)
                    if isinstance(t, torch.Tensor))
 
 

