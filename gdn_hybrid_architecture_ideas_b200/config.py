@@ -711,7 +711,7 @@ _TRAIN_BUILT = {
     "head_impl": ("fused", "chunked"),
     "activation_checkpoint": ("none", "layer", "block", "host", "host_overlap"),
     "freeze_trunk": (False,),
-    "precision_switch": (False,),
+    "precision_switch": (False, True),
     "cuda_graphs": ("none", "microbatch"),        # "step" (clip + optimizer inside a graph) is not built: the update kernels take the LR by value
     "wgrad_accum": ("autograd", "fp32"),
     "optimizer_sharding": ("replicated", "zero1", "zero2"),

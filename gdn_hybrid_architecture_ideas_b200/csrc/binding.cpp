@@ -498,11 +498,6 @@ void gemm_tp(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& out,
                               err.data_ptr<int>(), sm_count(), stream());
   TORCH_CHECK(rc == 0, "gemm_tp refused (code ", rc, "): M=", M, " N=", N, " K=", K, " cuerr=", ghb::last_encode_error());
 }
-void tp_rs_reduce(const Tensor& stage, Tensor& out, const Tensor& args, Tensor& err) {
-  const c10::cuda::CUDAGuard guard(stage.device());
-  TORCH_CHECK(is_bf16(stage) && stage.is_contiguous() && out.is_contiguous() && (is_bf16(out) || is_f32(out)), "tp_rs_reduce: layout");
-  check(ghb::tp_rs_reduce(stage.data_ptr(), out.data_ptr(), is_f32(out), out.numel(), args.data_ptr(), err.data_ptr<int>(), sm_count(), stream()), "tp_rs_reduce");
-}
 void tp_signal(const Tensor& args, int64_t word, const Tensor& like) {
   const c10::cuda::CUDAGuard guard(like.device());
   check(ghb::tp_signal(args.data_ptr(), word, stream()), "tp_signal");
@@ -550,7 +545,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prep_fwd", &attn_prep_fwd);
   m.def("attn_prep_bwd", &attn_prep_bwd);
   m.def("gemm_tp", &gemm_tp);
-  m.def("tp_rs_reduce", &tp_rs_reduce);
   m.def("tp_signal", &tp_signal);
   m.def("tp_args_bytes", &tp_args_bytes);
   m.def("tp_pad_words", &tp_pad_words);

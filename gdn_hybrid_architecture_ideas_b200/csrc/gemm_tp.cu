@@ -1,26 +1,32 @@
-// Tensor-parallel GEMMs fused with their sequence-parallel collectives over NVLink peer memory.
+// Tensor-parallel GEMMs fused with their sequence-parallel collectives over NVLink peer memory / NVSwitch multicast.
 //
 //   AG (all-gather -> GEMM): one operand is the concatenation over ranks of token shards ("gathered" buffer, rows
 //     [r Ts, (r+1) Ts) owned by rank r). A few CTAs of the launch push this rank's shard into every peer's gathered
-//     buffer with plain 16-byte peer stores, 128 rows at a time, and raise one flag per 128-row chunk on the
-//     destination; the GEMM CTAs of the same launch walk their tiles starting at the local shard and, before the TMA
-//     loads of a tile whose chunk came from a peer, wait (bounded) for that chunk's flag. The transfer of shard r + 2
-//     thus overlaps the math on shard r + 1. The gathered operand can be the row operand (forward, dgrad: chunks
-//     index the M tiles) or lie along the reduction (wgrad: chunks index the k-blocks).
-//   RS (GEMM -> reduce-scatter): the product is a partial sum over ranks whose rows are owned rank by rank. The
-//     epilogue stores each tile (bf16) straight into the owner's staging buffer, slot = this rank, starting with the
-//     next rank's rows so that at any time the ranks write to different owners; the last CTA to finish raises this
-//     rank's "landed" flag on every peer. `tp_rs_reduce` on the owner waits (bounded) for all ranks' flags and sums
-//     the slots in fp32: a deterministic reduction with bf16 on the wire.
+//     buffer, 128 rows at a time, and raise one flag per 128-row chunk on every destination. With a multicast mapping
+//     of the buffer the push is ONE `multimem.st` per 16 bytes that the switch delivers to all ranks (the shard leaves
+//     this GPU once instead of W - 1 times); without one, plain 16-byte peer stores rank by rank. The GEMM CTAs of the
+//     same launch walk their tiles starting at the local shard and, before the TMA loads of a tile whose chunk came
+//     from a peer, wait (bounded) for that chunk's flag: the transfer of later shards overlaps the math on earlier
+//     ones. The gathered operand can be the row operand (forward, dgrad: chunks index the M tiles) or lie along the
+//     reduction (wgrad: chunks index the k-blocks).
+//   RS (GEMM -> reduce-scatter): the product is a partial sum over ranks whose rows are owned rank by rank. Every rank
+//     writes its partial tiles (bf16, TMA tile stores) into its OWN symmetric buffer, walking the owners' row ranges
+//     starting with the next rank's, and raises "my partial rows for owner d are complete" on d as soon as they are.
+//     The same launch then reduces: each CTA, done with its tiles, waits (bounded) for every rank's flag for THIS
+//     rank's rows and sums them: one `multimem.ld_reduce` per 16 bytes when the buffer has a multicast mapping (the
+//     switch adds the W partial values in fp32 and returns the sum, so a row crosses this GPU's links once), else W
+//     peer loads summed in fp32. bf16 on the wire either way, a fixed summation order per path.
 //
 // Buffers are reused in rings; a writer never overwrites a slot before its readers are done: readers publish
-// "released up to call n" counters (`tp_signal`, the tail of `tp_rs_reduce`) and writers wait (bounded) for them.
+// "released up to call n" counters (`tp_signal`, and the tail of the RS launch) and writers wait (bounded) for them.
 // All flags are call sequence numbers written with system-scope release stores and read with acquire loads; a wait
-// that runs out writes a status code and the kernel drains and returns. No TMA load here uses cluster multicast.
+// that runs out writes a status code and the kernel drains and returns. No TMA load here uses cluster multicast
+// (`multimem.*` is the switch's multicast, a different mechanism).
 // The reference has no tensor parallelism; its sequence of NCCL calls for the same math would be all_gather_into_tensor
 // + matmul and matmul + reduce_scatter_tensor.
 #include "kernels.h"
 #include "sm100.cuh"
+#include "gemm_epilogue.cuh"
 #include <cstring>
 
 namespace ghb {
@@ -31,9 +37,7 @@ constexpr int BM = 128, BK = 64, UK = 16, BN = 256;
 constexpr int THREADS = 192;
 constexpr int STAGES = 4;
 constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-constexpr uint32_t STG_ROW = 144;      // bytes per staged row: 64 bf16 + 16 bytes of padding (conflict-free 16-byte accesses)
-constexpr uint32_t STG_BYTES = 4 * 32 * STG_ROW;   // RS epilogue staging: 4 warps x 32 rows
-constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + 256 + STG_BYTES + 1024;
+constexpr uint32_t SMEM = STAGES * (A_BYTES + B_BYTES) + EPI_SMEM_BYTES + 256 + 1024;      // operand ring, RS output slabs, barriers
 constexpr uint32_t TMEM_COLS = 2 * BN;
 constexpr int MAXR = 8;
 constexpr unsigned long long WAIT_NS = 2000000000ull;
@@ -61,9 +65,29 @@ struct Args {
   unsigned int need;                 // peers must have released uses <= need of the slot before it is overwritten
   int n_push;                        // CTAs [0, n_push) push, the rest multiply
   // --- scatter
-  __nv_bfloat16* stage[MAXR];        // every rank's staging buffer for this call's slot: [world][Ts][N]
+  __nv_bfloat16* stage[MAXR];        // every rank's partial-product buffer for this call's slot: [T][N]
   unsigned int* done_counter;        // local, zero between launches
+  unsigned int* owner_counters;      // local [MAXR], zero between launches: tiles of each owner's rows stored so far
+  // --- multicast views (null: peer loads / stores)
+  __nv_bfloat16* xg_mc;              // the gather slot on every rank at once
+  __nv_bfloat16* stage_mc;           // the partial-product slot of every rank at once
+  // --- scatter output
+  void* out;                         // [Ts][N] this rank's reduced rows
+  int out_f32;
+  int pad_;
 };
+
+__device__ __forceinline__ void mc_st16(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+               "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+// Sum over every rank's copy of 8 bf16 values, added in fp32 inside the switch, returned as bf16.
+__device__ __forceinline__ uint4 mc_ld_reduce_bf16x8(const void* p) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ unsigned long long now_ns() {
   unsigned long long t;
@@ -92,8 +116,8 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int se
 // out: 0 bf16, 1 fp32, 2 fp32 accumulate (modes AG and plain); RS writes bf16 staging tiles.
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(tp::THREADS, 1)
-gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, void* __restrict__ Cout,
-               long ldc, int M, int N, int K, const __grid_constant__ tp::Args a, int* __restrict__ err) {
+gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_c,
+               void* __restrict__ Cout, long ldc, int M, int N, int K, const __grid_constant__ tp::Args a, int* __restrict__ err) {
   using namespace tp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -108,6 +132,43 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const long chunks_per_shard = a.shard_rows / CHUNK;
     const long vec_per_row = a.row_elems / 8;                 // 16-byte vectors
     const __nv_bfloat16* src = a.xg[a.rank] + a.rank * a.shard_rows * a.ld;
+    constexpr int UNROLL = 8;                                  // loads in flight per thread: the copy is latency-bound otherwise
+    if (a.xg_mc) {
+      // one store per 16 bytes reaches every rank through the switch: wait until every destination has released the slot
+      if (threadIdx.x == 0) {
+        go = 1;
+        for (int d = 0; d < a.world && go; ++d)
+          if (d != a.rank) go = wait_flag(a.pad[a.rank] + PAD_AG_DONE + d, a.need) ? 1 : 0;
+        if (!go) atomicExch(err, 501);
+      }
+      __syncthreads();
+      if (!go) return;
+      __nv_bfloat16* dst = a.xg_mc + a.rank * a.shard_rows * a.ld;
+      for (long c = blockIdx.x; c < chunks_per_shard; c += a.n_push) {
+        const long total = CHUNK * vec_per_row;
+        for (long i0 = threadIdx.x; i0 < total; i0 += static_cast<long>(blockDim.x) * UNROLL) {
+          uint4 v[UNROLL];
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long i = i0 + static_cast<long>(u) * blockDim.x;
+            if (i < total) v[u] = reinterpret_cast<const uint4*>(src + (c * CHUNK + i / vec_per_row) * a.ld)[i % vec_per_row];
+          }
+#pragma unroll
+          for (int u = 0; u < UNROLL; ++u) {
+            const long i = i0 + static_cast<long>(u) * blockDim.x;
+            if (i < total) mc_st16(dst + (c * CHUNK + i / vec_per_row) * a.ld + (i % vec_per_row) * 8, v[u]);
+          }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          __threadfence_system();
+          for (int d = 0; d < a.world; ++d)
+            if (d != a.rank) st_release_sys(a.chunk[d] + a.rank * chunks_per_shard + c, a.seq);
+        }
+        __syncthreads();
+      }
+      return;
+    }
     for (int q = 1; q < a.world; ++q) {
       const int d = (a.rank - q + a.world) % a.world;         // destination d reads shard d + q as its q-th shard
       if (threadIdx.x == 0) {
@@ -119,7 +180,6 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       __nv_bfloat16* dst = a.xg[d] + a.rank * a.shard_rows * a.ld;
       for (long c = blockIdx.x; c < chunks_per_shard; c += a.n_push) {
         const long total = CHUNK * vec_per_row;
-        constexpr int UNROLL = 8;                              // loads in flight per thread: the copy is latency-bound otherwise
         for (long i0 = threadIdx.x; i0 < total; i0 += static_cast<long>(blockDim.x) * UNROLL) {
           uint4 v[UNROLL];
 #pragma unroll
@@ -147,12 +207,12 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   // ------------------------------------------------------------------ GEMM CTAs
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * (A_BYTES + B_BYTES));
+  uint8_t* slabs = smem + STAGES * (A_BYTES + B_BYTES);              // RS output staging (1024-byte aligned)
+  uint64_t* full = reinterpret_cast<uint64_t*>(slabs + EPI_SMEM_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
-  uint8_t* stg = smem + STAGES * (A_BYTES + B_BYTES) + 256;
 
   const int first = a.mode == 0 ? a.n_push : 0;
   const int cta = static_cast<int>(blockIdx.x) - first, n_cta = static_cast<int>(gridDim.x) - first;
@@ -170,6 +230,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (a.mode == 1) tma_prefetch_desc(&tma_c);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
     mbar_fence_init();
@@ -237,7 +298,8 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else {
     const int quad = warp & 3;
     int it = 0; bool ok = true;
-    unsigned int dest_ok = 0;                 // RS: destinations whose staging slot is known to be free
+    unsigned int dest_ok = 0;                 // RS: owners known to have finished reading this rank's buffer slot
+    uint32_t slab_count = 0;
     for (int t = cta; t < tiles && ok; t += n_cta, ++it) {
       const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
       int tm, tn; tile_of(t, tm, tn);
@@ -257,36 +319,22 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       }
       if (a.mode == 1) {
-        // RS: 64 columns at a time through shared memory, so that every peer store instruction covers 4 rows x 128
-        // contiguous bytes (a thread's own row segments would go out as isolated 16-byte writes over NVLink)
-        uint8_t* ws = stg + quad * 32 * STG_ROW;
+        // RS: the partial tile goes to THIS rank's buffer (TMA tile stores through the swizzled slabs); once every tile of an
+        // owner's row range is stored, the owner is told
         const int d = static_cast<int>((static_cast<long>(tm) * BM) / a.shard_rows);
-        __nv_bfloat16* tile0 = a.stage[d] + (static_cast<long>(a.rank) * a.shard_rows + (static_cast<long>(tm) * BM + quad * 32 - d * a.shard_rows)) * N;
-#pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          uint32_t r[64];
-          tmem_ld_x32(taddr + c * 64, r);
-          tmem_ld_x32(taddr + c * 64 + 32, r + 32);
-          tmem_ld_wait();
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            uint32_t p[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
-              p[e] = *reinterpret_cast<uint32_t*>(&h);
+        if (ok) {
+          epilogue_store_bf16<BN>(taddr, slabs, &tma_c, tm * BM, n0, N, quad, lane, slab_count, &tempty[acc]);
+          if (quad == 0 && lane == 0) {
+            tma_store_wait<0>();                       // the tile's stores are complete, not merely read out of shared memory
+            __threadfence_system();
+            const unsigned int total = static_cast<unsigned int>(tiles_per_shard) * static_cast<unsigned int>(tiles_n);
+            if (atomicAdd(a.owner_counters + d, 1u) + 1u == total) {
+              __threadfence_system();
+              st_release_sys(a.pad[d] + PAD_RS_READY + a.rank, a.seq);
+              a.owner_counters[d] = 0u;
             }
-            *reinterpret_cast<uint4*>(ws + lane * STG_ROW + v * 16) = make_uint4(p[0], p[1], p[2], p[3]);
           }
-          __syncwarp();
-          const int col0 = n0 + c * 64 + (lane & 7) * 8;
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int rr = it * 4 + (lane >> 3);
-            const uint4 v = *reinterpret_cast<const uint4*>(ws + rr * STG_ROW + (lane & 7) * 16);
-            if (ok && col0 < N) *reinterpret_cast<uint4*>(tile0 + static_cast<long>(rr) * N + col0) = v;
-          }
-          __syncwarp();
+          continue;
         }
       } else {
 #pragma unroll 1
@@ -340,57 +388,75 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (a.mode == 1 && threadIdx.x == 0) {      // RS: the last CTA to finish tells every rank that this rank's tiles have landed
-    __threadfence_system();
-    const unsigned int ticket = atomicAdd(a.done_counter, 1u);
-    if (ticket == gridDim.x - 1) {
-      __threadfence_system();
-      for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_READY + a.rank, a.seq);
-      *a.done_counter = 0u;
+  if (a.mode == 1) {
+    // RS, second half: this rank's rows. Every rank's partial rows for them are flagged as they complete; sum them (in the
+    // switch when the buffer is multicast-mapped) and write the reduced rows.
+    __shared__ int go_reduce;
+    if (threadIdx.x == 0) {
+      go_reduce = (*reinterpret_cast<volatile int*>(err) == 0) ? 1 : 0;
+      for (int j = 0; j < a.world && go_reduce; ++j) go_reduce = wait_flag(a.pad[a.rank] + PAD_RS_READY + j, a.seq) ? 1 : 0;
+      if (!go_reduce && *reinterpret_cast<volatile int*>(err) == 0) atomicExch(err, 508);
     }
-  }
-}
-
-// out[r][c] = sum_j stage[j][r][c] over the world's slots, after every rank's tiles of call `seq` have landed; then this
-// rank's "reduced" counter is published so writers may reuse the slot. out_f32: fp32 output (else bf16).
-__global__ void tp_rs_reduce_kernel(const __nv_bfloat16* __restrict__ stage, void* __restrict__ out, int out_f32, long n, tp::Args a,
-                                    int* __restrict__ err) {
-  using namespace tp;
-  __shared__ int go;
-  if (threadIdx.x == 0) {
-    go = 1;
-    for (int j = 0; j < a.world && go; ++j) go = wait_flag(a.pad[a.rank] + PAD_RS_READY + j, a.seq) ? 1 : 0;
-    if (!go) atomicExch(err, 508);
-  }
-  __syncthreads();
-  if (go) {
-    const long n8 = n / 8;
-    for (long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8; i += static_cast<long>(gridDim.x) * blockDim.x) {
-      float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int j = 0; j < a.world; ++j) {
-        const uint4 v = reinterpret_cast<const uint4*>(stage + j * n)[i];
+    __syncthreads();
+    if (go_reduce) {
+      // 16-byte items, several in flight per thread: a load over NVLink (or through the switch) takes microseconds, and the
+      // reduction is bound by how many of them are outstanding, not by arithmetic
+      constexpr int RU = 8;
+      const long n8 = a.shard_rows * N / 8;
+      const long base = static_cast<long>(a.rank) * a.shard_rows * N;
+      const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+      auto put = [&](long i, const float* sum) {
+        if (a.out_f32) {
+          float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + i * 8);
+          o[0] = make_float4(sum[0], sum[1], sum[2], sum[3]); o[1] = make_float4(sum[4], sum[5], sum[6], sum[7]);
+        } else {
+          uint32_t p[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { __nv_bfloat162 h = __floats2bfloat162_rn(sum[2 * e], sum[2 * e + 1]); p[e] = *reinterpret_cast<uint32_t*>(&h); }
+          reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + i * 8)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+      };
+      auto widen = [](const uint4 v, float* f, bool add) {
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e])); s[2 * e] += f.x; s[2 * e + 1] += f.y; }
-      }
-      if (out_f32) {
-        float4* o = reinterpret_cast<float4*>(static_cast<float*>(out) + i * 8);
-        o[0] = make_float4(s[0], s[1], s[2], s[3]); o[1] = make_float4(s[4], s[5], s[6], s[7]);
-      } else {
-        uint32_t p[4];
+        for (int e = 0; e < 4; ++e) {
+          const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+          f[2 * e] = (add ? f[2 * e] : 0.f) + t.x; f[2 * e + 1] = (add ? f[2 * e + 1] : 0.f) + t.y;
+        }
+      };
+      for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += stride * RU) {
+        if (a.stage_mc) {
+          uint4 v[RU];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) { __nv_bfloat162 h = __floats2bfloat162_rn(s[2 * e], s[2 * e + 1]); p[e] = *reinterpret_cast<uint32_t*>(&h); }
-        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out) + i * 8)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = mc_ld_reduce_bf16x8(a.stage_mc + base + i * 8); }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) {
+            const long i = i0 + u * stride;
+            if (i < n8) { float sum[8]; widen(v[u], sum, false); put(i, sum); }
+          }
+        } else {
+          float sum[RU][8];
+          for (int q = 0; q < a.world; ++q) {
+            const int j = (a.rank + q) % a.world;
+            uint4 v[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = reinterpret_cast<const uint4*>(a.stage[j] + base)[i]; }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) widen(v[u], sum[u], q != 0); }
+          }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) put(i, sum[u]); }
+        }
       }
     }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned int ticket = atomicAdd(a.done_counter, 1u);
-    if (ticket == gridDim.x - 1) {
-      if (go) for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_DONE + a.rank, a.seq);
-      *a.done_counter = 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) {      // the last CTA to finish publishes "this rank has read every rank's buffer slot of this call"
+      __threadfence_system();
+      const unsigned int arrived = atomicAdd(a.done_counter, 1u);
+      if (arrived == gridDim.x - 1) {
+        if (go_reduce) for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_DONE + a.rank, a.seq);
+        *a.done_counter = 0u;
+      }
     }
   }
 }
@@ -417,8 +483,8 @@ size_t tp_args_bytes() { return sizeof(tp::Args); }
 int tp_pad_words() { return tp::PAD_WORDS; }
 
 template <bool A_MN, bool B_MN, int OUT>
-static int tp_launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long ldc, int M, int N, int K, const tp::Args& a, int* err, int sms,
-                     cudaStream_t st) {
+static int tp_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, long ldc, int M, int N, int K, const tp::Args& a,
+                     int* err, int sms, cudaStream_t st) {
   auto kern = gemm_tp_kernel<A_MN, B_MN, OUT>;
   static bool attr = false;
   if (!attr) {
@@ -428,7 +494,7 @@ static int tp_launch(const CUtensorMap& ta, const CUtensorMap& tb, void* C, long
   const int tiles = ((M + tp::BM - 1) / tp::BM) * ((N + tp::BN - 1) / tp::BN);
   const int first = a.mode == 0 ? a.n_push : 0;
   const int grid = first + (tiles < sms - first ? tiles : sms - first);       // every CTA co-resident: one per SM
-  kern<<<grid, tp::THREADS, tp::SMEM, st>>>(ta, tb, C, ldc, M, N, K, a, err);
+  kern<<<grid, tp::THREADS, tp::SMEM, st>>>(ta, tb, tc, C, ldc, M, N, K, a, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -451,28 +517,27 @@ int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda
     if (a.mode == 0 && a.axis == 1 && static_cast<long>(K) != a.shard_rows * a.world) return 19;
     if (a.mode == 1 && (static_cast<long>(M) != a.shard_rows * a.world || N % 8)) return 19;
   }
-  CUtensorMap ta, tb;
+  CUtensorMap ta, tb, tc;
   if (!tp_encode(&ta, A, M, K, lda, a_mn, tp::BM)) return 21;
   if (!tp_encode(&tb, B, N, K, ldb, b_mn, tp::BN)) return 22;
+  tc = ta;
+  if (a.mode == 1) {      // the partial product [M, N] (bf16) in this rank's own buffer, stored as 64-column slabs
+    if (!a.stage[a.rank] || !a.out || !a.owner_counters) return 20;
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)}, strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, tp::BM};
+    if (!encode_tensor_map_2d(&tc, a.stage[a.rank], 2, dims, strides, box, true)) return 23;
+  }
 #define GHB_TP(AM, BMN)                                                                              \
   switch (a.mode == 1 ? 0 : out) {                                                                   \
-    case 0: return tp_launch<AM, BMN, 0>(ta, tb, C, ldc, M, N, K, a, err, sms, st);                  \
-    case 1: return tp_launch<AM, BMN, 1>(ta, tb, C, ldc, M, N, K, a, err, sms, st);                  \
-    default: return tp_launch<AM, BMN, 2>(ta, tb, C, ldc, M, N, K, a, err, sms, st);                 \
+    case 0: return tp_launch<AM, BMN, 0>(ta, tb, tc, C, ldc, M, N, K, a, err, sms, st);              \
+    case 1: return tp_launch<AM, BMN, 1>(ta, tb, tc, C, ldc, M, N, K, a, err, sms, st);              \
+    default: return tp_launch<AM, BMN, 2>(ta, tb, tc, C, ldc, M, N, K, a, err, sms, st);             \
   }
   if (!a_mn && !b_mn) { GHB_TP(false, false) }
   if (!a_mn && b_mn) { GHB_TP(false, true) }
   if (a_mn && !b_mn) { GHB_TP(true, false) }
   GHB_TP(true, true)
 #undef GHB_TP
-}
-
-int tp_rs_reduce(const void* stage, void* out, int out_f32, long n, const void* args, int* err, int sms, cudaStream_t st) {
-  if (n % 8) return 1;
-  tp::Args a;
-  memcpy(&a, args, sizeof(a));
-  tp_rs_reduce_kernel<<<sms * 4, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(stage), out, out_f32, n, a, err);
-  return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
 int tp_signal(const void* args, int word, cudaStream_t st) {

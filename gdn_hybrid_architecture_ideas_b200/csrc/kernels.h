@@ -117,7 +117,6 @@ size_t tp_args_bytes();
 int tp_pad_words();
 int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn, int out,
             const void* args, int* err, int sms, cudaStream_t st);
-int tp_rs_reduce(const void* stage, void* out, int out_f32, long n, const void* args, int* err, int sms, cudaStream_t st);
 int tp_signal(const void* args, int word, cudaStream_t st);
 
 }  // namespace ghb

@@ -10,9 +10,12 @@ sharded and every rank sees all tokens. The two boundaries are the collectives:
 Backward mirrors them (dx = reduce_scatter(dy W_r), dW_r = dy^T all_gather(x); dh = all_gather(dout) W_r,
 dW_r = all_gather(dout)^T h); activations are re-gathered in the backward rather than kept.
 
-Two implementations of the same functions: "fused" (csrc/gemm_tp.cu over symmetric memory: peer stores, flags,
-bounded waits) and "collective" (`torch.distributed` all_gather_into_tensor / reduce_scatter_tensor around a plain
-GEMM: the baseline and the CPU / gloo path). The reference has no tensor parallelism.
+Two implementations of the same functions: "fused" (csrc/gemm_tp.cu over symmetric memory: the gather's push is one
+`multimem.st` per 16 bytes through the NVSwitch multicast mapping of the buffer, the scatter's reduction one
+`multimem.ld_reduce`, both inside the GEMM launch, with flags and bounded waits; plain peer stores / loads when the
+allocation has no multicast mapping or GHB_COMM_MULTIMEM=0) and "collective" (`torch.distributed`
+all_gather_into_tensor / reduce_scatter_tensor around a plain GEMM: the baseline and the CPU / gloo path). The
+reference has no tensor parallelism.
 """
 
 from __future__ import annotations
@@ -29,7 +32,7 @@ CHUNK = 128
 N_GATHER_SLOTS = 4
 N_STAGE_SLOTS = 2
 PAD_AG_DONE, PAD_RS_READY, PAD_RS_DONE = 0, 8, 16
-_ARGS_FMT = "<8Q8Q8Q5i4x3q2Ii4x8QQ"
+_ARGS_FMT = "<8Q8Q8Q5i4x3q2Ii4x8Q5Q2i"
 
 
 class Gathered:
@@ -79,19 +82,27 @@ class TensorParallel:
         self.pad, hp = alloc(native.ext().tp_pad_words(), torch.int32)
         self._handles = (hg, hc, hs, hp)
         self._ptrs = {k: [int(p) for p in h.buffer_ptrs] for k, h in zip("gcsp", self._handles)}
+        use_mc = os.environ.get("GHB_COMM_MULTIMEM", "1") != "0"
+        self._mc = {k: (int(getattr(h, "multicast_ptr", 0) or 0) if use_mc else 0) for k, h in zip("gs", (hg, hs))}
+        self.multimem = bool(self._mc["g"] and self._mc["s"])
+        if not self.multimem:
+            self._mc = {"g": 0, "s": 0}
+        self.owner_counters = torch.zeros(MAXR, dtype=torch.int32, device=self.device)
         self.n_chunks = n_chunks
         self.slot_seq = [0] * N_GATHER_SLOTS
         self.next_slot = 0
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         # CTAs of a launch that push the local shard to the peers. Measured at 2 GPUs (200M, 16 rows): 8 -> 339 ms per step,
         # 32 -> 258, 64 -> 235, 96 -> 244, 128 -> 311 (the GEMM CTAs lose their SMs); 32 was the setting of the 8-GPU runs.
-        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", "64" if self.world <= 2 else "32"))
+        # With the multicast push a shard leaves the GPU once, whatever the world size: a few CTAs saturate the links.
+        default_push = "32" if self.multimem else ("64" if self.world <= 2 else "32")
+        self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", default_push))
         torch.cuda.synchronize(self.device)
         dp.barrier()
 
     # ------------------------------------------------------------------ argument table
 
-    def _args(self, mode, slot=0, seq=0, need=0, push=0, axis=0, shard_rows=0, row_elems=0, ld=8, stage_slot=0):
+    def _args(self, mode, slot=0, seq=0, need=0, push=0, axis=0, shard_rows=0, row_elems=0, ld=8, stage_slot=0, out=None):
         n_push = self.n_push if push else 0        # a later consumer of a gather multiplies on every SM
         def peers(key, offset_bytes):
             got = [p + offset_bytes for p in self._ptrs[key]]
@@ -101,7 +112,9 @@ class TensorParallel:
         c_off = slot * self.n_chunks * 4
         s_off = stage_slot * self.max_tokens * self.max_width * 2
         raw = struct.pack(_ARGS_FMT, *peers("g", g_off), *peers("c", c_off), *peers("p", 0), self.rank, self.world, mode, push, axis,
-                          shard_rows, row_elems, ld, seq, need, n_push, *peers("s", s_off), self.done_counter.data_ptr())
+                          shard_rows, row_elems, ld, seq, need, n_push, *peers("s", s_off), self.done_counter.data_ptr(),
+                          self.owner_counters.data_ptr(), (self._mc["g"] + g_off) if self._mc["g"] else 0, (self._mc["s"] + s_off) if self._mc["s"] else 0,
+                          0 if out is None else out.data_ptr(), int(out is not None and out.dtype == torch.float32), 0)
         return torch.frombuffer(bytearray(raw), dtype=torch.uint8)
 
     # ------------------------------------------------------------------ gather handles
@@ -196,15 +209,11 @@ class TensorParallel:
             raise ValueError(f"tensor parallel scatter of [{T}, {N}] exceeds the workspace ({self.max_tokens} x {self.max_width})")
         self.rs_seq += 1
         seq, slot = self.rs_seq, self.rs_seq % N_STAGE_SLOTS
-        args = self._args(1, seq=seq, need=max(seq - N_STAGE_SLOTS, 0), shard_rows=Ts, stage_slot=slot)
-        err = native.err_flag(self.device)
-        native.ext().gemm_tp(h, w, None, False, b_mn, False, args, err)
-        base = slot * self.max_tokens * self.max_width
-        stage = self.stage_buf[base:base + self.world * Ts * N]
-        out = torch.empty(Ts, N, dtype=out_dtype, device=self.device)
-        native.ext().tp_rs_reduce(stage, out, args, err)
-        native._count(2)
-        return out
+        out = torch.empty(Ts, N, dtype=out_dtype if out_dtype in (BF16, torch.float32) else BF16, device=self.device)
+        args = self._args(1, seq=seq, need=max(seq - N_STAGE_SLOTS, 0), shard_rows=Ts, stage_slot=slot, out=out)
+        native.ext().gemm_tp(h, w, None, False, b_mn, False, args, native.err_flag(self.device))      # partial tiles, flags and the reduction: one launch
+        native._count()
+        return out if out.dtype == out_dtype else out.to(out_dtype)
 
     @staticmethod
     def _plain(a, b, a_mn, b_mn, out_dtype):

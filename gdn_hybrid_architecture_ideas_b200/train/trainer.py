@@ -205,7 +205,7 @@ class Trainer:
             return short_rows(self.data, sh.first_row + self.rank * per, per, sh.seq_len, self.cfg.data.seq_len)
         B = self.cfg.data.batch_size
         first, count = self.dp.rows(B) if (self.dp is not None and self.tp is None) else (0, B)   # tensor-parallel ranks share the rows
-        src_step = step + self.cfg.data_start_step
+        src_step = step - self.cfg.data_start_step      # a stage on a new shard set starts its stream at its own first update
         if self.tst is not None:
             return self.tst.batch_at(src_step, first, count)
         return self.data.batch(src_step, first, count)
@@ -621,6 +621,52 @@ class Trainer:
         self.load_state_dict(ckpt.load(p))
         self.resume_info = {"path": str(p), "step": self.step}
         return True
+
+    # What a run that CONTINUES another run's checkpoint (`resume_from`) may differ in from its source, besides the fields
+    # that select an implementation: its own length and bookkeeping; under `stage: continue` also the decay's share, the
+    # shard set and where the data stream starts; under `precision_switch` also the low-precision recipes
+    # (reference: ced/config.py:2160-2215, ced/train/trainer.py:905-1076).
+    BRANCH_FREE = ("steps", "checkpoint_steps", "resume_from", "eval", "wandb")
+    STAGE_FREE = ("optim.decay_fraction", "data.shard_dir", "data.extra_shard_dirs", "data.loss_mask", "stage", "data_start_step")
+    PRECISION_FREE = ("model.nvfp4", "model.fp8", "precision_switch")
+
+    def continue_from(self, path: str | Path) -> None:
+        """Start this NEW run from another run's checkpoint: its whole training state (weights, optimizer state, step
+        counter, RNG states). Strict: the source's config must be this one apart from the fields above, its data this
+        run's (unless the stage brings a new shard set), and the two LR schedules must agree on every update the source
+        has made, so that the run is the run this config would have trained from its own start."""
+        cfg = self.cfg
+        if cfg.stage not in ("none", "continue"):
+            raise ValueError(f"stage {cfg.stage!r}: 'none' or 'continue'")
+        if cfg.precision_switch and cfg.stage != "continue":
+            raise ValueError("precision_switch is read with stage 'continue'")
+        if cfg.data_start_step and cfg.stage != "continue":
+            raise ValueError("data_start_step is read with stage 'continue'")
+        state = ckpt.load(Path(path))
+        src = C.from_dict(C.TrainConfig, C.checkpoint_config(state["config"]))
+        free = self.BRANCH_FREE + (self.STAGE_FREE if cfg.stage == "continue" else ()) + (self.PRECISION_FREE if cfg.precision_switch else ())
+        diff = [d for d in C.config_differences(C.to_dict(src), C.to_dict(cfg)) if not any(d == f or d.startswith(f + ".") for f in free)]
+        if diff:
+            raise ValueError(f"resume_from: the source run's config differs from this one in {diff}"
+                             + ("" if cfg.stage == "continue" else " (stage 'continue' frees the decay share, the shard set and data_start_step)"))
+        S = int(state["step"])
+        from .lr import lr_of as lr_fn
+
+        moved = [k for k in range(S) if lr_fn(src, k) != lr_fn(cfg, k)]
+        if moved:
+            raise ValueError(f"resume_from: the source trained update {moved[0]} at LR {lr_fn(src, moved[0])}, this config's schedule gives "
+                             f"{lr_fn(cfg, moved[0])}: the schedules must agree on every update the source has made")
+        new_data = cfg.stage == "continue" and (src.data.shard_dir != cfg.data.shard_dir or src.data.extra_shard_dirs != cfg.data.extra_shard_dirs)
+        if new_data and cfg.data_start_step != S:
+            raise ValueError(f"stage 'continue' on a new shard set starts its stream at this run's first update: data_start_step must be {S}")
+        if not new_data and cfg.data_start_step not in (0, src.data_start_step):
+            raise ValueError("data_start_step: 0 (or the source's own) when the shard set is the source's: the stream goes on where the source is")
+        if new_data or cfg.precision_switch:
+            state = {**state, "data_state": None}
+        self.load_state_dict(state, check_config=False)
+        self.resume_info = {"path": str(path), "step": self.step, "stage": cfg.stage,
+                            "precision": [C.to_dict(src.model.fp8)["mode"] + "/" + C.to_dict(src.model.nvfp4)["mode"],
+                                          C.to_dict(cfg.model.fp8)["mode"] + "/" + C.to_dict(cfg.model.nvfp4)["mode"]]}
 
     def init_from_checkpoint(self, path: str | Path) -> None:
         """Weights only, from another run; parameters the file lacks keep their initial values."""

@@ -9,6 +9,7 @@
 from __future__ import annotations
 
 import argparse
+import json
 import os
 import shlex
 import subprocess
@@ -32,17 +33,36 @@ def find_entry(runs: dict, name: str) -> dict:
     raise KeyError(f"no entry {name!r}; entries: {[e['name'] for e in runs.get('runs', [])]}")
 
 
-def build_command(runs: dict, entry: dict, run_root: str, nproc: int = 1, port: int = 29511) -> list[str]:
-    sets = list(entry.get("set", []))
+# Held-out text sets a run scores while it trains: name -> file inside the runs file's `eval_dir`; only files that exist are passed.
+EVAL_SETS = {"web": "web.pt", "code": "code.pt", "agent": "agent.pt", "general_web": "general_web.pt"}
+
+
+def build_command(runs: dict, entry: dict, run_root: str, nproc: int = 1, port: int = 29511, extra_sets=(), check_eval: bool = True) -> list[str]:
+    """The training process's argv for one entry. Overrides, in order: the seed (and, for a shard-fed entry, the data seed
+    1000 + seed, the first shard set and any further ones as one stream), the eval sets found in `eval_dir`, the entry's own
+    `set` list, then `extra_sets` from the command line."""
+    sets = []
     if "seed" in entry:
-        sets.append(f"seed={entry['seed']}")
+        sets.append(f"seed={int(entry['seed'])}")
     shards = entry.get("shards", runs.get("shards"))
-    if shards and not any(s.startswith("data.kind=") for s in sets):
-        sets.append(f"data.shard_dir={shards}")
+    own = [str(x) for x in entry.get("set", [])]
+    if shards and not any(x.startswith("data.kind=") for x in own):
+        first, *more = shards if isinstance(shards, list) else [shards]
+        if "seed" in entry:
+            sets.append(f"data.seed={1000 + int(entry['seed'])}")
+        sets += ["data.kind=shards", f"data.shard_dir={first}"]
+        if more:
+            sets.append("data.extra_shard_dirs=" + json.dumps(more))
+    eval_dir = runs.get("eval_dir")
+    if eval_dir:
+        present = {k: f"{eval_dir}/{v}" for k, v in EVAL_SETS.items() if not check_eval or (Path(eval_dir) / v).is_file()}
+        if present:
+            sets.append("eval.sets=" + json.dumps(present))
+    sets += own + [str(x) for x in extra_sets]
     train = [str(ROOT / "scripts" / "train.py"), "--config", str(ROOT / entry["config"]),
              "--run-dir", str(Path(run_root) / entry["name"])]
-    for s in sets:
-        train += ["--set", s]
+    for x in sets:
+        train += ["--set", x]
     if nproc > 1:
         return [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
                 "--master-addr", "127.0.0.1", "--master-port", str(port)] + train
@@ -57,14 +77,15 @@ def main(argv=None) -> int:
     ap.add_argument("--nproc", type=int, default=1)
     ap.add_argument("--data-root", default=os.environ.get("DATA_ROOT", "/data"))
     ap.add_argument("--run-root", default=os.environ.get("RUN_ROOT", "/tmp/runs"))
+    ap.add_argument("--set", dest="extra", action="append", default=[], metavar="KEY=VALUE", help="a further train.py override, after the entry's own")
     ap.add_argument("--dry-run", action="store_true")
     args = ap.parse_args(argv)
     runs = load_runs(args.runs, args.data_root, args.run_root)
     if args.list:
-        for e in runs.get("runs", []):
-            print(e["name"])
+        for e in runs.get("runs", []):       # an entry that continues another names it: run that one first
+            print(e["name"] + (f"  (after {e['after']} step {e.get('after_step', 'end')})" if e.get("after") else ""))
         return 0
-    cmd = build_command(runs, find_entry(runs, args.name), args.run_root, args.nproc)
+    cmd = build_command(runs, find_entry(runs, args.name), args.run_root, args.nproc, extra_sets=args.extra, check_eval=not args.dry_run)
     print(" ".join(shlex.quote(c) for c in cmd))
     return 0 if args.dry_run else subprocess.call(cmd)
 

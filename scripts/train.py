@@ -47,8 +47,8 @@ def prepare(args, dp=None) -> Trainer:
         state = ckpt.load(latest)
         trainer.load_state_dict(state, check_config=not args.allow_config_change)
         trainer.resume_info = {"path": str(latest), "step": trainer.step}
-    elif cfg.resume_from:
-        trainer.resume_from_checkpoint(cfg.resume_from)
+    elif cfg.resume_from:       # a new run that continues another run's checkpoint (a branch, or a stage on other data)
+        trainer.continue_from(cfg.resume_from)
     return trainer
 
 

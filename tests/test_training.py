@@ -597,3 +597,41 @@ def test_every_run_entry_builds():
             assert sum(p.numel() for p in model.parameters()) > 0, entry["name"]
             seen += 1
     assert seen >= 10
+
+
+def test_branch_and_stage_continue_another_run(tmp_path):
+    """`resume_from`: a new run that continues another run's kept checkpoint is the uninterrupted longer run bit for bit;
+    a changed config is refused unless `stage: continue` frees the field; the LR schedules must agree on the source's updates."""
+    src = tiny_train_config(steps=4)
+    src.optim.decay_fraction = 0.0
+    a = Trainer(copy.deepcopy(src), tmp_path / "a")
+    a.fit()
+    kept = ckpt.latest_path(tmp_path / "a")
+    whole = tiny_train_config(steps=8)
+    whole.optim.decay_fraction = 0.0
+    w = Trainer(copy.deepcopy(whole), tmp_path / "w")
+    w.fit()
+    branch = copy.deepcopy(whole)
+    branch.resume_from = str(kept)
+    b = Trainer(branch, tmp_path / "b")
+    b.continue_from(kept)
+    assert b.step == 4 and b.resume_info["path"] == str(kept)
+    b.fit()
+    assert all(torch.equal(x, y) for x, y in zip(weights(w).values(), weights(b).values()))
+    other = copy.deepcopy(branch)
+    other.optim.weight_decay = 0.3
+    with pytest.raises(ValueError, match="optim.weight_decay"):
+        Trainer(other, tmp_path / "c").continue_from(kept)
+    stage = copy.deepcopy(branch)
+    stage.optim.decay_fraction = 0.25          # the decay of the longer run starts after the source's last update: same LR on updates 0..3
+    with pytest.raises(ValueError, match="optim.decay_fraction"):
+        Trainer(copy.deepcopy(stage), tmp_path / "d").continue_from(kept)
+    stage.stage = "continue"
+    s = Trainer(stage, tmp_path / "e")
+    s.continue_from(kept)
+    assert s.step == 4 and s.resume_info["stage"] == "continue"
+    s.fit()
+    late = copy.deepcopy(stage)
+    late.optim.decay_fraction = 0.9            # would have decayed during the source's updates: refused
+    with pytest.raises(ValueError, match="schedules must agree"):
+        Trainer(late, tmp_path / "f").continue_from(kept)
