@@ -35,12 +35,12 @@ __device__ __forceinline__ int mxq_exponent(float amax) {
   const bool bump = m > 0 && e != 254 && (e != 0 || m > 0x400000);
   return e + (bump ? 1 : 0);
 }
-__device__ __forceinline__ uint8_t mxq_value(float x, int b, bool bad) {
-  if (bad) return 0x7F;      // E4M3 NaN
-  const float inv = __int_as_float(b == 254 ? 0x00400000 : (254 - b) << 23);
-  const float y = fminf(fmaxf(x * inv, -448.f), 448.f);
-  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(y, __NV_SATFINITE, __NV_E4M3));
+// Two values at once through the paired conversion instruction; low byte = a, high byte = b.
+__device__ __forceinline__ uint32_t mxq_pair(float a, float b, float inv) {
+  const float ya = fminf(fmaxf(a * inv, -448.f), 448.f), yb = fminf(fmaxf(b * inv, -448.f), 448.f);
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(ya, yb), __NV_SATFINITE, __NV_E4M3));
 }
+__device__ __forceinline__ float mxq_inverse_scale(int b) { return __int_as_float(b == 254 ? 0x00400000 : (254 - b) << 23); }
 __device__ __forceinline__ long mxq_scale_offset(long row, long block, long k_tiles) {
   return ((row >> 7) * k_tiles + (block >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + (block & 3);
 }
@@ -88,9 +88,8 @@ mx_quant_kernel(const T* __restrict__ x, long R, long C, long ld, uint8_t* __res
         }
         const int b = bad ? 255 : mxq_exponent(amax);
         if (r < R && c < C) {
-          uint32_t packed = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) packed |= static_cast<uint32_t>(mxq_value(v[e], b, bad)) << (8 * e);
+          const float inv = mxq_inverse_scale(b);
+          const uint32_t packed = bad ? 0x7F7F7F7Fu : (mxq_pair(v[0], v[1], inv) | (mxq_pair(v[2], v[3], inv) << 16));
           *reinterpret_cast<uint32_t*>(q_row + r * C + c) = packed;
           if ((lane & 7) == 0) sf_row[mxq_scale_offset(r, c >> 5, kt_row)] = static_cast<uint8_t>(b);
         }
@@ -104,22 +103,20 @@ mx_quant_kernel(const T* __restrict__ x, long R, long C, long ld, uint8_t* __res
         const int cc = u % QT, rb = u / QT;
         const long col = c0 + cc, row_b = r0 + rb * 32;
         if (col >= C || row_b >= R) continue;
+        float f[32];      // the block's 32 values, read from shared memory once
         float amax = 0.f; bool bad = false;
-#pragma unroll 8
+#pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float f = tile[(rb * 32 + i) * QS + cc];
-          bad |= !isfinite(f);
-          amax = fmaxf(amax, isnan(f) ? 0.f : fabsf(f));
+          f[i] = tile[(rb * 32 + i) * QS + cc];
+          bad |= !isfinite(f[i]);
+          amax = fmaxf(amax, isnan(f[i]) ? 0.f : fabsf(f[i]));
         }
         const int b = bad ? 255 : mxq_exponent(amax);
+        const float inv = mxq_inverse_scale(b);
         uint32_t w[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          uint32_t packed = 0;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) packed |= static_cast<uint32_t>(mxq_value(tile[(rb * 32 + i * 4 + e) * QS + cc], b, bad)) << (8 * e);
-          w[i] = packed;
-        }
+        for (int i = 0; i < 8; ++i)
+          w[i] = bad ? 0x7F7F7F7Fu : (mxq_pair(f[4 * i], f[4 * i + 1], inv) | (mxq_pair(f[4 * i + 2], f[4 * i + 3], inv) << 16));
         uint4* dst = reinterpret_cast<uint4*>(q_col + col * R + row_b);
         dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
         dst[1] = make_uint4(w[4], w[5], w[6], w[7]);

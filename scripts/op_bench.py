@@ -262,6 +262,17 @@ def bench_decode_attention(a):
     splits = 16
     po = torch.empty(B, Hq, splits, hd, device="cuda")
     pml = torch.empty(B, Hq, splits, 2, device="cuda")
+    if a.kv == "grid":      # 4 x 4 grid of 32-channel components: 256 cached channels per token, scored from the raw components
+        assert Hq == 16, "the grid kernel serves 16 query heads"
+        kg = torch.randn(B, T, 256, device="cuda").to(BF16)
+        vg = torch.randn(B, T, 256, device="cuda").to(BF16)
+        gain = torch.ones(64, device="cuda")
+        splits = max(16, min(256, 592 // max(B, 1)))
+        po = torch.empty(B, Hq, splits, hd, device="cuda")
+        pml = torch.empty(B, Hq, splits, 2, device="cuda")
+        ms = timed(lambda: nat.ext().decode_attention_grid(q, kg, vg, lens, None, cos_t, sin_t, gain, out, po, pml, rot, a.cap, splits, hd ** -0.5, 1e-6),
+                   a.iters, a.warmup)
+        return {"op": "decode_attention", "kv": "grid4x4", "B": B, "T": T, "Hq": Hq, "ms": ms, "gbs": 2 * B * T * 256 * 2 / ms / 1e6}
     ms = timed(lambda: nat.ext().decode_attention(q, k, v, lens, None, cos_t, sin_t, out, po, pml, rot, a.cap, splits, hd ** -0.5), a.iters, a.warmup)
     nb = 2 * B * T * Hkv * hd * 2
     return {"op": "decode_attention", "B": B, "T": T, "Hq": Hq, "Hkv": Hkv, "ms": ms, "gbs": nb / ms / 1e6}
@@ -270,6 +281,7 @@ def bench_decode_attention(a):
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("op", choices=["attention", "gdn", "gdn_prep", "gemm", "gemm_mx", "rmsnorm", "depth_mix", "swiglu", "lm_head", "adamw", "decode_attention"])
+    p.add_argument("--kv", choices=["gqa", "grid"], default="gqa", help="decode_attention: grouped KV heads or the 4 x 4 grid's raw components")
     p.add_argument("--sources", type=int, default=4)
     p.add_argument("--ffn", type=int, default=2816)
     p.add_argument("--vocab", type=int, default=32768)
