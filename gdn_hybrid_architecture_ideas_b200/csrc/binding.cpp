@@ -498,9 +498,20 @@ void gemm_tp(const Tensor& a, const Tensor& b, const c10::optional<Tensor>& out,
                               err.data_ptr<int>(), sm_count(), stream());
   TORCH_CHECK(rc == 0, "gemm_tp refused (code ", rc, "): M=", M, " N=", N, " K=", K, " cuerr=", ghb::last_encode_error());
 }
-void tp_signal(const Tensor& args, int64_t word, const Tensor& like) {
+void tp_signal(const Tensor& args, int64_t word, const Tensor& like, int64_t wait_word, const c10::optional<Tensor>& err) {
   const c10::cuda::CUDAGuard guard(like.device());
-  check(ghb::tp_signal(args.data_ptr(), word, stream()), "tp_signal");
+  TORCH_CHECK(wait_word < 0 || (err.has_value() && err->is_cuda()), "tp_signal: a wait needs the status word");
+  check(ghb::tp_signal(args.data_ptr(), word, wait_word, err.has_value() ? err->data_ptr<int>() : nullptr, stream()), "tp_signal");
+}
+// Queues the copy-engine push of a gather on the caller's side streams (handles; one per peer).
+void tp_push_copies(const Tensor& args, const Tensor& seq_src, int64_t pieces, const std::vector<int64_t>& stream_handles) {
+  TORCH_CHECK(!args.is_cuda() && args.numel() == static_cast<int64_t>(ghb::tp_args_bytes()), "tp_push_copies: argument table size");
+  TORCH_CHECK(seq_src.is_cuda() && seq_src.scalar_type() == at::kInt && seq_src.is_contiguous(), "tp_push_copies: int32 device words");
+  const c10::cuda::CUDAGuard guard(seq_src.device());
+  std::vector<cudaStream_t> streams;
+  for (int64_t h : stream_handles) streams.push_back(reinterpret_cast<cudaStream_t>(h));
+  const int rc = ghb::tp_push_copies(args.data_ptr(), seq_src.data_ptr(), pieces, streams.data(), static_cast<int>(streams.size()));
+  TORCH_CHECK(rc == 0, "tp_push_copies refused (code ", rc, ")");
 }
 int64_t tp_args_bytes() { return ghb::tp_args_bytes(); }
 int64_t tp_pad_words() { return ghb::tp_pad_words(); }
@@ -545,7 +556,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_prep_fwd", &attn_prep_fwd);
   m.def("attn_prep_bwd", &attn_prep_bwd);
   m.def("gemm_tp", &gemm_tp);
-  m.def("tp_signal", &tp_signal);
+  m.def("tp_signal", &tp_signal, py::arg("args"), py::arg("word"), py::arg("like"), py::arg("wait_word") = -1, py::arg("err") = py::none());
+  m.def("tp_push_copies", &tp_push_copies);
   m.def("tp_args_bytes", &tp_args_bytes);
   m.def("tp_pad_words", &tp_pad_words);
   m.def("attention_fwd", &attention_fwd);

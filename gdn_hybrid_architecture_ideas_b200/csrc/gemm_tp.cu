@@ -27,6 +27,7 @@
 #include "kernels.h"
 #include "sm100.cuh"
 #include "gemm_epilogue.cuh"
+#include <algorithm>
 #include <cstring>
 
 namespace ghb {
@@ -74,8 +75,17 @@ struct Args {
   // --- scatter output
   void* out;                         // [Ts][N] this rank's reduced rows
   int out_f32;
-  int pad_;
+  int tma;                           // 1: the bulk-copy engine moves the data between GPUs (PeerMaps), 0: threads do
 };
+
+// One tensor map per rank over the same buffer on every GPU. AG: the gather slot [T][row_elems] (boxes of PUSH_ROWS x
+// PUSH_COLS, unswizzled; this rank's own entry is the source of its pushes). RS: rank d's entry covers the rows that
+// THIS rank's partial products occupy in d's staging slot, [Ts][N] at source index `rank` (64-column swizzled slabs).
+struct PeerMaps {
+  CUtensorMap m[MAXR];
+};
+constexpr int PUSH_ROWS = CHUNK, PUSH_COLS = 128, PUSH_STAGES = 6;
+constexpr uint32_t PUSH_TILE_BYTES = PUSH_ROWS * PUSH_COLS * 2;
 
 __device__ __forceinline__ void mc_st16(void* p, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
@@ -117,7 +127,8 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int se
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(tp::THREADS, 1)
 gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const __grid_constant__ CUtensorMap tma_c,
-               void* __restrict__ Cout, long ldc, int M, int N, int K, const __grid_constant__ tp::Args a, int* __restrict__ err) {
+               void* __restrict__ Cout, long ldc, int M, int N, int K, const __grid_constant__ tp::Args a,
+               const __grid_constant__ tp::PeerMaps pm, int splits, int* __restrict__ err) {
   using namespace tp;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -133,6 +144,53 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const long vec_per_row = a.row_elems / 8;                 // 16-byte vectors
     const __nv_bfloat16* src = a.xg[a.rank] + a.rank * a.shard_rows * a.ld;
     constexpr int UNROLL = 8;                                  // loads in flight per thread: the copy is latency-bound otherwise
+    if (a.tma) {
+      // One thread drives the bulk-copy engine: a PUSH_ROWS x PUSH_COLS box of the local shard comes into shared memory
+      // (tile load) and leaves once per peer (tile stores into the same rows of that peer's buffer). Loads run
+      // PUSH_STAGES - 1 boxes ahead of the stores; a chunk's flag is raised on every peer once all of its stores are done.
+      if (threadIdx.x != 0) return;
+      uint8_t* ring = smem;
+      uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PUSH_STAGES * PUSH_TILE_BYTES);
+      for (int d = 0; d < a.world; ++d)
+        if (d != a.rank && !wait_flag(a.pad[a.rank] + PAD_AG_DONE + d, a.need)) { atomicExch(err, 501); return; }
+      for (int i = 0; i < PUSH_STAGES; ++i) mbar_init(&bars[i], 1);
+      mbar_fence_init();
+      for (int d = 0; d < a.world; ++d) tma_prefetch_desc(&pm.m[d]);
+      const long cols = (a.row_elems + PUSH_COLS - 1) / PUSH_COLS;
+      const long my_chunks = blockIdx.x < chunks_per_shard ? (chunks_per_shard - blockIdx.x + a.n_push - 1) / a.n_push : 0;
+      const long total = my_chunks * cols;
+      const long row_base = a.rank * a.shard_rows;
+      auto load = [&](long n) {
+        const int s = static_cast<int>(n % PUSH_STAGES);
+        const long c = blockIdx.x + (n / cols) * a.n_push;
+        mbar_expect_tx(&bars[s], PUSH_TILE_BYTES);
+        tma_load_2d(ring + s * PUSH_TILE_BYTES, &pm.m[a.rank], &bars[s], static_cast<int>((n % cols) * PUSH_COLS), static_cast<int>(row_base + c * CHUNK));
+      };
+      for (long n = 0; n < total && n < PUSH_STAGES - 1; ++n) load(n);
+      for (long n = 0; n < total; ++n) {
+        const int s = static_cast<int>(n % PUSH_STAGES);
+        const long c = blockIdx.x + (n / cols) * a.n_push;
+        if (!mbar_wait(&bars[s], static_cast<uint32_t>((n / PUSH_STAGES) & 1))) { atomicExch(err, 509); break; }
+        for (int q = 1; q < a.world; ++q) {
+          const int d = (a.rank - q + a.world) % a.world;
+          tma_store_2d(&pm.m[d], ring + s * PUSH_TILE_BYTES, static_cast<int>((n % cols) * PUSH_COLS), static_cast<int>(row_base + c * CHUNK));
+        }
+        tma_store_commit();
+        if (n + PUSH_STAGES - 1 < total) {
+          tma_store_wait_read<1>();          // the box stored one trip ago has left shared memory: its buffer takes the next load
+          load(n + PUSH_STAGES - 1);
+        }
+        if (n % cols == cols - 1) {          // the chunk's last box
+          tma_store_wait<0>();
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+          __threadfence_system();
+          for (int d = 0; d < a.world; ++d)
+            if (d != a.rank) st_release_sys(a.chunk[d] + a.rank * chunks_per_shard + c, a.seq);
+        }
+      }
+      tma_store_wait<0>();
+      return;
+    }
     if (a.xg_mc) {
       // one store per 16 bytes reaches every rank through the switch: wait until every destination has released the slot
       if (threadIdx.x == 0) {
@@ -222,9 +280,32 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int tiles_per_shard = a.mode == 2 ? 0 : static_cast<int>(a.shard_rows / BM);
   const int m_rot = a.mode == 0 ? (a.axis == 0 ? a.rank * tiles_per_shard : 0) : (a.mode == 1 ? ((a.rank + 1) % a.world) * tiles_per_shard : 0);
   const int kb_rot = (a.mode == 0 && a.axis == 1) ? static_cast<int>(a.rank * (a.shard_rows / BK)) : 0;
-  auto tile_of = [&](int t, int& tm, int& tn) {           // column tiles of one row tile are consecutive: they share its chunk
-    tm = (t / tiles_n + m_rot) % tiles_m;
+  const bool k_interleave = a.tma && a.mode == 0 && a.axis == 1;
+  const int chunks_in_shard = a.mode == 2 ? 1 : static_cast<int>(a.shard_rows / CHUNK);
+  auto kb_of = [&](int pos) -> int {      // position in this rank's reduction order -> k-block
+    if (!k_interleave) return (pos + kb_rot) % num_kb;
+    constexpr int PER = CHUNK / BK;       // chunk-major over the shards, own shard first (the order the pushed chunks arrive)
+    const int q = pos / PER, b = pos % PER, c = q / a.world, j = q % a.world;
+    return (((a.rank + j) % a.world) * chunks_in_shard + c) * PER + b;
+  };
+  // A work unit is (output tile, slice of the reduction); slices > 1 only where the gathered rows lie along K (weight
+  // gradients: few output tiles, K = all tokens). Units are ordered slice-major and the k-blocks are rotated to start at
+  // the local shard, so the first units need no peer's data; slices meet in the fp32 output through reductions in L2.
+  const int units = tiles * splits;
+  const int kbs = (num_kb + splits - 1) / splits;
+  auto tile_of = [&](int u, int& tm, int& tn, int& k_lo, int& k_hi) {     // column tiles of one row tile are consecutive: they share its chunk
+    const int t = u % tiles, sp = u / tiles;
+    if (a.tma && ((a.mode == 0 && a.axis == 0) || a.mode == 1)) {
+      // chunk-major over the shards: row tile c of every shard, then row tile c + 1 (AG: the order in which the pushed
+      // chunks arrive, own shard first; RS: every owner's link carries partial tiles during the whole product, own rows last)
+      const int i = t / tiles_n, c = i / a.world, j = i % a.world;
+      tm = ((a.rank + j + (a.mode == 1 ? 1 : 0)) % a.world) * tiles_per_shard + c;
+    } else {
+      tm = (t / tiles_n + m_rot) % tiles_m;
+    }
     tn = t % tiles_n;
+    k_lo = sp * kbs;
+    k_hi = k_lo + kbs < num_kb ? k_lo + kbs : num_kb;
   };
 
   if (threadIdx.x == 0) {
@@ -251,13 +332,13 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         asm volatile("fence.proxy.async.global;" ::: "memory");   // peer stores (generic proxy) before TMA reads (async proxy)
         return true;
       };
-      for (int t = cta; t < tiles && ok; t += n_cta) {
-        int tm, tn; tile_of(t, tm, tn);
+      for (int t = cta; t < units && ok; t += n_cta) {
+        int tm, tn, k_lo, k_hi; tile_of(t, tm, tn, k_lo, k_hi);
         const int m0 = tm * BM, n0 = tn * BN;
         if (a.mode == 0 && a.axis == 0 && !chunk_ready(tm)) { ok = false; break; }
-        for (int kk = 0; kk < num_kb; ++kk) {
-          const int kb = (kk + kb_rot) % num_kb;
-          if (a.mode == 0 && a.axis == 1 && (kb & 1) == 0 && !chunk_ready(kb / 2)) { ok = false; break; }
+        for (int kk = k_lo; kk < k_hi; ++kk) {
+          const int kb = kb_of(kk);
+          if (a.mode == 0 && a.axis == 1 && ((kb & 1) == 0 || kk == k_lo) && !chunk_ready(kb / 2)) { ok = false; break; }
           if (!mbar_wait(&empty[s], ph ^ 1)) { atomicExch(err, 503); ok = false; break; }
           mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
           uint8_t* pa = sA + s * A_BYTES; uint8_t* pb = sB + s * B_BYTES;
@@ -274,12 +355,13 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
       int s = 0; uint32_t ph = 0; int it = 0; bool ok = true;
-      for (int t = cta; t < tiles && ok; t += n_cta, ++it) {
+      for (int t = cta; t < units && ok; t += n_cta, ++it) {
         const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
+        int tm_, tn_, k_lo, k_hi; tile_of(t, tm_, tn_, k_lo, k_hi);
         if (!mbar_wait(&tempty[acc], aph ^ 1)) { atomicExch(err, 504); ok = false; break; }
         tc_fence_after();
         const uint32_t d = tmem_base + acc * BN;
-        for (int kk = 0; kk < num_kb; ++kk) {
+        for (int kk = k_lo; kk < k_hi; ++kk) {
           if (!mbar_wait(&full[s], ph)) { atomicExch(err, 505); ok = false; break; }
           tc_fence_after();
           const uint32_t pa = smem_u32(sA + s * A_BYTES), pb = smem_u32(sB + s * B_BYTES);
@@ -287,7 +369,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int k = 0; k < BK / UK; ++k) {
             const uint64_t da = A_MN ? umma_desc_sw128(pa + k * UK * 128, BK * 128, 1024) : umma_desc_sw128(pa + k * UK * 2, 16, 1024);
             const uint64_t db = B_MN ? umma_desc_sw128(pb + k * UK * 128, BK * 128, 1024) : umma_desc_sw128(pb + k * UK * 2, 16, 1024);
-            umma_bf16(d, da, db, idesc, kk != 0 || k != 0);
+            umma_bf16(d, da, db, idesc, kk != k_lo || k != 0);
           }
           umma_commit(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -300,9 +382,20 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     int it = 0; bool ok = true;
     unsigned int dest_ok = 0;                 // RS: owners known to have finished reading this rank's buffer slot
     uint32_t slab_count = 0;
-    for (int t = cta; t < tiles && ok; t += n_cta, ++it) {
+    int pending_owner = -1;                   // RS over the copy engine: owner of the tile whose stores may still be in flight
+    auto publish = [&](int owner) {           // one more tile of `owner`'s rows is complete in its staging slot
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence_system();
+      const unsigned int total = static_cast<unsigned int>(tiles_per_shard) * static_cast<unsigned int>(tiles_n);
+      if (atomicAdd(a.owner_counters + owner, 1u) + 1u == total) {
+        __threadfence_system();
+        st_release_sys(a.pad[owner] + PAD_RS_READY + a.rank, a.seq);
+        a.owner_counters[owner] = 0u;
+      }
+    };
+    for (int t = cta; t < units && ok; t += n_cta, ++it) {
       const int acc = it & 1; const uint32_t aph = (it >> 1) & 1;
-      int tm, tn; tile_of(t, tm, tn);
+      int tm, tn, k_lo_, k_hi_; tile_of(t, tm, tn, k_lo_, k_hi_);
       if (!mbar_wait(&tfull[acc], aph)) { if (lane == 0) atomicExch(err, 506); ok = false; break; }
       tc_fence_after();
       const long row = static_cast<long>(tm) * BM + quad * 32 + lane;
@@ -322,6 +415,20 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         // RS: the partial tile goes to THIS rank's buffer (TMA tile stores through the swizzled slabs); once every tile of an
         // owner's row range is stored, the owner is told
         const int d = static_cast<int>((static_cast<long>(tm) * BM) / a.shard_rows);
+        if (ok && a.tma) {
+          // the tile goes straight into owner d's staging slot, at this rank's source index: the bulk-copy engine writes
+          // it over NVLink while the next tile is multiplied. A tile is counted for its owner one tile later, once its
+          // stores are complete (at most the newest tile's stores stay in flight)
+          epilogue_store_bf16<BN>(taddr, slabs, &pm.m[d], tm * BM - d * static_cast<int>(a.shard_rows), n0, N, quad, lane, slab_count, &tempty[acc]);
+          if (quad == 0 && lane == 0) {
+            const bool whole = n0 + BN <= N;               // BN / 64 store groups were committed for this tile
+            if (whole) tma_store_wait<BN / 64>(); else tma_store_wait<0>();
+            if (pending_owner >= 0) publish(pending_owner);
+            pending_owner = d;
+            if (!whole) { publish(d); pending_owner = -1; }
+          }
+          continue;
+        }
         if (ok) {
           epilogue_store_bf16<BN>(taddr, slabs, &tma_c, tm * BM, n0, N, quad, lane, slab_count, &tempty[acc]);
           if (quad == 0 && lane == 0) {
@@ -364,7 +471,17 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
             }
           } else {
             float* out = reinterpret_cast<float*>(Cout) + row * ldc + col;
-            if (col + 32 <= N) {
+            if (splits > 1) {
+              if (col + 32 <= N) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + e), "f"(__uint_as_float(r[e])), "f"(__uint_as_float(r[e + 1])),
+                               "f"(__uint_as_float(r[e + 2])), "f"(__uint_as_float(r[e + 3])) : "memory");
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e) if (col + e < N) atomicAdd(out + e, __uint_as_float(r[e]));
+              }
+            } else if (col + 32 <= N) {
               float4* o4 = reinterpret_cast<float4*>(out);
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
@@ -383,6 +500,10 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+    if (a.mode == 1 && quad == 0 && lane == 0) {
+      tma_store_wait<0>();
+      if (pending_owner >= 0) publish(pending_owner);
     }
   }
   tc_fence_before();
@@ -425,7 +546,18 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         }
       };
       for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += stride * RU) {
-        if (a.stage_mc) {
+        if (a.tma) {       // every rank's partial rows already lie in this rank's slot, source after source: local loads, fixed order
+          float sum[RU][8];
+          for (int j = 0; j < a.world; ++j) {
+            uint4 v[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = reinterpret_cast<const uint4*>(a.stage[a.rank] + j * a.shard_rows * N)[i]; }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) widen(v[u], sum[u], j != 0); }
+          }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) put(i, sum[u]); }
+        } else if (a.stage_mc) {
           uint4 v[RU];
 #pragma unroll
           for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = mc_ld_reduce_bf16x8(a.stage_mc + base + i * 8); }
@@ -462,10 +594,15 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 }
 
 // Publishes "this rank has released gather-slot uses <= seq" to every rank (stream-ordered after the slot's readers).
-__global__ void tp_signal_kernel(tp::Args a, int word) {
+// With wait_word >= 0 it then waits (bounded) until every peer has published a.need in that word: what a push that no
+// kernel carries out (copy-engine copies queued behind this launch) must know before it overwrites the peers' slot.
+__global__ void tp_signal_kernel(tp::Args a, int word, int wait_word, int* err) {
   if (threadIdx.x == 0) {
     __threadfence_system();
-    for (int p = 0; p < a.world; ++p) tp::st_release_sys(a.pad[p] + word + a.rank, a.seq);
+    if (a.seq) for (int p = 0; p < a.world; ++p) tp::st_release_sys(a.pad[p] + word + a.rank, a.seq);
+    if (wait_word >= 0 && a.need)
+      for (int d = 0; d < a.world; ++d)
+        if (d != a.rank && !tp::wait_flag(a.pad[a.rank] + wait_word + d, a.need)) { atomicExch(err, 501); break; }
   }
 }
 
@@ -484,7 +621,7 @@ int tp_pad_words() { return tp::PAD_WORDS; }
 
 template <bool A_MN, bool B_MN, int OUT>
 static int tp_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C, long ldc, int M, int N, int K, const tp::Args& a,
-                     int* err, int sms, cudaStream_t st) {
+                     const tp::PeerMaps& pm, int splits, int* err, int sms, cudaStream_t st) {
   auto kern = gemm_tp_kernel<A_MN, B_MN, OUT>;
   static bool attr = false;
   if (!attr) {
@@ -493,8 +630,9 @@ static int tp_launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtenso
   }
   const int tiles = ((M + tp::BM - 1) / tp::BM) * ((N + tp::BN - 1) / tp::BN);
   const int first = a.mode == 0 ? a.n_push : 0;
-  const int grid = first + (tiles < sms - first ? tiles : sms - first);       // every CTA co-resident: one per SM
-  kern<<<grid, tp::THREADS, tp::SMEM, st>>>(ta, tb, tc, C, ldc, M, N, K, a, err);
+  const int units = tiles * splits;
+  const int grid = first + (units < sms - first ? units : sms - first);       // every CTA co-resident: one per SM
+  kern<<<grid, tp::THREADS, tp::SMEM, st>>>(ta, tb, tc, C, ldc, M, N, K, a, pm, splits, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }
 
@@ -527,11 +665,39 @@ int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda
     const uint32_t box[2] = {64, tp::BM};
     if (!encode_tensor_map_2d(&tc, a.stage[a.rank], 2, dims, strides, box, true)) return 23;
   }
+  // the same buffer on every GPU, one map per rank (pushes of a gather; partial tiles of a scatter)
+  static_assert(tp::PUSH_STAGES * tp::PUSH_TILE_BYTES + 256 <= tp::SMEM - 1024, "the push ring fits the kernel's shared memory");
+  tp::PeerMaps pm;
+  memset(&pm, 0, sizeof(pm));
+  if (a.tma && a.mode == 0 && a.push) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(a.row_elems), static_cast<uint64_t>(a.shard_rows * a.world)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(a.ld) * 2};
+    const uint32_t box[2] = {tp::PUSH_COLS, tp::PUSH_ROWS};
+    for (int d = 0; d < a.world; ++d)
+      if (!a.xg[d] || !encode_tensor_map_2d(&pm.m[d], a.xg[d], 2, dims, strides, box, false)) return 24;
+  }
+  if (a.tma && a.mode == 1) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(a.shard_rows)}, strides[1] = {static_cast<uint64_t>(N) * 2};
+    const uint32_t box[2] = {64, tp::BM};
+    for (int d = 0; d < a.world; ++d)
+      if (!a.stage[d] || !encode_tensor_map_2d(&pm.m[d], a.stage[d] + static_cast<long>(a.rank) * a.shard_rows * N, 2, dims, strides, box, true)) return 25;
+  }
+  // gathered rows along K with an fp32 output: slice the reduction so that the units fill the SMs the pushes leave
+  int splits = 1;
+  if (a.mode == 0 && a.axis == 1 && out != 0) {
+    const int tiles = ((M + tp::BM - 1) / tp::BM) * ((N + tp::BN - 1) / tp::BN), num_kb = (K + tp::BK - 1) / tp::BK;
+    const int free_sms = sms - (a.push ? a.n_push : 0);
+    // about four units per SM: the units of a slice run while the next slices' chunks are still arriving, and the
+    // last wave is short
+    splits = std::max(1, std::min(std::min((4 * free_sms + tiles / 2) / tiles, num_kb / 16), 32));
+    while (splits > 1 && (splits - 1) * ((num_kb + splits - 1) / splits) >= num_kb) --splits;
+    if (splits > 1 && out == 1 && cudaMemset2DAsync(C, ldc * 4, 0, static_cast<size_t>(N) * 4, M, st) != cudaSuccess) return 5;
+  }
 #define GHB_TP(AM, BMN)                                                                              \
   switch (a.mode == 1 ? 0 : out) {                                                                   \
-    case 0: return tp_launch<AM, BMN, 0>(ta, tb, tc, C, ldc, M, N, K, a, err, sms, st);              \
-    case 1: return tp_launch<AM, BMN, 1>(ta, tb, tc, C, ldc, M, N, K, a, err, sms, st);              \
-    default: return tp_launch<AM, BMN, 2>(ta, tb, tc, C, ldc, M, N, K, a, err, sms, st);             \
+    case 0: return tp_launch<AM, BMN, 0>(ta, tb, tc, C, ldc, M, N, K, a, pm, 1, err, sms, st);       \
+    case 1: return tp_launch<AM, BMN, 1>(ta, tb, tc, C, ldc, M, N, K, a, pm, splits, err, sms, st);  \
+    default: return tp_launch<AM, BMN, 2>(ta, tb, tc, C, ldc, M, N, K, a, pm, splits, err, sms, st); \
   }
   if (!a_mn && !b_mn) { GHB_TP(false, false) }
   if (!a_mn && b_mn) { GHB_TP(false, true) }
@@ -540,11 +706,38 @@ int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda
 #undef GHB_TP
 }
 
-int tp_signal(const void* args, int word, cudaStream_t st) {
+int tp_signal(const void* args, int word, int wait_word, int* err, cudaStream_t st) {
   tp::Args a;
   memcpy(&a, args, sizeof(a));
-  tp_signal_kernel<<<1, 32, 0, st>>>(a, word);
+  tp_signal_kernel<<<1, 32, 0, st>>>(a, word, wait_word, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// The gather's push by the copy engines: this rank's shard (already in its own slot) goes into the same rows of every
+// peer's slot, `pieces` row ranges per peer; behind each piece a second small copy writes the call's sequence number
+// into the peer's flags of the piece's chunks (`seq_src`: device words holding a.seq, at least shard_rows / CHUNK of
+// them). The peer at distance q (rank - q) is served by streams[q - 1]: copies of one stream run in order, so a flag
+// lands after its data, and the streams' copies run side by side on different engines (one peer-to-peer copy alone was
+// measured at about half of what the link carries). No SM is used; the consuming GEMM polls the flags chunk by chunk.
+int tp_push_copies(const void* args, const void* seq_src, int pieces, const cudaStream_t* streams, int n_streams) {
+  tp::Args a;
+  memcpy(&a, args, sizeof(a));
+  if (a.world < 1 || a.world > tp::MAXR || a.shard_rows % tp::CHUNK || a.ld != a.row_elems || pieces < 1 || n_streams < a.world - 1) return 1;
+  const long cps = a.shard_rows / tp::CHUNK;
+  if (pieces > cps) pieces = static_cast<int>(cps);
+  for (int p = 0; p < pieces; ++p) {
+    const long c0 = p * cps / pieces, c1 = (p + 1) * cps / pieces;
+    const long off = (a.rank * a.shard_rows + c0 * tp::CHUNK) * a.ld;
+    const size_t bytes = static_cast<size_t>((c1 - c0) * tp::CHUNK * a.ld) * 2;
+    for (int q = 1; q < a.world; ++q) {
+      const int d = (a.rank - q + a.world) % a.world;
+      cudaStream_t st = streams[q - 1];
+      if (!a.xg[d] || !a.chunk[d]) return 2;
+      if (cudaMemcpyAsync(a.xg[d] + off, a.xg[a.rank] + off, bytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return 5;
+      if (cudaMemcpyAsync(a.chunk[d] + a.rank * cps + c0, seq_src, static_cast<size_t>(c1 - c0) * 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return 5;
+    }
+  }
+  return 0;
 }
 
 }  // namespace ghb

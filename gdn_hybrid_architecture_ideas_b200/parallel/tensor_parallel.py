@@ -31,6 +31,7 @@ MAXR = 8
 CHUNK = 128
 N_GATHER_SLOTS = 4
 N_STAGE_SLOTS = 2
+SEQ_RING = 64          # copy-engine push: sequence-number source words of the gathers in flight
 PAD_AG_DONE, PAD_RS_READY, PAD_RS_DONE = 0, 8, 16
 _ARGS_FMT = "<8Q8Q8Q5i4x3q2Ii4x8Q5Q2i"
 
@@ -96,7 +97,30 @@ class TensorParallel:
         # 32 -> 258, 64 -> 235, 96 -> 244, 128 -> 311 (the GEMM CTAs lose their SMs); 32 was the setting of the 8-GPU runs.
         # With the multicast push a shard leaves the GPU once, whatever the world size: a few CTAs saturate the links.
         default_push = "32" if self.multimem else ("64" if self.world <= 2 else "32")
+        # GHB_TP_MOVER: who moves the bytes between GPUs. "tma" (default): the bulk-copy engine, driven by one thread per CTA
+        # (tile loads of the local shard, tile stores into the peers' buffers; the scatter's partial tiles go straight from
+        # the GEMM's epilogue into their owner's staging slot). "threads": 16-byte loads and stores of whole CTAs (through
+        # the switch's multicast where mapped). The engine needs few CTAs, so the GEMM keeps almost every SM.
+        # GHB_TP_MOVER: who moves the bytes between GPUs.
+        #   "ce" (default)  a gather's shard is pushed by the copy engines (plain device-to-device copies on a side stream,
+        #                   each followed by a small copy that raises the chunk flags on the peer): no SM is spent on the
+        #                   push and the consuming GEMM, which polls the flags chunk by chunk, keeps all of them. A
+        #                   scatter's partial tiles go from the GEMM's epilogue straight into their owner's staging slot
+        #                   (tile stores of the bulk-copy engine over NVLink) and are summed there from local memory.
+        #   "tma"           the same scatter; the gather's push by a few CTAs of the consuming launch driving tile loads
+        #                   and tile stores. Measured: one SM keeps about 13 GB/s of remote tile stores in flight, so the
+        #                   push needs ~60 SMs to fill a link; kept for comparison.
+        #   "threads"       16-byte loads and stores of whole CTAs (through the switch's multicast where mapped).
+        self.mover = os.environ.get("GHB_TP_MOVER", "ce")
+        if self.mover not in ("ce", "tma", "threads"):
+            raise ValueError(f"GHB_TP_MOVER {self.mover!r}: 'ce', 'tma' or 'threads'")
+        if self.mover == "tma":
+            default_push = "32" if self.world <= 2 else "16"
         self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", default_push))
+        if self.mover == "ce":
+            self.push_streams = [torch.cuda.Stream(self.device) for _ in range(self.world - 1)]       # one per peer
+            self.push_pieces = int(os.environ.get("GHB_TP_PUSH_PIECES", max(1, 8 // self.world)))
+            self.seq_words = torch.zeros(SEQ_RING, max_tokens // self.world // CHUNK, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         dp.barrier()
 
@@ -114,7 +138,7 @@ class TensorParallel:
         raw = struct.pack(_ARGS_FMT, *peers("g", g_off), *peers("c", c_off), *peers("p", 0), self.rank, self.world, mode, push, axis,
                           shard_rows, row_elems, ld, seq, need, n_push, *peers("s", s_off), self.done_counter.data_ptr(),
                           self.owner_counters.data_ptr(), (self._mc["g"] + g_off) if self._mc["g"] else 0, (self._mc["s"] + s_off) if self._mc["s"] else 0,
-                          0 if out is None else out.data_ptr(), int(out is not None and out.dtype == torch.float32), 0)
+                          0 if out is None else out.data_ptr(), int(out is not None and out.dtype == torch.float32), int(self.mover != "threads"))
         return torch.frombuffer(bytearray(raw), dtype=torch.uint8)
 
     # ------------------------------------------------------------------ gather handles
@@ -140,21 +164,48 @@ class TensorParallel:
                 raise ValueError(f"tensor parallel gather of [{Ts}, {width}] exceeds the workspace ({self.max_tokens} x {self.max_width})")
             slot = self.next_slot
             self.next_slot = (slot + 1) % N_GATHER_SLOTS
-            prev = self.slot_seq[slot]
-            if prev:       # everything launched so far has read the slot's previous contents: tell the peers it is free
-                native.ext().tp_signal(self._args(2, seq=prev), PAD_AG_DONE, self.pad)
-                self._cache = {k: v for k, v in self._cache.items() if v.slot != slot}
+            prev = self.slot_seq[slot]     # released to the peers during the previous gather call (below)
             self.ag_seq += 1
             self.slot_seq[slot] = self.ag_seq
             base = slot * self.max_tokens * self.max_width
             full = self.gather_buf[base:base + T * width].view(T, width)
             full[self.rank * Ts:(self.rank + 1) * Ts].copy_(x_shard)
             g = Gathered(slot, self.ag_seq, prev, full, Ts, width)
+            # The slot the NEXT gather will take: everything launched so far has read its contents, so tell the peers now,
+            # one gather ahead of its reuse; by the time the peers push into it the word has long arrived.
+            nxt, release = self.next_slot, self.slot_seq[self.next_slot]
+            if release:
+                self._cache = {k: v for k, v in self._cache.items() if v.slot != nxt}
+            if self.mover == "ce":
+                self._push_by_copy_engines(g, release)
+            elif release:
+                native.ext().tp_signal(self._args(2, seq=release), PAD_AG_DONE, self.pad)
         g.src = x_shard          # keeps the shard's memory alive while the handle is cached: its address cannot be recycled
         if len(self._cache) > 8:
             self._cache.clear()
         self._cache[key] = g
         return g
+
+    def _push_by_copy_engines(self, g: Gathered, release: int) -> None:
+        """Queues the push of gather `g` on the side stream: behind the local copy of the shard, behind the word that says
+        every peer has released the slot's previous use (a bounded wait in a one-thread kernel on the main stream, which
+        also publishes `release`), one data copy and one flag copy per peer and piece."""
+        from ..ops import native
+
+        # The flag copies read a ring entry of words holding the sequence number. An entry is rewritten SEQ_RING gathers
+        # later; by then its copies have run: this rank's main stream gets there only through GEMMs that needed every
+        # peer's later pushes, which the peers queued after GEMMs that needed these flags.
+        words = self.seq_words[g.seq % SEQ_RING]
+        words.fill_(g.seq)
+        args = self._args(0, slot=g.slot, seq=release, need=g.need, shard_rows=g.shard_rows, row_elems=g.width, ld=g.width)
+        native.ext().tp_signal(args, PAD_AG_DONE, self.pad, PAD_AG_DONE, native.err_flag(self.device))
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
+        for st in self.push_streams:
+            st.wait_event(ready)
+        args = self._args(0, slot=g.slot, seq=g.seq, need=g.need, shard_rows=g.shard_rows, row_elems=g.width, ld=g.width)
+        native.ext().tp_push_copies(args, words, self.push_pieces, [st.cuda_stream for st in self.push_streams])
+        g.pushed = True
 
     def _ag_args(self, g: Gathered, axis: int):
         push = 0 if g.pushed else 1
