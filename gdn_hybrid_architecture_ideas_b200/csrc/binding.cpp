@@ -503,6 +503,22 @@ void tp_signal(const Tensor& args, int64_t word, const Tensor& like, int64_t wai
   TORCH_CHECK(wait_word < 0 || (err.has_value() && err->is_cuda()), "tp_signal: a wait needs the status word");
   check(ghb::tp_signal(args.data_ptr(), word, wait_word, err.has_value() ? err->data_ptr<int>() : nullptr, stream()), "tp_signal");
 }
+// Sum of a scatter's partial rows delivered into this rank's staging slot (bounded wait for the peers' flags inside).
+void tp_reduce(const Tensor& args, int64_t N, Tensor& err) {
+  TORCH_CHECK(!args.is_cuda() && args.numel() == static_cast<int64_t>(ghb::tp_args_bytes()), "tp_reduce: argument table size");
+  const c10::cuda::CUDAGuard guard(err.device());
+  const int rc = ghb::tp_reduce(args.data_ptr(), static_cast<int>(N), err.data_ptr<int>(), sm_count(), stream());
+  TORCH_CHECK(rc == 0, "tp_reduce refused (code ", rc, ")");
+}
+// Copy-engine delivery into (possibly a peer's) memory by address, with a flag word behind it, on a side stream.
+void tp_copy_flagged(int64_t dst, const Tensor& src, int64_t bytes, int64_t flag_dst, const Tensor& flag_src, int64_t stream_handle) {
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && bytes <= static_cast<int64_t>(src.numel() * src.element_size()), "tp_copy_flagged: source");
+  TORCH_CHECK(flag_src.is_cuda() && flag_src.scalar_type() == at::kInt && flag_src.numel() >= 1, "tp_copy_flagged: flag source");
+  const c10::cuda::CUDAGuard guard(src.device());
+  const int rc = ghb::tp_copy_flagged(reinterpret_cast<void*>(dst), src.data_ptr(), static_cast<size_t>(bytes), reinterpret_cast<void*>(flag_dst),
+                                      flag_src.data_ptr(), reinterpret_cast<cudaStream_t>(stream_handle));
+  TORCH_CHECK(rc == 0, "tp_copy_flagged refused (code ", rc, ")");
+}
 // Queues the copy-engine push of a gather on the caller's side streams (handles; one per peer).
 void tp_push_copies(const Tensor& args, const Tensor& seq_src, int64_t pieces, const std::vector<int64_t>& stream_handles) {
   TORCH_CHECK(!args.is_cuda() && args.numel() == static_cast<int64_t>(ghb::tp_args_bytes()), "tp_push_copies: argument table size");
@@ -558,6 +574,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tp", &gemm_tp);
   m.def("tp_signal", &tp_signal, py::arg("args"), py::arg("word"), py::arg("like"), py::arg("wait_word") = -1, py::arg("err") = py::none());
   m.def("tp_push_copies", &tp_push_copies);
+  m.def("tp_reduce", &tp_reduce);
+  m.def("tp_copy_flagged", &tp_copy_flagged);
   m.def("tp_args_bytes", &tp_args_bytes);
   m.def("tp_pad_words", &tp_pad_words);
   m.def("attention_fwd", &attention_fwd);

@@ -123,6 +123,98 @@ __device__ __forceinline__ bool wait_flag(const unsigned int* p, unsigned int se
 }
 }  // namespace tp
 
+// The scatter's second half, run by every CTA of a launch: wait (bounded) until every rank's partial rows for THIS
+// rank's row range are flagged, sum them and write the reduced rows; the last CTA publishes "this rank has read the
+// slot" to every rank. Sources: with a.tma the partials lie in this rank's own slot, source after source (local loads, a
+// fixed order); else each rank's partial rows are read from that rank's buffer (through the switch's multicast
+// reduction when mapped).
+__device__ void tp_scatter_tail(const tp::Args& a, int N, int* __restrict__ err, bool wait_own) {
+  using namespace tp;
+  {
+    // RS, second half: this rank's rows. Every rank's partial rows for them are flagged as they complete; sum them (in the
+    // switch when the buffer is multicast-mapped) and write the reduced rows.
+    __shared__ int go_reduce;
+    if (threadIdx.x == 0) {
+      go_reduce = (*reinterpret_cast<volatile int*>(err) == 0) ? 1 : 0;
+      for (int j = 0; j < a.world && go_reduce; ++j)      // this rank's own rows may be complete by stream order instead
+        if (wait_own || j != a.rank) go_reduce = wait_flag(a.pad[a.rank] + PAD_RS_READY + j, a.seq) ? 1 : 0;
+      if (!go_reduce && *reinterpret_cast<volatile int*>(err) == 0) atomicExch(err, 508);
+    }
+    __syncthreads();
+    if (go_reduce) {
+      // 16-byte items, several in flight per thread: a load over NVLink (or through the switch) takes microseconds, and the
+      // reduction is bound by how many of them are outstanding, not by arithmetic
+      constexpr int RU = 8;
+      const long n8 = a.shard_rows * N / 8;
+      const long base = static_cast<long>(a.rank) * a.shard_rows * N;
+      const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+      auto put = [&](long i, const float* sum) {
+        if (a.out_f32) {
+          float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + i * 8);
+          o[0] = make_float4(sum[0], sum[1], sum[2], sum[3]); o[1] = make_float4(sum[4], sum[5], sum[6], sum[7]);
+        } else {
+          uint32_t p[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { __nv_bfloat162 h = __floats2bfloat162_rn(sum[2 * e], sum[2 * e + 1]); p[e] = *reinterpret_cast<uint32_t*>(&h); }
+          reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + i * 8)[0] = make_uint4(p[0], p[1], p[2], p[3]);
+        }
+      };
+      auto widen = [](const uint4 v, float* f, bool add) {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+          f[2 * e] = (add ? f[2 * e] : 0.f) + t.x; f[2 * e + 1] = (add ? f[2 * e + 1] : 0.f) + t.y;
+        }
+      };
+      for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += stride * RU) {
+        if (a.tma) {       // every rank's partial rows already lie in this rank's slot, source after source: local loads, fixed order
+          float sum[RU][8];
+          for (int j = 0; j < a.world; ++j) {
+            uint4 v[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = reinterpret_cast<const uint4*>(a.stage[a.rank] + j * a.shard_rows * N)[i]; }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) widen(v[u], sum[u], j != 0); }
+          }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) put(i, sum[u]); }
+        } else if (a.stage_mc) {
+          uint4 v[RU];
+#pragma unroll
+          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = mc_ld_reduce_bf16x8(a.stage_mc + base + i * 8); }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) {
+            const long i = i0 + u * stride;
+            if (i < n8) { float sum[8]; widen(v[u], sum, false); put(i, sum); }
+          }
+        } else {
+          float sum[RU][8];
+          for (int q = 0; q < a.world; ++q) {
+            const int j = (a.rank + q) % a.world;
+            uint4 v[RU];
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = reinterpret_cast<const uint4*>(a.stage[j] + base)[i]; }
+#pragma unroll
+            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) widen(v[u], sum[u], q != 0); }
+          }
+#pragma unroll
+          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) put(i, sum[u]); }
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {      // the last CTA to finish publishes "this rank has read every rank's buffer slot of this call"
+      __threadfence_system();
+      const unsigned int arrived = atomicAdd(a.done_counter, 1u);
+      if (arrived == gridDim.x - 1) {
+        if (go_reduce) for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_DONE + a.rank, a.seq);
+        *a.done_counter = 0u;
+      }
+    }
+  }
+}
+
 // out: 0 bf16, 1 fp32, 2 fp32 accumulate (modes AG and plain); RS writes bf16 staging tiles.
 template <bool A_MN, bool B_MN, int OUT>
 __global__ void __launch_bounds__(tp::THREADS, 1)
@@ -509,88 +601,14 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (a.mode == 1) {
-    // RS, second half: this rank's rows. Every rank's partial rows for them are flagged as they complete; sum them (in the
-    // switch when the buffer is multicast-mapped) and write the reduced rows.
-    __shared__ int go_reduce;
-    if (threadIdx.x == 0) {
-      go_reduce = (*reinterpret_cast<volatile int*>(err) == 0) ? 1 : 0;
-      for (int j = 0; j < a.world && go_reduce; ++j) go_reduce = wait_flag(a.pad[a.rank] + PAD_RS_READY + j, a.seq) ? 1 : 0;
-      if (!go_reduce && *reinterpret_cast<volatile int*>(err) == 0) atomicExch(err, 508);
-    }
-    __syncthreads();
-    if (go_reduce) {
-      // 16-byte items, several in flight per thread: a load over NVLink (or through the switch) takes microseconds, and the
-      // reduction is bound by how many of them are outstanding, not by arithmetic
-      constexpr int RU = 8;
-      const long n8 = a.shard_rows * N / 8;
-      const long base = static_cast<long>(a.rank) * a.shard_rows * N;
-      const long stride = static_cast<long>(gridDim.x) * blockDim.x;
-      auto put = [&](long i, const float* sum) {
-        if (a.out_f32) {
-          float4* o = reinterpret_cast<float4*>(static_cast<float*>(a.out) + i * 8);
-          o[0] = make_float4(sum[0], sum[1], sum[2], sum[3]); o[1] = make_float4(sum[4], sum[5], sum[6], sum[7]);
-        } else {
-          uint32_t p[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) { __nv_bfloat162 h = __floats2bfloat162_rn(sum[2 * e], sum[2 * e + 1]); p[e] = *reinterpret_cast<uint32_t*>(&h); }
-          reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + i * 8)[0] = make_uint4(p[0], p[1], p[2], p[3]);
-        }
-      };
-      auto widen = [](const uint4 v, float* f, bool add) {
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
-          f[2 * e] = (add ? f[2 * e] : 0.f) + t.x; f[2 * e + 1] = (add ? f[2 * e + 1] : 0.f) + t.y;
-        }
-      };
-      for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += stride * RU) {
-        if (a.tma) {       // every rank's partial rows already lie in this rank's slot, source after source: local loads, fixed order
-          float sum[RU][8];
-          for (int j = 0; j < a.world; ++j) {
-            uint4 v[RU];
-#pragma unroll
-            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = reinterpret_cast<const uint4*>(a.stage[a.rank] + j * a.shard_rows * N)[i]; }
-#pragma unroll
-            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) widen(v[u], sum[u], j != 0); }
-          }
-#pragma unroll
-          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) put(i, sum[u]); }
-        } else if (a.stage_mc) {
-          uint4 v[RU];
-#pragma unroll
-          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = mc_ld_reduce_bf16x8(a.stage_mc + base + i * 8); }
-#pragma unroll
-          for (int u = 0; u < RU; ++u) {
-            const long i = i0 + u * stride;
-            if (i < n8) { float sum[8]; widen(v[u], sum, false); put(i, sum); }
-          }
-        } else {
-          float sum[RU][8];
-          for (int q = 0; q < a.world; ++q) {
-            const int j = (a.rank + q) % a.world;
-            uint4 v[RU];
-#pragma unroll
-            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) v[u] = reinterpret_cast<const uint4*>(a.stage[j] + base)[i]; }
-#pragma unroll
-            for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) widen(v[u], sum[u], q != 0); }
-          }
-#pragma unroll
-          for (int u = 0; u < RU; ++u) { const long i = i0 + u * stride; if (i < n8) put(i, sum[u]); }
-        }
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {      // the last CTA to finish publishes "this rank has read every rank's buffer slot of this call"
-      __threadfence_system();
-      const unsigned int arrived = atomicAdd(a.done_counter, 1u);
-      if (arrived == gridDim.x - 1) {
-        if (go_reduce) for (int p = 0; p < a.world; ++p) st_release_sys(a.pad[p] + PAD_RS_DONE + a.rank, a.seq);
-        *a.done_counter = 0u;
-      }
-    }
-  }
+  if (a.mode == 1) tp_scatter_tail(a, N, err, true);
+}
+
+// The scatter's reduction as a launch of its own (partials delivered by the copy engines).
+__global__ void __launch_bounds__(tp::THREADS)
+tp_reduce_kernel(const __grid_constant__ tp::Args a, int N, int* __restrict__ err) {
+  if (*reinterpret_cast<volatile int*>(err) != 0) return;
+  tp_scatter_tail(a, N, err, false);
 }
 
 // Publishes "this rank has released gather-slot uses <= seq" to every rank (stream-ordered after the slot's readers).
@@ -737,6 +755,23 @@ int tp_push_copies(const void* args, const void* seq_src, int pieces, const cuda
       if (cudaMemcpyAsync(a.chunk[d] + a.rank * cps + c0, seq_src, static_cast<size_t>(c1 - c0) * 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return 5;
     }
   }
+  return 0;
+}
+
+// Reduction of a scatter whose partials the copy engines delivered: args as for mode RS (stage[rank], pad, seq, out).
+int tp_reduce(const void* args, int N, int* err, int sms, cudaStream_t st) {
+  tp::Args a;
+  memcpy(&a, args, sizeof(a));
+  if (a.world < 1 || a.world > tp::MAXR || !a.stage[a.rank] || !a.out || !a.done_counter || N % 8 || !a.tma) return 1;
+  tp_reduce_kernel<<<2 * sms, tp::THREADS, 0, st>>>(a, N, err);
+  return cudaGetLastError() == cudaSuccess ? 0 : 4;
+}
+
+// One copy-engine delivery: `bytes` from src to dst (this GPU's or a peer's memory), then a 4-byte copy of *flag_src to
+// flag_dst on the same stream (so the word lands after the data).
+int tp_copy_flagged(void* dst, const void* src, size_t bytes, void* flag_dst, const void* flag_src, cudaStream_t st) {
+  if (cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return 5;
+  if (cudaMemcpyAsync(flag_dst, flag_src, 4, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return 5;
   return 0;
 }
 

@@ -118,6 +118,8 @@ int tp_pad_words();
 int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc, bool a_mn, bool b_mn, int out,
             const void* args, int* err, int sms, cudaStream_t st);
 int tp_signal(const void* args, int word, int wait_word, int* err, cudaStream_t st);
+int tp_reduce(const void* args, int N, int* err, int sms, cudaStream_t st);
+int tp_copy_flagged(void* dst, const void* src, size_t bytes, void* flag_dst, const void* flag_src, cudaStream_t st);
 int tp_push_copies(const void* args, const void* seq_src, int pieces, const cudaStream_t* streams, int n_streams);
 
 }  // namespace ghb

@@ -121,6 +121,14 @@ class TensorParallel:
             self.push_streams = [torch.cuda.Stream(self.device) for _ in range(self.world - 1)]       # one per peer
             self.push_pieces = int(os.environ.get("GHB_TP_PUSH_PIECES", max(1, 8 // self.world)))
             self.seq_words = torch.zeros(SEQ_RING, max_tokens // self.world // CHUNK, dtype=torch.int32, device=self.device)
+            # GHB_TP_SCATTER: "ce" delivers a scatter's partial rows by the copy engines too (one GEMM launch per owner's
+            # row range, its block copied to the owner while the next range is multiplied); "tma" keeps one launch whose
+            # epilogue stores the tiles into the owners' slots.
+            self.scatter = os.environ.get("GHB_TP_SCATTER", "ce")
+            if self.scatter not in ("ce", "tma"):
+                raise ValueError(f"GHB_TP_SCATTER {self.scatter!r}: 'ce' or 'tma'")
+            self.rs_words = torch.zeros(SEQ_RING, dtype=torch.int32, device=self.device)
+            self.parts = None                      # [2][world - 1] blocks of partial rows in flight to their owners
         torch.cuda.synchronize(self.device)
         dp.barrier()
 
@@ -261,10 +269,51 @@ class TensorParallel:
         self.rs_seq += 1
         seq, slot = self.rs_seq, self.rs_seq % N_STAGE_SLOTS
         out = torch.empty(Ts, N, dtype=out_dtype if out_dtype in (BF16, torch.float32) else BF16, device=self.device)
+        if self.mover == "ce" and self.scatter == "ce":
+            self._scatter_by_copy_engines(h, w, b_mn, seq, slot, Ts, N, out)
+            return out if out.dtype == out_dtype else out.to(out_dtype)
         args = self._args(1, seq=seq, need=max(seq - N_STAGE_SLOTS, 0), shard_rows=Ts, stage_slot=slot, out=out)
         native.ext().gemm_tp(h, w, None, False, b_mn, False, args, native.err_flag(self.device))      # partial tiles, flags and the reduction: one launch
         native._count()
         return out if out.dtype == out_dtype else out.to(out_dtype)
+
+    def _scatter_by_copy_engines(self, h, w, b_mn, seq, slot, Ts, N, out) -> None:
+        """h w^T owner by owner, the next rank's rows first and this rank's last: each block of partial rows [Ts, N] is a
+        launch of the plain GEMM, and once it is complete a copy engine carries it into its owner's staging slot (at this
+        rank's source index) with the call's number behind it, while the next block is multiplied. The reduction launch
+        then waits (bounded) for every peer's number, sums the world's blocks from local memory in rank order and tells
+        the peers that the slot is read. Before the first block leaves, the peers must have read the slot's previous use
+        (bounded wait in a one-thread launch on this stream); that also means this rank's blocks of two calls ago have
+        been consumed, so their buffers can be written again."""
+        from ..ops import native
+
+        W, r = self.world, self.rank
+        e, err = native.ext(), native.err_flag(self.device)
+        main = torch.cuda.current_stream(self.device)
+        need = max(seq - N_STAGE_SLOTS, 0)
+        if need:
+            e.tp_signal(self._args(1, seq=0, need=need, shard_rows=Ts), PAD_RS_DONE, self.pad, PAD_RS_DONE, err)
+        if self.parts is None or self.parts[0][0].numel() < Ts * N:
+            self.parts = [[torch.empty(Ts * N, dtype=BF16, device=self.device) for _ in range(W - 1)] for _ in range(2)]
+        word = self.rs_words[seq % SEQ_RING:seq % SEQ_RING + 1]
+        word.fill_(seq)
+        slot_bytes = slot * self.max_tokens * self.max_width * 2
+        block_bytes = Ts * N * 2
+        for j in range(1, W):
+            d = (r + j) % W
+            part = self.parts[seq % 2][j - 1][:Ts * N].view(Ts, N)
+            native.gemm(h[d * Ts:(d + 1) * Ts], w, out=part, b_mn=b_mn)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            st = self.push_streams[j - 1]
+            st.wait_event(ready)
+            e.tp_copy_flagged(self._ptrs["s"][d] + slot_bytes + r * block_bytes, part, block_bytes,
+                              self._ptrs["p"][d] + (PAD_RS_READY + r) * 4, word, st.cuda_stream)
+        base = slot * self.max_tokens * self.max_width
+        own = self.stage_buf[base + r * Ts * N:base + (r + 1) * Ts * N].view(Ts, N)
+        native.gemm(h[r * Ts:(r + 1) * Ts], w, out=own, b_mn=b_mn)
+        e.tp_reduce(self._args(1, seq=seq, need=need, shard_rows=Ts, stage_slot=slot, out=out), N, err)
+        native._count()
 
     @staticmethod
     def _plain(a, b, a_mn, b_mn, out_dtype):
