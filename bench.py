@@ -196,7 +196,9 @@ def run_ours(args) -> dict:
                    "optimizer": "adamw", "vocab": VOCAB, "l2": "per-step working set (GBs of activations) >> 126 MB L2",
                    "comm": os.environ.get("GHB_COMM", "auto"), "fused": bool(zero is not None and zero.fused is not None),
                    "multimem": bool(zero is not None and zero.fused is not None and zero.fused.multimem),
-                   "cuda_graphs": cfg.cuda_graphs, "loss": m["loss"]},
+                   "cuda_graphs": cfg.cuda_graphs, "loss": m["loss"],
+                   **({"tp_gather": getattr(trainer.tp, "gather_by", None), "tp_scatter": getattr(trainer.tp, "scatter", None),
+                       "tp_multimem": bool(getattr(trainer.tp, "multimem", False))} if tp and trainer.tp is not None else {})},
         "clocks": clocks,
         "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": trainer.h2d_bytes, "d2h_bytes_per_step": trainer.d2h_bytes},

@@ -75,7 +75,9 @@ struct Args {
   // --- scatter output
   void* out;                         // [Ts][N] this rank's reduced rows
   int out_f32;
-  int tma;                           // 1: the bulk-copy engine moves the data between GPUs (PeerMaps), 0: threads do
+  int tma;                           // bit 0: a scatter's partial tiles are tile-stored into their owner's slot and summed there
+                                     // from local memory, and tiles / k-blocks are walked chunk-major over the shards;
+                                     // bit 1: a gather's push CTAs drive tile loads and tile stores (else threads copy)
 };
 
 // One tensor map per rank over the same buffer on every GPU. AG: the gather slot [T][row_elems] (boxes of PUSH_ROWS x
@@ -168,7 +170,7 @@ __device__ void tp_scatter_tail(const tp::Args& a, int N, int* __restrict__ err,
         }
       };
       for (long i0 = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n8; i0 += stride * RU) {
-        if (a.tma) {       // every rank's partial rows already lie in this rank's slot, source after source: local loads, fixed order
+        if (a.tma & 1) {       // every rank's partial rows already lie in this rank's slot, source after source: local loads, fixed order
           float sum[RU][8];
           for (int j = 0; j < a.world; ++j) {
             uint4 v[RU];
@@ -236,7 +238,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     const long vec_per_row = a.row_elems / 8;                 // 16-byte vectors
     const __nv_bfloat16* src = a.xg[a.rank] + a.rank * a.shard_rows * a.ld;
     constexpr int UNROLL = 8;                                  // loads in flight per thread: the copy is latency-bound otherwise
-    if (a.tma) {
+    if (a.tma & 2) {
       // One thread drives the bulk-copy engine: a PUSH_ROWS x PUSH_COLS box of the local shard comes into shared memory
       // (tile load) and leaves once per peer (tile stores into the same rows of that peer's buffer). Loads run
       // PUSH_STAGES - 1 boxes ahead of the stores; a chunk's flag is raised on every peer once all of its stores are done.
@@ -372,7 +374,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int tiles_per_shard = a.mode == 2 ? 0 : static_cast<int>(a.shard_rows / BM);
   const int m_rot = a.mode == 0 ? (a.axis == 0 ? a.rank * tiles_per_shard : 0) : (a.mode == 1 ? ((a.rank + 1) % a.world) * tiles_per_shard : 0);
   const int kb_rot = (a.mode == 0 && a.axis == 1) ? static_cast<int>(a.rank * (a.shard_rows / BK)) : 0;
-  const bool k_interleave = a.tma && a.mode == 0 && a.axis == 1;
+  const bool k_interleave = (a.tma & 1) && a.mode == 0 && a.axis == 1;
   const int chunks_in_shard = a.mode == 2 ? 1 : static_cast<int>(a.shard_rows / CHUNK);
   auto kb_of = [&](int pos) -> int {      // position in this rank's reduction order -> k-block
     if (!k_interleave) return (pos + kb_rot) % num_kb;
@@ -387,7 +389,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   const int kbs = (num_kb + splits - 1) / splits;
   auto tile_of = [&](int u, int& tm, int& tn, int& k_lo, int& k_hi) {     // column tiles of one row tile are consecutive: they share its chunk
     const int t = u % tiles, sp = u / tiles;
-    if (a.tma && ((a.mode == 0 && a.axis == 0) || a.mode == 1)) {
+    if ((a.tma & 1) && ((a.mode == 0 && a.axis == 0) || a.mode == 1)) {
       // chunk-major over the shards: row tile c of every shard, then row tile c + 1 (AG: the order in which the pushed
       // chunks arrive, own shard first; RS: every owner's link carries partial tiles during the whole product, own rows last)
       const int i = t / tiles_n, c = i / a.world, j = i % a.world;
@@ -507,7 +509,7 @@ gemm_tp_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         // RS: the partial tile goes to THIS rank's buffer (TMA tile stores through the swizzled slabs); once every tile of an
         // owner's row range is stored, the owner is told
         const int d = static_cast<int>((static_cast<long>(tm) * BM) / a.shard_rows);
-        if (ok && a.tma) {
+        if (ok && (a.tma & 1)) {
           // the tile goes straight into owner d's staging slot, at this rank's source index: the bulk-copy engine writes
           // it over NVLink while the next tile is multiplied. A tile is counted for its owner one tile later, once its
           // stores are complete (at most the newest tile's stores stay in flight)
@@ -687,14 +689,14 @@ int gemm_tp(const void* A, const void* B, void* C, int M, int N, int K, long lda
   static_assert(tp::PUSH_STAGES * tp::PUSH_TILE_BYTES + 256 <= tp::SMEM - 1024, "the push ring fits the kernel's shared memory");
   tp::PeerMaps pm;
   memset(&pm, 0, sizeof(pm));
-  if (a.tma && a.mode == 0 && a.push) {
+  if ((a.tma & 2) && a.mode == 0 && a.push) {
     const uint64_t dims[2] = {static_cast<uint64_t>(a.row_elems), static_cast<uint64_t>(a.shard_rows * a.world)};
     const uint64_t strides[1] = {static_cast<uint64_t>(a.ld) * 2};
     const uint32_t box[2] = {tp::PUSH_COLS, tp::PUSH_ROWS};
     for (int d = 0; d < a.world; ++d)
       if (!a.xg[d] || !encode_tensor_map_2d(&pm.m[d], a.xg[d], 2, dims, strides, box, false)) return 24;
   }
-  if (a.tma && a.mode == 1) {
+  if ((a.tma & 1) && a.mode == 1) {
     const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(a.shard_rows)}, strides[1] = {static_cast<uint64_t>(N) * 2};
     const uint32_t box[2] = {64, tp::BM};
     for (int d = 0; d < a.world; ++d)
@@ -762,7 +764,7 @@ int tp_push_copies(const void* args, const void* seq_src, int pieces, const cuda
 int tp_reduce(const void* args, int N, int* err, int sms, cudaStream_t st) {
   tp::Args a;
   memcpy(&a, args, sizeof(a));
-  if (a.world < 1 || a.world > tp::MAXR || !a.stage[a.rank] || !a.out || !a.done_counter || N % 8 || !a.tma) return 1;
+  if (a.world < 1 || a.world > tp::MAXR || !a.stage[a.rank] || !a.out || !a.done_counter || N % 8 || !(a.tma & 1)) return 1;
   tp_reduce_kernel<<<2 * sms, tp::THREADS, 0, st>>>(a, N, err);
   return cudaGetLastError() == cudaSuccess ? 0 : 4;
 }

@@ -97,38 +97,34 @@ class TensorParallel:
         # 32 -> 258, 64 -> 235, 96 -> 244, 128 -> 311 (the GEMM CTAs lose their SMs); 32 was the setting of the 8-GPU runs.
         # With the multicast push a shard leaves the GPU once, whatever the world size: a few CTAs saturate the links.
         default_push = "32" if self.multimem else ("64" if self.world <= 2 else "32")
-        # GHB_TP_MOVER: who moves the bytes between GPUs. "tma" (default): the bulk-copy engine, driven by one thread per CTA
-        # (tile loads of the local shard, tile stores into the peers' buffers; the scatter's partial tiles go straight from
-        # the GEMM's epilogue into their owner's staging slot). "threads": 16-byte loads and stores of whole CTAs (through
-        # the switch's multicast where mapped). The engine needs few CTAs, so the GEMM keeps almost every SM.
-        # GHB_TP_MOVER: who moves the bytes between GPUs.
-        #   "ce" (default)  a gather's shard is pushed by the copy engines (plain device-to-device copies on a side stream,
-        #                   each followed by a small copy that raises the chunk flags on the peer): no SM is spent on the
-        #                   push and the consuming GEMM, which polls the flags chunk by chunk, keeps all of them. A
-        #                   scatter's partial tiles go from the GEMM's epilogue straight into their owner's staging slot
-        #                   (tile stores of the bulk-copy engine over NVLink) and are summed there from local memory.
-        #   "tma"           the same scatter; the gather's push by a few CTAs of the consuming launch driving tile loads
-        #                   and tile stores. Measured: one SM keeps about 13 GB/s of remote tile stores in flight, so the
-        #                   push needs ~60 SMs to fill a link; kept for comparison.
-        #   "threads"       16-byte loads and stores of whole CTAs (through the switch's multicast where mapped).
-        self.mover = os.environ.get("GHB_TP_MOVER", "ce")
-        if self.mover not in ("ce", "tma", "threads"):
-            raise ValueError(f"GHB_TP_MOVER {self.mover!r}: 'ce', 'tma' or 'threads'")
-        if self.mover == "tma":
+        # Who moves the bytes between GPUs (measured per boundary with scripts/tp_bench.py, 65536 x 2048 bf16):
+        #   GHB_TP_GATHER   "ce": the shard is pushed by the copy engines (device-to-device copies on side streams, each
+        #                   followed by a small copy that raises the chunk flags on the peer): no SM is spent and the
+        #                   consuming GEMM, which polls the flags chunk by chunk, keeps all of them. Best at 2 ranks; at 8
+        #                   the engines carry about 300 GB/s in total, less than the links.
+        #                   "threads": a few CTAs of the consuming launch copy with 16-byte loads and stores, ONE multicast
+        #                   store per 16 bytes where the buffer is mapped through the switch (the shard leaves this GPU once
+        #                   whatever the world size). "tma": those CTAs drive tile loads and tile stores instead (one SM
+        #                   keeps about 13 GB/s of remote tile stores in flight: ~60 SMs to fill a link; for comparison).
+        #   GHB_TP_SCATTER  "tma": one launch whose epilogue tile-stores each partial tile into its owner's staging slot
+        #                   over NVLink; the owner sums the world's tiles from local memory. "ce": one GEMM launch per
+        #                   owner's rows, each block carried by a copy engine while the next is multiplied (best at 2
+        #                   ranks). "pull": partials stay local and the owner reads them from every rank (through the
+        #                   switch's reduction where mapped).
+        few = self.world <= 2 or not self.multimem
+        self.gather_by = os.environ.get("GHB_TP_GATHER", "ce" if few else "threads")
+        self.scatter = os.environ.get("GHB_TP_SCATTER", "ce" if self.world <= 2 else "tma")
+        if self.gather_by not in ("ce", "tma", "threads") or self.scatter not in ("ce", "tma", "pull"):
+            raise ValueError(f"GHB_TP_GATHER {self.gather_by!r} ('ce', 'tma', 'threads') / GHB_TP_SCATTER {self.scatter!r} ('ce', 'tma', 'pull')")
+        if self.gather_by == "tma":
             default_push = "32" if self.world <= 2 else "16"
         self.n_push = int(os.environ.get("GHB_TP_PUSH_CTAS", default_push))
-        if self.mover == "ce":
-            self.push_streams = [torch.cuda.Stream(self.device) for _ in range(self.world - 1)]       # one per peer
-            self.push_pieces = int(os.environ.get("GHB_TP_PUSH_PIECES", max(1, 8 // self.world)))
-            self.seq_words = torch.zeros(SEQ_RING, max_tokens // self.world // CHUNK, dtype=torch.int32, device=self.device)
-            # GHB_TP_SCATTER: "ce" delivers a scatter's partial rows by the copy engines too (one GEMM launch per owner's
-            # row range, its block copied to the owner while the next range is multiplied); "tma" keeps one launch whose
-            # epilogue stores the tiles into the owners' slots.
-            self.scatter = os.environ.get("GHB_TP_SCATTER", "ce")
-            if self.scatter not in ("ce", "tma"):
-                raise ValueError(f"GHB_TP_SCATTER {self.scatter!r}: 'ce' or 'tma'")
-            self.rs_words = torch.zeros(SEQ_RING, dtype=torch.int32, device=self.device)
-            self.parts = None                      # [2][world - 1] blocks of partial rows in flight to their owners
+        self.kernel_flags = (0 if self.scatter == "pull" else 1) | (2 if self.gather_by == "tma" else 0)
+        self.push_streams = [torch.cuda.Stream(self.device) for _ in range(self.world - 1)]       # one per peer
+        self.push_pieces = int(os.environ.get("GHB_TP_PUSH_PIECES", max(1, 8 // self.world)))
+        self.seq_words = torch.zeros(SEQ_RING, max_tokens // self.world // CHUNK, dtype=torch.int32, device=self.device)
+        self.rs_words = torch.zeros(SEQ_RING, dtype=torch.int32, device=self.device)
+        self.parts = None                      # [2][world - 1] blocks of partial rows in flight to their owners
         torch.cuda.synchronize(self.device)
         dp.barrier()
 
@@ -146,7 +142,7 @@ class TensorParallel:
         raw = struct.pack(_ARGS_FMT, *peers("g", g_off), *peers("c", c_off), *peers("p", 0), self.rank, self.world, mode, push, axis,
                           shard_rows, row_elems, ld, seq, need, n_push, *peers("s", s_off), self.done_counter.data_ptr(),
                           self.owner_counters.data_ptr(), (self._mc["g"] + g_off) if self._mc["g"] else 0, (self._mc["s"] + s_off) if self._mc["s"] else 0,
-                          0 if out is None else out.data_ptr(), int(out is not None and out.dtype == torch.float32), int(self.mover != "threads"))
+                          0 if out is None else out.data_ptr(), int(out is not None and out.dtype == torch.float32), self.kernel_flags)
         return torch.frombuffer(bytearray(raw), dtype=torch.uint8)
 
     # ------------------------------------------------------------------ gather handles
@@ -184,7 +180,7 @@ class TensorParallel:
             nxt, release = self.next_slot, self.slot_seq[self.next_slot]
             if release:
                 self._cache = {k: v for k, v in self._cache.items() if v.slot != nxt}
-            if self.mover == "ce":
+            if self.gather_by == "ce":
                 self._push_by_copy_engines(g, release)
             elif release:
                 native.ext().tp_signal(self._args(2, seq=release), PAD_AG_DONE, self.pad)
@@ -269,7 +265,7 @@ class TensorParallel:
         self.rs_seq += 1
         seq, slot = self.rs_seq, self.rs_seq % N_STAGE_SLOTS
         out = torch.empty(Ts, N, dtype=out_dtype if out_dtype in (BF16, torch.float32) else BF16, device=self.device)
-        if self.mover == "ce" and self.scatter == "ce":
+        if self.scatter == "ce":
             self._scatter_by_copy_engines(h, w, b_mn, seq, slot, Ts, N, out)
             return out if out.dtype == out_dtype else out.to(out_dtype)
         args = self._args(1, seq=seq, need=max(seq - N_STAGE_SLOTS, 0), shard_rows=Ts, stage_slot=slot, out=out)

@@ -118,7 +118,7 @@ def main():
                 print(json.dumps({"op": op, "impl": impl, "world": W, "tokens": T, "d": d, "n": n, "ms": round(ms, 4),
                                   "wire_MB_per_rank": round(wire / 1e6, 1), "gflop_per_rank": round(fl / 1e9, 1),
                                   "roofline_ms": round(target, 4), "fraction_of_roofline": round(target / ms, 3),
-                                  "mover": getattr(tp, "mover", None), "scatter": getattr(tp, "scatter", None)}), flush=True)
+                                  "gather": getattr(tp, "gather_by", None), "scatter": getattr(tp, "scatter", None)}), flush=True)
         if impl == "fused":
             from gdn_hybrid_architecture_ideas_b200.ops import native
             torch.cuda.synchronize()
