@@ -213,8 +213,11 @@ class HostPool:
 
     # -- the hooks
     def pack(self, t: torch.Tensor):
+        # Kept as they are: small tensors, parameters, and views into a larger storage (a slice of a flat weight buffer, a
+        # column range of an activation): the storage outlives the view, so parking it frees nothing, and code that saved
+        # two neighbouring views to address them as one block must get those very views back.
         if not isinstance(t, torch.Tensor) or t.device != self.device or t.numel() * t.element_size() < self.min_bytes or isinstance(t, torch.nn.Parameter) \
-                or not t.is_contiguous():
+                or not t.is_contiguous() or t.untyped_storage().nbytes() != t.numel() * t.element_size():
             self.stats["kept"] += 1
             return ("keep", t)
         buf = self._take(t.shape, t.dtype)

@@ -99,3 +99,44 @@ def test_the_lead_bounds_the_copies_in_flight():
     assert len(pool.in_flight) == 2 and pool.lane.done == 3      # the three oldest were waited for
     assert torch.equal(handles[0].buf, keep[0]) and torch.isnan(handles[4].buf).all()
     assert torch.equal(pool.unpack(handles[4]), keep[4])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["host", "host_overlap"])
+def test_parked_activations_train_the_same_on_the_device(mode):
+    """On a GPU the copies run on a CUDA stream (pinned buffers, events): the losses are those of keeping everything, up to
+    the summation order of the sliced weight-gradient GEMMs (floating-point reductions, not fixed from run to run)."""
+    from gdn_hybrid_architecture_ideas_b200.ops import native
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    def run(m):
+        model = C.hybrid_model_config("60m", full=True)
+        model.encoder.n_layers, model.encoder.nope_global_layers, model.vocab_size = 4, (0,), 4096
+        cfg = C.TrainConfig(model=model, data=C.DataConfig(kind="synthetic", seq_len=1024, batch_size=2, seed=5), steps=100, seed=7)
+        cfg.autocast, cfg.head_impl, cfg.metrics_jsonl, cfg.log_every = "bfloat16", "fused", False, 0
+        cfg.optim.warmup_steps, cfg.optim.lr, cfg.activation_checkpoint = 1, 1e-4, m
+        t = Trainer(cfg, None, None)
+        losses = [t.train_step()["loss"] for _ in range(3)]
+        native.check_status()
+        return losses, t
+
+    want, _ = run("none")
+    got, t = run(mode)
+    pool = t.model.encoder.host_pool
+    assert pool is not None and pool.stats["packed"] > 0 and pool.stats["unpacked"] > 0
+    if mode == "host_overlap":
+        assert pool.stats["prefetched"] > 0
+    assert got[0] == want[0] and max(abs(a - b) for a, b in zip(got, want)) < 1e-3, (got, want)
+
+
+def test_views_into_a_larger_storage_are_handed_back_untouched():
+    """Two neighbouring slices of one buffer, saved for a backward that addresses them as a single block, come back as the
+    same views: the pool parks only tensors that own their whole storage."""
+    pool = A.HostPool(torch.device("cpu"), min_bytes=0)
+    flat = torch.arange(24.0)
+    a, b = flat[:8].view(2, 4), flat[8:24].view(4, 4)
+    ha, hb, hc = pool.pack(a), pool.pack(b), pool.pack(torch.ones(3))
+    assert pool.unpack(ha) is a and pool.unpack(hb) is b and pool.stats["kept"] == 2 and pool.stats["packed"] == 1
+    joined = torch.as_strided(pool.unpack(ha), (6, 4), (4, 1))
+    assert torch.equal(joined, flat.view(6, 4))
+    assert torch.equal(pool.unpack(hc), torch.ones(3))
