@@ -43,6 +43,19 @@ class Gathered:
     def __init__(self, slot, seq, need, full, shard_rows, width):
         self.slot, self.seq, self.need, self.full, self.shard_rows, self.width = slot, seq, need, full, shard_rows, width
         self.pushed = False
+        self.fan = FanIn()
+
+
+class FanIn:
+    """The column-parallel projections that read one gathered input. Each of them owes the input a partial gradient
+    dy_i W_i over all tokens, to be reduce-scattered; their sum is one product over the concatenated hidden columns, so
+    the backward of every projection but the last to run only leaves (dy_i, W_i) here, and the last one multiplies and
+    scatters once: one scatter per input instead of one per projection."""
+
+    __slots__ = ("expected", "left")
+
+    def __init__(self):
+        self.expected, self.left = 0, []
 
 
 class TensorParallel:
@@ -57,6 +70,9 @@ class TensorParallel:
         self.max_tokens, self.max_width = max_tokens, max_width
         self.ag_seq = self.rs_seq = 0
         self._cache = {}
+        # GHB_TP_MERGE_DX=0: every column-parallel projection scatters its own input gradient (see FanIn)
+        self.merge_input_grads = os.environ.get("GHB_TP_MERGE_DX", "1") != "0"
+        self.open_fans: set = set()
         if impl != "fused":
             return
         import torch.distributed._symmetric_memory as symm
@@ -324,8 +340,20 @@ class TensorParallel:
 
     # ------------------------------------------------------------------ replicated parameters
 
+    def check_fans(self) -> None:
+        """After a backward: no input may still be waiting for projections whose backward never ran (an output that did
+        not reach the loss) — its gradient would be short of the parts left behind. Raises by naming the count."""
+        stuck = [f for f in self.open_fans if f.left]
+        self.open_fans.clear()
+        if stuck:
+            for f in stuck:
+                f.left, f.expected = [], 0
+            raise RuntimeError(f"tensor parallel: {len(stuck)} gathered input(s) received the backward of only some of their column-parallel "
+                               "projections; their input gradients were withheld (set GHB_TP_MERGE_DX=0 for models with unused projections)")
+
     def all_reduce_grads(self, params) -> None:
         """Sum over ranks of the gradients of replicated parameters (each rank saw its own token shard)."""
+        self.check_fans()
         grads = [p.grad for p in params if p.grad is not None]
         if not grads:
             return
@@ -350,9 +378,15 @@ class _ColumnParallel(torch.autograd.Function):
         if x.is_cuda:
             from ..ops.native import _pad_rows
             x2, w_lp = x2.to(BF16), _pad_rows(w_lp)       # output rows stay 16-byte aligned for projections with a few outputs
-        y = tp.ag_gemm(tp.gather(x2), w_lp, out_dtype=x2.dtype)
+        g = tp.gather(x2)
+        y = tp.ag_gemm(g, w_lp, out_dtype=x2.dtype)
         ctx.save_for_backward(x2, w_lp)
         ctx.tp, ctx.xshape, ctx.xdtype, ctx.n = tp, x.shape, x.dtype, n
+        ctx.fan = None
+        if ctx.needs_input_grad[0] and tp.merge_input_grads:
+            ctx.fan = g.fan
+            g.fan.expected += 1
+            tp.open_fans.add(g.fan)
         return y[:, :n] if n != w_lp.shape[0] else y
 
     @staticmethod
@@ -363,10 +397,22 @@ class _ColumnParallel(torch.autograd.Function):
         if ctx.n != w_lp.shape[0]:
             dy2 = torch.nn.functional.pad(dy2, (0, w_lp.shape[0] - ctx.n))
         dy2 = dy2.contiguous()
-        dx = tp.gemm_rs(dy2, w_lp, b_mn=True, out_dtype=x2.dtype)
+        fan, dx = ctx.fan, None
+        if fan is None:
+            if ctx.needs_input_grad[0]:
+                dx = tp.gemm_rs(dy2, w_lp, b_mn=True, out_dtype=x2.dtype)
+        else:
+            fan.left.append((dy2, w_lp))
+            if len(fan.left) == fan.expected:          # the last projection of this input: one product, one scatter
+                if len(fan.left) == 1:
+                    dx = tp.gemm_rs(dy2, w_lp, b_mn=True, out_dtype=x2.dtype)
+                else:
+                    dx = tp.gemm_rs(torch.cat([d for d, _ in fan.left], dim=1), torch.cat([w for _, w in fan.left], dim=0), b_mn=True, out_dtype=x2.dtype)
+                fan.left, fan.expected = [], 0
+                tp.open_fans.discard(fan)
         g = tp.gather(x2)
-        dw = tp.gemm_gathered_k(dy2, g.full, g)[:ctx.n]
-        return dx.view(ctx.xshape).to(ctx.xdtype), dw, None, None
+        dw = tp.gemm_gathered_k(dy2, g.full, g)[:ctx.n] if ctx.needs_input_grad[1] else None
+        return (None if dx is None else dx.view(ctx.xshape).to(ctx.xdtype)), dw, None, None
 
 
 class _RowParallel(torch.autograd.Function):

@@ -50,7 +50,28 @@ def main():
             row.weight.data.copy_(w_row[:, r * Kr:(r + 1) * Kr])
             o = tpm.row_parallel(h, row, tp)
             (o.float() * dout[r * Ts:(r + 1) * Ts].to(dev)).sum().backward()
-            out = [t.detach().float().cpu() for t in (y, ys, x.grad, lin.weight.grad, small.weight.grad, o, h.grad, row.weight.grad)]
+            out = [t.detach().float().cpu().clone() for t in (y, ys, x.grad, lin.weight.grad, small.weight.grad, o, h.grad, row.weight.grad)]
+        # the two projections of one input scatter their input gradient once, and a projection whose output never reached
+        # the loss is reported instead of silently shortening the gradient
+        calls, plain_rs = [0], tp.gemm_rs
+
+        def counted(*a, **k):
+            calls[0] += 1
+            return plain_rs(*a, **k)
+        tp.gemm_rs = counted
+        x = x_full[r * Ts:(r + 1) * Ts].to(dev, dt).requires_grad_()
+        (tpm.column_parallel(x, lin, tp).float().sum() + tpm.column_parallel(x, small, tp).float().sum()).backward()
+        assert calls[0] == 1 and x.grad is not None, calls
+        tp.check_fans()
+        x = x_full[r * Ts:(r + 1) * Ts].to(dev, dt).requires_grad_()
+        y, _unused = tpm.column_parallel(x, lin, tp), tpm.column_parallel(x, small, tp)
+        y.float().sum().backward()
+        try:
+            tp.check_fans()
+            raise AssertionError("an input whose projections did not all run backward was not reported")
+        except RuntimeError as err:
+            assert "withheld" in str(err)
+        tp.gemm_rs = plain_rs
         if cuda:
             from gdn_hybrid_architecture_ideas_b200.ops import native
             torch.cuda.synchronize()
