@@ -307,8 +307,8 @@ def test_shipped_configs_and_run_entries_load():
     for runs_file in sorted((root / "runs").glob("*.yaml")):
         runs = run_entry.load_runs(runs_file, "/data", "/tmp/runs")
         for entry in runs["runs"]:
-            cfg = C.load_yaml(root / entry["config"])
-            for item in entry.get("set", []):
+            cfg = C.load_yaml(root / (entry.get("config") or entry["base"]))
+            for item in run_entry.entry_overrides(runs, entry):
                 C.apply_override(cfg, item)
             C.require_supported(cfg)
             assert run_entry.build_command(runs, entry, "/tmp/runs", nproc=2)[1:3] == ["-m", "torch.distributed.run"]

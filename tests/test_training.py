@@ -578,25 +578,78 @@ def test_block_attn_res_trains(tmp_path, arm):
     assert any(n.endswith(want) for n, _ in t.model.named_parameters())
 
 
+def _entry_config(run_entry, runs, entry, root):
+    cmd = run_entry.build_command(runs, entry, "/runs", check_eval=False)
+    cfg = C.load_yaml(cmd[cmd.index("--config") + 1])
+    for i, x in enumerate(cmd):
+        if x == "--set":
+            C.apply_override(cfg, cmd[i + 1])
+    C.require_supported(cfg)
+    return cfg
+
+
 def test_every_run_entry_builds():
-    """Every entry of the shipped run files loads its config, applies its overrides and builds (meta device)."""
-    import yaml
+    """Every entry of the shipped runs files resolves through run_entry (common patch, nested patch, flat set list), passes the
+    refusal tables and builds (meta device; each distinct model once)."""
+    import importlib.util
+    import json
     from pathlib import Path
 
     from gdn_hybrid_architecture_ideas_b200.models import build_model
 
     root = Path(__file__).resolve().parent.parent
-    seen = 0
+    spec = importlib.util.spec_from_file_location("run_entry", root / "scripts" / "run_entry.py")
+    run_entry = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(run_entry)
+    seen, built = 0, set()
     for path in sorted((root / "runs").glob("*.yaml")):
-        for entry in yaml.safe_load(path.read_text())["runs"]:
-            cfg = C.load_yaml(root / entry["config"])
-            for s in entry.get("set", []):
-                C.apply_override(cfg, s)
-            with torch.device("meta"):
-                model = build_model(cfg.model)
-            assert sum(p.numel() for p in model.parameters()) > 0, entry["name"]
+        runs = run_entry.load_runs(path, "/data", "/runs")
+        for entry in runs["runs"]:
+            cfg = _entry_config(run_entry, runs, entry, root)
+            key = json.dumps(C.to_dict(cfg.model), sort_keys=True, default=str)
+            if key not in built:
+                built.add(key)
+                with torch.device("meta"):
+                    model = build_model(cfg.model)
+                assert sum(p.numel() for p in model.parameters()) > 0, entry["name"]
             seen += 1
-    assert seen >= 10
+    assert seen >= 140 and len(built) >= 25
+    # the flat form and the nested form of one entry resolve to the same config
+    flat = {"runs": [{"name": "x", "config": "configs/v2/control-a-60m.yaml", "seed": 1,
+                      "set": ["model.encoder.attn_res=block_entry", "model.encoder.n_layers=24", "steps=7", "tst.schedule=[[0,4],[3,1]]"]}]}
+    nested = {"common": {"steps": 7}, "runs": [{"name": "x", "base": "configs/v2/control-a-60m.yaml", "seed": 1,
+                                                "patch": {"model": {"encoder": {"attn_res": "block_entry", "n_layers": 24}}, "tst": {"schedule": [[0, 4], [3, 1]]}}}]}
+    a = _entry_config(run_entry, flat, flat["runs"][0], root)
+    b = _entry_config(run_entry, nested, nested["runs"][0], root)
+    assert C.to_dict(a) == C.to_dict(b)
+    with pytest.raises(KeyError, match="no_such_key"):
+        run_entry.flatten_patch({"model": {"no_such_key": 1}})
+
+
+def test_published_runs_files_load_as_they_are():
+    """The reference's own runs files (flat `set` lists over its base configs' names) resolve, pass the refusal tables and name
+    the same configs as the nested files shipped here."""
+    import importlib.util
+    from pathlib import Path
+
+    from tests.helpers import REFERENCE
+
+    theirs = Path(REFERENCE) / "runs"
+    if not theirs.is_dir():
+        pytest.skip("no reference checkout")
+    root = Path(__file__).resolve().parent.parent
+    spec = importlib.util.spec_from_file_location("run_entry", root / "scripts" / "run_entry.py")
+    run_entry = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(run_entry)
+    n = 0
+    for path in sorted(theirs.glob("*.yaml")):
+        pub = run_entry.load_runs(path, "/data", "/runs")
+        own = run_entry.load_runs(root / "runs" / path.name, "/data", "/runs")
+        assert [e["name"] for e in pub["runs"]] == [e["name"] for e in own["runs"]], path.name
+        for e_pub, e_own in zip(pub["runs"], own["runs"]):
+            assert C.to_dict(_entry_config(run_entry, pub, e_pub, root)) == C.to_dict(_entry_config(run_entry, own, e_own, root)), e_pub["name"]
+            n += 1
+    assert n >= 140
 
 
 def test_branch_and_stage_continue_another_run(tmp_path):
