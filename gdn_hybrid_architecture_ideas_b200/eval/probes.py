@@ -34,6 +34,8 @@ class Probe:
     answer_len: int
     pieces: tuple = ()       # multi-fact answers: (length, is_fact) per piece, in answer order
     group: str = ""          # multi-fact: the layout; transcode: the direction
+    candidates: tuple = ()   # multiple choice (text-level depth items): one single-token continuation per candidate
+    gold: int = -1           # index of the right candidate
 
 
 def _rand(g, lo, hi, n):
@@ -214,6 +216,9 @@ def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype
                 item["group"] = p.group
             if p.pieces:         # the headline of a multi-fact item counts the fact tokens only
                 item.update(multifact_metrics(p, (top[b, sl] == tgt[b, sl]).tolist(), ce[b, sl].tolist()), exact_all=hit)
+            if p.candidates:     # multiple choice among single-token continuations: the candidate with the largest logit
+                cand = torch.tensor([c[0] for c in p.candidates])
+                item["choice_ok"] = int(logits[b, p.answer_start - 1].float().cpu()[cand].argmax()) == p.gold
             if keep_tokens:
                 item.update(index=s + b, ok=(top[b, sl] == tgt[b, sl]).tolist(), nats=ce[b, sl].tolist())
             exact += int(item["exact"])

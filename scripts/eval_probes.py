@@ -42,9 +42,11 @@ def main(argv=None) -> int:
             ap.error(f"the set was built for a vocabulary of {blob['vocab']}, the model has {cfg.model.vocab_size}")
         stored = {}
         for p in blob["probes"]:
-            stored.setdefault((p["length"], p["kind"]), []).append(
-                probes.Probe(p["kind"], p["ids"], p["answer_start"], p["answer_len"], tuple(map(tuple, p["pieces"])), p["group"]))
-    cells = sorted(stored) if stored is not None else [(int(x), k) for x in a.lengths.split(",") for k in probes.PROBE_KINDS]
+            # token-id sets are keyed by their nominal length; text-level sets (scripts/build_text_probes.py) by their cell
+            stored.setdefault((p.get("cell", p["length"]), p["kind"]), []).append(
+                probes.Probe(p["kind"], p["ids"], p["answer_start"], p["answer_len"], tuple(map(tuple, p.get("pieces", ()))), p.get("group", ""),
+                             tuple(map(tuple, p.get("candidates", ()))), p.get("gold", -1)))
+    cells = sorted(stored, key=lambda c: (str(type(c[0])), c)) if stored is not None else [(int(x), k) for x in a.lengths.split(",") for k in probes.PROBE_KINDS]
     for length, kind in cells:
         ps = stored[(length, kind)] if stored is not None else [
             probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
@@ -57,11 +59,13 @@ def main(argv=None) -> int:
         if kind.startswith("mf_"):
             for key in ("fact_acc", "first_ok", "nats", "exact_all"):
                 cell[key] = sum(float(it[key]) for it in r["items"]) / len(r["items"])
+        if any("choice_ok" in it for it in r["items"]):
+            cell["choice_acc"] = sum(float(it.get("choice_ok", 0.0)) for it in r["items"]) / len(r["items"])
         if kind == "transcode":
             floors = [probes.copy_floor(q) for q in ps]
             cell["copy_floor"] = {k: sum(float(f[k]) for f in floors) / len(floors) for k in ("token_acc", "lcs_share")}
         table[f"{kind}@{length}"] = cell
-        print(f"{kind:9s} length {length:6d}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
+        print(f"{kind:11s} {('length ' + str(length)) if isinstance(length, int) else length}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
     if a.out:
         with open(a.out, "w") as f:
             json.dump({"step": step, "probes": table}, f, indent=1)

@@ -1,0 +1,168 @@
+"""Text-level probe generators: determinism, lengths, the facts in place, the stored form and its checks, the build script."""
+
+import gzip
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from gdn_hybrid_architecture_ideas_b200.eval import probe_text as T
+
+ROOT = Path(__file__).resolve().parent.parent
+WORDS = "the of and a to in is that it was for on are as with his they at be this from have or by one had not but what all were when we there can an your which their said if do will each about how up out them then she many some so these would other into has more her two like him see time could no make than first been its who now people my made over did down only way find use may water long little very after words called just where most know".split()
+
+
+def docs(n=60, seed=0):
+    rng = np.random.default_rng(seed)
+    out = []
+    for _ in range(n):
+        sents = []
+        for _ in range(int(rng.integers(30, 60))):
+            w = [WORDS[i] for i in rng.integers(len(WORDS), size=int(rng.integers(6, 16)))]
+            sents.append(" ".join(w).capitalize() + ".")
+        out.append(" ".join(sents))
+    return out
+
+
+COUNT = lambda text: len(text.encode("utf-8")) // 4          # a stand-in length measure: four bytes per token
+
+
+@pytest.fixture(scope="module")
+def pool():
+    return T.DocPool(docs())
+
+
+def test_a_needle_item_has_its_length_its_sentence_at_the_depth_and_is_reproducible(pool):
+    a = T.uuid_needle(pool, COUNT, 2048, 0.3, 5)
+    b = T.uuid_needle(pool, COUNT, 2048, 0.3, 5)
+    assert a.to_json() == b.to_json()
+    assert T.uuid_needle(pool, COUNT, 2048, 0.3, 6).answer != a.answer
+    n = COUNT(a.context + a.answer)
+    assert (1 - T.LENGTH_SLACK) * 2048 <= n <= 2048
+    name, value = a.meta["name"], a.answer.strip()
+    assert a.context.count(T.needle_sentence(name, value)) == 1 and a.context.endswith(T.needle_question(name))
+    at = a.context.index(value) / len(a.context)
+    assert abs(at - 0.3) < 0.08
+    assert T.question_text(a) == T.needle_question(name)
+    assert T.TextItem.from_json(json.loads(json.dumps(a.to_json()))).to_json() == a.to_json()
+
+
+def test_multikey_asks_one_of_n_distinct_needles(pool):
+    it = T.multikey(pool, COUNT, 2048, 4, 1)
+    sentences = [m for m in it.context.split(". ") if "The access code for" in m and "What is" not in m]
+    assert len(sentences) >= 4 and it.context.count(it.answer.strip()) == 1
+    assert len(it.meta["needle_offsets"]) == 4 and 0 <= it.meta["asked"] < 4
+
+
+def test_needle_at_a_token_distance(pool):
+    it = T.needle_at_distance(pool, COUNT, 4096, 1024, 2, tol=96)
+    at = it.context.rfind(it.answer.strip())
+    assert abs(COUNT(it.context[at:]) - 1024) <= 96 and it.cell["distance"] == 1024
+    same = T.needle_at_distance(pool, COUNT, 4096, 2048, 2, tol=96)
+    assert same.answer == it.answer and same.meta["name"] == it.meta["name"]          # the item keeps its name and value at every distance
+
+
+def test_path_copy_grids():
+    one = T.path_copy(8, (8, 1, 1), "deep", 3)
+    lines = [ln for ln in one.context.splitlines() if " -> " in ln]
+    paths = [ln.split(" -> ")[1] for ln in lines]
+    assert len(paths) == 8 and len(set(paths)) == 8 and one.answer.strip() in paths and one.context.endswith(f"class {one.meta['name']} ->")
+    parts = [p.split("/") for p in paths]
+    differing = [i for i in range(len(parts[0])) if len({p[i] for p in parts}) > 1]
+    assert len(differing) == 1                                           # one directory decides the path
+    near = T.path_copy(12, (2, 3, 4), "shallow", 0)
+    assert len({ln.split(" -> ")[1] for ln in near.context.splitlines() if " -> " in ln}) == 12
+    with pytest.raises(ValueError):
+        T.path_copy(12, (2, 2, 2), "deep", 0)
+
+
+@pytest.mark.parametrize("hops", [0, 3, 8])
+def test_depth_items_execute_to_their_answer_and_balance_the_rank(hops):
+    ranks = set()
+    for i in range(6):
+        it = T.depth(hops, i)
+        scope = {}
+        exec(it.context + it.answer + "\nmain()", scope)                  # the program is valid Python and its assert holds
+        wrong = next(c for c in it.candidates if c != it.answer)
+        with pytest.raises(AssertionError):
+            exec(it.context + wrong + "\nmain()", {})
+        assert it.candidates[it.gold] == it.answer and len(set(it.meta["assigned"])) == T.CHAINS
+        literal_lines = [ln.strip() for ln in it.context.splitlines() if ln.strip()[-1:].isdigit() and " = " in ln]
+        asked_first = next(k for k, ln in enumerate(literal_lines) if ln.endswith(f"= {it.answer}"))
+        assert asked_first == it.meta["rank"] == i % T.CHAINS
+        ranks.add(asked_first)
+    assert ranks == set(range(T.CHAINS))
+
+
+@pytest.mark.parametrize("probe", ["mf_chain", "mf_concat"])
+def test_multifact_answers_need_every_fact(pool, probe):
+    it = T.multifact(probe, pool, COUNT, 4096, 4, 1)
+    pieces = it.meta["pieces"]
+    assert "".join(p for p, _ in pieces) == it.answer and sum(1 for _, f in pieces if f) == 4
+    for text, is_fact in pieces:
+        if is_fact:
+            assert it.context.count(text.strip()) >= 1
+    assert it.group["layout"] == T.LAYOUTS[1]
+    offs = it.meta["fact_offsets"]
+    lo, hi = T.LAYOUT_SPAN["front"]
+    assert all(lo - 0.05 <= o <= hi + 0.1 for o in offs), offs
+    if probe == "mf_chain":
+        names = [p.strip() for p, f in pieces if f]
+        assert all(f"is {n}." in it.context for n in names)
+
+
+def test_stored_form_and_checks(pool):
+    enc = lambda s: list(s.encode("utf-8"))
+    rec = T.encode_item(T.uuid_needle(pool, COUNT, 1024, 0.5, 0), enc)
+    assert rec["ids"][rec["answer_start"]:] == enc(" " + bytes(rec["ids"][rec["answer_start"] + 1:]).decode()) and rec["checks"] == {"clean_boundary": True, "answer_once": True}
+    assert rec["question_tokens"] > 10 and rec["kind"] == "uuid_needle" and rec["cell"] == "length=1024"
+    d = T.encode_item(T.depth(2, 0), enc)
+    assert d["checks"]["single_token_candidates"] and d["candidates"][d["gold"]] == d["ids"][d["answer_start"]:]
+    mf = T.encode_item(T.multifact("mf_concat", pool, COUNT, 2048, 2, 0), enc)
+    assert mf["checks"]["pieces_add_up"] and [f for _, f in mf["pieces"]] == [True, False, True]
+
+
+def test_build_script_writes_text_sets_and_manifests(tmp_path):
+    src = tmp_path / "docs.jsonl.gz"
+    with gzip.open(src, "wt") as f:
+        for i, d in enumerate(docs(40, seed=3)):
+            f.write(json.dumps({"id": i, "text": d}) + "\n")
+    out = tmp_path / "set"
+    r = subprocess.run([sys.executable, str(ROOT / "scripts/build_text_probes.py"), "--out", str(out), "--tokenizer", "bytes=bytes", "--docs", str(src),
+                        "--probes", "uuid_needle,depth,mf_chain", "--lengths", "4096", "--per-cell", "1"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    manifest = json.loads((out / "manifest.json").read_text())
+    assert manifest["failed_checks"] == 0 and manifest["probes"] == {"uuid_needle": 5, "depth": 9, "mf_chain": 3}
+    stored = torch.load(out / "bytes" / "uuid_needle.pt", weights_only=False)
+    assert len(stored["probes"]) == 5 and all(3900 <= p["length"] <= 4096 for p in stored["probes"])
+    with gzip.open(out / "text" / "depth.jsonl.gz", "rt") as f:
+        assert len([T.TextItem.from_json(json.loads(x)) for x in f]) == 9
+
+
+def test_text_sets_are_scored_by_the_probe_scorer(tmp_path):
+    """A stored text-level set goes through scripts/eval_probes.py: cells by name, exact match, the ten-way choice of depth."""
+    from gdn_hybrid_architecture_ideas_b200 import config as C
+    from gdn_hybrid_architecture_ideas_b200.train.trainer import Trainer
+
+    model = C.tiny_full_config()
+    model.vocab_size = 256
+    cfg = C.TrainConfig(model=model, data=C.tiny_data_config())
+    cfg.steps, cfg.log_every, cfg.metrics_jsonl, cfg.device = 1, 0, False, "cpu"
+    Trainer(cfg, tmp_path / "run").fit()
+    out = tmp_path / "set"
+    r = subprocess.run([sys.executable, str(ROOT / "scripts/build_text_probes.py"), "--out", str(out), "--tokenizer", "bytes=bytes",
+                        "--probes", "path_copy,depth", "--per-cell", "1"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    for probe, cells in (("depth", len(T.HOPS)), ("path_copy", 2 * len(T.PATH_CELLS))):
+        res = tmp_path / f"{probe}.json"
+        r = subprocess.run([sys.executable, str(ROOT / "scripts/eval_probes.py"), "--checkpoint", str(tmp_path / "run"), "--set", str(out / "bytes" / f"{probe}.pt"),
+                            "--device", "cpu", "--batch-size", "2", "--out", str(res)], capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        table = json.loads(res.read_text())["probes"]
+        assert len(table) == cells and all(0.0 <= c["exact"] <= 1.0 and c["n"] == 1 for c in table.values())
+        if probe == "depth":
+            assert all("choice_acc" in c for c in table.values()) and "hops=3@depth" not in table and any(k.startswith("depth@hops=") for k in table)
