@@ -1,7 +1,7 @@
 """Text-level probe items: a context string and the continuation a model has to produce, built from held-out documents.
 
 `eval/probes.py` builds its probes on token ids of any vocabulary; the items here are TEXT, so one set can be tokenized
-for several tokenizers and read by people. Six probes:
+for several tokenizers and read by people. Seven probes:
 
   uuid_needle   a haystack of held-out documents of total length T with one sentence "The access code for <name> is
                 <uuid>." placed at the sentence start nearest a depth fraction; the question repeats the form and the
@@ -18,6 +18,8 @@ for several tokenizers and read by people. Six probes:
                 chain out, so every fact has to be retrieved.
   mf_concat     k sentences "The access code for Ni is Ci." and a question listing the names in another order; the
                 answer gives the codes in the question's order.
+  twohop        a link fact and a value fact per chain; the question asks for the value behind the link without naming
+                the bridge, with matched controls (one hop, the link alone, a link to nowhere, links moved one chain on).
 
 An item is a pure function of (seed, probe, cell, index), the document pool and the length measure `count` (a callable
 from text to a token count: the build script passes the largest count over its tokenizers, the tests a byte count).
@@ -56,7 +58,7 @@ LAYOUTS = ("spread", "front", "back")
 LAYOUT_SPAN = {"spread": (0.0, 1.0), "front": (0.05, 0.30), "back": (0.70, 0.95)}
 LENGTH_SLACK = 0.03          # an item's total length lies in [(1 - slack) T, T]
 JOIN = "\n\n"
-PROBES = ("uuid_needle", "multikey", "path_copy", "depth", "mf_chain", "mf_concat")
+PROBES = ("uuid_needle", "multikey", "path_copy", "depth", "mf_chain", "mf_concat", "twohop")
 _CODE = {p: i for i, p in enumerate(PROBES)}
 
 
@@ -433,6 +435,119 @@ def multifact(probe: str, pool: DocPool, count, length: int, k: int, index: int,
     return TextItem(f"{probe}/len={length}/k={k}/{index:04d}", probe, {"length": length, "k": k}, context, answer, group={"layout": layout}, meta=info)
 
 
+# ----------------------------------------------------------------------------------------------------------------- two-hop
+# A latent two-hop lookup: the answer is reached only by reading one fact (the link, "The supervisor of <head> is
+# <bridge>.") and using what it says as the key of a second one (the value, "The access code for <bridge> is <code>.");
+# nothing is written between the question and the answer, so the first hop stays unwritten (mf_chain writes it out).
+# D + 1 chains of that form are planted; chain 0 is asked. One base item gives five scored variants:
+#   twohop    "What is the access code for the supervisor of <head>? ..." -> " <code>"
+#   onehop    the value fact asked directly by its key (what the same answer costs without a hop)
+#   link      the link fact alone -> " <bridge>"
+#   shuffled  the two-hop question on a context whose asked link names a stranger with no code: the ceiling of guessing
+#   swapped   every link moved one chain on: each fact where it stood, every bridge still named twice, so whatever does
+#             not read the asked link scores as on twohop and a model that follows it gives another chain's code.
+#             twohop - swapped is the share of answers that follow the link.
+# Cell: length, gap between a chain's two facts ("adjacent", "near": about NEAR_TOKENS apart, "far": half the haystack),
+# distractor chains D, value "word" (one common word: the hop has to happen inside one token) or "uuid" (letter-first).
+# Group: the order of the two facts in the text, "AB" or "BA". Order and the asked chain's rank among the chains cycle
+# with the item index, so "the first code" is right 1 / (D + 1) of the time. Reference: ced/eval/probe_gen_twohop.py.
+TWOHOP_VARIANTS = ("twohop", "onehop", "link", "shuffled", "swapped")
+GAPS = ("adjacent", "near", "far")
+NEAR_TOKENS = 256
+CODE_WORDS = ("anchor bridge candle dragon engine forest garden hammer island jacket kitchen ladder marble needle orange pencil quartz "
+              "ribbon saddle tunnel umbrella velvet window yellow zipper").split()          # distinct first letters
+
+
+def _letter_uuid(rng, first: str) -> str:
+    u = fresh_uuid(rng)
+    return first + u[1:]
+
+
+def twohop(pool: DocPool, count, length: int, gap: str, distractors: int, value: str, index: int, seed: int = SEED) -> list[TextItem]:
+    """The five variants of base item `index` of the cell (same haystack, names, codes and places)."""
+    if gap not in GAPS or value not in ("word", "uuid") or distractors < 1:
+        raise ValueError(f"two-hop cell gap {gap!r} of {GAPS}, value {value!r} of ('word', 'uuid'), distractors {distractors} >= 1")
+    n = distractors + 1
+    cell = (length, GAPS.index(gap), distractors, value == "uuid")
+    content, hay_rng = stream("twohop", cell, index, 0, seed), stream("twohop", cell, index, 1, seed)
+    order = "AB" if index % 2 == 0 else "BA"
+    rank = (index // 2) % n                                   # the asked chain's place among the chains, in text order
+    candidates = full_names(content, 8 * n + 16)
+    if value == "word":
+        codes = [CODE_WORDS[i] for i in content.choice(len(CODE_WORDS), size=n, replace=False)]
+    else:
+        codes = [_letter_uuid(content, "abcdef"[i]) for i in content.choice(6, size=n, replace=False)]
+    span = 0.45 if gap == "far" else 0.9
+    slots = [0.04 + span * (i + 0.5) / n for i in range(n)]    # anchors of the chains, in text order
+    others = [int(i) for i in content.permutation(n - 1) + 1]
+    at = others[:rank] + [0] + others[rank:]                    # at[j]: which chain sits at slot j
+    slot_of = {c: j for j, c in enumerate(at)}
+    state = {}
+
+    def sentences(heads, bridges, linked):
+        """linked[c]: the name chain c's link fact gives."""
+        link = [f"The supervisor of {heads[c]} is {linked[c]}." for c in range(n)]
+        val = [f"The access code for {bridges[c]} is {codes[c]}." for c in range(n)]
+        return link, val
+
+    def render(hay, heads, bridges, linked, question):
+        link, val = sentences(heads, bridges, linked)
+        per_tok = len(hay) / max(count(hay), 1)
+        shift = {"adjacent": 0.0, "near": NEAR_TOKENS * per_tok / max(len(hay), 1), "far": 0.5}[gap]
+        planted = []
+        for c in range(n):
+            first, second = (link[c], val[c]) if order == "AB" else (val[c], link[c])
+            f = slots[slot_of[c]]
+            if gap == "adjacent":
+                planted.append((f, first + " " + second))
+            else:
+                planted += [(f, first), (min(f + shift, 0.98), second)]
+        body, _ = plant(hay, planted)
+        return body + JOIN + question
+
+    def finish(hay: str):
+        names = unseen_names(candidates, hay, 2 * n + 1)
+        heads, bridges, stranger = names[:n], names[n:2 * n], names[2 * n]
+        state.update(hay=hay, heads=heads, bridges=bridges, stranger=stranger)
+        q = f"What is the access code for the supervisor of {heads[0]}? The access code for the supervisor of {heads[0]} is"
+        return render(hay, heads, bridges, bridges, q), " " + codes[0]
+
+    _, _, info = haystack_to_length(pool, hay_rng, length, count, finish)
+    hay, heads, bridges, stranger = state["hay"], state["heads"], state["bridges"], state["stranger"]
+    two = f"What is the access code for the supervisor of {heads[0]}? The access code for the supervisor of {heads[0]} is"
+    one = f"What is the access code for {bridges[0]}? The access code for {bridges[0]} is"
+    lnk = f"Who is the supervisor of {heads[0]}? The supervisor of {heads[0]} is"
+    moved = [bridges[(c + 1) % n] for c in range(n)]
+    forms = {
+        "twohop": (bridges, two, " " + codes[0]),
+        "onehop": (bridges, one, " " + codes[0]),
+        "link": (bridges, lnk, " " + bridges[0]),
+        "shuffled": ([stranger] + bridges[1:], two, " " + codes[0]),
+        "swapped": (moved, two, " " + codes[0]),
+    }
+    out = []
+    for variant, (linked, question, answer) in forms.items():
+        context = render(hay, heads, bridges, linked, question)
+        meta = dict(info, codes=codes, rank=rank, head=heads[0], bridge=bridges[0], question_chars=len(question),
+                    followed=" " + codes[1 % n] if variant == "swapped" else None)
+        out.append(TextItem(f"twohop/len={length}/gap={gap}/d={distractors}/{value}/{variant}/{index:04d}", "twohop",
+                            {"length": length, "gap": gap, "distractors": distractors, "value": value, "variant": variant},
+                            context, answer, group={"order": order}, meta=meta))
+    return out
+
+
+def twohop_summary(scores: dict[str, list[float]]) -> dict:
+    """From per-variant lists of exact-match scores over the SAME base items (paired): the means, the share of answers
+    that follow the link (twohop - swapped) and what the hop costs (onehop - twohop)."""
+    mean = {v: sum(x) / max(len(x), 1) for v, x in scores.items()}
+    out = dict(mean)
+    if "twohop" in mean and "swapped" in mean:
+        out["follows_link"] = mean["twohop"] - mean["swapped"]
+    if "twohop" in mean and "onehop" in mean:
+        out["hop_cost"] = mean["onehop"] - mean["twohop"]
+    return out
+
+
 def question_text(item: TextItem) -> str:
     """The question of a needle or multi-fact item: the context from the question's first word to its end."""
     n = item.meta.get("question_chars")
@@ -465,6 +580,13 @@ def build_cells(probe: str, per_cell: int, pool: DocPool | None = None, count=No
         for T in lengths:
             for k in FACT_COUNTS:
                 out += [multifact(probe, pool, count, T, k, i, seed) for i in range(per_cell)]
+    elif probe == "twohop":
+        for T in lengths:
+            for gap in GAPS:
+                for d in (1, 3):
+                    for value in ("word", "uuid"):
+                        for i in range(per_cell):
+                            out += twohop(pool, count, T, gap, d, value, i, seed)
     else:
         raise ValueError(f"unknown probe {probe!r}: one of {PROBES}")
     return out
@@ -491,6 +613,9 @@ def encode_item(item: TextItem, encode: Callable[[str], list[int]]) -> dict:
            "checks": {"clean_boundary": clean_boundary(encode, item.context, item.answer)}}
     if item.probe in ("uuid_needle", "multikey", "path_copy"):
         rec["checks"]["answer_once"] = occurrences(ctx, ans) == 1
+    if item.probe == "twohop" and "codes" in item.meta:      # the first answer token decides: the codes start with different tokens
+        firsts = [encode(" " + c)[0] for c in item.meta["codes"]]
+        rec["checks"]["distinct_first_tokens"] = len(set(firsts)) == len(firsts)
     if item.candidates is not None:
         cands = [encode(c) for c in item.candidates]
         rec.update(candidates=cands, gold=item.gold)

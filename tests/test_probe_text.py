@@ -166,3 +166,28 @@ def test_text_sets_are_scored_by_the_probe_scorer(tmp_path):
         assert len(table) == cells and all(0.0 <= c["exact"] <= 1.0 and c["n"] == 1 for c in table.values())
         if probe == "depth":
             assert all("choice_acc" in c for c in table.values()) and "hops=3@depth" not in table and any(k.startswith("depth@hops=") for k in table)
+
+
+def test_twohop_variants_share_a_haystack_and_differ_in_their_links(pool):
+    items = {it.cell["variant"]: it for it in T.twohop(pool, COUNT, 4096, "near", 3, "word", 2)}
+    assert set(items) == set(T.TWOHOP_VARIANTS)
+    two, one, link, shuf, swap = (items[v] for v in T.TWOHOP_VARIANTS)
+    head, bridge, code = two.meta["head"], two.meta["bridge"], two.answer.strip()
+    assert bridge not in two.context.split(T.JOIN)[-1] and one.answer == two.answer == shuf.answer == swap.answer and link.answer.strip() == bridge
+    assert f"The supervisor of {head} is {bridge}." in two.context and f"The access code for {bridge} is {code}." in two.context
+    assert f"The supervisor of {head} is {bridge}." not in shuf.context and f"The access code for {bridge} is {code}." in shuf.context
+    assert f"The supervisor of {head} is {bridge}." not in swap.context and swap.context.count(f"is {bridge}.") == 1      # another head now names this bridge
+    codes = two.meta["codes"]
+    assert len({c[0] for c in codes}) == 4 and swap.meta["followed"].strip() == codes[1]
+    body = lambda it: it.context.rsplit(T.JOIN, 1)[0]
+    strip = lambda t: [ln for ln in t.split(". ") if "supervisor of" not in ln]
+    assert strip(body(two)) == strip(body(swap)) == strip(body(shuf))               # only link sentences differ between the variants
+    ranks = set()
+    for i in range(8):
+        it = T.twohop(pool, COUNT, 2048, "adjacent", 3, "uuid", i)[0]
+        order_in_text = sorted(it.meta["codes"], key=lambda c: it.context.index(c))
+        ranks.add((order_in_text.index(it.meta["codes"][0]), it.group["order"]))
+        assert it.meta["codes"][0][0] in "abcdef"
+    assert ranks == {(r, o) for r in range(4) for o in ("AB", "BA")}
+    s = T.twohop_summary({"twohop": [1, 1, 0, 1], "swapped": [0, 0, 0, 1], "onehop": [1, 1, 1, 1]})
+    assert s["follows_link"] == 0.5 and s["hop_cost"] == 0.25
