@@ -35,7 +35,7 @@ from .optim import build_optimizer, grad_norm
 EXIT_DIVERGED = 86
 
 
-from . import bpb_readout, monitor, periodic_eval
+from . import bpb_readout, monitor, periodic_eval, readout
 
 
 class Diverged(RuntimeError):
@@ -156,6 +156,8 @@ class Trainer:
 
             self.zero_wgrad = ZeroWgradMonitor(self.model)
         self._readout = None
+        readout.check_readout_config(cfg)
+        self._probe_readout = readout.Readout(self) if cfg.eval.readout_every else None      # the sample is read (and checked) before the run trains
         self.prefetch = None
         if cfg.data_prefetch:
             from ..data.prefetch import BatchPrefetcher
@@ -439,7 +441,11 @@ class Trainer:
                         self._readout = bpb_readout.BpbReadout(self)
                     scores = self._readout.run()
                     if self.lead and scores:
-                        self._jsonl({"event": "readout", "step": self.step, **scores})
+                        self._jsonl({"event": "bpb_readout", "step": self.step, **scores})
+                if self._probe_readout is not None and readout.readout_due(cfg, self.step, end):
+                    record = self._probe_readout.run(self)
+                    if record is not None:
+                        self._jsonl(record)
                 if periodic_eval.due(cfg, self.step):
                     scores = periodic_eval.run_eval_sets(self)
                     if self.lead:

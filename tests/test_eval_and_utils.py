@@ -389,7 +389,7 @@ def test_bpb_readout_uses_fixed_rows(tmp_path):
     assert a == b and a["readout/held/bpb"] > 0 and len(r.sets["held"].chosen) == 3
     t.fit()
     lines = [json.loads(x) for x in (tmp_path / "r" / "metrics.jsonl").read_text().splitlines()]
-    assert sum(1 for x in lines if x.get("event") == "readout") == 2
+    assert sum(1 for x in lines if x.get("event") == "bpb_readout") == 2
 
 
 def test_routed_swiglu_dispatch_equals_dense():
