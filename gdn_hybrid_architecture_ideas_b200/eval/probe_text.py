@@ -1,7 +1,7 @@
 """Text-level probe items: a context string and the continuation a model has to produce, built from held-out documents.
 
 `eval/probes.py` builds its probes on token ids of any vocabulary; the items here are TEXT, so one set can be tokenized
-for several tokenizers and read by people. Seven probes:
+for several tokenizers and read by people. Eight probes:
 
   uuid_needle   a haystack of held-out documents of total length T with one sentence "The access code for <name> is
                 <uuid>." placed at the sentence start nearest a depth fraction; the question repeats the form and the
@@ -18,6 +18,8 @@ for several tokenizers and read by people. Seven probes:
                 chain out, so every fact has to be retrieved.
   mf_concat     k sentences "The access code for Ni is Ci." and a question listing the names in another order; the
                 answer gives the codes in the question's order.
+  vt            variable tracking: two chains of assignments "VAR <B> = VAR <A>." scattered over the haystack; the answer lists
+                the variables that hold one chain's number, in order.
   twohop        a link fact and a value fact per chain; the question asks for the value behind the link without naming
                 the bridge, with matched controls (one hop, the link alone, a link to nowhere, links moved one chain on).
 
@@ -58,7 +60,7 @@ LAYOUTS = ("spread", "front", "back")
 LAYOUT_SPAN = {"spread": (0.0, 1.0), "front": (0.05, 0.30), "back": (0.70, 0.95)}
 LENGTH_SLACK = 0.03          # an item's total length lies in [(1 - slack) T, T]
 JOIN = "\n\n"
-PROBES = ("uuid_needle", "multikey", "path_copy", "depth", "mf_chain", "mf_concat", "twohop")
+PROBES = ("uuid_needle", "multikey", "path_copy", "depth", "mf_chain", "mf_concat", "twohop", "vt")
 _CODE = {p: i for i, p in enumerate(PROBES)}
 
 
@@ -435,6 +437,54 @@ def multifact(probe: str, pool: DocPool, count, length: int, k: int, index: int,
     return TextItem(f"{probe}/len={length}/k={k}/{index:04d}", probe, {"length": length, "k": k}, context, answer, group={"layout": layout}, meta=info)
 
 
+# -------------------------------------------------------------------------------------------------------- variable tracking
+# Two chains of VT_HOPS + 1 variables assigned at random places of the haystack, each chain's statements in order:
+# "VAR <A> = <number>." then "VAR <B> = VAR <A>." and so on; the chains hold different 5-digit numbers and the variables
+# are random 5-letter upper-case names absent from the haystack. The question asks which variables hold one chain's
+# number; the answer lists them in the chain's order. Copying every VAR name in order gives eight names, not four: the
+# second chain is what makes it tracking. Cell: length. Reference: ced/eval/report_pcr_gen.py (pcr_vt; RULER's VT).
+VT_HOPS, VT_CHAINS = 3, 2
+
+
+def _var_names(rng, n: int, text: str) -> list[str]:
+    out = []
+    while len(out) < n:
+        name = "".join(chr(65 + int(i)) for i in rng.integers(26, size=5))
+        if name not in text and name not in out:
+            out.append(name)
+    return out
+
+
+def var_track(pool: DocPool, count, length: int, index: int, seed: int = SEED) -> TextItem:
+    content, hay_rng = stream("vt", (length,), index, 0, seed), stream("vt", (length,), index, 1, seed)
+    numbers = [str(int(x)) for x in content.choice(90000, size=VT_CHAINS, replace=False) + 10000]
+    per = VT_HOPS + 1
+    fractions = sorted(float(x) for x in content.uniform(0.03, 0.97, size=VT_CHAINS * per))
+    owner = [c for c in range(VT_CHAINS) for _ in range(per)]
+    content.shuffle(owner)                                     # which chain each place belongs to; a chain fills its places in order
+    name_seed = int(content.integers(1 << 31))
+    state = {}
+
+    def finish(hay: str):
+        names = _var_names(np.random.default_rng(name_seed), VT_CHAINS * per, hay)       # the same candidates at every trial length
+        chains = [names[c * per:(c + 1) * per] for c in range(VT_CHAINS)]
+        step = [0] * VT_CHAINS
+        planted = []
+        for f, c in zip(fractions, owner):
+            j = step[c]
+            step[c] += 1
+            rhs = numbers[c] if j == 0 else f"VAR {chains[c][j - 1]}"
+            planted.append((f, f"VAR {chains[c][j]} = {rhs}."))
+        body, _ = plant(hay, planted)
+        q = f"Question: Which variables are assigned the value {numbers[0]}? Answer: The variables assigned the value {numbers[0]} are:"
+        state.update(chains=chains, question=q)
+        return body + JOIN + q, " " + " ".join(chains[0])
+
+    context, answer, info = haystack_to_length(pool, hay_rng, length, count, finish)
+    info.update(chains=state["chains"], numbers=numbers, question_chars=len(state["question"]))
+    return TextItem(f"vt/len={length}/{index:04d}", "vt", {"length": length}, context, answer, meta=info)
+
+
 # ----------------------------------------------------------------------------------------------------------------- two-hop
 # A latent two-hop lookup: the answer is reached only by reading one fact (the link, "The supervisor of <head> is
 # <bridge>.") and using what it says as the key of a second one (the value, "The access code for <bridge> is <code>.");
@@ -580,6 +630,9 @@ def build_cells(probe: str, per_cell: int, pool: DocPool | None = None, count=No
         for T in lengths:
             for k in FACT_COUNTS:
                 out += [multifact(probe, pool, count, T, k, i, seed) for i in range(per_cell)]
+    elif probe == "vt":
+        for T in lengths:
+            out += [var_track(pool, count, T, i, seed) for i in range(per_cell)]
     elif probe == "twohop":
         for T in lengths:
             for gap in GAPS:

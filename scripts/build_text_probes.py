@@ -11,6 +11,10 @@ Writes
     <out>/<tok>/manifest.json        counts, token lengths per cell, failed per-item checks, sha256 of the files
     <out>/manifest.json              seed, probes, length measure, the document pool, sha256 of everything written
 
+`--preset pcr`: the retrieval-inside-the-training-length set: uuid_needle, multikey and vt at 2,048 / 4,096 / 8,192 tokens,
+plus the copy-loss sequences of `eval/report_pcr.py` (pcr_copy2, pcr_copy3, pcr_fresh: random token sequences repeated, so
+they are written per tokenizer only) at --copy-lengths, --copy-per-length items each.
+
 `--docs`: JSON lines {"id", "text"} (gzip or plain) of documents that are in no training shard. An item's length is the
 largest of its token counts under the tokenizers given, so an item of nominal length T has at most T tokens under each.
 Per-item checks under every tokenizer (counted in the manifest; the build fails on a miss unless --allow-misses): context
@@ -75,7 +79,12 @@ def main(argv=None) -> int:
     ap.add_argument("--distance-keys", type=int, default=4)
     ap.add_argument("--distance-tol", type=int, default=64)
     ap.add_argument("--allow-misses", action="store_true")
+    ap.add_argument("--preset", choices=["pcr"])
+    ap.add_argument("--copy-lengths", default="64,256,1024")
+    ap.add_argument("--copy-per-length", type=int, default=32)
     a = ap.parse_args(argv)
+    if a.preset == "pcr":
+        a.probes, a.lengths = "uuid_needle,multikey,vt", "2048,4096,8192"
     toks = {}
     for spec in a.tokenizer:
         name, _, path = spec.partition("=")
@@ -122,6 +131,24 @@ def main(argv=None) -> int:
             misses += sum(failed.values())
             summary[probe][name] = {"cells": {c: {"items": len(v), "min_tokens": min(v), "max_tokens": max(v)} for c, v in sorted(per_cell.items())},
                                     "failed_checks": dict(failed)}
+    if a.preset == "pcr":
+        from gdn_hybrid_architecture_ideas_b200.eval import report_pcr as PCR
+
+        for name, tok in toks.items():
+            allowed = PCR.allowed_ids(tok.vocab_size, [tok.eos_id] if getattr(tok, "eos_id", None) is not None else [])
+            for variant in PCR.COPY_VARIANTS:
+                recs = []
+                for n in (int(x) for x in a.copy_lengths.split(",")):
+                    for i in range(a.copy_per_length):
+                        ids, first = PCR.copy_item(allowed, variant, n, i)
+                        recs.append({"id": PCR.copy_item_id(variant, n, i), "kind": variant, "cell": f"n={n}", "group": "", "ids": ids.tolist(),
+                                     "answer_start": int(first), "answer_len": len(ids) - int(first), "length": len(ids), "pieces": (), "checks": {}})
+                (out / name).mkdir(exist_ok=True)
+                path = out / name / f"{variant}.pt"
+                torch.save({"probes": recs, "vocab": tok.vocab_size, "seed": PCR.COPY_SEED, "tokenizer": getattr(tok, "name", name)}, path)
+                files[str(path.relative_to(out))] = sha256(path)
+                summary.setdefault(variant, {"items": len(recs)})[name] = {"cells": {}, "failed_checks": {}}
+        probes = probes + list(PCR.COPY_VARIANTS)
     for name in toks:
         (out / name / "manifest.json").write_text(json.dumps({p: summary[p][name] for p in probes} | {"sha256": {k: v for k, v in files.items() if k.startswith(name + "/")}}, indent=1))
     (out / "manifest.json").write_text(json.dumps({"seed": a.seed, "probes": {p: summary[p]["items"] for p in probes}, "lengths": lengths,

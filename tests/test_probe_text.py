@@ -191,3 +191,28 @@ def test_twohop_variants_share_a_haystack_and_differ_in_their_links(pool):
     assert ranks == {(r, o) for r in range(4) for o in ("AB", "BA")}
     s = T.twohop_summary({"twohop": [1, 1, 0, 1], "swapped": [0, 0, 0, 1], "onehop": [1, 1, 1, 1]})
     assert s["follows_link"] == 0.5 and s["hop_cost"] == 0.25
+
+
+def test_variable_tracking_has_two_chains_and_asks_for_one(pool):
+    it = T.var_track(pool, COUNT, 2048, 3)
+    asked, other = it.meta["chains"]
+    assert it.answer == " " + " ".join(asked) and len(asked) == len(other) == T.VT_HOPS + 1
+    stmts = [m for m in it.context.split(". ") if m.startswith("VAR ") or " VAR " in m[:12]]
+    text = it.context
+    assert text.index(f"VAR {asked[0]} = {it.meta['numbers'][0]}.") < text.index(f"VAR {asked[1]} = VAR {asked[0]}.") < text.index(f"VAR {asked[3]} = VAR {asked[2]}.")
+    assert f"VAR {other[0]} = {it.meta['numbers'][1]}." in text and it.meta["numbers"][0] != it.meta["numbers"][1]
+    assert text.count("VAR ") >= 2 * (T.VT_HOPS + 1) and (1 - T.LENGTH_SLACK) * 2048 <= COUNT(text + it.answer) <= 2048
+    assert T.var_track(pool, COUNT, 2048, 3).to_json() == it.to_json()
+
+
+def test_pcr_preset_writes_retrieval_and_copy_sets(tmp_path):
+    src = tmp_path / "docs.jsonl"
+    src.write_text("".join(json.dumps({"id": i, "text": d}) + "\n" for i, d in enumerate(docs(40, seed=4))))
+    out = tmp_path / "pcr"
+    r = subprocess.run([sys.executable, str(ROOT / "scripts/build_text_probes.py"), "--out", str(out), "--tokenizer", "bytes=bytes", "--docs", str(src),
+                        "--preset", "pcr", "--per-cell", "1", "--copy-lengths", "16,32", "--copy-per-length", "2"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    m = json.loads((out / "manifest.json").read_text())
+    assert m["probes"]["uuid_needle"] == 15 and m["probes"]["multikey"] == 6 and m["probes"]["vt"] == 3 and m["probes"]["pcr_copy3"] == 4
+    copy2 = torch.load(out / "bytes" / "pcr_copy2.pt", weights_only=False)["probes"]
+    assert copy2[0]["ids"][:16] == copy2[0]["ids"][16:32] and copy2[0]["answer_start"] == 16 and copy2[0]["cell"] == "n=16"
