@@ -41,6 +41,14 @@ from gdn_hybrid_architecture_ideas_b200.data.tokenizers import open_tokenizer  #
 from gdn_hybrid_architecture_ideas_b200.eval import probe_text as T  # noqa: E402
 
 
+def gz_text_writer(path: Path):
+    """A gzip text stream whose bytes depend on the content alone (no file name, no modification time in the header)."""
+    import io
+
+    raw = open(path, "wb")
+    return io.TextIOWrapper(gzip.GzipFile(filename="", mode="wb", fileobj=raw, mtime=0), encoding="utf-8")
+
+
 def sha256(path: Path) -> str:
     h = hashlib.sha256()
     with open(path, "rb") as f:
@@ -112,7 +120,7 @@ def main(argv=None) -> int:
                         if dist + 512 <= (1 - T.LENGTH_SLACK) * length:
                             items.append(T.needle_at_distance(pool, count, length, dist, i, keys, a.distance_tol, a.seed))
         text_path = out / "text" / f"{probe}.jsonl.gz"
-        with gzip.open(text_path, "wt", encoding="utf-8") as f:
+        with gz_text_writer(text_path) as f:
             for it in items:
                 f.write(json.dumps(it.to_json(), ensure_ascii=False) + "\n")
         files[str(text_path.relative_to(out))] = sha256(text_path)

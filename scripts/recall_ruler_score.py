@@ -2,7 +2,7 @@
 """Score a checkpoint on the RULER subset by greedy generation (reference: scripts/recall_ruler_score.py).
 
     python scripts/recall_ruler_score.py --checkpoint RUN_DIR_OR_FILE --tokenizer tokenizer.json|bytes --out OUT --run NAME \\
-        [--pool docs.jsonl] [--tasks ...] [--lengths 2048 4096 8192] [--n-per-cell 100] [--batch 8]
+        [--pool docs.jsonl | --items BUILD_DIR] [--tasks ...] [--lengths 2048 4096 8192] [--n-per-cell 100] [--batch 8]
 
 --pool: held-out documents for the open-haystack tasks, one JSON object with a "text" field per line; without it only the
 needle- and noise-haystack tasks run. Items are generated on the fly (a pure function of task, length, index and pool).
@@ -28,7 +28,24 @@ from gdn_hybrid_architecture_ideas_b200.eval.generate import generate_greedy_bat
 from gdn_hybrid_architecture_ideas_b200.train import checkpoint as ckpt  # noqa: E402
 
 
-def score(model, tok, tasks, lengths, n_per_cell, batch, pool, out_dir: Path, run: str, autocast=None, log=print) -> dict:
+def stored_items(directory: Path, task: str) -> dict:
+    """{(length, index): RulerItem} of a task from a build of scripts/build_recall_ruler.py."""
+    import gzip
+
+    path = Path(directory) / "items" / f"{task}.jsonl.gz"
+    if not path.is_file():
+        raise FileNotFoundError(f"--items: no {path}")
+    out = {}
+    with gzip.open(path, "rt", encoding="utf-8") as f:
+        for line in f:
+            d = json.loads(line)
+            d.pop("id", None)
+            it = RR.RulerItem(**d)
+            out[(it.length, it.index)] = it
+    return out
+
+
+def score(model, tok, tasks, lengths, n_per_cell, batch, pool, out_dir: Path, run: str, autocast=None, log=print, items_dir=None) -> dict:
     out_dir.mkdir(parents=True, exist_ok=True)
     items_path = out_dir / f"{run}.items.jsonl"
     have = {}
@@ -39,14 +56,20 @@ def score(model, tok, tasks, lengths, n_per_cell, batch, pool, out_dir: Path, ru
     count = lambda text: len(tok.encode(text))
     with items_path.open("a") as sink:
         for task in tasks:
+            stored = stored_items(items_dir, task) if items_dir else None
             for length in lengths:
                 todo = []
                 for i in range(n_per_cell):
-                    try:
-                        it = RR.make_item(task, length, i, count, pool)
-                    except RR.NoFitError as e:
-                        log(f"{task} len={length} #{i}: {e}")
-                        continue
+                    if stored is not None:
+                        it = stored.get((length, i))
+                        if it is None:
+                            continue
+                    else:
+                        try:
+                            it = RR.make_item(task, length, i, count, pool)
+                        except RR.NoFitError as e:
+                            log(f"{task} len={length} #{i}: {e}")
+                            continue
                     if it.id not in have:
                         todo.append(it)
                 for lo in range(0, len(todo), batch):
@@ -78,6 +101,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True)
     ap.add_argument("--run", required=True)
     ap.add_argument("--pool")
+    ap.add_argument("--items", help="a build of scripts/build_recall_ruler.py: its stored items are scored instead of items generated on the fly")
     ap.add_argument("--tasks", nargs="*", default=None)
     ap.add_argument("--lengths", nargs="*", type=int, default=list(RR.LENGTHS))
     ap.add_argument("--n-per-cell", type=int, default=100)
@@ -92,9 +116,9 @@ def main(argv=None) -> int:
     pool = None
     if a.pool:
         pool = [json.loads(line)["text"] for line in Path(a.pool).read_text().splitlines() if line.strip()]
-    tasks = a.tasks or [t for t in RR.TASKS if pool or RR.SPEC[t]["haystack"] != "open"]
+    tasks = a.tasks or [t for t in RR.TASKS if pool or RR.SPEC[t]["haystack"] != "open" or (a.items and (Path(a.items) / "items" / f"{t}.jsonl.gz").is_file())]
     ac = torch.bfloat16 if a.device.startswith("cuda") else None
-    values = score(model, tok, tasks, a.lengths, a.n_per_cell, a.batch, pool, Path(a.out), a.run, ac)
+    values = score(model, tok, tasks, a.lengths, a.n_per_cell, a.batch, pool, Path(a.out), a.run, ac, items_dir=a.items)
     for k in sorted(values["cells"]):
         if k.endswith("|recall"):
             print(f"{k}: {values['cells'][k]:.4f}")

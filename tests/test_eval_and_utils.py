@@ -465,6 +465,28 @@ def test_recall_ruler_items_and_scoring(tmp_path):
     assert values["n_items"] == 2 and "ruler|vt|1024|recall" in values["cells"]
     assert len((tmp_path / "o" / "t.items.jsonl").read_text().splitlines()) == 2
 
+    # stored items: built once (deterministic files, hashes, the documents used), then scored from the build
+    docs = tmp_path / "docs.jsonl"
+    docs.write_text("".join(json.dumps({"id": f"d{i}", "text": t}) + "\n" for i, t in enumerate(pool)))
+    build = [sys.executable, str(root / "scripts" / "build_recall_ruler.py"), "--tokenizer", "bytes", "--docs", str(docs), "--tasks", "vt", "niah_multikey_1",
+             "--lengths", "1024", "--per-cell", "2"]
+    for name in ("b1", "b2"):
+        r = subprocess.run(build + ["--out", str(tmp_path / name)], capture_output=True, text=True, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+    m1, m2 = (json.loads((tmp_path / n / "manifest.json").read_text()) for n in ("b1", "b2"))
+    assert m1["sha256"] == m2["sha256"] and m1["cells"]["vt|1024"]["items"] == 2 and not m1["token_count_mismatches"]
+    hashes = json.loads((tmp_path / "b1" / "item-hashes.json").read_text())
+    used = json.loads((tmp_path / "b1" / "haystack-docs-used.json").read_text())
+    assert set(hashes) == {"vt/len=1024/0000", "vt/len=1024/0001", "niah_multikey_1/len=1024/0000", "niah_multikey_1/len=1024/0001"}
+    assert used["all"] and set(used["per_task"]) == {"niah_multikey_1"}
+    r = subprocess.run([sys.executable, str(root / "scripts" / "recall_ruler_score.py"), "--checkpoint", str(tmp_path / "run"), "--tokenizer", "bytes",
+                        "--out", str(tmp_path / "o2"), "--run", "t", "--items", str(tmp_path / "b1"), "--tasks", "vt", "--lengths", "1024", "--n-per-cell", "2",
+                        "--batch", "2", "--device", "cpu"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    on_the_fly = [json.loads(x) for x in (tmp_path / "o" / "t.items.jsonl").read_text().splitlines()]
+    from_build = [json.loads(x) for x in (tmp_path / "o2" / "t.items.jsonl").read_text().splitlines()]
+    assert [(x["id"], x["pred"]) for x in on_the_fly] == [(x["id"], x["pred"]) for x in from_build]      # the same prompts either way
+
 
 def test_recall_based_protocol(tmp_path):
     """Based suite: item files round-trip with their checksums, left truncation keeps the end, the generation is cut at the
