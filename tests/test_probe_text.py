@@ -216,3 +216,32 @@ def test_pcr_preset_writes_retrieval_and_copy_sets(tmp_path):
     assert m["probes"]["uuid_needle"] == 15 and m["probes"]["multikey"] == 6 and m["probes"]["vt"] == 3 and m["probes"]["pcr_copy3"] == 4
     copy2 = torch.load(out / "bytes" / "pcr_copy2.pt", weights_only=False)["probes"]
     assert copy2[0]["ids"][:16] == copy2[0]["ids"][16:32] and copy2[0]["answer_start"] == 16 and copy2[0]["cell"] == "n=16"
+
+
+def test_recall_item_sets_plan_build_split_and_first_block(tmp_path):
+    src = tmp_path / "docs.jsonl"
+    src.write_text("".join(json.dumps({"id": i, "text": d}) + "\n" for i, d in enumerate(docs(50, seed=5))))
+    tool = [sys.executable, str(ROOT / "scripts/build_recall_items.py")]
+    run = lambda *args: subprocess.run(tool + list(args), capture_output=True, text=True, timeout=900)
+    r = run("plan", "--out", str(tmp_path / "plan.json"), "--n", "100", "--n-old", "50", "--n-keys", "4", "--lengths", "2048,4096", "--budget-s", "66")
+    assert r.returncode == 0, r.stderr[-1500:]
+    plan = json.loads((tmp_path / "plan.json").read_text())
+    assert len(plan["groups"]) >= 2 and sum(g["items"] for g in plan["groups"]) == 200
+    # a small build: 3 items per cell stands in for the plan's 100 (same generator, same first items)
+    small = dict(plan, cells=[dict(c, n=3, n_old=2) for c in plan["cells"]],
+                 groups=[{"name": "g1", "modelled_s": 1.0, "deadline_s": 300, "items": 4, "parts": [{"cell": c["key"], "start": 0, "stop": 2} for c in plan["cells"]]},
+                         {"name": "g2", "modelled_s": 1.0, "deadline_s": 300, "items": 2, "parts": [{"cell": c["key"], "start": 2, "stop": 3} for c in plan["cells"]]}])
+    (tmp_path / "small.json").write_text(json.dumps(small))
+    r = run("build", "--plan", str(tmp_path / "small.json"), "--out", str(tmp_path / "items"), "--tokenizer", "bytes=bytes", "--docs", str(src))
+    assert r.returncode == 0, r.stderr[-1500:]
+    r = run("split", "--plan", str(tmp_path / "small.json"), "--out", str(tmp_path / "items"))
+    assert r.returncode == 0 and json.loads(r.stdout.strip().splitlines()[-1]) == {"groups": 2, "items_written": 6}, r.stderr[-1500:]
+    g1 = torch.load(tmp_path / "items/groups/g1/bytes/multikey.pt", weights_only=False)["probes"]
+    g2 = torch.load(tmp_path / "items/groups/g2/bytes/multikey.pt", weights_only=False)["probes"]
+    assert [p["id"][-4:] for p in g1] == ["0000", "0001", "0000", "0001"] and [p["id"][-4:] for p in g2] == ["0002", "0002"]
+    raw = tmp_path / "items/raw/bytes/multikey.pt"
+    assert run("check-first-block", "--old", str(tmp_path / "items/groups/g1/bytes/multikey.pt"), "--new", str(raw)).returncode == 0
+    blob = torch.load(raw, weights_only=False)
+    blob["probes"][0]["ids"][5] += 1
+    torch.save(blob, tmp_path / "tampered.pt")
+    assert run("check-first-block", "--old", str(tmp_path / "items/groups/g1/bytes/multikey.pt"), "--new", str(tmp_path / "tampered.pt")).returncode == 4
