@@ -59,6 +59,9 @@ def main(argv=None) -> int:
     dp = data_parallel.from_environment()
     try:
         trainer = prepare(args, dp)
+        info = getattr(trainer, "resume_info", None)
+        if info and trainer.lead:
+            print(f"resumed from {info['path']} at step {info['step']}", flush=True)
         trainer.fit(args.until_step)
     except Diverged as e:
         print(f"stopped: {e}", file=sys.stderr)
