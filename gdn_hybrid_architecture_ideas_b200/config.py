@@ -716,6 +716,14 @@ _TRAIN_BUILT = {
     "wgrad_accum": ("autograd", "fp32"),
     "optimizer_sharding": ("replicated", "zero1", "zero2"),
     "data.kind": ("synthetic", "shards", "uniform"),
+    # the packer's fit of a row's assistant tokens to a decoder capacity belongs to the CED decoder, which is not built;
+    # the span_* keys, span_fraction and decoder_positions only place that decoder's positions and are read by nothing here
+    # (the control models train on every valid target), chat_whole is built (data/shards.py)
+    "data.fit_decoder_capacity": (False,),
+    "data.decoder_positions": ("data", "random"),
+    "data.union_order": ("permute", "sets_in_order"),
+    "decoder_opt": ("none",),
+    "loop_switch_step": (0,),
 }
 
 

@@ -7,6 +7,13 @@ and a resume needs only the step (reference: ced/train/shards.py:92-342 — same
 per-token loss mask (`data.loss_mask`: "assistant", or a loss-span mode) every row also carries which of its targets
 keep their loss, read from the shard set's side arrays; the invariants a mask relies on are checked when the packer is
 built and their identity goes into the checkpoint's data state.
+
+`data.chat_whole`: a chat document of at most one row is never cut by a row boundary. When it does not fit the rest of
+the current row, that space is filled with the head of the next non-chat document(s) of the permutation, the chat
+document opens the next row, and the tail of a partly used filler follows it: every token is still used once per epoch,
+only the order of the pieces changes. A chat document longer than a row, or one near the end of an epoch with no
+non-chat document left to fill with, is placed as it comes (counted in `chat_cut`). An epoch is then a list of segments
+(document, offset, length) instead of whole documents, computed once per epoch in one pass over the permutation.
 """
 
 from __future__ import annotations
@@ -48,9 +55,54 @@ class ShardPacker:
         if self._epoch == epoch:
             return
         rng = np.random.default_rng([self.cfg.seed, epoch])
-        self._perm = rng.permutation(self.n_docs)
-        self._cum = np.concatenate([[0], np.cumsum(self.shards.doc_len(self._perm))])
+        perm = rng.permutation(self.n_docs)
+        lens = np.asarray(self.shards.doc_len(perm), dtype=np.int64)
+        if getattr(self.cfg, "chat_whole", False) and bool(np.asarray(self.shards.doc_chat).any()):
+            self._seg_doc, self._seg_off, self._seg_len, self.chat_cut = self._whole_chat_segments(perm, lens)
+        else:
+            self._seg_doc, self._seg_off, self._seg_len, self.chat_cut = perm, np.zeros(self.n_docs, dtype=np.int64), lens, 0
+        self._cum = np.concatenate([[0], np.cumsum(self._seg_len)])
         self._epoch = epoch
+
+    def _whole_chat_segments(self, perm: np.ndarray, lens: np.ndarray):
+        """(document, offset, length) per segment of the epoch so that no chat document of at most a row crosses a row boundary."""
+        W = self.row_tokens
+        chat = np.asarray(self.shards.doc_chat).astype(bool)[perm]
+        taken = np.zeros(len(perm), dtype=bool)
+        fillers = [j for j in range(len(perm)) if not chat[j]]
+        nxt = 0                       # next filler candidate
+        doc, off, ln = [], [], []
+        pos = cut = 0
+        for j in range(len(perm)):
+            if taken[j]:
+                continue
+            taken[j] = True
+            n, tail = int(lens[j]), None
+            if chat[j] and n <= W:
+                room = W - pos % W
+                if n > room:          # does not fit: fill the rest of the row with non-chat text, then start the next row
+                    need = room
+                    while need > 0:
+                        while nxt < len(fillers) and (fillers[nxt] <= j or taken[fillers[nxt]]):
+                            nxt += 1
+                        if nxt == len(fillers):
+                            cut += 1
+                            break
+                        k = fillers[nxt]
+                        taken[k] = True
+                        take = min(need, int(lens[k]))
+                        doc.append(int(perm[k])), off.append(0), ln.append(take)
+                        pos, need = pos + take, need - take
+                        if take < int(lens[k]):
+                            tail = (int(perm[k]), take, int(lens[k]) - take)
+            elif chat[j]:
+                cut += 1
+            doc.append(int(perm[j])), off.append(0), ln.append(n)
+            pos += n
+            if tail is not None:
+                doc.append(tail[0]), off.append(tail[1]), ln.append(tail[2])
+                pos += tail[2]
+        return np.asarray(doc, dtype=np.int64), np.asarray(off, dtype=np.int64), np.asarray(ln, dtype=np.int64), cut
 
     def row(self, index: int):
         """(tokens (L+1,), doc ids (L+1,)) of global row `index`."""
@@ -60,10 +112,10 @@ class ShardPacker:
         d = int(np.searchsorted(self._cum, lo, side="right") - 1)
         toks, docs, keeps, at, k = [], [], [], lo, 0
         while at < hi:
-            which = int(self._perm[d])
+            which = int(self._seg_doc[d])
             doc = self.shards.doc(which)
-            a = at - int(self._cum[d])
-            take = min(len(doc) - a, hi - at)
+            a = int(self._seg_off[d]) + at - int(self._cum[d])           # offset inside the document
+            take = min(int(self._seg_off[d]) + int(self._seg_len[d]) - a, hi - at)
             toks.append(doc[a:a + take])
             docs.append(np.full(take, k, dtype=np.int64))
             if self._flags is not None:      # the mask value of every token of the piece, as a TARGET

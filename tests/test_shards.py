@@ -131,3 +131,47 @@ def test_check_names_a_broken_set(tmp_path):
         with SF.ShardWriter(plain, 50) as w:
             w.add_document(np.arange(40))
         SF.check_loss_spans(SF.open_shards([plain]), "assistant")
+
+
+def test_chat_whole_keeps_chat_documents_off_the_row_boundaries(tmp_path):
+    """With data.chat_whole no chat document of at most a row is cut by a row boundary, every token is still used once per
+    epoch, a filler's tail follows the chat document it made room for, and without chat documents nothing changes."""
+    docs = _docs(7, n=60)
+    shards = _write_own(tmp_path / "s", docs)
+    L = 63                                             # rows of 64 tokens; documents are 20..59 tokens
+    mk = lambda whole: ShardPacker(shards, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "s"), seq_len=L, batch_size=2, seed=3, chat_whole=whole))
+    whole, plain = mk(True), mk(False)
+    assert whole.rows_per_epoch == plain.rows_per_epoch
+    whole._load_epoch(0)
+    W = whole.row_tokens
+    chat = np.asarray(shards.doc_chat).astype(bool)
+    cuts = 0
+    for d, o, n, start in zip(whole._seg_doc, whole._seg_off, whole._seg_len, whole._cum[:-1]):
+        if chat[d]:
+            assert o == 0 and n == len(shards.doc(int(d)))               # a chat document is one segment
+            cuts += int(start // W != (start + n - 1) // W)
+    assert cuts == whole.chat_cut <= 1                                   # at most the epoch's last chat document, with no filler left
+    plain._load_epoch(0)
+    plain_cuts = sum(int(chat[d]) and int(s // W != (s + n - 1) // W) for d, n, s in zip(plain._seg_doc, plain._seg_len, plain._cum[:-1]))
+    assert plain_cuts > 3                                                # the plain stream does cut them: the option has work to do
+    # every token of the set exactly once per epoch, in some order of pieces
+    pieces = sorted((int(d), int(o), int(n)) for d, o, n in zip(whole._seg_doc, whole._seg_off, whole._seg_len))
+    covered = {}
+    for d, o, n in pieces:
+        assert covered.get(d, 0) == o
+        covered[d] = o + n
+    assert covered == {i: len(shards.doc(i)) for i in range(len(docs))}
+    # rows carry the same tokens the segments name, with document ids restarting at each piece
+    seq, ids, _ = whole.row(2)
+    lo = 2 * W
+    k = int(np.searchsorted(whole._cum, lo, side="right") - 1)
+    d, o = int(whole._seg_doc[k]), int(whole._seg_off[k]) + lo - int(whole._cum[k])
+    take = min(int(whole._seg_off[k] + whole._seg_len[k]) - o, W)
+    assert np.array_equal(seq[:take], shards.doc(d)[o:o + take]) and len(seq) == W and ids[0] == 0
+    assert torch.equal(whole.rows(0, 3).tokens, whole.rows(0, 3).tokens)
+    # no chat document in the set: chat_whole changes nothing
+    nochat = [(ids_, g * 0, s * 0, False) for ids_, g, s, _ in docs]
+    sh2 = _write_own(tmp_path / "n", nochat)
+    a = ShardPacker(sh2, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "n"), seq_len=L, batch_size=2, seed=3, chat_whole=True))
+    b = ShardPacker(sh2, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "n"), seq_len=L, batch_size=2, seed=3))
+    assert torch.equal(a.batch(1).tokens, b.batch(1).tokens)
