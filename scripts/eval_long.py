@@ -51,6 +51,9 @@ def main(argv=None) -> int:
     if a.gdn_diag:
         ids = docs[0]["ids"][: a.max_len or None][None]
         out["gdn_diag"] = gdn_diag.encoder_gdn_diag(model, ids, torch.zeros_like(ids), block=a.chunk, autocast_dtype=ac)
+        # state statistics by position bucket with their drift against the last bucket inside the training length
+        out["gdn_positions"] = gdn_diag.gdn_position_diag(model, ids, torch.zeros_like(ids), train_len=a.train_len or cfg.data.seq_len, block=a.chunk,
+                                                          autocast_dtype=ac)
     if a.window:
         rows = long_report.context_gain(model, docs if not a.max_len else [{k: v[:a.max_len] for k, v in d.items()} for d in docs], res["edges"], a.window,
                                         a.chunk, ac, full_records=res["records"])
