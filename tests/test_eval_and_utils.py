@@ -940,3 +940,39 @@ def test_gdn_walk_matches_the_cached_state_at_the_end_of_a_row():
             assert torch.allclose(hooks.state[i], c.S.float(), atol=1e-4, rtol=1e-4), i
             checked += 1
     assert checked >= 1
+
+
+def test_text_multiple_choice_tasks():
+    """The regression tasks' formats, whole-document packing, likelihood and byte-normalised accuracy, gold bpb, greedy cloze
+    accuracy, and sharded scoring that joins to the same numbers."""
+    from gdn_hybrid_architecture_ideas_b200.eval import multiple_choice as mc
+    from gdn_hybrid_architecture_ideas_b200.eval.span_bpb import build_eval_rows
+
+    rows_in = [
+        ("arc-easy", {"id": "q1", "question": "Which is a mammal?", "choices": {"text": ["trout", "otter", "finch"], "label": ["A", "B", "C"]}, "answerKey": "B"}),
+        ("piqa", {"goal": "dry a shirt", "sol1": "hang it in the sun", "sol2": "put it in the freezer", "label": 0}),
+        ("boolq", {"passage": "Ice floats on water.", "question": "does ice float", "answer": True}),
+        ("winogrande", {"sentence": "The cup fell off the shelf because _ was unsteady.", "option1": "the cup", "option2": "the shelf", "answer": "2"}),
+        ("lambada", {"text": "She opened the door and saw her old friend"}),
+    ]
+    items = [mc.format_item(t, r, i) for i, (t, r) in enumerate(rows_in)]
+    assert items[0].gold == 1 and items[0].choices[1] == " otter" and items[2].choices == [" no", " yes"] and items[2].gold == 1
+    assert items[3].contexts == ["The cup fell off the shelf because the cup", "The cup fell off the shelf because the shelf"] and items[3].choices[0] == " was unsteady." and items[3].gold == 1
+    assert items[4].kind == "cloze" and items[4].choices == [" friend"] and items[4].contexts[0].endswith("her old")
+    with pytest.raises(ValueError):
+        mc.format_item("trivia", {}, 0)
+    model = _tiny()
+    V = model.cfg.vocab_size
+    encode = lambda s: [1 + (b % (V - 1)) for b in s.encode("utf-8")]
+    docs, index = mc.encode_items(items, encode)
+    assert len(docs) == 3 + 2 + 2 + 2 + 1 and all(sum(d.byte_lens[len(d.ids) - sum(d.scored):]) == nb for d, (_, _, nb) in zip(docs, index))
+    table, records = mc.score_text_items(model, items, encode, seq_len=256, batch_size=2)
+    assert set(table) == {t for t, _ in rows_in} and all(r["n"] == 1 and r["gold_bpb"] > 0 for r in table.values())
+    assert "greedy_acc" in table["lambada"] and "greedy_acc" not in table["piqa"] and len(records) == 5
+    rows = build_eval_rows(docs, 256)
+    a = mc.score_choice_rows(model, rows, 1, row_indices=range(0, len(rows), 2))
+    b = mc.score_choice_rows(model, rows, 1, row_indices=range(1, len(rows), 2))
+    joined, _ = mc.choice_results(items, index, mc.join_choice_rows([a, b]))
+    assert joined == table
+    with pytest.raises(ValueError, match="longer than a row"):
+        mc.score_text_items(model, items, encode, seq_len=16)
