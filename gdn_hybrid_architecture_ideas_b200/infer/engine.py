@@ -24,6 +24,7 @@ from __future__ import annotations
 import torch
 
 from .. import ops
+from .arena import GuardedBuffers
 from ..models.attention import assemble_grid
 from ..models.encoder import apply_layer_scalars
 from ..models.gdn import READ_MIX_VARIANTS, GDNState
@@ -40,12 +41,15 @@ class DecodeEngine:
         self.native = self.device.type == "cuda" and ops.mode() == "native"
         self.use_graph = use_graph and self.device.type == "cuda"
         dev, B, T = self.device, batch, max_len
-        self.lens = torch.zeros(B, dtype=torch.int32, device=dev)           # cached positions per row
-        self.doc_start = torch.zeros(B, dtype=torch.int32, device=dev)      # start of each row's current document
-        self.doc_id = torch.zeros(B, dtype=torch.long, device=dev)
-        self.tokens = torch.zeros(B, dtype=torch.long, device=dev)          # static input of the step
-        self.next_tokens = torch.zeros(B, dtype=torch.long, device=dev)     # static output of the step
-        self.logits = torch.zeros(B, self.cfg.vocab_size, dtype=torch.float32, device=dev)
+        # every static buffer sits between guard bands (infer/arena.py); `check_guards()` after a run finds a write past an end
+        self.buffers = GuardedBuffers(dev)
+        z = self.buffers.zeros
+        self.lens = z("lens", B, torch.int32)                   # cached positions per row
+        self.doc_start = z("doc_start", B, torch.int32)         # start of each row's current document
+        self.doc_id = z("doc_id", B, torch.long)
+        self.tokens = z("tokens", B, torch.long)                # static input of the step
+        self.next_tokens = z("next_tokens", B, torch.long)      # static output of the step
+        self.logits = z("logits", (B, self.cfg.vocab_size), torch.float32)
         self.layers = []
         if self.cfg.encoder.attn_res in ("block", "ldm"):
             raise ValueError(f"the decode engine walks the plain and the block-entry stacks; model.encoder.attn_res {self.cfg.encoder.attn_res!r} "
@@ -64,15 +68,15 @@ class DecodeEngine:
             raise ValueError("the decode engine does not keep a Canon layer's input history (model.encoder.canon_kernel): "
                              "generate through the model's cached forward (eval.generate)")
         kv_dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
-        for layer in model.encoder.layers:
+        for li, layer in enumerate(model.encoder.layers):
             m = layer.mixer
             if layer.kind == "attention":
                 c = m.cfg
                 heads, width = (1, m.grid.width) if m.grid is not None else (c.n_kv_heads, c.head_dim)
                 rot = rotary_dims(c.head_dim, c.rope_fraction)
                 n_ang = (m.cap + 1) if m.cap is not None else max_len
-                st = {"k": torch.zeros(B, T, heads, width, dtype=kv_dtype, device=dev),
-                      "v": torch.zeros(B, T, heads, width, dtype=kv_dtype, device=dev), "rot": rot, "heads": heads}
+                st = {"k": z(f"layer{li}.k", (B, T, heads, width), kv_dtype),
+                      "v": z(f"layer{li}.v", (B, T, heads, width), kv_dtype), "rot": rot, "heads": heads}
                 if rot:
                     inv = c.rope_theta ** (-torch.arange(0, rot, 2, dtype=torch.float64, device=dev) / rot)
                     ang = torch.arange(n_ang, dtype=torch.float64, device=dev)[:, None] * inv
@@ -82,18 +86,22 @@ class DecodeEngine:
                 self.layers.append(st)
             else:
                 g = m.cfg
-                self.layers.append({"S": torch.zeros(B, g.n_v_heads, g.k_head_dim, g.v_head_dim, dtype=torch.float32, device=dev),
-                                    "conv": torch.zeros(B, g.conv_kernel - 1, m.conv_channels, dtype=kv_dtype, device=dev),
-                                    "conv_doc": torch.full((B, g.conv_kernel - 1), -1, dtype=torch.long, device=dev)})
+                self.layers.append({"S": z(f"layer{li}.S", (B, g.n_v_heads, g.k_head_dim, g.v_head_dim), torch.float32),
+                                    "conv": z(f"layer{li}.conv", (B, g.conv_kernel - 1, m.conv_channels), kv_dtype),
+                                    "conv_doc": self.buffers.full(f"layer{li}.conv_doc", (B, g.conv_kernel - 1), -1, torch.long)})
         hq = max((l.mixer.cfg.n_q_heads for l in model.encoder.layers if l.kind == "attention"), default=1)
         self.splits = splits or max(1, min(64, (148 * 2) // max(1, B)))
         grid_layers = any(l.kind == "attention" and l.mixer.grid is not None for l in model.encoder.layers)
         scratch_splits = self.splits * (4 if grid_layers else 1)
-        self.part_o = torch.zeros(B * hq * scratch_splits * 64, dtype=torch.float32, device=dev)
-        self.part_ml = torch.zeros(B * hq * scratch_splits * 2, dtype=torch.float32, device=dev)
+        self.part_o = z("part_o", B * hq * scratch_splits * 64, torch.float32)
+        self.part_ml = z("part_ml", B * hq * scratch_splits * 2, torch.float32)
         self.native_grid = True     # False: score grid layers through the assembled-heads statement (oracle of the grid kernel)
         self.graph = None
         self._host_len = 0          # host-side mirror of the (equal) row lengths: guards the static capacity before each launch
+
+    def check_guards(self) -> None:
+        """After a run: no static buffer was written past either end (raises `arena.GuardOverrun` naming it)."""
+        self.buffers.check()
 
     # ------------------------------------------------------------------ sizes
 

