@@ -35,6 +35,9 @@ def main(argv=None) -> int:
     ap.add_argument("--gdn-diag", action="store_true")
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--train-len", type=int, default=0, help="degradations are listed beyond this length (default: the run's seq_len)")
+    ap.add_argument("--agent-windows", default="", help="comma-separated context windows: the documents carry `assistant` flags (whole agent trajectories) and "
+                    "their assistant bpb is scored with the context cut to each window (and to --base, the reference window)")
+    ap.add_argument("--agent-tail", type=int, default=0, help="targets of the tail every window holds (default base / 2)")
     ap.add_argument("--summary")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--out")
@@ -42,6 +45,18 @@ def main(argv=None) -> int:
     model, cfg, step = ckpt.load_model(a.checkpoint, a.device)
     ac = torch.bfloat16 if a.device.startswith("cuda") else None
     docs = torch.load(a.docs, map_location="cpu", weights_only=False)["docs"]
+    if a.agent_windows:
+        missing = [i for i, d in enumerate(docs) if "assistant" not in d]
+        if missing:
+            ap.error(f"--agent-windows: documents {missing[:5]} carry no `assistant` flags")
+        res = long_context.score_agent_windows(model, docs, windows=[int(x) for x in a.agent_windows.split(",")], ref_window=a.base,
+                                               tail=a.agent_tail or None, base=a.base, chunk=a.chunk, autocast_dtype=ac)
+        for W, row in res["window"].items():
+            print(f"window {W:>7d}: assistant bpb {row['bpb']:.4f} ({row['trajectories']} trajectories, {row['filled']} filled)")
+        if a.out:
+            with open(a.out, "w") as f:
+                json.dump({"step": step, "agent_windows": res}, f, indent=1, default=lambda o: o.tolist() if hasattr(o, "tolist") else str(o))
+        return 0
     docs = [{"ids": torch.as_tensor(d["ids"]), "byte_lens": torch.as_tensor(d["byte_lens"])} for d in docs]
     res = long_context.score_position_bpb(model, docs, base=a.base, max_len=a.max_len or None, chunk=a.chunk, autocast_dtype=ac)
     for line in res["table"]:

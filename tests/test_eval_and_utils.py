@@ -976,3 +976,37 @@ def test_text_multiple_choice_tasks():
     assert joined == table
     with pytest.raises(ValueError, match="longer than a row"):
         mc.score_text_items(model, items, encode, seq_len=16)
+
+
+def test_agent_trajectories_by_context_window():
+    """Assistant bpb with the context cut to W: a window that holds the whole trajectory scores it whole (same sums as the
+    larger windows), the tail is the same targets at every window, deltas are paired against the reference window."""
+    from gdn_hybrid_architecture_ideas_b200.eval import long_context as lc
+
+    model = _tiny().eval()
+    V = model.cfg.vocab_size
+    g = torch.Generator().manual_seed(6)
+    docs = []
+    for i, n in enumerate((70, 45, 120, 20)):
+        asst = [int((t // 7) % 2 == 1) for t in range(n)]
+        docs.append({"id": f"t{i}", "group": i % 2, "ids": torch.randint(1, V, (n,), generator=g), "byte_lens": torch.randint(1, 4, (n,), generator=g), "assistant": asst})
+    res = lc.score_agent_windows(model, docs, windows=(64, 128), ref_window=32, tail=16, min_tokens=33, base=32, chunk=50)
+    assert res["windows"] == [32, 64, 128] and res["skipped_short"] == 1 and len(res["docs"]) == 3
+    d70 = next(d for d in res["docs"] if d["id"] == "t0")
+    assert d70["windows"][128] == dict(d70["windows"][128], m=69, filled=False) and d70["windows"][64]["filled"] and d70["windows"][32]["m"] == 32
+    assert {k: v for k, v in d70["windows"][128].items() if k != "filled"}["nats"] > d70["windows"][32]["nats"]      # more targets in the larger row
+    for d in res["docs"]:
+        tails = {W: (w["tail_tokens"], w["tail_bytes"]) for W, w in d["windows"].items()}
+        assert len(set(tails.values())) == 1                     # the same tail targets at every window
+        for w in d["windows"].values():
+            assert w["first_tokens"] <= w["spans"] <= w["tokens"] and w["tail_first_tokens"] <= w["first_tokens"]
+    # by hand: the tail of t0 at window 32 is the CE of a fresh row of its last 32 inputs over its assistant targets in the last 16
+    ids = docs[0]["ids"]
+    ce = lc.position_ce(model, ids[70 - 1 - 32:], 64)
+    tgt = torch.arange(70 - 32, 70)
+    mask = torch.tensor(docs[0]["assistant"]).bool()[tgt] & (tgt >= 70 - 16)
+    assert abs(float(ce[mask].sum()) - d70["windows"][32]["tail_nats"]) < 1e-4
+    assert set(res["window"]) == {32, 64, 128} and res["window"][32]["trajectories"] == 3 and res["window"][64]["filled"] == 2
+    assert set(res["tail_by_cohort"]) == {32, 64} and set(res["tail_by_cohort"][64]["by_window"]) == {32, 64}
+    ref = res["tail_by_cohort"][64]["by_window"][32]
+    assert abs(ref["delta_vs_ref"]) < 1e-12 and res["tail_by_cohort"][64]["trajectories"] == 2 and res["tail_by_cohort"][32]["clusters"] == 2
