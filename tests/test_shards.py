@@ -175,3 +175,50 @@ def test_chat_whole_keeps_chat_documents_off_the_row_boundaries(tmp_path):
     a = ShardPacker(sh2, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "n"), seq_len=L, batch_size=2, seed=3, chat_whole=True))
     b = ShardPacker(sh2, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "n"), seq_len=L, batch_size=2, seed=3))
     assert torch.equal(a.batch(1).tokens, b.batch(1).tokens)
+
+
+def test_build_shards_script_text_and_chat(tmp_path):
+    """The shard builder: plain documents with byte counts and a held-out split, chat conversations with generated flags and
+    loss-span classes that pass the set's invariants and train under the assistant mask."""
+    import gzip
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    docs = tmp_path / "docs.jsonl"
+    docs.write_text("".join(json.dumps({"text": f"Document {i} says hello to the reader. " * (3 + i % 4)}) + "\n" for i in range(12)))
+    r = subprocess.run([sys.executable, str(root / "scripts/build_shards.py"), "--out", str(tmp_path / "train"), "--tokenizer", "bytes", "--input", str(docs),
+                        "--holdout-every", "4", "--holdout-out", str(tmp_path / "held")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rep = json.loads(r.stdout.strip().splitlines()[-1])
+    assert rep["documents"] == {"train": 9, "held": 3, "short": 0} and rep["train"]["documents"] == 9
+    train = SF.open_shards([tmp_path / "train"])
+    first = "Document 0 says hello to the reader. " * 3
+    assert bytes(train.doc(0).astype(np.uint8).tolist()).decode() == first and train.n_tokens == rep["train"]["tokens"]
+    with gzip.open(tmp_path / "held" / "docs.jsonl.gz", "rt") as f:
+        held = [json.loads(x) for x in f]
+    assert len(held) == 3 and held[0]["text"].startswith("Document 3 ")
+    # chat conversations
+    conv = {"messages": [{"role": "system", "content": "You are terse."}, {"role": "user", "content": "List the files."},
+                         {"role": "assistant", "content": "Looking.", "tool_calls": [{"name": "ls", "arguments": {"path": "."}}]},
+                         {"role": "tool", "content": "a.txt\n" * 40}, {"role": "assistant", "content": "Forty copies of a.txt."}]}
+    chat = tmp_path / "chat.jsonl"
+    chat.write_text("".join(json.dumps(conv) + "\n" for _ in range(6)))
+    r = subprocess.run([sys.executable, str(root / "scripts/build_shards.py"), "--out", str(tmp_path / "chat"), "--tokenizer", "bytes", "--input", str(chat), "--chat"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    s = SF.open_shards([tmp_path / "chat"])
+    assert bool(np.asarray(s.doc_chat).all()) and s.vocab_size == 256 + 11
+    a, b = int(s.starts[0]), int(s.ends[0])
+    gen, cls = np.asarray(s.side("generated")[a:b]), np.asarray(s.side("loss_spans")[a:b])
+    toks = np.asarray(s.doc(0))
+    text_of = lambda mask: bytes(int(t) for t in toks[mask] if t < 256).decode()
+    assert "Looking." in text_of(gen == 1) and "Forty copies" in text_of(gen == 1) and "List the files" not in text_of(gen == 1)
+    assert set(np.unique(cls)) == {0, 1, 2, 3} and not bool((cls[gen == 1] > 0).any())
+    assert "a.txt" in text_of(cls == 1) and "a.txt" in text_of(cls == 2) and "You are terse" in text_of(cls == 3)
+    state = SF.check_loss_spans(s, "assistant")
+    assert state["mode"] == "assistant"
+    packer = ShardPacker(s, C.DataConfig(kind="shards", shard_dir=str(tmp_path / "chat"), seq_len=64, batch_size=2, seed=1, loss_mask="assistant", chat_whole=True))
+    b0 = packer.batch(0)
+    assert b0.loss_mask is not None and 0 < int(b0.loss_mask.sum()) < b0.loss_mask.numel()
