@@ -30,18 +30,20 @@ def main(argv=None) -> int:
     ap.add_argument("--batch-size", type=int, default=4)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--set", help="a stored probe set (scripts/build_probes.py) in place of probes built on the fly")
+    ap.add_argument("--keep-items", action="store_true", help="with --set: the output also lists every item's id and exact-match score")
     ap.add_argument("--out")
     a = ap.parse_args(argv)
     model, cfg, step = ckpt.load_model(a.checkpoint, a.device)
     ac = torch.bfloat16 if a.device.startswith("cuda") else None
-    table = {}
-    stored = None
+    table, item_records = {}, []
+    stored = stored_ids = None
     if a.set:
         blob = torch.load(a.set, map_location="cpu", weights_only=False)
         if blob["vocab"] > cfg.model.vocab_size:
             ap.error(f"the set was built for a vocabulary of {blob['vocab']}, the model has {cfg.model.vocab_size}")
-        stored = {}
+        stored, stored_ids = {}, {}
         for p in blob["probes"]:
+            stored_ids.setdefault((p.get("cell", p["length"]), p["kind"]), []).append(p.get("id"))
             # token-id sets are keyed by their nominal length; text-level sets (scripts/build_text_probes.py) by their cell
             stored.setdefault((p.get("cell", p["length"]), p["kind"]), []).append(
                 probes.Probe(p["kind"], p["ids"], p["answer_start"], p["answer_len"], tuple(map(tuple, p.get("pieces", ()))), p.get("group", ""),
@@ -52,6 +54,8 @@ def main(argv=None) -> int:
             probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
         r = probes.score_probes(model, ps, a.batch_size, ac)
         cell = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
+        if stored_ids is not None and a.keep_items:
+            item_records += [{"id": i, "kind": kind, "exact": bool(it["exact"]), "ce": it["ce"]} for i, it in zip(stored_ids[(length, kind)], r["items"])]
         groups = sorted({it["group"] for it in r["items"] if "group" in it})
         for gname in groups:        # multi-fact layouts, transcode directions
             own = [it for it in r["items"] if it.get("group") == gname]
@@ -68,7 +72,7 @@ def main(argv=None) -> int:
         print(f"{kind:11s} {('length ' + str(length)) if isinstance(length, int) else length}: exact {r['exact']:.3f}  ce {r['ce']:.3f}")
     if a.out:
         with open(a.out, "w") as f:
-            json.dump({"step": step, "probes": table}, f, indent=1)
+            json.dump({"step": step, "probes": table, **({"items": item_records} if a.keep_items else {})}, f, indent=1)
     return 0
 
 

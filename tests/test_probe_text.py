@@ -245,3 +245,35 @@ def test_recall_item_sets_plan_build_split_and_first_block(tmp_path):
     blob["probes"][0]["ids"][5] += 1
     torch.save(blob, tmp_path / "tampered.pt")
     assert run("check-first-block", "--old", str(tmp_path / "items/groups/g1/bytes/multikey.pt"), "--new", str(tmp_path / "tampered.pt")).returncode == 4
+
+
+def test_recall_items_values_from_group_outputs(tmp_path):
+    from gdn_hybrid_architecture_ideas_b200.eval import recall_items as RI
+
+    plan = RI.make_plan({"multikey_n4|2048": 6}, {"multikey_n4|2048": 2}, budget_s=70.0)
+    plan["groups"] = [{"name": "g1", "modelled_s": 1.0, "deadline_s": 300, "items": 4, "parts": [{"cell": "multikey_n4|2048", "start": 0, "stop": 4}]},
+                      {"name": "g2", "modelled_s": 1.0, "deadline_s": 300, "items": 2, "parts": [{"cell": "multikey_n4|2048", "start": 4, "stop": 6}]}]
+    (tmp_path / "plan.json").write_text(json.dumps(plan))
+    ids = [f"multikey/len=2048/n=4/{i:04d}" for i in range(6)]
+    exact = [True, False, True, True, False, True]
+    (tmp_path / "out").mkdir()
+    (tmp_path / "out" / "g1.json").write_text(json.dumps({"items": [{"id": i, "exact": e} for i, e in zip(ids[:4], exact[:4])]}))
+    tool = [sys.executable, str(ROOT / "scripts/recall_items_values.py")]
+    base = ["run", "--plan", str(tmp_path / "plan.json"), "--run", "r", "--probes-dir", str(tmp_path / "out")]
+    assert subprocess.run(tool + base + ["--out", str(tmp_path / "r.values.json")], capture_output=True, text=True).returncode == 3      # g2 missing
+    (tmp_path / "out" / "g2.json").write_text(json.dumps({"items": [{"id": i, "exact": e} for i, e in zip(ids[4:], exact[4:])]}))
+    r = subprocess.run(tool + base + ["--out", str(tmp_path / "r.values.json")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    v = json.loads((tmp_path / "r.values.json").read_text())
+    assert v["cells"] == {"items|multikey_n4|2048|exact": 4 / 6} and v["family"] == "items"
+    d = json.loads((tmp_path / "r.detail.json").read_text())["multikey_n4|2048"]
+    assert d["first_block"] == {"n": 2, "exact": 0.5, "se": RI.binomial_se(0.5, 2)} and d["new_block"]["n"] == 4 and d["missing"] == 0
+    (tmp_path / "ex.json").write_text(json.dumps(["multikey_n4:" + ids[1]]))
+    r = subprocess.run(tool + base + ["--out", str(tmp_path / "x.values.json"), "--exclude-file", str(tmp_path / "ex.json")], capture_output=True, text=True)
+    assert r.returncode == 0 and json.loads((tmp_path / "x.values.json").read_text())["cells"]["items|multikey_n4|2048|exact"] == 4 / 5
+    (tmp_path / "bad.json").write_text(json.dumps(["multikey/len=2048/n=4/0099"]))
+    assert subprocess.run(tool + base + ["--out", str(tmp_path / "y.json"), "--exclude-file", str(tmp_path / "bad.json")], capture_output=True, text=True).returncode == 3
+    r = subprocess.run(tool + base + ["--out", str(tmp_path / "f.values.json"), "--first-block-only"], capture_output=True, text=True)
+    assert r.returncode == 0 and json.loads((tmp_path / "f.values.json").read_text())["cells"]["items|multikey_n4|2048|exact"] == 0.5
+    b = subprocess.run(tool + ["brief", "--values", str(tmp_path / "r.values.json")], capture_output=True, text=True)
+    assert "0.6667" in b.stdout and "n=6" in b.stdout
