@@ -1010,3 +1010,34 @@ def test_agent_trajectories_by_context_window():
     assert set(res["tail_by_cohort"]) == {32, 64} and set(res["tail_by_cohort"][64]["by_window"]) == {32, 64}
     ref = res["tail_by_cohort"][64]["by_window"][32]
     assert abs(ref["delta_vs_ref"]) < 1e-12 and res["tail_by_cohort"][64]["trajectories"] == 2 and res["tail_by_cohort"][32]["clusters"] == 2
+
+
+def test_build_recall_based_from_raw_files(tmp_path):
+    import gzip
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from gdn_hybrid_architecture_ideas_b200.eval import recall_based as RB
+
+    root = Path(__file__).resolve().parent.parent
+    raw = tmp_path / "raw"
+    for task, n in (("squad", 3), ("fda", 2)):
+        (raw / task).mkdir(parents=True)
+        rows = [{"doc_id": f"{task}-{i}", "text": f"Context {i}. The answer to question {i} is", "value": f"value{i}"} for i in range(n)]
+        (raw / task / "validation.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
+    tool = [sys.executable, str(root / "scripts" / "build_recall_based.py"), "--raw", str(raw), "--tasks", "squad,fda", "--tokenizer", "bytes", "--texts"]
+    r = subprocess.run(tool + ["--out", str(tmp_path / "items")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-1500:]
+    items = RB.load_set(tmp_path / "items", "squad")                      # verified against the manifest's sha256
+    assert [i.id for i in items] == ["squad-0", "squad-1", "squad-2"] and items[1].value == "value1"
+    man = json.loads((tmp_path / "items" / "manifest.json").read_text())
+    assert man["fda"]["n"] == 2 and man["fda"]["source"]["rows"] == 2 and len(man["squad"]["source"]["sha256"]) == 64
+    rep = json.loads((tmp_path / "items" / "report.json").read_text())
+    assert rep["squad"]["repeated_texts"] == 0 and rep["squad"]["prompt_tokens"]["min"] > 10
+    cont = json.loads((tmp_path / "items" / "recall_based.contamination.json").read_text())
+    assert len(cont["squad"]["item_text_sha256"]) == 3 and "text" not in json.dumps(cont["squad"]["source"])
+    with gzip.open(tmp_path / "items" / "itemtexts" / "fda.jsonl.gz", "rt") as f:
+        assert len(f.read().splitlines()) == 2
+    bad = subprocess.run(tool + ["--out", str(tmp_path / "x"), "--expect-sha256", "squad=" + "0" * 64], capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and "not the expected" in bad.stderr
