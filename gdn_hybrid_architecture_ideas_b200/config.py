@@ -689,7 +689,6 @@ _BUILT = {
     "model.encoder.residual_dtype": ("float32", "bf16"),
     "model.encoder.gdn_ccr_spacing": (0,),
     "model.loop.pass2_gate": ("none",),
-    "model.loop.recur_layers": ((),),
     "model.loop.segment_passes": (None,),
     "model.loop.unscored_passes": (None,),
     "model.mtp.enabled": (False, True),
@@ -723,6 +722,7 @@ _TRAIN_BUILT = {
     "data.decoder_positions": ("data", "random"),
     "data.union_order": ("permute", "sets_in_order"),
     "decoder_opt": ("none",),
+    "optim.recur_b": ("adamw",),                  # the looped middle's injection matrix under Muon is not built
     "loop_switch_step": (0,),
 }
 

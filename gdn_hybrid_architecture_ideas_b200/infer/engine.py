@@ -54,6 +54,9 @@ class DecodeEngine:
         if self.cfg.encoder.attn_res in ("block", "ldm"):
             raise ValueError(f"the decode engine walks the plain and the block-entry stacks; model.encoder.attn_res {self.cfg.encoder.attn_res!r} "
                              "generates through the model's cached forward (eval.generate)")
+        if self.cfg.loop.recur_layers:
+            raise ValueError("the decode engine walks every layer once; a looped middle (model.loop.recur_layers) generates through the "
+                             "model's cached forward (eval.generate)")
         if self.cfg.encoder.attn_res_query != "static":
             raise ValueError("the decode engine's block-entry reads are the static ones; model.encoder.attn_res_query 'token' "
                              "generates through the model's cached forward (eval.generate)")

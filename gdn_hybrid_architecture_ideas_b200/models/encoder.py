@@ -21,7 +21,7 @@ from .. import ops
 from ..config import ModelConfig
 from . import act_checkpoint
 from .attention import GatedAttention
-from .depth_mix import EntryLayer, LayerQueries
+from .depth_mix import DepthQuery, EntryLayer, LayerQueries
 from .gdn import READ_MIX_VARIANTS, GatedDeltaNet, GDNArms
 from .mlp import dense_ffn
 from .norms import RMSNorm, round_stream
@@ -269,6 +269,23 @@ class Encoder(nn.Module):
                              "the layers' residual add (reference: ced/model/attn_res.py:166-168)")
         for name in names:
             setattr(self, name, nn.Parameter(torch.zeros(n)))
+        # A looped middle (models/recur.py): the layers first .. end - 1 run T times; what a pass reads is the injection's.
+        from . import recur as recur_mod
+
+        recur_mod.check_config(cfg)
+        self.recur = tuple(cfg.loop.recur_layers) or None
+        self.recur_norm = self.recur_injection = self.recur_mix = self.recur_depth = None
+        if self.recur is not None:
+            lc = cfg.loop
+            self.recur_state_init = lc.recur_state_init
+            if lc.injection == "parcae":
+                if lc.recur_prelude_norm:
+                    self.recur_norm = RMSNorm(d, eps)
+                self.recur_injection = recur_mod.RecurInjection(d, lc.parcae_init_decay, lc.recur_inject_b)
+            elif lc.injection == "mix":
+                self.recur_mix = nn.Parameter(torch.tensor(float(lc.recur_mix_init)))
+            elif lc.injection == "depth_mix":
+                self.recur_depth = DepthQuery(d, eps)
 
     def layer_scalar_args(self, x0):
         """Per layer (x0, a - 1, b) as 0-dim tensors, or None without the scalars."""
@@ -387,8 +404,57 @@ class Encoder(nn.Module):
             x = partial
         return x, new_caches
 
-    def forward(self, x: torch.Tensor, ctx: SeqContext, caches: list | None = None, need_state: bool = True):
-        """x: embedding-stage output (B, L, d). Returns (stream entering final_norm, per-layer caches)."""
+    def forward_recur(self, x: torch.Tensor, ctx: SeqContext, caches: list | None, need_state: bool, T: int):
+        """The stack with its looped middle at T passes (models/recur.py). `caches` and the returned list hold one entry per
+        layer application, in running order."""
+        from . import recur as recur_mod
+
+        if type(T) is not int or T < 1:
+            raise ValueError(f"T={T!r}: a pass count >= 1")
+        if self.activation_checkpoint == "block" and torch.is_grad_enabled() and x.requires_grad:
+            raise ValueError("activation_checkpoint 'block' is not built for a looped middle: use 'layer' or 'none'")
+        first, end = self.recur
+        want = recur_mod.cache_length(self.recur, len(self.layers), T)
+        if caches is not None and len(caches) != want:
+            raise ValueError(f"this cache holds {len(caches)} layer entries; a forward at T = {T} needs {want} (a cached sequence keeps its T)")
+        new_caches: list = []
+
+        def segment(h, layers):
+            for layer in layers:
+                h, c = self._run(layer, h, ctx, None if caches is None else caches[len(new_caches)], None, need_state)
+                new_caches.append(c)
+            return h
+
+        layers = list(self.layers)
+        x0 = x
+        p = segment(x, layers[:first])
+        if self.recur_depth is not None:
+            sources, z = [x0, p], None
+            for _ in range(T):
+                z = segment(self.recur_depth(sources), layers[first:end])
+                sources = sources + [z]
+            return segment(z, layers[end:]), new_caches
+        inject, mix = self.recur_injection, self.recur_mix
+        if inject is None:
+            e, z = (None if mix is None else p), p
+        else:
+            e = p if self.recur_norm is None else self.recur_norm(p, out_dtype=p.dtype)
+            z = e if self.recur_state_init == "prelude" else None
+        for k in range(T):
+            if inject is not None:
+                u = inject(z, e)
+            elif mix is not None and k > 0:
+                u = recur_mod.input_mix(e, z, mix)
+            else:
+                u = z
+            z = segment(u, layers[first:end])
+        return segment(z, layers[end:]), new_caches
+
+    def forward(self, x: torch.Tensor, ctx: SeqContext, caches: list | None = None, need_state: bool = True, T: int | None = None):
+        """x: embedding-stage output (B, L, d). Returns (stream entering final_norm, per-layer caches). T: the pass count of a
+        looped middle (models/recur.py); ignored by a stack without one."""
+        if self.recur is not None:
+            return self.forward_recur(x, ctx, caches, need_state, self.cfg.loop.t_eval if T is None else T)
         new_caches = []
         get = (lambda i: None) if caches is None else (lambda i: caches[i])
         sc = self.layer_scalar_args(x)

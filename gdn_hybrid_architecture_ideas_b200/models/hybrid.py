@@ -7,6 +7,8 @@ State-dict names follow the reference's control architecture (ced/model/control.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import torch
@@ -92,8 +94,18 @@ class HybridLM(nn.Module):
                 single_doc: bool = False) -> ModelOutput:
         """tokens (B, L) or bags (B, L, s); doc_ids (B, L). return_hidden: give the head input instead of logits
         (the fused loss consumes it). single_doc: the caller guarantees every row is one document (kernels skip
-        the document masks). dec_mask, T, capacity are accepted for call compatibility and ignored
+        the document masks). T: the pass count of a looped middle (models/recur.py; default loop.t_eval, or the cache's own T;
+        ignored by every other model). dec_mask and capacity are accepted for call compatibility and ignored
         (reference: ced/model/control.py:716-872)."""
+        if self.encoder.recur is not None:
+            if cache is not None:
+                if T is not None and T != cache.T:
+                    raise ValueError(f"this cache was prefilled at T = {cache.T}; a cached sequence keeps its pass count (got T = {T})")
+                T = cache.T
+            elif T is None:
+                T = int(os.environ.get("GHB_LOOP_T", self.cfg.loop.t_eval))
+        else:
+            T = None
         ctx, seq_state = sequence_context(doc_ids, cache.seq if cache else None)
         ctx.single_doc = bool(single_doc) and cache is None
         if varlen is not None:
@@ -111,22 +123,22 @@ class HybridLM(nn.Module):
             tp.batch_shape = (B, L)
             per = B * L // tp.world
             tokens = tokens.reshape(B * L, *tokens.shape[2:])[tp.rank * per:(tp.rank + 1) * per][None]     # this rank's token shard
-        h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state)
+        h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state, T=T)
         hidden = self.final_norm(h)
         logits = None if return_hidden else lm_head(hidden, self.head_weight())
         return ModelOutput(
             logits=logits, hidden_aux=hidden if return_hidden else None,
             kept=torch.zeros(B, L, dtype=torch.bool, device=tokens.device),
             n_dropped=torch.zeros(B, dtype=torch.long, device=tokens.device),
-            cache=ControlCache(seq=seq_state, encoder=caches) if return_cache else None)
+            cache=ControlCache(seq=seq_state, encoder=caches, T=T or 1) if return_cache else None)
 
     @torch.no_grad()
     def prefill(self, tokens, doc_ids, dec_mask=None, T=None) -> ModelOutput:
-        return self.forward(tokens, doc_ids, return_cache=True)
+        return self.forward(tokens, doc_ids, return_cache=True, T=T)
 
     @torch.no_grad()
     def extend(self, tokens, doc_ids, dec_mask, cache: ControlCache, T=None) -> ModelOutput:
-        return self.forward(tokens, doc_ids, cache=cache, return_cache=True)
+        return self.forward(tokens, doc_ids, cache=cache, return_cache=True, T=T)
 
 
 def build_model(cfg: ModelConfig) -> HybridLM:

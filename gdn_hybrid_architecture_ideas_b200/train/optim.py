@@ -18,7 +18,10 @@ from dataclasses import dataclass
 import torch
 
 NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gain", ".x0_gain", ".beta_proj.weight", ".beta_proj.bias",
-                     ".gamma_proj.weight", ".gamma_proj.bias")
+                     ".gamma_proj.weight", ".gamma_proj.bias",
+                     # a looped middle's injection (models/recur.py): B starts at the identity and w near 1, decay would pull both
+                     # away from their starts; A_log / dt_bias are covered by the GDN suffixes above
+                     "injection.B", ".recur_mix")
 ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
@@ -39,7 +42,7 @@ def no_decay_suffixes(o) -> tuple:
 def is_muon_param(name: str, p: torch.Tensor) -> bool:
     if p.ndim != 2 or name.endswith(("embed.weight", "conv_weight") + ADAMW_MATRIX_SUFFIXES):
         return False
-    return ".attn_res." not in name
+    return ".attn_res." not in name and "injection" not in name          # loop-boundary parameters stay on AdamW
 
 
 GDN_MUP_BASE_WIDTH = 512

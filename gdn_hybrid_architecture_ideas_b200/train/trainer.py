@@ -70,6 +70,18 @@ class Trainer:
         dtype = {"float32": torch.float32, "float64": torch.float64, "bfloat16": torch.bfloat16}[cfg.dtype]
         self.tp = None
         model_cfg = cfg.model
+        # A looped middle (models/recur.py): one pass count per optimizer step, drawn from loop.t_choices / t_probs; what it
+        # is not built together with is refused here, by key.
+        self.looped = bool(cfg.model.loop.recur_layers)
+        self.pass_count = 1
+        if self.looped:
+            clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
+                       "shape_schedule": bool(cfg.shape_schedule), "loop_switch_step": bool(cfg.loop_switch_step),
+                       "optimizer_sharding 'zero2' (its buckets follow one backward pass over the blocks)": cfg.optimizer_sharding == "zero2",
+                       "activation_checkpoint 'block'": cfg.activation_checkpoint == "block", "model.fp8.mode": cfg.model.fp8.mode != "none"}
+            hit = [k for k, v in clashes.items() if v]
+            if hit:
+                raise ValueError(f"model.loop.recur_layers (the looped middle) is not built together with: {', '.join(hit)}")
         if cfg.tensor_parallel > 1:
             from ..parallel import tp_model
 
@@ -249,6 +261,8 @@ class Trainer:
             kw.update(gdn_scale=s, gdn_beta_power=cfg.tst.gdn_resolution_gates == "E")
         if s > 1 and cfg.tst.token_scale_rope:
             kw.update(rope_scale=s)
+        if self.looped:
+            kw.update(T=self.pass_count)
         ac = torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast and not self.native)
         with ac:
             out = self.model(mb.tokens, mb.doc_ids, return_hidden=True, single_doc=mb.single_doc, **kw)
@@ -364,6 +378,10 @@ class Trainer:
         n_global, bad = self._global_counts(batch)
         if bad:
             self._halt_bad_batch(step)
+        if self.looped:
+            from ..models.recur import pass_count_for_step
+
+            self.pass_count = pass_count_for_step(cfg.model.loop, cfg.seed, step)
         lr = self.lr_at(step)
         if self.tst is not None:
             factor = self.tst.lr_factor(step)
@@ -386,6 +404,13 @@ class Trainer:
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        if self.looped:
+            m["T"] = self.pass_count
+            inj = self.model.encoder.recur_injection
+            if inj is not None and cfg.log_every and step % cfg.log_every == 0:
+                m["recur_injection"] = inj.summary()
+            if self.model.encoder.recur_mix is not None:
+                m["recur_mix"] = float(self.model.encoder.recur_mix.detach())
         if tst_event is not None:
             m["tst_switch"] = tst_event
         if host.numel() > 4:        # a logging step: gradient norm per parameter family, the depth-mix readers' state

@@ -327,3 +327,47 @@ def test_checkpoints_cross_between_the_trainers(reference, tmp_path):
     st = back.optimizer.state_dict()["state"]
     assert len(st) > 0 and all(float(v["step"]) == 3.0 for v in st.values())
     back.train_step()          # the loaded optimizer steps (every key torch's AdamW reads is in the file's groups)
+
+
+@pytest.mark.parametrize("injection,extra", [("none", {}), ("mix", {"recur_mix_init": 0.8}), ("parcae", {}),
+                                               ("parcae", {"recur_inject_b": "diag", "recur_state_init": "prelude", "recur_prelude_norm": False}), ("depth_mix", {})])
+def test_looped_middle_equals_the_reference(reference, injection, extra):
+    """The looped middle (loop.recur_layers) under every injection: state-dict keys and starts, logits and parameter
+    gradients at several pass counts, and the cache of a chunked read."""
+    cfg = C.tiny_control_config()
+    cfg.encoder.n_layers = 8
+    cfg.loop.recur_layers, cfg.loop.injection, cfg.loop.t_eval, cfg.loop.t_max = (2, 6), injection, 2, 3
+    cfg.loop.t_choices, cfg.loop.t_probs = [1, 2, 3], [0.25, 0.5, 0.25]
+    for k, v in extra.items():
+        setattr(cfg.loop, k, v)
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd)
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40)
+    for T in (1, 2, 3):
+        a, b = mine(tok, doc, T=T).logits, theirs(tok, doc, T=T).logits
+        assert (a - b).abs().max() < 1e-10, T
+        ga = torch.autograd.grad(a.logsumexp(-1).sum(), list(mine.parameters()), allow_unused=True)
+        gb = torch.autograd.grad(b.logsumexp(-1).sum(), list(theirs.parameters()), allow_unused=True)
+        for x, y in zip(ga, gb):
+            assert (x is None) == (y is None) and (x is None or (x - y).abs().max() < 1e-9)
+    assert torch.equal(mine(tok, doc).logits, mine(tok, doc, T=2).logits)                      # the default is loop.t_eval
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        full = mine(tok, doc, T=3).logits
+        out = mine.prefill(tok[:, :17], doc[:, :17], T=3)
+        ref_out = theirs.prefill(tok[:, :17], doc[:, :17], T=3)
+        parts = [out.logits]
+        for lo, hi in ((17, 18), (18, 40)):
+            out = mine.extend(tok[:, lo:hi], doc[:, lo:hi], None, out.cache)
+            ref_out = theirs.extend(tok[:, lo:hi], doc[:, lo:hi], None, ref_out.cache)
+            parts.append(out.logits)
+            assert (out.logits - ref_out.logits).abs().max() < 1e-10
+        assert (torch.cat(parts, 1) - full).abs().max() < 1e-9 and len(out.cache.encoder) == 2 + 3 * 4 + 2 and out.cache.T == 3
+        with pytest.raises(ValueError, match="keeps its pass count"):
+            mine.extend(tok[:, :2], doc[:, :2], None, out.cache, T=2)

@@ -688,3 +688,53 @@ def test_branch_and_stage_continue_another_run(tmp_path):
     late.optim.decay_fraction = 0.9            # would have decayed during the source's updates: refused
     with pytest.raises(ValueError, match="schedules must agree"):
         Trainer(late, tmp_path / "f").continue_from(kept)
+
+
+@pytest.mark.parametrize("injection", ["mix", "parcae", "depth_mix"])
+def test_looped_middle_trains_with_a_pass_count_per_step(tmp_path, injection):
+    """A looped middle through the trainer: one T per step from t_choices (a pure function of seed and step, so a resumed run
+    draws the same), recorded in the metrics; its own tensors train without weight decay on the injection; refusals by key."""
+    from gdn_hybrid_architecture_ideas_b200.models.recur import pass_count_for_step
+    from gdn_hybrid_architecture_ideas_b200.train.optim import param_groups
+
+    cfg = tiny_train_config(steps=6)
+    cfg.model = C.tiny_control_config()
+    cfg.model.encoder.n_layers = 8
+    lp = cfg.model.loop
+    lp.recur_layers, lp.injection, lp.t_eval, lp.t_choices, lp.t_probs = (2, 6), injection, 2, [1, 2, 3], [0.3, 0.4, 0.3]
+    cfg.metrics_jsonl, cfg.ckpt_every_steps = True, 3
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
+    start = {k: v.clone() for k, v in t.model.state_dict().items() if "recur" in k}
+    ms = [t.train_step() for _ in range(6)]
+    want = [pass_count_for_step(lp, cfg.seed, s) for s in range(6)]
+    assert [m["T"] for m in ms] == want and len(set(want)) > 1 and all(math.isfinite(m["loss"]) for m in ms)
+    moved = [k for k, v in t.model.state_dict().items() if "recur" in k and not torch.equal(v, start[k])]
+    assert moved, "the injection's tensors did not train"
+    groups = param_groups(t.model, cfg.optim)
+    names = {n: g["weight_decay"] for g in groups for n in g.get("names", [])}
+    for n, wd in names.items():
+        if n.endswith(("injection.B", ".recur_mix", "injection.A_log", "injection.dt_bias")):
+            assert wd == 0.0, n
+    # a resumed run continues with the same pass counts and ends in the same state
+    a = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    a.fit()
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(until_step=3)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 3
+    c.fit()
+    for (k, x), (_, y) in zip(a.model.state_dict().items(), c.model.state_dict().items()):
+        assert torch.equal(x, y), k
+    bad = copy.deepcopy(cfg)
+    bad.cuda_graphs = "microbatch"
+    with pytest.raises(ValueError, match="cuda_graphs"):
+        Trainer(bad, None)
+    bad = copy.deepcopy(cfg)
+    bad.model.encoder.attn_res = "block_entry"
+    with pytest.raises(ValueError, match="attn_res"):
+        Trainer(bad, None)
+    bad = copy.deepcopy(cfg)
+    bad.model.loop.recur_layers = ()
+    if injection != "parcae":
+        with pytest.raises(ValueError, match="looped middle"):
+            Trainer(bad, None)
