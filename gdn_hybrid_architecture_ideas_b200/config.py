@@ -708,6 +708,7 @@ _TRAIN_BUILT = {
     "loss.normalization": ("global_token_mean",),
     "loss.ce_form": ("standard", "fixed"),
     "head_impl": ("fused", "chunked"),
+    "head_precision": ("fp32", "bf16"),
     "activation_checkpoint": ("none", "layer", "block", "host", "host_overlap"),
     "freeze_trunk": (False,),
     "precision_switch": (False, True),

@@ -72,7 +72,9 @@ def _ce_grad_chunk(logits, targets, a, b, fixed: bool = False):
 
 class _FusedLinearCE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, hidden, weight, targets, a, b, chunk, fixed=False):
+    def forward(ctx, hidden, weight, targets, a, b, chunk, fixed=False, precision="fp32"):
+        from .head_precision import addmm_acc_, mm_acc
+
         dt = torch.promote_types(hidden.dtype, torch.float32)
         d = hidden.shape[-1]
         with torch.autocast(hidden.device.type, enabled=False):
@@ -88,10 +90,10 @@ class _FusedLinearCE(torch.autograd.Function):
             dW = torch.zeros_like(W)
             for lo in range(0, n, chunk):
                 hi = min(n, lo + chunk)
-                c, l, g = _ce_grad_chunk(h[lo:hi] @ W.T, t[lo:hi], a2[lo:hi], b1[lo:hi], fixed)
+                c, l, g = _ce_grad_chunk(mm_acc(h[lo:hi], W.T, precision), t[lo:hi], a2[lo:hi], b1[lo:hi], fixed)
                 ce[lo:hi], lse[lo:hi] = c, l
-                dh[lo:hi] = g @ W
-                dW.addmm_(g.T, h[lo:hi])
+                dh[lo:hi] = mm_acc(g, W, precision)
+                addmm_acc_(dW, g.T, h[lo:hi], precision)
             loss = ce.sum() + (b1 * lse * lse).sum()
         ctx.save_for_backward(dh, dW)
         ctx.meta = (hidden.dtype, hidden.shape, weight.dtype)
@@ -102,13 +104,17 @@ class _FusedLinearCE(torch.autograd.Function):
     def backward(ctx, g_loss, g_ce, g_lse):
         dh, dW = ctx.saved_tensors
         hd, hs, wd = ctx.meta
-        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None, None
+        return (dh * g_loss).to(hd).reshape(hs), (dW * g_loss).to(wd), None, None, None, None, None, None
 
 
-def fused_linear_ce(hidden, weight, targets, a, b, chunk: int | None = None, weight_lp=None, ce_form: str = "standard"):
+def fused_linear_ce(hidden, weight, targets, a, b, chunk: int | None = None, weight_lp=None, ce_form: str = "standard", precision: str = "fp32"):
     """hidden (..., d), weight (V, d), targets (...,) or (..., s), a like targets, b (...,) -> (loss, ce, lse) with
-    ce, lse per position and without gradient."""
+    ce, lse per position and without gradient. precision: the form of the PyTorch statements (train/head_precision.py); the
+    native kernels are the "bf16" form."""
+    from .head_precision import check_head_precision
+
     fixed = check_ce_form(ce_form)
+    check_head_precision(precision)
     if hidden.is_cuda:
         from .. import ops
 
@@ -116,10 +122,10 @@ def fused_linear_ce(hidden, weight, targets, a, b, chunk: int | None = None, wei
             from ..ops import native
 
             return native.fused_linear_ce(hidden, weight, targets, a, b, chunk or CHUNK, weight_lp, fixed)
-    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk or CHUNK, fixed)
+    return _FusedLinearCE.apply(hidden, weight, targets, a, b, chunk or CHUNK, fixed, precision)
 
 
-def chunked_ce(hidden, weight, targets, a, b, chunk: int = 1024, ce_form: str = "standard"):
+def chunked_ce(hidden, weight, targets, a, b, chunk: int = 1024, ce_form: str = "standard", precision: str = "fp32"):
     """Unfused head: checkpointed chunks of fp32 logits through autograd (reference: ced/train/chunked_loss.py:33-140).
     With the fixed form each term masks its own target column out of the log-sum-exp, so autograd's target gradient is
     -sigmoid(L') exactly (reference: ced/train/ce_fix.py:94-120)."""
@@ -133,8 +139,10 @@ def chunked_ce(hidden, weight, targets, a, b, chunk: int = 1024, ce_form: str = 
     a2, b1 = a.reshape(h.shape[0], -1), b.reshape(-1)
 
     def piece(hc, W, tc, ac, bc):
+        from .head_precision import head_linear
+
         dt = torch.promote_types(hc.dtype, torch.float32)
-        logits = F.linear(hc.to(dt), W.to(dt))
+        logits = head_linear(hc.to(dt), W.to(dt), precision)
         if fixed:
             tcl = tc.clamp(min=0)
             ces, lse = [], None

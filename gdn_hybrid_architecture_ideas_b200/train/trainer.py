@@ -284,10 +284,10 @@ class Trainer:
             a, b = valid * inv, valid * (z * inv)
         W = self.model.head_weight()
         if cfg.head_impl == "fused":
-            loss, ce, _ = fused_linear_ce(hidden, W, targets, a, b, cfg.head_chunk, self.model.head_weight_lp, cfg.loss.ce_form)
+            loss, ce, _ = fused_linear_ce(hidden, W, targets, a, b, cfg.head_chunk, self.model.head_weight_lp, cfg.loss.ce_form, cfg.head_precision)
             ce_sum = (ce.detach() if mb.multi_targets is not None else ce.detach()).sum()
         else:
-            loss, ce_sum = chunked_ce(hidden, W, targets, a, b, ce_form=cfg.loss.ce_form)
+            loss, ce_sum = chunked_ce(hidden, W, targets, a, b, ce_form=cfg.loss.ce_form, precision=cfg.head_precision)
             ce_sum = ce_sum.detach()
         return loss, ce_sum
 

@@ -738,3 +738,41 @@ def test_looped_middle_trains_with_a_pass_count_per_step(tmp_path, injection):
     if injection != "parcae":
         with pytest.raises(ValueError, match="looped middle"):
             Trainer(bad, None)
+
+
+def test_head_precision_bf16_rounds_the_operands_of_the_three_products(reference):
+    """`head_precision: bf16` on the PyTorch path: logits, dh and dW are exact products of operands rounded once to bfloat16,
+    accumulated in the compute dtype; equal to the reference's statement in float64; both heads agree; fp32 is untouched."""
+    from ced.train import head_precision as RH
+
+    from gdn_hybrid_architecture_ideas_b200.train import head_precision as HP
+    from gdn_hybrid_architecture_ideas_b200.train.fused_head import chunked_ce, fused_linear_ce
+
+    g = torch.Generator().manual_seed(0)
+    h = torch.randn(3, 7, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    W = torch.randn(40, 16, generator=g, dtype=torch.float64, requires_grad=True)
+    mine = HP.head_linear(h, W, "bf16")
+    theirs = RH.head_linear(h.detach().clone().requires_grad_(), W.detach().clone().requires_grad_(), "bf16")
+    assert torch.equal(mine, theirs) and not torch.equal(mine, torch.nn.functional.linear(h, W))
+    up = torch.randn(mine.shape, generator=g, dtype=torch.float64)
+    gh, gW = torch.autograd.grad(mine, (h, W), up)
+    r = lambda x: x.to(torch.bfloat16).to(torch.float64)
+    assert torch.equal(gh, r(up) @ r(W)) and torch.equal(gW, r(up).reshape(-1, 40).t() @ r(h).reshape(-1, 16))
+    assert torch.equal(HP.head_linear(h, W, "fp32"), torch.nn.functional.linear(h, W))
+    with pytest.raises(ValueError, match="head_precision"):
+        HP.head_linear(h, W, "fp8")
+    targets = torch.randint(0, 40, (3, 7), generator=g)
+    a, b = torch.full((3, 7), 0.1, dtype=torch.float64), torch.full((3, 7), 1e-4, dtype=torch.float64)
+    out = {}
+    for prec in HP.PRECISIONS:
+        for name, fn in (("fused", lambda: fused_linear_ce(h, W, targets, a, b, 8, precision=prec)[0]), ("chunked", lambda: chunked_ce(h, W, targets, a, b, 8, precision=prec)[0])):
+            loss = fn()
+            out[(prec, name)] = (loss.detach(), *torch.autograd.grad(loss, (h, W)))
+    for prec in HP.PRECISIONS:
+        for x, y in zip(out[(prec, "fused")], out[(prec, "chunked")]):
+            assert torch.allclose(x, y, atol=1e-12, rtol=1e-10), prec
+    assert not torch.allclose(out[("bf16", "fused")][0], out[("fp32", "fused")][0], atol=1e-9)
+    cfg = tiny_train_config(steps=2)
+    cfg.head_precision = "bf16"
+    t = Trainer(cfg, None)
+    assert math.isfinite(t.train_step()["loss"])
