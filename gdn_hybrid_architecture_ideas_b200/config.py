@@ -685,7 +685,6 @@ _BUILT = {
     "model.encoder.block_norm_gain": ("channel", "scalar"),
     "model.encoder.gdn_write_mix": ("none", "layer"),
     "model.encoder.gdn_write_variant": ("none", "qmix", "korig", "vonly", "kqmix", "qshare", "qshare_kv", "qshare_bd"),
-    "model.encoder.gdn_qmix_select_step": (0,),
     "model.encoder.residual_dtype": ("float32", "bf16"),
     "model.encoder.gdn_ccr_spacing": (0,),
     "model.loop.pass2_gate": ("none",),

@@ -244,7 +244,7 @@ class DecodeEngine:
                     xw = layer.mixer_in_norm(arms.write_query(sources) if arms.write_query is not None else sources[0])
                     xr = None
                     if arms.variant in READ_MIX_VARIANTS:
-                        xr = xw if arms.qmix_query is None else layer.mixer_in_norm(arms.qmix_query(sources))
+                        xr = xw if arms.qmix_query is None else layer.mixer_in_norm(arms.read_mix(sources))
                     kw = dict(arms=arms, x_write=xw, x_read=xr)
                 state = GDNState(conv_input=st["conv"], conv_doc=st["conv_doc"], S=st["S"])
                 mixed, new = layer.mixer(h, ctx, state, **kw)

@@ -25,6 +25,7 @@ from .depth_mix import DepthQuery, EntryLayer, LayerQueries
 from .gdn import READ_MIX_VARIANTS, GatedDeltaNet, GDNArms
 from .mlp import dense_ffn
 from .norms import RMSNorm, round_stream
+from .qmix_select import check_config as check_qmix_select, record_query_weights
 from .sequence import SeqContext
 
 
@@ -151,7 +152,7 @@ class EncoderLayer(nn.Module):
             x_write = self.mixer_in_norm(pre_w)
             x_read = None
             if arms.variant in READ_MIX_VARIANTS:
-                x_read = x_write if arms.qmix_query is None else self.mixer_in_norm(pre_q if pre_q is not None else arms.qmix_query(sources))
+                x_read = x_write if arms.qmix_query is None else self.mixer_in_norm(pre_q if pre_q is not None else arms.read_mix(sources))
             mixed, new_cache = self.mixer(h, ctx, cache, arms=arms, x_write=x_write, x_read=x_read, need_state=need_state)
         elif self.kind == "gdn":
             mixed, new_cache = self.mixer(h, ctx, cache, need_state=need_state)
@@ -187,6 +188,8 @@ class Encoder(nn.Module):
             for kind in enc.layer_kinds())
         self.block = enc.full_attn_interval
         self.block_entry = enc.attn_res == "block_entry"
+        check_qmix_select(cfg)
+        self.qmix_record: dict | None = None      # set for one forward by the trainer: every query mix's weight sums (models/qmix_select.py)
         self.block_every = enc.attn_res == "block"        # every sublayer reads the blocks
         self.ldm = enc.attn_res == "ldm"                  # linear depth memory: a per-position memory beside the stream
         self.activation_checkpoint = "none"
@@ -239,6 +242,8 @@ class Encoder(nn.Module):
                 if layer.kind == "gdn" and i > 0:
                     layer.gdn_arms = GDNArms(d, eps, has_query=i // S >= 1, variant=enc.gdn_write_variant)
                     layer.mixer.write_mix = "layer"
+                    if enc.gdn_qmix_select_step:
+                        layer.gdn_arms.register_qmix_keep(i // S + 1)
         elif enc.gdn_write_mix != "none":
             raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none' or 'layer'")
         # Canon layers: zeros as built; "uniform" draws each layer's taps from its own seeded CPU generator, so no other
@@ -367,7 +372,7 @@ class Encoder(nn.Module):
             if arms.write_query is not None:
                 keys.append((i, "w"))
                 readers.append(arms.write_query)
-            if arms.variant in READ_MIX_VARIANTS and arms.qmix_query is not None:
+            if arms.variant in READ_MIX_VARIANTS and arms.qmix_query is not None and not arms.qmix_static:
                 keys.append((i, "q"))
                 readers.append(arms.qmix_query)
         if len(readers) < 2 or len(readers) > 8 or any(r.heads > 1 for r in readers):
@@ -503,6 +508,8 @@ class Encoder(nn.Module):
                 layer = self.layers[i]
                 src = sources if getattr(layer, "gdn_arms", None) is not None else None
                 pre = (mixes.get((i, "w")), mixes.get((i, "q"))) if (src is not None and mixes) else None
+                if self.qmix_record is not None:
+                    record_query_weights(self.qmix_record, i, layer, src)
                 x, c = self._run(layer, x, ctx, get(i), src, need_state, scal(i), pre)
                 new_caches.append(c)
             sources = sources + [x - start]

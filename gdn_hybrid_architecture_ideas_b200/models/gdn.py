@@ -50,6 +50,42 @@ class GDNArms(nn.Module):
         if variant in READ_MIX_VARIANTS:
             self.qmix_lambda = nn.Parameter(torch.zeros(1))
             self.qmix_query = DepthQuery(d, eps) if has_query else None
+        self.qmix_static = False        # True once qmix_keep holds a choice (models/qmix_select.py)
+        self.n_sources = 0
+
+    def register_qmix_keep(self, n_sources: int) -> None:
+        """Under model.encoder.gdn_qmix_select_step, for a layer whose query mix reads more than two sources: the persistent
+        buffer qmix_keep ((2,) int64, -1 = not chosen) and a post-load hook that sets `qmix_static` from it, so every loader
+        of a state dict reads the form the weights were trained in (reference: ced/model/gdn_arms.py:616-641)."""
+        from .qmix_select import KEEP
+
+        self.n_sources = n_sources
+        if n_sources <= KEEP or getattr(self, "qmix_query", None) is None:
+            return
+        self.register_buffer("qmix_keep", torch.full((KEEP,), -1, dtype=torch.long))
+        self.register_load_state_dict_post_hook(_sync_qmix_static)
+
+    def chosen_sources(self) -> list | None:
+        """The chosen pair (ascending) or None before the choice; one host read."""
+        keep = getattr(self, "qmix_keep", None)
+        if keep is None or int(keep[0]) < 0:
+            return None
+        return [int(i) for i in keep.detach().cpu().tolist()]
+
+    def read_mix(self, sources: list) -> torch.Tensor:
+        """The query mix over `sources`: the softmax over all of them, or over the chosen pair once there is one."""
+        if self.qmix_static:
+            from .qmix_select import depth_mix_pair
+
+            return depth_mix_pair(sources, self.qmix_query, self.qmix_keep)
+        return self.qmix_query(sources)
+
+
+def _sync_qmix_static(module: "GDNArms", incompatible_keys) -> None:
+    chosen = module.chosen_sources()
+    if chosen is not None and not 0 <= chosen[0] < chosen[1] < module.n_sources:
+        raise ValueError(f"qmix_keep {chosen} is not 2 ascending sources of the layer's {module.n_sources}")
+    module.qmix_static = chosen is not None
 
 
 class GatedDeltaNet(nn.Module):

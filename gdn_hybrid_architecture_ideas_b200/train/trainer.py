@@ -167,6 +167,20 @@ class Trainer:
             from .zero_wgrad import ZeroWgradMonitor
 
             self.zero_wgrad = ZeroWgradMonitor(self.model)
+        # qmix's static top-2 query mix (models/qmix_select.py): the choice is made at the start of step S from one extra
+        # forward of the step's first micro-batch (reference: ced/train/trainer.py:1860-1876, 2420-2455).
+        self._qmix = self.model.encoder if cfg.model.encoder.gdn_qmix_select_step else None
+        self._qmix_chosen = None
+        if self._qmix is not None:
+            what = "model.encoder.gdn_qmix_select_step"
+            if self.dp is not None or self.tp is not None:
+                raise ValueError(f"{what} is not built with data or tensor parallelism: the choice is one process's statistic over its own rows")
+            if cfg.activation_checkpoint in ("block", "host", "host_overlap"):
+                raise ValueError(f"{what} is not built with activation_checkpoint {cfg.activation_checkpoint!r}: 'none' or 'layer'")
+            if cfg.cuda_graphs != "none":
+                raise ValueError(f"{what} is not built with cuda_graphs {cfg.cuda_graphs!r}: the choice is a host read and changes the captured forward")
+            if cfg.freeze_trunk:
+                raise ValueError(f"{what} is not built with freeze_trunk: the choice writes one of the trunk's tensors in a step")
         self._readout = None
         readout.check_readout_config(cfg)
         self._probe_readout = readout.Readout(self) if cfg.eval.readout_every else None      # the sample is read (and checked) before the run trains
@@ -314,6 +328,11 @@ class Trainer:
         ce_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         for lo in range(0, rows, micro):
             mb = batch if micro == rows else _slice(batch, lo, lo + micro)
+            if self._qmix is not None and lo == 0 and self.step >= cfg.model.encoder.gdn_qmix_select_step:
+                from ..models import qmix_select
+
+                if qmix_select.pending(self._qmix):      # once: the extra forward is discarded, nothing runs backward
+                    self._qmix_chosen = {"step": self.step, **qmix_select.choose(self._qmix, lambda: self._micro_loss(mb, max(n_global, 1)))}
             if self.graphs is not None:
                 loss, ce = self.graphs.micro(mb, n_global)
                 loss_sum += loss
@@ -419,10 +438,22 @@ class Trainer:
             if readers:
                 m["depth_readers"] = readers
         if cfg.log_stream_rms_every and self.step % cfg.log_stream_rms_every == 0:
-            with torch.no_grad(), monitor.StreamRMS(self.model) as rms:
-                probe = _slice(dev_batch, 0, 1)
-                self.model(probe.tokens, probe.doc_ids, return_hidden=True, single_doc=probe.single_doc)
+            if self._qmix is not None:
+                self._qmix.qmix_record = {}
+            try:
+                with torch.no_grad(), monitor.StreamRMS(self.model) as rms:
+                    probe = _slice(dev_batch, 0, 1)
+                    self.model(probe.tokens, probe.doc_ids, return_hidden=True, single_doc=probe.single_doc)
+            finally:
+                if self._qmix is not None:
+                    record, self._qmix.qmix_record = self._qmix.qmix_record, None
             m["stream_rms"] = rms.values()
+            if self._qmix is not None:      # each query mix's token-mean weights as the layer uses them now, on the probe row
+                from ..models import qmix_select
+
+                m["qmix_weights"] = qmix_select.weights_metrics(self._qmix, record)
+        if self._qmix_chosen is not None:
+            m["qmix_selection"], self._qmix_chosen = self._qmix_chosen, None
         if self.zero_wgrad is not None and self.step % cfg.log_zero_wgrad_every == 0:
             m.update(self.zero_wgrad.summary())
         self.last_metrics = m
@@ -628,6 +659,10 @@ class Trainer:
             for k, v in state["model"].items():
                 if k in own:
                     own[k].copy_(v)
+        if self.cfg.model.encoder.gdn_qmix_select_step:     # the layers' form follows the loaded buffers
+            from ..models import qmix_select
+
+            qmix_select.sync_static(self.model.encoder)
         self.flat.refresh_lp()
         if weights_only:
             return

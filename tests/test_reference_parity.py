@@ -371,3 +371,81 @@ def test_looped_middle_equals_the_reference(reference, injection, extra):
         assert (torch.cat(parts, 1) - full).abs().max() < 1e-9 and len(out.cache.encoder) == 2 + 3 * 4 + 2 and out.cache.T == 3
         with pytest.raises(ValueError, match="keeps its pass count"):
             mine.extend(tok[:, :2], doc[:, :2], None, out.cache, T=2)
+
+
+def test_qmix_static_pair_equals_the_reference(reference):
+    """qmix's static top-2 query mix (gdn_qmix_select_step): the buffer in the state dict, the recorded weight sums, the
+    choice, and logits / gradients / cached reads before and after it."""
+    from ced.model import gdn_arms as ref_arms
+
+    from gdn_hybrid_architecture_ideas_b200.models import qmix_select
+
+    cfg = C.tiny_full_config()
+    cfg.encoder.gdn_qmix_select_step = 2
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd)
+    keeps = [k for k in sd if k.endswith("qmix_keep")]
+    assert len(keeps) == 3 and all(sd[k].tolist() == [-1, -1] for k in keeps)        # the GDN layers of the third block: 3 sources
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40)
+
+    def same():
+        a, b = mine(tok, doc).logits, theirs(tok, doc).logits
+        assert (a - b).abs().max() < 1e-10
+        ga = torch.autograd.grad(a.logsumexp(-1).sum(), list(mine.parameters()), allow_unused=True)
+        gb = torch.autograd.grad(b.logsumexp(-1).sum(), list(theirs.parameters()), allow_unused=True)
+        for x, y in zip(ga, gb):
+            assert (x is None) == (y is None) and (x is None or (x - y).abs().max() < 1e-9)
+        return a
+
+    before = same()
+    assert qmix_select.pending(mine.encoder) and ref_arms.qmix_pending(theirs.encoder)
+    mine.encoder.qmix_record, theirs.encoder.qmix_record = {}, {}
+    mine(tok, doc), theirs(tok, doc)
+    rec, ref_rec = mine.encoder.qmix_record, theirs.encoder.qmix_record
+    mine.encoder.qmix_record = theirs.encoder.qmix_record = None
+    assert sorted(rec) == sorted(ref_rec) and len(rec) == 6          # every layer with a query mix of its own (blocks 2 and 3)
+    for i in rec:
+        assert rec[i][1] == ref_rec[i][1] == 80 and (rec[i][0] - ref_rec[i][0]).abs().max() < 1e-9
+        assert abs(float(rec[i][0].sum()) - 80) < 1e-9
+    chosen, ref_chosen = qmix_select.select_pairs(mine.encoder, rec), ref_arms.select_qmix_pairs(theirs.encoder, ref_rec)
+    assert list(chosen) == list(ref_chosen) == [8, 9, 10]
+    assert all(chosen[i]["pair"] == ref_chosen[i]["pair"] for i in chosen)
+    assert not qmix_select.pending(mine.encoder) and qmix_select.select_pairs(mine.encoder, rec) == {}
+    after = same()
+    assert (after - before).abs().max() > 1e-6                         # the third source no longer reaches the query rows
+    log = qmix_select.weights_metrics(mine.encoder, rec)
+    assert log["chosen"][-3:] == [chosen[i]["pair"] for i in chosen] and log["chosen"][:3] == [None] * 3 and log["n_sources"] == [2] * 3 + [3] * 3
+    # the state dict carries the choice: a new model reads the pair form
+    torch.manual_seed(0)
+    again = build_model(cfg).double()
+    assert not again.encoder.layers[8].gdn_arms.qmix_static
+    again.load_state_dict(mine.state_dict())
+    assert again.encoder.layers[8].gdn_arms.qmix_static and again.encoder.layers[8].gdn_arms.chosen_sources() == chosen[8]["pair"]
+    assert torch.equal(again(tok, doc).logits, after)
+    bad = mine.state_dict()
+    bad[keeps[0]] = torch.tensor([1, 1])
+    with pytest.raises(ValueError, match="ascending"):
+        again.load_state_dict(bad)
+    # after the choice the recorded weights are the pair's, zero on the third source
+    mine.encoder.qmix_record = {}
+    mine(tok, doc)
+    rec2, mine.encoder.qmix_record = mine.encoder.qmix_record, None
+    left_out = ({0, 1, 2} - set(chosen[9]["pair"])).pop()
+    assert float(rec2[9][0][left_out]) == 0 and abs(float(rec2[9][0].sum()) - 80) < 1e-9
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        out, ref_out = mine.prefill(tok[:, :17], doc[:, :17]), theirs.prefill(tok[:, :17], doc[:, :17])
+        out, ref_out = mine.extend(tok[:, 17:], doc[:, 17:], None, out.cache), theirs.extend(tok[:, 17:], doc[:, 17:], None, ref_out.cache)
+        assert (out.logits - ref_out.logits).abs().max() < 1e-10 and (out.logits - after[:, 17:]).abs().max() < 1e-9
+    for key, value, match in (("gdn_write_variant", "none", "qmix"), ("gdn_qmix_select_step", -1, "0 \\(off\\)"), ("gdn_qmix_select_step", True, "0 \\(off\\)")):
+        wrong = C.tiny_full_config()
+        wrong.encoder.gdn_qmix_select_step = 2
+        setattr(wrong.encoder, key, value)
+        with pytest.raises(ValueError, match=match):
+            build_model(wrong)

@@ -776,3 +776,43 @@ def test_head_precision_bf16_rounds_the_operands_of_the_three_products(reference
     cfg.head_precision = "bf16"
     t = Trainer(cfg, None)
     assert math.isfinite(t.train_step()["loss"])
+
+
+def test_qmix_static_pair_is_chosen_at_its_step_and_survives_a_resume(tmp_path):
+    """model.encoder.gdn_qmix_select_step S: before step S the full query mix; the step-S record names each layer's pair;
+    the pair sits in the checkpoint, a resume trains on in the pair form bit for bit; refused with what it is not built with."""
+    cfg = tiny_train_config()
+    cfg.model.encoder.gdn_qmix_select_step, cfg.log_stream_rms_every, cfg.micro_batch_size = 2, 2, 2
+    a = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    arms = [a.model.encoder.layers[i].gdn_arms for i in (8, 9, 10)]
+    m0 = a.train_step()
+    m1 = a.train_step()         # the stream log's cadence counts finished steps: the records of step indices 1 and 3 carry it
+    assert "qmix_selection" not in m0 and "qmix_selection" not in m1 and all(x.chosen_sources() is None for x in arms)
+    assert m1["qmix_weights"]["chosen"] == [None] * 6 and all(abs(sum(w) - 1) < 1e-6 for w in m1["qmix_weights"]["weights"])
+    m2 = a.train_step()
+    sel = m2["qmix_selection"]
+    assert sel["step"] == 2 and sel["layers"] == [8, 9, 10] and sel["tokens"] == 2 * 48
+    assert [x.chosen_sources() for x in arms] == sel["pair"] and all(len(p) == 2 and p[0] < p[1] for p in sel["pair"])
+    for w, p in zip(sel["weights"], sel["pair"]):       # the two largest token-means, ties to the lower source
+        assert sorted(sorted(range(3), key=lambda s: (-w[s], s))[:2]) == p
+    m3 = a.train_step()
+    assert "qmix_selection" not in m3 and m3["qmix_weights"]["chosen"][-3:] == sel["pair"]
+    for w, p in zip(m3["qmix_weights"]["weights"][-3:], sel["pair"]):
+        assert w[({0, 1, 2} - set(p)).pop()] == 0 and abs(sum(w) - 1) < 1e-6
+    a.fit()
+    assert "qmix_selection" not in a.last_metrics
+    first = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    first.fit(3)                                           # stops after the choice, with a checkpoint
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert not any(x.qmix_static for x in (b.model.encoder.layers[i].gdn_arms for i in (8, 9, 10)))
+    assert b.resume_from_checkpoint() and b.step == 3
+    assert [b.model.encoder.layers[i].gdn_arms.chosen_sources() for i in (8, 9, 10)] == sel["pair"]
+    assert all(b.model.encoder.layers[i].gdn_arms.qmix_static for i in (8, 9, 10))
+    b.fit()
+    wa, wb = weights(a), weights(b)
+    assert all(torch.equal(wa[k], wb[k]) for k in wa)
+    for key, value, match in (("activation_checkpoint", "block", "activation_checkpoint"), ("cuda_graphs", "microbatch", "cuda_graphs")):
+        bad = copy.deepcopy(cfg)
+        setattr(bad, key, value)
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
