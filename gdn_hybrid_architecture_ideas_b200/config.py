@@ -177,6 +177,72 @@ class _EncoderLayout:
             out.append(dataclasses.replace(self.gdn, n_k_heads=hk, n_v_heads=hv, k_head_dim=hd, v_head_dim=hd))
         return out
 
+    def dprod_carry(self) -> list:
+        """Which value heads of each GDN layer carry Gated DeltaProduct's extra steps, bottom first. None for every layer at
+        n_h 1 (the placement keys must then be at their defaults); else a tuple of value-head indices against the layer's
+        own shape: () for a layer that does not carry, every head for one that carries as a whole, a union of whole key
+        groups for one that carries some. `dprod.layers`: the GDN ordinals that carry (() = all); `dprod.heads` m: the
+        first m value heads of a carrying layer (0 = all); `dprod.heads_by_layer` {ordinal: heads} wins over `heads`
+        (reference: ced/config.py:775-834)."""
+        d, shapes = self.gdn.dprod, self.gdn_shapes()
+        n = len(shapes)
+        used = [k for k, on in (("layers", d.layers != ()), ("heads", d.heads != 0), ("heads_by_layer", d.heads_by_layer != {})) if on]
+        if d.n_h == 1:
+            if used:
+                raise ValueError(f"model.encoder.gdn.dprod.{', '.join(used)} set with n_h 1: the placement keys are read only with n_h >= 2")
+            return [None] * n
+        layers = tuple(d.layers) if isinstance(d.layers, (list, tuple)) else d.layers
+        if not (isinstance(layers, tuple) and all(type(i) is int and 0 <= i < n for i in layers) and list(layers) == sorted(set(layers))):
+            raise ValueError(f"model.encoder.gdn.dprod.layers {d.layers!r}: distinct GDN ordinals among the encoder's {n} GDN layers "
+                             f"(0 .. {n - 1}) in ascending order, or () for every layer")
+        if type(d.heads) is not int or d.heads < 0:
+            raise ValueError(f"model.encoder.gdn.dprod.heads {d.heads!r}: an integer >= 0 (0: every value head of a carrying layer)")
+        if not isinstance(d.heads_by_layer, dict):
+            raise ValueError(f"model.encoder.gdn.dprod.heads_by_layer {d.heads_by_layer!r}: a mapping {{GDN ordinal: [value heads]}}")
+        table = {int(k) if isinstance(k, str) and k.isdigit() else k: v for k, v in d.heads_by_layer.items()}
+        carrying = set(layers) if layers else set(range(n))
+        stray = [k for k in table if type(k) is not int or k not in carrying]
+        if stray:
+            raise ValueError(f"model.encoder.gdn.dprod.heads_by_layer keys {stray!r}: ordinals of layers that carry the extra steps ({sorted(carrying)!r})")
+        out = []
+        for i in range(n):
+            if i not in carrying:
+                out.append(())
+                continue
+            hk, hv = shapes[i].n_k_heads, shapes[i].n_v_heads
+            g = hv // hk
+            if i in table:
+                heads = table[i]
+                if not (isinstance(heads, (list, tuple)) and len(heads) > 0 and all(type(h) is int and 0 <= h < hv for h in heads)
+                        and list(heads) == sorted(set(heads))):
+                    raise ValueError(f"model.encoder.gdn.dprod.heads_by_layer[{i}] {heads!r}: distinct value heads among this layer's {hv} "
+                                     f"(0 .. {hv - 1}) in ascending order, at least one")
+                chosen = tuple(heads)
+            elif d.heads:
+                if d.heads % g or d.heads > hv:
+                    raise ValueError(f"model.encoder.gdn.dprod.heads {d.heads}: a multiple of the layer's {g} value heads a key head and at "
+                                     f"most its {hv} value heads (GDN layer {i})")
+                chosen = tuple(range(d.heads))
+            else:
+                chosen = tuple(range(hv))
+            cut = [k for k in sorted({h // g for h in chosen}) if not all(h in chosen for h in range(k * g, (k + 1) * g))]
+            if cut:
+                raise ValueError(f"model.encoder.gdn.dprod value heads {list(chosen)!r} of GDN layer {i}: key head(s) {cut!r} would be cut "
+                                 f"(a key head serves {g} consecutive value heads; the rule takes whole key groups)")
+            out.append(chosen)
+        return out
+
+    def gdn_layer_configs(self) -> list:
+        """(GDNConfig, carrying heads or None) each GDN layer is built from: `gdn_shapes()` with the placement applied. A layer
+        that does not carry gets the default DeltaProductConfig (n_h 1: the plain layer); one that carries gets the model's
+        own with the placement keys reset; the heads are None where every head carries (reference: ced/config.py:836-850)."""
+        shapes, carry, d = self.gdn_shapes(), self.dprod_carry(), self.gdn.dprod
+        if d.n_h == 1 or (d.layers == () and d.heads == 0 and d.heads_by_layer == {}):
+            return [(c, None) for c in shapes]
+        own = dataclasses.replace(d, layers=(), heads=0, heads_by_layer={})
+        return [(dataclasses.replace(c, dprod=own if h else DeltaProductConfig()), None if not h or len(h) == c.n_v_heads else tuple(h))
+                for c, h in zip(shapes, carry)]
+
     def global_attention(self) -> list["AttentionConfig"]:
         """Attention config of each global layer, bottom first; a layer listed in nope_global_layers gets a copy with
         rope_fraction 0 and no distance cap (position-free attention)."""
@@ -686,7 +752,6 @@ _BUILT = {
     "model.encoder.gdn_write_mix": ("none", "layer"),
     "model.encoder.gdn_write_variant": ("none", "qmix", "korig", "vonly", "kqmix", "qshare", "qshare_kv", "qshare_bd"),
     "model.encoder.residual_dtype": ("float32", "bf16"),
-    "model.encoder.gdn_ccr_spacing": (0,),
     "model.loop.pass2_gate": ("none",),
     "model.loop.segment_passes": (None,),
     "model.loop.unscored_passes": (None,),

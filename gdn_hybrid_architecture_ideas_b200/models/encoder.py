@@ -20,6 +20,7 @@ import torch.nn as nn
 from .. import ops
 from ..config import ModelConfig
 from . import act_checkpoint
+from . import ccr as ccr_mod
 from .attention import GatedAttention
 from .depth_mix import DepthQuery, EntryLayer, LayerQueries
 from .gdn import READ_MIX_VARIANTS, GatedDeltaNet, GDNArms
@@ -122,7 +123,8 @@ class EncoderLayer(nn.Module):
         self.mlp_in_norm = RMSNorm(d, eps, gain=gain)
         self.mlp_out_norm = RMSNorm(d, eps, gain=gain)
         if kind == "gdn":
-            self.mixer = GatedDeltaNet(d, gdn or cfg.encoder.gdn, eps, norm_gain=gain)
+            gdn_cfg, carry = gdn if isinstance(gdn, tuple) else (gdn or cfg.encoder.gdn, None)
+            self.mixer = GatedDeltaNet(d, gdn_cfg, eps, norm_gain=gain, dprod_carry=carry)
         elif kind == "attention":
             self.mixer = GatedAttention(d, attention or cfg.encoder.attention, eps)
         else:
@@ -131,10 +133,11 @@ class EncoderLayer(nn.Module):
         self.canon = CanonLayer(d, cfg.encoder.canon_kernel) if kind == "attention" and cfg.encoder.canon_kernel else None
 
     def forward(self, x: torch.Tensor, ctx: SeqContext, cache=None, sources: list | None = None, need_state: bool = True,
-                scalars: tuple | None = None, premixed: tuple | None = None):
+                scalars: tuple | None = None, premixed: tuple | None = None, ccr=None):
         """scalars: (x0, a - 1, b) of this layer's residual scalars, applied as the last term of the layer's own sum.
         premixed: (write mix, query mix) of this layer over `sources`, already formed by the stack (one kernel for all the
-        readers of a block); an entry that is None is formed here."""
+        readers of a block); an entry that is None is formed here. ccr: the record of the GDN layer this one
+        cross-reads (models/ccr.py); a writer leaves its own in the new cache entry's `ccr`."""
         x_in = x
         h, x = ops.prenorm(x, self.mixer_in_norm.weight, self.mixer_in_norm.eps)      # x: the stream, now read by the residual add only
         if self.canon is not None:
@@ -143,7 +146,9 @@ class EncoderLayer(nn.Module):
             h, canon_input, canon_doc = self.canon(h, ctx.doc, None if cache is None else cache.canon_input,
                                                    None if cache is None else cache.canon_doc)
         arms: GDNArms | None = getattr(self, "gdn_arms", None)
-        if arms is not None:
+        if arms is not None and arms.write_mix == "none":       # the cross-read alone
+            mixed, new_cache = self.mixer(h, ctx, cache, arms=arms, need_state=need_state, ccr=ccr)
+        elif arms is not None:
             if sources is None:
                 raise ValueError("a GDN layer with write/query mixes is called with the finished blocks (sources)")
             pre_w, pre_q = premixed if premixed is not None else (None, None)
@@ -153,7 +158,7 @@ class EncoderLayer(nn.Module):
             x_read = None
             if arms.variant in READ_MIX_VARIANTS:
                 x_read = x_write if arms.qmix_query is None else self.mixer_in_norm(pre_q if pre_q is not None else arms.read_mix(sources))
-            mixed, new_cache = self.mixer(h, ctx, cache, arms=arms, x_write=x_write, x_read=x_read, need_state=need_state)
+            mixed, new_cache = self.mixer(h, ctx, cache, arms=arms, x_write=x_write, x_read=x_read, need_state=need_state, ccr=ccr)
         elif self.kind == "gdn":
             mixed, new_cache = self.mixer(h, ctx, cache, need_state=need_state)
         else:
@@ -181,7 +186,7 @@ class Encoder(nn.Module):
         if enc.gdn_shape_by_layer and enc.gdn_write_mix != "none":
             raise ValueError("model.encoder.gdn_shape_by_layer is not built with model.encoder.gdn_write_mix "
                              "(reference: ced/model/gdn_dprod_place.py:185-203)")
-        per_global, per_gdn = iter(enc.global_attention()), iter(enc.gdn_shapes())
+        per_global, per_gdn = iter(enc.global_attention()), iter(enc.gdn_layer_configs())
         self.layers = nn.ModuleList(
             EncoderLayer(kind, cfg, scale, attention=next(per_global) if kind == "attention" else None,
                          gdn=next(per_gdn) if kind == "gdn" else None)
@@ -235,17 +240,28 @@ class Encoder(nn.Module):
                 if opens or closes:
                     layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1, heads=enc.attn_res_heads,
                                                 query_hidden=query_hidden)
-        if enc.gdn_write_mix == "layer":
-            if not self.block_entry:
-                raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry'")
-            for i, layer in enumerate(self.layers):
-                if layer.kind == "gdn" and i > 0:
-                    layer.gdn_arms = GDNArms(d, eps, has_query=i // S >= 1, variant=enc.gdn_write_variant)
-                    layer.mixer.write_mix = "layer"
-                    if enc.gdn_qmix_select_step:
-                        layer.gdn_arms.register_qmix_keep(i // S + 1)
-        elif enc.gdn_write_mix != "none":
+        if enc.gdn_write_mix not in ("none", "layer"):
             raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none' or 'layer'")
+        if enc.gdn_write_mix == "layer" and not self.block_entry:
+            raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry'")
+        ccr_mod.check_config(cfg)
+        reads, writes = ccr_mod.sources(cfg), set(ccr_mod.writers(cfg))
+        self.ccr = bool(reads)
+        for i, layer in enumerate(self.layers):
+            if layer.kind != "gdn":
+                continue
+            write = "layer" if enc.gdn_write_mix == "layer" and i > 0 else "none"
+            if write == "none" and i not in reads and i not in writes:
+                continue
+            g = enc.gdn
+            cross = None if not self.ccr else dict(
+                read=i in reads, write=i in writes, spacing=enc.gdn_ccr_spacing, layer=i, source=reads.get(i), target=enc.gdn_ccr_target,
+                translator=enc.gdn_ccr_translator, gate_init=enc.gdn_ccr_gate_init, gate_floor=enc.gdn_ccr_gate_floor,
+                hk=g.n_k_heads, hv=g.n_v_heads, dk=g.k_head_dim)
+            layer.gdn_arms = GDNArms(d, eps, has_query=i // S >= 1 if S > 0 else False, variant=enc.gdn_write_variant, write_mix=write, ccr=cross)
+            layer.mixer.write_mix, layer.mixer.arms_attached = write, True
+            if enc.gdn_qmix_select_step:
+                layer.gdn_arms.register_qmix_keep(i // S + 1)
         # Canon layers: zeros as built; "uniform" draws each layer's taps from its own seeded CPU generator, so no other
         # parameter's start changes (reference: ced/model/canon.py:101-115, ced/model/control.py:1195-1243).
         K = enc.canon_kernel
@@ -314,6 +330,30 @@ class Encoder(nn.Module):
         h.forward_enter(b)
         if torch.is_grad_enabled() and x.requires_grad:
             x.register_hook(lambda g, b=b: h.backward_done(b))
+
+    def _run_walk(self, walk, layer, x, ctx, cache, sources, need_state, scalars=None, premixed=None):
+        """`_run` for a stack with the checkpoint cross-read: a layer that takes part is called with the record it reads
+        and its own record is taken out of its new cache entry for the layers after it (models/ccr.py `Walk`). Under
+        activation_checkpoint "layer" the record is an input and an output of the layer's checkpointed call."""
+        arms = getattr(layer, "gdn_arms", None)
+        if walk is None or arms is None or not (arms.ccr_read or arms.ccr_write):
+            return self._run(layer, x, ctx, cache, sources, need_state, scalars, premixed)
+        rec = walk.record_in(arms)
+        mode = self.activation_checkpoint
+        if mode != "none" and cache is None and torch.is_grad_enabled() and x.requires_grad:
+            if mode not in ccr_mod.CHECKPOINT_MODES:
+                raise ValueError(f"model.encoder.gdn_ccr_spacing runs with activation_checkpoint {ccr_mod.CHECKPOINT_MODES}, not {mode!r}")
+
+            def call(x_, states, slot, *src):
+                r = None if states is None else ccr_mod.Record(states, slot, rec.source)
+                y_, c_ = layer(x_, ctx, None, list(src) if src else None, False, None, None, r)
+                return y_ if c_.ccr is None else (y_, c_.ccr.states, c_.ccr.slot)
+            out = act_checkpoint.run_checkpointed(call, x, None if rec is None else rec.states, None if rec is None else rec.slot, *(sources or ()))
+            y, own = (out, None) if isinstance(out, torch.Tensor) else (out[0], ccr_mod.Record(out[1], out[2], arms.layer))
+            walk.hand_record(arms, own)
+            return y, None
+        y, new_cache = layer(x, ctx, cache, sources, need_state, None, premixed, rec)
+        return y, walk.hand(arms, new_cache)
 
     def _run(self, layer, x, ctx, cache, sources, need_state, scalars=None, premixed=None):
         """One layer call under the stack's activation memory mode (models/act_checkpoint.py)."""
@@ -462,6 +502,9 @@ class Encoder(nn.Module):
             return self.forward_recur(x, ctx, caches, need_state, self.cfg.loop.t_eval if T is None else T)
         new_caches = []
         get = (lambda i: None) if caches is None else (lambda i: caches[i])
+        walk = ccr_mod.Walk() if self.ccr else None
+        if walk is not None and self.activation_checkpoint not in ccr_mod.CHECKPOINT_MODES and caches is None and torch.is_grad_enabled() and x.requires_grad:
+            raise ValueError(f"model.encoder.gdn_ccr_spacing runs with activation_checkpoint {ccr_mod.CHECKPOINT_MODES}, not {self.activation_checkpoint!r}")
         sc = self.layer_scalar_args(x)
         scal = (lambda i: None) if sc is None else (lambda i: sc[i])
         if self.block_every:
@@ -480,7 +523,7 @@ class Encoder(nn.Module):
             for i, layer in enumerate(self.layers):
                 if self.block > 0 and i % self.block == 0 and len(self.layers) % self.block == 0:
                     self._stage(i // self.block, x)
-                x, c = self._run(layer, x, ctx, get(i), None, need_state, scal(i))
+                x, c = self._run_walk(walk, layer, x, ctx, get(i), None, need_state, scal(i))
                 new_caches.append(c)
             return x, new_caches
         sources = [x]
@@ -510,7 +553,7 @@ class Encoder(nn.Module):
                 pre = (mixes.get((i, "w")), mixes.get((i, "q"))) if (src is not None and mixes) else None
                 if self.qmix_record is not None:
                     record_query_weights(self.qmix_record, i, layer, src)
-                x, c = self._run(layer, x, ctx, get(i), src, need_state, scal(i), pre)
+                x, c = self._run_walk(walk, layer, x, ctx, get(i), src, need_state, scal(i), pre)
                 new_caches.append(c)
             sources = sources + [x - start]
         last = self.layers[-1].attn_res

@@ -33,23 +33,41 @@ class GDNState:
     conv_input: torch.Tensor   # (B, K-1, C) last pre-conv inputs
     conv_doc: torch.Tensor     # (B, K-1) their document ids (-1: none)
     S: torch.Tensor | None     # (B, Hv, dk, dv)
+    ckpt: torch.Tensor | None = None    # a cross-read writer only: the checkpoint the next token reads (B, Hv, dk, dv)
+    ccr: object | None = None           # the record a writer's call hands its readers; taken out by the stack, never cached
 
 
 class GDNArms(nn.Module):
-    """Parameters of one GDN layer's write mix (and, for qmix/kqmix, query mix): lambda scalars and, from the second
-    block on, a depth query over the finished blocks. All zeros at init, so the layer starts as the plain layer."""
+    """What one GDN layer holds of the write / query mixes and of the checkpoint cross-read: the write mix's lambda and,
+    from the second block on, its depth query over the finished blocks; for qmix / kqmix the same for the query mix; for
+    a cross-read reader its gate (H_v,) and, with a translator, D = M - I (H_k, d_k, d_k). Lambdas, queries and D are zeros
+    at the start and the gates start at `gate_init` (0 unless asked), so the layer starts as the plain layer.
 
-    def __init__(self, d: int, eps: float, has_query: bool, variant: str):
+    ccr: None, or a dict(read, write, spacing, layer, source, target, translator, gate_init, gate_floor, hk, hv, dk) of
+    plain attributes (models/ccr.py); write_mix "none": a layer that only takes part in the cross-read."""
+
+    def __init__(self, d: int, eps: float, has_query: bool, variant: str, write_mix: str = "layer", ccr: dict | None = None):
         super().__init__()
         from .depth_mix import DepthQuery
 
-        self.write_mix = "layer"
-        self.variant = variant
-        self.write_query = DepthQuery(d, eps) if has_query else None
-        self.write_lambda = nn.Parameter(torch.zeros(1))
-        if variant in READ_MIX_VARIANTS:
+        self.write_mix = write_mix
+        self.variant = variant if write_mix != "none" else "none"
+        self.write_query = DepthQuery(d, eps) if has_query and write_mix != "none" else None
+        if write_mix != "none":
+            self.write_lambda = nn.Parameter(torch.zeros(1))
+        if self.variant in READ_MIX_VARIANTS:
             self.qmix_lambda = nn.Parameter(torch.zeros(1))
             self.qmix_query = DepthQuery(d, eps) if has_query else None
+        c = ccr or {}
+        self.ccr_read, self.ccr_write, self.spacing = bool(c.get("read")), bool(c.get("write")), int(c.get("spacing", 0))
+        self.layer, self.ccr_source, self.ccr_target = c.get("layer"), c.get("source"), c.get("target", "previous")
+        self.translator = c.get("translator", "none") if self.ccr_read else "none"
+        self.gate_floor = float(c.get("gate_floor", 0.0)) if self.ccr_read else 0.0
+        if self.ccr_read:
+            init = float(c.get("gate_init", 0.0))
+            self.ccr_gate = nn.Parameter(torch.zeros(c["hv"]) if init == 0 else torch.full((c["hv"],), init))
+            if self.translator == "key_head":
+                self.ccr_translator_delta = nn.Parameter(torch.zeros(c["hk"], c["dk"], c["dk"]))
         self.qmix_static = False        # True once qmix_keep holds a choice (models/qmix_select.py)
         self.n_sources = 0
 
@@ -89,7 +107,7 @@ def _sync_qmix_static(module: "GDNArms", incompatible_keys) -> None:
 
 
 class GatedDeltaNet(nn.Module):
-    def __init__(self, d_model: int, cfg: GDNConfig, norm_eps: float, norm_gain: str = "channel"):
+    def __init__(self, d_model: int, cfg: GDNConfig, norm_eps: float, norm_gain: str = "channel", dprod_carry: tuple | None = None):
         super().__init__()
         if cfg.n_v_heads % cfg.n_k_heads:
             raise ValueError("gdn.n_v_heads must be a multiple of gdn.n_k_heads")
@@ -122,12 +140,13 @@ class GatedDeltaNet(nn.Module):
         bound = 1.0 / math.sqrt(cfg.conv_kernel)
         nn.init.uniform_(self.conv_weight, -bound, bound)
         self.write_mix = "none"
+        self.arms_attached = False      # set by the encoder on a layer that holds GDNArms (a write mix, a cross-read, or both)
         # The erase direction (gdn.erase.mode 'eda'): its tensors come last and draw nothing from the global stream.
         gdn_erase.check_config(cfg)
         self.erase = gdn_erase.EraseGate(d_model, cfg) if gdn_erase.is_on(cfg) else None
         # Gated DeltaProduct (gdn.dprod.n_h >= 2): the extra steps' tensors, from a stream of their own as well.
         gdn_dprod.check_config(cfg)
-        self.dprod = gdn_dprod.DeltaProductSteps(d_model, cfg) if gdn_dprod.is_on(cfg) else None
+        self.dprod = gdn_dprod.build_steps(d_model, cfg, dprod_carry)
 
     @torch.no_grad()
     def reset_gate_parameters(self, scheme: str) -> None:
@@ -156,7 +175,7 @@ class GatedDeltaNet(nn.Module):
         reading the input its variant assigns."""
         hk, dk = self.cfg.n_k_heads, self.cfg.k_head_dim
         nq, C = hk * dk, self.conv_channels
-        if arms is None:
+        if arms is None or arms.write_mix == "none":
             return self.in_proj_qkv(x), self.in_proj_a(x), self.in_proj_b(x)
         v = arms.variant
         W = self.in_proj_qkv
@@ -186,13 +205,16 @@ class GatedDeltaNet(nn.Module):
     # ------------------------------------------------------------------ forward
 
     def forward(self, x: torch.Tensor, ctx: SeqContext, state: GDNState | None = None, arms: GDNArms | None = None,
-                x_write: torch.Tensor | None = None, x_read: torch.Tensor | None = None, need_state: bool = True):
+                x_write: torch.Tensor | None = None, x_read: torch.Tensor | None = None, need_state: bool = True, ccr=None):
         """x (B, L, d) normed layer input. Returns (y, GDNState). state: the cache of earlier chunks (None: the row
-        starts here). need_state False (training) lets the kernel skip the final state."""
-        if (arms is None) != (self.write_mix == "none"):
-            raise ValueError("a GDN layer with write/query mixes is called with its arms (through its encoder layer)")
+        starts here). need_state False (training) lets the kernel skip the final state. ccr: the record of the layer
+        this one cross-reads (models/ccr.py), for a reader only."""
+        if (arms is None) == self.arms_attached:
+            raise ValueError("a GDN layer with write/query mixes or the cross-read is called with its arms (through its encoder layer)")
         if self.kda is not None or self.erase is not None or self.dprod is not None:
             return self.forward_kda(x, ctx, state, arms)
+        if arms is not None and (arms.ccr_read or arms.ccr_write):
+            return self.forward_ccr(x, ctx, state, arms, x_write, x_read, ccr)
         B, L = ctx.doc.shape       # the input may be a token shard (tensor parallel); projections return all tokens
         cfg = self.cfg
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
@@ -213,6 +235,43 @@ class GatedDeltaNet(nn.Module):
         z = self.in_proj_z(x).view(B, L, hv, dv)
         y = self.out_proj(self.norm(o, z).flatten(2))
         return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S)
+
+    def forward_ccr(self, x, ctx: SeqContext, state: GDNState | None, arms, x_write, x_read, rec):
+        """The layer under the checkpoint cross-read (models/ccr.py): the scalar layer's input preparation, gates and
+        output norm; a writer's delta rule also takes the states its readers' checkpoints name, a reader adds
+        gate (*) ckpt^T q to the rule's output before the gated norm (reference: ced/model/gdn.py:715-823)."""
+        from . import ccr as ccr_mod
+
+        if (rec is not None) != arms.ccr_read:
+            raise ValueError("a cross-read reader takes its source's record, and only a reader does")
+        if ctx.gdn_scale != 1:
+            raise ValueError("model.encoder.gdn_ccr_spacing is not built with TST's resolution-explicit gates (a bag phase)")
+        cfg = self.cfg
+        B, L = ctx.doc.shape
+        hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        u_pre, a_lin, b_lin = self.project(x, arms, x_write, x_read)
+        hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
+        q, k, v, conv_input, conv_doc = ops.gdn_prep(u_pre, ctx.doc, self.conv_weight, hk, hv, dk, dv, hist, hist_doc, single_doc=ctx.single_doc)
+        g, beta = ops.gdn_gates(a_lin, b_lin, self.A_log, self.dt_bias)
+        if self.beta_max != 1:
+            beta = beta * self.beta_max
+        cross = ccr_mod.read(arms, rec, q, hv) if rec is not None else None
+        kernel = "recurrence" if cfg.kernel == "recurrence" else "chunked"
+        ckpt = out = None
+        if arms.ccr_write:
+            if state is not None and state.ckpt is None:
+                raise ValueError("this cache was written without the cross-read's checkpoints")
+            rep = hv // hk
+            S0 = x.new_zeros(B, hv, dk, dv, dtype=g.dtype) if state is None else state.S
+            o, S, out, ckpt = ccr_mod.write(q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2), v, g, beta, ctx, S0,
+                                            None if state is None else state.ckpt, arms.spacing, kernel, cfg.chunk_size, arms.layer)
+        else:
+            o, S = ops.delta_rule(q, k, v, g, beta, ctx.is_doc_start, None if state is None else state.S, kernel=kernel, chunk_size=cfg.chunk_size)
+        if cross is not None:
+            o = (o + arms.ccr_gate[:, None] * cross).to(o.dtype)
+        z = self.in_proj_z(x).view(B, L, hv, dv)
+        y = self.out_proj(self.norm(o.to(x.dtype), z).flatten(2))
+        return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S, ckpt=ckpt, ccr=out)
 
     def forward_kda(self, x, ctx: SeqContext, state: GDNState | None, arms):
         """The layer with one decay per key channel and / or the erase direction: the scalar layer's input preparation

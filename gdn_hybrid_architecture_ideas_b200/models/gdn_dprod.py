@@ -14,9 +14,16 @@ tensor, so the base layer starts as in the base model of the same seed.
 
 Paths: the token-and-step loop (`dprod_recurrence`), and the n_h T interleave into the chunked delta rule: sub-step
 n_h t + j - 1 is an ordinary step with k_{t,j}, v_{t,j}, beta_{t,j}; the decay and a document start on sub-step 1
-only, q_t on sub-step n_h only, where the output is read. Tensor ops on every device. Built: every layer, every head,
-projected keys and values; the placement, derived-key and sparse-step forms of the reference are refused by name
-(reference: ced/model/gdn_dprod.py:1-100, 155-210, 278-335, 389-476, 479-545).
+only, q_t on sub-step n_h only, where the output is read. Tensor ops on every device.
+
+Placement (`dprod.layers`, `dprod.heads`, `dprod.heads_by_layer`; resolved per GDN layer by the config's `dprod_carry` /
+`gdn_layer_configs`): a layer that does not carry is the plain layer (no module here); a layer that carries SOME value
+heads (whole key groups) holds `PartialSteps`, the extra steps' tensors sized for the carrying heads alone, and runs
+`forward_partial`: one projection and one conv over [q | k_1 | v_1 | the carrying heads' k_j, v_j], then the carrying
+heads through the n_h-step rule (beta = 2 sigmoid(b) on every step) and the others through the plain rule
+(beta = sigmoid(b), one write), the outputs and states joined along the head axis before the gated norm. Heads are cut
+by static slices. The derived-key and sparse-step forms of the reference are refused by name
+(reference: ced/model/gdn_dprod.py:1-100, 155-210, 278-335, 389-476, 479-545; ced/model/gdn_dprod_place.py:36-327).
 """
 
 from __future__ import annotations
@@ -49,11 +56,15 @@ def is_on(cfg) -> bool:
 def check_config(cfg) -> None:
     d, n = cfg.dprod, n_steps(cfg)
     default = type(d)()
-    moved = [k for k in ("route", "layers", "heads", "heads_by_layer", "key", "value", "beta", "rank", "perm", "conv", "stride", "summary",
-                         "first_beta") if getattr(d, k) != getattr(default, k)]
+    placed = [k for k in ("layers", "heads", "heads_by_layer") if getattr(d, k) != getattr(default, k)]
+    if placed:
+        raise ValueError(f"gdn.dprod.{', '.join(placed)} on a GDN layer built on its own: the placement keys are model.encoder.gdn.dprod's, "
+                         "resolved per layer (the layer is given its heads)")
+    moved = [k for k in ("route", "key", "value", "beta", "rank", "perm", "conv", "stride", "summary", "first_beta")
+             if getattr(d, k) != getattr(default, k)]
     if moved:
-        raise ValueError(f"gdn.dprod {', '.join(moved)}: only the plain Gated DeltaProduct form is built (every layer and head, projected "
-                         "keys, values and betas, the interleave route)")
+        raise ValueError(f"gdn.dprod {', '.join(moved)}: only the projected form is built (projected keys, values and betas, the "
+                         "interleave route)")
     m = d.beta_max
     if isinstance(m, bool) or not isinstance(m, int) or m not in BETA_MAXES:
         raise ValueError(f"gdn.dprod.beta_max {m!r}: 1 (beta = sigmoid(b)) or 2 (beta = 2 sigmoid(b), the default)")
@@ -71,6 +82,11 @@ def check_config(cfg) -> None:
 def check_model(cfg) -> None:
     if not is_on(cfg.encoder.gdn):
         return
+    d = cfg.encoder.gdn.dprod
+    partial = [i for i, (c, heads) in enumerate(cfg.encoder.gdn_layer_configs()) if heads is not None]
+    if partial and (d.beta_max != 2 or d.beta_init is not None):
+        raise ValueError(f"model.encoder.gdn.dprod.beta_max / beta_init with GDN layer(s) {partial} that carry only some of their value heads: "
+                         "the split layer writes 2 sigmoid(b) on the carrying heads and sigmoid(b) on the others and reads neither key")
     refused = [(cfg.encoder.gdn_write_mix != "none", f"model.encoder.gdn_write_mix {cfg.encoder.gdn_write_mix!r}"),
                (bool(cfg.encoder.gdn_shape_by_layer), "model.encoder.gdn_shape_by_layer"), (bool(cfg.mtp.enabled), "model.mtp.enabled"),
                (cfg.fp8.mode != "none", f"model.fp8.mode {cfg.fp8.mode!r}"), (cfg.nvfp4.mode != "none", f"model.nvfp4.mode {cfg.nvfp4.mode!r}")]
@@ -116,6 +132,67 @@ class DeltaProductSteps(nn.Module):
                 p.copy_(draw(p.shape).to(device=p.device, dtype=p.dtype))
 
 
+def runs_of(heads) -> tuple:
+    """((start, length), ...): the maximal runs of consecutive indices in `heads` (sorted, distinct)."""
+    out: list = []
+    for h in heads:
+        if out and out[-1][0] + out[-1][1] == h:
+            out[-1] = (out[-1][0], out[-1][1] + 1)
+        else:
+            out.append((h, 1))
+    return tuple(out)
+
+
+def take(t: torch.Tensor, runs: tuple, dim: int) -> torch.Tensor:
+    """The heads of `runs` along `dim`, in order: slices and at most one concatenation (no index tensor, no mask)."""
+    pieces = [t.narrow(dim, s, n) for s, n in runs]
+    return pieces[0] if len(pieces) == 1 else torch.cat(pieces, dim)
+
+
+def merge(a: torch.Tensor, runs_a: tuple, b: torch.Tensor, runs_b: tuple, dim: int) -> torch.Tensor:
+    """The inverse of `take` for a partition of the heads: a holds the heads of runs_a, b those of runs_b."""
+    pieces, at = [], 0
+    for s, n in runs_a:
+        pieces.append((s, a.narrow(dim, at, n)))
+        at += n
+    at = 0
+    for s, n in runs_b:
+        pieces.append((s, b.narrow(dim, at, n)))
+        at += n
+    return torch.cat([p for _, p in sorted(pieces, key=lambda x: x[0])], dim)
+
+
+class PartialSteps(DeltaProductSteps):
+    """The extra steps' tensors of a layer that carries only the value heads `carry` (whole key groups): DeltaProductSteps
+    at the carrying heads' counts, so names, shapes' meaning and draws are its own."""
+
+    def __init__(self, d_model: int, cfg, carry: tuple):
+        import dataclasses
+
+        hk, hv = cfg.n_k_heads, cfg.n_v_heads
+        g = hv // hk
+        keys = tuple(sorted({h // g for h in carry}))
+        if not (0 < len(carry) < hv and len(keys) * g == len(carry)):
+            raise ValueError(f"the carrying value heads {carry!r}: some whole key groups of {g} value heads, not all of the layer's {hv}")
+        self_hk, self_hv = len(keys), len(carry)
+        super().__init__(d_model, dataclasses.replace(cfg, n_k_heads=self_hk, n_v_heads=self_hv))
+        self.hk_c, self.hv_c, self.carry = self_hk, self_hv, tuple(carry)
+        self.runs_v, self.runs_k = runs_of(self.carry), runs_of(keys)
+        self.runs_v_plain = runs_of([h for h in range(hv) if h not in set(self.carry)])
+        self.runs_k_plain = runs_of([h for h in range(hk) if h not in set(keys)])
+
+
+def build_steps(d_model: int, cfg, carry: tuple | None):
+    """A GDN layer's extra steps: None at n_h 1, DeltaProductSteps when every head carries (carry None), else PartialSteps."""
+    if not is_on(cfg):
+        if carry:
+            raise ValueError(f"gdn.dprod.n_h 1 with carrying heads {tuple(carry)!r}: a layer that does not carry has none")
+        return None
+    if carry is None or len(carry) == cfg.n_v_heads:
+        return DeltaProductSteps(d_model, cfg)
+    return PartialSteps(d_model, cfg, tuple(carry))
+
+
 def init_own_parameters(model: nn.Module, std: float) -> int:
     steps = [m for m in model.modules() if isinstance(m, DeltaProductSteps)]
     if steps:
@@ -151,8 +228,57 @@ def last_substep(o: torch.Tensor, n_h: int) -> torch.Tensor:
     return o.reshape(B, T // n_h, n_h, *o.shape[2:])[:, :, n_h - 1]
 
 
+def forward_partial(layer, x, ctx, state):
+    """`forward` for a layer that carries some of its value heads (`PartialSteps`)."""
+    cfg, steps = layer.cfg, layer.dprod
+    B, L = ctx.doc.shape
+    hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+    hk_c, hv_c, n_x = steps.hk_c, steps.hv_c, steps.n_extra
+    n_h = n_x + 1
+    u_all = torch.cat([layer.in_proj_qkv(x), steps.in_proj_kv(x)], dim=-1)
+    w_all = torch.cat([layer.conv_weight, steps.conv_weight], dim=0)
+    if state is not None and state.conv_input.shape[-1] != u_all.shape[-1]:
+        raise ValueError(f"this GDN cache holds {state.conv_input.shape[-1]} conv channels; Gated DeltaProduct n_h {n_h} on {hv_c} of "
+                         f"{hv} value heads carries {u_all.shape[-1]}")
+    hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
+    u, conv_input, conv_doc = ops.ref.causal_doc_conv(u_all, ctx.doc, w_all, hist, hist_doc)
+    u = F.silu(u)
+    q, k1, rest = torch.split(u, [hk * dk, hk * dk, u.shape[-1] - 2 * hk * dk], dim=-1)
+    q = ops.ref.l2_normalize(q.reshape(B, L, hk, dk)) * dk ** -0.5
+    k1 = ops.ref.l2_normalize(k1.reshape(B, L, hk, dk))
+    parts = torch.split(rest, [hv * dv] + [hk_c * dk, hv_c * dv] * n_x, dim=-1)
+    v1 = parts[0].reshape(B, L, hv, dv)
+    xk = [ops.ref.l2_normalize(parts[1 + 2 * j].reshape(B, L, hk_c, dk)) for j in range(n_x)]
+    xv = [parts[2 + 2 * j].reshape(B, L, hv_c, dv) for j in range(n_x)]
+    g, beta1 = ops.ref.gdn_gates(layer.in_proj_a(x), layer.in_proj_b(x), layer.A_log, layer.dt_bias)
+    xb = list((2 * torch.sigmoid(steps.in_proj_b(x))).reshape(B, L, n_x, hv_c).unbind(2))
+    rv, rk, rvp, rkp = steps.runs_v, steps.runs_k, steps.runs_v_plain, steps.runs_k_plain
+    dt = ops.ref.work_dtype(q)
+    rep = hv // hk
+    qc = take(q, rk, 2).repeat_interleave(rep, dim=2).to(dt)
+    kc = torch.stack([take(k1, rk, 2)] + xk, dim=2).repeat_interleave(rep, dim=3).to(dt)
+    vc = torch.stack([take(v1, rv, 2)] + xv, dim=2).to(dt)
+    bc = torch.stack([2 * take(beta1, rv, 2)] + xb, dim=2).to(dt)        # step 1 of a carrying head writes with 2 sigmoid(b) too
+    gc = take(g, rv, 2).to(dt)
+    qp, kp = take(q, rkp, 2).repeat_interleave(rep, dim=2).to(dt), take(k1, rkp, 2).repeat_interleave(rep, dim=2).to(dt)
+    vp, gp, bp = take(v1, rvp, 2).to(dt), take(g, rvp, 2).to(dt), take(beta1, rvp, 2).to(dt)
+    S_all = x.new_zeros(B, hv, dk, dv, dtype=dt) if state is None else state.S.to(dt)
+    S0c, S0p = take(S_all, rv, 1), take(S_all, rvp, 1)
+    if cfg.kernel != "recurrence" and L > 1:
+        qi, ki, vi, gi, bi, si = interleave(qc, kc, vc, gc, bc, ctx.is_doc_start)
+        oi, S_c = ops.ref.chunked_delta_rule(qi, ki, vi, gi, bi, si, S0c, cfg.chunk_size)
+        o_c = last_substep(oi, n_h)
+        o_p, S_p = ops.ref.chunked_delta_rule(qp, kp, vp, gp, bp, ctx.is_doc_start, S0p, cfg.chunk_size)
+    else:
+        o_c, S_c = dprod_recurrence(qc, kc, vc, gc, bc, ctx.is_doc_start, S0c)
+        o_p, S_p = ops.ref.delta_rule_recurrence(qp, kp, vp, gp, bp, ctx.is_doc_start, S0p)
+    return merge(o_c, rv, o_p, rvp, 2), conv_input, conv_doc, merge(S_c, rv, S_p, rvp, 1)
+
+
 def forward(layer, x, ctx, state):
     """The GDN layer's forward with the extra steps: (y, conv history over all channels, its document ids, S)."""
+    if isinstance(layer.dprod, PartialSteps):
+        return forward_partial(layer, x, ctx, state)
     cfg, steps = layer.cfg, layer.dprod
     B, L = ctx.doc.shape
     hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim

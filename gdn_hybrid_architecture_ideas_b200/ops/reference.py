@@ -153,7 +153,8 @@ def chunk_local(q, k, v, g, beta, is_doc_start, C):
     sol = torch.linalg.solve_triangular(eye + A, rhs, upper=False, unitriangular=True)
     U, W = sol.split([v.shape[-1], dk], dim=-1)
     return dict(U=U, W=W, Aqk=(q @ k.transpose(-1, -2)) * decay, q_in=q * (gamma * first)[..., None],
-                k_out=k * (to_end * last)[..., None], carry=gamma[..., -1] * (seg[..., -1] == 0).to(wd))
+                k_out=k * (to_end * last)[..., None], carry=gamma[..., -1] * (seg[..., -1] == 0).to(wd),
+                k=k, decay=decay, gamma_first=gamma * first)      # the last three: `delta_rule_picks` only
 
 
 def chunk_scan(parts, S):
@@ -181,6 +182,61 @@ def chunked_delta_rule(q, k, v, g, beta, is_doc_start, S, chunk_size: int = 64):
     o, S = chunk_scan(parts, S.to(parts["U"].dtype))
     o = o.reshape(B, H, L + pad, -1)[:, :, :L].transpose(1, 2)
     return o.to(out_dt), S.to(out_dt)
+
+
+def delta_rule_picks(q, k, v, g, beta, is_doc_start, S, picks, kernel: str = "chunked", chunk_size: int = 64):
+    """The gated delta rule that also returns the state AFTER chosen positions. picks (B, K) long: indices into the call,
+    any value >= L for an unused entry (its state is returned as zeros). Returns (o, S_final, states (B, K, H, dk, dv)).
+
+    "recurrence": the token loop, each pick copied out when its token has been written. "chunked": the WY form; the
+    state after local index i of a chunk that starts at S_n is
+        [no document start up to i] exp(c_i) S_n + sum_{j <= i, same document} exp(c_i - c_j) k_j (x) v_new_j
+    with v_new = U - W S_n the chunk's corrected values, so each pick is one gather of its chunk's operands and one
+    small product, whatever the number of positions (fixed shapes; no state per position is formed)."""
+    B, L, H, dk = q.shape
+    K = picks.shape[1]
+    ok = picks < L
+    if kernel == "recurrence" or L == 1:
+        out = S.new_zeros(B, K, *S.shape[1:]) if K else S.new_zeros(B, 0, *S.shape[1:])
+        outs = []
+        for t, (q_t, k_t, v_t, g_t, b_t, s_t) in enumerate(zip(q.unbind(1), k.unbind(1), v.unbind(1), g.unbind(1), beta.unbind(1),
+                                                                is_doc_start.unbind(1))):
+            S = S * (~s_t).to(S.dtype)[:, None, None, None]
+            S = S * torch.exp(g_t)[:, :, None, None]
+            pred = torch.einsum("bhkv,bhk->bhv", S, k_t)
+            S = S + torch.einsum("bhk,bhv->bhkv", k_t, b_t[:, :, None] * (v_t - pred))
+            outs.append(torch.einsum("bhkv,bhk->bhv", S, q_t))
+            if K:
+                out = torch.where((picks == t)[:, :, None, None, None], S[:, None], out)
+        return torch.stack(outs, dim=1), S, out
+    out_dt = reduce(torch.promote_types, (t.dtype for t in (q, k, v, g, beta, S)))
+    C = min(chunk_size, L)
+    pad = (-L) % C
+    if pad:
+        q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+        g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
+        is_doc_start = F.pad(is_doc_start, (0, pad))
+    parts = chunk_local(q, k, v, g, beta, is_doc_start, C)
+    S = S.to(parts["U"].dtype)
+    outs, starts, news = [], [], []
+    for U, W, qi, Aqk, ko, cy in zip(*(parts[n].unbind(2) for n in ("U", "W", "q_in", "Aqk", "k_out", "carry"))):
+        starts.append(S)
+        vn = U - W @ S
+        news.append(vn)
+        outs.append(qi @ S + Aqk @ vn)
+        S = S * cy[..., None, None] + ko.transpose(-1, -2) @ vn
+    o = torch.stack(outs, dim=2).reshape(B, H, L + pad, -1)[:, :, :L].transpose(1, 2)
+    at = picks.clamp(max=L - 1)
+    n_i, i_i = at // C, at % C
+    rows = torch.arange(B, device=q.device)[:, None]
+    S_n = torch.stack(starts, dim=2)[rows, :, n_i]                                       # (B, K, H, dk, dv)
+    v_new = torch.stack(news, dim=2)[rows, :, n_i]                                       # (B, K, H, C, dv)
+    keys = parts["k"][rows, :, n_i]                                                      # (B, K, H, C, dk)
+    weight = parts["decay"].expand(B, H, -1, -1, -1)[rows, :, n_i, i_i]                  # (B, K, H, C): exp(c_i - c_j), 0 outside the document or after i
+    lead = parts["gamma_first"][rows, :, n_i, i_i]                                       # (B, K, H)
+    states = lead[..., None, None] * S_n + torch.einsum("bkhc,bkhcd,bkhce->bkhde", weight, keys, v_new)
+    states = states * ok[:, :, None, None, None].to(states.dtype)
+    return o.to(out_dt), S.to(out_dt), states.to(out_dt)
 
 
 # ------------------------------------------------------------------------------------------------ attention

@@ -33,6 +33,8 @@ def local_model_config(cfg: ModelConfig, world: int) -> ModelConfig:
     if g.kda.decay != "scalar" or g.erase.mode != "none" or g.dprod.n_h != 1:
         raise ValueError("tensor parallel shards the scalar-decay GDN layer: gdn.kda.decay 'channel', gdn.erase.mode 'eda' and "
                          "gdn.dprod.n_h >= 2 are not built with it")
+    if enc.gdn_ccr_spacing:
+        raise ValueError("tensor parallel is not built with the checkpoint cross-read (model.encoder.gdn_ccr_spacing)")
     if a.normalizer != "softmax":
         raise ValueError("tensor parallel shards the softmax attention: attention.normalizer 'asentmax' is not built with it")
     sizes = {"gdn.n_k_heads": g.n_k_heads, "gdn.n_v_heads": g.n_v_heads, "attention.n_q_heads": a.n_q_heads,

@@ -90,6 +90,20 @@ def depth_reader_summary(model) -> dict:
     return {"readers": [n for n, _ in items], "query_norm": norms, "key_gain_dev": gains}
 
 
+@torch.no_grad()
+def ccr_summary(model) -> dict:
+    """The checkpoint cross-read's tensors as they are now: per reader layer its gate's values and, with a translator,
+    ||M - I||_F per key head (0 at the start). One host read each (reference: ced/model/gdn_arms.py:1262-1314)."""
+    rows = [(i, a) for i, a in ((i, getattr(layer, "gdn_arms", None)) for i, layer in enumerate(model.encoder.layers))
+            if a is not None and a.ccr_read]
+    if not rows:
+        return {}
+    out = {"layers": [i for i, _ in rows], "ccr_gate": torch.stack([a.ccr_gate.double() for _, a in rows]).cpu().tolist()}
+    if any(a.translator != "none" for _, a in rows):
+        out["ccr_translator_dev"] = torch.stack([torch.linalg.matrix_norm(a.ccr_translator_delta.double()) for _, a in rows]).cpu().tolist()
+    return out
+
+
 class StreamRMS:
     """Root-mean-square of the residual stream leaving each layer, collected by forward hooks during ONE forward
     (`with StreamRMS(model) as rms: ...; rms.values()`): the growth of the stream along the depth."""

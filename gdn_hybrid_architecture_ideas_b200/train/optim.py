@@ -22,7 +22,12 @@ NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gai
                      # a looped middle's injection (models/recur.py): B starts at the identity and w near 1, decay would pull both
                      # away from their starts; A_log / dt_bias are covered by the GDN suffixes above
                      "injection.B", ".recur_mix")
-ZERO_GATE_SUFFIXES = (".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale")
+ZERO_GATE_SUFFIXES = (".gdn_arms.ccr_gate", ".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale")
+# The cross-read's query translators (models/ccr.py): D = M - I, (H_k, d_k, d_k) a reader, never a Muon matrix (3-D). One
+# AdamW group of their own, the last, at the depth readers' learning rate; optim.ccr_translator_decay "none": no decay,
+# "identity": the run's weight decay, which on D pulls M toward the identity (reference: ced/train/optim.py:283-312).
+CCR_TRANSLATOR_SUFFIX = ".gdn_arms.ccr_translator_delta"
+CCR_TRANSLATOR_DECAY_MODES = ("none", "identity")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
 ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight", "beta_proj.weight", "gamma_proj.weight", ".kda.f_down.weight",
@@ -113,6 +118,16 @@ def param_groups(model, o) -> list[dict]:
         raise ValueError(f"optim.gdn_mup_base_width {o.gdn_mup_base_width!r} is read with optim.gdn_mup true: leave it {GDN_MUP_BASE_WIDTH}")
     if o.gdn_mup:
         spec = _gdn_mup_spec(spec, model, o, 1.0 if o.name == "adamw" else o.adamw_lr_scale)
+    if o.ccr_translator_decay not in CCR_TRANSLATOR_DECAY_MODES:
+        raise ValueError(f"optim.ccr_translator_decay {o.ccr_translator_decay!r}: one of {CCR_TRANSLATOR_DECAY_MODES}")
+    mats = [(n, p) for n, p in named if n.endswith(CCR_TRANSLATOR_SUFFIX)]
+    if not mats and o.ccr_translator_decay != "none":
+        raise ValueError(f"optim.ccr_translator_decay {o.ccr_translator_decay!r} is read for the cross-read's query translators "
+                         "(model.encoder.gdn_ccr_translator 'key_head'); this model has none: leave it 'none'")
+    if mats:
+        taken = {n for n, _ in mats}
+        spec = [(k, [(n, p) for n, p in items if n not in taken], wd, sc) for k, items, wd, sc in spec]
+        spec.append(("adamw", mats, 0.0 if o.ccr_translator_decay == "none" else o.weight_decay, 1.0 if o.name == "adamw" else o.adamw_lr_scale))
     return [{"kind": k, "names": [n for n, _ in items], "params": [p for _, p in items], "weight_decay": wd, "lr_scale": s}
             for k, items, wd, s in spec if items]
 

@@ -181,6 +181,26 @@ class Trainer:
                 raise ValueError(f"{what} is not built with cuda_graphs {cfg.cuda_graphs!r}: the choice is a host read and changes the captured forward")
             if cfg.freeze_trunk:
                 raise ValueError(f"{what} is not built with freeze_trunk: the choice writes one of the trunk's tensors in a step")
+        # The checkpoint cross-read (models/ccr.py): tensor ops on one process; the gates' floor is a clamp after each step.
+        from ..models import ccr as ccr_mod
+
+        self._ccr_floor = None
+        if ccr_mod.on(cfg.model):
+            what = "model.encoder.gdn_ccr_spacing"
+            if self.tp is not None:
+                raise ValueError(f"{what} is not built with tensor parallelism: a reader's heads read its source's states on the same rank only")
+            if cfg.cuda_graphs != "none":
+                raise ValueError(f"{what} is not built with cuda_graphs {cfg.cuda_graphs!r}")
+            if cfg.activation_checkpoint not in ccr_mod.CHECKPOINT_MODES:
+                raise ValueError(f"{what} runs with activation_checkpoint {ccr_mod.CHECKPOINT_MODES}, not {cfg.activation_checkpoint!r}: "
+                                 "the record stays on the device and is an input and output of a layer's call")
+            if cfg.model.encoder.gdn_ccr_gate_floor:
+                if cfg.optim.zero_gate_decay != "none":
+                    raise ValueError(f"model.encoder.gdn_ccr_gate_floor {cfg.model.encoder.gdn_ccr_gate_floor!r} is built with optim.zero_gate_decay "
+                                     "'none': weight decay would pull a gate at its floor below it before the clamp")
+                if self.zero is not None:
+                    raise ValueError("model.encoder.gdn_ccr_gate_floor is not built with optimizer sharding: the clamp writes the whole parameter")
+                self._ccr_floor = self.model.encoder
         self._readout = None
         readout.check_readout_config(cfg)
         self._probe_readout = readout.Readout(self) if cfg.eval.readout_every else None      # the sample is read (and checked) before the run trains
@@ -373,6 +393,11 @@ class Trainer:
             if self.zero is not None:
                 self.zero.settle()
             self.model.encoder.project_layer_scalars()      # the span-bounded residual scalars back into their range
+        if self._ccr_floor is not None and not cfg.freeze_trunk:
+            from ..models.ccr import floor_gates_
+
+            floor_gates_(self._ccr_floor)                   # the cross-read gates back to at least their floor
+            self.flat.refresh_lp()
         nvtx_sync.__exit__(None, None, None)
         self.step += 1
         from .. import ops
@@ -437,6 +462,9 @@ class Trainer:
             readers = monitor.depth_reader_summary(self.model)
             if readers:
                 m["depth_readers"] = readers
+            cross = monitor.ccr_summary(self.model)
+            if cross:
+                m["ccr"] = cross
         if cfg.log_stream_rms_every and self.step % cfg.log_stream_rms_every == 0:
             if self._qmix is not None:
                 self._qmix.qmix_record = {}

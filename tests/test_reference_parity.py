@@ -20,7 +20,7 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "ldm"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "dprod_layers", "dprod_heads", "dprod_mixed", "ldm"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase", "dprod")) else C.tiny_full_config()
@@ -39,6 +39,14 @@ def test_state_dict_forward_backward(reference, preset):
         cfg.encoder.ldm_groups, cfg.encoder.ldm_key_dim, cfg.encoder.ldm_hidden = 4, 4, 6
     if preset.startswith("dprod"):
         cfg.encoder.gdn.dprod.n_h = 2 if preset == "dprod" else 3
+        if preset == "dprod_layers":           # GDN ordinals 0 and 3 carry the extra step; the others are the plain layer
+            cfg.encoder.gdn.dprod.layers = (0, 3)
+        if preset == "dprod_heads":            # the first key group of every layer carries it
+            cfg.encoder.gdn.dprod.heads = 2
+        if preset == "dprod_mixed":
+            d = cfg.encoder.gdn.dprod
+            d.n_h, d.layers, d.heads, d.heads_by_layer = 3, (1, 2, 5), 2, {2: (2, 3), 5: (0, 1, 2, 3)}
+            cfg.encoder.gdn.kernel, cfg.encoder.gdn.chunk_size = "chunked", 16
         if preset == "dprod_b1":
             cfg.encoder.gdn.dprod.beta_max, cfg.encoder.gdn.dprod.beta_init = 1, 0.95
     if preset.endswith("erase"):
@@ -449,3 +457,139 @@ def test_qmix_static_pair_equals_the_reference(reference):
         setattr(wrong.encoder, key, value)
         with pytest.raises(ValueError, match=match):
             build_model(wrong)
+
+
+@pytest.mark.parametrize("base,keys", [
+    ("control", {"gdn_ccr_spacing": 8}),
+    ("control", {"gdn_ccr_spacing": 8, "gdn.kernel": "chunked", "gdn.chunk_size": 16}),
+    ("control", {"gdn_ccr_spacing": 4, "gdn_ccr_target": "lowest", "gdn_ccr_translator": "key_head", "gdn_ccr_gate_init": 0.09}),
+    ("control", {"gdn_ccr_spacing": 8, "gdn_ccr_target": "group_first", "gdn_ccr_gate_init": 0.09, "gdn_ccr_gate_floor": 0.05}),
+    ("full", {"gdn_ccr_spacing": 8, "gdn_write_variant": "none"}),
+    ("full", {"gdn_ccr_spacing": 8, "gdn_write_variant": "none", "gdn_ccr_target": "group_first", "gdn_ccr_translator": "key_head"})])
+def test_checkpoint_cross_read_equals_the_reference(reference, base, keys):
+    """The checkpoint cross-read (gdn_ccr_spacing) under its three targets, with and without the translator, alone and with the
+    write mix: state-dict keys and starts, logits, gradients (the gates' among them, nonzero), chunked cached reads whose
+    cuts fall inside and across checkpoint spans, and activation_checkpoint 'layer'."""
+    cfg = C.tiny_full_config() if base == "full" else C.tiny_control_config()
+    for k, v in keys.items():
+        C.apply_override(cfg, f"encoder.{k}={v}")
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd)
+    gates = [k for k in sd if k.endswith("ccr_gate")]
+    assert gates and all(float(sd[k].min()) == float(sd[k].max()) and abs(float(sd[k][0]) - cfg.encoder.gdn_ccr_gate_init) < 1e-7 for k in gates)
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40)            # documents of 5 to 24 tokens: checkpoints at 8 and 16 (or 4 .. 20) are read
+
+    def grads(model, logits):
+        return torch.autograd.grad(logits.logsumexp(-1).sum(), list(model.parameters()), allow_unused=True)
+
+    a, b = mine(tok, doc).logits, theirs(tok, doc).logits
+    assert (a - b).abs().max() < 1e-10
+    ga, gb = grads(mine, a), grads(theirs, b)
+    for (n, _), x, y in zip(mine.named_parameters(), ga, gb):
+        assert (x is None) == (y is None) and (x is None or (x - y).abs().max() < 1e-9), n
+        if n.endswith("ccr_gate") or n.endswith("ccr_translator_delta"):
+            assert x.abs().max() > 1e-8, n
+    mine.encoder.activation_checkpoint = "layer"
+    gc = grads(mine, mine(tok, doc).logits)
+    assert all((x is None and y is None) or (x - y).abs().max() < 1e-12 for x, y in zip(ga, gc))
+    mine.encoder.activation_checkpoint = "block"
+    with pytest.raises(ValueError, match="activation_checkpoint"):
+        mine(tok, doc)
+    mine.encoder.activation_checkpoint = "none"
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        full = mine(tok, doc).logits
+        out, ref_out = mine.prefill(tok[:, :17], doc[:, :17]), theirs.prefill(tok[:, :17], doc[:, :17])
+        parts = [out.logits]
+        for lo, hi in ((17, 18), (18, 29), (29, 40)):
+            out = mine.extend(tok[:, lo:hi], doc[:, lo:hi], None, out.cache)
+            ref_out = theirs.extend(tok[:, lo:hi], doc[:, lo:hi], None, ref_out.cache)
+            parts.append(out.logits)
+            assert (out.logits - ref_out.logits).abs().max() < 1e-10
+        assert (torch.cat(parts, 1) - full).abs().max() < 1e-9
+
+
+def test_checkpoint_cross_read_records_and_refusals():
+    """The record's slots against a loop over positions; one state per pick, not per position; what the arm is refused with."""
+    from gdn_hybrid_architecture_ideas_b200.models import ccr
+
+    g = torch.Generator().manual_seed(0)
+    B, L, C_ = 3, 37, 5
+    start = torch.randint(0, 9, (B,), generator=g)            # the first document began before the call
+    cuts = [sorted(torch.randint(1, L, (2,), generator=g).tolist()) for _ in range(B)]
+    pos = torch.stack([torch.tensor([(start[b] + t if t < cuts[b][0] else t - cuts[b][0] if t < cuts[b][1] else t - cuts[b][1]) for t in range(L)]) for b in range(B)]).long()
+    picks, slot, nxt = ccr.picks_and_slots(pos, C_)
+    assert picks.shape == (B, L // C_ + 1)
+    for b in range(B):
+        taken = [t for t in range(L) if (int(pos[b, t]) + 1) % C_ == 0]
+        assert picks[b].tolist() == taken + [L] * (picks.shape[1] - len(taken))
+        for t in range(L + 1):
+            p = int(pos[b, t]) if t < L else int(pos[b, -1]) + 1
+            c = C_ * (p // C_)
+            j = t - (p - c) - 1
+            want = 0 if c == 0 else 1 if j < 0 else 2 + taken.index(j)
+            assert (int(slot[b, t]) if t < L else int(nxt[b])) == want, (b, t)
+    cfg = C.tiny_control_config()
+    cfg.encoder.gdn_ccr_spacing = 8
+    model = build_model(cfg)
+    tok, doc = random_rows(2, 40)
+    layer = model.encoder.layers[0]
+    seen = {}
+    layer.mixer.register_forward_hook(lambda m, a, out: seen.update(rec=out[1].ccr))
+    caches = model.prefill(tok, doc).cache.encoder
+    assert seen["rec"].states.shape[:2] == (2, 40 // 8 + 1 + 2) and all(getattr(c, "ccr", None) is None for c in caches)
+    assert caches[0].ckpt is not None and caches[-1].ckpt is None          # a writer carries its checkpoint; the last GDN layer writes none
+    for key, value, match in (("encoder.gdn_ccr_target", "nearest", "one of"), ("encoder.gdn_ccr_spacing", -1, "positive spacing"),
+                              ("encoder.layer_scalars", "skip", "layer_scalars"), ("encoder.gdn_ccr_gate_floor", 0.2, "above"),
+                              ("loop.recur_layers", "[1, 3]", "one pass"), ("encoder.attn_res", "block", "attn_res")):
+        bad = C.tiny_control_config()
+        bad.encoder.gdn_ccr_spacing = 8
+        C.apply_override(bad, f"{key}={value}")
+        with pytest.raises(ValueError, match=match):
+            build_model(bad)
+    off = C.tiny_control_config()
+    off.encoder.gdn_ccr_gate_init = 0.1
+    with pytest.raises(ValueError, match="CCR on"):
+        build_model(off)
+
+
+def test_delta_product_placement_is_resolved_and_refused_by_name():
+    """The placement keys of Gated DeltaProduct: which heads of which GDN layer carry, the tensors a split layer holds, and the
+    values refused by name."""
+    from gdn_hybrid_architecture_ideas_b200.models import gdn_dprod
+
+    cfg = C.tiny_control_config()                       # 8 GDN layers of 2 key / 4 value heads
+    d = cfg.encoder.gdn.dprod
+    d.n_h, d.layers, d.heads, d.heads_by_layer = 2, (1, 2, 5), 2, {2: (2, 3), 5: (0, 1, 2, 3)}
+    assert cfg.encoder.dprod_carry() == [(), (0, 1), (2, 3), (), (), (0, 1, 2, 3), (), ()]
+    built = cfg.encoder.gdn_layer_configs()
+    assert [c.dprod.n_h for c, _ in built] == [1, 2, 2, 1, 1, 2, 1, 1] and [h for _, h in built] == [None, (0, 1), (2, 3), None, None, None, None, None]
+    assert all(c.dprod.layers == () and c.dprod.heads == 0 and c.dprod.heads_by_layer == {} for c, _ in built)
+    model = build_model(cfg)
+    mixers = [layer.mixer for layer in model.encoder.layers if layer.kind == "gdn"]
+    assert [type(m.dprod).__name__ for m in mixers] == ["NoneType", "PartialSteps", "PartialSteps", "NoneType", "NoneType", "DeltaProductSteps", "NoneType", "NoneType"]
+    g = cfg.encoder.gdn
+    assert mixers[1].dprod.in_proj_kv.weight.shape[0] == g.k_head_dim + 2 * g.v_head_dim and mixers[1].dprod.in_proj_b.weight.shape[0] == 2
+    assert mixers[2].dprod.runs_v == ((2, 2),) and mixers[2].dprod.runs_k_plain == ((0, 1),)
+    assert sum(p.numel() for p in mixers[5].dprod.parameters()) == gdn_dprod.params_per_layer(cfg.d_model, g)
+    t = torch.arange(24.0).reshape(2, 6, 2)
+    runs_a, runs_b = gdn_dprod.runs_of([0, 3, 4]), gdn_dprod.runs_of([1, 2, 5])
+    assert runs_a == ((0, 1), (3, 2)) and torch.equal(gdn_dprod.merge(gdn_dprod.take(t, runs_a, 1), runs_a, gdn_dprod.take(t, runs_b, 1), runs_b, 1), t)
+    for key, value, match in (("layers", "[2, 1]", "ascending"), ("layers", "[9]", "ordinals"), ("heads", 3, "multiple"), ("heads", 6, "at most"),
+                              ("heads_by_layer", "{0: [1, 2]}", "cut"), ("heads_by_layer", "{0: [3, 2]}", "ascending"),
+                              ("heads_by_layer", "{9: [0, 1]}", "ordinals of layers"), ("beta_max", 1, "carry only some")):
+        bad = C.tiny_control_config()
+        bad.encoder.gdn.dprod.n_h, bad.encoder.gdn.dprod.heads = 2, 2
+        C.apply_override(bad, f"encoder.gdn.dprod.{key}={value}")
+        with pytest.raises(ValueError, match=match):
+            build_model(bad)
+    off = C.tiny_control_config()
+    off.encoder.gdn.dprod.heads = 2
+    with pytest.raises(ValueError, match="n_h 1"):
+        build_model(off)

@@ -816,3 +816,49 @@ def test_qmix_static_pair_is_chosen_at_its_step_and_survives_a_resume(tmp_path):
         setattr(bad, key, value)
         with pytest.raises(ValueError, match=match):
             Trainer(bad, None)
+
+
+def test_checkpoint_cross_read_trains_with_its_gate_floor(tmp_path):
+    """model.encoder.gdn_ccr_spacing through the trainer: gates and translators in their optimizer groups, the floor held
+    after every step, the log's summary, a bit-exact resume, and the refusals."""
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    cfg = tiny_train_config()
+    cfg.model = C.tiny_control_config()
+    e = cfg.model.encoder
+    e.gdn_ccr_spacing, e.gdn_ccr_target, e.gdn_ccr_translator, e.gdn_ccr_gate_init, e.gdn_ccr_gate_floor = 8, "group_first", "key_head", 0.09, 0.09
+    cfg.optim.zero_gate_decay, cfg.optim.ccr_translator_decay, cfg.log_every, cfg.activation_checkpoint = "none", "identity", 2, "layer"
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    groups = optim.param_groups(t.model, cfg.optim)
+    last = groups[-1]
+    assert all(n.endswith("ccr_translator_delta") for n in last["names"]) and last["weight_decay"] == cfg.optim.weight_decay
+    plain = [g for g in groups if g["weight_decay"] == 0.0][0]["names"]
+    gates = [n for n, _ in t.model.named_parameters() if n.endswith("ccr_gate")]
+    assert gates and all(n in plain for n in gates)
+    l0 = t.train_step()["loss"]
+    t.fit()
+    assert t.last_metrics["loss"] < l0
+    named = dict(t.model.named_parameters())
+    assert all(float(named[n].min()) >= 0.09 - 1e-7 for n in gates)
+    assert any(float(named[n].max()) > 0.09 + 1e-6 for n in gates) and any(float(named[n].min()) <= 0.09 + 1e-7 for n in gates)
+    assert any(float(named[n].abs().max()) > 0 for n in last["names"])
+    lines = [json.loads(x) for x in (tmp_path / "a" / "metrics.jsonl").read_text().splitlines()]
+    logged = [x["ccr"] for x in lines if "ccr" in x]
+    assert logged and len(logged[0]["ccr_gate"]) == len(gates) == len(logged[0]["ccr_translator_dev"])
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(3)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 3
+    c.fit()
+    wa, wc = weights(t), weights(c)
+    assert all(torch.equal(wa[k], wc[k]) for k in wa)
+    for key, value, match in (("activation_checkpoint", "host", "activation_checkpoint"), ("optim.zero_gate_decay", "decay", "zero_gate_decay"),
+                              ("cuda_graphs", "microbatch", "cuda_graphs")):
+        bad = copy.deepcopy(cfg)
+        C.apply_override(bad, f"{key}={value}")
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
+    off = tiny_train_config()
+    off.optim.ccr_translator_decay = "identity"
+    with pytest.raises(ValueError, match="this model has none"):
+        Trainer(off, None)
