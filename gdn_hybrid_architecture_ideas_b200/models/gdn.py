@@ -20,7 +20,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..config import GDNConfig
-from . import gdn_dprod, gdn_erase, gdn_kda
+from . import gdn_dprod, gdn_dprod_derived, gdn_erase, gdn_kda
 from .linear import Linear
 from .norms import GatedRMSNorm
 from .sequence import SeqContext
@@ -35,6 +35,7 @@ class GDNState:
     S: torch.Tensor | None     # (B, Hv, dk, dv)
     ckpt: torch.Tensor | None = None    # a cross-read writer only: the checkpoint the next token reads (B, Hv, dk, dv)
     ccr: object | None = None           # the record a writer's call hands its readers; taken out by the stack, never cached
+    k_prev: torch.Tensor | None = None  # gdn.dprod.key 'prev' only: the unit key of the last token processed (B, Hk, dk)
 
 
 class GDNArms(nn.Module):
@@ -283,6 +284,11 @@ class GatedDeltaNet(nn.Module):
         cfg = self.cfg
         B, L = ctx.doc.shape
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        if isinstance(self.dprod, gdn_dprod_derived.DerivedSteps):
+            o, conv_input, conv_doc, S, k_prev = gdn_dprod_derived.forward(self, x, ctx, state)
+            z = self.in_proj_z(x).view(B, L, hv, dv)
+            y = self.out_proj(self.norm(o.to(x.dtype), z).flatten(2))
+            return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S, k_prev=k_prev)
         if self.dprod is not None:
             o, conv_input, conv_doc, S = gdn_dprod.forward(self, x, ctx, state)
             z = self.in_proj_z(x).view(B, L, hv, dv)

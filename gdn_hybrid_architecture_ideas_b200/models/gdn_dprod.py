@@ -60,11 +60,17 @@ def check_config(cfg) -> None:
     if placed:
         raise ValueError(f"gdn.dprod.{', '.join(placed)} on a GDN layer built on its own: the placement keys are model.encoder.gdn.dprod's, "
                          "resolved per layer (the layer is given its heads)")
-    moved = [k for k in ("route", "key", "value", "beta", "rank", "perm", "conv", "stride", "summary", "first_beta")
-             if getattr(d, k) != getattr(default, k)]
+    from .gdn_dprod_derived import check_second, is_derived
+
+    check_second(cfg)
+    moved = [k for k in ("route", "stride", "summary", "first_beta") if getattr(d, k) != getattr(default, k)]
     if moved:
-        raise ValueError(f"gdn.dprod {', '.join(moved)}: only the projected form is built (projected keys, values and betas, the "
-                         "interleave route)")
+        raise ValueError(f"gdn.dprod {', '.join(moved)}: the one-readout route and the strided / summarised second steps are not built "
+                         "(built: projected steps with placement, and a second step derived from the first)")
+    if is_derived(cfg):
+        if n > 1 and (cfg.negeig.beta_max != 1 or cfg.kda.decay != "scalar" or cfg.erase.mode != "none"):
+            raise ValueError("gdn.dprod.n_h >= 2 is built on the scalar-decay layer alone: negeig.beta_max 1, kda.decay 'scalar', erase.mode 'none'")
+        return
     m = d.beta_max
     if isinstance(m, bool) or not isinstance(m, int) or m not in BETA_MAXES:
         raise ValueError(f"gdn.dprod.beta_max {m!r}: 1 (beta = sigmoid(b)) or 2 (beta = 2 sigmoid(b), the default)")
@@ -83,6 +89,13 @@ def check_model(cfg) -> None:
     if not is_on(cfg.encoder.gdn):
         return
     d = cfg.encoder.gdn.dprod
+    from .gdn_dprod_derived import is_derived
+
+    if is_derived(cfg.encoder.gdn) and cfg.encoder.gdn_shape_by_layer:
+        raise ValueError(f"model.encoder.gdn_shape_by_layer with model.encoder.gdn.dprod.key {d.key!r}: not built together")
+    if is_derived(cfg.encoder.gdn) and (d.layers != () or d.heads != 0 or d.heads_by_layer != {}):
+        raise ValueError(f"model.encoder.gdn.dprod.layers / heads / heads_by_layer with dprod.key {d.key!r}: the derived second step is built "
+                         "for every head of every GDN layer")
     partial = [i for i, (c, heads) in enumerate(cfg.encoder.gdn_layer_configs()) if heads is not None]
     if partial and (d.beta_max != 2 or d.beta_init is not None):
         raise ValueError(f"model.encoder.gdn.dprod.beta_max / beta_init with GDN layer(s) {partial} that carry only some of their value heads: "
@@ -188,13 +201,21 @@ def build_steps(d_model: int, cfg, carry: tuple | None):
         if carry:
             raise ValueError(f"gdn.dprod.n_h 1 with carrying heads {tuple(carry)!r}: a layer that does not carry has none")
         return None
+    from .gdn_dprod_derived import DerivedSteps, is_derived
+
+    if is_derived(cfg):
+        if carry is not None and tuple(carry) != tuple(range(cfg.n_v_heads)):
+            raise ValueError(f"gdn.dprod.key {cfg.dprod.key!r} with the carrying value heads {tuple(carry)!r}: the derived second step is built for every head of a layer")
+        return DerivedSteps(d_model, cfg)
     if carry is None or len(carry) == cfg.n_v_heads:
         return DeltaProductSteps(d_model, cfg)
     return PartialSteps(d_model, cfg, tuple(carry))
 
 
 def init_own_parameters(model: nn.Module, std: float) -> int:
-    steps = [m for m in model.modules() if isinstance(m, DeltaProductSteps)]
+    from .gdn_dprod_derived import DerivedSteps
+
+    steps = [m for m in model.modules() if isinstance(m, (DeltaProductSteps, DerivedSteps))]
     if steps:
         g = torch.Generator().manual_seed((torch.initial_seed() + SEED_OFFSET) % (1 << 63))
         for m in steps:

@@ -31,7 +31,8 @@ CCR_TRANSLATOR_DECAY_MODES = ("none", "identity")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
 ADAMW_MATRIX_SUFFIXES = ("in_proj_a.weight", "in_proj_b.weight", "beta_proj.weight", "gamma_proj.weight", ".kda.f_down.weight",
-                         ".kda.f_up.weight", ".erase.e_down.weight", ".erase.e_up.weight", ".erase.in_proj_gamma.weight")
+                         ".kda.f_up.weight", ".erase.e_down.weight", ".erase.e_up.weight", ".erase.in_proj_gamma.weight",
+                         ".dprod.k_down.weight", ".dprod.k_up.weight")      # the derived second key's low-rank address pair
 ALIGN = 64
 
 

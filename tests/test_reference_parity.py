@@ -20,7 +20,7 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "dprod_layers", "dprod_heads", "dprod_mixed", "ldm"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "dprod_layers", "dprod_heads", "dprod_mixed", "dprod_lowrank", "dprod_prev", "dprod_perm", "dprod_perm_random", "dprod_rot", "ldm"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase", "dprod")) else C.tiny_full_config()
@@ -47,6 +47,14 @@ def test_state_dict_forward_backward(reference, preset):
             d = cfg.encoder.gdn.dprod
             d.n_h, d.layers, d.heads, d.heads_by_layer = 3, (1, 2, 5), 2, {2: (2, 3), 5: (0, 1, 2, 3)}
             cfg.encoder.gdn.kernel, cfg.encoder.gdn.chunk_size = "chunked", 16
+        if preset in ("dprod_lowrank", "dprod_prev", "dprod_perm", "dprod_perm_random", "dprod_rot"):      # the second step made from the first
+            d = cfg.encoder.gdn.dprod
+            d.n_h, d.key, d.value, d.conv = 2, preset.split("_")[1], "v1", False
+            if preset == "dprod_lowrank":
+                d.rank = 4
+            if preset == "dprod_perm_random":
+                d.perm = "random"
+                cfg.encoder.gdn.kernel, cfg.encoder.gdn.chunk_size = "chunked", 16
         if preset == "dprod_b1":
             cfg.encoder.gdn.dprod.beta_max, cfg.encoder.gdn.dprod.beta_init = 1, 0.95
     if preset.endswith("erase"):
@@ -591,5 +599,53 @@ def test_delta_product_placement_is_resolved_and_refused_by_name():
             build_model(bad)
     off = C.tiny_control_config()
     off.encoder.gdn.dprod.heads = 2
+    with pytest.raises(ValueError, match="n_h 1"):
+        build_model(off)
+
+
+def test_delta_product_derived_second_step_tensors_and_refusals():
+    """The second step made from the first: the tensors each key adds, their optimizer group, the size of the low-rank
+    correction at the start, the rotation, the previous key across a cached cut, and the values refused by name."""
+    from gdn_hybrid_architecture_ideas_b200.models import gdn_dprod_derived as D
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    def cfg_of(key, **kw):
+        cfg = C.tiny_control_config()
+        d = cfg.encoder.gdn.dprod
+        d.n_h, d.key, d.value, d.conv = 2, key, "v1", False
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return cfg
+
+    cfg = cfg_of("lowrank", rank=4)
+    model = build_model(cfg)
+    steps = model.encoder.layers[0].mixer.dprod
+    g = cfg.encoder.gdn
+    assert sum(p.numel() for p in steps.parameters()) == D.params_per_layer(cfg.d_model, g)
+    x = torch.randn(4, 64, cfg.d_model)
+    k1 = torch.nn.functional.normalize(torch.randn(4, 64, g.n_k_heads, g.k_head_dim), dim=-1)
+    k2 = steps.second_key(x, k1, torch.zeros(4, 64, dtype=torch.bool), None)
+    cos = float((k1 * k2).sum(-1).mean())
+    assert 0.5 < cos < 0.9 and abs(float(k2.norm(dim=-1).mean()) - 1) < 1e-3          # a second address of k1's size, not k1 itself
+    groups = optim.param_groups(model, C.OptimConfig(name="muon"))
+    muon = [n for grp in groups if grp["kind"] == "muon" for n in grp["names"]]
+    assert not any(".dprod." in n for n in muon)
+    rot = build_model(cfg_of("rot")).encoder.layers[0].mixer.dprod.rot.double()
+    assert (rot @ rot.T - torch.eye(rot.shape[0], dtype=torch.double)).abs().max() < 1e-6 and abs(float(torch.linalg.det(rot)) - 1) < 1e-5
+    prev = build_model(cfg_of("prev")).double().eval()
+    tok, doc = random_rows(2, 40)
+    with torch.no_grad():
+        out = prev.prefill(tok[:, :17], doc[:, :17])
+        assert out.cache.encoder[0].k_prev.shape == (2, g.n_k_heads, g.k_head_dim)
+        out.cache.encoder[0].k_prev = None
+        with pytest.raises(ValueError, match="previous key"):
+            prev.extend(tok[:, 17:], doc[:, 17:], None, out.cache)
+    for key, kw, match in (("lowrank", {"rank": 99}, "rank"), ("prev", {"rank": 4}, "rank"), ("rot", {"perm": "random"}, "perm"), ("perm", {"value": "proj"}, "value"),
+                           ("perm", {"conv": True}, "conv"), ("perm", {"n_h": 3}, "n_h 2"), ("perm", {"beta_max": 1}, "beta_max"), ("perm", {"heads": 2}, "every head"),
+                           ("twist", {}, "one of"), ("proj", {}, "proj")):
+        with pytest.raises(ValueError, match=match):
+            build_model(cfg_of(key, **kw))
+    off = C.tiny_control_config()
+    off.encoder.gdn.dprod.key = "rot"
     with pytest.raises(ValueError, match="n_h 1"):
         build_model(off)
