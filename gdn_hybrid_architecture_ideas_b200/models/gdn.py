@@ -20,7 +20,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..config import GDNConfig
-from . import gdn_dprod, gdn_dprod_derived, gdn_erase, gdn_kda
+from . import gdn_dprod, gdn_dprod_derived, gdn_dprod_sparse, gdn_erase, gdn_kda
 from .linear import Linear
 from .norms import GatedRMSNorm
 from .sequence import SeqContext
@@ -36,6 +36,8 @@ class GDNState:
     ckpt: torch.Tensor | None = None    # a cross-read writer only: the checkpoint the next token reads (B, Hv, dk, dv)
     ccr: object | None = None           # the record a writer's call hands its readers; taken out by the stack, never cached
     k_prev: torch.Tensor | None = None  # gdn.dprod.key 'prev' only: the unit key of the last token processed (B, Hk, dk)
+    acc: torch.Tensor | None = None     # gdn.dprod.summary only: the sums (B, F) and the count (B,) of the group of tokens still open
+    cnt: torch.Tensor | None = None
 
 
 class GDNArms(nn.Module):
@@ -284,6 +286,11 @@ class GatedDeltaNet(nn.Module):
         cfg = self.cfg
         B, L = ctx.doc.shape
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+        if isinstance(self.dprod, gdn_dprod_sparse.SparseSteps):
+            o, conv_input, conv_doc, S, acc, cnt = gdn_dprod_sparse.forward(self, x, ctx, state)
+            z = self.in_proj_z(x).view(B, L, hv, dv)
+            y = self.out_proj(self.norm(o.to(x.dtype), z).flatten(2))
+            return y, GDNState(conv_input=conv_input, conv_doc=conv_doc, S=S, acc=acc, cnt=cnt)
         if isinstance(self.dprod, gdn_dprod_derived.DerivedSteps):
             o, conv_input, conv_doc, S, k_prev = gdn_dprod_derived.forward(self, x, ctx, state)
             z = self.in_proj_z(x).view(B, L, hv, dv)

@@ -62,12 +62,17 @@ def check_config(cfg) -> None:
                          "resolved per layer (the layer is given its heads)")
     from .gdn_dprod_derived import check_second, is_derived
 
-    check_second(cfg)
-    moved = [k for k in ("route", "stride", "summary", "first_beta") if getattr(d, k) != getattr(default, k)]
-    if moved:
-        raise ValueError(f"gdn.dprod {', '.join(moved)}: the one-readout route and the strided / summarised second steps are not built "
-                         "(built: projected steps with placement, and a second step derived from the first)")
-    if is_derived(cfg):
+    from . import gdn_dprod_sparse
+
+    gdn_dprod_sparse.check_keys(cfg)
+    if not gdn_dprod_sparse.is_sparse(cfg):
+        check_second(cfg)
+    if d.route != default.route:
+        raise ValueError(f"gdn.dprod.route {d.route!r}: the one-readout route is a kernel of the reference's fused path; the rule here runs as "
+                         "tensor ops on the interleave (leave it 'interleave')")
+    if isinstance(d.beta_max, bool) or d.beta_max not in BETA_MAXES:
+        raise ValueError(f"gdn.dprod.beta_max {d.beta_max!r}: 1 (beta = sigmoid(b)) or 2 (beta = 2 sigmoid(b), the default)")
+    if is_derived(cfg) or gdn_dprod_sparse.is_sparse(cfg):
         if n > 1 and (cfg.negeig.beta_max != 1 or cfg.kda.decay != "scalar" or cfg.erase.mode != "none"):
             raise ValueError("gdn.dprod.n_h >= 2 is built on the scalar-decay layer alone: negeig.beta_max 1, kda.decay 'scalar', erase.mode 'none'")
         return
@@ -96,6 +101,11 @@ def check_model(cfg) -> None:
     if is_derived(cfg.encoder.gdn) and (d.layers != () or d.heads != 0 or d.heads_by_layer != {}):
         raise ValueError(f"model.encoder.gdn.dprod.layers / heads / heads_by_layer with dprod.key {d.key!r}: the derived second step is built "
                          "for every head of every GDN layer")
+    from . import gdn_dprod_sparse
+
+    if gdn_dprod_sparse.is_sparse(cfg.encoder.gdn) and (d.layers != () or d.heads != 0 or d.heads_by_layer != {} or cfg.encoder.gdn_shape_by_layer):
+        raise ValueError("model.encoder.gdn.dprod.layers / heads / heads_by_layer (or gdn_shape_by_layer) with dprod.stride / summary / conv: "
+                         "the second step on a subset of the tokens is built for every head of every GDN layer")
     partial = [i for i, (c, heads) in enumerate(cfg.encoder.gdn_layer_configs()) if heads is not None]
     if partial and (d.beta_max != 2 or d.beta_init is not None):
         raise ValueError(f"model.encoder.gdn.dprod.beta_max / beta_init with GDN layer(s) {partial} that carry only some of their value heads: "
@@ -201,8 +211,13 @@ def build_steps(d_model: int, cfg, carry: tuple | None):
         if carry:
             raise ValueError(f"gdn.dprod.n_h 1 with carrying heads {tuple(carry)!r}: a layer that does not carry has none")
         return None
+    from . import gdn_dprod_sparse
     from .gdn_dprod_derived import DerivedSteps, is_derived
 
+    if gdn_dprod_sparse.is_sparse(cfg):
+        if carry is not None and tuple(carry) != tuple(range(cfg.n_v_heads)):
+            raise ValueError(f"gdn.dprod.stride / summary / conv with the carrying value heads {tuple(carry)!r}: not built together with a placement")
+        return gdn_dprod_sparse.SparseSteps(d_model, cfg)
     if is_derived(cfg):
         if carry is not None and tuple(carry) != tuple(range(cfg.n_v_heads)):
             raise ValueError(f"gdn.dprod.key {cfg.dprod.key!r} with the carrying value heads {tuple(carry)!r}: the derived second step is built for every head of a layer")
@@ -214,8 +229,9 @@ def build_steps(d_model: int, cfg, carry: tuple | None):
 
 def init_own_parameters(model: nn.Module, std: float) -> int:
     from .gdn_dprod_derived import DerivedSteps
+    from .gdn_dprod_sparse import SparseSteps
 
-    steps = [m for m in model.modules() if isinstance(m, (DeltaProductSteps, DerivedSteps))]
+    steps = [m for m in model.modules() if isinstance(m, (DeltaProductSteps, DerivedSteps, SparseSteps))]
     if steps:
         g = torch.Generator().manual_seed((torch.initial_seed() + SEED_OFFSET) % (1 << 63))
         for m in steps:

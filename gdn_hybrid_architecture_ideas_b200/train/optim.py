@@ -22,7 +22,7 @@ NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gai
                      # a looped middle's injection (models/recur.py): B starts at the identity and w near 1, decay would pull both
                      # away from their starts; A_log / dt_bias are covered by the GDN suffixes above
                      "injection.B", ".recur_mix")
-ZERO_GATE_SUFFIXES = (".gdn_arms.ccr_gate", ".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale")
+ZERO_GATE_SUFFIXES = (".gdn_arms.ccr_gate", ".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale", ".dprod.beta_const")
 # The cross-read's query translators (models/ccr.py): D = M - I, (H_k, d_k, d_k) a reader, never a Muon matrix (3-D). One
 # AdamW group of their own, the last, at the depth readers' learning rate; optim.ccr_translator_decay "none": no decay,
 # "identity": the run's weight decay, which on D pulls M toward the identity (reference: ced/train/optim.py:283-312).

@@ -20,7 +20,8 @@ def _pair(reference, cfg):
     return mine, theirs
 
 
-@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "dprod_layers", "dprod_heads", "dprod_mixed", "dprod_lowrank", "dprod_prev", "dprod_perm", "dprod_perm_random", "dprod_rot", "ldm"])
+@pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "dprod_layers", "dprod_heads", "dprod_mixed", "dprod_lowrank", "dprod_prev", "dprod_perm", "dprod_perm_random", "dprod_rot",
+                                    "dprod_noconv", "dprod_stride", "dprod_stride_all", "dprod_xmean", "dprod_kvmean", "dprod_xmean_b1", "ldm"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase", "dprod")) else C.tiny_full_config()
@@ -55,6 +56,17 @@ def test_state_dict_forward_backward(reference, preset):
             if preset == "dprod_perm_random":
                 d.perm = "random"
                 cfg.encoder.gdn.kernel, cfg.encoder.gdn.chunk_size = "chunked", 16
+        sparse = {"dprod_noconv": {}, "dprod_stride": {"stride": 4}, "dprod_stride_all": {"stride": 4, "first_beta": "all", "chunked": True},
+                  "dprod_xmean": {"stride": 8, "summary": "xmean"}, "dprod_kvmean": {"stride": 8, "summary": "kvmean", "chunked": True},
+                  "dprod_xmean_b1": {"stride": 3, "summary": "xmean", "beta_max": 1, "chunked": True}}
+        if preset in sparse:                   # the second step on a subset of the tokens (cached cuts fall inside groups)
+            d = cfg.encoder.gdn.dprod
+            d.n_h, d.conv = 2, False
+            for k, v in sparse[preset].items():
+                if k == "chunked":
+                    cfg.encoder.gdn.kernel, cfg.encoder.gdn.chunk_size = "chunked", 16
+                else:
+                    setattr(d, k, v)
         if preset == "dprod_b1":
             cfg.encoder.gdn.dprod.beta_max, cfg.encoder.gdn.dprod.beta_init = 1, 0.95
     if preset.endswith("erase"):
@@ -642,10 +654,59 @@ def test_delta_product_derived_second_step_tensors_and_refusals():
             prev.extend(tok[:, 17:], doc[:, 17:], None, out.cache)
     for key, kw, match in (("lowrank", {"rank": 99}, "rank"), ("prev", {"rank": 4}, "rank"), ("rot", {"perm": "random"}, "perm"), ("perm", {"value": "proj"}, "value"),
                            ("perm", {"conv": True}, "conv"), ("perm", {"n_h": 3}, "n_h 2"), ("perm", {"beta_max": 1}, "beta_max"), ("perm", {"heads": 2}, "every head"),
-                           ("twist", {}, "one of"), ("proj", {}, "proj")):
+                           ("twist", {}, "one of"), ("proj", {}, "not built together")):
         with pytest.raises(ValueError, match=match):
             build_model(cfg_of(key, **kw))
     off = C.tiny_control_config()
     off.encoder.gdn.dprod.key = "rot"
+    with pytest.raises(ValueError, match="n_h 1"):
+        build_model(off)
+
+
+def test_delta_product_sparse_second_step_layout_and_refusals():
+    """The second step on a subset of the tokens: the row layout's maps, the group sums across documents and calls, the tensors
+    each form holds, and the values refused by name."""
+    from gdn_hybrid_architecture_ideas_b200.models import gdn_dprod_sparse as SP
+
+    rows, last, n_c = SP.row_maps(10, 4, 1)                # tokens 1, 5, 9 carry
+    assert n_c == 3 and rows == [0, 1, 10, 2, 3, 4, 5, 11, 6, 7, 8, 9, 12] and last == [0, 2, 3, 4, 5, 7, 8, 9, 10, 12]
+    assert SP.carry_flags(10, 4, 2) == [i in (1, 5, 9) for i in range(10)] and SP.first_carry(2, 4) == 1
+    u = torch.arange(20.0).reshape(1, 10, 2)
+    doc = torch.tensor([[0, 0, 0, 0, 1, 1, 1, 1, 1, 1]])
+    sums, counts = SP.group_sums(u, doc, 4, 1, (torch.tensor([[100.0, 200.0]]), torch.tensor([2.0]), torch.tensor([1.0])))
+    assert counts.tolist() == [[4.0, 2.0, 4.0]]            # head group: tokens 0, 1 and the two carried; second: tokens 4, 5 of document 1 only
+    assert sums[0, 0].tolist() == [102.0, 204.0] and sums[0, 1].tolist() == [18.0, 20.0]
+    acc, cnt = SP.tail_sums(u[:, :9], doc[:, :9], 4, 1)
+    assert cnt.tolist() == [3.0] and acc[0].tolist() == [12.0 + 14 + 16, 13.0 + 15 + 17]
+
+    def cfg_of(**kw):
+        cfg = C.tiny_control_config()
+        d = cfg.encoder.gdn.dprod
+        d.n_h, d.conv = 2, False
+        for k, v in kw.items():
+            setattr(d, k, v)
+        return cfg
+
+    g = C.tiny_control_config().encoder.gdn
+    for kw in ({"stride": 4}, {"stride": 8, "summary": "kvmean"}):
+        model = build_model(cfg_of(**kw))
+        steps = model.encoder.layers[0].mixer.dprod
+        assert sum(p.numel() for p in steps.parameters()) == SP.params_per_layer(model.cfg.d_model, cfg_of(**kw).encoder.gdn)
+        assert not hasattr(steps, "conv_weight")
+    tok, doc2 = random_rows(2, 40)
+    summed = build_model(cfg_of(stride=8, summary="xmean")).double().eval()
+    with torch.no_grad():
+        out = summed.prefill(tok[:, :17], doc2[:, :17])
+        assert out.cache.encoder[0].acc.shape == (2, summed.cfg.d_model) and out.cache.encoder[0].cnt.shape == (2,)
+        out.cache.encoder[0].acc = None
+        with pytest.raises(ValueError, match="running sums"):
+            summed.extend(tok[:, 17:], doc2[:, 17:], None, out.cache)
+    for kw, match in (({"stride": 4, "conv": True}, "conv"), ({"stride": 0}, "stride"), ({"summary": "max"}, "one of"), ({"stride": 4, "n_h": 3}, "n_h 2"),
+                      ({"stride": 4, "heads": 2}, "placement|every head"), ({"stride": 4, "key": "rot", "value": "v1"}, "not built together"),
+                      ({"stride": 4, "beta_init": 0.9}, "beta_init"), ({"first_beta": "some"}, "one of"), ({"sparse_path": "slow"}, "sparse_path")):
+        with pytest.raises(ValueError, match=match):
+            build_model(cfg_of(**kw))
+    off = C.tiny_control_config()
+    off.encoder.gdn.dprod.stride = 4
     with pytest.raises(ValueError, match="n_h 1"):
         build_model(off)
