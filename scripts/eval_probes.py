@@ -36,14 +36,15 @@ def main(argv=None) -> int:
     model, cfg, step = ckpt.load_model(a.checkpoint, a.device)
     ac = torch.bfloat16 if a.device.startswith("cuda") else None
     table, item_records = {}, []
-    stored = stored_ids = None
+    stored = stored_ids = stored_recs = None
     if a.set:
         blob = torch.load(a.set, map_location="cpu", weights_only=False)
         if blob["vocab"] > cfg.model.vocab_size:
             ap.error(f"the set was built for a vocabulary of {blob['vocab']}, the model has {cfg.model.vocab_size}")
-        stored, stored_ids = {}, {}
+        stored, stored_ids, stored_recs = {}, {}, {}
         for p in blob["probes"]:
             stored_ids.setdefault((p.get("cell", p["length"]), p["kind"]), []).append(p.get("id"))
+            stored_recs.setdefault((p.get("cell", p["length"]), p["kind"]), []).append(p)
             # token-id sets are keyed by their nominal length; text-level sets (scripts/build_text_probes.py) by their cell
             stored.setdefault((p.get("cell", p["length"]), p["kind"]), []).append(
                 probes.Probe(p["kind"], p["ids"], p["answer_start"], p["answer_len"], tuple(map(tuple, p.get("pieces", ()))), p.get("group", ""),
@@ -52,8 +53,13 @@ def main(argv=None) -> int:
     for length, kind in cells:
         ps = stored[(length, kind)] if stored is not None else [
             probes.build_probe(kind, cfg.model.vocab_size, length, a.seed, i) for i in range(a.per_kind)]
-        r = probes.score_probes(model, ps, a.batch_size, ac)
+        synth = stored_recs is not None and any("floor" in p or "question" in p for p in stored_recs[(length, kind)])
+        r = probes.score_probes(model, ps, a.batch_size, ac, keep_tokens=synth)
         cell = {"exact": r["exact"], "ce": r["ce"], "n": r["n"]}
+        if synth:        # the probes on synthetic material (scripts/build_synth_probes.py): floors, near-duplicate tokens, line choices
+            from gdn_hybrid_architecture_ideas_b200.eval.probe_synth import cell_extras
+
+            cell.update(cell_extras(stored_recs[(length, kind)], r["items"]))
         if stored_ids is not None and a.keep_items:
             item_records += [{"id": i, "kind": kind, "exact": bool(it["exact"]), "ce": it["ce"]} for i, it in zip(stored_ids[(length, kind)], r["items"])]
         groups = sorted({it["group"] for it in r["items"] if "group" in it})
@@ -65,7 +71,7 @@ def main(argv=None) -> int:
                 cell[key] = sum(float(it[key]) for it in r["items"]) / len(r["items"])
         if any("choice_ok" in it for it in r["items"]):
             cell["choice_acc"] = sum(float(it.get("choice_ok", 0.0)) for it in r["items"]) / len(r["items"])
-        if kind == "transcode":
+        if kind == "transcode" and not synth:       # the token-id transcode probe; the synthetic-material one stores its floor per item
             floors = [probes.copy_floor(q) for q in ps]
             cell["copy_floor"] = {k: sum(float(f[k]) for f in floors) / len(floors) for k in ("token_acc", "lcs_share")}
         table[f"{kind}@{length}"] = cell
