@@ -752,7 +752,7 @@ _BUILT = {
     "model.encoder.gdn_write_mix": ("none", "layer"),
     "model.encoder.gdn_write_variant": ("none", "qmix", "korig", "vonly", "kqmix", "qshare", "qshare_kv", "qshare_bd"),
     "model.encoder.residual_dtype": ("float32", "bf16"),
-    "model.loop.pass2_gate": ("none",),
+    "model.loop.pass2_gate": ("none", "scalar"),
     "model.loop.segment_passes": (None,),
     "model.loop.unscored_passes": (None,),
     "model.mtp.enabled": (False, True),
@@ -788,7 +788,6 @@ _TRAIN_BUILT = {
     "data.union_order": ("permute", "sets_in_order"),
     "decoder_opt": ("none",),
     "optim.recur_b": ("adamw",),                  # the looped middle's injection matrix under Muon is not built
-    "loop_switch_step": (0,),
 }
 
 

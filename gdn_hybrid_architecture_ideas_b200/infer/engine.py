@@ -57,6 +57,9 @@ class DecodeEngine:
         if self.cfg.loop.recur_layers:
             raise ValueError("the decode engine walks every layer once; a looped middle (model.loop.recur_layers) generates through the "
                              "model's cached forward (eval.generate)")
+        if self.cfg.loop.pass2_gate != "none":
+            raise ValueError("the decode engine runs one pass; a gated second pass (model.loop.pass2_gate) generates through the model's "
+                             "cached forward (eval.generate)")
         if self.cfg.encoder.gdn_ccr_spacing:
             raise ValueError("the decode engine keeps one state a GDN layer; the checkpoint cross-read (model.encoder.gdn_ccr_spacing) "
                              "generates through the model's cached forward (eval.generate)")

@@ -370,7 +370,7 @@ class Encoder(nn.Module):
                 with self.host_pool.offload():
                     return layer(x, ctx, cache, sources, need_state, None, premixed)
             return layer(x, ctx, cache, sources, need_state, None, premixed)
-        if mode == "layer" and training:
+        if mode == "layer" and training and not getattr(layer, "keep_record", False):     # a layer a second pass reads again keeps its outputs
             def call(x_, *src):
                 return layer(x_, ctx, None, list(src) if src else None, False)[0]
             return act_checkpoint.run_checkpointed(call, x, *(sources or ())), None

@@ -36,6 +36,7 @@ class GDNState:
     ckpt: torch.Tensor | None = None    # a cross-read writer only: the checkpoint the next token reads (B, Hv, dk, dv)
     ccr: object | None = None           # the record a writer's call hands its readers; taken out by the stack, never cached
     k_prev: torch.Tensor | None = None  # gdn.dprod.key 'prev' only: the unit key of the last token processed (B, Hk, dk)
+    pass1: object | None = None         # the record a read-only second pass reads (models/second_pass.py); taken out by the model, never cached
     acc: torch.Tensor | None = None     # gdn.dprod.summary only: the sums (B, F) and the count (B,) of the group of tokens still open
     cnt: torch.Tensor | None = None
 
@@ -143,6 +144,7 @@ class GatedDeltaNet(nn.Module):
         bound = 1.0 / math.sqrt(cfg.conv_kernel)
         nn.init.uniform_(self.conv_weight, -bound, bound)
         self.write_mix = "none"
+        self.keep_record = False        # set for one forward by a model with a second pass: the layer also leaves what that pass reads
         self.arms_attached = False      # set by the encoder on a layer that holds GDNArms (a write mix, a cross-read, or both)
         # The erase direction (gdn.erase.mode 'eda'): its tensors come last and draw nothing from the global stream.
         gdn_erase.check_config(cfg)
@@ -218,6 +220,11 @@ class GatedDeltaNet(nn.Module):
             return self.forward_kda(x, ctx, state, arms)
         if arms is not None and (arms.ccr_read or arms.ccr_write):
             return self.forward_ccr(x, ctx, state, arms, x_write, x_read, ccr)
+        if self.keep_record:
+            from .second_pass import gdn_forward_keep
+
+            y, new_state, new_state.pass1 = gdn_forward_keep(self, x, ctx, state)
+            return y, new_state
         B, L = ctx.doc.shape       # the input may be a token shard (tensor parallel); projections return all tokens
         cfg = self.cfg
         hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim

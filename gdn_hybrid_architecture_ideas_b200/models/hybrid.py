@@ -49,11 +49,20 @@ class HybridLM(nn.Module):
         if cfg.arch != "control":
             raise ValueError(f"model.arch {cfg.arch!r}: this framework builds arch 'control' (the hybrid stack)")
         self.cfg = cfg
+        from . import second_pass
+
+        second_pass.check_config(cfg)
+        self.gated = second_pass.is_on(cfg)                      # a read-only second pass through the top `pass2_layers` layers
+        self.pass2_from = cfg.encoder.n_layers - (cfg.loop.pass2_layers if self.gated else 0)
+        if self.gated and cfg.loop.loop_embedding:
+            self.loop_embedding_pass2 = nn.Parameter(torch.zeros(cfg.d_model))
         self.embed = nn.Embedding(cfg.vocab_size, cfg.d_model)
         self.embed_norm = RMSNorm(cfg.d_model, cfg.norm_eps) if cfg.embed_norm else nn.Identity()
         self.encoder = Encoder(cfg)
         self.final_norm = RMSNorm(cfg.d_model, cfg.norm_eps)
         self.out_embed = None if cfg.tie_embeddings else nn.Embedding(cfg.vocab_size, cfg.d_model)
+        if self.gated:
+            self.hyper_connections = second_pass.SecondPassGate()
         self.head_weight_lp: torch.Tensor | None = None  # bf16 shadow of the head matrix (set by the engine)
         self.tp = None      # tensor-parallel context (parallel.tp_model.apply): the stream is then this rank's token shard
         for m in self.modules():
@@ -88,15 +97,34 @@ class HybridLM(nn.Module):
         e = ops.embedding(tokens, self.embed.weight)
         return self.embed_norm(e, out_dtype=e.dtype) if self.cfg.embed_norm else e   # the residual stream keeps the table's dtype
 
+    def pass2_parameter_names(self) -> list[str]:
+        from .second_pass import PASS2_PARAMETERS
+
+        return [n for n, _ in self.named_parameters() if n in PASS2_PARAMETERS] if self.gated else []
+
+    def alpha(self):
+        """The second pass's gate (0-dim, detached) or None."""
+        return self.hyper_connections.pass2_gate.detach() if self.gated else None
+
     def forward(self, tokens: torch.Tensor, doc_ids: torch.Tensor, dec_mask=None, T=None, capacity=None,
                 cache: ControlCache | None = None, return_cache: bool = False, return_hidden: bool = False,
                 varlen: dict | None = None, rope_scale: int = 1, gdn_scale: int = 1, gdn_beta_power: bool = False,
-                single_doc: bool = False) -> ModelOutput:
+                single_doc: bool = False, pass2_mask: torch.Tensor | None = None, pass2_capacity: int | None = None) -> ModelOutput:
         """tokens (B, L) or bags (B, L, s); doc_ids (B, L). return_hidden: give the head input instead of logits
         (the fused loss consumes it). single_doc: the caller guarantees every row is one document (kernels skip
-        the document masks). T: the pass count of a looped middle (models/recur.py; default loop.t_eval, or the cache's own T;
-        ignored by every other model). dec_mask and capacity are accepted for call compatibility and ignored
-        (reference: ced/model/control.py:716-872)."""
+        the document masks). T: the pass count of a looped middle (models/recur.py; default loop.t_eval, or the cache's own T)
+        or of a stack with a gated second pass (models/second_pass.py: 1 or 2, default loop.t_eval; at T = 2 pass 2 runs at
+        every position, or is kept at the first pass2_capacity positions of each row that pass2_mask marks, and `kept` /
+        `n_dropped` say where); ignored by every other model. dec_mask and capacity are accepted for call compatibility and
+        ignored (reference: ced/model/control.py:716-872)."""
+        two = False
+        if self.gated:
+            T = self.cfg.loop.t_eval if T is None else T
+            if T not in (1, 2):
+                raise ValueError(f"T={T!r}: a stack with a second pass runs T = 1 or T = 2")
+            two = T == 2 and not (pass2_mask is not None and pass2_capacity == 0)
+        elif pass2_mask is not None or pass2_capacity is not None:
+            raise ValueError("pass2_mask / pass2_capacity belong to a model with a gated second pass (model.loop.pass2_gate)")
         if self.encoder.recur is not None:
             if cache is not None:
                 if T is not None and T != cache.T:
@@ -104,7 +132,7 @@ class HybridLM(nn.Module):
                 T = cache.T
             elif T is None:
                 T = int(os.environ.get("GHB_LOOP_T", self.cfg.loop.t_eval))
-        else:
+        elif not self.gated:
             T = None
         ctx, seq_state = sequence_context(doc_ids, cache.seq if cache else None)
         ctx.single_doc = bool(single_doc) and cache is None
@@ -123,22 +151,55 @@ class HybridLM(nn.Module):
             tp.batch_shape = (B, L)
             per = B * L // tp.world
             tokens = tokens.reshape(B * L, *tokens.shape[2:])[tp.rank * per:(tp.rank + 1) * per][None]     # this rank's token shard
-        h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state, T=T)
+        kept = n_dropped = None
+        if two:
+            from . import second_pass
+
+            if tokens.dim() == 3 or rope_scale != 1 or gdn_scale != 1 or self.tp is not None:
+                raise ValueError("bags of tokens, rope_scale, gdn_scale and tensor parallel run on the one-pass stack")
+            block = list(self.encoder.layers)[self.pass2_from:]
+            for layer in block:
+                layer.keep_record = layer.mixer.keep_record = True
+            try:
+                z1, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state)
+            finally:
+                for layer in block:
+                    layer.keep_record = layer.mixer.keep_record = False
+            records = []
+            for layer, c in zip(block, caches[self.pass2_from:]):
+                if layer.kind == "gdn":
+                    records.append(c.pass1)
+                    c.pass1 = None                                   # the cache is pass 1's: the record does not travel with it
+                else:
+                    records.append(c)
+            checkpoint = cache is None and self.encoder.activation_checkpoint == "layer" and torch.is_grad_enabled() and z1.requires_grad
+            h, kept, n_dropped = second_pass.second_pass(self, z1, ctx, records, pass2_mask, pass2_capacity, checkpoint)
+            self.last_loop_usage = second_pass.loop_usage(z1.detach(), h.detach(), kept)
+        else:
+            h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state,
+                                     T=None if self.gated else T)
         hidden = self.final_norm(h)
         logits = None if return_hidden else lm_head(hidden, self.head_weight())
         return ModelOutput(
             logits=logits, hidden_aux=hidden if return_hidden else None,
-            kept=torch.zeros(B, L, dtype=torch.bool, device=tokens.device),
-            n_dropped=torch.zeros(B, dtype=torch.long, device=tokens.device),
+            kept=torch.zeros(B, L, dtype=torch.bool, device=tokens.device) if kept is None else kept,
+            n_dropped=torch.zeros(B, dtype=torch.long, device=tokens.device) if n_dropped is None else n_dropped,
             cache=ControlCache(seq=seq_state, encoder=caches, T=T or 1) if return_cache else None)
+
+    def _pass2_at(self, dec_mask, T) -> dict:
+        """prefill / extend: a decoder mask marks the positions whose logits are read, so pass 2 is kept there alone, with as
+        many slots as the fullest row has marked positions (one host read of the mask: inference only)."""
+        if dec_mask is None or not self.gated or (self.cfg.loop.t_eval if T is None else T) == 1:
+            return {}
+        return {"pass2_mask": dec_mask.bool(), "pass2_capacity": int(dec_mask.bool().sum(1).max())}
 
     @torch.no_grad()
     def prefill(self, tokens, doc_ids, dec_mask=None, T=None) -> ModelOutput:
-        return self.forward(tokens, doc_ids, return_cache=True, T=T)
+        return self.forward(tokens, doc_ids, return_cache=True, T=T, **self._pass2_at(dec_mask, T))
 
     @torch.no_grad()
     def extend(self, tokens, doc_ids, dec_mask, cache: ControlCache, T=None) -> ModelOutput:
-        return self.forward(tokens, doc_ids, cache=cache, return_cache=True, T=T)
+        return self.forward(tokens, doc_ids, cache=cache, return_cache=True, T=T, **self._pass2_at(dec_mask, T))
 
 
 def build_model(cfg: ModelConfig) -> HybridLM:

@@ -119,6 +119,21 @@ def param_groups(model, o) -> list[dict]:
         raise ValueError(f"optim.gdn_mup_base_width {o.gdn_mup_base_width!r} is read with optim.gdn_mup true: leave it {GDN_MUP_BASE_WIDTH}")
     if o.gdn_mup:
         spec = _gdn_mup_spec(spec, model, o, 1.0 if o.name == "adamw" else o.adamw_lr_scale)
+    # A gated second pass's own tensors (models/second_pass.py): AdamW groups of their own at optim.pass2_lr_scale x the LR of
+    # the other AdamW tensors; the pass-2 embedding with the run's weight decay, the gate without (reference: ced/train/optim.py:388-398).
+    from ..models.second_pass import PASS2_PARAMETERS
+
+    later = [(n, p) for n, p in named if n in PASS2_PARAMETERS]
+    if not (isinstance(o.pass2_lr_scale, (int, float)) and o.pass2_lr_scale > 0):
+        raise ValueError(f"optim.pass2_lr_scale {o.pass2_lr_scale!r}: a positive multiplier")
+    if later:
+        taken = {n for n, _ in later}
+        base = (1.0 if o.name == "adamw" else o.adamw_lr_scale) * o.pass2_lr_scale
+        spec = [(k, [(n, p) for n, p in items if n not in taken], wd, sc) for k, items, wd, sc in spec]
+        spec.append(("adamw", [(n, p) for n, p in later if not n.endswith("pass2_gate")], o.weight_decay, base))
+        spec.append(("adamw", [(n, p) for n, p in later if n.endswith("pass2_gate")], 0.0, base))
+    elif o.pass2_lr_scale != 1.0:
+        raise ValueError(f"optim.pass2_lr_scale {o.pass2_lr_scale!r} scales the LR of a gated second pass's tensors (model.loop.pass2_gate); this model has none: leave it 1.0")
     if o.ccr_translator_decay not in CCR_TRANSLATOR_DECAY_MODES:
         raise ValueError(f"optim.ccr_translator_decay {o.ccr_translator_decay!r}: one of {CCR_TRANSLATOR_DECAY_MODES}")
     mats = [(n, p) for n, p in named if n.endswith(CCR_TRANSLATOR_SUFFIX)]

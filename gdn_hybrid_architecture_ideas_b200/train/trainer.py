@@ -73,6 +73,7 @@ class Trainer:
         # A looped middle (models/recur.py): one pass count per optimizer step, drawn from loop.t_choices / t_probs; what it
         # is not built together with is refused here, by key.
         self.looped = bool(cfg.model.loop.recur_layers)
+        self.gated = cfg.model.loop.pass2_gate != "none"          # a read-only second pass (models/second_pass.py): T = 1 before loop_switch_step, then 2
         self.pass_count = 1
         if self.looped:
             clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
@@ -82,6 +83,22 @@ class Trainer:
             hit = [k for k, v in clashes.items() if v]
             if hit:
                 raise ValueError(f"model.loop.recur_layers (the looped middle) is not built together with: {', '.join(hit)}")
+        S = cfg.loop_switch_step
+        if type(S) is not int or not 0 <= S < max(cfg.steps, 1):
+            raise ValueError(f"loop_switch_step {S!r}: an optimizer step S with 0 <= S < steps ({cfg.steps})")
+        if S and not self.gated:
+            raise ValueError(f"loop_switch_step {S} switches a gated second pass on (model.loop.pass2_gate 'scalar' with pass2_layers): this model has none")
+        if self.gated:
+            clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
+                       "shape_schedule": bool(cfg.shape_schedule), "optim.schedule_steps": cfg.optim.schedule_steps is not None,
+                       "optim.switch_warmup_steps": bool(cfg.optim.switch_warmup_steps),
+                       "optimizer_sharding 'zero2' (its buckets follow one backward pass over the blocks)": cfg.optimizer_sharding == "zero2",
+                       "activation_checkpoint 'block' / 'host' / 'host_overlap'": cfg.activation_checkpoint in ("block", "host", "host_overlap")}
+            hit = [k for k, v in clashes.items() if v]
+            if hit:
+                raise ValueError(f"model.loop.pass2_gate (the gated second pass) is not built together with: {', '.join(hit)}")
+            if list(cfg.model.loop.t_choices) != [2]:
+                raise ValueError(f"model.loop.t_choices {cfg.model.loop.t_choices!r}: the gated second pass trains at T = 2, [2]; T = 1 before a switch-on is loop_switch_step")
         if cfg.tensor_parallel > 1:
             from ..parallel import tp_model
 
@@ -295,7 +312,7 @@ class Trainer:
             kw.update(gdn_scale=s, gdn_beta_power=cfg.tst.gdn_resolution_gates == "E")
         if s > 1 and cfg.tst.token_scale_rope:
             kw.update(rope_scale=s)
-        if self.looped:
+        if self.looped or self.gated:
             kw.update(T=self.pass_count)
         ac = torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast and not self.native)
         with ac:
@@ -426,6 +443,8 @@ class Trainer:
             from ..models.recur import pass_count_for_step
 
             self.pass_count = pass_count_for_step(cfg.model.loop, cfg.seed, step)
+        if self.gated:
+            self.pass_count = 1 if step < cfg.loop_switch_step else 2
         lr = self.lr_at(step)
         if self.tst is not None:
             factor = self.tst.lr_factor(step)
@@ -448,6 +467,12 @@ class Trainer:
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        if self.gated:
+            m["T"] = self.pass_count
+            if cfg.log_every and step % cfg.log_every == 0:
+                m["pass2_alpha"] = float(self.model.alpha())
+                if self.pass_count == 2 and getattr(self.model, "last_loop_usage", None) is not None:
+                    m["loop_usage"] = float(self.model.last_loop_usage)
         if self.looped:
             m["T"] = self.pass_count
             inj = self.model.encoder.recur_injection

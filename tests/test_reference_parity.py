@@ -710,3 +710,91 @@ def test_delta_product_sparse_second_step_layout_and_refusals():
     off.encoder.gdn.dprod.stride = 4
     with pytest.raises(ValueError, match="n_h 1"):
         build_model(off)
+
+
+@pytest.mark.parametrize("keys", [{}, {"encoder.gdn.kernel": "chunked", "encoder.gdn.chunk_size": 16, "loop.loop_embedding": False, "loop.pass2_layers": 10},
+                                  {"encoder.attention.rope_max_distance": 12, "encoder.attention.temperature": "ssmax", "encoder.attention.temperature_ref_len": 64}])
+def test_gated_second_pass_equals_the_reference(reference, keys):
+    """The read-only second pass through the top layers (loop.pass2_gate 'scalar'): the two new tensors first and last in
+    the state dict, logits and gradients at T = 1 and T = 2 (pass 1's keys, values and states trained through pass 2), cached
+    reads where a mask marks the positions whose logits are read, slots by capacity, activation_checkpoint 'layer'."""
+    cfg = C.tiny_control_config()
+    cfg.loop.pass2_gate, cfg.loop.pass2_layers, cfg.loop.t_max, cfg.loop.t_eval, cfg.loop.t_choices, cfg.loop.t_probs = "scalar", 6, 2, 2, [2], [1.0]
+    for k, v in keys.items():
+        C.apply_override(cfg, f"{k}={v}")
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd)
+    names = ["loop_embedding_pass2"] * bool(cfg.loop.loop_embedding) + ["hyper_connections.pass2_gate"]
+    assert mine.pass2_parameter_names() == theirs.pass2_parameter_names() == names and (list(sd)[0] == names[0] or not cfg.loop.loop_embedding)
+    tok, doc = random_rows(2, 40)
+    assert torch.equal(mine(tok, doc, T=2).logits, mine(tok, doc, T=1).logits)            # alpha = 0: the single-pass model exactly
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+
+    def grads(model, logits):
+        return torch.autograd.grad(logits.logsumexp(-1).sum(), list(model.parameters()), allow_unused=True)
+
+    for T in (1, 2):
+        a, b = mine(tok, doc, T=T).logits, theirs(tok, doc, T=T).logits
+        assert (a - b).abs().max() < 1e-10
+        ga, gb = grads(mine, a), grads(theirs, b)
+        for (n, _), x, y in zip(mine.named_parameters(), ga, gb):
+            assert (x is None) == (y is None) and (x is None or (x - y).abs().max() < 1e-9), (T, n)
+    assert torch.equal(mine(tok, doc).logits, mine(tok, doc, T=2).logits) and not torch.equal(mine(tok, doc).logits, mine(tok, doc, T=1).logits)
+    mine.encoder.activation_checkpoint = "layer"
+    gc = grads(mine, mine(tok, doc, T=2).logits)
+    assert all((x is None and y is None) or (x - y).abs().max() < 1e-12 for x, y in zip(ga, gc))
+    mine.encoder.activation_checkpoint = "none"
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        full = mine(tok, doc).logits
+        one = mine(tok, doc, T=1).logits
+        mask = torch.zeros(2, 40, dtype=torch.bool)
+        mask[:, 30:], mask[0, 5] = True, True
+        out, ref_out = mine.prefill(tok[:, :17], doc[:, :17], mask[:, :17]), theirs.prefill(tok[:, :17], doc[:, :17], mask[:, :17])
+        parts, kept = [out.logits], [out.kept]
+        assert (out.logits - ref_out.logits).abs().max() < 1e-10 and torch.equal(out.kept, ref_out.kept)
+        for lo, hi in ((17, 18), (18, 33), (33, 40)):
+            out = mine.extend(tok[:, lo:hi], doc[:, lo:hi], mask[:, lo:hi], out.cache)
+            ref_out = theirs.extend(tok[:, lo:hi], doc[:, lo:hi], mask[:, lo:hi], ref_out.cache)
+            parts.append(out.logits), kept.append(out.kept)
+            assert (out.logits - ref_out.logits).abs().max() < 1e-10 and torch.equal(out.kept, ref_out.kept) and torch.equal(out.n_dropped, ref_out.n_dropped)
+            assert all(getattr(c, "pass1", None) is None for c in out.cache.encoder)                 # the cache is pass 1's
+        got, k = torch.cat(parts, 1), torch.cat(kept, 1)
+        assert torch.equal(k, mask) and (got - full)[k].abs().max() < 1e-9 and (got - one)[~k].abs().max() < 1e-9
+        a, b = mine(tok, doc, pass2_mask=mask, pass2_capacity=3), theirs(tok, doc, pass2_mask=mask, pass2_capacity=3)
+        assert (a.logits - b.logits).abs().max() < 1e-10 and torch.equal(a.kept, b.kept) and torch.equal(a.n_dropped, b.n_dropped)
+        assert a.kept.sum(1).tolist() == [3, 3] and a.n_dropped.tolist() == [8, 7]
+        assert torch.equal(mine(tok, doc, pass2_mask=mask, pass2_capacity=0).logits, one)
+
+
+def test_gated_second_pass_is_refused_by_name_where_it_is_not_built():
+    def cfg_of(**kw):
+        cfg = C.tiny_control_config()
+        cfg.loop.pass2_gate, cfg.loop.pass2_layers, cfg.loop.t_max, cfg.loop.t_eval = "scalar", 4, 2, 2
+        for k, v in kw.items():
+            C.apply_override(cfg, f"{k}={v}")
+        return cfg
+
+    for kw, match in (({"loop.pass2_layers": 0}, "pass2_layers"), ({"loop.pass2_layers": 99}, "pass2_layers"), ({"loop.t_max": 3}, "t_max"),
+                      ({"loop.t_eval": 3}, "t_eval"), ({"loop.pass2_gate": "hc"}, "hc"), ({"encoder.layer_scalars": "skip"}, "layer_scalars"),
+                      ({"encoder.canon_kernel": 4}, "canon_kernel"), ({"loop.recur_layers": "[2, 6]"}, "recur_layers"),
+                      ({"encoder.gdn.dprod.n_h": 2}, "dprod"), ({"loop.segment_passes": "{a: 2}"}, "segment_passes")):
+        with pytest.raises(ValueError, match=match):
+            build_model(cfg_of(**{k: v for k, v in kw.items()}))
+    full = C.tiny_full_config()
+    full.loop.pass2_gate, full.loop.pass2_layers, full.loop.t_max, full.loop.t_eval = "scalar", 4, 2, 2
+    with pytest.raises(ValueError, match="attn_res"):
+        build_model(full)
+    plain = C.tiny_control_config()
+    plain.loop.pass2_layers = 3
+    with pytest.raises(ValueError, match="without loop.pass2_gate"):
+        build_model(plain)
+    model = build_model(C.tiny_control_config())
+    tok, doc = random_rows(1, 8)
+    with pytest.raises(ValueError, match="gated second pass"):
+        model(tok, doc, pass2_mask=torch.ones(1, 8, dtype=torch.bool))

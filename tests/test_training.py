@@ -862,3 +862,47 @@ def test_checkpoint_cross_read_trains_with_its_gate_floor(tmp_path):
     off.optim.ccr_translator_decay = "identity"
     with pytest.raises(ValueError, match="this model has none"):
         Trainer(off, None)
+
+
+def test_gated_second_pass_switches_on_at_its_step(tmp_path):
+    """loop.pass2_gate 'scalar' through the trainer: T = 1 before loop_switch_step and 2 from it on, the gate leaves 0 only
+    then, pass 2's tensors in AdamW groups of their own at pass2_lr_scale, a bit-exact resume across the switch, refusals."""
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    cfg = tiny_train_config()
+    cfg.model = C.tiny_control_config()
+    lp = cfg.model.loop
+    lp.pass2_gate, lp.pass2_layers, lp.t_max, lp.t_eval, lp.t_choices, lp.t_probs = "scalar", 4, 2, 2, [2], [1.0]
+    cfg.loop_switch_step, cfg.optim.pass2_lr_scale, cfg.log_every, cfg.activation_checkpoint, cfg.optim.name = 3, 4.0, 1, "layer", "muon"
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    groups = optim.param_groups(t.model, cfg.optim)
+    own = [g for g in groups if any(n in ("loop_embedding_pass2", "hyper_connections.pass2_gate") for n in g["names"])]
+    assert [g["names"] for g in own] == [["loop_embedding_pass2"], ["hyper_connections.pass2_gate"]]
+    assert all(g["kind"] == "adamw" and g["lr_scale"] == cfg.optim.adamw_lr_scale * 4.0 for g in own) and own[0]["weight_decay"] > 0 and own[1]["weight_decay"] == 0
+    rows = [t.train_step() for _ in range(3)]
+    assert [r["T"] for r in rows] == [1, 1, 1] and all(r["pass2_alpha"] == 0.0 for r in rows) and "loop_usage" not in rows[-1]
+    assert float(t.model.loop_embedding_pass2.abs().max()) == 0
+    rows += [t.train_step() for _ in range(3)]
+    assert [r["T"] for r in rows[3:]] == [2, 2, 2] and rows[3]["pass2_alpha"] != 0.0 and rows[5]["loop_usage"] > 0
+    assert float(t.model.loop_embedding_pass2.abs().max()) > 0 and math.isfinite(rows[-1]["loop_usage"])
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(3)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 3
+    c.fit()
+    wa, wc = weights(t), weights(c)
+    assert all(torch.equal(wa[k], wc[k]) for k in wa)
+    for key, value, match in (("activation_checkpoint", "block", "activation_checkpoint"), ("cuda_graphs", "microbatch", "cuda_graphs"),
+                              ("model.loop.t_choices", "[1, 2]", "t_choices"), ("loop_switch_step", 99, "loop_switch_step")):
+        bad = copy.deepcopy(cfg)
+        C.apply_override(bad, f"{key}={value}")
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
+    plain = tiny_train_config()
+    plain.loop_switch_step = 2
+    with pytest.raises(ValueError, match="this model has none"):
+        Trainer(plain, None)
+    plain = tiny_train_config()
+    plain.optim.pass2_lr_scale = 2.0
+    with pytest.raises(ValueError, match="this model has none"):
+        Trainer(plain, None)
