@@ -756,7 +756,6 @@ _BUILT = {
     "model.loop.segment_passes": (None,),
     "model.loop.unscored_passes": (None,),
     "model.mtp.enabled": (False, True),
-    "model.cp_head.enabled": (False,),
     "model.fp8.mode": ("none", "linears"),
     "model.fp8.scaling": ("rowwise", "tensorwise", "mxfp8"),
     "model.fp8.chains": ((),),
@@ -774,7 +773,6 @@ _TRAIN_BUILT = {
     "head_impl": ("fused", "chunked"),
     "head_precision": ("fp32", "bf16"),
     "activation_checkpoint": ("none", "layer", "block", "host", "host_overlap"),
-    "freeze_trunk": (False,),
     "precision_switch": (False, True),
     "cuda_graphs": ("none", "microbatch"),        # "step" (clip + optimizer inside a graph) is not built: the update kernels take the LR by value
     "wgrad_accum": ("autograd", "fp32"),

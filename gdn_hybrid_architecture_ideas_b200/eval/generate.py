@@ -19,6 +19,16 @@ def _last_logits(model, hidden_last: torch.Tensor) -> torch.Tensor:
     return lm_head(hidden_last, model.head_weight())
 
 
+def _step(model, tokens, docs, cache, ac):
+    """One cached forward: (cache, what the next token is read from at the last position). A model with a Copy-Paste head builds
+    its cache in a forward that returns logits (log p of the mixture, over the copy cache); every other model hands the last
+    hidden state to the head."""
+    copy = getattr(model, "cp_head", None) is not None
+    with torch.autocast(**ac):
+        out = model.forward(tokens, docs, cache=cache, return_cache=True, return_hidden=not copy)
+    return out.cache, (out.logits[:, -1:] if copy else out.hidden_aux[:, -1:]), copy
+
+
 @torch.no_grad()
 def generate_greedy(model, prompt: list[int], max_new: int, is_done: Callable[[int, list[int]], bool] | None = None,
                     eos_id: int | None = None, prefill_chunk: int = 1024, autocast_dtype=None) -> list[int]:
@@ -42,16 +52,15 @@ def generate_greedy_batched(model, prompts: list[list[int]], max_new: int, is_do
     tokens, docs = tokens.to(dev), docs.to(dev)
     cache, hidden = None, None
     ac = dict(device_type=dev.type, dtype=autocast_dtype, enabled=autocast_dtype is not None)
+    copy = False
     for s in range(0, width, prefill_chunk):
-        with torch.autocast(**ac):
-            out = model.forward(tokens[:, s:s + prefill_chunk], docs[:, s:s + prefill_chunk], cache=cache, return_cache=True, return_hidden=True)
-        cache, hidden = out.cache, out.hidden_aux[:, -1:]
+        cache, hidden, copy = _step(model, tokens[:, s:s + prefill_chunk], docs[:, s:s + prefill_chunk], cache, ac)
     one = torch.ones(B, 1, dtype=torch.long, device=dev)
     generated = torch.zeros(B, max_new, dtype=torch.long, device=dev)
     done = [False] * B
     lengths = [max_new] * B
     for step in range(max_new):
-        nxt = _last_logits(model, hidden).argmax(-1)       # (B, 1)
+        nxt = (hidden if copy else _last_logits(model, hidden)).argmax(-1)       # (B, 1)
         generated[:, step] = nxt[:, 0]
         if (step + 1) % check_every == 0 or step == max_new - 1:
             host = generated[:, :step + 1].cpu()
@@ -66,9 +75,7 @@ def generate_greedy_batched(model, prompts: list[list[int]], max_new: int, is_do
             if all(done):
                 break
         if step + 1 < max_new:
-            with torch.autocast(**ac):
-                out = model.forward(nxt, one, cache=cache, return_cache=True, return_hidden=True)
-            cache, hidden = out.cache, out.hidden_aux
+            cache, hidden, copy = _step(model, nxt, one, cache, ac)
     model.train(was_training)
     host = generated.cpu()
     return [host[b, :lengths[b]].tolist() for b in range(B)]

@@ -26,6 +26,7 @@ class ControlCache:
     seq: SeqState
     encoder: list
     T: int = 1
+    copy: object | None = None      # the Copy-Paste head's keys of every position so far (models/cp_head.py CopyCache)
 
 
 @dataclass
@@ -87,11 +88,27 @@ class HybridLM(nn.Module):
             from .depth_mix import init_own_parameters
 
             init_own_parameters(self, cfg.init_std)
+        from . import cp_head as cp_mod
 
-    def head_weight(self) -> torch.Tensor:
+        cp_mod.check_config(cfg)
+        if cfg.cp_head.enabled:          # the Copy-Paste head: after every other tensor, from a generator of its own
+            cp_mod.attach(self)
+
+    def lm_head_weight(self) -> torch.Tensor:
+        """The (V, d) LM head matrix: the input embedding when tied. With a Copy-Paste head this is p_LM's head."""
         return self.embed.weight if self.out_embed is None else self.out_embed.weight
 
-    lm_head_weight = head_weight
+    def head_weight(self) -> torch.Tensor:
+        """`lm_head_weight`, refused in eval mode for a model whose next-token distribution is the Copy-Paste mixture: a
+        scoring path that applies the bare head to hidden states would score p_LM by mistake (models/cp_head.py
+        `head_token_ce` scores the mixture)."""
+        if not self.training and getattr(self, "cp_head", None) is not None:
+            from .cp_head import score_mode
+
+            if score_mode(self) == "mixture" and not self.cfg.cp_head.force_lambda_zero:
+                raise ValueError("this model has a Copy-Paste head: its next-token distribution is the mixture, not softmax(h W^T). Score it with "
+                                 "models.cp_head.head_token_ce or the forward's logits (log p); lm_head_weight() is p_LM's head")
+        return self.lm_head_weight()
 
     def embed_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
         e = ops.embedding(tokens, self.embed.weight)
@@ -179,12 +196,24 @@ class HybridLM(nn.Module):
             h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state,
                                      T=None if self.gated else T)
         hidden = self.final_norm(h)
-        logits = None if return_hidden else lm_head(hidden, self.head_weight())
+        copy_cache = None
+        if return_hidden:
+            logits = None
+        elif getattr(self, "cp_head", None) is not None:
+            from .cp_head import forward_logits
+
+            if tokens.dim() != 2 or self.tp is not None:
+                raise ValueError("the Copy-Paste head's output is for token rows on one device, not bags or a token shard")
+            logits, copy_cache = forward_logits(self, hidden, tokens, doc_ids, ctx.idx, cache.copy if cache else None)
+        else:
+            logits = lm_head(hidden, self.lm_head_weight())
+        if return_cache and copy_cache is None and getattr(self, "cp_head", None) is not None:
+            raise ValueError("a cache of a Copy-Paste model is built by a forward that returns logits (prefill / extend)")
         return ModelOutput(
             logits=logits, hidden_aux=hidden if return_hidden else None,
             kept=torch.zeros(B, L, dtype=torch.bool, device=tokens.device) if kept is None else kept,
             n_dropped=torch.zeros(B, dtype=torch.long, device=tokens.device) if n_dropped is None else n_dropped,
-            cache=ControlCache(seq=seq_state, encoder=caches, T=T or 1) if return_cache else None)
+            cache=ControlCache(seq=seq_state, encoder=caches, T=T or 1, copy=copy_cache) if return_cache else None)
 
     def _pass2_at(self, dec_mask, T) -> dict:
         """prefill / extend: a decoder mask marks the positions whose logits are read, so pass 2 is kept there alone, with as

@@ -1,7 +1,12 @@
 """Guard for training a small part of a model on a frozen trunk: the frozen parameters take no gradient, own no
-optimizer state, and their bytes are checked against a digest taken at start
-(reference: ced/train/freeze_trunk.py:57-219, where the part that trains is the copy-paste head; here it guards the
-drafter head's training on a finished trunk, scripts/train_mtp.py)."""
+optimizer state (or, in the trainer's flat buffers, an update of learning-rate scale 0), and their bytes are checked
+against a digest. Two users: the drafter head's training on a finished trunk (scripts/train_mtp.py) and
+`TrainConfig.freeze_trunk`, the Copy-Paste head trained alone on the trunk that `init_from` loads (train/trainer.py):
+the digests are then taken when the trunk has been loaded (`take_digests`), a step before that is refused
+(`check_loaded`), every step checks that no frozen tensor has a gradient entry other than zero, and every save that the
+trunk's bytes are the start's (reference: ced/train/freeze_trunk.py:1-56, 100-219; there the head is the add-on form,
+whose sources are detached; here it is the base form, whose loss reaches the trunk's activations but, frozen, none of its
+tensors)."""
 
 from __future__ import annotations
 
@@ -26,9 +31,27 @@ class TrunkGuard:
         if not self.trainable:
             raise ValueError(f"freeze_trunk: no parameter matches the trainable prefixes {trainable_prefixes}")
         self.digests = {n: _digest(p) for n, p in self.frozen.items()}
+        self.loaded = False
+
+    def take_digests(self) -> None:
+        """The trunk has been loaded: its bytes from now on."""
+        self.digests = {n: _digest(p) for n, p in self.frozen.items()}
+        self.loaded = True
+
+    def summary(self) -> str:
+        """One sha256 over the frozen tensors' names and digests, in name order."""
+        h = hashlib.sha256()
+        for n in sorted(self.digests):
+            h.update(f"{n}|{self.digests[n]}|".encode())
+        return h.hexdigest()
+
+    def check_loaded(self) -> None:
+        if not self.loaded:
+            raise RuntimeError("freeze_trunk: a step before the trunk was loaded (init_from): a frozen random trunk would train a head on nothing")
 
     def check_grads(self) -> None:
-        bad = [n for n, p in self.frozen.items() if p.grad is not None]
+        """No frozen tensor has a gradient (a view of a flat gradient buffer counts when it holds anything but zeros)."""
+        bad = [n for n, p in self.frozen.items() if p.requires_grad or (p.grad is not None and bool(p.grad.ne(0).any()))]
         if bad:
             raise RuntimeError(f"freeze_trunk: frozen parameters received gradients: {bad[:4]}")
 

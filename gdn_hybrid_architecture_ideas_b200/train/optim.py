@@ -21,7 +21,9 @@ NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gai
                      ".gamma_proj.weight", ".gamma_proj.bias",
                      # a looped middle's injection (models/recur.py): B starts at the identity and w near 1, decay would pull both
                      # away from their starts; A_log / dt_bias are covered by the GDN suffixes above
-                     "injection.B", ".recur_mix")
+                     "injection.B", ".recur_mix",
+                     # the Copy-Paste head's <copy> row (the LM head's rule) and its QK-norm gain (the pointer's temperature)
+                     "cp_head.w_copy", "cp_head.qk_gain")
 ZERO_GATE_SUFFIXES = (".gdn_arms.ccr_gate", ".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale", ".dprod.beta_const")
 # The cross-read's query translators (models/ccr.py): D = M - I, (H_k, d_k, d_k) a reader, never a Muon matrix (3-D). One
 # AdamW group of their own, the last, at the depth readers' learning rate; optim.ccr_translator_decay "none": no decay,
@@ -48,7 +50,7 @@ def no_decay_suffixes(o) -> tuple:
 def is_muon_param(name: str, p: torch.Tensor) -> bool:
     if p.ndim != 2 or name.endswith(("embed.weight", "conv_weight") + ADAMW_MATRIX_SUFFIXES):
         return False
-    return ".attn_res." not in name and "injection" not in name          # loop-boundary parameters stay on AdamW
+    return ".attn_res." not in name and "injection" not in name and not name.startswith("cp_head.")   # loop-boundary and copy-head tensors stay on AdamW
 
 
 GDN_MUP_BASE_WIDTH = 512
@@ -98,8 +100,10 @@ def gdn_mup_init_(model, base_width: int = GDN_MUP_BASE_WIDTH) -> None:
         named[n].mul_((base_width / named[n].shape[1]) ** 0.5)
 
 
-def param_groups(model, o) -> list[dict]:
-    """Groups as dicts {"names", "params", "weight_decay", "lr_scale", "kind"}; kind "adamw" or "muon"."""
+def param_groups(model, o, trainable=None) -> list[dict]:
+    """Groups as dicts {"names", "params", "weight_decay", "lr_scale", "kind"}; kind "adamw" or "muon". trainable: an
+    optional predicate over parameter names (a frozen trunk): the tensors it rejects keep their place in the flat buffers
+    in AdamW groups of learning-rate scale 0 and no decay, so an update leaves their bytes as they are."""
     suffixes = no_decay_suffixes(o)
     named = list(model.named_parameters())
     if o.name == "adamw":
@@ -144,6 +148,9 @@ def param_groups(model, o) -> list[dict]:
         taken = {n for n, _ in mats}
         spec = [(k, [(n, p) for n, p in items if n not in taken], wd, sc) for k, items, wd, sc in spec]
         spec.append(("adamw", mats, 0.0 if o.ccr_translator_decay == "none" else o.weight_decay, 1.0 if o.name == "adamw" else o.adamw_lr_scale))
+    if trainable is not None:
+        frozen = [(n, p) for _, items, _, _ in spec for n, p in items if not trainable(n)]
+        spec = [(k, [(n, p) for n, p in items if trainable(n)], wd, sc) for k, items, wd, sc in spec] + [("adamw", frozen, 0.0, 0.0)]
     return [{"kind": k, "names": [n for n, _ in items], "params": [p for _, p in items], "weight_decay": wd, "lr_scale": s}
             for k, items, wd, s in spec if items]
 
@@ -357,9 +364,9 @@ def grad_norm(flat: FlatBuffers, lo: int = 0, hi: int | None = None) -> torch.Te
     return g.double().pow(2).sum().sqrt().float()
 
 
-def build_optimizer(model, cfg_optim, device, lp_dtype=None, shard=None):
+def build_optimizer(model, cfg_optim, device, lp_dtype=None, shard=None, trainable=None):
     """(flat buffers, optimizer) for `optim.name` 'adamw' or 'muon' (reference: ced/train/optim.py:927-979)."""
-    groups = param_groups(model, cfg_optim)
+    groups = param_groups(model, cfg_optim, trainable)
     flat = FlatBuffers(model, groups, device, lp_dtype)
     if cfg_optim.name == "muon":
         from .muon import MuonWithAdamW

@@ -136,7 +136,32 @@ class Trainer:
         self.sharding = cfg.optimizer_sharding if self.world > 1 else "replicated"
         if cfg.micro_batch_size is not None and dp is not None and self.tp is None:
             dp.check(cfg.data.batch_size, cfg.micro_batch_size)
+        # The Copy-Paste head (models/cp_head.py): the loss is the mixture's cross entropy; with freeze_trunk the head alone
+        # trains on a finished trunk (train/freeze_trunk.py): every tensor outside cp_head.* takes no gradient and an update of
+        # learning-rate scale 0, and its bytes are checked against a digest.
+        self._cp = getattr(self.model, "cp_head", None)
+        self._trainable = None
+        self.trunk_guard = None
+        if self._cp is not None:
+            clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
+                       "shape_schedule": bool(cfg.shape_schedule), "head_impl 'fused' (the mixture runs on the chunked head: set head_impl 'chunked')": cfg.head_impl == "fused"}
+            hit = [k for k, v in clashes.items() if v]
+            if hit:
+                raise ValueError(f"model.cp_head is not built together with: {', '.join(hit)}")
+        if cfg.freeze_trunk:
+            clashes = {"no model.cp_head.enabled (the part that trains)": self._cp is None, "no init_from (a frozen random trunk trains a head on nothing)": not cfg.init_from,
+                       "data parallelism": dp is not None, "activation_checkpoint": cfg.activation_checkpoint != "none",
+                       "optimizer_sharding": cfg.optimizer_sharding != "replicated", "wgrad_accum 'fp32'": cfg.wgrad_accum == "fp32",
+                       "log_zero_wgrad_every": bool(cfg.log_zero_wgrad_every), "model.encoder.gdn_qmix_select_step": bool(cfg.model.encoder.gdn_qmix_select_step)}
+            hit = [k for k, v in clashes.items() if v]
+            if hit:
+                raise ValueError(f"freeze_trunk is not built with: {', '.join(hit)}")
+            self._trainable = lambda name: name.startswith("cp_head.")
         self.flat, self.optimizer, self.zero = self._build_optimizer(lp)
+        if cfg.freeze_trunk:
+            from .freeze_trunk import TrunkGuard
+
+            self.trunk_guard = TrunkGuard(self.model, ("cp_head.",))       # requires_grad False outside the head; digests taken when the trunk is loaded
         self.data = make_data(cfg.data, cfg.model.vocab_size)
         self.tst = None
         if cfg.tst.schedule:
@@ -256,7 +281,7 @@ class Trainer:
             if self.device.type == "cuda":
                 zero.enable_fused()
         else:
-            flat, opt = build_optimizer(self.model, cfg.optim, self.device, lp)
+            flat, opt = build_optimizer(self.model, cfg.optim, self.device, lp, trainable=self._trainable)
         return flat, opt, zero
 
     # ------------------------------------------------------------------ data
@@ -333,6 +358,14 @@ class Trainer:
                 cut = slice(self.tp.rank * per, (self.tp.rank + 1) * per)
                 targets, valid = targets.reshape(-1)[cut][None], valid.reshape(-1)[cut][None]
             a, b = valid * inv, valid * (z * inv)
+        if self._cp is not None:
+            from ..models.cp_head import mixture_loss
+
+            if mb.multi_targets is not None:
+                raise ValueError("model.cp_head is built for one target a position")
+            loss, ce, lam = mixture_loss(self.model, hidden, targets, mb.tokens, mb.doc_ids, a, b, cfg.head_chunk)
+            self._cp_lambda = (lam * valid).sum() / valid.sum().clamp_min(1.0)
+            return loss, (ce * valid).sum().detach()
         W = self.model.head_weight()
         if cfg.head_impl == "fused":
             loss, ce, _ = fused_linear_ce(hidden, W, targets, a, b, cfg.head_chunk, self.model.head_weight_lp, cfg.loss.ce_form, cfg.head_precision)
@@ -348,6 +381,8 @@ class Trainer:
         (loss, ce sum, gradient norm, kernel status word); nothing is read back to the host here."""
         cfg = self.cfg
         lr = self.lr_at(self.step) if lr is None else lr
+        if self.trunk_guard is not None:
+            self.trunk_guard.check_loaded()
         if self.zero is not None:
             self.zero.before_step()     # the last step's first-read parameters have landed; peers are done with its gradients
         self.flat.grads.zero_()
@@ -402,6 +437,8 @@ class Trainer:
             if self.dp is not None:
                 self.dp.all_reduce_(self.flat.grads)
                 self.dp.all_reduce_(stats)
+            if self.trunk_guard is not None and (self.step == 0 or (cfg.log_every and self.step % cfg.log_every == 0)):
+                self.trunk_guard.check_grads()
             if cfg.log_every and self.step % cfg.log_every == 0:      # per-family gradient norms before clipping (whole gradients are here)
                 self._family_norms = monitor.family_grad_norms(self.flat)
             gnorm = grad_norm(self.flat)
@@ -467,6 +504,10 @@ class Trainer:
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+        if self._cp is not None and cfg.log_every and step % cfg.log_every == 0:
+            m["cp_lambda"] = float(self._cp_lambda)          # the mean copy weight at the scored targets of the step's last micro-batch
+            if self._cp.cfg.qk_norm:
+                m["cp_qk_gain"] = 1.0 + float(self._cp.qk_gain.detach())
         if self.gated:
             m["T"] = self.pass_count
             if cfg.log_every and step % cfg.log_every == 0:
@@ -672,6 +713,9 @@ class Trainer:
         }
         if self.dp is not None:
             state["data_parallel"] = {"world_size": self.world, "sharding": self.sharding}
+        if self.trunk_guard is not None:        # a checkpoint whose trunk is not the start's is not written
+            self.trunk_guard.check_values()
+            state["freeze_trunk"] = {"trunk_sha256": self.trunk_guard.summary(), "tensors": len(self.trunk_guard.frozen)}
         return state
 
     def save_checkpoint(self, sync: bool = True) -> Path | None:
@@ -719,6 +763,11 @@ class Trainer:
         self.flat.refresh_lp()
         if weights_only:
             return
+        if self.trunk_guard is not None:        # a resume: the file's trunk must hash to its record
+            self.trunk_guard.take_digests()
+            want = (state.get("freeze_trunk") or {}).get("trunk_sha256")
+            if want != self.trunk_guard.summary():
+                raise ValueError("freeze_trunk: the checkpoint's trunk does not hash to its record (the file was changed after the save, or was not written by a frozen-trunk run)")
         if self.zero is not None:
             self.zero.load_optimizer_state(self.optimizer, state["optimizer"])
         else:
@@ -792,6 +841,11 @@ class Trainer:
         state = ckpt.load(Path(path))
         self.load_state_dict(state, check_config=False, weights_only=True)
         self.init_info = {"path": str(path), "step": int(state.get("step", 0))}
+        own = set(self.model.state_dict())
+        self.init_info["grown"] = sorted(own - set(state["model"]))          # tensors the source lacks keep their own start (a head added to a finished trunk)
+        if getattr(self, "trunk_guard", None) is not None:
+            self.trunk_guard.take_digests()
+            self.init_info["trunk_sha256"] = self.trunk_guard.summary()
 
 
 def _scored(batch) -> torch.Tensor:

@@ -798,3 +798,79 @@ def test_gated_second_pass_is_refused_by_name_where_it_is_not_built():
     tok, doc = random_rows(1, 8)
     with pytest.raises(ValueError, match="gated second pass"):
         model(tok, doc, pass2_mask=torch.ones(1, 8, dtype=torch.bool))
+
+
+@pytest.mark.parametrize("base,keys", [("control", {}), ("control", {"qk_norm": True, "init": "reference"}),
+                                       ("control", {"qk_norm": True, "temperature": "ssmax", "sink_count": True}), ("full", {"qk_norm": True})])
+def test_copy_paste_head_equals_the_reference(reference, base, keys):
+    """The Copy-Paste head in its base form: the head's tensors last in the state dict with equal starts, the mixture's log p over V
+    (it sums to one and equals the training cross entropy at the target), the blockwise terms against the reference's and an
+    all-at-once statement, the loss's gradients through trunk and head, and cached generation with the copy cache."""
+    from ced.model import cp_head as RCP
+
+    from gdn_hybrid_architecture_ideas_b200.models import cp_head as CP
+
+    cfg = C.tiny_full_config() if base == "full" else C.tiny_control_config()
+    cfg.cp_head.enabled, cfg.cp_head.d_c, cfg.cp_head.query_chunk, cfg.encoder.gdn_write_variant = True, 8, 16, "none"
+    for k, v in keys.items():
+        setattr(cfg.cp_head, k, v)
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd) and list(sd)[-1].startswith("cp_head.")
+    plain = C.tiny_full_config() if base == "full" else C.tiny_control_config()
+    plain.encoder.gdn_write_variant = "none"
+    torch.manual_seed(0)
+    trunk = build_model(plain).double().state_dict()
+    assert all(torch.equal(trunk[k], sd[k]) for k in trunk)                    # the base model starts as the model without the key
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40, vocab=12)                                     # a small alphabet: most targets occur in the context
+    tgt = torch.roll(tok, -1, 1)
+    a, b = mine(tok, doc).logits, theirs(tok, doc).logits
+    assert (a - b).abs().max() < 1e-10 and (a.exp().sum(-1) - 1).abs().max() < 1e-9
+    ha, hb = mine(tok, doc, return_hidden=True).hidden_aux, theirs(tok, doc, return_hidden=True).hidden_aux
+    ta, tb, tn = CP.terms(mine.cp_head, ha, tok, tgt, doc), RCP.cp_terms(theirs.cp_head, hb, tok, tgt, doc), CP.terms_naive(mine.cp_head, ha, tok, tgt, doc)
+    for x, y, z in zip(ta, tb, tn):
+        fin = torch.isfinite(y)
+        assert torch.equal(torch.isfinite(x), fin) and torch.equal(torch.isfinite(z), fin) and (x - y)[fin].abs().max() < 1e-10 and (x - z)[fin].abs().max() < 1e-9
+    assert 0 < int((~torch.isfinite(ta[2])).sum()) < tgt.numel()                # some targets have no match in their context, most have one
+    w, z = torch.ones_like(tgt, dtype=torch.double), torch.full(tgt.shape, 1e-4, dtype=torch.double)
+    loss, ce, lam = CP.mixture_loss(mine, ha, tgt, tok, doc, w, z, chunk=16)
+    ce_r, lse_r = RCP.head_token_ce(theirs, hb, tgt, tok, doc)
+    assert (ce - ce_r).abs().max() < 1e-10 and (-a.gather(-1, tgt[..., None]).squeeze(-1) - ce).abs().max() < 1e-9 and 0 < float(lam.min()) and float(lam.max()) < 1
+    ga = torch.autograd.grad(loss, list(mine.parameters()), allow_unused=True)
+    gb = torch.autograd.grad((w * ce_r + z * lse_r * lse_r).sum(), list(theirs.parameters()), allow_unused=True)
+    for (n, _), x, y in zip(mine.named_parameters(), ga, gb):
+        assert (x is None) == (y is None) and (x is None or ((x - y).abs().max() < 1e-9 and torch.isfinite(x).all())), n
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        full = mine(tok, doc).logits
+        out, ref_out = mine.prefill(tok[:, :17], doc[:, :17]), theirs.prefill(tok[:, :17], doc[:, :17])
+        parts = [out.logits]
+        for lo, hi in ((17, 18), (18, 40)):
+            out, ref_out = mine.extend(tok[:, lo:hi], doc[:, lo:hi], None, out.cache), theirs.extend(tok[:, lo:hi], doc[:, lo:hi], None, ref_out.cache)
+            parts.append(out.logits)
+            assert (out.logits - ref_out.logits).abs().max() < 1e-10
+        assert (torch.cat(parts, 1) - full).abs().max() < 1e-9 and out.cache.copy.keys.k.shape[:2] == (2, 40)
+        ce_eval, _ = CP.head_token_ce(mine, mine(tok, doc, return_hidden=True).hidden_aux, tgt, tok, doc)
+        assert (ce_eval + full.gather(-1, tgt[..., None]).squeeze(-1)).abs().max() < 1e-9
+        with pytest.raises(ValueError, match="Copy-Paste head"):
+            mine.head_weight()
+        mine.cfg.cp_head.score = "lm"
+        lm = mine(tok, doc).logits
+        assert (lm - torch.nn.functional.linear(mine(tok, doc, return_hidden=True).hidden_aux, mine.lm_head_weight())).abs().max() < 1e-12
+
+
+def test_copy_paste_head_is_refused_by_name_where_it_is_not_built():
+    for key, value, match in (("cp_head.pointer_input", "mix", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.trunk_copy", "all", "trunk_copy"),
+                              ("cp_head.train_mode", "addon", "train_mode"), ("cp_head.window", 64, "window"), ("cp_head.kernel", "fused", "kernel"),
+                              ("cp_head.init", "zeros", "init"), ("cp_head.d_c", 0, "d_c"), ("loop.recur_layers", "[2, 6]", "one pass"),
+                              ("encoder.gdn_ccr_spacing", 8, "gdn_ccr_spacing"), ("encoder.attn_res", "ldm", "attn_res")):
+        cfg = C.tiny_control_config()
+        cfg.cp_head.enabled = True
+        C.apply_override(cfg, f"{key}={value}")
+        with pytest.raises(ValueError, match=match):
+            build_model(cfg)

@@ -906,3 +906,67 @@ def test_gated_second_pass_switches_on_at_its_step(tmp_path):
     plain.optim.pass2_lr_scale = 2.0
     with pytest.raises(ValueError, match="this model has none"):
         Trainer(plain, None)
+
+
+def test_copy_paste_head_trains_and_then_alone_on_a_frozen_trunk(tmp_path):
+    """model.cp_head through the trainer: the mixture's loss on the chunked head, the head's tensors on AdamW, a bit-exact resume;
+    then freeze_trunk: a head added to a finished trunk (init_from) trains alone, the trunk's bytes stay the source's, the
+    checkpoint carries the trunk's hash, a changed trunk is refused at the save and at a resume, and the refusals by name."""
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    base = tiny_train_config(head_impl="chunked")
+    base.model = C.tiny_control_config()
+    base.log_every = 2
+    trunk = Trainer(copy.deepcopy(base), tmp_path / "trunk")
+    trunk.fit()
+    source = ckpt.latest_path(tmp_path / "trunk")
+    cfg = copy.deepcopy(base)
+    cfg.model.cp_head.enabled, cfg.model.cp_head.d_c, cfg.model.cp_head.qk_norm, cfg.optim.name = True, 8, True, "muon"
+    joint = Trainer(copy.deepcopy(cfg), tmp_path / "joint")
+    groups = optim.param_groups(joint.model, cfg.optim)
+    assert not any(n.startswith("cp_head.") for g in groups if g["kind"] == "muon" for n in g["names"])
+    plain = [n for g in groups if g["weight_decay"] == 0.0 for n in g["names"]]
+    assert "cp_head.w_copy" in plain and "cp_head.qk_gain" in plain and "cp_head.w_q" not in plain
+    l0 = joint.train_step()["loss"]
+    joint.fit()
+    assert math.isfinite(joint.last_metrics["loss"]) and joint.last_metrics["loss"] < l0 + 0.5          # (random tokens: a handful of steps only has to stay sane)
+    lines = [json.loads(x) for x in (tmp_path / "joint" / "metrics.jsonl").read_text().splitlines()]
+    assert any(0 < x.get("cp_lambda", 0) < 1 for x in lines)
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(3)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 3
+    c.fit()
+    assert all(torch.equal(x, y) for x, y in zip(weights(joint).values(), weights(c).values()))
+    # the head alone on the finished trunk
+    frozen = copy.deepcopy(cfg)
+    frozen.freeze_trunk, frozen.init_from, frozen.optim.name = True, str(source), "adamw"
+    f = Trainer(copy.deepcopy(frozen), tmp_path / "frozen")
+    src = ckpt.load(source)["model"]
+    assert f.init_info["grown"] == sorted(n for n in f.model.state_dict() if n.startswith("cp_head.")) and len(f.init_info["trunk_sha256"]) == 64
+    head0 = {n: p.detach().clone() for n, p in f.model.named_parameters() if n.startswith("cp_head.")}
+    f.fit()
+    now = f.model.state_dict()
+    assert all(torch.equal(now[k], src[k]) for k in src) and any(not torch.equal(now[n], v) for n, v in head0.items())
+    assert all(not p.requires_grad for n, p in f.model.named_parameters() if not n.startswith("cp_head."))
+    saved = ckpt.load(ckpt.latest_path(tmp_path / "frozen"))
+    assert saved["freeze_trunk"]["trunk_sha256"] == f.init_info["trunk_sha256"] and saved["freeze_trunk"]["tensors"] == len(src)
+    r = Trainer(copy.deepcopy(frozen), tmp_path / "frozen")
+    assert r.resume_from_checkpoint() and r.step == frozen.steps
+    saved["model"]["embed.weight"] = saved["model"]["embed.weight"] + 1
+    with pytest.raises(ValueError, match="does not hash"):
+        Trainer(copy.deepcopy(frozen), None).load_state_dict(saved)
+    with torch.no_grad():
+        f.model.embed.weight.add_(1.0)
+    with pytest.raises(RuntimeError, match="changed"):
+        f.save_checkpoint()
+    for change, match in ((lambda t: setattr(t, "init_from", None), "init_from"), (lambda t: setattr(t.model.cp_head, "enabled", False), "cp_head"),
+                          (lambda t: setattr(t, "activation_checkpoint", "layer"), "activation_checkpoint")):
+        bad = copy.deepcopy(frozen)
+        change(bad)
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
+    fused = copy.deepcopy(cfg)
+    fused.head_impl = "fused"
+    with pytest.raises(ValueError, match="head_impl"):
+        Trainer(fused, None)
