@@ -753,8 +753,6 @@ _BUILT = {
     "model.encoder.gdn_write_variant": ("none", "qmix", "korig", "vonly", "kqmix", "qshare", "qshare_kv", "qshare_bd"),
     "model.encoder.residual_dtype": ("float32", "bf16"),
     "model.loop.pass2_gate": ("none", "scalar"),
-    "model.loop.segment_passes": (None,),
-    "model.loop.unscored_passes": (None,),
     "model.mtp.enabled": (False, True),
     "model.fp8.mode": ("none", "linears"),
     "model.fp8.scaling": ("rowwise", "tensorwise", "mxfp8"),

@@ -55,15 +55,22 @@ class HybridLM(nn.Module):
         second_pass.check_config(cfg)
         self.gated = second_pass.is_on(cfg)                      # a read-only second pass through the top `pass2_layers` layers
         self.pass2_from = cfg.encoder.n_layers - (cfg.loop.pass2_layers if self.gated else 0)
+        from . import pass_counts
+
+        self.schedule = pass_counts.schedule_of(cfg.loop) if self.gated else None      # pass counts by segment (models/pass_counts.py)
+        self.n_passes = pass_counts.built_passes(cfg.loop) if self.gated else 1
+        self.pass_scheduler = None           # per-position counts from the tokens when a caller gives none; built at first use from loop.segment_tokenizer
         if self.gated and cfg.loop.loop_embedding:
             self.loop_embedding_pass2 = nn.Parameter(torch.zeros(cfg.d_model))
+            if self.n_passes > 2:
+                self.loop_embedding_pass3 = nn.Parameter(torch.zeros(cfg.d_model))
         self.embed = nn.Embedding(cfg.vocab_size, cfg.d_model)
         self.embed_norm = RMSNorm(cfg.d_model, cfg.norm_eps) if cfg.embed_norm else nn.Identity()
         self.encoder = Encoder(cfg)
         self.final_norm = RMSNorm(cfg.d_model, cfg.norm_eps)
         self.out_embed = None if cfg.tie_embeddings else nn.Embedding(cfg.vocab_size, cfg.d_model)
         if self.gated:
-            self.hyper_connections = second_pass.SecondPassGate()
+            self.hyper_connections = second_pass.SecondPassGate(self.n_passes)
         self.head_weight_lp: torch.Tensor | None = None  # bf16 shadow of the head matrix (set by the engine)
         self.tp = None      # tensor-parallel context (parallel.tp_model.apply): the stream is then this rank's token shard
         for m in self.modules():
@@ -126,21 +133,27 @@ class HybridLM(nn.Module):
     def forward(self, tokens: torch.Tensor, doc_ids: torch.Tensor, dec_mask=None, T=None, capacity=None,
                 cache: ControlCache | None = None, return_cache: bool = False, return_hidden: bool = False,
                 varlen: dict | None = None, rope_scale: int = 1, gdn_scale: int = 1, gdn_beta_power: bool = False,
-                single_doc: bool = False, pass2_mask: torch.Tensor | None = None, pass2_capacity: int | None = None) -> ModelOutput:
+                single_doc: bool = False, pass2_mask: torch.Tensor | None = None, pass2_capacity: int | None = None,
+                pass_counts: torch.Tensor | None = None, scored: torch.Tensor | None = None) -> ModelOutput:
         """tokens (B, L) or bags (B, L, s); doc_ids (B, L). return_hidden: give the head input instead of logits
         (the fused loss consumes it). single_doc: the caller guarantees every row is one document (kernels skip
         the document masks). T: the pass count of a looped middle (models/recur.py; default loop.t_eval, or the cache's own T)
         or of a stack with a gated second pass (models/second_pass.py: 1 or 2, default loop.t_eval; at T = 2 pass 2 runs at
         every position, or is kept at the first pass2_capacity positions of each row that pass2_mask marks, and `kept` /
-        `n_dropped` say where); ignored by every other model. dec_mask and capacity are accepted for call compatibility and
-        ignored (reference: ced/model/control.py:716-872)."""
+        `n_dropped` say where); ignored by every other model. With a pass schedule (loop.segment_passes / unscored_passes) a
+        forward at T = 2 runs, at each position, the passes of pass_counts ((B, L) integers 1 .. 3) or, when none are given,
+        of the model's own scheduler over the tokens (whole rows, no cache; `scored` (B, L) for the unscored rule);
+        pass2_mask then marks the positions whose logits are read, every other one runs pass 1 only. dec_mask and capacity
+        are accepted for call compatibility and ignored (reference: ced/model/control.py:716-872)."""
         two = False
         if self.gated:
             T = self.cfg.loop.t_eval if T is None else T
             if T not in (1, 2):
                 raise ValueError(f"T={T!r}: a stack with a second pass runs T = 1 or T = 2")
             two = T == 2 and not (pass2_mask is not None and pass2_capacity == 0)
-        elif pass2_mask is not None or pass2_capacity is not None:
+            if pass_counts is not None and self.schedule is None:
+                raise ValueError("pass_counts are for a model with a pass schedule (model.loop.segment_passes / unscored_passes)")
+        elif pass2_mask is not None or pass2_capacity is not None or pass_counts is not None:
             raise ValueError("pass2_mask / pass2_capacity belong to a model with a gated second pass (model.loop.pass2_gate)")
         if self.encoder.recur is not None:
             if cache is not None:
@@ -190,7 +203,18 @@ class HybridLM(nn.Module):
                 else:
                     records.append(c)
             checkpoint = cache is None and self.encoder.activation_checkpoint == "layer" and torch.is_grad_enabled() and z1.requires_grad
-            h, kept, n_dropped = second_pass.second_pass(self, z1, ctx, records, pass2_mask, pass2_capacity, checkpoint)
+            if self.schedule is not None:
+                if pass2_capacity is not None:
+                    raise ValueError("pass2_capacity is the dense second pass's slot count; under a pass schedule the counts say where a pass runs")
+                counts = self._pass_counts(tokens, doc_ids, pass_counts, scored, cache)
+                if pass2_mask is not None:
+                    counts = torch.where(pass2_mask.bool().to(counts.device), counts, torch.ones_like(counts))
+                top = int(counts.max())                               # counts come from the host: no device wait
+                h, kept = second_pass.scheduled_passes(self, z1, ctx, records, counts.to(z1.device), top, checkpoint)
+                n_dropped = torch.zeros(B, dtype=torch.long, device=z1.device)
+                self.last_counts = counts
+            else:
+                h, kept, n_dropped = second_pass.second_pass(self, z1, ctx, records, pass2_mask, pass2_capacity, checkpoint)
             self.last_loop_usage = second_pass.loop_usage(z1.detach(), h.detach(), kept)
         else:
             h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state,
@@ -215,20 +239,38 @@ class HybridLM(nn.Module):
             n_dropped=torch.zeros(B, dtype=torch.long, device=tokens.device) if n_dropped is None else n_dropped,
             cache=ControlCache(seq=seq_state, encoder=caches, T=T or 1, copy=copy_cache) if return_cache else None)
 
+    def _pass_counts(self, tokens, doc_ids, given, scored, cache) -> torch.Tensor:
+        """The (B, L) pass counts of a scheduled forward, on the host: the caller's, or the model's own scheduler's over whole rows."""
+        if given is not None:
+            counts = given.detach().to("cpu", torch.long)
+            if counts.shape != tokens.shape[:2] or int(counts.min()) < 1 or int(counts.max()) > self.n_passes:
+                raise ValueError(f"pass_counts {tuple(counts.shape)}: (B, L) integers from 1 to {self.n_passes}")
+            return counts
+        if cache is not None:
+            raise ValueError("a cached forward of a model with a pass schedule takes its pass_counts from the caller (the segment of a position "
+                             "depends on the tokens before the chunk)")
+        if self.pass_scheduler is None:
+            from .pass_counts import PassScheduler
+
+            self.pass_scheduler = PassScheduler.from_tokenizer(self.schedule, self.cfg.loop.segment_tokenizer)
+        return self.pass_scheduler.counts(tokens, doc_ids, scored=scored)
+
     def _pass2_at(self, dec_mask, T) -> dict:
         """prefill / extend: a decoder mask marks the positions whose logits are read, so pass 2 is kept there alone, with as
         many slots as the fullest row has marked positions (one host read of the mask: inference only)."""
         if dec_mask is None or not self.gated or (self.cfg.loop.t_eval if T is None else T) == 1:
             return {}
+        if self.schedule is not None:            # the counts say where a pass runs; the mask whose logits are read
+            return {"pass2_mask": dec_mask.bool()}
         return {"pass2_mask": dec_mask.bool(), "pass2_capacity": int(dec_mask.bool().sum(1).max())}
 
     @torch.no_grad()
-    def prefill(self, tokens, doc_ids, dec_mask=None, T=None) -> ModelOutput:
-        return self.forward(tokens, doc_ids, return_cache=True, T=T, **self._pass2_at(dec_mask, T))
+    def prefill(self, tokens, doc_ids, dec_mask=None, T=None, pass_counts=None) -> ModelOutput:
+        return self.forward(tokens, doc_ids, return_cache=True, T=T, pass_counts=pass_counts, **self._pass2_at(dec_mask, T))
 
     @torch.no_grad()
-    def extend(self, tokens, doc_ids, dec_mask, cache: ControlCache, T=None) -> ModelOutput:
-        return self.forward(tokens, doc_ids, cache=cache, return_cache=True, T=T, **self._pass2_at(dec_mask, T))
+    def extend(self, tokens, doc_ids, dec_mask, cache: ControlCache, T=None, pass_counts=None) -> ModelOutput:
+        return self.forward(tokens, doc_ids, cache=cache, return_cache=True, T=T, pass_counts=pass_counts, **self._pass2_at(dec_mask, T))
 
 
 def build_model(cfg: ModelConfig) -> HybridLM:

@@ -21,8 +21,8 @@ records are not detached: pass 2's loss trains pass 1's keys, values and states.
 New tensors: `hyper_connections.pass2_gate` (alpha, 0-dim) and, with `loop.loop_embedding`, `loop_embedding_pass2` (d);
 a T = 1 checkpoint of the same stack loads into the rest. Reference: ced/model/control.py:19-54 (definition), :201-242
 (refusals), :511-560 (the pass), ced/model/encoder.py:349-400 (read-only layers), ced/model/gdn.py:851-975 (the GDN read),
-ced/model/loop.py:312-352 (the gate). The segment-based pass counts (`loop.segment_passes` / `unscored_passes`, a third
-pass) are refused by name.
+ced/model/loop.py:312-352 (the gate). Pass counts by segment (`loop.segment_passes` / `unscored_passes`, a third pass):
+models/pass_counts.py gives the counts, `scheduled_passes` here runs them.
 """
 
 from __future__ import annotations
@@ -36,7 +36,7 @@ import torch.nn.functional as F
 from .. import ops
 from . import act_checkpoint
 
-PASS2_PARAMETERS = ("loop_embedding_pass2", "hyper_connections.pass2_gate")
+PASS2_PARAMETERS = ("loop_embedding_pass2", "hyper_connections.pass2_gate", "loop_embedding_pass3", "hyper_connections.pass3_gate")
 
 
 def is_on(cfg) -> bool:
@@ -45,9 +45,10 @@ def is_on(cfg) -> bool:
 
 def check_config(cfg) -> None:
     lc, e = cfg.loop, cfg.encoder
-    if lc.segment_passes is not None or lc.unscored_passes is not None:
-        raise ValueError("model.loop.segment_passes / unscored_passes (pass counts by segment, a third pass) are not built: the gated second "
-                         "pass runs at every position or at the positions a mask marks")
+    from .pass_counts import schedule_of
+
+    if schedule_of(lc) is not None and not is_on(cfg):
+        raise ValueError("model.loop.segment_passes / unscored_passes set the passes of a gated second pass (model.loop.pass2_gate 'scalar'): this model has none")
     if not is_on(cfg):
         if lc.pass2_layers:
             raise ValueError(f"model.loop.pass2_layers {lc.pass2_layers!r} without loop.pass2_gate 'scalar': set both, or leave pass2_layers 0")
@@ -80,16 +81,21 @@ class SecondPassGate(nn.Module):
     """z_2 = z_1 + alpha (s_2 - z_1): a multiply and two sums in the stream's dtype, so alpha = 0 gives z_1 exactly; alpha gets a
     gradient at once, the block's pass-2 path exactly zero until alpha moves."""
 
-    def __init__(self):
+    def __init__(self, n_passes: int = 2):
         super().__init__()
+        self.n_passes = n_passes
         self.pass2_gate = nn.Parameter(torch.zeros(()))
+        if n_passes == 3:          # only through a 3 in model.loop.segment_passes
+            self.pass3_gate = nn.Parameter(torch.zeros(()))
 
-    def forward(self, z1: torch.Tensor, s2: torch.Tensor) -> torch.Tensor:
-        return z1 + self.pass2_gate.to(z1.dtype) * (s2 - z1)
+    def forward(self, z: torch.Tensor, s: torch.Tensor, k: int = 1) -> torch.Tensor:
+        """The state after the pass with 0-based index k from the state before it (z) and the block's output (s)."""
+        gate = self.pass2_gate if k == 1 else self.pass3_gate
+        return z + gate.to(z.dtype) * (s - z)
 
     @torch.no_grad()
     def is_identity(self) -> bool:
-        return bool(self.pass2_gate == 0)
+        return bool(self.pass2_gate == 0) and (self.n_passes < 3 or bool(self.pass3_gate == 0))
 
 
 @dataclass
@@ -188,11 +194,8 @@ def loop_usage(z1, z, kept) -> torch.Tensor:
     return ((num / den) * k).sum() / k.sum().clamp_min(1.0)
 
 
-def second_pass(model, z1, ctx, records: list, pass2_mask, capacity, checkpoint: bool):
-    """(z, kept, n_dropped): z_2 where pass 2 is kept and z_1 elsewhere."""
-    B, L, _ = z1.shape
-    e2 = getattr(model, "loop_embedding_pass2", None)
-    u = z1 if e2 is None else z1 + e2.to(z1.dtype)
+def block_read_all(model, u, ctx, records: list, checkpoint: bool):
+    """The top block's layers in read-only mode at every position, from the stream u."""
     block = list(model.encoder.layers)[model.pass2_from:]
     for layer, record in zip(block, records):
         if checkpoint:
@@ -200,6 +203,25 @@ def second_pass(model, z1, ctx, records: list, pass2_mask, capacity, checkpoint:
             u = act_checkpoint.run_checkpointed(lambda u_, *t, layer=layer, rebuild=rebuild: layer_read_all(layer, u_, ctx, rebuild(t)), u, *flat)
         else:
             u = layer_read_all(layer, u, ctx, record)
+    return u
+
+
+def scheduled_passes(model, z1, ctx, records: list, counts: torch.Tensor, max_count: int, checkpoint: bool):
+    """(z, kept): every position's state after the LAST pass its count asks for (models/pass_counts.py). counts (B, L) integer
+    on z1's device; max_count: its largest value, known on the host (a pass no position runs is not computed)."""
+    z = z1
+    for k in range(1, min(max_count, model.hyper_connections.n_passes)):
+        e = getattr(model, f"loop_embedding_pass{k + 1}", None)
+        s = block_read_all(model, z if e is None else z + e.to(z.dtype), ctx, records, checkpoint)
+        z = torch.where((counts > k)[..., None], model.hyper_connections(z, s, k), z)
+    return z, counts >= 2
+
+
+def second_pass(model, z1, ctx, records: list, pass2_mask, capacity, checkpoint: bool):
+    """(z, kept, n_dropped): z_2 where pass 2 is kept and z_1 elsewhere."""
+    B, L, _ = z1.shape
+    e2 = getattr(model, "loop_embedding_pass2", None)
+    u = block_read_all(model, z1 if e2 is None else z1 + e2.to(z1.dtype), ctx, records, checkpoint)
     z2 = model.hyper_connections(z1, u)
     if pass2_mask is None:
         return z2, torch.ones(B, L, dtype=torch.bool, device=z1.device), torch.zeros(B, dtype=torch.long, device=z1.device)

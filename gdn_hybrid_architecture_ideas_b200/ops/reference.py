@@ -116,7 +116,7 @@ def delta_rule_recurrence(q, k, v, g, beta, is_doc_start, S):
     return torch.stack(outs, dim=1), S
 
 
-def chunk_local(q, k, v, g, beta, is_doc_start, C):
+def chunk_local(q, k, v, g, beta, is_doc_start, C, extras: bool = False):
     """Everything of the chunked delta rule that does not depend on the carried state, for all chunks at once.
 
     Inputs as delta_rule_recurrence's, L a multiple of C. Returns a dict of (B,H,n,C,...) tensors:
@@ -152,9 +152,11 @@ def chunk_local(q, k, v, g, beta, is_doc_start, C):
     rhs = torch.cat([v * beta[..., None], kb * (gamma * first)[..., None]], dim=-1)
     sol = torch.linalg.solve_triangular(eye + A, rhs, upper=False, unitriangular=True)
     U, W = sol.split([v.shape[-1], dk], dim=-1)
-    return dict(U=U, W=W, Aqk=(q @ k.transpose(-1, -2)) * decay, q_in=q * (gamma * first)[..., None],
-                k_out=k * (to_end * last)[..., None], carry=gamma[..., -1] * (seg[..., -1] == 0).to(wd),
-                k=k, decay=decay, gamma_first=gamma * first)      # the last three: `delta_rule_picks` only
+    parts = dict(U=U, W=W, Aqk=(q @ k.transpose(-1, -2)) * decay, q_in=q * (gamma * first)[..., None],
+                 k_out=k * (to_end * last)[..., None], carry=gamma[..., -1] * (seg[..., -1] == 0).to(wd))
+    if extras:          # what `delta_rule_picks` reads to form the state after a position inside a chunk
+        parts.update(k=k, decay=decay, gamma_first=gamma * first)
+    return parts
 
 
 def chunk_scan(parts, S):
@@ -216,7 +218,7 @@ def delta_rule_picks(q, k, v, g, beta, is_doc_start, S, picks, kernel: str = "ch
         q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
         g, beta = (F.pad(t, (0, 0, 0, pad)) for t in (g, beta))
         is_doc_start = F.pad(is_doc_start, (0, pad))
-    parts = chunk_local(q, k, v, g, beta, is_doc_start, C)
+    parts = chunk_local(q, k, v, g, beta, is_doc_start, C, extras=True)
     S = S.to(parts["U"].dtype)
     outs, starts, news = [], [], []
     for U, W, qi, Aqk, ko, cy in zip(*(parts[n].unbind(2) for n in ("U", "W", "q_in", "Aqk", "k_out", "carry"))):

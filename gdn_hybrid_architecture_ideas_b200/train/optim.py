@@ -134,8 +134,8 @@ def param_groups(model, o, trainable=None) -> list[dict]:
         taken = {n for n, _ in later}
         base = (1.0 if o.name == "adamw" else o.adamw_lr_scale) * o.pass2_lr_scale
         spec = [(k, [(n, p) for n, p in items if n not in taken], wd, sc) for k, items, wd, sc in spec]
-        spec.append(("adamw", [(n, p) for n, p in later if not n.endswith("pass2_gate")], o.weight_decay, base))
-        spec.append(("adamw", [(n, p) for n, p in later if n.endswith("pass2_gate")], 0.0, base))
+        spec.append(("adamw", [(n, p) for n, p in later if not n.endswith("_gate")], o.weight_decay, base))
+        spec.append(("adamw", [(n, p) for n, p in later if n.endswith("_gate")], 0.0, base))
     elif o.pass2_lr_scale != 1.0:
         raise ValueError(f"optim.pass2_lr_scale {o.pass2_lr_scale!r} scales the LR of a gated second pass's tensors (model.loop.pass2_gate); this model has none: leave it 1.0")
     if o.ccr_translator_decay not in CCR_TRANSLATOR_DECAY_MODES:

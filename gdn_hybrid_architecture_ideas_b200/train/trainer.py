@@ -339,6 +339,8 @@ class Trainer:
             kw.update(rope_scale=s)
         if self.looped or self.gated:
             kw.update(T=self.pass_count)
+        if self.gated and self.pass_count == 2 and self.model.schedule is not None and self.model.schedule.unscored is not None:
+            kw.update(scored=_scored(mb))        # pass counts by segment (models/pass_counts.py): a target that does not count runs pass 1 only
         ac = torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast and not self.native)
         with ac:
             out = self.model(mb.tokens, mb.doc_ids, return_hidden=True, single_doc=mb.single_doc, **kw)
@@ -514,6 +516,9 @@ class Trainer:
                 m["pass2_alpha"] = float(self.model.alpha())
                 if self.pass_count == 2 and getattr(self.model, "last_loop_usage", None) is not None:
                     m["loop_usage"] = float(self.model.last_loop_usage)
+                if self.pass_count == 2 and self.model.schedule is not None:      # the share of positions at each pass count in the step's last micro-batch
+                    c = self.model.last_counts
+                    m["pass_counts"] = {str(k): float((c == k).float().mean()) for k in range(1, self.model.n_passes + 1)}
         if self.looped:
             m["T"] = self.pass_count
             inj = self.model.encoder.recur_injection
