@@ -759,7 +759,7 @@ _BUILT = {
     "model.fp8.chains": ((),),
     "model.fp8.folds": ((),),
     "model.nvfp4.mode": ("none", "all_linears", "all_but_gdn", "all_but_gdn_mixer", "mlp_only"),
-    "model.nvfp4.recipe": ("nvidia",),
+    "model.nvfp4.recipe": ("nvidia", "quartet2"),
 }
 
 _TRAIN_BUILT = {

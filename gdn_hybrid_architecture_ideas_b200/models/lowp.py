@@ -39,6 +39,10 @@ def apply_low_precision(model, cfg) -> list[str]:
             m.precision, m.lowp = cfg.fp8.scaling if cfg.fp8.scaling == "mxfp8" else "fp8_" + cfg.fp8.scaling, lowp.recipe_for(cfg, name)
             done.append(name)
     elif cfg.nvfp4.mode != "none":
+        nv = cfg.nvfp4
+        if nv.recipe == "quartet2" and (not nv.stochastic_rounding or not nv.rht or not nv.weight_2d):
+            raise ValueError("model.nvfp4.recipe 'quartet2' has its own roundings and transform: stochastic_rounding, rht and weight_2d are the "
+                             "'nvidia' recipe's switches and keep their defaults under it")
         names = list(quantised_linears(model, cfg.nvfp4.mode, 16))
         keep_last = int(round(cfg.nvfp4.keep_last_fraction * cfg.encoder.n_layers))
         for name, m in names:

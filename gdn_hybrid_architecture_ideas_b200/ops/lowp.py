@@ -169,6 +169,144 @@ def rht_tokens(t2d: torch.Tensor, transform: torch.Tensor | None) -> torch.Tenso
     return torch.matmul(t.reshape(n, m // NV_BLOCK, NV_BLOCK), transform.to(t.device)).reshape(n, m)
 
 
+# ------------------------------------------------------------------------------------------------------------ Quartet II
+# `model.nvfp4.recipe: quartet2` (Panferov et al., arXiv 2601.22813, Algorithm 1). Forward: activations and weights in 1 x 16
+# blocks along the dot product, round to nearest with ties AWAY from zero, and "four over six": every block is quantised
+# with its largest magnitude mapped to 6 and to 4 and keeps the one with the smaller squared error (6 on a tie); tensor
+# decode scale amax / 256 / 6. Backward: each operand of Dgrad and Wgrad (the gradient and the forward's QUANTISED weight and
+# activation) is re-quantised with MS-EDEN along its GEMM's dot product: one random Hadamard transform over 128-element
+# segments with ONE fresh sign vector a backward call (it cancels in each product), tensor scale amax / 255.99 / g with
+# g = 6 / (17/16 * 0.93), round to nearest, the per-block correction S = <x', x'> / <x', q>, and the corrected block scale
+# rounded STOCHASTICALLY to an E4M3 neighbour so that its expectation is S * scale. A quantised tensor is kept as (v, s_dec):
+# v = element x block scale (exact in bf16), the tensor scale applied to the GEMM's output
+# (reference: ced/model/nvfp4.py:296-449, 508-552).
+
+Q2_FWD_SCALES_MAX, Q2_BWD_SCALES_MAX, Q2_BWD_GRID_MAX, Q2_RHT = 256.0, 255.99, 6.0 / ((17.0 / 16.0) * 0.93), 128
+
+
+def e2m1_round_away(a: torch.Tensor) -> torch.Tensor:
+    """Magnitudes a >= 0 onto the E2M1 grid, ties away from zero, saturating at 6 (exact: the step is a power of two)."""
+    step = torch.where(a < 2.0, 0.5, torch.where(a < 4.0, 1.0, 2.0)).to(a.dtype)
+    t = a / step
+    n = torch.floor(t)
+    return torch.clamp((n + (t - n >= 0.5).to(a.dtype)) * step, max=E2M1_MAX)
+
+
+def _e4m3_or_one(s: torch.Tensor) -> torch.Tensor:
+    q = torch.clamp(s, max=E4M3_MAX).to(E4M3).float()
+    return torch.where(q == 0, torch.ones_like(q), q)       # a block whose scale underflows quantises to zeros
+
+
+def q2_rtn_quantize(x: torch.Tensor, four_over_six: bool = True):
+    """(v, s_dec) of the forward quantiser along x's last dimension; the dequantised tensor is v * s_dec."""
+    x32 = x.float()
+    shape = x32.shape
+    pad = (-shape[-1]) % NV_BLOCK
+    xp = F.pad(x32, (0, pad)) if pad else x32
+    blocks = xp.reshape(*xp.shape[:-1], -1, NV_BLOCK)
+    amax = x32.abs().amax()
+    s_dec = torch.where(amax > 0, amax / (Q2_FWD_SCALES_MAX if four_over_six else E4M3_MAX) / E2M1_MAX, torch.ones_like(amax))
+    amax_b = blocks.abs().amax(dim=-1, keepdim=True)
+
+    def candidate(scale):
+        unit = scale * s_dec
+        scaled = blocks / unit
+        q = torch.copysign(e2m1_round_away(scaled.abs()), scaled)
+        return q, ((blocks - q * unit) ** 2).sum(-1, keepdim=True)
+
+    scale = _e4m3_or_one(amax_b / E2M1_MAX / s_dec)
+    q, err = candidate(scale)
+    if four_over_six:
+        scale4 = _e4m3_or_one(amax_b / E2M1_MAX * 1.5 / s_dec)
+        q4, err4 = candidate(scale4)
+        six = err <= err4
+        q, scale = torch.where(six, q, q4), torch.where(six, scale, scale4)
+    return (q * scale).reshape(*blocks.shape[:-2], -1)[..., :shape[-1]], s_dec
+
+
+def q2_rotate(t2d: torch.Tensor, transform: torch.Tensor) -> torch.Tensor:
+    """(R, K) -> (R, K'): every n-segment of each row times the (n x n) transform, K zero-padded to a multiple of n."""
+    n = transform.shape[0]
+    t = t2d.float()
+    pad = (-t.shape[-1]) % n
+    if pad:
+        t = F.pad(t, (0, pad))
+    r, k = t.shape
+    return torch.matmul(t.reshape(r, k // n, n), transform.float()).reshape(r, k)
+
+
+def e4m3_neighbours(c: torch.Tensor):
+    """(down, up): the E4M3 values around c >= 0, both c itself when c is one."""
+    c = torch.clamp(c, max=E4M3_MAX)
+    near = c.to(E4M3)
+    bits = near.view(torch.uint8).to(torch.int16)
+    r = near.float()
+    at = lambda b: b.clamp(0, 0x7E).to(torch.uint8).view(E4M3).float()      # noqa: E731
+    above = r > c
+    return torch.where(above, at(bits - 1), r), torch.where(above, r, torch.where(r == c, r, at(bits + 1)))
+
+
+def q2_eden_quantize(t2d: torch.Tensor, transform: torch.Tensor, u: torch.Tensor | None = None):
+    """(v, s_dec) of MS-EDEN along K of t2d (R, K): the dequantised ROTATED tensor is v * s_dec. u (R, K' / 16) ~ U[0, 1)
+    decides each block scale's rounding (drawn here from the device's global generator when None)."""
+    xr = q2_rotate(t2d, transform)
+    r, k = xr.shape
+    blocks = xr.reshape(r, k // NV_BLOCK, NV_BLOCK)
+    amax = xr.abs().amax()
+    s_dec = torch.where(amax > 0, amax / Q2_BWD_SCALES_MAX / Q2_BWD_GRID_MAX, torch.ones_like(amax))
+    scale = _e4m3_or_one(blocks.abs().amax(dim=-1, keepdim=True) / Q2_BWD_GRID_MAX / s_dec)
+    scaled = blocks / (scale * s_dec)
+    q = torch.copysign(e2m1_round_away(scaled.abs()), scaled)
+    num, den = (scaled * scaled).sum(-1, keepdim=True), (scaled * q).sum(-1, keepdim=True)
+    zero = den == 0
+    c = scale * torch.where(zero, torch.ones_like(den), num / torch.where(zero, torch.ones_like(den), den))
+    down, up = e4m3_neighbours(c)
+    gap = up - down
+    p_up = torch.where(gap > 0, (c - down) / torch.where(gap > 0, gap, torch.ones_like(gap)), torch.zeros_like(gap))
+    if u is None:
+        u = torch.rand_like(num[..., 0])
+    return (q * torch.where(u[..., None] < p_up, up, down)).reshape(r, k), s_dec
+
+
+def q2_hadamard() -> torch.Tensor:
+    return hadamard(Q2_RHT) / math.sqrt(Q2_RHT)
+
+
+class _Quartet2Linear(torch.autograd.Function):
+    """Draws of a backward call, in this order from the device's global generator: the 128 signs, then the scale roundings of
+    dy and W^T (Dgrad), dy^T and x^T (Wgrad)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, native_gemm: bool):
+        k = x.shape[-1]
+        xv, xs = q2_rtn_quantize(x.reshape(-1, k))
+        wv, ws = q2_rtn_quantize(weight)
+        out_dtype = x.dtype if x.dtype != torch.float32 or not native_gemm else torch.bfloat16
+        y = (_mm(xv, wv, native_gemm, torch.float32) * (xs * ws)).to(out_dtype)
+        keep = torch.bfloat16 if native_gemm else xv.dtype
+        ctx.save_for_backward(xv.to(keep), xs, wv.to(keep), ws)
+        ctx.native_gemm, ctx.xshape, ctx.x_dtype, ctx.w_dtype = native_gemm, x.shape, x.dtype, weight.dtype
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        xv, xs, wv, ws = ctx.saved_tensors
+        n, k = wv.shape
+        dy2 = dy.reshape(-1, n)
+        signs = torch.where(torch.rand(Q2_RHT, device=dy.device) < 0.5, 1.0, -1.0)
+        transform = signs[:, None] * q2_hadamard().to(dy.device)
+        dx = dw = None
+        if ctx.needs_input_grad[0]:             # dx = dy W: the dot product over the output features
+            gv, gs = q2_eden_quantize(dy2, transform)
+            wtv, wts = q2_eden_quantize(wv.float().t(), transform)
+            dx = (_mm(gv, wtv, ctx.native_gemm, torch.float32) * (gs * wts * ws)).reshape(*ctx.xshape[:-1], k).to(ctx.x_dtype)
+        if ctx.needs_input_grad[1]:             # dW = dy^T x: the dot product over the tokens
+            gtv, gts = q2_eden_quantize(dy2.t(), transform)
+            xtv, xts = q2_eden_quantize(xv.float().reshape(-1, k).t(), transform)
+            dw = (_mm(gtv, xtv, ctx.native_gemm, torch.float32) * (gts * xts * xs)).to(ctx.w_dtype)
+        return dx, dw, None
+
+
 # ------------------------------------------------------------------------------------------------------------ FP8 scalings
 
 def fp8_scale(amax: torch.Tensor, fmax: float, pow2: bool) -> torch.Tensor:
@@ -232,6 +370,8 @@ class Recipe:
 
     # the op layer's two entry points
     def emulated_linear(self, x, weight):
+        if self.kind == "quartet2":
+            return _Quartet2Linear.apply(x, weight, False)
         return _LowpLinear.apply(x, weight, self, False)
 
 
@@ -243,6 +383,8 @@ def recipe_for(cfg, name: str) -> Recipe:
     nv = cfg.nvfp4
     if any(name.endswith(k) or k in name for k in nv.fp8_names):
         return Recipe("mxfp8")
+    if nv.recipe == "quartet2":
+        return Recipe("quartet2")
     return Recipe("nvfp4", stochastic=nv.stochastic_rounding, rht=nv.rht, weight_2d=nv.weight_2d)
 
 
@@ -357,4 +499,6 @@ def native_linear(x, lin):
 
     if lin.lowp.kind == "mxfp8" and mx_native_ok(x, lin.weight) and os.environ.get("GHB_MX_GEMM", "native") == "native":
         return _MxLinear.apply(x, lin.weight)
+    if lin.lowp.kind == "quartet2":
+        return _Quartet2Linear.apply(x, lin.weight, True)
     return _LowpLinear.apply(x, lin.weight, lin.lowp, True)

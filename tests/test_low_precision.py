@@ -66,7 +66,46 @@ def test_fp8_linear_matches_reference(reference, scaling):
     assert torch.allclose(w.grad, w2.grad, atol=1e-4, rtol=1e-4)
 
 
-@pytest.mark.parametrize("which", ["mxfp8", "nvfp4"])
+def test_quartet2_linear_equals_the_reference_draw_for_draw(reference):
+    """The Quartet II recipe: the four-over-six forward quantiser value for value; the backward (one sign vector a call, MS-EDEN
+    with stochastic scale roundings) bit for bit under the same seed; the estimator's error against the exact products; the
+    stochastic block scales unbiased around the corrected scale."""
+    import ced.model.nvfp4 as rnv
+
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(3, 40, 72, generator=g, requires_grad=True)
+    w = (torch.randn(48, 72, generator=g) * 0.05).requires_grad_()
+    x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    a = torch.rand(4000, generator=g) * 7
+    assert torch.equal(lowp.e2m1_round_away(a), rnv.e2m1_round_away(a)) and float(lowp.e2m1_round_away(torch.tensor([0.25, 0.75, 2.5, 5.0, 9.0])).sum()) == 0.5 + 1 + 3 + 6 + 6
+    for four in (True, False):
+        v, sd = lowp.q2_rtn_quantize(x.detach().reshape(-1, 72), four)
+        rv, rsd = rnv.quartet2_rtn_quantize(x.detach().reshape(-1, 72), four)
+        assert torch.equal(v, rv) and torch.equal(sd, rsd) and torch.equal(v.bfloat16().float(), v)          # operands exact in bf16
+    y = lowp.Recipe("quartet2").emulated_linear(x, w)
+    yr = rnv.Quartet2LinearFunction.apply(x2, w2, rnv.hadamard_matrix(128) / 128 ** 0.5, torch.float32)
+    assert torch.equal(y, yr)
+    gy = torch.randn(3, 40, 48, generator=g)
+    torch.manual_seed(11)
+    y.backward(gy)
+    torch.manual_seed(11)
+    yr.backward(gy)
+    assert torch.equal(x.grad, x2.grad) and torch.equal(w.grad, w2.grad)
+    exact_dx, exact_dw = gy @ w.detach(), gy.reshape(-1, 48).t() @ x.detach().reshape(-1, 72)
+    assert (x.grad - exact_dx).norm() / exact_dx.norm() < 0.3 and (w.grad - exact_dw).norm() / exact_dw.norm() < 0.3
+    c = torch.tensor([[0.3], [17.0], [100.0]])
+    down, up = lowp.e4m3_neighbours(c)
+    assert (down <= c).all() and (c <= up).all() and torch.equal(lowp.e4m3_neighbours(torch.tensor([16.0]))[0], torch.tensor([16.0]))
+    t = torch.randn(64, 256, generator=g)
+    T = lowp.q2_hadamard()
+    draws = torch.stack([lowp.q2_eden_quantize(t, T, torch.rand(64, 16, generator=g))[0] for _ in range(200)]).mean(0)
+    v0, s0 = lowp.q2_eden_quantize(t, T, torch.full((64, 16), 0.5))
+    rot = lowp.q2_rotate(t, T)
+    assert ((draws * s0 - rot).norm() / rot.norm()) < ((v0 * s0 - rot).norm() / rot.norm())            # averaging the draws approaches the rotated tensor
+    assert (T @ T.t() - torch.eye(128)).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("which", ["mxfp8", "nvfp4", "quartet2"])
 def test_quantised_model_trains_and_evaluates_in_high_precision(which):
     cfg = C.tiny_control_config()
     cfg.d_model, cfg.ffn_hidden = 64, 192
@@ -74,6 +113,12 @@ def test_quantised_model_trains_and_evaluates_in_high_precision(which):
         cfg.fp8.mode, cfg.fp8.scaling = "linears", "mxfp8"
     else:
         cfg.nvfp4.mode = "all_linears"
+        cfg.nvfp4.recipe = "nvidia" if which == "nvfp4" else "quartet2"
+    if which == "quartet2":
+        bad = C.tiny_control_config()
+        bad.nvfp4.mode, bad.nvfp4.recipe, bad.nvfp4.rht = "all_linears", "quartet2", False
+        with pytest.raises(ValueError, match="quartet2"):
+            build_model(bad)
     torch.manual_seed(0)
     m = build_model(cfg)
     plain = C.tiny_control_config()
