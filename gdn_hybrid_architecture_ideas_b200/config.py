@@ -783,7 +783,6 @@ _TRAIN_BUILT = {
     "data.decoder_positions": ("data", "random"),
     "data.union_order": ("permute", "sets_in_order"),
     "decoder_opt": ("none",),
-    "optim.recur_b": ("adamw",),                  # the looped middle's injection matrix under Muon is not built
 }
 
 

@@ -29,6 +29,8 @@ ZERO_GATE_SUFFIXES = (".gdn_arms.ccr_gate", ".gdn_arms.write_lambda", ".gdn_arms
 # AdamW group of their own, the last, at the depth readers' learning rate; optim.ccr_translator_decay "none": no decay,
 # "identity": the run's weight decay, which on D pulls M toward the identity (reference: ced/train/optim.py:283-312).
 CCR_TRANSLATOR_SUFFIX = ".gdn_arms.ccr_translator_delta"
+RECUR_B, RECUR_B_MODES = "encoder.recur_injection.B", ("adamw", "muon", "muon_no_decay")     # reference: ced/train/optim.py:427-441, 956-971
+SKIP_GAIN = "encoder.skip_gain"
 CCR_TRANSLATOR_DECAY_MODES = ("none", "identity")
 MIX_QUERY_DECAY = {"decay": (), "none_qmix": (".gdn_arms.qmix_query.query",),
                    "none_write_qmix": (".gdn_arms.write_query.query", ".gdn_arms.qmix_query.query")}
@@ -111,14 +113,35 @@ def param_groups(model, o, trainable=None) -> list[dict]:
         plain = [(n, p) for n, p in named if n.endswith(suffixes)]
         spec = [("adamw", decay, o.weight_decay, 1.0), ("adamw", plain, 0.0, 1.0)]
     elif o.name == "muon":
-        mats = [(n, p) for n, p in named if is_muon_param(n, p)]
-        rest = [(n, p) for n, p in named if not is_muon_param(n, p)]
+        b_muon = o.recur_b == "muon"            # the looped middle's dense injection matrix as one more Muon tensor (optim.recur_b)
+        mats = [(n, p) for n, p in named if is_muon_param(n, p) or (b_muon and n == RECUR_B)]
+        rest = [(n, p) for n, p in named if not is_muon_param(n, p) and not (o.recur_b != "adamw" and n == RECUR_B)]
         decay = [(n, p) for n, p in rest if not n.endswith(suffixes)]
         plain = [(n, p) for n, p in rest if n.endswith(suffixes)]
         spec = [("muon", mats, o.weight_decay, 1.0), ("adamw", decay, o.weight_decay, o.adamw_lr_scale),
                 ("adamw", plain, 0.0, o.adamw_lr_scale)]
     else:
         raise ValueError(f"optim.name {o.name!r}: 'adamw' or 'muon'")
+    if o.recur_b not in RECUR_B_MODES:
+        raise ValueError(f"optim.recur_b {o.recur_b!r}: one of {RECUR_B_MODES}")
+    if o.recur_b != "adamw":
+        if o.name != "muon":
+            raise ValueError(f"optim.recur_b {o.recur_b!r} is read under optim.name 'muon', not {o.name!r} (there every tensor is on AdamW)")
+        own = [(n, p) for n, p in named if n == RECUR_B and p.ndim == 2]
+        if not own:
+            raise ValueError(f"optim.recur_b {o.recur_b!r} is for the dense matrix {RECUR_B} of a looped middle's injection (model.loop.recur_layers "
+                             "with injection 'parcae' and recur_inject_b 'dense'); this model has none")
+        if o.recur_b == "muon_no_decay":        # the Muon update in a group of its own without weight decay, after the groups above
+            spec.append(("muon", own, 0.0, 1.0))
+    a_scale = o.layer_scalar_a_lr_scale
+    if isinstance(a_scale, bool) or not isinstance(a_scale, (int, float)) or not a_scale > 0 or a_scale != a_scale or a_scale == float("inf"):
+        raise ValueError(f"optim.layer_scalar_a_lr_scale {a_scale!r}: a finite number above 0")
+    if a_scale != 1.0:      # the residual scalars' a alone at its own learning rate: a group of its own, the last of these, without decay
+        gain = [(n, p) for n, p in named if n == SKIP_GAIN]
+        if not gain:
+            raise ValueError(f"optim.layer_scalar_a_lr_scale {a_scale!r} scales the LR of {SKIP_GAIN} (model.encoder.layer_scalars with a stored a); this model has none: leave it 1.0")
+        spec = [(k, [(n, p) for n, p in items if n != SKIP_GAIN], wd, sc) for k, items, wd, sc in spec]
+        spec.append(("adamw", gain, 0.0, (1.0 if o.name == "adamw" else o.adamw_lr_scale) * a_scale))
     if o.gdn_mup_base_width != GDN_MUP_BASE_WIDTH and not o.gdn_mup:
         raise ValueError(f"optim.gdn_mup_base_width {o.gdn_mup_base_width!r} is read with optim.gdn_mup true: leave it {GDN_MUP_BASE_WIDTH}")
     if o.gdn_mup:

@@ -970,3 +970,48 @@ def test_copy_paste_head_trains_and_then_alone_on_a_frozen_trunk(tmp_path):
     fused.head_impl = "fused"
     with pytest.raises(ValueError, match="head_impl"):
         Trainer(fused, None)
+
+
+def test_injection_matrix_under_muon_and_the_scalars_own_learning_rate():
+    """optim.recur_b puts the looped middle's dense injection matrix on Muon (with the run's decay, or in a last group without);
+    optim.layer_scalar_a_lr_scale gives the residual scalars' a a group of its own; both are refused where they name nothing."""
+    from gdn_hybrid_architecture_ideas_b200.models import build_model
+    from gdn_hybrid_architecture_ideas_b200.train import optim
+
+    mc = C.tiny_control_config()
+    mc.encoder.n_layers = 8
+    mc.loop.recur_layers, mc.loop.injection, mc.loop.t_eval, mc.loop.t_max, mc.loop.t_choices, mc.loop.t_probs = (2, 6), "parcae", 2, 2, [2], [1.0]
+    model = build_model(mc)
+    o = C.OptimConfig(name="muon")
+    B = "encoder.recur_injection.B"
+    base = optim.param_groups(model, o)
+    assert B in [n for g in base if g["kind"] == "adamw" and g["weight_decay"] == 0 for n in g["names"]]
+    o.recur_b = "muon"
+    g1 = optim.param_groups(model, o)
+    assert B in g1[0]["names"] and g1[0]["kind"] == "muon" and g1[0]["weight_decay"] == o.weight_decay and len(g1) == len(base)
+    o.recur_b = "muon_no_decay"
+    g2 = optim.param_groups(model, o)
+    assert g2[-1] == {"kind": "muon", "names": [B], "params": g2[-1]["params"], "weight_decay": 0.0, "lr_scale": 1.0} and B not in [n for g in g2[:-1] for n in g["names"]]
+    assert sum(len(g["names"]) for g in g2) == sum(len(g["names"]) for g in base)
+    cfg = tiny_train_config()
+    cfg.model, cfg.optim.name, cfg.optim.recur_b = mc, "muon", "muon"
+    t = Trainer(copy.deepcopy(cfg), None)
+    before = dict(t.model.named_parameters())[B].detach().clone()
+    t.train_step()
+    assert not torch.equal(before, dict(t.model.named_parameters())[B])
+    for change, match in ((lambda c: setattr(c.optim, "name", "adamw"), "read under optim.name 'muon'"), (lambda c: setattr(c.optim, "recur_b", "sgd"), "one of"),
+                          (lambda c: setattr(c.model.loop, "recur_inject_b", "diag"), "this model has none")):
+        bad = copy.deepcopy(cfg)
+        change(bad)
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
+    sc = C.tiny_control_config()
+    sc.encoder.layer_scalars = "skip_x0"
+    o2 = C.OptimConfig(name="muon", layer_scalar_a_lr_scale=0.01)
+    groups = optim.param_groups(build_model(sc), o2)
+    assert groups[-1]["names"] == ["encoder.skip_gain"] and groups[-1]["weight_decay"] == 0 and abs(groups[-1]["lr_scale"] - 0.01 * o2.adamw_lr_scale) < 1e-12
+    assert "encoder.x0_gain" in [n for g in groups[:-1] for n in g["names"]]
+    with pytest.raises(ValueError, match="this model has none"):
+        optim.param_groups(build_model(C.tiny_control_config()), o2)
+    with pytest.raises(ValueError, match="finite number above 0"):
+        optim.param_groups(build_model(sc), C.OptimConfig(layer_scalar_a_lr_scale=0.0))
