@@ -786,6 +786,30 @@ _TRAIN_BUILT = {
 }
 
 
+# Keys that belong to parts this framework does not build (the slot decoder of the looped architecture and its lane
+# hyper-connections, the other matrix optimizers, the unbuilt forms of the Copy-Paste head, auxiliary losses, the in-loop
+# long-context reads) and that nothing here reads. They load and round-trip; a value off the default would change nothing,
+# so it is refused by name instead of being ignored.
+_UNREAD = (
+    "model.encoder.write_mix_storage", "model.encoder.write_mix_row_term", "model.decoder.memory_attn_interval", "model.decoder.ffn_experts",
+    "model.decoder.ffn_top_k", "model.decoder.ffn_expert_hidden", "model.decoder.moe_balance_weight", "model.decoder.untie_mixers",
+    "model.decoder.router_z_weight", "model.decoder.memory_kv_per_layer", "model.decoder.capacity_fraction", "model.decoder.capacity_multiple",
+    "model.decoder.self_kv", "model.decoder.read_pattern", "model.decoder.local_window", "model.decoder.local_temperature",
+    "model.loop.draft_loss_weight", "model.loop.depth_attention", "model.loop.depth_attention_head_dim", "model.loop.depth_attention_rope_theta",
+    "model.loop.hc_streams", "model.loop.hc_write", "model.loop.hc_res_init", "model.second_pass.pass_embedding",
+    "model.fp8.te_nonfinite_check", "model.fp8.te_operands", "model.fp8.nonfinite_flag", "model.fp8.nonfinite_flag_form",
+    "model.cp_head.aux_weight", "model.cp_head.shared_layer", "model.cp_head.shared_head", "model.cp_head.shared_ssmax", "model.cp_head.trunk_k",
+    "model.cp_head.trunk_select_step")
+_TRAIN_UNREAD = (
+    "data.span_distribution", "data.span_sigma", "data.answer_min_context", "data.answer_gap_mean", "data.answer_capacity_fraction",
+    "data.answer_sinks", "data.answer_replay_window", "optim.hyperball_radius", "optim.soap_shampoo_beta", "optim.soap_precondition_frequency",
+    "optim.soap_eigh", "optim.shampoo_epsilon", "optim.shampoo_precondition_frequency", "optim.shampoo_start_step", "optim.normuon_beta2",
+    "optim.anvil2_preset", "optim.anvil2_single_rounding", "optim.anvil2_tavg", "optim.anvil2_decon", "optim.anvil2_scale", "optim.anvil2_points",
+    "optim.anvil2_tail_ema", "optim.anvil2_qk_head_pairs", "optim.soap_seeded_start", "optim.ours", "loss.aux_weight", "loss.aux_positions",
+    "loss.aux_fraction", "eval.replay_window", "eval.decoder_at", "eval.lc_every_steps", "eval.lc_dir", "eval.lc_length", "eval.lc_docs",
+    "eval.lc_base_len", "eval.lc_mf_items", "trim_decoder_slots", "pass_slot_buckets", "micro_batch_by_t", "tst.aux_weight", "stage_shape")
+
+
 def _get(cfg, dotted: str):
     node = cfg
     for part in dotted.split("."):
@@ -807,6 +831,16 @@ def unsupported_options(cfg) -> list[str]:
             value = _get(cfg, key)
             if value not in allowed:
                 bad.append(f"{key}={value!r} (built: {list(allowed)})")
+    plain_model, plain_train = ModelConfig(), TrainConfig()
+    for key in _UNREAD:
+        value, default = _get(model, key[len("model."):]), _get(plain_model, key[len("model."):])
+        if value != default:
+            bad.append(f"{key}={value!r} (read by nothing here: leave it {default!r})")
+    if isinstance(cfg, TrainConfig):
+        for key in _TRAIN_UNREAD:
+            value, default = _get(cfg, key), _get(plain_train, key)
+            if value != default:
+                bad.append(f"{key}={value!r} (read by nothing here: leave it {default!r})")
     enc = model.encoder
     if enc.gdn_write_variant != "none" and enc.gdn_write_mix != "layer":
         bad.append("model.encoder.gdn_write_variant needs model.encoder.gdn_write_mix=layer")

@@ -1015,3 +1015,37 @@ def test_injection_matrix_under_muon_and_the_scalars_own_learning_rate():
         optim.param_groups(build_model(C.tiny_control_config()), o2)
     with pytest.raises(ValueError, match="finite number above 0"):
         optim.param_groups(build_model(sc), C.OptimConfig(layer_scalar_a_lr_scale=0.0))
+
+
+def test_keys_that_nothing_reads_are_refused_off_their_defaults():
+    """A key of a part this framework does not build loads and round-trips, and is refused by name when it is set: it would
+    change nothing. Every key of the config is either read by the code, in a refusal table, or on that list."""
+    import dataclasses
+    import re
+    import subprocess
+
+    cfg = tiny_train_config()
+    assert C.unsupported_options(cfg) == []
+    for key, value in (("model.loop.hc_streams", 4), ("loss.aux_weight", 0.25), ("model.decoder.ffn_experts", 8), ("optim.normuon_beta2", 0.9), ("stage_shape", "[4, 4096]")):
+        bad = copy.deepcopy(cfg)
+        C.apply_override(bad, f"{key}={value}")
+        assert any(x.startswith(key + "=") and "read by nothing" in x for x in C.unsupported_options(bad)), key
+        with pytest.raises(ValueError, match="read by nothing"):
+            Trainer(bad, None)
+    root = Path(__file__).resolve().parent.parent
+    files = subprocess.run(["git", "ls-files", "gdn_hybrid_architecture_ideas_b200/*.py", "scripts/*.py", "bench.py"], capture_output=True, text=True, cwd=root).stdout.split()
+    src = "".join((root / f).read_text() for f in files if not f.endswith("gdn_hybrid_architecture_ideas_b200/config.py"))
+    cfg_src = (root / "gdn_hybrid_architecture_ideas_b200" / "config.py").read_text()
+    tables = cfg_src[cfg_src.index("_BUILT = {"):]
+
+    def leaves(cls, prefix=""):
+        for f in dataclasses.fields(cls):
+            t = f.default_factory() if f.default_factory is not dataclasses.MISSING else None
+            if dataclasses.is_dataclass(t):
+                yield from leaves(type(t), prefix + f.name + ".")
+            else:
+                yield prefix + f.name, f.name
+
+    orphans = [full for full, leaf in leaves(C.TrainConfig) if not re.search(r"\b" + re.escape(leaf) + r"\b", src) and leaf not in tables
+               and not full.startswith("optim.ours.")]
+    assert orphans == ["model.residual_scale.t_ref", "model.residual_scale.l_ref"], orphans      # (the two belong to residual-scale modes whose factor does not read them)
