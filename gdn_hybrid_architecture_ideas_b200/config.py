@@ -749,7 +749,7 @@ _BUILT = {
     "model.encoder.layer_scalars": ("none", "skip_x0", "skip_x0_span", "x0", "skip"),
     "model.encoder.attn_res": ("none", "block_entry", "block", "ldm"),
     "model.encoder.block_norm_gain": ("channel", "scalar"),
-    "model.encoder.gdn_write_mix": ("none", "layer"),
+    "model.encoder.gdn_write_mix": ("none", "layer", "head"),
     "model.encoder.gdn_write_variant": ("none", "qmix", "korig", "vonly", "kqmix", "qshare", "qshare_kv", "qshare_bd"),
     "model.encoder.residual_dtype": ("float32", "bf16"),
     "model.loop.pass2_gate": ("none", "scalar"),

@@ -240,9 +240,11 @@ class Encoder(nn.Module):
                 if opens or closes:
                     layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1, heads=enc.attn_res_heads,
                                                 query_hidden=query_hidden)
-        if enc.gdn_write_mix not in ("none", "layer"):
-            raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none' or 'layer'")
-        if enc.gdn_write_mix == "layer" and not self.block_entry:
+        if enc.gdn_write_mix not in ("none", "layer", "head"):
+            raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none', 'layer' or 'head'")
+        if enc.gdn_write_mix == "head" and (enc.gdn_write_variant != "none" or cfg.fp8.mode != "none" or cfg.nvfp4.mode != "none"):
+            raise ValueError("model.encoder.gdn_write_mix 'head' (one lambda a head) is built without a write variant and without model.fp8 / model.nvfp4")
+        if enc.gdn_write_mix != "none" and not self.block_entry:
             raise ValueError("model.encoder.gdn_write_mix reads the finished blocks of attn_res 'block_entry'")
         ccr_mod.check_config(cfg)
         reads, writes = ccr_mod.sources(cfg), set(ccr_mod.writers(cfg))
@@ -250,11 +252,12 @@ class Encoder(nn.Module):
         for i, layer in enumerate(self.layers):
             if layer.kind != "gdn":
                 continue
-            write = "layer" if enc.gdn_write_mix == "layer" and i > 0 else "none"
+            write = enc.gdn_write_mix if enc.gdn_write_mix != "none" and i > 0 else "none"
             if write == "none" and i not in reads and i not in writes:
                 continue
             g = enc.gdn
-            cross = None if not self.ccr else dict(
+            heads = {"heads": g.n_k_heads + g.n_v_heads}
+            cross = heads if not self.ccr else dict(heads=heads["heads"], 
                 read=i in reads, write=i in writes, spacing=enc.gdn_ccr_spacing, layer=i, source=reads.get(i), target=enc.gdn_ccr_target,
                 translator=enc.gdn_ccr_translator, gate_init=enc.gdn_ccr_gate_init, gate_floor=enc.gdn_ccr_gate_floor,
                 hk=g.n_k_heads, hv=g.n_v_heads, dk=g.k_head_dim)

@@ -57,8 +57,8 @@ class GDNArms(nn.Module):
         self.write_mix = write_mix
         self.variant = variant if write_mix != "none" else "none"
         self.write_query = DepthQuery(d, eps) if has_query and write_mix != "none" else None
-        if write_mix != "none":
-            self.write_lambda = nn.Parameter(torch.zeros(1))
+        if write_mix != "none":       # "layer": one scalar; "head": one a key head, then one a value head
+            self.write_lambda = nn.Parameter(torch.zeros(1 if write_mix == "layer" else (ccr or {}).get("heads", 1)))
         if self.variant in READ_MIX_VARIANTS:
             self.qmix_lambda = nn.Parameter(torch.zeros(1))
             self.qmix_query = DepthQuery(d, eps) if has_query else None
@@ -182,6 +182,21 @@ class GatedDeltaNet(nn.Module):
         nq, C = hk * dk, self.conv_channels
         if arms is None or arms.write_mix == "none":
             return self.in_proj_qkv(x), self.in_proj_a(x), self.in_proj_b(x)
+        if arms.write_mix == "head":
+            # One lambda per head: entry i < H_k the k channels of key head i, entry H_k + j the v channels, the write strength
+            # and the decay of value head j. By linearity P(x_w^h) = P(x) + lambda_h P(m' - x): one more projection of the k, v,
+            # a and b rows on the difference (reference: ced/model/gdn_arms.py:919-928).
+            hv, dv = self.cfg.n_v_heads, self.cfg.v_head_dim
+            lam = arms.write_lambda
+            d = (x_write - x).to(x.dtype)
+            u = self.in_proj_qkv(x)
+            lam_kv = torch.cat([lam[:hk].repeat_interleave(dk), lam[hk:].repeat_interleave(dv)]).to(u.dtype)
+            kv = u[..., nq:] + torch.nn.functional.linear(d, self.in_proj_qkv.weight[nq:].to(d.dtype)) * lam_kv
+            lam_v = lam[hk:]
+            a0, b0 = self.in_proj_a(x), self.in_proj_b(x)
+            a = a0 + self.in_proj_a(d) * lam_v.to(a0.dtype)
+            b = b0 + self.in_proj_b(d) * lam_v.to(b0.dtype)
+            return torch.cat([u[..., :nq], kv.to(u.dtype)], dim=-1), a.to(a0.dtype), b.to(b0.dtype)
         v = arms.variant
         W = self.in_proj_qkv
         reads = v in READ_MIX_VARIANTS

@@ -33,6 +33,8 @@ def local_model_config(cfg: ModelConfig, world: int) -> ModelConfig:
     if g.kda.decay != "scalar" or g.erase.mode != "none" or g.dprod.n_h != 1:
         raise ValueError("tensor parallel shards the scalar-decay GDN layer: gdn.kda.decay 'channel', gdn.erase.mode 'eda' and "
                          "gdn.dprod.n_h >= 2 are not built with it")
+    if enc.gdn_write_mix == "head":
+        raise ValueError("tensor parallel is not built with model.encoder.gdn_write_mix 'head' (its lambdas are indexed by the full stack's heads)")
     if cfg.loop.pass2_gate != "none":
         raise ValueError("tensor parallel is not built with a gated second pass (model.loop.pass2_gate)")
     if enc.gdn_ccr_spacing:

@@ -21,7 +21,7 @@ def _pair(reference, cfg):
 
 
 @pytest.mark.parametrize("preset", ["full", "control", "grid", "negeig", "skip_x0", "skip_x0_span", "x0", "skip", "canon", "canon_uniform", "gdn_shapes", "heads", "block_every", "token_query", "asentmax", "kda", "kda_floor", "erase", "kda_erase", "dprod", "dprod_b1", "dprod_layers", "dprod_heads", "dprod_mixed", "dprod_lowrank", "dprod_prev", "dprod_perm", "dprod_perm_random", "dprod_rot",
-                                    "dprod_noconv", "dprod_stride", "dprod_stride_all", "dprod_xmean", "dprod_kvmean", "dprod_xmean_b1", "ldm"])
+                                    "write_head", "dprod_noconv", "dprod_stride", "dprod_stride_all", "dprod_xmean", "dprod_kvmean", "dprod_xmean_b1", "ldm"])
 def test_state_dict_forward_backward(reference, preset):
     scalars = preset in ("skip_x0", "skip_x0_span", "x0", "skip")     # not built together with the depth mixing
     cfg = C.tiny_control_config() if preset in ("control", "gdn_shapes") or scalars or preset.startswith(("canon", "kda", "erase", "dprod")) else C.tiny_full_config()
@@ -32,6 +32,8 @@ def test_state_dict_forward_backward(reference, preset):
         cfg.encoder.gdn.negeig.beta_max = 2
     if scalars:
         cfg.encoder.layer_scalars = preset
+    if preset == "write_head":                 # the write mix with one lambda a key head and a value head
+        cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "head", "none"
     if preset == "block_every":
         cfg.encoder.attn_res = "block"
         cfg.encoder.gdn_write_mix, cfg.encoder.gdn_write_variant = "none", "none"
