@@ -25,7 +25,6 @@ import math
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from .. import ops
 from .linear import Linear
@@ -34,69 +33,70 @@ DERIVED = ("lowrank", "prev", "perm", "rot")
 KEYS = ("proj",) + DERIVED
 PERMS = ("roll", "random")
 STANDALONE_SEED = 0xC2_0D
+_SECOND = ("key", "value", "beta", "rank", "perm", "conv")           # the keys this module reads
+_FOREIGN = ("layers", "heads", "heads_by_layer", "beta_max", "beta_init", "stride", "summary", "first_beta", "route")
 
 
 def is_derived(cfg) -> bool:
     return getattr(cfg.dprod, "key", "proj") in DERIVED
 
 
+def _off_default(d, names) -> list:
+    plain = type(d)()
+    return [n for n in names if getattr(d, n) != getattr(plain, n)]
+
+
 def check_second(cfg, where: str = "gdn.dprod") -> None:
     """The second step's keys of one GDN config (ValueError naming the key)."""
     d = cfg.dprod
-    default = type(d)()
-    if d.key not in KEYS:
-        raise ValueError(f"{where}.key {d.key!r}: one of {KEYS}")
-    if d.value not in ("proj", "v1"):
-        raise ValueError(f"{where}.value {d.value!r}: 'proj' or 'v1'")
-    if d.beta != "proj":
-        raise ValueError(f"{where}.beta {d.beta!r}: 'proj' (its own projection; tied and constant forms are not built)")
-    if d.perm not in PERMS:
-        raise ValueError(f"{where}.perm {d.perm!r}: one of {PERMS}")
-    if type(d.rank) is not int or d.rank < 1 or (d.key == "lowrank" and d.rank > cfg.k_head_dim):
-        raise ValueError(f"{where}.rank {d.rank!r}: an integer >= 1 (with key 'lowrank' at most k_head_dim = {cfg.k_head_dim})")
-    if type(d.conv) is not bool:
-        raise ValueError(f"{where}.conv {d.conv!r}: true or false")
-    off = [k for k in ("key", "value", "beta", "rank", "perm", "conv") if getattr(d, k) != getattr(default, k)]
+    plain = type(d)()
+    domain = {"key": KEYS, "value": ("proj", "v1"), "beta": ("proj",), "perm": PERMS}
+    for name, allowed in domain.items():
+        if getattr(d, name) not in allowed:
+            raise ValueError(f"{where}.{name} {getattr(d, name)!r}: one of {allowed}")
+    limit = cfg.k_head_dim if d.key == "lowrank" else None
+    if type(d.rank) is not int or d.rank < 1 or (limit is not None and d.rank > limit):
+        raise ValueError(f"{where}.rank {d.rank!r}: an integer >= 1" + (f" and, with key 'lowrank', at most k_head_dim = {limit}" if limit else ""))
+    if not isinstance(d.conv, bool):
+        raise ValueError(f"{where}.conv {d.conv!r}: a bool")
+    moved = _off_default(d, _SECOND)
     if d.n_h == 1:
-        if off:
-            raise ValueError(f"{where}.{', '.join(off)} set with n_h 1: the second step's keys are read only with n_h 2")
+        if moved:
+            raise ValueError(f"{where}.{', '.join(moved)} set with n_h 1: the second step's keys are read only with n_h 2")
         return
-    if d.key == "proj":
-        wrong = [k for k in off if k != "key"]
-        if wrong:
-            raise ValueError(f"{where}.key 'proj' (full projections and the short conv) with {', '.join(wrong)} off their defaults: those belong "
+    if not is_derived(cfg):
+        extra = [n for n in moved if n != "key"]
+        if extra:
+            raise ValueError(f"{where}.key 'proj' (full projections and the short conv) with {', '.join(extra)} off their defaults: those belong "
                              "to a derived key (lowrank, prev, perm, rot); the strided and summarised second steps are not built")
         return
     if d.n_h != 2:
         raise ValueError(f"{where}.key {d.key!r} with n_h {d.n_h}: the derived second step is built for n_h 2")
-    wrong = [f"{k} {getattr(d, k)!r} (wants {w!r})" for k, w in (("value", "v1"), ("beta", "proj"), ("conv", False)) if getattr(d, k) != w]
+    needs = {"value": "v1", "beta": "proj", "conv": False}
+    wrong = [f"{n} {getattr(d, n)!r} (wants {w!r})" for n, w in needs.items() if getattr(d, n) != w]
     if wrong:
         raise ValueError(f"{where}.key {d.key!r}: {'; '.join(wrong)}: the second step has no value or conv channels of its own")
-    if d.key != "lowrank" and d.rank != default.rank:
-        raise ValueError(f"{where}.rank {d.rank!r} is read with key 'lowrank'; this layer's key is {d.key!r}")
-    if d.key != "perm" and d.perm != default.perm:
-        raise ValueError(f"{where}.perm {d.perm!r} is read with key 'perm'; this layer's key is {d.key!r}")
-    unread = [k for k in ("layers", "heads", "heads_by_layer", "beta_max", "beta_init", "stride", "summary", "first_beta", "route")
-              if getattr(d, k) != getattr(default, k)]
+    for name, owner in (("rank", "lowrank"), ("perm", "perm")):
+        if d.key != owner and getattr(d, name) != getattr(plain, name):
+            raise ValueError(f"{where}.{name} {getattr(d, name)!r} belongs to key {owner!r}; this layer's key is {d.key!r}")
+    unread = _off_default(d, _FOREIGN)
     if unread:
         raise ValueError(f"{where}.{', '.join(unread)} with key {d.key!r}: the derived second step reads none of these keys; not built together")
 
 
 def params_per_layer(d_model: int, cfg) -> int:
-    n = d_model * cfg.n_v_heads
-    if cfg.dprod.key == "lowrank":
-        n += d_model * cfg.dprod.rank * cfg.n_k_heads + cfg.dprod.rank * cfg.n_k_heads * cfg.k_head_dim
-    return n
+    extra = cfg.dprod.rank * cfg.n_k_heads * (d_model + cfg.k_head_dim) if cfg.dprod.key == "lowrank" else 0
+    return d_model * cfg.n_v_heads + extra
 
 
 def random_rotation(dk: int, g: torch.Generator) -> torch.Tensor:
     """A Haar rotation (det +1) from the CPU generator: Q of a Gaussian matrix's QR with R's diagonal made positive, the
     first column negated when the determinant is -1. float32."""
-    q, r = torch.linalg.qr(torch.randn(dk, dk, generator=g, dtype=torch.float64))
-    q = q * torch.sign(torch.diagonal(r))[None, :]
-    if float(torch.linalg.det(q)) < 0:
-        q[:, 0] = -q[:, 0]
-    return q.to(torch.float32)
+    basis, upper = torch.linalg.qr(torch.randn(dk, dk, generator=g, dtype=torch.float64))
+    basis = basis * upper.diagonal().sign().unsqueeze(0)
+    if torch.linalg.det(basis).item() < 0:
+        basis[:, 0].neg_()
+    return basis.float()
 
 
 class DerivedSteps(nn.Module):
@@ -105,49 +105,61 @@ class DerivedSteps(nn.Module):
     def __init__(self, d_model: int, cfg):
         super().__init__()
         check_second(cfg)
-        d = cfg.dprod
-        self.key, self.perm_kind, self.rank = d.key, d.perm, d.rank
+        self.key, self.perm_kind, self.rank = cfg.dprod.key, cfg.dprod.perm, cfg.dprod.rank
         self.d_model, self.hk, self.hv, self.dk = d_model, cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim
+        widths = {"in_proj_b": (d_model, self.hv)}
+        if self.key == "lowrank":
+            widths.update(k_down=(d_model, self.rank * self.hk), k_up=(self.rank, self.hk * self.dk))
         with torch.random.fork_rng(devices=[]):           # building draws nothing from the global stream
-            self.in_proj_b = Linear(d_model, self.hv)
-            if self.key == "lowrank":
-                self.k_down = Linear(d_model, self.rank * self.hk)
-                self.k_up = Linear(self.rank, self.hk * self.dk)
-        for m in self.children():
-            m.own_init = True
+            for name, (n_in, n_out) in widths.items():
+                lin = Linear(n_in, n_out)
+                lin.own_init = True
+                setattr(self, name, lin)
         if self.key == "rot":
             self.register_buffer("rot", torch.empty(self.dk, self.dk, dtype=torch.float32))
-        if self.key == "perm" and self.perm_kind == "random":
+        elif self.key == "perm" and self.perm_kind == "random":
             self.register_buffer("perm", torch.empty(self.dk, dtype=torch.long))
         self.reset_own(torch.Generator().manual_seed(STANDALONE_SEED), 0.02)
 
+    def _normal_draws(self, std: float) -> list:
+        """(tensor, its standard deviation) in draw order: in_proj_b, then the low-rank pair; k_up's so that the correction has about k1's size."""
+        out = [(self.in_proj_b.weight, std)]
+        if self.key == "lowrank":
+            out += [(self.k_down.weight, std), (self.k_up.weight, (self.dk * self.rank * self.d_model) ** -0.5 / std)]
+        return out
+
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float) -> None:
-        draws = [(self.in_proj_b.weight, std)]
-        if self.key == "lowrank":
-            draws += [(self.k_down.weight, std), (self.k_up.weight, 1.0 / (math.sqrt(self.dk * self.rank) * std * math.sqrt(self.d_model)))]
-        for p, s in draws:
-            if not p.is_meta:
-                p.copy_((torch.randn(p.shape, generator=g, dtype=torch.float32) * s).to(device=p.device, dtype=p.dtype))
-        if self.key == "rot" and not self.rot.is_meta:
-            self.rot.copy_(random_rotation(self.dk, g).to(device=self.rot.device, dtype=self.rot.dtype))
-        if self.key == "perm" and self.perm_kind == "random" and not self.perm.is_meta:
-            self.perm.copy_(torch.randperm(self.dk, generator=g).to(self.perm.device))
+        for tensor, sigma in self._normal_draws(std):
+            if tensor.is_meta:
+                continue
+            tensor.copy_(torch.randn(tensor.shape, generator=g, dtype=torch.float32).mul(sigma).to(tensor))
+        seeded = getattr(self, "rot", None) if self.key == "rot" else getattr(self, "perm", None)
+        if seeded is not None and not seeded.is_meta:
+            seeded.copy_((random_rotation(self.dk, g) if self.key == "rot" else torch.randperm(self.dk, generator=g)).to(seeded))
+
+    # one method per key: k2 (B, L, H_k, d_k) in k1's dtype (fixed shapes: a roll or an index buffer, one batched product, a shift and a 0 / 1 factor)
+
+    def _key_lowrank(self, x, k1, is_doc_start, k_prev):
+        wide = torch.promote_types(k1.dtype, torch.float32)
+        coeff = self.k_down(x).unflatten(-1, (self.hk, self.rank))
+        lift = self.k_up.weight.to(coeff.dtype).view(self.hk, self.dk, self.rank)
+        return ops.ref.l2_normalize(k1.to(wide) + torch.einsum("...hr,hdr->...hd", coeff, lift).to(wide)).to(k1.dtype)
+
+    def _key_prev(self, x, k1, is_doc_start, k_prev):
+        lead = k1.new_zeros(k1[:, :1].shape) if k_prev is None else k_prev.unsqueeze(1).to(k1.dtype)
+        shifted = torch.cat([lead, k1[:, :-1]], dim=1)
+        return shifted * is_doc_start.logical_not().to(shifted.dtype)[..., None, None]      # a document's first token reads no earlier key
+
+    def _key_perm(self, x, k1, is_doc_start, k_prev):
+        return k1.roll(self.dk // 2, -1) if self.perm_kind == "roll" else k1.index_select(-1, self.perm)
+
+    def _key_rot(self, x, k1, is_doc_start, k_prev):
+        wide = torch.promote_types(k1.dtype, torch.float32)
+        return torch.matmul(k1.to(wide), self.rot.to(wide).t()).to(k1.dtype)
 
     def second_key(self, x, k1, is_doc_start, k_prev):
-        """k2 (B, L, H_k, d_k) in k1's dtype. Fixed shapes: a roll or an index buffer, one batched product, a shift and a 0 / 1 factor."""
-        wide = torch.promote_types(k1.dtype, torch.float32)
-        if self.key == "lowrank":
-            z = self.k_down(x).unflatten(-1, (self.hk, self.rank))
-            w = self.k_up.weight.to(z.dtype).view(self.hk, self.dk, self.rank)
-            return ops.ref.l2_normalize(k1.to(wide) + torch.einsum("...hr,hdr->...hd", z, w).to(wide)).to(k1.dtype)
-        if self.key == "prev":
-            first = torch.zeros_like(k1[:, :1]) if k_prev is None else k_prev[:, None].to(k1.dtype)
-            prev = torch.cat([first, k1[:, :-1]], dim=1)
-            return prev * (~is_doc_start).to(prev.dtype)[..., None, None]
-        if self.key == "perm":
-            return torch.roll(k1, shifts=self.dk // 2, dims=-1) if self.perm_kind == "roll" else k1[..., self.perm]
-        return torch.einsum("...hd,ed->...he", k1.to(wide), self.rot.to(wide)).to(k1.dtype)
+        return getattr(self, "_key_" + self.key)(x, k1, is_doc_start, k_prev)
 
     def extra_repr(self) -> str:
         return f"key={self.key!r}" + (f", rank={self.rank}" if self.key == "lowrank" else "")
@@ -158,30 +170,29 @@ def forward(layer, x, ctx, state):
     and the two-step rule on the stacks (the loop, or the 2T interleave into the chunked rule)."""
     from .gdn_dprod import dprod_recurrence, interleave, last_substep
 
-    cfg, steps = layer.cfg, layer.dprod
-    B, L = ctx.doc.shape
-    hk, hv, dk, dv = cfg.n_k_heads, cfg.n_v_heads, cfg.k_head_dim, cfg.v_head_dim
+    g_cfg, steps = layer.cfg, layer.dprod
+    rows, length = ctx.doc.shape
+    n_k, n_v, d_k, d_v = g_cfg.n_k_heads, g_cfg.n_v_heads, g_cfg.k_head_dim, g_cfg.v_head_dim
     u = layer.in_proj_qkv(x)
-    if state is not None and state.conv_input.shape[-1] != u.shape[-1]:
-        raise ValueError(f"this GDN cache holds {state.conv_input.shape[-1]} conv channels; a layer with a derived second step carries {u.shape[-1]}")
-    if steps.key == "prev" and state is not None and state.k_prev is None:
-        raise ValueError("this GDN cache holds no previous key: it was not written by a layer with gdn.dprod.key 'prev'")
-    hist, hist_doc = (None, None) if state is None else (state.conv_input, state.conv_doc)
-    q, k1, v1, conv_input, conv_doc = ops.ref.gdn_prep(u, ctx.doc, layer.conv_weight, hk, hv, dk, dv, hist, hist_doc)
-    k2 = steps.second_key(x, k1, ctx.is_doc_start, None if state is None else state.k_prev)
+    if state is not None:
+        if state.conv_input.shape[-1] != u.shape[-1]:
+            raise ValueError(f"this GDN cache holds {state.conv_input.shape[-1]} conv channels; a layer with a derived second step carries {u.shape[-1]}")
+        if steps.key == "prev" and state.k_prev is None:
+            raise ValueError("this GDN cache holds no previous key: it was not written by a layer with gdn.dprod.key 'prev'")
+    past = (None, None) if state is None else (state.conv_input, state.conv_doc)
+    q, k1, v1, conv_input, conv_doc = ops.ref.gdn_prep(u, ctx.doc, layer.conv_weight, n_k, n_v, d_k, d_v, *past)
+    k2 = steps.second_key(x, k1, ctx.is_doc_start, state.k_prev if state is not None else None)
     g, beta1 = ops.ref.gdn_gates(layer.in_proj_a(x), layer.in_proj_b(x), layer.A_log, layer.dt_bias)
-    beta2 = 2 * torch.sigmoid(steps.in_proj_b(x))
-    rep = hv // hk
-    dt = ops.ref.work_dtype(q)
-    k = torch.stack([k1, k2], dim=2).repeat_interleave(rep, dim=3).to(dt)
-    v = torch.stack([v1, v1], dim=2).to(dt)
-    beta = torch.stack([2 * beta1, beta2], dim=2).to(dt)
-    qr, g = q.repeat_interleave(rep, dim=2).to(dt), g.to(dt)
-    S0 = x.new_zeros(B, hv, dk, dv, dtype=dt) if state is None else state.S.to(dt)
-    if cfg.kernel != "recurrence" and L > 1:
-        qi, ki, vi, gi, bi, si = interleave(qr, k, v, g, beta, ctx.is_doc_start)
-        oi, S = ops.ref.chunked_delta_rule(qi, ki, vi, gi, bi, si, S0, cfg.chunk_size)
-        o = last_substep(oi, 2)
+    work = ops.ref.work_dtype(q)
+    group = n_v // n_k
+    keys = torch.stack((k1, k2), dim=2).repeat_interleave(group, dim=3).to(work)
+    values = torch.stack((v1, v1), dim=2).to(work)                                      # one value, two addresses
+    betas = torch.stack((2 * beta1, 2 * torch.sigmoid(steps.in_proj_b(x))), dim=2).to(work)
+    query, decay = q.repeat_interleave(group, dim=2).to(work), g.to(work)
+    S0 = state.S.to(work) if state is not None else x.new_zeros(rows, n_v, d_k, d_v, dtype=work)
+    if g_cfg.kernel == "recurrence" or length == 1:
+        o, S = dprod_recurrence(query, keys, values, decay, betas, ctx.is_doc_start, S0)
     else:
-        o, S = dprod_recurrence(qr, k, v, g, beta, ctx.is_doc_start, S0)
+        o_rows, S = ops.ref.chunked_delta_rule(*interleave(query, keys, values, decay, betas, ctx.is_doc_start), S0, g_cfg.chunk_size)
+        o = last_substep(o_rows, 2)
     return o, conv_input, conv_doc, S, (k1[:, -1].clone() if steps.key == "prev" else None)

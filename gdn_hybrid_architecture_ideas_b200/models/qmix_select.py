@@ -19,34 +19,33 @@ import torch
 from .. import ops
 
 KEEP = 2
+_KEY = "model.encoder.gdn_qmix_select_step"
 
 
 def check_config(cfg) -> None:
     """cfg: ModelConfig. ValueError, by name, for a value that is not a non-negative int and for what the option is not built
     with: another write variant or write mix, MXFP8 / NVFP4 weights."""
-    e = cfg.encoder
-    s = e.gdn_qmix_select_step
-    if isinstance(s, bool) or not isinstance(s, int) or s < 0:
-        raise ValueError(f"model.encoder.gdn_qmix_select_step {s!r}: 0 (off) or the optimizer step >= 1 at whose start each layer's "
-                         f"{KEEP} sources are chosen")
-    if s == 0:
+    enc = cfg.encoder
+    step = enc.gdn_qmix_select_step
+    if type(step) is not int or step < 0:
+        raise ValueError(f"{_KEY} {step!r}: 0 (off) or the optimizer step >= 1 at whose start each layer's {KEEP} sources are chosen")
+    if step == 0:
         return
-    what = f"model.encoder.gdn_qmix_select_step {s!r}"
-    if e.gdn_write_variant != "qmix" or e.gdn_write_mix != "layer":
-        raise ValueError(f"{what} restricts the query mix of model.encoder.gdn_write_variant 'qmix' (with gdn_write_mix 'layer'), "
-                         f"not {e.gdn_write_variant!r} / {e.gdn_write_mix!r}")
-    if cfg.fp8.mode != "none" or cfg.nvfp4.mode != "none":
-        raise ValueError(f"{what} is not built together with model.fp8 / model.nvfp4: nothing tests the pair")
+    if (enc.gdn_write_variant, enc.gdn_write_mix) != ("qmix", "layer"):
+        raise ValueError(f"{_KEY} {step!r} restricts the query mix of model.encoder.gdn_write_variant 'qmix' (with gdn_write_mix 'layer'), "
+                         f"not {enc.gdn_write_variant!r} / {enc.gdn_write_mix!r}")
+    if "none" != cfg.fp8.mode or "none" != cfg.nvfp4.mode:
+        raise ValueError(f"{_KEY} {step!r} is not built together with model.fp8 / model.nvfp4: nothing tests the pair")
 
 
 def pair_sources(sources: list, keep: torch.Tensor) -> list:
     """The two sources `keep` names, gathered through the index buffer (a fixed shape: no host read, no mask); the gradient
     of the gather writes zeros to the sources left out."""
-    dt = sources[0].dtype
-    for s in sources[1:]:
-        dt = torch.promote_types(dt, s.dtype)
-    pair = torch.stack([s.to(dt) for s in sources]).index_select(0, keep)
-    return [pair[0], pair[1]]
+    wide = sources[0].dtype
+    for other in sources[1:]:
+        wide = torch.promote_types(wide, other.dtype)
+    first, second = torch.stack([t.to(wide) for t in sources], dim=0).index_select(0, keep).unbind(0)
+    return [first, second]
 
 
 def depth_mix_pair(sources: list, reader, keep: torch.Tensor) -> torch.Tensor:
@@ -54,55 +53,59 @@ def depth_mix_pair(sources: list, reader, keep: torch.Tensor) -> torch.Tensor:
     pseudo-query and key norm), in the first source's dtype."""
     if getattr(reader, "heads", 1) != 1:
         raise ValueError("the static pair is built for a pseudo-query with one head")
-    a, b = pair_sources(sources, keep)
-    return ops.depth_mix([a, b], reader.query, reader.key_norm.weight, reader.key_norm.eps).to(sources[0].dtype)
+    mixed = ops.depth_mix(pair_sources(sources, keep), reader.query, reader.key_norm.weight, reader.key_norm.eps)
+    return mixed.to(sources[0].dtype)
 
 
-def _weights(sources: list, reader) -> torch.Tensor:
-    """(B, L, n) softmax weights of `reader` over `sources`, >= float32."""
-    _, alpha = ops.ref.depth_mix(sources, reader.query, reader.key_norm.weight, reader.key_norm.eps, return_weights=True)
-    return alpha
+def _token_weight_sums(sources: list, reader) -> torch.Tensor:
+    """(n,) float64: the reader's softmax weights over `sources` (formed in >= float32), summed over every token."""
+    weights = ops.ref.depth_mix(sources, reader.query, reader.key_norm.weight, reader.key_norm.eps, return_weights=True)[1]
+    return weights.to(torch.float64).flatten(0, -2).sum(0)
 
 
 @torch.no_grad()
 def depth_weight_sums(sources: list, reader, keep: torch.Tensor | None = None) -> tuple[torch.Tensor, int]:
     """(sum over the tokens of the reader's weights, (n,) float64; the number of tokens). keep None: the softmax over all n
-    sources; else over the two it names, zero on the others. Each token's weights are formed in >= float32 and summed in
-    float64."""
-    srcs = [s.detach() for s in sources]
-    if keep is None:
-        sums = _weights(srcs, reader).double().sum(dim=(0, 1))
-    else:
-        alpha = _weights(pair_sources(srcs, keep), reader)
-        sums = torch.zeros(len(srcs), dtype=torch.float64, device=alpha.device).index_copy(0, keep, alpha.double().sum(dim=(0, 1)))
-    return sums, int(srcs[0].shape[0] * srcs[0].shape[1])
+    sources; else over the two it names, zero on the others."""
+    held = [t.detach() for t in sources]
+    tokens = held[0].shape[0] * held[0].shape[1]
+    if keep is not None:
+        two = _token_weight_sums(pair_sources(held, keep), reader)
+        return torch.zeros(len(held), dtype=two.dtype, device=two.device).index_copy(0, keep, two), int(tokens)
+    return _token_weight_sums(held, reader), int(tokens)
+
+
+def _query_mix_of(layer):
+    """The layer's arms when it has a query mix of its own under the qmix variant, else None."""
+    arms = getattr(layer, "gdn_arms", None)
+    return arms if arms is not None and arms.variant == "qmix" and arms.qmix_query is not None else None
 
 
 def record_query_weights(rec: dict, i: int, layer, sources: list | None) -> None:
     """Before layer i of a forward whose encoder has `qmix_record` set: rec[i] = (token-sums of the layer's query-mix
     weights as it is about to use them, tokens). A layer without a query mix of its own adds nothing."""
-    arms = getattr(layer, "gdn_arms", None)
-    if arms is None or arms.variant != "qmix" or arms.qmix_query is None or sources is None:
-        return
-    rec[i] = depth_weight_sums(sources, arms.qmix_query, arms.qmix_keep if arms.qmix_static else None)
+    arms = _query_mix_of(layer)
+    if arms is not None and sources is not None:
+        rec[i] = depth_weight_sums(sources, arms.qmix_query, arms.qmix_keep if arms.qmix_static else None)
 
 
 def read_query_weights(rec: dict) -> dict:
     """{layer: (token-mean weights as Python floats, tokens)}: the sums over the tokens, divided in float64; one host read."""
-    if not rec:
+    order = sorted(rec)
+    if not order:
         return {}
-    layers = sorted(rec)
-    flat = torch.cat([rec[i][0] for i in layers]).cpu()
-    out, at = {}, 0
-    for i in layers:
-        sums, tokens = rec[i]
-        out[i] = ((flat[at:at + sums.numel()] / tokens).tolist(), tokens)
-        at += sums.numel()
-    return out
+    host = torch.cat([rec[i][0] / rec[i][1] for i in order]).tolist()          # float64 sums / int tokens, one copy to the host
+    sizes = [rec[i][0].numel() for i in order]
+    starts = [sum(sizes[:k]) for k in range(len(order))]
+    return {i: (host[a:a + n], rec[i][1]) for i, a, n in zip(order, starts, sizes)}
 
 
-def _arms(encoder):
-    return [(i, getattr(layer, "gdn_arms", None)) for i, layer in enumerate(encoder.layers)]
+def _waiting(encoder):
+    """(index, arms) of the layers that hold the buffer and have not chosen, in stack order."""
+    for i, layer in enumerate(encoder.layers):
+        arms = getattr(layer, "gdn_arms", None)
+        if arms is not None and hasattr(arms, "qmix_keep") and not arms.qmix_static:
+            yield i, arms
 
 
 def sync_static(encoder) -> None:
@@ -110,14 +113,21 @@ def sync_static(encoder) -> None:
     form follows its buffer, as the post-load hook would set it."""
     from .gdn import _sync_qmix_static
 
-    for _, arms in _arms(encoder):
+    for layer in encoder.layers:
+        arms = getattr(layer, "gdn_arms", None)
         if arms is not None and hasattr(arms, "qmix_keep"):
             _sync_qmix_static(arms, None)
 
 
 def pending(encoder) -> bool:
     """Whether a layer has the buffer and has not chosen yet."""
-    return any(a is not None and hasattr(a, "qmix_keep") and not a.qmix_static for _, a in _arms(encoder))
+    return next(_waiting(encoder), None) is not None
+
+
+def top_pair(weights: list) -> list:
+    """The KEEP largest entries' indices, ties to the lower index, ascending."""
+    ranked = sorted(range(len(weights)), key=lambda j: (-weights[j], j))
+    return sorted(ranked[:KEEP])
 
 
 @torch.no_grad()
@@ -125,35 +135,28 @@ def select_pairs(encoder, rec: dict) -> dict:
     """The choice: every layer with the buffer that has not chosen takes the KEEP sources with the largest token-mean weight
     in `rec` (a record of the full softmax), ties to the lower index, written ascending into its buffer. Returns
     {layer: {"pair", "weights" (every source's token-mean), "tokens"}} for the layers chosen now, in stack order."""
-    means = read_query_weights(rec)
-    out = {}
-    for i, arms in _arms(encoder):
-        if arms is None or not hasattr(arms, "qmix_keep") or arms.qmix_static:
-            continue
+    means, chosen = read_query_weights(rec), {}
+    for i, arms in list(_waiting(encoder)):
         if i not in means:
             raise ValueError(f"layer {i} has no recorded query-mix weights: the choice follows a forward with encoder.qmix_record set")
-        w, tokens = means[i]
-        if len(w) != arms.n_sources:
-            raise ValueError(f"layer {i}: {len(w)} recorded weights for its {arms.n_sources} sources")
-        pair = sorted(sorted(range(len(w)), key=lambda s: (-w[s], s))[:KEEP])
-        arms.qmix_keep.copy_(torch.tensor(pair, dtype=torch.long, device=arms.qmix_keep.device))
+        weights, tokens = means[i]
+        if len(weights) != arms.n_sources:
+            raise ValueError(f"layer {i}: {len(weights)} recorded weights for its {arms.n_sources} sources")
+        pair = top_pair(weights)
+        arms.qmix_keep.copy_(torch.as_tensor(pair, dtype=arms.qmix_keep.dtype, device=arms.qmix_keep.device))
         arms.qmix_static = True
-        out[i] = {"pair": pair, "weights": w, "tokens": tokens}
-    return out
+        chosen[i] = dict(pair=pair, weights=weights, tokens=tokens)
+    return chosen
 
 
 def weights_metrics(encoder, rec: dict) -> dict:
     """The log of a recorded forward: layers, their source counts, every source's token-mean weight as the layer used it
     (after the choice: the pair's, zero on the others), the tokens, and each layer's pair (None before the choice)."""
     means = read_query_weights(rec)
-    layers = sorted(means)
-    chosen = []
-    for i in layers:
-        arms = encoder.layers[i].gdn_arms
-        chosen.append(arms.chosen_sources() if hasattr(arms, "qmix_keep") else None)
-    return {"layers": layers, "n_sources": [len(means[i][0]) for i in layers],
-            "weights": [[round(x, 8) for x in means[i][0]] for i in layers],
-            "tokens": means[layers[0]][1] if layers else 0, "chosen": chosen}
+    rows = sorted(means.items())
+    pairs = [encoder.layers[i].gdn_arms.chosen_sources() if hasattr(encoder.layers[i].gdn_arms, "qmix_keep") else None for i, _ in rows]
+    return dict(layers=[i for i, _ in rows], n_sources=[len(w) for _, (w, _) in rows], weights=[[round(x, 8) for x in w] for _, (w, _) in rows],
+                tokens=rows[0][1][1] if rows else 0, chosen=pairs)
 
 
 def choose(encoder, forward) -> dict:
@@ -164,7 +167,7 @@ def choose(encoder, forward) -> dict:
         forward()
     finally:
         rec, encoder.qmix_record = encoder.qmix_record, None
-    chosen = select_pairs(encoder, rec)
-    layers = list(chosen)
-    return {"layers": layers, "pair": [chosen[i]["pair"] for i in layers], "weights": [chosen[i]["weights"] for i in layers],
-            "tokens": chosen[layers[0]]["tokens"] if layers else 0}
+    picked = select_pairs(encoder, rec)
+    order = sorted(picked)
+    return dict(layers=order, pair=[picked[i]["pair"] for i in order], weights=[picked[i]["weights"] for i in order],
+                tokens=picked[order[0]]["tokens"] if order else 0)
