@@ -7,7 +7,7 @@
     c_t   = softmax over V u {<copy>} at <copy>, the <copy> logit z_copy = w_copy . h_t (a vector of its own, never a token)
     lambda_t = c_t (1 - s_t);    p(v) = (1 - lambda_t) p_LM(v) + lambda_t p_CP(v);   loss: cross entropy on p
 
-Everything is formed in log space and nothing of size T x T x V exists: the training terms (`terms`) are
+Everything is formed in log space and nothing of size T x T x V exists: the training terms (`terms`, a `Pointer`) are
 (log s, log(1 - s), log p_CP(target)) by blocks of queries against the keys up to the block's end, masks by comparisons
 and `where` (fixed shapes); a query without a matching key gives log p_CP = -inf with a gradient of exactly zero. The
 mixture at the target is `mixture_log_prob`. At inference `forward_logits` returns log p over V (p_CP over V by a
@@ -30,108 +30,125 @@ from __future__ import annotations
 
 import math
 import os
-from dataclasses import dataclass
+from dataclasses import dataclass, fields
+from functools import partial
+from typing import NamedTuple
 
 import torch
 import torch.nn as nn
-import torch.utils.checkpoint as ckpt
+import torch.nn.functional as F
+from torch.utils.checkpoint import checkpoint as recompute
 
 OWN_SEED_OFFSET = 0xC0_2610_19247        # shared with the reference: equal starts under equal seeds
-QK_NORM_EPS = float(torch.finfo(torch.float32).eps)
-INITS, SCORES, TEMPERATURES = ("spec", "reference"), ("mixture", "lm"), ("none", "ssmax")
+NORM_EPS = 2.0 ** -23
+BASE_FORM = dict(pointer_input="final", n_heads=1, combine="and", trunk_copy="none", train_mode="mixture", window=0, kernel="reference")
+CHOICES = dict(init=("spec", "reference"), score=("mixture", "lm"), temperature=("none", "ssmax"))
 ENV_SCORE = "GHB_CP_SCORE"               # a scoring process's override of model.cp_head.score
-PARAMETERS = ("cp_head.w_q", "cp_head.w_k", "cp_head.k_sink", "cp_head.w_copy", "cp_head.qk_gain")
 
 
 def check_config(cfg) -> None:
-    c = cfg.cp_head
-    if not c.enabled:
+    head = cfg.cp_head
+    if not head.enabled:
         return
-    fixed = {"pointer_input": "final", "n_heads": 1, "combine": "and", "trunk_copy": "none", "train_mode": "mixture", "window": 0, "kernel": "reference"}
-    moved = [f"{k} {getattr(c, k)!r}" for k, v in fixed.items() if getattr(c, k) != v]
-    if moved:
-        raise ValueError(f"model.cp_head {', '.join(moved)}: the head is built in its base form (pointer_input 'final', one pointer head, "
+    off_base = [f"{name} {getattr(head, name)!r}" for name, base in BASE_FORM.items() if getattr(head, name) != base]
+    if off_base:
+        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built in its base form (pointer_input 'final', one pointer head, "
                          "train_mode 'mixture', no band, no trunk copy, kernel 'reference')")
-    if type(c.d_c) is not int or c.d_c < 1 or type(c.query_chunk) is not int or c.query_chunk < 1:
-        raise ValueError(f"model.cp_head.d_c {c.d_c!r} / query_chunk {c.query_chunk!r}: integers >= 1")
-    if c.init not in INITS or c.score not in SCORES or c.temperature not in TEMPERATURES:
-        raise ValueError(f"model.cp_head.init {c.init!r} / score {c.score!r} / temperature {c.temperature!r}: of {INITS} / {SCORES} / {TEMPERATURES}")
-    e = cfg.encoder
-    refused = [(bool(cfg.loop.recur_layers) or cfg.loop.pass2_gate != "none", "a looped middle or a second pass (one pass only)"),
-               (e.attn_res not in ("none", "block_entry"), f"encoder.attn_res {e.attn_res!r}"),
-               (e.gdn_write_variant != "none" or bool(e.gdn_ccr_spacing), "encoder.gdn_write_variant / gdn_ccr_spacing (nothing tests the pair)"),
-               (cfg.fp8.mode != "none" or cfg.nvfp4.mode != "none", "model.fp8 / model.nvfp4"), (bool(cfg.mtp.enabled), "model.mtp")]
-    bad = [why for cond, why in refused if cond]
-    if bad:
-        raise ValueError(f"model.cp_head is not built with: {'; '.join(bad)}")
+    for name in ("d_c", "query_chunk"):
+        if type(getattr(head, name)) is not int or getattr(head, name) < 1:
+            raise ValueError(f"model.cp_head.{name} {getattr(head, name)!r}: an integer >= 1")
+    for name, allowed in CHOICES.items():
+        if getattr(head, name) not in allowed:
+            raise ValueError(f"model.cp_head.{name} {getattr(head, name)!r}: one of {allowed}")
+    enc, clashes = cfg.encoder, []
+    if cfg.loop.recur_layers or cfg.loop.pass2_gate != "none":
+        clashes.append("a looped middle or a second pass (one pass only)")
+    if enc.attn_res not in ("none", "block_entry"):
+        clashes.append(f"encoder.attn_res {enc.attn_res!r}")
+    if enc.gdn_write_variant != "none" or enc.gdn_ccr_spacing:
+        clashes.append("encoder.gdn_write_variant / gdn_ccr_spacing (nothing tests the pair)")
+    if (cfg.fp8.mode, cfg.nvfp4.mode) != ("none", "none"):
+        clashes.append("model.fp8 / model.nvfp4")
+    if cfg.mtp.enabled:
+        clashes.append("model.mtp")
+    if clashes:
+        raise ValueError(f"model.cp_head is not built with: {'; '.join(clashes)}")
 
 
-def work_dtype(x: torch.Tensor) -> torch.dtype:
+def _wide(x: torch.Tensor) -> torch.dtype:
+    """float32 for the 16-bit types, the tensor's own type above."""
     return torch.promote_types(x.dtype, torch.float32)
+
+
+def _no_autocast(x: torch.Tensor):
+    return torch.autocast(x.device.type, enabled=False)
 
 
 class CopyPasteHead(nn.Module):
     def __init__(self, d_model: int, cfg, ref_len: int = 8192):
         super().__init__()
-        self.cfg, self.ref_len = cfg, int(ref_len)
-        self.w_q = nn.Parameter(torch.empty(cfg.d_c, d_model))
-        self.w_k = nn.Parameter(torch.empty(cfg.d_c, d_model))
-        self.k_sink = nn.Parameter(torch.empty(cfg.d_c))
-        self.w_copy = nn.Parameter(torch.empty(d_model))
+        self.cfg, self.ref_len, self.scale = cfg, int(ref_len), cfg.d_c ** -0.5
+        for name, shape in (("w_q", (cfg.d_c, d_model)), ("w_k", (cfg.d_c, d_model)), ("k_sink", (cfg.d_c,)), ("w_copy", (d_model,))):
+            self.register_parameter(name, nn.Parameter(torch.empty(shape)))
         if cfg.qk_norm:
             self.qk_gain = nn.Parameter(torch.zeros(1))
-        self.scale = 1.0 / math.sqrt(cfg.d_c)
 
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float, init: str = "spec") -> None:
         """w_q, w_k, k_sink, w_copy ~ N(0, std) in that order; `reference` then redraws w_q / w_k as one uniform bank and
         the sink as N(0, 1 / d_c), w_copy keeping its draw."""
-        for p in (self.w_q, self.w_k, self.k_sink, self.w_copy):
-            p.copy_(torch.randn(p.shape, generator=g, dtype=torch.float32).to(p.dtype) * std)
+        draw = lambda shape: torch.randn(shape, generator=g, dtype=torch.float32)                  # noqa: E731
+        for name in ("w_q", "w_k", "k_sink", "w_copy"):
+            t = getattr(self, name)
+            t.copy_((draw(t.shape) * std).to(t.dtype) if t.dtype != torch.float32 else draw(t.shape) * std)
         if init == "reference":
             d_c, d = self.w_q.shape
-            bound = (3 ** 0.5) * d ** -0.5
-            bank = torch.empty(2, d_c, d, dtype=torch.float32).uniform_(-bound, bound, generator=g)
-            self.w_q.copy_(bank[0].to(self.w_q.dtype))
-            self.w_k.copy_(bank[1].to(self.w_k.dtype))
-            self.k_sink.copy_((torch.randn(d_c, generator=g, dtype=torch.float32) * d_c ** -0.5).to(self.k_sink.dtype))
+            limit = 3 ** 0.5 * d ** -0.5                           # this product, not sqrt(3 / d): equal bits with the reference's bank
+            both = torch.empty(2, d_c, d, dtype=torch.float32).uniform_(-limit, limit, generator=g)
+            self.w_q.copy_(both[0])
+            self.w_k.copy_(both[1])
+            self.k_sink.copy_(draw(d_c) * d_c ** -0.5)
         if self.cfg.qk_norm:
             self.qk_gain.zero_()
 
-    def _proj(self, h, w):
-        dt = work_dtype(h)
-        with torch.autocast(h.device.type, enabled=False):
-            return torch.nn.functional.linear(h.to(dt), w.to(dt))
-
-    @staticmethod
-    def _norm(x):
-        with torch.autocast(x.device.type, enabled=False):
-            return torch.nn.functional.rms_norm(x, (x.shape[-1],), eps=QK_NORM_EPS)
+    def _project(self, h, w, normed: bool):
+        wide = _wide(h)
+        with _no_autocast(h):
+            y = F.linear(h.to(wide), w.to(wide))
+            return F.rms_norm(y, y.shape[-1:], eps=NORM_EPS) if normed else y
 
     def queries(self, h):
-        q = self._proj(h, self.w_q)
-        return self._norm(q) * (1.0 + self.qk_gain.to(q.dtype)) if self.cfg.qk_norm else q
+        q = self._project(h, self.w_q, self.cfg.qk_norm)
+        return q * (1.0 + self.qk_gain.to(q.dtype)) if self.cfg.qk_norm else q
 
     def keys(self, h):
-        k = self._proj(h, self.w_k)
-        return self._norm(k) if self.cfg.qk_norm else k
+        return self._project(h, self.w_k, self.cfg.qk_norm)
 
     def copy_logit(self, h):
-        return self._proj(h, self.w_copy[None, :]).squeeze(-1)
+        return self._project(h, self.w_copy.unsqueeze(0), False)[..., 0]
+
+    def rule(self) -> "LengthRule":
+        return LengthRule(self.cfg.temperature == "ssmax", bool(self.cfg.sink_count), self.ref_len, self.scale)
 
 
 def attach(model) -> None:
-    cfg = model.cfg
-    head = CopyPasteHead(cfg.d_model, cfg.cp_head, cfg.encoder.attention.temperature_ref_len)
-    head.reset_own(torch.Generator().manual_seed((torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63)), cfg.init_std, cfg.cp_head.init)
-    model.cp_head = head
+    """Registers the head on the model, drawn from a generator of its own."""
+    mc = model.cfg
+    seed = (torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63)
+    model.cp_head = CopyPasteHead(mc.d_model, mc.cp_head, mc.encoder.attention.temperature_ref_len)
+    model.cp_head.reset_own(torch.Generator().manual_seed(seed), mc.init_std, mc.cp_head.init)
 
 
 def score_mode(model) -> str:
     return os.environ.get(ENV_SCORE) or model.cfg.cp_head.score
 
 
-# ------------------------------------------------------------------------------------------------------- keys and terms
+def _lm_only(model) -> bool:
+    head = getattr(model, "cp_head", None)
+    return head is None or head.cfg.force_lambda_zero or score_mode(model) == "lm"
+
+
+# ------------------------------------------------------------------------------------------------------- the pointer
 
 @dataclass
 class CopyKeys:
@@ -142,8 +159,11 @@ class CopyKeys:
     doc: torch.Tensor
     idx: torch.Tensor
 
-    def extend(self, other: "CopyKeys") -> "CopyKeys":
-        return CopyKeys(*(torch.cat([getattr(self, n), getattr(other, n)], dim=1) for n in ("k", "tok", "doc", "idx")))
+    def upto(self, S: int) -> "CopyKeys":
+        return CopyKeys(*(getattr(self, f.name)[:, :S] for f in fields(self)))
+
+    def extend(self, more: "CopyKeys") -> "CopyKeys":
+        return CopyKeys(*(torch.cat([getattr(self, f.name), getattr(more, f.name)], dim=1) for f in fields(self)))
 
 
 @dataclass
@@ -151,200 +171,198 @@ class CopyCache:
     keys: CopyKeys | None = None
 
 
-def _neg_inf(like):
-    return torch.full((), float("-inf"), dtype=like.dtype, device=like.device)
+class Pointer(NamedTuple):
+    """log s (the sink's share), log(1 - s), log p_CP(target); each (B, n)."""
+
+    log_sink: torch.Tensor
+    log_ctx: torch.Tensor
+    log_copy: torch.Tensor
+
+
+class LengthRule(NamedTuple):
+    ssmax: bool
+    sink_count: bool
+    ref_len: int
+    scale: float
+
+
+class Scores(NamedTuple):
+    e: torch.Tensor            # (B, C, S) scaled scores, -inf outside a query's context
+    sink: torch.Tensor         # (B, C)
+    norm_ctx: torch.Tensor     # LSE over the context
+    norm_all: torch.Tensor     # LSE over the context and the sink
+
+    def pointer(self, log_copy) -> Pointer:
+        return Pointer(self.sink - self.norm_all, self.norm_ctx - self.norm_all, log_copy)
 
 
 def context_mask(k_idx, k_doc, q_idx, q_doc):
     """(B, C, S): key s is a context position of query i (not later, same document)."""
-    return (k_idx[:, None, :] <= q_idx[:, :, None]) & (k_doc[:, None, :] == q_doc[:, :, None])
+    return (k_doc.unsqueeze(1) == q_doc.unsqueeze(2)).logical_and_(k_idx.unsqueeze(1) <= q_idx.unsqueeze(2))
 
 
-def length_terms(head, q, n):
-    """(q for the scores, what is added to the sink's logit or None) under the length rule; n (B, C) context counts."""
-    c = head.cfg
-    if c.temperature == "none" and not c.sink_count:
-        return q, None
-    n = n.clamp_min(1).to(q.dtype)
-    add = torch.log(n / head.ref_len) if c.sink_count else None
-    if c.temperature == "ssmax":
-        q = q * (1.0 + torch.log(n / head.ref_len) / math.log(head.ref_len))[..., None]
-    return q, add
+def attend(rule: LengthRule, q, k, k_sink, visible) -> Scores:
+    """The pointer's scores of C queries over S keys. The length rule needs each query's context count, which is the
+    visible mask's row sum: q is scaled (ssmax) and the sink's logit raised (sink_count) before anything is normalised."""
+    sink_shift = None
+    if rule.ssmax or rule.sink_count:
+        log_ratio = torch.log(visible.sum(-1).clamp_min(1).to(q.dtype) / rule.ref_len)
+        if rule.ssmax:
+            q = q * (1.0 + log_ratio / math.log(rule.ref_len)).unsqueeze(-1)
+        sink_shift = log_ratio if rule.sink_count else None
+    e = (q @ k.mT * rule.scale).masked_fill(~visible, float("-inf"))
+    sink = (q @ k_sink) * rule.scale
+    if sink_shift is not None:
+        sink = sink + sink_shift
+    norm_ctx = e.logsumexp(-1)
+    return Scores(e, sink, norm_ctx, torch.logaddexp(sink, norm_ctx))
 
 
-def block_terms(q, k, k_sink, k_tok, k_doc, k_idx, q_idx, q_doc, q_tgt, scale: float, sink_add=None):
-    """(log s, log(1 - s), log p_CP(target)), each (B, C), for C queries over S keys."""
-    neg = _neg_inf(q)
-    s = torch.matmul(q, k.transpose(1, 2)) * scale
-    e_sink = torch.matmul(q, k_sink) * scale
-    if sink_add is not None:
-        e_sink = e_sink + sink_add
-    ctx = context_mask(k_idx, k_doc, q_idx, q_doc)
-    match = ctx & (k_tok[:, None, :] == q_tgt[:, :, None])
-    lse_ctx = torch.logsumexp(torch.where(ctx, s, neg), dim=-1)
-    has = match.any(dim=-1)
-    fill = torch.where(has, neg, torch.zeros((), dtype=s.dtype, device=s.device))[..., None]      # a row without a match reads zeros: finite, gradient 0
-    lse_match = torch.logsumexp(torch.where(match, s, fill), dim=-1)
-    lse_all = torch.logaddexp(e_sink, lse_ctx)
-    return e_sink - lse_all, lse_ctx - lse_all, torch.where(has, lse_match - lse_ctx, neg)
+def _train_block(rule, q, k, k_sink, k_tok, k_doc, k_idx, q_idx, q_doc, q_tgt):
+    """One block of queries: the three terms as a plain tuple (what a recomputed block returns)."""
+    sc = attend(rule, q, k, k_sink, context_mask(k_idx, k_doc, q_idx, q_doc))
+    hit = (k_tok.unsqueeze(1) == q_tgt.unsqueeze(2)) & torch.isfinite(sc.e)
+    none = ~hit.any(-1)
+    # a row without a matching key is read as zeros: its LSE is finite, its gradient exactly zero, its result -inf below
+    picked = sc.e.masked_fill(~hit, float("-inf")).masked_fill(none.unsqueeze(-1), 0.0)
+    log_copy = (picked.logsumexp(-1) - sc.norm_ctx).masked_fill(none, float("-inf"))
+    return tuple(sc.pointer(log_copy))
 
 
 def terms(head, hidden, tokens, targets, doc_ids, chunk: int | None = None, checkpoint: bool = False, keys: CopyKeys | None = None,
-          q_idx: torch.Tensor | None = None):
-    """(log s, log(1 - s), log p_CP(target)), each (B, L), at every position of a forward. keys: the key side (default this
-    forward's own positions at indices 0 .. L - 1: a block of queries then reads the keys up to its own end only)."""
+          q_idx: torch.Tensor | None = None) -> Pointer:
+    """The pointer's terms at every position of a forward. keys: the key side (default this forward's own positions at
+    indices 0 .. L - 1: a block of queries then reads the keys up to its own end only)."""
     B, L = tokens.shape
+    step = chunk or head.cfg.query_chunk
     q = head.queries(hidden)
-    own = keys is None
-    idx = torch.arange(L, device=tokens.device).expand(B, L)
-    if own:
-        keys = CopyKeys(head.keys(hidden), tokens, doc_ids, idx)
-    q_idx = idx if q_idx is None else q_idx
-    C = chunk or head.cfg.query_chunk
-    sink_add = None
-    if head.cfg.temperature != "none" or head.cfg.sink_count:
-        if own:
-            from .sequence import sequence_context
-
-            n = sequence_context(doc_ids, None)[0].pos + 1
-        else:
-            n = torch.cat([context_mask(keys.idx, keys.doc, q_idx[:, a:a + C], doc_ids[:, a:a + C]).sum(-1) for a in range(0, L, C)], 1)
-        q, sink_add = length_terms(head, q, n)
-    k_sink = head.k_sink.to(q.dtype)
-    parts = []
-    for a in range(0, L, C):
-        S = min(a + C, L) if own else keys.k.shape[1]
-        args = (q[:, a:a + C], keys.k[:, :S], k_sink, keys.tok[:, :S], keys.doc[:, :S], keys.idx[:, :S], q_idx[:, a:a + C], doc_ids[:, a:a + C],
-                targets[:, a:a + C], head.scale, None if sink_add is None else sink_add[:, a:a + C])
-        parts.append(ckpt.checkpoint(block_terms, *args, use_reentrant=False) if checkpoint and torch.is_grad_enabled() else block_terms(*args))
-    return tuple(torch.cat([p[i] for p in parts], dim=1) for i in range(3))
+    causal_cut = keys is None
+    if causal_cut:
+        at = torch.arange(L, device=tokens.device).expand(B, L)
+        keys, q_idx = CopyKeys(head.keys(hidden), tokens, doc_ids, at), at
+    sink_key = head.k_sink.to(q.dtype)
+    block = partial(_train_block, head.rule())
+    if checkpoint and torch.is_grad_enabled():
+        block = partial(recompute, block, use_reentrant=False)
+    blocks = []
+    for lo in range(0, L, step):
+        hi = min(lo + step, L)
+        ks = keys.upto(hi) if causal_cut else keys
+        blocks.append(block(q[:, lo:hi], ks.k, sink_key, ks.tok, ks.doc, ks.idx, q_idx[:, lo:hi], doc_ids[:, lo:hi], targets[:, lo:hi]))
+    return Pointer(*(torch.cat(column, dim=1) for column in zip(*blocks)))
 
 
-def terms_naive(head, hidden, tokens, targets, doc_ids):
+def terms_naive(head, hidden, tokens, targets, doc_ids) -> Pointer:
     """The same three terms with every score of a row at once and the softmaxes taken explicitly (tests; small rows)."""
     B, L = tokens.shape
-    q, k = head.queries(hidden), head.keys(hidden)
-    idx = torch.arange(L, device=tokens.device).expand(B, L)
-    ctx = context_mask(idx, doc_ids, idx, doc_ids)
-    add = None
-    if head.cfg.temperature != "none" or head.cfg.sink_count:
-        q, add = length_terms(head, q, ctx.sum(-1))
-    e = torch.einsum("bqd,bkd->bqk", q, k) * head.scale
-    e_sink = (q @ head.k_sink.to(q.dtype)) * head.scale + (0 if add is None else add)
-    full = torch.cat([e_sink[..., None], e.masked_fill(~ctx, float("-inf"))], dim=-1).softmax(-1)
-    s = full[..., 0]
-    alpha = e.masked_fill(~ctx, float("-inf")).softmax(-1)
-    p_cp = (alpha * (tokens[:, None, :] == targets[:, :, None])).sum(-1)
-    return torch.log(s), torch.log1p(-s), torch.log(p_cp)
+    at = torch.arange(L, device=tokens.device).expand(B, L)
+    sc = attend(head.rule(), head.queries(hidden), head.keys(hidden), head.k_sink.to(_wide(hidden)), context_mask(at, doc_ids, at, doc_ids))
+    with_sink = torch.cat([sc.sink.unsqueeze(-1), sc.e], dim=-1).softmax(-1)
+    share = with_sink[..., 0]
+    p_copy = (sc.e.softmax(-1) * (tokens.unsqueeze(1) == targets.unsqueeze(2))).sum(-1)
+    return Pointer(share.log(), torch.log1p(-share), p_copy.log())
 
 
-def mixture_log_prob(lse_v, z_y, z_c, log_s, log_1ms, log_pcp):
-    """log p(y) from per-position LSE over V, the target's logit, the <copy> logit and the pointer's three terms."""
-    lse_all = torch.logaddexp(lse_v, z_c)
-    log_c, log_1mc = z_c - lse_all, lse_v - lse_all
-    log_lam = log_c + log_1ms
-    log_1mlam = torch.logaddexp(log_1mc, log_c + log_s)              # 1 - lambda = (1 - c) + c s
-    return torch.logaddexp(log_1mlam + z_y - lse_v, log_lam + log_pcp)
+# ------------------------------------------------------------------------------------------------------- the mixture
 
+@dataclass
+class Mixture:
+    """lambda = c (1 - s) in logs, with c the share of <copy> in softmax over V u {<copy>}."""
 
-def mixture_parts(lse_v, z_c, log_s, log_1ms):
-    """(log lambda, log(1 - lambda), log c)."""
-    lse_all = torch.logaddexp(lse_v, z_c)
-    log_c = z_c - lse_all
-    return log_c + log_1ms, torch.logaddexp(lse_v - lse_all, log_c + log_s), log_c
+    log_lam: torch.Tensor
+    log_keep: torch.Tensor          # log(1 - lambda) = log((1 - c) + c s)
+    log_c: torch.Tensor
+    lse_v: torch.Tensor
 
+    @classmethod
+    def of(cls, lse_v, z_copy, ptr: Pointer) -> "Mixture":
+        total = torch.logaddexp(lse_v, z_copy)
+        log_c = z_copy - total
+        return cls(log_c + ptr.log_ctx, torch.logaddexp(lse_v - total, log_c + ptr.log_sink), log_c, lse_v)
 
-# ---------------------------------------------------------------------------------------------------------- inference
+    def at_target(self, z_y, log_copy):
+        """log p(y) from the target's logit and log p_CP(y)."""
+        return torch.logaddexp(self.log_keep + (z_y - self.lse_v), self.log_lam + log_copy)
+
+    def over_vocab(self, logits, log_copy):
+        """log p over V from the logits and log p_CP over V, both (..., V)."""
+        return torch.logaddexp((self.log_keep - self.lse_v).unsqueeze(-1) + logits, self.log_lam.unsqueeze(-1) + log_copy)
+
 
 def logprobs_rows(head, hidden_q, q_idx, q_doc, keys: CopyKeys, weight_v, chunk: int | None = None):
-    """log p over V (B, P, V) at the queries, block by block ([B, C, S] alpha and [B, C, V] p_CP at a time)."""
-    B, P, _ = hidden_q.shape
-    V = weight_v.shape[0]
-    dt = work_dtype(hidden_q)
-    C = chunk or head.cfg.query_chunk
-    out = []
-    with torch.autocast(hidden_q.device.type, enabled=False):
-        W, k_sink = weight_v.to(dt), head.k_sink.to(dt)
-        for a in range(0, P, C):
-            h = hidden_q[:, a:a + C].to(dt)
-            qi, qd = q_idx[:, a:a + C], q_doc[:, a:a + C]
-            ctx = context_mask(keys.idx, keys.doc, qi, qd)
-            q, add = length_terms(head, head.queries(h), ctx.sum(-1))
-            e = torch.matmul(q, keys.k.to(dt).transpose(1, 2)) * head.scale
-            e_sink = torch.matmul(q, k_sink) * head.scale + (0 if add is None else add)
-            masked = torch.where(ctx, e, _neg_inf(e))
-            lse_ctx = torch.logsumexp(masked, dim=-1)
-            alpha = torch.exp(masked - lse_ctx[..., None])
-            lse_all = torch.logaddexp(e_sink, lse_ctx)
-            log_s, log_1ms = e_sink - lse_all, lse_ctx - lse_all
-            n = h.shape[1]
-            p_cp = torch.zeros(B, n, V, dtype=dt, device=h.device).scatter_add_(2, keys.tok[:, None, :].expand(B, n, keys.tok.shape[1]), alpha)
-            logits = torch.nn.functional.linear(h, W)
-            lse_v = torch.logsumexp(logits, dim=-1)
-            log_lam, log_1mlam, _ = mixture_parts(lse_v, head.copy_logit(h), log_s, log_1ms)
-            pos = p_cp > 0
-            log_pcp = torch.where(pos, torch.log(torch.where(pos, p_cp, torch.ones((), dtype=dt, device=h.device))), _neg_inf(p_cp))
-            out.append(torch.logaddexp((log_1mlam - lse_v)[..., None] + logits, log_lam[..., None] + log_pcp))
-    return torch.cat(out, dim=1)
+    """log p over V (B, P, V) at the queries, block by block ((B, C, S) alpha and (B, C, V) p_CP at a time)."""
+    wide = _wide(hidden_q)
+    step = chunk or head.cfg.query_chunk
+    rule, rows = head.rule(), []
+    with _no_autocast(hidden_q):
+        vocab, sink_key, k = weight_v.to(wide), head.k_sink.to(wide), keys.k.to(wide)
+        for lo in range(0, hidden_q.shape[1], step):
+            span = slice(lo, lo + step)
+            h = hidden_q[:, span].to(wide)
+            sc = attend(rule, head.queries(h), k, sink_key, context_mask(keys.idx, keys.doc, q_idx[:, span], q_doc[:, span]))
+            weights = (sc.e - sc.norm_ctx.unsqueeze(-1)).exp()                                      # alpha: softmax over the context alone
+            logits = F.linear(h, vocab)
+            p_copy = torch.zeros_like(logits).scatter_add_(2, keys.tok.unsqueeze(1).expand_as(weights), weights)
+            log_copy = p_copy.clamp_min(torch.finfo(wide).tiny).log().masked_fill(p_copy <= 0, float("-inf"))
+            mix = Mixture.of(logits.logsumexp(-1), head.copy_logit(h), sc.pointer(None))
+            rows.append(mix.over_vocab(logits, log_copy))
+    return torch.cat(rows, dim=1)
 
 
 def forward_logits(model, hidden, tokens, doc_ids, idx, cache: CopyCache | None):
     """(the model's `logits` of a forward: log p over V, or p_LM's logits under score 'lm'; the copy cache after the chunk)."""
-    head = model.cp_head
-    W = model.lm_head_weight()
-    dt = work_dtype(hidden)
-    with torch.autocast(hidden.device.type, enabled=False):
-        own = CopyKeys(head.keys(hidden.to(dt)), tokens, doc_ids, idx)
-        keys = own if cache is None or cache.keys is None else cache.keys.extend(own)
-        if score_mode(model) == "lm" or head.cfg.force_lambda_zero:
-            logits = torch.nn.functional.linear(hidden.to(dt), W.to(dt))
+    wide = _wide(hidden)
+    with _no_autocast(hidden):
+        keys = CopyKeys(model.cp_head.keys(hidden.to(wide)), tokens, doc_ids, idx)
+        if cache is not None and cache.keys is not None:
+            keys = cache.keys.extend(keys)                              # a chunk appends its own keys before its queries read
+        if _lm_only(model):
+            out = F.linear(hidden.to(wide), model.lm_head_weight().to(wide))
         else:
-            logits = logprobs_rows(head, hidden, idx, doc_ids, keys, W)
-    return logits, CopyCache(keys=keys)
+            out = logprobs_rows(model.cp_head, hidden, idx, doc_ids, keys, model.lm_head_weight())
+    return out, CopyCache(keys)
 
 
 def token_lse_zy(hidden, weight, targets, chunk: int = 1024):
     """(LSE over V, the target's logit) per position, by blocks of positions under activation checkpointing when gradients
     are on: the (block, V) logits exist only while a block's forward or backward runs."""
-    dt = work_dtype(hidden)
-    h, t = hidden.reshape(-1, hidden.shape[-1]), targets.reshape(-1)
+    wide = _wide(hidden)
+    flat_h, flat_t = hidden.flatten(0, -2), targets.flatten()
 
-    def block(hb, tb, W):
-        with torch.autocast(hb.device.type, enabled=False):
-            logits = torch.nn.functional.linear(hb.to(dt), W.to(dt))
-            return torch.logsumexp(logits, dim=-1), logits.gather(1, tb[:, None]).squeeze(1)
+    def rows(h, t, w):
+        with _no_autocast(h):
+            z = F.linear(h.to(wide), w.to(wide))
+            return z.logsumexp(-1), z.gather(1, t.unsqueeze(1))[:, 0]
 
-    parts = [ckpt.checkpoint(block, h[s:s + chunk], t[s:s + chunk], weight, use_reentrant=False) if torch.is_grad_enabled()
-             else block(h[s:s + chunk], t[s:s + chunk], weight) for s in range(0, h.shape[0], chunk)]
-    return torch.cat([p[0] for p in parts]).reshape(targets.shape), torch.cat([p[1] for p in parts]).reshape(targets.shape)
+    run = partial(recompute, rows, use_reentrant=False) if torch.is_grad_enabled() else rows
+    lse, z_y = zip(*(run(flat_h[lo:lo + chunk], flat_t[lo:lo + chunk], weight) for lo in range(0, flat_h.shape[0], chunk)))
+    return torch.cat(lse).view_as(targets), torch.cat(z_y).view_as(targets)
+
+
+def _mixture_at_targets(head, hidden, lse, tokens, targets, doc_ids, checkpoint: bool):
+    with _no_autocast(hidden):
+        ptr = Pointer(*(t.to(lse.dtype) for t in terms(head, hidden, tokens, targets, doc_ids, checkpoint=checkpoint)))
+        return Mixture.of(lse, head.copy_logit(hidden).to(lse.dtype), ptr), ptr
 
 
 def head_token_ce(model, hidden, targets, tokens, doc_ids, chunk: int = 1024):
     """(CE, LSE over V) per position of the model's next-token distribution from a forward's hidden states: p_LM's for a model
     without the head or under score 'lm', else the mixture's."""
-    head = getattr(model, "cp_head", None)
-    W = model.lm_head_weight()
-    lse, z_y = token_lse_zy(hidden, W, targets, chunk)
-    if head is None or score_mode(model) == "lm" or head.cfg.force_lambda_zero:
+    lse, z_y = token_lse_zy(hidden, model.lm_head_weight(), targets, chunk)
+    if _lm_only(model):
         return lse - z_y, lse
-    with torch.autocast(hidden.device.type, enabled=False):
-        log_s, log_1ms, log_pcp = (x.to(lse.dtype) for x in terms(head, hidden, tokens, targets, doc_ids))
-        return -mixture_log_prob(lse, z_y, head.copy_logit(hidden).to(lse.dtype), log_s, log_1ms, log_pcp), lse
+    mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, False)
+    return -mix.at_target(z_y, ptr.log_copy), lse
 
 
 def mixture_loss(model, hidden, targets, tokens, doc_ids, a, b, chunk: int = 1024):
     """The training loss sum(a CE + b LSE_V^2) of the mixture and the detached per-position (CE, lambda). a, b: per-position
     weights (0 where a target does not count)."""
-    head = model.cp_head
-    W = model.lm_head_weight()
-    lse, z_y = token_lse_zy(hidden, W, targets, chunk)
-    if head.cfg.force_lambda_zero:
+    lse, z_y = token_lse_zy(hidden, model.lm_head_weight(), targets, chunk)
+    if model.cp_head.cfg.force_lambda_zero:
         ce, lam = lse - z_y, torch.zeros_like(lse)
     else:
-        with torch.autocast(hidden.device.type, enabled=False):
-            log_s, log_1ms, log_pcp = (x.to(lse.dtype) for x in terms(head, hidden, tokens, targets, doc_ids, checkpoint=True))
-            z_c = head.copy_logit(hidden).to(lse.dtype)
-            ce = -mixture_log_prob(lse, z_y, z_c, log_s, log_1ms, log_pcp)
-            lam = torch.exp(mixture_parts(lse, z_c, log_s, log_1ms)[0]).detach()
-    loss = (a.to(ce.dtype) * ce + b.to(ce.dtype) * lse * lse).sum()
-    return loss, ce.detach(), lam
+        mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, True)
+        ce, lam = -mix.at_target(z_y, ptr.log_copy), mix.log_lam.detach().exp()
+    total = (ce * a.to(ce.dtype)).sum() + (lse.square() * b.to(ce.dtype)).sum()
+    return total, ce.detach(), lam
