@@ -9,34 +9,45 @@ them (reference: ced/model/attn_res.py:670-797). On CUDA the mix is one kernel t
 
 from __future__ import annotations
 
+from typing import Callable
+
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import ops
 from .norms import RMSNorm
 
+OWN_SEED_OFFSET = 0x1D3_2610_18809      # added to the run's seed for the address networks' generator (shared with the reference: equal starts)
 
-class DepthQuery(nn.Module):
-    """heads: the number of softmaxes over the sources, one per contiguous slice of d / heads channels
-    (`attn_res_heads`; a plain attribute, never in the state dict). 1 is the one-kernel read."""
 
-    def __init__(self, d: int, eps: float, heads: int = 1):
+class _Reader(nn.Module):
+    """What every reader has: the key norm's gain and the number of softmaxes over the sources, one per contiguous slice
+    of d / heads channels (`attn_res_heads`; a plain attribute, never in the state dict)."""
+
+    def __init__(self, width: int, norm_eps: float, n_heads: int):
         super().__init__()
-        if heads < 1 or d % heads:
-            raise ValueError(f"model.encoder.attn_res_heads {heads}: a divisor of d_model {d}")
-        self.query = nn.Parameter(torch.zeros(d))
-        self.key_norm = RMSNorm(d, eps)
-        self.heads = heads
+        if n_heads < 1 or width % n_heads:
+            raise ValueError(f"model.encoder.attn_res_heads {n_heads}: a divisor of d_model {width}")
+        self.heads = n_heads
+        self.key_norm = RMSNorm(width, norm_eps)
+
+    def mix(self, sources: list, query: torch.Tensor) -> torch.Tensor:
+        gain, eps = self.key_norm.weight, self.key_norm.eps
+        if self.heads == 1 and query.dim() == 1:
+            return ops.depth_mix(sources, query, gain, eps)                  # the one-kernel read
+        return ops.ref.depth_mix_heads(sources, query, gain, eps, self.heads)
+
+
+class DepthQuery(_Reader):
+    """The static reader: a (d,) pseudo-query, zeros at the start (a uniform read)."""
+
+    def __init__(self, width: int, norm_eps: float, n_heads: int = 1):
+        super().__init__(width, norm_eps, n_heads)
+        self.register_parameter("query", nn.Parameter(torch.zeros(width)))
 
     def forward(self, sources: list) -> torch.Tensor:
-        if len(sources) == 1:
-            return sources[0]
-        if self.heads > 1:
-            return ops.ref.depth_mix_heads(sources, self.query, self.key_norm.weight, self.key_norm.eps, self.heads)
-        return ops.depth_mix(sources, self.query, self.key_norm.weight, self.key_norm.eps)
-
-
-OWN_SEED_OFFSET = 0x1D3_2610_18809      # added to the run's seed for the address networks' generator (shared with the reference: equal starts)
+        return self.mix(sources, self.query) if len(sources) > 1 else sources[0]
 
 
 class OwnLinear(nn.Linear):
@@ -47,15 +58,15 @@ class OwnLinear(nn.Linear):
 
     own_init = True
 
+    @torch.no_grad()
     def reset_parameters(self) -> None:
-        for t in (self.weight, self.bias):
-            if t is not None:
-                nn.init.zeros_(t)
+        self.weight.zero_()
+        if self.bias is not None:
+            self.bias.zero_()
 
-
-def _affine(layer: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-    """layer(x) with the layer's tensors cast to x's dtype (the networks run in the stream's dtype under autocast too)."""
-    return torch.nn.functional.linear(x, layer.weight.to(x.dtype), layer.bias.to(x.dtype))
+    def at(self, x: torch.Tensor) -> torch.Tensor:
+        """The layer applied with its tensors cast to x's dtype (the networks run in the stream's dtype under autocast too)."""
+        return F.linear(x, self.weight.to(x.dtype), self.bias.to(x.dtype))
 
 
 class AddressNet(nn.Module):
@@ -66,74 +77,78 @@ class AddressNet(nn.Module):
     must start as the zero pseudo-query, i.e. a uniform read); every bias and the whole gate head zero (gates start
     open at sigmoid(0)). Draw order: inp.weight, then head.weight (reference: ced/model/ldm.py:103-137)."""
 
-    def __init__(self, d: int, hidden: int, out: int, eps: float, gates: int = 0, zero_head: bool = True):
+    def __init__(self, width: int, hidden: int, out: int, norm_eps: float, gates: int = 0, zero_head: bool = True):
         super().__init__()
-        self.norm = RMSNorm(d, eps)
-        self.inp = OwnLinear(d, hidden)
-        self.head = OwnLinear(hidden, out)
-        self.gate = OwnLinear(hidden, gates) if gates else None
         self.zero_head = zero_head
+        self.norm = RMSNorm(width, norm_eps)
+        self.inp, self.head = OwnLinear(width, hidden), OwnLinear(hidden, out)
+        self.gate = OwnLinear(hidden, gates) if gates > 0 else None
 
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float) -> None:
-        for layer in (self.inp, self.head, self.gate):
-            if layer is not None:
-                layer.reset_parameters()
-        drawn = [self.inp.weight] + ([] if self.zero_head else [self.head.weight])
-        for w in drawn:
-            w.copy_(torch.randn(w.shape, generator=g, dtype=torch.float32, device="cpu") * std)
+        for name, drawn in (("inp", True), ("head", not self.zero_head), ("gate", False)):
+            layer = getattr(self, name)
+            if layer is None:
+                continue
+            layer.reset_parameters()
+            if drawn:
+                layer.weight.copy_(torch.randn(layer.weight.shape, generator=g, dtype=torch.float32, device="cpu") * std)
 
     def hidden(self, x: torch.Tensor) -> torch.Tensor:
-        return torch.nn.functional.silu(_affine(self.inp, self.norm(x, out_dtype=x.dtype)))
+        return F.silu(self.inp.at(self.norm(x, out_dtype=x.dtype)))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return _affine(self.head, self.hidden(x))
+        return self.head.at(self.hidden(x))
 
     def both(self, x: torch.Tensor):
         """(address, gate logits) from one pass through the trunk."""
         h = self.hidden(x)
-        return _affine(self.head, h), _affine(self.gate, h)
+        return self.head.at(h), self.gate.at(h)
 
 
 def init_own_parameters(model: nn.Module, std: float) -> int:
     """Starts every AddressNet of `model`, in module order, from ONE CPU generator seeded with the run's seed + a fixed
     offset; the global generator is neither read nor advanced (reference: ced/model/ldm.py:423-438)."""
-    found = [m for m in model.modules() if isinstance(m, AddressNet)]
-    if found:
-        gen = torch.Generator().manual_seed((torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63))
-        for net in found:
-            net.reset_own(gen, std)
-    return len(found)
+    gen, count = None, 0
+    for m in model.modules():
+        if not isinstance(m, AddressNet):
+            continue
+        if gen is None:
+            gen = torch.Generator().manual_seed((torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63))
+        m.reset_own(gen, std)
+        count += 1
+    return count
 
 
-class TokenQuery(nn.Module):
+class TokenQuery(_Reader):
     """A block-entry reader whose query is a function of the stream at the read (`attn_res_query: token`): the key norm
     of a DepthQuery, and in place of the (d,) pseudo-query an address network whose head starts at zero, so the read
     starts uniform as the static reader does (reference: ced/model/attn_res.py:422-437)."""
 
-    def __init__(self, d: int, eps: float, hidden: int, heads: int = 1):
-        super().__init__()
-        self.key_norm = RMSNorm(d, eps)
-        self.net = AddressNet(d, hidden, d, eps)
-        self.heads = heads
+    def __init__(self, width: int, norm_eps: float, hidden: int, n_heads: int = 1):
+        super().__init__(width, norm_eps, n_heads)
+        self.net = AddressNet(width, hidden, width, norm_eps)
 
     def forward(self, sources: list, src: torch.Tensor) -> torch.Tensor:
-        if len(sources) == 1:
-            return sources[0]
-        return ops.ref.depth_mix_heads(sources, self.net(src), self.key_norm.weight, self.key_norm.eps, self.heads)
+        return self.mix(sources, self.net(src)) if len(sources) > 1 else sources[0]
+
+
+def reader_factory(width: int, norm_eps: float, n_heads: int = 1, query_hidden: int = 0) -> Callable[[], _Reader]:
+    """Builds block-entry readers of one kind: token-dependent when query_hidden > 0, static otherwise."""
+    if query_hidden:
+        return lambda: TokenQuery(width, norm_eps, query_hidden, n_heads)
+    return lambda: DepthQuery(width, norm_eps, n_heads)
 
 
 class EntryLayer(nn.Module):
     """What a layer that opens or closes a block holds: `entry` (reader of the block's input; first layer of blocks
-    2..N) and `out` (reader of the model output; last layer of the stack)."""
+    2..N) and `out` (reader of the model output; last layer of the stack). `token`: the readers take the stream at the read."""
 
-    def __init__(self, d: int, eps: float, entry: bool, closes: bool, last: bool, heads: int = 1, query_hidden: int = 0):
+    def __init__(self, make: Callable[[], _Reader], token: bool, opens: bool, closes: bool, last: bool):
         super().__init__()
-        reader = (lambda: TokenQuery(d, eps, query_hidden, heads)) if query_hidden else (lambda: DepthQuery(d, eps, heads))
-        self.entry = reader() if entry else None
-        self.closes = closes
-        self.out = reader() if last else None
-        self.token = bool(query_hidden)      # the readers take the stream at the read
+        self.token, self.closes = token, closes
+        for slot, wanted in (("entry", opens), ("out", last)):
+            self.add_module(slot, make() if wanted else None)
 
 
 class LayerQueries(nn.Module):
@@ -142,9 +157,8 @@ class LayerQueries(nn.Module):
     `first`: the layer opens a block; `out`: only in the last layer, the read of the model output
     (reference: ced/model/attn_res.py:439-452)."""
 
-    def __init__(self, d: int, eps: float, first: bool, has_mixer_query: bool, last: bool):
+    def __init__(self, width: int, norm_eps: float, first: bool, has_mixer_query: bool, last: bool):
         super().__init__()
         self.first = first
-        self.pre_mixer = DepthQuery(d, eps) if has_mixer_query else None
-        self.pre_mlp = DepthQuery(d, eps)
-        self.out = DepthQuery(d, eps) if last else None
+        for slot, wanted in (("pre_mixer", has_mixer_query), ("pre_mlp", True), ("out", last)):
+            self.add_module(slot, DepthQuery(width, norm_eps) if wanted else None)

@@ -22,7 +22,7 @@ from ..config import ModelConfig
 from . import act_checkpoint
 from . import ccr as ccr_mod
 from .attention import GatedAttention
-from .depth_mix import DepthQuery, EntryLayer, LayerQueries
+from .depth_mix import DepthQuery, EntryLayer, LayerQueries, reader_factory
 from .gdn import READ_MIX_VARIANTS, GatedDeltaNet, GDNArms
 from .mlp import dense_ffn
 from .norms import RMSNorm, round_stream
@@ -238,8 +238,7 @@ class Encoder(nn.Module):
             for i, layer in enumerate(self.layers):
                 opens, closes = i > 0 and i % S == 0, i % S == S - 1
                 if opens or closes:
-                    layer.attn_res = EntryLayer(d, eps, entry=opens, closes=closes, last=i == n - 1, heads=enc.attn_res_heads,
-                                                query_hidden=query_hidden)
+                    layer.attn_res = EntryLayer(reader_factory(d, eps, enc.attn_res_heads, query_hidden), bool(query_hidden), opens, closes, i == n - 1)
         if enc.gdn_write_mix not in ("none", "layer", "head"):
             raise ValueError(f"model.encoder.gdn_write_mix {enc.gdn_write_mix!r}: 'none', 'layer' or 'head'")
         if enc.gdn_write_mix == "head" and (enc.gdn_write_variant != "none" or cfg.fp8.mode != "none" or cfg.nvfp4.mode != "none"):

@@ -598,11 +598,12 @@ def test_delta_product_placement_is_resolved_and_refused_by_name():
     assert [type(m.dprod).__name__ for m in mixers] == ["NoneType", "PartialSteps", "PartialSteps", "NoneType", "NoneType", "DeltaProductSteps", "NoneType", "NoneType"]
     g = cfg.encoder.gdn
     assert mixers[1].dprod.in_proj_kv.weight.shape[0] == g.k_head_dim + 2 * g.v_head_dim and mixers[1].dprod.in_proj_b.weight.shape[0] == 2
-    assert mixers[2].dprod.runs_v == ((2, 2),) and mixers[2].dprod.runs_k_plain == ((0, 1),)
+    assert mixers[2].dprod.split.v["carry"] == (2, 3) and mixers[2].dprod.split.k["plain"] == (0,)
     assert sum(p.numel() for p in mixers[5].dprod.parameters()) == gdn_dprod.params_per_layer(cfg.d_model, g)
     t = torch.arange(24.0).reshape(2, 6, 2)
-    runs_a, runs_b = gdn_dprod.runs_of([0, 3, 4]), gdn_dprod.runs_of([1, 2, 5])
-    assert runs_a == ((0, 1), (3, 2)) and torch.equal(gdn_dprod.merge(gdn_dprod.take(t, runs_a, 1), runs_a, gdn_dprod.take(t, runs_b, 1), runs_b, 1), t)
+    cut = gdn_dprod.HeadSplit(3, 6, (0, 1, 4, 5))
+    assert cut.v["plain"] == (2, 3) and cut.k == {"carry": (0, 2), "plain": (1,)}
+    assert torch.equal(cut.pick(t, "carry", 1)[:, :, 0], t[:, [0, 1, 4, 5], 0]) and torch.equal(cut.join(cut.pick(t, "carry", 1), cut.pick(t, "plain", 1), 1), t)
     for key, value, match in (("layers", "[2, 1]", "ascending"), ("layers", "[9]", "ordinals"), ("heads", 3, "multiple"), ("heads", 6, "at most"),
                               ("heads_by_layer", "{0: [1, 2]}", "cut"), ("heads_by_layer", "{0: [3, 2]}", "ascending"),
                               ("heads_by_layer", "{9: [0, 1]}", "ordinals of layers"), ("beta_max", 1, "carry only some")):
