@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
+from typing import NamedTuple
 
 import torch
 import torch.nn.functional as F
@@ -182,90 +183,105 @@ def rht_tokens(t2d: torch.Tensor, transform: torch.Tensor | None) -> torch.Tenso
 # (reference: ced/model/nvfp4.py:296-449, 508-552).
 
 Q2_FWD_SCALES_MAX, Q2_BWD_SCALES_MAX, Q2_BWD_GRID_MAX, Q2_RHT = 256.0, 255.99, 6.0 / ((17.0 / 16.0) * 0.93), 128
+E2M1_GRID = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+class Quantized(NamedTuple):
+    """A quantised tensor as the GEMM takes it: `values` = element x block scale (exact in bf16) and the tensor's decode scale."""
+
+    values: torch.Tensor
+    scale: torch.Tensor
+
+    def dequant(self) -> torch.Tensor:
+        return self.values * self.scale
+
+
+def _constant(values, like: torch.Tensor) -> torch.Tensor:
+    return torch.tensor(values, dtype=like.dtype, device=like.device)
 
 
 def e2m1_round_away(a: torch.Tensor) -> torch.Tensor:
-    """Magnitudes a >= 0 onto the E2M1 grid, ties away from zero, saturating at 6 (exact: the step is a power of two)."""
-    step = torch.where(a < 2.0, 0.5, torch.where(a < 4.0, 1.0, 2.0)).to(a.dtype)
-    t = a / step
-    n = torch.floor(t)
-    return torch.clamp((n + (t - n >= 0.5).to(a.dtype)) * step, max=E2M1_MAX)
+    """Magnitudes a >= 0 onto the E2M1 grid, ties away from zero, saturating at 6: the grid point whose cell, cut at the
+    midpoints and closed below, holds a (one search over seven thresholds; exact)."""
+    grid = _constant(E2M1_GRID, a)
+    return grid[torch.bucketize(a, (grid[1:] + grid[:-1]) / 2, right=True)]
+
+
+def _signed_grid(t: torch.Tensor) -> torch.Tensor:
+    return torch.copysign(e2m1_round_away(t.abs()), t)
+
+
+def _block_view(t: torch.Tensor, n: int) -> torch.Tensor:
+    """(..., K) -> (..., K' / n, n) in float32, K zero-padded up to a multiple of n."""
+    t = t.float()
+    short = -t.shape[-1] % n
+    return (F.pad(t, (0, short)) if short else t).unflatten(-1, (-1, n))
+
+
+def _tensor_scale(t: torch.Tensor, denominator: tuple) -> torch.Tensor:
+    """amax / denominator / grid max as the reference divides (two divisions), 1 for a tensor of zeros."""
+    top = t.abs().amax()
+    return torch.where(top > 0, top / denominator[0] / denominator[1], torch.ones_like(top))
 
 
 def _e4m3_or_one(s: torch.Tensor) -> torch.Tensor:
-    q = torch.clamp(s, max=E4M3_MAX).to(E4M3).float()
-    return torch.where(q == 0, torch.ones_like(q), q)       # a block whose scale underflows quantises to zeros
+    """s (>= 0) rounded to E4M3 (saturating); 1 where that underflows to zero, so that such a block quantises to zeros."""
+    stored = s.clamp(max=E4M3_MAX).to(E4M3).float()
+    return stored.masked_fill(stored == 0, 1.0)
 
 
-def q2_rtn_quantize(x: torch.Tensor, four_over_six: bool = True):
-    """(v, s_dec) of the forward quantiser along x's last dimension; the dequantised tensor is v * s_dec."""
-    x32 = x.float()
-    shape = x32.shape
-    pad = (-shape[-1]) % NV_BLOCK
-    xp = F.pad(x32, (0, pad)) if pad else x32
-    blocks = xp.reshape(*xp.shape[:-1], -1, NV_BLOCK)
-    amax = x32.abs().amax()
-    s_dec = torch.where(amax > 0, amax / (Q2_FWD_SCALES_MAX if four_over_six else E4M3_MAX) / E2M1_MAX, torch.ones_like(amax))
-    amax_b = blocks.abs().amax(dim=-1, keepdim=True)
-
-    def candidate(scale):
-        unit = scale * s_dec
-        scaled = blocks / unit
-        q = torch.copysign(e2m1_round_away(scaled.abs()), scaled)
-        return q, ((blocks - q * unit) ** 2).sum(-1, keepdim=True)
-
-    scale = _e4m3_or_one(amax_b / E2M1_MAX / s_dec)
-    q, err = candidate(scale)
+def q2_rtn_quantize(x: torch.Tensor, four_over_six: bool = True) -> Quantized:
+    """The forward quantiser along x's last dimension. Under four-over-six both candidates of every block (largest magnitude
+    on 6, on 4) are formed side by side along a leading axis and the one with the smaller squared error is kept (6 on a tie)."""
+    blocks = _block_view(x, NV_BLOCK)
+    s_dec = _tensor_scale(x.float(), (Q2_FWD_SCALES_MAX if four_over_six else E4M3_MAX, E2M1_MAX))
+    peak = blocks.abs().amax(dim=-1, keepdim=True)
+    on_six = peak / E2M1_MAX / s_dec
+    tried = torch.stack([on_six, peak / E2M1_MAX * 1.5 / s_dec]) if four_over_six else on_six.unsqueeze(0)
+    scales = _e4m3_or_one(tried)
+    cell = scales * s_dec
+    grid = _signed_grid(blocks / cell)
+    kept = grid[0] * scales[0]
     if four_over_six:
-        scale4 = _e4m3_or_one(amax_b / E2M1_MAX * 1.5 / s_dec)
-        q4, err4 = candidate(scale4)
-        six = err <= err4
-        q, scale = torch.where(six, q, q4), torch.where(six, scale, scale4)
-    return (q * scale).reshape(*blocks.shape[:-2], -1)[..., :shape[-1]], s_dec
+        miss = (blocks - grid * cell).square().sum(-1, keepdim=True)
+        kept = torch.where(miss[1] < miss[0], grid[1] * scales[1], kept)
+    return Quantized(kept.flatten(-2)[..., :x.shape[-1]], s_dec)
 
 
 def q2_rotate(t2d: torch.Tensor, transform: torch.Tensor) -> torch.Tensor:
     """(R, K) -> (R, K'): every n-segment of each row times the (n x n) transform, K zero-padded to a multiple of n."""
-    n = transform.shape[0]
-    t = t2d.float()
-    pad = (-t.shape[-1]) % n
-    if pad:
-        t = F.pad(t, (0, pad))
-    r, k = t.shape
-    return torch.matmul(t.reshape(r, k // n, n), transform.float()).reshape(r, k)
+    return (_block_view(t2d, transform.shape[0]) @ transform.float()).flatten(-2)
 
 
 def e4m3_neighbours(c: torch.Tensor):
-    """(down, up): the E4M3 values around c >= 0, both c itself when c is one."""
-    c = torch.clamp(c, max=E4M3_MAX)
-    near = c.to(E4M3)
-    bits = near.view(torch.uint8).to(torch.int16)
-    r = near.float()
-    at = lambda b: b.clamp(0, 0x7E).to(torch.uint8).view(E4M3).float()      # noqa: E731
-    above = r > c
-    return torch.where(above, at(bits - 1), r), torch.where(above, r, torch.where(r == c, r, at(bits + 1)))
+    """(down, up): the E4M3 values around c >= 0, both c itself when c is one. Two searches in the table of the 127
+    finite non-negative codes."""
+    table = torch.arange(0x7F, dtype=torch.uint8, device=c.device).view(E4M3).to(c.dtype)
+    c = c.clamp(max=E4M3_MAX)
+    below = torch.bucketize(c, table, right=True) - 1                       # the last code <= c
+    above = torch.bucketize(c, table, right=False).clamp(max=table.numel() - 1)      # the first code >= c
+    return table[below], table[above]
 
 
-def q2_eden_quantize(t2d: torch.Tensor, transform: torch.Tensor, u: torch.Tensor | None = None):
-    """(v, s_dec) of MS-EDEN along K of t2d (R, K): the dequantised ROTATED tensor is v * s_dec. u (R, K' / 16) ~ U[0, 1)
+def q2_eden_quantize(t2d: torch.Tensor, transform: torch.Tensor, u: torch.Tensor | None = None) -> Quantized:
+    """MS-EDEN along K of t2d (R, K): the dequantised ROTATED tensor is values * scale. u (R, K' / 16) ~ U[0, 1)
     decides each block scale's rounding (drawn here from the device's global generator when None)."""
-    xr = q2_rotate(t2d, transform)
-    r, k = xr.shape
-    blocks = xr.reshape(r, k // NV_BLOCK, NV_BLOCK)
-    amax = xr.abs().amax()
-    s_dec = torch.where(amax > 0, amax / Q2_BWD_SCALES_MAX / Q2_BWD_GRID_MAX, torch.ones_like(amax))
+    rotated = q2_rotate(t2d, transform)
+    blocks = rotated.unflatten(-1, (-1, NV_BLOCK))
+    s_dec = _tensor_scale(rotated, (Q2_BWD_SCALES_MAX, Q2_BWD_GRID_MAX))
     scale = _e4m3_or_one(blocks.abs().amax(dim=-1, keepdim=True) / Q2_BWD_GRID_MAX / s_dec)
-    scaled = blocks / (scale * s_dec)
-    q = torch.copysign(e2m1_round_away(scaled.abs()), scaled)
-    num, den = (scaled * scaled).sum(-1, keepdim=True), (scaled * q).sum(-1, keepdim=True)
-    zero = den == 0
-    c = scale * torch.where(zero, torch.ones_like(den), num / torch.where(zero, torch.ones_like(den), den))
-    down, up = e4m3_neighbours(c)
-    gap = up - down
-    p_up = torch.where(gap > 0, (c - down) / torch.where(gap > 0, gap, torch.ones_like(gap)), torch.zeros_like(gap))
+    unit = blocks / (scale * s_dec)
+    grid = _signed_grid(unit)
+    # the correction <x', x'> / <x', q> of the block (1 for a block that quantised to zeros), folded into its scale
+    own, cross = (unit * unit).sum(-1, keepdim=True), (unit * grid).sum(-1, keepdim=True)
+    empty = cross == 0
+    wanted = scale * (own / cross.masked_fill(empty, 1.0)).masked_fill(empty, 1.0)
+    down, up = e4m3_neighbours(wanted)
+    width = up - down
+    chance_up = ((wanted - down) / width.masked_fill(width <= 0, 1.0)).masked_fill(width <= 0, 0.0)
     if u is None:
-        u = torch.rand_like(num[..., 0])
-    return (q * torch.where(u[..., None] < p_up, up, down)).reshape(r, k), s_dec
+        u = torch.rand_like(own[..., 0])
+    return Quantized((grid * torch.where(u.unsqueeze(-1) < chance_up, up, down)).flatten(-2), s_dec)
 
 
 def q2_hadamard() -> torch.Tensor:
@@ -278,32 +294,31 @@ class _Quartet2Linear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, native_gemm: bool):
-        k = x.shape[-1]
-        xv, xs = q2_rtn_quantize(x.reshape(-1, k))
-        wv, ws = q2_rtn_quantize(weight)
-        out_dtype = x.dtype if x.dtype != torch.float32 or not native_gemm else torch.bfloat16
-        y = (_mm(xv, wv, native_gemm, torch.float32) * (xs * ws)).to(out_dtype)
-        keep = torch.bfloat16 if native_gemm else xv.dtype
-        ctx.save_for_backward(xv.to(keep), xs, wv.to(keep), ws)
-        ctx.native_gemm, ctx.xshape, ctx.x_dtype, ctx.w_dtype = native_gemm, x.shape, x.dtype, weight.dtype
-        return y.reshape(*x.shape[:-1], weight.shape[0])
+        xq, wq = q2_rtn_quantize(x.flatten(0, -2)), q2_rtn_quantize(weight)
+        y = _mm(xq.values, wq.values, native_gemm, torch.float32) * (xq.scale * wq.scale)
+        stored = torch.bfloat16 if native_gemm else xq.values.dtype
+        ctx.save_for_backward(xq.values.to(stored), xq.scale, wq.values.to(stored), wq.scale)
+        ctx.native_gemm, ctx.like_x, ctx.like_w = native_gemm, (x.shape, x.dtype), weight.dtype
+        to = torch.bfloat16 if native_gemm and x.dtype == torch.float32 else x.dtype
+        return y.to(to).unflatten(0, x.shape[:-1])
 
     @staticmethod
     def backward(ctx, dy):
-        xv, xs, wv, ws = ctx.saved_tensors
-        n, k = wv.shape
-        dy2 = dy.reshape(-1, n)
-        signs = torch.where(torch.rand(Q2_RHT, device=dy.device) < 0.5, 1.0, -1.0)
-        transform = signs[:, None] * q2_hadamard().to(dy.device)
+        x_values, x_scale, w_values, w_scale = ctx.saved_tensors
+        (x_shape, x_dtype), rows = ctx.like_x, dy.flatten(0, -2)
+        flips = torch.where(torch.rand(Q2_RHT, device=dy.device) < 0.5, 1.0, -1.0)
+        turn = flips.unsqueeze(1) * q2_hadamard().to(dy.device)
+
+        def product(left, right, carried):
+            """left @ right^T with both sides re-quantised along the dot product; carried: the forward scale the stored side lacks."""
+            lq, rq = q2_eden_quantize(left, turn), q2_eden_quantize(right, turn)
+            return _mm(lq.values, rq.values, ctx.native_gemm, torch.float32) * (lq.scale * rq.scale * carried)
+
         dx = dw = None
         if ctx.needs_input_grad[0]:             # dx = dy W: the dot product over the output features
-            gv, gs = q2_eden_quantize(dy2, transform)
-            wtv, wts = q2_eden_quantize(wv.float().t(), transform)
-            dx = (_mm(gv, wtv, ctx.native_gemm, torch.float32) * (gs * wts * ws)).reshape(*ctx.xshape[:-1], k).to(ctx.x_dtype)
+            dx = product(rows, w_values.float().t(), w_scale).view(x_shape).to(x_dtype)
         if ctx.needs_input_grad[1]:             # dW = dy^T x: the dot product over the tokens
-            gtv, gts = q2_eden_quantize(dy2.t(), transform)
-            xtv, xts = q2_eden_quantize(xv.float().reshape(-1, k).t(), transform)
-            dw = (_mm(gtv, xtv, ctx.native_gemm, torch.float32) * (gts * xts * xs)).to(ctx.w_dtype)
+            dw = product(rows.t(), x_values.float().t(), x_scale).to(ctx.like_w)
         return dx, dw, None
 
 
