@@ -807,7 +807,7 @@ _TRAIN_UNREAD = (
     "optim.anvil2_preset", "optim.anvil2_single_rounding", "optim.anvil2_tavg", "optim.anvil2_decon", "optim.anvil2_scale", "optim.anvil2_points",
     "optim.anvil2_tail_ema", "optim.anvil2_qk_head_pairs", "optim.soap_seeded_start", "optim.ours", "loss.aux_weight", "loss.aux_positions",
     "loss.aux_fraction", "eval.replay_window", "eval.decoder_at", "eval.lc_every_steps", "eval.lc_dir", "eval.lc_length", "eval.lc_docs",
-    "eval.lc_base_len", "eval.lc_mf_items", "trim_decoder_slots", "pass_slot_buckets", "micro_batch_by_t", "tst.aux_weight", "stage_shape")
+    "eval.lc_base_len", "eval.lc_mf_items", "trim_decoder_slots", "pass_slot_buckets", "tst.aux_weight", "stage_shape")
 
 
 def _get(cfg, dotted: str):

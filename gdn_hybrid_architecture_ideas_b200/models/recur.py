@@ -36,6 +36,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+T_SAMPLINGS = ("step", "sequence")
 INJECTIONS = ("none", "mix", "parcae", "depth_mix")
 B_FORMS = ("dense", "diag")
 STATE_INITS = ("zeros", "prelude")
@@ -62,8 +63,10 @@ def check_config(cfg) -> None:
         raise ValueError(f"model.loop.recur_layers {list(r)!r}: [first, end] with 0 <= first < end <= {n} (the layers first .. end - 1 loop)")
     if lc.injection not in INJECTIONS:
         raise ValueError(f"model.loop.injection {lc.injection!r} with a looped middle: one of {INJECTIONS}")
-    if lc.t_sampling != "step":
-        raise ValueError(f"model.loop.t_sampling {lc.t_sampling!r}: a pass count per row is not built; 'step' draws one per optimizer step")
+    if lc.t_sampling not in T_SAMPLINGS:
+        raise ValueError(f"model.loop.t_sampling {lc.t_sampling!r}: one of {T_SAMPLINGS} (one pass count per optimizer step, or one per row)")
+    if lc.t_sampling == "sequence" and lc.injection == "depth_mix":
+        raise ValueError("model.loop.t_sampling 'sequence' (a pass count per row) is not built together with model.loop.injection 'depth_mix'")
     clashes = {"model.encoder.attn_res": enc.attn_res != "none", "model.encoder.layer_scalars": enc.layer_scalars != "none",
                "model.encoder.canon_kernel": bool(enc.canon_kernel), "model.nvfp4.mode": cfg.nvfp4.mode != "none",
                "model.encoder.attention.normalizer 'asentmax'": enc.attention.normalizer != "softmax", "model.mtp.enabled": bool(cfg.mtp.enabled)}
@@ -142,6 +145,44 @@ def pass_count_for_step(loop, seed: int, step: int) -> int:
     g = counter_generator(seed, step, 1)
     i = int(torch.multinomial(torch.tensor(loop.t_probs, dtype=torch.float64), 1, generator=g))
     return int(loop.t_choices[i])
+
+
+def rows_by_count(loop, batch_size: int) -> list:
+    """`t_sampling: sequence`: the pass counts a step's rows hold, t_probs[i] x batch_size rows of t_choices[i] in the
+    order of t_choices; refused unless every product is a whole number and they add up to the batch."""
+    held = []
+    for t, share in zip(loop.t_choices, loop.t_probs):
+        rows = share * batch_size
+        if round(rows) < 0 or abs(rows - round(rows)) > 1e-9:
+            raise ValueError(f"model.loop.t_sampling 'sequence': t_probs {list(loop.t_probs)!r} x data.batch_size {batch_size} must be whole numbers of rows "
+                             f"(T = {t}: {rows})")
+        held.extend([int(t)] * round(rows))
+    if len(held) != batch_size:
+        raise ValueError(f"model.loop.t_sampling 'sequence': t_probs {list(loop.t_probs)!r} give {len(held)} rows of data.batch_size {batch_size} (they must sum to 1)")
+    return held
+
+
+def row_pass_counts(held: list, seed: int, step: int) -> list:
+    """The pass count of every row of a step's batch, in row order: the step's multiset `held` dealt to the rows through
+    a permutation out of the counter-based generator of (seed, step), so a resume needs only the step."""
+    from ..data.synthetic import counter_generator
+
+    deal = torch.randperm(len(held), generator=counter_generator(seed, step, 2)).tolist()
+    counts = [0] * len(held)
+    for slot, row in enumerate(deal):
+        counts[row] = held[slot]
+    return counts
+
+
+def micro_plan(counts: list, rows_per_forward) -> list:
+    """[(rows, T)]: the rows of each pass count (ascending T, rows in batch order) in groups of rows_per_forward(T); every
+    forward has one T, and the groups' shapes are the same at every step because the multiset is."""
+    plan = []
+    for t in sorted(set(counts)):
+        rows = [i for i, c in enumerate(counts) if c == t]
+        size = rows_per_forward(t)
+        plan.extend((rows[lo:lo + size], t) for lo in range(0, len(rows), size))
+    return plan
 
 
 def mean_pass_count(loop) -> float:

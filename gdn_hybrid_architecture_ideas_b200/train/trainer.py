@@ -83,6 +83,21 @@ class Trainer:
             hit = [k for k, v in clashes.items() if v]
             if hit:
                 raise ValueError(f"model.loop.recur_layers (the looped middle) is not built together with: {', '.join(hit)}")
+        # A pass count per row (model.loop.t_sampling 'sequence'): the step's rows hold a fixed multiset of counts, and the
+        # micro-batches are formed from rows of equal count, micro_batch_by_t[T - 1] rows at a time.
+        self._rows_held = None
+        by_t = cfg.micro_batch_by_t
+        if not isinstance(by_t, list) or any(type(m) is not int or not 1 <= m <= cfg.data.batch_size for m in by_t):
+            raise ValueError(f"micro_batch_by_t {by_t!r}: a list of rows per forward by pass count (entry T - 1), each 1 .. data.batch_size ({cfg.data.batch_size})")
+        if by_t and not self.looped:
+            raise ValueError("micro_batch_by_t is read with a looped middle (model.loop.recur_layers); set micro_batch_size")
+        if self.looped and cfg.model.loop.t_sampling == "sequence":
+            from ..models.recur import rows_by_count
+
+            if self.world > 1:
+                raise ValueError("model.loop.t_sampling 'sequence' (a pass count per row: the step's multiset is dealt over the whole batch) is not built "
+                                 "together with data parallelism")
+            self._rows_held = rows_by_count(cfg.model.loop, cfg.data.batch_size)
         S = cfg.loop_switch_step
         if type(S) is not int or not 0 <= S < max(cfg.steps, 1):
             raise ValueError(f"loop_switch_step {S!r}: an optimizer step S with 0 <= S < steps ({cfg.steps})")
@@ -396,13 +411,19 @@ class Trainer:
             micro = max(1, min(rows, per_rank * cfg.data.seq_len // sh.seq_len))
             while rows % micro:
                 micro -= 1
-        if rows % micro:
+        if rows % micro and not cfg.micro_batch_by_t:
             raise ValueError(f"micro_batch_size {micro} does not divide this rank's {rows} rows")
         loss_sum = torch.zeros((), dtype=torch.float32, device=self.device)
         ce_sum = torch.zeros((), dtype=torch.float32, device=self.device)
-        for lo in range(0, rows, micro):
-            mb = batch if micro == rows else _slice(batch, lo, lo + micro)
-            if self._qmix is not None and lo == 0 and self.step >= cfg.model.encoder.gdn_qmix_select_step:
+        if self.looped and cfg.micro_batch_by_t and self._rows_held is None:
+            micro = self.micro_rows(self.pass_count)
+        plan = [(lo, self.pass_count) for lo in range(0, rows, micro)] if self._rows_held is None else self.row_plan(self.step)
+        for at, (lo, passes) in enumerate(plan):
+            if self._rows_held is None:
+                mb = batch if micro >= rows else _slice(batch, lo, min(lo + micro, rows))
+            else:       # the rows of one pass count: a gather by an index that goes to the device once
+                mb, self.pass_count = _rows(batch, torch.tensor(lo, dtype=torch.long).to(self.device, non_blocking=True)), passes
+            if self._qmix is not None and at == 0 and self.step >= cfg.model.encoder.gdn_qmix_select_step:
                 from ..models import qmix_select
 
                 if qmix_select.pending(self._qmix):      # once: the extra forward is discarded, nothing runs backward
@@ -414,7 +435,7 @@ class Trainer:
                 with monitor.nvtx_range("forward", self._nvtx):
                     loss, ce = self._micro_loss(mb, max(n_global, 1))
                 if self.zero is not None:       # gradients are final after the last micro-batch: its finished buckets may leave
-                    self.zero.armed = lo + micro >= rows
+                    self.zero.armed = at == len(plan) - 1
                 with monitor.nvtx_range("backward", self._nvtx):
                     loss.backward()
                 loss_sum += loss.detach().float()
@@ -462,6 +483,22 @@ class Trainer:
         out = torch.stack([stats[0].float(), stats[1].float(), gnorm.float(), status])
         fam, self._family_norms = getattr(self, "_family_norms", None), None
         return out if fam is None else torch.cat([out, fam.float()])
+
+    def micro_rows(self, passes: int) -> int:
+        """Rows per forward / backward at a pass count: micro_batch_by_t's entry (its last beyond the list), else micro_batch_size."""
+        by_t = self.cfg.micro_batch_by_t
+        return by_t[min(passes, len(by_t)) - 1] if by_t else (self.cfg.micro_batch_size or self.cfg.data.batch_size)
+
+    def row_passes(self, step: int):
+        """The pass count of every row of the step's batch (t_sampling 'sequence'; None otherwise): a function of (seed, step)."""
+        from ..models.recur import row_pass_counts
+
+        return None if self._rows_held is None else row_pass_counts(self._rows_held, self.cfg.seed, step)
+
+    def row_plan(self, step: int) -> list:
+        from ..models.recur import micro_plan
+
+        return micro_plan(self.row_passes(step), self.micro_rows)
 
     def train_step(self) -> dict:
         """One full training step through the public path: build this rank's batch (a pure function of the step),
@@ -521,6 +558,9 @@ class Trainer:
                     m["pass_counts"] = {str(k): float((c == k).float().mean()) for k in range(1, self.model.n_passes + 1)}
         if self.looped:
             m["T"] = self.pass_count
+            if self._rows_held is not None:
+                m["T_rows"] = self.row_passes(step)
+                m["T"] = sum(m["T_rows"]) / len(m["T_rows"])
             inj = self.model.encoder.recur_injection
             if inj is not None and cfg.log_every and step % cfg.log_every == 0:
                 m["recur_injection"] = inj.summary()
@@ -866,6 +906,17 @@ def _slice(batch, lo: int, hi: int):
     return Batch(tokens=cut(batch.tokens), targets=cut(batch.targets), target_valid=cut(batch.target_valid),
                  doc_ids=cut(batch.doc_ids), dec_mask=cut(batch.dec_mask), multi_targets=cut(batch.multi_targets),
                  multi_valid=cut(batch.multi_valid), loss_mask=cut(batch.loss_mask), single_doc=batch.single_doc)
+
+
+def _rows(batch, index: torch.Tensor):
+    """The batch's rows `index` (a device LongTensor, ascending), gathered."""
+    from ..data.synthetic import Batch
+
+    def take(t):
+        return t.index_select(0, index) if isinstance(t, torch.Tensor) else t
+    return Batch(tokens=take(batch.tokens), targets=take(batch.targets), target_valid=take(batch.target_valid),
+                 doc_ids=take(batch.doc_ids), dec_mask=take(batch.dec_mask), multi_targets=take(batch.multi_targets),
+                 multi_valid=take(batch.multi_valid), loss_mask=take(batch.loss_mask), single_doc=batch.single_doc)
 
 
 def _clip_coef(norm: torch.Tensor, max_norm: float):

@@ -740,6 +740,62 @@ def test_looped_middle_trains_with_a_pass_count_per_step(tmp_path, injection):
             Trainer(bad, None)
 
 
+def test_looped_middle_with_a_pass_count_per_row(tmp_path):
+    """`t_sampling: sequence`: every step's rows hold the same multiset of pass counts, dealt by (seed, step); the forwards are
+    formed from rows of equal count (`micro_batch_by_t` rows at a time) and the accumulated gradient is the gradient of the
+    sum of the rows' losses, each row at its own count; the metrics carry the rows' counts; a resume ends in the same state."""
+    from gdn_hybrid_architecture_ideas_b200.models.recur import micro_plan, row_pass_counts, rows_by_count
+
+    cfg = tiny_train_config(steps=4)
+    cfg.model = C.tiny_control_config()
+    cfg.model.encoder.n_layers, cfg.dtype = 8, "float64"
+    cfg.data.batch_size = 4
+    lp = cfg.model.loop
+    lp.recur_layers, lp.injection, lp.t_eval, lp.t_choices, lp.t_probs, lp.t_sampling = (2, 6), "mix", 2, [1, 3], [0.5, 0.5], "sequence"
+    cfg.micro_batch_by_t, cfg.ckpt_every_steps, cfg.optim.grad_clip = [2, 2, 1], 2, 0.0
+    held = rows_by_count(lp, 4)
+    assert held == [1, 1, 3, 3]
+    deals = [row_pass_counts(held, cfg.seed, s) for s in range(8)]
+    assert all(sorted(d) == held for d in deals) and len({tuple(d) for d in deals}) > 1 and deals[3] == row_pass_counts(held, cfg.seed, 3)
+    assert micro_plan([3, 1, 3, 1], lambda t: {1: 2, 3: 1}[t]) == [([1, 3], 1), ([0], 3), ([2], 3)]
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
+    assert t.micro_rows(1) == 2 and t.micro_rows(3) == 1 and t.micro_rows(7) == 1 and len(t.row_plan(0)) == 3
+    batch = t.batch_at(0).to(t.device)
+    n = int(batch.target_valid.sum())
+    t.device_step(copy.deepcopy(batch), n)
+    got = t.flat.grads.clone()
+    u = Trainer(copy.deepcopy(cfg), tmp_path / "u")
+    counts = u.row_passes(0)
+    u.flat.grads.zero_()
+    for row, passes in enumerate(counts):                                   # every row on its own, at its own pass count
+        from gdn_hybrid_architecture_ideas_b200.train.trainer import _slice
+
+        u.pass_count = passes
+        u._micro_loss(_slice(batch, row, row + 1), n)[0].backward()
+    assert (got - u.flat.grads).abs().max() < 2e-6 * float(got.abs().max()) and float(got.abs().max()) > 0      # float32 gradient buffers
+    m = t.train_step()
+    assert m["T_rows"] == t.row_passes(1) and m["T"] == 2.0
+    a = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    a.fit()
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(until_step=2)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 2
+    c.fit()
+    for (k, x), (_, y) in zip(a.model.state_dict().items(), c.model.state_dict().items()):
+        assert torch.equal(x, y), k
+    for change, match in ((lambda c: setattr(c.model.loop, "t_probs", [0.3, 0.7]), "whole numbers"), (lambda c: setattr(c.model.loop, "injection", "depth_mix"), "depth_mix"),
+                          (lambda c: setattr(c, "micro_batch_by_t", [0]), "micro_batch_by_t"), (lambda c: setattr(c.model.loop, "t_sampling", "row"), "t_sampling")):
+        bad = copy.deepcopy(cfg)
+        change(bad)
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
+    bad = copy.deepcopy(cfg)
+    bad.model.loop.recur_layers, bad.model.loop.injection, bad.model.loop.t_sampling, bad.model.loop.t_eval = (), "none", "step", 1
+    with pytest.raises(ValueError, match="micro_batch_by_t"):
+        Trainer(bad, None)
+
+
 def test_head_precision_bf16_rounds_the_operands_of_the_three_products(reference):
     """`head_precision: bf16` on the PyTorch path: logits, dh and dW are exact products of operands rounded once to bfloat16,
     accumulated in the compute dtype; equal to the reference's statement in float64; both heads agree; fp32 is untouched."""
