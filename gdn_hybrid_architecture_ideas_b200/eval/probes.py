@@ -187,9 +187,10 @@ def multifact_metrics(p: Probe, ok: list[bool], nats: list[float]) -> dict:
 
 
 @torch.no_grad()
-def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype=None, keep_tokens: bool = False) -> dict:
+def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype=None, keep_tokens: bool = False, passes: int | None = None) -> dict:
     """Teacher-forced: exact = every answer token is the argmax given the true prefix. keep_tokens: every item also
-    carries its per-token record ("ok", "nats") and its index, what `eval/probe_analysis.py` reads."""
+    carries its per-token record ("ok", "nats") and its index, what `eval/probe_analysis.py` reads. passes: the pass count
+    of a model with a looped middle or a second pass (None: the model's own evaluation count)."""
     dev = next(model.parameters()).device
     exact, ce_sum, n_tok, per = 0, 0.0, 0, []
     for s in range(0, len(probes), batch_size):
@@ -203,7 +204,7 @@ def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype
             tok[b, :n], tgt[b, :n] = torch.tensor(p.ids[:-1]), torch.tensor(p.ids[1:])
             doc[b, :n] = 0
         with torch.autocast(dev.type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
-            logits = model(tok.to(dev), doc.to(dev)).logits
+            logits = model(tok.to(dev), doc.to(dev), **({} if passes is None else {"T": passes})).logits
         ce = token_cross_entropy(logits, tgt.to(dev)).cpu()
         top = logits.argmax(-1).cpu()
         for b, p in enumerate(group):

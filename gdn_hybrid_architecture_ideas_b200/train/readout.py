@@ -9,6 +9,17 @@ sample is scored teacher-forced and one record goes to the run's metrics.jsonl:
 A row's value is the mean over its items; the pooled value is the mean over the rows. `logp` is the mean log probability
 of an answer token.
 
+A model with a looped middle or a gated second pass is scored at one pass and at two on the same items, and the record is
+
+    {"event": "readout", "step": s, "passes": [1, 2], "items": n, "exact": {"1": ..., "2": ...}, "logp": {"1": ..., "2": ...},
+     "gap": {"mean": ..., "se": ...}, "gap_logp": {"mean": ..., "se": ...},                T = 2 minus T = 1, paired by item
+     "rows": {"<set>/<cell>": {"n", "exact": [T1, T2], "logp": [T1, T2], "gap": {...}, "gap_logp": {...}}}, "sample": ...}
+
+A row's gap is the mean of the per-item differences (exact as 0 / 1; logp as the item's mean log probability of an answer
+token) with the standard error of that mean (sample deviation over sqrt(n); 0 for one item); the pooled gap is the mean
+of the rows' gaps, its error the root of the rows' summed squared errors over the number of rows (rows hold different
+items). Such a run is also scored at its `loop_switch_step`, the last step before the second pass joins.
+
 The sample (`eval.readout_sets`): a list of [stored probe file, cells, items per cell]. The file is what
 `scripts/build_probes.py` or `scripts/build_text_probes.py` wrote; `cells` is "*" or a list of kind names / cell names;
 of each cell the FIRST `items per cell` items are taken, in file order: no random draw, so `scripts/eval_probes.py --set`
@@ -21,8 +32,8 @@ time is not a step's time (it runs in fit() between two steps). An error while s
 {"event": "readout_failed"} and switches the readout off for the rest of the process: it never stops training. A step
 whose record is already in metrics.jsonl is not scored again, so a resumed run that repeats steps writes no readout
 twice. Only the lead rank scores (the sample is small).
-Reference: ced/train/readout.py:84-434 (there the sample is scored at one and at two passes of a looped model on a
-scoring twin; the models here have one pass and no compiled graph to protect, so the training model itself is read).
+Reference: ced/train/readout.py:84-434 (there the sample is scored on a scoring twin that shares the trainer's parameter
+tensors; there is no compiled graph to protect here, so the training model itself is read).
 """
 
 from __future__ import annotations
@@ -67,7 +78,26 @@ def check_readout_config(cfg) -> None:
 
 def readout_due(cfg, step: int, total_steps: int | None = None) -> bool:
     r = cfg.eval.readout_every
-    return bool(r) and step > 0 and (step % r == 0 or step == (cfg.steps if total_steps is None else total_steps))
+    last = cfg.steps if total_steps is None else total_steps
+    return bool(r) and step > 0 and (step % r == 0 or step == last or step == cfg.loop_switch_step)
+
+
+def passes_of(model) -> tuple:
+    """(1, 2) for a model that can run a second pass (a looped middle, a gated second pass), (1,) otherwise."""
+    looped = bool(model.cfg.loop.recur_layers) or model.cfg.loop.pass2_gate != "none"
+    return (1, 2) if looped else (1,)
+
+
+def paired_gap(later: list, first: list) -> dict:
+    """The mean of the per-item differences later - first and the standard error of that mean."""
+    d = torch.tensor(later, dtype=torch.float64) - torch.tensor(first, dtype=torch.float64)
+    se = float(d.std(unbiased=True) / len(d) ** 0.5) if len(d) > 1 else 0.0
+    return {"mean": round(float(d.mean()), 6), "se": round(se, 6)}
+
+
+def pooled_gap(gaps: list) -> dict:
+    n = max(len(gaps), 1)
+    return {"mean": round(sum(g["mean"] for g in gaps) / n, 6), "se": round(sum(g["se"] ** 2 for g in gaps) ** 0.5 / n, 6)}
 
 
 def load_sample(sets: list[dict], vocab_size: int) -> list[dict]:
@@ -136,17 +166,26 @@ def batches_by_tokens(items: list, budget: int) -> list[list]:
     return out
 
 
-def score_sample(model, rows: list[dict], batch_tokens: int, autocast_dtype=None) -> dict:
+def score_sample(model, rows: list[dict], batch_tokens: int, autocast_dtype=None, passes: tuple = (1,)) -> dict:
+    """{row: {"n", "exact", "logp"}}; with two pass counts the values are [T1, T2] lists and the row carries its gaps."""
     table = {}
     for r in rows:
-        exact, nats, tokens = 0.0, 0.0, 0
-        for group in batches_by_tokens(r["probes"], batch_tokens):
-            res = probes.score_probes(model, group, batch_size=len(group), autocast_dtype=autocast_dtype)
-            exact += sum(float(it["exact"]) for it in res["items"])
-            nats += sum(it["ce"] * p.answer_len for it, p in zip(res["items"], group))
-            tokens += sum(p.answer_len for p in group)
+        per_pass = []
+        for t in passes:
+            hits, logps, nats, tokens = [], [], 0.0, 0
+            for group in batches_by_tokens(r["probes"], batch_tokens):
+                res = probes.score_probes(model, group, batch_size=len(group), autocast_dtype=autocast_dtype, passes=t if len(passes) > 1 else None)
+                hits += [float(it["exact"]) for it in res["items"]]
+                logps += [-it["ce"] for it in res["items"]]
+                nats += sum(it["ce"] * p.answer_len for it, p in zip(res["items"], group))
+                tokens += sum(p.answer_len for p in group)
+            per_pass.append({"hits": hits, "logps": logps, "exact": round(sum(hits) / len(hits), 6), "logp": round(-nats / max(tokens, 1), 6)})
         n = len(r["probes"])
-        table[r["row"]] = {"n": n, "exact": round(exact / n, 6), "logp": round(-nats / max(tokens, 1), 6)}
+        if len(passes) == 1:
+            table[r["row"]] = {"n": n, "exact": per_pass[0]["exact"], "logp": per_pass[0]["logp"]}
+        else:
+            table[r["row"]] = {"n": n, "exact": [p["exact"] for p in per_pass], "logp": [p["logp"] for p in per_pass],
+                               "gap": paired_gap(per_pass[-1]["hits"], per_pass[0]["hits"]), "gap_logp": paired_gap(per_pass[-1]["logps"], per_pass[0]["logps"])}
     return table
 
 
@@ -171,7 +210,8 @@ class Readout:
         try:
             trainer.model.eval()
             ac = torch.bfloat16 if trainer.cfg.autocast == "bfloat16" and trainer.device.type == "cuda" else None
-            table = score_sample(trainer.model, self.rows, trainer.cfg.eval.readout_batch_tokens, ac)
+            passes = passes_of(trainer.model)
+            table = score_sample(trainer.model, self.rows, trainer.cfg.eval.readout_batch_tokens, ac, passes)
         except Exception as err:          # never stops training
             self.off = True
             record = {"event": FAILED, "step": step, "error": f"{type(err).__name__}: {err}"[:500]}
@@ -182,6 +222,10 @@ class Readout:
             periodic_eval.rng_restore(saved, trainer.device)
         self.done.add(step)
         n_rows = max(len(table), 1)
-        return {"event": EVENT, "step": step, "items": sum(v["n"] for v in table.values()), "seconds": round(time.perf_counter() - t0, 3),
-                "exact": round(sum(v["exact"] for v in table.values()) / n_rows, 6), "logp": round(sum(v["logp"] for v in table.values()) / n_rows, 6),
-                "rows": table, "sample": self.sample}
+        head = {"event": EVENT, "step": step, "passes": list(passes), "items": sum(v["n"] for v in table.values()), "seconds": round(time.perf_counter() - t0, 3)}
+        if len(passes) == 1:
+            pooled = {k: round(sum(v[k] for v in table.values()) / n_rows, 6) for k in ("exact", "logp")}
+        else:
+            pooled = {k: {str(t): round(sum(v[k][i] for v in table.values()) / n_rows, 6) for i, t in enumerate(passes)} for k in ("exact", "logp")}
+            pooled.update(gap=pooled_gap([v["gap"] for v in table.values()]), gap_logp=pooled_gap([v["gap_logp"] for v in table.values()]))
+        return {**head, **pooled, "rows": table, "sample": self.sample}

@@ -99,3 +99,31 @@ def test_cells_can_be_chosen_by_name_and_batches_respect_the_token_budget(probe_
     longest = max(len(p.ids) for p in items)
     assert [len(b) for b in R.batches_by_tokens(items, 2 * longest)] == [2, 1] and [len(b) for b in R.batches_by_tokens(items, 1)] == [1, 1, 1]
     assert R.readout_due(train_cfg(probe_file, 3), 3) and R.readout_due(train_cfg(probe_file, 3), 4) and not R.readout_due(train_cfg(probe_file, 3), 2)
+
+
+def test_a_model_with_a_second_pass_is_scored_at_one_pass_and_at_two(tmp_path, probe_file):
+    """The readout of a gated second pass: both pass counts on the same items, gaps paired by item, a record at the switch
+    step; before the gate leaves zero the two pass counts are one function (gap 0); the numbers are the scorer's own."""
+    from gdn_hybrid_architecture_ideas_b200.eval import probes
+
+    cfg = train_cfg(probe_file, 4)
+    cfg.model = C.tiny_control_config()
+    lp = cfg.model.loop
+    lp.pass2_gate, lp.pass2_layers, lp.t_max, lp.t_eval, lp.t_choices, lp.t_probs = "scalar", 4, 2, 2, [2], [1.0]
+    cfg.steps, cfg.loop_switch_step, cfg.optim.pass2_lr_scale, cfg.activation_checkpoint = 8, 2, 50.0, "layer"
+    t = Trainer(cfg, tmp_path / "g")
+    t.fit()
+    recs = records(tmp_path / "g", "readout")
+    assert [r["step"] for r in recs] == [2, 4, 8] and all(r["passes"] == [1, 2] for r in recs)
+    at_switch, last = recs[0], recs[-1]
+    assert at_switch["gap"] == {"mean": 0.0, "se": 0.0} and at_switch["gap_logp"] == {"mean": 0.0, "se": 0.0} and at_switch["logp"]["1"] == at_switch["logp"]["2"]
+    assert last["gap_logp"]["mean"] != 0.0 and last["gap_logp"]["se"] > 0 and set(last["exact"]) == {"1", "2"}
+    row = next(iter(t._probe_readout.rows))
+    t.model.eval()
+    by_pass = [probes.score_probes(t.model, row["probes"], batch_size=len(row["probes"]), passes=p) for p in (1, 2)]
+    got = last["rows"][row["row"]]
+    diffs = [-(b["ce"]) + a["ce"] for a, b in zip(by_pass[0]["items"], by_pass[1]["items"])]
+    assert abs(got["gap_logp"]["mean"] - sum(diffs) / len(diffs)) < 1e-5 and got["exact"] == [round(s["exact"], 6) for s in by_pass]
+    assert abs(last["gap"]["mean"] - sum(v["gap"]["mean"] for v in last["rows"].values()) / len(last["rows"])) < 1e-6
+    assert R.paired_gap([1.0, 0.0, 1.0], [0.0, 0.0, 1.0]) == {"mean": 0.333333, "se": 0.333333} and R.paired_gap([2.0], [1.0]) == {"mean": 1.0, "se": 0.0}
+    assert R.pooled_gap([{"mean": 0.2, "se": 0.3}, {"mean": 0.4, "se": 0.4}]) == {"mean": 0.3, "se": 0.25}
