@@ -307,6 +307,11 @@ class DecoderConfig(_Section):
     n_sinks: int = 4
     local_temperature: str = 'inherit'
 
+    def layer_kinds(self) -> list[str]:
+        """Every `memory_attn_interval`-th decoder layer reads the memory; the others are Gated DeltaNet over the slots."""
+        every = self.memory_attn_interval
+        return ["gdn" if (i + 1) % every else "memory_attention" for i in range(self.n_layers)]
+
 @dataclass
 class LoopConfig(_Section):
     t_max: int = 3
@@ -731,7 +736,7 @@ def apply_override(cfg, assignment: str) -> None:
 # ----------------------------------------------------------------------------------------------------------------
 
 _BUILT = {
-    "model.arch": ("control",),
+    "model.arch": ("control", "looped_ced"),
     "model.ffn_activation": ("swiglu", "relu2"),
     "model.encoder.attention.gate": ("elementwise", "headwise", "none"),
     "model.encoder.attention.temperature": ("fixed", "learned", "ssmax"),
@@ -791,15 +796,17 @@ _TRAIN_BUILT = {
 # long-context reads) and that nothing here reads. They load and round-trip; a value off the default would change nothing,
 # so it is refused by name instead of being ignored.
 _UNREAD = (
-    "model.encoder.write_mix_storage", "model.encoder.write_mix_row_term", "model.decoder.memory_attn_interval", "model.decoder.ffn_experts",
-    "model.decoder.ffn_top_k", "model.decoder.ffn_expert_hidden", "model.decoder.moe_balance_weight", "model.decoder.untie_mixers",
-    "model.decoder.router_z_weight", "model.decoder.memory_kv_per_layer", "model.decoder.capacity_fraction", "model.decoder.capacity_multiple",
-    "model.decoder.self_kv", "model.decoder.read_pattern", "model.decoder.local_window", "model.decoder.local_temperature",
-    "model.loop.draft_loss_weight", "model.loop.depth_attention", "model.loop.depth_attention_head_dim", "model.loop.depth_attention_rope_theta",
-    "model.loop.hc_streams", "model.loop.hc_write", "model.loop.hc_res_init", "model.second_pass.pass_embedding",
+    "model.encoder.write_mix_storage", "model.encoder.write_mix_row_term", "model.decoder.self_kv", "model.decoder.read_pattern",
+    "model.decoder.local_window", "model.decoder.local_temperature", "model.loop.hc_res_init", "model.second_pass.pass_embedding",
     "model.fp8.te_nonfinite_check", "model.fp8.te_operands", "model.fp8.nonfinite_flag", "model.fp8.nonfinite_flag_form",
     "model.cp_head.aux_weight", "model.cp_head.shared_layer", "model.cp_head.shared_head", "model.cp_head.shared_ssmax", "model.cp_head.trunk_k",
     "model.cp_head.trunk_select_step")
+# The slot decoder's keys: read by arch 'looped_ced' (models/looped_decoder.py), by nothing on the hybrid stack.
+_UNREAD_STACK = (
+    "model.decoder.memory_attn_interval", "model.decoder.ffn_experts", "model.decoder.ffn_top_k", "model.decoder.ffn_expert_hidden",
+    "model.decoder.moe_balance_weight", "model.decoder.untie_mixers", "model.decoder.router_z_weight", "model.decoder.memory_kv_per_layer",
+    "model.decoder.capacity_fraction", "model.decoder.capacity_multiple", "model.loop.draft_loss_weight", "model.loop.depth_attention",
+    "model.loop.depth_attention_head_dim", "model.loop.depth_attention_rope_theta", "model.loop.hc_streams", "model.loop.hc_write")
 _TRAIN_UNREAD = (
     "data.span_distribution", "data.span_sigma", "data.answer_min_context", "data.answer_gap_mean", "data.answer_capacity_fraction",
     "data.answer_sinks", "data.answer_replay_window", "optim.hyperball_radius", "optim.soap_shampoo_beta", "optim.soap_precondition_frequency",
@@ -832,7 +839,7 @@ def unsupported_options(cfg) -> list[str]:
             if value not in allowed:
                 bad.append(f"{key}={value!r} (built: {list(allowed)})")
     plain_model, plain_train = ModelConfig(), TrainConfig()
-    for key in _UNREAD:
+    for key in _UNREAD + (_UNREAD_STACK if model.arch != "looped_ced" else ()):
         value, default = _get(model, key[len("model."):]), _get(plain_model, key[len("model."):])
         if value != default:
             bad.append(f"{key}={value!r} (read by nothing here: leave it {default!r})")
@@ -913,6 +920,19 @@ def tiny_control_config() -> ModelConfig:
     gdn = GDNConfig(n_k_heads=2, n_v_heads=4, k_head_dim=16, v_head_dim=16, conv_kernel=4)
     return ModelConfig(arch="control", vocab_size=256, d_model=64, ffn_hidden=192,
                        encoder=EncoderConfig(n_layers=10, full_attn_interval=4, attention=attn, gdn=gdn))
+
+
+def tiny_looped_config() -> ModelConfig:
+    """CPU-sized looped encoder-decoder: 8 encoder layers, a 2-layer decoder block (GDN, memory attention) at up to 3 passes,
+    a quarter of each row's positions in decoder slots."""
+    cfg = tiny_control_config()
+    cfg.arch = "looped_ced"
+    cfg.encoder.n_layers = 8
+    dec = cfg.decoder
+    dec.n_layers, dec.memory_attn_interval, dec.capacity_fraction, dec.capacity_multiple = 2, 2, 0.25, 8
+    dec.attention, dec.gdn = dataclasses.replace(cfg.encoder.attention), dataclasses.replace(cfg.encoder.gdn)
+    cfg.loop.t_max, cfg.loop.t_choices, cfg.loop.t_probs, cfg.loop.t_eval = 3, [2, 3], [0.5, 0.5], 3
+    return cfg
 
 
 def tiny_full_config() -> ModelConfig:

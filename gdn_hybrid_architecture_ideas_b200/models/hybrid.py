@@ -273,10 +273,15 @@ class HybridLM(nn.Module):
         return self.forward(tokens, doc_ids, cache=cache, return_cache=True, T=T, pass_counts=pass_counts, **self._pass2_at(dec_mask, T))
 
 
-def build_model(cfg: ModelConfig) -> HybridLM:
+def build_model(cfg: ModelConfig):
     """Validated model with initial weights: every Linear/Embedding N(0, init_std); norm gains, depth queries and mix
-    lambdas zero; GDN gates by `gdn.init`; low-precision recipes applied last (reference: ced/model/control.py:1246-1346)."""
+    lambdas zero; GDN gates by `gdn.init`; low-precision recipes applied last (reference: ced/model/control.py:1246-1346).
+    arch 'looped_ced' builds the looped encoder-decoder (models/looped_decoder.py)."""
     require_supported(cfg)
+    if cfg.arch == "looped_ced":
+        from .looped_decoder import LoopedCED
+
+        return LoopedCED(cfg)
     from .mtp import attach_mtp, check_mtp
 
     check_mtp(cfg)

@@ -877,3 +877,90 @@ def test_copy_paste_head_is_refused_by_name_where_it_is_not_built():
         C.apply_override(cfg, f"{key}={value}")
         with pytest.raises(ValueError, match=match):
             build_model(cfg)
+
+
+@pytest.mark.parametrize("arm", ["base", "lanes", "depth", "untied", "routed", "per_layer", "scaled"])
+def test_looped_encoder_decoder_equals_the_reference(reference, arm):
+    """arch looped_ced: equal starts under equal seeds, the logits at every position (decoder head at the kept slots, aux
+    head elsewhere), the drafts, the two-head loss's gradients, prefill + cached extension, at T = 1 .. 3 and every loop
+    boundary arm; rows with more decoder positions than slots drop the later ones."""
+    from ced.model.control import build_model as ref_build  # noqa: F401
+
+    cfg = C.tiny_looped_config()
+    lp, dec = cfg.loop, cfg.decoder
+    if arm == "lanes":
+        lp.hyper_connections, lp.injection, lp.hc_streams = "static", "none", 3
+    if arm == "depth":
+        lp.depth_attention, lp.depth_attention_head_dim = "layer", 8
+    if arm == "untied":
+        dec.untie_mixers, dec.n_layers, dec.memory_attn_interval = "all", 3, 3
+    if arm == "routed":
+        dec.ffn_experts, dec.ffn_top_k, dec.router_z_weight = 4, 2, 0.01
+    if arm == "per_layer":
+        dec.n_layers, dec.memory_attn_interval, dec.memory_kv_per_layer, cfg.tie_embeddings = 2, 1, True, False
+    if arm == "scaled":
+        cfg.residual_scale.mode, cfg.residual_scale.lam = "inverse_loops", 1.5
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd)
+    if arm == "base":
+        for change, match in ((lambda c: setattr(c.decoder.attention, "rope_max_distance", 6), "rope_max_distance"), (lambda c: setattr(c.loop, "injection", "mix"), "injection"),
+                              (lambda c: setattr(c.decoder, "memory_attn_interval", 5), "memory-attention"), (lambda c: setattr(c.encoder, "attn_res", "block_entry"), "attn_res"),
+                              (lambda c: setattr(c.loop, "t_eval", 4), "t_eval"), (lambda c: setattr(c.decoder, "untie_mixers", "some"), "untie_mixers")):
+            bad = C.tiny_looped_config()
+            change(bad)
+            with pytest.raises(ValueError, match=match):
+                build_model(bad)
+    g = torch.Generator().manual_seed(3)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40)
+    dm = torch.rand(2, 40, generator=g) < 0.3
+    dm[1, 5:30] = True                                           # more decoder positions than the row's 16 slots: the later ones are dropped
+    tgt = torch.roll(tok, -1, 1)
+    for T in (1, 2, 3):
+        a, b = mine(tok, doc, dm, T=T, return_drafts=True), theirs(tok, doc, dm, T=T, return_drafts=True)
+        assert torch.equal(a.kept, b.kept) and torch.equal(a.n_dropped, b.n_dropped) and int(a.n_dropped[1]) > 0 and torch.equal(a.slot_index, b.slot_index)
+        assert (a.logits - b.logits).abs().max() < 1e-10, T
+        for x, y in zip(a.draft_logits, b.draft_logits):
+            assert (x - y)[a.slot_valid].abs().max() < 1e-10
+    from gdn_hybrid_architecture_ideas_b200.models.looped_decoder import two_head_loss
+
+    a, b = mine(tok, doc, dm, T=3, return_hidden=True, return_drafts=True), theirs(tok, doc, dm, T=3, return_hidden=True, return_drafts=True)
+    valid = torch.ones_like(dm)
+    loss, sums = two_head_loss(mine, a, tgt, valid, n_valid=80.0, n_dec=float(a.kept.sum()), n_aux=float((~a.kept).sum()), z_loss=1e-4, aux_weight=0.5, draft_weight=0.3)
+    W = theirs.head_weight()
+    ce = lambda h, t: torch.nn.functional.cross_entropy(h @ W.t(), t, reduction="none")                  # noqa: E731
+    lse = lambda h: torch.logsumexp(h @ W.t(), -1)                                                          # noqa: E731
+    from ced.model.capacity import gather_slots
+
+    t_slots = gather_slots(tgt, b.slot_index, fill=0)
+    flat = lambda h: h.reshape(-1, h.shape[-1])                                                              # noqa: E731
+    ce_d = (ce(flat(b.hidden_dec), t_slots.reshape(-1)) + 1e-4 * lse(flat(b.hidden_dec)) ** 2).reshape(t_slots.shape)
+    ce_a = (ce(flat(b.hidden_aux), tgt.reshape(-1)) + 1e-4 * lse(flat(b.hidden_aux)) ** 2).reshape(tgt.shape)
+    ref_loss = ((ce_d * b.slot_valid).sum() + 0.5 * (ce_a * ~b.kept).sum()) / 80.0
+    for h in b.hidden_drafts:
+        ref_loss = ref_loss + 0.3 * (ce(flat(h), t_slots.reshape(-1)).reshape(t_slots.shape) * b.slot_valid).sum() / float(b.kept.sum())
+    if b.aux_loss is not None:
+        ref_loss = ref_loss + b.aux_loss
+    assert abs(float(loss) - float(ref_loss)) < 1e-10
+    ga = torch.autograd.grad(loss, list(mine.parameters()), allow_unused=True)
+    gb = torch.autograd.grad(ref_loss, list(theirs.parameters()), allow_unused=True)
+    for (n, _), x, y in zip(mine.named_parameters(), ga, gb):
+        assert (x is None) == (y is None) and (x is None or (x - y).abs().max() < 1e-9), n
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        full = mine(tok, doc, dm, T=2, capacity=40).logits
+        out, ref_out = mine.prefill(tok[:, :17], doc[:, :17], dm[:, :17], T=2), theirs.prefill(tok[:, :17], doc[:, :17], dm[:, :17], T=2)
+        parts = [out.logits]
+        for lo, hi in ((17, 18), (18, 40)):
+            out, ref_out = mine.extend(tok[:, lo:hi], doc[:, lo:hi], dm[:, lo:hi], out.cache), theirs.extend(tok[:, lo:hi], doc[:, lo:hi], dm[:, lo:hi], ref_out.cache)
+            parts.append(out.logits)
+            assert (out.logits - ref_out.logits).abs().max() < 1e-10
+        assert (torch.cat(parts, 1) - full).abs().max() < 1e-9
+        prompt, pdoc, pmask = tok[:, :12], doc[:, :12] * 0, torch.ones(2, 12, dtype=torch.bool)
+        mine_tokens, mine_logits = mine.generate(prompt, pdoc, pmask, 5, T=2)
+        ref_tokens, ref_logits = theirs.generate(prompt, pdoc, pmask, 5, T=2)
+        assert torch.equal(mine_tokens, ref_tokens) and (mine_logits - ref_logits).abs().max() < 1e-10
