@@ -771,7 +771,7 @@ _TRAIN_BUILT = {
     "optim.name": ("adamw", "muon"),
     "optim.hyperball": (False,),
     "optim.gdn_mup": (False, True),
-    "loss.normalization": ("global_token_mean",),
+    "loss.normalization": ("global_token_mean", "per_head_mean"),
     "loss.ce_form": ("standard", "fixed"),
     "head_impl": ("fused", "chunked"),
     "head_precision": ("fp32", "bf16"),
@@ -808,11 +808,11 @@ _UNREAD_STACK = (
     "model.decoder.capacity_fraction", "model.decoder.capacity_multiple", "model.loop.draft_loss_weight", "model.loop.depth_attention",
     "model.loop.depth_attention_head_dim", "model.loop.depth_attention_rope_theta", "model.loop.hc_streams", "model.loop.hc_write")
 _TRAIN_UNREAD = (
-    "data.span_distribution", "data.span_sigma", "data.answer_min_context", "data.answer_gap_mean", "data.answer_capacity_fraction",
+    "data.answer_min_context", "data.answer_gap_mean", "data.answer_capacity_fraction",
     "data.answer_sinks", "data.answer_replay_window", "optim.hyperball_radius", "optim.soap_shampoo_beta", "optim.soap_precondition_frequency",
     "optim.soap_eigh", "optim.shampoo_epsilon", "optim.shampoo_precondition_frequency", "optim.shampoo_start_step", "optim.normuon_beta2",
     "optim.anvil2_preset", "optim.anvil2_single_rounding", "optim.anvil2_tavg", "optim.anvil2_decon", "optim.anvil2_scale", "optim.anvil2_points",
-    "optim.anvil2_tail_ema", "optim.anvil2_qk_head_pairs", "optim.soap_seeded_start", "optim.ours", "loss.aux_weight", "loss.aux_positions",
+    "optim.anvil2_tail_ema", "optim.anvil2_qk_head_pairs", "optim.soap_seeded_start", "optim.ours", "loss.aux_positions",
     "loss.aux_fraction", "eval.replay_window", "eval.decoder_at", "eval.lc_every_steps", "eval.lc_dir", "eval.lc_length", "eval.lc_docs",
     "eval.lc_base_len", "eval.lc_mf_items", "trim_decoder_slots", "pass_slot_buckets", "tst.aux_weight", "stage_shape")
 
@@ -839,6 +839,9 @@ def unsupported_options(cfg) -> list[str]:
             if value not in allowed:
                 bad.append(f"{key}={value!r} (built: {list(allowed)})")
     plain_model, plain_train = ModelConfig(), TrainConfig()
+    if isinstance(cfg, TrainConfig) and model.arch != "looped_ced":       # the two heads' loss keys: the hybrid stack has one head
+        if cfg.loss.aux_weight != plain_train.loss.aux_weight or cfg.loss.normalization != plain_train.loss.normalization:
+            bad.append(f"loss.aux_weight={cfg.loss.aux_weight!r} / loss.normalization={cfg.loss.normalization!r} (the two heads' loss of arch 'looped_ced'; read by nothing on arch {model.arch!r})")
     for key in _UNREAD + (_UNREAD_STACK if model.arch != "looped_ced" else ()):
         value, default = _get(model, key[len("model."):]), _get(plain_model, key[len("model."):])
         if value != default:

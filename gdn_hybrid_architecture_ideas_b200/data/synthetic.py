@@ -97,11 +97,20 @@ class SyntheticPackedData:
     """Rows of seq_len + 1 tokens packed with documents of doc_len_min .. doc_len_max tokens; inside a document a
     token follows its predecessor through one of 4 fixed successors with probability 0.8, else is uniform."""
 
-    def __init__(self, cfg: DataConfig, vocab_size: int):
+    def __init__(self, cfg: DataConfig, vocab_size: int, capacity: int | None = None):
+        """capacity: decoder positions a row marks in spans (the looped encoder-decoder; data/spans.py), None for no mask."""
         self.cfg = cfg
         self.vocab_size = vocab_size
+        self.capacity = capacity
         g = counter_generator(cfg.seed, -1, 0)
         self.successors = torch.randint(0, vocab_size, (vocab_size, 4), generator=g)
+
+    def _spans(self, g: torch.Generator) -> torch.Tensor:
+        from .spans import sample_spans
+
+        c = self.cfg
+        return sample_spans(c.seq_len, self.capacity, g, distribution=c.span_distribution, median=c.span_median, sigma=c.span_sigma,
+                            span_min=c.span_min, span_max=c.span_max)
 
     def _row(self, g: torch.Generator):
         c, n = self.cfg, self.cfg.seq_len + 1
@@ -134,8 +143,11 @@ class SyntheticPackedData:
         rows = [self._row(counter_generator(self.cfg.seed, g // B, 1000 + g % B)) for g in range(first, first + count)]
         seq = torch.stack([r[0] for r in rows])
         docs = torch.stack([r[1] for r in rows])
+        dec = None
+        if self.capacity is not None:        # a generator of the row's own, apart from its tokens'
+            dec = torch.stack([self._spans(counter_generator(self.cfg.seed, g // B, 2000 + g % B)) for g in range(first, first + count)])
         return Batch(tokens=seq[:, :-1].contiguous(), targets=seq[:, 1:].contiguous(),
-                     target_valid=(docs[:, 1:] == docs[:, :-1]).contiguous(), doc_ids=docs[:, :-1].contiguous(),
+                     target_valid=(docs[:, 1:] == docs[:, :-1]).contiguous(), doc_ids=docs[:, :-1].contiguous(), dec_mask=dec,
                      single_doc=self.cfg.doc_len_min > self.cfg.seq_len)
 
 
@@ -161,9 +173,11 @@ class UniformTokens:
                      single_doc=True)
 
 
-def make_data(cfg: DataConfig, vocab_size: int):
+def make_data(cfg: DataConfig, vocab_size: int, capacity: int | None = None):
     if cfg.kind == "synthetic":
-        return SyntheticPackedData(cfg, vocab_size)
+        return SyntheticPackedData(cfg, vocab_size, capacity)
+    if capacity is not None:
+        raise ValueError(f"data.kind {cfg.kind!r}: the looped encoder-decoder's decoder positions are placed on data.kind 'synthetic'")
     if cfg.kind == "uniform":
         return UniformTokens(cfg, vocab_size)
     if cfg.kind == "shards":

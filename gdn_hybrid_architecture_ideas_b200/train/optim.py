@@ -22,6 +22,8 @@ NO_DECAY_SUFFIXES = ("embed.weight", ".A_log", ".dt_bias", ".temp_w", ".skip_gai
                      # a looped middle's injection (models/recur.py): B starts at the identity and w near 1, decay would pull both
                      # away from their starts; A_log / dt_bias are covered by the GDN suffixes above
                      "injection.B", ".recur_mix",
+                     # the lanes of the looped encoder-decoder (models/looped_decoder.py) start as the plain loop: no pull toward 0
+                     "hyper_connections.read_weights", "hyper_connections.mix_weights", "hyper_connections.write_weights",
                      # the Copy-Paste head's <copy> row (the LM head's rule) and its QK-norm gain (the pointer's temperature)
                      "cp_head.w_copy", "cp_head.qk_gain")
 ZERO_GATE_SUFFIXES = (".gdn_arms.ccr_gate", ".gdn_arms.write_lambda", ".gdn_arms.qmix_lambda", ".erase.scale", ".dprod.beta_const")
@@ -52,7 +54,8 @@ def no_decay_suffixes(o) -> tuple:
 def is_muon_param(name: str, p: torch.Tensor) -> bool:
     if p.ndim != 2 or name.endswith(("embed.weight", "conv_weight") + ADAMW_MATRIX_SUFFIXES):
         return False
-    return ".attn_res." not in name and "injection" not in name and not name.startswith("cp_head.")   # loop-boundary and copy-head tensors stay on AdamW
+    # loop-boundary tensors (injection, lanes, loop embedding), routers, depth mixers and the copy head stay on AdamW
+    return not any(part in name for part in (".attn_res.", "injection", "hyper_connections", "router", "loop_embedding")) and not name.startswith("cp_head.")
 
 
 GDN_MUP_BASE_WIDTH = 512

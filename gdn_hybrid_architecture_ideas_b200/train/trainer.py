@@ -73,6 +73,19 @@ class Trainer:
         # A looped middle (models/recur.py): one pass count per optimizer step, drawn from loop.t_choices / t_probs; what it
         # is not built together with is refused here, by key.
         self.looped = bool(cfg.model.loop.recur_layers)
+        # The looped encoder-decoder (models/looped_decoder.py): decoder positions in spans from the data, one pass count per
+        # optimizer step, the two heads' loss.
+        self.slot_decoder = cfg.model.arch == "looped_ced"
+        if self.slot_decoder:
+            clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
+                       "shape_schedule": bool(cfg.shape_schedule), "loop_switch_step": bool(cfg.loop_switch_step), "freeze_trunk": bool(cfg.freeze_trunk),
+                       "optimizer_sharding 'zero2'": cfg.optimizer_sharding == "zero2", "data.kind other than 'synthetic'": cfg.data.kind != "synthetic",
+                       "data.loss_mask": cfg.data.loss_mask != "all", "eval.readout_every": bool(cfg.eval.readout_every),
+                       "eval.every_steps / eval.bpb_readout_every (the scorers call the one-head stack)": bool(cfg.eval.every_steps or cfg.eval.bpb_readout_every),
+                       "activation_checkpoint 'block' / 'host' / 'host_overlap'": cfg.activation_checkpoint in ("block", "host", "host_overlap")}
+            hit = [k for k, v in clashes.items() if v]
+            if hit:
+                raise ValueError(f"model.arch 'looped_ced' is not built together with: {', '.join(hit)}")
         self.gated = cfg.model.loop.pass2_gate != "none"          # a read-only second pass (models/second_pass.py): T = 1 before loop_switch_step, then 2
         self.pass_count = 1
         if self.looped:
@@ -177,7 +190,8 @@ class Trainer:
             from .freeze_trunk import TrunkGuard
 
             self.trunk_guard = TrunkGuard(self.model, ("cp_head.",))       # requires_grad False outside the head; digests taken when the trunk is loaded
-        self.data = make_data(cfg.data, cfg.model.vocab_size)
+        self.capacity = self.model.capacity(cfg.data.seq_len) if self.slot_decoder else None
+        self.data = make_data(cfg.data, cfg.model.vocab_size, self.capacity)
         self.tst = None
         if cfg.tst.schedule:
             from .tst import TSTPlan
@@ -334,9 +348,35 @@ class Trainer:
         except BatchError as e:
             bad, self._bad = 1, e
         n = int(_scored(batch).sum()) if batch.multi_valid is None else int(batch.multi_valid.any(-1).sum())
+        if self.slot_decoder:       # the two heads' own counts: valid targets at the kept slots, and at the other positions
+            from ..models.looped_decoder import select_slots
+
+            kept = select_slots(batch.dec_mask, self.capacity).kept
+            heads = [int((batch.target_valid & kept).sum()), int((batch.target_valid & ~kept).sum())]
+            if self.dp is not None:
+                n, bad, *heads = self.dp.sum_host([n, bad, *heads])
+            self._head_counts = heads
+            return n, bad
         if self.dp is not None and self.tp is None:
             n, bad = self.dp.sum_host([n, bad])
         return n, bad
+
+    def _two_head_micro(self, mb, n_global):
+        """The looped encoder-decoder's micro-batch: (its share of the batch loss, the decoder head's CE sum)."""
+        from ..models.looped_decoder import two_head_loss
+
+        cfg = self.cfg
+        draft = cfg.model.loop.draft_loss_weight
+        with torch.autocast(self.device.type, dtype=torch.bfloat16, enabled=self.autocast and not self.native):
+            out = self.model(mb.tokens, mb.doc_ids, mb.dec_mask, T=self.pass_count, capacity=self.capacity, return_hidden=True, return_drafts=draft > 0)
+        n_dec, n_aux = (max(c, 1) for c in self._head_counts)
+        share = mb.tokens.shape[0] / cfg.data.batch_size           # a routed FFN's balance term counts at the micro-batch's share of the rows
+        loss, sums = two_head_loss(self.model, out, mb.targets, mb.target_valid, float(n_global), float(n_dec), float(n_aux), cfg.loss.z_loss,
+                                   cfg.loss.aux_weight, cfg.loss.normalization, draft, share)
+        for k, v in sums.items():
+            self._head_sums[k] = self._head_sums.get(k, 0) + v
+        self._head_sums["dropped"] = self._head_sums.get("dropped", 0) + out.n_dropped.sum()
+        return loss, sums["ce_dec"] / n_dec
 
     # ------------------------------------------------------------------ one step
 
@@ -344,6 +384,8 @@ class Trainer:
         """n_global: the number of valid targets over all ranks (int), or a 0-dim device tensor holding its inverse
         (CUDA-graph replay: the normaliser must not be baked into the graph)."""
         cfg = self.cfg
+        if self.slot_decoder:
+            return self._two_head_micro(mb, n_global)
         inv = n_global if isinstance(n_global, torch.Tensor) else 1.0 / n_global
         z = cfg.loss.z_loss
         s = mb.tokens.shape[2] if mb.tokens.dim() == 3 else 1
@@ -515,10 +557,11 @@ class Trainer:
         n_global, bad = self._global_counts(batch)
         if bad:
             self._halt_bad_batch(step)
-        if self.looped:
+        if self.looped or self.slot_decoder:
             from ..models.recur import pass_count_for_step
 
             self.pass_count = pass_count_for_step(cfg.model.loop, cfg.seed, step)
+            self._head_sums = {}
         if self.gated:
             self.pass_count = 1 if step < cfg.loop_switch_step else 2
         lr = self.lr_at(step)
@@ -556,6 +599,11 @@ class Trainer:
                 if self.pass_count == 2 and self.model.schedule is not None:      # the share of positions at each pass count in the step's last micro-batch
                     c = self.model.last_counts
                     m["pass_counts"] = {str(k): float((c == k).float().mean()) for k in range(1, self.model.n_passes + 1)}
+        if self.slot_decoder:       # the heads' mean CE over their own counts (one more host read of a few scalars)
+            m["T"] = self.pass_count
+            n_dec, n_aux = (max(c, 1) for c in self._head_counts)
+            for k, v in self._head_sums.items():
+                m[k] = float(v) / (n_aux if k == "ce_aux" else 1 if k in ("moe_balance", "dropped") else n_dec)
         if self.looped:
             m["T"] = self.pass_count
             if self._rows_held is not None:

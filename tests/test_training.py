@@ -1104,4 +1104,54 @@ def test_keys_that_nothing_reads_are_refused_off_their_defaults():
 
     orphans = [full for full, leaf in leaves(C.TrainConfig) if not re.search(r"\b" + re.escape(leaf) + r"\b", src) and leaf not in tables
                and not full.startswith("optim.ours.")]
-    assert orphans == ["model.residual_scale.t_ref", "model.residual_scale.l_ref"], orphans      # (the two belong to residual-scale modes whose factor does not read them)
+    assert orphans == [], orphans
+
+
+def test_looped_encoder_decoder_trains_through_the_trainer(tmp_path):
+    """arch looped_ced: decoder positions in spans from the data (exactly the row's capacity, from a generator of their own),
+    a pass count per step, the two heads' loss and metrics, loop-boundary tensors on AdamW without decay, a bit-exact resume;
+    the accumulated gradient does not depend on the micro-batch size; refusals by key."""
+    from gdn_hybrid_architecture_ideas_b200.models.recur import pass_count_for_step
+    from gdn_hybrid_architecture_ideas_b200.train.optim import param_groups
+
+    cfg = tiny_train_config(steps=4)
+    cfg.model = C.tiny_looped_config()
+    cfg.model.loop.hyper_connections, cfg.model.loop.draft_loss_weight = "static", 0.2
+    cfg.loss.aux_weight, cfg.ckpt_every_steps, cfg.dtype = 0.5, 2, "float64"
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "r")
+    assert t.capacity == 16 and t.data.capacity == 16
+    b0 = t.batch_at(0)
+    assert b0.dec_mask.shape == b0.tokens.shape and b0.dec_mask.sum(1).tolist() == [16] * cfg.data.batch_size
+    assert torch.equal(b0.dec_mask, t.batch_at(0).dec_mask) and not torch.equal(b0.dec_mask, t.batch_at(1).dec_mask)
+    groups = param_groups(t.model, cfg.optim)
+    kind = {n: (g["kind"], g["weight_decay"]) for g in groups for n in g["names"]}
+    assert kind["injection.B"] == ("adamw", 0.0) and kind["hyper_connections.mix_weights"] == ("adamw", 0.0) and kind["loop_embedding"][0] == "adamw"
+    ms = [t.train_step() for _ in range(4)]
+    assert [m["T"] for m in ms] == [pass_count_for_step(cfg.model.loop, cfg.seed, s) for s in range(4)]
+    assert all(math.isfinite(m["loss"]) and m["ce_dec"] > 0 and m["ce_aux"] > 0 and m["dropped"] == 0 for m in ms)
+    assert any("ce_draft_loop1" in m for m in ms) and ms[-1]["loss"] < ms[0]["loss"] + 0.5
+    whole, halves = Trainer(copy.deepcopy(cfg), tmp_path / "w"), copy.deepcopy(cfg)
+    halves.micro_batch_size = cfg.data.batch_size // 2
+    halves = Trainer(halves, tmp_path / "h")
+    for tr in (whole, halves):
+        tr.train_step()
+    assert (whole.flat.grads - halves.flat.grads).abs().max() < 2e-6 * float(whole.flat.grads.abs().max())
+    a = Trainer(copy.deepcopy(cfg), tmp_path / "a")
+    a.fit()
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(until_step=2)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 2
+    c.fit()
+    for (k, x), (_, y) in zip(a.model.state_dict().items(), c.model.state_dict().items()):
+        assert torch.equal(x, y), k
+    for change, match in ((lambda c: setattr(c, "cuda_graphs", "microbatch"), "cuda_graphs"), (lambda c: setattr(c.data, "kind", "uniform"), "data.kind"),
+                          (lambda c: setattr(c, "freeze_trunk", True), "freeze_trunk|looped_ced")):
+        bad = copy.deepcopy(cfg)
+        change(bad)
+        with pytest.raises(ValueError, match=match):
+            Trainer(bad, None)
+    plain = tiny_train_config(steps=2)
+    plain.loss.aux_weight = 0.5
+    with pytest.raises(ValueError, match="aux_weight"):
+        Trainer(plain, None)
