@@ -203,8 +203,14 @@ def score_probes(model, probes: list[Probe], batch_size: int = 8, autocast_dtype
             n = len(p.ids) - 1
             tok[b, :n], tgt[b, :n] = torch.tensor(p.ids[:-1]), torch.tensor(p.ids[1:])
             doc[b, :n] = 0
+        extra = {} if passes is None else {"T": passes}
+        if model.cfg.arch == "looped_ced":        # the answer's positions run the decoder (their next token is generated); every slot is kept
+            dec = torch.zeros_like(tok, dtype=torch.bool)
+            for b, p in enumerate(group):
+                dec[b, p.answer_start - 1: p.answer_start - 1 + p.answer_len] = True
+            extra.update(dec_mask=dec.to(dev), capacity=width)
         with torch.autocast(dev.type, dtype=autocast_dtype, enabled=autocast_dtype is not None):
-            logits = model(tok.to(dev), doc.to(dev), **({} if passes is None else {"T": passes})).logits
+            logits = model(tok.to(dev), doc.to(dev), **extra).logits
         ce = token_cross_entropy(logits, tgt.to(dev)).cpu()
         top = logits.argmax(-1).cpu()
         for b, p in enumerate(group):

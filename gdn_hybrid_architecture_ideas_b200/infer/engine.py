@@ -51,6 +51,9 @@ class DecodeEngine:
         self.next_tokens = z("next_tokens", B, torch.long)      # static output of the step
         self.logits = z("logits", (B, self.cfg.vocab_size), torch.float32)
         self.layers = []
+        if self.cfg.arch != "control":
+            raise ValueError(f"the decode engine runs the hybrid stack (model.arch 'control'); arch {self.cfg.arch!r} generates through the model's own "
+                             "cached forward (LoopedCED.generate)")
         if self.cfg.encoder.attn_res in ("block", "ldm"):
             raise ValueError(f"the decode engine walks the plain and the block-entry stacks; model.encoder.attn_res {self.cfg.encoder.attn_res!r} "
                              "generates through the model's cached forward (eval.generate)")

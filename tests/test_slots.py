@@ -94,3 +94,29 @@ def test_spans_equal_the_reference_draw_for_draw(reference):
     for seed in range(60):
         for L, n, kw in ((64, 16, dict(median=5.0, span_min=2, span_max=12)), (200, 50, {}), (40, 39, dict(distribution="uniform", span_min=3, span_max=9))):
             assert torch.equal(sample_spans(L, n, torch.Generator().manual_seed(seed), **kw), theirs(L, n, torch.Generator().manual_seed(seed), **kw))
+
+
+def test_the_probe_scorer_runs_the_looped_model_with_the_answer_at_decoder_positions():
+    """Stored probes score a looped encoder-decoder: the answer's positions run the decoder, every slot kept; the numbers are
+    those of the model's own forward on the same mask."""
+    from gdn_hybrid_architecture_ideas_b200.eval import probes
+
+    torch.manual_seed(0)
+    cfg = C.tiny_looped_config()
+    model = build_model(cfg).eval()
+    items = [probes.build_probe(kind, cfg.vocab_size, 48, 0, i) for kind in ("needle", "copy") for i in range(2)]
+    res = probes.score_probes(model, items, batch_size=4, passes=2)
+    assert res["n"] == 4 and all(math.isfinite(it["ce"]) for it in res["items"])
+    p = items[0]
+    ids = torch.tensor(p.ids)[None]
+    dec = torch.zeros(1, len(p.ids) - 1, dtype=torch.bool)
+    dec[0, p.answer_start - 1: p.answer_start - 1 + p.answer_len] = True
+    with torch.no_grad():
+        logits = model(ids[:, :-1], torch.zeros_like(ids[:, :-1]), dec, T=2, capacity=dec.shape[1]).logits
+    sl = slice(p.answer_start - 1, p.answer_start - 1 + p.answer_len)
+    ce = torch.nn.functional.cross_entropy(logits[0, sl].float(), ids[0, 1:][sl])
+    assert abs(float(ce) - res["items"][0]["ce"]) < 1e-4
+    with pytest.raises(ValueError, match="arch"):
+        from gdn_hybrid_architecture_ideas_b200.infer.engine import DecodeEngine
+
+        DecodeEngine(model, 1, 64, device="cpu", use_graph=False)
