@@ -337,6 +337,24 @@ class LoopedCache:
 
 
 @dataclass
+class Chunk:
+    """What the passes need of a chunk: the bookkeeping and caches after its encoder, the memory of all positions so far,
+    the aux head's input, the slots and the injected input e (B, C, d)."""
+
+    seq_state: SeqState
+    encoder: list
+    memory: list
+    aux_hidden: torch.Tensor
+    slots: Slots
+    at: SlotContext
+    e: torch.Tensor
+
+    @property
+    def seq(self):
+        return self.seq_state
+
+
+@dataclass
 class LoopedOutput:
     logits: torch.Tensor | None          # (B, L, V): the decoder head at the kept positions, the aux head elsewhere
     kept: torch.Tensor
@@ -418,6 +436,36 @@ class LoopedCED(nn.Module):
         wide = torch.promote_types(hidden.dtype, torch.float32)
         return F.linear(hidden.to(wide), self.head_weight().to(wide))
 
+    def encode(self, tokens, doc_ids, dec_mask, capacity: int, cache) -> "Chunk":
+        """The encoder over a chunk's positions, the aux head's input, the slots, the memory and the injected input. cache:
+        anything with `seq`, `encoder` and `memory` of the earlier chunks (or None)."""
+        ctx, seq_state = sequence_context(doc_ids, cache.seq if cache else None)
+        h, enc_caches = self.encoder(self.embed_norm(self.embed(tokens)), ctx, cache.encoder if cache else None)
+        slots = select_slots(dec_mask, capacity)
+        memory = [KeySet.cat(cache.memory[i] if cache else None, mem(h, ctx, ~slots.kept)) for i, mem in enumerate(self.memory_kv)]
+        at = SlotContext(idx=slots.take(ctx.idx, -1), doc=slots.take(ctx.doc, -1), pos=slots.take(ctx.pos, 0), valid=slots.valid)
+        return Chunk(seq_state, enc_caches, memory, self.aux_norm(h), slots, at, self.inject_norm(slots.take(h)))
+
+    def run_pass(self, k: int, chunk: "Chunk", Y, own_past: list | None, stacks: list | None = None):
+        """Pass k of the shared block over the chunk's slots: (the lanes after it, this pass's cache entries by layer)."""
+        lanes = self.hyper_connections
+        z = lanes.read(Y, k)
+        u = self.injection(z, chunk.e)
+        if self.loop_embedding is not None:
+            u = u + self.loop_embedding[k]
+        entries = []
+        for l, layer in enumerate(self.decoder_layers):
+            mem = chunk.memory[self.memory_of[l]] if layer.kind == "memory_attention" else None
+            u, entry = layer(u, chunk.at, mem, own_past[l] if own_past else None, k, depth=k * len(self.decoder_layers) + l,
+                             stack=None if stacks is None else stacks[l])
+            entries.append(entry)
+        return lanes.write(Y, z, u, k), entries
+
+    def slot_logits(self, Y, passes_done: int, T: int):
+        """(B, C, V) from the lanes after `passes_done` passes: the decoder head's when all T ran, else that draft's."""
+        norm = self.decoder_norm if passes_done == T else self.readout_norms[passes_done - 1]
+        return self._head(norm(self.hyper_connections.finish(Y)))
+
     def forward(self, tokens, doc_ids, dec_mask, T: int | None = None, capacity: int | None = None, cache: LoopedCache | None = None,
                 return_cache: bool = False, return_drafts: bool = False, return_hidden: bool = False) -> LoopedOutput:
         """tokens, doc_ids (B, L); dec_mask (B, L) bool, True where the position's next token is generated. capacity: the
@@ -433,33 +481,18 @@ class LoopedCED(nn.Module):
         routed = [layer.mlp for layer in self.decoder_layers if isinstance(layer.mlp, RoutedSwiGLU)]
         for mlp in routed:
             mlp.reset_stats()
-        ctx, seq_state = sequence_context(doc_ids, cache.seq if cache else None)
-        h, enc_caches = self.encoder(self.embed_norm(self.embed(tokens)), ctx, cache.encoder if cache else None)
-        aux_hidden = self.aux_norm(h)
-        slots = select_slots(dec_mask, capacity)
-        memory = [KeySet.cat(cache.memory[i] if cache else None, mem(h, ctx, ~slots.kept)) for i, mem in enumerate(self.memory_kv)]
-        at = SlotContext(idx=slots.take(ctx.idx, -1), doc=slots.take(ctx.doc, -1), pos=slots.take(ctx.pos, 0), valid=slots.valid)
-        e = self.inject_norm(slots.take(h))
-        lanes = self.hyper_connections
-        Y = lanes.start(e)
+        chunk = self.encode(tokens, doc_ids, dec_mask, capacity, cache)
+        slots, aux_hidden, lanes = chunk.slots, chunk.aux_hidden, self.hyper_connections
+        Y = lanes.start(chunk.e)
         stacks = [[] for _ in self.decoder_layers] if cfg.loop.depth_attention == "layer" else None
         own, drafts = [], []
         for k in range(T):
-            z = lanes.read(Y, k)
-            u = self.injection(z, e)
-            if self.loop_embedding is not None:
-                u = u + self.loop_embedding[k]
-            entries = []
-            for l, layer in enumerate(self.decoder_layers):
-                mem = memory[self.memory_of[l]] if layer.kind == "memory_attention" else None
-                u, entry = layer(u, at, mem, cache.own[k][l] if cache else None, k, depth=k * len(self.decoder_layers) + l,
-                                 stack=None if stacks is None else stacks[l])
-                entries.append(entry)
+            Y, entries = self.run_pass(k, chunk, Y, cache.own[k] if cache else None, stacks)
             own.append(entries)
-            Y = lanes.write(Y, z, u, k)
             if return_drafts and k < T - 1:
                 drafts.append(self.readout_norms[k](lanes.finish(Y)))
         final = self.decoder_norm(lanes.finish(Y))
+        seq_state, enc_caches, memory = chunk.seq_state, chunk.encoder, chunk.memory
         logits = None if return_hidden else slots.put(self._head(aux_hidden), self._head(final))
         aux_loss = None
         if routed:

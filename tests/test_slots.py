@@ -120,3 +120,37 @@ def test_the_probe_scorer_runs_the_looped_model_with_the_answer_at_decoder_posit
         from gdn_hybrid_architecture_ideas_b200.infer.engine import DecodeEngine
 
         DecodeEngine(model, 1, 64, device="cpu", use_graph=False)
+
+
+def test_loopspec_emits_the_greedy_tokens_of_two_passes():
+    """Speculative decoding from the first pass: exactly `generate` at T = 2 whatever the acceptance; a model whose draft head
+    is its decoder head after an identity second pass accepts everything; the statistics count steps and accepts."""
+    from gdn_hybrid_architecture_ideas_b200.infer.loopspec import LoopSpec
+
+    torch.manual_seed(0)
+    cfg = C.tiny_looped_config()
+    model = build_model(cfg).double().eval()
+    g = torch.Generator().manual_seed(2)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    prompt = torch.randint(0, cfg.vocab_size, (1, 14), generator=g)
+    doc, dec = torch.zeros_like(prompt), torch.zeros_like(prompt, dtype=torch.bool)
+    dec[0, 9:] = True
+    want, _ = model.generate(prompt, doc, dec, 12, T=2)
+    got, stats = LoopSpec(model).generate(prompt, doc, dec, 12)
+    assert got == want[0].tolist() and stats.steps == 11 and stats.accepted == sum(stats.flags) and 0 <= stats.acceptance <= 1
+    assert LoopSpec(model).generate(prompt, doc, dec, 1)[0] == want[0, :1].tolist()
+    with torch.no_grad():                    # the draft norm equal to the decoder norm and a second pass that changes nothing: every draft is right
+        model.readout_norms[0].weight.copy_(model.decoder_norm.weight)
+        for layer in model.decoder_layers:
+            layer.residual_scale = 0.0
+        model.injection.A_log.fill_(-30.0)               # decay 1: the injection passes the state through
+        model.injection.B.zero_()
+        model.loop_embedding.zero_()
+    same, stats = LoopSpec(model).generate(prompt, doc, dec, 8)
+    assert same == model.generate(prompt, doc, dec, 8, T=2)[0][0].tolist() and stats.acceptance == 1.0
+    bad = C.tiny_looped_config()
+    bad.loop.depth_attention, bad.loop.depth_attention_head_dim = "layer", 8
+    with pytest.raises(ValueError, match="depth_attention"):
+        LoopSpec(build_model(bad))
