@@ -18,10 +18,14 @@ appends its own before its queries read (tau = t included).
 Options built: `qk_norm` (q and k RMS-normed over d_c at eps 2^-23, q times 1 + `qk_gain`), `init: spec` (every tensor
 N(0, init_std)) / `reference` (W_Q, W_K U(+-sqrt(3 / d)), the sink N(0, 1 / d_c)), the length rule (`temperature: ssmax`:
 q times ln(n_t) / ln(ref); `sink_count`: e_sink + ln(n_t / ref); n_t the context positions a query sees, ref the global
-layers' temperature_ref_len), `force_lambda_zero`, `query_chunk`. The tensors are registered after every other tensor and
-drawn from a generator of their own, so the base model starts as the model without the key. Refused by name: pointers that
-read the depth sources or an attention head (`pointer_input` mix / shared), several pointer heads, the copy from the trunk's
-own attention (`trunk_copy`), the auxiliary and add-on training modes, a band (`window`), the fused kernel.
+layers' temperature_ref_len), `force_lambda_zero`, `query_chunk`, a band (`window` W: a query sees the W latest context
+positions; without the length rule, which counts them all), and the pointer that reads the depth sources
+(`pointer_input: mix`, on a block-entry stack: x^q and x^k are two depth reads of their own over the finished blocks
+[b_0 .. b_N], each through a norm of its own, readers and norms zeros at the start so that both start as the stream's mean
+read; q = W_Q x^q, k = W_K x^k, the <copy> row and the LM head still read h; `cp_head.mix.*`). The tensors are registered
+after every other tensor and drawn from a generator of their own, so the base model starts as the model without the key.
+Refused by name: the pointer that reads an attention head (`pointer_input: shared`), several pointer heads, the copy from
+the trunk's own attention (`trunk_copy`), the auxiliary and add-on training modes, the fused kernel.
 Reference: ced/model/cp_head.py:1-100 (the form), :454-660 (the module), :899-1016 (length rule, block terms),
 :1223-1245 (mixture), :1282-1370 (inference), :1443-1483 (cache).
 """
@@ -41,7 +45,9 @@ from torch.utils.checkpoint import checkpoint as recompute
 
 OWN_SEED_OFFSET = 0xC0_2610_19247        # shared with the reference: equal starts under equal seeds
 NORM_EPS = 2.0 ** -23
-BASE_FORM = dict(pointer_input="final", n_heads=1, combine="and", trunk_copy="none", train_mode="mixture", window=0, kernel="reference")
+BASE_FORM = dict(n_heads=1, combine="and", trunk_copy="none", train_mode="mixture", kernel="reference")
+POINTER_INPUTS = ("final", "mix")
+SOURCES_KEY = "cp_pointer_sources"       # where a block-entry stack leaves [b_0 .. b_N] for the pointer's readers (SeqContext.memo)
 CHOICES = dict(init=("spec", "reference"), score=("mixture", "lm"), temperature=("none", "ssmax"))
 ENV_SCORE = "GHB_CP_SCORE"               # a scoring process's override of model.cp_head.score
 
@@ -52,8 +58,17 @@ def check_config(cfg) -> None:
         return
     off_base = [f"{name} {getattr(head, name)!r}" for name, base in BASE_FORM.items() if getattr(head, name) != base]
     if off_base:
-        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built in its base form (pointer_input 'final', one pointer head, "
-                         "train_mode 'mixture', no band, no trunk copy, kernel 'reference')")
+        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built with one pointer head, train_mode 'mixture', no trunk copy, "
+                         "kernel 'reference'")
+    if head.pointer_input not in POINTER_INPUTS:
+        raise ValueError(f"model.cp_head.pointer_input {head.pointer_input!r}: built are {POINTER_INPUTS} (the final norm's output, or depth reads of the finished blocks)")
+    if type(head.window) is not int or head.window < 0:
+        raise ValueError(f"model.cp_head.window {head.window!r}: the pointer's reach in positions, an integer >= 1 (0: every earlier position)")
+    if head.window and (head.temperature != "none" or head.sink_count or head.pointer_input != "final"):
+        raise ValueError(f"model.cp_head.window {head.window} is built on the base pointer without the length rule: temperature 'none', sink_count false, "
+                         "pointer_input 'final' (the rule counts every earlier position, which a band does not see)")
+    if head.pointer_input == "mix" and (cfg.encoder.attn_res != "block_entry" or cfg.encoder.attn_res_query == "token" or cfg.encoder.attn_res_heads != 1):
+        raise ValueError("model.cp_head.pointer_input 'mix' reads the finished blocks of model.encoder.attn_res 'block_entry' through static one-softmax readers")
     for name in ("d_c", "query_chunk"):
         if type(getattr(head, name)) is not int or getattr(head, name) < 1:
             raise ValueError(f"model.cp_head.{name} {getattr(head, name)!r}: an integer >= 1")
@@ -84,14 +99,52 @@ def _no_autocast(x: torch.Tensor):
     return torch.autocast(x.device.type, enabled=False)
 
 
+class PointerMix(nn.Module):
+    """The two depth reads of `pointer_input: mix`: x^q = norm_q(read_q(sources)), x^k = norm_k(read_k(sources)); a reader is
+    the stack's static block-entry reader (zeros: the sources' mean)."""
+
+    def __init__(self, d_model: int, eps: float):
+        super().__init__()
+        from .depth_mix import DepthQuery
+        from .norms import RMSNorm
+
+        self.read_q, self.read_k = DepthQuery(d_model, eps), DepthQuery(d_model, eps)
+        self.norm_q, self.norm_k = RMSNorm(d_model, eps), RMSNorm(d_model, eps)
+
+    def forward(self, sources: list) -> "PointerInputs":
+        return PointerInputs(self.norm_q(self.read_q(sources)), self.norm_k(self.read_k(sources)))
+
+
+class PointerInputs(NamedTuple):
+    """What the pointer's query and key projections read in one forward, each (B, L, d); the forward hands them on as
+    `ModelOutput.cp_pointer` and every scoring function takes them as `pointer=`."""
+
+    q: torch.Tensor
+    k: torch.Tensor
+
+
+def pointer_sides(head, hidden, pointer):
+    """(the query side's input, the key side's input): h twice for the base pointer, the forward's reads under `mix`."""
+    if head.cfg.pointer_input == "final":
+        if pointer is not None:
+            raise ValueError("pointer inputs were given to a Copy-Paste head whose pointer reads h (model.cp_head.pointer_input 'final')")
+        return hidden, hidden
+    if pointer is None:
+        raise ValueError("this Copy-Paste head's pointer reads the finished blocks (model.cp_head.pointer_input 'mix'): pass the forward's "
+                         "ModelOutput.cp_pointer as pointer=")
+    return pointer.q, pointer.k
+
+
 class CopyPasteHead(nn.Module):
-    def __init__(self, d_model: int, cfg, ref_len: int = 8192):
+    def __init__(self, d_model: int, cfg, ref_len: int = 8192, eps: float = 1e-6):
         super().__init__()
         self.cfg, self.ref_len, self.scale = cfg, int(ref_len), cfg.d_c ** -0.5
         for name, shape in (("w_q", (cfg.d_c, d_model)), ("w_k", (cfg.d_c, d_model)), ("k_sink", (cfg.d_c,)), ("w_copy", (d_model,))):
             self.register_parameter(name, nn.Parameter(torch.empty(shape)))
         if cfg.qk_norm:
             self.qk_gain = nn.Parameter(torch.zeros(1))
+        if cfg.pointer_input == "mix":
+            self.mix = PointerMix(d_model, eps)
 
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float, init: str = "spec") -> None:
@@ -128,14 +181,16 @@ class CopyPasteHead(nn.Module):
         return self._project(h, self.w_copy.unsqueeze(0), False)[..., 0]
 
     def rule(self) -> "LengthRule":
-        return LengthRule(self.cfg.temperature == "ssmax", bool(self.cfg.sink_count), self.ref_len, self.scale)
+        return LengthRule(self.cfg.temperature == "ssmax", bool(self.cfg.sink_count), self.ref_len, self.scale, self.cfg.window)
 
 
 def attach(model) -> None:
     """Registers the head on the model, drawn from a generator of its own."""
     mc = model.cfg
     seed = (torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63)
-    model.cp_head = CopyPasteHead(mc.d_model, mc.cp_head, mc.encoder.attention.temperature_ref_len)
+    model.cp_head = CopyPasteHead(mc.d_model, mc.cp_head, mc.encoder.attention.temperature_ref_len, mc.norm_eps)
+    if mc.cp_head.pointer_input == "mix":
+        model.encoder.keep_sources = True        # the stack leaves [b_0 .. b_N] in the forward's memo
     model.cp_head.reset_own(torch.Generator().manual_seed(seed), mc.init_std, mc.cp_head.init)
 
 
@@ -184,6 +239,7 @@ class LengthRule(NamedTuple):
     sink_count: bool
     ref_len: int
     scale: float
+    window: int = 0
 
 
 class Scores(NamedTuple):
@@ -196,9 +252,11 @@ class Scores(NamedTuple):
         return Pointer(self.sink - self.norm_all, self.norm_ctx - self.norm_all, log_copy)
 
 
-def context_mask(k_idx, k_doc, q_idx, q_doc):
-    """(B, C, S): key s is a context position of query i (not later, same document)."""
-    return (k_doc.unsqueeze(1) == q_doc.unsqueeze(2)).logical_and_(k_idx.unsqueeze(1) <= q_idx.unsqueeze(2))
+def context_mask(k_idx, k_doc, q_idx, q_doc, window: int = 0):
+    """(B, C, S): key s is a context position of query i (not later, same document; with a band, fewer than `window` back)."""
+    back = q_idx.unsqueeze(2) - k_idx.unsqueeze(1)
+    seen = (k_doc.unsqueeze(1) == q_doc.unsqueeze(2)).logical_and_(back >= 0)
+    return seen.logical_and_(back < window) if window else seen
 
 
 def attend(rule: LengthRule, q, k, k_sink, visible) -> Scores:
@@ -220,7 +278,7 @@ def attend(rule: LengthRule, q, k, k_sink, visible) -> Scores:
 
 def _train_block(rule, q, k, k_sink, k_tok, k_doc, k_idx, q_idx, q_doc, q_tgt):
     """One block of queries: the three terms as a plain tuple (what a recomputed block returns)."""
-    sc = attend(rule, q, k, k_sink, context_mask(k_idx, k_doc, q_idx, q_doc))
+    sc = attend(rule, q, k, k_sink, context_mask(k_idx, k_doc, q_idx, q_doc, rule.window))
     hit = (k_tok.unsqueeze(1) == q_tgt.unsqueeze(2)) & torch.isfinite(sc.e)
     none = ~hit.any(-1)
     # a row without a matching key is read as zeros: its LSE is finite, its gradient exactly zero, its result -inf below
@@ -230,16 +288,17 @@ def _train_block(rule, q, k, k_sink, k_tok, k_doc, k_idx, q_idx, q_doc, q_tgt):
 
 
 def terms(head, hidden, tokens, targets, doc_ids, chunk: int | None = None, checkpoint: bool = False, keys: CopyKeys | None = None,
-          q_idx: torch.Tensor | None = None) -> Pointer:
+          q_idx: torch.Tensor | None = None, pointer: PointerInputs | None = None) -> Pointer:
     """The pointer's terms at every position of a forward. keys: the key side (default this forward's own positions at
     indices 0 .. L - 1: a block of queries then reads the keys up to its own end only)."""
     B, L = tokens.shape
     step = chunk or head.cfg.query_chunk
-    q = head.queries(hidden)
+    q_side, k_side = pointer_sides(head, hidden, pointer)
+    q = head.queries(q_side)
     causal_cut = keys is None
     if causal_cut:
         at = torch.arange(L, device=tokens.device).expand(B, L)
-        keys, q_idx = CopyKeys(head.keys(hidden), tokens, doc_ids, at), at
+        keys, q_idx = CopyKeys(head.keys(k_side), tokens, doc_ids, at), at
     sink_key = head.k_sink.to(q.dtype)
     block = partial(_train_block, head.rule())
     if checkpoint and torch.is_grad_enabled():
@@ -252,11 +311,12 @@ def terms(head, hidden, tokens, targets, doc_ids, chunk: int | None = None, chec
     return Pointer(*(torch.cat(column, dim=1) for column in zip(*blocks)))
 
 
-def terms_naive(head, hidden, tokens, targets, doc_ids) -> Pointer:
+def terms_naive(head, hidden, tokens, targets, doc_ids, pointer: PointerInputs | None = None) -> Pointer:
     """The same three terms with every score of a row at once and the softmaxes taken explicitly (tests; small rows)."""
     B, L = tokens.shape
     at = torch.arange(L, device=tokens.device).expand(B, L)
-    sc = attend(head.rule(), head.queries(hidden), head.keys(hidden), head.k_sink.to(_wide(hidden)), context_mask(at, doc_ids, at, doc_ids))
+    q_side, k_side = pointer_sides(head, hidden, pointer)
+    sc = attend(head.rule(), head.queries(q_side), head.keys(k_side), head.k_sink.to(_wide(hidden)), context_mask(at, doc_ids, at, doc_ids, head.cfg.window))
     with_sink = torch.cat([sc.sink.unsqueeze(-1), sc.e], dim=-1).softmax(-1)
     share = with_sink[..., 0]
     p_copy = (sc.e.softmax(-1) * (tokens.unsqueeze(1) == targets.unsqueeze(2))).sum(-1)
@@ -289,8 +349,9 @@ class Mixture:
         return torch.logaddexp((self.log_keep - self.lse_v).unsqueeze(-1) + logits, self.log_lam.unsqueeze(-1) + log_copy)
 
 
-def logprobs_rows(head, hidden_q, q_idx, q_doc, keys: CopyKeys, weight_v, chunk: int | None = None):
-    """log p over V (B, P, V) at the queries, block by block ((B, C, S) alpha and (B, C, V) p_CP at a time)."""
+def logprobs_rows(head, hidden_q, q_idx, q_doc, keys: CopyKeys, weight_v, chunk: int | None = None, q_side=None):
+    """log p over V (B, P, V) at the queries, block by block ((B, C, S) alpha and (B, C, V) p_CP at a time). q_side: what the
+    query projection reads when that is not the hidden states (`pointer_input: mix`)."""
     wide = _wide(hidden_q)
     step = chunk or head.cfg.query_chunk
     rule, rows = head.rule(), []
@@ -299,7 +360,8 @@ def logprobs_rows(head, hidden_q, q_idx, q_doc, keys: CopyKeys, weight_v, chunk:
         for lo in range(0, hidden_q.shape[1], step):
             span = slice(lo, lo + step)
             h = hidden_q[:, span].to(wide)
-            sc = attend(rule, head.queries(h), k, sink_key, context_mask(keys.idx, keys.doc, q_idx[:, span], q_doc[:, span]))
+            q = head.queries(h if q_side is None else q_side[:, span].to(wide))
+            sc = attend(rule, q, k, sink_key, context_mask(keys.idx, keys.doc, q_idx[:, span], q_doc[:, span], rule.window))
             weights = (sc.e - sc.norm_ctx.unsqueeze(-1)).exp()                                      # alpha: softmax over the context alone
             logits = F.linear(h, vocab)
             p_copy = torch.zeros_like(logits).scatter_add_(2, keys.tok.unsqueeze(1).expand_as(weights), weights)
@@ -309,17 +371,18 @@ def logprobs_rows(head, hidden_q, q_idx, q_doc, keys: CopyKeys, weight_v, chunk:
     return torch.cat(rows, dim=1)
 
 
-def forward_logits(model, hidden, tokens, doc_ids, idx, cache: CopyCache | None):
+def forward_logits(model, hidden, tokens, doc_ids, idx, cache: CopyCache | None, pointer: PointerInputs | None = None):
     """(the model's `logits` of a forward: log p over V, or p_LM's logits under score 'lm'; the copy cache after the chunk)."""
     wide = _wide(hidden)
+    q_side, k_side = pointer_sides(model.cp_head, hidden, pointer)
     with _no_autocast(hidden):
-        keys = CopyKeys(model.cp_head.keys(hidden.to(wide)), tokens, doc_ids, idx)
+        keys = CopyKeys(model.cp_head.keys(k_side.to(wide)), tokens, doc_ids, idx)
         if cache is not None and cache.keys is not None:
             keys = cache.keys.extend(keys)                              # a chunk appends its own keys before its queries read
         if _lm_only(model):
             out = F.linear(hidden.to(wide), model.lm_head_weight().to(wide))
         else:
-            out = logprobs_rows(model.cp_head, hidden, idx, doc_ids, keys, model.lm_head_weight())
+            out = logprobs_rows(model.cp_head, hidden, idx, doc_ids, keys, model.lm_head_weight(), q_side=None if pointer is None else q_side)
     return out, CopyCache(keys)
 
 
@@ -339,30 +402,30 @@ def token_lse_zy(hidden, weight, targets, chunk: int = 1024):
     return torch.cat(lse).view_as(targets), torch.cat(z_y).view_as(targets)
 
 
-def _mixture_at_targets(head, hidden, lse, tokens, targets, doc_ids, checkpoint: bool):
+def _mixture_at_targets(head, hidden, lse, tokens, targets, doc_ids, checkpoint: bool, pointer=None):
     with _no_autocast(hidden):
-        ptr = Pointer(*(t.to(lse.dtype) for t in terms(head, hidden, tokens, targets, doc_ids, checkpoint=checkpoint)))
+        ptr = Pointer(*(t.to(lse.dtype) for t in terms(head, hidden, tokens, targets, doc_ids, checkpoint=checkpoint, pointer=pointer)))
         return Mixture.of(lse, head.copy_logit(hidden).to(lse.dtype), ptr), ptr
 
 
-def head_token_ce(model, hidden, targets, tokens, doc_ids, chunk: int = 1024):
+def head_token_ce(model, hidden, targets, tokens, doc_ids, chunk: int = 1024, pointer: PointerInputs | None = None):
     """(CE, LSE over V) per position of the model's next-token distribution from a forward's hidden states: p_LM's for a model
     without the head or under score 'lm', else the mixture's."""
     lse, z_y = token_lse_zy(hidden, model.lm_head_weight(), targets, chunk)
     if _lm_only(model):
         return lse - z_y, lse
-    mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, False)
+    mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, False, pointer)
     return -mix.at_target(z_y, ptr.log_copy), lse
 
 
-def mixture_loss(model, hidden, targets, tokens, doc_ids, a, b, chunk: int = 1024):
+def mixture_loss(model, hidden, targets, tokens, doc_ids, a, b, chunk: int = 1024, pointer: PointerInputs | None = None):
     """The training loss sum(a CE + b LSE_V^2) of the mixture and the detached per-position (CE, lambda). a, b: per-position
     weights (0 where a target does not count)."""
     lse, z_y = token_lse_zy(hidden, model.lm_head_weight(), targets, chunk)
     if model.cp_head.cfg.force_lambda_zero:
         ce, lam = lse - z_y, torch.zeros_like(lse)
     else:
-        mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, True)
+        mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, True, pointer)
         ce, lam = -mix.at_target(z_y, ptr.log_copy), mix.log_lam.detach().exp()
     total = (ce * a.to(ce.dtype)).sum() + (lse.square() * b.to(ce.dtype)).sum()
     return total, ce.detach(), lam

@@ -559,4 +559,6 @@ class Encoder(nn.Module):
                 new_caches.append(c)
             sources = sources + [x - start]
         last = self.layers[-1].attn_res
+        if getattr(self, "keep_sources", False):       # the Copy-Paste pointer's readers read the same [b_0 .. b_N] (models/cp_head.py)
+            ctx.memo["cp_pointer_sources"] = sources
         return (last.out(sources, x) if self.token_query else last.out(sources)), new_caches

@@ -36,6 +36,7 @@ class ModelOutput:
     kept: torch.Tensor | None = None
     n_dropped: torch.Tensor | None = None
     cache: ControlCache | None = None
+    cp_pointer: object | None = None      # the Copy-Paste pointer's own inputs (models/cp_head.py `PointerInputs`; pointer_input 'mix')
 
 
 def lm_head(h: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -220,7 +221,11 @@ class HybridLM(nn.Module):
             h, caches = self.encoder(self.embed_tokens(tokens), ctx, cache.encoder if cache else None, need_state=need_state,
                                      T=None if self.gated else T)
         hidden = self.final_norm(h)
-        copy_cache = None
+        copy_cache = pointer = None
+        if getattr(self, "cp_head", None) is not None and self.cfg.cp_head.pointer_input == "mix":
+            from .cp_head import SOURCES_KEY
+
+            pointer = self.cp_head.mix(ctx.memo.pop(SOURCES_KEY))
         if return_hidden:
             logits = None
         elif getattr(self, "cp_head", None) is not None:
@@ -228,13 +233,13 @@ class HybridLM(nn.Module):
 
             if tokens.dim() != 2 or self.tp is not None:
                 raise ValueError("the Copy-Paste head's output is for token rows on one device, not bags or a token shard")
-            logits, copy_cache = forward_logits(self, hidden, tokens, doc_ids, ctx.idx, cache.copy if cache else None)
+            logits, copy_cache = forward_logits(self, hidden, tokens, doc_ids, ctx.idx, cache.copy if cache else None, pointer)
         else:
             logits = lm_head(hidden, self.lm_head_weight())
         if return_cache and copy_cache is None and getattr(self, "cp_head", None) is not None:
             raise ValueError("a cache of a Copy-Paste model is built by a forward that returns logits (prefill / extend)")
         return ModelOutput(
-            logits=logits, hidden_aux=hidden if return_hidden else None,
+            logits=logits, hidden_aux=hidden if return_hidden else None, cp_pointer=pointer,
             kept=torch.zeros(B, L, dtype=torch.bool, device=tokens.device) if kept is None else kept,
             n_dropped=torch.zeros(B, dtype=torch.long, device=tokens.device) if n_dropped is None else n_dropped,
             cache=ControlCache(seq=seq_state, encoder=caches, T=T or 1, copy=copy_cache) if return_cache else None)

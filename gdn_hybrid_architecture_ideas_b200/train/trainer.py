@@ -422,7 +422,7 @@ class Trainer:
 
             if mb.multi_targets is not None:
                 raise ValueError("model.cp_head is built for one target a position")
-            loss, ce, lam = mixture_loss(self.model, hidden, targets, mb.tokens, mb.doc_ids, a, b, cfg.head_chunk)
+            loss, ce, lam = mixture_loss(self.model, hidden, targets, mb.tokens, mb.doc_ids, a, b, cfg.head_chunk, out.cp_pointer)
             self._cp_lambda = (lam * valid).sum() / valid.sum().clamp_min(1.0)
             return loss, (ce * valid).sum().detach()
         W = self.model.head_weight()

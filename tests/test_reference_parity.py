@@ -804,7 +804,8 @@ def test_gated_second_pass_is_refused_by_name_where_it_is_not_built():
 
 
 @pytest.mark.parametrize("base,keys", [("control", {}), ("control", {"qk_norm": True, "init": "reference"}),
-                                       ("control", {"qk_norm": True, "temperature": "ssmax", "sink_count": True}), ("full", {"qk_norm": True})])
+                                       ("control", {"qk_norm": True, "temperature": "ssmax", "sink_count": True}), ("full", {"qk_norm": True}),
+                                       ("control", {"window": 7}), ("full", {"pointer_input": "mix", "qk_norm": True, "temperature": "ssmax"})])
 def test_copy_paste_head_equals_the_reference(reference, base, keys):
     """The Copy-Paste head in its base form: the head's tensors last in the state dict with equal starts, the mixture's log p over V
     (it sums to one and equals the training cross entropy at the target), the blockwise terms against the reference's and an
@@ -834,15 +835,18 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
     tgt = torch.roll(tok, -1, 1)
     a, b = mine(tok, doc).logits, theirs(tok, doc).logits
     assert (a - b).abs().max() < 1e-10 and (a.exp().sum(-1) - 1).abs().max() < 1e-9
-    ha, hb = mine(tok, doc, return_hidden=True).hidden_aux, theirs(tok, doc, return_hidden=True).hidden_aux
-    ta, tb, tn = CP.terms(mine.cp_head, ha, tok, tgt, doc), RCP.cp_terms(theirs.cp_head, hb, tok, tgt, doc), CP.terms_naive(mine.cp_head, ha, tok, tgt, doc)
+    oa, ob = mine(tok, doc, return_hidden=True), theirs(tok, doc, return_hidden=True)
+    ha, hb, pa, pb = oa.hidden_aux, ob.hidden_aux, oa.cp_pointer, ob.cp_pointer
+    assert (pa is None) == (keys.get("pointer_input") != "mix")
+    ta, tb = CP.terms(mine.cp_head, ha, tok, tgt, doc, pointer=pa), RCP.cp_terms(theirs.cp_head, hb, tok, tgt, doc, pointer=pb)
+    tn = CP.terms_naive(mine.cp_head, ha, tok, tgt, doc, pointer=pa)
     for x, y, z in zip(ta, tb, tn):
         fin = torch.isfinite(y)
         assert torch.equal(torch.isfinite(x), fin) and torch.equal(torch.isfinite(z), fin) and (x - y)[fin].abs().max() < 1e-10 and (x - z)[fin].abs().max() < 1e-9
     assert 0 < int((~torch.isfinite(ta[2])).sum()) < tgt.numel()                # some targets have no match in their context, most have one
     w, z = torch.ones_like(tgt, dtype=torch.double), torch.full(tgt.shape, 1e-4, dtype=torch.double)
-    loss, ce, lam = CP.mixture_loss(mine, ha, tgt, tok, doc, w, z, chunk=16)
-    ce_r, lse_r = RCP.head_token_ce(theirs, hb, tgt, tok, doc)
+    loss, ce, lam = CP.mixture_loss(mine, ha, tgt, tok, doc, w, z, chunk=16, pointer=pa)
+    ce_r, lse_r = RCP.head_token_ce(theirs, hb, tgt, tok, doc, pointer=pb)
     assert (ce - ce_r).abs().max() < 1e-10 and (-a.gather(-1, tgt[..., None]).squeeze(-1) - ce).abs().max() < 1e-9 and 0 < float(lam.min()) and float(lam.max()) < 1
     ga = torch.autograd.grad(loss, list(mine.parameters()), allow_unused=True)
     gb = torch.autograd.grad((w * ce_r + z * lse_r * lse_r).sum(), list(theirs.parameters()), allow_unused=True)
@@ -858,7 +862,8 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
             parts.append(out.logits)
             assert (out.logits - ref_out.logits).abs().max() < 1e-10
         assert (torch.cat(parts, 1) - full).abs().max() < 1e-9 and out.cache.copy.keys.k.shape[:2] == (2, 40)
-        ce_eval, _ = CP.head_token_ce(mine, mine(tok, doc, return_hidden=True).hidden_aux, tgt, tok, doc)
+        oe = mine(tok, doc, return_hidden=True)
+        ce_eval, _ = CP.head_token_ce(mine, oe.hidden_aux, tgt, tok, doc, pointer=oe.cp_pointer)
         assert (ce_eval + full.gather(-1, tgt[..., None]).squeeze(-1)).abs().max() < 1e-9
         with pytest.raises(ValueError, match="Copy-Paste head"):
             mine.head_weight()
@@ -868,8 +873,8 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
 
 
 def test_copy_paste_head_is_refused_by_name_where_it_is_not_built():
-    for key, value, match in (("cp_head.pointer_input", "mix", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.trunk_copy", "all", "trunk_copy"),
-                              ("cp_head.train_mode", "addon", "train_mode"), ("cp_head.window", 64, "window"), ("cp_head.kernel", "fused", "kernel"),
+    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"),
+                              ("cp_head.trunk_copy", "all", "trunk_copy"), ("cp_head.train_mode", "addon", "train_mode"), ("cp_head.window", -1, "window"), ("cp_head.kernel", "fused", "kernel"),
                               ("cp_head.init", "zeros", "init"), ("cp_head.d_c", 0, "d_c"), ("loop.recur_layers", "[2, 6]", "one pass"),
                               ("encoder.gdn_ccr_spacing", 8, "gdn_ccr_spacing"), ("encoder.attn_res", "ldm", "attn_res")):
         cfg = C.tiny_control_config()
