@@ -23,7 +23,7 @@ def _step(model, tokens, docs, cache, ac):
     """One cached forward: (cache, what the next token is read from at the last position). A model with a Copy-Paste head builds
     its cache in a forward that returns logits (log p of the mixture, over the copy cache); every other model hands the last
     hidden state to the head."""
-    copy = getattr(model, "cp_head", None) is not None
+    copy = getattr(model, "cp_head", None) is not None and model.cp_head.gated
     with torch.autocast(**ac):
         out = model.forward(tokens, docs, cache=cache, return_cache=True, return_hidden=not copy)
     return out.cache, (out.logits[:, -1:] if copy else out.hidden_aux[:, -1:]), copy

@@ -24,8 +24,12 @@ positions; without the length rule, which counts them all), and the pointer that
 [b_0 .. b_N], each through a norm of its own, readers and norms zeros at the start so that both start as the stream's mean
 read; q = W_Q x^q, k = W_K x^k, the <copy> row and the LM head still read h; `cp_head.mix.*`). The tensors are registered
 after every other tensor and drawn from a generator of their own, so the base model starts as the model without the key.
+`train_mode: aux` (on the `mix` pointer): nothing is mixed into the prediction; the pointer has no <copy> row and learns from
+its own loss alone, L_aux(t) = -log of the pointer's mass on the context positions holding the next token (= -(log p_CP(y) +
+log(1 - s))), or -log s where the next token is not in the context, added to p_LM's loss at `aux_weight`; in eval mode the
+pointer is dropped (logits are p_LM's, no copy cache), so every scorer reads the model without the head (`aux_terms`).
 Refused by name: the pointer that reads an attention head (`pointer_input: shared`), several pointer heads, the copy from
-the trunk's own attention (`trunk_copy`), the auxiliary and add-on training modes, the fused kernel.
+the trunk's own attention (`trunk_copy`), the add-on training mode, the fused kernel.
 Reference: ced/model/cp_head.py:1-100 (the form), :454-660 (the module), :899-1016 (length rule, block terms),
 :1223-1245 (mixture), :1282-1370 (inference), :1443-1483 (cache).
 """
@@ -45,7 +49,8 @@ from torch.utils.checkpoint import checkpoint as recompute
 
 OWN_SEED_OFFSET = 0xC0_2610_19247        # shared with the reference: equal starts under equal seeds
 NORM_EPS = 2.0 ** -23
-BASE_FORM = dict(n_heads=1, combine="and", trunk_copy="none", train_mode="mixture", kernel="reference")
+BASE_FORM = dict(n_heads=1, combine="and", trunk_copy="none", kernel="reference")
+TRAIN_MODES = ("mixture", "aux")
 POINTER_INPUTS = ("final", "mix")
 SOURCES_KEY = "cp_pointer_sources"       # where a block-entry stack leaves [b_0 .. b_N] for the pointer's readers (SeqContext.memo)
 CHOICES = dict(init=("spec", "reference"), score=("mixture", "lm"), temperature=("none", "ssmax"))
@@ -58,8 +63,24 @@ def check_config(cfg) -> None:
         return
     off_base = [f"{name} {getattr(head, name)!r}" for name, base in BASE_FORM.items() if getattr(head, name) != base]
     if off_base:
-        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built with one pointer head, train_mode 'mixture', no trunk copy, "
-                         "kernel 'reference'")
+        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built with one pointer head, no trunk copy, kernel 'reference'")
+    if head.train_mode not in TRAIN_MODES:
+        raise ValueError(f"model.cp_head.train_mode {head.train_mode!r}: built are {TRAIN_MODES} (the mixture's loss; the pointer's own auxiliary loss)")
+    weight = head.aux_weight
+    if type(weight) not in (int, float) or not math.isfinite(weight) or weight < 0:
+        raise ValueError(f"model.cp_head.aux_weight {weight!r}: the auxiliary loss's weight, a finite number >= 0")
+    if head.train_mode == "mixture" and weight != 0:
+        raise ValueError(f"model.cp_head.aux_weight {weight!r} without model.cp_head.train_mode 'aux': the key would be ignored")
+    if head.train_mode == "aux":
+        plain = type(head)()
+        if weight <= 0:
+            raise ValueError("model.cp_head.aux_weight 0 with model.cp_head.train_mode 'aux': the pointer's only loss is the auxiliary one; give the weight, > 0")
+        wrong = [k for k in ("force_lambda_zero", "score", "temperature", "sink_count") if getattr(head, k) != getattr(plain, k)]
+        if cfg.encoder.gdn_write_mix != "none":
+            raise ValueError(f"model.cp_head.train_mode 'aux' is not built together with model.encoder.gdn_write_mix {cfg.encoder.gdn_write_mix!r} (nothing tests the pair)")
+        if head.pointer_input != "mix" or wrong:
+            raise ValueError("model.cp_head.train_mode 'aux' is built for the pointer on depth reads (pointer_input 'mix') without force_lambda_zero, score, "
+                             f"temperature or sink_count (set: pointer_input {head.pointer_input!r}{', ' + ', '.join(wrong) if wrong else ''})")
     if head.pointer_input not in POINTER_INPUTS:
         raise ValueError(f"model.cp_head.pointer_input {head.pointer_input!r}: built are {POINTER_INPUTS} (the final norm's output, or depth reads of the finished blocks)")
     if type(head.window) is not int or head.window < 0:
@@ -139,8 +160,11 @@ class CopyPasteHead(nn.Module):
     def __init__(self, d_model: int, cfg, ref_len: int = 8192, eps: float = 1e-6):
         super().__init__()
         self.cfg, self.ref_len, self.scale = cfg, int(ref_len), cfg.d_c ** -0.5
+        self.gated = cfg.train_mode != "aux"            # the <copy> row exists only where something is mixed into the prediction
         for name, shape in (("w_q", (cfg.d_c, d_model)), ("w_k", (cfg.d_c, d_model)), ("k_sink", (cfg.d_c,)), ("w_copy", (d_model,))):
-            self.register_parameter(name, nn.Parameter(torch.empty(shape)))
+            if name != "w_copy" or self.gated:
+                self.register_parameter(name, nn.Parameter(torch.empty(shape)))
+        self.d_model = d_model
         if cfg.qk_norm:
             self.qk_gain = nn.Parameter(torch.zeros(1))
         if cfg.pointer_input == "mix":
@@ -152,6 +176,9 @@ class CopyPasteHead(nn.Module):
         the sink as N(0, 1 / d_c), w_copy keeping its draw."""
         draw = lambda shape: torch.randn(shape, generator=g, dtype=torch.float32)                  # noqa: E731
         for name in ("w_q", "w_k", "k_sink", "w_copy"):
+            if name == "w_copy" and not self.gated:
+                draw((self.d_model,))                      # the row's draw is taken and dropped: the other tensors are the gated head's
+                continue
             t = getattr(self, name)
             t.copy_((draw(t.shape) * std).to(t.dtype) if t.dtype != torch.float32 else draw(t.shape) * std)
         if init == "reference":
@@ -178,6 +205,9 @@ class CopyPasteHead(nn.Module):
         return self._project(h, self.w_k, self.cfg.qk_norm)
 
     def copy_logit(self, h):
+        if not self.gated:
+            raise ValueError("this Copy-Paste head trains on its auxiliary loss (model.cp_head.train_mode 'aux'): it has no <copy> row and nothing is mixed "
+                             "into the prediction")
         return self._project(h, self.w_copy.unsqueeze(0), False)[..., 0]
 
     def rule(self) -> "LengthRule":
@@ -200,7 +230,14 @@ def score_mode(model) -> str:
 
 def _lm_only(model) -> bool:
     head = getattr(model, "cp_head", None)
-    return head is None or head.cfg.force_lambda_zero or score_mode(model) == "lm"
+    return head is None or not head.gated or head.cfg.force_lambda_zero or score_mode(model) == "lm"
+
+
+def aux_terms(ptr: "Pointer"):
+    """(L_aux, at the sink) per position from the pointer's terms: -(log p_CP(y) + log(1 - s)) where the next token is in the
+    context, else -log s; the branch not taken gets a zero gradient."""
+    found = torch.isfinite(ptr.log_copy)
+    return torch.where(found, -(ptr.log_copy.masked_fill(~found, 0.0) + ptr.log_ctx), -ptr.log_sink), ~found
 
 
 # ------------------------------------------------------------------------------------------------------- the pointer

@@ -110,7 +110,7 @@ class HybridLM(nn.Module):
         """`lm_head_weight`, refused in eval mode for a model whose next-token distribution is the Copy-Paste mixture: a
         scoring path that applies the bare head to hidden states would score p_LM by mistake (models/cp_head.py
         `head_token_ce` scores the mixture)."""
-        if not self.training and getattr(self, "cp_head", None) is not None:
+        if not self.training and getattr(self, "cp_head", None) is not None and self.cp_head.gated:
             from .cp_head import score_mode
 
             if score_mode(self) == "mixture" and not self.cfg.cp_head.force_lambda_zero:
@@ -225,10 +225,12 @@ class HybridLM(nn.Module):
         if getattr(self, "cp_head", None) is not None and self.cfg.cp_head.pointer_input == "mix":
             from .cp_head import SOURCES_KEY
 
-            pointer = self.cp_head.mix(ctx.memo.pop(SOURCES_KEY))
+            sources = ctx.memo.pop(SOURCES_KEY)
+            if self.cp_head.gated or self.training:       # a pointer trained on its auxiliary loss is dropped at evaluation
+                pointer = self.cp_head.mix(sources)
         if return_hidden:
             logits = None
-        elif getattr(self, "cp_head", None) is not None:
+        elif getattr(self, "cp_head", None) is not None and self.cp_head.gated:
             from .cp_head import forward_logits
 
             if tokens.dim() != 2 or self.tp is not None:
@@ -236,7 +238,7 @@ class HybridLM(nn.Module):
             logits, copy_cache = forward_logits(self, hidden, tokens, doc_ids, ctx.idx, cache.copy if cache else None, pointer)
         else:
             logits = lm_head(hidden, self.lm_head_weight())
-        if return_cache and copy_cache is None and getattr(self, "cp_head", None) is not None:
+        if return_cache and copy_cache is None and getattr(self, "cp_head", None) is not None and self.cp_head.gated:
             raise ValueError("a cache of a Copy-Paste model is built by a forward that returns logits (prefill / extend)")
         return ModelOutput(
             logits=logits, hidden_aux=hidden if return_hidden else None, cp_pointer=pointer,

@@ -417,7 +417,16 @@ class Trainer:
                 cut = slice(self.tp.rank * per, (self.tp.rank + 1) * per)
                 targets, valid = targets.reshape(-1)[cut][None], valid.reshape(-1)[cut][None]
             a, b = valid * inv, valid * (z * inv)
-        if self._cp is not None:
+        if self._cp is not None and not self._cp.gated:       # the pointer's own loss beside p_LM's (models/cp_head.py, train_mode 'aux')
+            from ..models.cp_head import aux_terms, terms
+
+            if mb.multi_targets is not None:
+                raise ValueError("model.cp_head is built for one target a position")
+            with torch.autocast(self.device.type, enabled=False):
+                l_aux, at_sink = aux_terms(terms(self._cp, hidden, mb.tokens, targets, mb.doc_ids, checkpoint=True, pointer=out.cp_pointer))
+            aux = (l_aux * valid).sum() * (self._cp.cfg.aux_weight * inv)
+            self._cp_aux = ((l_aux.detach() * valid).sum() / valid.sum().clamp_min(1.0), (at_sink.to(valid.dtype) * valid).sum() / valid.sum().clamp_min(1.0))
+        elif self._cp is not None:
             from ..models.cp_head import mixture_loss
 
             if mb.multi_targets is not None:
@@ -432,6 +441,8 @@ class Trainer:
         else:
             loss, ce_sum = chunked_ce(hidden, W, targets, a, b, ce_form=cfg.loss.ce_form, precision=cfg.head_precision)
             ce_sum = ce_sum.detach()
+        if self._cp is not None and not self._cp.gated:
+            loss = loss + aux.to(loss.dtype)
         return loss, ce_sum
 
     def device_step(self, batch, n_global: int, lr: float | None = None) -> torch.Tensor:
@@ -586,7 +597,9 @@ class Trainer:
              "step_seconds": seconds, "tokens_per_s": n_tokens / seconds}
         if self.device.type == "cuda":
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
-        if self._cp is not None and cfg.log_every and step % cfg.log_every == 0:
+        if self._cp is not None and not self._cp.gated:
+            m["cp_aux"], m["cp_aux_sink"] = (float(x) for x in self._cp_aux)      # the step's last micro-batch: the mean auxiliary CE, the share of targets at the sink
+        elif self._cp is not None and cfg.log_every and step % cfg.log_every == 0:
             m["cp_lambda"] = float(self._cp_lambda)          # the mean copy weight at the scored targets of the step's last micro-batch
             if self._cp.cfg.qk_norm:
                 m["cp_qk_gain"] = 1.0 + float(self._cp.qk_gain.detach())

@@ -1,6 +1,8 @@
 """The model equals the reference implementation on CPU in float64: state-dict keys and initial values with the same
 seed, logits, parameter gradients, and cached generation; parameter counts of the published 200M / 60M entries."""
 
+import copy
+
 import pytest
 import torch
 
@@ -969,3 +971,55 @@ def test_looped_encoder_decoder_equals_the_reference(reference, arm):
         mine_tokens, mine_logits = mine.generate(prompt, pdoc, pmask, 5, T=2)
         ref_tokens, ref_logits = theirs.generate(prompt, pdoc, pmask, 5, T=2)
         assert torch.equal(mine_tokens, ref_tokens) and (mine_logits - ref_logits).abs().max() < 1e-10
+
+
+def test_copy_paste_pointer_trained_on_its_auxiliary_loss_equals_the_reference(reference):
+    """cp_head.train_mode aux: no <copy> row and the other tensors the mixture head's of the same seed; the pointer's inputs are
+    formed in training mode only; L_aux and its gradients (the pointer's tensors alone learn from it); in eval mode the model
+    is the model without the head (logits, cached generation)."""
+    from ced.model import cp_aux as RAUX
+    from ced.model import cp_head as RCP
+
+    from gdn_hybrid_architecture_ideas_b200.models import cp_head as CP
+
+    cfg = C.tiny_full_config()
+    cfg.encoder.gdn_write_variant, cfg.encoder.gdn_write_mix = "none", "none"
+    cfg.cp_head.enabled, cfg.cp_head.d_c, cfg.cp_head.query_chunk, cfg.cp_head.pointer_input, cfg.cp_head.qk_norm = True, 8, 16, "mix", True
+    gated, _ = _pair(reference, cfg)
+    cfg.cp_head.train_mode, cfg.cp_head.aux_weight = "aux", 0.5
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd) and "cp_head.w_copy" not in sd
+    assert all(torch.equal(sd[k], v) for k, v in gated.state_dict().items() if k != "cp_head.w_copy")
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40, vocab=12)
+    tgt = torch.roll(tok, -1, 1)
+    oa, ob = mine(tok, doc, return_hidden=True), theirs(tok, doc, return_hidden=True)
+    la, sink_a = CP.aux_terms(CP.terms(mine.cp_head, oa.hidden_aux, tok, tgt, doc, pointer=oa.cp_pointer))
+    lb, sink_b = RAUX.aux_ce(*RCP.cp_terms(theirs.cp_head, ob.hidden_aux, tok, tgt, doc, pointer=ob.cp_pointer))
+    assert torch.equal(sink_a, sink_b) and 0 < int(sink_a.sum()) < sink_a.numel() and (la - lb).abs().max() < 1e-10
+    ga = torch.autograd.grad(la.sum(), list(mine.parameters()), allow_unused=True)
+    gb = torch.autograd.grad(lb.sum(), list(theirs.parameters()), allow_unused=True)
+    for (n, _), x, y in zip(mine.named_parameters(), ga, gb):
+        assert (x is None) == (y is None) and (x is None or ((x - y).abs().max() < 1e-9 and torch.isfinite(x).all())), n
+    assert all(x is not None for (n, _), x in zip(mine.named_parameters(), ga) if n.startswith("cp_head."))
+    with pytest.raises(ValueError, match="no <copy> row"):
+        mine.cp_head.copy_logit(oa.hidden_aux)
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        out = mine(tok, doc, return_hidden=True)
+        assert out.cp_pointer is None
+        full, ref_full = mine(tok, doc).logits, theirs(tok, doc).logits
+        assert (full - ref_full).abs().max() < 1e-10 and (full - torch.nn.functional.linear(out.hidden_aux, mine.head_weight())).abs().max() < 1e-12
+        a = mine.prefill(tok[:, :20], doc[:, :20])
+        b = mine.extend(tok[:, 20:], doc[:, 20:], None, a.cache)
+        assert a.cache.copy is None and (torch.cat([a.logits, b.logits], 1) - full).abs().max() < 1e-9
+    for key, value, match in (("aux_weight", 0.0, "aux_weight"), ("pointer_input", "final", "pointer_input"), ("force_lambda_zero", True, "force_lambda_zero"), ("train_mode", "addon", "train_mode")):
+        bad = copy.deepcopy(cfg)
+        setattr(bad.cp_head, key, value)
+        with pytest.raises(ValueError, match=match):
+            build_model(bad)

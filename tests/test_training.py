@@ -1155,3 +1155,32 @@ def test_looped_encoder_decoder_trains_through_the_trainer(tmp_path):
     plain.loss.aux_weight = 0.5
     with pytest.raises(ValueError, match="aux_weight"):
         Trainer(plain, None)
+
+
+def test_copy_paste_pointer_trains_on_its_auxiliary_loss_beside_the_plain_loss(tmp_path):
+    """cp_head.train_mode aux through the trainer: the loss is p_LM's plus aux_weight x the pointer's own; the trunk's gradient
+    from p_LM's term is the plain model's; the pointer's tensors move; metrics cp_aux / cp_aux_sink; a bit-exact resume."""
+    cfg = tiny_train_config(steps=4)
+    cfg.model = C.tiny_full_config()
+    cfg.model.encoder.gdn_write_variant, cfg.model.encoder.gdn_write_mix = "none", "none"
+    plain = copy.deepcopy(cfg)
+    h = cfg.model.cp_head
+    h.enabled, h.d_c, h.qk_norm, h.pointer_input, h.train_mode, h.aux_weight = True, 8, True, "mix", "aux", 0.5
+    cfg.head_impl, plain.head_impl, cfg.ckpt_every_steps = "chunked", "chunked", 2
+    t, base = Trainer(copy.deepcopy(cfg), tmp_path / "a"), Trainer(plain, tmp_path / "p")
+    assert "cp_head.w_copy" not in t.model.state_dict() and "cp_head.mix.read_q.query" in t.model.state_dict()
+    start = {n: p.detach().clone() for n, p in t.model.named_parameters() if n.startswith("cp_head.")}
+    m, mb = t.train_step(), base.train_step()
+    assert m["cp_aux"] > 0 and 0 <= m["cp_aux_sink"] <= 1 and m["loss"] > mb["loss"] and abs(m["ce_dec"] - mb["ce_dec"]) < 1e-5
+    assert abs(m["loss"] - mb["loss"] - 0.5 * m["cp_aux"]) < 1e-4
+    for _ in range(3):
+        t.train_step()
+    moved = [n for n, p in t.model.named_parameters() if n.startswith("cp_head.") and not torch.equal(p, start[n])]
+    assert {"cp_head.w_q", "cp_head.w_k", "cp_head.k_sink"} <= set(moved)
+    b = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    b.fit(until_step=2)
+    c = Trainer(copy.deepcopy(cfg), tmp_path / "b")
+    assert c.resume_from_checkpoint() and c.step == 2
+    c.fit()
+    for (k, x), (_, y) in zip(t.model.state_dict().items(), c.model.state_dict().items()):
+        assert torch.equal(x, y), k
