@@ -28,8 +28,12 @@ after every other tensor and drawn from a generator of their own, so the base mo
 its own loss alone, L_aux(t) = -log of the pointer's mass on the context positions holding the next token (= -(log p_CP(y) +
 log(1 - s))), or -log s where the next token is not in the context, added to p_LM's loss at `aux_weight`; in eval mode the
 pointer is dropped (logits are p_LM's, no copy cache), so every scorer reads the model without the head (`aux_terms`).
+`train_mode: addon` (on the `mix` pointer): the head is the mixture head and every evaluation reads the mixture; in training
+the trunk and the LM head learn from p_LM's loss alone, and the head from the mixture's CE in which p_LM's numbers (LSE_V,
+log p_LM(y)), the <copy> row's input h and the readers' sources are all detached, so no gradient of the mixture reaches a
+trunk tensor (`addon_loss`); the trainer clips the two parts by their own norms.
 Refused by name: the pointer that reads an attention head (`pointer_input: shared`), several pointer heads, the copy from
-the trunk's own attention (`trunk_copy`), the add-on training mode, the fused kernel.
+the trunk's own attention (`trunk_copy`), the fused kernel.
 Reference: ced/model/cp_head.py:1-100 (the form), :454-660 (the module), :899-1016 (length rule, block terms),
 :1223-1245 (mixture), :1282-1370 (inference), :1443-1483 (cache).
 """
@@ -50,7 +54,7 @@ from torch.utils.checkpoint import checkpoint as recompute
 OWN_SEED_OFFSET = 0xC0_2610_19247        # shared with the reference: equal starts under equal seeds
 NORM_EPS = 2.0 ** -23
 BASE_FORM = dict(n_heads=1, combine="and", trunk_copy="none", kernel="reference")
-TRAIN_MODES = ("mixture", "aux")
+TRAIN_MODES = ("mixture", "aux", "addon")
 POINTER_INPUTS = ("final", "mix")
 SOURCES_KEY = "cp_pointer_sources"       # where a block-entry stack leaves [b_0 .. b_N] for the pointer's readers (SeqContext.memo)
 CHOICES = dict(init=("spec", "reference"), score=("mixture", "lm"), temperature=("none", "ssmax"))
@@ -69,8 +73,14 @@ def check_config(cfg) -> None:
     weight = head.aux_weight
     if type(weight) not in (int, float) or not math.isfinite(weight) or weight < 0:
         raise ValueError(f"model.cp_head.aux_weight {weight!r}: the auxiliary loss's weight, a finite number >= 0")
-    if head.train_mode == "mixture" and weight != 0:
+    if head.train_mode != "aux" and weight != 0:
         raise ValueError(f"model.cp_head.aux_weight {weight!r} without model.cp_head.train_mode 'aux': the key would be ignored")
+    if head.train_mode == "addon":
+        plain = type(head)()
+        wrong = [k for k in ("force_lambda_zero", "temperature", "sink_count") if getattr(head, k) != getattr(plain, k)]
+        if head.pointer_input != "mix" or wrong:
+            raise ValueError("model.cp_head.train_mode 'addon' is built for the pointer on depth reads (pointer_input 'mix') without force_lambda_zero, temperature "
+                             f"or sink_count (set: pointer_input {head.pointer_input!r}{', ' + ', '.join(wrong) if wrong else ''})")
     if head.train_mode == "aux":
         plain = type(head)()
         if weight <= 0:
@@ -381,6 +391,10 @@ class Mixture:
         """log p(y) from the target's logit and log p_CP(y)."""
         return torch.logaddexp(self.log_keep + (z_y - self.lse_v), self.log_lam + log_copy)
 
+    def at_target_given(self, log_lm_y, log_copy):
+        """log p(y) with log p_LM(y) given as a number of its own (no LSE_V - LSE_V cancellation)."""
+        return torch.logaddexp(self.log_keep + log_lm_y, self.log_lam + log_copy)
+
     def over_vocab(self, logits, log_copy):
         """log p over V from the logits and log p_CP over V, both (..., V)."""
         return torch.logaddexp((self.log_keep - self.lse_v).unsqueeze(-1) + logits, self.log_lam.unsqueeze(-1) + log_copy)
@@ -453,6 +467,20 @@ def head_token_ce(model, hidden, targets, tokens, doc_ids, chunk: int = 1024, po
         return lse - z_y, lse
     mix, ptr = _mixture_at_targets(model.cp_head, hidden, lse, tokens, targets, doc_ids, False, pointer)
     return -mix.at_target(z_y, ptr.log_copy), lse
+
+
+def addon_loss(model, hidden, targets, tokens, doc_ids, weights, chunk: int = 1024, pointer: PointerInputs | None = None):
+    """sum(weights x the mixture's CE) with everything of the trunk and the LM head detached, and the detached per-position
+    (mixture CE, lambda): the gradient reaches the head's own tensors alone."""
+    head = model.cp_head
+    still = hidden.detach()
+    with torch.no_grad():
+        lse, z_y = token_lse_zy(still, model.lm_head_weight().detach(), targets, chunk)
+    with _no_autocast(hidden):
+        ptr = Pointer(*(t.to(lse.dtype) for t in terms(head, still, tokens, targets, doc_ids, checkpoint=True, pointer=pointer)))
+        mix = Mixture.of(lse, head.copy_logit(still).to(lse.dtype), ptr)
+        ce = -mix.at_target_given(z_y - lse, ptr.log_copy)
+    return (ce * weights.to(ce.dtype)).sum(), ce.detach(), mix.log_lam.detach().exp()
 
 
 def mixture_loss(model, hidden, targets, tokens, doc_ids, a, b, chunk: int = 1024, pointer: PointerInputs | None = None):

@@ -226,6 +226,8 @@ class HybridLM(nn.Module):
             from .cp_head import SOURCES_KEY
 
             sources = ctx.memo.pop(SOURCES_KEY)
+            if self.training and self.cfg.cp_head.train_mode == "addon":      # the add-on head's readers send no gradient into the stack
+                sources = [b.detach() for b in sources]
             if self.cp_head.gated or self.training:       # a pointer trained on its auxiliary loss is dropped at evaluation
                 pointer = self.cp_head.mix(sources)
         if return_hidden:

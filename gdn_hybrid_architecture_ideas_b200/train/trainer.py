@@ -173,6 +173,8 @@ class Trainer:
         if self._cp is not None:
             clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
                        "shape_schedule": bool(cfg.shape_schedule), "head_impl 'fused' (the mixture runs on the chunked head: set head_impl 'chunked')": cfg.head_impl == "fused"}
+            if cfg.model.cp_head.train_mode == "addon":        # the two clips are one process's
+                clashes.update({"data parallelism (train_mode 'addon')": self.world > 1, "freeze_trunk (train_mode 'addon')": bool(cfg.freeze_trunk)})
             hit = [k for k, v in clashes.items() if v]
             if hit:
                 raise ValueError(f"model.cp_head is not built together with: {', '.join(hit)}")
@@ -426,6 +428,14 @@ class Trainer:
                 l_aux, at_sink = aux_terms(terms(self._cp, hidden, mb.tokens, targets, mb.doc_ids, checkpoint=True, pointer=out.cp_pointer))
             aux = (l_aux * valid).sum() * (self._cp.cfg.aux_weight * inv)
             self._cp_aux = ((l_aux.detach() * valid).sum() / valid.sum().clamp_min(1.0), (at_sink.to(valid.dtype) * valid).sum() / valid.sum().clamp_min(1.0))
+        elif self._cp is not None and self._cp.cfg.train_mode == "addon":      # the head's own term beside p_LM's loss, nothing of the trunk in its graph
+            from ..models.cp_head import addon_loss
+
+            if mb.multi_targets is not None:
+                raise ValueError("model.cp_head is built for one target a position")
+            aux, ce_mix, lam = addon_loss(self.model, hidden, targets, mb.tokens, mb.doc_ids, valid * inv, cfg.head_chunk, out.cp_pointer)
+            self._cp_lambda = (lam * valid).sum() / valid.sum().clamp_min(1.0)
+            self._cp_mix = (ce_mix * valid).sum() / valid.sum().clamp_min(1.0)
         elif self._cp is not None:
             from ..models.cp_head import mixture_loss
 
@@ -441,7 +451,7 @@ class Trainer:
         else:
             loss, ce_sum = chunked_ce(hidden, W, targets, a, b, ce_form=cfg.loss.ce_form, precision=cfg.head_precision)
             ce_sum = ce_sum.detach()
-        if self._cp is not None and not self._cp.gated:
+        if self._cp is not None and (not self._cp.gated or self._cp.cfg.train_mode == "addon"):
             loss = loss + aux.to(loss.dtype)
         return loss, ce_sum
 
@@ -518,6 +528,16 @@ class Trainer:
             if cfg.log_every and self.step % cfg.log_every == 0:      # per-family gradient norms before clipping (whole gradients are here)
                 self._family_norms = monitor.family_grad_norms(self.flat)
             gnorm = grad_norm(self.flat)
+            if self._cp is not None and self._cp.cfg.train_mode == "addon":
+                # two clips: the trunk and the LM head by their own norm (the model's without the head), the head by its own; the
+                # optimizer applies the trunk's factor to everything, so the head's gradients are scaled to theirs first
+                own = [p.grad for n, p in self.model.named_parameters() if n.startswith("cp_head.") and p.grad is not None]
+                head_norm = torch.stack([g.double().pow(2).sum() for g in own]).sum().sqrt().float()
+                gnorm = (gnorm.double().pow(2) - head_norm.double().pow(2)).clamp_min(0).sqrt().float()
+                ratio = _clip_coef(head_norm, cfg.optim.grad_clip) / _clip_coef(gnorm, cfg.optim.grad_clip)
+                for g in own:
+                    g.mul_(ratio.to(g.dtype) if isinstance(ratio, torch.Tensor) else ratio)
+                self._cp_grad_norm = head_norm
             self.optimizer.step(lr, _clip_coef(gnorm, cfg.optim.grad_clip))
         if not cfg.freeze_trunk and self.model.encoder.scalar_form != "none":
             if self.zero is not None:
@@ -599,7 +619,9 @@ class Trainer:
             m["peak_alloc_gib"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
         if self._cp is not None and not self._cp.gated:
             m["cp_aux"], m["cp_aux_sink"] = (float(x) for x in self._cp_aux)      # the step's last micro-batch: the mean auxiliary CE, the share of targets at the sink
-        elif self._cp is not None and cfg.log_every and step % cfg.log_every == 0:
+        if self._cp is not None and self._cp.cfg.train_mode == "addon":
+            m["ce_mix"], m["cp_grad_norm"] = float(self._cp_mix), float(self._cp_grad_norm)      # grad_norm above is the trunk's and the LM head's
+        if self._cp is not None and self._cp.gated and cfg.log_every and step % cfg.log_every == 0:
             m["cp_lambda"] = float(self._cp_lambda)          # the mean copy weight at the scored targets of the step's last micro-batch
             if self._cp.cfg.qk_norm:
                 m["cp_qk_gain"] = 1.0 + float(self._cp.qk_gain.detach())

@@ -1023,3 +1023,55 @@ def test_copy_paste_pointer_trained_on_its_auxiliary_loss_equals_the_reference(r
         setattr(bad.cp_head, key, value)
         with pytest.raises(ValueError, match=match):
             build_model(bad)
+
+
+def test_add_on_copy_paste_head_equals_the_reference(reference):
+    """cp_head.train_mode addon: the mixture head's tensors; evaluation reads the mixture; in training mode the pointer's inputs
+    carry no gradient into the stack, and the head's own term, the mixture's CE with p_LM's numbers and h detached, equals
+    the reference's and sends its gradient to the head's tensors alone."""
+    from ced.model import cp_aux as RAUX
+    from ced.model import cp_head as RCP
+
+    from gdn_hybrid_architecture_ideas_b200.models import cp_head as CP
+
+    cfg = C.tiny_full_config()
+    cfg.encoder.gdn_write_variant = "none"
+    cfg.cp_head.enabled, cfg.cp_head.d_c, cfg.cp_head.query_chunk, cfg.cp_head.pointer_input, cfg.cp_head.qk_norm = True, 8, 16, "mix", True
+    gated, _ = _pair(reference, cfg)
+    cfg.cp_head.train_mode = "addon"
+    mine, theirs = _pair(reference, cfg)
+    sd, rsd = mine.state_dict(), theirs.state_dict()
+    assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd) and all(torch.equal(sd[k], v) for k, v in gated.state_dict().items())
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for p in theirs.parameters():
+            p.add_(torch.randn(p.shape, generator=g, dtype=p.dtype) * 0.05)
+    mine.load_state_dict(theirs.state_dict())
+    tok, doc = random_rows(2, 40, vocab=12)
+    tgt = torch.roll(tok, -1, 1)
+    w = torch.full(tgt.shape, 1.0 / tgt.numel(), dtype=torch.double)
+    oa, ob = mine(tok, doc, return_hidden=True), theirs(tok, doc, return_hidden=True)
+    assert not oa.cp_pointer.q.requires_grad or all(x is None for x in torch.autograd.grad(oa.cp_pointer.q.sum(), [p for n, p in mine.named_parameters() if not n.startswith("cp_head.")], allow_unused=True))
+    loss, ce_mix, lam = CP.addon_loss(mine, oa.hidden_aux, tgt, tok, doc, w, pointer=oa.cp_pointer)
+    hb = ob.hidden_aux.detach()
+    W = theirs.lm_head_weight().detach()
+    logits = hb @ W.t()
+    lse_r = torch.logsumexp(logits, -1)
+    log_lm = logits.gather(-1, tgt[..., None]).squeeze(-1) - lse_r
+    ls, l1s, lp = RCP.cp_terms(theirs.cp_head, hb, tok, tgt, doc, pointer=ob.cp_pointer)
+    ce_r = -RAUX.addon_log_prob(lse_r, log_lm, theirs.cp_head.copy_logit(hb), ls, l1s, lp)
+    assert (ce_mix - ce_r).abs().max() < 1e-10 and abs(float(loss) - float((ce_r * w).sum())) < 1e-12 and 0 < float(lam.min()) and float(lam.max()) < 1
+    ga = torch.autograd.grad(loss, list(mine.parameters()), allow_unused=True)
+    gb = torch.autograd.grad((ce_r * w).sum(), list(theirs.parameters()), allow_unused=True)
+    for (n, _), x, y in zip(mine.named_parameters(), ga, gb):
+        assert (x is None) == (y is None) and (x is None) == (not n.startswith("cp_head.")), n
+        assert x is None or (x - y).abs().max() < 1e-9, n
+    mine.eval(), theirs.eval()
+    with torch.no_grad():
+        a, b = mine(tok, doc).logits, theirs(tok, doc).logits
+        assert (a - b).abs().max() < 1e-10 and (a.exp().sum(-1) - 1).abs().max() < 1e-9
+    for key, value in (("pointer_input", "final"), ("temperature", "ssmax"), ("aux_weight", 0.5)):
+        bad = copy.deepcopy(cfg)
+        setattr(bad.cp_head, key, value)
+        with pytest.raises(ValueError, match="addon|aux_weight"):
+            build_model(bad)

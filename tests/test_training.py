@@ -1184,3 +1184,26 @@ def test_copy_paste_pointer_trains_on_its_auxiliary_loss_beside_the_plain_loss(t
     c.fit()
     for (k, x), (_, y) in zip(t.model.state_dict().items(), c.model.state_dict().items()):
         assert torch.equal(x, y), k
+
+
+def test_add_on_copy_paste_head_leaves_the_trunk_training_as_the_plain_model(tmp_path):
+    """cp_head.train_mode addon through the trainer: the trunk's and the LM head's updates are those of the model without the
+    head (their loss is p_LM's and their clip their own), while the head trains on the mixture's term under a clip of its own;
+    metrics ce_mix / cp_lambda / cp_grad_norm; data parallelism is refused."""
+    cfg = tiny_train_config(steps=3)
+    cfg.model = C.tiny_full_config()
+    cfg.model.encoder.gdn_write_variant = "none"
+    cfg.head_impl, cfg.log_every, cfg.optim.grad_clip = "chunked", 1, 0.05          # a clip that binds: the two norms must stay apart
+    plain = copy.deepcopy(cfg)
+    h = cfg.model.cp_head
+    h.enabled, h.d_c, h.qk_norm, h.pointer_input, h.train_mode = True, 8, True, "mix", "addon"
+    t, base = Trainer(copy.deepcopy(cfg), tmp_path / "a"), Trainer(plain, tmp_path / "p")
+    head0 = {n: p.detach().clone() for n, p in t.model.named_parameters() if n.startswith("cp_head.")}
+    for _ in range(3):
+        m, mb = t.train_step(), base.train_step()
+        assert abs(m["grad_norm"] - mb["grad_norm"]) < 1e-4 * mb["grad_norm"] and abs(m["ce_dec"] - mb["ce_dec"]) < 1e-5
+        assert m["ce_mix"] > 0 and m["cp_grad_norm"] > 0 and 0 < m["cp_lambda"] < 1 and m["loss"] > mb["loss"]
+    ours, theirs = t.model.state_dict(), base.model.state_dict()
+    worst = max(float((ours[k] - v).abs().max()) for k, v in theirs.items())
+    assert worst < 1e-6, worst
+    assert all(not torch.equal(p, head0[n]) for n, p in t.model.named_parameters() if n in ("cp_head.w_q", "cp_head.w_copy", "cp_head.k_sink"))
