@@ -33,7 +33,11 @@ the trunk and the LM head learn from p_LM's loss alone, and the head from the mi
 log p_LM(y)), the <copy> row's input h and the readers' sources are all detached, so no gradient of the mixture reaches a
 trunk tensor (`addon_loss`); the trainer clips the two parts by their own norms.
 Refused by name: the pointer that reads an attention head (`pointer_input: shared`), several pointer heads, the copy from
-the trunk's own attention (`trunk_copy`), the fused kernel.
+the trunk's own attention (`trunk_copy`), the heads mixed by a router (`combine: or`), the fused kernel. Several pointer
+heads (`n_heads` H on the `mix` pointer with `qk_norm`): head h has its own pair of depth reads (`cp_head.mix.heads.<h>`), its
+own rows h d_c .. (h + 1) d_c - 1 of W_Q / W_K, its own norm over d_c, gain and slice of the sink key; q and k are held flat
+(H d_c) and scored at 1 / sqrt(d_c), which sums the heads' scores into one logit a position, one softmax; head 0 and the
+<copy> row are drawn first, so they are the one-head pointer's of the same seed.
 Reference: ced/model/cp_head.py:1-100 (the form), :454-660 (the module), :899-1016 (length rule, block terms),
 :1223-1245 (mixture), :1282-1370 (inference), :1443-1483 (cache).
 """
@@ -53,7 +57,7 @@ from torch.utils.checkpoint import checkpoint as recompute
 
 OWN_SEED_OFFSET = 0xC0_2610_19247        # shared with the reference: equal starts under equal seeds
 NORM_EPS = 2.0 ** -23
-BASE_FORM = dict(n_heads=1, combine="and", trunk_copy="none", kernel="reference")
+BASE_FORM = dict(combine="and", trunk_copy="none", kernel="reference")
 TRAIN_MODES = ("mixture", "aux", "addon")
 POINTER_INPUTS = ("final", "mix")
 SOURCES_KEY = "cp_pointer_sources"       # where a block-entry stack leaves [b_0 .. b_N] for the pointer's readers (SeqContext.memo)
@@ -67,7 +71,16 @@ def check_config(cfg) -> None:
         return
     off_base = [f"{name} {getattr(head, name)!r}" for name, base in BASE_FORM.items() if getattr(head, name) != base]
     if off_base:
-        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built with one pointer head, no trunk copy, kernel 'reference'")
+        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built with the heads' scores summed (combine 'and'), no trunk copy, kernel 'reference'")
+    if type(head.n_heads) is not int or head.n_heads < 1:
+        raise ValueError(f"model.cp_head.n_heads {head.n_heads!r}: the pointer's heads, an integer >= 1")
+    if head.n_heads > 1:
+        single = {"pointer_input 'mix'": head.pointer_input == "mix", "qk_norm true (each head's own gain)": bool(head.qk_norm), "no window": not head.window,
+                  "no sink_count": not head.sink_count, "train_mode 'mixture'": head.train_mode == "mixture",
+                  "model.encoder.gdn_write_mix 'none'": cfg.encoder.gdn_write_mix == "none"}
+        missing = [k for k, ok in single.items() if not ok]
+        if missing:
+            raise ValueError(f"model.cp_head.n_heads {head.n_heads} is built with: {', '.join(missing)}")
     if head.train_mode not in TRAIN_MODES:
         raise ValueError(f"model.cp_head.train_mode {head.train_mode!r}: built are {TRAIN_MODES} (the mixture's loss; the pointer's own auxiliary loss)")
     weight = head.aux_weight
@@ -146,6 +159,18 @@ class PointerMix(nn.Module):
         return PointerInputs(self.norm_q(self.read_q(sources)), self.norm_k(self.read_k(sources)))
 
 
+class HeadsMix(nn.Module):
+    """One pair of depth reads a pointer head: (x^q, x^k), each (B, L, H, d), head h's on axis -2."""
+
+    def __init__(self, d_model: int, eps: float, heads: int):
+        super().__init__()
+        self.heads = nn.ModuleList(PointerMix(d_model, eps) for _ in range(heads))
+
+    def forward(self, sources: list) -> "PointerInputs":
+        reads = [m(sources) for m in self.heads]
+        return PointerInputs(torch.stack([r.q for r in reads], dim=-2), torch.stack([r.k for r in reads], dim=-2))
+
+
 class PointerInputs(NamedTuple):
     """What the pointer's query and key projections read in one forward, each (B, L, d); the forward hands them on as
     `ModelOutput.cp_pointer` and every scoring function takes them as `pointer=`."""
@@ -171,33 +196,43 @@ class CopyPasteHead(nn.Module):
         super().__init__()
         self.cfg, self.ref_len, self.scale = cfg, int(ref_len), cfg.d_c ** -0.5
         self.gated = cfg.train_mode != "aux"            # the <copy> row exists only where something is mixed into the prediction
-        for name, shape in (("w_q", (cfg.d_c, d_model)), ("w_k", (cfg.d_c, d_model)), ("k_sink", (cfg.d_c,)), ("w_copy", (d_model,))):
+        H = self.heads = cfg.n_heads
+        for name, shape in (("w_q", (H * cfg.d_c, d_model)), ("w_k", (H * cfg.d_c, d_model)), ("k_sink", (H * cfg.d_c,)), ("w_copy", (d_model,))):
             if name != "w_copy" or self.gated:
                 self.register_parameter(name, nn.Parameter(torch.empty(shape)))
         self.d_model = d_model
         if cfg.qk_norm:
-            self.qk_gain = nn.Parameter(torch.zeros(1))
+            self.qk_gain = nn.Parameter(torch.zeros(H))
         if cfg.pointer_input == "mix":
-            self.mix = PointerMix(d_model, eps)
+            self.mix = PointerMix(d_model, eps) if H == 1 else HeadsMix(d_model, eps, H)
 
     @torch.no_grad()
     def reset_own(self, g: torch.Generator, std: float, init: str = "spec") -> None:
         """w_q, w_k, k_sink, w_copy ~ N(0, std) in that order; `reference` then redraws w_q / w_k as one uniform bank and
         the sink as N(0, 1 / d_c), w_copy keeping its draw."""
         draw = lambda shape: torch.randn(shape, generator=g, dtype=torch.float32)                  # noqa: E731
-        for name in ("w_q", "w_k", "k_sink", "w_copy"):
-            if name == "w_copy" and not self.gated:
-                draw((self.d_model,))                      # the row's draw is taken and dropped: the other tensors are the gated head's
-                continue
-            t = getattr(self, name)
-            t.copy_((draw(t.shape) * std).to(t.dtype) if t.dtype != torch.float32 else draw(t.shape) * std)
-        if init == "reference":
-            d_c, d = self.w_q.shape
-            limit = 3 ** 0.5 * d ** -0.5                           # this product, not sqrt(3 / d): equal bits with the reference's bank
-            both = torch.empty(2, d_c, d, dtype=torch.float32).uniform_(-limit, limit, generator=g)
-            self.w_q.copy_(both[0])
-            self.w_k.copy_(both[1])
-            self.k_sink.copy_(draw(d_c) * d_c ** -0.5)
+        d_c, d = self.cfg.d_c, self.d_model
+        limit = 3 ** 0.5 * d ** -0.5                           # this product, not sqrt(3 / d): equal bits with the reference's bank
+
+        def start(rows: slice) -> None:
+            """The tensors' rows of some heads: N(0, std) each, and under `reference` one uniform bank for W_Q / W_K and the sink N(0, 1 / d_c)."""
+            parts = [getattr(self, name)[rows] for name in ("w_q", "w_k", "k_sink")]
+            for t in parts:
+                t.copy_(draw(t.shape) * std)
+            if rows.start == 0:                                 # the <copy> row follows head 0's draws (taken and dropped without the row)
+                row = draw((d,)) * std
+                if self.gated:
+                    self.w_copy.copy_(row)
+            if init == "reference":
+                n = parts[0].shape[0]
+                both = torch.empty(2, n, d, dtype=torch.float32).uniform_(-limit, limit, generator=g)
+                parts[0].copy_(both[0])
+                parts[1].copy_(both[1])
+                parts[2].copy_(draw(n) * d_c ** -0.5)
+
+        start(slice(0, d_c))
+        if self.heads > 1:
+            start(slice(d_c, self.heads * d_c))
         if self.cfg.qk_norm:
             self.qk_gain.zero_()
 
@@ -207,11 +242,23 @@ class CopyPasteHead(nn.Module):
             y = F.linear(h.to(wide), w.to(wide))
             return F.rms_norm(y, y.shape[-1:], eps=NORM_EPS) if normed else y
 
+    def _project_heads(self, x, w):
+        """x (..., H, d), head h's own input, through head h's rows of w: (..., H, d_c), each head normed over its own d_c."""
+        wide = _wide(x)
+        with _no_autocast(x):
+            y = torch.einsum("...hd,hcd->...hc", x.to(wide), w.to(wide).unflatten(0, (self.heads, self.cfg.d_c)))
+            return F.rms_norm(y, y.shape[-1:], eps=NORM_EPS)
+
     def queries(self, h):
+        if self.heads > 1:
+            q = self._project_heads(h, self.w_q)
+            return (q * (1.0 + self.qk_gain.to(q.dtype)).unsqueeze(-1)).flatten(-2)
         q = self._project(h, self.w_q, self.cfg.qk_norm)
         return q * (1.0 + self.qk_gain.to(q.dtype)) if self.cfg.qk_norm else q
 
     def keys(self, h):
+        if self.heads > 1:
+            return self._project_heads(h, self.w_k).flatten(-2)
         return self._project(h, self.w_k, self.cfg.qk_norm)
 
     def copy_logit(self, h):

@@ -624,7 +624,8 @@ class Trainer:
         if self._cp is not None and self._cp.gated and cfg.log_every and step % cfg.log_every == 0:
             m["cp_lambda"] = float(self._cp_lambda)          # the mean copy weight at the scored targets of the step's last micro-batch
             if self._cp.cfg.qk_norm:
-                m["cp_qk_gain"] = 1.0 + float(self._cp.qk_gain.detach())
+                gains = (1.0 + self._cp.qk_gain.detach().float()).tolist()          # one a pointer head
+                m["cp_qk_gain"] = gains[0] if len(gains) == 1 else gains
         if self.gated:
             m["T"] = self.pass_count
             if cfg.log_every and step % cfg.log_every == 0:

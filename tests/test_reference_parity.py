@@ -807,7 +807,8 @@ def test_gated_second_pass_is_refused_by_name_where_it_is_not_built():
 
 @pytest.mark.parametrize("base,keys", [("control", {}), ("control", {"qk_norm": True, "init": "reference"}),
                                        ("control", {"qk_norm": True, "temperature": "ssmax", "sink_count": True}), ("full", {"qk_norm": True}),
-                                       ("control", {"window": 7}), ("full", {"pointer_input": "mix", "qk_norm": True, "temperature": "ssmax"})])
+                                       ("control", {"window": 7}), ("full", {"pointer_input": "mix", "qk_norm": True, "temperature": "ssmax"}),
+                                       ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "init": "reference"}), ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 2, "temperature": "ssmax"})])
 def test_copy_paste_head_equals_the_reference(reference, base, keys):
     """The Copy-Paste head in its base form: the head's tensors last in the state dict with equal starts, the mixture's log p over V
     (it sums to one and equals the training cross entropy at the target), the blockwise terms against the reference's and an
@@ -820,11 +821,13 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
     cfg.cp_head.enabled, cfg.cp_head.d_c, cfg.cp_head.query_chunk, cfg.encoder.gdn_write_variant = True, 8, 16, "none"
     for k, v in keys.items():
         setattr(cfg.cp_head, k, v)
+    if keys.get("n_heads", 1) > 1:
+        cfg.encoder.gdn_write_mix = "none"
     mine, theirs = _pair(reference, cfg)
     sd, rsd = mine.state_dict(), theirs.state_dict()
     assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd) and list(sd)[-1].startswith("cp_head.")
     plain = C.tiny_full_config() if base == "full" else C.tiny_control_config()
-    plain.encoder.gdn_write_variant = "none"
+    plain.encoder.gdn_write_variant, plain.encoder.gdn_write_mix = "none", cfg.encoder.gdn_write_mix
     torch.manual_seed(0)
     trunk = build_model(plain).double().state_dict()
     assert all(torch.equal(trunk[k], sd[k]) for k in trunk)                    # the base model starts as the model without the key
@@ -875,7 +878,7 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
 
 
 def test_copy_paste_head_is_refused_by_name_where_it_is_not_built():
-    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"),
+    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.combine", "or", "combine"),
                               ("cp_head.trunk_copy", "all", "trunk_copy"), ("cp_head.train_mode", "addon", "train_mode"), ("cp_head.window", -1, "window"), ("cp_head.kernel", "fused", "kernel"),
                               ("cp_head.init", "zeros", "init"), ("cp_head.d_c", 0, "d_c"), ("loop.recur_layers", "[2, 6]", "one pass"),
                               ("encoder.gdn_ccr_spacing", 8, "gdn_ccr_spacing"), ("encoder.attn_res", "ldm", "attn_res")):
