@@ -33,11 +33,14 @@ the trunk and the LM head learn from p_LM's loss alone, and the head from the mi
 log p_LM(y)), the <copy> row's input h and the readers' sources are all detached, so no gradient of the mixture reaches a
 trunk tensor (`addon_loss`); the trainer clips the two parts by their own norms.
 Refused by name: the pointer that reads an attention head (`pointer_input: shared`), several pointer heads, the copy from
-the trunk's own attention (`trunk_copy`), the heads mixed by a router (`combine: or`), the fused kernel. Several pointer
+the trunk's own attention (`trunk_copy`), the fused kernel. Several pointer
 heads (`n_heads` H on the `mix` pointer with `qk_norm`): head h has its own pair of depth reads (`cp_head.mix.heads.<h>`), its
 own rows h d_c .. (h + 1) d_c - 1 of W_Q / W_K, its own norm over d_c, gain and slice of the sink key; q and k are held flat
 (H d_c) and scored at 1 / sqrt(d_c), which sums the heads' scores into one logit a position, one softmax; head 0 and the
-<copy> row are drawn first, so they are the one-head pointer's of the same seed.
+<copy> row are drawn first, so they are the one-head pointer's of the same seed. `combine: or` keeps the heads apart: head h
+has its own s_h, alpha_h, p_CP,h, and a router pi_t = softmax_h(W_route h_t) (`head_router`, zeros: uniform) mixes the
+heads' distributions over {sink} u ctx: log s = LSE_h(log pi_h + log s_h), log(1 - s) = LSE_h(log pi_h + log(1 - s_h)),
+w_h = pi_h (1 - s_h) / (1 - s), p_CP = sum_h w_h p_CP,h; at one head log pi = 0 and the router is never read.
 Reference: ced/model/cp_head.py:1-100 (the form), :454-660 (the module), :899-1016 (length rule, block terms),
 :1223-1245 (mixture), :1282-1370 (inference), :1443-1483 (cache).
 """
@@ -57,7 +60,8 @@ from torch.utils.checkpoint import checkpoint as recompute
 
 OWN_SEED_OFFSET = 0xC0_2610_19247        # shared with the reference: equal starts under equal seeds
 NORM_EPS = 2.0 ** -23
-BASE_FORM = dict(combine="and", trunk_copy="none", kernel="reference")
+BASE_FORM = dict(trunk_copy="none", kernel="reference")
+COMBINES = ("and", "or")
 TRAIN_MODES = ("mixture", "aux", "addon")
 POINTER_INPUTS = ("final", "mix")
 SOURCES_KEY = "cp_pointer_sources"       # where a block-entry stack leaves [b_0 .. b_N] for the pointer's readers (SeqContext.memo)
@@ -71,7 +75,13 @@ def check_config(cfg) -> None:
         return
     off_base = [f"{name} {getattr(head, name)!r}" for name, base in BASE_FORM.items() if getattr(head, name) != base]
     if off_base:
-        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built with the heads' scores summed (combine 'and'), no trunk copy, kernel 'reference'")
+        raise ValueError(f"model.cp_head {', '.join(off_base)}: the head is built without the trunk copy, kernel 'reference'")
+    if head.combine not in COMBINES:
+        raise ValueError(f"model.cp_head.combine {head.combine!r}: one of {COMBINES}")
+    if head.combine == "or" and (head.pointer_input != "mix" or not head.qk_norm or head.window or head.sink_count or head.train_mode != "mixture"
+                                 or cfg.encoder.gdn_write_mix != "none"):
+        raise ValueError("model.cp_head.combine 'or' (the heads mixed by a router) is built on the pointer on depth reads with qk_norm, without window or "
+                         "sink_count, train_mode 'mixture', model.encoder.gdn_write_mix 'none'")
     if type(head.n_heads) is not int or head.n_heads < 1:
         raise ValueError(f"model.cp_head.n_heads {head.n_heads!r}: the pointer's heads, an integer >= 1")
     if head.n_heads > 1:
@@ -203,6 +213,8 @@ class CopyPasteHead(nn.Module):
         self.d_model = d_model
         if cfg.qk_norm:
             self.qk_gain = nn.Parameter(torch.zeros(H))
+        if cfg.combine == "or":
+            self.head_router = nn.Parameter(torch.zeros(H, d_model))
         if cfg.pointer_input == "mix":
             self.mix = PointerMix(d_model, eps) if H == 1 else HeadsMix(d_model, eps, H)
 
@@ -235,6 +247,8 @@ class CopyPasteHead(nn.Module):
             start(slice(d_c, self.heads * d_c))
         if self.cfg.qk_norm:
             self.qk_gain.zero_()
+        if self.cfg.combine == "or":
+            self.head_router.zero_()
 
     def _project(self, h, w, normed: bool):
         wide = _wide(h)
@@ -260,6 +274,14 @@ class CopyPasteHead(nn.Module):
         if self.heads > 1:
             return self._project_heads(h, self.w_k).flatten(-2)
         return self._project(h, self.w_k, self.cfg.qk_norm)
+
+    def route(self, h):
+        """log pi (..., H) of `combine: or` from the final norm's output; zeros at one head, without reading h or the router."""
+        wide = _wide(h)
+        if self.heads == 1:
+            return h.new_zeros(*h.shape[:-1], 1, dtype=wide)
+        with _no_autocast(h):
+            return F.linear(h.to(wide), self.head_router.to(wide)).log_softmax(-1)
 
     def copy_logit(self, h):
         if not self.gated:
@@ -370,15 +392,30 @@ def attend(rule: LengthRule, q, k, k_sink, visible) -> Scores:
     return Scores(e, sink, norm_ctx, torch.logaddexp(sink, norm_ctx))
 
 
-def _train_block(rule, q, k, k_sink, k_tok, k_doc, k_idx, q_idx, q_doc, q_tgt):
-    """One block of queries: the three terms as a plain tuple (what a recomputed block returns)."""
-    sc = attend(rule, q, k, k_sink, context_mask(k_idx, k_doc, q_idx, q_doc, rule.window))
-    hit = (k_tok.unsqueeze(1) == q_tgt.unsqueeze(2)) & torch.isfinite(sc.e)
+def _head_terms(rule, q, k, k_sink, seen, same_token):
+    """One head's (scores, log p_CP(target) where a key matches, the rows without a match). A row without a matching key is
+    read as zeros: its LSE is finite and its gradient exactly zero; the caller writes -inf there."""
+    sc = attend(rule, q, k, k_sink, seen)
+    hit = same_token & seen
     none = ~hit.any(-1)
-    # a row without a matching key is read as zeros: its LSE is finite, its gradient exactly zero, its result -inf below
     picked = sc.e.masked_fill(~hit, float("-inf")).masked_fill(none.unsqueeze(-1), 0.0)
-    log_copy = (picked.logsumexp(-1) - sc.norm_ctx).masked_fill(none, float("-inf"))
-    return tuple(sc.pointer(log_copy))
+    return sc, picked.logsumexp(-1) - sc.norm_ctx, none
+
+
+def _train_block(rule, q, k, k_sink, k_tok, k_doc, k_idx, q_idx, q_doc, q_tgt, log_pi=None):
+    """One block of queries: the three terms as a plain tuple (what a recomputed block returns). log_pi (B, C, H): the
+    router's log weights of `combine: or`, the heads then scored one by one on their slices and mixed."""
+    seen = context_mask(k_idx, k_doc, q_idx, q_doc, rule.window)
+    same_token = k_tok.unsqueeze(1) == q_tgt.unsqueeze(2)
+    if log_pi is None:
+        sc, log_copy, none = _head_terms(rule, q, k, k_sink, seen, same_token)
+        return tuple(sc.pointer(log_copy.masked_fill(none, float("-inf"))))
+    H = log_pi.shape[-1]
+    per = [_head_terms(rule, qh, kh, sh, seen, same_token) for qh, kh, sh in zip(q.chunk(H, -1), k.chunk(H, -1), k_sink.chunk(H, -1))]
+    sink = torch.stack([sc.sink - sc.norm_all for sc, _, _ in per], -1) + log_pi              # log pi_h + log s_h
+    ctx = torch.stack([sc.norm_ctx - sc.norm_all for sc, _, _ in per], -1) + log_pi             # log pi_h + log(1 - s_h)
+    log_copy = (ctx.log_softmax(-1) + torch.stack([c for _, c, _ in per], -1)).logsumexp(-1)
+    return sink.logsumexp(-1), ctx.logsumexp(-1), log_copy.masked_fill(per[0][2], float("-inf"))
 
 
 def terms(head, hidden, tokens, targets, doc_ids, chunk: int | None = None, checkpoint: bool = False, keys: CopyKeys | None = None,
@@ -394,6 +431,7 @@ def terms(head, hidden, tokens, targets, doc_ids, chunk: int | None = None, chec
         at = torch.arange(L, device=tokens.device).expand(B, L)
         keys, q_idx = CopyKeys(head.keys(k_side), tokens, doc_ids, at), at
     sink_key = head.k_sink.to(q.dtype)
+    log_pi = head.route(hidden).to(q.dtype) if head.cfg.combine == "or" else None
     block = partial(_train_block, head.rule())
     if checkpoint and torch.is_grad_enabled():
         block = partial(recompute, block, use_reentrant=False)
@@ -401,7 +439,8 @@ def terms(head, hidden, tokens, targets, doc_ids, chunk: int | None = None, chec
     for lo in range(0, L, step):
         hi = min(lo + step, L)
         ks = keys.upto(hi) if causal_cut else keys
-        blocks.append(block(q[:, lo:hi], ks.k, sink_key, ks.tok, ks.doc, ks.idx, q_idx[:, lo:hi], doc_ids[:, lo:hi], targets[:, lo:hi]))
+        blocks.append(block(q[:, lo:hi], ks.k, sink_key, ks.tok, ks.doc, ks.idx, q_idx[:, lo:hi], doc_ids[:, lo:hi], targets[:, lo:hi],
+                            None if log_pi is None else log_pi[:, lo:hi]))
     return Pointer(*(torch.cat(column, dim=1) for column in zip(*blocks)))
 
 
@@ -410,6 +449,8 @@ def terms_naive(head, hidden, tokens, targets, doc_ids, pointer: PointerInputs |
     B, L = tokens.shape
     at = torch.arange(L, device=tokens.device).expand(B, L)
     q_side, k_side = pointer_sides(head, hidden, pointer)
+    if head.cfg.combine == "or":
+        raise ValueError("terms_naive states the single softmax of combine 'and'")
     sc = attend(head.rule(), head.queries(q_side), head.keys(k_side), head.k_sink.to(_wide(hidden)), context_mask(at, doc_ids, at, doc_ids, head.cfg.window))
     with_sink = torch.cat([sc.sink.unsqueeze(-1), sc.e], dim=-1).softmax(-1)
     share = with_sink[..., 0]
@@ -459,8 +500,18 @@ def logprobs_rows(head, hidden_q, q_idx, q_doc, keys: CopyKeys, weight_v, chunk:
             span = slice(lo, lo + step)
             h = hidden_q[:, span].to(wide)
             q = head.queries(h if q_side is None else q_side[:, span].to(wide))
-            sc = attend(rule, q, k, sink_key, context_mask(keys.idx, keys.doc, q_idx[:, span], q_doc[:, span], rule.window))
-            weights = (sc.e - sc.norm_ctx.unsqueeze(-1)).exp()                                      # alpha: softmax over the context alone
+            seen = context_mask(keys.idx, keys.doc, q_idx[:, span], q_doc[:, span], rule.window)
+            if head.cfg.combine == "or":            # each head's own softmaxes, mixed by the router's weights
+                H, log_pi = head.heads, head.route(h)
+                per = [attend(rule, qh, kh, sh, seen) for qh, kh, sh in zip(q.chunk(H, -1), k.chunk(H, -1), sink_key.chunk(H, -1))]
+                ctx = torch.stack([x.norm_ctx - x.norm_all for x in per], -1) + log_pi
+                share = ctx.softmax(-1)
+                weights = sum(share[..., i:i + 1] * (x.e - x.norm_ctx.unsqueeze(-1)).exp() for i, x in enumerate(per))
+                log_sink = (torch.stack([x.sink - x.norm_all for x in per], -1) + log_pi).logsumexp(-1)
+                sc = Scores(None, log_sink, ctx.logsumexp(-1), torch.zeros_like(log_sink))      # already normalised: sink and context in logs
+            else:
+                sc = attend(rule, q, k, sink_key, seen)
+                weights = (sc.e - sc.norm_ctx.unsqueeze(-1)).exp()                                  # alpha: softmax over the context alone
             logits = F.linear(h, vocab)
             p_copy = torch.zeros_like(logits).scatter_add_(2, keys.tok.unsqueeze(1).expand_as(weights), weights)
             log_copy = p_copy.clamp_min(torch.finfo(wide).tiny).log().masked_fill(p_copy <= 0, float("-inf"))

@@ -808,7 +808,8 @@ def test_gated_second_pass_is_refused_by_name_where_it_is_not_built():
 @pytest.mark.parametrize("base,keys", [("control", {}), ("control", {"qk_norm": True, "init": "reference"}),
                                        ("control", {"qk_norm": True, "temperature": "ssmax", "sink_count": True}), ("full", {"qk_norm": True}),
                                        ("control", {"window": 7}), ("full", {"pointer_input": "mix", "qk_norm": True, "temperature": "ssmax"}),
-                                       ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "init": "reference"}), ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 2, "temperature": "ssmax"})])
+                                       ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "init": "reference"}), ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 2, "temperature": "ssmax"}),
+                                       ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "combine": "or"}), ("full", {"pointer_input": "mix", "qk_norm": True, "combine": "or"})])
 def test_copy_paste_head_equals_the_reference(reference, base, keys):
     """The Copy-Paste head in its base form: the head's tensors last in the state dict with equal starts, the mixture's log p over V
     (it sums to one and equals the training cross entropy at the target), the blockwise terms against the reference's and an
@@ -821,7 +822,7 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
     cfg.cp_head.enabled, cfg.cp_head.d_c, cfg.cp_head.query_chunk, cfg.encoder.gdn_write_variant = True, 8, 16, "none"
     for k, v in keys.items():
         setattr(cfg.cp_head, k, v)
-    if keys.get("n_heads", 1) > 1:
+    if keys.get("n_heads", 1) > 1 or keys.get("combine") == "or":
         cfg.encoder.gdn_write_mix = "none"
     mine, theirs = _pair(reference, cfg)
     sd, rsd = mine.state_dict(), theirs.state_dict()
@@ -844,7 +845,7 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
     ha, hb, pa, pb = oa.hidden_aux, ob.hidden_aux, oa.cp_pointer, ob.cp_pointer
     assert (pa is None) == (keys.get("pointer_input") != "mix")
     ta, tb = CP.terms(mine.cp_head, ha, tok, tgt, doc, pointer=pa), RCP.cp_terms(theirs.cp_head, hb, tok, tgt, doc, pointer=pb)
-    tn = CP.terms_naive(mine.cp_head, ha, tok, tgt, doc, pointer=pa)
+    tn = ta if keys.get("combine") == "or" else CP.terms_naive(mine.cp_head, ha, tok, tgt, doc, pointer=pa)
     for x, y, z in zip(ta, tb, tn):
         fin = torch.isfinite(y)
         assert torch.equal(torch.isfinite(x), fin) and torch.equal(torch.isfinite(z), fin) and (x - y)[fin].abs().max() < 1e-10 and (x - z)[fin].abs().max() < 1e-9
@@ -878,7 +879,7 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
 
 
 def test_copy_paste_head_is_refused_by_name_where_it_is_not_built():
-    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.combine", "or", "combine"),
+    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.combine", "or", "combine"), ("cp_head.combine", "xor", "combine"),
                               ("cp_head.trunk_copy", "all", "trunk_copy"), ("cp_head.train_mode", "addon", "train_mode"), ("cp_head.window", -1, "window"), ("cp_head.kernel", "fused", "kernel"),
                               ("cp_head.init", "zeros", "init"), ("cp_head.d_c", 0, "d_c"), ("loop.recur_layers", "[2, 6]", "one pass"),
                               ("encoder.gdn_ccr_spacing", 8, "gdn_ccr_spacing"), ("encoder.attn_res", "ldm", "attn_res")):
