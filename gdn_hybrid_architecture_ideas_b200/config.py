@@ -799,7 +799,7 @@ _UNREAD = (
     "model.encoder.write_mix_storage", "model.encoder.write_mix_row_term", "model.decoder.self_kv", "model.decoder.read_pattern",
     "model.decoder.local_window", "model.decoder.local_temperature", "model.loop.hc_res_init", "model.second_pass.pass_embedding",
     "model.fp8.te_nonfinite_check", "model.fp8.te_operands", "model.fp8.nonfinite_flag", "model.fp8.nonfinite_flag_form",
-    "model.cp_head.shared_layer", "model.cp_head.shared_head", "model.cp_head.shared_ssmax", "model.cp_head.trunk_k",
+    "model.cp_head.trunk_k",
     "model.cp_head.trunk_select_step")
 # The slot decoder's keys: read by arch 'looped_ced' (models/looped_decoder.py), by nothing on the hybrid stack.
 _UNREAD_STACK = (

@@ -40,6 +40,8 @@ class KeySet:
     ok: torch.Tensor
     k_far: torch.Tensor | None = None
     pos: torch.Tensor | None = None
+    cp_q: torch.Tensor | None = None           # the Copy-Paste pointer's shared head: this chunk's head query and its key head's key
+    cp_k: torch.Tensor | None = None           # (B, L, hd) each; set by the shared layer, taken off by the model, not joined by `cat`
     canon_input: torch.Tensor | None = None    # last K - 1 inputs of the layer's Canon convolution and their documents:
     canon_doc: torch.Tensor | None = None      # set by the encoder layer, not joined by `cat`
 
@@ -156,6 +158,8 @@ class GatedAttention(nn.Module):
         self.k_norm = RMSNorm(hd, norm_eps) if cfg.qk_norm else nn.Identity()
         self.temp_w = nn.Parameter(torch.zeros(hq)) if cfg.temperature != "fixed" else None
         self.cap = rope_cap(cfg)
+        self.cp_query = None      # (head, after the temperature?) when the Copy-Paste pointer shares one of this layer's heads (models/cp_head.py)
+        self._q_plain = None
         if cfg.normalizer not in ("softmax", "asentmax"):
             raise ValueError(f"attention.normalizer {cfg.normalizer!r}: 'softmax' or 'asentmax'")
         self.entmax = cfg.normalizer == "asentmax"
@@ -225,6 +229,7 @@ class GatedAttention(nn.Module):
                 gate = self.g_proj(x).view(B, L, hq, 1)
         qn = self.q_norm(q)
         q = self._rot(qn, rot_pos)
+        self._q_plain = q if self.cp_query is not None else None        # the shared head's query before the temperature
         q_far = self._rot(qn, rot_pos.new_full((1, 1), self.cap)) if self.cap is not None else None
         f = self.query_factor(pos, torch.promote_types(q.dtype, torch.float32))
         if self.entmax:
@@ -252,7 +257,7 @@ class GatedAttention(nn.Module):
         dimension 64, QK-norm on, fixed temperature, grouped (not grid) keys, 0 or a power of two (<= 32) rotary pairs."""
         cfg = self.cfg
         r2 = rotary_dims(cfg.head_dim, cfg.rope_fraction) // 2
-        return (ops.use_native(x) and not self.entmax and x.dtype == torch.bfloat16 and self.grid is None and cfg.qk_norm and cfg.temperature == "fixed"
+        return (ops.use_native(x) and not self.entmax and self.cp_query is None and x.dtype == torch.bfloat16 and self.grid is None and cfg.qk_norm and cfg.temperature == "fixed"
                 and cfg.head_dim == 64 and cfg.gate in ("elementwise", "none") and r2 in (0, 2, 4, 8, 16, 32))
 
     def _forward_fused(self, x, ctx, cache, rot_pos, cap):
@@ -318,6 +323,12 @@ class GatedAttention(nn.Module):
             new = KeySet(k=k_new, v=self.v_proj(x).view(B, L, hkv, hd), idx=ctx.idx, doc=ctx.doc, ok=ok, k_far=kf_new)
             keys = KeySet.cat(cache, new)
             k, k_far, v = keys.k, keys.k_far, keys.v
+            if self.cp_query is not None:      # this chunk's query of the shared head and the key of the key head that serves it
+                import dataclasses
+
+                head, after_temperature = self.cp_query
+                keys = dataclasses.replace(keys, cp_q=(q if after_temperature else self._q_plain)[:, :, head], cp_k=k_new[:, :, head // (cfg.n_q_heads // hkv)])
+                self._q_plain = None
         if self.entmax:      # the exact tensor-op statement on every path
             o = ops.ref.entmax_attention(q, k, v, ctx.idx, ctx.doc, keys.idx, keys.doc, None if cache is None else keys.ok,
                                          chunk=self.cfg.asentmax_chunk)

@@ -32,8 +32,7 @@ pointer is dropped (logits are p_LM's, no copy cache), so every scorer reads the
 the trunk and the LM head learn from p_LM's loss alone, and the head from the mixture's CE in which p_LM's numbers (LSE_V,
 log p_LM(y)), the <copy> row's input h and the readers' sources are all detached, so no gradient of the mixture reaches a
 trunk tensor (`addon_loss`); the trainer clips the two parts by their own norms.
-Refused by name: the pointer that reads an attention head (`pointer_input: shared`), several pointer heads, the copy from
-the trunk's own attention (`trunk_copy`), the fused kernel. Several pointer
+Refused by name: the copy from the trunk's own attention (`trunk_copy`), the fused kernel. Several pointer
 heads (`n_heads` H on the `mix` pointer with `qk_norm`): head h has its own pair of depth reads (`cp_head.mix.heads.<h>`), its
 own rows h d_c .. (h + 1) d_c - 1 of W_Q / W_K, its own norm over d_c, gain and slice of the sink key; q and k are held flat
 (H d_c) and scored at 1 / sqrt(d_c), which sums the heads' scores into one logit a position, one softmax; head 0 and the
@@ -63,7 +62,7 @@ NORM_EPS = 2.0 ** -23
 BASE_FORM = dict(trunk_copy="none", kernel="reference")
 COMBINES = ("and", "or")
 TRAIN_MODES = ("mixture", "aux", "addon")
-POINTER_INPUTS = ("final", "mix")
+POINTER_INPUTS = ("final", "mix", "shared")
 SOURCES_KEY = "cp_pointer_sources"       # where a block-entry stack leaves [b_0 .. b_N] for the pointer's readers (SeqContext.memo)
 CHOICES = dict(init=("spec", "reference"), score=("mixture", "lm"), temperature=("none", "ssmax"))
 ENV_SCORE = "GHB_CP_SCORE"               # a scoring process's override of model.cp_head.score
@@ -115,7 +114,19 @@ def check_config(cfg) -> None:
             raise ValueError("model.cp_head.train_mode 'aux' is built for the pointer on depth reads (pointer_input 'mix') without force_lambda_zero, score, "
                              f"temperature or sink_count (set: pointer_input {head.pointer_input!r}{', ' + ', '.join(wrong) if wrong else ''})")
     if head.pointer_input not in POINTER_INPUTS:
-        raise ValueError(f"model.cp_head.pointer_input {head.pointer_input!r}: built are {POINTER_INPUTS} (the final norm's output, or depth reads of the finished blocks)")
+        raise ValueError(f"model.cp_head.pointer_input {head.pointer_input!r}: built are {POINTER_INPUTS} (the final norm's output, depth reads of the finished "
+                         "blocks, or one head of a global attention layer)")
+    if head.pointer_input == "shared":
+        shared_layer_index(cfg)
+        plain = type(head)()
+        clash = {"d_c (the width is the shared head's)": head.d_c != plain.d_c, "qk_norm false": not head.qk_norm, "window": bool(head.window),
+                 "temperature (the shared head's form is shared_ssmax)": head.temperature != "none", "n_heads": head.n_heads != 1,
+                 "train_mode": head.train_mode != "mixture", "model.encoder.gdn_write_mix": cfg.encoder.gdn_write_mix != "none"}
+        hit = [k for k, v in clash.items() if v]
+        if hit:
+            raise ValueError(f"model.cp_head.pointer_input 'shared' is not built together with: {', '.join(hit)}")
+    elif (head.shared_layer, head.shared_head, head.shared_ssmax) != (-1, 0, False):
+        raise ValueError("model.cp_head.shared_layer / shared_head / shared_ssmax are read with pointer_input 'shared'")
     if type(head.window) is not int or head.window < 0:
         raise ValueError(f"model.cp_head.window {head.window!r}: the pointer's reach in positions, an integer >= 1 (0: every earlier position)")
     if head.window and (head.temperature != "none" or head.sink_count or head.pointer_input != "final"):
@@ -142,6 +153,25 @@ def check_config(cfg) -> None:
         clashes.append("model.mtp")
     if clashes:
         raise ValueError(f"model.cp_head is not built with: {'; '.join(clashes)}")
+
+
+def shared_layer_index(cfg) -> int:
+    """The stack index of the global layer whose head the pointer shares (`shared_layer`; -1: the last global layer): a layer
+    without a rotary part (its score is its own q . k), with QK-norm and the softmax normaliser, `shared_head` one of its heads."""
+    head, enc = cfg.cp_head, cfg.encoder
+    layers = enc.global_layers()
+    if not layers:
+        raise ValueError("model.cp_head.pointer_input 'shared' needs a global attention layer in the stack: there is none")
+    at = layers[-1] if head.shared_layer == -1 else head.shared_layer
+    if at not in layers:
+        raise ValueError(f"model.cp_head.shared_layer {at}: not a global attention layer of the stack (they are {layers})")
+    attn = enc.global_attention()[layers.index(at)]
+    if attn.rope_fraction != 0.0 or not attn.qk_norm or attn.normalizer != "softmax" or attn.kv_sharing != "gqa":
+        raise ValueError(f"model.cp_head.shared_layer {at}: the pointer shares a head of a global layer without a rotary part (model.encoder.nope_global_layers) "
+                         "that has QK-norm, the softmax normaliser and grouped keys")
+    if not 0 <= head.shared_head < attn.n_q_heads:
+        raise ValueError(f"model.cp_head.shared_head {head.shared_head}: layer {at} has {attn.n_q_heads} query heads")
+    return at
 
 
 def _wide(x: torch.Tensor) -> torch.dtype:
@@ -196,19 +226,22 @@ def pointer_sides(head, hidden, pointer):
             raise ValueError("pointer inputs were given to a Copy-Paste head whose pointer reads h (model.cp_head.pointer_input 'final')")
         return hidden, hidden
     if pointer is None:
-        raise ValueError("this Copy-Paste head's pointer reads the finished blocks (model.cp_head.pointer_input 'mix'): pass the forward's "
+        raise ValueError(f"this Copy-Paste head's pointer reads inputs of its own (model.cp_head.pointer_input {head.cfg.pointer_input!r}): pass the forward's "
                          "ModelOutput.cp_pointer as pointer=")
     return pointer.q, pointer.k
 
 
 class CopyPasteHead(nn.Module):
-    def __init__(self, d_model: int, cfg, ref_len: int = 8192, eps: float = 1e-6):
+    def __init__(self, d_model: int, cfg, ref_len: int = 8192, eps: float = 1e-6, shared_width: int | None = None):
+        """shared_width: the shared head's head_dim under `pointer_input: shared` (the pointer's width and the sink key's)."""
         super().__init__()
-        self.cfg, self.ref_len, self.scale = cfg, int(ref_len), cfg.d_c ** -0.5
+        self.shared, self.shared_layer = shared_width is not None, None
+        self.width = shared_width if self.shared else cfg.d_c
+        self.cfg, self.ref_len, self.scale = cfg, int(ref_len), self.width ** -0.5
         self.gated = cfg.train_mode != "aux"            # the <copy> row exists only where something is mixed into the prediction
         H = self.heads = cfg.n_heads
-        for name, shape in (("w_q", (H * cfg.d_c, d_model)), ("w_k", (H * cfg.d_c, d_model)), ("k_sink", (H * cfg.d_c,)), ("w_copy", (d_model,))):
-            if name != "w_copy" or self.gated:
+        for name, shape in (("w_q", (H * cfg.d_c, d_model)), ("w_k", (H * cfg.d_c, d_model)), ("k_sink", (H * self.width,)), ("w_copy", (d_model,))):
+            if (name != "w_copy" or self.gated) and not (self.shared and name in ("w_q", "w_k")):
                 self.register_parameter(name, nn.Parameter(torch.empty(shape)))
         self.d_model = d_model
         if cfg.qk_norm:
@@ -228,7 +261,10 @@ class CopyPasteHead(nn.Module):
 
         def start(rows: slice) -> None:
             """The tensors' rows of some heads: N(0, std) each, and under `reference` one uniform bank for W_Q / W_K and the sink N(0, 1 / d_c)."""
-            parts = [getattr(self, name)[rows] for name in ("w_q", "w_k", "k_sink")]
+            if self.shared:         # the base pointer's tensors drawn into stand-ins and dropped: the <copy> row is the base head's
+                parts = [torch.empty(d_c, d), torch.empty(d_c, d), torch.empty(d_c)]
+            else:
+                parts = [getattr(self, name)[rows] for name in ("w_q", "w_k", "k_sink")]
             for t in parts:
                 t.copy_(draw(t.shape) * std)
             if rows.start == 0:                                 # the <copy> row follows head 0's draws (taken and dropped without the row)
@@ -245,6 +281,8 @@ class CopyPasteHead(nn.Module):
         start(slice(0, d_c))
         if self.heads > 1:
             start(slice(d_c, self.heads * d_c))
+        if self.shared:             # the sink in the shared head's key space, after the base head's draws
+            self.k_sink.copy_(draw(self.width) * (self.width ** -0.5 if init == "reference" else std))
         if self.cfg.qk_norm:
             self.qk_gain.zero_()
         if self.cfg.combine == "or":
@@ -264,6 +302,10 @@ class CopyPasteHead(nn.Module):
             return F.rms_norm(y, y.shape[-1:], eps=NORM_EPS)
 
     def queries(self, h):
+        if self.shared:             # h is the shared head's own QK-normed query
+            wide = _wide(h)
+            with _no_autocast(h):
+                return h.to(wide) * (1.0 + self.qk_gain.to(wide))
         if self.heads > 1:
             q = self._project_heads(h, self.w_q)
             return (q * (1.0 + self.qk_gain.to(q.dtype)).unsqueeze(-1)).flatten(-2)
@@ -271,6 +313,8 @@ class CopyPasteHead(nn.Module):
         return q * (1.0 + self.qk_gain.to(q.dtype)) if self.cfg.qk_norm else q
 
     def keys(self, h):
+        if self.shared:
+            return h.to(_wide(h))
         if self.heads > 1:
             return self._project_heads(h, self.w_k).flatten(-2)
         return self._project(h, self.w_k, self.cfg.qk_norm)
@@ -297,7 +341,14 @@ def attach(model) -> None:
     """Registers the head on the model, drawn from a generator of its own."""
     mc = model.cfg
     seed = (torch.initial_seed() + OWN_SEED_OFFSET) % (1 << 63)
-    model.cp_head = CopyPasteHead(mc.d_model, mc.cp_head, mc.encoder.attention.temperature_ref_len, mc.norm_eps)
+    width = None
+    if mc.cp_head.pointer_input == "shared":
+        at = shared_layer_index(mc)
+        mixer = model.encoder.layers[at].mixer
+        mixer.cp_query, width = (mc.cp_head.shared_head, bool(mc.cp_head.shared_ssmax)), mixer.cfg.head_dim
+    model.cp_head = CopyPasteHead(mc.d_model, mc.cp_head, mc.encoder.attention.temperature_ref_len, mc.norm_eps, width)
+    if width is not None:
+        model.cp_head.shared_layer = at
     if mc.cp_head.pointer_input == "mix":
         model.encoder.keep_sources = True        # the stack leaves [b_0 .. b_N] in the forward's memo
     model.cp_head.reset_own(torch.Generator().manual_seed(seed), mc.init_std, mc.cp_head.init)

@@ -222,6 +222,17 @@ class HybridLM(nn.Module):
                                      T=None if self.gated else T)
         hidden = self.final_norm(h)
         copy_cache = pointer = None
+        if getattr(self, "cp_head", None) is not None and self.cfg.cp_head.pointer_input == "shared":
+            import dataclasses
+
+            from .cp_head import PointerInputs
+
+            entry = caches[self.cp_head.shared_layer]
+            if entry is None or entry.cp_q is None:
+                raise ValueError("model.cp_head.pointer_input 'shared': the shared layer handed over no query and key (activation checkpointing drops a layer's key set)")
+            pointer = PointerInputs(entry.cp_q, entry.cp_k)
+            caches = list(caches)
+            caches[self.cp_head.shared_layer] = dataclasses.replace(entry, cp_q=None, cp_k=None)       # a cache keeps keys only
         if getattr(self, "cp_head", None) is not None and self.cfg.cp_head.pointer_input == "mix":
             from .cp_head import SOURCES_KEY
 

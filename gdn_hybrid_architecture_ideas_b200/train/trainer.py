@@ -173,6 +173,8 @@ class Trainer:
         if self._cp is not None:
             clashes = {"tensor_parallel": cfg.tensor_parallel > 1, "cuda_graphs": cfg.cuda_graphs != "none", "tst.schedule": bool(cfg.tst.schedule),
                        "shape_schedule": bool(cfg.shape_schedule), "head_impl 'fused' (the mixture runs on the chunked head: set head_impl 'chunked')": cfg.head_impl == "fused"}
+            if cfg.model.cp_head.pointer_input == "shared":     # a recomputed layer returns no key set, and with it no head query and key
+                clashes["activation_checkpoint (pointer_input 'shared' reads the shared layer's key set: set it 'none')"] = cfg.activation_checkpoint != "none"
             if cfg.model.cp_head.train_mode == "addon":        # the two clips are one process's
                 clashes.update({"data parallelism (train_mode 'addon')": self.world > 1, "freeze_trunk (train_mode 'addon')": bool(cfg.freeze_trunk)})
             hit = [k for k, v in clashes.items() if v]

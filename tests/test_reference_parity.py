@@ -809,7 +809,9 @@ def test_gated_second_pass_is_refused_by_name_where_it_is_not_built():
                                        ("control", {"qk_norm": True, "temperature": "ssmax", "sink_count": True}), ("full", {"qk_norm": True}),
                                        ("control", {"window": 7}), ("full", {"pointer_input": "mix", "qk_norm": True, "temperature": "ssmax"}),
                                        ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "init": "reference"}), ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 2, "temperature": "ssmax"}),
-                                       ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "combine": "or"}), ("full", {"pointer_input": "mix", "qk_norm": True, "combine": "or"})])
+                                       ("full", {"pointer_input": "mix", "qk_norm": True, "n_heads": 3, "combine": "or"}), ("full", {"pointer_input": "mix", "qk_norm": True, "combine": "or"}),
+                                       ("full", {"pointer_input": "shared", "qk_norm": True, "shared_head": 3, "init": "reference"}),
+                                       ("full", {"pointer_input": "shared", "qk_norm": True, "shared_ssmax": True, "sink_count": True})])
 def test_copy_paste_head_equals_the_reference(reference, base, keys):
     """The Copy-Paste head in its base form: the head's tensors last in the state dict with equal starts, the mixture's log p over V
     (it sums to one and equals the training cross entropy at the target), the blockwise terms against the reference's and an
@@ -822,8 +824,11 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
     cfg.cp_head.enabled, cfg.cp_head.d_c, cfg.cp_head.query_chunk, cfg.encoder.gdn_write_variant = True, 8, 16, "none"
     for k, v in keys.items():
         setattr(cfg.cp_head, k, v)
-    if keys.get("n_heads", 1) > 1 or keys.get("combine") == "or":
+    if keys.get("n_heads", 1) > 1 or keys.get("combine") == "or" or keys.get("pointer_input") == "shared":
         cfg.encoder.gdn_write_mix = "none"
+    if keys.get("pointer_input") == "shared":
+        cfg.encoder.nope_global_layers = (2,)            # the last global layer has no rotary part
+        cfg.cp_head.d_c = type(cfg.cp_head)().d_c        # the pointer's width is the shared head's: the key stays at its default
     mine, theirs = _pair(reference, cfg)
     sd, rsd = mine.state_dict(), theirs.state_dict()
     assert list(sd) == list(rsd) and all(torch.equal(sd[k], rsd[k]) for k in sd) and list(sd)[-1].startswith("cp_head.")
@@ -843,7 +848,7 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
     assert (a - b).abs().max() < 1e-10 and (a.exp().sum(-1) - 1).abs().max() < 1e-9
     oa, ob = mine(tok, doc, return_hidden=True), theirs(tok, doc, return_hidden=True)
     ha, hb, pa, pb = oa.hidden_aux, ob.hidden_aux, oa.cp_pointer, ob.cp_pointer
-    assert (pa is None) == (keys.get("pointer_input") != "mix")
+    assert (pa is None) == (keys.get("pointer_input") not in ("mix", "shared"))
     ta, tb = CP.terms(mine.cp_head, ha, tok, tgt, doc, pointer=pa), RCP.cp_terms(theirs.cp_head, hb, tok, tgt, doc, pointer=pb)
     tn = ta if keys.get("combine") == "or" else CP.terms_naive(mine.cp_head, ha, tok, tgt, doc, pointer=pa)
     for x, y, z in zip(ta, tb, tn):
@@ -879,7 +884,7 @@ def test_copy_paste_head_equals_the_reference(reference, base, keys):
 
 
 def test_copy_paste_head_is_refused_by_name_where_it_is_not_built():
-    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "pointer_input"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.combine", "or", "combine"), ("cp_head.combine", "xor", "combine"),
+    for key, value, match in (("cp_head.pointer_input", "mix", "block_entry"), ("cp_head.pointer_input", "shared", "shared"), ("cp_head.shared_head", 2, "shared_head"), ("cp_head.n_heads", 2, "n_heads"), ("cp_head.combine", "or", "combine"), ("cp_head.combine", "xor", "combine"),
                               ("cp_head.trunk_copy", "all", "trunk_copy"), ("cp_head.train_mode", "addon", "train_mode"), ("cp_head.window", -1, "window"), ("cp_head.kernel", "fused", "kernel"),
                               ("cp_head.init", "zeros", "init"), ("cp_head.d_c", 0, "d_c"), ("loop.recur_layers", "[2, 6]", "one pass"),
                               ("encoder.gdn_ccr_spacing", 8, "gdn_ccr_spacing"), ("encoder.attn_res", "ldm", "attn_res")):

@@ -1207,3 +1207,23 @@ def test_add_on_copy_paste_head_leaves_the_trunk_training_as_the_plain_model(tmp
     worst = max(float((ours[k] - v).abs().max()) for k, v in theirs.items())
     assert worst < 1e-6, worst
     assert all(not torch.equal(p, head0[n]) for n, p in t.model.named_parameters() if n in ("cp_head.w_q", "cp_head.w_copy", "cp_head.k_sink"))
+
+
+def test_copy_paste_pointer_on_a_shared_attention_head_trains(tmp_path):
+    """cp_head.pointer_input shared through the trainer: no W_Q / W_K, the head and the trunk train; refused with activation checkpointing."""
+    cfg = tiny_train_config(steps=2)
+    cfg.model = C.tiny_full_config()
+    cfg.model.encoder.gdn_write_variant, cfg.model.encoder.gdn_write_mix, cfg.model.encoder.nope_global_layers = "none", "none", (2,)
+    h = cfg.model.cp_head
+    h.enabled, h.qk_norm, h.pointer_input, h.shared_head, cfg.head_impl, cfg.log_every = True, True, "shared", 1, "chunked", 1
+    t = Trainer(copy.deepcopy(cfg), tmp_path / "s")
+    names = [n for n, _ in t.model.named_parameters() if n.startswith("cp_head.")]
+    assert names == ["cp_head.k_sink", "cp_head.w_copy", "cp_head.qk_gain"] and t.model.cp_head.k_sink.shape[0] == cfg.model.encoder.attention.head_dim
+    start = {n: p.detach().clone() for n, p in t.model.named_parameters()}
+    ms = [t.train_step() for _ in range(2)]
+    assert all(math.isfinite(m["loss"]) and 0 < m["cp_lambda"] < 1 for m in ms)
+    assert all(not torch.equal(p, start[n]) for n, p in t.model.named_parameters() if n in ("cp_head.k_sink", "cp_head.w_copy", "encoder.layers.11.mixer.q_proj.weight"))
+    bad = copy.deepcopy(cfg)
+    bad.activation_checkpoint = "layer"
+    with pytest.raises(ValueError, match="activation_checkpoint"):
+        Trainer(bad, None)
